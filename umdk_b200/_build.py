@@ -1,0 +1,172 @@
+"""In-tree native build: compiles every CUDA / C++ source of the framework into shared libraries and tools under
+``umdk_b200/_lib``. CUDA sources are compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a``).
+
+Usage: ``python -m umdk_b200._build [--force] [--verbose]`` or :func:`build_all` from Python.
+The reference project builds with CMake/Bazel plus CANN scripts (build/cam/build.sh); here one dependency-free
+driver does the same job so that the libraries sit next to the Python package that loads them.
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures as cf
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+LIB = Path(__file__).resolve().parent / "_lib"
+OBJ = ROOT / "build" / "obj"
+
+NVCC = os.environ.get("NVCC", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("CXX", "g++")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-Xptxas", "-v",
+]
+CXX_FLAGS = ["-O2", "-g", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread", "-fvisibility=hidden"]
+
+
+def _targets():
+    """name -> dict(kind, sources, includes, libs, out)."""
+    t = {}
+    cam = sorted((CSRC / "cam").glob("*.cu")) + sorted((CSRC / "cam").glob("*.cpp"))
+    t["umdk_cam"] = dict(kind="cuda_shared", sources=cam, includes=[CSRC / "cam", CSRC / "common"],
+                         libs=["-lcudart", "-lpthread", "-ldl", "-lrt"], out=LIB / "libumdk_cam.so")
+    for name, dirs, deps in [
+        ("umdk_urma", ["common", "urma"], []),
+        ("umdk_umq", ["umq"], ["umdk_urma"]),
+        ("umdk_urpc", ["urpc"], ["umdk_umq", "umdk_urma"]),
+        ("umdk_dlock", ["dlock"], ["umdk_urma"]),
+        ("umdk_usock", ["usock"], []),
+    ]:
+        srcs = []
+        for d in dirs:
+            srcs += sorted((CSRC / d).glob("*.cpp"))
+        srcs = [s for s in srcs if not s.name.endswith("_preload.cpp")]
+        if not srcs:
+            continue
+        t[name] = dict(kind="cxx_shared", sources=srcs,
+                       includes=[CSRC / "common", CSRC / "urma", CSRC / "umq", CSRC / "urpc", CSRC / "dlock",
+                                 CSRC / "usock"],
+                       libs=["-L" + str(LIB), "-Wl,-rpath,$ORIGIN"] + ["-l" + d for d in deps] +
+                            ["-lpthread", "-ldl", "-lrt"],
+                       deps=deps, out=LIB / f"lib{name}.so")
+    pre = CSRC / "usock" / "ums_preload.cpp"
+    if pre.exists():
+        t["ums_preload"] = dict(kind="cxx_shared", sources=[pre], includes=[CSRC / "usock", CSRC / "common"],
+                                libs=["-L" + str(LIB), "-Wl,-rpath,$ORIGIN", "-lumdk_usock", "-ldl", "-lpthread",
+                                      "-lrt"], deps=["umdk_usock"], out=LIB / "libums_preload.so")
+    for tool in sorted((CSRC / "tools").glob("*.cpp")):
+        t["tool_" + tool.stem] = dict(
+            kind="cxx_exe", sources=[tool],
+            includes=[CSRC / "common", CSRC / "urma", CSRC / "umq", CSRC / "urpc", CSRC / "dlock", CSRC / "usock"],
+            libs=["-L" + str(LIB), "-Wl,-rpath,$ORIGIN/..", "-lumdk_urpc", "-lumdk_umq", "-lumdk_dlock",
+                  "-lumdk_usock", "-lumdk_urma", "-lpthread", "-ldl", "-lrt"],
+            deps=["umdk_urma", "umdk_umq", "umdk_urpc", "umdk_dlock", "umdk_usock"], out=LIB / "bin" / tool.stem)
+    return t
+
+
+def _headers_digest(includes) -> str:
+    h = hashlib.sha1()
+    for inc in includes:
+        for p in sorted(Path(inc).glob("*.h")) + sorted(Path(inc).glob("*.cuh")) + sorted(Path(inc).glob("*.hpp")):
+            st = p.stat()
+            h.update(f"{p}:{st.st_mtime_ns}:{st.st_size}".encode())
+    return h.hexdigest()
+
+
+def _run(cmd, verbose, log_path=None):
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if log_path is not None:
+        Path(log_path).write_text(" ".join(map(str, cmd)) + "\n" + p.stdout)
+    if p.returncode != 0:
+        raise RuntimeError("build command failed:\n" + " ".join(map(str, cmd)) + "\n" + p.stdout)
+    if verbose and p.stdout.strip():
+        print(p.stdout)
+    return p.stdout
+
+
+def _compile_one(src: Path, tgt: dict, force: bool, verbose: bool, hdr_digest: str) -> Path:
+    obj = OBJ / (src.parent.name + "_" + src.stem + ".o")
+    stamp = obj.with_suffix(".stamp")
+    key = f"{src.stat().st_mtime_ns}:{src.stat().st_size}:{hdr_digest}"
+    if not force and obj.exists() and stamp.exists() and stamp.read_text() == key:
+        return obj
+    inc = []
+    for i in tgt["includes"]:
+        inc += ["-I", str(i)]
+    if src.suffix == ".cu":
+        cmd = [NVCC, *NVCC_FLAGS, *inc, "-c", str(src), "-o", str(obj)]
+    elif tgt["kind"] == "cuda_shared":
+        cmd = [NVCC, "-O2", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden", *inc, "-c", str(src), "-o",
+               str(obj)]
+    else:
+        cmd = [CXX, *CXX_FLAGS, *inc, "-c", str(src), "-o", str(obj)]
+    _run(cmd, verbose, log_path=obj.with_suffix(".log"))
+    stamp.write_text(key)
+    return obj
+
+
+def build_all(force: bool = False, verbose: bool = False, only=None) -> dict:
+    """Builds all targets (or those whose names are in ``only``); returns name -> output path."""
+    LIB.mkdir(parents=True, exist_ok=True)
+    (LIB / "bin").mkdir(parents=True, exist_ok=True)
+    OBJ.mkdir(parents=True, exist_ok=True)
+    targets = _targets()
+    order = ["umdk_cam", "umdk_urma", "umdk_umq", "umdk_usock", "umdk_dlock", "umdk_urpc", "ums_preload"]
+    order += [n for n in targets if n.startswith("tool_")]
+    outs = {}
+    # compile all objects of all targets in parallel first
+    jobs = {}
+    with cf.ThreadPoolExecutor(max_workers=max(2, (os.cpu_count() or 4))) as ex:
+        for name in order:
+            if name not in targets or (only and name not in only):
+                continue
+            tgt = targets[name]
+            dig = _headers_digest(tgt["includes"])
+            jobs[name] = [ex.submit(_compile_one, s, tgt, force, verbose, dig) for s in tgt["sources"]]
+        objs = {name: [f.result() for f in fs] for name, fs in jobs.items()}
+    for name in order:
+        if name not in objs:
+            continue
+        tgt = targets[name]
+        out = tgt["out"]
+        newest = max(o.stat().st_mtime_ns for o in objs[name])
+        if force or not out.exists() or out.stat().st_mtime_ns < newest:
+            if tgt["kind"] == "cuda_shared":
+                cmd = [NVCC, "-shared", "-o", str(out), *map(str, objs[name]), *tgt["libs"]]
+            elif tgt["kind"] == "cxx_shared":
+                cmd = [CXX, "-shared", "-o", str(out), *map(str, objs[name]), *tgt["libs"]]
+            else:
+                cmd = [CXX, "-o", str(out), *map(str, objs[name]), *tgt["libs"]]
+            _run(cmd, verbose)
+        outs[name] = out
+    return outs
+
+
+def ptxas_report() -> str:
+    """Concatenated ``-Xptxas -v`` output of the last CUDA compile (registers, spills, shared memory)."""
+    parts = []
+    for log in sorted(OBJ.glob("cam_*.log")):
+        parts.append(f"== {log.name}\n{log.read_text()}")
+    return "\n".join(parts)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--only", nargs="*")
+    a = ap.parse_args(argv)
+    outs = build_all(a.force, a.verbose, a.only)
+    for k, v in outs.items():
+        print(f"{k}: {v}")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
