@@ -1,0 +1,74 @@
+// Geometry and symmetric-heap layout shared by the expert-parallel (EP) dispatch/combine kernels.
+#pragma once
+#include "common.h"
+
+namespace umdk {
+
+constexpr int kMaxRanks = 32;    // one box: peers are addressed through a 32-bit rank mask
+constexpr int kMaxTopk = 16;     // same limit as the reference's prefill path (CAM API Guide: top-k <= 16)
+
+struct EpGeom {
+  int R;          // ranks in the EP group
+  int rank;       // this rank
+  int E;          // global routed experts
+  int E_local;    // experts per rank
+  int K;          // top-k
+  int H;          // hidden size (elements)
+  int cap;        // max tokens any rank sends in one call (per-source capacity of the arrival buffers)
+  int quant;      // 1: fp8 e4m3 payload with fp32 scale per 1x128 block; 0: bf16 payload
+  int row_bytes;  // payload bytes per token on the wire
+  int nscale;     // H / 128 (0 when quant == 0)
+  int meta_words; // int32 words of per-token metadata on the wire
+  int J;          // combine slots per token on the owner (max(R, K))
+};
+
+__host__ __device__ inline uint64_t align_up_u64(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+// Byte offsets inside every rank's symmetric heap. Index [h] selects the ping-pong half (epoch parity).
+struct EpNormalOffsets {
+  uint64_t notify[2];       // [R src][E_local + 4] int32
+  uint64_t notify_flag[2];  // [R] uint64
+  uint64_t data_flag[2];    // [R] uint64
+  uint64_t comb_flag[2];    // [R] uint64
+  uint64_t arr_x[2];        // [R][cap][row_bytes]
+  uint64_t arr_scale[2];    // [R][cap][nscale] fp32
+  uint64_t arr_meta[2];     // [R][cap][meta_words] int32
+  uint64_t comb_buf[2];     // [cap][J][H] bf16
+  uint64_t total;
+};
+
+__host__ __device__ inline int ep_meta_words(int K) { return ((2 * K + 2) + 3) / 4 * 4; }
+__host__ __device__ inline int ep_notify_words(int E_local) { return E_local + 4; }
+
+__host__ __device__ inline EpNormalOffsets ep_normal_offsets(const EpGeom& g) {
+  EpNormalOffsets o;
+  uint64_t off = 0;
+  for (int h = 0; h < 2; ++h) {
+    o.notify[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * ep_notify_words(g.E_local) * 4, 256);
+    o.notify_flag[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * 8, 256);
+    o.data_flag[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * 8, 256);
+    o.comb_flag[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * 8, 256);
+  }
+  for (int h = 0; h < 2; ++h) {
+    o.arr_x[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * g.cap * g.row_bytes, 256);
+    o.arr_scale[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * g.cap * (g.nscale > 0 ? g.nscale : 1) * 4, 256);
+    o.arr_meta[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * g.cap * g.meta_words * 4, 256);
+    o.comb_buf[h] = off;
+    off = align_up_u64(off + (uint64_t)g.cap * g.J * g.H * 2, 256);
+  }
+  o.total = off;
+  return o;
+}
+
+struct PeerTable {
+  uint8_t* base[kMaxRanks];
+};
+
+}  // namespace umdk

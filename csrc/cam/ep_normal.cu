@@ -1,0 +1,758 @@
+// Normal-mode (prefill / high-throughput) expert-parallel kernels: layout, dispatch, combine.
+//
+// What the reference does (Ascend, src/cam/comm_operator/ascend_kernels/):
+//   dispatch_layout/op_kernel/dispatch_layout.h:112-165   per-expert histogram + per-(token,k) bucket slot
+//   notify_dispatch/op_kernel/notify_dispatch.h:91-110     all-to-all of per-expert counts, prefix sums
+//   moe_dispatch_normal/op_kernel/moe_dispatch_normal.h:346-591  per-(token,k) record written to the sender's own
+//       window, flag per (expert, srcRank), receiver pulls records
+//   moe_combine_normal/op_kernel/moe_combine_normal.h:224-377    push rows to the owner's (t*K+k) slot, weighted sum
+//
+// What this file does instead (B200, NVLink 5 through NVSwitch, peer pointers from the symmetric heap):
+//   * ep_layout: one launch; stable bucket positions for (token,k) per expert AND per destination rank.
+//   * ep_dispatch: ONE kernel = notify + quantise + push + expand. Each token crosses NVLink once per destination
+//     rank (the reference sends it once per expert), already quantised to fp8 e4m3 with one fp32 scale per 1x128
+//     block, using 16-byte stores into the receiver's arrival buffer; the receiver then expands arrivals into the
+//     expert-major / source-rank-minor slab that the grouped GEMM consumes (same order as the reference's
+//     recv_x: index = localExpert * R + srcRank, notify_dispatch.h:264-412).
+//   * ep_combine: expert side pre-reduces the rows of one token on this rank (fp32), pushes one bf16 row per
+//     (token, rank) to the owner, owner sums over ranks. A row-per-(token,k) mode reproduces the reference's
+//     stateless moe_combine_prefill contract.
+// Flags are epoch-tagged and buffers are double-buffered on epoch parity, so no barrier is needed between calls.
+#include "ep_common.cuh"
+#include "ptx.cuh"
+#include "sync.cuh"
+
+namespace umdk {
+namespace {
+
+constexpr int kLayoutWarps = 8;
+constexpr int kEpThreads = 512;
+constexpr int kEpWarps = kEpThreads / 32;
+
+// ------------------------------------------------------------------------------------------------------------
+// Layout
+// ------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kLayoutWarps * 32)
+ep_layout_kernel(const int64_t* __restrict__ topk_idx, int T, int K, int E, int R, int* __restrict__ num_per_expert,
+                 int* __restrict__ num_per_rank, uint8_t* __restrict__ in_rank, int* __restrict__ send_idx,
+                 int* __restrict__ rank_slot, int* __restrict__ scratch, uint32_t* bar, int* status) {
+  extern __shared__ int sm_layout[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cols = E + R;
+  const int E_local = E / R;
+  int* hist = sm_layout + warp * cols;
+  int* stage = sm_layout + kLayoutWarps * cols + warp * 32 * kMaxTopk;
+  const int num_chunks = (T + 31) / 32;
+  const int gwarp = blockIdx.x * kLayoutWarps + warp;
+  const int total_warps = gridDim.x * kLayoutWarps;
+
+  // Phase A: per-chunk histograms and positions inside the chunk (stable in token order).
+  for (int c = gwarp; c < num_chunks; c += total_warps) {
+    for (int i = lane; i < cols; i += 32) hist[i] = 0;
+    const int t0 = c * 32;
+    const int nt = min(32, T - t0);
+    for (int i = lane; i < nt * K; i += 32) {
+      long long e = topk_idx[(size_t)t0 * K + i];
+      stage[i] = (e >= 0 && e < E) ? (int)e : -1;
+    }
+    __syncwarp();
+    for (int i = 0; i < nt; ++i) {
+      const int t = t0 + i;
+      const int e = lane < K ? stage[i * K + lane] : -1;
+      const uint32_t rm = __reduce_or_sync(0xffffffffu, e >= 0 ? (1u << (e / E_local)) : 0u);
+      if (lane < K) send_idx[(size_t)t * K + lane] = e >= 0 ? atomicAdd(&hist[e], 1) : -1;
+      if (lane < R) {
+        const bool in = (rm >> lane) & 1u;
+        rank_slot[(size_t)t * R + lane] = in ? atomicAdd(&hist[E + lane], 1) : -1;
+        in_rank[(size_t)t * R + lane] = in ? 1 : 0;
+      }
+      __syncwarp();
+    }
+    for (int i = lane; i < cols; i += 32) scratch[(size_t)c * cols + i] = hist[i];
+    __syncwarp();
+  }
+  if (!grid_barrier(bar, gridDim.x)) {
+    umdk_set_status(status, UMDK_ERR_TIMEOUT, UMDK_PH_BARRIER, 0, 0);
+    return;
+  }
+  // Phase B: exclusive scan over chunks, one thread per column.
+  for (int col = blockIdx.x * blockDim.x + threadIdx.x; col < cols; col += gridDim.x * blockDim.x) {
+    int base = 0;
+    for (int c = 0; c < num_chunks; ++c) {
+      const int v = scratch[(size_t)c * cols + col];
+      scratch[(size_t)c * cols + col] = base;
+      base += v;
+    }
+    if (col < E) num_per_expert[col] = base;
+    else num_per_rank[col - E] = base;
+  }
+  if (!grid_barrier(bar, gridDim.x)) {
+    umdk_set_status(status, UMDK_ERR_TIMEOUT, UMDK_PH_BARRIER, 1, 0);
+    return;
+  }
+  // Phase C: add the chunk bases.
+  for (int c = gwarp; c < num_chunks; c += total_warps) {
+    const int t0 = c * 32;
+    const int nt = min(32, T - t0);
+    const int* base = scratch + (size_t)c * cols;
+    for (int i = lane; i < nt * K; i += 32) {
+      long long e = topk_idx[(size_t)t0 * K + i];
+      if (e >= 0 && e < E) send_idx[(size_t)t0 * K + i] += base[e];
+    }
+    for (int i = lane; i < nt * R; i += 32) {
+      const int v = rank_slot[(size_t)t0 * R + i];
+      if (v >= 0) rank_slot[(size_t)t0 * R + i] = v + base[E + (i % R)];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Dispatch
+// ------------------------------------------------------------------------------------------------------------
+struct DispatchArgs {
+  EpGeom g;
+  EpNormalOffsets off;
+  PeerTable peers;
+  // inputs on this rank
+  const __nv_bfloat16* x;      // [T, H]
+  const int64_t* topk_idx;     // [T, K]
+  const float* topk_w;         // [T, K] (may be null)
+  const int* send_idx;         // [T, K] from layout
+  const int* rank_slot;        // [T, R] from layout
+  const int* num_per_expert;   // [E]
+  const int* num_per_rank;     // [R]
+  int T;
+  // outputs on this rank
+  uint8_t* recv_x;             // [n_cap, row_bytes] expert-major, then source rank
+  float* recv_scales;          // [n_cap, nscale]
+  int* expand_idx;             // [n_cap, 3] (srcRank, srcToken, k)
+  int* recv_count;             // [E_local * R] inclusive prefix, index = le * R + src
+  int64_t* recv_per_expert;    // [E_local]
+  int* recv_meta;              // [a_cap, 2K+2] per arrival: src, srcToken, rows[K], weight bits[K]
+  int* counts_dev;             // [4]: expanded rows N, arrivals A, max tokens from one source, 0
+  volatile int* counts_host;   // same 4 ints in mapped pinned host memory + [4] = epoch stamp (may be null)
+  int n_cap, a_cap;
+  // control
+  uint32_t* ctrl;              // [0] epoch, [1] send-done counter, [2] recv-done counter
+  int* status;
+  int phase_mask;              // bit0: notify + send, bit1: receive + expand (both for normal use)
+};
+
+__device__ __forceinline__ uint32_t pack_fp8x4(float a, float b, float c, float d) {
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
+__device__ __forceinline__ void bf16x8_to_float(const int4& v, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+__global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const DispatchArgs a) {
+  const EpGeom& g = a.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_cnt[1024 + 64];   // counts [le][src] -> exclusive offsets; tail: per-source arrivals
+  __shared__ int s_ok;
+  __shared__ int s_slot[kEpWarps][kMaxRanks];  // per-warp staging: destination slots of the current token
+  __shared__ int s_row[kEpWarps][kMaxTopk];    // per-warp staging: expanded rows of the current arrival
+  if (threadIdx.x == 0) {
+    s_epoch = a.ctrl[0];
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int h = epoch & 1;
+  const uint64_t tag = (uint64_t)epoch + 1;
+  const int nw = ep_notify_words(g.E_local);
+
+  if (a.phase_mask & 1) {
+    // ---- notify: CTA 0, one warp per destination rank (looping) ----
+    if (blockIdx.x == 0) {
+      for (int d = warp; d < g.R; d += kEpWarps) {
+        int* dst = reinterpret_cast<int*>(a.peers.base[d] + a.off.notify[h]) + (size_t)g.rank * nw;
+        for (int i = lane; i < g.E_local; i += 32) dst[i] = a.num_per_expert[d * g.E_local + i];
+        if (lane == 0) dst[g.E_local] = a.num_per_rank[d];
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[d] + a.off.notify_flag[h]) + g.rank, tag);
+        }
+      }
+    }
+    // ---- send: one warp per token ----
+    for (int t = blockIdx.x * kEpWarps + warp; t < a.T; t += gridDim.x * kEpWarps) {
+      // destination mask and slots
+      int my_slot = -1;
+      if (lane < g.R) my_slot = a.rank_slot[(size_t)t * g.R + lane];
+      const uint32_t dmask = __ballot_sync(0xffffffffu, my_slot >= 0);
+      if (dmask == 0) continue;
+      __syncwarp();
+      if (lane < g.R) s_slot[warp][lane] = my_slot;
+      __syncwarp();
+      // metadata: lanes 0..K-1 hold (expert, bucket position, weight)
+      int e = -1, sidx = -1;
+      float w = 0.f;
+      if (lane < g.K) {
+        const long long ee = a.topk_idx[(size_t)t * g.K + lane];
+        e = (ee >= 0 && ee < g.E) ? (int)ee : -1;
+        sidx = a.send_idx[(size_t)t * g.K + lane];
+        w = a.topk_w ? a.topk_w[(size_t)t * g.K + lane] : 1.f;
+      }
+      for (uint32_t m = dmask; m; m &= m - 1) {
+        const int d = __ffs(m) - 1;
+        const int slot = s_slot[warp][d];
+        if (slot >= g.cap) {
+          umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, d, slot);
+          continue;
+        }
+        int* meta = reinterpret_cast<int*>(a.peers.base[d] + a.off.arr_meta[h]) +
+                    ((size_t)g.rank * g.cap + slot) * g.meta_words;
+        if (lane < g.K) {
+          const bool mine = e >= 0 && (e / g.E_local) == d;
+          meta[lane] = mine ? (((e % g.E_local) << 16) | (sidx & 0xffff)) : -1;
+          meta[g.K + lane] = __float_as_int(w);
+        }
+        if (lane == 0) meta[2 * g.K] = t;
+      }
+      const int4* xrow = reinterpret_cast<const int4*>(a.x + (size_t)t * g.H);
+      if (g.quant) {
+        // each lane: 16 elements per step; 8 lanes share one 1x128 block
+        const int nblk = g.H / 128;
+        for (int b0 = 0; b0 < nblk; b0 += 4) {
+          const int blk = b0 + (lane >> 3);
+          const bool active = blk < nblk;
+          float f[16];
+          if (active) {
+            const int4 v0 = __ldg(xrow + blk * 16 + (lane & 7) * 2);
+            const int4 v1 = __ldg(xrow + blk * 16 + (lane & 7) * 2 + 1);
+            bf16x8_to_float(v0, f);
+            bf16x8_to_float(v1, f + 8);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) f[i] = 0.f;
+          }
+          float amax = 0.f;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+          amax = fmaxf(amax, 1e-4f);
+          const float scale = amax * (1.f / 448.f);
+          const float inv = 448.f / amax;
+          int4 q;
+          q.x = pack_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+          q.y = pack_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+          q.z = pack_fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+          q.w = pack_fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+          if (active) {
+            for (uint32_t m = dmask; m; m &= m - 1) {
+              const int d = __ffs(m) - 1;
+              const int slot = s_slot[warp][d];
+              if (slot >= g.cap) continue;
+              const size_t rec = (size_t)g.rank * g.cap + slot;
+              uint8_t* px = a.peers.base[d] + a.off.arr_x[h] + rec * g.row_bytes;
+              st_na_v4(px + blk * 128 + (lane & 7) * 16, q);
+              if ((lane & 7) == 0) {
+                float* ps = reinterpret_cast<float*>(a.peers.base[d] + a.off.arr_scale[h]) + rec * g.nscale;
+                ps[blk] = scale;
+              }
+            }
+          }
+        }
+      } else {
+        const int nvec = g.H / 8;  // 16-byte vectors per row
+        for (int i = lane; i < nvec; i += 32) {
+          const int4 v = __ldg(xrow + i);
+          for (uint32_t m = dmask; m; m &= m - 1) {
+            const int d = __ffs(m) - 1;
+            const int slot = s_slot[warp][d];
+            if (slot >= g.cap) continue;
+            uint8_t* px = a.peers.base[d] + a.off.arr_x[h] + ((size_t)g.rank * g.cap + slot) * g.row_bytes;
+            st_na_v4(px + (size_t)i * 16, v);
+          }
+        }
+      }
+    }
+    // ---- publish: the last CTA to finish sending raises this rank's data flag on every peer ----
+    if (cta_done_is_last(&a.ctrl[1], gridDim.x)) {
+      if (threadIdx.x < g.R) {
+        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.off.data_flag[h]) + g.rank, tag);
+      }
+    }
+  }
+
+  if (!(a.phase_mask & 2)) return;
+
+  // ---- receive: wait for every source's counts, build offsets ----
+  uint8_t* self = a.peers.base[g.rank];
+  if (threadIdx.x < g.R) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.notify_flag[h]) + threadIdx.x;
+    if (!wait_flag_ge_sys(f, tag)) {
+      umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_COUNT, threadIdx.x, (int)epoch);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int* notify = reinterpret_cast<const int*>(self + a.off.notify[h]);
+  const int nle = g.E_local * g.R;
+  int* s_arr = s_cnt + 1024;  // [R] arrivals per source, then [R] exclusive arrival base
+  for (int i = threadIdx.x; i < nle; i += blockDim.x) {
+    const int le = i / g.R, src = i % g.R;
+    s_cnt[i] = notify[(size_t)src * nw + le];
+  }
+  if (threadIdx.x < g.R) s_arr[threadIdx.x] = notify[(size_t)threadIdx.x * nw + g.E_local];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0, amax_src = 0, abase = 0;
+    for (int i = 0; i < nle; ++i) {
+      const int c = s_cnt[i];
+      s_cnt[i] = run;  // exclusive offset of (le, src)
+      run += c;
+      if (blockIdx.x == 0) {
+        a.recv_count[i] = run;  // inclusive prefix, as the reference returns it
+        if ((i % g.R) == g.R - 1) {
+          const int le = i / g.R;
+          a.recv_per_expert[le] = (int64_t)(run - s_cnt[le * g.R]);
+        }
+      }
+    }
+    for (int r = 0; r < g.R; ++r) {
+      const int c = s_arr[r];
+      amax_src = max(amax_src, c);
+      s_arr[g.R + r] = abase;
+      abase += c;
+    }
+    s_cnt[1023] = run;
+    if (blockIdx.x == 0) {
+      a.counts_dev[0] = run;
+      a.counts_dev[1] = abase;
+      a.counts_dev[2] = amax_src;
+      if (a.counts_host) {
+        a.counts_host[0] = run;
+        a.counts_host[1] = abase;
+        a.counts_host[2] = amax_src;
+        __threadfence_system();
+        a.counts_host[4] = (int)tag;
+      }
+      if (run > a.n_cap || abase > a.a_cap) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_COUNT, run, abase);
+    }
+  }
+  __syncthreads();
+
+  // ---- expand: arrivals -> expert-major rows ----
+  const int mw2 = 2 * g.K + 2;
+  for (int i = 0; i < g.R; ++i) {
+    const int src = (g.rank + i) % g.R;  // own tokens first (they are already here)
+    if (threadIdx.x == 0) {
+      const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.data_flag[h]) + src;
+      if (!wait_flag_ge_sys(f, tag)) {
+        umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_DATA, src, (int)epoch);
+        s_ok = 0;
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const int n_from = min(s_arr[src], g.cap);
+    const int abase = s_arr[g.R + src];
+    for (int p = blockIdx.x * kEpWarps + warp; p < n_from; p += gridDim.x * kEpWarps) {
+      const size_t rec = (size_t)src * g.cap + p;
+      const int* meta = reinterpret_cast<const int*>(self + a.off.arr_meta[h]) + rec * g.meta_words;
+      int code = -1, wbits = 0;
+      if (lane < g.K) {
+        code = meta[lane];
+        wbits = meta[g.K + lane];
+      }
+      const int src_tok = meta[2 * g.K];
+      int row = -1;
+      if (code >= 0) {
+        const int le = code >> 16, pos = code & 0xffff;
+        row = s_cnt[le * g.R + src] + pos;
+        if (row >= a.n_cap) {
+          umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, src, row);
+          row = -1;
+        }
+      }
+      if (abase + p < a.a_cap) {
+        int* rm = a.recv_meta + (size_t)(abase + p) * mw2;
+        if (lane == 0) {
+          rm[0] = src;
+          rm[1] = src_tok;
+        }
+        if (lane < g.K) {
+          rm[2 + lane] = row;
+          rm[2 + g.K + lane] = wbits;
+        }
+      }
+      if (row >= 0) {
+        a.expand_idx[(size_t)row * 3 + 0] = src;
+        a.expand_idx[(size_t)row * 3 + 1] = src_tok;
+        a.expand_idx[(size_t)row * 3 + 2] = lane;
+      }
+      const uint32_t kmask = __ballot_sync(0xffffffffu, row >= 0);
+      __syncwarp();
+      if (lane < g.K) s_row[warp][lane] = row;
+      __syncwarp();
+      const int4* px = reinterpret_cast<const int4*>(self + a.off.arr_x[h] + rec * g.row_bytes);
+      const int nvec = g.row_bytes / 16;
+      for (int v = lane; v < nvec; v += 32) {
+        const int4 val = px[v];
+        for (uint32_t m = kmask; m; m &= m - 1) {
+          const int r2 = s_row[warp][__ffs(m) - 1];
+          reinterpret_cast<int4*>(a.recv_x + (size_t)r2 * g.row_bytes)[v] = val;
+        }
+      }
+      if (g.quant) {
+        const float* ps = reinterpret_cast<const float*>(self + a.off.arr_scale[h]) + rec * g.nscale;
+        for (int v = lane; v < g.nscale; v += 32) {
+          const float val = ps[v];
+          for (uint32_t m = kmask; m; m &= m - 1) {
+            const int r2 = s_row[warp][__ffs(m) - 1];
+            a.recv_scales[(size_t)r2 * g.nscale + v] = val;
+          }
+        }
+      }
+    }
+  }
+  // ---- epoch advance by the last CTA ----
+  if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
+    if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Combine
+// ------------------------------------------------------------------------------------------------------------
+struct CombineArgs {
+  EpGeom g;
+  EpNormalOffsets off;
+  PeerTable peers;
+  const __nv_bfloat16* y;     // [N, H] expert outputs in the dispatch row order
+  // mode 0 (per-rank pre-reduction): arrival metadata from dispatch
+  const int* recv_meta;       // [A, 2K+2]
+  const int* counts_dev;      // [0] = N, [1] = A
+  // mode 1 (row per (token,k), reference contract): (srcRank, srcToken, k) per row
+  const int* src_idx;         // [N, 3]
+  int n_rows;                 // mode 1: number of rows; mode 0: ignored
+  // owner side
+  const uint8_t* in_rank;     // [T, R] (mode 0)
+  const int64_t* topk_idx;    // [T, K] (mode 1)
+  const float* topk_w;        // [T, K] (mode 1)
+  __nv_bfloat16* out;         // [T, H]
+  int T;
+  int mode;
+  int apply_weights;          // mode 0: multiply rows by the weights shipped at dispatch time
+  uint32_t* ctrl;             // [3] epoch, [4] send-done, [5] recv-done
+  int* status;
+  int phase_mask;
+};
+
+__global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const CombineArgs a) {
+  const EpGeom& g = a.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  __shared__ int s_row[kEpWarps][kMaxRanks];
+  __shared__ float s_coef[kEpWarps][kMaxRanks];
+  if (threadIdx.x == 0) {
+    s_epoch = a.ctrl[3];
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int h = epoch & 1;
+  const uint64_t tag = (uint64_t)epoch + 1;
+  const int nvec = g.H / 8;
+  const int mw2 = 2 * g.K + 2;
+
+  if (a.phase_mask & 1) {
+    const int items = a.mode == 0 ? a.counts_dev[1] : a.n_rows;
+    for (int it = blockIdx.x * kEpWarps + warp; it < items; it += gridDim.x * kEpWarps) {
+      int dst_rank, dst_tok, slot_j;
+      int row = -1;
+      float w = 1.f;
+      if (a.mode == 0) {
+        const int* rm = a.recv_meta + (size_t)it * mw2;
+        dst_rank = rm[0];
+        dst_tok = rm[1];
+        slot_j = g.rank;
+        if (lane < g.K) {
+          row = rm[2 + lane];
+          if (a.apply_weights) w = __int_as_float(rm[2 + g.K + lane]);
+        }
+      } else {
+        dst_rank = a.src_idx[(size_t)it * 3 + 0];
+        dst_tok = a.src_idx[(size_t)it * 3 + 1];
+        slot_j = a.src_idx[(size_t)it * 3 + 2];
+        if (lane == 0) row = it;
+      }
+      if (dst_rank < 0 || dst_rank >= g.R || dst_tok < 0 || dst_tok >= g.cap || slot_j < 0 || slot_j >= g.J) {
+        umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_COMBINE_DATA, dst_rank, dst_tok);
+        continue;
+      }
+      const uint32_t kmask = __ballot_sync(0xffffffffu, row >= 0);
+      __syncwarp();
+      s_row[warp][lane] = row;
+      s_coef[warp][lane] = w;
+      __syncwarp();
+      int4* dst = reinterpret_cast<int4*>(a.peers.base[dst_rank] + a.off.comb_buf[h] +
+                                          ((size_t)dst_tok * g.J + slot_j) * g.H * 2);
+      for (int v0 = 0; v0 < nvec; v0 += 32) {
+        const int v = v0 + lane;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (uint32_t m = kmask; m; m &= m - 1) {
+          const int k = __ffs(m) - 1;
+          const int r2 = s_row[warp][k];
+          const float w2 = s_coef[warp][k];
+          if (v < nvec) {
+            const int4 val = __ldg(reinterpret_cast<const int4*>(a.y + (size_t)r2 * g.H) + v);
+            float f[8];
+            bf16x8_to_float(val, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(w2, f[i], acc[i]);
+          }
+        }
+        if (v < nvec) {
+          int4 o;
+          __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+          st_na_v4(dst + v, o);
+        }
+      }
+    }
+    if (cta_done_is_last(&a.ctrl[4], gridDim.x)) {
+      if (threadIdx.x < g.R) {
+        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.off.comb_flag[h]) + g.rank, tag);
+      }
+    }
+  }
+  if (!(a.phase_mask & 2)) return;
+
+  uint8_t* self = a.peers.base[g.rank];
+  if (threadIdx.x < g.R) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.comb_flag[h]) + threadIdx.x;
+    if (!wait_flag_ge_sys(f, tag)) {
+      umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_COMBINE_DATA, threadIdx.x, (int)epoch);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int J = a.mode == 0 ? g.R : g.K;
+  for (int t = blockIdx.x * kEpWarps + warp; t < a.T; t += gridDim.x * kEpWarps) {
+    float coef = 0.f;
+    if (lane < J) {
+      if (a.mode == 0) coef = a.in_rank[(size_t)t * g.R + lane] ? 1.f : 0.f;
+      else coef = a.topk_idx[(size_t)t * g.K + lane] >= 0 ? a.topk_w[(size_t)t * g.K + lane] : 0.f;
+    }
+    const bool used = lane < J && (a.mode == 0 ? coef != 0.f : a.topk_idx[(size_t)t * g.K + lane] >= 0);
+    const uint32_t jmask = __ballot_sync(0xffffffffu, used);
+    __syncwarp();
+    s_coef[warp][lane] = coef;
+    __syncwarp();
+    const int4* src = reinterpret_cast<const int4*>(self + a.off.comb_buf[h] + (size_t)t * g.J * g.H * 2);
+    for (int v0 = 0; v0 < nvec; v0 += 32) {
+      const int v = v0 + lane;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (uint32_t m = jmask; m; m &= m - 1) {
+        const int j = __ffs(m) - 1;
+        const float c = s_coef[warp][j];
+        if (v < nvec) {
+          const int4 val = src[(size_t)j * nvec + v];
+          float f[8];
+          bf16x8_to_float(val, f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = fmaf(c, f[i], acc[i]);
+        }
+      }
+      if (v < nvec) {
+        int4 o;
+        __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        reinterpret_cast<int4*>(a.out + (size_t)t * g.H)[v] = o;
+      }
+    }
+  }
+  if (cta_done_is_last(&a.ctrl[5], gridDim.x)) {
+    if (threadIdx.x == 0) a.ctrl[3] = epoch + 1;
+  }
+}
+
+}  // namespace
+}  // namespace umdk
+
+using namespace umdk;
+
+static int fill_geom(EpGeom* g, int R, int rank, int E, int K, int H, int cap, int quant) {
+  if (R < 1 || R > kMaxRanks || rank < 0 || rank >= R || E < R || (E % R) || K < 1 || K > kMaxTopk || H < 128 ||
+      (H % 128) || cap < 1 || cap > 65535 || (E / R) * R > 1024 - 1)
+    return -UMDK_ERR_BAD_ARG;
+  g->R = R;
+  g->rank = rank;
+  g->E = E;
+  g->E_local = E / R;
+  g->K = K;
+  g->H = H;
+  g->cap = cap;
+  g->quant = quant;
+  g->row_bytes = quant ? H : 2 * H;
+  g->nscale = quant ? H / 128 : 0;
+  g->meta_words = ep_meta_words(K);
+  g->J = R > K ? R : K;
+  return 0;
+}
+
+// Bytes of symmetric heap each rank needs for normal-mode dispatch + combine with this geometry.
+// Heap layout is sized for the larger payload format (bf16 rows, plus room for scales) so that quantised and
+// unquantised calls share one heap.
+static EpGeom layout_geom(EpGeom g) {
+  g.quant = 0;
+  g.row_bytes = 2 * g.H;
+  g.nscale = g.H / 128;
+  return g;
+}
+
+UMDK_API long long umdk_ep_normal_heap_bytes(int R, int E, int K, int H, int cap) {
+  EpGeom g;
+  if (fill_geom(&g, R, 0, E, K, H, cap, 0)) return -1;
+  return (long long)ep_normal_offsets(layout_geom(g)).total;
+}
+
+// scratch: int32[(ceil(T/32)) * (E + R)]; bar: uint32[2] zero-initialised once.
+UMDK_API int umdk_ep_layout(const int64_t* topk_idx, int T, int K, int E, int R, int* num_per_expert,
+                            int* num_per_rank, uint8_t* in_rank, int* send_idx, int* rank_slot, int* scratch,
+                            uint32_t* bar, int* status, void* stream) {
+  if (T < 0 || K < 1 || K > kMaxTopk || R < 1 || R > kMaxRanks || E < R || (E % R)) return -UMDK_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    UMDK_CUDA_CHECK(cudaMemsetAsync(num_per_expert, 0, sizeof(int) * E, s));
+    UMDK_CUDA_CHECK(cudaMemsetAsync(num_per_rank, 0, sizeof(int) * R, s));
+    return 0;
+  }
+  const int chunks = (T + 31) / 32;
+  int grid = (chunks + kLayoutWarps - 1) / kLayoutWarps;
+  if (grid > sm_count()) grid = sm_count();
+  const size_t smem = sizeof(int) * (size_t)kLayoutWarps * ((E + R) + 32 * kMaxTopk);
+  if (smem > 48 * 1024) {
+    UMDK_CUDA_CHECK(cudaFuncSetAttribute(ep_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  ep_layout_kernel<<<grid, kLayoutWarps * 32, smem, s>>>(topk_idx, T, K, E, R, num_per_expert, num_per_rank, in_rank,
+                                                         send_idx, rank_slot, scratch, bar, status);
+  UMDK_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+struct UmdkEpDispatchParams {
+  int R, rank, E, K, H, cap, quant, T;
+  int n_cap, a_cap, num_ctas, phase_mask;
+  void* peers[kMaxRanks];
+  const void* x;
+  const int64_t* topk_idx;
+  const float* topk_w;
+  const int* send_idx;
+  const int* rank_slot;
+  const int* num_per_expert;
+  const int* num_per_rank;
+  void* recv_x;
+  float* recv_scales;
+  int* expand_idx;
+  int* recv_count;
+  int64_t* recv_per_expert;
+  int* recv_meta;
+  int* counts_dev;
+  int* counts_host;
+  uint32_t* ctrl;
+  int* status;
+};
+
+UMDK_API int umdk_ep_dispatch(const UmdkEpDispatchParams* p, void* stream) {
+  DispatchArgs a;
+  if (int rc = fill_geom(&a.g, p->R, p->rank, p->E, p->K, p->H, p->cap, p->quant)) return rc;
+  if (p->T > p->cap) return -UMDK_ERR_BAD_ARG;
+  a.off = ep_normal_offsets(layout_geom(a.g));
+  for (int i = 0; i < p->R; ++i) a.peers.base[i] = static_cast<uint8_t*>(p->peers[i]);
+  a.x = static_cast<const __nv_bfloat16*>(p->x);
+  a.topk_idx = p->topk_idx;
+  a.topk_w = p->topk_w;
+  a.send_idx = p->send_idx;
+  a.rank_slot = p->rank_slot;
+  a.num_per_expert = p->num_per_expert;
+  a.num_per_rank = p->num_per_rank;
+  a.T = p->T;
+  a.recv_x = static_cast<uint8_t*>(p->recv_x);
+  a.recv_scales = p->recv_scales;
+  a.expand_idx = p->expand_idx;
+  a.recv_count = p->recv_count;
+  a.recv_per_expert = p->recv_per_expert;
+  a.recv_meta = p->recv_meta;
+  a.counts_dev = p->counts_dev;
+  a.counts_host = p->counts_host;
+  a.n_cap = p->n_cap;
+  a.a_cap = p->a_cap;
+  a.ctrl = p->ctrl;
+  a.status = p->status;
+  a.phase_mask = p->phase_mask ? p->phase_mask : 3;
+  int grid = p->num_ctas > 0 ? p->num_ctas : sm_count();
+  if (grid > sm_count()) grid = sm_count();  // CTAs wait on peers: the whole grid must be resident
+  ep_dispatch_kernel<<<grid, kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  UMDK_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+struct UmdkEpCombineParams {
+  int R, rank, E, K, H, cap, T;
+  int mode, apply_weights, n_rows, num_ctas, phase_mask;
+  void* peers[kMaxRanks];
+  const void* y;
+  const int* recv_meta;
+  const int* counts_dev;
+  const int* src_idx;
+  const uint8_t* in_rank;
+  const int64_t* topk_idx;
+  const float* topk_w;
+  void* out;
+  uint32_t* ctrl;
+  int* status;
+};
+
+UMDK_API int umdk_ep_combine(const UmdkEpCombineParams* p, void* stream) {
+  CombineArgs a;
+  if (int rc = fill_geom(&a.g, p->R, p->rank, p->E, p->K, p->H, p->cap, 0)) return rc;
+  a.off = ep_normal_offsets(layout_geom(a.g));
+  for (int i = 0; i < p->R; ++i) a.peers.base[i] = static_cast<uint8_t*>(p->peers[i]);
+  a.y = static_cast<const __nv_bfloat16*>(p->y);
+  a.recv_meta = p->recv_meta;
+  a.counts_dev = p->counts_dev;
+  a.src_idx = p->src_idx;
+  a.n_rows = p->n_rows;
+  a.in_rank = p->in_rank;
+  a.topk_idx = p->topk_idx;
+  a.topk_w = p->topk_w;
+  a.out = static_cast<__nv_bfloat16*>(p->out);
+  a.T = p->T;
+  a.mode = p->mode;
+  a.apply_weights = p->apply_weights;
+  a.ctrl = p->ctrl;
+  a.status = p->status;
+  a.phase_mask = p->phase_mask ? p->phase_mask : 3;
+  if (p->T > p->cap) return -UMDK_ERR_BAD_ARG;
+  int grid = p->num_ctas > 0 ? p->num_ctas : sm_count();
+  if (grid > sm_count()) grid = sm_count();
+  ep_combine_kernel<<<grid, kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  UMDK_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,252 @@
+"""Normal-mode expert-parallel dispatch / combine on the GPU (hand-written sm_100a kernels in csrc/cam/ep_normal.cu).
+
+``EpNormal`` owns the per-geometry state one rank needs: its slice of the symmetric heap, the control words
+(epochs, arrival counters), the layout scratch and the status record that kernels fill when a bounded wait runs
+out. The public, user-facing surface is :class:`umdk_b200.buffer.Buffer` and the ``umdk_cam_op_lib`` torch ops; this
+module is the thin layer between them and the C entry points.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from .. import _native
+from ..parallel.symm import HostMirror, SymmetricHeap
+
+MAX_RANKS = 32
+
+
+class _DispatchParams(ctypes.Structure):
+    _fields_ = [
+        ("R", ctypes.c_int), ("rank", ctypes.c_int), ("E", ctypes.c_int), ("K", ctypes.c_int), ("H", ctypes.c_int),
+        ("cap", ctypes.c_int), ("quant", ctypes.c_int), ("T", ctypes.c_int),
+        ("n_cap", ctypes.c_int), ("a_cap", ctypes.c_int), ("num_ctas", ctypes.c_int), ("phase_mask", ctypes.c_int),
+        ("peers", ctypes.c_void_p * MAX_RANKS),
+        ("x", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p), ("topk_w", ctypes.c_void_p),
+        ("send_idx", ctypes.c_void_p), ("rank_slot", ctypes.c_void_p), ("num_per_expert", ctypes.c_void_p),
+        ("num_per_rank", ctypes.c_void_p),
+        ("recv_x", ctypes.c_void_p), ("recv_scales", ctypes.c_void_p), ("expand_idx", ctypes.c_void_p),
+        ("recv_count", ctypes.c_void_p), ("recv_per_expert", ctypes.c_void_p), ("recv_meta", ctypes.c_void_p),
+        ("counts_dev", ctypes.c_void_p), ("counts_host", ctypes.c_void_p),
+        ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+    ]
+
+
+class _CombineParams(ctypes.Structure):
+    _fields_ = [
+        ("R", ctypes.c_int), ("rank", ctypes.c_int), ("E", ctypes.c_int), ("K", ctypes.c_int), ("H", ctypes.c_int),
+        ("cap", ctypes.c_int), ("T", ctypes.c_int),
+        ("mode", ctypes.c_int), ("apply_weights", ctypes.c_int), ("n_rows", ctypes.c_int),
+        ("num_ctas", ctypes.c_int), ("phase_mask", ctypes.c_int),
+        ("peers", ctypes.c_void_p * MAX_RANKS),
+        ("y", ctypes.c_void_p), ("recv_meta", ctypes.c_void_p), ("counts_dev", ctypes.c_void_p),
+        ("src_idx", ctypes.c_void_p), ("in_rank", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p),
+        ("topk_w", ctypes.c_void_p), ("out", ctypes.c_void_p), ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+    ]
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel gave up on a bounded wait or rejected an out-of-range index; the record says where."""
+
+
+_PHASES = {1: "tma-empty", 2: "tma-full", 3: "tmem-full", 4: "tmem-empty", 5: "dispatch-count", 6: "dispatch-data",
+           7: "combine-data", 8: "grid-barrier", 9: "group-ready", 10: "allreduce", 11: "ag-chunk", 12: "rs-chunk"}
+_CODES = {1: "timeout", 2: "bad-argument", 3: "overflow", 4: "cuda-error"}
+
+
+def check_status(status: torch.Tensor, what: str = "kernel"):
+    """Reads the 4-int status record (synchronises) and raises if a kernel reported an error."""
+    s = status.tolist()
+    if s[0] != 0:
+        status.zero_()
+        raise KernelStatusError(f"{what}: {_CODES.get(s[0], s[0])} in phase {_PHASES.get(s[1], s[1])} "
+                                f"(detail {s[2]}, {s[3]})")
+
+
+@dataclass
+class LayoutResult:
+    num_tokens_per_expert: torch.Tensor
+    num_tokens_per_rank: torch.Tensor
+    is_token_in_rank: torch.Tensor
+    send_token_idx: torch.Tensor
+    rank_slot: torch.Tensor
+
+
+@dataclass
+class DispatchResult:
+    recv_x: torch.Tensor                 # [n_cap, H] fp8 (uint8 storage viewed as float8_e4m3fn) or bf16
+    recv_scales: Optional[torch.Tensor]  # [n_cap, H/128] fp32
+    expand_idx: torch.Tensor             # [n_cap, 3]
+    recv_count: torch.Tensor             # [E_local * R] inclusive prefix
+    recv_tokens_per_expert: torch.Tensor # [E_local] int64
+    recv_meta: torch.Tensor              # [a_cap, 2K+2]
+    counts: torch.Tensor                 # device [4]: rows N, arrivals A, max from one source
+    layout: LayoutResult
+    topk_idx: torch.Tensor
+    topk_weights: Optional[torch.Tensor]
+    num_tokens: int
+    quant: bool
+    num_recv: Optional[int] = None       # host value of N when the caller asked for it
+
+
+def layout(topk_idx: torch.Tensor, num_experts: int, num_ranks: int, scratch=None, bar=None, status=None
+           ) -> LayoutResult:
+    """GPU ``get_dispatch_layout``: stable bucket positions per expert and per destination rank."""
+    lib = _native.cam()
+    assert topk_idx.is_cuda and topk_idx.dtype == torch.int64 and topk_idx.is_contiguous()
+    T, K = topk_idx.shape
+    dev = topk_idx.device
+    E, R = num_experts, num_ranks
+    npe = torch.empty(E, dtype=torch.int32, device=dev)
+    npr = torch.empty(R, dtype=torch.int32, device=dev)
+    inr = torch.empty(T, R, dtype=torch.uint8, device=dev)
+    sidx = torch.empty(T, K, dtype=torch.int32, device=dev)
+    rslot = torch.empty(T, R, dtype=torch.int32, device=dev)
+    chunks = (T + 31) // 32
+    if scratch is None or scratch.numel() < max(1, chunks) * (E + R):
+        scratch = torch.empty(max(1, chunks) * (E + R), dtype=torch.int32, device=dev)
+    if bar is None:
+        bar = torch.zeros(2, dtype=torch.int32, device=dev)
+    if status is None:
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+    rc = lib.umdk_ep_layout(_native.ptr(topk_idx), T, K, E, R, _native.ptr(npe), _native.ptr(npr), _native.ptr(inr),
+                            _native.ptr(sidx), _native.ptr(rslot), _native.ptr(scratch), _native.ptr(bar),
+                            _native.ptr(status), _native.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"umdk_ep_layout failed: {rc}")
+    return LayoutResult(npe, npr, inr.view(torch.bool), sidx, rslot)
+
+
+class EpNormal:
+    """State of one rank for normal-mode dispatch / combine at a fixed geometry (E, K, H, cap)."""
+
+    def __init__(self, heap: SymmetricHeap, num_experts: int, top_k: int, hidden: int, cap: int,
+                 num_ctas: int = 0, device=None):
+        self.lib = _native.cam()
+        self.heap = heap
+        self.R, self.rank = heap.world, heap.rank
+        self.E, self.K, self.H, self.cap = num_experts, top_k, hidden, cap
+        self.num_ctas = num_ctas
+        need = self.heap_bytes(self.R, num_experts, top_k, hidden, cap)
+        if need > heap.nbytes:
+            raise ValueError(f"symmetric heap too small: need {need} bytes, have {heap.nbytes}")
+        dev = device or torch.device("cuda", torch.cuda.current_device())
+        self.device = dev
+        self.ctrl = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.layout_bar = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.layout_scratch = torch.empty(((cap + 31) // 32) * (num_experts + self.R), dtype=torch.int32, device=dev)
+        self.mirror = HostMirror(8)
+
+    @staticmethod
+    def heap_bytes(R: int, E: int, K: int, H: int, cap: int) -> int:
+        lib = _native.cam()
+        lib.umdk_ep_normal_heap_bytes.restype = ctypes.c_longlong
+        n = lib.umdk_ep_normal_heap_bytes(R, E, K, H, cap)
+        if n < 0:
+            raise ValueError(f"unsupported EP geometry R={R} E={E} K={K} H={H} cap={cap}")
+        return int(n)
+
+    def layout(self, topk_idx: torch.Tensor) -> LayoutResult:
+        return layout(topk_idx, self.E, self.R, self.layout_scratch, self.layout_bar, self.status)
+
+    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: Optional[torch.Tensor],
+                 lay: Optional[LayoutResult] = None, quant: bool = True, n_cap: Optional[int] = None,
+                 a_cap: Optional[int] = None, phase_mask: int = 3, out: Optional[DispatchResult] = None,
+                 sync_counts: bool = False) -> DispatchResult:
+        """Runs notify + quantise + push + expand. ``phase_mask`` 1 / 2 run only the send / receive half (used to
+        drive several virtual ranks from one process on one GPU)."""
+        assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+        T, H = x.shape
+        assert H == self.H and T <= self.cap
+        K = self.K
+        if lay is None:
+            lay = out.layout if out is not None else self.layout(topk_idx)
+        if out is None:
+            n_cap = n_cap if n_cap is not None else self.R * self.cap * min(K, self.E // self.R)
+            a_cap = a_cap if a_cap is not None else self.R * self.cap
+            dev = x.device
+            if quant:
+                recv_x = torch.empty(n_cap, H, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+                recv_s = torch.empty(n_cap, H // 128, dtype=torch.float32, device=dev)
+            else:
+                recv_x = torch.empty(n_cap, H, dtype=torch.bfloat16, device=dev)
+                recv_s = None
+            out = DispatchResult(
+                recv_x, recv_s, torch.empty(n_cap, 3, dtype=torch.int32, device=dev),
+                torch.empty(self.E, dtype=torch.int32, device=dev),
+                torch.empty(self.E // self.R, dtype=torch.int64, device=dev),
+                torch.empty(a_cap, 2 * K + 2, dtype=torch.int32, device=dev),
+                torch.zeros(4, dtype=torch.int32, device=dev), lay, topk_idx, topk_weights, T, quant)
+        p = _DispatchParams()
+        p.R, p.rank, p.E, p.K, p.H, p.cap, p.quant, p.T = self.R, self.rank, self.E, K, H, self.cap, int(quant), T
+        p.n_cap, p.a_cap = out.recv_x.shape[0], out.recv_meta.shape[0]
+        p.num_ctas, p.phase_mask = self.num_ctas, phase_mask
+        for i, pp in enumerate(self.heap.peer_ptrs):
+            p.peers[i] = pp
+        p.x, p.topk_idx = x.data_ptr(), topk_idx.data_ptr()
+        p.topk_w = topk_weights.data_ptr() if topk_weights is not None else None
+        p.send_idx, p.rank_slot = lay.send_token_idx.data_ptr(), lay.rank_slot.data_ptr()
+        p.num_per_expert, p.num_per_rank = lay.num_tokens_per_expert.data_ptr(), lay.num_tokens_per_rank.data_ptr()
+        p.recv_x = out.recv_x.data_ptr()
+        p.recv_scales = out.recv_scales.data_ptr() if out.recv_scales is not None else None
+        p.expand_idx, p.recv_count = out.expand_idx.data_ptr(), out.recv_count.data_ptr()
+        p.recv_per_expert, p.recv_meta = out.recv_tokens_per_expert.data_ptr(), out.recv_meta.data_ptr()
+        p.counts_dev, p.counts_host = out.counts.data_ptr(), self.mirror.dev_ptr
+        p.ctrl, p.status = self.ctrl.data_ptr(), self.status.data_ptr()
+        rc = self.lib.umdk_ep_dispatch(ctypes.byref(p), _native.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"umdk_ep_dispatch failed: {rc}")
+        if sync_counts and (phase_mask & 2):
+            torch.cuda.current_stream().synchronize()
+            check_status(self.status, "ep_dispatch")
+            out.num_recv = int(self.mirror.host[0])
+        return out
+
+    def combine(self, y: torch.Tensor, disp: DispatchResult, apply_weights: bool = True, phase_mask: int = 3,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Per-rank pre-reduced combine: out[t] = sum over ranks of (sum_k w[t,k] * y_row(t,k))."""
+        assert y.is_cuda and y.dtype == torch.bfloat16 and y.is_contiguous() and y.shape[1] == self.H
+        T = disp.num_tokens
+        if out is None:
+            out = torch.empty(T, self.H, dtype=torch.bfloat16, device=y.device)
+        p = _CombineParams()
+        p.R, p.rank, p.E, p.K, p.H, p.cap, p.T = self.R, self.rank, self.E, self.K, self.H, self.cap, T
+        p.mode, p.apply_weights, p.n_rows = 0, int(apply_weights), 0
+        p.num_ctas, p.phase_mask = self.num_ctas, phase_mask
+        for i, pp in enumerate(self.heap.peer_ptrs):
+            p.peers[i] = pp
+        p.y, p.recv_meta, p.counts_dev = y.data_ptr(), disp.recv_meta.data_ptr(), disp.counts.data_ptr()
+        p.in_rank = disp.layout.is_token_in_rank.data_ptr()
+        p.out, p.ctrl, p.status = out.data_ptr(), self.ctrl.data_ptr(), self.status.data_ptr()
+        rc = self.lib.umdk_ep_combine(ctypes.byref(p), _native.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"umdk_ep_combine failed: {rc}")
+        return out
+
+    def combine_rows(self, y: torch.Tensor, src_idx: torch.Tensor, topk_idx: torch.Tensor,
+                     topk_weights: torch.Tensor, phase_mask: int = 3, out: Optional[torch.Tensor] = None
+                     ) -> torch.Tensor:
+        """Row-per-(token,k) combine with the reference's stateless contract (moe_combine_prefill)."""
+        T = topk_idx.shape[0]
+        if out is None:
+            out = torch.empty(T, self.H, dtype=torch.bfloat16, device=y.device)
+        p = _CombineParams()
+        p.R, p.rank, p.E, p.K, p.H, p.cap, p.T = self.R, self.rank, self.E, self.K, self.H, self.cap, T
+        p.mode, p.apply_weights, p.n_rows = 1, 1, y.shape[0]
+        p.num_ctas, p.phase_mask = self.num_ctas, phase_mask
+        for i, pp in enumerate(self.heap.peer_ptrs):
+            p.peers[i] = pp
+        p.y, p.src_idx = y.data_ptr(), src_idx.data_ptr()
+        p.topk_idx, p.topk_w = topk_idx.data_ptr(), topk_weights.data_ptr()
+        p.out, p.ctrl, p.status = out.data_ptr(), self.ctrl.data_ptr(), self.status.data_ptr()
+        rc = self.lib.umdk_ep_combine(ctypes.byref(p), _native.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"umdk_ep_combine failed: {rc}")
+        return out
+
+    def check(self, what: str = "ep"):
+        check_status(self.status, what)
