@@ -67,6 +67,56 @@ __host__ __device__ inline EpNormalOffsets ep_normal_offsets(const EpGeom& g) {
   return o;
 }
 
+// Low-latency (decode) layout. Rows are pushed straight to their final position in an expert-major slab, so the
+// slab is directly the activation operand of the grouped GEMM.
+struct EpLLGeom {
+  int R, rank, E, E_local, K, H, T_cap;
+  int n_cap;   // rows of the receive slab: R * T_cap * min(K, E_local)
+};
+
+struct EpLLOffsets {
+  uint64_t cnt[2];        // [R src][E] int32: every rank's per-expert token counts (all-gathered)
+  uint64_t cnt_flag[2];   // [R] uint64
+  uint64_t data_flag[2];  // [R] uint64
+  uint64_t comb_flag[2];  // [R] uint64
+  uint64_t slab_x[2];     // [n_cap][H] fp8
+  uint64_t slab_s[2];     // [n_cap][H/128] fp32
+  uint64_t slab_meta[2];  // [n_cap][2] int32: owner rank, owner slot (token * K + k)
+  uint64_t comb_buf[2];   // [T_cap][K][H] bf16
+  uint64_t total;
+};
+
+__host__ __device__ inline int ep_ll_n_cap(int R, int T_cap, int K, int E_local) {
+  return R * T_cap * (K < E_local ? K : E_local);
+}
+
+__host__ __device__ inline EpLLOffsets ep_ll_offsets(const EpLLGeom& g) {
+  EpLLOffsets o;
+  uint64_t off = 0;
+  for (int h = 0; h < 2; ++h) {
+    o.cnt[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * g.E * 4, 256);
+    o.cnt_flag[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * 8, 256);
+    o.data_flag[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * 8, 256);
+    o.comb_flag[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * 8, 256);
+  }
+  for (int h = 0; h < 2; ++h) {
+    o.slab_x[h] = off;
+    off = align_up_u64(off + (uint64_t)g.n_cap * g.H, 1024);
+    o.slab_s[h] = off;
+    off = align_up_u64(off + (uint64_t)g.n_cap * (g.H / 128) * 4, 256);
+    o.slab_meta[h] = off;
+    off = align_up_u64(off + (uint64_t)g.n_cap * 8, 256);
+    o.comb_buf[h] = off;
+    off = align_up_u64(off + (uint64_t)g.T_cap * g.K * g.H * 2, 1024);
+  }
+  o.total = off;
+  return o;
+}
+
 struct PeerTable {
   uint8_t* base[kMaxRanks];
 };

@@ -225,3 +225,41 @@ def mean_rel_err(a: torch.Tensor, ref: torch.Tensor) -> float:
     a = a.double()
     ref = ref.double()
     return float(((a - ref).abs().sum() / ref.abs().sum().clamp_min(1e-12)))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# expert FFN (fp8 block-scaled) reference
+# ------------------------------------------------------------------------------------------------------------------
+def ref_gemm1_swiglu_quant(xq, xs, group_off, w1q, w1s):
+    """fp32 statement of the gate/up projection + SwiGLU + fp8 1x128 re-quantisation, group by group.
+    Returns (hq float8 [N, F], hs fp32 [N, F/128], h fp32 [N, F] before quantisation)."""
+    N = xq.shape[0]
+    F = w1q.shape[1] // 2
+    x = dequant_fp8_1x128(xq.cpu(), xs.cpu())
+    h = torch.zeros(N, F, dtype=torch.float32)
+    off = group_off.cpu().tolist()
+    for g in range(w1q.shape[0]):
+        a, b = off[g], off[g + 1]
+        if b <= a:
+            continue
+        w = dequant_fp8_128x128(w1q[g].cpu(), w1s[g].cpu())
+        y1 = x[a:b] @ w.t()
+        gate, up = y1[:, :F], y1[:, F:]
+        h[a:b] = torch.nn.functional.silu(gate) * up
+    hq, hs = quant_fp8_1x128(h)
+    return hq, hs, h
+
+
+def ref_gemm2(hq, hs, group_off, w2q, w2s):
+    N = hq.shape[0]
+    H = w2q.shape[1]
+    hdeq = dequant_fp8_1x128(hq.cpu(), hs.cpu())
+    y = torch.zeros(N, H, dtype=torch.float32)
+    off = group_off.cpu().tolist()
+    for g in range(w2q.shape[0]):
+        a, b = off[g], off[g + 1]
+        if b <= a:
+            continue
+        w = dequant_fp8_128x128(w2q[g].cpu(), w2s[g].cpu())
+        y[a:b] = hdeq[a:b] @ w.t()
+    return y
