@@ -91,9 +91,11 @@ __host__ __device__ inline int ep_ll_n_cap(int R, int T_cap, int K, int E_local)
 }
 
 __host__ __device__ inline EpLLOffsets ep_ll_offsets(const EpLLGeom& g) {
+  // Single-buffered: a rank can only start call n+1 after it has received every peer's combine flags of call n,
+  // i.e. after every peer has finished reading its slab and combine buffer of call n. Both halves alias.
   EpLLOffsets o;
   uint64_t off = 0;
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < 1; ++h) {
     o.cnt[h] = off;
     off = align_up_u64(off + (uint64_t)g.R * g.E * 4, 256);
     o.cnt_flag[h] = off;
@@ -103,7 +105,7 @@ __host__ __device__ inline EpLLOffsets ep_ll_offsets(const EpLLGeom& g) {
     o.comb_flag[h] = off;
     off = align_up_u64(off + (uint64_t)g.R * 8, 256);
   }
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < 1; ++h) {
     o.slab_x[h] = off;
     off = align_up_u64(off + (uint64_t)g.n_cap * g.H, 1024);
     o.slab_s[h] = off;
@@ -113,6 +115,14 @@ __host__ __device__ inline EpLLOffsets ep_ll_offsets(const EpLLGeom& g) {
     o.comb_buf[h] = off;
     off = align_up_u64(off + (uint64_t)g.T_cap * g.K * g.H * 2, 1024);
   }
+  o.cnt[1] = o.cnt[0];
+  o.cnt_flag[1] = o.cnt_flag[0];
+  o.data_flag[1] = o.data_flag[0];
+  o.comb_flag[1] = o.comb_flag[0];
+  o.slab_x[1] = o.slab_x[0];
+  o.slab_s[1] = o.slab_s[0];
+  o.slab_meta[1] = o.slab_meta[0];
+  o.comb_buf[1] = o.comb_buf[0];
   o.total = off;
   return o;
 }

@@ -57,6 +57,7 @@ struct MoeGemmArgs {
   __nv_bfloat16* out;         // [T, Nout]
   int T, Kt, T_cap;
   uint32_t* ctrl;             // [0] epoch (advanced here), [1] send-done counter, [2] reduce-done counter
+  int phase_mask;             // MODE 2: bit0 GEMM + combine-send + flags, bit1 wait + reduce + epoch advance
   int* status;
 };
 
@@ -176,7 +177,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     tile_pref[a.G] = run;
   }
   __syncthreads();
-  const int num_items = s_ok ? tile_pref[a.G] * NT : 0;
+  const int num_items = (s_ok && (MODE != 2 || (a.phase_mask & 1))) ? tile_pref[a.G] * NT : 0;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -386,11 +387,14 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 
   if (MODE == 2) {
     // ---- completion flags to every peer, then the owner-side weighted reduction ----
-    if (cta_done_is_last(&a.ctrl[1], gridDim.x)) {
-      if (threadIdx.x < a.R) {
-        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.comb_flag_off[h]) + a.rank, tag);
+    if (a.phase_mask & 1) {
+      if (cta_done_is_last(&a.ctrl[1], gridDim.x)) {
+        if (threadIdx.x < a.R) {
+          st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.comb_flag_off[h]) + a.rank, tag);
+        }
       }
     }
+    if (!(a.phase_mask & 2)) return;
     uint8_t* self = a.peers.base[a.rank];
     if (threadIdx.x < a.R) {
       const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.comb_flag_off[h]) + threadIdx.x;
@@ -489,6 +493,7 @@ struct UmdkMoeGemmParams {
   void* out;
   uint32_t* ctrl;
   int* status;
+  int phase_mask;
 };
 
 UMDK_API int umdk_moe_gemm(const UmdkMoeGemmParams* p, void* stream) {
@@ -526,6 +531,7 @@ UMDK_API int umdk_moe_gemm(const UmdkMoeGemmParams* p, void* stream) {
   a.T_cap = p->T_cap;
   a.ctrl = p->ctrl;
   a.status = p->status;
+  a.phase_mask = p->phase_mask ? p->phase_mask : 3;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (p->mode) {
     case 0: return launch<0>(p->w, p->x, a, s, p->max_ctas);

@@ -1,0 +1,107 @@
+"""Low-latency MoE layer (dispatch -> fp8 grouped GEMMs -> combine fused in the GEMM2 epilogue) against the dense
+fp32 oracle. Several ranks are emulated on one GPU by running each communication phase for every rank in turn."""
+import pytest
+import torch
+
+from umdk_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _weights(E, H, F, seed):
+    g = torch.Generator().manual_seed(seed)
+    w1 = torch.randn(E, 2 * F, H, generator=g) * 0.02
+    w2 = torch.randn(E, H, F, generator=g) * 0.02
+    return ref.quant_fp8_128x128(w1) + ref.quant_fp8_128x128(w2)
+
+
+def _inputs(R, T, H, E, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    xs, idxs, ws = [], [], []
+    for r in range(R):
+        xs.append(torch.randn(T, H, generator=g).to(torch.bfloat16))
+        p = torch.softmax(torch.randn(T, E, generator=g), dim=-1)
+        w, idx = torch.topk(p, K, dim=-1)
+        idx = idx.to(torch.int64)
+        if T > 4:
+            idx[::5, K - 1] = -1
+        idxs.append(idx)
+        ws.append((w / w.sum(-1, keepdim=True)).float())
+    return xs, idxs, ws
+
+
+@pytest.mark.parametrize("R,T,H,F,E,K", [
+    (1, 16, 512, 256, 4, 2),
+    (2, 40, 1024, 256, 8, 2),
+    (4, 33, 1024, 512, 16, 4),
+    (8, 24, 2048, 512, 64, 8),
+])
+def test_low_latency_moe_virtual_ranks(R, T, H, F, E, K):
+    from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
+    from umdk_b200.parallel.symm import SymmetricHeap
+    w1q, w1s, w2q, w2s = _weights(E, H, F, seed=E)
+    xs, idxs, ws = _inputs(R, T, H, E, K, seed=R * 100 + T)
+    heaps = SymmetricHeap.virtual(EpLowLatency.heap_bytes(R, E, K, H, T), R)
+    try:
+        st = [EpLowLatency(h, E, K, H, F, T) for h in heaps]
+        el = E // R
+        wts = [ExpertWeights(w1q[r * el:(r + 1) * el].cuda().contiguous(), w1s[r * el:(r + 1) * el].cuda().contiguous(),
+                             w2q[r * el:(r + 1) * el].cuda().contiguous(), w2s[r * el:(r + 1) * el].cuda().contiguous())
+               for r in range(R)]
+        dx = [x.cuda() for x in xs]
+        di = [i.cuda() for i in idxs]
+        dw = [w.cuda() for w in ws]
+        for rnd in range(2):
+            lays = [st[r].dispatch(dx[r], di[r], phase_mask=1) for r in range(R)]
+            for r in range(R):
+                st[r].dispatch(dx[r], di[r], phase_mask=2, lay=lays[r])
+            for r in range(R):
+                st[r]._gemm1(wts[r])
+            outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+            for r in range(R):
+                st[r]._gemm2_combine(wts[r], di[r], dw[r], outs[r], phase_mask=1)
+            for r in range(R):
+                st[r]._gemm2_combine(wts[r], di[r], dw[r], outs[r], phase_mask=2)
+            torch.cuda.synchronize()
+            for s in st:
+                s.check()
+            # token counts per local expert are exact
+            for r in range(R):
+                want_cnt = torch.zeros(el, dtype=torch.int64)
+                for s in range(R):
+                    v = idxs[s][(idxs[s] >= r * el) & (idxs[s] < (r + 1) * el)] - r * el
+                    want_cnt += torch.bincount(v, minlength=el)
+                assert torch.equal(st[r].recv_per_expert.cpu(), want_cnt)
+            for r in range(R):
+                want = ref.ref_fused_moe(xs[r], idxs[r], ws[r], w1q, w1s, w2q, w2s)
+                err = ref.mean_rel_err(outs[r].float().cpu(), want)
+                assert err < 0.02, (rnd, r, err)
+    finally:
+        for h in heaps:
+            h.close()
+
+
+def test_low_latency_moe_single_call_with_shared_expert():
+    from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
+    from umdk_b200.parallel.symm import SymmetricHeap
+    R, T, H, F, E, K = 1, 64, 1024, 512, 8, 4
+    w1q, w1s, w2q, w2s = _weights(E, H, F, seed=7)
+    s1q, s1s, s2q, s2s = _weights(1, H, F, seed=8)
+    xs, idxs, ws = _inputs(R, T, H, E, K, seed=5)
+    heap = SymmetricHeap(EpLowLatency.heap_bytes(R, E, K, H, T))
+    try:
+        st = EpLowLatency(heap, E, K, H, F, T)
+        w = ExpertWeights(w1q.cuda(), w1s.cuda(), w2q.cuda(), w2s.cuda())
+        sh = ExpertWeights(s1q.cuda(), s1s.cuda(), s2q.cuda(), s2s.cuda())
+        for _ in range(3):
+            out, share, cnt = st.moe(xs[0].cuda(), idxs[0].cuda(), ws[0].cuda(), w, shared=sh)
+        torch.cuda.synchronize()
+        st.check()
+        want = ref.ref_fused_moe(xs[0], idxs[0], ws[0], w1q, w1s, w2q, w2s)
+        assert ref.mean_rel_err(out.float().cpu(), want) < 0.02
+        ones = torch.ones(T, 1)
+        want_sh = ref.ref_fused_moe(xs[0], torch.zeros(T, 1, dtype=torch.int64), ones, s1q, s1s, s2q, s2s)
+        assert ref.mean_rel_err(share.float().cpu(), want_sh) < 0.02
+        assert int(cnt.sum().item()) == int((idxs[0] >= 0).sum().item())
+    finally:
+        heap.close()

@@ -1,0 +1,208 @@
+"""Low-latency (decode) expert-parallel MoE layer on the GPU: dispatch -> grouped fp8 GEMM1 + SwiGLU + re-quant ->
+grouped fp8 GEMM2 whose epilogue stores rows into the token owners' combine buffers -> top-k weighted reduction.
+
+Kernel chain per call (all on the caller's stream, capturable in a CUDA graph):
+  ep_layout           bucket positions of (token, k) per expert
+  ep_ll_dispatch      count all-gather + fp8 1x128 quantisation + direct push into the destination slab rows
+  moe_gemm mode 0     waits for the arrival flags, then gate/up projection + SwiGLU + fp8 re-quantisation
+  moe_gemm mode 2     down projection, combine-send epilogue, completion flags, owner-side weighted reduction
+The shared expert (if any) runs through the same GEMM kernels on the locally quantised tokens.
+
+Mirrors the contract of the reference's ``fused_deep_moe`` (src/cam/comm_operator/pybind/fused_deep_moe.cpp:30-83;
+doc/en/cam/CAM API Guide.md:150-226): returns (combine_x, share_output, expert_token_nums) with the shared expert's
+output returned separately, ``expert_ids == -1`` skipped.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _native
+from ..parallel.symm import SymmetricHeap
+from . import moe_gemm
+from .ep import check_status, layout as ep_layout
+
+MAX_RANKS = 32
+
+
+class _LLLayout(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_uint64) for n in
+                ("cnt", "cnt_flag", "data_flag", "comb_flag", "slab_x", "slab_s", "slab_meta", "comb_buf", "total")] + \
+               [("n_cap", ctypes.c_int)]
+
+
+class _LLDispatchParams(ctypes.Structure):
+    _fields_ = [
+        ("R", ctypes.c_int), ("rank", ctypes.c_int), ("E", ctypes.c_int), ("K", ctypes.c_int), ("H", ctypes.c_int),
+        ("T_cap", ctypes.c_int), ("T", ctypes.c_int), ("num_ctas", ctypes.c_int), ("phase_mask", ctypes.c_int),
+        ("peers", ctypes.c_void_p * MAX_RANKS),
+        ("x", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p), ("send_idx", ctypes.c_void_p),
+        ("num_per_expert", ctypes.c_void_p), ("group_off", ctypes.c_void_p), ("recv_per_expert", ctypes.c_void_p),
+        ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+    ]
+
+
+def ll_layout(R: int, E: int, K: int, H: int, T_cap: int) -> _LLLayout:
+    lib = _native.cam()
+    lay = _LLLayout()
+    rc = lib.umdk_ep_ll_layout(R, E, K, H, T_cap, ctypes.byref(lay))
+    if rc != 0:
+        raise ValueError(f"unsupported low-latency geometry R={R} E={E} K={K} H={H} T_cap={T_cap}")
+    return lay
+
+
+def quant_fp8_1x128(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [T, H] -> (fp8 e4m3 [T, H], fp32 scales [T, H/128]) with the hand-written kernel."""
+    lib = _native.cam()
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+    T, H = x.shape
+    q = torch.empty(T, H, dtype=torch.uint8, device=x.device).view(torch.float8_e4m3fn)
+    s = torch.empty(T, H // 128, dtype=torch.float32, device=x.device)
+    rc = lib.umdk_quant_fp8_1x128(_native.ptr(x), T, H, _native.ptr(q), _native.ptr(s), _native.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"umdk_quant_fp8_1x128 failed: {rc}")
+    return q, s
+
+
+@dataclass
+class ExpertWeights:
+    """fp8 e4m3 expert weights with 128x128 block scales. w1: [G, 2F, H] (gate rows first), w2: [G, H, F]."""
+    w1q: torch.Tensor
+    w1s: torch.Tensor
+    w2q: torch.Tensor
+    w2s: torch.Tensor
+
+
+class EpLowLatency:
+    """Per-rank state of the low-latency MoE path at a fixed geometry."""
+
+    def __init__(self, heap: SymmetricHeap, num_experts: int, top_k: int, hidden: int, ffn: int, t_cap: int,
+                 dispatch_ctas: int = 32, gemm_ctas: int = 0):
+        self.lib = _native.cam()
+        self.heap = heap
+        self.R, self.rank = heap.world, heap.rank
+        self.E, self.K, self.H, self.F, self.T_cap = num_experts, top_k, hidden, ffn, t_cap
+        self.E_local = num_experts // self.R
+        self.lay = ll_layout(self.R, num_experts, top_k, hidden, t_cap)
+        if self.lay.total > heap.nbytes:
+            raise ValueError(f"symmetric heap too small: need {self.lay.total}, have {heap.nbytes}")
+        self.n_cap = self.lay.n_cap
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.device = dev
+        self.ctrl = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.layout_bar = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.layout_scratch = torch.empty(((t_cap + 31) // 32) * (num_experts + self.R), dtype=torch.int32, device=dev)
+        self.group_off = torch.zeros(self.E_local + 1, dtype=torch.int32, device=dev)
+        self.recv_per_expert = torch.zeros(self.E_local, dtype=torch.int64, device=dev)
+        self.hq = torch.empty(self.n_cap, ffn, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+        self.hs = torch.empty(self.n_cap, ffn // 128, dtype=torch.float32, device=dev)
+        self.dispatch_ctas, self.gemm_ctas = dispatch_ctas, gemm_ctas
+        # shared-expert scratch
+        self.sh_off = torch.tensor([0, 0], dtype=torch.int32, device=dev)
+        self.sh_hq = torch.empty(t_cap, ffn, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+        self.sh_hs = torch.empty(t_cap, ffn // 128, dtype=torch.float32, device=dev)
+
+    @staticmethod
+    def heap_bytes(R: int, E: int, K: int, H: int, T_cap: int) -> int:
+        return int(ll_layout(R, E, K, H, T_cap).total)
+
+    # -- views into this rank's own heap -------------------------------------------------------------------------
+    def _local(self, off: int) -> int:
+        return self.heap.local_ptr + off
+
+    def slab_views(self):
+        """(slab_x fp8 [n_cap, H], slab_s fp32 [n_cap, H/128], slab_meta int32 [n_cap, 2]) as torch tensors."""
+        from ..utils.rawtensor import from_ptr
+        x = from_ptr(self._local(self.lay.slab_x), (self.n_cap, self.H), torch.uint8, self.device).view(
+            torch.float8_e4m3fn)
+        s = from_ptr(self._local(self.lay.slab_s), (self.n_cap, self.H // 128), torch.float32, self.device)
+        m = from_ptr(self._local(self.lay.slab_meta), (self.n_cap, 2), torch.int32, self.device)
+        return x, s, m
+
+    # -- kernels -------------------------------------------------------------------------------------------------
+    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, phase_mask: int = 3, lay=None):
+        assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and topk_idx.dtype == torch.int64
+        T = x.shape[0]
+        assert T <= self.T_cap and x.shape[1] == self.H
+        if lay is None:
+            lay = ep_layout(topk_idx, self.E, self.R, self.layout_scratch, self.layout_bar, self.status)
+        p = _LLDispatchParams()
+        p.R, p.rank, p.E, p.K, p.H, p.T_cap, p.T = self.R, self.rank, self.E, self.K, self.H, self.T_cap, T
+        p.num_ctas, p.phase_mask = self.dispatch_ctas, phase_mask
+        for i, pp in enumerate(self.heap.peer_ptrs):
+            p.peers[i] = pp
+        p.x, p.topk_idx = x.data_ptr(), topk_idx.data_ptr()
+        p.send_idx, p.num_per_expert = lay.send_token_idx.data_ptr(), lay.num_tokens_per_expert.data_ptr()
+        p.group_off, p.recv_per_expert = self.group_off.data_ptr(), self.recv_per_expert.data_ptr()
+        p.ctrl, p.status = self.ctrl.data_ptr(), self.status.data_ptr()
+        rc = self.lib.umdk_ep_ll_dispatch(ctypes.byref(p), _native.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"umdk_ep_ll_dispatch failed: {rc}")
+        return lay
+
+    def _gemm1(self, w: ExpertWeights):
+        p = moe_gemm.MoeGemmParams()
+        p.mode, p.G, p.Nout, p.K = 0, self.E_local, self.F, self.H
+        p.n_rows_cap, p.max_ctas = self.n_cap, self.gemm_ctas
+        p.w, p.ws = w.w1q.data_ptr(), w.w1s.data_ptr()
+        p.x, p.xs = self._local(self.lay.slab_x), self._local(self.lay.slab_s)
+        p.group_off = self.group_off.data_ptr()
+        p.hq, p.hs = self.hq.data_ptr(), self.hs.data_ptr()
+        p.wait_flags[0] = p.wait_flags[1] = self._local(self.lay.data_flag)
+        p.wait_n, p.epoch_ptr = self.R, self.ctrl.data_ptr()
+        p.status = self.status.data_ptr()
+        rc = self.lib.umdk_moe_gemm(ctypes.byref(p), _native.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"umdk_moe_gemm(mode 0) failed: {rc}")
+
+    def _gemm2_combine(self, w: ExpertWeights, topk_idx, topk_w, out, phase_mask: int = 3):
+        T = topk_idx.shape[0]
+        p = moe_gemm.MoeGemmParams()
+        p.mode, p.G, p.Nout, p.K = 2, self.E_local, self.H, self.F
+        p.n_rows_cap, p.max_ctas = self.n_cap, self.gemm_ctas
+        p.w, p.ws = w.w2q.data_ptr(), w.w2s.data_ptr()
+        p.x, p.xs = self.hq.data_ptr(), self.hs.data_ptr()
+        p.group_off = self.group_off.data_ptr()
+        p.epoch_ptr = self.ctrl.data_ptr()
+        p.R, p.rank, p.T, p.Kt, p.T_cap = self.R, self.rank, T, self.K, self.T_cap
+        for i, pp in enumerate(self.heap.peer_ptrs):
+            p.peers[i] = pp
+        p.comb_buf_off[0] = p.comb_buf_off[1] = self.lay.comb_buf
+        p.comb_flag_off[0] = p.comb_flag_off[1] = self.lay.comb_flag
+        p.row_meta = self._local(self.lay.slab_meta)
+        p.topk_idx, p.topk_w, p.out = topk_idx.data_ptr(), topk_w.data_ptr(), out.data_ptr()
+        p.ctrl = self.ctrl.data_ptr()
+        p.status = self.status.data_ptr()
+        p.phase_mask = phase_mask
+        rc = self.lib.umdk_moe_gemm(ctypes.byref(p), _native.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"umdk_moe_gemm(mode 2) failed: {rc}")
+
+    def shared_expert(self, x: torch.Tensor, w: ExpertWeights, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Dense SwiGLU FFN of the shared expert on this rank's own tokens (fp8 block-scaled, same GEMM kernels)."""
+        T = x.shape[0]
+        xq, xs = quant_fp8_1x128(x)
+        self.sh_off[1] = T
+        moe_gemm.gemm1_swiglu_quant(xq, xs, self.sh_off, w.w1q, w.w1s, self.status, self.sh_hq[:T], self.sh_hs[:T],
+                                    max_ctas=self.gemm_ctas)
+        return moe_gemm.gemm2(self.sh_hq[:T], self.sh_hs[:T], self.sh_off, w.w2q, w.w2s, self.status, y=out,
+                              max_ctas=self.gemm_ctas)
+
+    def moe(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w: ExpertWeights,
+            shared: Optional[ExpertWeights] = None, out: Optional[torch.Tensor] = None):
+        """Full layer: returns (combine_x [T, H] bf16, share_output or None, expert_token_nums [E_local] int64)."""
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
+        self.dispatch(x, topk_idx)
+        share_out = self.shared_expert(x, shared) if shared is not None else None
+        self._gemm1(w)
+        self._gemm2_combine(w, topk_idx, topk_w, out)
+        return out, share_out, self.recv_per_expert
+
+    def check(self, what: str = "ep_ll"):
+        check_status(self.status, what)

@@ -25,6 +25,7 @@ class MoeGemmParams(ctypes.Structure):
         ("comb_buf_off", ctypes.c_uint64 * 2), ("comb_flag_off", ctypes.c_uint64 * 2),
         ("row_meta", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p), ("topk_w", ctypes.c_void_p),
         ("out", ctypes.c_void_p), ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("phase_mask", ctypes.c_int),
     ]
 
 

@@ -263,3 +263,29 @@ def ref_gemm2(hq, hs, group_off, w2q, w2s):
         w = dequant_fp8_128x128(w2q[g].cpu(), w2s[g].cpu())
         y[a:b] = hdeq[a:b] @ w.t()
     return y
+
+
+def ref_fused_moe(x, topk_idx, topk_w, w1q, w1s, w2q, w2s):
+    """Dense fp32 statement of the low-latency MoE layer for ONE rank's tokens against ALL experts:
+    x -> fp8 1x128 -> W1 (fp8 128x128) -> SwiGLU -> fp8 1x128 -> W2 -> bf16 rows -> sum_k w[t,k] * row (fp32).
+    w1q: [E, 2F, H], w2q: [E, H, F] over the global expert index."""
+    T, K = topk_idx.shape
+    xq, xs = quant_fp8_1x128(x.cpu())
+    xd = dequant_fp8_1x128(xq, xs)
+    F = w1q.shape[1] // 2
+    out = torch.zeros(T, w2q.shape[1], dtype=torch.float32)
+    idx = topk_idx.cpu()
+    w = topk_w.cpu().float()
+    for e in torch.unique(idx).tolist():
+        if e < 0:
+            continue
+        tk = torch.nonzero(idx == e)
+        t, k = tk[:, 0], tk[:, 1]
+        w1 = dequant_fp8_128x128(w1q[e].cpu(), w1s[e].cpu())
+        w2 = dequant_fp8_128x128(w2q[e].cpu(), w2s[e].cpu())
+        y1 = xd[t] @ w1.t()
+        h = torch.nn.functional.silu(y1[:, :F]) * y1[:, F:]
+        hq, hs = quant_fp8_1x128(h)
+        y2 = (dequant_fp8_1x128(hq, hs) @ w2.t()).to(torch.bfloat16).float()
+        out.index_add_(0, t, y2 * w[t, k].unsqueeze(1))
+    return out
