@@ -1,0 +1,230 @@
+#!/usr/bin/env python
+"""Flagship benchmark: MoE decode tokens/sec per box on a DeepSeek-V3-shaped 4-layer MoE decoder.
+
+One decode step per rank = batch 64 sequences x 1 token, context 32768 in a paged bf16 MLA KV cache (64-token pages),
+sparse attention over top-2048 KV rows per query chosen uniformly at random, half of every sequence's pages offloaded
+to pinned host memory and prefetched with cudaMemcpyAsync on a side stream, MoE layers with 256 routed experts
+(top-8, fp8 e4m3 SwiGLU experts 7168 -> 2048 -> 7168 with 128x128 block scales) plus one shared expert, experts
+sharded over the N ranks (EP = N), attention data parallel (weak scaling: 64 sequences per GPU).
+
+    python bench.py --gpus 1 --steps 8 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 8 --warmup 3
+
+Rank 0 prints ONE JSON line. `value` is device-timed (CUDA events, max over ranks) with inputs resident on the
+device; `e2e.value` goes through the public `DecoderRank.step` API with the step's inputs copied from pinned host
+memory and the sampled tokens read back on the host every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REFERENCE_UNAVAILABLE = ("reference is Ascend-only (AscendC kernels built with CANN/HCCL, UB kernel modules; no "
+                         "setup.py/pyproject at its root: pip reports 'Neither setup.py nor pyproject.toml found'); "
+                         "it cannot be built for or run on NVIDIA GPUs")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU every 200 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self._proc = None
+        self._thread = None
+
+    def start(self):
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self._proc = None
+            return
+        self._thread = threading.Thread(target=self._read, daemon=True)
+        self._thread.start()
+
+    def _read(self):
+        for line in self._proc.stdout:
+            parts = [p.strip() for p in line.strip().split(",")]
+            if len(parts) >= 8:
+                self.rows.append(parts)
+
+    def stop(self) -> dict:
+        if self._proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self._proc.terminate()
+        try:
+            self._proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self._proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="umdk", choices=["umdk", "reference"])
+    ap.add_argument("--config", default="full", choices=["full", "tiny"])
+    ap.add_argument("--no-offload", action="store_true", help="keep the whole KV cache on the device (not the "
+                    "benchmark configuration; for kernel-only studies)")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from umdk_b200 import _native
+    from umdk_b200.models.dsv3_decoder import DecoderConfig, DecoderRank
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus or world == 1, f"launched with WORLD_SIZE={world} but --gpus {args.gpus}"
+
+    cfg = DecoderConfig() if args.config == "full" else DecoderConfig.tiny()
+    cfg.offload = not args.no_offload
+    model = DecoderRank(cfg, device=dev)
+    B, L = cfg.batch, cfg.n_layers
+
+    # synthetic inputs of the named shape: a ring of distinct steps in pinned host memory
+    ring = 4
+    g = torch.Generator().manual_seed(1234 + rank)
+    host_tokens = [torch.randint(0, cfg.vocab, (B,), generator=g).pin_memory() for _ in range(ring)]
+    host_idx = [[torch.stack([torch.randperm(cfg.ctx + 1, generator=g)[:cfg.topk_kv] for _ in range(B)])
+                 .to(torch.int32).pin_memory() for _ in range(L)] for _ in range(ring)]
+    dev_tokens = [t.to(dev) for t in host_tokens]
+    dev_idx = [[t.to(dev) for t in per] for per in host_idx]
+    in_tokens = torch.empty(B, dtype=torch.int64, device=dev)
+    in_idx = [torch.empty(B, cfg.topk_kv, dtype=torch.int32, device=dev) for _ in range(L)]
+    host_out = torch.empty(B, dtype=torch.int64).pin_memory()
+    h2d_bytes = host_tokens[0].numel() * 8 + sum(t.numel() * 4 for t in host_idx[0])
+    d2h_bytes = host_out.numel() * 8
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-timed: inputs resident on the device ----
+    for i in range(args.warmup):
+        model.step(dev_tokens[i % ring], dev_idx[i % ring])
+    torch.cuda.synchronize()
+    model.check()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    launches0 = _native.LAUNCH_COUNT
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        model.step(dev_tokens[i % ring], dev_idx[i % ring])
+    e1.record()
+    barrier()
+    launches = _native.LAUNCH_COUNT - launches0
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop()
+    model.check()
+
+    # ---- end to end through the public step API: pinned host inputs in, sampled tokens out, every step ----
+    def e2e_step(i: int):
+        in_tokens.copy_(host_tokens[i % ring], non_blocking=True)
+        for l in range(L):
+            in_idx[l].copy_(host_idx[i % ring][l], non_blocking=True)
+        nxt = model.step(in_tokens, in_idx)
+        model.prefetch()  # the next step's KV pages are known: start moving them while the host reads the result
+        host_out.copy_(nxt, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return int(host_out[0])
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    c1.record()
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max_over_ranks(max(c0.elapsed_time(c1), wall_ms))
+    model.check()
+    kv_stats = model.kvm.stats() if model.kvm is not None else {"bytes_h2d": 0, "copies": 0}
+
+    tokens = world * B * args.steps
+    value = tokens / (ms * 1e-3)
+    e2e_value = tokens / (e2e_ms * 1e-3)
+    kv_bytes_step = (cfg.n_layers * model.n_staging * 64 * 576 * 2) if cfg.offload else 0
+    if rank == 0:
+        print(json.dumps({
+            "metric": "moe_decode_tokens_per_sec_per_box", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations/KV, fp8-e4m3 expert GEMMs",
+            "data": "synthetic (random-init weights, random KV cache, random top-2048 indices)",
+            "impl": "umdk_b200",
+            "config": {"model": "deepseek-v3-shaped 4-layer MoE decoder" if args.config == "full" else "tiny",
+                       "global_batch": world * B, "seq_len": cfg.ctx, "parallelism": f"ep{world}+dp{world}",
+                       "experts": cfg.n_experts, "top_k": cfg.top_k, "moe_ffn": cfg.moe_ffn, "hidden": cfg.hidden,
+                       "kv_topk": cfg.topk_kv, "kv_page": 64, "kv_offload": "half of each sequence's pages in pinned "
+                       "host memory, prefetched every step with cudaMemcpyAsync on a side stream" if cfg.offload
+                       else "off", "kv_prefetch_bytes_per_step_per_gpu": kv_bytes_step,
+                       "l2": "per-step working set (expert weights + KV) is far larger than the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
+            "gpu_launches": launches,
+            "kv_copies_total": kv_stats["copies"],
+        }))
+    model.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

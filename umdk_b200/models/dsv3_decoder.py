@@ -1,0 +1,237 @@
+"""DeepSeek-V3-shaped MoE decoder for the serving decode step (one token per sequence per step).
+
+Per layer: RMSNorm -> multi-head latent attention with absorbed projections, computed by the sparse top-k MLA
+flash-decode kernel over a paged KV cache whose second half of pages lives in pinned host memory and is prefetched
+on a side stream -> RMSNorm -> softmax top-k router -> expert-parallel low-latency MoE (fp8 dispatch, tcgen05 grouped
+GEMMs, combine fused in the down-projection epilogue) plus a shared expert. Attention is data parallel (every rank
+decodes its own batch), experts are sharded over the ranks of the EP group.
+
+Dense projections (q/kv/o, router, lm_head) are plain library GEMMs through torch.matmul. The reference project has
+no model code; the architecture and shapes come from the serving benchmark configuration.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from ..ops import reference as ref
+from ..ops.attention import DIM as KV_DIM, DIM_V, HEADS, PAGE, sparse_mla_decode
+from ..ops.ep_ll import EpLowLatency, ExpertWeights
+from ..ops.kv_offload import KvOffloadManager
+from ..parallel.symm import SymmetricHeap
+
+
+@dataclass
+class DecoderConfig:
+    hidden: int = 7168
+    n_layers: int = 4
+    q_lora: int = 1536
+    qk_nope: int = 128
+    qk_rope: int = 64
+    v_head: int = 128
+    n_experts: int = 256
+    top_k: int = 8
+    moe_ffn: int = 2048
+    shared_expert: bool = True
+    vocab: int = 129280
+    batch: int = 64          # sequences per rank
+    ctx: int = 32768         # tokens already in the cache
+    topk_kv: int = 2048      # KV rows attended per query
+    offload: bool = True     # second half of each sequence's pages in pinned host memory
+    rope_theta: float = 10000.0
+    seed: int = 0
+
+    @staticmethod
+    def tiny() -> "DecoderConfig":
+        return DecoderConfig(hidden=1024, n_layers=2, q_lora=256, n_experts=16, top_k=4, moe_ffn=256, vocab=2048,
+                             batch=8, ctx=1024, topk_kv=256)
+
+
+def _quant_experts(n: int, rows: int, cols: int, gen_device, gen: torch.Generator, std: float = 0.02):
+    """n expert matrices [rows, cols] drawn N(0, std) in bf16, quantised to fp8 e4m3 with 128x128 block scales."""
+    q = torch.empty(n, rows, cols, dtype=torch.uint8, device=gen_device).view(torch.float8_e4m3fn)
+    s = torch.empty(n, rows // 128, cols // 128, dtype=torch.float32, device=gen_device)
+    for i in range(n):
+        w = torch.randn(rows, cols, device=gen_device, generator=gen, dtype=torch.float32) * std
+        wf = w.reshape(rows // 128, 128, cols // 128, 128)
+        amax = wf.abs().amax(dim=(1, 3)).clamp_min(1e-4)
+        q[i] = (wf * (448.0 / amax)[:, None, :, None]).reshape(rows, cols).to(torch.float8_e4m3fn)
+        s[i] = amax / 448.0
+    return q, s
+
+
+class DecoderRank:
+    """One rank's shard of the decoder plus its KV cache, offload manager and EP state."""
+
+    def __init__(self, cfg: DecoderConfig, group: Optional[dist.ProcessGroup] = None, device=None):
+        self.cfg = cfg
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        dev = device or torch.device("cuda", torch.cuda.current_device())
+        self.device = dev
+        c = cfg
+        assert c.n_experts % self.world == 0 and c.ctx % PAGE == 0 and (c.ctx // PAGE) % 2 == 0
+        H = c.hidden
+        g = torch.Generator(device=dev).manual_seed(c.seed)  # replicated weights: same seed on every rank
+        bf = torch.bfloat16
+
+        def lin(o, i):
+            return (torch.randn(o, i, device=dev, generator=g, dtype=torch.float32) * 0.02).to(bf)
+
+        self.embed = lin(c.vocab, H)
+        self.lm_head = lin(c.vocab, H)
+        self.final_norm = torch.ones(H, device=dev, dtype=bf)
+        self.layers = []
+        for _ in range(c.n_layers):
+            L = {}
+            L["attn_norm"] = torch.ones(H, device=dev, dtype=bf)
+            L["wq_a"] = lin(c.q_lora, H)
+            L["q_norm"] = torch.ones(c.q_lora, device=dev, dtype=bf)
+            L["wq_b"] = lin(HEADS * (c.qk_nope + c.qk_rope), c.q_lora)
+            L["wkv_a"] = lin(DIM_V + c.qk_rope, H)
+            L["kv_norm"] = torch.ones(DIM_V, device=dev, dtype=bf)
+            L["w_uk"] = (torch.randn(HEADS, c.qk_nope, DIM_V, device=dev, generator=g) * 0.02).to(bf)
+            L["w_uv"] = (torch.randn(HEADS, DIM_V, c.v_head, device=dev, generator=g) * 0.02).to(bf)
+            L["wo"] = lin(H, HEADS * c.v_head)
+            L["ffn_norm"] = torch.ones(H, device=dev, dtype=bf)
+            L["router"] = torch.randn(c.n_experts, H, device=dev, generator=g, dtype=torch.float32) * 0.02
+            self.layers.append(L)
+        # expert shards: a different stream per rank
+        ge = torch.Generator(device=dev).manual_seed(c.seed + 1000 + self.rank)
+        el = c.n_experts // self.world
+        for L in self.layers:
+            w1q, w1s = _quant_experts(el, 2 * c.moe_ffn, H, dev, ge)
+            w2q, w2s = _quant_experts(el, H, c.moe_ffn, dev, ge)
+            L["experts"] = ExpertWeights(w1q, w1s, w2q, w2s)
+            if c.shared_expert:
+                s1q, s1s = _quant_experts(1, 2 * c.moe_ffn, H, dev, g)
+                s2q, s2s = _quant_experts(1, H, c.moe_ffn, dev, g)
+                L["shared"] = ExpertWeights(s1q, s1s, s2q, s2s)
+            else:
+                L["shared"] = None
+        # EP state
+        nbytes = EpLowLatency.heap_bytes(self.world, c.n_experts, c.top_k, H, c.batch)
+        self.heap = SymmetricHeap(nbytes, group) if self.world > 1 else SymmetricHeap(nbytes)
+        self.ep = EpLowLatency(self.heap, c.n_experts, c.top_k, H, c.moe_ffn, c.batch)
+        # KV cache: pages [0, P/2) resident, [P/2, P) staged from host, page P holds the token being decoded
+        B = c.batch
+        P = c.ctx // PAGE
+        self.pages_per_seq = P + 1
+        half = P // 2
+        self.n_resident = B * (half + 1)
+        self.n_staging = B * half
+        n_dev_pages = self.n_resident + self.n_staging
+        bt = torch.empty(B, P + 1, dtype=torch.int32)
+        for b in range(B):
+            bt[b, :half] = torch.arange(half) + b * (half + 1)
+            bt[b, half:P] = self.n_resident + b * half + torch.arange(half)
+            bt[b, P] = b * (half + 1) + half
+        self.block_table = bt.to(dev)
+        self.new_page = bt[:, P].to(dev).long()
+        self.kv = []
+        gk = torch.Generator(device=dev).manual_seed(c.seed + 5000 + self.rank)
+        for _ in range(c.n_layers):
+            pool = torch.empty(n_dev_pages, PAGE, KV_DIM, device=dev, dtype=bf)
+            for s0 in range(0, n_dev_pages, 4096):
+                s1 = min(n_dev_pages, s0 + 4096)
+                pool[s0:s1] = (torch.randn(s1 - s0, PAGE, KV_DIM, device=dev, generator=gk) * 0.5).to(bf)
+            self.kv.append(pool)
+        self.kvm = None
+        if c.offload:
+            page_bytes = PAGE * KV_DIM * 2
+            self.kvm = KvOffloadManager(page_bytes, c.n_layers * self.n_staging, channels=c.n_layers)
+            self._dev_ids = (ctypes.c_int * self.n_staging)(*range(self.n_resident, self.n_resident + self.n_staging))
+            self._host_ids = []
+            for l in range(c.n_layers):
+                hs = list(range(l * self.n_staging, (l + 1) * self.n_staging))
+                self._host_ids.append((ctypes.c_int * self.n_staging)(*hs))
+                # move the staged half out to pinned host memory (the state every decode step starts from)
+                self.kvm.offload(self.kv[l], list(self._dev_ids), hs)
+            self.kvm.sync()
+        pos = float(c.ctx)
+        inv_freq = 1.0 / (c.rope_theta ** (torch.arange(0, c.qk_rope, 2, device=dev, dtype=torch.float32) / c.qk_rope))
+        self.cos = torch.cos(pos * inv_freq)
+        self.sin = torch.sin(pos * inv_freq)
+        self.sm_scale = 1.0 / math.sqrt(c.qk_nope + c.qk_rope)
+        self.attn_status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.kernel_launches_per_step = 0
+        self._prefetched = False
+
+    # ------------------------------------------------------------------------------------------------------------
+    def _rope(self, x: torch.Tensor) -> torch.Tensor:
+        x1, x2 = x[..., 0::2].float(), x[..., 1::2].float()
+        out = torch.stack((x1 * self.cos - x2 * self.sin, x1 * self.sin + x2 * self.cos), dim=-1)
+        return out.flatten(-2).to(x.dtype)
+
+    def prefetch(self):
+        """Queues the host -> device copies of the staged KV pages of every layer on the side stream."""
+        if self.kvm is None:
+            return
+        for l in range(self.cfg.n_layers):
+            self.kvm.prefetch(l, self.kv[l], self._dev_ids, self._host_ids[l], self.n_staging)
+        self._prefetched = True
+
+    def _layer(self, l: int, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        c, L = self.cfg, self.layers[l]
+        B, H = x.shape
+        h = F.rms_norm(x, (H,), L["attn_norm"])
+        qa = F.rms_norm(h @ L["wq_a"].t(), (c.q_lora,), L["q_norm"])
+        q = (qa @ L["wq_b"].t()).view(B, HEADS, c.qk_nope + c.qk_rope)
+        kva = h @ L["wkv_a"].t()
+        ckv = F.rms_norm(kva[:, :DIM_V], (DIM_V,), L["kv_norm"])
+        krope = self._rope(kva[:, DIM_V:])
+        self.kv[l][self.new_page, 0] = torch.cat((ckv, krope), dim=-1)
+        q_lat = torch.einsum("bhd,hdc->bhc", q[..., :c.qk_nope], L["w_uk"])
+        q_full = torch.cat((q_lat, self._rope(q[..., c.qk_nope:])), dim=-1).contiguous()
+        if self.kvm is not None:
+            self.kvm.wait(l)
+        o_lat, _ = sparse_mla_decode(q_full, self.kv[l], self.block_table, indices, self.sm_scale,
+                                     status=self.attn_status)
+        if self.kvm is not None:
+            self.kvm.release(l)
+        o = torch.einsum("bhc,hcd->bhd", o_lat, L["w_uv"]).reshape(B, HEADS * c.v_head)
+        x = x + o @ L["wo"].t()
+        h = F.rms_norm(x, (H,), L["ffn_norm"])
+        probs = torch.softmax(h.float() @ L["router"].t(), dim=-1)
+        w, idx = torch.topk(probs, c.top_k, dim=-1)
+        w = (w / w.sum(dim=-1, keepdim=True)).contiguous()
+        moe, share, _ = self.ep.moe(h.contiguous(), idx.contiguous(), w, L["experts"], L["shared"])
+        x = x + moe
+        if share is not None:
+            x = x + share
+        return x
+
+    def step(self, tokens: torch.Tensor, indices: List[torch.Tensor]) -> torch.Tensor:
+        """tokens [B] int64 (device), indices[l] [B, topk_kv] int32 (device) -> next tokens [B] int64 (device)."""
+        if self.kvm is not None and not self._prefetched:
+            self.prefetch()
+        self._prefetched = False
+        x = self.embed[tokens]
+        for l in range(self.cfg.n_layers):
+            x = self._layer(l, x, indices[l])
+        x = F.rms_norm(x, (self.cfg.hidden,), self.final_norm)
+        logits = x @ self.lm_head.t()
+        return torch.argmax(logits, dim=-1)
+
+    def check(self):
+        from ..ops.ep import check_status
+        self.ep.check("decoder MoE")
+        check_status(self.attn_status, "sparse_mla_decode")
+
+    def close(self):
+        if self.kvm is not None:
+            self.kvm.close()
+        self.heap.close()
+
+
+def reference_layer_moe(cfg: DecoderConfig, h: torch.Tensor, idx: torch.Tensor, w: torch.Tensor,
+                        experts: ExpertWeights) -> torch.Tensor:
+    """fp32 oracle of one rank's MoE output when the EP group has a single rank (used by tests)."""
+    return ref.ref_fused_moe(h, idx, w, experts.w1q, experts.w1s, experts.w2q, experts.w2s)
