@@ -756,3 +756,66 @@ UMDK_API int umdk_ep_combine(const UmdkEpCombineParams* p, void* stream) {
   UMDK_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// Allocation-free layout entry point (see ep_layout_noalloc.h for who needs it and the rules that come with it)
+// ------------------------------------------------------------------------------------------------------------
+#include "ep_layout_noalloc.h"
+
+#include <mutex>
+
+// Layout of the array: [0, 256) bytes = grid-barrier words (two uint32 used), then the per-chunk histogram.
+// In host code this name is only a stand-in for the symbol; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_layout_noalloc_scratch[UMDK_EP_LAYOUT_NOALLOC_BYTES];
+
+static int layout_noalloc_scratch_ptr(unsigned char** out) {
+  static std::mutex mu;
+  static unsigned char* per_device[64] = {nullptr};
+  int dev = -1;
+  UMDK_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return -UMDK_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lock(mu);
+  if (per_device[dev] == nullptr) {
+    void* p = nullptr;
+    UMDK_CUDA_CHECK(cudaGetSymbolAddress(&p, g_layout_noalloc_scratch));
+    per_device[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = per_device[dev];
+  return 0;
+}
+
+UMDK_API int umdk_ep_layout_noalloc(const int64_t* topk_idx, int T, int K, int E, int R, int* num_per_expert,
+                                    int* num_per_rank, uint8_t* in_rank, int* send_idx, int* rank_slot, int* status,
+                                    void* stream) {
+  if (T < 0 || K < 1 || K > kMaxTopk || R < 1 || R > kMaxRanks || E < R || (E % R)) return -UMDK_ERR_BAD_ARG;
+  if (T > UMDK_EP_LAYOUT_NOALLOC_MAX_TOKENS || E + R > UMDK_EP_LAYOUT_NOALLOC_MAX_COLS) {
+    fprintf(stderr,
+            "[umdk] umdk_ep_layout_noalloc: T=%d (max %d) or num_experts+num_ranks=%d (max %d) exceeds the built-in "
+            "scratch; use umdk_ep_layout with caller-provided scratch instead\n",
+            T, UMDK_EP_LAYOUT_NOALLOC_MAX_TOKENS, E + R, UMDK_EP_LAYOUT_NOALLOC_MAX_COLS);
+    return -UMDK_ERR_BAD_ARG;
+  }
+  unsigned char* base = nullptr;
+  if (int rc = layout_noalloc_scratch_ptr(&base)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    UMDK_CUDA_CHECK(cudaMemsetAsync(num_per_expert, 0, sizeof(int) * E, s));
+    UMDK_CUDA_CHECK(cudaMemsetAsync(num_per_rank, 0, sizeof(int) * R, s));
+    return 0;
+  }
+  uint32_t* bar = reinterpret_cast<uint32_t*>(base);
+  int* scratch = reinterpret_cast<int*>(base + 256);
+  // the barrier must start from a clean arrival count even if an earlier call was cut short
+  UMDK_CUDA_CHECK(cudaMemsetAsync(bar, 0, 2 * sizeof(uint32_t), s));
+  const int chunks = (T + 31) / 32;
+  int grid = (chunks + kLayoutWarps - 1) / kLayoutWarps;
+  if (grid > sm_count()) grid = sm_count();
+  const size_t smem = sizeof(int) * (size_t)kLayoutWarps * ((E + R) + 32 * kMaxTopk);
+  if (smem > 48 * 1024) {
+    UMDK_CUDA_CHECK(cudaFuncSetAttribute(ep_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  ep_layout_kernel<<<grid, kLayoutWarps * 32, smem, s>>>(topk_idx, T, K, E, R, num_per_expert, num_per_rank, in_rank,
+                                                         send_idx, rank_slot, scratch, bar, status);
+  UMDK_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
