@@ -1,0 +1,206 @@
+#!/usr/bin/env python
+"""Single-GPU timing of the individual hand-written kernels with their roofline fractions.
+
+    python bench/kernel_bench.py moe_gemm1 --tokens-per-expert 32 --experts 32
+    python bench/kernel_bench.py moe_gemm2 | mla | dispatch | combine | gemm_bf16 | quant | all
+
+Timing hygiene: >= 3 warm-up launches, an L2 flush (256 MB write) before every timed launch, CUDA events on the
+launching stream. The same role as the reference's `bench()` helper (src/cam/examples/utils.py:67-101: 256 MB L2
+flush, event timing). Roofline denominators come from MEASURED_PEAKS.json at the repo root when present
+(6553 GB/s copy bandwidth, 1602.6 TFLOP/s bf16 burst), otherwise the fallback 6650 GB/s / 1590 TFLOP/s.
+`--small` shrinks a case so that a profiler capture of it stays short.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from umdk_b200.ops import reference as ref  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def time_kernel(fn, iters=10, warmup=3):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2] * 1e-3, ts[0] * 1e-3
+
+
+def report(name, sec_med, sec_min, bytes_, flops, extra=None):
+    hbm, tf, how = peaks()
+    gbs = bytes_ / sec_med / 1e9
+    tfl = flops / sec_med / 1e12
+    t_roof = max(bytes_ / (hbm * 1e9), flops / (tf * 1e12))
+    out = {"kernel": name, "us": sec_med * 1e6, "us_min": sec_min * 1e6, "GB/s": gbs, "TFLOP/s": tfl,
+           "frac_of_hbm_" + how: gbs / hbm, "frac_of_bf16_" + how: tfl / tf, "roofline_us": t_roof * 1e6,
+           "frac_of_roofline": t_roof / sec_med}
+    if extra:
+        out.update(extra)
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def _rand_fp8(*shape):
+    # random e4m3 payload in [-1.75, 1.75] without going through a large fp32 tensor
+    b = torch.randint(0, 0x40, shape, dtype=torch.uint8, device="cuda")
+    b |= (torch.randint(0, 2, shape, dtype=torch.uint8, device="cuda") << 7)
+    return b.view(torch.float8_e4m3fn)
+
+
+def bench_moe_gemm(which, experts, tpe, H=7168, F=2048):
+    from umdk_b200.ops import moe_gemm
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    N = experts * tpe
+    off = (torch.arange(experts + 1, dtype=torch.int32) * tpe).cuda()
+    if which == 1:
+        xq, xs = _rand_fp8(N, H), torch.rand(N, H // 128, device="cuda") * 0.01 + 0.005
+        wq, ws = _rand_fp8(experts, 2 * F, H), torch.rand(experts, 2 * F // 128, H // 128, device="cuda") * 0.01
+        hq = torch.empty(N, F, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+        hs = torch.empty(N, F // 128, dtype=torch.float32, device="cuda")
+        fn = lambda: moe_gemm.gemm1_swiglu_quant(xq, xs, off, wq, ws, status, hq, hs)
+        bytes_ = wq.numel() + ws.numel() * 4 + xq.numel() + xs.numel() * 4 + hq.numel() + hs.numel() * 4
+        flops = 2.0 * N * 2 * F * H
+        name = "moe_gemm_mode0(gate/up+SwiGLU+requant)"
+    else:
+        xq, xs = _rand_fp8(N, F), torch.rand(N, F // 128, device="cuda") * 0.01 + 0.005
+        wq, ws = _rand_fp8(experts, H, F), torch.rand(experts, H // 128, F // 128, device="cuda") * 0.01
+        y = torch.empty(N, H, dtype=torch.bfloat16, device="cuda")
+        fn = lambda: moe_gemm.gemm2(xq, xs, off, wq, ws, status, y)
+        bytes_ = wq.numel() + ws.numel() * 4 + xq.numel() + xs.numel() * 4 + y.numel() * 2
+        flops = 2.0 * N * H * F
+        name = "moe_gemm_mode1(down)"
+    med, mn = time_kernel(fn)
+    assert status.tolist()[0] == 0, status.tolist()
+    return report(name, med, mn, bytes_, flops, {"experts": experts, "tokens_per_expert": tpe, "H": H, "F": F})
+
+
+def bench_mla(B, ctx, topk):
+    from umdk_b200.ops.attention import DIM, HEADS, PAGE, sparse_mla_decode
+    pps = ctx // PAGE
+    kv = (torch.randn(B * pps, PAGE, DIM, device="cuda") * 0.5).to(torch.bfloat16)
+    bt = torch.arange(B * pps, dtype=torch.int32, device="cuda").reshape(B, pps)
+    q = (torch.randn(B, HEADS, DIM, device="cuda") * 0.5).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(ctx, device="cuda")[:topk] for _ in range(B)]).to(torch.int32)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = torch.empty(B, HEADS, 512, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: sparse_mla_decode(q, kv, bt, idx, DIM ** -0.5, out=out, status=status)
+    med, mn = time_kernel(fn)
+    assert status.tolist()[0] == 0
+    bytes_ = B * topk * DIM * 2 + q.numel() * 2 + out.numel() * 2
+    flops = 2.0 * B * HEADS * topk * (DIM + 512)
+    return report("sparse_mla_decode", med, mn, bytes_, flops, {"B": B, "ctx": ctx, "topk": topk})
+
+
+def bench_dispatch_combine(T, H, E, K):
+    """World size 1: every token stays on the GPU, so this measures the kernels' local memory path only."""
+    from umdk_b200.ops.ep import EpNormal
+    from umdk_b200.parallel.symm import SymmetricHeap
+    heap = SymmetricHeap(EpNormal.heap_bytes(1, E, K, H, T))
+    st = EpNormal(heap, E, K, H, T)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    idx = torch.topk(torch.rand(T, E, device="cuda"), K, dim=-1).indices.to(torch.int64)
+    w = torch.rand(T, K, device="cuda")
+    lay = st.layout(idx)
+    out = st.dispatch(x, idx, w, lay=lay, quant=True)
+    res = []
+    med, mn = time_kernel(lambda: st.layout(idx))
+    res.append(report("ep_layout", med, mn, idx.numel() * 8 + T * K * 4 + T * 4, 0, {"T": T, "E": E, "K": K}))
+    med, mn = time_kernel(lambda: st.dispatch(x, idx, w, lay=lay, quant=True, out=out))
+    n = T * K
+    bytes_ = x.numel() * 2 + 2 * T * (H + H // 32) + n * (H + H // 32)  # read x, write+read arrivals, write rows
+    res.append(report("ep_dispatch(world=1)", med, mn, bytes_, 0, {"T": T, "H": H, "rows": n}))
+    y = torch.randn(out.recv_x.shape[0], H, device="cuda").to(torch.bfloat16)
+    o = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    med, mn = time_kernel(lambda: st.combine(y, out, out=o))
+    bytes_ = n * H * 2 + 2 * T * H * 2 + T * H * 2
+    res.append(report("ep_combine(world=1)", med, mn, bytes_, 0, {"T": T, "H": H, "rows": n}))
+    st.check()
+    heap.close()
+    return res
+
+
+def bench_gemm_bf16(M, N, K):
+    from umdk_b200 import _native
+    lib = _native.cam()
+    A = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    B = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    C = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    st = torch.zeros(4, dtype=torch.int32, device="cuda")
+
+    def fn():
+        rc = lib.umdk_gemm_bf16(_native.ptr(A), _native.ptr(B), _native.ptr(C), M, N, K, K, K, N, _native.ptr(st),
+                                _native.stream_ptr(), 0)
+        assert rc == 0
+    med, mn = time_kernel(fn)
+    r = report("gemm_bf16_tcgen05", med, mn, (M * K + N * K + M * N) * 2, 2.0 * M * N * K, {"M": M, "N": N, "K": K})
+    med, mn = time_kernel(lambda: torch.matmul(A, B.t(), out=C))
+    report("cublas_bf16(torch.matmul)", med, mn, (M * K + N * K + M * N) * 2, 2.0 * M * N * K, {"M": M, "N": N, "K": K})
+    return r
+
+
+def bench_quant(T, H):
+    from umdk_b200.ops.ep_ll import quant_fp8_1x128
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    med, mn = time_kernel(lambda: quant_fp8_1x128(x))
+    return report("quant_fp8_1x128", med, mn, T * H * 3 + T * H // 32, 0, {"T": T, "H": H})
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["moe_gemm1", "moe_gemm2", "mla", "dispatch", "gemm_bf16", "quant", "all"])
+    ap.add_argument("--experts", type=int, default=32)
+    ap.add_argument("--tokens-per-expert", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--topk", type=int, default=2048)
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--small", action="store_true")
+    a = ap.parse_args()
+    if a.small:
+        a.experts, a.batch, a.ctx, a.tokens = min(a.experts, 8), min(a.batch, 16), min(a.ctx, 8192), min(a.tokens, 1024)
+    if a.what in ("moe_gemm1", "all"):
+        bench_moe_gemm(1, a.experts, a.tokens_per_expert)
+    if a.what in ("moe_gemm2", "all"):
+        bench_moe_gemm(2, a.experts, a.tokens_per_expert)
+    if a.what in ("mla", "all"):
+        bench_mla(a.batch, a.ctx, a.topk)
+    if a.what in ("dispatch", "all"):
+        bench_dispatch_combine(a.tokens, 7168, 256, 8)
+    if a.what in ("gemm_bf16", "all"):
+        bench_gemm_bf16(8192, 8192, 8192) if not a.small else bench_gemm_bf16(4096, 4096, 4096)
+    if a.what in ("quant", "all"):
+        bench_quant(a.tokens, 7168)
+
+
+if __name__ == "__main__":
+    main()

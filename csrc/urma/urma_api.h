@@ -1,0 +1,125 @@
+/* URMA northbound API. Function names and argument order follow the reference's
+ * src/urma/lib/urma/core/include/urma_api.h (init :27-33, devices :42-89, context :97-112, JFC :120-198,
+ * JFS :206-304, JFR :312-460, Jetty :472-735, jetty group :747-754, JFCE :761-768, async events :776-783,
+ * token id :790-807, segments :816-857, post WR :866-893, write/read/send/recv :908-952,
+ * poll/rearm/wait/ack :962-994, user_ctl :1001-1011, logging :1018-1057) and urma_perf.h:60-74. */
+#ifndef UMDK_URMA_API_H
+#define UMDK_URMA_API_H
+
+#include "urma_types.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#define URMA_EXPORT __attribute__((visibility("default")))
+
+/* lifecycle */
+URMA_EXPORT urma_status_t urma_init(const urma_init_attr_t* attr);
+URMA_EXPORT urma_status_t urma_uninit(void);
+/* devices */
+URMA_EXPORT urma_device_t** urma_get_device_list(int* num_devices);
+URMA_EXPORT void urma_free_device_list(urma_device_t** list);
+URMA_EXPORT urma_device_t* urma_get_device_by_name(const char* name);
+URMA_EXPORT urma_device_t* urma_get_device_by_eid(urma_eid_t eid);
+URMA_EXPORT urma_status_t urma_query_device(urma_device_t* dev, urma_device_attr_t* attr);
+URMA_EXPORT urma_eid_info_t* urma_get_eid_list(urma_device_t* dev, uint32_t* cnt);
+URMA_EXPORT void urma_free_eid_list(urma_eid_info_t* list);
+URMA_EXPORT int urma_str_to_eid(const char* s, urma_eid_t* eid);
+URMA_EXPORT void urma_eid_to_str(const urma_eid_t* eid, char* buf, size_t len);
+/* context */
+URMA_EXPORT urma_context_t* urma_create_context(urma_device_t* dev, uint32_t eid_index);
+URMA_EXPORT urma_status_t urma_delete_context(urma_context_t* ctx);
+URMA_EXPORT uint32_t urma_get_uasid(urma_context_t* ctx);
+/* JFC / JFCE */
+URMA_EXPORT urma_jfc_t* urma_create_jfc(urma_context_t* ctx, const urma_jfc_cfg_t* cfg);
+URMA_EXPORT urma_status_t urma_modify_jfc(urma_jfc_t* jfc, uint32_t moderate_count, uint32_t moderate_period);
+URMA_EXPORT urma_status_t urma_delete_jfc(urma_jfc_t* jfc);
+URMA_EXPORT urma_jfce_t* urma_create_jfce(urma_context_t* ctx);
+URMA_EXPORT urma_status_t urma_delete_jfce(urma_jfce_t* jfce);
+/* JFS */
+URMA_EXPORT urma_jfs_t* urma_create_jfs(urma_context_t* ctx, const urma_jfs_cfg_t* cfg);
+URMA_EXPORT urma_status_t urma_modify_jfs(urma_jfs_t* jfs, urma_jetty_state_t state);
+URMA_EXPORT urma_status_t urma_query_jfs(urma_jfs_t* jfs, urma_jfs_cfg_t* cfg, urma_jetty_state_t* state);
+URMA_EXPORT int urma_flush_jfs(urma_jfs_t* jfs, int cr_cnt, urma_cr_t* cr);
+URMA_EXPORT urma_status_t urma_delete_jfs(urma_jfs_t* jfs);
+/* JFR */
+URMA_EXPORT urma_jfr_t* urma_create_jfr(urma_context_t* ctx, const urma_jfr_cfg_t* cfg);
+URMA_EXPORT urma_status_t urma_modify_jfr(urma_jfr_t* jfr, urma_jetty_state_t state, uint32_t rx_threshold);
+URMA_EXPORT urma_status_t urma_query_jfr(urma_jfr_t* jfr, urma_jfr_cfg_t* cfg, urma_jetty_state_t* state);
+URMA_EXPORT urma_status_t urma_delete_jfr(urma_jfr_t* jfr);
+URMA_EXPORT urma_target_jetty_t* urma_import_jfr(urma_context_t* ctx, const urma_rjfr_t* rjfr,
+                                                 const urma_token_t* token);
+URMA_EXPORT urma_status_t urma_unimport_jfr(urma_target_jetty_t* tjfr);
+URMA_EXPORT urma_status_t urma_advise_jfr(urma_jfs_t* jfs, urma_target_jetty_t* tjfr);
+URMA_EXPORT urma_status_t urma_unadvise_jfr(urma_jfs_t* jfs, urma_target_jetty_t* tjfr);
+/* Jetty */
+URMA_EXPORT urma_jetty_t* urma_create_jetty(urma_context_t* ctx, const urma_jetty_cfg_t* cfg);
+URMA_EXPORT urma_status_t urma_modify_jetty(urma_jetty_t* jetty, urma_jetty_state_t state);
+URMA_EXPORT urma_status_t urma_query_jetty(urma_jetty_t* jetty, urma_jetty_cfg_t* cfg, urma_jetty_state_t* state);
+URMA_EXPORT int urma_flush_jetty(urma_jetty_t* jetty, int cr_cnt, urma_cr_t* cr);
+URMA_EXPORT urma_status_t urma_delete_jetty(urma_jetty_t* jetty);
+URMA_EXPORT urma_target_jetty_t* urma_import_jetty(urma_context_t* ctx, const urma_rjetty_t* rjetty,
+                                                   const urma_token_t* token);
+URMA_EXPORT urma_status_t urma_unimport_jetty(urma_target_jetty_t* tjetty);
+URMA_EXPORT urma_status_t urma_bind_jetty(urma_jetty_t* jetty, urma_target_jetty_t* tjetty);
+URMA_EXPORT urma_status_t urma_unbind_jetty(urma_jetty_t* jetty);
+URMA_EXPORT urma_status_t urma_advise_jetty(urma_jetty_t* jetty, urma_target_jetty_t* tjetty);
+URMA_EXPORT urma_status_t urma_unadvise_jetty(urma_jetty_t* jetty, urma_target_jetty_t* tjetty);
+URMA_EXPORT urma_jetty_grp_t* urma_create_jetty_grp(urma_context_t* ctx, const char* name, uint32_t policy);
+URMA_EXPORT urma_status_t urma_delete_jetty_grp(urma_jetty_grp_t* grp);
+/* token ids and segments */
+URMA_EXPORT urma_token_id_t* urma_alloc_token_id(urma_context_t* ctx);
+URMA_EXPORT urma_status_t urma_free_token_id(urma_token_id_t* token_id);
+URMA_EXPORT urma_target_seg_t* urma_register_seg(urma_context_t* ctx, const urma_seg_cfg_t* cfg);
+URMA_EXPORT urma_status_t urma_unregister_seg(urma_target_seg_t* tseg);
+URMA_EXPORT urma_target_seg_t* urma_import_seg(urma_context_t* ctx, const urma_seg_t* seg, const urma_token_t* token,
+                                               uint64_t addr, uint32_t flag);
+URMA_EXPORT urma_status_t urma_unimport_seg(urma_target_seg_t* tseg);
+/* data plane */
+URMA_EXPORT urma_status_t urma_post_jfs_wr(urma_jfs_t* jfs, urma_jfs_wr_t* wr, urma_jfs_wr_t** bad_wr);
+URMA_EXPORT urma_status_t urma_post_jfr_wr(urma_jfr_t* jfr, urma_jfr_wr_t* wr, urma_jfr_wr_t** bad_wr);
+URMA_EXPORT urma_status_t urma_post_jetty_send_wr(urma_jetty_t* jetty, urma_jfs_wr_t* wr, urma_jfs_wr_t** bad_wr);
+URMA_EXPORT urma_status_t urma_post_jetty_recv_wr(urma_jetty_t* jetty, urma_jfr_wr_t* wr, urma_jfr_wr_t** bad_wr);
+URMA_EXPORT urma_status_t urma_write(urma_jfs_t* jfs, urma_target_jetty_t* tjfr, urma_target_seg_t* dst_tseg,
+                                     urma_target_seg_t* src_tseg, uint64_t dst, uint64_t src, uint32_t len,
+                                     uint32_t flag, uint64_t user_ctx);
+URMA_EXPORT urma_status_t urma_read(urma_jfs_t* jfs, urma_target_jetty_t* tjfr, urma_target_seg_t* dst_tseg,
+                                    urma_target_seg_t* src_tseg, uint64_t dst, uint64_t src, uint32_t len,
+                                    uint32_t flag, uint64_t user_ctx);
+URMA_EXPORT urma_status_t urma_send(urma_jfs_t* jfs, urma_target_jetty_t* tjfr, urma_target_seg_t* src_tseg,
+                                    uint64_t src, uint32_t len, uint32_t flag, uint64_t user_ctx);
+URMA_EXPORT urma_status_t urma_recv(urma_jfr_t* jfr, urma_target_seg_t* recv_tseg, uint64_t buf, uint32_t len,
+                                    uint64_t user_ctx);
+URMA_EXPORT int urma_poll_jfc(urma_jfc_t* jfc, int cr_cnt, urma_cr_t* cr);
+URMA_EXPORT urma_status_t urma_rearm_jfc(urma_jfc_t* jfc, bool solicited_only);
+URMA_EXPORT int urma_wait_jfc(urma_jfce_t* jfce, uint32_t jfc_cnt, int time_out, urma_jfc_t* jfc[]);
+URMA_EXPORT void urma_ack_jfc(urma_jfc_t* jfc[], uint32_t nevents[], uint32_t jfc_cnt);
+/* async events, user control */
+URMA_EXPORT urma_status_t urma_get_async_event(urma_context_t* ctx, urma_async_event_t* event);
+URMA_EXPORT void urma_ack_async_event(urma_async_event_t* event);
+URMA_EXPORT int urma_user_ctl(urma_context_t* ctx, urma_user_ctl_in_t* in, urma_user_ctl_out_t* out);
+/* logging */
+URMA_EXPORT urma_status_t urma_register_log_func(urma_log_cb_t func);
+URMA_EXPORT urma_status_t urma_unregister_log_func(void);
+URMA_EXPORT urma_vlog_level_t urma_log_get_level(void);
+URMA_EXPORT void urma_log_set_level(urma_vlog_level_t level);
+URMA_EXPORT void urma_log_set_thread_tag(const char* tag);
+URMA_EXPORT void urma_log(int level, const char* func, int line, const char* fmt, ...)
+    __attribute__((format(printf, 4, 5)));
+/* perf sampling of the data-plane calls */
+typedef enum urma_perf_op {
+  URMA_PERF_WRITE = 0, URMA_PERF_READ, URMA_PERF_SEND, URMA_PERF_RECV, URMA_PERF_POST_JFS, URMA_PERF_POST_JFR,
+  URMA_PERF_POST_JETTY_SEND, URMA_PERF_POST_JETTY_RECV, URMA_PERF_POLL_JFC, URMA_PERF_OP_MAX
+} urma_perf_op_t;
+typedef struct urma_perf_entry {
+  uint64_t count, min_ns, max_ns, avg_ns, p90_ns, p99_ns, p9999_ns;
+} urma_perf_entry_t;
+URMA_EXPORT urma_status_t urma_start_perf(void);
+URMA_EXPORT urma_status_t urma_stop_perf(void);
+URMA_EXPORT urma_status_t urma_get_perf_info(urma_perf_entry_t* entries /* [URMA_PERF_OP_MAX] */, char* text,
+                                             uint32_t* text_len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
