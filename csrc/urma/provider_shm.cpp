@@ -1,0 +1,1323 @@
+// "shm" URMA provider: a software NIC per context, connected through POSIX shared memory. It gives the whole
+// northbound API real semantics (one-sided write/read, atomics, two-sided send/recv with immediate data, completion
+// and event queues, tokens and access checks, error completions on timeouts) between threads and between processes
+// of one host, with no special hardware. It plays the role that the reference's hardware user driver plays
+// (src/urma/hw/udma: udma_u_jfs.c post_sq_wr / udma_u_jfc.c poll) and doubles as the fake device that the
+// reference's unit tests build with link-time mocks (test/urma/include/urma_hw_mock.h).
+//
+// Wire model: every context owns an "inbox", a bounded multi-producer ring in a shared-memory file. Initiators write
+// request messages (header + up to 4 KiB of payload per slot, larger transfers are fragmented) into the target's
+// inbox; the target's NIC thread executes them against the target process's memory after checking segment token,
+// bounds and access rights, and answers into the initiator's inbox; the initiator's NIC thread turns answers into
+// completion records. Pending requests carry a deadline, so a dead peer produces URMA_CR_ACK_TIMEOUT_ERR rather
+// than a hang.
+#include <errno.h>
+#include <fcntl.h>
+#include <poll.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/eventfd.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <deque>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include "ub_util.h"
+#include "urma_api.h"
+#include "urma_provider.h"
+
+namespace {
+
+constexpr uint32_t kSlotPayload = 4096;
+constexpr uint32_t kRingSlots = 1024;  // power of two
+constexpr uint32_t kMaxCtx = 256;
+constexpr uint32_t kRegMagic = 0x55524d41;  // "URMA"
+
+enum MsgType : uint32_t { MSG_WRITE = 1, MSG_READ, MSG_ATOMIC, MSG_SEND, MSG_RESP, MSG_RESP_DATA, MSG_PROBE };
+enum MsgFlag : uint32_t { F_FIRST = 1, F_LAST = 2, F_IMM = 4, F_WANT_ACK = 8 };
+
+struct MsgHdr {
+  uint32_t type, opcode, flags, status;
+  uint32_t src_uasid, src_jetty, dst_jetty, token_id;
+  uint32_t token_val, len, total_len, frag_off;
+  uint64_t remote_va, wr_id, operand, cmp;
+  uint8_t src_eid[16];
+};
+struct Slot {
+  std::atomic<uint64_t> seq;
+  MsgHdr h;
+  uint8_t payload[kSlotPayload];
+};
+struct Inbox {
+  std::atomic<uint32_t> magic;
+  std::atomic<uint32_t> owner_pid;
+  std::atomic<uint64_t> enq;
+  char pad0[48];
+  std::atomic<uint64_t> deq;
+  char pad1[56];
+  Slot slots[kRingSlots];
+};
+struct CtxSlot {
+  std::atomic<uint32_t> uasid;  // 0 = free
+  std::atomic<uint32_t> pid;
+  std::atomic<uint64_t> heartbeat_ns;
+};
+struct DevReg {
+  std::atomic<uint32_t> magic;
+  std::atomic<uint32_t> next_uasid;
+  std::atomic<uint32_t> next_jetty;
+  std::atomic<uint32_t> next_token;
+  CtxSlot ctx[kMaxCtx];
+};
+
+std::string shm_dir() {
+  const char* e = getenv("URMA_SHM_DIR");
+  if (e && *e) return e;
+  return "/dev/shm/umdk_urma_" + std::to_string(getuid());
+}
+
+void* map_file(const std::string& path, size_t bytes, bool create, bool* created = nullptr) {
+  int fd = open(path.c_str(), O_RDWR | (create ? O_CREAT : 0), 0600);
+  if (fd < 0) return nullptr;
+  struct stat st;
+  if (fstat(fd, &st) != 0) {
+    close(fd);
+    return nullptr;
+  }
+  if (static_cast<size_t>(st.st_size) < bytes) {
+    if (!create || ftruncate(fd, bytes) != 0) {
+      close(fd);
+      return nullptr;
+    }
+    if (created) *created = true;
+  }
+  void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  return p == MAP_FAILED ? nullptr : p;
+}
+
+// Vyukov bounded queue, multi-producer side. Returns the reserved slot or nullptr when the ring is full.
+Slot* ring_reserve(Inbox* in, uint64_t* pos_out) {
+  uint64_t pos = in->enq.load(std::memory_order_relaxed);
+  for (;;) {
+    Slot* s = &in->slots[pos & (kRingSlots - 1)];
+    const uint64_t seq = s->seq.load(std::memory_order_acquire);
+    const int64_t dif = static_cast<int64_t>(seq) - static_cast<int64_t>(pos);
+    if (dif == 0) {
+      if (in->enq.compare_exchange_weak(pos, pos + 1, std::memory_order_relaxed)) {
+        *pos_out = pos;
+        return s;
+      }
+    } else if (dif < 0) {
+      return nullptr;
+    } else {
+      pos = in->enq.load(std::memory_order_relaxed);
+    }
+  }
+}
+void ring_publish(Slot* s, uint64_t pos) { s->seq.store(pos + 1, std::memory_order_release); }
+
+struct Device {
+  std::string name;
+  urma_eid_t eid;
+  DevReg* reg = nullptr;
+};
+std::vector<Device> g_devs;
+std::mutex g_mu;
+
+struct SegReg {
+  uint64_t va, len;
+  uint32_t access, token_val;
+};
+struct RecvWr {
+  std::vector<urma_sge_t> sges;
+  uint64_t user_ctx;
+};
+struct Unexpected {
+  std::vector<uint8_t> data;
+  uint64_t imm;
+  bool has_imm;
+  uint32_t src_uasid, src_jetty;
+  uint64_t wr_id;
+  urma_eid_t src_eid;
+  bool want_ack;
+};
+struct ShmJfce {
+  urma_jfce_t pub;
+  int efd;
+  std::mutex mu;
+  std::deque<urma_jfc_t*> fired;
+};
+struct ShmJfc {
+  urma_jfc_t pub;
+  std::mutex mu;
+  std::deque<urma_cr_t> q;
+  bool armed = false;
+  uint32_t overflow = 0;
+};
+struct ShmCtx;
+struct RecvQueue {  // a JFR, or the receive half of a jetty
+  uint32_t id;
+  ShmJfc* jfc;
+  uint32_t depth;
+  uint32_t token_val;
+  std::mutex mu;
+  std::deque<RecvWr> posted;
+  std::deque<Unexpected> unexpected;
+  std::atomic<int> state{URMA_JETTY_STATE_READY};
+};
+struct SendQueue {
+  uint32_t id;
+  ShmJfc* jfc;
+  uint32_t depth;
+  std::atomic<int> state{URMA_JETTY_STATE_READY};
+  std::atomic<uint32_t> inflight{0};
+  uint32_t err_timeout_ms = 2000;
+};
+struct ShmJfs {
+  urma_jfs_t pub;
+  SendQueue sq;
+};
+struct ShmJfr {
+  urma_jfr_t pub;
+  RecvQueue rq;
+};
+struct ShmJetty {
+  urma_jetty_t pub;
+  SendQueue sq;
+  RecvQueue own_rq;
+  RecvQueue* rq;  // own_rq or a shared JFR's queue
+};
+struct Pending {
+  SendQueue* sq;
+  uint64_t user_ctx;
+  uint32_t flag;
+  urma_opcode_t opcode;
+  std::vector<urma_sge_t> local;  // destination of READ data / atomic old value
+  uint32_t total = 0, received = 0;
+  uint64_t deadline_ns;
+  urma_jetty_id_t remote;
+};
+struct Reasm {
+  std::vector<uint8_t> data;
+  uint32_t got = 0;
+};
+struct ShmCtx {
+  urma_context_t pub;
+  Device* dev;
+  Inbox* inbox = nullptr;
+  std::string inbox_path;
+  int reg_slot = -1;
+  std::thread nic;
+  std::atomic<bool> stop{false};
+  std::mutex mu;  // guards the tables below
+  std::unordered_map<uint32_t, SegReg> segs;
+  std::unordered_map<uint32_t, RecvQueue*> rqs;
+  std::unordered_map<uint64_t, Pending> pending;
+  std::atomic<uint64_t> next_wr{1};
+  std::unordered_map<uint32_t, Inbox*> peers;
+  std::map<std::pair<uint32_t, uint64_t>, Reasm> reasm;
+  std::deque<urma_async_event_t> events;
+  int event_fd = -1;
+};
+
+// ---------------------------------------------------------------------------------------------- helpers
+void push_cr(ShmJfc* jfc, const urma_cr_t& cr) {
+  if (!jfc) return;
+  ShmJfce* ce = nullptr;
+  {
+    std::lock_guard<std::mutex> l(jfc->mu);
+    if (jfc->q.size() >= jfc->pub.cfg.depth) {
+      ++jfc->overflow;
+      return;
+    }
+    jfc->q.push_back(cr);
+    if (jfc->armed && jfc->pub.cfg.jfce) {
+      jfc->armed = false;
+      ce = reinterpret_cast<ShmJfce*>(jfc->pub.cfg.jfce->priv);
+    }
+  }
+  if (ce) {
+    {
+      std::lock_guard<std::mutex> l(ce->mu);
+      ce->fired.push_back(&jfc->pub);
+    }
+    uint64_t one = 1;
+    if (write(ce->efd, &one, sizeof(one)) < 0) {
+    }
+  }
+}
+
+Inbox* peer_inbox(ShmCtx* c, uint32_t uasid) {
+  if (uasid == c->pub.uasid) return c->inbox;
+  std::lock_guard<std::mutex> l(c->mu);
+  auto it = c->peers.find(uasid);
+  if (it != c->peers.end()) return it->second;
+  const std::string path = shm_dir() + "/inbox_" + c->dev->name + "_" + std::to_string(uasid);
+  Inbox* in = static_cast<Inbox*>(map_file(path, sizeof(Inbox), false));
+  if (in && in->magic.load() != kRegMagic) {
+    munmap(in, sizeof(Inbox));
+    in = nullptr;
+  }
+  if (in) c->peers[uasid] = in;
+  return in;
+}
+
+// Blocks (bounded) until a slot is free in the target inbox. Returns false if the ring stayed full.
+bool send_msg(Inbox* in, const MsgHdr& h, const void* payload, uint32_t timeout_ms = 2000) {
+  const uint64_t t0 = ub::now_ns();
+  for (;;) {
+    uint64_t pos;
+    Slot* s = ring_reserve(in, &pos);
+    if (s) {
+      s->h = h;
+      if (h.len && payload) memcpy(s->payload, payload, h.len);
+      ring_publish(s, pos);
+      return true;
+    }
+    if (ub::now_ns() - t0 > uint64_t(timeout_ms) * 1000000ull) return false;
+    sched_yield();
+  }
+}
+
+// scatter `len` bytes at `src` into an SGE list starting at byte offset `off`
+void scatter(const std::vector<urma_sge_t>& sges, uint32_t off, const uint8_t* src, uint32_t len) {
+  for (const auto& g : sges) {
+    if (len == 0) break;
+    if (off >= g.len) {
+      off -= g.len;
+      continue;
+    }
+    const uint32_t n = std::min(len, g.len - off);
+    memcpy(reinterpret_cast<void*>(g.addr + off), src, n);
+    src += n;
+    len -= n;
+    off = 0;
+  }
+}
+uint32_t sg_len(const urma_sg_t& sg) {
+  uint32_t n = 0;
+  for (uint32_t i = 0; i < sg.num_sge; ++i) n += sg.sge[i].len;
+  return n;
+}
+
+urma_cr_status_t check_seg(ShmCtx* c, const MsgHdr& h, uint32_t need, uint64_t len) {
+  std::lock_guard<std::mutex> l(c->mu);
+  auto it = c->segs.find(h.token_id);
+  if (it == c->segs.end()) return URMA_CR_REM_ACCESS_ABORT_ERR;
+  const SegReg& s = it->second;
+  if (s.token_val != h.token_val) return URMA_CR_REM_ACCESS_ABORT_ERR;
+  if ((s.access & need) != need) return URMA_CR_REM_ACCESS_ABORT_ERR;
+  if (h.remote_va < s.va || h.remote_va + len > s.va + s.len) return URMA_CR_REM_OPERATION_ERR;
+  return URMA_CR_SUCCESS;
+}
+
+void reply(ShmCtx* c, const MsgHdr& req, uint32_t type, urma_cr_status_t st, uint64_t operand = 0,
+           const void* payload = nullptr, uint32_t len = 0, uint32_t off = 0, uint32_t flags = F_LAST) {
+  Inbox* in = peer_inbox(c, req.src_uasid);
+  if (!in) return;
+  MsgHdr r{};
+  r.type = type;
+  r.opcode = req.opcode;
+  r.flags = flags;
+  r.status = st;
+  r.src_uasid = c->pub.uasid;
+  r.wr_id = req.wr_id;
+  r.operand = operand;
+  r.len = len;
+  r.frag_off = off;
+  send_msg(in, r, payload);
+}
+
+// Delivers a complete incoming message into a posted receive buffer, or parks it until one is posted.
+void deliver(ShmCtx* c, RecvQueue* rq, Unexpected&& u) {
+  RecvWr wr;
+  {
+    std::lock_guard<std::mutex> l(rq->mu);
+    if (rq->posted.empty()) {
+      rq->unexpected.push_back(std::move(u));
+      return;
+    }
+    wr = std::move(rq->posted.front());
+    rq->posted.pop_front();
+  }
+  uint32_t cap = 0;
+  for (auto& g : wr.sges) cap += g.len;
+  urma_cr_t cr{};
+  cr.user_ctx = wr.user_ctx;
+  cr.flag = URMA_CR_FLAG_RECV;
+  cr.local_id = rq->id;
+  cr.remote_id.eid = u.src_eid;
+  cr.remote_id.uasid = u.src_uasid;
+  cr.remote_id.id = u.src_jetty;
+  cr.imm_data = u.imm;
+  cr.opcode = u.has_imm ? URMA_CR_OPC_SEND_WITH_IMM : URMA_CR_OPC_SEND;
+  urma_cr_status_t st = URMA_CR_SUCCESS;
+  if (u.data.size() > cap) {
+    st = URMA_CR_LOC_LEN_ERR;
+  } else {
+    scatter(wr.sges, 0, u.data.data(), static_cast<uint32_t>(u.data.size()));
+    cr.completion_len = static_cast<uint32_t>(u.data.size());
+  }
+  cr.status = st;
+  push_cr(rq->jfc, cr);
+  if (u.want_ack) {
+    MsgHdr req{};
+    req.src_uasid = u.src_uasid;
+    req.wr_id = u.wr_id;
+    req.opcode = URMA_OPC_SEND;
+    reply(c, req, MSG_RESP, st == URMA_CR_SUCCESS ? URMA_CR_SUCCESS : URMA_CR_REM_RESP_LEN_ERR);
+  }
+}
+
+void complete_pending(ShmCtx* c, uint64_t wr_id, urma_cr_status_t st, uint64_t operand, bool have_operand) {
+  Pending p;
+  {
+    std::lock_guard<std::mutex> l(c->mu);
+    auto it = c->pending.find(wr_id);
+    if (it == c->pending.end()) return;
+    p = std::move(it->second);
+    c->pending.erase(it);
+  }
+  if (have_operand && !p.local.empty() && st == URMA_CR_SUCCESS)
+    scatter(p.local, 0, reinterpret_cast<const uint8_t*>(&operand), 8);
+  p.sq->inflight.fetch_sub(1);
+  if ((p.flag & URMA_WR_FLAG_COMPLETE_ENABLE) || st != URMA_CR_SUCCESS) {
+    urma_cr_t cr{};
+    cr.status = st;
+    cr.user_ctx = p.user_ctx;
+    cr.local_id = p.sq->id;
+    cr.remote_id = p.remote;
+    cr.completion_len = p.total;
+    push_cr(p.sq->jfc, cr);
+  }
+  if (st != URMA_CR_SUCCESS) p.sq->state = URMA_JETTY_STATE_ERROR;
+}
+
+void handle(ShmCtx* c, Slot* s) {
+  const MsgHdr& h = s->h;
+  switch (h.type) {
+    case MSG_WRITE: {
+      urma_cr_status_t st = check_seg(c, h, URMA_ACCESS_WRITE, h.len);
+      if (st == URMA_CR_SUCCESS && h.len) memcpy(reinterpret_cast<void*>(h.remote_va), s->payload, h.len);
+      if (h.flags & F_LAST) {
+        if (st == URMA_CR_SUCCESS && (h.flags & F_IMM)) {  // WRITE_IMM / WRITE_NOTIFY consume a receive WR
+          RecvQueue* rq = nullptr;
+          {
+            std::lock_guard<std::mutex> l(c->mu);
+            auto it = c->rqs.find(h.dst_jetty);
+            if (it != c->rqs.end()) rq = it->second;
+          }
+          if (rq) {
+            RecvWr wr;
+            bool have = false;
+            {
+              std::lock_guard<std::mutex> l(rq->mu);
+              if (!rq->posted.empty()) {
+                wr = std::move(rq->posted.front());
+                rq->posted.pop_front();
+                have = true;
+              }
+            }
+            if (have) {
+              urma_cr_t cr{};
+              cr.user_ctx = wr.user_ctx;
+              cr.flag = URMA_CR_FLAG_RECV;
+              cr.opcode = URMA_CR_OPC_WRITE_WITH_IMM;
+              cr.imm_data = h.operand;
+              cr.completion_len = h.total_len;
+              cr.local_id = rq->id;
+              cr.remote_id.uasid = h.src_uasid;
+              cr.remote_id.id = h.src_jetty;
+              memcpy(cr.remote_id.eid.raw, h.src_eid, 16);
+              push_cr(rq->jfc, cr);
+            } else {
+              st = URMA_CR_RNR_RETRY_CNT_EXC_ERR;
+            }
+          } else {
+            st = URMA_CR_REM_OPERATION_ERR;
+          }
+        }
+        reply(c, h, MSG_RESP, st);
+      } else if (st != URMA_CR_SUCCESS) {
+        reply(c, h, MSG_RESP, st);
+      }
+      break;
+    }
+    case MSG_READ: {
+      urma_cr_status_t st = check_seg(c, h, URMA_ACCESS_READ, h.total_len);
+      if (st != URMA_CR_SUCCESS) {
+        reply(c, h, MSG_RESP, st);
+        break;
+      }
+      uint32_t off = 0;
+      while (off < h.total_len) {
+        const uint32_t n = std::min(kSlotPayload, h.total_len - off);
+        reply(c, h, MSG_RESP_DATA, URMA_CR_SUCCESS, 0, reinterpret_cast<void*>(h.remote_va + off), n, off,
+              off + n == h.total_len ? F_LAST : 0);
+        off += n;
+      }
+      break;
+    }
+    case MSG_ATOMIC: {
+      urma_cr_status_t st = check_seg(c, h, URMA_ACCESS_ATOMIC, 8);
+      uint64_t old = 0;
+      if (st == URMA_CR_SUCCESS && (h.remote_va & 7)) st = URMA_CR_REM_OPERATION_ERR;
+      if (st == URMA_CR_SUCCESS) {
+        uint64_t* p = reinterpret_cast<uint64_t*>(h.remote_va);
+        switch (h.opcode) {
+          case URMA_OPC_CAS: {
+            uint64_t exp = h.cmp;
+            __atomic_compare_exchange_n(p, &exp, h.operand, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST);
+            old = exp;
+            break;
+          }
+          case URMA_OPC_SWAP: old = __atomic_exchange_n(p, h.operand, __ATOMIC_SEQ_CST); break;
+          case URMA_OPC_FADD: old = __atomic_fetch_add(p, h.operand, __ATOMIC_SEQ_CST); break;
+          case URMA_OPC_FSUB: old = __atomic_fetch_sub(p, h.operand, __ATOMIC_SEQ_CST); break;
+          case URMA_OPC_FAND: old = __atomic_fetch_and(p, h.operand, __ATOMIC_SEQ_CST); break;
+          case URMA_OPC_FOR: old = __atomic_fetch_or(p, h.operand, __ATOMIC_SEQ_CST); break;
+          case URMA_OPC_FXOR: old = __atomic_fetch_xor(p, h.operand, __ATOMIC_SEQ_CST); break;
+          default: st = URMA_CR_REM_UNSUPPORTED_REQ_ERR;
+        }
+      }
+      reply(c, h, MSG_RESP, st, old);
+      break;
+    }
+    case MSG_SEND: {
+      RecvQueue* rq = nullptr;
+      {
+        std::lock_guard<std::mutex> l(c->mu);
+        auto it = c->rqs.find(h.dst_jetty);
+        if (it != c->rqs.end()) rq = it->second;
+      }
+      if (!rq || rq->state.load() != URMA_JETTY_STATE_READY || rq->token_val != h.token_val) {
+        if (h.flags & F_LAST) reply(c, h, MSG_RESP, rq ? URMA_CR_REM_ACCESS_ABORT_ERR : URMA_CR_REM_OPERATION_ERR);
+        break;
+      }
+      const auto key = std::make_pair(h.src_uasid, h.wr_id);
+      Reasm* r;
+      {
+        std::lock_guard<std::mutex> l(c->mu);
+        r = &c->reasm[key];
+      }
+      if (h.flags & F_FIRST) r->data.resize(h.total_len);
+      if (h.frag_off + h.len <= r->data.size() && h.len) memcpy(r->data.data() + h.frag_off, s->payload, h.len);
+      if (h.flags & F_LAST) {
+        Unexpected u;
+        u.data = std::move(r->data);
+        u.imm = h.operand;
+        u.has_imm = (h.flags & F_IMM) != 0;
+        u.src_uasid = h.src_uasid;
+        u.src_jetty = h.src_jetty;
+        u.wr_id = h.wr_id;
+        u.want_ack = true;
+        memcpy(u.src_eid.raw, h.src_eid, 16);
+        {
+          std::lock_guard<std::mutex> l(c->mu);
+          c->reasm.erase(key);
+        }
+        deliver(c, rq, std::move(u));
+      }
+      break;
+    }
+    case MSG_RESP: complete_pending(c, h.wr_id, static_cast<urma_cr_status_t>(h.status), h.operand,
+                                    h.opcode >= URMA_OPC_CAS && h.opcode <= URMA_OPC_FXOR); break;
+    case MSG_RESP_DATA: {
+      bool done = false;
+      {
+        std::lock_guard<std::mutex> l(c->mu);
+        auto it = c->pending.find(h.wr_id);
+        if (it != c->pending.end()) {
+          scatter(it->second.local, h.frag_off, s->payload, h.len);
+          it->second.received += h.len;
+          done = (h.flags & F_LAST) != 0;
+        }
+      }
+      if (done) complete_pending(c, h.wr_id, URMA_CR_SUCCESS, 0, false);
+      break;
+    }
+    case MSG_PROBE: reply(c, h, MSG_RESP, URMA_CR_SUCCESS); break;
+    default: break;
+  }
+}
+
+void nic_loop(ShmCtx* c) {
+  urma_log_set_thread_tag("shm-nic");
+  uint32_t idle = 0;
+  uint64_t last_scan = ub::now_ns();
+  while (!c->stop.load(std::memory_order_relaxed)) {
+    Inbox* in = c->inbox;
+    const uint64_t pos = in->deq.load(std::memory_order_relaxed);
+    Slot* s = &in->slots[pos & (kRingSlots - 1)];
+    if (s->seq.load(std::memory_order_acquire) == pos + 1) {
+      handle(c, s);
+      in->deq.store(pos + 1, std::memory_order_relaxed);
+      s->seq.store(pos + kRingSlots, std::memory_order_release);
+      idle = 0;
+      continue;
+    }
+    if (++idle < 4000) {
+      if ((idle & 63) == 0) sched_yield();
+    } else {
+      usleep(50);
+    }
+    const uint64_t now = ub::now_ns();
+    if (now - last_scan > 20000000ull) {  // every 20 ms: heartbeat + request deadlines
+      last_scan = now;
+      if (c->reg_slot >= 0) c->dev->reg->ctx[c->reg_slot].heartbeat_ns.store(now);
+      std::vector<uint64_t> expired;
+      {
+        std::lock_guard<std::mutex> l(c->mu);
+        for (auto& kv : c->pending)
+          if (now > kv.second.deadline_ns) expired.push_back(kv.first);
+      }
+      for (uint64_t id : expired) complete_pending(c, id, URMA_CR_ACK_TIMEOUT_ERR, 0, false);
+    }
+  }
+}
+
+ShmCtx* C(urma_context_t* ctx) { return reinterpret_cast<ShmCtx*>(ctx->priv); }
+
+// ---------------------------------------------------------------------------------------------- ops: queues
+urma_jfc_t* op_create_jfc(urma_context_t*, const urma_jfc_cfg_t* cfg) {
+  ShmJfc* j = new ShmJfc();
+  j->pub.cfg = *cfg;
+  j->pub.priv = j;
+  static std::atomic<uint32_t> ids{1};
+  j->pub.id = ids++;
+  return &j->pub;
+}
+urma_status_t op_modify_jfc(urma_jfc_t*, uint32_t, uint32_t) { return URMA_SUCCESS; }
+urma_status_t op_delete_jfc(urma_jfc_t* jfc) {
+  delete reinterpret_cast<ShmJfc*>(jfc->priv);
+  return URMA_SUCCESS;
+}
+urma_jfce_t* op_create_jfce(urma_context_t*) {
+  ShmJfce* e = new ShmJfce();
+  e->efd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+  e->pub.fd = e->efd;
+  e->pub.priv = e;
+  return &e->pub;
+}
+urma_status_t op_delete_jfce(urma_jfce_t* jfce) {
+  ShmJfce* e = reinterpret_cast<ShmJfce*>(jfce->priv);
+  close(e->efd);
+  delete e;
+  return URMA_SUCCESS;
+}
+
+uint32_t new_jetty_id(ShmCtx* c, uint32_t want) {
+  if (want) return want;
+  return c->dev->reg->next_jetty.fetch_add(1) + 1;
+}
+void fill_id(ShmCtx* c, urma_jetty_id_t* id, uint32_t n) {
+  id->eid = c->pub.eid;
+  id->uasid = c->pub.uasid;
+  id->id = n;
+}
+
+urma_jfs_t* op_create_jfs(urma_context_t* ctx, const urma_jfs_cfg_t* cfg) {
+  ShmCtx* c = C(ctx);
+  ShmJfs* j = new ShmJfs();
+  j->sq.id = new_jetty_id(c, 0);
+  j->sq.jfc = reinterpret_cast<ShmJfc*>(cfg->jfc->priv);
+  j->sq.depth = cfg->depth;
+  if (cfg->err_timeout) j->sq.err_timeout_ms = 100u << cfg->err_timeout;
+  fill_id(c, &j->pub.jfs_id, j->sq.id);
+  j->pub.priv = j;
+  return &j->pub;
+}
+urma_status_t op_modify_jfs(urma_jfs_t* jfs, urma_jetty_state_t st) {
+  reinterpret_cast<ShmJfs*>(jfs->priv)->sq.state = st;
+  return URMA_SUCCESS;
+}
+urma_status_t op_query_jfs(urma_jfs_t* jfs, urma_jfs_cfg_t* cfg, urma_jetty_state_t* st) {
+  *cfg = jfs->cfg;
+  *st = static_cast<urma_jetty_state_t>(reinterpret_cast<ShmJfs*>(jfs->priv)->sq.state.load());
+  return URMA_SUCCESS;
+}
+int flush_sq(ShmCtx* c, SendQueue* sq, int cr_cnt, urma_cr_t* cr) {
+  std::vector<uint64_t> ids;
+  {
+    std::lock_guard<std::mutex> l(c->mu);
+    for (auto& kv : c->pending)
+      if (kv.second.sq == sq) ids.push_back(kv.first);
+  }
+  int n = 0;
+  for (uint64_t id : ids) {
+    if (n >= cr_cnt) break;
+    Pending p;
+    {
+      std::lock_guard<std::mutex> l(c->mu);
+      auto it = c->pending.find(id);
+      if (it == c->pending.end()) continue;
+      p = std::move(it->second);
+      c->pending.erase(it);
+    }
+    sq->inflight.fetch_sub(1);
+    cr[n] = urma_cr_t{};
+    cr[n].status = URMA_CR_WR_FLUSH_ERR;
+    cr[n].user_ctx = p.user_ctx;
+    cr[n].local_id = sq->id;
+    ++n;
+  }
+  return n;
+}
+int op_flush_jfs(urma_jfs_t* jfs, int cr_cnt, urma_cr_t* cr) {
+  return flush_sq(C(jfs->ctx), &reinterpret_cast<ShmJfs*>(jfs->priv)->sq, cr_cnt, cr);
+}
+urma_status_t op_delete_jfs(urma_jfs_t* jfs) {
+  ShmJfs* j = reinterpret_cast<ShmJfs*>(jfs->priv);
+  urma_cr_t tmp[16];
+  while (flush_sq(C(jfs->ctx), &j->sq, 16, tmp) == 16) {
+  }
+  delete j;
+  return URMA_SUCCESS;
+}
+
+void rq_init(ShmCtx* c, RecvQueue* rq, const urma_jfr_cfg_t* cfg) {
+  rq->id = new_jetty_id(c, cfg->id);
+  rq->jfc = reinterpret_cast<ShmJfc*>(cfg->jfc->priv);
+  rq->depth = cfg->depth;
+  rq->token_val = cfg->token_value.token;
+  std::lock_guard<std::mutex> l(c->mu);
+  c->rqs[rq->id] = rq;
+}
+void rq_fini(ShmCtx* c, RecvQueue* rq) {
+  std::lock_guard<std::mutex> l(c->mu);
+  c->rqs.erase(rq->id);
+}
+urma_jfr_t* op_create_jfr(urma_context_t* ctx, const urma_jfr_cfg_t* cfg) {
+  ShmCtx* c = C(ctx);
+  ShmJfr* j = new ShmJfr();
+  rq_init(c, &j->rq, cfg);
+  fill_id(c, &j->pub.jfr_id, j->rq.id);
+  j->pub.priv = j;
+  return &j->pub;
+}
+urma_status_t op_modify_jfr(urma_jfr_t* jfr, urma_jetty_state_t st, uint32_t) {
+  reinterpret_cast<ShmJfr*>(jfr->priv)->rq.state = st;
+  return URMA_SUCCESS;
+}
+urma_status_t op_query_jfr(urma_jfr_t* jfr, urma_jfr_cfg_t* cfg, urma_jetty_state_t* st) {
+  *cfg = jfr->cfg;
+  *st = static_cast<urma_jetty_state_t>(reinterpret_cast<ShmJfr*>(jfr->priv)->rq.state.load());
+  return URMA_SUCCESS;
+}
+urma_status_t op_delete_jfr(urma_jfr_t* jfr) {
+  ShmJfr* j = reinterpret_cast<ShmJfr*>(jfr->priv);
+  rq_fini(C(jfr->ctx), &j->rq);
+  delete j;
+  return URMA_SUCCESS;
+}
+
+struct ShmTarget {
+  urma_target_jetty_t pub;
+  uint32_t token_val;
+};
+urma_target_jetty_t* op_import(urma_context_t* ctx, const urma_rjetty_t* rj, const urma_token_t* token) {
+  ShmCtx* c = C(ctx);
+  if (memcmp(rj->jetty_id.eid.raw, c->pub.eid.raw, 16) != 0) {
+    urma_log(URMA_VLOG_LEVEL_ERR, __func__, __LINE__, "remote jetty is on another device (EID mismatch)");
+    return nullptr;
+  }
+  if (!peer_inbox(c, rj->jetty_id.uasid)) {
+    urma_log(URMA_VLOG_LEVEL_ERR, __func__, __LINE__, "no context with uasid %u on %s", rj->jetty_id.uasid,
+             c->dev->name.c_str());
+    return nullptr;
+  }
+  ShmTarget* t = new ShmTarget();
+  t->pub.id = rj->jetty_id;
+  t->pub.trans_mode = rj->trans_mode;
+  t->pub.type = rj->type;
+  t->pub.priv = t;
+  t->token_val = token ? token->token : 0;
+  return &t->pub;
+}
+urma_status_t op_unimport(urma_target_jetty_t* t) {
+  delete reinterpret_cast<ShmTarget*>(t->priv);
+  return URMA_SUCCESS;
+}
+
+urma_jetty_t* op_create_jetty(urma_context_t* ctx, const urma_jetty_cfg_t* cfg) {
+  ShmCtx* c = C(ctx);
+  ShmJetty* j = new ShmJetty();
+  const uint32_t id = new_jetty_id(c, cfg->id);
+  j->sq.id = id;
+  j->sq.jfc = reinterpret_cast<ShmJfc*>(cfg->jfs_cfg.jfc->priv);
+  j->sq.depth = cfg->jfs_cfg.depth;
+  if (cfg->jfs_cfg.err_timeout) j->sq.err_timeout_ms = 100u << cfg->jfs_cfg.err_timeout;
+  if (cfg->shared_jfr) {
+    j->rq = &reinterpret_cast<ShmJfr*>(cfg->shared_jfr->priv)->rq;
+  } else {
+    urma_jfr_cfg_t rc = cfg->jfr_cfg;
+    rc.id = id;
+    rq_init(c, &j->own_rq, &rc);
+    j->rq = &j->own_rq;
+  }
+  fill_id(c, &j->pub.jetty_id, id);
+  j->pub.priv = j;
+  return &j->pub;
+}
+urma_status_t op_modify_jetty(urma_jetty_t* jt, urma_jetty_state_t st) {
+  ShmJetty* j = reinterpret_cast<ShmJetty*>(jt->priv);
+  j->sq.state = st;
+  if (j->rq == &j->own_rq) j->own_rq.state = st;
+  return URMA_SUCCESS;
+}
+urma_status_t op_query_jetty(urma_jetty_t* jt, urma_jetty_cfg_t* cfg, urma_jetty_state_t* st) {
+  *cfg = jt->cfg;
+  *st = static_cast<urma_jetty_state_t>(reinterpret_cast<ShmJetty*>(jt->priv)->sq.state.load());
+  return URMA_SUCCESS;
+}
+int op_flush_jetty(urma_jetty_t* jt, int n, urma_cr_t* cr) {
+  return flush_sq(C(jt->ctx), &reinterpret_cast<ShmJetty*>(jt->priv)->sq, n, cr);
+}
+urma_status_t op_delete_jetty(urma_jetty_t* jt) {
+  ShmJetty* j = reinterpret_cast<ShmJetty*>(jt->priv);
+  urma_cr_t tmp[16];
+  while (flush_sq(C(jt->ctx), &j->sq, 16, tmp) == 16) {
+  }
+  if (j->rq == &j->own_rq) rq_fini(C(jt->ctx), &j->own_rq);
+  delete j;
+  return URMA_SUCCESS;
+}
+urma_status_t op_bind(urma_jetty_t*, urma_target_jetty_t*) { return URMA_SUCCESS; }
+urma_status_t op_unbind(urma_jetty_t*) { return URMA_SUCCESS; }
+urma_jetty_grp_t* op_create_grp(urma_context_t* ctx, const char* name, uint32_t policy) {
+  urma_jetty_grp_t* g = new urma_jetty_grp_t();
+  snprintf(g->name, sizeof(g->name), "%s", name);
+  g->policy = policy;
+  fill_id(C(ctx), &g->id, new_jetty_id(C(ctx), 0));
+  return g;
+}
+urma_status_t op_delete_grp(urma_jetty_grp_t* g) {
+  delete g;
+  return URMA_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------------- ops: memory
+urma_token_id_t* op_alloc_token(urma_context_t* ctx) {
+  urma_token_id_t* t = new urma_token_id_t();
+  t->token_id = C(ctx)->dev->reg->next_token.fetch_add(1) + 1;
+  return t;
+}
+urma_status_t op_free_token(urma_token_id_t* t) {
+  delete t;
+  return URMA_SUCCESS;
+}
+struct ShmSeg {
+  urma_target_seg_t pub;
+  uint32_t token_val;
+};
+urma_target_seg_t* op_register_seg(urma_context_t* ctx, const urma_seg_cfg_t* cfg) {
+  ShmCtx* c = C(ctx);
+  ShmSeg* s = new ShmSeg();
+  s->pub.seg.ubva.eid = c->pub.eid;
+  s->pub.seg.ubva.uasid = c->pub.uasid;
+  s->pub.seg.ubva.va = cfg->va;
+  s->pub.seg.len = cfg->len;
+  s->pub.seg.attr = cfg->access;
+  s->pub.seg.token_id = cfg->token_id->token_id;
+  s->pub.priv = s;
+  s->token_val = cfg->token_value.token;
+  std::lock_guard<std::mutex> l(c->mu);
+  if (c->segs.count(s->pub.seg.token_id)) {
+    delete s;
+    return nullptr;  // one registration per token id
+  }
+  c->segs[s->pub.seg.token_id] = SegReg{cfg->va, cfg->len, cfg->access, cfg->token_value.token};
+  return &s->pub;
+}
+urma_status_t op_unregister_seg(urma_target_seg_t* t) {
+  ShmCtx* c = C(t->ctx);
+  {
+    std::lock_guard<std::mutex> l(c->mu);
+    c->segs.erase(t->seg.token_id);
+  }
+  delete reinterpret_cast<ShmSeg*>(t->priv);
+  return URMA_SUCCESS;
+}
+urma_target_seg_t* op_import_seg(urma_context_t* ctx, const urma_seg_t* seg, const urma_token_t* token, uint64_t,
+                                 uint32_t) {
+  ShmCtx* c = C(ctx);
+  if (memcmp(seg->ubva.eid.raw, c->pub.eid.raw, 16) != 0) return nullptr;
+  ShmSeg* s = new ShmSeg();
+  s->pub.seg = *seg;
+  s->pub.priv = s;
+  s->token_val = token ? token->token : 0;
+  return &s->pub;
+}
+urma_status_t op_unimport_seg(urma_target_seg_t* t) {
+  delete reinterpret_cast<ShmSeg*>(t->priv);
+  return URMA_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------------- ops: data plane
+bool local_ok(const urma_sge_t& g) { return g.addr != 0 || g.len == 0; }
+
+urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urma_jfs_wr_t* wr) {
+  if (sq->state.load() != URMA_JETTY_STATE_READY) return URMA_FAIL;
+  urma_target_jetty_t* tj = wr->tjetty ? wr->tjetty : bound;
+  if (!tj) return URMA_EINVAL;
+  if (sq->inflight.load() >= sq->depth) return URMA_EAGAIN;
+  Inbox* in = peer_inbox(c, tj->id.uasid);
+  if (!in) return URMA_FAIL;
+  const uint64_t id = c->next_wr.fetch_add(1);
+  Pending p;
+  p.sq = sq;
+  p.user_ctx = wr->user_ctx;
+  p.flag = wr->flag;
+  p.opcode = wr->opcode;
+  p.deadline_ns = ub::now_ns() + uint64_t(sq->err_timeout_ms) * 1000000ull;
+  p.remote = tj->id;
+  MsgHdr h{};
+  h.opcode = wr->opcode;
+  h.src_uasid = c->pub.uasid;
+  h.src_jetty = sq->id;
+  h.dst_jetty = tj->id.id;
+  h.wr_id = id;
+  memcpy(h.src_eid, c->pub.eid.raw, 16);
+  auto add_pending = [&]() {
+    sq->inflight.fetch_add(1);
+    std::lock_guard<std::mutex> l(c->mu);
+    c->pending[id] = std::move(p);
+  };
+  auto fail_pending = [&]() {
+    std::lock_guard<std::mutex> l(c->mu);
+    if (c->pending.erase(id)) sq->inflight.fetch_sub(1);
+  };
+  switch (wr->opcode) {
+    case URMA_OPC_WRITE:
+    case URMA_OPC_WRITE_IMM:
+    case URMA_OPC_WRITE_NOTIFY: {
+      const urma_sg_t &src = wr->rw.src, &dst = wr->rw.dst;
+      if (dst.num_sge != 1 || src.num_sge == 0 || src.num_sge > URMA_MAX_SGE || !dst.sge[0].tseg) return URMA_EINVAL;
+      const uint32_t total = sg_len(src);
+      if (total != dst.sge[0].len) return URMA_EINVAL;
+      ShmSeg* rs = reinterpret_cast<ShmSeg*>(dst.sge[0].tseg->priv);
+      h.type = MSG_WRITE;
+      h.token_id = dst.sge[0].tseg->seg.token_id;
+      h.token_val = rs->token_val;
+      h.total_len = total;
+      h.operand = wr->rw.notify_data;
+      p.total = total;
+      add_pending();
+      // gather source SGEs into fragments
+      uint32_t off = 0, si = 0, so = 0;
+      uint8_t buf[kSlotPayload];
+      do {
+        uint32_t n = 0;
+        while (n < kSlotPayload && si < src.num_sge) {
+          const uint32_t take = std::min(kSlotPayload - n, src.sge[si].len - so);
+          memcpy(buf + n, reinterpret_cast<void*>(src.sge[si].addr + so), take);
+          n += take;
+          so += take;
+          if (so == src.sge[si].len) {
+            ++si;
+            so = 0;
+          }
+        }
+        h.len = n;
+        h.frag_off = off;
+        h.remote_va = dst.sge[0].addr + off;
+        h.flags = (off == 0 ? F_FIRST : 0) | (off + n == total ? F_LAST : 0) |
+                  (wr->opcode != URMA_OPC_WRITE ? F_IMM : 0);
+        if (!send_msg(in, h, buf, sq->err_timeout_ms)) {
+          fail_pending();
+          return URMA_EAGAIN;
+        }
+        off += n;
+      } while (off < total);
+      return URMA_SUCCESS;
+    }
+    case URMA_OPC_READ: {
+      const urma_sg_t &src = wr->rw.src, &dst = wr->rw.dst;  // src = remote, dst = local
+      if (src.num_sge != 1 || dst.num_sge == 0 || dst.num_sge > URMA_MAX_SGE || !src.sge[0].tseg) return URMA_EINVAL;
+      const uint32_t total = src.sge[0].len;
+      if (total != sg_len(dst)) return URMA_EINVAL;
+      ShmSeg* rs = reinterpret_cast<ShmSeg*>(src.sge[0].tseg->priv);
+      h.type = MSG_READ;
+      h.token_id = src.sge[0].tseg->seg.token_id;
+      h.token_val = rs->token_val;
+      h.total_len = total;
+      h.remote_va = src.sge[0].addr;
+      p.total = total;
+      p.local.assign(dst.sge, dst.sge + dst.num_sge);
+      add_pending();
+      if (!send_msg(in, h, nullptr, sq->err_timeout_ms)) {
+        fail_pending();
+        return URMA_EAGAIN;
+      }
+      return URMA_SUCCESS;
+    }
+    case URMA_OPC_CAS:
+    case URMA_OPC_SWAP:
+    case URMA_OPC_FADD:
+    case URMA_OPC_FSUB:
+    case URMA_OPC_FAND:
+    case URMA_OPC_FOR:
+    case URMA_OPC_FXOR: {
+      const bool cas = wr->opcode == URMA_OPC_CAS || wr->opcode == URMA_OPC_SWAP;
+      urma_sge_t* d = cas ? wr->cas.dst : wr->faa.dst;
+      urma_sge_t* s = cas ? wr->cas.src : wr->faa.src;
+      if (!d || !d->tseg || d->len != 8) return URMA_EINVAL;
+      ShmSeg* rs = reinterpret_cast<ShmSeg*>(d->tseg->priv);
+      h.type = MSG_ATOMIC;
+      h.token_id = d->tseg->seg.token_id;
+      h.token_val = rs->token_val;
+      h.remote_va = d->addr;
+      h.operand = cas ? wr->cas.swap_data : wr->faa.operand;
+      h.cmp = cas ? wr->cas.cmp_data : 0;
+      p.total = 8;
+      if (s && s->addr) p.local.push_back(*s);
+      add_pending();
+      if (!send_msg(in, h, nullptr, sq->err_timeout_ms)) {
+        fail_pending();
+        return URMA_EAGAIN;
+      }
+      return URMA_SUCCESS;
+    }
+    case URMA_OPC_SEND:
+    case URMA_OPC_SEND_IMM:
+    case URMA_OPC_SEND_INVALIDATE: {
+      const urma_sg_t& src = wr->send.src;
+      if (src.num_sge > URMA_MAX_SGE) return URMA_EINVAL;
+      const uint32_t total = sg_len(src);
+      h.type = MSG_SEND;
+      h.token_val = reinterpret_cast<ShmTarget*>(tj->priv)->token_val;
+      h.total_len = total;
+      h.operand = wr->send.imm_data;
+      p.total = total;
+      add_pending();
+      uint32_t off = 0, si = 0, so = 0;
+      uint8_t buf[kSlotPayload];
+      do {
+        uint32_t n = 0;
+        while (n < kSlotPayload && si < src.num_sge) {
+          const uint32_t take = std::min(kSlotPayload - n, src.sge[si].len - so);
+          if (take) memcpy(buf + n, reinterpret_cast<void*>(src.sge[si].addr + so), take);
+          n += take;
+          so += take;
+          if (so == src.sge[si].len) {
+            ++si;
+            so = 0;
+          }
+        }
+        h.len = n;
+        h.frag_off = off;
+        h.flags = (off == 0 ? F_FIRST : 0) | (off + n == total ? F_LAST : 0) |
+                  (wr->opcode == URMA_OPC_SEND_IMM ? F_IMM : 0);
+        if (!send_msg(in, h, buf, sq->err_timeout_ms)) {
+          fail_pending();
+          return URMA_EAGAIN;
+        }
+        off += n;
+      } while (off < total);
+      return URMA_SUCCESS;
+    }
+    case URMA_OPC_NOP: {
+      h.type = MSG_PROBE;
+      add_pending();
+      if (!send_msg(in, h, nullptr, sq->err_timeout_ms)) {
+        fail_pending();
+        return URMA_EAGAIN;
+      }
+      return URMA_SUCCESS;
+    }
+    default: return URMA_EINVAL;
+  }
+}
+
+urma_status_t post_send_list(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urma_jfs_wr_t* wr,
+                             urma_jfs_wr_t** bad) {
+  for (urma_jfs_wr_t* w = wr; w; w = w->next) {
+    const urma_status_t s = post_one(c, sq, bound, w);
+    if (s != URMA_SUCCESS) {
+      *bad = w;
+      return s;
+    }
+  }
+  *bad = nullptr;
+  return URMA_SUCCESS;
+}
+urma_status_t post_recv_list(ShmCtx* c, RecvQueue* rq, urma_jfr_wr_t* wr, urma_jfr_wr_t** bad) {
+  for (urma_jfr_wr_t* w = wr; w; w = w->next) {
+    if (rq->state.load() != URMA_JETTY_STATE_READY || w->src.num_sge > URMA_MAX_SGE) {
+      *bad = w;
+      return URMA_EINVAL;
+    }
+    RecvWr r;
+    r.user_ctx = w->user_ctx;
+    r.sges.assign(w->src.sge, w->src.sge + w->src.num_sge);
+    Unexpected u;
+    bool have = false;
+    {
+      std::lock_guard<std::mutex> l(rq->mu);
+      if (rq->posted.size() >= rq->depth) {
+        *bad = w;
+        return URMA_EAGAIN;
+      }
+      rq->posted.push_back(std::move(r));
+      if (!rq->unexpected.empty()) {
+        u = std::move(rq->unexpected.front());
+        rq->unexpected.pop_front();
+        have = true;
+      }
+    }
+    if (have) deliver(c, rq, std::move(u));
+  }
+  *bad = nullptr;
+  return URMA_SUCCESS;
+}
+urma_status_t op_post_jfs(urma_jfs_t* jfs, urma_jfs_wr_t* wr, urma_jfs_wr_t** bad) {
+  return post_send_list(C(jfs->ctx), &reinterpret_cast<ShmJfs*>(jfs->priv)->sq, nullptr, wr, bad);
+}
+urma_status_t op_post_jfr(urma_jfr_t* jfr, urma_jfr_wr_t* wr, urma_jfr_wr_t** bad) {
+  return post_recv_list(C(jfr->ctx), &reinterpret_cast<ShmJfr*>(jfr->priv)->rq, wr, bad);
+}
+urma_status_t op_post_jetty_send(urma_jetty_t* jt, urma_jfs_wr_t* wr, urma_jfs_wr_t** bad) {
+  return post_send_list(C(jt->ctx), &reinterpret_cast<ShmJetty*>(jt->priv)->sq, jt->remote_jetty, wr, bad);
+}
+urma_status_t op_post_jetty_recv(urma_jetty_t* jt, urma_jfr_wr_t* wr, urma_jfr_wr_t** bad) {
+  return post_recv_list(C(jt->ctx), reinterpret_cast<ShmJetty*>(jt->priv)->rq, wr, bad);
+}
+int op_poll_jfc(urma_jfc_t* jfc, int n, urma_cr_t* cr) {
+  ShmJfc* j = reinterpret_cast<ShmJfc*>(jfc->priv);
+  std::lock_guard<std::mutex> l(j->mu);
+  int k = 0;
+  while (k < n && !j->q.empty()) {
+    cr[k++] = j->q.front();
+    j->q.pop_front();
+  }
+  return k;
+}
+urma_status_t op_rearm_jfc(urma_jfc_t* jfc, bool) {
+  ShmJfc* j = reinterpret_cast<ShmJfc*>(jfc->priv);
+  ShmJfce* ce = nullptr;
+  {
+    std::lock_guard<std::mutex> l(j->mu);
+    if (!j->q.empty() && jfc->cfg.jfce) ce = reinterpret_cast<ShmJfce*>(jfc->cfg.jfce->priv);  // fire at once
+    else j->armed = true;
+  }
+  if (ce) {
+    {
+      std::lock_guard<std::mutex> l(ce->mu);
+      ce->fired.push_back(jfc);
+    }
+    uint64_t one = 1;
+    if (write(ce->efd, &one, sizeof(one)) < 0) {
+    }
+  }
+  return URMA_SUCCESS;
+}
+int op_wait_jfc(urma_jfce_t* jfce, uint32_t cnt, int timeout_ms, urma_jfc_t* out[]) {
+  ShmJfce* e = reinterpret_cast<ShmJfce*>(jfce->priv);
+  for (;;) {
+    {
+      std::lock_guard<std::mutex> l(e->mu);
+      if (!e->fired.empty()) {
+        uint32_t k = 0;
+        while (k < cnt && !e->fired.empty()) {
+          out[k++] = e->fired.front();
+          e->fired.pop_front();
+        }
+        return static_cast<int>(k);
+      }
+    }
+    pollfd pfd{e->efd, POLLIN, 0};
+    const int r = poll(&pfd, 1, timeout_ms);
+    if (r == 0) return 0;
+    if (r < 0 && errno != EINTR) return -1;
+    uint64_t v;
+    if (read(e->efd, &v, sizeof(v)) < 0) {
+    }
+  }
+}
+void op_ack_jfc(urma_jfc_t*[], uint32_t[], uint32_t) {}
+
+urma_status_t op_get_async_event(urma_context_t* ctx, urma_async_event_t* ev) {
+  ShmCtx* c = C(ctx);
+  std::lock_guard<std::mutex> l(c->mu);
+  if (c->events.empty()) return URMA_EAGAIN;
+  *ev = c->events.front();
+  c->events.pop_front();
+  uint64_t v;
+  if (read(c->event_fd, &v, sizeof(v)) < 0) {
+  }
+  return URMA_SUCCESS;
+}
+void op_ack_async_event(urma_async_event_t*) {}
+
+// user_ctl opcodes of this provider: 1 = number of pending requests, 2 = inject an async event (in->addr = type),
+// 3 = peer liveness: in->addr = uasid, out->rsv = age of the peer's heartbeat in ms (or 0xffffffff if unknown)
+int op_user_ctl(urma_context_t* ctx, urma_user_ctl_in_t* in, urma_user_ctl_out_t* out) {
+  ShmCtx* c = C(ctx);
+  switch (in->opcode) {
+    case 1: {
+      std::lock_guard<std::mutex> l(c->mu);
+      out->rsv = static_cast<uint32_t>(c->pending.size());
+      return 0;
+    }
+    case 2: {
+      urma_async_event_t ev{};
+      ev.ctx = ctx;
+      ev.event_type = static_cast<urma_async_event_type_t>(in->addr);
+      {
+        std::lock_guard<std::mutex> l(c->mu);
+        c->events.push_back(ev);
+      }
+      uint64_t one = 1;
+      if (write(c->event_fd, &one, sizeof(one)) < 0) {
+      }
+      return 0;
+    }
+    case 3: {
+      out->rsv = 0xffffffffu;
+      for (uint32_t i = 0; i < kMaxCtx; ++i) {
+        if (c->dev->reg->ctx[i].uasid.load() == static_cast<uint32_t>(in->addr)) {
+          const uint64_t hb = c->dev->reg->ctx[i].heartbeat_ns.load();
+          const uint64_t now = ub::now_ns();
+          out->rsv = static_cast<uint32_t>((now > hb ? now - hb : 0) / 1000000ull);
+        }
+      }
+      return 0;
+    }
+    default: return -1;
+  }
+}
+
+const urma_ops_t g_ops = {
+    "shm",           op_create_jfc,   op_modify_jfc,   op_delete_jfc,     op_create_jfce,     op_delete_jfce,
+    op_create_jfs,   op_modify_jfs,   op_query_jfs,    op_flush_jfs,      op_delete_jfs,      op_create_jfr,
+    op_modify_jfr,   op_query_jfr,    op_delete_jfr,   op_import,         op_unimport,        op_create_jetty,
+    op_modify_jetty, op_query_jetty,  op_flush_jetty,  op_delete_jetty,   op_import,          op_unimport,
+    op_bind,         op_unbind,       op_create_grp,   op_delete_grp,     op_alloc_token,     op_free_token,
+    op_register_seg, op_unregister_seg, op_import_seg, op_unimport_seg,   op_post_jfs,        op_post_jfr,
+    op_post_jetty_send, op_post_jetty_recv, op_poll_jfc, op_rearm_jfc,    op_wait_jfc,        op_ack_jfc,
+    op_get_async_event, op_ack_async_event, op_user_ctl,
+};
+
+// ---------------------------------------------------------------------------------------------- provider ops
+urma_status_t prov_init(const urma_init_attr_t*) {
+  std::lock_guard<std::mutex> l(g_mu);
+  if (!g_devs.empty()) return URMA_SUCCESS;
+  const std::string dir = shm_dir();
+  mkdir(dir.c_str(), 0700);
+  int n = 2;
+  if (const char* e = getenv("URMA_SHM_DEVICES")) n = std::max(1, std::min(8, atoi(e)));
+  for (int i = 0; i < n; ++i) {
+    Device d;
+    d.name = "shm" + std::to_string(i);
+    memset(d.eid.raw, 0, 16);
+    memcpy(d.eid.raw, "umdk", 4);
+    const uint32_t uid = getuid();
+    memcpy(d.eid.raw + 8, &uid, 4);
+    d.eid.raw[15] = static_cast<uint8_t>(i + 1);
+    bool created = false;
+    d.reg = static_cast<DevReg*>(map_file(dir + "/dev_" + d.name + ".reg", sizeof(DevReg), true, &created));
+    if (!d.reg) return URMA_FAIL;
+    uint32_t exp = 0;
+    d.reg->magic.compare_exchange_strong(exp, kRegMagic);
+    g_devs.push_back(d);
+  }
+  return URMA_SUCCESS;
+}
+urma_status_t prov_uninit(void) { return URMA_SUCCESS; }
+int prov_get_devices(urma_device_t* devs, int max) {
+  std::lock_guard<std::mutex> l(g_mu);
+  int n = 0;
+  for (auto& d : g_devs) {
+    if (n >= max) break;
+    memset(&devs[n], 0, sizeof(urma_device_t));
+    snprintf(devs[n].name, sizeof(devs[n].name), "%s", d.name.c_str());
+    devs[n].eid = d.eid;
+    devs[n].priv = &d;
+    ++n;
+  }
+  return n;
+}
+urma_status_t prov_query(const urma_device_t*, urma_device_attr_t* a) {
+  memset(a, 0, sizeof(*a));
+  a->max_jfc = a->max_jfs = a->max_jfr = a->max_jetty = 65536;
+  a->max_seg = 1u << 20;
+  a->max_jfc_depth = a->max_jfs_depth = a->max_jfr_depth = 65536;
+  a->max_sge = URMA_MAX_SGE;
+  a->max_msg_size = 1ull << 30;
+  a->transport_modes = URMA_TM_RM | URMA_TM_RC | URMA_TM_UM;
+  a->port_cnt = 1;
+  a->atomic_supported = true;
+  return URMA_SUCCESS;
+}
+urma_context_t* prov_create_context(urma_device_t* dev, uint32_t eid_index) {
+  Device* d = static_cast<Device*>(dev->priv);
+  if (eid_index != 0) return nullptr;
+  ShmCtx* c = new ShmCtx();
+  c->dev = d;
+  c->pub.ops = &g_ops;
+  c->pub.eid = d->eid;
+  c->pub.eid_index = 0;
+  c->pub.priv = c;
+  uint32_t uasid = d->reg->next_uasid.fetch_add(1) + 1;
+  c->pub.uasid = uasid;
+  const uint64_t now = ub::now_ns();
+  for (uint32_t i = 0; i < kMaxCtx; ++i) {
+    uint32_t exp = 0;
+    CtxSlot& s = d->reg->ctx[i];
+    // reuse free slots and slots whose owner stopped beating for 10 s
+    const uint32_t cur = s.uasid.load();
+    if (cur != 0 && now - s.heartbeat_ns.load() > 10000000000ull) exp = cur;
+    if (s.uasid.compare_exchange_strong(exp, uasid)) {
+      s.pid = getpid();
+      s.heartbeat_ns = now;
+      c->reg_slot = static_cast<int>(i);
+      break;
+    }
+  }
+  c->inbox_path = shm_dir() + "/inbox_" + d->name + "_" + std::to_string(uasid);
+  unlink(c->inbox_path.c_str());
+  c->inbox = static_cast<Inbox*>(map_file(c->inbox_path, sizeof(Inbox), true));
+  if (!c->inbox) {
+    delete c;
+    return nullptr;
+  }
+  for (uint32_t i = 0; i < kRingSlots; ++i) c->inbox->slots[i].seq.store(i);
+  c->inbox->enq = 0;
+  c->inbox->deq = 0;
+  c->inbox->owner_pid = getpid();
+  c->inbox->magic.store(kRegMagic, std::memory_order_release);
+  c->event_fd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC | EFD_SEMAPHORE);
+  c->pub.async_fd = c->event_fd;
+  c->nic = std::thread(nic_loop, c);
+  return &c->pub;
+}
+urma_status_t prov_delete_context(urma_context_t* ctx) {
+  ShmCtx* c = C(ctx);
+  c->stop = true;
+  if (c->nic.joinable()) c->nic.join();
+  if (c->reg_slot >= 0) c->dev->reg->ctx[c->reg_slot].uasid.store(0);
+  c->inbox->magic.store(0);
+  munmap(c->inbox, sizeof(Inbox));
+  unlink(c->inbox_path.c_str());
+  for (auto& kv : c->peers) munmap(kv.second, sizeof(Inbox));
+  close(c->event_fd);
+  delete c;
+  return URMA_SUCCESS;
+}
+
+const urma_provider_ops_t g_prov = {"shm",      prov_init,           prov_uninit,        prov_get_devices,
+                                    prov_query, prov_create_context, prov_delete_context};
+
+__attribute__((constructor)) void shm_provider_ctor() { urma_register_provider_ops(&g_prov); }
+
+}  // namespace
