@@ -228,6 +228,7 @@ struct ShmCtx {
   std::map<std::pair<uint32_t, uint64_t>, Reasm> reasm;
   std::deque<urma_async_event_t> events;
   int event_fd = -1;
+  std::atomic<bool> drop_tx{false};  // fault injection: outgoing requests vanish (a dead link)
 };
 
 // ---------------------------------------------------------------------------------------------- helpers
@@ -933,7 +934,7 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
         h.remote_va = dst.sge[0].addr + off;
         h.flags = (off == 0 ? F_FIRST : 0) | (off + n == total ? F_LAST : 0) |
                   (wr->opcode != URMA_OPC_WRITE ? F_IMM : 0);
-        if (!send_msg(in, h, buf, sq->err_timeout_ms)) {
+        if (!c->drop_tx.load() && !send_msg(in, h, buf, sq->err_timeout_ms)) {
           fail_pending();
           return URMA_EAGAIN;
         }
@@ -955,7 +956,7 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
       p.total = total;
       p.local.assign(dst.sge, dst.sge + dst.num_sge);
       add_pending();
-      if (!send_msg(in, h, nullptr, sq->err_timeout_ms)) {
+      if (!c->drop_tx.load() && !send_msg(in, h, nullptr, sq->err_timeout_ms)) {
         fail_pending();
         return URMA_EAGAIN;
       }
@@ -982,7 +983,7 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
       p.total = 8;
       if (s && s->addr) p.local.push_back(*s);
       add_pending();
-      if (!send_msg(in, h, nullptr, sq->err_timeout_ms)) {
+      if (!c->drop_tx.load() && !send_msg(in, h, nullptr, sq->err_timeout_ms)) {
         fail_pending();
         return URMA_EAGAIN;
       }
@@ -1018,7 +1019,7 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
         h.frag_off = off;
         h.flags = (off == 0 ? F_FIRST : 0) | (off + n == total ? F_LAST : 0) |
                   (wr->opcode == URMA_OPC_SEND_IMM ? F_IMM : 0);
-        if (!send_msg(in, h, buf, sq->err_timeout_ms)) {
+        if (!c->drop_tx.load() && !send_msg(in, h, buf, sq->err_timeout_ms)) {
           fail_pending();
           return URMA_EAGAIN;
         }
@@ -1029,7 +1030,7 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
     case URMA_OPC_NOP: {
       h.type = MSG_PROBE;
       add_pending();
-      if (!send_msg(in, h, nullptr, sq->err_timeout_ms)) {
+      if (!c->drop_tx.load() && !send_msg(in, h, nullptr, sq->err_timeout_ms)) {
         fail_pending();
         return URMA_EAGAIN;
       }
@@ -1160,7 +1161,9 @@ urma_status_t op_get_async_event(urma_context_t* ctx, urma_async_event_t* ev) {
 void op_ack_async_event(urma_async_event_t*) {}
 
 // user_ctl opcodes of this provider: 1 = number of pending requests, 2 = inject an async event (in->addr = type),
-// 3 = peer liveness: in->addr = uasid, out->rsv = age of the peer's heartbeat in ms (or 0xffffffff if unknown)
+// 3 = peer liveness: in->addr = uasid, out->rsv = age of the peer's heartbeat in ms (or 0xffffffff if unknown),
+// 4 = fault injection: in->addr != 0 makes every outgoing request vanish (requests then end with
+//     URMA_CR_ACK_TIMEOUT_ERR after the send queue's error timeout), 0 restores the link
 int op_user_ctl(urma_context_t* ctx, urma_user_ctl_in_t* in, urma_user_ctl_out_t* out) {
   ShmCtx* c = C(ctx);
   switch (in->opcode) {
@@ -1193,6 +1196,7 @@ int op_user_ctl(urma_context_t* ctx, urma_user_ctl_in_t* in, urma_user_ctl_out_t
       }
       return 0;
     }
+    case 4: c->drop_tx = in->addr != 0; return 0;
     default: return -1;
   }
 }

@@ -50,11 +50,12 @@ urma_simple_ep_t* urma_simple_ep_create(urma_context_t* ctx, uint32_t depth, uin
   jc.jfr_cfg.jfc = ep->jfc;
   jc.jfr_cfg.token_value.token = recv_token;
   ep->jetty = ep->jfc ? urma_create_jetty(ctx, &jc) : nullptr;
-  if (!ep->jfce || !ep->jfc || !ep->jetty) {
+  if (!ep->jfc || !ep->jetty) {
     urma_simple_ep_destroy(ep);
     return nullptr;
   }
-  if (interrupt_mode) urma_rearm_jfc(ep->jfc, false);
+  if (!ep->jfce) ep->interrupt_mode = 0;  // devices without event channels (bond) are polled
+  if (ep->interrupt_mode) urma_rearm_jfc(ep->jfc, false);
   return ep;
 }
 int urma_simple_ep_destroy(urma_simple_ep_t* ep) {

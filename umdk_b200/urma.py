@@ -228,3 +228,32 @@ class Context:
         if self.handle:
             self.lib.urma_simple_close(self.handle)
             self.handle = None
+
+
+class _CtlIn(ctypes.Structure):
+    _fields_ = [("addr", ctypes.c_uint64), ("len", ctypes.c_uint32), ("opcode", ctypes.c_uint32)]
+
+
+class _CtlOut(ctypes.Structure):
+    _fields_ = [("addr", ctypes.c_uint64), ("len", ctypes.c_uint32), ("rsv", ctypes.c_uint32)]
+
+
+def user_ctl(ctx: Context, opcode: int, addr: int = 0, length: int = 0, out_buf=None) -> int:
+    """Provider-specific control call (urma_user_ctl). Returns the provider's 32-bit result word."""
+    lib = _lib()
+    lib.urma_user_ctl.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    cin = _CtlIn(addr, length, opcode)
+    cout = _CtlOut(ctypes.addressof(out_buf) if out_buf is not None else 0,
+                   ctypes.sizeof(out_buf) if out_buf is not None else 0, 0)
+    rc = lib.urma_user_ctl(ctx.handle, ctypes.byref(cin), ctypes.byref(cout))
+    if rc != 0:
+        raise UrmaError(f"urma_user_ctl(opcode {opcode}) failed: {rc}")
+    return cout.rsv
+
+
+def bond_path_stats(ctx: Context):
+    """[{up, tx, errors, failovers, failbacks, admin_down}] per physical path of a bond context."""
+    buf = (ctypes.c_uint64 * (6 * 4))()
+    n = user_ctl(ctx, 1, out_buf=buf)
+    keys = ("up", "tx", "errors", "failovers", "failbacks", "admin_down")
+    return [dict(zip(keys, [int(buf[i * 6 + k]) for k in range(6)])) for i in range(n)]
