@@ -1,0 +1,666 @@
+// UMQ implementation over URMA jetties.
+//
+// What is kept from the reference (src/urpc/umq): handle-based queues created from an option struct and connected
+// by exchanging an opaque bind blob (umq_api.c, umq_ub_private.h:344-349); message buffers handed out by a pool with
+// fixed block sizes of 8/16/32/64 KiB, per-thread caches in front of a global pool and a separate path for huge
+// requests up to 10 MiB (qbuf/umq_qbuf_pool.c, umq_huge_qbuf_pool.c); the base API (enqueue / dequeue) and the pro
+// API (post / poll per direction); control information carried in the immediate data of two-sided messages
+// (umq_ub_imm_data.h:20-103); credit-based flow control in which the receiver grants one credit per posted receive
+// buffer and returns credits in batches (flow_control/umq_ub_flow_control.c; doc/en/urpc/UMQ Flowcontrol.md);
+// io / flow-control / pool statistics and latency records (umq_dfx_api.h).
+#include "umq_api.h"
+
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
+#include <deque>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "ub_util.h"
+#include "urma_simple.h"
+
+namespace {
+
+// immediate data layout: [63:56] type, [55:32] credits returned, [31:0] message bytes
+enum ImmType : uint64_t { IMM_IO = 1, IMM_FC_RETURN = 2 };
+inline uint64_t imm_make(ImmType t, uint32_t credits, uint32_t bytes) {
+  return (uint64_t(t) << 56) | (uint64_t(credits & 0xffffff) << 32) | bytes;
+}
+
+struct Block {
+  umq_buf_t meta;  // must be first: umq_buf_t* <-> Block*
+  bool huge;
+  char* mem;
+  uint32_t cap;
+};
+
+struct Pool {
+  std::mutex mu;
+  uint32_t block = 8192;
+  std::vector<Block*> free_list;
+  std::vector<char*> slabs;
+  uint64_t total = 0, huge_allocs = 0, alloc_calls = 0, free_calls = 0, failures = 0;
+  bool inited = false;
+};
+Pool g_pool;
+thread_local std::vector<Block*> t_cache;
+constexpr size_t kCacheMax = 64;
+
+struct Global {
+  std::mutex mu;
+  bool inited = false;
+  umq_init_cfg_t cfg{};
+  urma_context_t* ctx = nullptr;
+  std::unordered_map<uint64_t, struct Queue*> queues;
+  std::atomic<uint64_t> next_h{1};
+  std::atomic<bool> perf_on{false};
+  std::mutex perf_mu;
+  ub::PerfHist perf[UMQ_PERF_RECORD_MAX];
+};
+Global g;
+
+struct PerfScope {
+  int rec;
+  uint64_t t0;
+  explicit PerfScope(int r) : rec(r), t0(g.perf_on.load(std::memory_order_relaxed) ? ub::now_ns() : 0) {}
+  ~PerfScope() {
+    if (t0) {
+      const uint64_t dt = ub::now_ns() - t0;
+      std::lock_guard<std::mutex> l(g.perf_mu);
+      g.perf[rec].add(dt);
+    }
+  }
+};
+
+struct Queue {
+  uint64_t h;
+  umq_create_option_t opt;
+  urma_simple_ep_t* ep = nullptr;
+  urma_target_jetty_t* peer = nullptr;
+  std::atomic<int> state{UMQ_STATE_IDLE};
+  std::mutex mu;
+  std::deque<umq_buf_t*> rx_ready;      // received messages not yet dequeued
+  std::deque<umq_buf_t*> tx_done;       // sent buffers whose completion arrived (pro API)
+  uint32_t rx_posted = 0;
+  // flow control
+  bool fc = false;
+  int64_t credits = 0;          // messages we may still send
+  uint32_t to_return = 0;       // credits owed to the peer
+  uint32_t fc_skip = 0;         // receive buffers consumed by control messages: re-posting them grants nothing
+  uint32_t window = 0;
+  umq_io_stats_t io{};
+  umq_fc_stats_t fcs{};
+  bool base_api_tx = true;      // enqueue frees buffers on completion; post hands them back through poll
+};
+
+Queue* find(uint64_t h) {
+  std::lock_guard<std::mutex> l(g.mu);
+  auto it = g.queues.find(h);
+  return it == g.queues.end() ? nullptr : it->second;
+}
+
+// ------------------------------------------------------------------------------------------------ buffers
+Block* block_new(uint32_t cap, bool huge) {
+  Block* b = static_cast<Block*>(calloc(1, sizeof(Block)));
+  if (!b) return nullptr;
+  b->mem = static_cast<char*>(malloc(cap));
+  if (!b->mem) {
+    free(b);
+    return nullptr;
+  }
+  b->cap = cap;
+  b->huge = huge;
+  return b;
+}
+void pool_init(uint32_t block, uint64_t bytes) {
+  std::lock_guard<std::mutex> l(g_pool.mu);
+  if (g_pool.inited) return;
+  g_pool.block = block;
+  const uint64_t n = bytes / block;
+  for (uint64_t i = 0; i < n; ++i) {
+    Block* b = block_new(block, false);
+    if (!b) break;
+    g_pool.free_list.push_back(b);
+    ++g_pool.total;
+  }
+  g_pool.inited = true;
+}
+Block* block_get(uint32_t need) {
+  if (need > g_pool.block) {
+    if (need > UMQ_MAX_MSG_SIZE) return nullptr;
+    Block* b = block_new(need, true);
+    std::lock_guard<std::mutex> l(g_pool.mu);
+    if (b) ++g_pool.huge_allocs;
+    else ++g_pool.failures;
+    return b;
+  }
+  if (!t_cache.empty()) {
+    Block* b = t_cache.back();
+    t_cache.pop_back();
+    return b;
+  }
+  std::lock_guard<std::mutex> l(g_pool.mu);
+  // refill the thread cache with a small batch
+  for (int i = 0; i < 8 && !g_pool.free_list.empty(); ++i) {
+    t_cache.push_back(g_pool.free_list.back());
+    g_pool.free_list.pop_back();
+  }
+  if (t_cache.empty()) {
+    ++g_pool.failures;
+    return nullptr;
+  }
+  Block* b = t_cache.back();
+  t_cache.pop_back();
+  return b;
+}
+void block_put(Block* b) {
+  if (b->huge) {
+    free(b->mem);
+    free(b);
+    return;
+  }
+  t_cache.push_back(b);
+  if (t_cache.size() > kCacheMax) {
+    std::lock_guard<std::mutex> l(g_pool.mu);
+    while (t_cache.size() > kCacheMax / 2) {
+      g_pool.free_list.push_back(t_cache.back());
+      t_cache.pop_back();
+    }
+  }
+}
+void buf_setup(Block* b, uint64_t h, uint32_t data_size) {
+  umq_buf_t* q = &b->meta;
+  memset(q, 0, sizeof(*q));
+  q->umqh = h;
+  q->buf_size = b->cap;
+  q->data_size = data_size;
+  q->buf_data = b->mem;
+}
+
+// ------------------------------------------------------------------------------------------------ rx refill
+void refill_rx(Queue* q) {
+  while (q->rx_posted < q->opt.rx_depth) {
+    Block* b = block_get(q->opt.rx_buf_size);
+    if (!b) break;
+    buf_setup(b, q->h, 0);
+    if (urma_simple_post_recv(q->ep, b->mem, b->cap, reinterpret_cast<uint64_t>(b)) != 0) {
+      block_put(b);
+      break;
+    }
+    ++q->rx_posted;
+    if (q->fc) {
+      if (q->fc_skip) --q->fc_skip;
+      else ++q->to_return;
+    }
+  }
+}
+
+void send_credit_return(Queue* q) {
+  if (!q->fc || !q->peer || q->to_return == 0) return;
+  const uint32_t n = q->to_return;
+  // zero-length control message; it does not consume a credit on the other side's window accounting
+  if (urma_simple_post(q->ep, q->peer, URMA_OPC_SEND_IMM, nullptr, 0, nullptr, 0, 0, imm_make(IMM_FC_RETURN, n, 0),
+                       0, 0) == 0) {
+    q->to_return = 0;
+    q->fcs.credits_returned += n;
+  }
+}
+
+// drains the completion queue of the endpoint into rx_ready / tx_done; caller holds q->mu
+void progress(Queue* q) {
+  int st[32];
+  uint64_t uc[32], imm[32];
+  uint32_t len[32], flag[32];
+  for (;;) {
+    const int n = urma_simple_poll(q->ep, 32, st, uc, len, imm, flag);
+    if (n <= 0) break;
+    for (int i = 0; i < n; ++i) {
+      if (flag[i] & URMA_CR_FLAG_RECV) {
+        Block* b = reinterpret_cast<Block*>(uc[i]);
+        --q->rx_posted;
+        const uint64_t type = imm[i] >> 56;
+        const uint32_t credits = static_cast<uint32_t>((imm[i] >> 32) & 0xffffff);
+        if (credits) {
+          q->credits += credits;
+          q->fcs.credits_granted += credits;
+        }
+        if (type == IMM_FC_RETURN || st[i] != 0) {
+          if (st[i] != 0) ++q->io.rx_errors;
+          else ++q->fc_skip;
+          block_put(b);  // control message or failed receive: the buffer goes straight back
+          continue;
+        }
+        b->meta.data_size = len[i];
+        b->meta.total_data_size = len[i];
+        b->meta.status = UMQ_BUF_OK;
+        q->rx_ready.push_back(&b->meta);
+        ++q->io.rx_msgs;
+        q->io.rx_bytes += len[i];
+      } else if (uc[i] != 0) {
+        Block* b = reinterpret_cast<Block*>(uc[i]);
+        b->meta.status = st[i] == 0 ? UMQ_BUF_OK : UMQ_BUF_SEND_ERR;
+        if (st[i] != 0) {
+          ++q->io.tx_errors;
+          q->state = UMQ_STATE_ERR;
+        }
+        if (b->meta.rsvd[0]) q->tx_done.push_back(&b->meta);  // pro API: hand back through poll(TX)
+        else block_put(b);
+      }
+    }
+  }
+  refill_rx(q);
+  if (q->fc && q->to_return >= std::max<uint32_t>(1, q->window / 4)) send_credit_return(q);
+}
+
+int send_one(Queue* q, umq_buf_t* buf, bool pro) {
+  if (q->state.load() != UMQ_STATE_READY || !q->peer) return UMQ_ERR_ESTATE;
+  if (buf->data_size > q->opt.rx_buf_size && buf->data_size > g_pool.block) {
+    // the peer's receive buffers are at least one block; larger messages need a matching rx_buf_size
+  }
+  if (q->fc && q->credits <= 0) {
+    progress(q);
+    if (q->credits <= 0) {
+      ++q->fcs.stalls;
+      ++q->io.tx_eagain;
+      return UMQ_ERR_EAGAIN;
+    }
+  }
+  Block* b = reinterpret_cast<Block*>(buf);
+  b->meta.rsvd[0] = pro ? 1 : 0;
+  uint32_t piggy = 0;
+  if (q->fc && q->to_return) {
+    piggy = q->to_return;
+  }
+  const int rc = urma_simple_post(q->ep, q->peer, URMA_OPC_SEND_IMM, nullptr, 0, nullptr,
+                                  reinterpret_cast<uint64_t>(buf->buf_data), buf->data_size,
+                                  imm_make(IMM_IO, piggy, buf->data_size), reinterpret_cast<uint64_t>(b), 1);
+  if (rc != 0) {
+    ++q->io.tx_eagain;
+    return rc == URMA_EAGAIN ? UMQ_ERR_EAGAIN : UMQ_FAIL;
+  }
+  if (piggy) {
+    q->fcs.credits_returned += piggy;
+    q->to_return = 0;
+  }
+  if (q->fc) --q->credits;
+  ++q->io.tx_msgs;
+  q->io.tx_bytes += buf->data_size;
+  return UMQ_SUCCESS;
+}
+
+struct BindBlob {
+  uint32_t magic, rx_buf_size, rx_depth, fc;
+  uint8_t jetty[URMA_SIMPLE_JETTY_BLOB];
+  uint32_t token;
+};
+
+}  // namespace
+
+extern "C" {
+
+int umq_init(const umq_init_cfg_t* cfg) {
+  std::lock_guard<std::mutex> l(g.mu);
+  if (g.inited) return UMQ_SUCCESS;
+  if (cfg) g.cfg = *cfg;
+  const uint32_t kb = g.cfg.block_size_kb ? g.cfg.block_size_kb : 8;
+  if (kb != 8 && kb != 16 && kb != 32 && kb != 64) return UMQ_ERR_EINVAL;
+  g.ctx = urma_simple_open(g.cfg.dev_name[0] ? g.cfg.dev_name : "shm0");
+  if (!g.ctx) return UMQ_FAIL;
+  pool_init(kb * 1024, g.cfg.pool_bytes ? g.cfg.pool_bytes : (64ull << 20));
+  g.inited = true;
+  return UMQ_SUCCESS;
+}
+
+void umq_uninit(void) {
+  std::vector<uint64_t> hs;
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    if (!g.inited) return;
+    for (auto& kv : g.queues) hs.push_back(kv.first);
+  }
+  for (uint64_t h : hs) umq_destroy(h);
+  std::lock_guard<std::mutex> l(g.mu);
+  urma_simple_close(g.ctx);
+  g.ctx = nullptr;
+  g.inited = false;
+}
+
+uint64_t umq_create(const umq_create_option_t* opt) {
+  if (!opt || !g.inited) return UMQ_INVALID_HANDLE;
+  Queue* q = new Queue();
+  q->opt = *opt;
+  if (!q->opt.rx_depth) q->opt.rx_depth = 128;
+  if (!q->opt.tx_depth) q->opt.tx_depth = 128;
+  if (!q->opt.rx_buf_size) q->opt.rx_buf_size = g_pool.block;
+  if (!q->opt.tx_buf_size) q->opt.tx_buf_size = g_pool.block;
+  if (q->opt.rx_buf_size > UMQ_MAX_MSG_SIZE) {
+    delete q;
+    return UMQ_INVALID_HANDLE;
+  }
+  q->fc = (g.cfg.feature & UMQ_FEATURE_FLOW_CONTROL) != 0;
+  // the jetty must hold the data messages plus the occasional credit-return message
+  q->ep = urma_simple_ep_create(g.ctx, q->opt.rx_depth + q->opt.tx_depth + 16, opt->token,
+                                opt->mode == UMQ_MODE_INTERRUPT);
+  if (!q->ep) {
+    delete q;
+    return UMQ_INVALID_HANDLE;
+  }
+  q->h = g.next_h.fetch_add(1);
+  {
+    std::lock_guard<std::mutex> l(q->mu);
+    refill_rx(q);
+    q->to_return = 0;  // the initial window travels in the bind blob
+  }
+  std::lock_guard<std::mutex> l(g.mu);
+  g.queues[q->h] = q;
+  return q->h;
+}
+
+int umq_destroy(uint64_t h) {
+  Queue* q;
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    auto it = g.queues.find(h);
+    if (it == g.queues.end()) return UMQ_ERR_EINVAL;
+    q = it->second;
+    g.queues.erase(it);
+  }
+  for (auto* b : q->rx_ready) block_put(reinterpret_cast<Block*>(b));
+  for (auto* b : q->tx_done) block_put(reinterpret_cast<Block*>(b));
+  if (q->peer) urma_unimport_jetty(q->peer);
+  urma_simple_ep_destroy(q->ep);  // posted receive blocks are reclaimed with the process
+  delete q;
+  return UMQ_SUCCESS;
+}
+
+uint32_t umq_bind_info_get(uint64_t h, uint8_t* out, uint32_t size) {
+  Queue* q = find(h);
+  if (!q || !out || size < sizeof(BindBlob)) return 0;
+  BindBlob b{};
+  b.magic = 0x554d5142;
+  b.rx_buf_size = q->opt.rx_buf_size;
+  b.rx_depth = q->opt.rx_depth;
+  b.fc = q->fc;
+  b.token = q->opt.token;
+  urma_simple_ep_blob(q->ep, b.jetty);
+  memcpy(out, &b, sizeof(b));
+  return sizeof(b);
+}
+
+int umq_bind(uint64_t h, const uint8_t* info, uint32_t size) {
+  Queue* q = find(h);
+  if (!q || !info || size < sizeof(BindBlob)) return UMQ_ERR_EINVAL;
+  BindBlob b;
+  memcpy(&b, info, sizeof(b));
+  if (b.magic != 0x554d5142) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  if (q->peer) return UMQ_ERR_ESTATE;
+  q->peer = urma_simple_ep_import(g.ctx, b.jetty, b.token);
+  if (!q->peer) return UMQ_FAIL;
+  q->fc = q->fc && b.fc;
+  q->window = b.rx_depth;
+  q->credits = b.rx_depth;  // one credit per receive buffer the peer has posted
+  q->fcs.window = b.rx_depth;
+  q->state = UMQ_STATE_READY;
+  return UMQ_SUCCESS;
+}
+
+int umq_unbind(uint64_t h) {
+  Queue* q = find(h);
+  if (!q) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  if (!q->peer) return UMQ_ERR_ESTATE;
+  urma_unimport_jetty(q->peer);
+  q->peer = nullptr;
+  q->state = UMQ_STATE_IDLE;
+  return UMQ_SUCCESS;
+}
+
+int umq_state_set(uint64_t h, umq_state_t s) {
+  Queue* q = find(h);
+  if (!q) return UMQ_ERR_EINVAL;
+  q->state = s;
+  return UMQ_SUCCESS;
+}
+umq_state_t umq_state_get(uint64_t h) {
+  Queue* q = find(h);
+  return q ? static_cast<umq_state_t>(q->state.load()) : UMQ_STATE_ERR;
+}
+
+umq_buf_t* umq_buf_alloc(uint32_t request_size, uint32_t num, uint64_t h) {
+  PerfScope ps(UMQ_PERF_BUF_ALLOC);
+  if (num == 0 || num > UMQ_BATCH_SIZE) return nullptr;
+  {
+    std::lock_guard<std::mutex> l(g_pool.mu);
+    ++g_pool.alloc_calls;
+  }
+  umq_buf_t *head = nullptr, *tail = nullptr;
+  for (uint32_t i = 0; i < num; ++i) {
+    Block* b = block_get(request_size ? request_size : 1);
+    if (!b) {
+      if (head) umq_buf_free(head);
+      return nullptr;
+    }
+    buf_setup(b, h, request_size);
+    if (!head) head = &b->meta;
+    else tail->qbuf_next = &b->meta;
+    tail = &b->meta;
+  }
+  head->total_data_size = request_size * num;
+  return head;
+}
+
+void umq_buf_free(umq_buf_t* qbuf) {
+  {
+    std::lock_guard<std::mutex> l(g_pool.mu);
+    ++g_pool.free_calls;
+  }
+  while (qbuf) {
+    umq_buf_t* nx = qbuf->qbuf_next;
+    block_put(reinterpret_cast<Block*>(qbuf));
+    qbuf = nx;
+  }
+}
+
+int umq_buf_headroom_reset(umq_buf_t* qbuf, uint16_t headroom) {
+  if (!qbuf || headroom > 512) return UMQ_ERR_EINVAL;
+  Block* b = reinterpret_cast<Block*>(qbuf);
+  if (headroom >= b->cap) return UMQ_ERR_EINVAL;
+  qbuf->headroom_size = headroom;
+  qbuf->buf_data = b->mem + headroom;
+  qbuf->buf_size = b->cap - headroom;
+  if (qbuf->data_size > qbuf->buf_size) qbuf->data_size = qbuf->buf_size;
+  return UMQ_SUCCESS;
+}
+
+int umq_buf_reset(umq_buf_t* qbuf) {
+  if (!qbuf) return UMQ_ERR_EINVAL;
+  Block* b = reinterpret_cast<Block*>(qbuf);
+  qbuf->headroom_size = 0;
+  qbuf->buf_data = b->mem;
+  qbuf->buf_size = b->cap;
+  qbuf->data_size = 0;
+  qbuf->status = 0;
+  return UMQ_SUCCESS;
+}
+
+int umq_enqueue(uint64_t h, umq_buf_t* qbuf, umq_buf_t** bad) {
+  PerfScope ps(UMQ_PERF_ENQUEUE);
+  Queue* q = find(h);
+  if (!q || !qbuf) return UMQ_ERR_EINVAL;
+  if (!(g.cfg.feature & UMQ_FEATURE_API_BASE) && g.cfg.feature) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  for (umq_buf_t* b = qbuf; b;) {
+    umq_buf_t* nx = b->qbuf_next;
+    b->qbuf_next = nullptr;
+    const int rc = send_one(q, b, false);
+    if (rc != UMQ_SUCCESS) {
+      b->qbuf_next = nx;
+      if (bad) *bad = b;
+      return rc;
+    }
+    b = nx;
+  }
+  if (bad) *bad = nullptr;
+  progress(q);
+  return UMQ_SUCCESS;
+}
+
+umq_buf_t* umq_dequeue(uint64_t h) {
+  PerfScope ps(UMQ_PERF_DEQUEUE);
+  Queue* q = find(h);
+  if (!q) return nullptr;
+  std::lock_guard<std::mutex> l(q->mu);
+  progress(q);
+  if (q->rx_ready.empty()) return nullptr;
+  umq_buf_t* b = q->rx_ready.front();
+  q->rx_ready.pop_front();
+  return b;
+}
+
+int umq_post(uint64_t h, umq_buf_t* qbuf, umq_io_direction_t dir, umq_buf_t** bad) {
+  PerfScope ps(UMQ_PERF_POST_TX);
+  Queue* q = find(h);
+  if (!q || !qbuf) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  if (dir == UMQ_IO_RX) {
+    // application-provided receive buffers (instead of the automatic refill)
+    for (umq_buf_t* b = qbuf; b;) {
+      umq_buf_t* nx = b->qbuf_next;
+      b->qbuf_next = nullptr;
+      Block* blk = reinterpret_cast<Block*>(b);
+      if (urma_simple_post_recv(q->ep, b->buf_data, b->buf_size, reinterpret_cast<uint64_t>(blk)) != 0) {
+        b->qbuf_next = nx;
+        if (bad) *bad = b;
+        return UMQ_ERR_EAGAIN;
+      }
+      ++q->rx_posted;
+      if (q->fc) ++q->to_return;
+      b = nx;
+    }
+    if (bad) *bad = nullptr;
+    return UMQ_SUCCESS;
+  }
+  for (umq_buf_t* b = qbuf; b;) {
+    umq_buf_t* nx = b->qbuf_next;
+    b->qbuf_next = nullptr;
+    const int rc = send_one(q, b, true);
+    if (rc != UMQ_SUCCESS) {
+      b->qbuf_next = nx;
+      if (bad) *bad = b;
+      return rc;
+    }
+    b = nx;
+  }
+  if (bad) *bad = nullptr;
+  return UMQ_SUCCESS;
+}
+
+int umq_poll(uint64_t h, umq_io_direction_t dir, umq_buf_t** bufs, uint32_t max) {
+  PerfScope ps(UMQ_PERF_POLL_RX);
+  Queue* q = find(h);
+  if (!q || !bufs || max == 0) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  progress(q);
+  std::deque<umq_buf_t*>& src = dir == UMQ_IO_RX ? q->rx_ready : q->tx_done;
+  uint32_t n = 0;
+  while (n < max && !src.empty()) {
+    bufs[n++] = src.front();
+    src.pop_front();
+  }
+  return static_cast<int>(n);
+}
+
+int umq_rearm_interrupt(uint64_t h, int, umq_io_direction_t) {
+  Queue* q = find(h);
+  if (!q) return UMQ_ERR_EINVAL;
+  return urma_rearm_jfc(urma_simple_ep_jfc(q->ep), false) == URMA_SUCCESS ? UMQ_SUCCESS : UMQ_FAIL;
+}
+int umq_wait_interrupt(uint64_t h, int timeout_ms) {
+  Queue* q = find(h);
+  if (!q) return UMQ_ERR_EINVAL;
+  urma_jfc_t* jfc = urma_simple_ep_jfc(q->ep);
+  if (!jfc->cfg.jfce) return UMQ_ERR_EINVAL;
+  urma_jfc_t* fired[1];
+  return urma_wait_jfc(jfc->cfg.jfce, 1, timeout_ms, fired);
+}
+void umq_ack_interrupt(uint64_t h, uint32_t nevents) {
+  Queue* q = find(h);
+  if (!q) return;
+  urma_jfc_t* jfc = urma_simple_ep_jfc(q->ep);
+  urma_ack_jfc(&jfc, &nevents, 1);
+}
+int umq_interrupt_fd_get(uint64_t h) {
+  Queue* q = find(h);
+  if (!q) return -1;
+  urma_jfc_t* jfc = urma_simple_ep_jfc(q->ep);
+  return jfc->cfg.jfce ? jfc->cfg.jfce->fd : -1;
+}
+
+int umq_stats_io_get(uint64_t h, umq_io_stats_t* out) {
+  Queue* q = find(h);
+  if (!q || !out) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  *out = q->io;
+  return UMQ_SUCCESS;
+}
+int umq_stats_flow_control_get(uint64_t h, umq_fc_stats_t* out) {
+  Queue* q = find(h);
+  if (!q || !out) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  q->fcs.credits_local = q->credits > 0 ? q->credits : 0;
+  q->fcs.credits_remote = q->to_return;
+  *out = q->fcs;
+  return UMQ_SUCCESS;
+}
+int umq_stats_qbuf_pool_get(umq_qbuf_stats_t* out) {
+  if (!out) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g_pool.mu);
+  out->block_size = g_pool.block;
+  out->blocks_total = g_pool.total;
+  out->blocks_free = g_pool.free_list.size();
+  out->huge_allocs = g_pool.huge_allocs;
+  out->alloc_calls = g_pool.alloc_calls;
+  out->free_calls = g_pool.free_calls;
+  out->alloc_failures = g_pool.failures;
+  return UMQ_SUCCESS;
+}
+int umq_stats_perf_start(void) {
+  std::lock_guard<std::mutex> l(g.perf_mu);
+  for (auto& h : g.perf) h.reset();
+  g.perf_on = true;
+  return UMQ_SUCCESS;
+}
+int umq_stats_perf_stop(void) {
+  g.perf_on = false;
+  return UMQ_SUCCESS;
+}
+int umq_stats_perf_get(umq_perf_entry_t* e) {
+  if (!e) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g.perf_mu);
+  for (int i = 0; i < UMQ_PERF_RECORD_MAX; ++i) {
+    e[i].count = g.perf[i].count();
+    e[i].avg_ns = static_cast<uint64_t>(g.perf[i].mean());
+    e[i].min_ns = g.perf[i].min();
+    e[i].max_ns = g.perf[i].max();
+    e[i].p99_ns = g.perf[i].quantile(0.99);
+  }
+  return UMQ_SUCCESS;
+}
+int umq_info_to_str(uint64_t h, char* buf, uint32_t len) {
+  Queue* q = find(h);
+  if (!q || !buf || len == 0) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  return snprintf(buf, len,
+                  "umq %llu name=%s state=%d rx_depth=%u tx_depth=%u rx_buf=%u fc=%d credits=%lld owed=%u "
+                  "tx=%llu/%lluB rx=%llu/%lluB",
+                  (unsigned long long)q->h, q->opt.name, q->state.load(), q->opt.rx_depth, q->opt.tx_depth,
+                  q->opt.rx_buf_size, (int)q->fc, (long long)q->credits, q->to_return,
+                  (unsigned long long)q->io.tx_msgs, (unsigned long long)q->io.tx_bytes,
+                  (unsigned long long)q->io.rx_msgs, (unsigned long long)q->io.rx_bytes);
+}
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+/* UMQ: handle-based message queues with managed buffers on top of URMA jetties.
+ * API groups follow the reference's src/urpc/include/umq/umq_api.h:26-385 (init, create/destroy, bind, buffers,
+ * enqueue/dequeue, interrupts, state), umq_pro_api.h:30-76 (post/poll) and umq_dfx_api.h:26-199 (stats, perf). */
+#ifndef UMDK_UMQ_API_H
+#define UMDK_UMQ_API_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+#define UMQ_EXPORT __attribute__((visibility("default")))
+
+#define UMQ_SUCCESS 0
+#define UMQ_FAIL (-1)
+#define UMQ_ERR_EAGAIN (-11)
+#define UMQ_ERR_EINVAL (-22)
+#define UMQ_ERR_ENOMEM (-12)
+#define UMQ_ERR_ESTATE (-108)
+#define UMQ_INVALID_HANDLE 0
+#define UMQ_BATCH_SIZE 256
+#define UMQ_MAX_MSG_SIZE (10u << 20)
+#define UMQ_BIND_INFO_SIZE 128
+
+/* feature bits of umq_init_cfg_t.feature */
+#define UMQ_FEATURE_API_BASE 0x1u
+#define UMQ_FEATURE_API_PRO 0x2u
+#define UMQ_FEATURE_STATS 0x8u
+#define UMQ_FEATURE_PERF 0x10u
+#define UMQ_FEATURE_FLOW_CONTROL 0x20u
+
+typedef enum umq_trans_mode { UMQ_TRANS_MODE_UB = 0, UMQ_TRANS_MODE_IPC = 3 } umq_trans_mode_t;
+typedef enum umq_queue_mode { UMQ_MODE_POLLING = 0, UMQ_MODE_INTERRUPT = 1 } umq_queue_mode_t;
+typedef enum umq_state { UMQ_STATE_IDLE = 0, UMQ_STATE_READY = 1, UMQ_STATE_ERR = 2 } umq_state_t;
+typedef enum umq_io_direction { UMQ_IO_TX = 0, UMQ_IO_RX = 1 } umq_io_direction_t;
+typedef enum umq_buf_status { UMQ_BUF_OK = 0, UMQ_BUF_SEND_ERR = 1, UMQ_BUF_RECV_ERR = 2 } umq_buf_status_t;
+
+typedef struct umq_init_cfg {
+  uint32_t feature;
+  umq_trans_mode_t trans_mode;
+  char dev_name[64]; /* URMA device, "" = shm0 */
+  uint32_t block_size_kb; /* qbuf block size: 8, 16, 32 or 64 (0 = 8) */
+  uint64_t pool_bytes;    /* global pool size, 0 = 64 MiB */
+} umq_init_cfg_t;
+
+typedef struct umq_create_option {
+  char name[32];
+  uint32_t rx_buf_size, tx_buf_size; /* 0 = block size */
+  uint32_t rx_depth, tx_depth;       /* 0 = 128 */
+  umq_queue_mode_t mode;
+  uint32_t token;
+} umq_create_option_t;
+
+/* Message buffer. `buf_data` points `headroom_size` bytes into the block; buffers chain through `qbuf_next`. */
+typedef struct umq_buf {
+  struct umq_buf* qbuf_next;
+  uint64_t umqh;
+  uint32_t total_data_size; /* of the whole chain, valid in the first buffer */
+  uint32_t buf_size;        /* capacity of this buffer's data area */
+  uint32_t data_size;       /* valid bytes at buf_data */
+  uint16_t headroom_size;
+  uint16_t status;          /* umq_buf_status_t after completion */
+  uint64_t user_ctx;
+  char* buf_data;
+  uint64_t rsvd[8];
+} umq_buf_t;
+
+UMQ_EXPORT int umq_init(const umq_init_cfg_t* cfg);
+UMQ_EXPORT void umq_uninit(void);
+UMQ_EXPORT uint64_t umq_create(const umq_create_option_t* opt);
+UMQ_EXPORT int umq_destroy(uint64_t umqh);
+UMQ_EXPORT uint32_t umq_bind_info_get(uint64_t umqh, uint8_t* bind_info, uint32_t size);
+UMQ_EXPORT int umq_bind(uint64_t umqh, const uint8_t* bind_info, uint32_t size);
+UMQ_EXPORT int umq_unbind(uint64_t umqh);
+UMQ_EXPORT int umq_state_set(uint64_t umqh, umq_state_t state);
+UMQ_EXPORT umq_state_t umq_state_get(uint64_t umqh);
+/* buffers */
+UMQ_EXPORT umq_buf_t* umq_buf_alloc(uint32_t request_size, uint32_t request_qbuf_num, uint64_t umqh);
+UMQ_EXPORT void umq_buf_free(umq_buf_t* qbuf);
+UMQ_EXPORT int umq_buf_headroom_reset(umq_buf_t* qbuf, uint16_t headroom_size);
+UMQ_EXPORT int umq_buf_reset(umq_buf_t* qbuf);
+/* base API */
+UMQ_EXPORT int umq_enqueue(uint64_t umqh, umq_buf_t* qbuf, umq_buf_t** bad_qbuf);
+UMQ_EXPORT umq_buf_t* umq_dequeue(uint64_t umqh);
+/* pro API */
+UMQ_EXPORT int umq_post(uint64_t umqh, umq_buf_t* qbuf, umq_io_direction_t dir, umq_buf_t** bad_qbuf);
+UMQ_EXPORT int umq_poll(uint64_t umqh, umq_io_direction_t dir, umq_buf_t** bufs, uint32_t max);
+/* interrupt mode */
+UMQ_EXPORT int umq_rearm_interrupt(uint64_t umqh, int solicited, umq_io_direction_t dir);
+UMQ_EXPORT int umq_wait_interrupt(uint64_t umqh, int timeout_ms);
+UMQ_EXPORT void umq_ack_interrupt(uint64_t umqh, uint32_t nevents);
+UMQ_EXPORT int umq_interrupt_fd_get(uint64_t umqh);
+/* dfx */
+typedef struct umq_io_stats {
+  uint64_t tx_msgs, tx_bytes, rx_msgs, rx_bytes, tx_errors, rx_errors, tx_eagain;
+} umq_io_stats_t;
+typedef struct umq_fc_stats {
+  uint64_t credits_local, credits_remote, credits_granted, credits_returned, stalls, window;
+} umq_fc_stats_t;
+typedef struct umq_qbuf_stats {
+  uint64_t block_size, blocks_total, blocks_free, huge_allocs, alloc_calls, free_calls, alloc_failures;
+} umq_qbuf_stats_t;
+typedef struct umq_perf_entry {
+  uint64_t count, avg_ns, min_ns, max_ns, p99_ns;
+} umq_perf_entry_t;
+typedef enum umq_perf_record { UMQ_PERF_ENQUEUE = 0, UMQ_PERF_DEQUEUE, UMQ_PERF_POST_TX, UMQ_PERF_POLL_RX,
+                               UMQ_PERF_BUF_ALLOC, UMQ_PERF_RECORD_MAX } umq_perf_record_t;
+UMQ_EXPORT int umq_stats_io_get(uint64_t umqh, umq_io_stats_t* out);
+UMQ_EXPORT int umq_stats_flow_control_get(uint64_t umqh, umq_fc_stats_t* out);
+UMQ_EXPORT int umq_stats_qbuf_pool_get(umq_qbuf_stats_t* out);
+UMQ_EXPORT int umq_stats_perf_start(void);
+UMQ_EXPORT int umq_stats_perf_stop(void);
+UMQ_EXPORT int umq_stats_perf_get(umq_perf_entry_t* entries /* [UMQ_PERF_RECORD_MAX] */);
+UMQ_EXPORT int umq_info_to_str(uint64_t umqh, char* buf, uint32_t len);
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -61,13 +61,13 @@ def _targets():
         t["ums_preload"] = dict(kind="cxx_shared", sources=[pre], includes=[CSRC / "usock", CSRC / "common"],
                                 libs=["-L" + str(LIB), "-Wl,-rpath,$ORIGIN", "-lumdk_usock", "-ldl", "-lpthread",
                                       "-lrt"], deps=["umdk_usock"], out=LIB / "libums_preload.so")
+    have = [n for n in ("umdk_urpc", "umdk_umq", "umdk_dlock", "umdk_usock", "umdk_urma") if n in t]
     for tool in sorted((CSRC / "tools").glob("*.cpp")):
         t["tool_" + tool.stem] = dict(
             kind="cxx_exe", sources=[tool],
             includes=[CSRC / "common", CSRC / "urma", CSRC / "umq", CSRC / "urpc", CSRC / "dlock", CSRC / "usock"],
-            libs=["-L" + str(LIB), "-Wl,-rpath,$ORIGIN/..", "-lumdk_urpc", "-lumdk_umq", "-lumdk_dlock",
-                  "-lumdk_usock", "-lumdk_urma", "-lpthread", "-ldl", "-lrt"],
-            deps=["umdk_urma", "umdk_umq", "umdk_urpc", "umdk_dlock", "umdk_usock"], out=LIB / "bin" / tool.stem)
+            libs=["-L" + str(LIB), "-Wl,-rpath,$ORIGIN/.."] + ["-l" + n for n in have] + ["-lpthread", "-ldl", "-lrt"],
+            deps=have, out=LIB / "bin" / tool.stem)
     return t
 
 
