@@ -229,6 +229,14 @@ struct ShmCtx {
   std::deque<urma_async_event_t> events;
   int event_fd = -1;
   std::atomic<bool> drop_tx{false};  // fault injection: outgoing requests vanish (a dead link)
+  // Answers that did not fit into a full peer inbox. The NIC thread never blocks on a full ring (two NIC threads
+  // answering into each other's full inbox would deadlock); it parks the answer here and retries later.
+  struct Deferred {
+    uint32_t uasid;
+    MsgHdr h;
+    std::vector<uint8_t> payload;
+  };
+  std::deque<Deferred> deferred;  // touched by the NIC thread only
 };
 
 // ---------------------------------------------------------------------------------------------- helpers
@@ -336,7 +344,39 @@ void reply(ShmCtx* c, const MsgHdr& req, uint32_t type, urma_cr_status_t st, uin
   r.operand = operand;
   r.len = len;
   r.frag_off = off;
-  send_msg(in, r, payload);
+  if (c->deferred.empty()) {
+    uint64_t pos;
+    if (Slot* s = ring_reserve(in, &pos)) {
+      s->h = r;
+      if (len && payload) memcpy(s->payload, payload, len);
+      ring_publish(s, pos);
+      return;
+    }
+  }
+  ShmCtx::Deferred d;
+  d.uasid = req.src_uasid;
+  d.h = r;
+  if (len && payload) d.payload.assign(static_cast<const uint8_t*>(payload), static_cast<const uint8_t*>(payload) + len);
+  c->deferred.push_back(std::move(d));
+}
+
+// Retries parked answers in order; stops at the first one that still does not fit.
+void flush_deferred(ShmCtx* c) {
+  while (!c->deferred.empty()) {
+    ShmCtx::Deferred& d = c->deferred.front();
+    Inbox* in = peer_inbox(c, d.uasid);
+    if (!in) {
+      c->deferred.pop_front();
+      continue;
+    }
+    uint64_t pos;
+    Slot* s = ring_reserve(in, &pos);
+    if (!s) return;
+    s->h = d.h;
+    if (!d.payload.empty()) memcpy(s->payload, d.payload.data(), d.payload.size());
+    ring_publish(s, pos);
+    c->deferred.pop_front();
+  }
 }
 
 // Delivers a complete incoming message into a posted receive buffer, or parks it until one is posted.
@@ -557,6 +597,7 @@ void nic_loop(ShmCtx* c) {
   uint32_t idle = 0;
   uint64_t last_scan = ub::now_ns();
   while (!c->stop.load(std::memory_order_relaxed)) {
+    if (!c->deferred.empty()) flush_deferred(c);
     Inbox* in = c->inbox;
     const uint64_t pos = in->deq.load(std::memory_order_relaxed);
     Slot* s = &in->slots[pos & (kRingSlots - 1)];
