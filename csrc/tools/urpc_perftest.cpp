@@ -1,0 +1,178 @@
+// urpc_perftest: latency / call-rate measurement and self-check of the URPC framework (server thread + client in
+// one process by default; `--server PORT` / `--client PORT` run the two sides as separate processes).
+//   urpc_perftest [--size N] [--iters N] [--selftest]
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <thread>
+#include <vector>
+
+#include "ub_util.h"
+#include "urpc_api.h"
+
+static int echo_fn(const void* a, uint32_t len, void* rsp, uint32_t* rlen, void*) {
+  if (len > *rlen) return -1;
+  memcpy(rsp, a, len);
+  *rlen = len;
+  return 0;
+}
+static int sum_fn(const void* a, uint32_t len, void* rsp, uint32_t* rlen, void*) {
+  uint64_t s = 0;
+  const uint8_t* p = static_cast<const uint8_t*>(a);
+  for (uint32_t i = 0; i < len; ++i) s += p[i];
+  memcpy(rsp, &s, 8);
+  *rlen = 8;
+  return 0;
+}
+static std::atomic<int> g_lost{0};
+static void ka_cb(uint32_t, int alive, void*) {
+  if (!alive) ++g_lost;
+}
+static int fail(const char* w) {
+  fprintf(stderr, "urpc_perftest: FAILED: %s\n", w);
+  return 1;
+}
+
+int main(int argc, char** argv) {
+  uint32_t size = 4096, iters = 5000;
+  bool selftest = false;
+  int server_port = -1, client_port = -1;
+  for (int i = 1; i < argc; ++i) {
+    if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--selftest")) selftest = true;
+    else if (!strcmp(argv[i], "--server") && i + 1 < argc) server_port = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--client") && i + 1 < argc) client_port = atoi(argv[++i]);
+  }
+  urpc_config_t cfg{};
+  cfg.role = URPC_ROLE_SERVER_CLIENT;
+  cfg.keepalive_interval_ms = selftest ? 50 : 0;
+  cfg.keepalive_miss_limit = 3;
+  cfg.default_timeout_ms = 3000;
+  if (urpc_init(&cfg) != URPC_SUCCESS) return fail("urpc_init");
+  urpc_keepalive_callback_register(ka_cb, nullptr);
+  std::atomic<bool> stop{false}, serve{true};
+  std::thread srv;
+  int port = client_port;
+  if (client_port < 0) {
+    urpc_func_register(1, echo_fn, nullptr);
+    urpc_func_register(2, sum_fn, nullptr);
+    port = urpc_server_start("127.0.0.1", server_port > 0 ? server_port : 0);
+    if (port <= 0) return fail("server_start");
+    srv = std::thread([&] {
+      urpc_poll_msg_t m[8];
+      while (!stop.load()) {
+        if (!serve.load()) {
+          usleep(1000);
+          continue;
+        }
+        const int n = urpc_server_poll(m, 8);
+        for (int i = 0; i < n; ++i) {
+          if (m[i].func_id == 7) {  // handled by the application: reverse the bytes
+            std::vector<uint8_t> r(static_cast<uint8_t*>(m[i].data), static_cast<uint8_t*>(m[i].data) + m[i].len);
+            for (size_t a = 0, b = r.size(); a + 1 < b; ++a, --b) std::swap(r[a], r[b - 1]);
+            urpc_func_return(&m[i], r.data(), (uint32_t)r.size(), 0);
+          }  // func 9: never answered (timeout test)
+          urpc_msg_release(&m[i]);
+        }
+        if (n == 0) sched_yield();
+      }
+    });
+    if (server_port > 0) {
+      printf("urpc server on port %d\n", port);
+      fflush(stdout);
+      pause();
+    }
+  }
+  const int ch = urpc_channel_create();
+  if (ch < 0 || urpc_channel_server_attach(ch, "127.0.0.1", (uint16_t)port) != URPC_SUCCESS) return fail("attach");
+  std::vector<uint8_t> arg(size), rsp(size + 64);
+  for (uint32_t i = 0; i < size; ++i) arg[i] = (uint8_t)(i * 7 + 1);
+  urpc_sge_t sg{arg.data(), size};
+  urpc_call_wr_t wr{1, &sg, 1, 0};
+  uint32_t rlen = 0;
+  urpc_call_option_t sync{0, 1, rsp.data(), (uint32_t)rsp.size(), &rlen};
+  int rc = 0;
+  // synchronous echo: latency
+  uint64_t t0 = ub::now_ns();
+  const uint32_t lat_iters = iters < 2000 ? iters : 2000;
+  for (uint32_t i = 0; i < lat_iters; ++i) {
+    arg[0] = (uint8_t)i;
+    if (urpc_func_call(ch, &wr, &sync) != 0 || rlen != size || memcmp(arg.data(), rsp.data(), size)) {
+      rc = fail("sync echo");
+      break;
+    }
+  }
+  const double lat_us = (ub::now_ns() - t0) / 1e3 / lat_iters;
+  // pipelined asynchronous calls: rate
+  t0 = ub::now_ns();
+  uint32_t sent = 0, done = 0;
+  urpc_poll_msg_t m[32];
+  wr.func_id = 2;
+  uint64_t expect = 0;
+  for (uint32_t i = 0; i < size; ++i) expect += arg[i];
+  while (done < iters && rc == 0) {
+    while (sent < iters && sent - done < 64) {
+      wr.user_ctx = sent;
+      const int r = urpc_func_call(ch, &wr, nullptr);
+      if (r == URPC_ERR_EAGAIN) break;
+      if (r < 0) {
+        rc = fail("async call");
+        break;
+      }
+      ++sent;
+    }
+    const int n = urpc_func_poll(ch, m, 32);
+    for (int i = 0; i < n; ++i) {
+      uint64_t s = 0;
+      if (m[i].event != URPC_POLL_RSP || m[i].len != 8 || (memcpy(&s, m[i].data, 8), s != expect)) rc = fail("async rsp");
+      urpc_msg_release(&m[i]);
+      ++done;
+    }
+  }
+  const double sec = (ub::now_ns() - t0) * 1e-9;
+  uint64_t cnt, avg, p99;
+  urpc_perf_get(&cnt, &avg, &p99);
+  printf("size=%u: sync echo %.1f us/call; async %.0f calls/s (%.1f MB/s args); call latency avg %.1f us p99 %.1f us\n",
+         size, lat_us, iters / sec, iters * (double)size / sec / 1e6, avg / 1e3, p99 / 1e3);
+  if (selftest && rc == 0) {
+    // request handled by the application through poll / return
+    wr.func_id = 7;
+    if (urpc_func_call(ch, &wr, &sync) != 0 || rlen != size || rsp[0] != arg[size - 1] || rsp[size - 1] != arg[0])
+      rc = fail("manual return");
+    // a call that the server never answers times out, synchronously and asynchronously
+    wr.func_id = 9;
+    urpc_call_option_t quick{200, 1, rsp.data(), (uint32_t)rsp.size(), &rlen};
+    if (urpc_func_call(ch, &wr, &quick) != URPC_ERR_TIMEOUT) rc = fail("sync timeout");
+    urpc_call_option_t aq{200, 0, nullptr, 0, nullptr};
+    if (urpc_func_call(ch, &wr, &aq) < 0) rc = fail("async call for timeout");
+    bool got_timeout = false;
+    for (int tries = 0; tries < 2000 && !got_timeout; ++tries) {
+      const int n = urpc_func_poll(ch, m, 4);
+      for (int i = 0; i < n; ++i) got_timeout |= m[i].event == URPC_POLL_TIMEOUT;
+      usleep(1000);
+    }
+    if (!got_timeout) rc = fail("async timeout event");
+    // unknown function id with nobody handling it
+    urpc_stats_t st{};
+    urpc_stats_get(&st);
+    if (st.timeouts < 2 || st.calls < iters) rc = fail("statistics");
+    // the server stops polling: keepalive probes go unanswered and the callback fires; later calls fail fast
+    serve = false;
+    for (int i = 0; i < 400 && g_lost.load() == 0; ++i) usleep(10000);
+    if (g_lost.load() == 0) rc = fail("keepalive did not detect the silent server");
+    wr.func_id = 1;
+    if (urpc_func_call(ch, &wr, &sync) != URPC_ERR_SESSION_CLOSE) rc = fail("call on a lost channel must fail");
+    serve = true;
+  }
+  urpc_channel_server_detach(ch);
+  urpc_channel_destroy(ch);
+  stop = true;
+  if (srv.joinable()) srv.join();
+  urpc_uninit();
+  if (rc == 0) printf("urpc_perftest: OK\n");
+  return rc;
+}

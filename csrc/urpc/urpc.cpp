@@ -1,0 +1,651 @@
+// URPC framework: function calls over UMQ queues with a TCP control plane.
+//
+// Kept from the reference (src/urpc/framework): a client "channel" is attached to a server through a TCP handshake
+// that exchanges queue information (lib/control/ip/ip_handshaker.c:329-371); requests carry a packed header with
+// function id, request id and client channel (protocol/protocol.h); `urpc_func_call` records a pending entry with a
+// deadline and optionally blocks (lib/datapath/dp.c:352-535); the server polls its queues, executes the registered
+// function and returns the response (dp.c:1258-1322, 1897-2002); the client matches responses to pending entries
+// (dp.c:1333-1452); request timeouts and keepalive probes with a callback on peer loss
+// (lib/manager/keepalive_probe.c, keepalive_task.c); counters and a call-latency record (lib/control/dfx).
+#include "urpc_api.h"
+
+#include <arpa/inet.h>
+#include <errno.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
+#include <poll.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <map>
+#include <mutex>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include "ub_util.h"
+#include "umq_api.h"
+#include "urpc_proto.h"
+
+namespace {
+
+using urpc_proto::Head;
+constexpr uint32_t kHelloMagic = 0x55525043;  // "URPC"
+
+struct Hello {
+  uint32_t magic, version, blob_len, channel;
+  uint8_t blob[UMQ_BIND_INFO_SIZE];
+};
+
+struct Pending {
+  uint64_t func_id, user_ctx, t0, deadline;
+  bool sync = false;
+  bool done = false;
+  int status = 0;
+  std::vector<uint8_t> rsp;
+};
+struct Ready {
+  urpc_poll_event_t ev;
+  uint64_t func_id, user_ctx;
+  uint32_t req_id;
+  int status;
+  umq_buf_t* buf;  // owns the payload (may be null)
+};
+struct Channel {
+  uint32_t id;
+  uint64_t umqh = 0;
+  int tcp = -1;
+  std::atomic<bool> attached{false};
+  std::atomic<bool> lost{false};
+  std::mutex mu;
+  std::unordered_map<uint32_t, Pending> pending;
+  std::deque<Ready> ready;
+  uint32_t next_req = 1;
+  uint32_t ka_outstanding = 0;
+};
+struct Session {
+  uint64_t umqh;
+  int tcp;
+  uint32_t id;
+};
+struct Func {
+  urpc_func_t fn;
+  void* ctx;
+};
+
+struct Global {
+  std::mutex mu;
+  bool inited = false;
+  urpc_config_t cfg{};
+  std::map<uint32_t, Channel*> channels;
+  uint32_t next_ch = 0;
+  std::vector<Session*> sessions;
+  std::unordered_map<uint64_t, Func> funcs;
+  int listen_fd = -1;
+  std::thread accept_thr, ka_thr;
+  std::atomic<bool> stop{false};
+  urpc_keepalive_cb_t ka_cb = nullptr;
+  void* ka_ctx = nullptr;
+  urpc_stats_t stats{};
+  ub::PerfHist lat;
+  std::mutex stat_mu;
+};
+Global g;
+
+bool read_full(int fd, void* buf, size_t n, int timeout_ms = 5000) {
+  uint8_t* p = static_cast<uint8_t*>(buf);
+  while (n) {
+    pollfd pf{fd, POLLIN, 0};
+    if (poll(&pf, 1, timeout_ms) <= 0) return false;
+    const ssize_t r = read(fd, p, n);
+    if (r <= 0) return false;
+    p += r;
+    n -= r;
+  }
+  return true;
+}
+bool write_full(int fd, const void* buf, size_t n) {
+  const uint8_t* p = static_cast<const uint8_t*>(buf);
+  while (n) {
+    const ssize_t r = write(fd, p, n);
+    if (r <= 0) return false;
+    p += r;
+    n -= r;
+  }
+  return true;
+}
+
+uint64_t make_queue(const char* name) {
+  umq_create_option_t o{};
+  snprintf(o.name, sizeof(o.name), "%s", name);
+  o.rx_depth = 128;
+  o.tx_depth = 128;
+  o.rx_buf_size = 64 * 1024;
+  o.token = 0x75727063;
+  return umq_create(&o);
+}
+
+int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, const void* flat, uint32_t flat_len) {
+  uint32_t total = flat_len;
+  for (uint32_t i = 0; i < nsg; ++i) total += sg[i].len;
+  umq_buf_t* b = umq_buf_alloc(sizeof(urpc_req_head_t) + total, 1, umqh);
+  if (!b) return URPC_ERR_EAGAIN;
+  Head hh = h;
+  hh.total_size = total;
+  urpc_proto::encode(hh, reinterpret_cast<urpc_req_head_t*>(b->buf_data));
+  char* p = b->buf_data + sizeof(urpc_req_head_t);
+  for (uint32_t i = 0; i < nsg; ++i) {
+    memcpy(p, sg[i].addr, sg[i].len);
+    p += sg[i].len;
+  }
+  if (flat_len) memcpy(p, flat, flat_len);
+  b->data_size = sizeof(urpc_req_head_t) + total;
+  umq_buf_t* bad = nullptr;
+  const uint64_t deadline = ub::now_ns() + 2000000000ull;
+  for (;;) {
+    const int rc = umq_enqueue(umqh, b, &bad);
+    if (rc == UMQ_SUCCESS) break;
+    if (rc != UMQ_ERR_EAGAIN || ub::now_ns() > deadline) {
+      umq_buf_free(b);
+      return rc == UMQ_ERR_EAGAIN ? URPC_ERR_EAGAIN : URPC_FAIL;
+    }
+    sched_yield();
+  }
+  std::lock_guard<std::mutex> l(g.stat_mu);
+  g.stats.bytes_tx += total;
+  return URPC_SUCCESS;
+}
+
+// Drains the channel's queue: responses complete pending calls, expired calls time out. Caller holds ch->mu.
+void channel_progress(Channel* ch) {
+  for (;;) {
+    umq_buf_t* b = umq_dequeue(ch->umqh);
+    if (!b) break;
+    Head h;
+    if (b->data_size < sizeof(urpc_req_head_t) ||
+        !urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) ||
+        (h.type != URPC_MSG_RSP && h.type != URPC_MSG_ACK_AND_RSP)) {
+      umq_buf_free(b);
+      continue;
+    }
+    {
+      std::lock_guard<std::mutex> l(g.stat_mu);
+      g.stats.bytes_rx += h.total_size;
+    }
+    if (h.func_id == URPC_FUNC_ID_KEEPALIVE) {
+      ch->ka_outstanding = 0;
+      umq_buf_free(b);
+      continue;
+    }
+    auto it = ch->pending.find(h.req_id);
+    if (it == ch->pending.end()) {  // late answer of a call that already timed out or was cancelled
+      umq_buf_free(b);
+      continue;
+    }
+    Pending& p = it->second;
+    {
+      std::lock_guard<std::mutex> l(g.stat_mu);
+      ++g.stats.responses;
+      g.lat.add(ub::now_ns() - p.t0);
+    }
+    if (p.sync) {
+      p.rsp.assign(b->buf_data + sizeof(urpc_req_head_t), b->buf_data + b->data_size);
+      p.status = h.status;
+      p.done = true;
+      umq_buf_free(b);
+    } else {
+      ch->ready.push_back(Ready{URPC_POLL_RSP, p.func_id, p.user_ctx, h.req_id, h.status, b});
+      ch->pending.erase(it);
+    }
+  }
+  const uint64_t now = ub::now_ns();
+  for (auto it = ch->pending.begin(); it != ch->pending.end();) {
+    Pending& p = it->second;
+    if (!p.done && now > p.deadline) {
+      {
+        std::lock_guard<std::mutex> l(g.stat_mu);
+        ++g.stats.timeouts;
+      }
+      if (p.sync) {
+        p.status = URPC_ERR_TIMEOUT;
+        p.done = true;
+        ++it;
+      } else {
+        ch->ready.push_back(Ready{URPC_POLL_TIMEOUT, p.func_id, p.user_ctx, it->first, URPC_ERR_TIMEOUT, nullptr});
+        it = ch->pending.erase(it);
+      }
+    } else {
+      ++it;
+    }
+  }
+}
+
+void accept_loop() {
+  while (!g.stop.load()) {
+    pollfd pf{g.listen_fd, POLLIN, 0};
+    if (poll(&pf, 1, 100) <= 0) continue;
+    const int fd = accept(g.listen_fd, nullptr, nullptr);
+    if (fd < 0) continue;
+    int one = 1;
+    setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+    Hello hello;
+    if (!read_full(fd, &hello, sizeof(hello)) || hello.magic != kHelloMagic || hello.version != urpc_proto::kVersion) {
+      close(fd);
+      continue;
+    }
+    const uint64_t q = make_queue("urpc-srv");
+    Hello rsp{kHelloMagic, urpc_proto::kVersion, 0, 0, {0}};
+    if (!q || umq_bind(q, hello.blob, hello.blob_len) != UMQ_SUCCESS) {
+      if (q) umq_destroy(q);
+      close(fd);
+      continue;
+    }
+    rsp.blob_len = umq_bind_info_get(q, rsp.blob, sizeof(rsp.blob));
+    Session* s = new Session{q, fd, 0};
+    {
+      std::lock_guard<std::mutex> l(g.mu);
+      s->id = static_cast<uint32_t>(g.sessions.size());
+      rsp.channel = s->id;
+      g.sessions.push_back(s);
+    }
+    if (!write_full(fd, &rsp, sizeof(rsp))) {
+      // the client went away during the handshake; the session is reaped by server_poll when its socket closes
+    }
+  }
+}
+
+void keepalive_loop() {
+  const uint32_t interval = g.cfg.keepalive_interval_ms;
+  const uint32_t limit = g.cfg.keepalive_miss_limit ? g.cfg.keepalive_miss_limit : 3;
+  while (!g.stop.load()) {
+    for (uint32_t slept = 0; slept < interval && !g.stop.load(); slept += 10) usleep(10000);
+    std::vector<Channel*> chs;
+    {
+      std::lock_guard<std::mutex> l(g.mu);
+      for (auto& kv : g.channels) chs.push_back(kv.second);
+    }
+    for (Channel* ch : chs) {
+      if (!ch->attached.load() || ch->lost.load()) continue;
+      bool lost = false;
+      {
+        std::lock_guard<std::mutex> l(ch->mu);
+        channel_progress(ch);
+        if (ch->ka_outstanding >= limit) {
+          lost = true;
+        } else {
+          Head h{urpc_proto::kVersion, URPC_MSG_REQ, 1, URPC_FUNC_ID_KEEPALIVE, 0, ch->id, 0, 0};
+          send_msg(ch->umqh, h, nullptr, 0, nullptr, 0);
+          ++ch->ka_outstanding;
+          std::lock_guard<std::mutex> l2(g.stat_mu);
+          ++g.stats.keepalive_sent;
+        }
+      }
+      if (lost) {
+        ch->lost = true;
+        {
+          std::lock_guard<std::mutex> l(g.stat_mu);
+          ++g.stats.keepalive_lost;
+        }
+        if (g.ka_cb) g.ka_cb(ch->id, 0, g.ka_ctx);
+      }
+    }
+  }
+}
+
+Channel* get_channel(uint32_t id) {
+  std::lock_guard<std::mutex> l(g.mu);
+  auto it = g.channels.find(id);
+  return it == g.channels.end() ? nullptr : it->second;
+}
+
+}  // namespace
+
+extern "C" {
+
+int urpc_init(const urpc_config_t* cfg) {
+  std::lock_guard<std::mutex> l(g.mu);
+  if (g.inited) return URPC_SUCCESS;
+  if (cfg) g.cfg = *cfg;
+  if (!g.cfg.default_timeout_ms) g.cfg.default_timeout_ms = 5000;
+  umq_init_cfg_t uc{};
+  uc.feature = UMQ_FEATURE_API_BASE | UMQ_FEATURE_STATS | UMQ_FEATURE_FLOW_CONTROL;
+  uc.block_size_kb = 64;
+  snprintf(uc.dev_name, sizeof(uc.dev_name), "%s", g.cfg.dev_name);
+  if (umq_init(&uc) != UMQ_SUCCESS) return URPC_FAIL;
+  g.stop = false;
+  g.inited = true;
+  if (g.cfg.keepalive_interval_ms) g.ka_thr = std::thread(keepalive_loop);
+  return URPC_SUCCESS;
+}
+
+void urpc_uninit(void) {
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    if (!g.inited) return;
+    g.stop = true;
+  }
+  if (g.accept_thr.joinable()) g.accept_thr.join();
+  if (g.ka_thr.joinable()) g.ka_thr.join();
+  std::lock_guard<std::mutex> l(g.mu);
+  if (g.listen_fd >= 0) close(g.listen_fd);
+  g.listen_fd = -1;
+  for (auto& kv : g.channels) {
+    if (kv.second->tcp >= 0) close(kv.second->tcp);
+    if (kv.second->umqh) umq_destroy(kv.second->umqh);
+    delete kv.second;
+  }
+  g.channels.clear();
+  for (Session* s : g.sessions) {
+    if (s->tcp >= 0) close(s->tcp);
+    umq_destroy(s->umqh);
+    delete s;
+  }
+  g.sessions.clear();
+  g.funcs.clear();
+  umq_uninit();
+  g.inited = false;
+}
+
+int urpc_server_start(const char* ip, uint16_t port) {
+  if (!g.inited) return URPC_FAIL;
+  const int fd = socket(AF_INET, SOCK_STREAM, 0);
+  if (fd < 0) return URPC_FAIL;
+  int one = 1;
+  setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+  sockaddr_in a{};
+  a.sin_family = AF_INET;
+  a.sin_port = htons(port);
+  a.sin_addr.s_addr = ip && *ip ? inet_addr(ip) : htonl(INADDR_LOOPBACK);
+  if (bind(fd, reinterpret_cast<sockaddr*>(&a), sizeof(a)) != 0 || listen(fd, 64) != 0) {
+    close(fd);
+    return URPC_FAIL;
+  }
+  socklen_t len = sizeof(a);
+  getsockname(fd, reinterpret_cast<sockaddr*>(&a), &len);
+  g.listen_fd = fd;
+  g.accept_thr = std::thread(accept_loop);
+  return ntohs(a.sin_port);
+}
+
+int urpc_func_register(uint64_t func_id, urpc_func_t fn, void* ctx) {
+  if (!fn || func_id >= URPC_FUNC_ID_KEEPALIVE) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g.mu);
+  if (g.funcs.count(func_id)) return URPC_ERR_EINVAL;
+  g.funcs[func_id] = Func{fn, ctx};
+  return URPC_SUCCESS;
+}
+int urpc_func_unregister(uint64_t func_id) {
+  std::lock_guard<std::mutex> l(g.mu);
+  return g.funcs.erase(func_id) ? URPC_SUCCESS : URPC_ERR_FUNC_NOT_FOUND;
+}
+
+int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
+  std::vector<Session*> ss;
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    ss = g.sessions;
+  }
+  int n = 0;
+  static thread_local std::vector<uint8_t> rsp(64 * 1024);
+  for (Session* s : ss) {
+    for (int budget = 0; budget < 64; ++budget) {
+      umq_buf_t* b = umq_dequeue(s->umqh);
+      if (!b) break;
+      Head h;
+      if (b->data_size < sizeof(urpc_req_head_t) ||
+          !urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) || h.type != URPC_MSG_REQ) {
+        umq_buf_free(b);
+        continue;
+      }
+      const char* args = b->buf_data + sizeof(urpc_req_head_t);
+      const uint32_t alen = b->data_size - sizeof(urpc_req_head_t);
+      Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, h.func_id, h.req_id, h.channel, 0, 0};
+      if (h.func_id == URPC_FUNC_ID_KEEPALIVE) {
+        send_msg(s->umqh, rh, nullptr, 0, nullptr, 0);
+        umq_buf_free(b);
+        continue;
+      }
+      Func f{nullptr, nullptr};
+      {
+        std::lock_guard<std::mutex> l(g.mu);
+        auto it = g.funcs.find(h.func_id);
+        if (it != g.funcs.end()) f = it->second;
+      }
+      {
+        std::lock_guard<std::mutex> l(g.stat_mu);
+        ++g.stats.requests_served;
+        g.stats.bytes_rx += alen;
+      }
+      if (f.fn) {
+        uint32_t rlen = static_cast<uint32_t>(rsp.size());
+        const int st = f.fn(args, alen, rsp.data(), &rlen, f.ctx);
+        rh.status = static_cast<int8_t>(st);
+        send_msg(s->umqh, rh, nullptr, 0, rsp.data(), rlen > rsp.size() ? 0 : rlen);
+        umq_buf_free(b);
+      } else if (msgs && n < max) {
+        msgs[n].event = URPC_POLL_REQ;
+        msgs[n].func_id = h.func_id;
+        msgs[n].req_id = h.req_id;
+        msgs[n].user_ctx = (uint64_t(s->id) << 32) | h.channel;
+        msgs[n].data = const_cast<char*>(args);
+        msgs[n].len = alen;
+        msgs[n].status = 0;
+        msgs[n].priv = b;
+        ++n;
+      } else {
+        rh.status = static_cast<int8_t>(URPC_ERR_FUNC_NOT_FOUND);
+        send_msg(s->umqh, rh, nullptr, 0, nullptr, 0);
+        umq_buf_free(b);
+      }
+    }
+  }
+  return n;
+}
+
+int urpc_func_return(const urpc_poll_msg_t* req, const void* rsp, uint32_t len, int status) {
+  if (!req) return URPC_ERR_EINVAL;
+  const uint32_t sid = static_cast<uint32_t>(req->user_ctx >> 32);
+  Session* s = nullptr;
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    if (sid < g.sessions.size()) s = g.sessions[sid];
+  }
+  if (!s) return URPC_ERR_EINVAL;
+  Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, req->func_id, req->req_id,
+          static_cast<uint32_t>(req->user_ctx & 0xffffff), 0, static_cast<int8_t>(status)};
+  return send_msg(s->umqh, rh, nullptr, 0, rsp, len);
+}
+
+int urpc_channel_create(void) {
+  if (!g.inited) return URPC_FAIL;
+  Channel* ch = new Channel();
+  ch->umqh = make_queue("urpc-cli");
+  if (!ch->umqh) {
+    delete ch;
+    return URPC_FAIL;
+  }
+  std::lock_guard<std::mutex> l(g.mu);
+  ch->id = g.next_ch++;
+  g.channels[ch->id] = ch;
+  return static_cast<int>(ch->id);
+}
+
+int urpc_channel_server_attach(uint32_t chid, const char* ip, uint16_t port) {
+  Channel* ch = get_channel(chid);
+  if (!ch || ch->attached.load()) return URPC_ERR_EINVAL;
+  const int fd = socket(AF_INET, SOCK_STREAM, 0);
+  if (fd < 0) return URPC_FAIL;
+  sockaddr_in a{};
+  a.sin_family = AF_INET;
+  a.sin_port = htons(port);
+  a.sin_addr.s_addr = ip && *ip ? inet_addr(ip) : htonl(INADDR_LOOPBACK);
+  if (connect(fd, reinterpret_cast<sockaddr*>(&a), sizeof(a)) != 0) {
+    close(fd);
+    return URPC_FAIL;
+  }
+  int one = 1;
+  setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+  Hello hello{kHelloMagic, urpc_proto::kVersion, 0, chid, {0}};
+  hello.blob_len = umq_bind_info_get(ch->umqh, hello.blob, sizeof(hello.blob));
+  Hello rsp;
+  if (!write_full(fd, &hello, sizeof(hello)) || !read_full(fd, &rsp, sizeof(rsp)) || rsp.magic != kHelloMagic ||
+      umq_bind(ch->umqh, rsp.blob, rsp.blob_len) != UMQ_SUCCESS) {
+    close(fd);
+    return URPC_FAIL;
+  }
+  ch->tcp = fd;
+  ch->lost = false;
+  ch->attached = true;
+  return URPC_SUCCESS;
+}
+
+int urpc_channel_server_detach(uint32_t chid) {
+  Channel* ch = get_channel(chid);
+  if (!ch || !ch->attached.load()) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(ch->mu);
+  ch->attached = false;
+  umq_unbind(ch->umqh);
+  if (ch->tcp >= 0) close(ch->tcp);
+  ch->tcp = -1;
+  for (auto& kv : ch->pending)
+    if (!kv.second.sync)
+      ch->ready.push_back(Ready{URPC_POLL_ERR, kv.second.func_id, kv.second.user_ctx, kv.first,
+                                URPC_ERR_SESSION_CLOSE, nullptr});
+  ch->pending.clear();
+  return URPC_SUCCESS;
+}
+
+int urpc_channel_destroy(uint32_t chid) {
+  Channel* ch;
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    auto it = g.channels.find(chid);
+    if (it == g.channels.end()) return URPC_ERR_EINVAL;
+    ch = it->second;
+    g.channels.erase(it);
+  }
+  if (ch->tcp >= 0) close(ch->tcp);
+  for (auto& r : ch->ready)
+    if (r.buf) umq_buf_free(r.buf);
+  umq_destroy(ch->umqh);
+  delete ch;
+  return URPC_SUCCESS;
+}
+
+int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_option_t* opt) {
+  Channel* ch = get_channel(chid);
+  if (!ch || !wr || wr->func_id >= URPC_FUNC_ID_KEEPALIVE) return URPC_ERR_EINVAL;
+  if (!ch->attached.load() || ch->lost.load()) return URPC_ERR_SESSION_CLOSE;
+  const uint32_t tmo = opt && opt->timeout_ms ? opt->timeout_ms : g.cfg.default_timeout_ms;
+  uint32_t req_id;
+  {
+    std::lock_guard<std::mutex> l(ch->mu);
+    req_id = ch->next_req++;
+    Pending p;
+    p.func_id = wr->func_id;
+    p.user_ctx = wr->user_ctx;
+    p.t0 = ub::now_ns();
+    p.deadline = p.t0 + uint64_t(tmo) * 1000000ull;
+    p.sync = opt && opt->sync;
+    ch->pending[req_id] = std::move(p);
+    Head h{urpc_proto::kVersion, URPC_MSG_REQ, 1, wr->func_id, req_id, chid, 0, 0};
+    const int rc = send_msg(ch->umqh, h, wr->args, wr->num_args, nullptr, 0);
+    if (rc != URPC_SUCCESS) {
+      ch->pending.erase(req_id);
+      std::lock_guard<std::mutex> l2(g.stat_mu);
+      ++g.stats.errors;
+      return rc;
+    }
+    std::lock_guard<std::mutex> l2(g.stat_mu);
+    ++g.stats.calls;
+  }
+  if (!(opt && opt->sync)) return static_cast<int>(req_id);
+  for (;;) {
+    {
+      std::lock_guard<std::mutex> l(ch->mu);
+      channel_progress(ch);
+      auto it = ch->pending.find(req_id);
+      if (it == ch->pending.end()) return URPC_FAIL;
+      if (it->second.done) {
+        const int st = it->second.status;
+        if (st == 0 && opt->rsp_buf) {
+          const uint32_t n = std::min<uint32_t>(opt->rsp_buf_len, it->second.rsp.size());
+          memcpy(opt->rsp_buf, it->second.rsp.data(), n);
+          if (opt->rsp_len) *opt->rsp_len = static_cast<uint32_t>(it->second.rsp.size());
+        }
+        ch->pending.erase(it);
+        return st;
+      }
+    }
+    if (ch->lost.load()) {
+      std::lock_guard<std::mutex> l(ch->mu);
+      ch->pending.erase(req_id);
+      return URPC_ERR_SESSION_CLOSE;
+    }
+    sched_yield();
+  }
+}
+
+int urpc_func_poll(uint32_t chid, urpc_poll_msg_t* msgs, int max) {
+  Channel* ch = get_channel(chid);
+  if (!ch || !msgs || max <= 0) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(ch->mu);
+  if (ch->attached.load()) channel_progress(ch);
+  int n = 0;
+  while (n < max && !ch->ready.empty()) {
+    Ready r = ch->ready.front();
+    ch->ready.pop_front();
+    msgs[n].event = r.ev;
+    msgs[n].func_id = r.func_id;
+    msgs[n].req_id = r.req_id;
+    msgs[n].user_ctx = r.user_ctx;
+    msgs[n].status = r.status;
+    msgs[n].priv = r.buf;
+    msgs[n].data = r.buf ? r.buf->buf_data + sizeof(urpc_req_head_t) : nullptr;
+    msgs[n].len = r.buf ? r.buf->data_size - sizeof(urpc_req_head_t) : 0;
+    ++n;
+  }
+  return n;
+}
+
+void urpc_msg_release(urpc_poll_msg_t* msg) {
+  if (msg && msg->priv) {
+    umq_buf_free(static_cast<umq_buf_t*>(msg->priv));
+    msg->priv = nullptr;
+    msg->data = nullptr;
+  }
+}
+
+int urpc_keepalive_callback_register(urpc_keepalive_cb_t cb, void* ctx) {
+  g.ka_cb = cb;
+  g.ka_ctx = ctx;
+  return URPC_SUCCESS;
+}
+
+int urpc_channel_task_cancel(uint32_t chid, uint32_t req_id) {
+  Channel* ch = get_channel(chid);
+  if (!ch) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(ch->mu);
+  return ch->pending.erase(req_id) ? URPC_SUCCESS : URPC_ERR_EINVAL;
+}
+
+int urpc_stats_get(urpc_stats_t* out) {
+  if (!out) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g.stat_mu);
+  *out = g.stats;
+  return URPC_SUCCESS;
+}
+int urpc_perf_get(uint64_t* count, uint64_t* avg_ns, uint64_t* p99_ns) {
+  std::lock_guard<std::mutex> l(g.stat_mu);
+  if (count) *count = g.lat.count();
+  if (avg_ns) *avg_ns = static_cast<uint64_t>(g.lat.mean());
+  if (p99_ns) *p99_ns = g.lat.quantile(0.99);
+  return URPC_SUCCESS;
+}
+
+}  // extern "C"
