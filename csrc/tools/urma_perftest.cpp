@@ -1,0 +1,219 @@
+// urma_perftest: latency and bandwidth of URMA verbs (write / read / send / atomic) between two endpoints.
+//   urma_perftest [--dev shm0|bond0] [--op write|read|send|faa|cas] [--size N] [--iters N] [--depth N]
+//   urma_perftest --server PORT         waits for one client, serves its one-sided and two-sided traffic
+//   urma_perftest --client HOST PORT    measures against a server in another process
+// Without --server/--client both endpoints live in this process. Option names follow the reference's tool
+// (src/urma/tools/urma_perftest, doc/en/urma/URMA User Guide.md:1690-1740: test type, message size, iterations,
+// queue depth, out-of-band TCP exchange of segment and jetty information).
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <sched.h>
+#include <stdio.h>
+#include <sys/select.h>
+#include <stdlib.h>
+#include <string.h>
+#include <unistd.h>
+
+#include <string>
+#include <vector>
+
+#include "ub_util.h"
+#include "urma_simple.h"
+
+struct Blob {
+  uint8_t ep[URMA_SIMPLE_JETTY_BLOB];
+  uint8_t seg[URMA_SIMPLE_SEG_BLOB];
+};
+static int fail(const char* w) {
+  fprintf(stderr, "urma_perftest: FAILED: %s\n", w);
+  return 1;
+}
+static bool xfer(int fd, void* b, size_t n, bool tx) {
+  char* p = (char*)b;
+  while (n) {
+    const ssize_t r = tx ? write(fd, p, n) : read(fd, p, n);
+    if (r <= 0) return false;
+    p += r;
+    n -= r;
+  }
+  return true;
+}
+static int wait_n(urma_simple_ep_t* ep, int want, int* bad) {
+  int st[64];
+  uint64_t uc[64];
+  uint32_t fl[64];
+  int got = 0;
+  const uint64_t deadline = ub::now_ns() + 10000000000ull;
+  while (got < want && ub::now_ns() < deadline) {
+    const int n = urma_simple_poll(ep, std::min(64, want - got), st, uc, nullptr, nullptr, fl);
+    for (int i = 0; i < n; ++i)
+      if (st[i] != 0) ++*bad;
+    if (n > 0) got += n;
+    else sched_yield();
+  }
+  return got;
+}
+
+int main(int argc, char** argv) {
+  std::string dev = "shm0", op = "write", host = "127.0.0.1";
+  uint32_t size = 4096, iters = 20000, depth = 64;
+  int server = -1, client = -1;
+  for (int i = 1; i < argc; ++i) {
+    if (!strcmp(argv[i], "--dev") && i + 1 < argc) dev = argv[++i];
+    else if (!strcmp(argv[i], "--op") && i + 1 < argc) op = argv[++i];
+    else if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--depth") && i + 1 < argc) depth = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--server") && i + 1 < argc) server = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--client") && i + 2 < argc) {
+      host = argv[++i];
+      client = atoi(argv[++i]);
+    }
+  }
+  urma_context_t* ctx = urma_simple_open(dev.c_str());
+  if (!ctx) return fail("open device");
+  const uint32_t seg_bytes = std::max<uint32_t>(size, 4096) * 2;
+  std::vector<uint8_t> mem_a(seg_bytes, 1), mem_b(seg_bytes, 2);
+  urma_simple_ep_t* ea = urma_simple_ep_create(ctx, depth * 2, 1, 0);
+  Blob mine{}, peer{};
+  urma_target_seg_t* seg_a = urma_simple_seg_register(ctx, mem_a.data(), seg_bytes, 14, 1, mine.seg);
+  if (!ea || !seg_a) return fail("endpoint / segment");
+  urma_simple_ep_blob(ea, mine.ep);
+  urma_simple_ep_t* eb = nullptr;
+  urma_context_t* ctx_b = nullptr;
+  int tcp = -1;
+  if (server >= 0 || client >= 0) {
+    if (server >= 0) {
+      const int ls = socket(AF_INET, SOCK_STREAM, 0);
+      int one = 1;
+      setsockopt(ls, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+      sockaddr_in a{};
+      a.sin_family = AF_INET;
+      a.sin_port = htons(server);
+      a.sin_addr.s_addr = htonl(INADDR_ANY);
+      if (bind(ls, (sockaddr*)&a, sizeof(a)) || listen(ls, 1)) return fail("listen");
+      printf("urma_perftest server ready on port %d\n", server);
+      fflush(stdout);
+      tcp = accept(ls, nullptr, nullptr);
+      close(ls);
+    } else {
+      tcp = socket(AF_INET, SOCK_STREAM, 0);
+      sockaddr_in a{};
+      a.sin_family = AF_INET;
+      a.sin_port = htons(client);
+      a.sin_addr.s_addr = inet_addr(host.c_str());
+      if (connect(tcp, (sockaddr*)&a, sizeof(a))) return fail("connect");
+    }
+    if (!xfer(tcp, &mine, sizeof(mine), true) || !xfer(tcp, &peer, sizeof(peer), false)) return fail("exchange");
+  } else {
+    ctx_b = urma_simple_open(dev.c_str());
+    eb = urma_simple_ep_create(ctx_b, depth * 2, 1, 0);
+    urma_target_seg_t* seg_b = urma_simple_seg_register(ctx_b, mem_b.data(), seg_bytes, 14, 1, peer.seg);
+    if (!eb || !seg_b) return fail("second endpoint");
+    urma_simple_ep_blob(eb, peer.ep);
+  }
+  urma_target_jetty_t* tj = urma_simple_ep_import(ctx, peer.ep, 1);
+  urma_target_seg_t* rseg = urma_simple_seg_import(ctx, peer.seg, 1);
+  if (!tj || !rseg) return fail("import");
+  const uint64_t rva = rseg->seg.ubva.va;
+  if (server >= 0) {  // passive side: keep receives posted until the client says goodbye
+    std::vector<std::vector<uint8_t>> rb(depth, std::vector<uint8_t>(size));
+    for (uint32_t i = 0; i < depth; ++i) urma_simple_post_recv(ea, rb[i].data(), size, i);
+    char bye;
+    for (;;) {
+      int st[32];
+      uint64_t uc[32];
+      uint32_t fl[32];
+      const int n = urma_simple_poll(ea, 32, st, uc, nullptr, nullptr, fl);
+      for (int i = 0; i < n; ++i)
+        if (fl[i] & URMA_CR_FLAG_RECV) urma_simple_post_recv(ea, rb[uc[i]].data(), size, uc[i]);
+      {
+        fd_set s;
+        FD_ZERO(&s);
+        FD_SET(tcp, &s);
+        timeval tv{0, n > 0 ? 0 : 200};
+        if (select(tcp + 1, &s, nullptr, nullptr, &tv) > 0 && read(tcp, &bye, 1) <= 1) break;
+      }
+    }
+    printf("urma_perftest server: done\n");
+    return 0;
+  }
+  int opc = URMA_OPC_WRITE;
+  bool atomic = false, two_sided = false;
+  if (op == "read") opc = URMA_OPC_READ;
+  else if (op == "send") {
+    opc = URMA_OPC_SEND;
+    two_sided = true;
+  } else if (op == "faa") {
+    opc = URMA_OPC_FADD;
+    atomic = true;
+    size = 8;
+  } else if (op == "cas") {
+    opc = URMA_OPC_CAS;
+    atomic = true;
+    size = 8;
+  }
+  std::vector<std::vector<uint8_t>> rb;
+  if (two_sided && eb) {
+    rb.assign(depth * 2, std::vector<uint8_t>(size));
+    for (uint32_t i = 0; i < depth * 2; ++i) urma_simple_post_recv(eb, rb[i].data(), size, i);
+  }
+  auto post = [&](uint64_t id) {
+    if (atomic) return urma_simple_atomic(ea, tj, opc, rseg, rva, 1, 0, nullptr, id);
+    return urma_simple_post(ea, tj, opc, two_sided ? nullptr : rseg, rva, nullptr, (uint64_t)mem_a.data(), size, 0, id, 1);
+  };
+  int bad = 0;
+  // latency: one operation at a time
+  const uint32_t lat_iters = std::min<uint32_t>(iters, 5000);
+  ub::PerfHist h;
+  for (uint32_t i = 0; i < lat_iters; ++i) {
+    const uint64_t t0 = ub::now_ns();
+    if (post(i) != 0) return fail("post");
+    if (wait_n(ea, 1, &bad) != 1) return fail("completion timeout");
+    h.add(ub::now_ns() - t0);
+    if (two_sided && eb) {
+      int st;
+      uint64_t uc;
+      uint32_t fl;
+      while (urma_simple_poll(eb, 1, &st, &uc, nullptr, nullptr, &fl) == 1)
+        if (fl & URMA_CR_FLAG_RECV) urma_simple_post_recv(eb, rb[uc].data(), size, uc);
+    }
+  }
+  // bandwidth / rate: keep `depth` operations in flight
+  uint32_t sent = 0, done = 0;
+  const uint64_t t0 = ub::now_ns();
+  while (done < iters) {
+    while (sent < iters && sent - done < depth) {
+      const int rc = post(sent);
+      if (rc == URMA_EAGAIN) break;
+      if (rc != 0) return fail("post (pipelined)");
+      ++sent;
+    }
+    const int n = wait_n(ea, 1, &bad);
+    if (n <= 0) return fail("completion timeout (pipelined)");
+    done += n;
+    if (two_sided && eb) {
+      int st[16];
+      uint64_t uc[16];
+      uint32_t fl[16];
+      const int m = urma_simple_poll(eb, 16, st, uc, nullptr, nullptr, fl);
+      for (int i = 0; i < m; ++i)
+        if (fl[i] & URMA_CR_FLAG_RECV) urma_simple_post_recv(eb, rb[uc[i]].data(), size, uc[i]);
+    }
+  }
+  const double sec = (ub::now_ns() - t0) * 1e-9;
+  printf("%s dev=%s size=%u depth=%u: latency avg %.2f us p99 %.2f us min %.2f us | %.0f ops/s, %.2f MB/s | errors %d\n",
+         op.c_str(), dev.c_str(), size, depth, h.mean() / 1e3, h.quantile(0.99) / 1e3, h.min() / 1e3, iters / sec,
+         iters * (double)size / sec / 1e6, bad);
+  if (tcp >= 0) {
+    char bye = 'q';
+    if (write(tcp, &bye, 1) < 0) {
+    }
+    close(tcp);
+  }
+  if (bad) return fail("completions with error status");
+  if (!two_sided && !atomic && opc == URMA_OPC_WRITE && eb && memcmp(mem_a.data(), mem_b.data(), size) != 0)
+    return fail("written data differs");
+  printf("urma_perftest: OK\n");
+  return 0;
+}

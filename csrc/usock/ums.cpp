@@ -1,0 +1,468 @@
+// UMS implementation (see ums.h).
+#include "ums.h"
+
+#include <arpa/inet.h>
+#include <dlfcn.h>
+#include <errno.h>
+#include <fcntl.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
+#include <poll.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+namespace {
+
+// The real libc entry points. When the preload shim is active, plain calls from this library would be interposed by
+// the shim and come straight back here, so the library always goes through RTLD_NEXT.
+struct Libc {
+  int (*socket)(int, int, int);
+  int (*listen)(int, int);
+  int (*accept)(int, struct sockaddr*, socklen_t*);
+  int (*connect)(int, const struct sockaddr*, socklen_t);
+  ssize_t (*send)(int, const void*, size_t, int);
+  ssize_t (*recv)(int, void*, size_t, int);
+  int (*shutdown)(int, int);
+  int (*close)(int);
+  Libc() {
+    // Resolve directly inside libc: this library may sit after libc in the lookup order (it is pulled in as a
+    // dependency of the preload shim), in which case RTLD_NEXT would find nothing.
+    void* h = dlopen("libc.so.6", RTLD_LAZY | RTLD_NOLOAD);
+    if (!h) h = dlopen("libc.so.6", RTLD_LAZY);
+    auto sym = [&](const char* n) {
+      void* p = h ? dlsym(h, n) : nullptr;
+      return p ? p : dlsym(RTLD_NEXT, n);
+    };
+    socket = reinterpret_cast<decltype(socket)>(sym("socket"));
+    listen = reinterpret_cast<decltype(listen)>(sym("listen"));
+    accept = reinterpret_cast<decltype(accept)>(sym("accept"));
+    connect = reinterpret_cast<decltype(connect)>(sym("connect"));
+    send = reinterpret_cast<decltype(send)>(sym("send"));
+    recv = reinterpret_cast<decltype(recv)>(sym("recv"));
+    shutdown = reinterpret_cast<decltype(shutdown)>(sym("shutdown"));
+    close = reinterpret_cast<decltype(close)>(sym("close"));
+  }
+};
+const Libc& libc() {
+  static const Libc l;
+  return l;
+}
+
+constexpr uint32_t kClcMagic = 0x554d5331;  // "UMS1"
+constexpr size_t kRingBytes = 1 << 20;      // per direction
+
+struct Ring {
+  std::atomic<uint64_t> prod;
+  char pad0[56];
+  std::atomic<uint64_t> cons;
+  char pad1[56];
+  std::atomic<uint32_t> closed;  // producer side shut down
+  std::atomic<uint32_t> waiter;  // the consumer is (about to be) asleep on its descriptor: ring the doorbell
+  char pad2[56];
+  char data[kRingBytes];
+};
+struct ConnShm {
+  Ring c2s;  // client -> server
+  Ring s2c;
+};
+struct Clc {
+  uint32_t magic;
+  uint32_t accept;  // reply: 1 = accelerated, 0 = declined
+  char shm_name[64];
+};
+
+struct Conn {
+  bool accelerated = false;
+  bool listener = false;
+  uint16_t port = 0;
+  ConnShm* shm = nullptr;
+  Ring* tx = nullptr;
+  Ring* rx = nullptr;
+  std::string shm_path;
+  bool owner = false;
+};
+// Heap-allocated on first use and never destroyed: the preload shim can call into this library before its static
+// constructors ran (during process start-up) and after its destructors ran (during exit).
+struct State {
+  std::mutex mu;
+  std::unordered_map<int, Conn> conns;
+  ums_stats_t stats{};
+};
+State& state() {
+  static State* s = new State();
+  return *s;
+}
+#define g_mu (state().mu)
+#define g_conns (state().conns)
+#define g_stats (state().stats)
+std::atomic<uint64_t> g_seq{1};
+
+std::string dir() {
+  const char* e = getenv("UMS_SHM_DIR");
+  std::string d = (e && *e) ? e : "/dev/shm/ums_" + std::to_string(getuid());
+  mkdir(d.c_str(), 0700);
+  return d;
+}
+std::string listen_marker(uint16_t port) { return dir() + "/listen_" + std::to_string(port); }
+
+bool rd_full(int fd, void* b, size_t n, int tmo_ms) {
+  char* p = static_cast<char*>(b);
+  while (n) {
+    pollfd pf{fd, POLLIN, 0};
+    if (poll(&pf, 1, tmo_ms) <= 0) return false;
+    const ssize_t r = libc().recv(fd, p, n, 0);
+    if (r <= 0) return false;
+    p += r;
+    n -= r;
+  }
+  return true;
+}
+bool wr_full(int fd, const void* b, size_t n) {
+  const char* p = static_cast<const char*>(b);
+  while (n) {
+    const ssize_t r = libc().send(fd, p, n, MSG_NOSIGNAL);
+    if (r <= 0) return false;
+    p += r;
+    n -= r;
+  }
+  return true;
+}
+
+Conn* find(int fd) {
+  auto it = g_conns.find(fd);
+  return it == g_conns.end() ? nullptr : &it->second;
+}
+
+size_t ring_write(Ring* r, const char* src, size_t n) {
+  const uint64_t prod = r->prod.load(std::memory_order_relaxed);
+  const uint64_t cons = r->cons.load(std::memory_order_acquire);
+  const size_t space = kRingBytes - static_cast<size_t>(prod - cons);
+  const size_t k = n < space ? n : space;
+  if (k == 0) return 0;
+  const size_t off = prod % kRingBytes;
+  const size_t first = k < kRingBytes - off ? k : kRingBytes - off;
+  memcpy(r->data + off, src, first);
+  memcpy(r->data, src + first, k - first);
+  r->prod.store(prod + k, std::memory_order_release);
+  return k;
+}
+size_t ring_read(Ring* r, char* dst, size_t n, bool peek) {
+  const uint64_t cons = r->cons.load(std::memory_order_relaxed);
+  const uint64_t prod = r->prod.load(std::memory_order_acquire);
+  const size_t avail = static_cast<size_t>(prod - cons);
+  const size_t k = n < avail ? n : avail;
+  if (k == 0) return 0;
+  const size_t off = cons % kRingBytes;
+  const size_t first = k < kRingBytes - off ? k : kRingBytes - off;
+  memcpy(dst, r->data + off, first);
+  memcpy(dst + first, r->data, k - first);
+  if (!peek) r->cons.store(cons + k, std::memory_order_release);
+  return k;
+}
+
+bool nonblocking(int fd) { return (fcntl(fd, F_GETFL) & O_NONBLOCK) != 0; }
+
+}  // namespace
+
+extern "C" {
+
+int ums_socket(int domain, int type, int protocol) {
+  const int fd = libc().socket(domain, type, protocol);
+  if (fd >= 0 && (domain == AF_INET || domain == AF_INET6) && (type & 0xf) == SOCK_STREAM) {
+    std::lock_guard<std::mutex> l(g_mu);
+    g_conns[fd] = Conn();
+  }
+  return fd;
+}
+int ums_bind(int fd, const struct sockaddr* addr, socklen_t len) { return ::bind(fd, addr, len); }
+
+int ums_adopt_listener(int fd) {
+  sockaddr_in a{};
+  socklen_t l = sizeof(a);
+  if (getsockname(fd, reinterpret_cast<sockaddr*>(&a), &l) != 0) return -1;
+  std::lock_guard<std::mutex> lk(g_mu);
+  Conn& c = g_conns[fd];
+  c.listener = true;
+  c.port = ntohs(a.sin_port);
+  const int m = ::open(listen_marker(c.port).c_str(), O_CREAT | O_WRONLY, 0600);  // "this port speaks UMS"
+  if (m >= 0) libc().close(m);
+  return 0;
+}
+int ums_listen(int fd, int backlog) {
+  const int rc = libc().listen(fd, backlog);
+  if (rc == 0) ums_adopt_listener(fd);
+  return rc;
+}
+
+int ums_adopt_accepted(int listen_fd, int fd) {
+  {
+    std::lock_guard<std::mutex> l(g_mu);
+    Conn* lc = find(listen_fd);
+    if (!lc || !lc->listener) return 0;
+  }
+  // server side of the handshake: the client speaks first
+  Clc in{};
+  Conn c;
+  if (rd_full(fd, &in, sizeof(in), 2000) && in.magic == kClcMagic) {
+    Clc out{kClcMagic, 0, {0}};
+    const std::string path = dir() + "/" + in.shm_name;
+    const int sfd = ::open(path.c_str(), O_RDWR);
+    void* p = MAP_FAILED;
+    if (sfd >= 0) {
+      p = mmap(nullptr, sizeof(ConnShm), PROT_READ | PROT_WRITE, MAP_SHARED, sfd, 0);
+      libc().close(sfd);
+    }
+    if (p != MAP_FAILED) {
+      out.accept = 1;
+      c.accelerated = true;
+      c.shm = static_cast<ConnShm*>(p);
+      c.tx = &c.shm->s2c;
+      c.rx = &c.shm->c2s;
+      c.shm_path = path;
+    }
+    wr_full(fd, &out, sizeof(out));
+  }
+  int one = 1;
+  setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+  std::lock_guard<std::mutex> l(g_mu);
+  if (c.accelerated) ++g_stats.conns_ums;
+  else ++g_stats.conns_fallback;
+  g_conns[fd] = c;
+  return c.accelerated ? 1 : 0;
+}
+int ums_accept(int fd, struct sockaddr* addr, socklen_t* len) {
+  const int nfd = libc().accept(fd, addr, len);
+  if (nfd >= 0) ums_adopt_accepted(fd, nfd);
+  return nfd;
+}
+
+int ums_adopt_connected(int fd, const struct sockaddr* peer) {
+  Conn c;
+  const sockaddr_in* a = reinterpret_cast<const sockaddr_in*>(peer);
+  bool try_ums = false;
+  if (peer->sa_family == AF_INET && ntohl(a->sin_addr.s_addr) >> 24 == 127) {
+    // same host: accelerate only if the listener announced itself, otherwise stay on plain TCP without touching
+    // the byte stream (the peer may be an ordinary TCP server)
+    try_ums = access(listen_marker(ntohs(a->sin_port)).c_str(), F_OK) == 0;
+  }
+  if (try_ums) {
+    Clc out{kClcMagic, 0, {0}};
+    snprintf(out.shm_name, sizeof(out.shm_name), "conn_%d_%llu", getpid(), (unsigned long long)g_seq.fetch_add(1));
+    const std::string path = dir() + "/" + out.shm_name;
+    const int sfd = ::open(path.c_str(), O_CREAT | O_RDWR | O_TRUNC, 0600);
+    void* p = MAP_FAILED;
+    if (sfd >= 0 && ftruncate(sfd, sizeof(ConnShm)) == 0)
+      p = mmap(nullptr, sizeof(ConnShm), PROT_READ | PROT_WRITE, MAP_SHARED, sfd, 0);
+    if (sfd >= 0) libc().close(sfd);
+    const bool was_nb = nonblocking(fd);
+    if (was_nb) fcntl(fd, F_SETFL, fcntl(fd, F_GETFL) & ~O_NONBLOCK);
+    Clc in{};
+    if (p != MAP_FAILED && wr_full(fd, &out, sizeof(out)) && rd_full(fd, &in, sizeof(in), 2000) &&
+        in.magic == kClcMagic && in.accept) {
+      c.accelerated = true;
+      c.shm = static_cast<ConnShm*>(p);
+      c.tx = &c.shm->c2s;
+      c.rx = &c.shm->s2c;
+      c.shm_path = path;
+      c.owner = true;
+    } else if (p != MAP_FAILED) {
+      munmap(p, sizeof(ConnShm));
+      unlink(path.c_str());
+    }
+    if (was_nb) fcntl(fd, F_SETFL, fcntl(fd, F_GETFL) | O_NONBLOCK);
+    int one = 1;
+    setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+  }
+  std::lock_guard<std::mutex> l(g_mu);
+  if (c.accelerated) ++g_stats.conns_ums;
+  else ++g_stats.conns_fallback;
+  g_conns[fd] = c;
+  return c.accelerated ? 1 : 0;
+}
+int ums_connect(int fd, const struct sockaddr* addr, socklen_t len) {
+  const int rc = libc().connect(fd, addr, len);
+  if (rc == 0) ums_adopt_connected(fd, addr);
+  return rc;
+}
+
+ssize_t ums_send(int fd, const void* buf, size_t n, int flags) {
+  Conn c;
+  {
+    std::lock_guard<std::mutex> l(g_mu);
+    Conn* p = find(fd);
+    if (!p || !p->accelerated) {
+      if (p) g_stats.bytes_tx_tcp += n;
+      c.accelerated = false;
+    } else {
+      c = *p;
+    }
+  }
+  if (!c.accelerated) return libc().send(fd, buf, n, flags);
+  if (c.tx->closed.load()) {
+    errno = EPIPE;
+    return -1;
+  }
+  const char* p = static_cast<const char*>(buf);
+  size_t sent = 0;
+  const bool nb = nonblocking(fd) || (flags & MSG_DONTWAIT);
+  uint32_t spins = 0;
+  while (sent < n) {
+    const uint64_t before = c.tx->prod.load(std::memory_order_relaxed);
+    const size_t k = ring_write(c.tx, p + sent, n - sent);
+    if (k) {
+      sent += k;
+      // The reader may have gone to sleep on the TCP descriptor if it had consumed everything that was published
+      // before this write. Checking AFTER publishing closes the lost-wakeup window.
+      std::atomic_thread_fence(std::memory_order_seq_cst);
+      (void)before;
+      if (c.tx->waiter.load(std::memory_order_relaxed)) {  // one byte makes the peer's descriptor readable
+        const char bell = 1;
+        if (libc().send(fd, &bell, 1, MSG_NOSIGNAL | MSG_DONTWAIT) < 0 && errno != EAGAIN && errno != EWOULDBLOCK) {
+          if (sent) break;
+          return -1;
+        }
+        std::lock_guard<std::mutex> l(g_mu);
+        ++g_stats.doorbells;
+      }
+      spins = 0;
+      continue;
+    }
+    if (nb) {
+      if (sent) break;
+      errno = EAGAIN;
+      return -1;
+    }
+    // ring full: wait for the reader; give up if the peer closed its TCP side
+    if (++spins > 2000) {
+      pollfd pf{fd, 0, 0};
+      poll(&pf, 1, 1);
+      if (pf.revents & (POLLHUP | POLLERR)) {
+        errno = EPIPE;
+        return sent ? (ssize_t)sent : -1;
+      }
+      std::lock_guard<std::mutex> l(g_mu);
+      ++g_stats.tx_waits;
+    } else {
+      sched_yield();
+    }
+  }
+  std::lock_guard<std::mutex> l(g_mu);
+  g_stats.bytes_tx_ring += sent;
+  return static_cast<ssize_t>(sent);
+}
+
+ssize_t ums_recv(int fd, void* buf, size_t n, int flags) {
+  Conn c;
+  {
+    std::lock_guard<std::mutex> l(g_mu);
+    Conn* p = find(fd);
+    if (!p || !p->accelerated) c.accelerated = false;
+    else c = *p;
+  }
+  if (!c.accelerated) {
+    const ssize_t r = libc().recv(fd, buf, n, flags);
+    if (r > 0) {
+      std::lock_guard<std::mutex> l(g_mu);
+      g_stats.bytes_rx_tcp += r;
+    }
+    return r;
+  }
+  const bool nb = nonblocking(fd) || (flags & MSG_DONTWAIT);
+  for (;;) {
+    size_t k = ring_read(c.rx, static_cast<char*>(buf), n, flags & MSG_PEEK);
+    if (!k && !nb) {
+      // short busy-poll before sleeping: a request/response partner usually answers within microseconds, and the
+      // answer is then picked up without a system call on either side
+      for (int spin = 0; spin < 4000 && !k; ++spin) {
+#if defined(__x86_64__)
+        __builtin_ia32_pause();
+#else
+        __asm__ __volatile__("" ::: "memory");
+#endif
+        k = ring_read(c.rx, static_cast<char*>(buf), n, flags & MSG_PEEK);
+      }
+    }
+    if (!k) {
+      // announce that we are going to wait on the descriptor, then look once more (no lost wake-up)
+      c.rx->waiter.store(1, std::memory_order_relaxed);
+      std::atomic_thread_fence(std::memory_order_seq_cst);
+      k = ring_read(c.rx, static_cast<char*>(buf), n, flags & MSG_PEEK);
+    }
+    if (k) {
+      if (c.rx->waiter.load(std::memory_order_relaxed)) c.rx->waiter.store(0, std::memory_order_relaxed);
+      std::lock_guard<std::mutex> l(g_mu);
+      g_stats.bytes_rx_ring += k;
+      return static_cast<ssize_t>(k);
+    }
+    // nothing in the ring: consume doorbells (or learn that the peer closed)
+    char bells[64];
+    const ssize_t r = libc().recv(fd, bells, sizeof(bells), nb ? MSG_DONTWAIT : 0);
+    if (r == 0) {
+      // orderly shutdown of the peer: deliver what is still in the ring, then end of stream
+      const size_t k2 = ring_read(c.rx, static_cast<char*>(buf), n, flags & MSG_PEEK);
+      return static_cast<ssize_t>(k2);
+    }
+    if (r < 0) {
+      if (errno == EINTR) continue;
+      if ((errno == EAGAIN || errno == EWOULDBLOCK) && c.rx->prod.load() != c.rx->cons.load()) continue;
+      return -1;
+    }
+  }
+}
+
+int ums_shutdown(int fd, int how) {
+  {
+    std::lock_guard<std::mutex> l(g_mu);
+    Conn* p = find(fd);
+    if (p && p->accelerated && (how == SHUT_WR || how == SHUT_RDWR)) p->tx->closed = 1;
+  }
+  return libc().shutdown(fd, how);
+}
+
+int ums_close(int fd) {
+  Conn c;
+  bool known = false;
+  {
+    std::lock_guard<std::mutex> l(g_mu);
+    auto it = g_conns.find(fd);
+    if (it != g_conns.end()) {
+      c = it->second;
+      known = true;
+      g_conns.erase(it);
+    }
+  }
+  if (known) {
+    if (c.listener) unlink(listen_marker(c.port).c_str());
+    if (c.accelerated) {
+      c.tx->closed = 1;
+      munmap(c.shm, sizeof(ConnShm));
+      if (c.owner) unlink(c.shm_path.c_str());
+    }
+  }
+  return libc().close(fd);
+}
+
+int ums_is_accelerated(int fd) {
+  std::lock_guard<std::mutex> l(g_mu);
+  Conn* p = find(fd);
+  return p ? (p->accelerated ? 1 : 0) : -1;
+}
+int ums_owns(int fd) {
+  std::lock_guard<std::mutex> l(g_mu);
+  return find(fd) != nullptr;
+}
+void ums_get_stats(ums_stats_t* out) {
+  std::lock_guard<std::mutex> l(g_mu);
+  *out = g_stats;
+}
+
+}  // extern "C"

