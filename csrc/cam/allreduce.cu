@@ -1,0 +1,191 @@
+// All-reduce over NVLink peer memory: one-shot (every rank reads all peers and reduces; latency-optimal for small
+// messages) and two-shot (reduce-scatter then all-gather through peer loads; bandwidth-optimal for large ones).
+// Data lives in a double-buffered region of the symmetric heap; barriers are epoch-tagged flags with bounded waits.
+// There is no all-reduce in the reference (its operators only use point-to-point window traffic); this implements
+// the all-reduce part of the tensor-parallel configuration.
+#include "common.h"
+#include "ep_common.cuh"
+#include "ptx.cuh"
+#include "sync.cuh"
+
+namespace umdk {
+namespace {
+
+constexpr int kArThreads = 512;
+
+struct ArArgs {
+  int R, rank, algo;       // algo 0 = one-shot, 1 = two-shot
+  PeerTable peers;
+  uint64_t buf_off[2];     // [max_bytes] per epoch parity
+  uint64_t flag_off;       // [3][R] uint64: start / middle / end barriers
+  const __nv_bfloat16* in; // local input (copied into the heap buffer by the kernel)
+  __nv_bfloat16* out;
+  size_t n;                // elements, multiple of 8 * R
+  uint32_t* ctrl;          // [0] epoch, [1] done counter, [2..3] grid barrier
+  int* status;
+  int phase_mask;          // 1 = copy-in + publish, 2 = reduce (+ gather) ; 3 = both
+};
+
+__device__ __forceinline__ void acc8(float* acc, const int4& v) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(p[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+__device__ __forceinline__ int4 pack8(const float* acc) {
+  int4 o;
+  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  return o;
+}
+
+// Barrier across ranks: the last CTA of this grid to arrive publishes `tag` to every peer; everyone then waits for
+// all peers' flags. `which` selects one of the three flag rows.
+__device__ bool rank_barrier(const ArArgs& a, int which, uint64_t tag, uint32_t* grid_cnt, bool publish, bool wait) {
+  __shared__ int s_ok_b;
+  if (threadIdx.x == 0) s_ok_b = 1;
+  if (publish) {
+    if (cta_done_is_last(grid_cnt, gridDim.x)) {
+      if (threadIdx.x < a.R) {
+        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.flag_off) + which * a.R + a.rank, tag);
+      }
+    }
+  }
+  __syncthreads();
+  if (wait) {
+    if (threadIdx.x < a.R) {
+      const uint64_t* f = reinterpret_cast<const uint64_t*>(a.peers.base[a.rank] + a.flag_off) + which * a.R + threadIdx.x;
+      if (!wait_flag_ge_sys(f, tag)) {
+        umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_ALLREDUCE, which, threadIdx.x);
+        s_ok_b = 0;
+      }
+    }
+    __syncthreads();
+  }
+  return s_ok_b != 0;
+}
+
+__global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a) {
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) s_epoch = a.ctrl[0];
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int slot = epoch & 1;
+  const uint64_t tag = (uint64_t)epoch + 1;
+  const size_t nvec = a.n / 8;
+  const size_t tid = (size_t)blockIdx.x * kArThreads + threadIdx.x;
+  const size_t nthreads = (size_t)gridDim.x * kArThreads;
+  int4* mine = reinterpret_cast<int4*>(a.peers.base[a.rank] + a.buf_off[slot]);
+
+  if (a.phase_mask & 1) {
+    // this buffer parity was last used two calls ago: every peer must have finished reading it
+    if (epoch >= 2) {
+      __shared__ int s_ok0;
+      if (threadIdx.x == 0) s_ok0 = 1;
+      __syncthreads();
+      if (threadIdx.x < a.R) {
+        const uint64_t* f = reinterpret_cast<const uint64_t*>(a.peers.base[a.rank] + a.flag_off) + 2 * a.R + threadIdx.x;
+        if (!wait_flag_ge_sys(f, (uint64_t)epoch - 1)) {
+          umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_ALLREDUCE, 3, threadIdx.x);
+          s_ok0 = 0;
+        }
+      }
+      __syncthreads();
+      if (!s_ok0) return;
+    }
+    const int4* src = reinterpret_cast<const int4*>(a.in);
+    for (size_t v = tid; v < nvec; v += nthreads) mine[v] = src[v];
+  }
+  if (!rank_barrier(a, 0, tag, &a.ctrl[1], a.phase_mask & 1, a.phase_mask & 2)) return;
+  if (!(a.phase_mask & 2)) return;
+
+  if (a.algo == 0) {
+    int4* dst = reinterpret_cast<int4*>(a.out);
+    for (size_t v = tid; v < nvec; v += nthreads) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int i = 0; i < a.R; ++i) {
+        const int p = (a.rank + i) % a.R;
+        acc8(acc, ld_relaxed_sys_v4(reinterpret_cast<const int4*>(a.peers.base[p] + a.buf_off[slot]) + v));
+      }
+      dst[v] = pack8(acc);
+    }
+  } else {
+    // stage 1: reduce my 1/R slice from all peers into my own buffer (in place: only I write my slice)
+    const size_t per = nvec / a.R;
+    const size_t lo = per * a.rank;
+    for (size_t v = tid; v < per; v += nthreads) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int i = 0; i < a.R; ++i) {
+        const int p = (a.rank + i) % a.R;
+        acc8(acc, ld_relaxed_sys_v4(reinterpret_cast<const int4*>(a.peers.base[p] + a.buf_off[slot]) + lo + v));
+      }
+      mine[lo + v] = pack8(acc);
+    }
+    if (!rank_barrier(a, 1, tag, &a.ctrl[1], true, true)) return;
+    // stage 2: gather every rank's reduced slice
+    int4* dst = reinterpret_cast<int4*>(a.out);
+    for (int i = 0; i < a.R; ++i) {
+      const int p = (a.rank + i) % a.R;
+      const int4* from = reinterpret_cast<const int4*>(a.peers.base[p] + a.buf_off[slot]) + per * p;
+      for (size_t v = tid; v < per; v += nthreads) dst[per * p + v] = ld_relaxed_sys_v4(from + v);
+    }
+  }
+  // the buffer of this parity is reused two calls later; peers must have finished reading it by then
+  rank_barrier(a, 2, tag, &a.ctrl[1], true, false);
+  if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
+    if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+  }
+}
+
+}  // namespace
+}  // namespace umdk
+
+using namespace umdk;
+
+struct UmdkAllreduceParams {
+  int R, rank, algo, num_ctas, phase_mask;
+  void* peers[kMaxRanks];
+  uint64_t buf_off[2];
+  uint64_t flag_off;
+  const void* in;
+  void* out;
+  unsigned long long n;
+  uint32_t* ctrl;
+  int* status;
+};
+
+UMDK_API long long umdk_allreduce_heap_bytes(unsigned long long max_bytes, int R) {
+  return (long long)(2 * align_up_u64(max_bytes, 1024) + align_up_u64(3ull * R * 8, 256));
+}
+
+UMDK_API int umdk_allreduce(const UmdkAllreduceParams* p, void* stream) {
+  if (p->R < 1 || p->R > kMaxRanks || p->n == 0 || (p->n % (8ull * p->R))) return -UMDK_ERR_BAD_ARG;
+  ArArgs a;
+  a.R = p->R;
+  a.rank = p->rank;
+  a.algo = p->algo;
+  for (int i = 0; i < kMaxRanks; ++i) a.peers.base[i] = i < p->R ? static_cast<uint8_t*>(p->peers[i]) : nullptr;
+  a.buf_off[0] = p->buf_off[0];
+  a.buf_off[1] = p->buf_off[1];
+  a.flag_off = p->flag_off;
+  a.in = static_cast<const __nv_bfloat16*>(p->in);
+  a.out = static_cast<__nv_bfloat16*>(p->out);
+  a.n = p->n;
+  a.ctrl = p->ctrl;
+  a.status = p->status;
+  a.phase_mask = p->phase_mask ? p->phase_mask : 3;
+  int grid = p->num_ctas;
+  if (grid <= 0) {
+    const size_t nvec = p->n / 8;
+    grid = (int)((nvec + kArThreads * 4 - 1) / (kArThreads * 4));
+    if (grid < 1) grid = 1;
+  }
+  if (grid > sm_count()) grid = sm_count();
+  allreduce_kernel<<<grid, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  UMDK_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}

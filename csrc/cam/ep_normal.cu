@@ -75,16 +75,25 @@ ep_layout_kernel(const int64_t* __restrict__ topk_idx, int T, int K, int E, int 
     umdk_set_status(status, UMDK_ERR_TIMEOUT, UMDK_PH_BARRIER, 0, 0);
     return;
   }
-  // Phase B: exclusive scan over chunks, one thread per column.
-  for (int col = blockIdx.x * blockDim.x + threadIdx.x; col < cols; col += gridDim.x * blockDim.x) {
-    int base = 0;
-    for (int c = 0; c < num_chunks; ++c) {
-      const int v = scratch[(size_t)c * cols + col];
-      scratch[(size_t)c * cols + col] = base;
-      base += v;
+  // Phase B: exclusive scan over chunks, one warp per column (32 chunk values per step, warp-level scan).
+  for (int col = gwarp; col < cols; col += total_warps) {
+    int carry = 0;
+    for (int c0 = 0; c0 < num_chunks; c0 += 32) {
+      const int c = c0 + lane;
+      const int v = c < num_chunks ? scratch[(size_t)c * cols + col] : 0;
+      int x = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, d);
+        if (lane >= d) x += y;
+      }
+      if (c < num_chunks) scratch[(size_t)c * cols + col] = x - v + carry;
+      carry += __shfl_sync(0xffffffffu, x, 31);
     }
-    if (col < E) num_per_expert[col] = base;
-    else num_per_rank[col - E] = base;
+    if (lane == 0) {
+      if (col < E) num_per_expert[col] = carry;
+      else num_per_rank[col - E] = carry;
+    }
   }
   if (!grid_barrier(bar, gridDim.x)) {
     umdk_set_status(status, UMDK_ERR_TIMEOUT, UMDK_PH_BARRIER, 1, 0);

@@ -80,9 +80,11 @@ __device__ __forceinline__ bool grid_barrier(uint32_t* bar, uint32_t num_ctas) {
 // stores). Returns true in exactly one CTA - the last to arrive - and resets the counter for the next launch.
 __device__ __forceinline__ bool cta_done_is_last(uint32_t* counter, uint32_t num_ctas) {
   __shared__ int s_last;
-  __threadfence_system();
+  // All threads' stores are ordered before the barrier; one system-scope fence by the thread that signals then
+  // orders them (cumulatively) before the counter update, the same shape as a cooperative grid barrier.
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const uint32_t old = atomicAdd(counter, 1u);
     s_last = (old == num_ctas - 1) ? 1 : 0;
     if (s_last) {
