@@ -49,10 +49,16 @@ __device__ bool rank_barrier(const ArArgs& a, int which, uint64_t tag, uint32_t*
   __shared__ int s_ok_b;
   if (threadIdx.x == 0) s_ok_b = 1;
   if (publish) {
-    if (cta_done_is_last(grid_cnt, gridDim.x)) {
-      if (threadIdx.x < a.R) {
-        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.flag_off) + which * a.R + a.rank, tag);
-      }
+    bool last;
+    if (gridDim.x == 1) {  // latency path for small messages: no inter-CTA counting needed
+      __syncthreads();
+      if (threadIdx.x < a.R) __threadfence_system();
+      last = true;
+    } else {
+      last = cta_done_is_last(grid_cnt, gridDim.x);
+    }
+    if (last && threadIdx.x < a.R) {
+      st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.flag_off) + which * a.R + a.rank, tag);
     }
   }
   __syncthreads();
@@ -136,7 +142,9 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
   }
   // the buffer of this parity is reused two calls later; peers must have finished reading it by then
   rank_barrier(a, 2, tag, &a.ctrl[1], true, false);
-  if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
+  if (gridDim.x == 1) {
+    if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+  } else if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
     if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
   }
 }
@@ -181,7 +189,7 @@ UMDK_API int umdk_allreduce(const UmdkAllreduceParams* p, void* stream) {
   int grid = p->num_ctas;
   if (grid <= 0) {
     const size_t nvec = p->n / 8;
-    grid = (int)((nvec + kArThreads * 4 - 1) / (kArThreads * 4));
+    grid = nvec <= 2048 ? 1 : (int)((nvec + kArThreads * 2 - 1) / (kArThreads * 2));
     if (grid < 1) grid = 1;
   }
   if (grid > sm_count()) grid = sm_count();

@@ -1,0 +1,43 @@
+"""URMA over GPU memory (cuda_ipc provider): one-sided write / read between device segments and system-scope
+atomics, within one process on one GPU. The cross-process path (CUDA IPC handles) is covered by the multi-GPU test."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_cuda_ipc_write_read_atomics():
+    from umdk_b200 import urma
+    a, b = urma.Context("cuda0"), urma.Context("cuda0")
+    try:
+        ea, eb = a.endpoint(depth=64), b.endpoint(depth=64)
+        mem_b = torch.zeros(1 << 18, dtype=torch.float32, device="cuda")
+        cnt_b = torch.zeros(16, dtype=torch.int64, device="cuda")
+        seg_b = b.register(mem_b, token=21)
+        cseg_b = b.register(cnt_b, token=22)
+        peer_b = a.import_endpoint(eb.blob)
+        rseg, rcnt = a.import_segment(seg_b.blob, token=21), a.import_segment(cseg_b.blob, token=22)
+        src = torch.randn(4096, device="cuda")
+        ea.write(peer_b, rseg, rseg.va + 4096 * 4, src.data_ptr(), src.numel() * 4)
+        ea.wait(1)
+        assert torch.equal(mem_b[4096:8192], src)
+        back = torch.zeros(4096, device="cuda")
+        ea.read(peer_b, rseg, rseg.va + 4096 * 4, back.data_ptr(), back.numel() * 4)
+        ea.wait(1)
+        assert torch.equal(back, src)
+        res = ctypes.c_uint64(0)
+        for i in range(100):
+            ea.atomic(peer_b, urma.OPC_FADD, rcnt, rcnt.va, 3, 0, ctypes.addressof(res))
+        got = ea.wait(100, timeout_ms=10000)
+        assert len(got) == 100 and int(cnt_b[0]) == 300 and res.value == 297
+        assert ea.compare_swap(peer_b, rcnt, rcnt.va + 8, 0, 77) == 0 and int(cnt_b[1]) == 77
+        # wrong token: refused with an error completion, memory untouched
+        bad = a.import_segment(seg_b.blob, token=999)
+        ea.write(peer_b, bad, bad.va, src.data_ptr(), 16)
+        c = ea.wait(1, check=False)
+        assert c[0].status == urma.CR_REM_ACCESS_ABORT
+    finally:
+        a.close()
+        b.close()

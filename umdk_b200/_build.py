@@ -56,6 +56,12 @@ def _targets():
                        libs=["-L" + str(LIB), "-Wl,-rpath,$ORIGIN"] + ["-l" + d for d in deps] +
                             ["-lpthread", "-ldl", "-lrt"],
                        deps=deps, out=LIB / f"lib{name}.so")
+    cu_prov = sorted((CSRC / "urma_cuda").glob("*.cu"))
+    if cu_prov and "umdk_urma" in t:
+        # URMA provider plug-in for GPU memory: found by urma_init in <lib dir>/urma/liburma-*.so
+        t["urma_cuda_ipc"] = dict(kind="cuda_shared", sources=cu_prov, includes=[CSRC / "urma", CSRC / "common"],
+                                  libs=["-lcudart", "-L" + str(LIB), "-Xlinker", "-rpath=$ORIGIN/..", "-lumdk_urma",
+                                        "-lpthread"], deps=["umdk_urma"], out=LIB / "urma" / "liburma-cuda-ipc.so")
     pre = CSRC / "usock" / "ums_preload.cpp"
     if pre.exists():
         t["ums_preload"] = dict(kind="cxx_shared", sources=[pre], includes=[CSRC / "usock", CSRC / "common"],
@@ -116,9 +122,11 @@ def build_all(force: bool = False, verbose: bool = False, only=None) -> dict:
     """Builds all targets (or those whose names are in ``only``); returns name -> output path."""
     LIB.mkdir(parents=True, exist_ok=True)
     (LIB / "bin").mkdir(parents=True, exist_ok=True)
+    (LIB / "urma").mkdir(parents=True, exist_ok=True)
     OBJ.mkdir(parents=True, exist_ok=True)
     targets = _targets()
-    order = ["umdk_cam", "umdk_urma", "umdk_umq", "umdk_usock", "umdk_dlock", "umdk_urpc", "ums_preload"]
+    order = ["umdk_cam", "umdk_urma", "urma_cuda_ipc", "umdk_umq", "umdk_usock", "umdk_dlock", "umdk_urpc",
+             "ums_preload"]
     order += [n for n in targets if n.startswith("tool_")]
     outs = {}
     # compile all objects of all targets in parallel first
