@@ -81,7 +81,16 @@ def bench_allreduce(rank, world, a):
     from umdk_b200.parallel.symm import SymmetricHeap
     max_bytes = a.max_bytes
     nbytes = AllReduce.heap_bytes(max_bytes, world)
-    heap = SymmetricHeap(nbytes, None) if world > 1 else SymmetricHeap(nbytes)
+    heap, nvls = None, False
+    if world > 1 and not a.no_nvls:
+        try:
+            heap = SymmetricHeap.multicast(nbytes, None)
+            nvls = True
+        except Exception as e:  # no multicast support: peer pointers only
+            if rank == 0:
+                print(f"# NVLS heap unavailable ({e}); using CUDA IPC heap", flush=True)
+    if heap is None:
+        heap = SymmetricHeap(nbytes, None) if world > 1 else SymmetricHeap(nbytes)
     ar = AllReduce(heap, max_bytes)
     size = 1024
     while size <= max_bytes:
@@ -95,13 +104,18 @@ def bench_allreduce(rank, world, a):
             if algo == "one_shot" and size > (8 << 20):
                 continue
             res[algo] = timed(lambda: ar(x, out=out, algo=algo), iters, a.warmup, world)
+        if nvls:
+            res["nvls"] = timed(lambda: ar(x, out=out, algo="nvls"), iters, a.warmup, world)
+            # caller keeps its tensor in the symmetric heap: no copy in, no copy out
+            res["nvls_in_place"] = timed(lambda: ar(None, algo="nvls", in_place=True, n=n), iters, a.warmup, world)
         ar.check()
         tb = timed(lambda: dist.all_reduce(out) if world > 1 else out.copy_(x), iters, a.warmup, world)
         best = min(res, key=res.get)
         bus = lambda t: 2.0 * (world - 1) / world * n * 2 / t / 1e9
         emit(rank, {"config": "allreduce", "n_gpus": world, "bytes": n * 2, "impl": "umdk_b200", "best_algo": best,
                     "us": res[best] * 1e6, "us_one_shot": res.get("one_shot", 0) * 1e6 or None,
-                    "us_two_shot": res["two_shot"] * 1e6, "bus_GBps": bus(res[best]),
+                    "us_two_shot": res["two_shot"] * 1e6, "us_nvls": res.get("nvls", 0) * 1e6 or None,
+                    "us_nvls_in_place": res.get("nvls_in_place", 0) * 1e6 or None, "bus_GBps": bus(res[best]),
                     "nccl_us": tb * 1e6, "nccl_bus_GBps": bus(tb), "speedup_vs_nccl": tb / res[best]})
         size *= 4
     heap.close()
@@ -115,6 +129,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--n-copy", type=int, default=16)
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--no-nvls", action="store_true")
     a = ap.parse_args()
     rank, world = setup()
     if a.what in ("mlp", "all"):

@@ -14,7 +14,9 @@ namespace {
 constexpr int kArThreads = 512;
 
 struct ArArgs {
-  int R, rank, algo;       // algo 0 = one-shot, 1 = two-shot
+  int R, rank, algo;       // algo 0 = one-shot, 1 = two-shot, 2 = NVLS (multimem reduce + broadcast in NVSwitch)
+  uint8_t* mc_base;        // multicast alias of the heap (algo 2)
+  int in_place;            // input already sits in the heap buffer and the result stays there (no copies)
   PeerTable peers;
   uint64_t buf_off[2];     // [max_bytes] per epoch parity
   uint64_t flag_off;       // [3][R] uint64: start / middle / end barriers
@@ -87,7 +89,7 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
   const size_t nthreads = (size_t)gridDim.x * kArThreads;
   int4* mine = reinterpret_cast<int4*>(a.peers.base[a.rank] + a.buf_off[slot]);
 
-  if (a.phase_mask & 1) {
+  if ((a.phase_mask & 1) && !a.in_place) {
     // this buffer parity was last used two calls ago: every peer must have finished reading it
     if (epoch >= 2) {
       __shared__ int s_ok0;
@@ -118,6 +120,21 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
         acc8(acc, ld_relaxed_sys_v4(reinterpret_cast<const int4*>(a.peers.base[p] + a.buf_off[slot]) + v));
       }
       dst[v] = pack8(acc);
+    }
+  } else if (a.algo == 2) {
+    // NVLS: this rank owns slice `rank`; one multimem load reduces the slice over all ranks inside the switch and one
+    // multimem store broadcasts the result into every rank's buffer (in place, nobody else touches this slice)
+    const size_t per = nvec / a.R;
+    const size_t lo = per * a.rank;
+    uint8_t* mc = a.mc_base + a.buf_off[slot];
+    for (size_t v = tid; v < per; v += nthreads) {
+      const int4 r = multimem_ld_reduce_bf16x8(mc + (lo + v) * 16);
+      multimem_st_v4(mc + (lo + v) * 16, r);
+    }
+    if (!rank_barrier(a, 1, tag, &a.ctrl[1], true, true)) return;
+    if (!a.in_place) {
+      int4* dst = reinterpret_cast<int4*>(a.out);
+      for (size_t v = tid; v < nvec; v += nthreads) dst[v] = mine[v];
     }
   } else {
     // stage 1: reduce my 1/R slice from all peers into my own buffer (in place: only I write my slice)
@@ -164,6 +181,8 @@ struct UmdkAllreduceParams {
   unsigned long long n;
   uint32_t* ctrl;
   int* status;
+  void* mc_base;
+  int in_place;
 };
 
 UMDK_API long long umdk_allreduce_heap_bytes(unsigned long long max_bytes, int R) {
@@ -186,6 +205,9 @@ UMDK_API int umdk_allreduce(const UmdkAllreduceParams* p, void* stream) {
   a.ctrl = p->ctrl;
   a.status = p->status;
   a.phase_mask = p->phase_mask ? p->phase_mask : 3;
+  a.mc_base = static_cast<uint8_t*>(p->mc_base);
+  a.in_place = p->in_place;
+  if (a.algo == 2 && a.mc_base == nullptr) return -UMDK_ERR_BAD_ARG;
   int grid = p->num_ctas;
   if (grid <= 0) {
     const size_t nvec = p->n / 8;

@@ -35,6 +35,19 @@ struct Cfg {
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two: 256 or 512)
 };
 
+// Tile order: super-rows of kGroupM m-tiles are swept column by column, so that the ~148 tiles in flight at any time
+// touch about 16 A panels and 9 B panels (tens of MB, L2-resident) instead of every A panel of the matrix.
+constexpr int kGroupM = 16;
+__device__ __forceinline__ void tile_to_mn(int t, int mb, int nb, int* m_blk, int* n_blk) {
+  const int per_group = kGroupM * nb;
+  const int g = t / per_group;
+  const int first_m = g * kGroupM;
+  const int gm = min(kGroupM, mb - first_m);
+  const int r = t - g * per_group;
+  *m_blk = first_m + r % gm;
+  *n_blk = r / gm;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -86,8 +99,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m0 = (t % mb) * BM;
-        const int n0 = (t / mb) * BN;
+        int m_blk, n_blk;
+        tile_to_mn(t, mb, nb, &m_blk, &n_blk);
+        const int m0 = m_blk * BM, n0 = n_blk * BN;
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1)) {
             umdk_set_status(status, UMDK_ERR_TIMEOUT, UMDK_PH_TMA_EMPTY, t, kb);
@@ -151,8 +165,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int it = 0;
     int buf = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
-      const int m0 = (t % mb) * BM;
-      const int n0 = (t / mb) * BN;
+      int m_blk, n_blk;
+      tile_to_mn(t, mb, nb, &m_blk, &n_blk);
+      const int m0 = m_blk * BM, n0 = n_blk * BN;
       const int ab = it & 1;
       const uint32_t aph = (it >> 1) & 1;
       if (!mbar_wait(&tfull[ab], aph)) {

@@ -301,6 +301,21 @@ __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void red_add_release_gpu(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// NVLS: a load on a multicast address returns the sum over all GPUs bound to it (reduced inside NVSwitch, fp32
+// accumulation); a store on it lands in every GPU's copy.
+__device__ __forceinline__ int4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  int4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const int4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 // 16-byte streaming store / load that bypass L1 (peer memory is never cached in the local L1 coherently).
 __device__ __forceinline__ void st_na_v4(void* p, const int4& v) {

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def _torchrun(script, nproc, timeout=600):
     env = dict(os.environ)
-    env.setdefault("NCCL_NVLS_ENABLE", "0")
+    env.setdefault("URMA_SHM_DIR", f"/tmp/umdk_urma_test_{os.getpid()}")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.join(HERE, script)]
     p = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout)
@@ -24,3 +24,10 @@ def test_ep_kernels_across_gpus():
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     rc, out = _torchrun("mp_ep_worker.py", n)
     assert rc == 0 and "MP_EP_OK" in out, out[-4000:]
+
+
+def test_tp_kernels_allreduce_and_urma_across_gpus():
+    n = min(torch.cuda.device_count(), 8)
+    n = 8 if n >= 8 else 4 if n >= 4 else 2
+    rc, out = _torchrun("mp_tp_worker.py", n)
+    assert rc == 0 and "MP_TP_OK" in out, out[-4000:]

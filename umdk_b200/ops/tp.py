@@ -35,6 +35,7 @@ class _ArParams(ctypes.Structure):
         ("buf_off", ctypes.c_uint64 * 2), ("flag_off", ctypes.c_uint64),
         ("inp", ctypes.c_void_p), ("out", ctypes.c_void_p), ("n", ctypes.c_ulonglong),
         ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("mc_base", ctypes.c_void_p), ("in_place", ctypes.c_int),
     ]
 
 
@@ -148,6 +149,11 @@ class AllReduce:
         dev = torch.device("cuda", torch.cuda.current_device())
         self.ctrl = torch.zeros(8, dtype=torch.int32, device=dev)
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.calls = 0  # host mirror of the device epoch (buffer parity of the next call = calls & 1)
+
+    @property
+    def next_parity(self) -> int:
+        return self.calls & 1
 
     @staticmethod
     def heap_bytes(max_bytes: int, R: int) -> int:
@@ -155,27 +161,42 @@ class AllReduce:
         lib.umdk_allreduce_heap_bytes.restype = ctypes.c_longlong
         return int(lib.umdk_allreduce_heap_bytes(ctypes.c_ulonglong(max_bytes), R))
 
-    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, algo: str = "auto", num_ctas: int = 0,
-                 phase_mask: int = 3) -> torch.Tensor:
-        assert x.dtype == torch.bfloat16 and x.is_contiguous()
-        n = x.numel()
+    def buffer(self, n: int, parity: int) -> torch.Tensor:
+        """bf16 view of the heap buffer of the given epoch parity: fill it and call with ``in_place=True`` to skip
+        the copy-in / copy-out (the result replaces the input in that buffer)."""
+        from ..utils.rawtensor import from_ptr
+        return from_ptr(self.heap.local_ptr + self.buf[parity], (n,), torch.bfloat16, self.ctrl.device)
+
+    def __call__(self, x: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, algo: str = "auto",
+                 num_ctas: int = 0, phase_mask: int = 3, in_place: bool = False, n: Optional[int] = None
+                 ) -> Optional[torch.Tensor]:
+        if not in_place:
+            assert x.dtype == torch.bfloat16 and x.is_contiguous()
+            n = x.numel()
+            if out is None:
+                out = torch.empty_like(x)
         assert n * 2 <= self.max_bytes and n % (8 * self.R) == 0, "size must be a multiple of 8 * world elements"
-        if out is None:
-            out = torch.empty_like(x)
+        has_mc = getattr(self.heap, "multicast_ptr", 0) != 0
         if algo == "auto":
-            algo = "one_shot" if n * 2 <= 512 * 1024 else "two_shot"
+            algo = "one_shot" if n * 2 <= 512 * 1024 else ("nvls" if has_mc else "two_shot")
+        code = {"one_shot": 0, "two_shot": 1, "nvls": 2}[algo]
         p = _ArParams()
-        p.R, p.rank, p.algo, p.num_ctas, p.phase_mask = self.R, self.rank, 0 if algo == "one_shot" else 1, num_ctas, \
-            phase_mask
+        p.R, p.rank, p.algo, p.num_ctas, p.phase_mask = self.R, self.rank, code, num_ctas, phase_mask
+        p.mc_base = getattr(self.heap, "multicast_ptr", 0) or None
+        p.in_place = int(in_place)
         for i, pp in enumerate(self.heap.peer_ptrs):
             p.peers[i] = pp
         p.buf_off[0], p.buf_off[1] = self.buf
         p.flag_off = self.flag
-        p.inp, p.out, p.n = x.data_ptr(), out.data_ptr(), n
+        p.inp = x.data_ptr() if x is not None else None
+        p.out = out.data_ptr() if out is not None else None
+        p.n = n
         p.ctrl, p.status = self.ctrl.data_ptr(), self.status.data_ptr()
         rc = self.lib.umdk_allreduce(ctypes.byref(p), _native.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"umdk_allreduce failed: {rc}")
+        if phase_mask & 2:
+            self.calls += 1
         return out
 
     def check(self):

@@ -81,6 +81,38 @@ class SymmetricHeap:
             heaps.append(h)
         return heaps
 
+    @classmethod
+    def multicast(cls, nbytes: int, group: Optional[dist.ProcessGroup] = None) -> "SymmetricHeap":
+        """Heap whose slabs are also bound to an NVLink multicast object (NVLS): besides the per-peer pointers it
+        offers ``multicast_ptr``, an address on which ``multimem`` loads reduce over all ranks inside NVSwitch and
+        ``multimem`` stores broadcast to all ranks. Allocation and handle exchange go through
+        ``torch.distributed._symmetric_memory`` (plumbing only; the kernels that use the pointers are this
+        package's). Raises if the platform cannot provide a multicast mapping."""
+        import torch.distributed._symmetric_memory as symm_mem
+        pg = group if group is not None else dist.group.WORLD
+        dev = torch.device("cuda", torch.cuda.current_device())
+        t = symm_mem.empty(int(nbytes), dtype=torch.uint8, device=dev)
+        hdl = symm_mem.rendezvous(t, pg)
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        if mc == 0:
+            raise RuntimeError("no NVLink multicast mapping available for this group")
+        t.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        h = cls.__new__(cls)
+        h.nbytes = int(nbytes)
+        h.group = group
+        h.rank = dist.get_rank(group)
+        h.world = dist.get_world_size(group)
+        h._lib = _native.cam()
+        h._local = ctypes.c_void_p(int(hdl.buffer_ptrs[h.rank]))
+        h._imported = []
+        h.peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
+        h.multicast_ptr = mc
+        h._torch_keepalive = (t, hdl)
+        h._virtual_children = []
+        return h
+
     @property
     def local_ptr(self) -> int:
         return self._local.value
@@ -93,6 +125,10 @@ class SymmetricHeap:
 
     def close(self):
         lib = self._lib
+        if getattr(self, "_torch_keepalive", None) is not None:
+            self._torch_keepalive = None  # memory is owned by torch's symmetric-memory allocator
+            self._local = ctypes.c_void_p()
+            return
         for p in self._imported:
             lib.umdk_symm_unimport(ctypes.c_void_p(p))
         self._imported = []
