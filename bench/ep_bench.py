@@ -152,6 +152,7 @@ def bench_ll(rank, world, a):
     out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
     t_all = timed(lambda: ll.moe(x, idx, w, experts, shared, out=out), a.iters, a.warmup, world)
     t_routed = timed(lambda: ll.moe(x, idx, w, experts, None, out=out), a.iters, a.warmup, world)
+    t_two = timed(lambda: ll.moe(x, idx, w, experts, None, out=out, fused=False), a.iters, a.warmup, world)
     ll.check("ll")
     rows = int(ll.group_off[-1].item())
     w_bytes = (w1q.numel() + w2q.numel())              # routed expert weights read once per call
@@ -165,6 +166,8 @@ def bench_ll(rank, world, a):
     emit(rank, dict(common, impl="umdk_b200", op="dispatch+GEMM1+SwiGLU+quant+GEMM2+combine (routed only)",
                     us=t_routed * 1e6, roofline_us=roof * 1e6, frac_of_roofline=roof / t_routed,
                     weight_GBps=w_bytes / t_routed / 1e9))
+    emit(rank, dict(common, impl="umdk_b200", op="same, expert GEMMs as two launches (moe_gemm mode 0 + mode 2)",
+                    us=t_two * 1e6, frac_of_roofline=roof / t_two))
     if world >= 1:
         # baseline: NCCL all-to-all + separate quant + cuBLAS bf16 expert GEMMs + NCCL all-to-all + index_add
         w1b = ref.dequant_fp8_128x128(w1q, w1s).to(torch.bfloat16) if el <= 64 else None

@@ -9,6 +9,10 @@
 
 #include "urma_types.h"
 
+#ifndef URMA_EXPORT
+#define URMA_EXPORT __attribute__((visibility("default")))
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -79,8 +83,8 @@ typedef struct urma_provider_ops {
 } urma_provider_ops_t;
 
 /* Called by providers (typically from a constructor of a liburma-*.so plug-in, or statically for built-ins). */
-int urma_register_provider_ops(const urma_provider_ops_t* ops);
-int urma_unregister_provider_ops(const urma_provider_ops_t* ops);
+URMA_EXPORT int urma_register_provider_ops(const urma_provider_ops_t* ops);
+URMA_EXPORT int urma_unregister_provider_ops(const urma_provider_ops_t* ops);
 
 #ifdef __cplusplus
 }

@@ -30,13 +30,16 @@ def _inputs(R, T, H, E, K, seed):
     return xs, idxs, ws
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("R,T,H,F,E,K", [
     (1, 16, 512, 256, 4, 2),
     (2, 40, 1024, 256, 8, 2),
     (4, 33, 1024, 512, 16, 4),
     (8, 24, 2048, 512, 64, 8),
+    (2, 128, 2048, 1024, 256, 8),   # more (token tile x weight tile) items than CTAs in both phases
+    (2, 512, 1024, 256, 4, 2),      # several token tiles per expert
 ])
-def test_low_latency_moe_virtual_ranks(R, T, H, F, E, K):
+def test_low_latency_moe_virtual_ranks(R, T, H, F, E, K, fused):
     from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
     from umdk_b200.parallel.symm import SymmetricHeap
     w1q, w1s, w2q, w2s = _weights(E, H, F, seed=E)
@@ -55,16 +58,23 @@ def test_low_latency_moe_virtual_ranks(R, T, H, F, E, K):
             lays = [st[r].dispatch(dx[r], di[r], phase_mask=1) for r in range(R)]
             for r in range(R):
                 st[r].dispatch(dx[r], di[r], phase_mask=2, lay=lays[r])
-            for r in range(R):
-                st[r]._gemm1(wts[r])
             outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
-            for r in range(R):
-                st[r]._gemm2_combine(wts[r], di[r], dw[r], outs[r], phase_mask=1)
-            for r in range(R):
-                st[r]._gemm2_combine(wts[r], di[r], dw[r], outs[r], phase_mask=2)
+            if fused:
+                for r in range(R):
+                    st[r]._fused(wts[r], di[r], dw[r], outs[r], phase_mask=1)
+                for r in range(R):
+                    st[r]._fused(wts[r], di[r], dw[r], outs[r], phase_mask=2)
+            else:
+                for r in range(R):
+                    st[r]._gemm1(wts[r])
+                for r in range(R):
+                    st[r]._gemm2_combine(wts[r], di[r], dw[r], outs[r], phase_mask=1)
+                for r in range(R):
+                    st[r]._gemm2_combine(wts[r], di[r], dw[r], outs[r], phase_mask=2)
             torch.cuda.synchronize()
             for s in st:
                 s.check()
+                assert int(s.tile_done.abs().sum().item()) == 0   # the fused kernel leaves its counters at zero
             # token counts per local expert are exact
             for r in range(R):
                 want_cnt = torch.zeros(el, dtype=torch.int64)
@@ -93,12 +103,12 @@ def test_low_latency_moe_single_call_with_shared_expert():
         st = EpLowLatency(heap, E, K, H, F, T)
         w = ExpertWeights(w1q.cuda(), w1s.cuda(), w2q.cuda(), w2s.cuda())
         sh = ExpertWeights(s1q.cuda(), s1s.cuda(), s2q.cuda(), s2s.cuda())
-        for _ in range(3):
-            out, share, cnt = st.moe(xs[0].cuda(), idxs[0].cuda(), ws[0].cuda(), w, shared=sh)
-        torch.cuda.synchronize()
-        st.check()
         want = ref.ref_fused_moe(xs[0], idxs[0], ws[0], w1q, w1s, w2q, w2s)
-        assert ref.mean_rel_err(out.float().cpu(), want) < 0.02
+        for fused in (True, False, True):
+            out, share, cnt = st.moe(xs[0].cuda(), idxs[0].cuda(), ws[0].cuda(), w, shared=sh, fused=fused)
+            torch.cuda.synchronize()
+            st.check()
+            assert ref.mean_rel_err(out.float().cpu(), want) < 0.02, fused
         ones = torch.ones(T, 1)
         want_sh = ref.ref_fused_moe(xs[0], torch.zeros(T, 1, dtype=torch.int64), ones, s1q, s1s, s2q, s2s)
         assert ref.mean_rel_err(share.float().cpu(), want_sh) < 0.02

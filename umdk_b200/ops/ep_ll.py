@@ -4,8 +4,9 @@ grouped fp8 GEMM2 whose epilogue stores rows into the token owners' combine buff
 Kernel chain per call (all on the caller's stream, capturable in a CUDA graph):
   ep_layout           bucket positions of (token, k) per expert
   ep_ll_dispatch      count all-gather + fp8 1x128 quantisation + direct push into the destination slab rows
-  moe_gemm mode 0     waits for the arrival flags, then gate/up projection + SwiGLU + fp8 re-quantisation
-  moe_gemm mode 2     down projection, combine-send epilogue, completion flags, owner-side weighted reduction
+  moe_fused           waits for the arrival flags, gate/up projection + SwiGLU + fp8 re-quantisation, down projection
+                      with the combine-send epilogue, completion flags, owner-side weighted reduction: one launch
+                      (or, with fused=False, moe_gemm mode 0 followed by moe_gemm mode 2)
 The shared expert (if any) runs through the same GEMM kernels on the locally quantised tokens.
 
 Mirrors the contract of the reference's ``fused_deep_moe`` (src/cam/comm_operator/pybind/fused_deep_moe.cpp:30-83;
@@ -42,6 +43,24 @@ class _LLDispatchParams(ctypes.Structure):
         ("x", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p), ("send_idx", ctypes.c_void_p),
         ("num_per_expert", ctypes.c_void_p), ("group_off", ctypes.c_void_p), ("recv_per_expert", ctypes.c_void_p),
         ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+    ]
+
+
+class _MoeFusedParams(ctypes.Structure):
+    _fields_ = [
+        ("G", ctypes.c_int), ("F", ctypes.c_int), ("H", ctypes.c_int), ("n_rows_cap", ctypes.c_int),
+        ("max_ctas", ctypes.c_int),
+        ("w1", ctypes.c_void_p), ("w1s", ctypes.c_void_p), ("w2", ctypes.c_void_p), ("w2s", ctypes.c_void_p),
+        ("x", ctypes.c_void_p), ("xs", ctypes.c_void_p), ("group_off", ctypes.c_void_p),
+        ("hq", ctypes.c_void_p), ("hs", ctypes.c_void_p), ("tile_done", ctypes.c_void_p),
+        ("wait_flags", ctypes.c_void_p), ("wait_n", ctypes.c_int),
+        ("R", ctypes.c_int), ("rank", ctypes.c_int), ("T", ctypes.c_int), ("Kt", ctypes.c_int),
+        ("T_cap", ctypes.c_int),
+        ("peers", ctypes.c_void_p * MAX_RANKS),
+        ("comb_buf_off", ctypes.c_uint64), ("comb_flag_off", ctypes.c_uint64),
+        ("row_meta", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p), ("topk_w", ctypes.c_void_p),
+        ("out", ctypes.c_void_p), ("ctrl", ctypes.c_void_p), ("phase_mask", ctypes.c_int),
+        ("status", ctypes.c_void_p),
     ]
 
 
@@ -101,6 +120,8 @@ class EpLowLatency:
         self.hq = torch.empty(self.n_cap, ffn, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
         self.hs = torch.empty(self.n_cap, ffn // 128, dtype=torch.float32, device=dev)
         self.dispatch_ctas, self.gemm_ctas = dispatch_ctas, gemm_ctas
+        # per-token-tile completion counters of the fused kernel (zero between calls; the kernel resets them)
+        self.tile_done = torch.zeros(self.n_cap // 64 + self.E_local + 1, dtype=torch.int32, device=dev)
         # shared-expert scratch
         self.sh_off = torch.tensor([0, 0], dtype=torch.int32, device=dev)
         self.sh_hq = torch.empty(t_cap, ffn, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
@@ -182,6 +203,27 @@ class EpLowLatency:
         if rc != 0:
             raise RuntimeError(f"umdk_moe_gemm(mode 2) failed: {rc}")
 
+    def _fused(self, w: ExpertWeights, topk_idx, topk_w, out, phase_mask: int = 3):
+        """GEMM1 + SwiGLU + re-quant + GEMM2 + combine-send + weighted reduction in ONE persistent launch
+        (csrc/cam/moe_fused.cu)."""
+        p = _MoeFusedParams()
+        p.G, p.F, p.H, p.n_rows_cap, p.max_ctas = self.E_local, self.F, self.H, self.n_cap, self.gemm_ctas
+        p.w1, p.w1s, p.w2, p.w2s = w.w1q.data_ptr(), w.w1s.data_ptr(), w.w2q.data_ptr(), w.w2s.data_ptr()
+        p.x, p.xs = self._local(self.lay.slab_x), self._local(self.lay.slab_s)
+        p.group_off = self.group_off.data_ptr()
+        p.hq, p.hs, p.tile_done = self.hq.data_ptr(), self.hs.data_ptr(), self.tile_done.data_ptr()
+        p.wait_flags, p.wait_n = self._local(self.lay.data_flag), self.R
+        p.R, p.rank, p.T, p.Kt, p.T_cap = self.R, self.rank, topk_idx.shape[0], self.K, self.T_cap
+        for i, pp in enumerate(self.heap.peer_ptrs):
+            p.peers[i] = pp
+        p.comb_buf_off, p.comb_flag_off = self.lay.comb_buf, self.lay.comb_flag
+        p.row_meta = self._local(self.lay.slab_meta)
+        p.topk_idx, p.topk_w, p.out = topk_idx.data_ptr(), topk_w.data_ptr(), out.data_ptr()
+        p.ctrl, p.phase_mask, p.status = self.ctrl.data_ptr(), phase_mask, self.status.data_ptr()
+        rc = self.lib.umdk_moe_fused(ctypes.byref(p), _native.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"umdk_moe_fused failed: {rc}")
+
     def shared_expert(self, x: torch.Tensor, w: ExpertWeights, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Dense SwiGLU FFN of the shared expert on this rank's own tokens (fp8 block-scaled, same GEMM kernels)."""
         T = x.shape[0]
@@ -193,15 +235,19 @@ class EpLowLatency:
                               max_ctas=self.gemm_ctas)
 
     def moe(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w: ExpertWeights,
-            shared: Optional[ExpertWeights] = None, out: Optional[torch.Tensor] = None):
-        """Full layer: returns (combine_x [T, H] bf16, share_output or None, expert_token_nums [E_local] int64)."""
+            shared: Optional[ExpertWeights] = None, out: Optional[torch.Tensor] = None, fused: bool = True):
+        """Full layer: returns (combine_x [T, H] bf16, share_output or None, expert_token_nums [E_local] int64).
+        ``fused`` runs both expert GEMMs and the combine as one persistent kernel; otherwise as two launches."""
         T = x.shape[0]
         if out is None:
             out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
         self.dispatch(x, topk_idx)
         share_out = self.shared_expert(x, shared) if shared is not None else None
-        self._gemm1(w)
-        self._gemm2_combine(w, topk_idx, topk_w, out)
+        if fused:
+            self._fused(w, topk_idx, topk_w, out)
+        else:
+            self._gemm1(w)
+            self._gemm2_combine(w, topk_idx, topk_w, out)
         return out, share_out, self.recv_per_expert
 
     def check(self, what: str = "ep_ll"):
