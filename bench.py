@@ -3,7 +3,9 @@
 
 One decode step per rank = batch 64 sequences x 1 token, context 32768 in a paged bf16 MLA KV cache (64-token pages),
 sparse attention over top-2048 KV rows per query chosen uniformly at random, half of every sequence's pages offloaded
-to pinned host memory and prefetched with cudaMemcpyAsync on a side stream, MoE layers with 256 routed experts
+to pinned host memory (cudaMemcpyAsync on a side stream) and brought back on that side stream every step - by default
+only the token rows the step's indices select, gathered by a kernel that reads the pinned pool directly
+(--kv-fetch rows); or every offloaded page with cudaMemcpyAsync (--kv-fetch pages) - MoE layers with 256 routed experts
 (top-8, fp8 e4m3 SwiGLU experts 7168 -> 2048 -> 7168 with 128x128 block scales) plus one shared expert, experts
 sharded over the N ranks (EP = N), attention data parallel (weak scaling: 64 sequences per GPU).
 
@@ -92,6 +94,12 @@ def main():
     ap.add_argument("--config", default="full", choices=["full", "tiny"])
     ap.add_argument("--no-offload", action="store_true", help="keep the whole KV cache on the device (not the "
                     "benchmark configuration; for kernel-only studies)")
+    ap.add_argument("--kv-fetch", default="rows", choices=["rows", "pages"],
+                    help="how offloaded KV returns each step: the selected token rows only (gather kernel reading "
+                    "pinned host memory) or all offloaded pages (cudaMemcpyAsync)")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="after the warm-up run ONE step between cudaProfilerStart/Stop and exit (for a launch list: "
+                    "ncu --profile-from-start off --metrics gpu__time_duration.sum ...); prints no benchmark line")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -121,6 +129,7 @@ def main():
 
     cfg = DecoderConfig() if args.config == "full" else DecoderConfig.tiny()
     cfg.offload = not args.no_offload
+    cfg.kv_fetch = args.kv_fetch
     model = DecoderRank(cfg, device=dev)
     B, L = cfg.batch, cfg.n_layers
 
@@ -133,7 +142,7 @@ def main():
     dev_tokens = [t.to(dev) for t in host_tokens]
     dev_idx = [[t.to(dev) for t in per] for per in host_idx]
     in_tokens = torch.empty(B, dtype=torch.int64, device=dev)
-    in_idx = [torch.empty(B, cfg.topk_kv, dtype=torch.int32, device=dev) for _ in range(L)]
+    in_idx = [[torch.empty(B, cfg.topk_kv, dtype=torch.int32, device=dev) for _ in range(L)] for _ in range(2)]
     host_out = torch.empty(B, dtype=torch.int64).pin_memory()
     h2d_bytes = host_tokens[0].numel() * 8 + sum(t.numel() * 4 for t in host_idx[0])
     d2h_bytes = host_out.numel() * 8
@@ -150,11 +159,29 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def wait_prefetch():
+        if model.kvm is not None:
+            for l in range(L):
+                model.kvm.wait(l)
+
     # ---- device-timed: inputs resident on the device ----
+    # Step i+1's KV transfers are queued on the side stream as soon as step i has been launched (its indices are
+    # inputs, not model outputs). The compute stream waits for every queued transfer before the closing event, so
+    # the timed region holds K steps of compute and K steps of transfers.
     for i in range(args.warmup):
         model.step(dev_tokens[i % ring], dev_idx[i % ring])
+        model.prefetch(dev_idx[(i + 1) % ring], after_compute=False)
     torch.cuda.synchronize()
     model.check()
+    if args.profile_step:
+        torch.cuda.profiler.start()
+        model.step(dev_tokens[0], dev_idx[args.warmup % ring])
+        wait_prefetch()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        model.close()
+        return 0
+    rows0 = model.kvm.rows_fetched() if (model.kvm is not None and model.rows_mode) else 0
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
@@ -162,25 +189,43 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        model.step(dev_tokens[i % ring], dev_idx[i % ring])
+        k = args.warmup + i
+        model.step(dev_tokens[k % ring], dev_idx[k % ring])
+        model.prefetch(dev_idx[(k + 1) % ring], after_compute=False)
+    wait_prefetch()
     e1.record()
     barrier()
+    rows_per_step = ((model.kvm.rows_fetched() - rows0) / args.steps
+                     if (model.kvm is not None and model.rows_mode) else 0)
     launches = _native.LAUNCH_COUNT - launches0
     ms = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop()
     model.check()
 
     # ---- end to end through the public step API: pinned host inputs in, sampled tokens out, every step ----
+    # Every step copies, from pinned host memory, its own tokens and the NEXT step's KV indices (double-buffered;
+    # they feed the transfers that overlap this step), runs the public step(), and reads the sampled tokens back.
+    side = model.kvm.side_stream() if model.kvm is not None else torch.cuda.current_stream()
+
+    def stage_indices(i: int):
+        buf = in_idx[i % 2]
+        with torch.cuda.stream(side):   # the indices travel on the stream that consumes them
+            for l in range(L):
+                buf[l].copy_(host_idx[i % ring][l], non_blocking=True)
+        model.prefetch(buf, after_compute=False)
+
     def e2e_step(i: int):
         in_tokens.copy_(host_tokens[i % ring], non_blocking=True)
-        for l in range(L):
-            in_idx[l].copy_(host_idx[i % ring][l], non_blocking=True)
-        nxt = model.step(in_tokens, in_idx)
-        model.prefetch()  # the next step's KV pages are known: start moving them while the host reads the result
+        nxt = model.step(in_tokens, in_idx[i % 2])
+        stage_indices(i + 1)
         host_out.copy_(nxt, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return int(host_out[0])
 
+    wait_prefetch()          # the transfer queued by the last device-timed step used other index buffers
+    torch.cuda.synchronize()
+    model._prefetched = False
+    stage_indices(0)
     for i in range(args.warmup):
         e2e_step(i)
     barrier()
@@ -188,7 +233,8 @@ def main():
     c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     c0.record()
     for i in range(args.steps):
-        e2e_step(i)
+        e2e_step(args.warmup + i)
+    wait_prefetch()
     c1.record()
     barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
@@ -199,7 +245,17 @@ def main():
     tokens = world * B * args.steps
     value = tokens / (ms * 1e-3)
     e2e_value = tokens / (e2e_ms * 1e-3)
-    kv_bytes_step = (cfg.n_layers * model.n_staging * 64 * 576 * 2) if cfg.offload else 0
+    if not cfg.offload:
+        kv_bytes_step, kv_how = 0, "off"
+    elif model.rows_mode:
+        kv_bytes_step = int(rows_per_step * 576 * 2)
+        kv_how = ("half of each sequence's pages in pinned host memory (moved out with cudaMemcpyAsync on a side "
+                  "stream); every step a gather kernel on the side stream reads the token rows that the step's "
+                  "top-2048 indices select straight from the pinned pool into a device landing area")
+    else:
+        kv_bytes_step = cfg.n_layers * model.n_staging * 64 * 576 * 2
+        kv_how = ("half of each sequence's pages in pinned host memory, all of them prefetched every step with "
+                  "cudaMemcpyAsync on a side stream")
     if rank == 0:
         print(json.dumps({
             "metric": "moe_decode_tokens_per_sec_per_box", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -210,9 +266,8 @@ def main():
             "config": {"model": "deepseek-v3-shaped 4-layer MoE decoder" if args.config == "full" else "tiny",
                        "global_batch": world * B, "seq_len": cfg.ctx, "parallelism": f"ep{world}+dp{world}",
                        "experts": cfg.n_experts, "top_k": cfg.top_k, "moe_ffn": cfg.moe_ffn, "hidden": cfg.hidden,
-                       "kv_topk": cfg.topk_kv, "kv_page": 64, "kv_offload": "half of each sequence's pages in pinned "
-                       "host memory, prefetched every step with cudaMemcpyAsync on a side stream" if cfg.offload
-                       else "off", "kv_prefetch_bytes_per_step_per_gpu": kv_bytes_step,
+                       "kv_topk": cfg.topk_kv, "kv_page": 64, "kv_offload": kv_how, "kv_fetch": cfg.kv_fetch if cfg.offload else None,
+                       "kv_prefetch_bytes_per_step_per_gpu": kv_bytes_step,
                        "l2": "per-step working set (expert weights + KV) is far larger than the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,

@@ -121,6 +121,46 @@ def bench_mla(B, ctx, topk):
     return report("sparse_mla_decode", med, mn, bytes_, flops, {"B": B, "ctx": ctx, "topk": topk})
 
 
+def bench_kv_gather(B, ctx, topk):
+    """Row-granular KV prefetch: rows of the offloaded half of every sequence read straight from pinned host memory
+    by the gather kernel (PCIe-bound; the HBM columns of the report do not apply)."""
+    from umdk_b200.ops.attention import DIM, PAGE
+    from umdk_b200.ops.kv_offload import KvOffloadManager
+    P = ctx // PAGE
+    half = P // 2
+    kvm = KvOffloadManager(PAGE * DIM * 2, B * half, channels=1)
+    kvm.host_pool_tensor()[:] = 1.0
+    host_tab = torch.full((B, P), -1, dtype=torch.int32)
+    for b in range(B):
+        host_tab[b, half:] = b * half + torch.arange(half)
+    host_tab = host_tab.cuda()
+    idx = torch.stack([torch.randperm(ctx, device="cuda")[:topk] for _ in range(B)]).to(torch.int32)
+    landing = torch.empty(B * topk, DIM, dtype=torch.bfloat16, device="cuda")
+    remap = torch.empty_like(idx)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+
+    def fn():
+        kvm.prefetch_rows(0, idx, host_tab, landing, remap, P * PAGE, PAGE, status=status)
+        kvm.wait(0)
+
+    med, mn = time_kernel(fn)
+    assert status.tolist()[0] == 0
+    n_host = int((idx >= half * PAGE).sum())
+    bytes_ = n_host * DIM * 2
+    out = {"kernel": "kv_gather_rows (pinned host -> device over PCIe)", "us": med * 1e6, "us_min": mn * 1e6,
+           "host_rows": n_host, "row_bytes": DIM * 2, "pcie_GB/s": bytes_ / med / 1e9, "B": B, "ctx": ctx,
+           "topk": topk}
+    print(json.dumps(out), flush=True)
+    # the same bytes as one contiguous cudaMemcpyAsync, for the PCIe ceiling of this box
+    src = torch.empty(bytes_, dtype=torch.uint8).pin_memory()
+    dst = torch.empty(bytes_, dtype=torch.uint8, device="cuda")
+    med2, _ = time_kernel(lambda: dst.copy_(src, non_blocking=True))
+    print(json.dumps({"kernel": "cudaMemcpyAsync H2D of the same byte count (ceiling)", "us": med2 * 1e6,
+                      "pcie_GB/s": bytes_ / med2 / 1e9}), flush=True)
+    kvm.close()
+    return out
+
+
 def bench_dispatch_combine(T, H, E, K):
     """World size 1: every token stays on the GPU, so this measures the kernels' local memory path only."""
     from umdk_b200.ops.ep import EpNormal
@@ -177,7 +217,7 @@ def bench_quant(T, H):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["moe_gemm1", "moe_gemm2", "mla", "dispatch", "gemm_bf16", "quant", "all"])
+    ap.add_argument("what", choices=["moe_gemm1", "moe_gemm2", "mla", "kv_gather", "dispatch", "gemm_bf16", "quant", "all"])
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--tokens-per-expert", type=int, default=32)
     ap.add_argument("--batch", type=int, default=64)
@@ -194,6 +234,8 @@ def main():
         bench_moe_gemm(2, a.experts, a.tokens_per_expert)
     if a.what in ("mla", "all"):
         bench_mla(a.batch, a.ctx, a.topk)
+    if a.what in ("kv_gather", "all"):
+        bench_kv_gather(a.batch, a.ctx, a.topk)
     if a.what in ("dispatch", "all"):
         bench_dispatch_combine(a.tokens, 7168, 256, 8)
     if a.what in ("gemm_bf16", "all"):

@@ -7,6 +7,12 @@
 // compute stream in both directions (data ready before attention reads it; attention finished before the slots are
 // overwritten by the next prefetch). There is no KV-cache code in the reference project (its roadmap lists
 // "KVCache transfer" as future work, src/cam/README.md:21-23); this is specified by the serving configuration.
+//
+// Second prefetch form, for sparse attention: `umdk_kv_prefetch_rows` runs a gather kernel on the same side stream
+// that reads ONLY the selected token rows of host-resident pages straight out of the pinned pool (the pool is mapped
+// into the device address space, so the loads travel over PCIe as 512-byte warp requests) and lands them in a small
+// device area; the index list is rewritten so that attention finds those rows there. With top-2048 of 32768 tokens
+// selected per query this moves 1/16 of the bytes of a page-granular prefetch and needs 1/8 of the landing memory.
 #include "common.h"
 
 #include <stdlib.h>
@@ -16,11 +22,61 @@
 
 namespace {
 
+struct KvGatherArgs {
+  const int* indices;       // [B, topk] token positions (-1 = unused)
+  const int* host_table;    // [B, n_log_pages] host slot of each logical page, -1 if the page is on the device
+  const uint8_t* host_pool; // device alias of the pinned pool
+  uint8_t* landing;         // [B * topk] rows on the device
+  int* indices_out;         // [B, topk] positions for attention: unchanged, or virt_base + i for a landed row
+  unsigned long long* row_counter;
+  int* status;
+  long long host_rows;      // rows in the pool (bounds check)
+  int B, topk, n_log_pages, page_tokens, row_bytes, virt_base;
+};
+
+// One warp per selected row. Rows of device-resident pages are left where they are.
+__global__ void __launch_bounds__(256) kv_gather_rows_kernel(const KvGatherArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  const int total = a.B * a.topk;
+  const int nvec = a.row_bytes >> 4;
+  unsigned long long moved = 0;
+  for (int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < total; row += warps) {
+    const int b = row / a.topk, i = row - b * a.topk;
+    const int idx = a.indices[row];
+    int out = idx;
+    if (idx >= 0) {
+      const int page = idx / a.page_tokens;
+      if (page < a.n_log_pages) {
+        const int slot = a.host_table[(size_t)b * a.n_log_pages + page];
+        if (slot >= 0) {
+          const long long hrow = (long long)slot * a.page_tokens + (idx - page * a.page_tokens);
+          if (hrow >= a.host_rows) {
+            if (lane == 0) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_NONE, b, slot);
+            out = -1;
+          } else {
+            const int4* s = reinterpret_cast<const int4*>(a.host_pool + (size_t)hrow * a.row_bytes);
+            int4* d = reinterpret_cast<int4*>(a.landing + (size_t)row * a.row_bytes);
+            for (int c = lane; c < nvec; c += 32) d[c] = __ldcs(s + c);
+            out = a.virt_base + i;
+            ++moved;
+          }
+        }
+      }
+    }
+    if (lane == 0) a.indices_out[row] = out;
+  }
+  if (lane == 0 && moved && a.row_counter) atomicAdd(a.row_counter, moved);
+}
+
 struct KvOffload {
   size_t page_bytes = 0;
   size_t host_pages = 0;
   uint8_t* host_pool = nullptr;
+  uint8_t* host_pool_dev = nullptr;    // the same memory as seen from kernels
+  unsigned long long* row_counter = nullptr;  // device: host rows fetched by the gather kernel so far
   cudaStream_t copy_stream = nullptr;
+  bool own_stream = true;
   std::vector<cudaEvent_t> ready;      // per channel: prefetch finished
   std::vector<cudaEvent_t> consumed;   // per channel: compute finished reading the prefetched slots
   std::vector<char> consumed_valid;
@@ -29,17 +85,32 @@ struct KvOffload {
 
 }  // namespace
 
-UMDK_API void* umdk_kv_create(size_t page_bytes, size_t host_pages, int channels) {
+// `stream`: side stream to use (owned by the caller, must outlive the manager), or nullptr to create one.
+UMDK_API void* umdk_kv_create_on_stream(size_t page_bytes, size_t host_pages, int channels, void* stream) {
   if (page_bytes == 0 || (page_bytes % 16) || host_pages == 0 || channels < 1 || channels > 1024) return nullptr;
   KvOffload* k = new KvOffload();
   k->page_bytes = page_bytes;
   k->host_pages = host_pages;
-  if (cudaHostAlloc(reinterpret_cast<void**>(&k->host_pool), page_bytes * host_pages, cudaHostAllocDefault) !=
-      cudaSuccess) {
+  if (cudaHostAlloc(reinterpret_cast<void**>(&k->host_pool), page_bytes * host_pages,
+                    cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+    cudaGetLastError();
     delete k;
     return nullptr;
   }
-  if (cudaStreamCreateWithFlags(&k->copy_stream, cudaStreamNonBlocking) != cudaSuccess) {
+  if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&k->host_pool_dev), k->host_pool, 0) != cudaSuccess) {
+    cudaGetLastError();
+    k->host_pool_dev = nullptr;  // page-granular copies still work; the row gather reports an error
+  }
+  if (cudaMalloc(reinterpret_cast<void**>(&k->row_counter), 8) == cudaSuccess) {
+    cudaMemset(k->row_counter, 0, 8);
+  } else {
+    cudaGetLastError();
+    k->row_counter = nullptr;
+  }
+  if (stream) {
+    k->copy_stream = static_cast<cudaStream_t>(stream);
+    k->own_stream = false;
+  } else if (cudaStreamCreateWithFlags(&k->copy_stream, cudaStreamNonBlocking) != cudaSuccess) {
     cudaFreeHost(k->host_pool);
     delete k;
     return nullptr;
@@ -54,14 +125,19 @@ UMDK_API void* umdk_kv_create(size_t page_bytes, size_t host_pages, int channels
   return k;
 }
 
+UMDK_API void* umdk_kv_create(size_t page_bytes, size_t host_pages, int channels) {
+  return umdk_kv_create_on_stream(page_bytes, host_pages, channels, nullptr);
+}
+
 UMDK_API void umdk_kv_destroy(void* h) {
   KvOffload* k = static_cast<KvOffload*>(h);
   if (!k) return;
   cudaStreamSynchronize(k->copy_stream);
   for (auto e : k->ready) cudaEventDestroy(e);
   for (auto e : k->consumed) cudaEventDestroy(e);
-  cudaStreamDestroy(k->copy_stream);
+  if (k->own_stream) cudaStreamDestroy(k->copy_stream);
   cudaFreeHost(k->host_pool);
+  if (k->row_counter) cudaFree(k->row_counter);
   delete k;
 }
 
@@ -116,6 +192,62 @@ UMDK_API int umdk_kv_prefetch(void* h, int channel, void* dev_pool, const int* d
   if (int rc = copy_pages(k, dev_pool, dev_pages, host_slots, n, 0)) return rc;
   UMDK_CUDA_CHECK(cudaEventRecord(k->ready[channel], k->copy_stream));
   return 0;
+}
+
+// Row-granular prefetch for sparse attention (see the top of the file). The gather kernel runs on the copy stream
+// after (a) everything queued so far on `compute_stream` if `after_compute` is set (the indices were produced there;
+// pass 0 when they are already final or were written on the copy stream itself), and (b) the last reader of the
+// channel's landing area. landing: [B * topk] rows of row_bytes; indices_out: [B, topk].
+UMDK_API int umdk_kv_prefetch_rows(void* h, int channel, const int* indices, const int* host_table, void* landing,
+                                   int* indices_out, int B, int topk, int n_log_pages, int page_tokens, int row_bytes,
+                                   int virt_base, int* status, int after_compute, void* compute_stream) {
+  KvOffload* k = static_cast<KvOffload*>(h);
+  if (channel < 0 || channel >= (int)k->ready.size() || B < 1 || topk < 1 || n_log_pages < 1 || page_tokens < 1 ||
+      row_bytes < 16 || (row_bytes % 16) || (size_t)page_tokens * row_bytes != k->page_bytes)
+    return -UMDK_ERR_BAD_ARG;
+  if (!k->host_pool_dev) return -UMDK_ERR_CUDA;
+  if (after_compute) {
+    cudaEvent_t e;
+    UMDK_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    UMDK_CUDA_CHECK(cudaEventRecord(e, static_cast<cudaStream_t>(compute_stream)));
+    UMDK_CUDA_CHECK(cudaStreamWaitEvent(k->copy_stream, e, 0));
+    UMDK_CUDA_CHECK(cudaEventDestroy(e));
+  }
+  if (k->consumed_valid[channel]) UMDK_CUDA_CHECK(cudaStreamWaitEvent(k->copy_stream, k->consumed[channel], 0));
+  KvGatherArgs a;
+  a.indices = indices;
+  a.host_table = host_table;
+  a.host_pool = k->host_pool_dev;
+  a.landing = static_cast<uint8_t*>(landing);
+  a.indices_out = indices_out;
+  a.row_counter = k->row_counter;
+  a.status = status;
+  a.host_rows = (long long)k->host_pages * page_tokens;
+  a.B = B;
+  a.topk = topk;
+  a.n_log_pages = n_log_pages;
+  a.page_tokens = page_tokens;
+  a.row_bytes = row_bytes;
+  a.virt_base = virt_base;
+  const long long rows = (long long)B * topk;
+  int grid = (int)((rows + 7) / 8);
+  const int cap = umdk::sm_count() * 8;
+  if (grid > cap) grid = cap;
+  kv_gather_rows_kernel<<<grid, 256, 0, k->copy_stream>>>(a);
+  UMDK_CUDA_CHECK(cudaGetLastError());
+  UMDK_CUDA_CHECK(cudaEventRecord(k->ready[channel], k->copy_stream));
+  return 0;
+}
+
+// Host rows fetched by the gather kernel since creation (synchronises the copy stream).
+UMDK_API long long umdk_kv_rows_fetched(void* h) {
+  KvOffload* k = static_cast<KvOffload*>(h);
+  if (!k->row_counter) return -1;
+  unsigned long long v = 0;
+  if (cudaStreamSynchronize(k->copy_stream) != cudaSuccess ||
+      cudaMemcpy(&v, k->row_counter, 8, cudaMemcpyDeviceToHost) != cudaSuccess)
+    return -1;
+  return (long long)v;
 }
 
 // Makes `compute_stream` wait until the channel's prefetch has landed.

@@ -10,7 +10,7 @@
 // Work split: phase-1 items are dealt round-robin; phase-2 items (about 1/7 of the cost each) are dealt in
 // contiguous ranges sized so that every CTA ends at the same time, the CTAs with fewer phase-1 items taking the
 // earliest (first ready) phase-2 items. Roles per CTA as in moe_gemm.cu: TMA producer warp, single-thread MMA issuer,
-// TMEM allocator warp, four promotion/epilogue warps. Same math and operand formats as moe_gemm.cu modes 0 and 2.
+// TMEM allocator warp, eight promotion/epilogue warps (two per scheduler, so one hides the other's TMEM-load latency). Same math and operand formats as moe_gemm.cu modes 0 and 2.
 // Reference counterpart: the fused_deep_moe operator (src/cam/comm_operator/ascend_kernels/fused_deep_moe/op_kernel/
 // fused_deep_moe.h:354-448), whose cube cores likewise wait per expert group for arrived tokens
 // (gemm/kernel/grouped_matmul_slice_m_per_token_dequant_swiglu_quant_multistage_workspace.h:271-280) - there with an
@@ -25,7 +25,8 @@ namespace {
 constexpr int TT = 64;
 constexpr int BMW = 128;
 constexpr int BKB = 128;
-constexpr int kThreads = 256;
+constexpr int kThreads = 384;      // TMA, MMA, TMEM-allocator and one spare warp + 8 promotion / epilogue warps
+constexpr int kEpiThreads = 256;
 constexpr int kTransStride = 129;
 constexpr int kRingBytes = 4 * (2 * BMW * BKB + TT * BKB);  // 160 KB: 4 x 40 KB (phase 1) or 6 x 24 KB (phase 2)
 constexpr int kTmemCols = 256;
@@ -49,6 +50,7 @@ struct FusedArgs {
   const int64_t* topk_idx;
   const float* topk_w;
   __nv_bfloat16* out;
+  __nv_bfloat16* share_out;  // optional [T, H]: the row of the LAST top-k slot goes here unweighted instead of into `out`
   int T, Kt, T_cap;
   uint32_t* ctrl;          // [0] epoch (advanced here), [1] send-done, [2] reduce-done
   int phase_mask;          // bit0: gate + both GEMM phases + combine-send + flags; bit1: wait + reduce + epoch advance
@@ -72,11 +74,12 @@ struct Shared {
   int* tile_pref;
   int* goff;
   int* epi_flag;
+  int* meta_sm;    // [TT][2] owner rank and slot of the rows of the current token tile (phase 2)
   uint64_t* bars;  // per phase: full[6], empty[6], tfull[2], tempty[2] = 16 barriers
   uint8_t* ring;
 };
 
-__device__ __forceinline__ void bar_epi() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void bar_epi() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack_fp8x4(float a, float b, float c, float d) {
   const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
   const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
@@ -120,6 +123,30 @@ __device__ __forceinline__ void run_phase(const CUtensorMap* tmW, const CUtensor
       uint32_t ph = 0;
       bool ok = true;
       int ready_tile = -1;
+      // L2 prefetch cursor: runs kL2Ahead weight k-blocks ahead of the shared-memory ring (across item boundaries and,
+      // in phase 2, across the wait for the token tile), so that ring fills hit L2 instead of paying DRAM latency
+      // with only kStages tiles in flight.
+      constexpr int kL2Ahead = PH == 1 ? 8 : 16;
+      int pw = first, pkb = 0, pe = 0, pj = 0;
+      auto pre_locate = [&]() {
+        if (pw < last) {
+          int r0, mm;
+          locate_tile(sh.tile_pref, sh.goff, a.G, pw / NT, &pe, &r0, &mm);
+          pj = pw % NT;
+        }
+      };
+      auto pre_issue = [&]() {
+        if (pw >= last) return;
+        tma_prefetch_l2_2d(tmW, pkb * BKB, pe * w_rows + pj * BMW);
+        if (PH == 1) tma_prefetch_l2_2d(tmW, pkb * BKB, pe * w_rows + a.F + pj * BMW);
+        if (++pkb == kb_total) {
+          pkb = 0;
+          pw += step;
+          pre_locate();
+        }
+      };
+      pre_locate();
+      for (int i = 0; i < kL2Ahead; ++i) pre_issue();
       for (int w = first; w < last && ok; w += step) {
         int e, row0, m;
         const int tile = w / NT;
@@ -142,6 +169,7 @@ __device__ __forceinline__ void run_phase(const CUtensorMap* tmW, const CUtensor
           }
           mbar_expect_tx(&full[s], C::kStageBytes);
           uint8_t* st = sh.ring + s * C::kStageBytes;
+          pre_issue();
           tma_load_2d_hint(st, tmW, &full[s], kb * BKB, e * w_rows + j * BMW, pol_w);
           if (PH == 1) tma_load_2d_hint(st + BMW * BKB, tmW, &full[s], kb * BKB, e * w_rows + a.F + j * BMW, pol_w);
           tma_load_2d_hint(st + C::kABytes, tmX, &full[s], kb * BKB, row0, pol_x);
@@ -193,15 +221,22 @@ __device__ __forceinline__ void run_phase(const CUtensorMap* tmW, const CUtensor
       }
     }
   } else if (warp >= 4) {
+    // Eight promotion / epilogue warps. TMEM lane = weight row of the tile; a warp may only touch the 32 lanes
+    // selected by (warp index mod 4), so warps 4..7 and 8..11 cover the same rows and split the 64 token columns.
     const int ew = warp - 4;
-    const int tid = ew * 32 + lane;
+    const int q = warp & 3, hh = ew >> 2;
+    const int tid = ew * 32 + lane;         // 0..255 inside the epilogue group
+    const int wrow = q * 32 + lane;         // weight row of this thread inside the 128-row tile
+    constexpr int HC = TT / 2;              // token columns per thread
     const int nsb = K / 128;
     const int wsb = w_rows / 128;
     const float* xs = PH == 1 ? a.xs : a.hs;
     const float* ws = PH == 1 ? a.w1s : a.w2s;
     uint32_t kbc = 0;
     bool ok = true;
-    int ready_tile = -1;
+    int ready_tile = -1, loaded_tile = -1;
+    float ws_next = 0.f;
+    bool have_ws_next = false;
     for (int w = first; w < last && ok; w += step) {
       int e, row0, m;
       const int tile = w / NT;
@@ -214,24 +249,47 @@ __device__ __forceinline__ void run_phase(const CUtensorMap* tmW, const CUtensor
         if (!*sh.epi_flag) break;  // the producer records the timeout
         ready_tile = tile;
       }
-      for (int i = tid; i < TT * kb_total; i += 128) {
-        const int t = i / kb_total, kb = i - t * kb_total;
-        // phase 2 reads scales written by other SMs during this launch: bypass L1
-        sh.xs_sm[kb * TT + t] = t < m ? __ldcg(xs + (size_t)(row0 + t) * nsb + kb) : 0.f;
+      if (PH == 1 || tile != loaded_tile) {
+        // activation scales (and, in phase 2, the owner / slot of every row) depend on the token tile only; a CTA's
+        // phase-2 items walk the weight tiles of one token tile back to back, so they are fetched once per tile
+        for (int i = tid; i < TT * kb_total; i += kEpiThreads) {
+          const int t = i / kb_total, kb = i - t * kb_total;
+          // phase 2 reads scales written by other SMs during this launch: bypass L1
+          sh.xs_sm[kb * TT + t] = t < m ? __ldcg(xs + (size_t)(row0 + t) * nsb + kb) : 0.f;
+        }
+        if (PH == 2 && tid < 2 * TT) sh.meta_sm[tid] = (tid >> 1) < m ? a.row_meta[2 * row0 + tid] : -1;
+        loaded_tile = tile;
       }
-      for (int i = tid; i < C::kATiles * kb_total; i += 128) {
-        const int which = i / kb_total, kb = i - which * kb_total;
-        const int brow = which == 0 ? j : (a.F / 128 + j);
-        sh.ws_sm[which * kb_total + kb] = ws[((size_t)e * wsb + brow) * nsb + kb];
+      if (!have_ws_next) {
+        for (int i = tid; i < C::kATiles * kb_total; i += kEpiThreads) {
+          const int which = i / kb_total, kb = i - which * kb_total;
+          const int brow = which == 0 ? j : (a.F / 128 + j);
+          sh.ws_sm[which * kb_total + kb] = ws[((size_t)e * wsb + brow) * nsb + kb];
+        }
+      } else if (tid < C::kATiles * kb_total) {
+        sh.ws_sm[tid] = ws_next;   // fetched while the previous item was in its k-loop
+      }
+      have_ws_next = false;
+      if (w + step < last && C::kATiles * kb_total <= kEpiThreads) {
+        // weight scales of the NEXT item: the load is in flight during this item's k-loop
+        int e2, r2, m2;
+        const int w2 = w + step;
+        locate_tile(sh.tile_pref, sh.goff, a.G, w2 / NT, &e2, &r2, &m2);
+        if (tid < C::kATiles * kb_total) {
+          const int which = tid / kb_total, kb = tid - which * kb_total;
+          const int brow = which == 0 ? (w2 % NT) : (a.F / 128 + (w2 % NT));
+          ws_next = ws[((size_t)e2 * wsb + brow) * nsb + kb];
+        }
+        have_ws_next = true;
       }
       bar_epi();
-      float acc_g[TT];
-      float acc_u[PH == 1 ? TT : 1];
+      float acc_g[HC];
+      float acc_u[PH == 1 ? HC : 1];
 #pragma unroll
-      for (int c = 0; c < TT; ++c) acc_g[c] = 0.f;
+      for (int c = 0; c < HC; ++c) acc_g[c] = 0.f;
       if (PH == 1) {
 #pragma unroll
-        for (int c = 0; c < TT; ++c) acc_u[c] = 0.f;
+        for (int c = 0; c < HC; ++c) acc_u[c] = 0.f;
       }
       for (int kb = 0; kb < kb_total; ++kb, ++kbc) {
         const int ts = kbc & 1;
@@ -242,59 +300,68 @@ __device__ __forceinline__ void run_phase(const CUtensorMap* tmW, const CUtensor
           break;
         }
         tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ts * C::kTmemStageCols + hh * HC;
+        uint32_t rg[HC];
+        uint32_t ru[PH == 1 ? HC : 1];
+        tmem_ld_x32(taddr, rg);
+        if constexpr (PH == 1) tmem_ld_x32(taddr + TT, ru);
         const float wg = sh.ws_sm[kb];
         const float wu = PH == 1 ? sh.ws_sm[kb_total + kb] : 0.f;
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + ts * C::kTmemStageCols;
-        const float* xsk = sh.xs_sm + kb * TT;
-#pragma unroll
-        for (int c0 = 0; c0 < TT; c0 += 16) {
-          uint32_t rg[16];
-          uint32_t ru[16];
-          tmem_ld_x16(taddr + c0, rg);
-          if (PH == 1) tmem_ld_x16(taddr + TT + c0, ru);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float xsv = xsk[c0 + c];
-            acc_g[c0 + c] = fmaf(__uint_as_float(rg[c]), xsv * wg, acc_g[c0 + c]);
-            if (PH == 1) acc_u[c0 + c] = fmaf(__uint_as_float(ru[c]), xsv * wu, acc_u[c0 + c]);
-          }
-        }
+        const float4* xsk = reinterpret_cast<const float4*>(sh.xs_sm + kb * TT + hh * HC);
+        tmem_ld_wait();
+        // the accumulator stage is free as soon as its values are in registers
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[ts]);
+#pragma unroll
+        for (int c4 = 0; c4 < HC / 4; ++c4) {
+          const float4 x4 = xsk[c4];
+          acc_g[4 * c4 + 0] = fmaf(__uint_as_float(rg[4 * c4 + 0]), x4.x * wg, acc_g[4 * c4 + 0]);
+          acc_g[4 * c4 + 1] = fmaf(__uint_as_float(rg[4 * c4 + 1]), x4.y * wg, acc_g[4 * c4 + 1]);
+          acc_g[4 * c4 + 2] = fmaf(__uint_as_float(rg[4 * c4 + 2]), x4.z * wg, acc_g[4 * c4 + 2]);
+          acc_g[4 * c4 + 3] = fmaf(__uint_as_float(rg[4 * c4 + 3]), x4.w * wg, acc_g[4 * c4 + 3]);
+          if constexpr (PH == 1) {
+            acc_u[4 * c4 + 0] = fmaf(__uint_as_float(ru[4 * c4 + 0]), x4.x * wu, acc_u[4 * c4 + 0]);
+            acc_u[4 * c4 + 1] = fmaf(__uint_as_float(ru[4 * c4 + 1]), x4.y * wu, acc_u[4 * c4 + 1]);
+            acc_u[4 * c4 + 2] = fmaf(__uint_as_float(ru[4 * c4 + 2]), x4.z * wu, acc_u[4 * c4 + 2]);
+            acc_u[4 * c4 + 3] = fmaf(__uint_as_float(ru[4 * c4 + 3]), x4.w * wu, acc_u[4 * c4 + 3]);
+          }
+        }
       }
       if (!ok) break;
+      // transpose through shared memory: trans[token][weight row]
 #pragma unroll
-      for (int c = 0; c < TT; ++c) {
+      for (int c = 0; c < HC; ++c) {
         float v = acc_g[c];
-        if (PH == 1) v = (v / (1.f + __expf(-v))) * acc_u[c];
-        sh.trans[c * kTransStride + tid] = v;
+        if constexpr (PH == 1) v = (v / (1.f + __expf(-v))) * acc_u[c];
+        sh.trans[(hh * HC + c) * kTransStride + wrow] = v;
       }
       bar_epi();
-      const int t = tid & 63, half = tid >> 6;
-      const float* src = sh.trans + t * kTransStride + half * 64;
+      const int t = tid & 63, qtr = tid >> 6;     // token, 32-column quarter of the 128 output columns
+      const float* src = sh.trans + t * kTransStride + qtr * 32;
       const int row = row0 + t;
       if (PH == 1) {
         float amax = 0.f;
 #pragma unroll 8
-        for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(src[i]));
+        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(src[i]));
         sh.amax_sm[tid] = amax;
         bar_epi();
-        amax = fmaxf(fmaxf(sh.amax_sm[t], sh.amax_sm[t + 64]), 1e-4f);
+        amax = fmaxf(fmaxf(fmaxf(sh.amax_sm[t], sh.amax_sm[t + 64]), fmaxf(sh.amax_sm[t + 128], sh.amax_sm[t + 192])),
+                     1e-4f);
         const float inv = 448.f / amax;
         if (t < m) {
-          uint8_t* dst = a.hq + (size_t)row * a.F + j * BMW + half * 64;
+          uint8_t* dst = a.hq + (size_t)row * a.F + j * BMW + qtr * 32;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int qq = 0; qq < 2; ++qq) {
             int4 o;
-            o.x = pack_fp8x4(src[q * 16 + 0] * inv, src[q * 16 + 1] * inv, src[q * 16 + 2] * inv, src[q * 16 + 3] * inv);
-            o.y = pack_fp8x4(src[q * 16 + 4] * inv, src[q * 16 + 5] * inv, src[q * 16 + 6] * inv, src[q * 16 + 7] * inv);
-            o.z = pack_fp8x4(src[q * 16 + 8] * inv, src[q * 16 + 9] * inv, src[q * 16 + 10] * inv, src[q * 16 + 11] * inv);
-            o.w = pack_fp8x4(src[q * 16 + 12] * inv, src[q * 16 + 13] * inv, src[q * 16 + 14] * inv, src[q * 16 + 15] * inv);
-            reinterpret_cast<int4*>(dst)[q] = o;
+            const float* s4 = src + qq * 16;
+            o.x = pack_fp8x4(s4[0] * inv, s4[1] * inv, s4[2] * inv, s4[3] * inv);
+            o.y = pack_fp8x4(s4[4] * inv, s4[5] * inv, s4[6] * inv, s4[7] * inv);
+            o.z = pack_fp8x4(s4[8] * inv, s4[9] * inv, s4[10] * inv, s4[11] * inv);
+            o.w = pack_fp8x4(s4[12] * inv, s4[13] * inv, s4[14] * inv, s4[15] * inv);
+            reinterpret_cast<int4*>(dst)[qq] = o;
           }
-          if (half == 0) a.hs[(size_t)row * (a.F / 128) + j] = amax * (1.f / 448.f);
+          if (qtr == 0) a.hs[(size_t)row * (a.F / 128) + j] = amax * (1.f / 448.f);
         }
         // publish: the rows of this item are in global memory -> one more phase-1 item of this token tile is done
         __threadfence();
@@ -302,18 +369,18 @@ __device__ __forceinline__ void run_phase(const CUtensorMap* tmW, const CUtensor
         if (tid == 0) red_add_release_gpu(&a.tile_done[tile], 1u);
       } else {
         if (t < m) {
-          const int owner = a.row_meta[2 * row], slot = a.row_meta[2 * row + 1];
+          const int owner = sh.meta_sm[2 * t], slot = sh.meta_sm[2 * t + 1];
           if (owner < 0 || owner >= a.R || slot < 0 || slot >= a.T_cap * a.Kt) {
             umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_COMBINE_DATA, owner, slot);
           } else {
-            uint8_t* dst = a.peers.base[owner] + a.comb_buf_off + ((size_t)slot * a.H + j * BMW + half * 64) * 2;
+            uint8_t* dst = a.peers.base[owner] + a.comb_buf_off + ((size_t)slot * a.H + j * BMW + qtr * 32) * 2;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
+            for (int qq = 0; qq < 4; ++qq) {
               int4 o;
               __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-              for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(src[q * 8 + 2 * i], src[q * 8 + 2 * i + 1]);
-              st_na_v4(dst + q * 16, o);
+              for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(src[qq * 8 + 2 * i], src[qq * 8 + 2 * i + 1]);
+              st_na_v4(dst + qq * 16, o);
             }
           }
         }
@@ -335,10 +402,11 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
   sh.xs_sm = sh.trans + TT * kTransStride;
   sh.ws_sm = sh.xs_sm + kb_max * TT;
   sh.amax_sm = sh.ws_sm + 2 * kb_max;
-  sh.tile_pref = reinterpret_cast<int*>(sh.amax_sm + 128);
+  sh.tile_pref = reinterpret_cast<int*>(sh.amax_sm + kEpiThreads);
   sh.goff = sh.tile_pref + (a.G + 1);
   sh.epi_flag = sh.goff + (a.G + 1);
-  sh.bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(sh.epi_flag + 1) + 15) & ~uintptr_t(15));
+  sh.meta_sm = sh.epi_flag + 1;
+  sh.bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(sh.meta_sm + 2 * TT) + 15) & ~uintptr_t(15));
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sh.bars + 32);
   __shared__ int s_ok;
   __shared__ uint32_t s_epoch;
@@ -353,7 +421,7 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
       }
       for (int i = 0; i < 2; ++i) {
         mbar_init(&b[12 + i], 1);
-        mbar_init(&b[14 + i], 4);
+        mbar_init(&b[14 + i], 8);
       }
     }
     mbar_fence_init();
@@ -471,7 +539,13 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        for (int k = 0; k < a.Kt; ++k) {
+        const int k_sum = a.share_out ? a.Kt - 1 : a.Kt;
+        if (a.share_out) {
+          const bool have = a.topk_idx[(size_t)t * a.Kt + k_sum] >= 0;
+          const int4 val = have ? ld_relaxed_sys_v4(src + (size_t)k_sum * nvec + v) : make_int4(0, 0, 0, 0);
+          reinterpret_cast<int4*>(a.share_out + (size_t)t * a.H)[v] = val;
+        }
+        for (int k = 0; k < k_sum; ++k) {
           if (a.topk_idx[(size_t)t * a.Kt + k] < 0) continue;
           const float wk = a.topk_w[(size_t)t * a.Kt + k];
           const int4 val = ld_relaxed_sys_v4(src + (size_t)k * nvec + v);
@@ -522,6 +596,7 @@ struct UmdkMoeFusedParams {
   const int64_t* topk_idx;
   const float* topk_w;
   void* out;
+  void* share_out;
   uint32_t* ctrl;
   int phase_mask;
   int* status;
@@ -554,6 +629,7 @@ UMDK_API int umdk_moe_fused(const UmdkMoeFusedParams* p, void* stream) {
   a.topk_idx = p->topk_idx;
   a.topk_w = p->topk_w;
   a.out = static_cast<__nv_bfloat16*>(p->out);
+  a.share_out = static_cast<__nv_bfloat16*>(p->share_out);
   a.T = p->T;
   a.Kt = p->Kt;
   a.T_cap = p->T_cap;
@@ -568,7 +644,7 @@ UMDK_API int umdk_moe_fused(const UmdkMoeFusedParams* p, void* stream) {
     return -UMDK_ERR_BAD_ARG;
   const int kb_max = (p->H > p->F ? p->H : p->F) / BKB;
   const size_t smem = 1024 + (size_t)kRingBytes + TT * kTransStride * 4 + (size_t)kb_max * TT * 4 + 2 * kb_max * 4 +
-                      128 * 4 + 2 * (size_t)(p->G + 1) * 4 + 4 + 16 + 32 * 8 + 16;
+                      256 * 4 + 2 * (size_t)(p->G + 1) * 4 + 4 + 2 * TT * 4 + 16 + 32 * 8 + 16;
   if (smem > 227 * 1024) return -UMDK_ERR_BAD_ARG;
   UMDK_CUDA_CHECK(cudaFuncSetAttribute(moe_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = sm_count();

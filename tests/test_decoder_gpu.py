@@ -1,4 +1,4 @@
-"""Flagship decoder: the offloaded-KV path must give the same tokens as the all-resident path, and the MoE block of
+"""Flagship decoder: the offloaded-KV paths must give the same tokens as the all-resident path, and the MoE block of
 a layer must match the dense fp32 oracle."""
 import pytest
 import torch
@@ -14,27 +14,44 @@ def _inputs(cfg, seed=0):
     return tokens, idx
 
 
-def test_offloaded_kv_matches_resident_kv():
+@pytest.mark.parametrize("kv_fetch", ["rows", "pages"])
+def test_offloaded_kv_matches_resident_kv(kv_fetch):
+    """Both ways of bringing offloaded KV back (row gather from pinned memory, whole-page cudaMemcpyAsync) must
+    decode the same tokens as a cache that is entirely on the device and holds the same values."""
     from umdk_b200.models.dsv3_decoder import DecoderConfig, DecoderRank
-    outs = []
-    for offload in (True, False):
-        cfg = DecoderConfig.tiny()
-        cfg.offload = offload
-        m = DecoderRank(cfg)
+    cfg_r = DecoderConfig.tiny()
+    cfg_r.offload = False
+    r = DecoderRank(cfg_r)
+    cfg = DecoderConfig.tiny()
+    cfg.offload, cfg.kv_fetch = True, kv_fetch
+    m = DecoderRank(cfg)
+    try:
+        assert m.n_resident == r.n_resident and m.n_staging == r.n_staging
+        host = m.kvm.host_pool_tensor()
+        for l in range(cfg.n_layers):
+            m.kv[l][:m.n_resident] = r.kv[l][:r.n_resident]
+            host[l * m.n_staging:(l + 1) * m.n_staging] = \
+                r.kv[l][r.n_resident:r.n_resident + r.n_staging].cpu().reshape(m.n_staging, -1)
+            m.kv[l][m.n_resident:].zero_()   # only a working prefetch can fill the landing / staging pages
         tokens, idx = _inputs(cfg)
-        if offload:
-            # scribble over the staging pages: only a working prefetch can restore them
-            for pool in m.kv:
-                pool[m.n_resident:].zero_()
-        for _ in range(3):
-            nxt = m.step(tokens, idx)
+        for step in range(3):
+            want = r.step(tokens, idx)
+            got = m.step(tokens, idx)
+            if step == 1:
+                m.prefetch(idx, after_compute=False)   # queued ahead, as the benchmark does
         torch.cuda.synchronize()
         m.check()
-        if offload:
+        r.check()
+        if kv_fetch == "pages":
             assert m.kvm.stats()["bytes_h2d"] == 3 * cfg.n_layers * m.n_staging * 64 * 576 * 2
-        outs.append(nxt.cpu())
+        else:
+            half = cfg.ctx // 2
+            n_host = sum(int(((i >= half) & (i < cfg.ctx)).sum()) for i in idx)
+            assert m.kvm.rows_fetched() == 3 * n_host
+        assert torch.equal(got.cpu(), want.cpu())
+    finally:
         m.close()
-    assert torch.equal(outs[0], outs[1])
+        r.close()
 
 
 def test_decoder_moe_block_matches_oracle():

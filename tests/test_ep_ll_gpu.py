@@ -115,3 +115,52 @@ def test_low_latency_moe_single_call_with_shared_expert():
         assert int(cnt.sum().item()) == int((idxs[0] >= 0).sum().item())
     finally:
         heap.close()
+
+
+@pytest.mark.parametrize("R,T,H,F,E,K", [(1, 64, 1024, 512, 8, 4), (4, 33, 1024, 512, 16, 4)])
+def test_low_latency_moe_shared_expert_folded_into_routed_pipeline(R, T, H, F, E, K):
+    """fold_shared: the shared expert is one more local expert of every rank; results must equal the routed oracle
+    and the separate shared-expert oracle."""
+    from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
+    from umdk_b200.parallel.symm import SymmetricHeap
+    w1q, w1s, w2q, w2s = _weights(E, H, F, seed=E)
+    s1q, s1s, s2q, s2s = _weights(1, H, F, seed=99)
+    xs, idxs, ws = _inputs(R, T, H, E, K, seed=R * 10 + T)
+    heaps = SymmetricHeap.virtual(EpLowLatency.heap_bytes(R, E, K, H, T, fold_shared=True), R)
+    try:
+        st = [EpLowLatency(h, E, K, H, F, T, fold_shared=True) for h in heaps]
+        el = E // R
+        sh = ExpertWeights(s1q.cuda(), s1s.cuda(), s2q.cuda(), s2s.cuda())
+        wts = [ExpertWeights.with_shared(
+            ExpertWeights(w1q[r * el:(r + 1) * el].cuda(), w1s[r * el:(r + 1) * el].cuda(),
+                          w2q[r * el:(r + 1) * el].cuda(), w2s[r * el:(r + 1) * el].cuda()), sh) for r in range(R)]
+        dx = [x.cuda() for x in xs]
+        folded = [st[r].fold_routing(idxs[r].cuda(), ws[r].cuda()) for r in range(R)]
+        for rnd in range(2):
+            lays = [st[r].dispatch(dx[r], folded[r][0], phase_mask=1) for r in range(R)]
+            for r in range(R):
+                st[r].dispatch(dx[r], folded[r][0], phase_mask=2, lay=lays[r])
+            outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+            shares = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+            for r in range(R):
+                st[r]._fused(wts[r], folded[r][0], folded[r][1], outs[r], phase_mask=1, share_out=shares[r])
+            for r in range(R):
+                st[r]._fused(wts[r], folded[r][0], folded[r][1], outs[r], phase_mask=2, share_out=shares[r])
+            torch.cuda.synchronize()
+            for s in st:
+                s.check()
+            ones = torch.ones(T, 1)
+            for r in range(R):
+                want = ref.ref_fused_moe(xs[r], idxs[r], ws[r], w1q, w1s, w2q, w2s)
+                assert ref.mean_rel_err(outs[r].float().cpu(), want) < 0.02, (rnd, r)
+                want_sh = ref.ref_fused_moe(xs[r], torch.zeros(T, 1, dtype=torch.int64), ones, s1q, s1s, s2q, s2s)
+                assert ref.mean_rel_err(shares[r].float().cpu(), want_sh) < 0.02, (rnd, r)
+        if R == 1:
+            out, share, cnt = st[0].moe(dx[0], idxs[0].cuda(), ws[0].cuda(), wts[0])
+            torch.cuda.synchronize()
+            st[0].check()
+            assert ref.mean_rel_err(out.float().cpu(), ref.ref_fused_moe(xs[0], idxs[0], ws[0], w1q, w1s, w2q, w2s)) < 0.02
+            assert cnt.shape[0] == el and int(cnt.sum()) == int((idxs[0] >= 0).sum())
+    finally:
+        for h in heaps:
+            h.close()

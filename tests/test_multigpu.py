@@ -10,7 +10,7 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _torchrun(script, nproc, timeout=600):
+def _torchrun(script, nproc, timeout=240):
     env = dict(os.environ)
     env.setdefault("URMA_SHM_DIR", f"/tmp/umdk_urma_test_{os.getpid()}")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",

@@ -24,11 +24,11 @@ def test_shmem_ops_virtual_pes(R):
     lib = _native.cam()
     heaps = SymmetricHeap.virtual(1 << 16, R)
     try:
-        for h in heaps:
-            h.zero()
-        # word 3 of the 32-bit atomics starts as all-ones so that the AND of every PE clears one bit each
         from umdk_b200.utils.rawtensor import from_ptr
         dev = torch.device("cuda", torch.cuda.current_device())
+        for h in heaps:
+            from_ptr(h.local_ptr, (h.nbytes,), torch.uint8, dev).zero_()
+        # word 3 of the 32-bit atomics starts as all-ones so that the AND of every PE clears one bit each
         a32 = from_ptr(heaps[0].local_ptr + 17408 + 512, (4,), torch.int32, dev)
         a32[3] = -1
         res = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(R)]
@@ -59,7 +59,9 @@ def test_shmem_wait_times_out_with_status():
     lib = _native.cam()
     heaps = SymmetricHeap.virtual(1 << 16, 1)
     try:
-        heaps[0].zero()
+        from umdk_b200.utils.rawtensor import from_ptr
+        from_ptr(heaps[0].local_ptr, (heaps[0].nbytes,), torch.uint8,
+                 torch.device("cuda", torch.cuda.current_device())).zero_()
         res = torch.zeros(16, dtype=torch.int32, device="cuda")
         _run(lib, heaps, 0, 3, 1, 2_000_000, res)   # about a millisecond of budget
         torch.cuda.synchronize()

@@ -44,6 +44,10 @@ class DecoderConfig:
     ctx: int = 32768         # tokens already in the cache
     topk_kv: int = 2048      # KV rows attended per query
     offload: bool = True     # second half of each sequence's pages in pinned host memory
+    # how offloaded KV comes back each step: "rows" = gather only the token rows the step's top-k indices select
+    # (zero-copy reads of the pinned pool by a kernel on the side stream); "pages" = cudaMemcpyAsync of every
+    # offloaded page into a device staging area as large as the offloaded half
+    kv_fetch: str = "rows"
     rope_theta: float = 10000.0
     seed: int = 0
 
@@ -109,31 +113,48 @@ class DecoderRank:
         for L in self.layers:
             w1q, w1s = _quant_experts(el, 2 * c.moe_ffn, H, dev, ge)
             w2q, w2s = _quant_experts(el, H, c.moe_ffn, dev, ge)
-            L["experts"] = ExpertWeights(w1q, w1s, w2q, w2s)
             if c.shared_expert:
+                # the shared expert (replicated: common generator) is stored as one more local expert so that it
+                # runs inside the routed pipeline (EpLowLatency fold_shared)
                 s1q, s1s = _quant_experts(1, 2 * c.moe_ffn, H, dev, g)
                 s2q, s2s = _quant_experts(1, H, c.moe_ffn, dev, g)
-                L["shared"] = ExpertWeights(s1q, s1s, s2q, s2s)
+                L["experts"] = ExpertWeights.with_shared(ExpertWeights(w1q, w1s, w2q, w2s),
+                                                         ExpertWeights(s1q, s1s, s2q, s2s))
+                del w1q, w2q, s1q, s2q
             else:
-                L["shared"] = None
+                L["experts"] = ExpertWeights(w1q, w1s, w2q, w2s)
+            L["shared"] = None
         # EP state
-        nbytes = EpLowLatency.heap_bytes(self.world, c.n_experts, c.top_k, H, c.batch)
+        nbytes = EpLowLatency.heap_bytes(self.world, c.n_experts, c.top_k, H, c.batch, fold_shared=c.shared_expert)
         self.heap = SymmetricHeap(nbytes, group) if self.world > 1 else SymmetricHeap(nbytes)
-        self.ep = EpLowLatency(self.heap, c.n_experts, c.top_k, H, c.moe_ffn, c.batch)
+        self.ep = EpLowLatency(self.heap, c.n_experts, c.top_k, H, c.moe_ffn, c.batch, fold_shared=c.shared_expert)
         # KV cache: pages [0, P/2) resident, [P/2, P) staged from host, page P holds the token being decoded
         B = c.batch
         P = c.ctx // PAGE
         self.pages_per_seq = P + 1
         half = P // 2
+        assert c.kv_fetch in ("rows", "pages")
+        self.rows_mode = c.offload and c.kv_fetch == "rows"
         self.n_resident = B * (half + 1)
-        self.n_staging = B * half
-        n_dev_pages = self.n_resident + self.n_staging
-        bt = torch.empty(B, P + 1, dtype=torch.int32)
+        self.n_staging = B * half            # pages per layer that live in host memory
+        # device pages behind the resident ones: the whole offloaded half ("pages"), or topk rows per sequence
+        self.land_pages_per_seq = (c.topk_kv + PAGE - 1) // PAGE
+        self.n_landing = B * self.land_pages_per_seq if self.rows_mode else self.n_staging
+        n_dev_pages = self.n_resident + self.n_landing
+        ncol = P + 1 + (self.land_pages_per_seq if self.rows_mode else 0)
+        bt = torch.zeros(B, ncol, dtype=torch.int32)
+        host_tab = torch.full((B, P + 1), -1, dtype=torch.int32)
         for b in range(B):
             bt[b, :half] = torch.arange(half) + b * (half + 1)
-            bt[b, half:P] = self.n_resident + b * half + torch.arange(half)
             bt[b, P] = b * (half + 1) + half
+            if self.rows_mode:
+                # logical pages [half, P) have no device page; selected rows land in the virtual pages behind P
+                bt[b, P + 1:] = self.n_resident + b * self.land_pages_per_seq + torch.arange(self.land_pages_per_seq)
+            else:
+                bt[b, half:P] = self.n_resident + b * half + torch.arange(half)
+            host_tab[b, half:P] = b * half + torch.arange(half)
         self.block_table = bt.to(dev)
+        self.virt_base = (P + 1) * PAGE
         self.new_page = bt[:, P].to(dev).long()
         self.kv = []
         gk = torch.Generator(device=dev).manual_seed(c.seed + 5000 + self.rank)
@@ -147,14 +168,31 @@ class DecoderRank:
         if c.offload:
             page_bytes = PAGE * KV_DIM * 2
             self.kvm = KvOffloadManager(page_bytes, c.n_layers * self.n_staging, channels=c.n_layers)
-            self._dev_ids = (ctypes.c_int * self.n_staging)(*range(self.n_resident, self.n_resident + self.n_staging))
             self._host_ids = []
-            for l in range(c.n_layers):
-                hs = list(range(l * self.n_staging, (l + 1) * self.n_staging))
-                self._host_ids.append((ctypes.c_int * self.n_staging)(*hs))
-                # move the staged half out to pinned host memory (the state every decode step starts from)
-                self.kvm.offload(self.kv[l], list(self._dev_ids), hs)
-            self.kvm.sync()
+            self._host_tab, self._idx_remap = [], []
+            if self.rows_mode:
+                # the offloaded half is generated chunk by chunk and moved out with cudaMemcpyAsync on the side stream
+                chunk = max(1, min(self.n_staging, self.n_landing))
+                scratch = torch.empty(chunk, PAGE, KV_DIM, device=dev, dtype=bf)
+                for l in range(c.n_layers):
+                    for s0 in range(0, self.n_staging, chunk):
+                        n = min(chunk, self.n_staging - s0)
+                        scratch[:n] = (torch.randn(n, PAGE, KV_DIM, device=dev, generator=gk) * 0.5).to(bf)
+                        self.kvm.offload(scratch, list(range(n)),
+                                         list(range(l * self.n_staging + s0, l * self.n_staging + s0 + n)))
+                        self.kvm.sync()
+                    self._host_tab.append((host_tab + torch.where(host_tab >= 0, l * self.n_staging, 0))
+                                          .to(torch.int32).to(dev).contiguous())
+                    self._idx_remap.append(torch.empty(B, c.topk_kv, dtype=torch.int32, device=dev))
+            else:
+                self._dev_ids = (ctypes.c_int * self.n_staging)(*range(self.n_resident,
+                                                                       self.n_resident + self.n_staging))
+                for l in range(c.n_layers):
+                    hs = list(range(l * self.n_staging, (l + 1) * self.n_staging))
+                    self._host_ids.append((ctypes.c_int * self.n_staging)(*hs))
+                    # move the staged half out to pinned host memory (the state every decode step starts from)
+                    self.kvm.offload(self.kv[l], list(self._dev_ids), hs)
+                self.kvm.sync()
         pos = float(c.ctx)
         inv_freq = 1.0 / (c.rope_theta ** (torch.arange(0, c.qk_rope, 2, device=dev, dtype=torch.float32) / c.qk_rope))
         self.cos = torch.cos(pos * inv_freq)
@@ -170,12 +208,21 @@ class DecoderRank:
         out = torch.stack((x1 * self.cos - x2 * self.sin, x1 * self.sin + x2 * self.cos), dim=-1)
         return out.flatten(-2).to(x.dtype)
 
-    def prefetch(self):
-        """Queues the host -> device copies of the staged KV pages of every layer on the side stream."""
+    def prefetch(self, indices: Optional[List[torch.Tensor]] = None, after_compute: bool = True):
+        """Queues, on the side stream, the transfers that bring the offloaded KV of every layer back: the rows that
+        ``indices`` select (kv_fetch == "rows"; they must be the indices of the next ``step``) or every offloaded
+        page ("pages"). ``after_compute=False`` lets the transfers start at once instead of after the work already
+        queued on the compute stream; the caller then guarantees that ``indices`` are final (static, or written on
+        ``kvm.side_stream()``)."""
         if self.kvm is None:
             return
         for l in range(self.cfg.n_layers):
-            self.kvm.prefetch(l, self.kv[l], self._dev_ids, self._host_ids[l], self.n_staging)
+            if self.rows_mode:
+                landing = self.kv[l][self.n_resident:]
+                self.kvm.prefetch_rows(l, indices[l], self._host_tab[l], landing, self._idx_remap[l],
+                                       self.virt_base, PAGE, status=self.attn_status, after_compute=after_compute)
+            else:
+                self.kvm.prefetch(l, self.kv[l], self._dev_ids, self._host_ids[l], self.n_staging)
         self._prefetched = True
 
     def _layer(self, l: int, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
@@ -192,6 +239,8 @@ class DecoderRank:
         q_full = torch.cat((q_lat, self._rope(q[..., c.qk_nope:])), dim=-1).contiguous()
         if self.kvm is not None:
             self.kvm.wait(l)
+            if self.rows_mode:
+                indices = self._idx_remap[l]
         o_lat, _ = sparse_mla_decode(q_full, self.kv[l], self.block_table, indices, self.sm_scale,
                                      status=self.attn_status)
         if self.kvm is not None:
@@ -211,7 +260,7 @@ class DecoderRank:
     def step(self, tokens: torch.Tensor, indices: List[torch.Tensor]) -> torch.Tensor:
         """tokens [B] int64 (device), indices[l] [B, topk_kv] int32 (device) -> next tokens [B] int64 (device)."""
         if self.kvm is not None and not self._prefetched:
-            self.prefetch()
+            self.prefetch(indices)
         self._prefetched = False
         x = self.embed[tokens]
         for l in range(self.cfg.n_layers):

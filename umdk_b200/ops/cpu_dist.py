@@ -29,16 +29,36 @@ class CpuDispatchResult:
     quant: bool
 
 
+
+def _world(group) -> int:
+    """World size of the group; 1 when torch.distributed is not initialised (single-process use)."""
+    return dist.get_world_size(group) if dist.is_initialized() else 1
+
+
+def _all_to_all_single(out, send, output_split_sizes=None, input_split_sizes=None, group=None):
+    if not dist.is_initialized():
+        out.copy_(send)   # one rank: everything it sends comes back to it
+        return
+    dist.all_to_all_single(out, send, output_split_sizes=output_split_sizes, input_split_sizes=input_split_sizes,
+                           group=group)
+
+
 def _a2a(send: torch.Tensor, send_splits, recv_splits, group) -> torch.Tensor:
-    out = torch.empty((sum(recv_splits),) + tuple(send.shape[1:]), dtype=send.dtype)
-    dist.all_to_all_single(out, send.contiguous(), output_split_sizes=list(recv_splits),
-                           input_split_sizes=list(send_splits), group=group)
-    return out
+    """Variable-split all-to-all of rows. Rows travel as raw bytes, so any dtype works on gloo."""
+    send = send.contiguous()
+    tail = tuple(send.shape[1:])
+    raw = send.reshape(send.shape[0], -1).view(torch.uint8) if send.shape[0] else \
+        torch.empty(0, max(1, send[0:0].reshape(0, -1).shape[1]) * send.element_size(), dtype=torch.uint8)
+    row_bytes = raw.shape[1]
+    out = torch.empty(sum(recv_splits), row_bytes, dtype=torch.uint8)
+    _all_to_all_single(out, raw.contiguous(), output_split_sizes=list(recv_splits),
+                       input_split_sizes=list(send_splits), group=group)
+    return out.view(send.dtype).reshape((sum(recv_splits),) + tail)
 
 
 def cpu_dispatch(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: Optional[torch.Tensor], num_experts: int,
                  group=None, quant: bool = False) -> CpuDispatchResult:
-    R = dist.get_world_size(group)
+    R = _world(group)
     E = num_experts
     el = E // R
     T, K = topk_idx.shape
@@ -49,7 +69,7 @@ def cpu_dispatch(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: Optional[torch
     # 1. counts: cnt_from[src][le]
     my_counts = lay.num_tokens_per_expert.reshape(R, el).to(torch.int64)
     cnt_from = torch.empty(R, el, dtype=torch.int64)
-    dist.all_to_all_single(cnt_from, my_counts.contiguous(), group=group)
+    _all_to_all_single(cnt_from, my_counts.contiguous(), group=group)
     # 2. rows sorted by (destination expert, bucket position) == (destination rank, local expert, position)
     valid = (idx >= 0) & (idx < E)
     tt, kk = torch.nonzero(valid, as_tuple=True)
@@ -98,13 +118,13 @@ def cpu_dispatch(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: Optional[torch
 def cpu_combine(y: torch.Tensor, expand_idx: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
                 num_tokens: int, group=None, out_dtype=torch.bfloat16) -> torch.Tensor:
     """Returns each row to (srcRank, srcToken, k) and forms sum_k w[t,k] * row in fp32, rounded once."""
-    R = dist.get_world_size(group)
+    R = _world(group)
     H = y.shape[1]
     src = expand_idx[:, 0].to(torch.int64)
     order = torch.argsort(src, stable=True)
     send_splits = torch.bincount(src, minlength=R).tolist()
     recv_cnt = torch.empty(R, dtype=torch.int64)
-    dist.all_to_all_single(recv_cnt, torch.tensor(send_splits, dtype=torch.int64), group=group)
+    _all_to_all_single(recv_cnt, torch.tensor(send_splits, dtype=torch.int64), group=group)
     recv_splits = recv_cnt.tolist()
     rows = _a2a(y.float()[order], send_splits, recv_splits, group)
     meta = _a2a(expand_idx[order][:, 1:].to(torch.int64).contiguous(), send_splits, recv_splits, group)

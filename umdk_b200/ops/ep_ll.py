@@ -59,8 +59,8 @@ class _MoeFusedParams(ctypes.Structure):
         ("peers", ctypes.c_void_p * MAX_RANKS),
         ("comb_buf_off", ctypes.c_uint64), ("comb_flag_off", ctypes.c_uint64),
         ("row_meta", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p), ("topk_w", ctypes.c_void_p),
-        ("out", ctypes.c_void_p), ("ctrl", ctypes.c_void_p), ("phase_mask", ctypes.c_int),
-        ("status", ctypes.c_void_p),
+        ("out", ctypes.c_void_p), ("share_out", ctypes.c_void_p), ("ctrl", ctypes.c_void_p),
+        ("phase_mask", ctypes.c_int), ("status", ctypes.c_void_p),
     ]
 
 
@@ -94,15 +94,32 @@ class ExpertWeights:
     w2q: torch.Tensor
     w2s: torch.Tensor
 
+    @staticmethod
+    def with_shared(experts: "ExpertWeights", shared: "ExpertWeights") -> "ExpertWeights":
+        """Local experts followed by the shared expert as one more local expert (the layout ``fold_shared`` wants)."""
+        def cat8(a, b):
+            return torch.cat((a.view(torch.uint8), b.view(torch.uint8))).contiguous().view(torch.float8_e4m3fn)
+        return ExpertWeights(cat8(experts.w1q, shared.w1q), torch.cat((experts.w1s, shared.w1s)).contiguous(),
+                             cat8(experts.w2q, shared.w2q), torch.cat((experts.w2s, shared.w2s)).contiguous())
+
 
 class EpLowLatency:
     """Per-rank state of the low-latency MoE path at a fixed geometry."""
 
     def __init__(self, heap: SymmetricHeap, num_experts: int, top_k: int, hidden: int, ffn: int, t_cap: int,
-                 dispatch_ctas: int = 32, gemm_ctas: int = 0):
+                 dispatch_ctas: int = 32, gemm_ctas: int = 0, fold_shared: bool = False):
+        """``fold_shared``: the shared expert runs inside the routed pipeline as one more local expert that every
+        token of this rank is sent to with weight 1 (so its tiles are scheduled with all the others instead of a
+        separate under-filled launch). The geometry then has num_experts + R experts and top_k + 1 slots; ``moe`` takes
+        weights built by ``ExpertWeights.with_shared`` and still returns the shared output separately. Use
+        ``heap_bytes(..., fold_shared=True)`` to size the heap."""
         self.lib = _native.cam()
         self.heap = heap
         self.R, self.rank = heap.world, heap.rank
+        self.fold = fold_shared
+        self.E_user, self.K_user = num_experts, top_k
+        if fold_shared:
+            num_experts, top_k = num_experts + heap.world, top_k + 1
         self.E, self.K, self.H, self.F, self.T_cap = num_experts, top_k, hidden, ffn, t_cap
         self.E_local = num_experts // self.R
         self.lay = ll_layout(self.R, num_experts, top_k, hidden, t_cap)
@@ -128,8 +145,24 @@ class EpLowLatency:
         self.sh_hs = torch.empty(t_cap, ffn // 128, dtype=torch.float32, device=dev)
 
     @staticmethod
-    def heap_bytes(R: int, E: int, K: int, H: int, T_cap: int) -> int:
+    def heap_bytes(R: int, E: int, K: int, H: int, T_cap: int, fold_shared: bool = False) -> int:
+        if fold_shared:
+            E, K = E + R, K + 1
         return int(ll_layout(R, E, K, H, T_cap).total)
+
+    def fold_routing(self, topk_idx: torch.Tensor, topk_w: torch.Tensor):
+        """[T, K] routing over the user's experts -> [T, K + 1] routing over the folded expert numbering (every rank
+        has one more local expert, the shared one, which each of its own tokens selects with weight 1)."""
+        el = self.E_user // self.R
+        T = topk_idx.shape[0]
+        idx = torch.empty(T, self.K, dtype=torch.int64, device=topk_idx.device)
+        w = torch.empty(T, self.K, dtype=torch.float32, device=topk_idx.device)
+        idx[:, :self.K_user] = torch.where(topk_idx >= 0, topk_idx + torch.div(topk_idx, el, rounding_mode="floor"),
+                                           topk_idx)
+        idx[:, self.K_user] = self.rank * (el + 1) + el
+        w[:, :self.K_user] = topk_w
+        w[:, self.K_user] = 1.0
+        return idx, w
 
     # -- views into this rank's own heap -------------------------------------------------------------------------
     def _local(self, off: int) -> int:
@@ -203,7 +236,7 @@ class EpLowLatency:
         if rc != 0:
             raise RuntimeError(f"umdk_moe_gemm(mode 2) failed: {rc}")
 
-    def _fused(self, w: ExpertWeights, topk_idx, topk_w, out, phase_mask: int = 3):
+    def _fused(self, w: ExpertWeights, topk_idx, topk_w, out, phase_mask: int = 3, share_out=None):
         """GEMM1 + SwiGLU + re-quant + GEMM2 + combine-send + weighted reduction in ONE persistent launch
         (csrc/cam/moe_fused.cu)."""
         p = _MoeFusedParams()
@@ -219,6 +252,7 @@ class EpLowLatency:
         p.comb_buf_off, p.comb_flag_off = self.lay.comb_buf, self.lay.comb_flag
         p.row_meta = self._local(self.lay.slab_meta)
         p.topk_idx, p.topk_w, p.out = topk_idx.data_ptr(), topk_w.data_ptr(), out.data_ptr()
+        p.share_out = share_out.data_ptr() if share_out is not None else None
         p.ctrl, p.phase_mask, p.status = self.ctrl.data_ptr(), phase_mask, self.status.data_ptr()
         rc = self.lib.umdk_moe_fused(ctypes.byref(p), _native.stream_ptr())
         if rc != 0:
@@ -241,6 +275,14 @@ class EpLowLatency:
         T = x.shape[0]
         if out is None:
             out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
+        if self.fold:
+            assert shared is None and fused and w.w1q.shape[0] == self.E_local, \
+                "fold_shared: pass ExpertWeights.with_shared(experts, shared) as w"
+            idx, wts = self.fold_routing(topk_idx, topk_w)
+            share_out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
+            self.dispatch(x, idx)
+            self._fused(w, idx, wts, out, share_out=share_out)
+            return out, share_out, self.recv_per_expert[:self.E_local - 1]
         self.dispatch(x, topk_idx)
         share_out = self.shared_expert(x, shared) if shared is not None else None
         if fused:
