@@ -153,6 +153,9 @@ def bench_ll(rank, world, a):
     t_all = timed(lambda: ll.moe(x, idx, w, experts, shared, out=out), a.iters, a.warmup, world)
     t_routed = timed(lambda: ll.moe(x, idx, w, experts, None, out=out), a.iters, a.warmup, world)
     t_two = timed(lambda: ll.moe(x, idx, w, experts, None, out=out, fused=False), a.iters, a.warmup, world)
+    tiled = experts.to_tiled()
+    t_tiled = timed(lambda: ll.moe(x, idx, w, tiled, None, out=out), a.iters, a.warmup, world)
+    del tiled
     ll.check("ll")
     rows = int(ll.group_off[-1].item())
     w_bytes = (w1q.numel() + w2q.numel())              # routed expert weights read once per call
@@ -166,6 +169,8 @@ def bench_ll(rank, world, a):
     emit(rank, dict(common, impl="umdk_b200", op="dispatch+GEMM1+SwiGLU+quant+GEMM2+combine (routed only)",
                     us=t_routed * 1e6, roofline_us=roof * 1e6, frac_of_roofline=roof / t_routed,
                     weight_GBps=w_bytes / t_routed / 1e9))
+    emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights (ExpertWeights.to_tiled)",
+                    us=t_tiled * 1e6, frac_of_roofline=roof / t_tiled, weight_GBps=w_bytes / t_tiled / 1e9))
     emit(rank, dict(common, impl="umdk_b200", op="same, expert GEMMs as two launches (moe_gemm mode 0 + mode 2)",
                     us=t_two * 1e6, frac_of_roofline=roof / t_two))
     if world >= 1:

@@ -121,7 +121,7 @@ def bench_mla(B, ctx, topk):
     return report("sparse_mla_decode", med, mn, bytes_, flops, {"B": B, "ctx": ctx, "topk": topk})
 
 
-def bench_kv_gather(B, ctx, topk):
+def bench_kv_gather(B, ctx, topk, num_ctas=8):
     """Row-granular KV prefetch: rows of the offloaded half of every sequence read straight from pinned host memory
     by the gather kernel (PCIe-bound; the HBM columns of the report do not apply)."""
     from umdk_b200.ops.attention import DIM, PAGE
@@ -140,7 +140,7 @@ def bench_kv_gather(B, ctx, topk):
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
 
     def fn():
-        kvm.prefetch_rows(0, idx, host_tab, landing, remap, P * PAGE, PAGE, status=status)
+        kvm.prefetch_rows(0, idx, host_tab, landing, remap, P * PAGE, PAGE, status=status, num_ctas=num_ctas)
         kvm.wait(0)
 
     med, mn = time_kernel(fn)
@@ -149,7 +149,7 @@ def bench_kv_gather(B, ctx, topk):
     bytes_ = n_host * DIM * 2
     out = {"kernel": "kv_gather_rows (pinned host -> device over PCIe)", "us": med * 1e6, "us_min": mn * 1e6,
            "host_rows": n_host, "row_bytes": DIM * 2, "pcie_GB/s": bytes_ / med / 1e9, "B": B, "ctx": ctx,
-           "topk": topk}
+           "topk": topk, "ctas_of_1024_threads": num_ctas}
     print(json.dumps(out), flush=True)
     # the same bytes as one contiguous cudaMemcpyAsync, for the PCIe ceiling of this box
     src = torch.empty(bytes_, dtype=torch.uint8).pin_memory()
@@ -235,7 +235,8 @@ def main():
     if a.what in ("mla", "all"):
         bench_mla(a.batch, a.ctx, a.topk)
     if a.what in ("kv_gather", "all"):
-        bench_kv_gather(a.batch, a.ctx, a.topk)
+        for n in (4, 8, 16, 32):
+            bench_kv_gather(a.batch, a.ctx, a.topk, n)
     if a.what in ("dispatch", "all"):
         bench_dispatch_combine(a.tokens, 7168, 256, 8)
     if a.what in ("gemm_bf16", "all"):

@@ -34,8 +34,11 @@ struct KvGatherArgs {
   int B, topk, n_log_pages, page_tokens, row_bytes, virt_base;
 };
 
-// One warp per selected row. Rows of device-resident pages are left where they are.
-__global__ void __launch_bounds__(256) kv_gather_rows_kernel(const KvGatherArgs a) {
+// One warp per selected row. Rows of device-resident pages are left where they are. The launch uses a handful of
+// 1024-thread CTAs: the transfer is PCIe-bound, a few hundred KB of loads in flight saturate the link, and a small
+// grid occupies only that many SMs, so a persistent compute kernel that runs at the same time on the other SMs
+// (one CTA per SM, all registers) is not held up.
+__global__ void __launch_bounds__(1024) kv_gather_rows_kernel(const KvGatherArgs a) {
   const int lane = threadIdx.x & 31;
   const int warps = gridDim.x * (blockDim.x >> 5);
   const int total = a.B * a.topk;
@@ -200,7 +203,7 @@ UMDK_API int umdk_kv_prefetch(void* h, int channel, void* dev_pool, const int* d
 // channel's landing area. landing: [B * topk] rows of row_bytes; indices_out: [B, topk].
 UMDK_API int umdk_kv_prefetch_rows(void* h, int channel, const int* indices, const int* host_table, void* landing,
                                    int* indices_out, int B, int topk, int n_log_pages, int page_tokens, int row_bytes,
-                                   int virt_base, int* status, int after_compute, void* compute_stream) {
+                                   int virt_base, int* status, int after_compute, int num_ctas, void* compute_stream) {
   KvOffload* k = static_cast<KvOffload*>(h);
   if (channel < 0 || channel >= (int)k->ready.size() || B < 1 || topk < 1 || n_log_pages < 1 || page_tokens < 1 ||
       row_bytes < 16 || (row_bytes % 16) || (size_t)page_tokens * row_bytes != k->page_bytes)
@@ -230,10 +233,10 @@ UMDK_API int umdk_kv_prefetch_rows(void* h, int channel, const int* indices, con
   a.row_bytes = row_bytes;
   a.virt_base = virt_base;
   const long long rows = (long long)B * topk;
-  int grid = (int)((rows + 7) / 8);
-  const int cap = umdk::sm_count() * 8;
-  if (grid > cap) grid = cap;
-  kv_gather_rows_kernel<<<grid, 256, 0, k->copy_stream>>>(a);
+  int grid = num_ctas > 0 ? num_ctas : 8;
+  if (grid > (rows + 31) / 32) grid = (int)((rows + 31) / 32);
+  if (grid > umdk::sm_count()) grid = umdk::sm_count();
+  kv_gather_rows_kernel<<<grid, 1024, 0, k->copy_stream>>>(a);
   UMDK_CUDA_CHECK(cudaGetLastError());
   UMDK_CUDA_CHECK(cudaEventRecord(k->ready[channel], k->copy_stream));
   return 0;

@@ -53,6 +53,7 @@ struct FusedArgs {
   __nv_bfloat16* share_out;  // optional [T, H]: the row of the LAST top-k slot goes here unweighted instead of into `out`
   int T, Kt, T_cap;
   uint32_t* ctrl;          // [0] epoch (advanced here), [1] send-done, [2] reduce-done
+  int w_tiled;             // weights are stored tile by tile (see umdk_moe_fused)
   int phase_mask;          // bit0: gate + both GEMM phases + combine-send + flags; bit1: wait + reduce + epoch advance
   int* status;
 };
@@ -123,30 +124,6 @@ __device__ __forceinline__ void run_phase(const CUtensorMap* tmW, const CUtensor
       uint32_t ph = 0;
       bool ok = true;
       int ready_tile = -1;
-      // L2 prefetch cursor: runs kL2Ahead weight k-blocks ahead of the shared-memory ring (across item boundaries and,
-      // in phase 2, across the wait for the token tile), so that ring fills hit L2 instead of paying DRAM latency
-      // with only kStages tiles in flight.
-      constexpr int kL2Ahead = PH == 1 ? 8 : 16;
-      int pw = first, pkb = 0, pe = 0, pj = 0;
-      auto pre_locate = [&]() {
-        if (pw < last) {
-          int r0, mm;
-          locate_tile(sh.tile_pref, sh.goff, a.G, pw / NT, &pe, &r0, &mm);
-          pj = pw % NT;
-        }
-      };
-      auto pre_issue = [&]() {
-        if (pw >= last) return;
-        tma_prefetch_l2_2d(tmW, pkb * BKB, pe * w_rows + pj * BMW);
-        if (PH == 1) tma_prefetch_l2_2d(tmW, pkb * BKB, pe * w_rows + a.F + pj * BMW);
-        if (++pkb == kb_total) {
-          pkb = 0;
-          pw += step;
-          pre_locate();
-        }
-      };
-      pre_locate();
-      for (int i = 0; i < kL2Ahead; ++i) pre_issue();
       for (int w = first; w < last && ok; w += step) {
         int e, row0, m;
         const int tile = w / NT;
@@ -169,9 +146,13 @@ __device__ __forceinline__ void run_phase(const CUtensorMap* tmW, const CUtensor
           }
           mbar_expect_tx(&full[s], C::kStageBytes);
           uint8_t* st = sh.ring + s * C::kStageBytes;
-          pre_issue();
-          tma_load_2d_hint(st, tmW, &full[s], kb * BKB, e * w_rows + j * BMW, pol_w);
-          if (PH == 1) tma_load_2d_hint(st + BMW * BKB, tmW, &full[s], kb * BKB, e * w_rows + a.F + j * BMW, pol_w);
+          if (a.w_tiled) {
+            // one contiguous chunk per k-block: 128 x 128 B (phase 2) or gate + up = 256 x 128 B (phase 1)
+            tma_load_2d_hint(st, tmW, &full[s], 0, ((e * NT + j) * kb_total + kb) * (C::kATiles * BMW), pol_w);
+          } else {
+            tma_load_2d_hint(st, tmW, &full[s], kb * BKB, e * w_rows + j * BMW, pol_w);
+            if (PH == 1) tma_load_2d_hint(st + BMW * BKB, tmW, &full[s], kb * BKB, e * w_rows + a.F + j * BMW, pol_w);
+          }
           tma_load_2d_hint(st + C::kABytes, tmX, &full[s], kb * BKB, row0, pol_x);
           if (++s == C::kStages) {
             s = 0;
@@ -577,6 +558,7 @@ using namespace umdk;
 
 struct UmdkMoeFusedParams {
   int G, F, H, n_rows_cap, max_ctas;
+  int w_tiled;             // 0: w1 [G, 2F, H], w2 [G, H, F] row-major; 1: tile-major, see below
   const void* w1;          // fp8 [G, 2F, H]
   const float* w1s;
   const void* w2;          // fp8 [G, H, F]
@@ -602,6 +584,12 @@ struct UmdkMoeFusedParams {
   int* status;
 };
 
+// Weight layouts. Row-major (w_tiled = 0): every 128 x 128-byte weight tile that a k-block needs is 128 separate
+// 128-byte pieces H (or F) bytes apart. Tile-major (w_tiled = 1): the same bytes repacked once at load time so that
+// the tile of (expert e, weight tile j, k-block kb) is one contiguous chunk -
+//   w1: [G][F/128][H/128][256][128]  rows 0..127 = gate rows j*128.., rows 128..255 = up rows F + j*128..
+//   w2: [G][H/128][F/128][128][128]
+// - which turns the weight stream into 32 KB / 16 KB sequential DRAM reads. Scales are unchanged.
 UMDK_API int umdk_moe_fused(const UmdkMoeFusedParams* p, void* stream) {
   if (p->G < 1 || p->F < 128 || (p->F % 128) || p->H < 128 || (p->H % 128) || p->n_rows_cap < 1 || p->R < 1 ||
       p->R > kMaxRanks)
@@ -635,11 +623,20 @@ UMDK_API int umdk_moe_fused(const UmdkMoeFusedParams* p, void* stream) {
   a.T_cap = p->T_cap;
   a.ctrl = p->ctrl;
   a.phase_mask = p->phase_mask ? p->phase_mask : 3;
+  a.w_tiled = p->w_tiled;
   a.status = p->status;
   CUtensorMap tmW1, tmX, tmW2, tmH;
-  if (make_tmap_2d(&tmW1, TMAP_U8, p->w1, p->H, (uint64_t)p->G * 2 * p->F, p->H, BKB, BMW, TMAP_SW_128B) ||
+  int bad;
+  if (p->w_tiled) {
+    bad = make_tmap_2d(&tmW1, TMAP_U8, p->w1, BKB, (uint64_t)p->G * 2 * p->F * (p->H / BKB), BKB, BKB, 2 * BMW,
+                       TMAP_SW_128B) ||
+          make_tmap_2d(&tmW2, TMAP_U8, p->w2, BKB, (uint64_t)p->G * p->H * (p->F / BKB), BKB, BKB, BMW, TMAP_SW_128B);
+  } else {
+    bad = make_tmap_2d(&tmW1, TMAP_U8, p->w1, p->H, (uint64_t)p->G * 2 * p->F, p->H, BKB, BMW, TMAP_SW_128B) ||
+          make_tmap_2d(&tmW2, TMAP_U8, p->w2, p->F, (uint64_t)p->G * p->H, p->F, BKB, BMW, TMAP_SW_128B);
+  }
+  if (bad ||
       make_tmap_2d(&tmX, TMAP_U8, p->x, p->H, p->n_rows_cap, p->H, BKB, TT, TMAP_SW_128B) ||
-      make_tmap_2d(&tmW2, TMAP_U8, p->w2, p->F, (uint64_t)p->G * p->H, p->F, BKB, BMW, TMAP_SW_128B) ||
       make_tmap_2d(&tmH, TMAP_U8, p->hq, p->F, p->n_rows_cap, p->F, BKB, TT, TMAP_SW_128B))
     return -UMDK_ERR_BAD_ARG;
   const int kb_max = (p->H > p->F ? p->H : p->F) / BKB;

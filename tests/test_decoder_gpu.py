@@ -63,7 +63,7 @@ def test_decoder_moe_block_matches_oracle():
     g = torch.Generator().manual_seed(3)
     h = torch.randn(cfg.batch, cfg.hidden, generator=g).to(torch.bfloat16).cuda()
     L = m.layers[0]
-    probs = torch.softmax(h.float() @ L["router"].t(), dim=-1)
+    probs = torch.softmax((h @ L["router"].t()).float(), dim=-1)
     w, idx = torch.topk(probs, cfg.top_k, dim=-1)
     w = (w / w.sum(-1, keepdim=True)).contiguous()
     out, share, cnt = m.ep.moe(h, idx.contiguous(), w, L["experts"], L["shared"])

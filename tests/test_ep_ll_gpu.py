@@ -104,11 +104,15 @@ def test_low_latency_moe_single_call_with_shared_expert():
         w = ExpertWeights(w1q.cuda(), w1s.cuda(), w2q.cuda(), w2s.cuda())
         sh = ExpertWeights(s1q.cuda(), s1s.cuda(), s2q.cuda(), s2s.cuda())
         want = ref.ref_fused_moe(xs[0], idxs[0], ws[0], w1q, w1s, w2q, w2s)
-        for fused in (True, False, True):
-            out, share, cnt = st.moe(xs[0].cuda(), idxs[0].cuda(), ws[0].cuda(), w, shared=sh, fused=fused)
+        wt = w.to_tiled()
+        back = wt.to_row_major()
+        assert torch.equal(back.w1q.view(torch.uint8), w.w1q.view(torch.uint8))
+        assert torch.equal(back.w2q.view(torch.uint8), w.w2q.view(torch.uint8))
+        for fused, weights in ((True, w), (False, w), (True, wt)):
+            out, share, cnt = st.moe(xs[0].cuda(), idxs[0].cuda(), ws[0].cuda(), weights, shared=sh, fused=fused)
             torch.cuda.synchronize()
             st.check()
-            assert ref.mean_rel_err(out.float().cpu(), want) < 0.02, fused
+            assert ref.mean_rel_err(out.float().cpu(), want) < 0.02, (fused, weights.tiled)
         ones = torch.ones(T, 1)
         want_sh = ref.ref_fused_moe(xs[0], torch.zeros(T, 1, dtype=torch.int64), ones, s1q, s1s, s2q, s2s)
         assert ref.mean_rel_err(share.float().cpu(), want_sh) < 0.02

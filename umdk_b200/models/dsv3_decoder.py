@@ -105,7 +105,7 @@ class DecoderRank:
             L["w_uv"] = (torch.randn(HEADS, DIM_V, c.v_head, device=dev, generator=g) * 0.02).to(bf)
             L["wo"] = lin(H, HEADS * c.v_head)
             L["ffn_norm"] = torch.ones(H, device=dev, dtype=bf)
-            L["router"] = torch.randn(c.n_experts, H, device=dev, generator=g, dtype=torch.float32) * 0.02
+            L["router"] = (torch.randn(c.n_experts, H, device=dev, generator=g, dtype=torch.float32) * 0.02).to(bf)
             self.layers.append(L)
         # expert shards: a different stream per rank
         ge = torch.Generator(device=dev).manual_seed(c.seed + 1000 + self.rank)
@@ -123,11 +123,18 @@ class DecoderRank:
                 del w1q, w2q, s1q, s2q
             else:
                 L["experts"] = ExpertWeights(w1q, w1s, w2q, w2s)
+            L["experts"] = L["experts"].to_tiled()   # tile-major: sequential DRAM reads in the fused kernel
             L["shared"] = None
         # EP state
         nbytes = EpLowLatency.heap_bytes(self.world, c.n_experts, c.top_k, H, c.batch, fold_shared=c.shared_expert)
         self.heap = SymmetricHeap(nbytes, group) if self.world > 1 else SymmetricHeap(nbytes)
-        self.ep = EpLowLatency(self.heap, c.n_experts, c.top_k, H, c.moe_ffn, c.batch, fold_shared=c.shared_expert)
+        # with the row-gather prefetch running beside it, the persistent MoE kernel leaves a few SMs to the gather
+        # (its CTAs take every register of their SM, so the two kernels cannot share one)
+        self.gather_ctas = 8
+        n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+        moe_ctas = n_sm - self.gather_ctas if (c.offload and c.kv_fetch == "rows") else 0
+        self.ep = EpLowLatency(self.heap, c.n_experts, c.top_k, H, c.moe_ffn, c.batch, gemm_ctas=moe_ctas,
+                               fold_shared=c.shared_expert)
         # KV cache: pages [0, P/2) resident, [P/2, P) staged from host, page P holds the token being decoded
         B = c.batch
         P = c.ctx // PAGE
@@ -220,7 +227,8 @@ class DecoderRank:
             if self.rows_mode:
                 landing = self.kv[l][self.n_resident:]
                 self.kvm.prefetch_rows(l, indices[l], self._host_tab[l], landing, self._idx_remap[l],
-                                       self.virt_base, PAGE, status=self.attn_status, after_compute=after_compute)
+                                       self.virt_base, PAGE, status=self.attn_status, after_compute=after_compute,
+                                       num_ctas=self.gather_ctas)
             else:
                 self.kvm.prefetch(l, self.kv[l], self._dev_ids, self._host_ids[l], self.n_staging)
         self._prefetched = True
@@ -248,7 +256,7 @@ class DecoderRank:
         o = torch.einsum("bhc,hcd->bhd", o_lat, L["w_uv"]).reshape(B, HEADS * c.v_head)
         x = x + o @ L["wo"].t()
         h = F.rms_norm(x, (H,), L["ffn_norm"])
-        probs = torch.softmax(h.float() @ L["router"].t(), dim=-1)
+        probs = torch.softmax((h @ L["router"].t()).float(), dim=-1)
         w, idx = torch.topk(probs, c.top_k, dim=-1)
         w = (w / w.sum(dim=-1, keepdim=True)).contiguous()
         moe, share, _ = self.ep.moe(h.contiguous(), idx.contiguous(), w, L["experts"], L["shared"])
@@ -283,4 +291,5 @@ class DecoderRank:
 def reference_layer_moe(cfg: DecoderConfig, h: torch.Tensor, idx: torch.Tensor, w: torch.Tensor,
                         experts: ExpertWeights) -> torch.Tensor:
     """fp32 oracle of one rank's MoE output when the EP group has a single rank (used by tests)."""
+    experts = experts.to_row_major()
     return ref.ref_fused_moe(h, idx, w, experts.w1q, experts.w1s, experts.w2q, experts.w2s)

@@ -49,7 +49,7 @@ class _LLDispatchParams(ctypes.Structure):
 class _MoeFusedParams(ctypes.Structure):
     _fields_ = [
         ("G", ctypes.c_int), ("F", ctypes.c_int), ("H", ctypes.c_int), ("n_rows_cap", ctypes.c_int),
-        ("max_ctas", ctypes.c_int),
+        ("max_ctas", ctypes.c_int), ("w_tiled", ctypes.c_int),
         ("w1", ctypes.c_void_p), ("w1s", ctypes.c_void_p), ("w2", ctypes.c_void_p), ("w2s", ctypes.c_void_p),
         ("x", ctypes.c_void_p), ("xs", ctypes.c_void_p), ("group_off", ctypes.c_void_p),
         ("hq", ctypes.c_void_p), ("hs", ctypes.c_void_p), ("tile_done", ctypes.c_void_p),
@@ -93,6 +93,37 @@ class ExpertWeights:
     w1s: torch.Tensor
     w2q: torch.Tensor
     w2s: torch.Tensor
+    tiled: bool = False   # w1q / w2q hold the tile-major repacking (only the fused kernel reads it)
+
+    def to_tiled(self) -> "ExpertWeights":
+        """Repacks the fp8 weights so that every 128 x 128-byte tile a k-block needs is one contiguous chunk
+        (w1: [G, F/128, H/128, 256, 128] with the gate rows of the tile followed by its up rows;
+        w2: [G, H/128, F/128, 128, 128]). Done once at load time; the fused kernel then streams 32 KB / 16 KB
+        sequential pieces instead of 128-byte pieces a row apart. Scales are shared with the original."""
+        if self.tiled:
+            return self
+        G, F2, H = self.w1q.shape
+        F = F2 // 2
+        w1 = self.w1q.view(torch.uint8).view(G, 2, F // 128, 128, H // 128, 128)
+        w1t = w1.permute(0, 2, 4, 1, 3, 5).contiguous().view(G, F // 128, H // 128, 256, 128)
+        w2 = self.w2q.view(torch.uint8).view(G, H // 128, 128, F // 128, 128)
+        w2t = w2.permute(0, 1, 3, 2, 4).contiguous()
+        return ExpertWeights(w1t.view(torch.float8_e4m3fn), self.w1s, w2t.view(torch.float8_e4m3fn), self.w2s, True)
+
+    def to_row_major(self) -> "ExpertWeights":
+        """Inverse of ``to_tiled`` (w1: [G, 2F, H], w2: [G, H, F])."""
+        if not self.tiled:
+            return self
+        G, nt, kb = self.w1q.shape[:3]
+        w1 = self.w1q.view(torch.uint8).view(G, nt, kb, 2, 128, 128).permute(0, 3, 1, 4, 2, 5).contiguous()
+        w2 = self.w2q.view(torch.uint8).permute(0, 1, 3, 2, 4).contiguous()
+        return ExpertWeights(w1.view(G, 2 * nt * 128, kb * 128).view(torch.float8_e4m3fn), self.w1s,
+                             w2.view(G, self.w2q.shape[1] * 128, self.w2q.shape[2] * 128).view(torch.float8_e4m3fn),
+                             self.w2s, False)
+
+    @property
+    def num_local_experts(self) -> int:
+        return self.w1q.shape[0]
 
     @staticmethod
     def with_shared(experts: "ExpertWeights", shared: "ExpertWeights") -> "ExpertWeights":
@@ -241,6 +272,7 @@ class EpLowLatency:
         (csrc/cam/moe_fused.cu)."""
         p = _MoeFusedParams()
         p.G, p.F, p.H, p.n_rows_cap, p.max_ctas = self.E_local, self.F, self.H, self.n_cap, self.gemm_ctas
+        p.w_tiled = 1 if w.tiled else 0
         p.w1, p.w1s, p.w2, p.w2s = w.w1q.data_ptr(), w.w1s.data_ptr(), w.w2q.data_ptr(), w.w2s.data_ptr()
         p.x, p.xs = self._local(self.lay.slab_x), self._local(self.lay.slab_s)
         p.group_off = self.group_off.data_ptr()
@@ -288,6 +320,7 @@ class EpLowLatency:
         if fused:
             self._fused(w, topk_idx, topk_w, out)
         else:
+            assert not w.tiled, "the two-launch path reads row-major weights"
             self._gemm1(w)
             self._gemm2_combine(w, topk_idx, topk_w, out)
         return out, share_out, self.recv_per_expert

@@ -58,7 +58,7 @@ class KvOffloadManager:
 
     def prefetch_rows(self, channel: int, indices: torch.Tensor, host_table: torch.Tensor, landing: torch.Tensor,
                       indices_out: torch.Tensor, virt_base: int, page_tokens: int, status: torch.Tensor = None,
-                      after_compute: bool = True):
+                      after_compute: bool = True, num_ctas: int = 8):
         """Fetches the selected rows that live in host pages into ``landing`` ([B * topk, row] device rows) and writes
         ``indices_out``: the position itself for rows of device pages, ``virt_base + i`` for landed rows.
         indices [B, topk] int32 (device), host_table [B, n_logical_pages] int32 (device; host slot or -1).
@@ -74,7 +74,7 @@ class KvOffloadManager:
         rc = self._lib.umdk_kv_prefetch_rows(self._h, channel, _native.ptr(indices), _native.ptr(host_table),
                                              _native.ptr(landing), _native.ptr(indices_out), B, topk,
                                              host_table.shape[1], page_tokens, row_bytes, virt_base,
-                                             _native.ptr(status), 1 if after_compute else 0,
+                                             _native.ptr(status), 1 if after_compute else 0, num_ctas,
                                              _native.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"umdk_kv_prefetch_rows failed: {rc}")
