@@ -37,6 +37,33 @@ __device__ __forceinline__ void acc8(float* acc, const int4& v) {
     acc[2 * i + 1] += f.y;
   }
 }
+// Sum over all ranks of vector `v` of their buffers: the loads of up to eight peers are issued back to back, so one
+// NVLink round trip covers them all instead of one round trip per peer.
+__device__ __forceinline__ void reduce_over_ranks(float* acc, const PeerTable& peers, uint64_t off, int R, int rank,
+                                                  size_t v) {
+  for (int i0 = 0; i0 < R; i0 += 8) {
+    int4 vals[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (i0 + u < R) {
+        const int p = (rank + i0 + u) % R;
+        vals[u] = ld_relaxed_sys_v4(reinterpret_cast<const int4*>(peers.base[p] + off) + v);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (i0 + u < R) {
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&vals[u]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(p2[i]);
+          acc[2 * i] += f.x;
+          acc[2 * i + 1] += f.y;
+        }
+      }
+    }
+  }
+}
 __device__ __forceinline__ int4 pack8(const float* acc) {
   int4 o;
   __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
@@ -115,10 +142,7 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
     int4* dst = reinterpret_cast<int4*>(a.out);
     for (size_t v = tid; v < nvec; v += nthreads) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int i = 0; i < a.R; ++i) {
-        const int p = (a.rank + i) % a.R;
-        acc8(acc, ld_relaxed_sys_v4(reinterpret_cast<const int4*>(a.peers.base[p] + a.buf_off[slot]) + v));
-      }
+      reduce_over_ranks(acc, a.peers, a.buf_off[slot], a.R, a.rank, v);
       dst[v] = pack8(acc);
     }
   } else if (a.algo == 2) {
@@ -127,9 +151,17 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
     const size_t per = nvec / a.R;
     const size_t lo = per * a.rank;
     uint8_t* mc = a.mc_base + a.buf_off[slot];
-    for (size_t v = tid; v < per; v += nthreads) {
-      const int4 r = multimem_ld_reduce_bf16x8(mc + (lo + v) * 16);
-      multimem_st_v4(mc + (lo + v) * 16, r);
+    // four switch reductions in flight per thread before the first broadcast store
+    for (size_t v0 = tid; v0 < per; v0 += 4 * nthreads) {
+      int4 r[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (v0 + u * nthreads < per) r[u] = multimem_ld_reduce_bf16x8(mc + (lo + v0 + u * nthreads) * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (v0 + u * nthreads < per) multimem_st_v4(mc + (lo + v0 + u * nthreads) * 16, r[u]);
+      }
     }
     if (!rank_barrier(a, 1, tag, &a.ctrl[1], true, true)) return;
     if (!a.in_place) {
@@ -142,10 +174,7 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
     const size_t lo = per * a.rank;
     for (size_t v = tid; v < per; v += nthreads) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int i = 0; i < a.R; ++i) {
-        const int p = (a.rank + i) % a.R;
-        acc8(acc, ld_relaxed_sys_v4(reinterpret_cast<const int4*>(a.peers.base[p] + a.buf_off[slot]) + lo + v));
-      }
+      reduce_over_ranks(acc, a.peers, a.buf_off[slot], a.R, a.rank, lo + v);
       mine[lo + v] = pack8(acc);
     }
     if (!rank_barrier(a, 1, tag, &a.ctrl[1], true, true)) return;
@@ -154,7 +183,17 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
     for (int i = 0; i < a.R; ++i) {
       const int p = (a.rank + i) % a.R;
       const int4* from = reinterpret_cast<const int4*>(a.peers.base[p] + a.buf_off[slot]) + per * p;
-      for (size_t v = tid; v < per; v += nthreads) dst[per * p + v] = ld_relaxed_sys_v4(from + v);
+      for (size_t v0 = tid; v0 < per; v0 += 4 * nthreads) {
+        int4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (v0 + u * nthreads < per) r[u] = ld_relaxed_sys_v4(from + v0 + u * nthreads);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (v0 + u * nthreads < per) dst[per * p + v0 + u * nthreads] = r[u];
+        }
+      }
     }
   }
   // the buffer of this parity is reused two calls later; peers must have finished reading it by then

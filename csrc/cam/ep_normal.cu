@@ -234,44 +234,53 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
       if (g.quant) {
         // each lane: 16 elements per step; 8 lanes share one 1x128 block
         const int nblk = g.H / 128;
-        for (int b0 = 0; b0 < nblk; b0 += 4) {
-          const int blk = b0 + (lane >> 3);
-          const bool active = blk < nblk;
-          float f[16];
-          if (active) {
-            const int4 v0 = __ldg(xrow + blk * 16 + (lane & 7) * 2);
-            const int4 v1 = __ldg(xrow + blk * 16 + (lane & 7) * 2 + 1);
-            bf16x8_to_float(v0, f);
-            bf16x8_to_float(v1, f + 8);
-          } else {
+        for (int b0 = 0; b0 < nblk; b0 += 8) {
+          // two groups of four 1x128 blocks per iteration; all four 16-byte loads of a lane are issued first
+          int4 raw[2][2];
+          bool active[2];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) f[i] = 0.f;
+          for (int u = 0; u < 2; ++u) {
+            const int blk = b0 + 4 * u + (lane >> 3);
+            active[u] = blk < nblk;
+            if (active[u]) {
+              raw[u][0] = __ldg(xrow + blk * 16 + (lane & 7) * 2);
+              raw[u][1] = __ldg(xrow + blk * 16 + (lane & 7) * 2 + 1);
+            } else {
+              raw[u][0] = raw[u][1] = make_int4(0, 0, 0, 0);
+            }
           }
-          float amax = 0.f;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
-          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-          amax = fmaxf(amax, 1e-4f);
-          const float scale = amax * (1.f / 448.f);
-          const float inv = 448.f / amax;
-          int4 q;
-          q.x = pack_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
-          q.y = pack_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
-          q.z = pack_fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
-          q.w = pack_fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
-          if (active) {
-            for (uint32_t m = dmask; m; m &= m - 1) {
-              const int d = __ffs(m) - 1;
-              const int slot = s_slot[warp][d];
-              if (slot >= g.cap) continue;
-              const size_t rec = (size_t)g.rank * g.cap + slot;
-              uint8_t* px = a.peers.base[d] + a.off.arr_x[h] + rec * g.row_bytes;
-              st_na_v4(px + blk * 128 + (lane & 7) * 16, q);
-              if ((lane & 7) == 0) {
-                float* ps = reinterpret_cast<float*>(a.peers.base[d] + a.off.arr_scale[h]) + rec * g.nscale;
-                ps[blk] = scale;
+          for (int u = 0; u < 2; ++u) {
+            const int blk = b0 + 4 * u + (lane >> 3);
+            float f[16];
+            bf16x8_to_float(raw[u][0], f);
+            bf16x8_to_float(raw[u][1], f + 8);
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            amax = fmaxf(amax, 1e-4f);
+            const float scale = amax * (1.f / 448.f);
+            const float inv = 448.f / amax;
+            int4 q;
+            q.x = pack_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+            q.y = pack_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+            q.z = pack_fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+            q.w = pack_fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+            if (active[u]) {
+              for (uint32_t m = dmask; m; m &= m - 1) {
+                const int d = __ffs(m) - 1;
+                const int slot = s_slot[warp][d];
+                if (slot >= g.cap) continue;
+                const size_t rec = (size_t)g.rank * g.cap + slot;
+                uint8_t* px = a.peers.base[d] + a.off.arr_x[h] + rec * g.row_bytes;
+                st_na_v4(px + blk * 128 + (lane & 7) * 16, q);
+                if ((lane & 7) == 0) {
+                  float* ps = reinterpret_cast<float*>(a.peers.base[d] + a.off.arr_scale[h]) + rec * g.nscale;
+                  ps[blk] = scale;
+                }
               }
             }
           }
@@ -412,11 +421,19 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
       __syncwarp();
       const int4* px = reinterpret_cast<const int4*>(self + a.off.arr_x[h] + rec * g.row_bytes);
       const int nvec = g.row_bytes / 16;
-      for (int v = lane; v < nvec; v += 32) {
-        const int4 val = px[v];
+      // four 512-byte loads per warp in flight before the first store
+      for (int v0 = lane; v0 < nvec; v0 += 128) {
+        int4 val[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (v0 + 32 * u < nvec) val[u] = px[v0 + 32 * u];
+        }
         for (uint32_t m = kmask; m; m &= m - 1) {
-          const int r2 = s_row[warp][__ffs(m) - 1];
-          reinterpret_cast<int4*>(a.recv_x + (size_t)r2 * g.row_bytes)[v] = val;
+          int4* drow = reinterpret_cast<int4*>(a.recv_x + (size_t)s_row[warp][__ffs(m) - 1] * g.row_bytes);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (v0 + 32 * u < nvec) drow[v0 + 32 * u] = val[u];
+          }
         }
       }
       if (g.quant) {
@@ -464,6 +481,8 @@ struct CombineArgs {
   int phase_mask;
 };
 
+constexpr int kBatch = 8;  // rows whose loads are issued back to back before any of them is consumed
+
 __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const CombineArgs a) {
   const EpGeom& g = a.g;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -507,10 +526,15 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const Combine
         umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_COMBINE_DATA, dst_rank, dst_tok);
         continue;
       }
+      // compact the valid rows so that the loads below can be issued as fixed-size batches (all in flight at once)
       const uint32_t kmask = __ballot_sync(0xffffffffu, row >= 0);
+      const int n = __popc(kmask);
       __syncwarp();
-      s_row[warp][lane] = row;
-      s_coef[warp][lane] = w;
+      if (row >= 0) {
+        const int pos = __popc(kmask & ((1u << lane) - 1u));
+        s_row[warp][pos] = row;
+        s_coef[warp][pos] = w;
+      }
       __syncwarp();
       int4* dst = reinterpret_cast<int4*>(a.peers.base[dst_rank] + a.off.comb_buf[h] +
                                           ((size_t)dst_tok * g.J + slot_j) * g.H * 2);
@@ -519,19 +543,25 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const Combine
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        for (uint32_t m = kmask; m; m &= m - 1) {
-          const int k = __ffs(m) - 1;
-          const int r2 = s_row[warp][k];
-          const float w2 = s_coef[warp][k];
-          if (v < nvec) {
-            const int4 val = __ldg(reinterpret_cast<const int4*>(a.y + (size_t)r2 * g.H) + v);
-            float f[8];
-            bf16x8_to_float(val, f);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = fmaf(w2, f[i], acc[i]);
-          }
-        }
         if (v < nvec) {
+          for (int base = 0; base < n; base += kBatch) {
+            int4 vals[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+              if (base + u < n)
+                vals[u] = __ldg(reinterpret_cast<const int4*>(a.y + (size_t)s_row[warp][base + u] * g.H) + v);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+              if (base + u < n) {
+                const float w2 = s_coef[warp][base + u];
+                float f[8];
+                bf16x8_to_float(vals[u], f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = fmaf(w2, f[i], acc[i]);
+              }
+            }
+          }
           int4 o;
           __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
@@ -567,33 +597,43 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const Combine
     }
     const bool used = lane < J && (a.mode == 0 ? coef != 0.f : a.topk_idx[(size_t)t * g.K + lane] >= 0);
     const uint32_t jmask = __ballot_sync(0xffffffffu, used);
+    const int n = __popc(jmask);
     __syncwarp();
-    s_coef[warp][lane] = coef;
+    if (used) {
+      const int pos = __popc(jmask & ((1u << lane) - 1u));
+      s_row[warp][pos] = lane;
+      s_coef[warp][pos] = coef;
+    }
     __syncwarp();
     const int4* src = reinterpret_cast<const int4*>(self + a.off.comb_buf[h] + (size_t)t * g.J * g.H * 2);
     for (int v0 = 0; v0 < nvec; v0 += 32) {
       const int v = v0 + lane;
+      if (v >= nvec) continue;
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (uint32_t m = jmask; m; m &= m - 1) {
-        const int j = __ffs(m) - 1;
-        const float c = s_coef[warp][j];
-        if (v < nvec) {
-          const int4 val = src[(size_t)j * nvec + v];
-          float f[8];
-          bf16x8_to_float(val, f);
+      for (int base = 0; base < n; base += kBatch) {
+        int4 vals[kBatch];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = fmaf(c, f[i], acc[i]);
+        for (int u = 0; u < kBatch; ++u) {
+          if (base + u < n) vals[u] = src[(size_t)s_row[warp][base + u] * nvec + v];
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          if (base + u < n) {
+            const float c = s_coef[warp][base + u];
+            float f[8];
+            bf16x8_to_float(vals[u], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(c, f[i], acc[i]);
+          }
         }
       }
-      if (v < nvec) {
-        int4 o;
-        __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+      int4 o;
+      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        reinterpret_cast<int4*>(a.out + (size_t)t * g.H)[v] = o;
-      }
+      for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      reinterpret_cast<int4*>(a.out + (size_t)t * g.H)[v] = o;
     }
   }
   if (cta_done_is_last(&a.ctrl[5], gridDim.x)) {
