@@ -203,6 +203,15 @@ def bench_gemm_bf16(M, N, K):
         assert rc == 0
     med, mn = time_kernel(fn)
     r = report("gemm_bf16_tcgen05", med, mn, (M * K + N * K + M * N) * 2, 2.0 * M * N * K, {"M": M, "N": N, "K": K})
+    if M % 256 == 0 and N % 256 == 0 and K % 64 == 0:
+        def fn2():
+            rc = lib.umdk_gemm_bf16_2sm(_native.ptr(A), _native.ptr(B), _native.ptr(C), M, N, K, K, K, N,
+                                        _native.ptr(st), _native.stream_ptr(), 0)
+            assert rc == 0
+        med, mn = time_kernel(fn2)
+        assert st.tolist()[0] == 0, st.tolist()
+        report("gemm_bf16_tcgen05_cta_pair", med, mn, (M * K + N * K + M * N) * 2, 2.0 * M * N * K,
+               {"M": M, "N": N, "K": K})
     med, mn = time_kernel(lambda: torch.matmul(A, B.t(), out=C))
     report("cublas_bf16(torch.matmul)", med, mn, (M * K + N * K + M * N) * 2, 2.0 * M * N * K, {"M": M, "N": N, "K": K})
     return r

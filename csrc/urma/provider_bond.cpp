@@ -31,6 +31,7 @@
 #include "ub_util.h"
 #include "urma_api.h"
 #include "urma_provider.h"
+#include "uvs_topo.h"
 
 namespace {
 
@@ -916,7 +917,13 @@ urma_context_t* prov_create_context(urma_device_t*, uint32_t) {
       pos = comma + 1;
     }
   } else {
-    for (int i = 0; i < kMaxPaths; ++i) names.push_back("shm" + std::to_string(i));
+    // members registered for the aggregation device "bond0" in the topology library, else every shm* device
+    uvs_agg_dev_t agg;
+    if (uvs_get_agg_dev("bond0", &agg) == 0) {
+      for (uint32_t i = 0; i < agg.member_num; ++i) names.push_back(agg.member_names[i]);
+    } else {
+      for (int i = 0; i < kMaxPaths; ++i) names.push_back("shm" + std::to_string(i));
+    }
   }
   for (auto& n : names) {
     if (c->npaths >= kMaxPaths) break;

@@ -81,6 +81,27 @@ def test_urma_perftest_two_processes(tmp_path):
             srv.kill()
 
 
+def test_urma_ping_self_and_two_processes(tmp_path):
+    rc, out = _run([BIN / "urma_ping", "--dev", "shm0", "--count", "3", "--interval-ms", "5"], tmp_path)
+    assert rc == 0 and "3 sent, 3 received, 0% loss" in out, out
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"))
+    srv = subprocess.Popen([str(BIN / "urma_ping"), "--dev", "shm0", "--server", str(port)], stdout=subprocess.PIPE,
+                           stderr=subprocess.STDOUT, text=True, env=env)
+    try:
+        assert "ready" in srv.stdout.readline()
+        rc, out = _run([BIN / "urma_ping", "--dev", "shm0", "--client", "127.0.0.1", str(port), "--count", "4",
+                        "--size", "1024", "--interval-ms", "5"], tmp_path)
+        assert rc == 0 and "4 sent, 4 received, 0% loss" in out and "rtt min/avg/max" in out, out
+        srv.wait(timeout=20)
+    finally:
+        if srv.poll() is None:
+            srv.kill()
+
+
 def test_urma_admin(tmp_path):
     rc, out = _run([BIN / "urma_admin", "show"], tmp_path)
     assert rc == 0 and "shm0" in out and "bond0" in out, out
