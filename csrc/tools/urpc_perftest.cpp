@@ -39,11 +39,13 @@ static int fail(const char* w) {
 int main(int argc, char** argv) {
   uint32_t size = 4096, iters = 5000;
   bool selftest = false;
+  int hold_ms = 0;  // keep the process (and its management socket) alive this long after the run
   int server_port = -1, client_port = -1;
   for (int i = 1; i < argc; ++i) {
     if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--selftest")) selftest = true;
+    else if (!strcmp(argv[i], "--hold-ms") && i + 1 < argc) hold_ms = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--server") && i + 1 < argc) server_port = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--client") && i + 1 < argc) client_port = atoi(argv[++i]);
   }
@@ -167,6 +169,17 @@ int main(int argc, char** argv) {
     wr.func_id = 1;
     if (urpc_func_call(ch, &wr, &sync) != URPC_ERR_SESSION_CLOSE) rc = fail("call on a lost channel must fail");
     serve = true;
+  }
+  if (selftest && rc == 0) {
+    char rep[1024];
+    if (urpc_admin_query("stats", rep, sizeof(rep)) <= 0 || !strstr(rep, "calls ") || !strstr(rep, "timeouts "))
+      rc = fail("management report");
+    if (urpc_admin_query("channels", rep, sizeof(rep)) <= 0 || !strstr(rep, "channel ")) rc = fail("channel report");
+  }
+  if (hold_ms > 0) {
+    printf("urpc_perftest: holding\n");
+    fflush(stdout);
+    usleep(hold_ms * 1000);
   }
   urpc_channel_server_detach(ch);
   urpc_channel_destroy(ch);

@@ -17,7 +17,11 @@
 #include <stdlib.h>
 #include <string.h>
 #include <sys/socket.h>
+#include <sys/un.h>
 #include <unistd.h>
+
+#include <algorithm>
+#include <string>
 
 #include <atomic>
 #include <condition_variable>
@@ -94,6 +98,10 @@ struct Global {
   urpc_stats_t stats{};
   ub::PerfHist lat;
   std::mutex stat_mu;
+  int admin_fd = -1;
+  std::string admin_path;
+  std::thread admin_thr;
+  std::atomic<bool> admin_stop{false};
 };
 Global g;
 
@@ -320,6 +328,7 @@ int urpc_init(const urpc_config_t* cfg) {
   g.stop = false;
   g.inited = true;
   if (g.cfg.keepalive_interval_ms) g.ka_thr = std::thread(keepalive_loop);
+  if (const char* p = getenv("URPC_ADMIN_SOCKET")) urpc_admin_start(p);
   return URPC_SUCCESS;
 }
 
@@ -331,6 +340,7 @@ void urpc_uninit(void) {
   }
   if (g.accept_thr.joinable()) g.accept_thr.join();
   if (g.ka_thr.joinable()) g.ka_thr.join();
+  urpc_admin_stop();
   std::lock_guard<std::mutex> l(g.mu);
   if (g.listen_fd >= 0) close(g.listen_fd);
   g.listen_fd = -1;
@@ -632,6 +642,115 @@ int urpc_channel_task_cancel(uint32_t chid, uint32_t req_id) {
   if (!ch) return URPC_ERR_EINVAL;
   std::lock_guard<std::mutex> l(ch->mu);
   return ch->pending.erase(req_id) ? URPC_SUCCESS : URPC_ERR_EINVAL;
+}
+
+// ---------------------------------------------------------------------------------------------- management socket
+static std::string admin_report(const std::string& cmd) {
+  char line[512];
+  std::string r;
+  if (cmd == "version") {
+    r = "urpc 1.0 (umdk_b200), protocol version " + std::to_string((int)urpc_proto::kVersion) + "\n";
+  } else if (cmd == "stats") {
+    urpc_stats_t s{};
+    urpc_stats_get(&s);
+    snprintf(line, sizeof(line),
+             "calls %llu\nresponses %llu\ntimeouts %llu\nerrors %llu\nrequests_served %llu\nkeepalive_sent %llu\n"
+             "keepalive_lost %llu\nbytes_tx %llu\nbytes_rx %llu\n",
+             (unsigned long long)s.calls, (unsigned long long)s.responses, (unsigned long long)s.timeouts,
+             (unsigned long long)s.errors, (unsigned long long)s.requests_served, (unsigned long long)s.keepalive_sent,
+             (unsigned long long)s.keepalive_lost, (unsigned long long)s.bytes_tx, (unsigned long long)s.bytes_rx);
+    r = line;
+  } else if (cmd == "perf") {
+    uint64_t c = 0, avg = 0, p99 = 0;
+    urpc_perf_get(&c, &avg, &p99);
+    snprintf(line, sizeof(line), "call_to_response count %llu avg_ns %llu p99_ns %llu\n", (unsigned long long)c,
+             (unsigned long long)avg, (unsigned long long)p99);
+    r = line;
+  } else if (cmd == "channels") {
+    std::lock_guard<std::mutex> l(g.mu);
+    for (auto& kv : g.channels) {
+      Channel* ch = kv.second;
+      std::lock_guard<std::mutex> cl(ch->mu);
+      snprintf(line, sizeof(line), "channel %u attached %d lost %d pending %zu ready %zu next_req %u\n", ch->id,
+               (int)ch->attached.load(), (int)ch->lost.load(), ch->pending.size(), ch->ready.size(), ch->next_req);
+      r += line;
+    }
+    if (r.empty()) r = "(no channels)\n";
+  } else if (cmd == "sessions") {
+    std::lock_guard<std::mutex> l(g.mu);
+    for (Session* s : g.sessions) {
+      snprintf(line, sizeof(line), "session %u tcp_fd %d queue %llx\n", s->id, s->tcp, (unsigned long long)s->umqh);
+      r += line;
+    }
+    if (r.empty()) r = "(no sessions)\n";
+  } else if (cmd == "funcs") {
+    std::lock_guard<std::mutex> l(g.mu);
+    for (auto& kv : g.funcs) {
+      snprintf(line, sizeof(line), "func 0x%llx\n", (unsigned long long)kv.first);
+      r += line;
+    }
+    if (r.empty()) r = "(no functions)\n";
+  } else {
+    r = "unknown command; try: version stats perf channels sessions funcs\n";
+  }
+  return r;
+}
+
+static void admin_loop() {
+  while (!g.admin_stop.load()) {
+    pollfd pf{g.admin_fd, POLLIN, 0};
+    if (poll(&pf, 1, 100) <= 0) continue;
+    const int c = accept(g.admin_fd, nullptr, nullptr);
+    if (c < 0) continue;
+    char buf[128] = {0};
+    pollfd pc{c, POLLIN, 0};
+    if (poll(&pc, 1, 1000) > 0) {
+      const ssize_t n = read(c, buf, sizeof(buf) - 1);
+      if (n > 0) {
+        std::string cmd(buf, n);
+        while (!cmd.empty() && (cmd.back() == '\n' || cmd.back() == '\r' || cmd.back() == ' ')) cmd.pop_back();
+        const std::string rep = admin_report(cmd);
+        write_full(c, rep.data(), rep.size());
+      }
+    }
+    close(c);
+  }
+}
+
+int urpc_admin_start(const char* path) {
+  if (!path || !*path || strlen(path) >= sizeof(sockaddr_un::sun_path)) return URPC_ERR_EINVAL;
+  if (g.admin_fd >= 0) return URPC_FAIL;
+  const int fd = socket(AF_UNIX, SOCK_STREAM, 0);
+  if (fd < 0) return URPC_FAIL;
+  sockaddr_un a{};
+  a.sun_family = AF_UNIX;
+  snprintf(a.sun_path, sizeof(a.sun_path), "%s", path);
+  unlink(path);
+  if (bind(fd, reinterpret_cast<sockaddr*>(&a), sizeof(a)) != 0 || listen(fd, 4) != 0) {
+    close(fd);
+    return URPC_FAIL;
+  }
+  g.admin_fd = fd;
+  g.admin_path = path;
+  g.admin_stop = false;
+  g.admin_thr = std::thread(admin_loop);
+  return URPC_SUCCESS;
+}
+void urpc_admin_stop(void) {
+  if (g.admin_fd < 0) return;
+  g.admin_stop = true;
+  if (g.admin_thr.joinable()) g.admin_thr.join();
+  close(g.admin_fd);
+  g.admin_fd = -1;
+  unlink(g.admin_path.c_str());
+}
+int urpc_admin_query(const char* command, char* out, uint32_t cap) {
+  if (!command || !out || cap == 0) return URPC_ERR_EINVAL;
+  const std::string rep = admin_report(command);
+  const uint32_t n = std::min<uint32_t>(cap - 1, (uint32_t)rep.size());
+  memcpy(out, rep.data(), n);
+  out[n] = 0;
+  return (int)n;
 }
 
 int urpc_stats_get(urpc_stats_t* out) {

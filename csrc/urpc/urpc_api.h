@@ -101,6 +101,13 @@ typedef struct urpc_stats {
 } urpc_stats_t;
 URPC_EXPORT int urpc_stats_get(urpc_stats_t* out);
 URPC_EXPORT int urpc_perf_get(uint64_t* count, uint64_t* avg_ns, uint64_t* p99_ns); /* call -> response latency */
+/* Management socket: a unix-domain stream socket at `path` that answers one text command per connection
+ * ("version", "stats", "perf", "channels", "sessions", "funcs") with a text report; `urpc_admin` is its client.
+ * Also started by urpc_init when the environment names a path in URPC_ADMIN_SOCKET. */
+URPC_EXPORT int urpc_admin_start(const char* path);
+URPC_EXPORT void urpc_admin_stop(void);
+/* the same reports without a socket; returns the number of bytes written (truncated to cap - 1) or < 0 */
+URPC_EXPORT int urpc_admin_query(const char* command, char* out, uint32_t cap);
 #ifdef __cplusplus
 }
 #endif

@@ -40,6 +40,29 @@ def test_urpc_selftest_timeouts_and_keepalive(tmp_path):
     assert rc == 0 and "urpc_perftest: OK" in out, out
 
 
+def test_urpc_admin_reads_the_management_socket(tmp_path):
+    sock = str(tmp_path / "urpc.sock")
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"), URPC_ADMIN_SOCKET=sock)
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    srv = subprocess.Popen([str(BIN / "urpc_perftest"), "--iters", "500", "--hold-ms", "4000"],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+    try:
+        for line in srv.stdout:
+            if "holding" in line:
+                break
+        rc, out = _run([BIN / "urpc_admin", sock, "stats"], tmp_path)
+        assert rc == 0 and "calls " in out and "bytes_tx " in out, out
+        assert int(out.split("calls ")[1].split()[0]) >= 500
+        rc, out = _run([BIN / "urpc_admin", sock, "version"], tmp_path)
+        assert rc == 0 and "protocol version 1" in out, out
+        rc, out = _run([BIN / "urpc_admin", sock, "channels"], tmp_path)
+        assert rc == 0 and "channel 0 attached 1" in out, out
+        srv.wait(timeout=30)
+    finally:
+        if srv.poll() is None:
+            srv.kill()
+
+
 def test_dlock_selftest_including_recovery(tmp_path):
     rc, out = _run([BIN / "dlock_example", "--selftest", "--iters", "2000"], tmp_path)
     assert rc == 0 and "dlock_example: OK" in out, out
