@@ -17,10 +17,7 @@
 // The reference has no tensor-parallel operator (its TP hooks are compiled out, tpSize = 1 in
 // src/cam/comm_operator/pybind/moe_dispatch_prefill.cpp:55-56); these kernels implement the tensor-parallel part of
 // the serving configuration.
-#include "common.h"
-#include "ep_common.cuh"
-#include "ptx.cuh"
-#include "sync.cuh"
+#include "tp_common.cuh"
 
 namespace umdk {
 namespace {
@@ -29,7 +26,7 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int kStages = 4;
-constexpr int kThreads = 256;
+constexpr int kThreads = kTpThreads;
 constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -37,32 +34,6 @@ constexpr int kEpiBufBytes = 32 * 64 * 2;
 constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 256 + 1024;
 constexpr int kTmemCols = 2 * BN;
-
-struct TpArgs {
-  int mode;
-  int R, rank;
-  int Ts;          // rows per rank shard (multiple of 128)
-  int N, K;        // GEMM N and K seen by this rank
-  int n_copy;      // MODE 0: number of copy CTAs (the first n_copy CTAs of the grid)
-  PeerTable peers;
-  // MODE 0
-  uint64_t x_slot_off[2];   // [Ts, K] bf16 shard of each rank (ping-pong)
-  uint64_t ready_off[2];    // [R] uint64: peer r's shard for this epoch is in place
-  const __nv_bfloat16* x_local;  // this rank's shard [Ts, K]; the copy CTAs place it into the heap slot themselves
-  __nv_bfloat16* xg;        // local gathered activations [R*Ts, K]
-  uint32_t* chunk_done;     // [R] local counters, advanced by n_copy per call and source
-  // MODE 1
-  uint64_t recv_off[2];     // [R src][Ts][N] bf16 on every rank, one per epoch parity (a source may start call
-                            // n+1 while the owner still reduces call n; call n+2 cannot start before that ended)
-  uint64_t arrive_off;      // [R] uint32 counters on every rank, advanced by tiles*4 per call and source
-  __nv_bfloat16* out;       // [Ts, N]
-  uint32_t* ctrl;           // [0] epoch, [1] done counter, [2] copy-CTA counter
-  int* status;
-  // Normal use: 3. Splitting lets several ranks be emulated on one GPU by running each phase for every rank in turn:
-  // MODE 0: 4 = only publish this rank's "shard ready" flags (one CTA), 3 = everything;
-  // MODE 1: 1 = GEMM + push, 2 = wait + reduce. The epoch advances only when bit 1 (value 2) is set.
-  int phase_mask;
-};
 
 __global__ void __launch_bounds__(kThreads, 1)
 tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -111,51 +82,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 
   if (a.mode == 0 && is_copy_cta) {
-    // ---------------------------------------------------------------- copy role (no tensor cores, no TMEM)
-    const size_t shard_vec = (size_t)a.Ts * a.K * 2 / 16;
-    const size_t per_cta = (shard_vec + n_copy - 1) / n_copy;
-    const size_t v0 = (size_t)blockIdx.x * per_cta;
-    const size_t v1 = v0 + per_cta < shard_vec ? v0 + per_cta : shard_vec;
-    {
-      // place this rank's shard into its heap slot; the last copy CTA to finish tells every peer it is in place
-      const int4* from = reinterpret_cast<const int4*>(a.x_local);
-      int4* to = reinterpret_cast<int4*>(a.peers.base[a.rank] + a.x_slot_off[slot]);
-      for (size_t v = v0 + threadIdx.x; v < v1; v += kThreads) to[v] = from[v];
-      if (cta_done_is_last(&a.ctrl[2], n_copy)) {
-        if (threadIdx.x < a.R) {
-          st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.ready_off[slot]) + a.rank, tag);
-        }
-      }
-    }
-    for (int i = 0; i < a.R; ++i) {
-      const int src = (a.rank + i) % a.R;
-      if (threadIdx.x == 0) {
-        const uint64_t* f = reinterpret_cast<const uint64_t*>(a.peers.base[a.rank] + a.ready_off[slot]) + src;
-        if (!wait_flag_ge_sys(f, tag)) {
-          umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_AG_CHUNK, src, (int)epoch);
-          s_ok = 0;
-        }
-      }
-      __syncthreads();
-      if (!s_ok) break;
-      const int4* from = reinterpret_cast<const int4*>(a.peers.base[src] + a.x_slot_off[slot]);
-      int4* to = reinterpret_cast<int4*>(a.xg + (size_t)src * a.Ts * a.K);
-      for (size_t v = v0 + threadIdx.x; v < v1; v += 4 * kThreads) {
-        // four independent 16-byte loads in flight per thread
-        int4 r0 = ld_relaxed_sys_v4(from + v), r1, r2, r3;
-        const bool h1 = v + kThreads < v1, h2 = v + 2 * kThreads < v1, h3 = v + 3 * kThreads < v1;
-        if (h1) r1 = ld_relaxed_sys_v4(from + v + kThreads);
-        if (h2) r2 = ld_relaxed_sys_v4(from + v + 2 * kThreads);
-        if (h3) r3 = ld_relaxed_sys_v4(from + v + 3 * kThreads);
-        to[v] = r0;
-        if (h1) to[v + kThreads] = r1;
-        if (h2) to[v + 2 * kThreads] = r2;
-        if (h3) to[v + 3 * kThreads] = r3;
-      }
-      __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) red_add_release_gpu(&a.chunk_done[src], 1u);
-    }
+    tp_copy_role(a, n_copy, slot, tag, epoch, &s_ok);
   } else {
     // ---------------------------------------------------------------- GEMM role
     if (threadIdx.x == 0) {
@@ -346,40 +273,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
 
     if (a.mode == 1 && (a.phase_mask & 2)) {
-      // ---- owner-side reduction of the R partial results of this rank's rows ----
-      const uint32_t per_src = (uint32_t)(mb_per_chunk * nb * 4);  // tiles per (source, owner) x 4 epilogue warps
-      if (threadIdx.x < a.R) {
-        const uint32_t* f = reinterpret_cast<const uint32_t*>(a.peers.base[a.rank] + a.arrive_off) + threadIdx.x;
-        if (!wait_flag_ge_sys(f, (uint32_t)tag * per_src)) {
-          umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_RS_CHUNK, threadIdx.x, (int)epoch);
-          s_ok = 0;
-        }
-      }
-      __syncthreads();
-      if (s_ok) {
-        const size_t nvec = (size_t)a.Ts * a.N / 8;
-        const int4* base = reinterpret_cast<const int4*>(a.peers.base[a.rank] + a.recv_off[slot]);
-        for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < nvec; v += (size_t)gridDim.x * kThreads) {
-          float acc[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-          for (int s = 0; s < a.R; ++s) {
-            const int4 val = ld_relaxed_sys_v4(base + (size_t)s * nvec + v);
-            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&val);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = __bfloat1622float2(p[i]);
-              acc[2 * i] += f.x;
-              acc[2 * i + 1] += f.y;
-            }
-          }
-          int4 o;
-          __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-          reinterpret_cast<int4*>(a.out)[v] = o;
-        }
-      }
+      tp_owner_reduce(a, (uint32_t)(mb_per_chunk * nb * 4), slot, tag, epoch, &s_ok);
     }
   }
   if (cta_done_is_last(&a.ctrl[1], gridDim.x)) {
@@ -390,6 +284,9 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }  // namespace
 }  // namespace umdk
 
+namespace umdk {
+int tp_gemm_2sm_launch(const TpArgs& a, const void* A, const void* w, void* out, int grid, cudaStream_t stream);
+}
 using namespace umdk;
 
 struct UmdkTpGemmParams {
@@ -407,6 +304,7 @@ struct UmdkTpGemmParams {
   uint32_t* ctrl;        // [0] epoch, [1] done counter
   int* status;
   int phase_mask;        // 0 = 3 (everything); see TpArgs
+  int impl;              // 0 = CTA pairs where the shape allows (Ts and N multiples of 256), 1 = one CTA per tile
 };
 
 // Symmetric-heap bytes a rank needs: MODE 0 regions (two shards + flags) followed by MODE 1 regions.
@@ -448,8 +346,16 @@ UMDK_API int umdk_tp_gemm(const UmdkTpGemmParams* p, void* stream) {
   a.status = p->status;
   a.phase_mask = p->phase_mask ? p->phase_mask : 3;
   const int M = p->R * p->Ts;
-  CUtensorMap tmA, tmB, tmC;
   const void* A = p->mode == 0 ? p->xg : p->a_local;
+  if (p->impl == 0 && a.phase_mask != 4 && (p->Ts % 256) == 0 && (p->N % 256) == 0) {
+    int grid = sm_count();
+    if (p->max_ctas > 0 && p->max_ctas < grid) grid = p->max_ctas;
+    grid &= ~1;
+    a.n_copy = (a.n_copy + 1) & ~1;   // whole pairs take the copy role
+    if (grid <= a.n_copy + 1) return -UMDK_ERR_BAD_ARG;
+    return tp_gemm_2sm_launch(a, A, p->w, p->out, grid, static_cast<cudaStream_t>(stream));
+  }
+  CUtensorMap tmA, tmB, tmC;
   if (make_tmap_2d(&tmA, TMAP_BF16, A, p->K, M, (uint64_t)p->K * 2, BK, BM, TMAP_SW_128B)) return -UMDK_ERR_BAD_ARG;
   if (make_tmap_2d(&tmB, TMAP_BF16, p->w, p->K, p->N, (uint64_t)p->K * 2, BK, BN, TMAP_SW_128B))
     return -UMDK_ERR_BAD_ARG;

@@ -10,8 +10,10 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-9)).item()
 
 
-@pytest.mark.parametrize("R,Ts,K,N", [(1, 128, 256, 256), (2, 128, 512, 512), (4, 256, 1024, 768)])
-def test_allgather_gemm(R, Ts, K, N):
+# shapes with Ts and N multiples of 256 run on CTA pairs unless single_cta is set; the others always on one CTA per tile
+@pytest.mark.parametrize("single_cta", [False, True])
+@pytest.mark.parametrize("R,Ts,K,N", [(1, 128, 256, 256), (2, 128, 512, 512), (4, 256, 1024, 768), (2, 512, 512, 512)])
+def test_allgather_gemm(R, Ts, K, N, single_cta):
     from umdk_b200.ops.tp import TpComm
     from umdk_b200.parallel.symm import SymmetricHeap
     g = torch.Generator().manual_seed(R)
@@ -19,7 +21,7 @@ def test_allgather_gemm(R, Ts, K, N):
     ws = [(torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda() for _ in range(R)]
     heaps = SymmetricHeap.virtual(TpComm.heap_bytes(R, Ts, K, 256), R)
     try:
-        comms = [TpComm(h, Ts, K, 256, n_copy=4) for h in heaps]
+        comms = [TpComm(h, Ts, K, 256, n_copy=4, single_cta=single_cta) for h in heaps]
         for rnd in range(3):
             for r in range(R):
                 comms[r].ag_gemm(xs[r], ws[r], phase_mask=4)
@@ -35,8 +37,10 @@ def test_allgather_gemm(R, Ts, K, N):
             h.close()
 
 
-@pytest.mark.parametrize("R,Ts,Kr,N", [(1, 128, 128, 256), (2, 128, 256, 512), (4, 128, 512, 256)])
-def test_gemm_reduce_scatter(R, Ts, Kr, N):
+@pytest.mark.parametrize("single_cta", [False, True])
+@pytest.mark.parametrize("R,Ts,Kr,N", [(1, 128, 128, 256), (2, 128, 256, 512), (4, 128, 512, 256), (2, 256, 256, 512),
+                                       (4, 512, 320, 256)])
+def test_gemm_reduce_scatter(R, Ts, Kr, N, single_cta):
     from umdk_b200.ops.tp import TpComm
     from umdk_b200.parallel.symm import SymmetricHeap
     g = torch.Generator().manual_seed(10 + R)
@@ -44,7 +48,7 @@ def test_gemm_reduce_scatter(R, Ts, Kr, N):
     ws = [(torch.randn(N, Kr, generator=g) * 0.05).to(torch.bfloat16).cuda() for _ in range(R)]
     heaps = SymmetricHeap.virtual(TpComm.heap_bytes(R, Ts, 256, N), R)
     try:
-        comms = [TpComm(h, Ts, 256, N) for h in heaps]
+        comms = [TpComm(h, Ts, 256, N, single_cta=single_cta) for h in heaps]
         for rnd in range(3):
             outs = [comms[r].gemm_rs(ys[r], ws[r], phase_mask=1) for r in range(R)]
             for r in range(R):

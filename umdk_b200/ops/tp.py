@@ -23,7 +23,7 @@ class _TpParams(ctypes.Structure):
         ("arrive_off", ctypes.c_uint64),
         ("a_local", ctypes.c_void_p), ("xg", ctypes.c_void_p), ("w", ctypes.c_void_p), ("out", ctypes.c_void_p),
         ("chunk_done", ctypes.c_void_p), ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
-        ("phase_mask", ctypes.c_int),
+        ("phase_mask", ctypes.c_int), ("impl", ctypes.c_int),
     ]
 
 
@@ -49,7 +49,8 @@ class TpComm:
     ``ag_gemm(x_shard [Ts, K], w [N, K]) -> [R*Ts, N]`` and ``gemm_rs(y [R*Ts, Kr], w [N, Kr]) -> [Ts, N]``.
     """
 
-    def __init__(self, heap: SymmetricHeap, ts: int, k_ag: int, n_rs: int, n_copy: int = 16, max_ctas: int = 0):
+    def __init__(self, heap: SymmetricHeap, ts: int, k_ag: int, n_rs: int, n_copy: int = 16, max_ctas: int = 0,
+                 single_cta: bool = False):
         self.lib = _native.cam()
         self.heap, self.R, self.rank = heap, heap.world, heap.rank
         self.Ts, self.K_ag, self.N_rs = ts, k_ag, n_rs
@@ -74,6 +75,8 @@ class TpComm:
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
         self.xg = torch.empty(self.R * ts, k_ag, dtype=torch.bfloat16, device=dev)
         self.n_copy, self.max_ctas = n_copy, max_ctas
+        # False: CTA pairs (256 x 256 tiles) where Ts and N are multiples of 256; True: always one CTA per tile
+        self.single_cta = single_cta
 
     @staticmethod
     def heap_bytes(R: int, ts: int, k_ag: int, n_rs: int) -> int:
@@ -88,6 +91,7 @@ class TpComm:
         p = _TpParams()
         p.mode, p.R, p.rank, p.Ts = mode, self.R, self.rank, self.Ts
         p.n_copy, p.max_ctas = self.n_copy, self.max_ctas
+        p.impl = 1 if self.single_cta else 0
         for i, pp in enumerate(self.heap.peer_ptrs):
             p.peers[i] = pp
         p.x_slot_off[0], p.x_slot_off[1] = self.x_slot
