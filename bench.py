@@ -120,6 +120,8 @@ def main():
     from umdk_b200 import _native
     from umdk_b200.models.dsv3_decoder import DecoderConfig, DecoderRank
 
+    from umdk_b200.utils.affinity import bind_to_gpu
+    cpus = bind_to_gpu(local_rank)   # pinned pools land on the GPU's NUMA node
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -273,6 +275,7 @@ def main():
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
             "gpu_launches": launches,
+            "cpu_affinity": f"{len(cpus)} CPUs local to GPU {local_rank}" if cpus else "unchanged",
             "kv_copies_total": kv_stats["copies"],
         }))
     model.close()

@@ -121,6 +121,58 @@ def bench_mla(B, ctx, topk):
     return report("sparse_mla_decode", med, mn, bytes_, flops, {"B": B, "ctx": ctx, "topk": topk})
 
 
+def bench_moe_fused(experts, tokens, H=7168, F=2048, K=8, tiled=True):
+    """The low-latency MoE layer at EP = 1 (dispatch + fused expert kernel): every token stays on this GPU, so the
+    NVLink stores of the combine epilogue land in local memory."""
+    from umdk_b200.models.dsv3_decoder import _quant_experts
+    from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
+    from umdk_b200.parallel.symm import SymmetricHeap
+    g = torch.Generator(device="cuda").manual_seed(3)
+    K = min(K, experts)
+    x = torch.randn(tokens, H, device="cuda", generator=g).to(torch.bfloat16)
+    p = torch.softmax(torch.randn(tokens, experts, device="cuda", generator=g), dim=-1)
+    w, idx = torch.topk(p, K, dim=-1)
+    w = (w / w.sum(-1, keepdim=True)).float().contiguous()
+    idx = idx.to(torch.int64).contiguous()
+    ew = ExpertWeights(*_quant_experts(experts, 2 * F, H, "cuda", g), *_quant_experts(experts, H, F, "cuda", g))
+    if tiled:
+        ew = ew.to_tiled()
+    heap = SymmetricHeap(EpLowLatency.heap_bytes(1, experts, K, H, tokens))
+    ll = EpLowLatency(heap, experts, K, H, F, tokens)
+    out = torch.empty(tokens, H, dtype=torch.bfloat16, device="cuda")
+    med, mn = time_kernel(lambda: ll.moe(x, idx, w, ew, None, out=out))
+    ll.check("moe_fused")
+    bytes_ = experts * 3 * F * H
+    flops = 2.0 * tokens * K * 3 * F * H
+    r = report("ep_layout + ep_ll_dispatch + moe_fused (EP=1)", med, mn, bytes_, flops,
+               {"experts": experts, "tokens": tokens, "top_k": K, "H": H, "F": F, "tile_major_weights": tiled})
+    heap.close()
+    return r
+
+
+def bench_tp_loopback(Ts, K, N):
+    """Tensor-parallel fused kernels with a single rank: the copy CTAs and the push epilogue run against this GPU's own
+    heap, so this times the kernels' compute path (CTA pairs) without NVLink."""
+    from umdk_b200.ops.tp import TpComm
+    from umdk_b200.parallel.symm import SymmetricHeap
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(Ts, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    heap = SymmetricHeap(TpComm.heap_bytes(1, Ts, K, N))
+    tp = TpComm(heap, Ts, K, N)
+    out = torch.empty(Ts, N, dtype=torch.bfloat16, device="cuda")
+    med, mn = time_kernel(lambda: tp.ag_gemm(x, w, out=out))
+    tp.check()
+    report("tp all-gather->GEMM, 1 rank (CTA pairs)", med, mn, (Ts * K + N * K + Ts * N) * 2, 2.0 * Ts * N * K,
+           {"Ts": Ts, "K": K, "N": N})
+    med, mn = time_kernel(lambda: tp.gemm_rs(x, w, out=out))
+    tp.check()
+    r = report("tp GEMM->reduce-scatter, 1 rank (CTA pairs)", med, mn, (Ts * K + N * K + 3 * Ts * N) * 2,
+               2.0 * Ts * N * K, {"Ts": Ts, "K": K, "N": N})
+    heap.close()
+    return r
+
+
 def bench_kv_gather(B, ctx, topk, num_ctas=8):
     """Row-granular KV prefetch: rows of the offloaded half of every sequence read straight from pinned host memory
     by the gather kernel (PCIe-bound; the HBM columns of the report do not apply)."""
@@ -226,7 +278,7 @@ def bench_quant(T, H):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["moe_gemm1", "moe_gemm2", "mla", "kv_gather", "dispatch", "gemm_bf16", "quant", "all"])
+    ap.add_argument("what", choices=["moe_gemm1", "moe_gemm2", "mla", "kv_gather", "dispatch", "gemm_bf16", "quant", "moe_fused", "tp", "all"])
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--tokens-per-expert", type=int, default=32)
     ap.add_argument("--batch", type=int, default=64)
@@ -243,6 +295,10 @@ def main():
         bench_moe_gemm(2, a.experts, a.tokens_per_expert)
     if a.what in ("mla", "all"):
         bench_mla(a.batch, a.ctx, a.topk)
+    if a.what in ("moe_fused", "all"):
+        bench_moe_fused(a.experts if a.small else 256, 128)
+    if a.what in ("tp", "all"):
+        bench_tp_loopback(2048, 4096, 4096) if a.small else bench_tp_loopback(8192, 8192, 7168)
     if a.what in ("kv_gather", "all"):
         for n in (4, 8, 16, 32):
             bench_kv_gather(a.batch, a.ctx, a.topk, n)

@@ -89,6 +89,115 @@ __device__ __forceinline__ void tp_copy_role(const TpArgs& a, int n_copy, int sl
   }
 }
 
+// Copy role on the bulk-copy engine of the SM (for CTAs that ONLY copy): one thread streams 32 KB pieces
+// peer memory -> shared memory -> local memory with untiled bulk copies, two half-rings of `kCopyHalf` pieces so that
+// the loads of one half are in flight while the other half drains. A handful of CTAs keeps hundreds of KB in flight
+// on NVLink without spending registers or issue slots, so few SMs are taken from the GEMM.
+// `ring`: >= 2 * kCopyHalf * kCopyPiece bytes of shared memory (1024-aligned); `bars`: 2 * kCopyHalf mbarriers.
+constexpr int kCopyPiece = 32768;
+constexpr int kCopyHalf = 3;
+
+struct BulkCopier {
+  uint8_t* ring;
+  uint64_t* bars;
+  uint32_t use[2 * kCopyHalf];   // how often each slot's barrier has completed (parity = use & 1)
+  int* status;
+
+  __device__ __forceinline__ void init(uint8_t* r, uint64_t* b, int* st) {
+    ring = r;
+    bars = b;
+    status = st;
+    for (int i = 0; i < 2 * kCopyHalf; ++i) {
+      use[i] = 0;
+      mbar_init(&bars[i], 1);
+    }
+    mbar_fence_init();
+  }
+  // Copies bytes [b0, b1) of `src` to the same offsets of `dst` (one thread). Returns false on a barrier timeout.
+  __device__ __forceinline__ bool copy(uint8_t* dst, const uint8_t* src, size_t b0, size_t b1) {
+    size_t next = b0;          // next byte to load
+    size_t drain_pos[2] = {0, 0};
+    int drain_cnt[2] = {0, 0};
+    auto issue_half = [&](int h) {
+      drain_pos[h] = next;
+      drain_cnt[h] = 0;
+      for (int i = 0; i < kCopyHalf && next < b1; ++i) {
+        const int s = h * kCopyHalf + i;
+        const uint32_t n = (uint32_t)((b1 - next) < (size_t)kCopyPiece ? (b1 - next) : (size_t)kCopyPiece);
+        mbar_expect_tx(&bars[s], n);
+        bulk_load_1d(ring + (size_t)s * kCopyPiece, src + next, n, &bars[s]);
+        next += n;
+        ++drain_cnt[h];
+      }
+    };
+    issue_half(0);
+    for (int h = 0; drain_cnt[h] > 0; h ^= 1) {
+      issue_half(h ^ 1);   // the other half's earlier stores were waited for at the end of the previous round
+      size_t pos = drain_pos[h];
+      for (int i = 0; i < drain_cnt[h]; ++i) {
+        const int s = h * kCopyHalf + i;
+        if (!mbar_wait(&bars[s], use[s] & 1)) {
+          umdk_set_status(status, UMDK_ERR_TIMEOUT, UMDK_PH_AG_CHUNK, s, (int)(pos >> 10));
+          tma_store_wait<0>();
+          return false;
+        }
+        ++use[s];
+        const uint32_t n = (uint32_t)((b1 - pos) < (size_t)kCopyPiece ? (b1 - pos) : (size_t)kCopyPiece);
+        bulk_store_1d(dst + pos, ring + (size_t)s * kCopyPiece, n);
+        tma_store_commit();
+        pos += n;
+      }
+      tma_store_wait_read<0>();   // this half's shared memory may be overwritten by the next loads
+    }
+    tma_store_wait<0>();          // everything written
+    return true;
+  }
+};
+
+__device__ __forceinline__ void tp_copy_role_bulk(const TpArgs& a, int n_copy, int slot, uint64_t tag, uint32_t epoch,
+                                                  int* s_ok, uint8_t* ring, uint64_t* bars) {
+  const size_t shard_bytes = (size_t)a.Ts * a.K * 2;
+  const size_t npieces = (shard_bytes + kCopyPiece - 1) / kCopyPiece;
+  const size_t per = (npieces + n_copy - 1) / n_copy;
+  size_t b0 = (size_t)blockIdx.x * per * kCopyPiece, b1 = b0 + per * kCopyPiece;
+  if (b0 > shard_bytes) b0 = shard_bytes;
+  if (b1 > shard_bytes) b1 = shard_bytes;
+  __shared__ BulkCopier bc;
+  if (threadIdx.x == 0) {
+    bc.init(ring, bars, a.status);
+    // own shard into its heap slot; the last copy CTA to finish tells every peer that it is in place
+    if (!bc.copy(a.peers.base[a.rank] + a.x_slot_off[slot], reinterpret_cast<const uint8_t*>(a.x_local), b0, b1))
+      *s_ok = 0;
+    fence_proxy_async_all();
+  }
+  if (cta_done_is_last(&a.ctrl[2], n_copy)) {
+    if (threadIdx.x < a.R) {
+      st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.ready_off[slot]) + a.rank, tag);
+    }
+  }
+  for (int i = 0; i < a.R; ++i) {
+    const int src = (a.rank + i) % a.R;
+    if (threadIdx.x == 0) {
+      const uint64_t* f = reinterpret_cast<const uint64_t*>(a.peers.base[a.rank] + a.ready_off[slot]) + src;
+      if (!wait_flag_ge_sys(f, tag)) {
+        umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_AG_CHUNK, src, (int)epoch);
+        *s_ok = 0;
+      }
+      if (*s_ok) {
+        fence_proxy_async_all();   // the flag was read by the generic proxy, the data is read by the bulk engine
+        if (!bc.copy(reinterpret_cast<uint8_t*>(a.xg + (size_t)src * a.Ts * a.K),
+                     a.peers.base[src] + a.x_slot_off[slot], b0, b1))
+          *s_ok = 0;
+        fence_proxy_async_all();
+        __threadfence();
+      }
+    }
+    __syncthreads();
+    if (!*s_ok) break;
+    if (threadIdx.x == 0) red_add_release_gpu(&a.chunk_done[src], 1u);
+  }
+}
+
 // Owner side of MODE 1, run by every CTA after its tiles: wait (bounded) until every source rank has delivered
 // `per_src` epilogue arrivals for this call, then sum the R partial results of the owned rows in fp32.
 __device__ __forceinline__ void tp_owner_reduce(const TpArgs& a, uint32_t per_src, int slot, uint64_t tag,

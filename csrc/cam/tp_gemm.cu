@@ -351,7 +351,8 @@ UMDK_API int umdk_tp_gemm(const UmdkTpGemmParams* p, void* stream) {
     int grid = sm_count();
     if (p->max_ctas > 0 && p->max_ctas < grid) grid = p->max_ctas;
     grid &= ~1;
-    a.n_copy = (a.n_copy + 1) & ~1;   // whole pairs take the copy role
+    // whole pairs take the copy role; the bulk-copy engine needs few of them (default 4 pairs)
+    a.n_copy = p->n_copy > 0 ? ((p->n_copy + 1) & ~1) : 8;
     if (grid <= a.n_copy + 1) return -UMDK_ERR_BAD_ARG;
     return tp_gemm_2sm_launch(a, A, p->w, p->out, grid, static_cast<cudaStream_t>(stream));
   }

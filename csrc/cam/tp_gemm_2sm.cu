@@ -56,7 +56,8 @@ tp_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const bool is_copy_cta = (int)blockIdx.x < n_copy;
 
   if (a.mode == 0 && is_copy_cta) {
-    tp_copy_role(a, n_copy, slot, tag, epoch, &s_ok);
+    // dedicated copy CTAs (whole pairs): the GEMM ring and barrier area serve as the bulk-copy ring
+    tp_copy_role_bulk(a, n_copy, slot, tag, epoch, &s_ok, smem, bars);
   } else {
     const uint32_t cta = cluster_ctarank();
     const int pair = ((int)blockIdx.x - n_copy) >> 1;
@@ -88,12 +89,19 @@ tp_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // tile t -> chunk i = t / tiles_per_chunk (source / owner rank (rank + shift + i) % R; MODE 0 starts with the own
     // shard, MODE 1 ends with the own rows), 256-row block and 256-column block inside the chunk
     const int tiles_per_chunk = mb_per_chunk * nb;
+    // inside a chunk, groups of kGroupM row blocks are swept column by column: the ~74 tiles in flight then share
+    // 8 A panels and ~9 B panels, which stay in L2
+    constexpr int kGroupM = 8;
     auto tile_coords = [&](int t, int* m0, int* n0, int* peer) {
       const int i = t / tiles_per_chunk, r = t - i * tiles_per_chunk;
       const int p = (a.rank + (a.mode == 0 ? 0 : 1) + i) % a.R;
+      const int per_group = kGroupM * nb;
+      const int g = r / per_group, rg = r - g * per_group;
+      const int gm = min(kGroupM, mb_per_chunk - g * kGroupM);
+      const int mblk = g * kGroupM + rg % gm, nblk = rg / gm;
       *peer = p;
-      *m0 = (p * mb_per_chunk + r % mb_per_chunk) * 2 * BMH + (int)cta * BMH;   // this CTA's 128 rows
-      *n0 = (r / mb_per_chunk) * BN;
+      *m0 = (p * mb_per_chunk + mblk) * 2 * BMH + (int)cta * BMH;   // this CTA's 128 rows
+      *n0 = nblk * BN;
     };
 
     if (warp == 0) {
@@ -218,23 +226,38 @@ tp_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             buf ^= 1;
           }
         } else {
-          // rows m0 + ew*32 + lane of the full result belong to rank `peer`; local row inside its shard:
-          const int lrow = m0 - peer * a.Ts + ew * 32 + lane;
-          uint8_t* rowp = a.peers.base[peer] + a.recv_off[slot] + (((size_t)a.rank * a.Ts + lrow) * a.N + n0) * 2;
+          // rows m0 + ew*32 .. +31 of the full result belong to rank `peer`. Each 32 x 64 chunk goes through the
+          // warp's swizzled staging buffer so that the stores to the owner are whole 128-byte lines (4 rows per
+          // instruction) instead of 32 scattered 16-byte pieces.
+          const int lrow0 = m0 - peer * a.Ts + ew * 32;
+          uint8_t* tile_base = a.peers.base[peer] + a.recv_off[slot] + (((size_t)a.rank * a.Ts + lrow0) * a.N + n0) * 2;
+          uint8_t* stage = my_epi;
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_x32(t_addr + c * 32, r);
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t r[64];
+            tmem_ld_x32(t_addr + c * 64, r);
+            tmem_ld_x32(t_addr + c * 64 + 32, r + 32);
             tmem_ld_wait();
+            uint8_t* dst = stage + lane * 128;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              int4 o;
-              __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+            for (int j = 0; j < 8; ++j) {
+              uint32_t p[4];
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                po[i] = __floats2bfloat162_rn(__uint_as_float(r[q * 8 + 2 * i]), __uint_as_float(r[q * 8 + 2 * i + 1]));
-              st_na_v4(rowp + c * 64 + q * 16, o);
+              for (int q = 0; q < 4; ++q) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[j * 8 + 2 * q]),
+                                                         __uint_as_float(r[j * 8 + 2 * q + 1]));
+                p[q] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
             }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = i * 4 + (lane >> 3), seg = lane & 7;
+              const int4 v = *reinterpret_cast<const int4*>(stage + row * 128 + ((seg ^ (row & 7)) << 4));
+              st_na_v4(tile_base + (size_t)row * a.N * 2 + c * 128 + seg * 16, v);
+            }
+            __syncwarp();
           }
           __threadfence_system();
           __syncwarp();
