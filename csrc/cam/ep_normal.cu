@@ -145,6 +145,7 @@ struct DispatchArgs {
   uint32_t* ctrl;              // [0] epoch, [1] send-done counter, [2] recv-done counter
   int* status;
   int phase_mask;              // bit0: notify + send, bit1: receive + expand (both for normal use)
+  long long* diag;             // optional [R]: nanoseconds CTA 0 waited for each source rank's data (diagnose mode)
 };
 
 __device__ __forceinline__ uint32_t pack_fp8x4(float a, float b, float c, float d) {
@@ -372,10 +373,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
     const int src = (g.rank + i) % g.R;  // own tokens first (they are already here)
     if (threadIdx.x == 0) {
       const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.data_flag[h]) + src;
+      const long long t0 = a.diag ? (long long)globaltimer_ns() : 0;
       if (!wait_flag_ge_sys(f, tag)) {
         umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_DATA, src, (int)epoch);
         s_ok = 0;
       }
+      if (a.diag && blockIdx.x == 0) a.diag[src] = (long long)globaltimer_ns() - t0;
     }
     __syncthreads();
     if (!s_ok) return;
@@ -479,6 +482,7 @@ struct CombineArgs {
   uint32_t* ctrl;             // [3] epoch, [4] send-done, [5] recv-done
   int* status;
   int phase_mask;
+  long long* diag;            // optional [R]: nanoseconds CTA 0 waited for each source rank's rows
 };
 
 constexpr int kBatch = 8;  // rows whose loads are issued back to back before any of them is consumed
@@ -581,10 +585,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const Combine
   uint8_t* self = a.peers.base[g.rank];
   if (threadIdx.x < g.R) {
     const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.comb_flag[h]) + threadIdx.x;
+    const long long t0 = a.diag ? (long long)globaltimer_ns() : 0;
     if (!wait_flag_ge_sys(f, tag)) {
       umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_COMBINE_DATA, threadIdx.x, (int)epoch);
       s_ok = 0;
     }
+    if (a.diag && blockIdx.x == 0) a.diag[threadIdx.x] = (long long)globaltimer_ns() - t0;
   }
   __syncthreads();
   if (!s_ok) return;
@@ -726,6 +732,7 @@ struct UmdkEpDispatchParams {
   int* counts_host;
   uint32_t* ctrl;
   int* status;
+  long long* diag;   // optional [R] per-source wait times in ns (diagnose mode), else null
 };
 
 UMDK_API int umdk_ep_dispatch(const UmdkEpDispatchParams* p, void* stream) {
@@ -754,6 +761,7 @@ UMDK_API int umdk_ep_dispatch(const UmdkEpDispatchParams* p, void* stream) {
   a.a_cap = p->a_cap;
   a.ctrl = p->ctrl;
   a.status = p->status;
+  a.diag = p->diag;
   a.phase_mask = p->phase_mask ? p->phase_mask : 3;
   int grid = p->num_ctas > 0 ? p->num_ctas : sm_count();
   if (grid > sm_count()) grid = sm_count();  // CTAs wait on peers: the whole grid must be resident
@@ -776,6 +784,7 @@ struct UmdkEpCombineParams {
   void* out;
   uint32_t* ctrl;
   int* status;
+  long long* diag;   // optional [R] per-source wait times in ns (diagnose mode), else null
 };
 
 UMDK_API int umdk_ep_combine(const UmdkEpCombineParams* p, void* stream) {
@@ -797,6 +806,7 @@ UMDK_API int umdk_ep_combine(const UmdkEpCombineParams* p, void* stream) {
   a.apply_weights = p->apply_weights;
   a.ctrl = p->ctrl;
   a.status = p->status;
+  a.diag = p->diag;
   a.phase_mask = p->phase_mask ? p->phase_mask : 3;
   if (p->T > p->cap) return -UMDK_ERR_BAD_ARG;
   int grid = p->num_ctas > 0 ? p->num_ctas : sm_count();

@@ -58,6 +58,14 @@ urma_simple_ep_t* urma_simple_ep_create(urma_context_t* ctx, uint32_t depth, uin
   if (ep->interrupt_mode) urma_rearm_jfc(ep->jfc, false);
   return ep;
 }
+int urma_simple_ep_recover(urma_simple_ep_t* ep) {
+  if (!ep || !ep->jetty) return -1;
+  urma_cr_t cr[16];
+  int flushed = 0, n;
+  while ((n = urma_flush_jetty(ep->jetty, 16, cr)) > 0) flushed += n;
+  if (urma_modify_jetty(ep->jetty, URMA_JETTY_STATE_READY) != URMA_SUCCESS) return -1;
+  return flushed;
+}
 int urma_simple_ep_destroy(urma_simple_ep_t* ep) {
   if (!ep) return -1;
   if (ep->jetty) urma_delete_jetty(ep->jetty);

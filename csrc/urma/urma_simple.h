@@ -25,6 +25,9 @@ URMA_EXPORT void urma_simple_ep_blob(urma_simple_ep_t* ep, uint8_t out[URMA_SIMP
 URMA_EXPORT urma_target_jetty_t* urma_simple_ep_import(urma_context_t* ctx, const uint8_t blob[URMA_SIMPLE_JETTY_BLOB],
                                                        uint32_t token);
 URMA_EXPORT urma_jetty_t* urma_simple_ep_jetty(urma_simple_ep_t* ep);
+/* After an error completion the jetty is in the ERROR state and refuses new work requests: drain what is left and
+ * put it back to READY. Returns the number of flushed work requests or < 0. */
+URMA_EXPORT int urma_simple_ep_recover(urma_simple_ep_t* ep);
 URMA_EXPORT urma_jfc_t* urma_simple_ep_jfc(urma_simple_ep_t* ep);
 
 URMA_EXPORT urma_target_seg_t* urma_simple_seg_register(urma_context_t* ctx, void* va, uint64_t len, uint32_t access,

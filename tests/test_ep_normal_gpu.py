@@ -128,3 +128,29 @@ def test_dispatch_combine_virtual_ranks(R, T, H, E, K, quant):
     finally:
         for h in heaps:
             h.close()
+
+
+def test_diagnose_mode_records_wait_times():
+    """With diagnose on, dispatch and combine fill one wait time per source rank (non-negative, small on one GPU)."""
+    from umdk_b200.ops.ep import EpNormal
+    from umdk_b200.parallel.symm import SymmetricHeap
+    R, T, H, E, K = 1, 64, 512, 8, 2
+    heap = SymmetricHeap(EpNormal.heap_bytes(R, E, K, H, T))
+    try:
+        st = EpNormal(heap, E, K, H, T)
+        st.diagnose = True
+        st.diag_dispatch.fill_(-1)
+        st.diag_combine.fill_(-1)
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+        idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int64).cuda()
+        w = torch.full((T, K), 0.5).cuda()
+        d = st.dispatch(x, idx, w, quant=False, sync_counts=True)
+        y = d.recv_x[:d.num_recv].view(torch.bfloat16).reshape(d.num_recv, H).contiguous()
+        out = st.combine(y, d)
+        torch.cuda.synchronize()
+        wd, wc = st.wait_times_us()
+        assert (wd >= 0).all() and (wc >= 0).all() and float(wd.max()) < 1e6
+        assert ref.mean_rel_err(out.float().cpu(), x.float().cpu()) < 1e-2
+    finally:
+        heap.close()

@@ -31,7 +31,7 @@ class _DispatchParams(ctypes.Structure):
         ("recv_x", ctypes.c_void_p), ("recv_scales", ctypes.c_void_p), ("expand_idx", ctypes.c_void_p),
         ("recv_count", ctypes.c_void_p), ("recv_per_expert", ctypes.c_void_p), ("recv_meta", ctypes.c_void_p),
         ("counts_dev", ctypes.c_void_p), ("counts_host", ctypes.c_void_p),
-        ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p), ("diag", ctypes.c_void_p),
     ]
 
 
@@ -45,6 +45,7 @@ class _CombineParams(ctypes.Structure):
         ("y", ctypes.c_void_p), ("recv_meta", ctypes.c_void_p), ("counts_dev", ctypes.c_void_p),
         ("src_idx", ctypes.c_void_p), ("in_rank", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p),
         ("topk_w", ctypes.c_void_p), ("out", ctypes.c_void_p), ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("diag", ctypes.c_void_p),
     ]
 
 
@@ -140,6 +141,16 @@ class EpNormal:
         self.layout_bar = torch.zeros(2, dtype=torch.int32, device=dev)
         self.layout_scratch = torch.empty(((cap + 31) // 32) * (num_experts + self.R), dtype=torch.int32, device=dev)
         self.mirror = HostMirror(8)
+        # diagnose mode: the kernels record how long (ns) this rank waited for each source rank's data; gather the
+        # rows of all ranks into a matrix and pass it to examples/utils.py:diagnose_matrix to find a slow rank or link
+        # (the reference's in-kernel wait statistics: moe_dispatch_normal.h:489-529, moe_combine_normal.h:259-280)
+        self.diagnose = False
+        self.diag_dispatch = torch.zeros(self.R, dtype=torch.int64, device=dev)
+        self.diag_combine = torch.zeros(self.R, dtype=torch.int64, device=dev)
+
+    def wait_times_us(self):
+        """(dispatch, combine) wait time per source rank in microseconds from the last diagnosed calls."""
+        return self.diag_dispatch.double().cpu() / 1e3, self.diag_combine.double().cpu() / 1e3
 
     @staticmethod
     def heap_bytes(R: int, E: int, K: int, H: int, cap: int) -> int:
@@ -197,6 +208,7 @@ class EpNormal:
         p.recv_per_expert, p.recv_meta = out.recv_tokens_per_expert.data_ptr(), out.recv_meta.data_ptr()
         p.counts_dev, p.counts_host = out.counts.data_ptr(), self.mirror.dev_ptr
         p.ctrl, p.status = self.ctrl.data_ptr(), self.status.data_ptr()
+        p.diag = self.diag_dispatch.data_ptr() if self.diagnose else None
         rc = self.lib.umdk_ep_dispatch(ctypes.byref(p), _native.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"umdk_ep_dispatch failed: {rc}")
@@ -222,6 +234,7 @@ class EpNormal:
         p.y, p.recv_meta, p.counts_dev = y.data_ptr(), disp.recv_meta.data_ptr(), disp.counts.data_ptr()
         p.in_rank = disp.layout.is_token_in_rank.data_ptr()
         p.out, p.ctrl, p.status = out.data_ptr(), self.ctrl.data_ptr(), self.status.data_ptr()
+        p.diag = self.diag_combine.data_ptr() if self.diagnose else None
         rc = self.lib.umdk_ep_combine(ctypes.byref(p), _native.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"umdk_ep_combine failed: {rc}")
@@ -243,6 +256,7 @@ class EpNormal:
         p.y, p.src_idx = y.data_ptr(), src_idx.data_ptr()
         p.topk_idx, p.topk_w = topk_idx.data_ptr(), topk_weights.data_ptr()
         p.out, p.ctrl, p.status = out.data_ptr(), self.ctrl.data_ptr(), self.status.data_ptr()
+        p.diag = self.diag_combine.data_ptr() if self.diagnose else None
         rc = self.lib.umdk_ep_combine(ctypes.byref(p), _native.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"umdk_ep_combine failed: {rc}")

@@ -165,6 +165,14 @@ class Endpoint:
                 raise UrmaError(f"completion with error status {bad[0].status}")
         return out
 
+    def recover(self) -> int:
+        """An error completion leaves the jetty in the ERROR state (new posts are refused): flush what is queued and
+        return it to READY. Returns the number of flushed work requests."""
+        n = self.lib.urma_simple_ep_recover(self.handle)
+        if n < 0:
+            raise UrmaError("cannot recover the endpoint")
+        return n
+
     def _collect(self, fn, max_n):
         st = (ctypes.c_int * max_n)()
         uc = (ctypes.c_uint64 * max_n)()
