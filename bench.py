@@ -34,62 +34,115 @@ REFERENCE_UNAVAILABLE = ("reference is Ascend-only (AscendC kernels built with C
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons of one GPU every 200 ms while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs: NVML (read-only queries) from
+    a thread every 10 ms, or `nvidia-smi -lms 50` if the NVML binding is missing."""
 
+    REASONS = ((0x4, "sw_power_cap"), (0x8, "hw_slowdown"), (0x20, "sw_thermal_slowdown"),
+               (0x40, "hw_thermal_slowdown"))
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
-        self.rows = []
-        self._proc = None
+        self.gpu = self._physical_index(gpu_index)
+        self.sm, self.mx, self.reasons, self.power = [], None, set(), []
+        self._stop = threading.Event()
         self._thread = None
+        self._proc = None
+        self._how = None
+
+    @staticmethod
+    def _physical_index(i: int) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if i < len(ids) and ids[i].isdigit():
+                return int(ids[i])
+        return i
 
     def start(self):
         try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.mx = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+            self._how = "nvml"
+            self._thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._how = None
+        try:
             self._proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._how = "nvidia-smi"
+            self._thread = threading.Thread(target=self._read_smi, daemon=True)
+            self._thread.start()
         except OSError:
             self._proc = None
-            return
-        self._thread = threading.Thread(target=self._read, daemon=True)
-        self._thread.start()
 
-    def _read(self):
+    def _poll_nvml(self):
+        n = self._nvml
+        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM)))
+                self.power.append(n.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
+                if get_reasons is not None:
+                    mask = int(get_reasons(self._h))
+                    for bit, name in self.REASONS:
+                        if mask & bit:
+                            self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.01)
+
+    def _read_smi(self):
         for line in self._proc.stdout:
             parts = [p.strip() for p in line.strip().split(",")]
-            if len(parts) >= 8:
-                self.rows.append(parts)
-
-    def stop(self) -> dict:
-        if self._proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self._proc.terminate()
-        try:
-            self._proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self._proc.kill()
-        sm, mx, reasons = [], None, set()
-        for r in self.rows:
+            if len(parts) < 8:
+                continue
             try:
-                sm.append(float(r[0]))
-                mx = float(r[1])
+                self.sm.append(float(parts[0]))
+                self.mx = float(parts[1])
+                self.power.append(float(parts[2]))
             except ValueError:
                 continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                               parts[4:8]):
                 if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                    self.reasons.add(name)
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        if self._how == "nvml":
+            try:
+                self._nvml.nvmlShutdown()
+            except Exception:
+                pass
+        if self._how is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML binding and no nvidia-smi"]}
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.mx,
+                "reasons": sorted(self.reasons), "samples": len(self.sm),
+                "power_w": statistics.median(self.power) if self.power else None, "source": self._how}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=8)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="umdk", choices=["umdk", "reference"])
     ap.add_argument("--config", default="full", choices=["full", "tiny"])
     ap.add_argument("--no-offload", action="store_true", help="keep the whole KV cache on the device (not the "

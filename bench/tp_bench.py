@@ -80,7 +80,7 @@ def bench_allreduce(rank, world, a):
     from umdk_b200.ops.tp import AllReduce
     from umdk_b200.parallel.symm import SymmetricHeap
     max_bytes = a.max_bytes
-    nbytes = AllReduce.heap_bytes(max_bytes, world)
+    nbytes = AllReduce.heap_bytes(2 * max_bytes, world)   # the store-only variant stages into a second message-size area
     heap, nvls = None, False
     if world > 1 and not a.no_nvls:
         try:
@@ -91,7 +91,7 @@ def bench_allreduce(rank, world, a):
                 print(f"# NVLS heap unavailable ({e}); using CUDA IPC heap", flush=True)
     if heap is None:
         heap = SymmetricHeap(nbytes, None) if world > 1 else SymmetricHeap(nbytes)
-    ar = AllReduce(heap, max_bytes)
+    ar = AllReduce(heap, 2 * max_bytes)
     size = 1024
     while size <= max_bytes:
         n = max(size // 2, 8 * world)
@@ -104,6 +104,8 @@ def bench_allreduce(rank, world, a):
             if algo == "one_shot" and size > (8 << 20):
                 continue
             res[algo] = timed(lambda: ar(x, out=out, algo=algo), iters, a.warmup, world)
+        if size >= (256 << 10):
+            res["push"] = timed(lambda: ar(x, out=out, algo="push"), iters, a.warmup, world)
         if nvls:
             res["nvls"] = timed(lambda: ar(x, out=out, algo="nvls"), iters, a.warmup, world)
             # caller keeps its tensor in the symmetric heap: no copy in, no copy out
@@ -114,7 +116,7 @@ def bench_allreduce(rank, world, a):
         bus = lambda t: 2.0 * (world - 1) / world * n * 2 / t / 1e9
         emit(rank, {"config": "allreduce", "n_gpus": world, "bytes": n * 2, "impl": "umdk_b200", "best_algo": best,
                     "us": res[best] * 1e6, "us_one_shot": res.get("one_shot", 0) * 1e6 or None,
-                    "us_two_shot": res["two_shot"] * 1e6, "us_nvls": res.get("nvls", 0) * 1e6 or None,
+                    "us_two_shot": res["two_shot"] * 1e6, "us_push": res.get("push", 0) * 1e6 or None, "us_nvls": res.get("nvls", 0) * 1e6 or None,
                     "us_nvls_in_place": res.get("nvls_in_place", 0) * 1e6 or None, "bus_GBps": bus(res[best]),
                     "nccl_us": tb * 1e6, "nccl_bus_GBps": bus(tb), "speedup_vs_nccl": tb / res[best]})
         size *= 4

@@ -14,7 +14,8 @@ namespace {
 constexpr int kArThreads = 512;
 
 struct ArArgs {
-  int R, rank, algo;       // algo 0 = one-shot, 1 = two-shot, 2 = NVLS (multimem reduce + broadcast in NVSwitch)
+  int R, rank, algo;       // algo 0 = one-shot, 1 = two-shot (peer loads), 2 = NVLS (multimem reduce + broadcast in
+                           // NVSwitch), 3 = two-shot with peer STORES only (reduce-scatter push, all-gather push)
   uint8_t* mc_base;        // multicast alias of the heap (algo 2)
   int in_place;            // input already sits in the heap buffer and the result stays there (no copies)
   PeerTable peers;
@@ -116,6 +117,101 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
   const size_t nthreads = (size_t)gridDim.x * kArThreads;
   int4* mine = reinterpret_cast<int4*>(a.peers.base[a.rank] + a.buf_off[slot]);
 
+  if (a.algo == 3) {
+    // Push variant: every byte that crosses NVLink is a store (posted, no round trip), the way ring / tree
+    // libraries move data. Buffer of this parity on every rank: [0, n) gathered result, [n, 2n) staging with one
+    // slot of n / R elements per source rank.
+    const size_t per = nvec / a.R;
+    const size_t lo = per * a.rank;
+    const int4* src = reinterpret_cast<const int4*>(a.in);
+    __shared__ int s_ok3;
+    if (threadIdx.x == 0) s_ok3 = 1;
+    __syncthreads();
+    // phase bits: 1 = push contributions, 2 = reduce own slice + push result, 4 = copy out + finish (normal: all)
+    const int pm = a.phase_mask;
+    if (pm & 1) {
+      if (epoch >= 2) {   // peers wrote nothing here since call e-2; they must also have finished READING it
+        if (threadIdx.x < a.R) {
+          const uint64_t* f =
+              reinterpret_cast<const uint64_t*>(a.peers.base[a.rank] + a.flag_off) + 2 * a.R + threadIdx.x;
+          if (!wait_flag_ge_sys(f, (uint64_t)epoch - 1)) {
+            umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_ALLREDUCE, 3, threadIdx.x);
+            s_ok3 = 0;
+          }
+        }
+        __syncthreads();
+        if (!s_ok3) return;
+      }
+      // reduce-scatter push: my contribution to slice p goes into peer p's staging slot [rank]
+      for (int i = 1; i < a.R; ++i) {
+        const int p = (a.rank + i) % a.R;
+        int4* dst = reinterpret_cast<int4*>(a.peers.base[p] + a.buf_off[slot]) + nvec + per * a.rank;
+        const int4* from = src + per * p;
+        for (size_t v0 = tid; v0 < per; v0 += 4 * nthreads) {
+          int4 r[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v0 + u * nthreads < per) r[u] = __ldg(from + v0 + u * nthreads);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v0 + u * nthreads < per) st_na_v4(dst + v0 + u * nthreads, r[u]);
+        }
+      }
+    }
+    if ((pm & 3) && !rank_barrier(a, 0, tag, &a.ctrl[1], pm & 1, pm & 2)) return;
+    // reduce my slice (own input + R-1 staged contributions), keep it, and push it to every peer's result area
+    if (pm & 2) {
+      const int4* stage = mine + nvec;
+      int4* out4 = reinterpret_cast<int4*>(a.out);
+      for (size_t v = tid; v < per; v += nthreads) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        int4 vals[8];
+        vals[0] = __ldg(src + lo + v);
+        acc8(acc, vals[0]);
+        for (int i0 = 1; i0 < a.R; i0 += 8) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (i0 + u < a.R) vals[u] = stage[per * ((a.rank + i0 + u) % a.R) + v];
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (i0 + u < a.R) acc8(acc, vals[u]);
+          }
+        }
+        const int4 r = pack8(acc);
+        out4[lo + v] = r;
+        for (int i = 1; i < a.R; ++i) {
+          const int p = (a.rank + i) % a.R;
+          st_na_v4(reinterpret_cast<int4*>(a.peers.base[p] + a.buf_off[slot]) + lo + v, r);
+        }
+      }
+    }
+    if ((pm & 6) && !rank_barrier(a, 1, tag, &a.ctrl[1], pm & 2, pm & 4)) return;
+    if (!(pm & 4)) return;
+    // the other ranks' slices have landed in my result area: local copy into the output
+    {
+      int4* out4 = reinterpret_cast<int4*>(a.out);
+      for (int i = 1; i < a.R; ++i) {
+        const size_t off = per * ((a.rank + i) % a.R);
+        for (size_t v0 = tid; v0 < per; v0 += 4 * nthreads) {
+          int4 r[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v0 + u * nthreads < per) r[u] = mine[off + v0 + u * nthreads];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v0 + u * nthreads < per) out4[off + v0 + u * nthreads] = r[u];
+        }
+      }
+    }
+    rank_barrier(a, 2, tag, &a.ctrl[1], true, false);
+    if (gridDim.x == 1) {
+      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+    } else if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
+      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+    }
+    return;
+  }
   if ((a.phase_mask & 1) && !a.in_place) {
     // this buffer parity was last used two calls ago: every peer must have finished reading it
     if (epoch >= 2) {
@@ -222,6 +318,7 @@ struct UmdkAllreduceParams {
   int* status;
   void* mc_base;
   int in_place;
+  unsigned long long buf_bytes;   // size of each parity buffer (algo 3 needs 2 * n * 2 bytes of it)
 };
 
 UMDK_API long long umdk_allreduce_heap_bytes(unsigned long long max_bytes, int R) {
@@ -243,10 +340,12 @@ UMDK_API int umdk_allreduce(const UmdkAllreduceParams* p, void* stream) {
   a.n = p->n;
   a.ctrl = p->ctrl;
   a.status = p->status;
-  a.phase_mask = p->phase_mask ? p->phase_mask : 3;
+  a.phase_mask = p->phase_mask ? p->phase_mask : (p->algo == 3 ? 7 : 3);
   a.mc_base = static_cast<uint8_t*>(p->mc_base);
   a.in_place = p->in_place;
   if (a.algo == 2 && a.mc_base == nullptr) return -UMDK_ERR_BAD_ARG;
+  if (a.algo == 3 && p->buf_bytes < 4ull * p->n) return -UMDK_ERR_BAD_ARG;
+  if (a.algo < 0 || a.algo > 3) return -UMDK_ERR_BAD_ARG;
   int grid = p->num_ctas;
   if (grid <= 0) {
     const size_t nvec = p->n / 8;

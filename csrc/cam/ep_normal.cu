@@ -485,8 +485,6 @@ struct CombineArgs {
   long long* diag;            // optional [R]: nanoseconds CTA 0 waited for each source rank's rows
 };
 
-constexpr int kBatch = 8;  // rows whose loads are issued back to back before any of them is consumed
-
 __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const CombineArgs a) {
   const EpGeom& g = a.g;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -542,35 +540,54 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const Combine
       __syncwarp();
       int4* dst = reinterpret_cast<int4*>(a.peers.base[dst_rank] + a.off.comb_buf[h] +
                                           ((size_t)dst_tok * g.J + slot_j) * g.H * 2);
-      for (int v0 = 0; v0 < nvec; v0 += 32) {
-        const int v = v0 + lane;
-        float acc[8];
+      // four 512-byte chunks of the row per step and two source rows per batch: eight 16-byte loads per lane are in
+      // flight before the first one is consumed (an arrival has 1.5 rows on average, so the parallelism has to come
+      // from the chunks)
+      for (int v0 = 0; v0 < nvec; v0 += 4 * 32) {
+        float acc[4][8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        if (v < nvec) {
-          for (int base = 0; base < n; base += kBatch) {
-            int4 vals[kBatch];
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-              if (base + u < n)
-                vals[u] = __ldg(reinterpret_cast<const int4*>(a.y + (size_t)s_row[warp][base + u] * g.H) + v);
-            }
+          for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
+        for (int base = 0; base < n; base += 2) {
+          int4 vals[2][4];
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-              if (base + u < n) {
-                const float w2 = s_coef[warp][base + u];
-                float f[8];
-                bf16x8_to_float(vals[u], f);
+          for (int u = 0; u < 2; ++u) {
+            if (base + u < n) {
+              const int4* rowp = reinterpret_cast<const int4*>(a.y + (size_t)s_row[warp][base + u] * g.H);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] = fmaf(w2, f[i], acc[i]);
+              for (int c = 0; c < 4; ++c) {
+                const int v = v0 + c * 32 + lane;
+                if (v < nvec) vals[u][c] = __ldg(rowp + v);
               }
             }
           }
-          int4 o;
-          __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-          st_na_v4(dst + v, o);
+          for (int u = 0; u < 2; ++u) {
+            if (base + u < n) {
+              const float w2 = s_coef[warp][base + u];
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                if (v0 + c * 32 + lane < nvec) {
+                  float f[8];
+                  bf16x8_to_float(vals[u][c], f);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) acc[c][i] = fmaf(w2, f[i], acc[c][i]);
+                }
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int v = v0 + c * 32 + lane;
+          if (v < nvec) {
+            int4 o;
+            __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[c][2 * i], acc[c][2 * i + 1]);
+            st_na_v4(dst + v, o);
+          }
         }
       }
     }
@@ -612,34 +629,52 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const Combine
     }
     __syncwarp();
     const int4* src = reinterpret_cast<const int4*>(self + a.off.comb_buf[h] + (size_t)t * g.J * g.H * 2);
-    for (int v0 = 0; v0 < nvec; v0 += 32) {
-      const int v = v0 + lane;
-      if (v >= nvec) continue;
-      float acc[8];
+    for (int v0 = 0; v0 < nvec; v0 += 2 * 32) {
+      float acc[2][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int base = 0; base < n; base += kBatch) {
-        int4 vals[kBatch];
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
-          if (base + u < n) vals[u] = src[(size_t)s_row[warp][base + u] * nvec + v];
+        for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
+      for (int base = 0; base < n; base += 4) {
+        int4 vals[4][2];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (base + u < n) {
+            const int4* rowp = src + (size_t)s_row[warp][base + u] * nvec;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const int v = v0 + c * 32 + lane;
+              if (v < nvec) vals[u][c] = rowp[v];
+            }
+          }
         }
 #pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
+        for (int u = 0; u < 4; ++u) {
           if (base + u < n) {
-            const float c = s_coef[warp][base + u];
-            float f[8];
-            bf16x8_to_float(vals[u], f);
+            const float cf = s_coef[warp][base + u];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = fmaf(c, f[i], acc[i]);
+            for (int c = 0; c < 2; ++c) {
+              if (v0 + c * 32 + lane < nvec) {
+                float f[8];
+                bf16x8_to_float(vals[u][c], f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[c][i] = fmaf(cf, f[i], acc[c][i]);
+              }
+            }
           }
         }
       }
-      int4 o;
-      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-      reinterpret_cast<int4*>(a.out + (size_t)t * g.H)[v] = o;
+      for (int c = 0; c < 2; ++c) {
+        const int v = v0 + c * 32 + lane;
+        if (v < nvec) {
+          int4 o;
+          __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[c][2 * i], acc[c][2 * i + 1]);
+          reinterpret_cast<int4*>(a.out + (size_t)t * g.H)[v] = o;
+        }
+      }
     }
   }
   if (cta_done_is_last(&a.ctrl[5], gridDim.x)) {

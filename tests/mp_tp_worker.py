@@ -43,9 +43,9 @@ def main():
     n = 1 << 20
     vals = [torch.randn(n, generator=g).to(torch.bfloat16) for _ in range(R)]
     want = sum(v.float() for v in vals)
-    heap = SymmetricHeap(AllReduce.heap_bytes(n * 2, R))
-    ar = AllReduce(heap, n * 2)
-    for algo in ("one_shot", "two_shot", "one_shot", "two_shot", "two_shot"):
+    heap = SymmetricHeap(AllReduce.heap_bytes(n * 4, R))
+    ar = AllReduce(heap, n * 4)
+    for algo in ("one_shot", "two_shot", "push", "one_shot", "push", "push", "two_shot"):
         out = ar(vals[rank].cuda(), algo=algo)
         torch.cuda.synchronize()
         ar.check()

@@ -87,6 +87,31 @@ def test_one_shot_allreduce_virtual_ranks(R, n):
             h.close()
 
 
+@pytest.mark.parametrize("R,n", [(1, 4096), (2, 1 << 16), (4, 1 << 18), (8, 64 * 1024)])
+def test_push_allreduce_virtual_ranks(R, n):
+    """Store-only two-shot: contributions pushed, slices reduced and pushed back, then copied out (three phases)."""
+    from umdk_b200.ops.tp import AllReduce
+    from umdk_b200.parallel.symm import SymmetricHeap
+    g = torch.Generator().manual_seed(n + 1)
+    heaps = SymmetricHeap.virtual(AllReduce.heap_bytes(n * 4, R), R)
+    try:
+        ars = [AllReduce(h, n * 4) for h in heaps]
+        for rnd in range(4):
+            xs = [torch.randn(n, generator=g).to(torch.bfloat16).cuda() for _ in range(R)]
+            outs = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+            for phase in (1, 2, 4):
+                for r in range(R):
+                    ars[r](xs[r], out=outs[r], algo="push", phase_mask=phase)
+            torch.cuda.synchronize()
+            want = sum(x.float() for x in xs)
+            for r in range(R):
+                ars[r].check()
+                assert _rel(outs[r], want) < 1e-2, (rnd, r)
+    finally:
+        for h in heaps:
+            h.close()
+
+
 def test_two_shot_allreduce_single_rank():
     from umdk_b200.ops.tp import AllReduce
     from umdk_b200.parallel.symm import SymmetricHeap

@@ -35,7 +35,7 @@ class _ArParams(ctypes.Structure):
         ("buf_off", ctypes.c_uint64 * 2), ("flag_off", ctypes.c_uint64),
         ("inp", ctypes.c_void_p), ("out", ctypes.c_void_p), ("n", ctypes.c_ulonglong),
         ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
-        ("mc_base", ctypes.c_void_p), ("in_place", ctypes.c_int),
+        ("mc_base", ctypes.c_void_p), ("in_place", ctypes.c_int), ("buf_bytes", ctypes.c_ulonglong),
     ]
 
 
@@ -139,7 +139,10 @@ class TpComm:
 
 
 class AllReduce:
-    """bf16 sum all-reduce through peer loads; ``algo`` 'one_shot', 'two_shot' or 'auto' (by size)."""
+    """bf16 sum all-reduce over NVLink peer memory. ``algo``: 'one_shot' (every rank loads all peers' data),
+    'two_shot' (reduce-scatter + all-gather with peer loads), 'push' (the same two stages with peer STORES only; needs
+    buffers of twice the message size), 'nvls' (multimem reduce / broadcast inside NVSwitch; multicast heap), or
+    'auto' (by size and heap kind)."""
 
     def __init__(self, heap: SymmetricHeap, max_bytes: int):
         self.lib = _native.cam()
@@ -183,7 +186,11 @@ class AllReduce:
         has_mc = getattr(self.heap, "multicast_ptr", 0) != 0
         if algo == "auto":
             algo = "one_shot" if n * 2 <= 512 * 1024 else ("nvls" if has_mc else "two_shot")
-        code = {"one_shot": 0, "two_shot": 1, "nvls": 2}[algo]
+        code = {"one_shot": 0, "two_shot": 1, "nvls": 2, "push": 3}[algo]
+        if code == 3:
+            assert 4 * n <= self.max_bytes, "'push' needs max_bytes >= 2 x the message size"
+            if phase_mask == 3:
+                phase_mask = 7
         p = _ArParams()
         p.R, p.rank, p.algo, p.num_ctas, p.phase_mask = self.R, self.rank, code, num_ctas, phase_mask
         p.mc_base = getattr(self.heap, "multicast_ptr", 0) or None
@@ -196,10 +203,11 @@ class AllReduce:
         p.out = out.data_ptr() if out is not None else None
         p.n = n
         p.ctrl, p.status = self.ctrl.data_ptr(), self.status.data_ptr()
+        p.buf_bytes = _align(self.max_bytes, 1024)
         rc = self.lib.umdk_allreduce(ctypes.byref(p), _native.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"umdk_allreduce failed: {rc}")
-        if phase_mask & 2:
+        if phase_mask & (4 if code == 3 else 2):
             self.calls += 1
         return out
 
