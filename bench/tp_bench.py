@@ -104,6 +104,8 @@ def bench_allreduce(rank, world, a):
             if algo == "one_shot" and size > (8 << 20):
                 continue
             res[algo] = timed(lambda: ar(x, out=out, algo=algo), iters, a.warmup, world)
+        if 2 * n * world <= 2 * max_bytes and size <= (8 << 20):
+            res["one_shot_push"] = timed(lambda: ar(x, out=out, algo="one_shot_push"), iters, a.warmup, world)
         if size >= (256 << 10):
             res["push"] = timed(lambda: ar(x, out=out, algo="push"), iters, a.warmup, world)
         if nvls:
@@ -116,7 +118,7 @@ def bench_allreduce(rank, world, a):
         bus = lambda t: 2.0 * (world - 1) / world * n * 2 / t / 1e9
         emit(rank, {"config": "allreduce", "n_gpus": world, "bytes": n * 2, "impl": "umdk_b200", "best_algo": best,
                     "us": res[best] * 1e6, "us_one_shot": res.get("one_shot", 0) * 1e6 or None,
-                    "us_two_shot": res["two_shot"] * 1e6, "us_push": res.get("push", 0) * 1e6 or None, "us_nvls": res.get("nvls", 0) * 1e6 or None,
+                    "us_two_shot": res["two_shot"] * 1e6, "us_push": res.get("push", 0) * 1e6 or None, "us_one_shot_push": res.get("one_shot_push", 0) * 1e6 or None, "us_nvls": res.get("nvls", 0) * 1e6 or None,
                     "us_nvls_in_place": res.get("nvls_in_place", 0) * 1e6 or None, "bus_GBps": bus(res[best]),
                     "nccl_us": tb * 1e6, "nccl_bus_GBps": bus(tb), "speedup_vs_nccl": tb / res[best]})
         size *= 4

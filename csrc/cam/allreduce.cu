@@ -15,12 +15,14 @@ constexpr int kArThreads = 512;
 
 struct ArArgs {
   int R, rank, algo;       // algo 0 = one-shot, 1 = two-shot (peer loads), 2 = NVLS (multimem reduce + broadcast in
-                           // NVSwitch), 3 = two-shot with peer STORES only (reduce-scatter push, all-gather push)
+                           // NVSwitch), 3 = two-shot with peer STORES only (reduce-scatter push, all-gather push),
+                           // 4 = one-shot with peer stores only (every rank sends its vector to all peers)
   uint8_t* mc_base;        // multicast alias of the heap (algo 2)
   int in_place;            // input already sits in the heap buffer and the result stays there (no copies)
   PeerTable peers;
   uint64_t buf_off[2];     // [max_bytes] per epoch parity
   uint64_t flag_off;       // [3][R] uint64: start / middle / end barriers
+  uint64_t cta_flag_off;   // [kMaxArCtas][R] uint64: per-CTA "slice in place" flags of the multi-CTA one-shot path
   const __nv_bfloat16* in; // local input (copied into the heap buffer by the kernel)
   __nv_bfloat16* out;
   size_t n;                // elements, multiple of 8 * R
@@ -212,6 +214,132 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
     }
     return;
   }
+  if (a.algo == 4) {
+    // One-shot with stores only: CTA c sends its slice of the input to slot [rank] of every peer's buffer (posted
+    // writes, no round trip), raises its per-CTA flag there, waits for the peers' slice-c flags and sums the slots
+    // out of LOCAL memory. Buffer of this parity: R slots of n elements. Latency = one NVLink store + one flag.
+    const size_t per_cta = (nvec + gridDim.x - 1) / gridDim.x;
+    const size_t v_lo = per_cta * blockIdx.x;
+    const size_t v_hi = v_lo + per_cta < nvec ? v_lo + per_cta : nvec;
+    uint64_t* cta_flags = reinterpret_cast<uint64_t*>(a.peers.base[a.rank] + a.cta_flag_off);
+    const int4* src = reinterpret_cast<const int4*>(a.in);
+    __shared__ int s_okp;
+    if (threadIdx.x == 0) s_okp = 1;
+    __syncthreads();
+    if (a.phase_mask & 1) {
+      if (epoch >= 2 && threadIdx.x < a.R) {
+        const uint64_t* f =
+            reinterpret_cast<const uint64_t*>(a.peers.base[a.rank] + a.flag_off) + 2 * a.R + threadIdx.x;
+        if (!wait_flag_ge_sys(f, (uint64_t)epoch - 1)) {
+          umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_ALLREDUCE, 3, threadIdx.x);
+          s_okp = 0;
+        }
+      }
+      __syncthreads();
+      if (!s_okp) return;
+      for (size_t v = v_lo + threadIdx.x; v < v_hi; v += kArThreads) {
+        const int4 val = __ldg(src + v);
+        for (int i = 1; i < a.R; ++i) {
+          const int p = (a.rank + i) % a.R;
+          st_na_v4(reinterpret_cast<int4*>(a.peers.base[p] + a.buf_off[slot]) + nvec * a.rank + v, val);
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x < a.R) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.cta_flag_off) +
+                           (size_t)blockIdx.x * a.R + a.rank,
+                       tag);
+      }
+    }
+    if (!(a.phase_mask & 2)) return;
+    if (threadIdx.x < a.R) {
+      if (!wait_flag_ge_sys(cta_flags + (size_t)blockIdx.x * a.R + threadIdx.x, tag)) {
+        umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_ALLREDUCE, 0, threadIdx.x);
+        s_okp = 0;
+      }
+    }
+    __syncthreads();
+    if (!s_okp) return;
+    int4* dst = reinterpret_cast<int4*>(a.out);
+    for (size_t v = v_lo + threadIdx.x; v < v_hi; v += kArThreads) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      acc8(acc, __ldg(src + v));
+      for (int i0 = 1; i0 < a.R; i0 += 8) {
+        int4 vals[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (i0 + u < a.R) vals[u] = mine[nvec * ((a.rank + i0 + u) % a.R) + v];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (i0 + u < a.R) acc8(acc, vals[u]);
+        }
+      }
+      dst[v] = pack8(acc);
+    }
+    rank_barrier(a, 2, tag, &a.ctrl[1], true, false);
+    if (gridDim.x == 1) {
+      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+    } else if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
+      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+    }
+    return;
+  }
+  if (a.algo == 0 && gridDim.x > 1 && !a.in_place) {
+    // One-shot with several CTAs and NO grid-wide step on the critical path: CTA c owns the contiguous slice c of the
+    // vector on every rank, announces "my slice c is in place" to CTA c of every peer through its own flag word and
+    // waits only for the peers' slice-c flags. (All ranks launch the same grid for the same size.)
+    const size_t per_cta = (nvec + gridDim.x - 1) / gridDim.x;
+    const size_t v_lo = per_cta * blockIdx.x;
+    const size_t v_hi = v_lo + per_cta < nvec ? v_lo + per_cta : nvec;
+    uint64_t* cta_flags = reinterpret_cast<uint64_t*>(a.peers.base[a.rank] + a.cta_flag_off);
+    __shared__ int s_okf;
+    if (threadIdx.x == 0) s_okf = 1;
+    __syncthreads();
+    if (a.phase_mask & 1) {
+      if (epoch >= 2 && threadIdx.x < a.R) {   // buffer reuse: the peers' call e-2 has ended (flag row 2)
+        const uint64_t* f =
+            reinterpret_cast<const uint64_t*>(a.peers.base[a.rank] + a.flag_off) + 2 * a.R + threadIdx.x;
+        if (!wait_flag_ge_sys(f, (uint64_t)epoch - 1)) {
+          umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_ALLREDUCE, 3, threadIdx.x);
+          s_okf = 0;
+        }
+      }
+      __syncthreads();
+      if (!s_okf) return;
+      const int4* src = reinterpret_cast<const int4*>(a.in);
+      for (size_t v = v_lo + threadIdx.x; v < v_hi; v += kArThreads) mine[v] = src[v];
+      __syncthreads();
+      if (threadIdx.x < a.R) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.cta_flag_off) +
+                           (size_t)blockIdx.x * a.R + a.rank,
+                       tag);
+      }
+    }
+    if (!(a.phase_mask & 2)) return;
+    if (threadIdx.x < a.R) {
+      if (!wait_flag_ge_sys(cta_flags + (size_t)blockIdx.x * a.R + threadIdx.x, tag)) {
+        umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_ALLREDUCE, 0, threadIdx.x);
+        s_okf = 0;
+      }
+    }
+    __syncthreads();
+    if (!s_okf) return;
+    int4* dst = reinterpret_cast<int4*>(a.out);
+    for (size_t v = v_lo + threadIdx.x; v < v_hi; v += kArThreads) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      reduce_over_ranks(acc, a.peers, a.buf_off[slot], a.R, a.rank, v);
+      dst[v] = pack8(acc);
+    }
+    // end of call (off the critical path): the last CTA tells the peers that this rank has finished reading
+    rank_barrier(a, 2, tag, &a.ctrl[1], true, false);
+    if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
+      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+    }
+    return;
+  }
   if ((a.phase_mask & 1) && !a.in_place) {
     // this buffer parity was last used two calls ago: every peer must have finished reading it
     if (epoch >= 2) {
@@ -321,8 +449,11 @@ struct UmdkAllreduceParams {
   unsigned long long buf_bytes;   // size of each parity buffer (algo 3 needs 2 * n * 2 bytes of it)
 };
 
+constexpr int kMaxArCtas = 160;
+
 UMDK_API long long umdk_allreduce_heap_bytes(unsigned long long max_bytes, int R) {
-  return (long long)(2 * align_up_u64(max_bytes, 1024) + align_up_u64(3ull * R * 8, 256));
+  return (long long)(2 * align_up_u64(max_bytes, 1024) + align_up_u64(3ull * R * 8, 256) +
+                     align_up_u64((uint64_t)kMaxArCtas * R * 8, 256));
 }
 
 UMDK_API int umdk_allreduce(const UmdkAllreduceParams* p, void* stream) {
@@ -335,6 +466,7 @@ UMDK_API int umdk_allreduce(const UmdkAllreduceParams* p, void* stream) {
   a.buf_off[0] = p->buf_off[0];
   a.buf_off[1] = p->buf_off[1];
   a.flag_off = p->flag_off;
+  a.cta_flag_off = p->flag_off + align_up_u64(3ull * p->R * 8, 256);
   a.in = static_cast<const __nv_bfloat16*>(p->in);
   a.out = static_cast<__nv_bfloat16*>(p->out);
   a.n = p->n;
@@ -345,7 +477,8 @@ UMDK_API int umdk_allreduce(const UmdkAllreduceParams* p, void* stream) {
   a.in_place = p->in_place;
   if (a.algo == 2 && a.mc_base == nullptr) return -UMDK_ERR_BAD_ARG;
   if (a.algo == 3 && p->buf_bytes < 4ull * p->n) return -UMDK_ERR_BAD_ARG;
-  if (a.algo < 0 || a.algo > 3) return -UMDK_ERR_BAD_ARG;
+  if (a.algo == 4 && p->buf_bytes < 2ull * p->n * p->R) return -UMDK_ERR_BAD_ARG;
+  if (a.algo < 0 || a.algo > 4) return -UMDK_ERR_BAD_ARG;
   int grid = p->num_ctas;
   if (grid <= 0) {
     const size_t nvec = p->n / 8;
@@ -353,6 +486,7 @@ UMDK_API int umdk_allreduce(const UmdkAllreduceParams* p, void* stream) {
     if (grid < 1) grid = 1;
   }
   if (grid > sm_count()) grid = sm_count();
+  if (grid > kMaxArCtas) grid = kMaxArCtas;
   allreduce_kernel<<<grid, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   UMDK_CUDA_CHECK(cudaGetLastError());
   return 0;

@@ -1,5 +1,6 @@
 // UMS implementation (see ums.h).
 #include "ums.h"
+#include "ums_shm.h"
 
 #include <arpa/inet.h>
 #include <dlfcn.h>
@@ -21,6 +22,8 @@
 #include <unordered_map>
 
 namespace {
+
+using namespace ums_shm;
 
 // The real libc entry points. When the preload shim is active, plain calls from this library would be interposed by
 // the shim and come straight back here, so the library always goes through RTLD_NEXT.
@@ -57,23 +60,6 @@ const Libc& libc() {
   return l;
 }
 
-constexpr uint32_t kClcMagic = 0x554d5331;  // "UMS1"
-constexpr size_t kRingBytes = 1 << 20;      // per direction
-
-struct Ring {
-  std::atomic<uint64_t> prod;
-  char pad0[56];
-  std::atomic<uint64_t> cons;
-  char pad1[56];
-  std::atomic<uint32_t> closed;  // producer side shut down
-  std::atomic<uint32_t> waiter;  // the consumer is (about to be) asleep on its descriptor: ring the doorbell
-  char pad2[56];
-  char data[kRingBytes];
-};
-struct ConnShm {
-  Ring c2s;  // client -> server
-  Ring s2c;
-};
 struct Clc {
   uint32_t magic;
   uint32_t accept;  // reply: 1 = accelerated, 0 = declined

@@ -159,3 +159,30 @@ def test_ums_preload_accelerates_an_unmodified_python_tcp_program(tmp_path):
     assert rc == 0 and "ECHO_OK" in out, out
     # the shared-memory connection files prove that the data path was taken over
     assert any(p.name.startswith("conn_") or p.name.startswith("listen_") for p in (tmp_path / "ums").iterdir()) or True
+
+
+def test_ums_admin_shows_live_connections(tmp_path):
+    """A preloaded program holds an accelerated connection open while ums_admin inspects the shared directory."""
+    script = tmp_path / "hold.py"
+    script.write_text(
+        "import socket, sys, time, threading\n"
+        "ls = socket.socket(); ls.bind(('127.0.0.1', 0)); ls.listen(4); port = ls.getsockname()[1]\n"
+        "acc = []\n"
+        "t = threading.Thread(target=lambda: acc.append(ls.accept()[0])); t.start()\n"
+        "c = socket.create_connection(('127.0.0.1', port)); t.join(); s = acc[0]\n"
+        "c.sendall(b'x' * 5000); got = b''\n"
+        "while len(got) < 5000: got += s.recv(5000 - len(got))\n"
+        "print('HOLDING', flush=True); time.sleep(4)\n")
+    wrapper = _native.lib_dir().parent / "bin" / "ums_run"
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"), UMS_SHM_DIR=str(tmp_path / "ums"))
+    p = subprocess.Popen([str(wrapper), sys.executable, str(script)], stdout=subprocess.PIPE,
+                         stderr=subprocess.STDOUT, text=True, env=env)
+    try:
+        assert "HOLDING" in p.stdout.readline()
+        rc, out = _run([BIN / "ums_admin", "show", tmp_path / "ums"], tmp_path)
+        assert rc == 0 and "1 listener(s)" in out and "1 connection(s)" in out, out
+        assert "produced 5000  consumed 5000  in flight 0  open" in out, out
+        p.wait(timeout=30)
+    finally:
+        if p.poll() is None:
+            p.kill()

@@ -112,6 +112,29 @@ def test_push_allreduce_virtual_ranks(R, n):
             h.close()
 
 
+@pytest.mark.parametrize("R,n", [(2, 4096), (4, 1 << 16), (8, 1 << 17)])
+def test_one_shot_push_allreduce_virtual_ranks(R, n):
+    from umdk_b200.ops.tp import AllReduce
+    from umdk_b200.parallel.symm import SymmetricHeap
+    g = torch.Generator().manual_seed(n + 2)
+    heaps = SymmetricHeap.virtual(AllReduce.heap_bytes(n * 2 * R, R), R)
+    try:
+        ars = [AllReduce(h, n * 2 * R) for h in heaps]
+        for rnd in range(4):
+            xs = [torch.randn(n, generator=g).to(torch.bfloat16).cuda() for _ in range(R)]
+            outs = [ars[r](xs[r], algo="one_shot_push", phase_mask=1) for r in range(R)]
+            for r in range(R):
+                ars[r](xs[r], out=outs[r], algo="one_shot_push", phase_mask=2)
+            torch.cuda.synchronize()
+            want = sum(x.float() for x in xs)
+            for r in range(R):
+                ars[r].check()
+                assert _rel(outs[r], want) < 1e-2, (rnd, r)
+    finally:
+        for h in heaps:
+            h.close()
+
+
 def test_two_shot_allreduce_single_rank():
     from umdk_b200.ops.tp import AllReduce
     from umdk_b200.parallel.symm import SymmetricHeap

@@ -142,7 +142,8 @@ class AllReduce:
     """bf16 sum all-reduce over NVLink peer memory. ``algo``: 'one_shot' (every rank loads all peers' data),
     'two_shot' (reduce-scatter + all-gather with peer loads), 'push' (the same two stages with peer STORES only; needs
     buffers of twice the message size), 'nvls' (multimem reduce / broadcast inside NVSwitch; multicast heap), or
-    'auto' (by size and heap kind)."""
+    'one_shot_push' (every rank stores its vector into a slot on every peer, then sums locally; needs world x the
+    message size), or 'auto' (by size and heap kind)."""
 
     def __init__(self, heap: SymmetricHeap, max_bytes: int):
         self.lib = _native.cam()
@@ -186,7 +187,9 @@ class AllReduce:
         has_mc = getattr(self.heap, "multicast_ptr", 0) != 0
         if algo == "auto":
             algo = "one_shot" if n * 2 <= 512 * 1024 else ("nvls" if has_mc else "two_shot")
-        code = {"one_shot": 0, "two_shot": 1, "nvls": 2, "push": 3}[algo]
+        code = {"one_shot": 0, "two_shot": 1, "nvls": 2, "push": 3, "one_shot_push": 4}[algo]
+        if code == 4:
+            assert 2 * n * self.R <= self.max_bytes, "'one_shot_push' needs max_bytes >= world x the message size"
         if code == 3:
             assert 4 * n <= self.max_bytes, "'push' needs max_bytes >= 2 x the message size"
             if phase_mask == 3:
