@@ -155,6 +155,27 @@ def bench_ll(rank, world, a):
     t_two = timed(lambda: ll.moe(x, idx, w, experts, None, out=out, fused=False), a.iters, a.warmup, world)
     tiled = experts.to_tiled()
     t_tiled = timed(lambda: ll.moe(x, idx, w, tiled, None, out=out), a.iters, a.warmup, world)
+    # stage breakdown of the same call chain: events between the three launches (stage times include waiting for peers)
+    from umdk_b200.ops.ep import layout as ep_layout
+    stage = torch.zeros(3, dtype=torch.float64, device="cuda")
+    for _ in range(a.iters):
+        _flush.zero_()
+        if world > 1:
+            dist.barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ev[0].record()
+        lay = ep_layout(idx, ll.E, ll.R, ll.layout_scratch, ll.layout_bar, ll.status)
+        ev[1].record()
+        ll.dispatch(x, idx, lay=lay)
+        ev[2].record()
+        ll._fused(tiled, idx, w, out)
+        ev[3].record()
+        torch.cuda.synchronize()
+        stage += torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(3)], dtype=torch.float64, device="cuda")
+    stage /= a.iters
+    if world > 1:
+        dist.all_reduce(stage, op=dist.ReduceOp.MAX)
+    stage_us = [float(v) * 1e3 for v in stage.tolist()]
     del tiled
     ll.check("ll")
     rows = int(ll.group_off[-1].item())
@@ -170,7 +191,8 @@ def bench_ll(rank, world, a):
                     us=t_routed * 1e6, roofline_us=roof * 1e6, frac_of_roofline=roof / t_routed,
                     weight_GBps=w_bytes / t_routed / 1e9))
     emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights (ExpertWeights.to_tiled)",
-                    us=t_tiled * 1e6, frac_of_roofline=roof / t_tiled, weight_GBps=w_bytes / t_tiled / 1e9))
+                    us=t_tiled * 1e6, frac_of_roofline=roof / t_tiled, weight_GBps=w_bytes / t_tiled / 1e9,
+                    stage_us={"ep_layout": stage_us[0], "ep_ll_dispatch": stage_us[1], "moe_fused": stage_us[2]}))
     emit(rank, dict(common, impl="umdk_b200", op="same, expert GEMMs as two launches (moe_gemm mode 0 + mode 2)",
                     us=t_two * 1e6, frac_of_roofline=roof / t_two))
     if world >= 1:

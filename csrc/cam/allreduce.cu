@@ -107,6 +107,26 @@ __device__ bool rank_barrier(const ArArgs& a, int which, uint64_t tag, uint32_t*
   return s_ok_b != 0;
 }
 
+// End of a call: the last CTA of the grid to get here tells every peer that this rank has finished reading their
+// buffers of this parity (flag row 2; the buffers are reused two calls later) and advances the epoch. Being last to
+// arrive also proves that every CTA has read the epoch at kernel start, so one counter serves both purposes.
+__device__ __forceinline__ void finish_call(const ArArgs& a, uint64_t tag, uint32_t epoch) {
+  bool last;
+  if (gridDim.x == 1) {
+    __syncthreads();
+    if (threadIdx.x < a.R) __threadfence_system();
+    last = true;
+  } else {
+    last = cta_done_is_last(&a.ctrl[1], gridDim.x);
+  }
+  if (last) {
+    if (threadIdx.x < a.R) {
+      st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.flag_off) + 2 * a.R + a.rank, tag);
+    }
+    if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+  }
+}
+
 __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a) {
   __shared__ uint32_t s_epoch;
   if (threadIdx.x == 0) s_epoch = a.ctrl[0];
@@ -206,12 +226,7 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
         }
       }
     }
-    rank_barrier(a, 2, tag, &a.ctrl[1], true, false);
-    if (gridDim.x == 1) {
-      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
-    } else if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
-      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
-    }
+    finish_call(a, tag, epoch);
     return;
   }
   if (a.algo == 4) {
@@ -278,12 +293,7 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
       }
       dst[v] = pack8(acc);
     }
-    rank_barrier(a, 2, tag, &a.ctrl[1], true, false);
-    if (gridDim.x == 1) {
-      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
-    } else if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
-      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
-    }
+    finish_call(a, tag, epoch);
     return;
   }
   if (a.algo == 0 && gridDim.x > 1 && !a.in_place) {
@@ -333,11 +343,7 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
       reduce_over_ranks(acc, a.peers, a.buf_off[slot], a.R, a.rank, v);
       dst[v] = pack8(acc);
     }
-    // end of call (off the critical path): the last CTA tells the peers that this rank has finished reading
-    rank_barrier(a, 2, tag, &a.ctrl[1], true, false);
-    if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
-      if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
-    }
+    finish_call(a, tag, epoch);
     return;
   }
   if ((a.phase_mask & 1) && !a.in_place) {
@@ -420,13 +426,7 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_kernel(const ArArgs a
       }
     }
   }
-  // the buffer of this parity is reused two calls later; peers must have finished reading it by then
-  rank_barrier(a, 2, tag, &a.ctrl[1], true, false);
-  if (gridDim.x == 1) {
-    if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
-  } else if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
-    if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
-  }
+  finish_call(a, tag, epoch);
 }
 
 }  // namespace
