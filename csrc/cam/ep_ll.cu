@@ -109,10 +109,23 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
   const int* cnt = reinterpret_cast<const int*>(self + a.off.cnt[0]);  // [src][E]
   // per-expert totals over sources, then exclusive prefix inside each destination rank
   __shared__ int s_tot[1024];
+  // totals over sources and the part that comes from lower-numbered sources (my rows start after theirs); the
+  // loads of eight sources are issued together
+  __shared__ int s_before[1024];
   for (int e = threadIdx.x; e < g.E; e += blockDim.x) {
-    int tot = 0;
-    for (int s = 0; s < g.R; ++s) tot += cnt[(size_t)s * g.E + e];
+    int tot = 0, before = 0;
+    for (int s0 = 0; s0 < g.R; s0 += 8) {
+      int v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = s0 + u < g.R ? __ldcg(cnt + (size_t)(s0 + u) * g.E + e) : 0;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        tot += v[u];
+        if (s0 + u < g.rank) before += v[u];
+      }
+    }
     s_tot[e] = tot;
+    s_before[e] = before;
   }
   __syncthreads();
   // one thread per destination rank walks its experts (E_local steps)
@@ -134,11 +147,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
     }
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < g.E; e += blockDim.x) {
-    int before_me = 0;
-    for (int s = 0; s < g.rank; ++s) before_me += cnt[(size_t)s * g.E + e];
-    s_base[e] += before_me;
-  }
+  for (int e = threadIdx.x; e < g.E; e += blockDim.x) s_base[e] += s_before[e];
   __syncthreads();
 
   const int nblk = g.H / 128;
@@ -166,25 +175,34 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
     }
     __syncwarp();
     const int4* xrow = reinterpret_cast<const int4*>(a.x + (size_t)t * g.H);
-    for (int b0 = 0; b0 < nblk; b0 += 4) {
-      const int blk = b0 + (lane >> 3);
-      const bool active = blk < nblk;
-      float f[16];
-      if (active) {
-        bf16x8_to_float(__ldg(xrow + blk * 16 + (lane & 7) * 2), f);
-        bf16x8_to_float(__ldg(xrow + blk * 16 + (lane & 7) * 2 + 1), f + 8);
-      } else {
+    // four groups of four 1x128 blocks per step: eight 16-byte loads per lane are in flight together
+    for (int b0 = 0; b0 < nblk; b0 += 16) {
+      int4 raw[4][2];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) f[i] = 0.f;
+      for (int u = 0; u < 4; ++u) {
+        const int blk = b0 + 4 * u + (lane >> 3);
+        if (blk < nblk) {
+          raw[u][0] = __ldg(xrow + blk * 16 + (lane & 7) * 2);
+          raw[u][1] = __ldg(xrow + blk * 16 + (lane & 7) * 2 + 1);
+        } else {
+          raw[u][0] = raw[u][1] = make_int4(0, 0, 0, 0);
+        }
       }
-      float scale;
-      const int4 q = quant16(f, &scale);
-      if (active) {
-        for (int k = 0; k < g.K; ++k) {
-          uint8_t* dx = s_dx[warp][k];
-          if (dx == nullptr) continue;
-          st_na_v4(dx + blk * 128 + (lane & 7) * 16, q);
-          if ((lane & 7) == 0) s_ds[warp][k][blk] = scale;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int blk = b0 + 4 * u + (lane >> 3);
+        float f[16];
+        bf16x8_to_float(raw[u][0], f);
+        bf16x8_to_float(raw[u][1], f + 8);
+        float scale;
+        const int4 q = quant16(f, &scale);   // shuffles inside: executed by all lanes
+        if (blk < nblk) {
+          for (int k = 0; k < g.K; ++k) {
+            uint8_t* dx = s_dx[warp][k];
+            if (dx == nullptr) continue;
+            st_na_v4(dx + blk * 128 + (lane & 7) * 16, q);
+            if ((lane & 7) == 0) s_ds[warp][k][blk] = scale;
+          }
         }
       }
     }

@@ -115,6 +115,76 @@ ep_layout_kernel(const int64_t* __restrict__ topk_idx, int T, int K, int E, int 
   }
 }
 
+// Layout for small token counts (decode): ONE CTA, one warp per 32-token chunk, every intermediate in shared memory.
+// Same outputs and the same (token-order) positions as ep_layout_kernel; no global scratch, no grid barrier, so the
+// whole thing costs a few microseconds instead of several dependent global-memory round trips.
+constexpr int kSmallLayoutWarps = 32;
+__global__ void __launch_bounds__(kSmallLayoutWarps * 32)
+ep_layout_small_kernel(const int64_t* __restrict__ topk_idx, int T, int K, int E, int R,
+                       int* __restrict__ num_per_expert, int* __restrict__ num_per_rank,
+                       uint8_t* __restrict__ in_rank, int* __restrict__ send_idx, int* __restrict__ rank_slot) {
+  extern __shared__ int sm_small[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cols = E + R;
+  const int E_local = E / R;
+  const int num_chunks = (T + 31) / 32;          // <= kSmallLayoutWarps
+  int* hist_all = sm_small;                      // [num_chunks][cols]
+  int* stage_all = sm_small + num_chunks * cols; // [num_chunks][32 * K]
+  for (int i = threadIdx.x; i < num_chunks * cols; i += blockDim.x) hist_all[i] = 0;
+  __syncthreads();
+  if (warp < num_chunks) {
+    int* hist = hist_all + warp * cols;
+    int* stage = stage_all + warp * 32 * K;
+    const int t0 = warp * 32;
+    const int nt = min(32, T - t0);
+    for (int i = lane; i < nt * K; i += 32) {
+      long long e = topk_idx[(size_t)t0 * K + i];
+      stage[i] = (e >= 0 && e < E) ? (int)e : -1;
+    }
+    __syncwarp();
+    for (int i = 0; i < nt; ++i) {
+      const int t = t0 + i;
+      const int e = lane < K ? stage[i * K + lane] : -1;
+      const uint32_t rm = __reduce_or_sync(0xffffffffu, e >= 0 ? (1u << (e / E_local)) : 0u);
+      // positions inside the chunk; the chunk base is added below (stage keeps the local position)
+      if (lane < K) stage[i * K + lane] = e >= 0 ? ((atomicAdd(&hist[e], 1) << 12) | e) : -1;
+      if (lane < R) {
+        const bool in = (rm >> lane) & 1u;
+        rank_slot[(size_t)t * R + lane] = in ? atomicAdd(&hist[E + lane], 1) : -1;
+        in_rank[(size_t)t * R + lane] = in ? 1 : 0;
+      }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  // exclusive scan over the chunks, one thread per column
+  for (int col = threadIdx.x; col < cols; col += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < num_chunks; ++c) {
+      const int v = hist_all[c * cols + col];
+      hist_all[c * cols + col] = run;
+      run += v;
+    }
+    if (col < E) num_per_expert[col] = run;
+    else num_per_rank[col - E] = run;
+  }
+  __syncthreads();
+  if (warp < num_chunks) {
+    const int* base = hist_all + warp * cols;
+    const int* stage = stage_all + warp * 32 * K;
+    const int t0 = warp * 32;
+    const int nt = min(32, T - t0);
+    for (int i = lane; i < nt * K; i += 32) {
+      const int v = stage[i];
+      send_idx[(size_t)t0 * K + i] = v >= 0 ? (v >> 12) + base[v & 0xfff] : -1;
+    }
+    for (int i = lane; i < nt * R; i += 32) {
+      const int v = rank_slot[(size_t)t0 * R + i];   // written by this warp above
+      if (v >= 0) rank_slot[(size_t)t0 * R + i] = v + base[E + (i % R)];
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------------------
 // Dispatch
 // ------------------------------------------------------------------------------------------------------------
@@ -734,6 +804,20 @@ UMDK_API int umdk_ep_layout(const int64_t* topk_idx, int T, int K, int E, int R,
     return 0;
   }
   const int chunks = (T + 31) / 32;
+  {
+    // decode-sized inputs: one CTA with everything in shared memory (expert ids must fit the 12-bit packing)
+    const size_t small_smem = sizeof(int) * (size_t)chunks * ((E + R) + 32 * K);
+    if (chunks <= kSmallLayoutWarps && E <= 4096 && small_smem <= 160 * 1024) {
+      if (small_smem > 48 * 1024) {
+        UMDK_CUDA_CHECK(cudaFuncSetAttribute(ep_layout_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)small_smem));
+      }
+      ep_layout_small_kernel<<<1, kSmallLayoutWarps * 32, small_smem, s>>>(topk_idx, T, K, E, R, num_per_expert,
+                                                                           num_per_rank, in_rank, send_idx, rank_slot);
+      UMDK_CUDA_CHECK(cudaGetLastError());
+      return 0;
+    }
+  }
   int grid = (chunks + kLayoutWarps - 1) / kLayoutWarps;
   if (grid > sm_count()) grid = sm_count();
   const size_t smem = sizeof(int) * (size_t)kLayoutWarps * ((E + R) + 32 * kMaxTopk);
