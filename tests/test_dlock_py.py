@@ -1,0 +1,84 @@
+"""Distributed locks through the Python binding: two clients contend for exclusive, shared and fair locks with
+leases, and hammer a shared 64-bit object with fetch-add / compare-and-swap from threads."""
+import os
+import threading
+import time
+
+import pytest
+
+
+@pytest.fixture()
+def service(tmp_path):
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import dlock
+    srv = dlock.Server()
+    a, b = dlock.Client(srv.ip, srv.port), dlock.Client(srv.ip, srv.port)
+    yield dlock, srv, a, b
+    a.close()
+    b.close()
+    srv.stop()
+
+
+def test_exclusive_shared_and_lease(service):
+    dlock, srv, a, b = service
+    la, lb = a.get_lock("L1", dlock.ATOMIC), b.get_lock("L1", dlock.ATOMIC)
+    assert a.trylock(la) is True
+    assert b.trylock(lb) is False                 # held by a
+    with pytest.raises(dlock.DlockError):
+        b.unlock(lb)                              # not the owner
+    a.unlock(la)
+    assert b.trylock(lb) is True
+    b.unlock(lb)
+    # readers share, a writer waits for them
+    ra, rb = a.get_lock("RW1", dlock.RW), b.get_lock("RW1", dlock.RW)
+    assert a.trylock(ra, shared=True) and b.trylock(rb, shared=True)
+    a.unlock(ra)
+    b.unlock(rb)
+    assert b.trylock(rb) is True
+    b.unlock(rb)
+    # a lease that runs out can be taken over
+    assert a.trylock(la, expire_ms=100) is True
+    time.sleep(0.3)
+    assert b.trylock(lb, expire_ms=1000) is True
+    b.unlock(lb)
+    assert srv.stats()["expired_takeover"] >= 1
+
+
+def test_fair_lock_blocks_until_released(service):
+    dlock, srv, a, b = service
+    fa, fb = a.get_lock("F1", dlock.FAIR), b.get_lock("F1", dlock.FAIR)
+    a.lock(fa)
+    got = []
+
+    def waiter():
+        b.lock(fb, timeout_ms=5000)
+        got.append(time.monotonic())
+        b.unlock(fb)
+
+    t = threading.Thread(target=waiter)
+    t.start()
+    time.sleep(0.2)
+    released = time.monotonic()
+    a.unlock(fa)
+    t.join(timeout=10)
+    assert got and got[0] >= released
+
+
+def test_atomic_object_from_two_clients(service):
+    dlock, srv, a, b = service
+    oa = a.atomic_create("counter", 5)
+    ob = b.atomic_get("counter")
+
+    def hammer(cl, oid):
+        for _ in range(2000):
+            cl.atomic_faa(oid, 1)
+
+    ts = [threading.Thread(target=hammer, args=(a, oa)), threading.Thread(target=hammer, args=(b, ob))]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert a.atomic_snapshot(oa) == 5 + 4000
+    assert b.atomic_cas(ob, 4005, 1) == 4005 and a.atomic_snapshot(oa) == 1
+    assert b.atomic_cas(ob, 4005, 2) == 1 and a.atomic_snapshot(oa) == 1

@@ -1,0 +1,200 @@
+"""Python binding of URPC, remote procedure calls over UMQ / URMA (csrc/urpc: liburpc).
+
+One process can serve functions (``serve`` + ``Server.register``; a polling thread executes them) and call them
+through a ``Channel`` (``call`` synchronously, or ``call_async`` + ``poll``). Follows the reference's framework
+API (urpc_func_call / urpc_func_poll / urpc_func_return, keepalive callback, request timeouts;
+src/urpc/include/framework/urpc_framework_api.h).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+import time
+from typing import Callable, Dict, List, Optional, Tuple
+
+from . import _native
+
+ERR_TIMEOUT, ERR_SESSION_CLOSE, ERR_FUNC_NOT_FOUND = -110, -104, -38
+POLL_REQ, POLL_RSP, POLL_ERR, POLL_TIMEOUT = 1, 2, 3, 4
+
+
+class UrpcError(RuntimeError):
+    def __init__(self, what: str, code: int):
+        super().__init__(f"{what}: {code}")
+        self.code = code
+
+
+class _Config(ctypes.Structure):
+    _fields_ = [("role", ctypes.c_int), ("dev_name", ctypes.c_char * 64), ("keepalive_interval_ms", ctypes.c_uint32),
+                ("keepalive_miss_limit", ctypes.c_uint32), ("default_timeout_ms", ctypes.c_uint32)]
+
+
+class _Sge(ctypes.Structure):
+    _fields_ = [("addr", ctypes.c_void_p), ("len", ctypes.c_uint32)]
+
+
+class _CallWr(ctypes.Structure):
+    _fields_ = [("func_id", ctypes.c_uint64), ("args", ctypes.POINTER(_Sge)), ("num_args", ctypes.c_uint32),
+                ("user_ctx", ctypes.c_uint64)]
+
+
+class _CallOpt(ctypes.Structure):
+    _fields_ = [("timeout_ms", ctypes.c_uint32), ("sync", ctypes.c_int), ("rsp_buf", ctypes.c_void_p),
+                ("rsp_buf_len", ctypes.c_uint32), ("rsp_len", ctypes.POINTER(ctypes.c_uint32))]
+
+
+class _PollMsg(ctypes.Structure):
+    _fields_ = [("event", ctypes.c_int), ("func_id", ctypes.c_uint64), ("req_id", ctypes.c_uint32),
+                ("user_ctx", ctypes.c_uint64), ("data", ctypes.c_void_p), ("len", ctypes.c_uint32),
+                ("status", ctypes.c_int), ("priv", ctypes.c_void_p)]
+
+
+class _Stats(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_uint64) for n in ("calls", "responses", "timeouts", "errors", "requests_served",
+                                               "keepalive_sent", "keepalive_lost", "bytes_tx", "bytes_rx")]
+
+
+_FUNC = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p,
+                         ctypes.POINTER(ctypes.c_uint32), ctypes.c_void_p)
+_KA_CB = ctypes.CFUNCTYPE(None, ctypes.c_uint32, ctypes.c_int, ctypes.c_void_p)
+
+_lib_cache = None
+_keep: List[object] = []   # ctypes callbacks must outlive their registration
+
+
+def _lib():
+    global _lib_cache
+    if _lib_cache is None:
+        _lib_cache = ctypes.CDLL(os.path.join(_native.lib_dir(), "libumdk_urpc.so"))
+    return _lib_cache
+
+
+def init(dev: str = "shm0", keepalive_interval_ms: int = 0, keepalive_miss_limit: int = 3,
+         default_timeout_ms: int = 5000) -> None:
+    cfg = _Config()
+    cfg.role, cfg.dev_name = 2, dev.encode()
+    cfg.keepalive_interval_ms, cfg.keepalive_miss_limit = keepalive_interval_ms, keepalive_miss_limit
+    cfg.default_timeout_ms = default_timeout_ms
+    rc = _lib().urpc_init(ctypes.byref(cfg))
+    if rc != 0:
+        raise UrpcError("urpc_init", rc)
+
+
+def uninit() -> None:
+    _lib().urpc_uninit()
+    _keep.clear()
+
+
+def stats() -> dict:
+    s = _Stats()
+    _lib().urpc_stats_get(ctypes.byref(s))
+    return {n: int(getattr(s, n)) for n, _ in _Stats._fields_}
+
+
+def on_keepalive(cb: Callable[[int, bool], None]) -> None:
+    """cb(channel_id, alive) when a peer stops or resumes answering keepalive probes."""
+    c = _KA_CB(lambda chid, alive, _ctx: cb(int(chid), bool(alive)))
+    _keep.append(c)
+    _lib().urpc_keepalive_callback_register(c, None)
+
+
+class Server:
+    """Serves registered functions from a background polling thread."""
+
+    def __init__(self, ip: str = "127.0.0.1", port: int = 0):
+        p = _lib().urpc_server_start(ip.encode(), port)
+        if p <= 0:
+            raise UrpcError("urpc_server_start", p)
+        self.ip, self.port = ip, p
+        self._stop = threading.Event()
+        self.paused = False   # True: requests are left unanswered (to exercise timeouts / keepalive)
+        self._thr = threading.Thread(target=self._loop, daemon=True)
+        self._thr.start()
+
+    def register(self, func_id: int, fn: Callable[[bytes], bytes]) -> None:
+        def handler(args, n, rsp, rsp_len, _ctx):
+            try:
+                out = fn(ctypes.string_at(args, n) if n else b"")
+            except Exception:
+                return -1
+            if len(out) > rsp_len[0]:
+                return -1
+            ctypes.memmove(rsp, out, len(out))
+            rsp_len[0] = len(out)
+            return 0
+        c = _FUNC(handler)
+        _keep.append(c)
+        rc = _lib().urpc_func_register(ctypes.c_uint64(func_id), c, None)
+        if rc != 0:
+            raise UrpcError("urpc_func_register", rc)
+
+    def _loop(self):
+        msgs = (_PollMsg * 16)()
+        lib = _lib()
+        while not self._stop.is_set():
+            if self.paused:
+                time.sleep(0.005)
+                continue
+            n = lib.urpc_server_poll(msgs, 16)
+            for i in range(max(n, 0)):
+                lib.urpc_msg_release(ctypes.byref(msgs[i]))   # registered functions were executed by the library
+            if n <= 0:
+                time.sleep(0.0002)
+
+    def stop(self):
+        self._stop.set()
+        self._thr.join(timeout=2)
+
+
+class Channel:
+    def __init__(self, ip: str, port: int):
+        ch = _lib().urpc_channel_create()
+        if ch < 0:
+            raise UrpcError("urpc_channel_create", ch)
+        self.id = ch
+        rc = _lib().urpc_channel_server_attach(ch, ip.encode(), port)
+        if rc != 0:
+            _lib().urpc_channel_destroy(ch)
+            raise UrpcError("urpc_channel_server_attach", rc)
+
+    def _wr(self, func_id: int, args: bytes, user_ctx: int):
+        buf = ctypes.create_string_buffer(args, len(args)) if args else None
+        sge = _Sge(ctypes.cast(buf, ctypes.c_void_p) if buf else None, len(args))
+        wr = _CallWr(func_id, ctypes.pointer(sge), 1 if args else 0, user_ctx)
+        return wr, (buf, sge)
+
+    def call(self, func_id: int, args: bytes = b"", timeout_ms: int = 0, max_rsp: int = 65536) -> bytes:
+        wr, keep = self._wr(func_id, args, 0)
+        rsp = ctypes.create_string_buffer(max_rsp)
+        n = ctypes.c_uint32(0)
+        opt = _CallOpt(timeout_ms, 1, ctypes.cast(rsp, ctypes.c_void_p), max_rsp, ctypes.pointer(n))
+        rc = _lib().urpc_func_call(self.id, ctypes.byref(wr), ctypes.byref(opt))
+        if rc != 0:
+            raise UrpcError("urpc_func_call", rc)
+        return rsp.raw[:n.value]
+
+    def call_async(self, func_id: int, args: bytes = b"", user_ctx: int = 0, timeout_ms: int = 0) -> int:
+        wr, keep = self._wr(func_id, args, user_ctx)
+        opt = _CallOpt(timeout_ms, 0, None, 0, None)
+        rc = _lib().urpc_func_call(self.id, ctypes.byref(wr), ctypes.byref(opt))
+        if rc < 0:
+            raise UrpcError("urpc_func_call", rc)
+        return rc   # request id
+
+    def poll(self, max_n: int = 16) -> List[Tuple[int, int, int, bytes]]:
+        """[(event, user_ctx, status, payload)] for completed asynchronous calls."""
+        msgs = (_PollMsg * max_n)()
+        n = _lib().urpc_func_poll(self.id, msgs, max_n)
+        out = []
+        for i in range(max(n, 0)):
+            m = msgs[i]
+            out.append((m.event, int(m.user_ctx), m.status, ctypes.string_at(m.data, m.len) if m.data and m.len else b""))
+            _lib().urpc_msg_release(ctypes.byref(m))
+        return out
+
+    def close(self):
+        if self.id >= 0:
+            _lib().urpc_channel_server_detach(self.id)
+            _lib().urpc_channel_destroy(self.id)
+            self.id = -1
