@@ -176,6 +176,19 @@ def bench_ll(rank, world, a):
     if world > 1:
         dist.all_reduce(stage, op=dist.ReduceOp.MAX)
     stage_us = [float(v) * 1e3 for v in stage.tolist()]
+    # the same layer as one CUDA-graph replay: no Python / launch cost between the three kernels
+    t_graph = None
+    try:
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        graph, _ = ll.capture(x, idx, w, tiled, None, out=out)
+        t_graph = timed(graph.replay, a.iters, a.warmup, world)
+        ll.check("ll graph")
+        del graph
+    except Exception as e:  # capture not possible in this environment: report without it
+        if rank == 0:
+            print(f"# CUDA graph capture of the layer failed: {e}", flush=True)
     del tiled
     ll.check("ll")
     rows = int(ll.group_off[-1].item())
@@ -193,6 +206,9 @@ def bench_ll(rank, world, a):
     emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights (ExpertWeights.to_tiled)",
                     us=t_tiled * 1e6, frac_of_roofline=roof / t_tiled, weight_GBps=w_bytes / t_tiled / 1e9,
                     stage_us={"ep_layout": stage_us[0], "ep_ll_dispatch": stage_us[1], "moe_fused": stage_us[2]}))
+    if t_graph is not None:
+        emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights, one CUDA-graph replay per layer",
+                        us=t_graph * 1e6, frac_of_roofline=roof / t_graph, weight_GBps=w_bytes / t_graph / 1e9))
     emit(rank, dict(common, impl="umdk_b200", op="same, expert GEMMs as two launches (moe_gemm mode 0 + mode 2)",
                     us=t_two * 1e6, frac_of_roofline=roof / t_two))
     if world >= 1:

@@ -17,6 +17,7 @@
 #include <deque>
 #include <mutex>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 #include "ub_util.h"
@@ -46,7 +47,19 @@ struct Pool {
   bool inited = false;
 };
 Pool g_pool;
-thread_local std::vector<Block*> t_cache;
+// Per-thread cache of free blocks. A thread that ends hands its cached blocks back to the global pool (a worker
+// thread that polled a queue for a while would otherwise take them with it).
+struct ThreadCache {
+  std::vector<Block*> v;
+  ~ThreadCache();
+};
+thread_local ThreadCache t_cache_holder;
+#define t_cache (t_cache_holder.v)
+ThreadCache::~ThreadCache() {
+  std::lock_guard<std::mutex> l(g_pool.mu);
+  for (Block* b : v) g_pool.free_list.push_back(b);
+  v.clear();
+}
 constexpr size_t kCacheMax = 64;
 
 struct Global {
@@ -85,6 +98,7 @@ struct Queue {
   std::deque<umq_buf_t*> rx_ready;      // received messages not yet dequeued
   std::deque<umq_buf_t*> tx_done;       // sent buffers whose completion arrived (pro API)
   uint32_t rx_posted = 0;
+  std::unordered_set<struct Block*> in_flight;  // blocks owned by the endpoint: posted receives, sends not yet completed
   // flow control
   bool fc = false;
   int64_t credits = 0;          // messages we may still send
@@ -191,6 +205,7 @@ void refill_rx(Queue* q) {
       break;
     }
     ++q->rx_posted;
+    q->in_flight.insert(b);
     if (q->fc) {
       if (q->fc_skip) --q->fc_skip;
       else ++q->to_return;
@@ -221,6 +236,7 @@ void progress(Queue* q) {
       if (flag[i] & URMA_CR_FLAG_RECV) {
         Block* b = reinterpret_cast<Block*>(uc[i]);
         --q->rx_posted;
+        q->in_flight.erase(b);
         const uint64_t type = imm[i] >> 56;
         const uint32_t credits = static_cast<uint32_t>((imm[i] >> 32) & 0xffffff);
         if (credits) {
@@ -241,6 +257,7 @@ void progress(Queue* q) {
         q->io.rx_bytes += len[i];
       } else if (uc[i] != 0) {
         Block* b = reinterpret_cast<Block*>(uc[i]);
+        q->in_flight.erase(b);
         b->meta.status = st[i] == 0 ? UMQ_BUF_OK : UMQ_BUF_SEND_ERR;
         if (st[i] != 0) {
           ++q->io.tx_errors;
@@ -281,6 +298,7 @@ int send_one(Queue* q, umq_buf_t* buf, bool pro) {
     ++q->io.tx_eagain;
     return rc == URMA_EAGAIN ? UMQ_ERR_EAGAIN : UMQ_FAIL;
   }
+  q->in_flight.insert(b);
   if (piggy) {
     q->fcs.credits_returned += piggy;
     q->to_return = 0;
@@ -371,7 +389,9 @@ int umq_destroy(uint64_t h) {
   for (auto* b : q->rx_ready) block_put(reinterpret_cast<Block*>(b));
   for (auto* b : q->tx_done) block_put(reinterpret_cast<Block*>(b));
   if (q->peer) urma_unimport_jetty(q->peer);
-  urma_simple_ep_destroy(q->ep);  // posted receive blocks are reclaimed with the process
+  urma_simple_ep_destroy(q->ep);
+  // the endpoint is gone: nothing can complete into the blocks it still held (posted receives, unfinished sends)
+  for (Block* b : q->in_flight) block_put(b);
   delete q;
   return UMQ_SUCCESS;
 }
@@ -538,6 +558,7 @@ int umq_post(uint64_t h, umq_buf_t* qbuf, umq_io_direction_t dir, umq_buf_t** ba
         return UMQ_ERR_EAGAIN;
       }
       ++q->rx_posted;
+      q->in_flight.insert(blk);
       if (q->fc) ++q->to_return;
       b = nx;
     }

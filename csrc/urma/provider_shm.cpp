@@ -220,6 +220,9 @@ struct ShmCtx {
   std::thread nic;
   std::atomic<bool> stop{false};
   std::mutex mu;  // guards the tables below
+  // Held by the NIC thread while it handles one message (it may touch queues it looked up under `mu` after dropping
+  // `mu`) and by the delete operations while they free a queue: an object is never freed under the NIC thread's feet.
+  std::mutex life_mu;
   std::unordered_map<uint32_t, SegReg> segs;
   std::unordered_map<uint32_t, RecvQueue*> rqs;
   std::unordered_map<uint64_t, Pending> pending;
@@ -602,7 +605,10 @@ void nic_loop(ShmCtx* c) {
     const uint64_t pos = in->deq.load(std::memory_order_relaxed);
     Slot* s = &in->slots[pos & (kRingSlots - 1)];
     if (s->seq.load(std::memory_order_acquire) == pos + 1) {
-      handle(c, s);
+      {
+        std::lock_guard<std::mutex> life(c->life_mu);
+        handle(c, s);
+      }
       in->deq.store(pos + 1, std::memory_order_relaxed);
       s->seq.store(pos + kRingSlots, std::memory_order_release);
       idle = 0;
@@ -641,6 +647,7 @@ urma_jfc_t* op_create_jfc(urma_context_t*, const urma_jfc_cfg_t* cfg) {
 }
 urma_status_t op_modify_jfc(urma_jfc_t*, uint32_t, uint32_t) { return URMA_SUCCESS; }
 urma_status_t op_delete_jfc(urma_jfc_t* jfc) {
+  std::lock_guard<std::mutex> life(C(jfc->ctx)->life_mu);
   delete reinterpret_cast<ShmJfc*>(jfc->priv);
   return URMA_SUCCESS;
 }
@@ -723,6 +730,7 @@ urma_status_t op_delete_jfs(urma_jfs_t* jfs) {
   urma_cr_t tmp[16];
   while (flush_sq(C(jfs->ctx), &j->sq, 16, tmp) == 16) {
   }
+  std::lock_guard<std::mutex> life(C(jfs->ctx)->life_mu);
   delete j;
   return URMA_SUCCESS;
 }
@@ -759,6 +767,7 @@ urma_status_t op_query_jfr(urma_jfr_t* jfr, urma_jfr_cfg_t* cfg, urma_jetty_stat
 urma_status_t op_delete_jfr(urma_jfr_t* jfr) {
   ShmJfr* j = reinterpret_cast<ShmJfr*>(jfr->priv);
   rq_fini(C(jfr->ctx), &j->rq);
+  std::lock_guard<std::mutex> life(C(jfr->ctx)->life_mu);
   delete j;
   return URMA_SUCCESS;
 }
@@ -831,6 +840,7 @@ urma_status_t op_delete_jetty(urma_jetty_t* jt) {
   while (flush_sq(C(jt->ctx), &j->sq, 16, tmp) == 16) {
   }
   if (j->rq == &j->own_rq) rq_fini(C(jt->ctx), &j->own_rq);
+  std::lock_guard<std::mutex> life(C(jt->ctx)->life_mu);
   delete j;
   return URMA_SUCCESS;
 }

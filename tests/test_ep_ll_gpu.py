@@ -168,3 +168,31 @@ def test_low_latency_moe_shared_expert_folded_into_routed_pipeline(R, T, H, F, E
     finally:
         for h in heaps:
             h.close()
+
+
+def test_low_latency_moe_cuda_graph_replay():
+    """The layer captured once and replayed on new inputs gives the same result as direct calls."""
+    from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
+    from umdk_b200.parallel.symm import SymmetricHeap
+    R, T, H, F, E, K = 1, 64, 1024, 512, 8, 4
+    w1q, w1s, w2q, w2s = _weights(E, H, F, seed=17)
+    xs, idxs, ws = _inputs(R, T, H, E, K, seed=6)
+    xs2, idxs2, ws2 = _inputs(R, T, H, E, K, seed=7)
+    heap = SymmetricHeap(EpLowLatency.heap_bytes(R, E, K, H, T))
+    try:
+        st = EpLowLatency(heap, E, K, H, F, T)
+        w = ExpertWeights(w1q.cuda(), w1s.cuda(), w2q.cuda(), w2s.cuda()).to_tiled()
+        x, idx, wt = xs[0].cuda(), idxs[0].cuda(), ws[0].cuda()
+        graph, (out, _, cnt) = st.capture(x, idx, wt, w)
+        for xin, iin, win in ((xs[0], idxs[0], ws[0]), (xs2[0], idxs2[0], ws2[0]), (xs[0], idxs[0], ws[0])):
+            x.copy_(xin)
+            idx.copy_(iin)
+            wt.copy_(win)
+            graph.replay()
+            torch.cuda.synchronize()
+            st.check()
+            want = ref.ref_fused_moe(xin, iin, win, w1q, w1s, w2q, w2s)
+            assert ref.mean_rel_err(out.float().cpu(), want) < 0.02
+            assert int(cnt.sum()) == int((iin >= 0).sum())
+    finally:
+        heap.close()

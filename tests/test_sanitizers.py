@@ -1,0 +1,41 @@
+"""Host libraries under AddressSanitizer / LeakSanitizer and ThreadSanitizer: the sanitizer flavours are built into
+build/lib_<kind>/ and the UMQ and URPC tools run their self-tests there without a single report. (The reference
+ships asan / tsan build configurations for the same purpose; kernels have no such tool on this hardware pool and are
+covered by bounds checks and oracles instead.)"""
+import os
+import shutil
+import subprocess
+
+import pytest
+
+from umdk_b200 import _build
+
+
+def _run(exe, args, tmp_path, extra_env=None):
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"))
+    env.update(extra_env or {})
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    p = subprocess.run([str(exe), *args], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=400,
+                       env=env)
+    return p.returncode, p.stdout
+
+
+needs_gxx = pytest.mark.skipif(not os.path.exists("/usr/bin/g++") and shutil.which("g++") is None,
+                               reason="no host compiler")
+
+
+@needs_gxx
+def test_address_and_leak_sanitizer_clean(tmp_path):
+    outs = _build.build_sanitized("address")
+    rc, out = _run(outs["tool_umq_perftest"], ["--iters", "500", "--flow-control"], tmp_path)
+    assert rc == 0 and "umq_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
+    rc, out = _run(outs["tool_urpc_perftest"], ["--selftest", "--iters", "300"], tmp_path)
+    assert rc == 0 and "urpc_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
+
+
+@needs_gxx
+def test_thread_sanitizer_clean(tmp_path):
+    outs = _build.build_sanitized("thread")
+    for _ in range(2):   # the teardown race this guards against showed up in about one run out of three
+        rc, out = _run(outs["tool_umq_perftest"], ["--iters", "300", "--flow-control"], tmp_path)
+        assert rc == 0 and "umq_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]

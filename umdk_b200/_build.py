@@ -149,12 +149,44 @@ def build_all(force: bool = False, verbose: bool = False, only=None) -> dict:
             if tgt["kind"] == "cuda_shared":
                 cmd = [NVCC, "-shared", "-o", str(out), *map(str, objs[name]), *tgt["libs"]]
             elif tgt["kind"] == "cxx_shared":
-                cmd = [CXX, "-shared", "-o", str(out), *map(str, objs[name]), *tgt["libs"]]
+                cmd = [CXX, "-shared", "-o", str(out), *map(str, objs[name]), *tgt["libs"], *LINK_EXTRA]
             else:
-                cmd = [CXX, "-o", str(out), *map(str, objs[name]), *tgt["libs"]]
+                cmd = [CXX, "-o", str(out), *map(str, objs[name]), *tgt["libs"], *LINK_EXTRA]
             _run(cmd, verbose)
         outs[name] = out
     return outs
+
+
+LINK_EXTRA: list = []
+
+
+HOST_LIBS = ("umdk_urma", "umdk_umq", "umdk_urpc", "umdk_dlock", "umdk_usock")
+
+
+def build_sanitized(kind: str = "address", only=HOST_LIBS + ("tool_umq_perftest", "tool_urpc_perftest")) -> dict:
+    """Host libraries and tools compiled with -fsanitize=<kind> ('address', 'thread' or 'undefined') into
+    build/lib_<kind>/ (objects in build/obj_<kind>/), leaving the normal build untouched. The counterpart of the
+    reference's asan / tsan build flavours (src/urma/.bazelrc:39-50, umdk.spec:2-8). CUDA targets are not built."""
+    global LIB, OBJ, CXX_FLAGS, LINK_EXTRA, CXX
+    assert kind in ("address", "thread", "undefined")
+    saved = (LIB, OBJ, CXX_FLAGS, LINK_EXTRA)
+    saved_cxx = CXX
+    # the distribution compiler carries the sanitizer runtimes; a toolchain named by $CXX may not
+    CXX = os.environ.get("UMDK_SANITIZER_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else CXX)
+    LIB = ROOT / "build" / f"lib_{kind}"
+    OBJ = ROOT / "build" / f"obj_{kind}"
+    CXX_FLAGS = [f for f in CXX_FLAGS if f != "-O2"] + ["-O1", f"-fsanitize={kind}", "-fno-omit-frame-pointer"]
+    # the static runtime goes into the executables (this image ships no shared sanitizer runtimes)
+    LINK_EXTRA = [f"-fsanitize={kind}", {"address": "-static-libasan", "thread": "-static-libtsan",
+                                          "undefined": "-static-libubsan"}[kind]]
+    try:
+        names = [n for n in only if not n.startswith("umdk_cam") and n != "urma_cuda_ipc"]
+        if any(n.startswith("tool_") for n in names):   # the tools link every host library
+            names = list(dict.fromkeys(list(HOST_LIBS) + names))
+        return build_all(only=names)
+    finally:
+        LIB, OBJ, CXX_FLAGS, LINK_EXTRA = saved
+        CXX = saved_cxx
 
 
 def ptxas_report() -> str:
@@ -170,8 +202,13 @@ def main(argv=None):
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--only", nargs="*")
+    ap.add_argument("--sanitize", choices=["address", "thread", "undefined"],
+                    help="build the host libraries / tools named by --only with this sanitizer into build/lib_<kind>")
     a = ap.parse_args(argv)
-    outs = build_all(a.force, a.verbose, a.only)
+    if a.sanitize:
+        outs = build_sanitized(a.sanitize, *([tuple(a.only)] if a.only else []))
+    else:
+        outs = build_all(a.force, a.verbose, a.only)
     for k, v in outs.items():
         print(f"{k}: {v}")
 

@@ -325,5 +325,23 @@ class EpLowLatency:
             self._gemm2_combine(w, topk_idx, topk_w, out)
         return out, share_out, self.recv_per_expert
 
+    def capture(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w: ExpertWeights,
+                shared: Optional[ExpertWeights] = None, out: Optional[torch.Tensor] = None):
+        """Records the whole layer (layout, dispatch, fused expert kernel) into a CUDA graph and returns
+        ``(graph, (combine_x, share_output, expert_token_nums))``. ``graph.replay()`` then re-runs it on the CURRENT
+        contents of ``x`` / ``topk_idx`` / ``topk_w`` with one launch from the host, which takes the Python and
+        driver launch costs of the three kernels off the critical path of a decode step. All epoch / flag state
+        lives in device memory, so replays chain like ordinary calls; every rank must replay the same number of
+        times. Call ``torch.cuda.synchronize()`` (and a barrier across ranks) before capturing."""
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
+        self.moe(x, topk_idx, topk_w, w, shared, out=out)   # first call outside the capture: attribute setup, caches
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            res = self.moe(x, topk_idx, topk_w, w, shared, out=out)
+        return g, res
+
     def check(self, what: str = "ep_ll"):
         check_status(self.status, what)
