@@ -104,6 +104,17 @@ def bench_normal(rank, world, a):
     t_disp = timed(lambda: st.dispatch(x, idx, w, lay=lay, quant=True, out=out), a.iters, a.warmup, world)
     t_comb = timed(lambda: st.combine(y, out, out=res), a.iters, a.warmup, world)
     st.check("normal")
+    # diagnose mode: how long CTA 0 of this rank waited for each source rank's data (max over ranks per source)
+    st.diagnose = True
+    st.dispatch(x, idx, w, lay=lay, quant=True, out=out)
+    st.combine(y, out, out=res)
+    torch.cuda.synchronize()
+    wd, wc = st.wait_times_us()
+    st.diagnose = False
+    waits = torch.stack((wd, wc)).cuda()
+    if world > 1:
+        dist.all_reduce(waits, op=dist.ReduceOp.MAX)
+    waits = waits.cpu()
     row_b = H + H // 32
     wire_d = arrivals * row_b * remote_frac          # each token crosses once per destination rank
     wire_c = arrivals * H * 2 * remote_frac
@@ -117,6 +128,8 @@ def bench_normal(rank, world, a):
     emit(rank, dict(common, op="combine(bf16, top-8 weighted)", us=t_comb * 1e6,
                     recv_GBps=n * H * 2 / t_comb / 1e9, nvlink_GBps=wire_c / t_comb / 1e9,
                     frac_of_nvlink_roofline=(wire_c / (NVLINK_GBS * 1e9)) / t_comb if world > 1 else None))
+    emit(rank, dict(common, op="diagnose: wait per source rank (us, max over ranks)",
+                    dispatch=[round(float(v), 1) for v in waits[0]], combine=[round(float(v), 1) for v in waits[1]]))
     if world > 1:
         base = NcclEp(None, E)
         recv, h = base.dispatch(x, idx, True)
