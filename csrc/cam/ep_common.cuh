@@ -34,6 +34,8 @@ struct EpNormalOffsets {
   uint64_t arr_scale[2];    // [R][cap][nscale] fp32
   uint64_t arr_meta[2];     // [R][cap][meta_words] int32
   uint64_t comb_buf[2];     // [cap][J][H] bf16
+  uint64_t snotify[2];      // standalone notify op: [R src][E_local + 4] int32
+  uint64_t snotify_flag[2]; // [R] uint64
   uint64_t total;
 };
 
@@ -62,6 +64,12 @@ __host__ __device__ inline EpNormalOffsets ep_normal_offsets(const EpGeom& g) {
     off = align_up_u64(off + (uint64_t)g.R * g.cap * g.meta_words * 4, 256);
     o.comb_buf[h] = off;
     off = align_up_u64(off + (uint64_t)g.cap * g.J * g.H * 2, 256);
+  }
+  for (int h = 0; h < 2; ++h) {
+    o.snotify[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * ep_notify_words(g.E_local) * 4, 256);
+    o.snotify_flag[h] = off;
+    off = align_up_u64(off + (uint64_t)g.R * 8, 256);
   }
   o.total = off;
   return o;

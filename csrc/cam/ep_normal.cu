@@ -935,6 +935,126 @@ UMDK_API int umdk_ep_combine(const UmdkEpCombineParams* p, void* stream) {
 }
 
 // ------------------------------------------------------------------------------------------------------------
+// Standalone notify: the count exchange of dispatch as an operator of its own
+// ------------------------------------------------------------------------------------------------------------
+// Every rank sends, to each peer, how many of its (token, k) pairs go to each of that peer's local experts and how
+// many tokens it sends there at all; from what it receives it derives the totals and prefix tables a receiver needs
+// to size and address its buffers. Same outputs as the reference's notify_dispatch
+// (src/cam/comm_operator/ascend_kernels/notify_dispatch/op_kernel/notify_dispatch.h:91-160: totalRecvTokens, recvCount
+// as inclusive prefix over [localExpert][srcRank], recvOffset, maxBs, recvTokensPerExpert). Dispatch does the same
+// exchange internally; this entry exists for callers that want the numbers before they dispatch. Own flag region and
+// epoch word (ctrl[8]), so it can be mixed freely with dispatch / combine calls.
+struct NotifyArgs {
+  EpGeom g;
+  EpNormalOffsets off;
+  PeerTable peers;
+  const int* num_per_expert;   // [E]
+  const int* num_per_rank;     // [R]
+  int* recv_count;             // [E_local * R] inclusive prefix, index = le * R + src
+  int* recv_offset;            // [E_local * R] exclusive prefix
+  int64_t* recv_per_expert;    // [E_local]
+  int* totals;                 // [4]: rows to receive, arrivals (tokens) to receive, max tokens from one source, 0
+  uint32_t* ctrl;              // [8] epoch of this operator
+  int* status;
+  int phase_mask;              // 1 = send, 2 = receive
+};
+
+__global__ void __launch_bounds__(256, 1) ep_notify_kernel(const NotifyArgs a) {
+  const EpGeom& g = a.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ int s_cnt[1024];
+  __shared__ int s_ok;
+  const uint32_t epoch = a.ctrl[8];
+  const int h = epoch & 1;
+  const uint64_t tag = (uint64_t)epoch + 1;
+  const int nw = ep_notify_words(g.E_local);
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (a.phase_mask & 1) {
+    for (int d = warp; d < g.R; d += 8) {
+      int* dst = reinterpret_cast<int*>(a.peers.base[d] + a.off.snotify[h]) + (size_t)g.rank * nw;
+      for (int i = lane; i < g.E_local; i += 32) dst[i] = a.num_per_expert[d * g.E_local + i];
+      if (lane == 0) dst[g.E_local] = a.num_per_rank[d];
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) {
+        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[d] + a.off.snotify_flag[h]) + g.rank, tag);
+      }
+    }
+  }
+  if (!(a.phase_mask & 2)) return;
+  uint8_t* self = a.peers.base[g.rank];
+  if (threadIdx.x < g.R) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.snotify_flag[h]) + threadIdx.x;
+    if (!wait_flag_ge_sys(f, tag)) {
+      umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_COUNT, threadIdx.x, (int)epoch);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int* notify = reinterpret_cast<const int*>(self + a.off.snotify[h]);
+  const int nle = g.E_local * g.R;
+  for (int i = threadIdx.x; i < nle; i += blockDim.x) s_cnt[i] = __ldcg(notify + (size_t)(i % g.R) * nw + i / g.R);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0, arrivals = 0, max_src = 0;
+    for (int i = 0; i < nle; ++i) {
+      a.recv_offset[i] = run;
+      run += s_cnt[i];
+      a.recv_count[i] = run;
+      if ((i % g.R) == g.R - 1) {
+        const int le = i / g.R;
+        a.recv_per_expert[le] = (int64_t)(run - a.recv_offset[le * g.R]);
+      }
+    }
+    for (int r = 0; r < g.R; ++r) {
+      const int c = __ldcg(notify + (size_t)r * nw + g.E_local);
+      arrivals += c;
+      max_src = max(max_src, c);
+    }
+    a.totals[0] = run;
+    a.totals[1] = arrivals;
+    a.totals[2] = max_src;
+    a.totals[3] = 0;
+    a.ctrl[8] = epoch + 1;
+  }
+}
+
+struct UmdkEpNotifyParams {
+  int R, rank, E, K, H, cap, phase_mask;
+  void* peers[kMaxRanks];
+  const int* num_per_expert;
+  const int* num_per_rank;
+  int* recv_count;
+  int* recv_offset;
+  int64_t* recv_per_expert;
+  int* totals;
+  uint32_t* ctrl;
+  int* status;
+};
+
+UMDK_API int umdk_ep_notify(const UmdkEpNotifyParams* p, void* stream) {
+  NotifyArgs a;
+  if (int rc = fill_geom(&a.g, p->R, p->rank, p->E, p->K, p->H, p->cap, 0)) return rc;
+  if (a.g.E_local * a.g.R > 1024) return -UMDK_ERR_BAD_ARG;
+  a.off = ep_normal_offsets(layout_geom(a.g));
+  for (int i = 0; i < p->R; ++i) a.peers.base[i] = static_cast<uint8_t*>(p->peers[i]);
+  a.num_per_expert = p->num_per_expert;
+  a.num_per_rank = p->num_per_rank;
+  a.recv_count = p->recv_count;
+  a.recv_offset = p->recv_offset;
+  a.recv_per_expert = p->recv_per_expert;
+  a.totals = p->totals;
+  a.ctrl = p->ctrl;
+  a.status = p->status;
+  a.phase_mask = p->phase_mask ? p->phase_mask : 3;
+  ep_notify_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  UMDK_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------------------
 // Allocation-free layout entry point (see ep_layout_noalloc.h for who needs it and the rules that come with it)
 // ------------------------------------------------------------------------------------------------------------
 #include "ep_layout_noalloc.h"

@@ -44,6 +44,10 @@ def _worker(rank, world, port, use_ops, quant, q):
             npe, sidx = o.get_dispatch_layout(idx, E, world)
             recv_x, scales, expand_idx, recv_count, per_expert = o.moe_dispatch_prefill(
                 x, idx, w, npe, sidx, "ep", rank, world, quant)
+            npr = ref.ref_layout(idx, E, world).num_tokens_per_rank
+            n_cnt, n_off, n_pe, n_tot = o.notify_dispatch(npe, npr, "ep", idx.shape[1], x.shape[1], x.shape[0])
+            assert torch.equal(n_cnt, recv_count) and torch.equal(n_pe, per_expert)
+            assert n_tot[0] == recv_x.shape[0] and torch.equal(n_off[1:], n_cnt[:-1])
             xin = ref.dequant_fp8_1x128(recv_x, scales) if quant else recv_x
             le = torch.repeat_interleave(torch.arange(el), per_expert)
             y = xin * (le + rank * el + 1).float().unsqueeze(1)

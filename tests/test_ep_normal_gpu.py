@@ -154,3 +154,40 @@ def test_diagnose_mode_records_wait_times():
         assert ref.mean_rel_err(out.float().cpu(), x.float().cpu()) < 1e-2
     finally:
         heap.close()
+
+
+@pytest.mark.parametrize("R,T,E,K", [(1, 64, 8, 2), (2, 128, 16, 2), (8, 300, 256, 8)])
+def test_notify_matches_dispatch_counts(R, T, E, K):
+    """The standalone count exchange gives the numbers dispatch derives internally, and can be interleaved with it."""
+    H = 1024
+    xs, idxs, ws = _make_inputs(R, T, H, E, K, seed=R * 31 + T, drop=True)
+    heaps, states = _virtual_states(R, E, K, H, cap=T)
+    try:
+        di = [i.cuda() for i in idxs]
+        el = E // R
+        for rnd in range(3):
+            lays = [states[r].layout(di[r]) for r in range(R)]
+            outs = [states[r].notify(lays[r], phase_mask=1) for r in range(R)]
+            outs = [states[r].notify(lays[r], phase_mask=2, out=outs[r]) for r in range(R)]
+            if rnd == 1:  # a dispatch in between must not disturb the operator's own epoch
+                d = [states[r].dispatch(xs[r].cuda(), di[r], ws[r].cuda(), phase_mask=1) for r in range(R)]
+                d = [states[r].dispatch(xs[r].cuda(), di[r], ws[r].cuda(), phase_mask=2, out=d[r]) for r in range(R)]
+            torch.cuda.synchronize()
+            want_lay = [ref.ref_layout(i, E, R) for i in idxs]
+            for r in range(R):
+                states[r].check("notify")
+                cnt = torch.stack([want_lay[s].num_tokens_per_expert[r * el:(r + 1) * el] for s in range(R)])  # [src, le]
+                flat = cnt.t().reshape(-1).to(torch.int64)
+                incl = torch.cumsum(flat, 0)
+                assert torch.equal(outs[r].recv_count.cpu().long(), incl)
+                assert torch.equal(outs[r].recv_offset.cpu().long(), incl - flat)
+                assert torch.equal(outs[r].recv_tokens_per_expert.cpu(), cnt.sum(0).to(torch.int64))
+                arr = [int(want_lay[s].num_tokens_per_rank[r]) for s in range(R)]
+                assert outs[r].totals.tolist()[:3] == [int(flat.sum()), sum(arr), max(arr)]
+                if rnd == 1:
+                    assert torch.equal(d[r].recv_count.cpu(), outs[r].recv_count.cpu())
+            idxs = [torch.roll(i, 1, 0) for i in idxs]
+            di = [i.cuda() for i in idxs]
+    finally:
+        for h in heaps:
+            h.close()

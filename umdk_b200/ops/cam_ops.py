@@ -43,6 +43,8 @@ def _buf(name: str) -> Buffer:
 
 _lib = torch.library.Library("umdk_cam_op_lib", "DEF")
 _lib.define("get_dispatch_layout(Tensor topk_idx, int num_experts, int num_ranks) -> (Tensor, Tensor)")
+_lib.define("notify_dispatch(Tensor num_tokens_per_expert, Tensor num_tokens_per_rank, str group_ep, int top_k, "
+            "int hidden, int max_tokens) -> (Tensor, Tensor, Tensor, Tensor)")
 _lib.define("moe_dispatch_prefill(Tensor x, Tensor topk_idx, Tensor topk_weights, Tensor num_tokens_per_expert, "
             "Tensor send_token_idx_small, str group_ep, int rank, int num_ranks, bool use_quant) -> "
             "(Tensor, Tensor, Tensor, Tensor, Tensor)")
@@ -64,6 +66,20 @@ def _get_dispatch_layout(topk_idx, num_experts, num_ranks):
     else:
         lay = ref.ref_layout(topk_idx, num_experts, num_ranks)
     return lay.num_tokens_per_expert, lay.send_token_idx
+
+
+def _notify_dispatch(num_tokens_per_expert, num_tokens_per_rank, group_ep, top_k, hidden, max_tokens):
+    """Count exchange as an operator of its own -> (recv_count, recv_offset, recv_tokens_per_expert, totals). The
+    reference runs it as the first half of moe_dispatch_prefill (pybind/moe_dispatch_prefill.cpp, aclnnNotifyDispatch)."""
+    buf = _buf(group_ep)
+    if num_tokens_per_expert.is_cuda:
+        from .ep import LayoutResult
+        st = buf._normal_state(num_tokens_per_expert.numel(), top_k, hidden, max_tokens)
+        lay = LayoutResult(num_tokens_per_expert.to(torch.int32).contiguous(),
+                           num_tokens_per_rank.to(torch.int32).contiguous(), None, None, None)
+        out = st.notify(lay)
+        return out.recv_count, out.recv_offset, out.recv_tokens_per_expert, out.totals
+    return cpu_dist.cpu_notify(num_tokens_per_expert, num_tokens_per_rank, buf.group)
 
 
 def _moe_dispatch_prefill(x, topk_idx, topk_weights, num_tokens_per_expert, send_token_idx_small, group_ep, rank,
@@ -128,6 +144,7 @@ def _fused_deep_moe(x, expert_ids, gmm1_weight, gmm1_weight_scale, gmm2_weight, 
     return [out, share, cnt]
 
 
-for _name, _fn in (("get_dispatch_layout", _get_dispatch_layout), ("moe_dispatch_prefill", _moe_dispatch_prefill),
+for _name, _fn in (("get_dispatch_layout", _get_dispatch_layout), ("notify_dispatch", _notify_dispatch),
+                   ("moe_dispatch_prefill", _moe_dispatch_prefill),
                    ("moe_combine_prefill", _moe_combine_prefill), ("fused_deep_moe", _fused_deep_moe)):
     _lib.impl(_name, _fn, "CompositeExplicitAutograd")

@@ -115,6 +115,24 @@ def cpu_dispatch(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: Optional[torch
                              incl.to(torch.int32), cnt_from.sum(dim=0), wts[inv], lay, T, quant)
 
 
+def cpu_notify(num_tokens_per_expert: torch.Tensor, num_tokens_per_rank: torch.Tensor, group=None):
+    """Count exchange alone on CPU ranks: returns (recv_count inclusive prefix [le*R+src], recv_offset,
+    recv_tokens_per_expert, totals[rows, tokens, max tokens from one source]) - the same numbers the GPU operator
+    gives (notify_dispatch.h:91-160 in the reference)."""
+    R = _world(group)
+    el = num_tokens_per_expert.numel() // R
+    mine = torch.cat((num_tokens_per_expert.reshape(R, el).to(torch.int64),
+                      num_tokens_per_rank.reshape(R, 1).to(torch.int64)), dim=1).contiguous()
+    got = torch.empty_like(mine)
+    _all_to_all_single(got, mine, group=group)
+    flat = got[:, :el].t().reshape(-1)
+    incl = torch.cumsum(flat, dim=0)
+    arrivals = got[:, el]
+    totals = torch.tensor([int(flat.sum()), int(arrivals.sum()), int(arrivals.max()) if R else 0, 0],
+                          dtype=torch.int32)
+    return incl.to(torch.int32), (incl - flat).to(torch.int32), got[:, :el].sum(dim=0), totals
+
+
 def cpu_combine(y: torch.Tensor, expand_idx: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
                 num_tokens: int, group=None, out_dtype=torch.bfloat16) -> torch.Tensor:
     """Returns each row to (srcRank, srcToken, k) and forms sum_k w[t,k] * row in fp32, rounded once."""

@@ -49,6 +49,17 @@ class _CombineParams(ctypes.Structure):
     ]
 
 
+class _NotifyParams(ctypes.Structure):
+    _fields_ = [
+        ("R", ctypes.c_int), ("rank", ctypes.c_int), ("E", ctypes.c_int), ("K", ctypes.c_int), ("H", ctypes.c_int),
+        ("cap", ctypes.c_int), ("phase_mask", ctypes.c_int),
+        ("peers", ctypes.c_void_p * MAX_RANKS),
+        ("num_per_expert", ctypes.c_void_p), ("num_per_rank", ctypes.c_void_p),
+        ("recv_count", ctypes.c_void_p), ("recv_offset", ctypes.c_void_p), ("recv_per_expert", ctypes.c_void_p),
+        ("totals", ctypes.c_void_p), ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+    ]
+
+
 class KernelStatusError(RuntimeError):
     """A kernel gave up on a bounded wait or rejected an out-of-range index; the record says where."""
 
@@ -74,6 +85,16 @@ class LayoutResult:
     is_token_in_rank: torch.Tensor
     send_token_idx: torch.Tensor
     rank_slot: torch.Tensor
+
+
+@dataclass
+class NotifyResult:
+    """What a rank learns from the count exchange before any token moves (the outputs of the reference's
+    notify_dispatch operator: notify_dispatch.h:91-160)."""
+    recv_count: torch.Tensor              # [E_local * R] inclusive prefix over (local expert, source rank)
+    recv_offset: torch.Tensor             # [E_local * R] exclusive prefix
+    recv_tokens_per_expert: torch.Tensor  # [E_local] int64
+    totals: torch.Tensor                  # [4] int32: rows to receive, tokens to receive, max tokens from one source
 
 
 @dataclass
@@ -163,6 +184,30 @@ class EpNormal:
 
     def layout(self, topk_idx: torch.Tensor) -> LayoutResult:
         return layout(topk_idx, self.E, self.R, self.layout_scratch, self.layout_bar, self.status)
+
+    def notify(self, lay: LayoutResult, phase_mask: int = 3, out: Optional[NotifyResult] = None) -> NotifyResult:
+        """Count exchange alone: tells every peer how many rows / tokens this rank will send to each of its local
+        experts and returns what this rank will receive. ``dispatch`` does the same exchange internally; call this
+        when the sizes are needed first (to size buffers, or to balance load) - one launch of one CTA."""
+        El = self.E // self.R
+        if out is None:
+            dev = self.device
+            out = NotifyResult(torch.empty(El * self.R, dtype=torch.int32, device=dev),
+                               torch.empty(El * self.R, dtype=torch.int32, device=dev),
+                               torch.empty(El, dtype=torch.int64, device=dev),
+                               torch.zeros(4, dtype=torch.int32, device=dev))
+        p = _NotifyParams()
+        p.R, p.rank, p.E, p.K, p.H, p.cap, p.phase_mask = self.R, self.rank, self.E, self.K, self.H, self.cap, phase_mask
+        for i, pp in enumerate(self.heap.peer_ptrs):
+            p.peers[i] = pp
+        p.num_per_expert, p.num_per_rank = lay.num_tokens_per_expert.data_ptr(), lay.num_tokens_per_rank.data_ptr()
+        p.recv_count, p.recv_offset = out.recv_count.data_ptr(), out.recv_offset.data_ptr()
+        p.recv_per_expert, p.totals = out.recv_tokens_per_expert.data_ptr(), out.totals.data_ptr()
+        p.ctrl, p.status = self.ctrl.data_ptr(), self.status.data_ptr()
+        rc = self.lib.umdk_ep_notify(ctypes.byref(p), _native.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"umdk_ep_notify failed: {rc}")
+        return out
 
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: Optional[torch.Tensor],
                  lay: Optional[LayoutResult] = None, quant: bool = True, n_cap: Optional[int] = None,
