@@ -36,6 +36,8 @@ struct EpNormalOffsets {
   uint64_t comb_buf[2];     // [cap][J][H] bf16
   uint64_t snotify[2];      // standalone notify op: [R src][E_local + 4] int32
   uint64_t snotify_flag[2]; // [R] uint64
+  uint64_t stage_x;         // [cap][H] fp8: this rank's quantised tokens, read by its own per-destination passes
+  uint64_t stage_scale;     // [cap][H / 128] fp32
   uint64_t total;
 };
 
@@ -71,6 +73,10 @@ __host__ __device__ inline EpNormalOffsets ep_normal_offsets(const EpGeom& g) {
     o.snotify_flag[h] = off;
     off = align_up_u64(off + (uint64_t)g.R * 8, 256);
   }
+  o.stage_x = off;
+  off = align_up_u64(off + (uint64_t)g.cap * g.H, 256);
+  o.stage_scale = off;
+  off = align_up_u64(off + (uint64_t)g.cap * (g.H / 128) * 4, 256);
   o.total = off;
   return o;
 }

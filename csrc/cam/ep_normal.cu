@@ -207,11 +207,13 @@ struct DispatchArgs {
   int* recv_count;             // [E_local * R] inclusive prefix, index = le * R + src
   int64_t* recv_per_expert;    // [E_local]
   int* recv_meta;              // [a_cap, 2K+2] per arrival: src, srcToken, rows[K], weight bits[K]
-  int* counts_dev;             // [4]: expanded rows N, arrivals A, max tokens from one source, 0
+  int* counts_dev;             // [4 + R]: expanded rows N, arrivals A, max tokens from one source, 0, then the
+                               // index of the first arrival of every source
   volatile int* counts_host;   // same 4 ints in mapped pinned host memory + [4] = epoch stamp (may be null)
   int n_cap, a_cap;
   // control
-  uint32_t* ctrl;              // [0] epoch, [1] send-done counter, [2] recv-done counter
+  uint32_t* ctrl;              // [0] epoch, [2] recv-done counter, [10] staging gate (tag of the last staged call),
+                               // [16 + i] done counter of send pass i
   int* status;
   int phase_mask;              // bit0: notify + send, bit1: receive + expand (both for normal use)
   long long* diag;             // optional [R]: nanoseconds CTA 0 waited for each source rank's data (diagnose mode)
@@ -233,28 +235,127 @@ __device__ __forceinline__ void bf16x8_to_float(const int4& v, float* f) {
   }
 }
 
+// Barrier over the warps of one role (named barrier `id`, `nthreads` a multiple of 32).
+__device__ __forceinline__ void role_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// One warp quantises token t (bf16 -> fp8 e4m3, fp32 scale per 1x128 block) and writes the row to up to two places.
+__device__ __forceinline__ void quant_row_to(const int4* xrow, int H, int lane, uint8_t* px0, float* ps0, uint8_t* px1,
+                                             float* ps1) {
+  const int nblk = H / 128;
+  // each lane: 16 elements per step; 8 lanes share one 1x128 block; two groups of four blocks per iteration with all
+  // four 16-byte loads of a lane issued first
+  for (int b0 = 0; b0 < nblk; b0 += 8) {
+    int4 raw[2][2];
+    bool active[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int blk = b0 + 4 * u + (lane >> 3);
+      active[u] = blk < nblk;
+      if (active[u]) {
+        raw[u][0] = __ldg(xrow + blk * 16 + (lane & 7) * 2);
+        raw[u][1] = __ldg(xrow + blk * 16 + (lane & 7) * 2 + 1);
+      } else {
+        raw[u][0] = raw[u][1] = make_int4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int blk = b0 + 4 * u + (lane >> 3);
+      float f[16];
+      bf16x8_to_float(raw[u][0], f);
+      bf16x8_to_float(raw[u][1], f + 8);
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      amax = fmaxf(amax, 1e-4f);
+      const float scale = amax * (1.f / 448.f);
+      const float inv = 448.f / amax;
+      int4 q;
+      q.x = pack_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+      q.y = pack_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+      q.z = pack_fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+      q.w = pack_fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+      if (active[u]) {
+        const int o = blk * 128 + (lane & 7) * 16;
+        if (px0) st_na_v4(px0 + o, q);
+        if (px1) st_na_v4(px1 + o, q);
+        if ((lane & 7) == 0) {
+          if (ps0) ps0[blk] = scale;
+          if (ps1) ps1[blk] = scale;
+        }
+      }
+    }
+  }
+}
+
+// One warp copies `bytes` (a multiple of 16) with eight 16-byte loads per lane in flight before the first store.
+template <bool kFromThisKernel>
+__device__ __forceinline__ void warp_copy_row(uint8_t* dst, const uint8_t* src, int bytes, int lane) {
+  const int nvec = bytes / 16;
+  const int4* s = reinterpret_cast<const int4*>(src);
+  int4* d = reinterpret_cast<int4*>(dst);
+  for (int v0 = 0; v0 < nvec; v0 += 8 * 32) {
+    int4 x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int v = v0 + u * 32 + lane;
+      if (v < nvec) x[u] = kFromThisKernel ? __ldcg(s + v) : __ldg(s + v);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int v = v0 + u * 32 + lane;
+      if (v < nvec) st_na_v4(d + v, x[u]);
+    }
+  }
+}
+
+// Dispatch = two roles that run side by side in every CTA (phase_mask 3: warps [0, 8) send, warps [8, 16) receive)
+// or one at a time with all warps (phase_mask 1 or 2, which is how several ranks are emulated on one GPU).
+//
+// Sender. Pass 0 quantises every token once into a local staging area (and into this rank's own arrival slots for
+// the tokens that stay here). Then one pass per peer, destination (rank + i) % R in pass i: the rows that go there
+// are copied from the staging area into the peer's arrival slots, and the peer's data flag is raised as soon as the
+// pass is complete on all CTAs. Every rank walks the ring in the same direction, so at any moment the ranks write to
+// different destinations - a rotating permutation that keeps each inbound link busy with one writer - and a receiver
+// gets its sources one after the other, in the order (rank, rank - 1, rank - 2, ...), which is the order in which
+// its receiving warps expand them.
 __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const DispatchArgs a) {
   const EpGeom& g = a.g;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   __shared__ uint32_t s_epoch;
   __shared__ int s_cnt[1024 + 64];   // counts [le][src] -> exclusive offsets; tail: per-source arrivals
-  __shared__ int s_ok;
-  __shared__ int s_slot[kEpWarps][kMaxRanks];  // per-warp staging: destination slots of the current token
+  __shared__ int s_ok_send, s_ok_recv;
   __shared__ int s_row[kEpWarps][kMaxTopk];    // per-warp staging: expanded rows of the current arrival
   if (threadIdx.x == 0) {
     s_epoch = a.ctrl[0];
-    s_ok = 1;
+    s_ok_send = 1;
+    s_ok_recv = 1;
   }
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const int h = epoch & 1;
   const uint64_t tag = (uint64_t)epoch + 1;
   const int nw = ep_notify_words(g.E_local);
+  const bool both = (a.phase_mask & 3) == 3;
+  const int n_send_warps = both ? kEpWarps / 2 : kEpWarps;
+  const bool is_sender = (a.phase_mask & 1) && (!both || warp < n_send_warps);
+  const bool is_receiver = (a.phase_mask & 2) && (!both || warp >= n_send_warps);
+  uint8_t* self = a.peers.base[g.rank];
 
-  if (a.phase_mask & 1) {
+  if (is_sender) {
+    const int sw = warp;                       // sender warps are always the first ones
+    const int nthr = n_send_warps * 32;
+    const bool stage = g.quant && g.R > 1;
+    uint8_t* stage_x = self + a.off.stage_x;
+    float* stage_s = reinterpret_cast<float*>(self + a.off.stage_scale);
     // ---- notify: CTA 0, one warp per destination rank (looping) ----
     if (blockIdx.x == 0) {
-      for (int d = warp; d < g.R; d += kEpWarps) {
+      for (int d = sw; d < g.R; d += n_send_warps) {
         int* dst = reinterpret_cast<int*>(a.peers.base[d] + a.off.notify[h]) + (size_t)g.rank * nw;
         for (int i = lane; i < g.E_local; i += 32) dst[i] = a.num_per_expert[d * g.E_local + i];
         if (lane == 0) dst[g.E_local] = a.num_per_rank[d];
@@ -265,141 +366,103 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
         }
       }
     }
-    // ---- send: one warp per token ----
-    for (int t = blockIdx.x * kEpWarps + warp; t < a.T; t += gridDim.x * kEpWarps) {
-      // destination mask and slots
-      int my_slot = -1;
-      if (lane < g.R) my_slot = a.rank_slot[(size_t)t * g.R + lane];
-      const uint32_t dmask = __ballot_sync(0xffffffffu, my_slot >= 0);
-      if (dmask == 0) continue;
-      __syncwarp();
-      if (lane < g.R) s_slot[warp][lane] = my_slot;
-      __syncwarp();
-      // metadata: lanes 0..K-1 hold (expert, bucket position, weight)
-      int e = -1, sidx = -1;
-      float w = 0.f;
-      if (lane < g.K) {
-        const long long ee = a.topk_idx[(size_t)t * g.K + lane];
-        e = (ee >= 0 && ee < g.E) ? (int)ee : -1;
-        sidx = a.send_idx[(size_t)t * g.K + lane];
-        w = a.topk_w ? a.topk_w[(size_t)t * g.K + lane] : 1.f;
-      }
-      for (uint32_t m = dmask; m; m &= m - 1) {
-        const int d = __ffs(m) - 1;
-        const int slot = s_slot[warp][d];
+    for (int pass = 0; pass < g.R; ++pass) {
+      const int d = (g.rank + pass) % g.R;
+      uint8_t* peer = a.peers.base[d];
+      for (int t = blockIdx.x * n_send_warps + sw; t < a.T; t += gridDim.x * n_send_warps) {
+        const int slot = a.rank_slot[(size_t)t * g.R + d];
         if (slot >= g.cap) {
-          umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, d, slot);
-          continue;
+          if (lane == 0) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, d, slot);
         }
-        int* meta = reinterpret_cast<int*>(a.peers.base[d] + a.off.arr_meta[h]) +
-                    ((size_t)g.rank * g.cap + slot) * g.meta_words;
-        if (lane < g.K) {
-          const bool mine = e >= 0 && (e / g.E_local) == d;
-          meta[lane] = mine ? (((e % g.E_local) << 16) | (sidx & 0xffff)) : -1;
-          meta[g.K + lane] = __float_as_int(w);
+        const bool goes = slot >= 0 && slot < g.cap;
+        if (!goes && !(pass == 0 && stage)) continue;
+        const size_t rec = (size_t)g.rank * g.cap + (goes ? slot : 0);
+        if (goes) {
+          // metadata: lanes 0..K-1 hold (local expert << 16 | bucket position) or -1, then the weights, then the token
+          int* meta = reinterpret_cast<int*>(peer + a.off.arr_meta[h]) + rec * g.meta_words;
+          if (lane < g.K) {
+            const long long ee = a.topk_idx[(size_t)t * g.K + lane];
+            const int e = (ee >= 0 && ee < g.E) ? (int)ee : -1;
+            const bool mine = e >= 0 && (e / g.E_local) == d;
+            meta[lane] = mine ? (((e % g.E_local) << 16) | (a.send_idx[(size_t)t * g.K + lane] & 0xffff)) : -1;
+            meta[g.K + lane] = __float_as_int(a.topk_w ? a.topk_w[(size_t)t * g.K + lane] : 1.f);
+          }
+          if (lane == 0) meta[2 * g.K] = t;
         }
-        if (lane == 0) meta[2 * g.K] = t;
+        uint8_t* px = goes ? peer + a.off.arr_x[h] + rec * g.row_bytes : nullptr;
+        float* ps = goes ? reinterpret_cast<float*>(peer + a.off.arr_scale[h]) + rec * g.nscale : nullptr;
+        if (!g.quant) {
+          warp_copy_row<false>(px, reinterpret_cast<const uint8_t*>(a.x + (size_t)t * g.H), g.row_bytes, lane);
+        } else if (pass == 0) {
+          quant_row_to(reinterpret_cast<const int4*>(a.x + (size_t)t * g.H), g.H, lane,
+                       stage ? stage_x + (size_t)t * g.H : nullptr, stage ? stage_s + (size_t)t * g.nscale : nullptr,
+                       px, ps);
+        } else {
+          warp_copy_row<true>(px, stage_x + (size_t)t * g.H, g.row_bytes, lane);
+          for (int v = lane; v < g.nscale; v += 32) ps[v] = __ldcg(stage_s + (size_t)t * g.nscale + v);
+        }
       }
-      const int4* xrow = reinterpret_cast<const int4*>(a.x + (size_t)t * g.H);
-      if (g.quant) {
-        // each lane: 16 elements per step; 8 lanes share one 1x128 block
-        const int nblk = g.H / 128;
-        for (int b0 = 0; b0 < nblk; b0 += 8) {
-          // two groups of four 1x128 blocks per iteration; all four 16-byte loads of a lane are issued first
-          int4 raw[2][2];
-          bool active[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int blk = b0 + 4 * u + (lane >> 3);
-            active[u] = blk < nblk;
-            if (active[u]) {
-              raw[u][0] = __ldg(xrow + blk * 16 + (lane & 7) * 2);
-              raw[u][1] = __ldg(xrow + blk * 16 + (lane & 7) * 2 + 1);
-            } else {
-              raw[u][0] = raw[u][1] = make_int4(0, 0, 0, 0);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int blk = b0 + 4 * u + (lane >> 3);
-            float f[16];
-            bf16x8_to_float(raw[u][0], f);
-            bf16x8_to_float(raw[u][1], f + 8);
-            float amax = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-            amax = fmaxf(amax, 1e-4f);
-            const float scale = amax * (1.f / 448.f);
-            const float inv = 448.f / amax;
-            int4 q;
-            q.x = pack_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
-            q.y = pack_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
-            q.z = pack_fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
-            q.w = pack_fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
-            if (active[u]) {
-              for (uint32_t m = dmask; m; m &= m - 1) {
-                const int d = __ffs(m) - 1;
-                const int slot = s_slot[warp][d];
-                if (slot >= g.cap) continue;
-                const size_t rec = (size_t)g.rank * g.cap + slot;
-                uint8_t* px = a.peers.base[d] + a.off.arr_x[h] + rec * g.row_bytes;
-                st_na_v4(px + blk * 128 + (lane & 7) * 16, q);
-                if ((lane & 7) == 0) {
-                  float* ps = reinterpret_cast<float*>(a.peers.base[d] + a.off.arr_scale[h]) + rec * g.nscale;
-                  ps[blk] = scale;
-                }
-              }
-            }
+      // ---- end of the pass: the last CTA to finish it raises this rank's data flag on the destination ----
+      role_sync(1, nthr);
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint32_t old = atomicAdd(&a.ctrl[16 + pass], 1u);
+        if (old == gridDim.x - 1) {
+          a.ctrl[16 + pass] = 0;
+          __threadfence_system();
+          st_release_sys(reinterpret_cast<uint64_t*>(peer + a.off.data_flag[h]) + g.rank, tag);
+          if (pass == 0 && stage) {   // staging area complete: open the gate for this call
+            __threadfence();
+            atomicExch(&a.ctrl[10], epoch + 1);
           }
         }
-      } else {
-        const int nvec = g.H / 8;  // 16-byte vectors per row
-        for (int i = lane; i < nvec; i += 32) {
-          const int4 v = __ldg(xrow + i);
-          for (uint32_t m = dmask; m; m &= m - 1) {
-            const int d = __ffs(m) - 1;
-            const int slot = s_slot[warp][d];
-            if (slot >= g.cap) continue;
-            uint8_t* px = a.peers.base[d] + a.off.arr_x[h] + ((size_t)g.rank * g.cap + slot) * g.row_bytes;
-            st_na_v4(px + (size_t)i * 16, v);
+        if (pass == 0 && stage) {
+          // the later passes read rows that other CTAs quantised: wait until all of them are through pass 0
+          const uint32_t want = epoch + 1;   // the gate holds the tag of the last call whose staging is complete
+          const long long t0 = clock64();
+          while ((int32_t)(ld_acquire_gpu(&a.ctrl[10]) - want) < 0) {
+            if (clock64() - t0 > kSpinLimitCycles) {
+              umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_BARRIER, blockIdx.x, (int)epoch);
+              s_ok_send = 0;
+              break;
+            }
+            __nanosleep(20);
           }
         }
       }
-    }
-    // ---- publish: the last CTA to finish sending raises this rank's data flag on every peer ----
-    if (cta_done_is_last(&a.ctrl[1], gridDim.x)) {
-      if (threadIdx.x < g.R) {
-        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.off.data_flag[h]) + g.rank, tag);
+      if (pass == 0 && stage) {
+        role_sync(1, nthr);
+        if (!s_ok_send) break;
       }
     }
   }
 
-  if (!(a.phase_mask & 2)) return;
+  if (!is_receiver) return;
+  const int rw = both ? warp - n_send_warps : warp;   // index among the receiving warps
+  const int n_recv_warps = both ? kEpWarps - n_send_warps : kEpWarps;
+  const int rthr = n_recv_warps * 32;
+  const int rtid = threadIdx.x - (both ? n_send_warps * 32 : 0);
 
   // ---- receive: wait for every source's counts, build offsets ----
-  uint8_t* self = a.peers.base[g.rank];
-  if (threadIdx.x < g.R) {
-    const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.notify_flag[h]) + threadIdx.x;
+  if (rtid < g.R) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.notify_flag[h]) + rtid;
     if (!wait_flag_ge_sys(f, tag)) {
-      umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_COUNT, threadIdx.x, (int)epoch);
-      s_ok = 0;
+      umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_COUNT, rtid, (int)epoch);
+      s_ok_recv = 0;
     }
   }
-  __syncthreads();
-  if (!s_ok) return;
+  role_sync(2, rthr);
+  if (!s_ok_recv) return;
   const int* notify = reinterpret_cast<const int*>(self + a.off.notify[h]);
   const int nle = g.E_local * g.R;
   int* s_arr = s_cnt + 1024;  // [R] arrivals per source, then [R] exclusive arrival base
-  for (int i = threadIdx.x; i < nle; i += blockDim.x) {
+  for (int i = rtid; i < nle; i += rthr) {
     const int le = i / g.R, src = i % g.R;
     s_cnt[i] = notify[(size_t)src * nw + le];
   }
-  if (threadIdx.x < g.R) s_arr[threadIdx.x] = notify[(size_t)threadIdx.x * nw + g.E_local];
-  __syncthreads();
-  if (threadIdx.x == 0) {
+  if (rtid < g.R) s_arr[rtid] = notify[(size_t)rtid * nw + g.E_local];
+  role_sync(2, rthr);
+  if (rtid == 0) {
     int run = 0, amax_src = 0, abase = 0;
     for (int i = 0; i < nle; ++i) {
       const int c = s_cnt[i];
@@ -424,6 +487,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
       a.counts_dev[0] = run;
       a.counts_dev[1] = abase;
       a.counts_dev[2] = amax_src;
+      for (int r = 0; r < g.R; ++r) a.counts_dev[4 + r] = s_arr[g.R + r];  // first arrival of each source
       if (a.counts_host) {
         a.counts_host[0] = run;
         a.counts_host[1] = abase;
@@ -434,26 +498,26 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
       if (run > a.n_cap || abase > a.a_cap) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_COUNT, run, abase);
     }
   }
-  __syncthreads();
+  role_sync(2, rthr);
 
-  // ---- expand: arrivals -> expert-major rows ----
+  // ---- expand: arrivals -> expert-major rows, sources in the order in which their passes reach this rank ----
   const int mw2 = 2 * g.K + 2;
   for (int i = 0; i < g.R; ++i) {
-    const int src = (g.rank + i) % g.R;  // own tokens first (they are already here)
-    if (threadIdx.x == 0) {
+    const int src = (g.rank - i + g.R) % g.R;  // own tokens first (they are already here)
+    if (rtid == 0) {
       const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.data_flag[h]) + src;
       const long long t0 = a.diag ? (long long)globaltimer_ns() : 0;
       if (!wait_flag_ge_sys(f, tag)) {
         umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_DATA, src, (int)epoch);
-        s_ok = 0;
+        s_ok_recv = 0;
       }
       if (a.diag && blockIdx.x == 0) a.diag[src] = (long long)globaltimer_ns() - t0;
     }
-    __syncthreads();
-    if (!s_ok) return;
+    role_sync(2, rthr);
+    if (!s_ok_recv) return;
     const int n_from = min(s_arr[src], g.cap);
     const int abase = s_arr[g.R + src];
-    for (int p = blockIdx.x * kEpWarps + warp; p < n_from; p += gridDim.x * kEpWarps) {
+    for (int p = blockIdx.x * n_recv_warps + rw; p < n_from; p += gridDim.x * n_recv_warps) {
       const size_t rec = (size_t)src * g.cap + p;
       const int* meta = reinterpret_cast<const int*>(self + a.off.arr_meta[h]) + rec * g.meta_words;
       int code = -1, wbits = 0;
@@ -521,8 +585,14 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
     }
   }
   // ---- epoch advance by the last CTA ----
-  if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
-    if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+  role_sync(2, rthr);
+  if (rtid == 0) {
+    __threadfence_system();
+    const uint32_t old = atomicAdd(&a.ctrl[2], 1u);
+    if (old == gridDim.x - 1) {
+      a.ctrl[2] = 0;
+      a.ctrl[0] = epoch + 1;
+    }
   }
 }
 
@@ -536,7 +606,7 @@ struct CombineArgs {
   const __nv_bfloat16* y;     // [N, H] expert outputs in the dispatch row order
   // mode 0 (per-rank pre-reduction): arrival metadata from dispatch
   const int* recv_meta;       // [A, 2K+2]
-  const int* counts_dev;      // [0] = N, [1] = A
+  const int* counts_dev;      // [0] = N, [1] = A, [4 + r] = index of the first arrival from source r
   // mode 1 (row per (token,k), reference contract): (srcRank, srcToken, k) per row
   const int* src_idx;         // [N, 3]
   int n_rows;                 // mode 1: number of rows; mode 0: ignored
@@ -574,7 +644,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(const Combine
 
   if (a.phase_mask & 1) {
     const int items = a.mode == 0 ? a.counts_dev[1] : a.n_rows;
-    for (int it = blockIdx.x * kEpWarps + warp; it < items; it += gridDim.x * kEpWarps) {
+    // Arrivals are stored source by source. Every rank starts with the arrivals of its right-hand neighbour and goes
+    // round from there, so that at any moment the ranks send to different destinations (a rotating permutation)
+    // instead of all to the same one, whose inbound link would then be the bottleneck of the whole box.
+    const int start = (a.mode == 0 && g.R > 1) ? min(max(a.counts_dev[4 + (g.rank + 1) % g.R], 0), items) : 0;
+    for (int it0 = blockIdx.x * kEpWarps + warp; it0 < items; it0 += gridDim.x * kEpWarps) {
+      const int it = it0 + start < items ? it0 + start : it0 + start - items;
       int dst_rank, dst_tok, slot_j;
       int row = -1;
       float w = 1.f;
@@ -804,9 +879,10 @@ UMDK_API int umdk_ep_layout(const int64_t* topk_idx, int T, int K, int E, int R,
   }
   const int chunks = (T + 31) / 32;
   {
-    // one CTA with everything in shared memory, whenever the per-chunk histograms fit
+    // decode-sized inputs: one CTA with everything in shared memory (no grid barriers, no scratch); measured at
+    // 4096 tokens the single CTA takes 96 us against 35-48 us for the multi-CTA kernel, so it is kept to small inputs
     const size_t small_smem = sizeof(int) * ((size_t)chunks * (E + R) + (size_t)kSmallLayoutWarps * 32 * K);
-    if (small_smem <= 200 * 1024) {
+    if (T <= 1024 && small_smem <= 200 * 1024) {
       if (small_smem > 48 * 1024) {
         UMDK_CUDA_CHECK(cudaFuncSetAttribute(ep_layout_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)small_smem));

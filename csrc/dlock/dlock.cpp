@@ -9,7 +9,11 @@
 // and push it to a restarted server, which answers DLOCK_NOT_READY until enough clients have re-registered
 // (dlock_server.cpp:2685-2890, DLock User Guide :218-236); 64-bit atomic objects accessed with one-sided URMA
 // fetch-add / compare-swap on a server segment (common/jetty_mgr.cpp:518-527); debug counters.
-// The control channel is plain TCP here (the reference can wrap it in TLS).
+// Security (the reference's ssl_connection.cpp and dlock_cipher.cpp): with a pre-shared key configured (dlock_set_psk or
+// DLOCK_PSK / DLOCK_PSK_ID in the environment) the control channel runs TLS 1.3 PSK with TLS_AES_256_GCM_SHA384, the
+// server hands each client a random 256-bit data key inside that channel, and every lock command and reply on the
+// URMA data channel is sealed with AES-256-GCM under that key (client id in clear as the key selector, a message
+// counter as the nonce, replayed or unsealed commands refused).
 #include "dlock_api.h"
 
 #include <arpa/inet.h>
@@ -30,6 +34,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "ub_secure.h"
 #include "ub_util.h"
 #include "urma_simple.h"
 
@@ -48,7 +53,8 @@ struct CtlMsg {
   uint8_t ep_blob[URMA_SIMPLE_JETTY_BLOB];
   uint8_t seg_blob[URMA_SIMPLE_SEG_BLOB];
   uint32_t epoch;      // server incarnation
-  uint32_t pad;
+  uint32_t secure;     // init reply: 1 = data_key is valid and commands must be sealed
+  uint8_t data_key[32];
 };
 struct CmdMsg {  // data plane
   uint32_t magic, seq;
@@ -58,27 +64,63 @@ struct CmdMsg {  // data plane
   uint32_t epoch;
 };
 
-bool rd(int fd, void* b, size_t n, int tmo = 3000) {
-  uint8_t* p = static_cast<uint8_t*>(b);
-  while (n) {
-    pollfd pf{fd, POLLIN, 0};
-    if (poll(&pf, 1, tmo) <= 0) return false;
-    const ssize_t r = read(fd, p, n);
-    if (r <= 0) return false;
-    p += r;
-    n -= r;
+// What travels on the data channel: the command itself, or its sealed form.
+struct CmdWire {
+  int32_t client_id;   // in clear: selects the key on the server
+  uint32_t sealed;     // 0 = body holds a plain CmdMsg, 1 = AES-256-GCM ciphertext + tag
+  uint64_t nonce;      // sender's message counter, never reused under one key
+  uint8_t body[sizeof(CmdMsg) + ub::AeadCipher::kTagBytes];
+};
+constexpr uint32_t kDirToServer = 0, kDirToClient = 1;  // nonce salts: the two directions never share a nonce
+
+struct DataKey {
+  std::unique_ptr<ub::AeadCipher> tx, rx;
+  uint64_t tx_nonce = 0, rx_last = 0;
+  void set(const uint8_t key[32], bool is_server) {
+    tx.reset(new ub::AeadCipher(key, is_server ? kDirToClient : kDirToServer));
+    rx.reset(new ub::AeadCipher(key, is_server ? kDirToServer : kDirToClient));
+    tx_nonce = rx_last = 0;
   }
-  return true;
+  bool on() const { return tx != nullptr; }
+};
+
+void pack_cmd(CmdWire* w, const CmdMsg& m, DataKey* k) {
+  w->client_id = m.client_id;
+  if (k && k->on()) {
+    w->sealed = 1;
+    w->nonce = ++k->tx_nonce;
+    k->tx->seal(w->nonce, w, 16, &m, sizeof(m), w->body);
+  } else {
+    w->sealed = 0;
+    w->nonce = 0;
+    memcpy(w->body, &m, sizeof(m));
+  }
 }
-bool wr(int fd, const void* b, size_t n) {
-  const uint8_t* p = static_cast<const uint8_t*>(b);
-  while (n) {
-    const ssize_t r = send(fd, p, n, MSG_NOSIGNAL);
-    if (r <= 0) return false;
-    p += r;
-    n -= r;
+// False when the message must be dropped: sealed without a key, unsealed although a key is set, bad tag, replay.
+bool unpack_cmd(const CmdWire& w, CmdMsg* m, DataKey* k) {
+  if (!k || !k->on()) {
+    if (w.sealed) return false;
+    memcpy(m, w.body, sizeof(*m));
+    return true;
   }
-  return true;
+  if (!w.sealed || w.nonce <= k->rx_last) return false;
+  if (!k->rx->open(w.nonce, &w, 16, w.body, sizeof(w.body), m)) return false;
+  k->rx_last = w.nonce;
+  return m->client_id == w.client_id;
+}
+
+std::mutex g_psk_mu;
+ub::PskConfig g_psk;
+bool g_psk_loaded = false, g_psk_bad = false;
+// The key in force: the one set with dlock_set_psk, else the environment's. *bad: the environment's key is malformed.
+ub::PskConfig current_psk(bool* bad) {
+  std::lock_guard<std::mutex> l(g_psk_mu);
+  if (!g_psk_loaded) {
+    g_psk = ub::PskConfig::from_env("DLOCK", &g_psk_bad);
+    g_psk_loaded = true;
+  }
+  *bad = g_psk_bad;
+  return g_psk;
 }
 
 // ------------------------------------------------------------------------------------------------ lock memory
@@ -209,6 +251,8 @@ struct LockMemory {
 struct SrvClient {
   int32_t id;
   int fd;
+  std::unique_ptr<ub::SecureConn> conn;
+  DataKey key;
   urma_target_jetty_t* ep = nullptr;
   uint64_t last_seen;
   bool alive = true;
@@ -222,6 +266,7 @@ struct Server {
   std::atomic<bool> stop{false};
   std::mutex mu;
   LockMemory mem;
+  ub::PskConfig psk;
   std::vector<SrvClient*> clients;
   urma_context_t* ctx = nullptr;
   urma_simple_ep_t* ep = nullptr;
@@ -230,9 +275,9 @@ struct Server {
   std::unordered_map<std::string, int32_t> obj_by_name;
   urma_target_seg_t* obj_seg = nullptr;
   uint8_t obj_blob[URMA_SIMPLE_SEG_BLOB];
-  std::vector<CmdMsg> rx;  // receive ring
-  std::deque<CmdMsg*> tx_free;
-  std::vector<CmdMsg> tx;
+  std::vector<CmdWire> rx;  // receive ring
+  std::deque<CmdWire*> tx_free;
+  std::vector<CmdWire> tx;
   bool recovering = false;
   uint32_t recovered_clients = 0;
   uint64_t recovery_deadline = 0;
@@ -374,7 +419,7 @@ void srv_handle_ctl(Server* s, SrvClient* c, const CtlMsg& in) {
       break;
     default: out.status = DLOCK_EINVAL;
   }
-  wr(c->fd, &out, sizeof(out));
+  c->conn->write_full(&out, sizeof(out));
 }
 
 void srv_ctl_loop(Server* s) {
@@ -390,25 +435,39 @@ void srv_ctl_loop(Server* s) {
           cs.push_back(c);
         }
     }
-    if (poll(pfs.data(), pfs.size(), 50) <= 0) continue;
+    bool buffered = false;  // decrypted bytes waiting inside a TLS object do not show up in poll()
+    for (auto* c : cs) buffered |= c->conn->pending();
+    if (poll(pfs.data(), pfs.size(), buffered ? 0 : 50) <= 0 && !buffered) continue;
     if (pfs[0].revents & POLLIN) {
       const int fd = accept(s->listen_fd, nullptr, nullptr);
       if (fd >= 0) {
         int one = 1;
         setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
         CtlMsg m;
-        if (rd(fd, &m, sizeof(m)) && m.magic == kMagic && (m.op == C_INIT || m.op == C_REINIT)) {
+        std::string err;
+        std::unique_ptr<ub::SecureConn> conn = ub::SecureConn::server(fd, s->psk, 3000, &err);
+        if (!conn) {
+          std::lock_guard<std::mutex> l(s->mu);
+          ++s->mem.st.tls_rejected;
+          close(fd);
+        } else if (conn->read_full(&m, sizeof(m), 3000) && m.magic == kMagic && (m.op == C_INIT || m.op == C_REINIT)) {
           std::lock_guard<std::mutex> l(s->mu);
           CtlMsg out = m;
           out.epoch = s->epoch;
           if (s->clients.size() >= s->cfg.max_clients) {
             out.status = DLOCK_SERVER_FULL;
-            wr(fd, &out, sizeof(out));
+            conn->write_full(&out, sizeof(out));
+            conn.reset();
             close(fd);
           } else {
             SrvClient* c = new SrvClient();
             c->id = m.op == C_REINIT && m.client_id >= 0 ? m.client_id : (int32_t)s->clients.size() + 1000 * (int32_t)(s->epoch & 0xff);
             c->fd = fd;
+            out.secure = 0;
+            if (conn->encrypted() && ub::random_bytes(out.data_key, sizeof(out.data_key))) {
+              out.secure = 1;
+              c->key.set(out.data_key, true);
+            }
             c->last_seen = ub::now_ns();
             c->ep = urma_simple_ep_import(s->ctx, m.ep_blob, 0x646c);
             s->clients.push_back(c);
@@ -418,9 +477,12 @@ void srv_ctl_loop(Server* s) {
             out.status = c->ep ? DLOCK_SUCCESS : DLOCK_FAIL;
             urma_simple_ep_blob(s->ep, out.ep_blob);
             memcpy(out.seg_blob, s->obj_blob, sizeof(out.seg_blob));
-            wr(fd, &out, sizeof(out));
+            if (conn->encrypted() && !out.secure) out.status = DLOCK_FAIL;  // no randomness for a data key
+            conn->write_full(&out, sizeof(out));
+            c->conn = std::move(conn);
           }
         } else {
+          conn.reset();
           close(fd);
         }
       }
@@ -432,9 +494,9 @@ void srv_ctl_loop(Server* s) {
         c->alive = false;  // connection lost: the client's leases run out on their own
         continue;
       }
-      if (pfs[i].revents & POLLIN) {
+      if ((pfs[i].revents & POLLIN) || c->conn->pending()) {
         CtlMsg m;
-        if (!rd(c->fd, &m, sizeof(m), 1000) || m.magic != kMagic) {
+        if (!c->conn->read_full(&m, sizeof(m), 1000) || m.magic != kMagic) {
           std::lock_guard<std::mutex> l(s->mu);
           c->alive = false;
           continue;
@@ -462,16 +524,28 @@ void srv_cmd_loop(Server* s) {
       if (!(flag[i] & URMA_CR_FLAG_RECV)) {
         if (uc[i]) {
           std::lock_guard<std::mutex> l(s->mu);
-          s->tx_free.push_back(reinterpret_cast<CmdMsg*>(uc[i]));
+          s->tx_free.push_back(reinterpret_cast<CmdWire*>(uc[i]));
         }
         continue;
       }
-      CmdMsg* in = reinterpret_cast<CmdMsg*>(uc[i]);
-      CmdMsg reply = *in;
+      CmdWire* wire = reinterpret_cast<CmdWire*>(uc[i]);
+      CmdMsg cmd{};
+      CmdMsg* in = &cmd;
+      CmdMsg reply{};
       urma_target_jetty_t* dst = nullptr;
+      SrvClient* from = nullptr;
       {
         std::lock_guard<std::mutex> l(s->mu);
         ++s->mem.st.data_msgs;
+        for (auto* c : s->clients)
+          if (c->id == wire->client_id && c->alive) from = c;
+        // a command that does not open under its sender's key (or comes in clear to a secured server) is dropped
+        if (st[i] != 0 || !from || !unpack_cmd(*wire, &cmd, &from->key)) {
+          ++s->mem.st.sealed_rejected;
+          urma_simple_post_recv(s->ep, wire, sizeof(CmdWire), reinterpret_cast<uint64_t>(wire));
+          continue;
+        }
+        reply = cmd;
         if (s->recovering) {
           if (s->recovered_clients >= s->cfg.recovery_client_num || ub::now_ns() > s->recovery_deadline)
             s->recovering = false;
@@ -480,12 +554,11 @@ void srv_cmd_loop(Server* s) {
         else if (s->recovering) reply.status = DLOCK_NOT_READY;
         else reply.status = s->mem.apply(in->client_id, in->lock_id, in->op, in->expire_ms);
         reply.epoch = s->epoch;
-        for (auto* c : s->clients)
-          if (c->id == in->client_id && c->alive) dst = c->ep;
+        dst = from->ep;
       }
-      urma_simple_post_recv(s->ep, in, sizeof(CmdMsg), reinterpret_cast<uint64_t>(in));
+      urma_simple_post_recv(s->ep, wire, sizeof(CmdWire), reinterpret_cast<uint64_t>(wire));
       if (!dst) continue;
-      CmdMsg* out = nullptr;
+      CmdWire* out = nullptr;
       {
         std::lock_guard<std::mutex> l(s->mu);
         if (!s->tx_free.empty()) {
@@ -494,9 +567,12 @@ void srv_cmd_loop(Server* s) {
         }
       }
       if (!out) continue;  // reply ring exhausted: the client retries after its timeout
-      *out = reply;
+      {
+        std::lock_guard<std::mutex> l(s->mu);
+        pack_cmd(out, reply, &from->key);
+      }
       if (urma_simple_post(s->ep, dst, URMA_OPC_SEND, nullptr, 0, nullptr, reinterpret_cast<uint64_t>(out),
-                           sizeof(CmdMsg), 0, reinterpret_cast<uint64_t>(out), 1) != 0) {
+                           sizeof(CmdWire), 0, reinterpret_cast<uint64_t>(out), 1) != 0) {
         std::lock_guard<std::mutex> l(s->mu);
         s->tx_free.push_back(out);
       }
@@ -514,6 +590,8 @@ struct HeldLock {
 struct Client {
   int32_t id = -1;
   int fd = -1;
+  std::unique_ptr<ub::SecureConn> conn;
+  DataKey key;
   uint32_t epoch = 0;
   urma_context_t* ctx = nullptr;
   urma_simple_ep_t* ep = nullptr;
@@ -522,7 +600,8 @@ struct Client {
   uint64_t obj_va = 0;
   std::mutex mu;
   uint32_t seq = 1;
-  CmdMsg tx, rx[8];
+  CmdMsg tx;
+  CmdWire tx_wire, rx[8];
   uint64_t result;
   std::map<int32_t, HeldLock> locks;  // lock id -> description and state (the recovery cache)
   dlock_debug_stats_t st{};
@@ -541,7 +620,8 @@ int ctl_call(Client* c, CtlMsg* m) {
   m->magic = kMagic;
   m->client_id = c->id;
   ++c->st.control_msgs;
-  if (!wr(c->fd, m, sizeof(*m)) || !rd(c->fd, m, sizeof(*m))) return DLOCK_BAD_RESPONSE;
+  if (!c->conn || !c->conn->write_full(m, sizeof(*m)) || !c->conn->read_full(m, sizeof(*m), 3000))
+    return DLOCK_BAD_RESPONSE;
   if (m->epoch != c->epoch) return DLOCK_BAD_RESPONSE;
   return m->status;
 }
@@ -559,17 +639,35 @@ int connect_server(Client* c, const char* ip, uint16_t port, bool reinit) {
   }
   int one = 1;
   setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+  bool bad_key = false;
+  const ub::PskConfig psk = current_psk(&bad_key);
+  if (bad_key) {
+    close(fd);
+    return DLOCK_EINVAL;
+  }
+  std::string err;
+  std::unique_ptr<ub::SecureConn> conn = ub::SecureConn::client(fd, psk, 3000, &err);
+  if (!conn) {
+    close(fd);
+    return DLOCK_BAD_RESPONSE;  // the server refused the key, speaks no TLS, or is gone
+  }
   CtlMsg m{};
   m.magic = kMagic;
   m.op = reinit ? C_REINIT : C_INIT;
   m.client_id = c->id;
   urma_simple_ep_blob(c->ep, m.ep_blob);
-  if (!wr(fd, &m, sizeof(m)) || !rd(fd, &m, sizeof(m)) || m.status != DLOCK_SUCCESS) {
+  if (!conn->write_full(&m, sizeof(m)) || !conn->read_full(&m, sizeof(m), 3000) || m.status != DLOCK_SUCCESS ||
+      (conn->encrypted() && !m.secure)) {
+    conn.reset();
     close(fd);
     return m.status ? m.status : DLOCK_BAD_RESPONSE;
   }
+  c->conn.reset();
   if (c->fd >= 0) close(c->fd);
   c->fd = fd;
+  c->conn = std::move(conn);
+  if (m.secure) c->key.set(m.data_key, false);
+  else c->key = DataKey();
   c->id = m.client_id;
   c->epoch = m.epoch;
   if (c->srv) urma_unimport_jetty(c->srv);
@@ -585,8 +683,9 @@ int connect_server(Client* c, const char* ip, uint16_t port, bool reinit) {
 int data_call(Client* c, int32_t lock_id, uint32_t op, uint32_t expire_ms) {
   c->tx = CmdMsg{kMagic, c->seq++, c->id, lock_id, op, expire_ms, 0, c->epoch};
   ++c->st.data_msgs;
-  if (urma_simple_post(c->ep, c->srv, URMA_OPC_SEND, nullptr, 0, nullptr, reinterpret_cast<uint64_t>(&c->tx),
-                       sizeof(CmdMsg), 0, 0, 0) != 0)
+  pack_cmd(&c->tx_wire, c->tx, &c->key);
+  if (urma_simple_post(c->ep, c->srv, URMA_OPC_SEND, nullptr, 0, nullptr, reinterpret_cast<uint64_t>(&c->tx_wire),
+                       sizeof(CmdWire), 0, 0, 0) != 0)
     return DLOCK_BAD_RESPONSE;
   int st[4];
   uint64_t uc[4], imm[4];
@@ -599,10 +698,11 @@ int data_call(Client* c, int32_t lock_id, uint32_t op, uint32_t expire_ms) {
         if (st[i] != 0) return DLOCK_BAD_RESPONSE;
         continue;
       }
-      CmdMsg* r = reinterpret_cast<CmdMsg*>(uc[i]);
-      const CmdMsg got = *r;
-      urma_simple_post_recv(c->ep, r, sizeof(CmdMsg), reinterpret_cast<uint64_t>(r));
-      if (got.magic == kMagic && got.seq == c->tx.seq) {
+      CmdWire* r = reinterpret_cast<CmdWire*>(uc[i]);
+      CmdMsg got{};
+      const bool opened = unpack_cmd(*r, &got, &c->key);
+      urma_simple_post_recv(c->ep, r, sizeof(CmdWire), reinterpret_cast<uint64_t>(r));
+      if (opened && got.magic == kMagic && got.seq == c->tx.seq) {
         if (got.epoch != c->epoch) return DLOCK_BAD_RESPONSE;
         return got.status;
       }
@@ -620,6 +720,12 @@ int dlock_server_start(const dlock_server_cfg_t* cfg, int* server_id, uint16_t* 
   if (!cfg || !server_id) return DLOCK_EINVAL;
   Server* s = new Server();
   s->cfg = *cfg;
+  bool bad_key = false;
+  s->psk = current_psk(&bad_key);
+  if (bad_key) {  // a malformed key must not silently leave the server in clear text
+    delete s;
+    return DLOCK_EINVAL;
+  }
   if (!s->cfg.max_clients) s->cfg.max_clients = 1000;
   if (!s->cfg.max_locks) s->cfg.max_locks = 51200;
   if (!s->cfg.max_objects) s->cfg.max_objects = 4096;
@@ -641,7 +747,7 @@ int dlock_server_start(const dlock_server_cfg_t* cfg, int* server_id, uint16_t* 
     return DLOCK_FAIL;
   }
   s->rx.resize(512);
-  for (auto& m : s->rx) urma_simple_post_recv(s->ep, &m, sizeof(CmdMsg), reinterpret_cast<uint64_t>(&m));
+  for (auto& m : s->rx) urma_simple_post_recv(s->ep, &m, sizeof(CmdWire), reinterpret_cast<uint64_t>(&m));
   s->tx.resize(512);
   for (auto& m : s->tx) s->tx_free.push_back(&m);
   s->listen_fd = socket(AF_INET, SOCK_STREAM, 0);
@@ -686,6 +792,7 @@ int dlock_server_stop(int server_id) {
   s->cmd.join();
   close(s->listen_fd);
   for (auto* c : s->clients) {
+    c->conn.reset();
     close(c->fd);
     if (c->ep) urma_unimport_jetty(c->ep);
     delete c;
@@ -694,6 +801,19 @@ int dlock_server_stop(int server_id) {
   urma_simple_ep_destroy(s->ep);
   urma_simple_close(s->ctx);
   delete s;
+  return DLOCK_SUCCESS;
+}
+
+int dlock_set_psk(const char* key_hex, const char* identity) {
+  ub::PskConfig cfg;
+  if (key_hex && *key_hex) {
+    if (!ub::PskConfig::parse_hex(key_hex, &cfg.key) || cfg.key.size() < 16 || cfg.key.size() > 64) return DLOCK_EINVAL;
+  }
+  if (identity && *identity) cfg.identity = identity;
+  std::lock_guard<std::mutex> l(g_psk_mu);
+  g_psk = cfg;
+  g_psk_loaded = true;
+  g_psk_bad = false;
   return DLOCK_SUCCESS;
 }
 
@@ -715,7 +835,7 @@ int dlock_client_init(int* client_id, const char* ip, uint16_t port) {
     delete c;
     return DLOCK_FAIL;
   }
-  for (auto& m : c->rx) urma_simple_post_recv(c->ep, &m, sizeof(CmdMsg), reinterpret_cast<uint64_t>(&m));
+  for (auto& m : c->rx) urma_simple_post_recv(c->ep, &m, sizeof(CmdWire), reinterpret_cast<uint64_t>(&m));
   const int rc = connect_server(c, ip, port, false);
   if (rc != DLOCK_SUCCESS) {
     urma_simple_ep_destroy(c->ep);
@@ -748,6 +868,7 @@ int dlock_client_deinit(int handle) {
   CtlMsg m{};
   m.op = C_DEINIT;
   ctl_call(c, &m);
+  c->conn.reset();
   close(c->fd);
   if (c->srv) urma_unimport_jetty(c->srv);
   if (c->objseg) urma_unimport_seg(c->objseg);

@@ -55,8 +55,15 @@ typedef struct dlock_lock_req {
 
 typedef struct dlock_debug_stats {
   uint64_t trylock_ok, trylock_busy, unlock_ok, unlock_fail, extend_ok, expired_takeover, heartbeat, recovered_locks,
-      control_msgs, data_msgs, objects, object_ops, clients;
+      control_msgs, data_msgs, objects, object_ops, clients,
+      tls_rejected,    /* control connections refused: TLS handshake failed (wrong key, clear-text client) */
+      sealed_rejected; /* data-channel commands dropped: unknown sender, bad seal, replay, or clear text to a secured server */
 } dlock_debug_stats_t;
+
+/* Security: a pre-shared key (hex, 16..64 bytes) switches the control channel to TLS 1.3 PSK and seals the data
+ * channel with AES-256-GCM; an empty key switches both off. Applies to servers started and clients initialised
+ * afterwards. Without a call the key comes from DLOCK_PSK / DLOCK_PSK_ID in the environment. */
+DLOCK_EXPORT int dlock_set_psk(const char* key_hex, const char* identity);
 
 /* server */
 DLOCK_EXPORT int dlock_server_start(const dlock_server_cfg_t* cfg, int* server_id, uint16_t* port_out);

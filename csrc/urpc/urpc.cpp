@@ -32,6 +32,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "ub_secure.h"
 #include "ub_util.h"
 #include "umq_api.h"
 #include "urpc_proto.h"
@@ -44,6 +45,8 @@ constexpr uint32_t kHelloMagic = 0x55525043;  // "URPC"
 struct Hello {
   uint32_t magic, version, blob_len, channel;
   uint8_t blob[UMQ_BIND_INFO_SIZE];
+  uint32_t sealed;        // response: 1 = data_key is valid and every payload must be sealed with it
+  uint8_t data_key[32];   // only ever sent inside the TLS channel
 };
 
 struct Pending {
@@ -60,10 +63,27 @@ struct Ready {
   int status;
   umq_buf_t* buf;  // owns the payload (may be null)
 };
+// Payload sealing of one connection (channel on the client, session on the server): AES-256-GCM under a random key
+// that the server hands over inside the TLS handshake exchange. The 32-byte message header travels in clear as
+// additional authenticated data and carries the sender's message counter (bytes 20..27), which is the nonce.
+constexpr uint8_t kFlagSealed = 0x80;
+struct Sealer {
+  std::mutex mu;
+  std::unique_ptr<ub::AeadCipher> tx, rx;
+  uint64_t tx_nonce = 0, rx_last = 0;
+  void set(const uint8_t key[32], bool is_server) {
+    tx.reset(new ub::AeadCipher(key, is_server ? 1u : 0u));
+    rx.reset(new ub::AeadCipher(key, is_server ? 0u : 1u));
+  }
+  bool on() const { return tx != nullptr; }
+};
+
 struct Channel {
   uint32_t id;
   uint64_t umqh = 0;
   int tcp = -1;
+  std::unique_ptr<ub::SecureConn> conn;
+  Sealer seal;
   std::atomic<bool> attached{false};
   std::atomic<bool> lost{false};
   std::mutex mu;
@@ -76,6 +96,8 @@ struct Session {
   uint64_t umqh;
   int tcp;
   uint32_t id;
+  std::unique_ptr<ub::SecureConn> conn;
+  Sealer seal;
 };
 struct Func {
   urpc_func_t fn;
@@ -102,6 +124,9 @@ struct Global {
   std::string admin_path;
   std::thread admin_thr;
   std::atomic<bool> admin_stop{false};
+  ub::PskConfig psk;
+  ub::PskConfig server_psk;   // the key in force when the server was started
+  bool psk_set = false;   // urpc_set_psk was called: the environment is not consulted
 };
 Global g;
 
@@ -138,13 +163,17 @@ uint64_t make_queue(const char* name) {
   return umq_create(&o);
 }
 
-int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, const void* flat, uint32_t flat_len) {
+int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, const void* flat, uint32_t flat_len,
+             Sealer* seal = nullptr) {
   uint32_t total = flat_len;
   for (uint32_t i = 0; i < nsg; ++i) total += sg[i].len;
-  umq_buf_t* b = umq_buf_alloc(sizeof(urpc_req_head_t) + total, 1, umqh);
+  const bool sealed = seal && seal->on();
+  const uint32_t tag = sealed ? (uint32_t)ub::AeadCipher::kTagBytes : 0u;
+  umq_buf_t* b = umq_buf_alloc(sizeof(urpc_req_head_t) + total + tag, 1, umqh);
   if (!b) return URPC_ERR_EAGAIN;
   Head hh = h;
   hh.total_size = total;
+  if (sealed) hh.flags |= kFlagSealed;
   urpc_proto::encode(hh, reinterpret_cast<urpc_req_head_t*>(b->buf_data));
   char* p = b->buf_data + sizeof(urpc_req_head_t);
   for (uint32_t i = 0; i < nsg; ++i) {
@@ -152,7 +181,21 @@ int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, c
     p += sg[i].len;
   }
   if (flat_len) memcpy(p, flat, flat_len);
-  b->data_size = sizeof(urpc_req_head_t) + total;
+  if (sealed) {
+    // seal in place: header (with the message counter) authenticated, payload encrypted, tag appended
+    std::lock_guard<std::mutex> l(seal->mu);
+    uint8_t* hb = reinterpret_cast<uint8_t*>(b->buf_data);
+    const uint64_t nonce = ++seal->tx_nonce;
+    urpc_proto::put_le(hb + 20, nonce, 8);
+    uint8_t* body = hb + sizeof(urpc_req_head_t);
+    std::vector<uint8_t> ct(total + tag);
+    if (!seal->tx->seal(nonce, hb, sizeof(urpc_req_head_t), body, total, ct.data())) {
+      umq_buf_free(b);
+      return URPC_FAIL;
+    }
+    memcpy(body, ct.data(), ct.size());
+  }
+  b->data_size = sizeof(urpc_req_head_t) + total + tag;
   umq_buf_t* bad = nullptr;
   const uint64_t deadline = ub::now_ns() + 2000000000ull;
   for (;;) {
@@ -169,6 +212,25 @@ int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, c
   return URPC_SUCCESS;
 }
 
+// Checks and removes the seal of a received message in place. False = drop it: sealed without a key, clear although a
+// key is set, replayed counter, or bad tag.
+bool open_msg(umq_buf_t* b, const Head& h, Sealer* seal) {
+  const bool sealed = (h.flags & kFlagSealed) != 0;
+  if (!seal || !seal->on()) return !sealed;
+  if (!sealed || b->data_size < sizeof(urpc_req_head_t) + ub::AeadCipher::kTagBytes) return false;
+  std::lock_guard<std::mutex> l(seal->mu);
+  uint8_t* hb = reinterpret_cast<uint8_t*>(b->buf_data);
+  const uint64_t nonce = urpc_proto::get_le(hb + 20, 8);
+  if (nonce <= seal->rx_last) return false;
+  const size_t n_sealed = b->data_size - sizeof(urpc_req_head_t);
+  std::vector<uint8_t> pt(n_sealed);
+  if (!seal->rx->open(nonce, hb, sizeof(urpc_req_head_t), hb + sizeof(urpc_req_head_t), n_sealed, pt.data())) return false;
+  seal->rx_last = nonce;
+  memcpy(hb + sizeof(urpc_req_head_t), pt.data(), n_sealed - ub::AeadCipher::kTagBytes);
+  b->data_size -= ub::AeadCipher::kTagBytes;
+  return true;
+}
+
 // Drains the channel's queue: responses complete pending calls, expired calls time out. Caller holds ch->mu.
 void channel_progress(Channel* ch) {
   for (;;) {
@@ -177,7 +239,11 @@ void channel_progress(Channel* ch) {
     Head h;
     if (b->data_size < sizeof(urpc_req_head_t) ||
         !urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) ||
-        (h.type != URPC_MSG_RSP && h.type != URPC_MSG_ACK_AND_RSP)) {
+        (h.type != URPC_MSG_RSP && h.type != URPC_MSG_ACK_AND_RSP) || !open_msg(b, h, &ch->seal)) {
+      if (b->data_size >= sizeof(urpc_req_head_t)) {
+        std::lock_guard<std::mutex> l(g.stat_mu);
+        ++g.stats.errors;
+      }
       umq_buf_free(b);
       continue;
     }
@@ -233,6 +299,22 @@ void channel_progress(Channel* ch) {
   }
 }
 
+// The key in force: the one given to urpc_set_psk, else URPC_PSK / URPC_PSK_ID from the environment (a malformed
+// environment key yields a key nobody else has, so that connections fail instead of running in clear text).
+ub::PskConfig current_psk() {
+  std::lock_guard<std::mutex> l(g.mu);
+  if (!g.psk_set) {
+    bool bad = false;
+    g.psk = ub::PskConfig::from_env("URPC", &bad);
+    if (bad) {
+      g.psk.key.assign(32, 0);
+      ub::random_bytes(g.psk.key.data(), g.psk.key.size());
+    }
+    g.psk_set = true;
+  }
+  return g.psk;
+}
+
 void accept_loop() {
   while (!g.stop.load()) {
     pollfd pf{g.listen_fd, POLLIN, 0};
@@ -242,26 +324,54 @@ void accept_loop() {
     int one = 1;
     setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
     Hello hello;
-    if (!read_full(fd, &hello, sizeof(hello)) || hello.magic != kHelloMagic || hello.version != urpc_proto::kVersion) {
+    std::string err;
+    std::unique_ptr<ub::SecureConn> conn = ub::SecureConn::server(fd, g.server_psk, 3000, &err);
+    if (!conn) {  // wrong key, clear-text client, or a client that stalled in the handshake
+      std::lock_guard<std::mutex> l(g.stat_mu);
+      ++g.stats.errors;
+      close(fd);
+      continue;
+    }
+    if (!conn->read_full(&hello, sizeof(hello), 5000) || hello.magic != kHelloMagic ||
+        hello.version != urpc_proto::kVersion) {
+      conn.reset();
       close(fd);
       continue;
     }
     const uint64_t q = make_queue("urpc-srv");
-    Hello rsp{kHelloMagic, urpc_proto::kVersion, 0, 0, {0}};
+    Hello rsp{};
+    rsp.magic = kHelloMagic;
+    rsp.version = urpc_proto::kVersion;
     if (!q || umq_bind(q, hello.blob, hello.blob_len) != UMQ_SUCCESS) {
       if (q) umq_destroy(q);
+      conn.reset();
       close(fd);
       continue;
     }
     rsp.blob_len = umq_bind_info_get(q, rsp.blob, sizeof(rsp.blob));
-    Session* s = new Session{q, fd, 0};
+    Session* s = new Session();
+    s->umqh = q;
+    s->tcp = fd;
+    s->id = 0;
+    if (conn->encrypted()) {
+      if (!ub::random_bytes(rsp.data_key, sizeof(rsp.data_key))) {
+        umq_destroy(q);
+        delete s;
+        conn.reset();
+        close(fd);
+        continue;
+      }
+      rsp.sealed = 1;
+      s->seal.set(rsp.data_key, true);
+    }
     {
       std::lock_guard<std::mutex> l(g.mu);
       s->id = static_cast<uint32_t>(g.sessions.size());
       rsp.channel = s->id;
       g.sessions.push_back(s);
     }
-    if (!write_full(fd, &rsp, sizeof(rsp))) {
+    s->conn = std::move(conn);
+    if (!s->conn->write_full(&rsp, sizeof(rsp))) {
       // the client went away during the handshake; the session is reaped by server_poll when its socket closes
     }
   }
@@ -287,7 +397,7 @@ void keepalive_loop() {
           lost = true;
         } else {
           Head h{urpc_proto::kVersion, URPC_MSG_REQ, 1, URPC_FUNC_ID_KEEPALIVE, 0, ch->id, 0, 0};
-          send_msg(ch->umqh, h, nullptr, 0, nullptr, 0);
+          send_msg(ch->umqh, h, nullptr, 0, nullptr, 0, &ch->seal);
           ++ch->ka_outstanding;
           std::lock_guard<std::mutex> l2(g.stat_mu);
           ++g.stats.keepalive_sent;
@@ -314,6 +424,18 @@ Channel* get_channel(uint32_t id) {
 }  // namespace
 
 extern "C" {
+
+int urpc_set_psk(const char* key_hex, const char* identity) {
+  ub::PskConfig cfg;
+  if (key_hex && *key_hex) {
+    if (!ub::PskConfig::parse_hex(key_hex, &cfg.key) || cfg.key.size() < 16 || cfg.key.size() > 64) return URPC_ERR_EINVAL;
+  }
+  if (identity && *identity) cfg.identity = identity;
+  std::lock_guard<std::mutex> l(g.mu);
+  g.psk = cfg;
+  g.psk_set = true;
+  return URPC_SUCCESS;
+}
 
 int urpc_init(const urpc_config_t* cfg) {
   std::lock_guard<std::mutex> l(g.mu);
@@ -345,12 +467,14 @@ void urpc_uninit(void) {
   if (g.listen_fd >= 0) close(g.listen_fd);
   g.listen_fd = -1;
   for (auto& kv : g.channels) {
+    kv.second->conn.reset();
     if (kv.second->tcp >= 0) close(kv.second->tcp);
     if (kv.second->umqh) umq_destroy(kv.second->umqh);
     delete kv.second;
   }
   g.channels.clear();
   for (Session* s : g.sessions) {
+    s->conn.reset();
     if (s->tcp >= 0) close(s->tcp);
     umq_destroy(s->umqh);
     delete s;
@@ -377,6 +501,7 @@ int urpc_server_start(const char* ip, uint16_t port) {
   }
   socklen_t len = sizeof(a);
   getsockname(fd, reinterpret_cast<sockaddr*>(&a), &len);
+  g.server_psk = current_psk();
   g.listen_fd = fd;
   g.accept_thr = std::thread(accept_loop);
   return ntohs(a.sin_port);
@@ -408,7 +533,12 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
       if (!b) break;
       Head h;
       if (b->data_size < sizeof(urpc_req_head_t) ||
-          !urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) || h.type != URPC_MSG_REQ) {
+          !urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) || h.type != URPC_MSG_REQ ||
+          !open_msg(b, h, &s->seal)) {
+        if (b->data_size >= sizeof(urpc_req_head_t)) {  // a request that fails the seal check is dropped and counted
+          std::lock_guard<std::mutex> l(g.stat_mu);
+          ++g.stats.errors;
+        }
         umq_buf_free(b);
         continue;
       }
@@ -416,7 +546,7 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
       const uint32_t alen = b->data_size - sizeof(urpc_req_head_t);
       Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, h.func_id, h.req_id, h.channel, 0, 0};
       if (h.func_id == URPC_FUNC_ID_KEEPALIVE) {
-        send_msg(s->umqh, rh, nullptr, 0, nullptr, 0);
+        send_msg(s->umqh, rh, nullptr, 0, nullptr, 0, &s->seal);
         umq_buf_free(b);
         continue;
       }
@@ -435,7 +565,7 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         uint32_t rlen = static_cast<uint32_t>(rsp.size());
         const int st = f.fn(args, alen, rsp.data(), &rlen, f.ctx);
         rh.status = static_cast<int8_t>(st);
-        send_msg(s->umqh, rh, nullptr, 0, rsp.data(), rlen > rsp.size() ? 0 : rlen);
+        send_msg(s->umqh, rh, nullptr, 0, rsp.data(), rlen > rsp.size() ? 0 : rlen, &s->seal);
         umq_buf_free(b);
       } else if (msgs && n < max) {
         msgs[n].event = URPC_POLL_REQ;
@@ -449,7 +579,7 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         ++n;
       } else {
         rh.status = static_cast<int8_t>(URPC_ERR_FUNC_NOT_FOUND);
-        send_msg(s->umqh, rh, nullptr, 0, nullptr, 0);
+        send_msg(s->umqh, rh, nullptr, 0, nullptr, 0, &s->seal);
         umq_buf_free(b);
       }
     }
@@ -468,7 +598,7 @@ int urpc_func_return(const urpc_poll_msg_t* req, const void* rsp, uint32_t len, 
   if (!s) return URPC_ERR_EINVAL;
   Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, req->func_id, req->req_id,
           static_cast<uint32_t>(req->user_ctx & 0xffffff), 0, static_cast<int8_t>(status)};
-  return send_msg(s->umqh, rh, nullptr, 0, rsp, len);
+  return send_msg(s->umqh, rh, nullptr, 0, rsp, len, &s->seal);
 }
 
 int urpc_channel_create(void) {
@@ -500,14 +630,32 @@ int urpc_channel_server_attach(uint32_t chid, const char* ip, uint16_t port) {
   }
   int one = 1;
   setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
-  Hello hello{kHelloMagic, urpc_proto::kVersion, 0, chid, {0}};
-  hello.blob_len = umq_bind_info_get(ch->umqh, hello.blob, sizeof(hello.blob));
-  Hello rsp;
-  if (!write_full(fd, &hello, sizeof(hello)) || !read_full(fd, &rsp, sizeof(rsp)) || rsp.magic != kHelloMagic ||
-      umq_bind(ch->umqh, rsp.blob, rsp.blob_len) != UMQ_SUCCESS) {
+  std::string err;
+  std::unique_ptr<ub::SecureConn> conn = ub::SecureConn::client(fd, current_psk(), 3000, &err);
+  if (!conn) {
     close(fd);
     return URPC_FAIL;
   }
+  Hello hello{};
+  hello.magic = kHelloMagic;
+  hello.version = urpc_proto::kVersion;
+  hello.channel = chid;
+  hello.blob_len = umq_bind_info_get(ch->umqh, hello.blob, sizeof(hello.blob));
+  Hello rsp;
+  if (!conn->write_full(&hello, sizeof(hello)) || !conn->read_full(&rsp, sizeof(rsp), 5000) ||
+      rsp.magic != kHelloMagic || (conn->encrypted() && !rsp.sealed) ||
+      umq_bind(ch->umqh, rsp.blob, rsp.blob_len) != UMQ_SUCCESS) {
+    conn.reset();
+    close(fd);
+    return URPC_FAIL;
+  }
+  {
+    std::lock_guard<std::mutex> l(ch->seal.mu);
+    if (rsp.sealed) ch->seal.set(rsp.data_key, false);
+    else ch->seal.tx.reset(), ch->seal.rx.reset();
+    ch->seal.tx_nonce = ch->seal.rx_last = 0;
+  }
+  ch->conn = std::move(conn);
   ch->tcp = fd;
   ch->lost = false;
   ch->attached = true;
@@ -520,6 +668,7 @@ int urpc_channel_server_detach(uint32_t chid) {
   std::lock_guard<std::mutex> l(ch->mu);
   ch->attached = false;
   umq_unbind(ch->umqh);
+  ch->conn.reset();
   if (ch->tcp >= 0) close(ch->tcp);
   ch->tcp = -1;
   for (auto& kv : ch->pending)
@@ -539,6 +688,7 @@ int urpc_channel_destroy(uint32_t chid) {
     ch = it->second;
     g.channels.erase(it);
   }
+  ch->conn.reset();
   if (ch->tcp >= 0) close(ch->tcp);
   for (auto& r : ch->ready)
     if (r.buf) umq_buf_free(r.buf);
@@ -564,7 +714,7 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
     p.sync = opt && opt->sync;
     ch->pending[req_id] = std::move(p);
     Head h{urpc_proto::kVersion, URPC_MSG_REQ, 1, wr->func_id, req_id, chid, 0, 0};
-    const int rc = send_msg(ch->umqh, h, wr->args, wr->num_args, nullptr, 0);
+    const int rc = send_msg(ch->umqh, h, wr->args, wr->num_args, nullptr, 0, &ch->seal);
     if (rc != URPC_SUCCESS) {
       ch->pending.erase(req_id);
       std::lock_guard<std::mutex> l2(g.stat_mu);
@@ -679,7 +829,8 @@ static std::string admin_report(const std::string& cmd) {
   } else if (cmd == "sessions") {
     std::lock_guard<std::mutex> l(g.mu);
     for (Session* s : g.sessions) {
-      snprintf(line, sizeof(line), "session %u tcp_fd %d queue %llx\n", s->id, s->tcp, (unsigned long long)s->umqh);
+      snprintf(line, sizeof(line), "session %u tcp_fd %d queue %llx control %s payload %s\n", s->id, s->tcp,
+               (unsigned long long)s->umqh, s->conn ? s->conn->cipher() : "none", s->seal.on() ? "sealed" : "clear");
       r += line;
     }
     if (r.empty()) r = "(no sessions)\n";

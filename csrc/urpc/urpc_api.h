@@ -75,6 +75,11 @@ typedef struct urpc_poll_msg {
 typedef int (*urpc_func_t)(const void* args, uint32_t len, void* rsp, uint32_t* rsp_len, void* ctx);
 typedef void (*urpc_keepalive_cb_t)(uint32_t chid, int alive, void* ctx);
 
+/* Security: a pre-shared key (hex, 16..64 bytes) makes the connection handshake run inside TLS 1.3 PSK
+ * (TLS_AES_256_GCM_SHA384) and seals every request / response payload with AES-256-GCM under a per-connection key
+ * the server hands out in that handshake. Empty key = off. Without a call the key comes from URPC_PSK /
+ * URPC_PSK_ID in the environment. Call before urpc_server_start / urpc_channel_server_attach. */
+URPC_EXPORT int urpc_set_psk(const char* key_hex, const char* identity);
 URPC_EXPORT int urpc_init(const urpc_config_t* cfg);
 URPC_EXPORT void urpc_uninit(void);
 /* server */

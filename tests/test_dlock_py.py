@@ -82,3 +82,41 @@ def test_atomic_object_from_two_clients(service):
     assert a.atomic_snapshot(oa) == 5 + 4000
     assert b.atomic_cas(ob, 4005, 1) == 4005 and a.atomic_snapshot(oa) == 1
     assert b.atomic_cas(ob, 4005, 2) == 1 and a.atomic_snapshot(oa) == 1
+
+
+def test_secured_service_locks_work_and_wrong_keys_are_refused(tmp_path):
+    """With a pre-shared key the control channel is TLS 1.3 PSK and lock commands are sealed; a client with another
+    key or with none cannot join, and the server counts the refusals."""
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import dlock
+    key = "a1" * 32
+    dlock.set_psk(key, "locks")
+    srv = None
+    try:
+        srv = dlock.Server()
+        a, b = dlock.Client(srv.ip, srv.port), dlock.Client(srv.ip, srv.port)
+        la, lb = a.get_lock("S1", dlock.ATOMIC), b.get_lock("S1", dlock.ATOMIC)
+        assert a.trylock(la) is True and b.trylock(lb) is False
+        a.unlock(la)
+        assert b.trylock(lb) is True
+        b.unlock(lb)
+        obj = a.atomic_create("ctr", 5)
+        assert a.atomic_faa(obj, 3) == 5 and b.atomic_snapshot(b.atomic_get("ctr")) == 8
+        assert a.heartbeat() == 0
+        st = srv.stats()
+        assert st["sealed_rejected"] == 0 and st["tls_rejected"] == 0 and st["data_msgs"] >= 4
+        for bad_key, ident in (("b2" * 32, "locks"), (key, "other"), ("", "")):
+            dlock.set_psk(bad_key, ident)
+            with pytest.raises(dlock.DlockError):
+                dlock.Client(srv.ip, srv.port)
+        assert srv.stats()["tls_rejected"] == 3
+        dlock.set_psk(key, "locks")
+        a.close()
+        b.close()
+        with pytest.raises(dlock.DlockError):
+            dlock.set_psk("zz", "")          # malformed keys are refused, never ignored
+    finally:
+        if srv is not None:
+            srv.stop()
+        dlock.set_psk("", "")

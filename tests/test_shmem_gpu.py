@@ -71,3 +71,27 @@ def test_shmem_wait_times_out_with_status():
         assert int(torch.arange(10, device="cuda").sum().item()) == 45
     finally:
         heaps[0].close()
+
+
+@pytest.mark.parametrize("mode,piece", [(0, 0), (1, 0), (2, 2048), (2, 7168), (3, 4096), (3, 14336)])
+def test_put_patterns_copy_every_row(mode, piece):
+    """Each access pattern of the put-bandwidth probe moves every row to its scattered destination row."""
+    import ctypes
+    from umdk_b200 import _native
+    lib = _native.cam()
+    rows, rb = 1000, 14336
+    src = torch.randint(0, 255, (rows, rb), dtype=torch.uint8, device="cuda")
+    dst = torch.zeros_like(src)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    lib.umdk_shmem_put_bench.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
+                                         ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    rc = lib.umdk_shmem_put_bench(dst.data_ptr(), src.data_ptr(), rows, rb, piece, mode, 16, status.data_ptr(),
+                                  _native.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+    if mode == 0:
+        assert torch.equal(dst, src)
+    else:
+        perm = (torch.arange(rows) * 9973 + 17) % rows
+        assert torch.equal(dst[perm.cuda()], src)

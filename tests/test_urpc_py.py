@@ -47,3 +47,31 @@ def test_sync_async_timeout(rpc):
     assert ch.call(1, b"ab") == b"ba"
     st = urpc.stats()
     assert st["calls"] >= 12 and st["timeouts"] >= 1 and st["requests_served"] >= 11
+
+
+def test_secured_connection_seals_payloads_and_refuses_other_keys(tmp_path):
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import urpc
+    key = "5c" * 32
+    urpc.set_psk(key, "rpc")
+    urpc.init(default_timeout_ms=2000)
+    srv = urpc.Server()
+    try:
+        srv.register(1, lambda b: b[::-1])
+        ch = urpc.Channel(srv.ip, srv.port)
+        big = bytes(range(256)) * 100
+        assert ch.call(1, b"sealed") == b"delaes" and ch.call(1, big) == big[::-1]
+        rep = urpc.admin_query("sessions")
+        assert "TLS_AES_256_GCM_SHA384" in rep and "payload sealed" in rep
+        for bad_key, ident in (("6d" * 32, "rpc"), (key, "nobody"), ("", "")):
+            urpc.set_psk(bad_key, ident)
+            with pytest.raises(urpc.UrpcError):
+                urpc.Channel(srv.ip, srv.port)
+        urpc.set_psk(key, "rpc")
+        assert ch.call(1, b"still works") == b"skrow llits"
+        ch.close()
+    finally:
+        srv.stop()
+        urpc.uninit()
+        urpc.set_psk("", "")

@@ -54,7 +54,7 @@ def _targets():
                        includes=[CSRC / "common", CSRC / "urma", CSRC / "umq", CSRC / "urpc", CSRC / "dlock",
                                  CSRC / "usock"],
                        libs=["-L" + str(LIB), "-Wl,-rpath,$ORIGIN"] + ["-l" + d for d in deps] +
-                            ["-lpthread", "-ldl", "-lrt"],
+                            (["-lssl", "-lcrypto"] if name == "umdk_urma" else []) + ["-lpthread", "-ldl", "-lrt"],
                        deps=deps, out=LIB / f"lib{name}.so")
     cu_prov = sorted((CSRC / "urma_cuda").glob("*.cu"))
     if cu_prov and "umdk_urma" in t:

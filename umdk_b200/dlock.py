@@ -42,7 +42,8 @@ class _LockReq(ctypes.Structure):
 class _Stats(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in
                 ("trylock_ok", "trylock_busy", "unlock_ok", "unlock_fail", "extend_ok", "expired_takeover",
-                 "heartbeat", "recovered_locks", "control_msgs", "data_msgs", "objects", "object_ops", "clients")]
+                 "heartbeat", "recovered_locks", "control_msgs", "data_msgs", "objects", "object_ops", "clients",
+                 "tls_rejected", "sealed_rejected")]
 
 
 _lib_cache = None
@@ -57,6 +58,14 @@ def _lib():
 
 def _stats_dict(s: _Stats) -> dict:
     return {n: int(getattr(s, n)) for n, _ in _Stats._fields_}
+
+
+def set_psk(key_hex: str = "", identity: str = "") -> None:
+    """Pre-shared key for servers started and clients created afterwards: TLS 1.3 PSK on the control channel and
+    AES-256-GCM sealed lock commands on the data channel. An empty key switches both off."""
+    rc = _lib().dlock_set_psk(key_hex.encode(), identity.encode())
+    if rc != 0:
+        raise DlockError("set_psk", rc)
 
 
 class Server:

@@ -105,7 +105,8 @@ class DispatchResult:
     recv_count: torch.Tensor             # [E_local * R] inclusive prefix
     recv_tokens_per_expert: torch.Tensor # [E_local] int64
     recv_meta: torch.Tensor              # [a_cap, 2K+2]
-    counts: torch.Tensor                 # device [4]: rows N, arrivals A, max from one source
+    counts: torch.Tensor                 # device [4 + 32]: rows N, arrivals A, max from one source, 0; then the
+                                         # index of the first arrival of every source rank
     layout: LayoutResult
     topk_idx: torch.Tensor
     topk_weights: Optional[torch.Tensor]
@@ -157,7 +158,7 @@ class EpNormal:
             raise ValueError(f"symmetric heap too small: need {need} bytes, have {heap.nbytes}")
         dev = device or torch.device("cuda", torch.cuda.current_device())
         self.device = dev
-        self.ctrl = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.ctrl = torch.zeros(64, dtype=torch.int32, device=dev)
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
         self.layout_bar = torch.zeros(2, dtype=torch.int32, device=dev)
         self.layout_scratch = torch.empty(((cap + 31) // 32) * (num_experts + self.R), dtype=torch.int32, device=dev)
@@ -236,7 +237,7 @@ class EpNormal:
                 torch.empty(self.E, dtype=torch.int32, device=dev),
                 torch.empty(self.E // self.R, dtype=torch.int64, device=dev),
                 torch.empty(a_cap, 2 * K + 2, dtype=torch.int32, device=dev),
-                torch.zeros(4, dtype=torch.int32, device=dev), lay, topk_idx, topk_weights, T, quant)
+                torch.zeros(4 + MAX_RANKS, dtype=torch.int32, device=dev), lay, topk_idx, topk_weights, T, quant)
         p = _DispatchParams()
         p.R, p.rank, p.E, p.K, p.H, p.cap, p.quant, p.T = self.R, self.rank, self.E, K, H, self.cap, int(quant), T
         p.n_cap, p.a_cap = out.recv_x.shape[0], out.recv_meta.shape[0]

@@ -81,6 +81,21 @@ def init(dev: str = "shm0", keepalive_interval_ms: int = 0, keepalive_miss_limit
         raise UrpcError("urpc_init", rc)
 
 
+def set_psk(key_hex: str = "", identity: str = "") -> None:
+    """Pre-shared key for servers started and channels attached afterwards: the connection handshake runs in TLS 1.3
+    PSK and every payload is sealed with AES-256-GCM. An empty key switches both off."""
+    rc = _lib().urpc_set_psk(key_hex.encode(), identity.encode())
+    if rc != 0:
+        raise UrpcError("urpc_set_psk", rc)
+
+
+def admin_query(command: str) -> str:
+    """The management report (`version`, `stats`, `perf`, `channels`, `sessions`, `functions`) as text."""
+    buf = ctypes.create_string_buffer(16384)
+    n = _lib().urpc_admin_query(command.encode(), buf, len(buf))
+    return buf.value.decode() if n >= 0 else ""
+
+
 def uninit() -> None:
     _lib().urpc_uninit()
     _keep.clear()
