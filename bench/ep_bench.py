@@ -149,7 +149,7 @@ def bench_ll(rank, world, a):
     from umdk_b200.ops import reference as ref
     from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
     from umdk_b200.parallel.symm import SymmetricHeap
-    T, H, F, E, K = a.ll_tokens, 7168, 2048, 256, 8
+    T, H, F, E, K = a.ll_tokens, 7168, 2048, a.ll_experts, 8
     el = E // world
     g = torch.Generator(device="cuda").manual_seed(300 + rank)
     x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
@@ -246,6 +246,8 @@ def main():
     ap.add_argument("what", choices=["normal", "ll", "all"])
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--ll-tokens", type=int, default=128)
+    ap.add_argument("--ll-experts", type=int, default=256,
+                    help="routed experts in total; 32 on one GPU is the share of one rank at EP = 8, without the wire")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     a = ap.parse_args()

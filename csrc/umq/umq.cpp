@@ -12,9 +12,13 @@
 
 #include <stdlib.h>
 #include <string.h>
+#include <sys/syscall.h>
+#include <unistd.h>
 
 #include <atomic>
 #include <deque>
+#include <memory>
+#include <thread>
 #include <mutex>
 #include <unordered_map>
 #include <unordered_set>
@@ -75,15 +79,102 @@ struct Global {
 };
 Global g;
 
+// Trace: every thread owns a single-producer ring of {start, duration, record point} entries; a flusher thread wakes on
+// a timer, drains all rings and appends one text line per entry to the trace file. A full ring drops (and counts)
+// new entries instead of blocking the data path. Same shape as the reference's per-thread trace rings flushed by a
+// timer (src/urpc/umq/dfx/trace.c:72-526).
+struct TraceRec {
+  uint64_t t0, dt;
+  uint32_t rec, pad;
+};
+struct TraceRing {
+  std::vector<TraceRec> buf;
+  std::atomic<uint64_t> head{0}, tail{0};   // head: next slot the owner writes; tail: next slot the flusher reads
+  std::atomic<uint64_t> dropped{0};
+  uint64_t tid = 0;
+};
+struct Trace {
+  std::atomic<bool> on{false};
+  std::mutex mu;                            // guards rings, file, thread
+  std::vector<std::shared_ptr<TraceRing>> rings;
+  FILE* file = nullptr;
+  std::thread flusher;
+  std::atomic<bool> stop{false};
+  uint32_t interval_ms = 100, ring_entries = 4096;
+  std::atomic<uint64_t> generation{0};      // bumped at every start: threads re-register their ring
+  std::atomic<uint64_t> written{0};
+};
+Trace g_trace;
+const char* const kRecordNames[UMQ_PERF_RECORD_MAX] = {"enqueue", "dequeue", "post_tx", "poll_rx", "buf_alloc"};
+
+TraceRing* my_trace_ring() {
+  thread_local std::shared_ptr<TraceRing> ring;
+  thread_local uint64_t ring_gen = 0;
+  const uint64_t gen = g_trace.generation.load(std::memory_order_acquire);
+  if (!ring || ring_gen != gen) {
+    auto r = std::make_shared<TraceRing>();
+    r->buf.resize(g_trace.ring_entries);
+    r->tid = static_cast<uint64_t>(syscall(SYS_gettid));
+    std::lock_guard<std::mutex> l(g_trace.mu);
+    if (!g_trace.on.load()) return nullptr;
+    g_trace.rings.push_back(r);
+    ring = r;
+    ring_gen = gen;
+  }
+  return ring.get();
+}
+
+void trace_add(int rec, uint64_t t0, uint64_t dt) {
+  TraceRing* r = my_trace_ring();
+  if (!r) return;
+  const uint64_t h = r->head.load(std::memory_order_relaxed);
+  if (h - r->tail.load(std::memory_order_acquire) >= r->buf.size()) {
+    r->dropped.fetch_add(1, std::memory_order_relaxed);
+    return;
+  }
+  r->buf[h % r->buf.size()] = TraceRec{t0, dt, static_cast<uint32_t>(rec), 0};
+  r->head.store(h + 1, std::memory_order_release);
+}
+
+// Caller holds g_trace.mu.
+void trace_drain_locked() {
+  if (!g_trace.file) return;
+  for (auto& r : g_trace.rings) {
+    uint64_t t = r->tail.load(std::memory_order_relaxed);
+    const uint64_t h = r->head.load(std::memory_order_acquire);
+    for (; t < h; ++t) {
+      const TraceRec& e = r->buf[t % r->buf.size()];
+      fprintf(g_trace.file, "%llu %llu %s %llu\n", (unsigned long long)e.t0, (unsigned long long)r->tid,
+              e.rec < UMQ_PERF_RECORD_MAX ? kRecordNames[e.rec] : "?", (unsigned long long)e.dt);
+      g_trace.written.fetch_add(1, std::memory_order_relaxed);
+    }
+    r->tail.store(t, std::memory_order_release);
+  }
+  fflush(g_trace.file);
+}
+
+void trace_flush_loop() {
+  while (!g_trace.stop.load()) {
+    for (uint32_t slept = 0; slept < g_trace.interval_ms && !g_trace.stop.load(); slept += 5) usleep(5000);
+    std::lock_guard<std::mutex> l(g_trace.mu);
+    trace_drain_locked();
+  }
+}
+
 struct PerfScope {
   int rec;
   uint64_t t0;
-  explicit PerfScope(int r) : rec(r), t0(g.perf_on.load(std::memory_order_relaxed) ? ub::now_ns() : 0) {}
+  explicit PerfScope(int r)
+      : rec(r), t0((g.perf_on.load(std::memory_order_relaxed) || g_trace.on.load(std::memory_order_relaxed))
+                       ? ub::now_ns() : 0) {}
   ~PerfScope() {
     if (t0) {
       const uint64_t dt = ub::now_ns() - t0;
-      std::lock_guard<std::mutex> l(g.perf_mu);
-      g.perf[rec].add(dt);
+      if (g_trace.on.load(std::memory_order_relaxed)) trace_add(rec, t0, dt);
+      if (g.perf_on.load(std::memory_order_relaxed)) {
+        std::lock_guard<std::mutex> l(g.perf_mu);
+        g.perf[rec].add(dt);
+      }
     }
   }
 };
@@ -669,6 +760,47 @@ int umq_stats_perf_get(umq_perf_entry_t* e) {
     e[i].max_ns = g.perf[i].max();
     e[i].p99_ns = g.perf[i].quantile(0.99);
   }
+  return UMQ_SUCCESS;
+}
+int umq_trace_start(const char* path, uint32_t flush_interval_ms, uint32_t ring_entries) {
+  if (!path || !*path) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g_trace.mu);
+  if (g_trace.on.load()) return UMQ_ERR_EINVAL;
+  g_trace.file = fopen(path, "w");
+  if (!g_trace.file) return UMQ_FAIL;
+  fprintf(g_trace.file, "# start_ns tid record duration_ns\n");
+  g_trace.interval_ms = flush_interval_ms ? flush_interval_ms : 100;
+  g_trace.ring_entries = ring_entries ? ring_entries : 4096;
+  g_trace.rings.clear();
+  g_trace.written = 0;
+  g_trace.stop = false;
+  g_trace.generation.fetch_add(1, std::memory_order_release);
+  g_trace.on = true;
+  g_trace.flusher = std::thread(trace_flush_loop);
+  return UMQ_SUCCESS;
+}
+int umq_trace_stop(void) {
+  std::thread t;
+  {
+    std::lock_guard<std::mutex> l(g_trace.mu);
+    if (!g_trace.on.load()) return UMQ_ERR_EINVAL;
+    g_trace.on = false;
+    g_trace.stop = true;
+    t = std::move(g_trace.flusher);
+  }
+  if (t.joinable()) t.join();
+  std::lock_guard<std::mutex> l(g_trace.mu);
+  trace_drain_locked();
+  if (g_trace.file) fclose(g_trace.file);
+  g_trace.file = nullptr;
+  return UMQ_SUCCESS;
+}
+int umq_trace_stats(uint64_t* written, uint64_t* dropped) {
+  std::lock_guard<std::mutex> l(g_trace.mu);
+  uint64_t d = 0;
+  for (auto& r : g_trace.rings) d += r->dropped.load();
+  if (written) *written = g_trace.written.load();
+  if (dropped) *dropped = d;
   return UMQ_SUCCESS;
 }
 int umq_info_to_str(uint64_t h, char* buf, uint32_t len) {

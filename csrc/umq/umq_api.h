@@ -110,6 +110,12 @@ UMQ_EXPORT int umq_stats_qbuf_pool_get(umq_qbuf_stats_t* out);
 UMQ_EXPORT int umq_stats_perf_start(void);
 UMQ_EXPORT int umq_stats_perf_stop(void);
 UMQ_EXPORT int umq_stats_perf_get(umq_perf_entry_t* entries /* [UMQ_PERF_RECORD_MAX] */);
+/* Trace: one text line `start_ns tid record duration_ns` per API call at the perf record points, collected in
+ * per-thread rings (ring_entries each, 0 = 4096; a full ring drops and counts) and appended to `path` by a flusher
+ * thread every flush_interval_ms (0 = 100). */
+UMQ_EXPORT int umq_trace_start(const char* path, uint32_t flush_interval_ms, uint32_t ring_entries);
+UMQ_EXPORT int umq_trace_stop(void);
+UMQ_EXPORT int umq_trace_stats(uint64_t* written, uint64_t* dropped);
 UMQ_EXPORT int umq_info_to_str(uint64_t umqh, char* buf, uint32_t len);
 #ifdef __cplusplus
 }

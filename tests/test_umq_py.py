@@ -34,3 +34,29 @@ def test_messages_both_ways_in_order(pair):
     st = a.io_stats()
     assert st["tx_msgs"] >= 100 and st["tx_bytes"] >= sum(map(len, msgs))
     assert b.flow_control_stats()["credits_returned"] > 0 or b.flow_control_stats()["credits_granted"] > 0
+
+
+def test_trace_records_every_operation(pair, tmp_path):
+    umq, a, b = pair
+    path = tmp_path / "umq.trace"
+    umq.trace_start(str(path), flush_interval_ms=20)
+    for i in range(40):
+        a.send(bytes([i]) * 100)
+        assert b.recv() == bytes([i]) * 100
+    import time
+    time.sleep(0.1)                       # let the timer flush at least once while the trace is running
+    mid = path.read_text().count("\n")
+    st = umq.trace_stop()
+    lines = [l.split() for l in path.read_text().splitlines() if not l.startswith("#")]
+    assert mid > 1 and st["dropped"] == 0 and st["written"] == len(lines)
+    kinds = {l[2] for l in lines}
+    assert {"enqueue", "dequeue", "buf_alloc"} <= kinds
+    assert sum(1 for l in lines if l[2] == "enqueue") >= 40
+    assert all(int(l[0]) > 0 and int(l[3]) >= 0 for l in lines)
+    # a second trace with a tiny ring overflows between flushes: entries are dropped and counted, nothing blocks
+    umq.trace_start(str(tmp_path / "t2.trace"), flush_interval_ms=2000, ring_entries=8)
+    for i in range(40):
+        a.send(b"x")
+        assert b.recv() == b"x"
+    st2 = umq.trace_stop()
+    assert st2["dropped"] > 0 and st2["written"] <= 8 * 4

@@ -90,6 +90,25 @@ def uninit() -> None:
     _lib().umq_uninit()
 
 
+def trace_start(path: str, flush_interval_ms: int = 100, ring_entries: int = 4096) -> None:
+    """Starts writing one line `start_ns tid record duration_ns` per queue operation to `path` (per-thread rings
+    drained by a timer thread)."""
+    rc = _lib().umq_trace_start(path.encode(), flush_interval_ms, ring_entries)
+    if rc != 0:
+        raise UmqError(f"umq_trace_start failed: {rc}")
+
+
+def trace_stop() -> dict:
+    """Stops the trace, flushes what is left and returns {"written", "dropped"}."""
+    lib = _lib()
+    rc = lib.umq_trace_stop()
+    if rc != 0:
+        raise UmqError(f"umq_trace_stop failed: {rc}")
+    w, d = ctypes.c_uint64(), ctypes.c_uint64()
+    lib.umq_trace_stats(ctypes.byref(w), ctypes.byref(d))
+    return {"written": int(w.value), "dropped": int(d.value)}
+
+
 class Queue:
     def __init__(self, name: str, depth: int = 128, buf_size: int = 0, token: int = 0x756d71):
         o = _CreateOpt()
