@@ -1,5 +1,7 @@
 // UMS implementation (see ums.h).
 #include "ums.h"
+
+#include "ub_secure.h"
 #include "ums_shm.h"
 
 #include <arpa/inet.h>
@@ -64,7 +66,45 @@ struct Clc {
   uint32_t magic;
   uint32_t accept;  // reply: 1 = accelerated, 0 = declined
   char shm_name[64];
+  uint64_t nonce;   // with a pre-shared key: random per message
+  uint8_t tag[16];  // AES-256-GCM tag over everything above (key derived from UMS_PSK), else zero
 };
+constexpr size_t kClcSigned = offsetof(Clc, tag);
+
+// Handshake authentication. The reference's ums_agent carries the ring tokens of two hosts over a TLS connection of
+// its own (ums_agent_tls_conn.c, ums_agent_token_proxy.c); here both ends are on one host and the token is the name
+// of the ring file, so the handshake message itself is authenticated with a key derived from a pre-shared secret
+// (UMS_PSK, hex). A message whose tag does not verify is treated like a peer that declined: the connection stays on
+// TCP and is counted in conns_auth_fail.
+struct ClcAuth {
+  bool on = false, bad = false;
+  uint8_t key[32];
+  ClcAuth() {
+    const ub::PskConfig cfg = ub::PskConfig::from_env("UMS", &bad);
+    on = cfg.enabled() && ub::derive_key(cfg, "ums-clc", "ums", 3, key);
+  }
+};
+const ClcAuth& clc_auth() {
+  static const ClcAuth a;
+  return a;
+}
+void clc_sign(Clc* m, bool from_server) {
+  memset(m->tag, 0, sizeof(m->tag));
+  m->nonce = 0;
+  const ClcAuth& a = clc_auth();
+  if (!a.on) return;
+  ub::random_bytes(&m->nonce, sizeof(m->nonce));
+  ub::AeadCipher c(a.key, from_server ? 1u : 0u);
+  c.seal(m->nonce, m, kClcSigned, nullptr, 0, m->tag);
+}
+bool clc_verify(const Clc& m, bool from_server) {
+  const ClcAuth& a = clc_auth();
+  if (a.bad) return false;          // a malformed key never authenticates anything
+  if (!a.on) return true;
+  ub::AeadCipher c(a.key, from_server ? 1u : 0u);
+  uint8_t none = 0;
+  return c.open(m.nonce, &m, kClcSigned, m.tag, sizeof(m.tag), &none);
+}
 
 struct Conn {
   bool accelerated = false;
@@ -199,9 +239,16 @@ int ums_adopt_accepted(int listen_fd, int fd) {
   Clc in{};
   Conn c;
   if (rd_full(fd, &in, sizeof(in), 2000) && in.magic == kClcMagic) {
-    Clc out{kClcMagic, 0, {0}};
+    Clc out{};
+    out.magic = kClcMagic;
+    in.shm_name[sizeof(in.shm_name) - 1] = 0;
+    const bool trusted = clc_verify(in, false) && !strchr(in.shm_name, '/');
+    if (!trusted) {
+      std::lock_guard<std::mutex> l(g_mu);
+      ++g_stats.conns_auth_fail;
+    }
     const std::string path = dir() + "/" + in.shm_name;
-    const int sfd = ::open(path.c_str(), O_RDWR);
+    const int sfd = trusted ? ::open(path.c_str(), O_RDWR) : -1;
     void* p = MAP_FAILED;
     if (sfd >= 0) {
       p = mmap(nullptr, sizeof(ConnShm), PROT_READ | PROT_WRITE, MAP_SHARED, sfd, 0);
@@ -215,6 +262,7 @@ int ums_adopt_accepted(int listen_fd, int fd) {
       c.rx = &c.shm->c2s;
       c.shm_path = path;
     }
+    clc_sign(&out, true);
     wr_full(fd, &out, sizeof(out));
   }
   int one = 1;
@@ -241,8 +289,10 @@ int ums_adopt_connected(int fd, const struct sockaddr* peer) {
     try_ums = access(listen_marker(ntohs(a->sin_port)).c_str(), F_OK) == 0;
   }
   if (try_ums) {
-    Clc out{kClcMagic, 0, {0}};
+    Clc out{};
+    out.magic = kClcMagic;
     snprintf(out.shm_name, sizeof(out.shm_name), "conn_%d_%llu", getpid(), (unsigned long long)g_seq.fetch_add(1));
+    clc_sign(&out, false);
     const std::string path = dir() + "/" + out.shm_name;
     const int sfd = ::open(path.c_str(), O_CREAT | O_RDWR | O_TRUNC, 0600);
     void* p = MAP_FAILED;
@@ -252,8 +302,14 @@ int ums_adopt_connected(int fd, const struct sockaddr* peer) {
     const bool was_nb = nonblocking(fd);
     if (was_nb) fcntl(fd, F_SETFL, fcntl(fd, F_GETFL) & ~O_NONBLOCK);
     Clc in{};
-    if (p != MAP_FAILED && wr_full(fd, &out, sizeof(out)) && rd_full(fd, &in, sizeof(in), 2000) &&
-        in.magic == kClcMagic && in.accept) {
+    const bool answered = p != MAP_FAILED && wr_full(fd, &out, sizeof(out)) && rd_full(fd, &in, sizeof(in), 2000) &&
+                          in.magic == kClcMagic;
+    const bool trusted = answered && clc_verify(in, true);
+    if (answered && !trusted) {
+      std::lock_guard<std::mutex> l(g_mu);
+      ++g_stats.conns_auth_fail;
+    }
+    if (trusted && in.accept) {
       c.accelerated = true;
       c.shm = static_cast<ConnShm*>(p);
       c.tx = &c.shm->c2s;

@@ -29,6 +29,7 @@ UMS_EXPORT int ums_is_accelerated(int fd);
 
 typedef struct ums_stats {
   uint64_t conns_ums, conns_fallback, bytes_tx_ring, bytes_rx_ring, bytes_tx_tcp, bytes_rx_tcp, doorbells, tx_waits;
+  uint64_t conns_auth_fail; /* handshakes refused because the peer's message did not verify under UMS_PSK */
 } ums_stats_t;
 UMS_EXPORT void ums_get_stats(ums_stats_t* out);
 /* used by the preload shim */

@@ -186,3 +186,57 @@ def test_ums_admin_shows_live_connections(tmp_path):
     finally:
         if p.poll() is None:
             p.kill()
+
+
+def test_ums_handshake_is_authenticated_with_a_pre_shared_key(tmp_path):
+    """With UMS_PSK set, a client with the same key is accelerated; one with another key (or none) is refused the
+    rings, stays on TCP with its byte stream intact, and the refusal is counted."""
+    lib = _native.lib_dir() / "libumdk_usock.so"
+    server = tmp_path / "srv.py"
+    server.write_text(
+        "import socket, sys\n"
+        "ls = socket.socket(); ls.bind(('127.0.0.1', 0)); ls.listen(4)\n"
+        "print(ls.getsockname()[1], flush=True)\n"
+        "for _ in range(3):\n"
+        "    c, _ = ls.accept()\n"
+        "    while True:\n"
+        "        d = c.recv(65536)\n"
+        "        if not d: break\n"
+        "        c.sendall(d)\n"
+        "    c.close()\n")
+    client = tmp_path / "cli.py"
+    client.write_text(
+        "import socket, sys, ctypes\n"
+        "c = socket.create_connection(('127.0.0.1', int(sys.argv[1])))\n"
+        "msg = bytes(range(256)) * 16\n"
+        "for _ in range(20):\n"
+        "    c.sendall(msg); got = b''\n"
+        "    while len(got) < len(msg): got += c.recv(len(msg) - len(got))\n"
+        "    assert got == msg\n"
+        "c.close()\n"
+        f"lib = ctypes.CDLL({str(lib)!r})\n"
+        "st = (ctypes.c_uint64 * 9)(); lib.ums_get_stats(st)\n"
+        "print('STATS ums=%d fallback=%d auth_fail=%d' % (st[0], st[1], st[8]))\n")
+    wrapper = _native.lib_dir().parent / "bin" / "ums_run"
+    base = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"), UMS_SHM_DIR=str(tmp_path / "ums"))
+    key, other = "7e" * 32, "11" * 32
+    srv = subprocess.Popen([str(wrapper), sys.executable, str(server)], stdout=subprocess.PIPE, text=True,
+                           env=dict(base, UMS_PSK=key))
+    try:
+        port = srv.stdout.readline().strip()
+        outs = []
+        for k in (key, other, None):
+            env = dict(base)
+            if k:
+                env["UMS_PSK"] = k
+            r = subprocess.run([str(wrapper), sys.executable, str(client), port], env=env, capture_output=True,
+                               text=True, timeout=60)
+            assert r.returncode == 0, r.stdout + r.stderr
+            outs.append(r.stdout.strip().splitlines()[-1])
+        assert outs[0] == "STATS ums=1 fallback=0 auth_fail=0", outs
+        assert outs[1] == "STATS ums=0 fallback=1 auth_fail=1", outs      # the server's reply did not verify either
+        assert outs[2] == "STATS ums=0 fallback=1 auth_fail=0", outs      # no key: the server declined, plain TCP
+        srv.wait(timeout=30)
+    finally:
+        if srv.poll() is None:
+            srv.kill()

@@ -42,7 +42,7 @@ def _targets():
         ("umdk_umq", ["umq"], ["umdk_urma"]),
         ("umdk_urpc", ["urpc"], ["umdk_umq", "umdk_urma"]),
         ("umdk_dlock", ["dlock"], ["umdk_urma"]),
-        ("umdk_usock", ["usock"], []),
+        ("umdk_usock", ["usock"], ["umdk_urma"]),
     ]:
         srcs = []
         for d in dirs:
