@@ -3,6 +3,9 @@
 // (ub_list.h, ub_hmap.h, ub_bitmap.h, ub_hash.h, ub_dstring.h, ub_get_clock.h) and the percentile tables of
 // src/urma/lib/urma/core/urma_perf.c, written from scratch as C++17.
 #pragma once
+#include <cstdlib>
+#include <cstdio>
+#include <cstdarg>
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -288,6 +291,45 @@ class PerfHist {
   }
   uint64_t b_[kBuckets] = {0};
   uint64_t n_ = 0, sum_ = 0, min_ = ~0ull, max_ = 0;
+};
+
+// Leveled logger shared by the queue / RPC libraries: one instance per component, default sink stderr, optional user
+// callback, level from the component's API or from <TAG>_LOG_LEVEL (0 = error ... 4 = debug). Same controls as the
+// reference's *_log_config_set calls (src/urpc/include/umq/umq_api.h, urpc_framework_api.h).
+enum LogLevel : int { kLogErr = 0, kLogWarn = 1, kLogNotice = 2, kLogInfo = 3, kLogDebug = 4 };
+typedef void (*log_cb_t)(int level, const char* msg);
+class Logger {
+ public:
+  explicit Logger(const char* tag) : tag_(tag) {
+    char name[64];
+    snprintf(name, sizeof(name), "%s_LOG_LEVEL", tag);
+    if (const char* e = getenv(name)) level_ = atoi(e);
+  }
+  void configure(int level, log_cb_t cb) {
+    level_ = level;
+    cb_ = cb;
+  }
+  int level() const { return level_; }
+  void log(int lvl, const char* fmt, ...) __attribute__((format(printf, 3, 4))) {
+    if (lvl > level_) return;
+    char msg[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(msg, sizeof(msg), fmt, ap);
+    va_end(ap);
+    log_cb_t cb = cb_;
+    if (cb) {
+      cb(lvl, msg);
+    } else {
+      static const char* const names[] = {"ERR", "WARN", "NOTICE", "INFO", "DEBUG"};
+      fprintf(stderr, "[%s][%s] %s\n", tag_, names[lvl < 0 ? 0 : (lvl > 4 ? 4 : lvl)], msg);
+    }
+  }
+
+ private:
+  const char* tag_;
+  std::atomic<int> level_{kLogWarn};
+  std::atomic<log_cb_t> cb_{nullptr};
 };
 
 }  // namespace ub

@@ -78,6 +78,19 @@ struct Global {
   ub::PerfHist perf[UMQ_PERF_RECORD_MAX];
 };
 Global g;
+ub::Logger g_log("UMQ");
+
+// Asynchronous events (queue went into the error state): a bounded FIFO the application drains with
+// umq_async_event_get, like the reference's UMQ_EVENT_QH_ERR (doc/en/urpc/UMQ Abnormal Event.md).
+std::mutex g_ev_mu;
+std::deque<umq_async_event_t> g_events;
+void push_event(umq_async_event_type_t type, uint64_t h, int detail) {
+  std::lock_guard<std::mutex> l(g_ev_mu);
+  if (g_events.size() >= 1024) g_events.pop_front();
+  g_events.push_back(umq_async_event_t{type, h, detail});
+}
+std::atomic<umq_io_perf_cb_t> g_perf_cb{nullptr};
+std::atomic<void*> g_perf_cb_ctx{nullptr};
 
 // Trace: every thread owns a single-producer ring of {start, duration, record point} entries; a flusher thread wakes on
 // a timer, drains all rings and appends one text line per entry to the trace file. A full ring drops (and counts)
@@ -165,12 +178,14 @@ struct PerfScope {
   int rec;
   uint64_t t0;
   explicit PerfScope(int r)
-      : rec(r), t0((g.perf_on.load(std::memory_order_relaxed) || g_trace.on.load(std::memory_order_relaxed))
+      : rec(r), t0((g.perf_on.load(std::memory_order_relaxed) || g_trace.on.load(std::memory_order_relaxed) ||
+                    g_perf_cb.load(std::memory_order_relaxed))
                        ? ub::now_ns() : 0) {}
   ~PerfScope() {
     if (t0) {
       const uint64_t dt = ub::now_ns() - t0;
       if (g_trace.on.load(std::memory_order_relaxed)) trace_add(rec, t0, dt);
+      if (umq_io_perf_cb_t cb = g_perf_cb.load(std::memory_order_relaxed)) cb(rec, dt, g_perf_cb_ctx.load());
       if (g.perf_on.load(std::memory_order_relaxed)) {
         std::lock_guard<std::mutex> l(g.perf_mu);
         g.perf[rec].add(dt);
@@ -352,7 +367,11 @@ void progress(Queue* q) {
         b->meta.status = st[i] == 0 ? UMQ_BUF_OK : UMQ_BUF_SEND_ERR;
         if (st[i] != 0) {
           ++q->io.tx_errors;
-          q->state = UMQ_STATE_ERR;
+          if (q->state.exchange(UMQ_STATE_ERR) != UMQ_STATE_ERR) {
+            g_log.log(ub::kLogErr, "queue %llu (%s): send completed with status %d, queue set to ERR",
+                      (unsigned long long)q->h, q->opt.name, st[i]);
+            push_event(UMQ_EVENT_QH_ERR, q->h, st[i]);
+          }
         }
         if (b->meta.rsvd[0]) q->tx_done.push_back(&b->meta);  // pro API: hand back through poll(TX)
         else block_put(b);
@@ -533,7 +552,9 @@ int umq_unbind(uint64_t h) {
 int umq_state_set(uint64_t h, umq_state_t s) {
   Queue* q = find(h);
   if (!q) return UMQ_ERR_EINVAL;
-  q->state = s;
+  const int old = q->state.exchange(s);
+  if (s == UMQ_STATE_ERR && old != UMQ_STATE_ERR) push_event(UMQ_EVENT_QH_ERR, h, 0);
+  g_log.log(ub::kLogInfo, "queue %llu (%s): state %d -> %d", (unsigned long long)h, q->opt.name, old, (int)s);
   return UMQ_SUCCESS;
 }
 umq_state_t umq_state_get(uint64_t h) {
@@ -760,6 +781,24 @@ int umq_stats_perf_get(umq_perf_entry_t* e) {
     e[i].max_ns = g.perf[i].max();
     e[i].p99_ns = g.perf[i].quantile(0.99);
   }
+  return UMQ_SUCCESS;
+}
+int umq_log_config_set(int level, umq_log_cb_t cb) {
+  if (level < 0 || level > 4) return UMQ_ERR_EINVAL;
+  g_log.configure(level, cb);
+  return UMQ_SUCCESS;
+}
+int umq_io_perf_callback_register(umq_io_perf_cb_t cb, void* ctx) {
+  g_perf_cb_ctx = ctx;
+  g_perf_cb = cb;
+  return UMQ_SUCCESS;
+}
+int umq_async_event_get(umq_async_event_t* ev) {
+  if (!ev) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g_ev_mu);
+  if (g_events.empty()) return UMQ_ERR_EAGAIN;
+  *ev = g_events.front();
+  g_events.pop_front();
   return UMQ_SUCCESS;
 }
 int umq_trace_start(const char* path, uint32_t flush_interval_ms, uint32_t ring_entries) {

@@ -110,6 +110,21 @@ UMQ_EXPORT int umq_stats_qbuf_pool_get(umq_qbuf_stats_t* out);
 UMQ_EXPORT int umq_stats_perf_start(void);
 UMQ_EXPORT int umq_stats_perf_stop(void);
 UMQ_EXPORT int umq_stats_perf_get(umq_perf_entry_t* entries /* [UMQ_PERF_RECORD_MAX] */);
+/* Logging: level 0 (errors) .. 4 (debug), default 1 or UMQ_LOG_LEVEL; cb NULL = stderr. */
+typedef void (*umq_log_cb_t)(int level, const char* msg);
+UMQ_EXPORT int umq_log_config_set(int level, umq_log_cb_t cb);
+/* Called with (record point, duration in ns, ctx) after every API call at a perf record point; NULL unregisters. */
+typedef void (*umq_io_perf_cb_t)(int record, uint64_t duration_ns, void* ctx);
+UMQ_EXPORT int umq_io_perf_callback_register(umq_io_perf_cb_t cb, void* ctx);
+/* Asynchronous events. UMQ_EVENT_QH_ERR: the queue entered UMQ_STATE_ERR (a send completed in error, or the
+ * application set the state); detail = completion status. Returns UMQ_ERR_EAGAIN when there is none. */
+typedef enum umq_async_event_type { UMQ_EVENT_QH_ERR = 1 } umq_async_event_type_t;
+typedef struct umq_async_event {
+  umq_async_event_type_t type;
+  uint64_t umqh;
+  int detail;
+} umq_async_event_t;
+UMQ_EXPORT int umq_async_event_get(umq_async_event_t* ev);
 /* Trace: one text line `start_ns tid record duration_ns` per API call at the perf record points, collected in
  * per-thread rings (ring_entries each, 0 = 4096; a full ring drops and counts) and appended to `path` by a flusher
  * thread every flush_interval_ms (0 = 100). */

@@ -129,6 +129,12 @@ struct Global {
   bool psk_set = false;   // urpc_set_psk was called: the environment is not consulted
 };
 Global g;
+ub::Logger g_log("URPC");
+std::atomic<urpc_perf_recorder_t> g_recorder{nullptr};
+std::atomic<void*> g_recorder_ctx{nullptr};
+inline void record(urpc_perf_point_t pt, uint64_t ns) {
+  if (urpc_perf_recorder_t cb = g_recorder.load(std::memory_order_relaxed)) cb(pt, ns, g_recorder_ctx.load());
+}
 
 bool read_full(int fd, void* buf, size_t n, int timeout_ms = 5000) {
   uint8_t* p = static_cast<uint8_t*>(buf);
@@ -266,6 +272,7 @@ void channel_progress(Channel* ch) {
       std::lock_guard<std::mutex> l(g.stat_mu);
       ++g.stats.responses;
       g.lat.add(ub::now_ns() - p.t0);
+      record(URPC_PERF_CALL_TO_RESPONSE, ub::now_ns() - p.t0);
     }
     if (p.sync) {
       p.rsp.assign(b->buf_data + sizeof(urpc_req_head_t), b->buf_data + b->data_size);
@@ -327,6 +334,7 @@ void accept_loop() {
     std::string err;
     std::unique_ptr<ub::SecureConn> conn = ub::SecureConn::server(fd, g.server_psk, 3000, &err);
     if (!conn) {  // wrong key, clear-text client, or a client that stalled in the handshake
+      g_log.log(ub::kLogWarn, "connection refused in the secure handshake: %s", err.c_str());
       std::lock_guard<std::mutex> l(g.stat_mu);
       ++g.stats.errors;
       close(fd);
@@ -409,6 +417,7 @@ void keepalive_loop() {
           std::lock_guard<std::mutex> l(g.stat_mu);
           ++g.stats.keepalive_lost;
         }
+        g_log.log(ub::kLogWarn, "channel %u: peer missed %u keepalive probes, marked lost", ch->id, limit);
         if (g.ka_cb) g.ka_cb(ch->id, 0, g.ka_ctx);
       }
     }
@@ -563,9 +572,13 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
       }
       if (f.fn) {
         uint32_t rlen = static_cast<uint32_t>(rsp.size());
+        const uint64_t e0 = ub::now_ns();
         const int st = f.fn(args, alen, rsp.data(), &rlen, f.ctx);
+        const uint64_t e1 = ub::now_ns();
+        record(URPC_PERF_FUNC_EXEC, e1 - e0);
         rh.status = static_cast<int8_t>(st);
         send_msg(s->umqh, rh, nullptr, 0, rsp.data(), rlen > rsp.size() ? 0 : rlen, &s->seal);
+        record(URPC_PERF_FUNC_RETURN, ub::now_ns() - e1);
         umq_buf_free(b);
       } else if (msgs && n < max) {
         msgs[n].event = URPC_POLL_REQ;
@@ -715,6 +728,7 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
     ch->pending[req_id] = std::move(p);
     Head h{urpc_proto::kVersion, URPC_MSG_REQ, 1, wr->func_id, req_id, chid, 0, 0};
     const int rc = send_msg(ch->umqh, h, wr->args, wr->num_args, nullptr, 0, &ch->seal);
+    record(URPC_PERF_FUNC_CALL, ub::now_ns() - ch->pending[req_id].t0);
     if (rc != URPC_SUCCESS) {
       ch->pending.erase(req_id);
       std::lock_guard<std::mutex> l2(g.stat_mu);
@@ -908,6 +922,16 @@ int urpc_stats_get(urpc_stats_t* out) {
   if (!out) return URPC_ERR_EINVAL;
   std::lock_guard<std::mutex> l(g.stat_mu);
   *out = g.stats;
+  return URPC_SUCCESS;
+}
+int urpc_perf_recorder_register(urpc_perf_recorder_t cb, void* ctx) {
+  g_recorder_ctx = ctx;
+  g_recorder = cb;
+  return URPC_SUCCESS;
+}
+int urpc_log_config_set(int level, urpc_log_cb_t cb) {
+  if (level < 0 || level > 4) return URPC_ERR_EINVAL;
+  g_log.configure(level, cb);
   return URPC_SUCCESS;
 }
 int urpc_perf_get(uint64_t* count, uint64_t* avg_ns, uint64_t* p99_ns) {

@@ -106,6 +106,16 @@ typedef struct urpc_stats {
 } urpc_stats_t;
 URPC_EXPORT int urpc_stats_get(urpc_stats_t* out);
 URPC_EXPORT int urpc_perf_get(uint64_t* count, uint64_t* avg_ns, uint64_t* p99_ns); /* call -> response latency */
+/* User recorder: called with (record point, nanoseconds, ctx) at the points below; NULL unregisters.
+ * FUNC_CALL = time inside urpc_func_call until the request is queued, CALL_TO_RESPONSE = request queued until its
+ * response is matched, FUNC_EXEC = the registered handler on the server, FUNC_RETURN = sending the response. */
+typedef enum urpc_perf_point { URPC_PERF_FUNC_CALL = 0, URPC_PERF_CALL_TO_RESPONSE, URPC_PERF_FUNC_EXEC,
+                               URPC_PERF_FUNC_RETURN, URPC_PERF_POINT_MAX } urpc_perf_point_t;
+typedef void (*urpc_perf_recorder_t)(urpc_perf_point_t point, uint64_t ns, void* ctx);
+URPC_EXPORT int urpc_perf_recorder_register(urpc_perf_recorder_t cb, void* ctx);
+/* Logging: level 0 (errors) .. 4 (debug), default 1 or URPC_LOG_LEVEL; cb NULL = stderr. */
+typedef void (*urpc_log_cb_t)(int level, const char* msg);
+URPC_EXPORT int urpc_log_config_set(int level, urpc_log_cb_t cb);
 /* Management socket: a unix-domain stream socket at `path` that answers one text command per connection
  * ("version", "stats", "perf", "channels", "sessions", "funcs") with a text report; `urpc_admin` is its client.
  * Also started by urpc_init when the environment names a path in URPC_ADMIN_SOCKET. */

@@ -60,3 +60,23 @@ def test_trace_records_every_operation(pair, tmp_path):
         assert b.recv() == b"x"
     st2 = umq.trace_stop()
     assert st2["dropped"] > 0 and st2["written"] <= 8 * 4
+
+
+def test_perf_callback_log_sink_and_error_event(pair):
+    umq, a, b = pair
+    seen, logs = [], []
+    umq.io_perf_callback(lambda rec, ns: seen.append((rec, ns)))
+    umq.log_config(3, lambda lvl, msg: logs.append((lvl, msg)))
+    try:
+        a.send(b"hello")
+        assert b.recv() == b"hello"
+        assert {"enqueue", "dequeue", "buf_alloc"} <= {r for r, _ in seen} and all(ns >= 0 for _, ns in seen)
+        assert umq.async_events() == []
+        a.set_state(2)
+        ev = umq.async_events()
+        assert ev == [(1, a.h, 0)] and a.state() == 2
+        assert any("state" in m for _, m in logs)
+        a.set_state(1)
+    finally:
+        umq.io_perf_callback(None)
+        umq.log_config(1, None)

@@ -75,3 +75,17 @@ def test_secured_connection_seals_payloads_and_refuses_other_keys(tmp_path):
         srv.stop()
         urpc.uninit()
         urpc.set_psk("", "")
+
+
+def test_perf_recorder_sees_every_point(rpc):
+    urpc, srv, ch = rpc
+    got = {}
+    urpc.perf_recorder(lambda point, ns: got.setdefault(point, []).append(ns))
+    try:
+        for _ in range(5):
+            assert ch.call(1, b"abc") == b"cba"
+    finally:
+        urpc.perf_recorder(None)
+    assert set(got) == set(urpc.PERF_POINTS)
+    assert all(len(v) >= 5 for v in got.values())
+    assert min(got["call_to_response"]) >= min(got["func_exec"])

@@ -21,6 +21,7 @@ import torch.distributed as dist
 
 from .ops import cpu_dist
 from .ops import reference as ref
+from .utils import trace as _trace
 
 
 class EventOverlap:
@@ -118,6 +119,7 @@ class Buffer:
         self._ll.clear()
 
     # ---- layout ------------------------------------------------------------------------------------------------
+    @_trace.traced("umdk.buffer.get_dispatch_layout")
     def get_dispatch_layout(self, topk_idx: torch.Tensor, num_experts: int, previous_event=None,
                             async_finish: bool = False, allocate_on_comm_stream: bool = False):
         """-> (num_tokens_per_rank, num_tokens_per_rdma_rank (None on one box), num_tokens_per_expert,
@@ -134,6 +136,7 @@ class Buffer:
         return lay.num_tokens_per_rank, None, lay.num_tokens_per_expert, lay.is_token_in_rank, ev
 
     # ---- normal mode ---------------------------------------------------------------------------------------------
+    @_trace.traced("umdk.buffer.dispatch")
     def dispatch(self, x: Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]], handle=None,
                  num_tokens_per_rank=None, num_tokens_per_rdma_rank=None, is_token_in_rank=None,
                  num_tokens_per_expert=None, topk_idx: Optional[torch.Tensor] = None,
@@ -177,6 +180,7 @@ class Buffer:
         h = DispatchHandle("cpu", topk_idx, topk_weights, T, cpu=res)
         return recv_x, rows_le, res.recv_weights, res.recv_tokens_per_expert.tolist(), h, EventOverlap()
 
+    @_trace.traced("umdk.buffer.combine")
     def combine(self, x: torch.Tensor, handle: DispatchHandle, topk_weights: Optional[torch.Tensor] = None,
                 config: Optional[Config] = None, previous_event=None, async_finish: bool = False,
                 allocate_on_comm_stream: bool = False):
@@ -206,6 +210,7 @@ class Buffer:
         return out, w, EventOverlap()
 
     # ---- low-latency mode ------------------------------------------------------------------------------------
+    @_trace.traced("umdk.buffer.low_latency_dispatch")
     def low_latency_dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, num_max_dispatch_tokens_per_rank: int,
                              num_experts: int, use_fp8: bool = True, async_finish: bool = False,
                              return_recv_hook: bool = False, ffn_hidden: Optional[int] = None):
@@ -220,6 +225,7 @@ class Buffer:
         ev = EventOverlap(torch.cuda.current_stream().record_event()) if async_finish else EventOverlap()
         return (sx, ss), st.recv_per_expert, st, ev, (lambda: None) if return_recv_hook else None
 
+    @_trace.traced("umdk.buffer.fused_moe")
     def fused_moe(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, experts, shared=None,
                   num_experts: Optional[int] = None, num_max_tokens_per_rank: Optional[int] = None):
         """dispatch -> expert SwiGLU FFN (fp8, tcgen05) -> combine in one call chain.
@@ -231,6 +237,7 @@ class Buffer:
         st = self._ll_state(E, K, x.shape[1], F, cap)
         return st.moe(x.contiguous(), topk_idx.contiguous(), topk_weights.contiguous(), experts, shared)
 
+    @_trace.traced("umdk.buffer.low_latency_combine")
     def low_latency_combine(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, handle,
                             async_finish: bool = False, return_recv_hook: bool = False,
                             out: Optional[torch.Tensor] = None):

@@ -15,6 +15,7 @@ import torch
 
 from .. import _native
 from ..parallel.symm import HostMirror, SymmetricHeap
+from ..utils import trace as _trace
 
 MAX_RANKS = 32
 
@@ -183,9 +184,11 @@ class EpNormal:
             raise ValueError(f"unsupported EP geometry R={R} E={E} K={K} H={H} cap={cap}")
         return int(n)
 
+    @_trace.traced("umdk.ep.layout")
     def layout(self, topk_idx: torch.Tensor) -> LayoutResult:
         return layout(topk_idx, self.E, self.R, self.layout_scratch, self.layout_bar, self.status)
 
+    @_trace.traced("umdk.ep.notify")
     def notify(self, lay: LayoutResult, phase_mask: int = 3, out: Optional[NotifyResult] = None) -> NotifyResult:
         """Count exchange alone: tells every peer how many rows / tokens this rank will send to each of its local
         experts and returns what this rank will receive. ``dispatch`` does the same exchange internally; call this
@@ -210,6 +213,7 @@ class EpNormal:
             raise RuntimeError(f"umdk_ep_notify failed: {rc}")
         return out
 
+    @_trace.traced("umdk.ep.dispatch")
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: Optional[torch.Tensor],
                  lay: Optional[LayoutResult] = None, quant: bool = True, n_cap: Optional[int] = None,
                  a_cap: Optional[int] = None, phase_mask: int = 3, out: Optional[DispatchResult] = None,
@@ -264,6 +268,7 @@ class EpNormal:
             out.num_recv = int(self.mirror.host[0])
         return out
 
+    @_trace.traced("umdk.ep.combine")
     def combine(self, y: torch.Tensor, disp: DispatchResult, apply_weights: bool = True, phase_mask: int = 3,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Per-rank pre-reduced combine: out[t] = sum over ranks of (sum_k w[t,k] * y_row(t,k))."""
@@ -286,6 +291,7 @@ class EpNormal:
             raise RuntimeError(f"umdk_ep_combine failed: {rc}")
         return out
 
+    @_trace.traced("umdk.ep.combine_rows")
     def combine_rows(self, y: torch.Tensor, src_idx: torch.Tensor, topk_idx: torch.Tensor,
                      topk_weights: torch.Tensor, phase_mask: int = 3, out: Optional[torch.Tensor] = None
                      ) -> torch.Tensor:

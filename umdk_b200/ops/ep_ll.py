@@ -25,6 +25,7 @@ from .. import _native
 from ..parallel.symm import SymmetricHeap
 from . import moe_gemm
 from .ep import check_status, layout as ep_layout
+from ..utils import trace as _trace
 
 MAX_RANKS = 32
 
@@ -209,6 +210,7 @@ class EpLowLatency:
         return x, s, m
 
     # -- kernels -------------------------------------------------------------------------------------------------
+    @_trace.traced("umdk.ep_ll.dispatch")
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, phase_mask: int = 3, lay=None):
         assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and topk_idx.dtype == torch.int64
         T = x.shape[0]
@@ -300,6 +302,7 @@ class EpLowLatency:
         return moe_gemm.gemm2(self.sh_hq[:T], self.sh_hs[:T], self.sh_off, w.w2q, w.w2s, self.status, y=out,
                               max_ctas=self.gemm_ctas)
 
+    @_trace.traced("umdk.ep_ll.moe")
     def moe(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w: ExpertWeights,
             shared: Optional[ExpertWeights] = None, out: Optional[torch.Tensor] = None, fused: bool = True):
         """Full layer: returns (combine_x [T, H] bf16, share_output or None, expert_token_nums [E_local] int64).
@@ -325,6 +328,7 @@ class EpLowLatency:
             self._gemm2_combine(w, topk_idx, topk_w, out)
         return out, share_out, self.recv_per_expert
 
+    @_trace.traced("umdk.ep_ll.capture")
     def capture(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w: ExpertWeights,
                 shared: Optional[ExpertWeights] = None, out: Optional[torch.Tensor] = None):
         """Records the whole layer (layout, dispatch, fused expert kernel) into a CUDA graph and returns

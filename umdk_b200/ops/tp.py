@@ -10,6 +10,7 @@ import torch
 from .. import _native
 from ..parallel.symm import SymmetricHeap
 from .ep import check_status
+from ..utils import trace as _trace
 
 MAX_RANKS = 32
 
@@ -101,6 +102,7 @@ class TpComm:
         p.status = self.status.data_ptr()
         return p
 
+    @_trace.traced("umdk.tp.ag_gemm")
     def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                 phase_mask: int = 3) -> torch.Tensor:
         assert x_shard.dtype == torch.bfloat16 and x_shard.is_contiguous() and w.is_contiguous()
@@ -118,6 +120,7 @@ class TpComm:
             raise RuntimeError(f"umdk_tp_gemm(all-gather GEMM) failed: {rc}")
         return out
 
+    @_trace.traced("umdk.tp.gemm_rs")
     def gemm_rs(self, y: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                 phase_mask: int = 3) -> torch.Tensor:
         assert y.dtype == torch.bfloat16 and y.is_contiguous() and w.is_contiguous()
@@ -175,6 +178,7 @@ class AllReduce:
         from ..utils.rawtensor import from_ptr
         return from_ptr(self.heap.local_ptr + self.buf[parity], (n,), torch.bfloat16, self.ctrl.device)
 
+    @_trace.traced("umdk.tp.all_reduce")
     def __call__(self, x: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, algo: str = "auto",
                  num_ctas: int = 0, phase_mask: int = 3, in_place: bool = False, n: Optional[int] = None
                  ) -> Optional[torch.Tensor]:

@@ -90,6 +90,46 @@ def uninit() -> None:
     _lib().umq_uninit()
 
 
+PERF_RECORDS = ("enqueue", "dequeue", "post_tx", "poll_rx", "buf_alloc")
+_PERF_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p)
+_LOG_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_char_p)
+_keep = []   # ctypes callbacks must outlive their registration
+
+
+class _AsyncEvent(ctypes.Structure):
+    _fields_ = [("type", ctypes.c_int), ("umqh", ctypes.c_uint64), ("detail", ctypes.c_int)]
+
+
+def io_perf_callback(cb) -> None:
+    """cb(record name, nanoseconds) after every queue operation; None unregisters."""
+    if cb is None:
+        _lib().umq_io_perf_callback_register(None, None)
+        return
+    c = _PERF_CB(lambda rec, ns, _ctx: cb(PERF_RECORDS[rec] if 0 <= rec < len(PERF_RECORDS) else str(rec), int(ns)))
+    _keep.append(c)
+    _lib().umq_io_perf_callback_register(c, None)
+
+
+def log_config(level: int, cb=None) -> None:
+    """Log level 0 (errors) .. 4 (debug); cb(level, message) replaces the stderr sink."""
+    c = None
+    if cb is not None:
+        c = _LOG_CB(lambda lvl, msg: cb(int(lvl), msg.decode(errors="replace")))
+        _keep.append(c)
+    rc = _lib().umq_log_config_set(level, c)
+    if rc != 0:
+        raise UmqError(f"umq_log_config_set failed: {rc}")
+
+
+def async_events() -> list:
+    """Drains the asynchronous event queue: [(type, queue handle, detail)]; type 1 = queue entered the error state."""
+    out = []
+    ev = _AsyncEvent()
+    while _lib().umq_async_event_get(ctypes.byref(ev)) == 0:
+        out.append((int(ev.type), int(ev.umqh), int(ev.detail)))
+    return out
+
+
 def trace_start(path: str, flush_interval_ms: int = 100, ring_entries: int = 4096) -> None:
     """Starts writing one line `start_ns tid record duration_ns` per queue operation to `path` (per-thread rings
     drained by a timer thread)."""
@@ -173,6 +213,14 @@ class Queue:
             if time.monotonic() > deadline:
                 return None
             time.sleep(0.0002)
+
+    def set_state(self, state: int) -> None:
+        """0 = idle, 1 = ready, 2 = error (raises a queue-error event)."""
+        if _lib().umq_state_set(self.h, state) != 0:
+            raise UmqError("umq_state_set failed")
+
+    def state(self) -> int:
+        return int(_lib().umq_state_get(self.h))
 
     def io_stats(self) -> dict:
         s = _IoStats()

@@ -89,6 +89,32 @@ def set_psk(key_hex: str = "", identity: str = "") -> None:
         raise UrpcError("urpc_set_psk", rc)
 
 
+PERF_POINTS = ("func_call", "call_to_response", "func_exec", "func_return")
+_REC_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p)
+_LOG_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_char_p)
+
+
+def perf_recorder(cb: Optional[Callable[[str, int], None]]) -> None:
+    """cb(point name, nanoseconds) at every record point (see PERF_POINTS); None unregisters."""
+    if cb is None:
+        _lib().urpc_perf_recorder_register(None, None)
+        return
+    c = _REC_CB(lambda pt, ns, _ctx: cb(PERF_POINTS[pt] if 0 <= pt < len(PERF_POINTS) else str(pt), int(ns)))
+    _keep.append(c)
+    _lib().urpc_perf_recorder_register(c, None)
+
+
+def log_config(level: int, cb: Optional[Callable[[int, str], None]] = None) -> None:
+    """Log level 0 (errors) .. 4 (debug); cb(level, message) replaces the stderr sink."""
+    c = None
+    if cb is not None:
+        c = _LOG_CB(lambda lvl, msg: cb(int(lvl), msg.decode(errors="replace")))
+        _keep.append(c)
+    rc = _lib().urpc_log_config_set(level, c)
+    if rc != 0:
+        raise UrpcError("urpc_log_config_set", rc)
+
+
 def admin_query(command: str) -> str:
     """The management report (`version`, `stats`, `perf`, `channels`, `sessions`, `functions`) as text."""
     buf = ctypes.create_string_buffer(16384)
