@@ -1,5 +1,10 @@
 // urma_perftest: latency and bandwidth of URMA verbs (write / read / send / atomic) between two endpoints.
 //   urma_perftest [--dev shm0|bond0] [--op write|read|send|faa|cas] [--size N] [--iters N] [--depth N]
+//                 [--duration SEC] [--jettys N] [--cq-mod N] [--rate-limit MB/s]
+//     --duration   run the pipelined part for a time instead of a number of operations
+//     --jettys     N endpoint pairs driven round-robin (in-process mode)
+//     --cq-mod     ask for a completion only on every N-th operation (completion moderation)
+//     --rate-limit pace the pipelined part to this many MB/s
 //   urma_perftest --server PORT         waits for one client, serves its one-sided and two-sided traffic
 //   urma_perftest --client HOST PORT    measures against a server in another process
 // Without --server/--client both endpoints live in this process. Option names follow the reference's tool
@@ -58,8 +63,14 @@ int main(int argc, char** argv) {
   std::string dev = "shm0", op = "write", host = "127.0.0.1";
   uint32_t size = 4096, iters = 20000, depth = 64;
   int server = -1, client = -1;
+  uint32_t jettys = 1, cq_mod = 1;
+  double duration = 0, rate_mbs = 0;
   for (int i = 1; i < argc; ++i) {
-    if (!strcmp(argv[i], "--dev") && i + 1 < argc) dev = argv[++i];
+    if (!strcmp(argv[i], "--duration") && i + 1 < argc) duration = atof(argv[++i]);
+    else if (!strcmp(argv[i], "--jettys") && i + 1 < argc) jettys = std::max(1, atoi(argv[++i]));
+    else if (!strcmp(argv[i], "--cq-mod") && i + 1 < argc) cq_mod = std::max(1, atoi(argv[++i]));
+    else if (!strcmp(argv[i], "--rate-limit") && i + 1 < argc) rate_mbs = atof(argv[++i]);
+    else if (!strcmp(argv[i], "--dev") && i + 1 < argc) dev = argv[++i];
     else if (!strcmp(argv[i], "--op") && i + 1 < argc) op = argv[++i];
     else if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
@@ -111,6 +122,25 @@ int main(int argc, char** argv) {
     urma_target_seg_t* seg_b = urma_simple_seg_register(ctx_b, mem_b.data(), seg_bytes, 14, 1, peer.seg);
     if (!eb || !seg_b) return fail("second endpoint");
     urma_simple_ep_blob(eb, peer.ep);
+  }
+  // extra endpoint pairs for --jettys (in-process mode): pair j = (ex_a[j], ex_b[j]), same segments
+  std::vector<urma_simple_ep_t*> ex_a, ex_b;
+  std::vector<urma_target_jetty_t*> ex_t;
+  if (eb) {
+    for (uint32_t j = 1; j < jettys; ++j) {
+      urma_simple_ep_t* a2 = urma_simple_ep_create(ctx, depth * 2, 1, 0);
+      urma_simple_ep_t* b2 = urma_simple_ep_create(ctx_b, depth * 2, 1, 0);
+      if (!a2 || !b2) return fail("extra endpoints");
+      uint8_t blob[URMA_SIMPLE_JETTY_BLOB];
+      urma_simple_ep_blob(b2, blob);
+      urma_target_jetty_t* t2 = urma_simple_ep_import(ctx, blob, 1);
+      if (!t2) return fail("import of an extra endpoint");
+      ex_a.push_back(a2);
+      ex_b.push_back(b2);
+      ex_t.push_back(t2);
+    }
+  } else {
+    jettys = 1;
   }
   urma_target_jetty_t* tj = urma_simple_ep_import(ctx, peer.ep, 1);
   urma_target_seg_t* rseg = urma_simple_seg_import(ctx, peer.seg, 1);
@@ -179,31 +209,90 @@ int main(int argc, char** argv) {
         if (fl & URMA_CR_FLAG_RECV) urma_simple_post_recv(eb, rb[uc].data(), size, uc);
     }
   }
-  // bandwidth / rate: keep `depth` operations in flight
-  uint32_t sent = 0, done = 0;
+  // bandwidth / rate: keep `depth` operations in flight on every endpoint pair
+  std::vector<urma_simple_ep_t*> all_a{ea}, all_b{eb};
+  std::vector<urma_target_jetty_t*> all_t{tj};
+  for (size_t j = 0; j < ex_a.size(); ++j) {
+    all_a.push_back(ex_a[j]);
+    all_b.push_back(ex_b[j]);
+    all_t.push_back(ex_t[j]);
+  }
+  if (two_sided && eb) {
+    for (size_t j = 1; j < all_b.size(); ++j)
+      for (uint32_t i = 0; i < depth * 2; ++i) urma_simple_post_recv(all_b[j], rb[i].data(), size, i);
+  }
+  std::vector<uint64_t> sent(jettys, 0), done(jettys, 0);
+  std::vector<char> last_sig(jettys, 1), flushed(jettys, 0);
+  uint64_t total_sent = 0, total_done = 0;
   const uint64_t t0 = ub::now_ns();
-  while (done < iters) {
-    while (sent < iters && sent - done < depth) {
-      const int rc = post(sent);
-      if (rc == URMA_EAGAIN) break;
-      if (rc != 0) return fail("post (pipelined)");
-      ++sent;
+  const uint64_t t_end = duration > 0 ? t0 + (uint64_t)(duration * 1e9) : 0;
+  auto more = [&]() { return t_end ? ub::now_ns() < t_end : total_sent < iters; };
+  auto paced = [&]() {  // true while the byte budget of --rate-limit allows another operation
+    if (rate_mbs <= 0) return true;
+    return total_sent * (double)size <= rate_mbs * 1e6 * ((ub::now_ns() - t0) * 1e-9);
+  };
+  while (more() || total_done < total_sent) {
+    for (uint32_t j = 0; j < jettys; ++j) {
+      while (more() && paced() && sent[j] - done[j] < depth) {
+        // completion moderation: only every cq_mod-th operation of a pair asks for a completion, which then stands
+        // for the cq_mod operations up to it (the last operation of the run always asks)
+        const bool sig = ((sent[j] + 1) % cq_mod) == 0 || atomic;
+        int rc;
+        if (atomic) rc = urma_simple_atomic(all_a[j], all_t[j], opc, rseg, rva, 1, 0, nullptr, sent[j]);
+        else rc = urma_simple_post(all_a[j], all_t[j], opc, two_sided ? nullptr : rseg, rva, nullptr,
+                                   (uint64_t)mem_a.data(), size, 0, sent[j], sig ? 1 : 0);
+        if (rc == URMA_EAGAIN) break;
+        if (rc != 0) return fail("post (pipelined)");
+        ++sent[j];
+        ++total_sent;
+        last_sig[j] = sig;
+      }
     }
-    const int n = wait_n(ea, 1, &bad);
-    if (n <= 0) return fail("completion timeout (pipelined)");
-    done += n;
-    if (two_sided && eb) {
-      int st[16];
-      uint64_t uc[16];
-      uint32_t fl[16];
-      const int m = urma_simple_poll(eb, 16, st, uc, nullptr, nullptr, fl);
-      for (int i = 0; i < m; ++i)
-        if (fl[i] & URMA_CR_FLAG_RECV) urma_simple_post_recv(eb, rb[uc[i]].data(), size, uc[i]);
+    bool progressed = false;
+    for (uint32_t j = 0; j < jettys; ++j) {
+      int st[64];
+      uint64_t uc[64];
+      uint32_t fl[64];
+      const int n = urma_simple_poll(all_a[j], 64, st, uc, nullptr, nullptr, fl);
+      for (int i = 0; i < n; ++i) {
+        if (st[i] != 0) ++bad;
+        const uint64_t upto = uc[i] + 1;          // operations are completed in order on one endpoint
+        if (upto > done[j]) {
+          total_done += upto - done[j];
+          done[j] = upto;
+        }
+        progressed = true;
+      }
+      if (two_sided && all_b[j]) {
+        const int m = urma_simple_poll(all_b[j], 64, st, uc, nullptr, nullptr, fl);
+        for (int i = 0; i < m; ++i)
+          if (fl[i] & URMA_CR_FLAG_RECV) urma_simple_post_recv(all_b[j], rb[uc[i]].data(), size, uc[i]);
+      }
+    }
+    if (!more()) {
+      // flush the tail: operations after the last signalled one complete silently, so one more signalled operation
+      // per pair is posted, whose completion stands for everything before it
+      for (uint32_t j = 0; j < jettys; ++j) {
+        if (done[j] < sent[j] && !last_sig[j] && !flushed[j]) {
+          if (urma_simple_post(all_a[j], all_t[j], opc, two_sided ? nullptr : rseg, rva, nullptr,
+                               (uint64_t)mem_a.data(), size, 0, sent[j], 1) == 0) {
+            ++sent[j];
+            ++total_sent;
+            flushed[j] = true;
+          }
+        }
+      }
+    }
+    if (!progressed) {
+      if (ub::now_ns() - t0 > (uint64_t)((duration > 0 ? duration : 0) * 1e9) + 20000000000ull)
+        return fail("completion timeout (pipelined)");
+      sched_yield();
     }
   }
+  iters = (uint32_t)total_done;
   const double sec = (ub::now_ns() - t0) * 1e-9;
-  printf("%s dev=%s size=%u depth=%u: latency avg %.2f us p99 %.2f us min %.2f us | %.0f ops/s, %.2f MB/s | errors %d\n",
-         op.c_str(), dev.c_str(), size, depth, h.mean() / 1e3, h.quantile(0.99) / 1e3, h.min() / 1e3, iters / sec,
+  printf("%s dev=%s size=%u depth=%u jettys=%u cq_mod=%u: latency avg %.2f us p99 %.2f us min %.2f us | %.0f ops/s, %.2f MB/s | errors %d\n",
+         op.c_str(), dev.c_str(), size, depth, jettys, cq_mod, h.mean() / 1e3, h.quantile(0.99) / 1e3, h.min() / 1e3, iters / sec,
          iters * (double)size / sec / 1e6, bad);
   if (tcp >= 0) {
     char bye = 'q';

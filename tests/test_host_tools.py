@@ -240,3 +240,17 @@ def test_ums_handshake_is_authenticated_with_a_pre_shared_key(tmp_path):
     finally:
         if srv.poll() is None:
             srv.kill()
+
+
+def test_urma_perftest_duration_jettys_moderation_and_rate_limit(tmp_path):
+    rc, out = _run([BIN / "urma_perftest", "--op", "write", "--size", "4096", "--duration", "0.3", "--jettys", "3",
+                    "--cq-mod", "4"], tmp_path)
+    assert rc == 0 and "jettys=3 cq_mod=4" in out and "urma_perftest: OK" in out, out
+    rc, out = _run([BIN / "urma_perftest", "--op", "write", "--size", "65536", "--duration", "0.5", "--rate-limit",
+                    "200"], tmp_path)
+    assert rc == 0 and "urma_perftest: OK" in out, out
+    mbs = float(out.split("ops/s,")[1].split("MB/s")[0])
+    assert 150 <= mbs <= 215, out            # paced to the requested 200 MB/s
+    rc, out = _run([BIN / "urma_perftest", "--op", "send", "--size", "512", "--iters", "4001", "--cq-mod", "8",
+                    "--jettys", "2"], tmp_path)
+    assert rc == 0 and "errors 0" in out, out
