@@ -3,6 +3,10 @@
 //   urma_admin perf <seconds>       samples the data-plane calls of a built-in loopback workload and prints the
 //                                   per-call latency table (avg / min / max / p90 / p99 / p99.99)
 //   urma_admin ping <dev>           round-trip of a NOP work request on <dev> (link check)
+//   urma_admin agg [name]           members of an aggregation device (default bond0)
+//   urma_admin topo                 discovered topology: nodes, ports, and the path set between the first two nodes
+//   urma_admin stats <bond-dev> [seconds]   per-path state and counters of a multipath device while a loopback
+//                                   workload runs on it (up, sent, errors, failovers, failbacks, admin state)
 // Mirrors the `show` / `perf start|show` commands of the reference's urma_admin
 // (doc/en/urma/URMA User Guide.md:1874-2010) and the EID-level reachability check of its urma_ping.
 #include <sched.h>
@@ -15,6 +19,7 @@
 
 #include "ub_util.h"
 #include "urma_simple.h"
+#include "uvs_topo.h"
 
 static int show() {
   urma_init_attr_t attr{};
@@ -95,10 +100,111 @@ static int perf(int seconds) {
   return 0;
 }
 
+static int agg(const char* name) {
+  urma_init_attr_t attr{};
+  urma_init(&attr);
+  uvs_agg_dev_t d;
+  if (uvs_get_agg_dev(name, &d) != 0) {
+    // nothing registered under this name: a multipath device then takes $BOND_DEVICES or every shm* device
+    urma_device_t* dev = urma_get_device_by_name(name);
+    if (!dev) {
+      fprintf(stderr, "urma_admin: no aggregation device %s\n", name);
+      return 1;
+    }
+    const char* env = getenv("BOND_DEVICES");
+    printf("%s: not in the aggregation registry; members = %s\n", name, env ? env : "every shm* device");
+    return 0;
+  }
+  char eid[64];
+  urma_eid_to_str(&d.agg_eid, eid, sizeof(eid));
+  printf("%s eid %s members %u\n", d.name, eid, d.member_num);
+  for (uint32_t i = 0; i < d.member_num; ++i) {
+    urma_eid_to_str(&d.member_eids[i], eid, sizeof(eid));
+    printf("  member %u: %-8s %s\n", i, d.member_names[i], eid);
+  }
+  return 0;
+}
+
+static int topo() {
+  urma_init_attr_t attr{};
+  urma_init(&attr);
+  if (uvs_discover_local_topology() <= 0) {
+    fprintf(stderr, "urma_admin: topology discovery failed\n");
+    return 1;
+  }
+  std::vector<uvs_topo_node_t> nodes(UVS_MAX_NODES);
+  uint32_t n = 0;
+  if (uvs_get_topo_info(nodes.data(), UVS_MAX_NODES, &n) != 0) return 1;
+  printf("%u node(s)\n", n);
+  for (uint32_t i = 0; i < n; ++i) {
+    char eid[64];
+    urma_eid_to_str(&nodes[i].primary_eid, eid, sizeof(eid));
+    printf("  node %u: %s, %u port(s), eid %s%s\n", nodes[i].node_id,
+           nodes[i].type == UVS_TOPO_CLOS_PLANES ? "switch planes" : "full mesh", nodes[i].port_num, eid,
+           nodes[i].is_current ? " (this process)" : "");
+  }
+  if (n >= 2) {
+    uvs_path_set_t ps;
+    if (uvs_get_path_set(&nodes[0].primary_eid, &nodes[1].primary_eid, UVS_RTP, &ps) == 0) {
+      printf("paths node %u -> node %u: %u\n", nodes[0].node_id, nodes[1].node_id, ps.path_count);
+      for (uint32_t i = 0; i < ps.path_count && i < 4; ++i)
+        printf("  port %u -> port %u\n", ps.paths[i].src_port, ps.paths[i].dst_port);
+      if (ps.path_count > 4) printf("  ...\n");
+    }
+  }
+  return 0;
+}
+
+static int stats(const char* dev, int seconds) {
+  urma_context_t* ctx = urma_simple_open(dev);
+  if (!ctx) {
+    fprintf(stderr, "urma_admin: no such device %s\n", dev);
+    return 1;
+  }
+  urma_simple_ep_t* ep = urma_simple_ep_create(ctx, 64, 0, 0);
+  uint8_t blob[URMA_SIMPLE_JETTY_BLOB], sblob[URMA_SIMPLE_SEG_BLOB];
+  std::vector<uint8_t> mem(8192);
+  urma_target_seg_t* seg = ep ? urma_simple_seg_register(ctx, mem.data(), mem.size(), 14, 5, sblob) : nullptr;
+  if (!ep || !seg) return 1;
+  urma_simple_ep_blob(ep, blob);
+  urma_target_jetty_t* self = urma_simple_ep_import(ctx, blob, 0);
+  urma_target_seg_t* rseg = urma_simple_seg_import(ctx, sblob, 5);
+  if (!self || !rseg) return 1;
+  const uint64_t end = ub::now_ns() + uint64_t(seconds) * 1000000000ull;
+  int st;
+  uint64_t uc;
+  uint32_t fl;
+  uint64_t ops = 0;
+  do {
+    urma_simple_post(ep, self, URMA_OPC_WRITE, rseg, rseg->seg.ubva.va, nullptr, (uint64_t)mem.data() + 4096, 512, 0, 1,
+                     1);
+    urma_simple_wait(ep, 1, 1000, 1, &st, &uc, nullptr, nullptr, &fl);
+    ++ops;
+  } while (ub::now_ns() < end);
+  uint64_t table[UVS_MAX_MEMBERS * 4][6];
+  urma_user_ctl_in_t in{0, 0, 1};
+  urma_user_ctl_out_t out{reinterpret_cast<uint64_t>(table), (uint32_t)sizeof(table), 0};
+  if (urma_user_ctl(ctx, &in, &out) != 0) {
+    fprintf(stderr, "urma_admin: %s has no path statistics (not a multipath device)\n", dev);
+    return 1;
+  }
+  printf("%s: %llu loopback writes, %u path(s)\n", dev, (unsigned long long)ops, out.rsv);
+  printf("%-5s %-5s %-10s %-8s %-10s %-10s %s\n", "path", "up", "sent", "errors", "failovers", "failbacks", "admin");
+  for (uint32_t i = 0; i < out.rsv; ++i)
+    printf("%-5u %-5llu %-10llu %-8llu %-10llu %-10llu %s\n", i, (unsigned long long)table[i][0],
+           (unsigned long long)table[i][1], (unsigned long long)table[i][2], (unsigned long long)table[i][3],
+           (unsigned long long)table[i][4], table[i][5] ? "down" : "up");
+  return 0;
+}
+
 int main(int argc, char** argv) {
   if (argc >= 2 && !strcmp(argv[1], "show")) return show();
   if (argc >= 3 && !strcmp(argv[1], "perf")) return perf(atoi(argv[2]));
   if (argc >= 3 && !strcmp(argv[1], "ping")) return ping(argv[2], argc >= 4 ? atoi(argv[3]) : 5);
-  fprintf(stderr, "usage: urma_admin show | perf <seconds> | ping <dev> [count]\n");
+  if (argc >= 2 && !strcmp(argv[1], "agg")) return agg(argc >= 3 ? argv[2] : "bond0");
+  if (argc >= 2 && !strcmp(argv[1], "topo")) return topo();
+  if (argc >= 3 && !strcmp(argv[1], "stats")) return stats(argv[2], argc >= 4 ? atoi(argv[3]) : 0);
+  fprintf(stderr, "usage: urma_admin show | perf <seconds> | ping <dev> [count] | agg [name] | topo | "
+                  "stats <bond-dev> [seconds]\n");
   return 2;
 }

@@ -254,3 +254,16 @@ def test_urma_perftest_duration_jettys_moderation_and_rate_limit(tmp_path):
     rc, out = _run([BIN / "urma_perftest", "--op", "send", "--size", "512", "--iters", "4001", "--cq-mod", "8",
                     "--jettys", "2"], tmp_path)
     assert rc == 0 and "errors 0" in out, out
+
+
+def test_urma_admin_topology_aggregation_and_path_statistics(tmp_path):
+    rc, out = _run([BIN / "urma_admin", "topo"], tmp_path)
+    assert rc == 0 and "node(s)" in out and "paths node 0 -> node 1" in out, out
+    rc, out = _run([BIN / "urma_admin", "agg"], tmp_path)
+    assert rc == 0 and "bond0" in out, out
+    rc, out = _run([BIN / "urma_admin", "stats", "bond0", "1"], tmp_path)
+    assert rc == 0 and "2 path(s)" in out, out
+    rows = [l.split() for l in out.splitlines() if l[:1].isdigit()]
+    assert len(rows) == 2 and all(r[1] == "1" and int(r[2]) > 0 and r[3] == "0" for r in rows), out   # both up, balanced
+    rc, out = _run([BIN / "urma_admin", "stats", "shm0"], tmp_path)
+    assert rc == 0 and "0 path(s)" in out, out
