@@ -189,6 +189,19 @@ def bench_ll(rank, world, a):
     if world > 1:
         dist.all_reduce(stage, op=dist.ReduceOp.MAX)
     stage_us = [float(v) * 1e3 for v in stage.tolist()]
+    # inside the fused kernel: global-timer stamps of its stages (median of 5 calls, max over ranks)
+    ll.diagnose = True
+    tls = []
+    for _ in range(5):
+        ll.timeline_reset()
+        ll.moe(x, idx, w, tiled, None, out=out)
+        torch.cuda.synchronize()
+        tls.append(list(ll.timeline_us().values()))
+    ll.diagnose = False
+    tl = torch.tensor(tls, dtype=torch.float64).median(dim=0).values.cuda()
+    if world > 1:
+        dist.all_reduce(tl, op=dist.ReduceOp.MAX)
+    timeline = dict(zip(("rows_ready", "phase1", "phase2", "peers_done", "end"), [round(float(v), 1) for v in tl]))
     # the same layer as one CUDA-graph replay: no Python / launch cost between the three kernels
     t_graph = None
     try:
@@ -218,7 +231,8 @@ def bench_ll(rank, world, a):
                     weight_GBps=w_bytes / t_routed / 1e9))
     emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights (ExpertWeights.to_tiled)",
                     us=t_tiled * 1e6, frac_of_roofline=roof / t_tiled, weight_GBps=w_bytes / t_tiled / 1e9,
-                    stage_us={"ep_layout": stage_us[0], "ep_ll_dispatch": stage_us[1], "moe_fused": stage_us[2]}))
+                    stage_us={"ep_layout": stage_us[0], "ep_ll_dispatch": stage_us[1], "moe_fused": stage_us[2]},
+                    fused_timeline_us=timeline))
     if t_graph is not None:
         emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights, one CUDA-graph replay per layer",
                         us=t_graph * 1e6, frac_of_roofline=roof / t_graph, weight_GBps=w_bytes / t_graph / 1e9))

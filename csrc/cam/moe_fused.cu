@@ -56,6 +56,9 @@ struct FusedArgs {
   int w_tiled;             // weights are stored tile by tile (see umdk_moe_fused)
   int phase_mask;          // bit0: gate + both GEMM phases + combine-send + flags; bit1: wait + reduce + epoch advance
   int* status;
+  // optional [6] global-timer stamps (ns): [0] earliest CTA start, then the latest CTA to pass: [1] the wait for the
+  // dispatched rows, [2] phase 1, [3] phase 2, [4] the wait for the peers' combine flags, [5] the end of the kernel
+  unsigned long long* diag;
 };
 
 template <int PH>
@@ -423,6 +426,13 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t epoch = s_epoch;
   const uint64_t tag = (uint64_t)epoch + 1;
+  auto stamp = [&](int i) {
+    if (a.diag && threadIdx.x == 0) {
+      if (i == 0) atomicMin(&a.diag[0], globaltimer_ns());
+      else atomicMax(&a.diag[i], globaltimer_ns());
+    }
+  };
+  stamp(0);
 
   if (a.wait_n > 0) {
     if (threadIdx.x < a.wait_n) {
@@ -433,6 +443,7 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
     }
     __syncthreads();
   }
+  stamp(1);
   for (int i = threadIdx.x; i <= a.G; i += blockDim.x) sh.goff[i] = a.group_off[i];
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -459,6 +470,7 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
   run_phase<1>(&tmW1, &tmX, a, sh, tmem_base, c, items1, grid);
   tc_fence_before();
   __syncthreads();  // the ring and the TMEM stages change their layout
+  stamp(2);
   tc_fence_after();
 
   // ---- phase 2: contiguous ranges sized so that all CTAs finish together ----
@@ -486,6 +498,7 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
+  stamp(3);
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -510,42 +523,59 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
     }
   }
   __syncthreads();
+  stamp(4);
   if (s_ok) {
+    // One work item = 512 bytes of one token's output (32 lanes x 16 bytes), spread over every warp of the grid: with
+    // decode-sized batches a warp per token would leave most of the GPU idle while a few warps walk whole rows.
+    // All K rows of an item are loaded before the first is used.
     const int lane = threadIdx.x & 31;
     const int nvec = a.H / 8;
+    const int nchunk = (nvec + 31) / 32;
     const int nwarps = kThreads / 32;
-    for (int t = blockIdx.x * nwarps + warp; t < a.T; t += gridDim.x * nwarps) {
+    const int k_sum = a.share_out ? a.Kt - 1 : a.Kt;
+    constexpr int kMaxK = 8;
+    for (int item = blockIdx.x * nwarps + warp; item < a.T * nchunk; item += gridDim.x * nwarps) {
+      const int t = item / nchunk;
+      const int v = (item % nchunk) * 32 + lane;
+      if (v >= nvec) continue;
       const int4* src = reinterpret_cast<const int4*>(self + a.comb_buf_off + (size_t)t * a.Kt * a.H * 2);
-      for (int v = lane; v < nvec; v += 32) {
-        float acc[8];
+      if (a.share_out) {
+        const bool have = a.topk_idx[(size_t)t * a.Kt + k_sum] >= 0;
+        const int4 val = have ? ld_relaxed_sys_v4(src + (size_t)k_sum * nvec + v) : make_int4(0, 0, 0, 0);
+        reinterpret_cast<int4*>(a.share_out + (size_t)t * a.H)[v] = val;
+      }
+      float acc[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        const int k_sum = a.share_out ? a.Kt - 1 : a.Kt;
-        if (a.share_out) {
-          const bool have = a.topk_idx[(size_t)t * a.Kt + k_sum] >= 0;
-          const int4 val = have ? ld_relaxed_sys_v4(src + (size_t)k_sum * nvec + v) : make_int4(0, 0, 0, 0);
-          reinterpret_cast<int4*>(a.share_out + (size_t)t * a.H)[v] = val;
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int k0 = 0; k0 < k_sum; k0 += kMaxK) {
+        int4 vals[kMaxK];
+        float wk[kMaxK];
+#pragma unroll
+        for (int u = 0; u < kMaxK; ++u) {
+          const int k = k0 + u;
+          const bool on = k < k_sum && a.topk_idx[(size_t)t * a.Kt + k] >= 0;
+          wk[u] = on ? a.topk_w[(size_t)t * a.Kt + k] : 0.f;
+          vals[u] = on ? ld_relaxed_sys_v4(src + (size_t)k * nvec + v) : make_int4(0, 0, 0, 0);
         }
-        for (int k = 0; k < k_sum; ++k) {
-          if (a.topk_idx[(size_t)t * a.Kt + k] < 0) continue;
-          const float wk = a.topk_w[(size_t)t * a.Kt + k];
-          const int4 val = ld_relaxed_sys_v4(src + (size_t)k * nvec + v);
-          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&val);
+#pragma unroll
+        for (int u = 0; u < kMaxK; ++u) {
+          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&vals[u]);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float2 f = __bfloat1622float2(p[i]);
-            acc[2 * i] = fmaf(wk, f.x, acc[2 * i]);
-            acc[2 * i + 1] = fmaf(wk, f.y, acc[2 * i + 1]);
+            acc[2 * i] = fmaf(wk[u], f.x, acc[2 * i]);
+            acc[2 * i + 1] = fmaf(wk[u], f.y, acc[2 * i + 1]);
           }
         }
-        int4 o;
-        __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        reinterpret_cast<int4*>(a.out + (size_t)t * a.H)[v] = o;
       }
+      int4 o;
+      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      reinterpret_cast<int4*>(a.out + (size_t)t * a.H)[v] = o;
     }
   }
+  stamp(5);
   if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
     if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
   }
@@ -582,6 +612,7 @@ struct UmdkMoeFusedParams {
   uint32_t* ctrl;
   int phase_mask;
   int* status;
+  unsigned long long* diag;   // optional timeline, see FusedArgs::diag
 };
 
 // Weight layouts. Row-major (w_tiled = 0): every 128 x 128-byte weight tile that a k-block needs is 128 separate
@@ -625,6 +656,7 @@ UMDK_API int umdk_moe_fused(const UmdkMoeFusedParams* p, void* stream) {
   a.phase_mask = p->phase_mask ? p->phase_mask : 3;
   a.w_tiled = p->w_tiled;
   a.status = p->status;
+  a.diag = p->diag;
   CUtensorMap tmW1, tmX, tmW2, tmH;
   int bad;
   if (p->w_tiled) {

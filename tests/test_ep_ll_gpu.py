@@ -196,3 +196,28 @@ def test_low_latency_moe_cuda_graph_replay():
             assert int(cnt.sum()) == int((iin >= 0).sum())
     finally:
         heap.close()
+
+
+def test_fused_kernel_timeline_in_diagnose_mode():
+    """Diagnose mode stamps the stages of the fused kernel; they come out in order and the result is unchanged."""
+    from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
+    from umdk_b200.parallel.symm import SymmetricHeap
+    R, T, H, F, E, K = 1, 96, 1024, 512, 8, 4
+    w1q, w1s, w2q, w2s = _weights(E, H, F, seed=23)
+    xs, idxs, ws = _inputs(R, T, H, E, K, seed=9)
+    heap = SymmetricHeap(EpLowLatency.heap_bytes(R, E, K, H, T))
+    try:
+        st = EpLowLatency(heap, E, K, H, F, T)
+        w = ExpertWeights(w1q.cuda(), w1s.cuda(), w2q.cuda(), w2s.cuda())
+        st.diagnose = True
+        st.timeline_reset()
+        out, _, _ = st.moe(xs[0].cuda(), idxs[0].cuda(), ws[0].cuda(), w, None)
+        torch.cuda.synchronize()
+        st.check()
+        tl = st.timeline_us()
+        order = [tl[k] for k in ("rows_ready", "phase1", "phase2", "peers_done", "end")]
+        assert order[0] >= 0 and all(b >= a for a, b in zip(order, order[1:])) and order[-1] < 1e6, tl
+        want = ref.ref_fused_moe(xs[0], idxs[0], ws[0], w1q, w1s, w2q, w2s)
+        assert ref.mean_rel_err(out.float().cpu(), want) < 0.02
+    finally:
+        heap.close()

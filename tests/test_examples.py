@@ -69,3 +69,18 @@ def test_prefill_sample_gpu():
                     "--hidden", "1024", "--experts-per-rank", "8", "--topk", "4", "--iters", "3", "--warmup", "1"])
     assert rc == 0, out[-3000:]
     assert _json_lines(out)[0]["ok"] is True
+
+
+@pytest.mark.parametrize("script,args", [
+    ("urma_sample.py", ["--self"]),
+    ("urpc_echo.py", ["--calls", "50", "--psk", "ab" * 32]),
+    ("umq_pingpong.py", ["--rounds", "50"]),
+    ("dlock_counter.py", ["--threads", "3", "--increments", "50", "--fair"]),
+])
+def test_host_library_samples(script, args, tmp_path):
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"))
+    (tmp_path / "urma").mkdir()
+    p = subprocess.run([sys.executable, os.path.join(EX, script)] + args, cwd=ROOT, env=env, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT, text=True, timeout=120)
+    assert p.returncode == 0, p.stdout[-2000:]
+    assert _json_lines(p.stdout)[-1]["ok"] is True

@@ -61,7 +61,7 @@ class _MoeFusedParams(ctypes.Structure):
         ("comb_buf_off", ctypes.c_uint64), ("comb_flag_off", ctypes.c_uint64),
         ("row_meta", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p), ("topk_w", ctypes.c_void_p),
         ("out", ctypes.c_void_p), ("share_out", ctypes.c_void_p), ("ctrl", ctypes.c_void_p),
-        ("phase_mask", ctypes.c_int), ("status", ctypes.c_void_p),
+        ("phase_mask", ctypes.c_int), ("status", ctypes.c_void_p), ("diag", ctypes.c_void_p),
     ]
 
 
@@ -161,6 +161,9 @@ class EpLowLatency:
         dev = torch.device("cuda", torch.cuda.current_device())
         self.device = dev
         self.ctrl = torch.zeros(16, dtype=torch.int32, device=dev)
+        # diagnose mode: the fused kernel stamps its stages with the global timer (see timeline_us)
+        self.diagnose = False
+        self.diag_fused = torch.zeros(6, dtype=torch.int64, device=dev)
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
         self.layout_bar = torch.zeros(2, dtype=torch.int32, device=dev)
         self.layout_scratch = torch.empty(((t_cap + 31) // 32) * (num_experts + self.R), dtype=torch.int32, device=dev)
@@ -269,6 +272,19 @@ class EpLowLatency:
         if rc != 0:
             raise RuntimeError(f"umdk_moe_gemm(mode 2) failed: {rc}")
 
+    def timeline_reset(self) -> None:
+        """Arms the stage stamps of the next fused call (diagnose mode)."""
+        self.diag_fused.zero_()
+        self.diag_fused[0] = torch.iinfo(torch.int64).max
+
+    def timeline_us(self) -> dict:
+        """Stages of the last fused kernel in microseconds since its first CTA started, each taken at the LAST CTA to
+        get there: rows_ready (dispatched rows arrived), phase1 (GEMM1 + SwiGLU + requant), phase2 (GEMM2 + combine
+        send), peers_done (every peer's combine flag seen), end."""
+        d = self.diag_fused.tolist()
+        names = ("rows_ready", "phase1", "phase2", "peers_done", "end")
+        return {n: (d[i + 1] - d[0]) / 1e3 for i, n in enumerate(names)}
+
     def _fused(self, w: ExpertWeights, topk_idx, topk_w, out, phase_mask: int = 3, share_out=None):
         """GEMM1 + SwiGLU + re-quant + GEMM2 + combine-send + weighted reduction in ONE persistent launch
         (csrc/cam/moe_fused.cu)."""
@@ -288,6 +304,7 @@ class EpLowLatency:
         p.topk_idx, p.topk_w, p.out = topk_idx.data_ptr(), topk_w.data_ptr(), out.data_ptr()
         p.share_out = share_out.data_ptr() if share_out is not None else None
         p.ctrl, p.phase_mask, p.status = self.ctrl.data_ptr(), phase_mask, self.status.data_ptr()
+        p.diag = self.diag_fused.data_ptr() if self.diagnose else None
         rc = self.lib.umdk_moe_fused(ctypes.byref(p), _native.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"umdk_moe_fused failed: {rc}")
