@@ -168,6 +168,9 @@ def bench_ll(rank, world, a):
     t_two = timed(lambda: ll.moe(x, idx, w, experts, None, out=out, fused=False), a.iters, a.warmup, world)
     tiled = experts.to_tiled()
     t_tiled = timed(lambda: ll.moe(x, idx, w, tiled, None, out=out), a.iters, a.warmup, world)
+    ll.inline_layout = False    # the layout as a kernel launch of its own, for comparison
+    t_sep_layout = timed(lambda: ll.moe(x, idx, w, tiled, None, out=out), a.iters, a.warmup, world)
+    ll.inline_layout = True
     # stage breakdown of the same call chain: events between the three launches (stage times include waiting for peers)
     from umdk_b200.ops.ep import layout as ep_layout
     stage = torch.zeros(3, dtype=torch.float64, device="cuda")
@@ -231,6 +234,7 @@ def bench_ll(rank, world, a):
                     weight_GBps=w_bytes / t_routed / 1e9))
     emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights (ExpertWeights.to_tiled)",
                     us=t_tiled * 1e6, frac_of_roofline=roof / t_tiled, weight_GBps=w_bytes / t_tiled / 1e9,
+                    us_with_separate_layout_launch=t_sep_layout * 1e6,
                     stage_us={"ep_layout": stage_us[0], "ep_ll_dispatch": stage_us[1], "moe_fused": stage_us[2]},
                     fused_timeline_us=timeline))
     if t_graph is not None:

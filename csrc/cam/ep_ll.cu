@@ -24,8 +24,9 @@ struct LLDispatchArgs {
   PeerTable peers;
   const __nv_bfloat16* x;     // [T, H]
   const int64_t* topk_idx;    // [T, K] (-1 = skip)
-  const int* send_idx;        // [T, K] position inside the expert bucket on this rank (layout kernel)
-  const int* num_per_expert;  // [E]
+  const int* send_idx;        // [T, K] position inside the expert bucket on this rank (layout kernel), or null:
+                              // then every CTA derives both tables from topk_idx itself, in shared memory
+  const int* num_per_expert;  // [E] (null together with send_idx)
   int T;
   int* group_off;             // out [E_local + 1]: row offsets of this rank's experts inside its slab
   int64_t* recv_per_expert;   // out [E_local]
@@ -81,6 +82,54 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
     s_epoch = a.ctrl[0];
     s_ok = 1;
   }
+  // ---- layout inside the kernel (decode-sized inputs) ----
+  // Every CTA computes, for all T x K entries, the position of the entry inside its expert's bucket (token-major
+  // order) and the bucket sizes: per 32-token chunk a warp walks its tokens in order with shared-memory counters,
+  // then the chunks are scanned per expert. A few microseconds of redundant work per CTA instead of a kernel launch
+  // and a pass through global memory.
+  extern __shared__ __align__(16) uint8_t ll_dyn[];
+  const bool own_layout = a.send_idx == nullptr;
+  const int n_chunks = (a.T + 31) / 32;
+  uint16_t* s_hist = reinterpret_cast<uint16_t*>(ll_dyn);              // [n_chunks][E] counts, then exclusive bases
+  uint16_t* s_sidx = s_hist + (size_t)n_chunks * g.E;                  // [T * K] positions
+  __shared__ int s_npe[1024];
+  if (own_layout) {
+    for (int i = threadIdx.x; i < n_chunks * g.E; i += blockDim.x) s_hist[i] = 0;
+    __syncthreads();
+    for (int c = warp; c < n_chunks; c += kLLWarps) {
+      uint16_t* hist = s_hist + (size_t)c * g.E;
+      const int t_end = min(a.T, (c + 1) * 32);
+      for (int t = c * 32; t < t_end; ++t) {
+        if (lane < g.K) {
+          const long long ee = a.topk_idx[(size_t)t * g.K + lane];
+          uint16_t pos = 0xffff;
+          if (ee >= 0 && ee < g.E) {
+            // the K experts of one token are distinct, so the lanes touch different counters; a repeated expert in
+            // one row would only make the two entries share a position, which the bounds checks below reject
+            pos = hist[ee];
+            hist[ee] = pos + 1;
+          }
+          s_sidx[(size_t)t * g.K + lane] = pos;
+        }
+        __syncwarp();
+      }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < g.E; e += blockDim.x) {
+      int run = 0;
+      for (int c = 0; c < n_chunks; ++c) {
+        const int v = s_hist[(size_t)c * g.E + e];
+        s_hist[(size_t)c * g.E + e] = (uint16_t)run;
+        run += v;
+      }
+      s_npe[e] = run;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.T * g.K; i += blockDim.x) {
+      const long long ee = a.topk_idx[i];
+      if (ee >= 0 && ee < g.E) s_sidx[i] += s_hist[(size_t)((i / g.K) / 32) * g.E + ee];
+    }
+  }
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const uint64_t tag = (uint64_t)epoch + 1;
@@ -89,7 +138,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
   if ((a.phase_mask & 1) && blockIdx.x == 0) {
     for (int d = warp; d < g.R; d += kLLWarps) {
       int* dst = reinterpret_cast<int*>(a.peers.base[d] + a.off.cnt[0]) + (size_t)g.rank * g.E;
-      for (int i = lane; i < g.E; i += 32) dst[i] = a.num_per_expert[i];
+      for (int i = lane; i < g.E; i += 32) dst[i] = own_layout ? s_npe[i] : a.num_per_expert[i];
       __threadfence_system();
       __syncwarp();
       if (lane == 0) st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[d] + a.off.cnt_flag[0]) + g.rank, tag);
@@ -159,7 +208,8 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
       float* ds = nullptr;
       if (ee >= 0 && ee < g.E) {
         const int e = (int)ee, d = e / g.E_local;
-        const int row = s_base[e] + a.send_idx[(size_t)t * g.K + lane];
+        const int row = s_base[e] + (own_layout ? (int)s_sidx[(size_t)t * g.K + lane]
+                                               : a.send_idx[(size_t)t * g.K + lane]);
         if (row < 0 || row >= g.n_cap) {
           umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, e, row);
         } else {
@@ -316,7 +366,20 @@ UMDK_API int umdk_ep_ll_dispatch(const UmdkEpLLDispatchParams* p, void* stream) 
   a.phase_mask = p->phase_mask ? p->phase_mask : 3;
   int grid = p->num_ctas > 0 ? p->num_ctas : 32;
   if (grid > sm_count()) grid = sm_count();
-  ep_ll_dispatch_kernel<<<grid, kLLThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  size_t dyn = 0;
+  if (!p->send_idx) {
+    // layout inside the kernel: 16-bit counters and positions, so at most 65535 entries per expert and a table that
+    // fits in shared memory
+    if (p->num_per_expert || p->T > 2048 || p->E > 1024) return -UMDK_ERR_BAD_ARG;
+    dyn = sizeof(uint16_t) * ((size_t)((p->T + 31) / 32) * p->E + (size_t)p->T * p->K);
+    if (dyn > 160 * 1024) return -UMDK_ERR_BAD_ARG;
+    if (dyn > 16 * 1024) {
+      UMDK_CUDA_CHECK(cudaFuncSetAttribute(ep_ll_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    }
+  } else if (!p->num_per_expert) {
+    return -UMDK_ERR_BAD_ARG;
+  }
+  ep_ll_dispatch_kernel<<<grid, kLLThreads, dyn, static_cast<cudaStream_t>(stream)>>>(a);
   UMDK_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

@@ -221,3 +221,36 @@ def test_fused_kernel_timeline_in_diagnose_mode():
         assert ref.mean_rel_err(out.float().cpu(), want) < 0.02
     finally:
         heap.close()
+
+
+@pytest.mark.parametrize("T,E,K", [(1, 8, 1), (37, 16, 4), (128, 256, 8), (500, 64, 6)])
+def test_dispatch_with_layout_inside_matches_separate_layout(T, E, K):
+    """The dispatch kernel's own bucket positions and sizes give the same slab as the layout kernel's."""
+    from umdk_b200.ops.ep_ll import EpLowLatency
+    from umdk_b200.parallel.symm import SymmetricHeap
+    H, F = 1024, 512
+    xs, idxs, _ = _inputs(1, T, H, E, K, seed=T)
+    idx = idxs[0].clone()
+    if T > 4:
+        idx[::5, 0] = -1                      # dropped entries
+    heap = SymmetricHeap(EpLowLatency.heap_bytes(1, E, K, H, T))
+    try:
+        st = EpLowLatency(heap, E, K, H, F, T)
+        x, di = xs[0].cuda(), idx.cuda()
+        outs = []
+        for inline in (False, True):
+            st.inline_layout = inline
+            st.dispatch(x, di)
+            torch.cuda.synchronize()
+            st.check()
+            n = int(st.group_off[-1])
+            sx, ss, sm = st.slab_views()
+            outs.append((st.group_off.clone(), st.recv_per_expert.clone(), sx[:n].view(torch.uint8).clone(),
+                         ss[:n].clone(), sm[:n].clone()))
+            # close the call so that the next dispatch starts a new epoch
+            st.ctrl[0] += 1
+        for a, b in zip(outs[0], outs[1]):
+            assert torch.equal(a, b)
+        assert int(outs[0][0][-1]) == int((idx >= 0).sum())
+    finally:
+        heap.close()

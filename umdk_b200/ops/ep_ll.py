@@ -164,6 +164,7 @@ class EpLowLatency:
         # diagnose mode: the fused kernel stamps its stages with the global timer (see timeline_us)
         self.diagnose = False
         self.diag_fused = torch.zeros(6, dtype=torch.int64, device=dev)
+        self.inline_layout = True   # False: run the layout kernel as a launch of its own before every dispatch
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
         self.layout_bar = torch.zeros(2, dtype=torch.int32, device=dev)
         self.layout_scratch = torch.empty(((t_cap + 31) // 32) * (num_experts + self.R), dtype=torch.int32, device=dev)
@@ -218,7 +219,10 @@ class EpLowLatency:
         assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and topk_idx.dtype == torch.int64
         T = x.shape[0]
         assert T <= self.T_cap and x.shape[1] == self.H
-        if lay is None:
+        # decode-sized inputs: the dispatch kernel derives bucket positions and sizes itself (no layout launch)
+        inline = lay is None and self.inline_layout and T <= 2048 and self.E <= 1024 and \
+            2 * (((T + 31) // 32) * self.E + T * self.K) <= 160 * 1024
+        if lay is None and not inline:
             lay = ep_layout(topk_idx, self.E, self.R, self.layout_scratch, self.layout_bar, self.status)
         p = _LLDispatchParams()
         p.R, p.rank, p.E, p.K, p.H, p.T_cap, p.T = self.R, self.rank, self.E, self.K, self.H, self.T_cap, T
@@ -226,7 +230,10 @@ class EpLowLatency:
         for i, pp in enumerate(self.heap.peer_ptrs):
             p.peers[i] = pp
         p.x, p.topk_idx = x.data_ptr(), topk_idx.data_ptr()
-        p.send_idx, p.num_per_expert = lay.send_token_idx.data_ptr(), lay.num_tokens_per_expert.data_ptr()
+        if lay is not None:
+            p.send_idx, p.num_per_expert = lay.send_token_idx.data_ptr(), lay.num_tokens_per_expert.data_ptr()
+        else:
+            p.send_idx = p.num_per_expert = None
         p.group_off, p.recv_per_expert = self.group_off.data_ptr(), self.recv_per_expert.data_ptr()
         p.ctrl, p.status = self.ctrl.data_ptr(), self.status.data_ptr()
         rc = self.lib.umdk_ep_ll_dispatch(ctypes.byref(p), _native.stream_ptr())
