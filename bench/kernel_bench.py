@@ -286,6 +286,8 @@ def main():
     ap.add_argument("--topk", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--fused-experts", type=int, default=0,
+                    help="moe_fused: local experts (32 = the share of one rank at EP = 8); default 256, or 8 with --small")
     a = ap.parse_args()
     if a.small:
         a.experts, a.batch, a.ctx, a.tokens = min(a.experts, 8), min(a.batch, 16), min(a.ctx, 8192), min(a.tokens, 1024)
@@ -296,7 +298,7 @@ def main():
     if a.what in ("mla", "all"):
         bench_mla(a.batch, a.ctx, a.topk)
     if a.what in ("moe_fused", "all"):
-        bench_moe_fused(a.experts if a.small else 256, 128)
+        bench_moe_fused(a.fused_experts or (a.experts if a.small else 256), 128)
     if a.what in ("tp", "all"):
         bench_tp_loopback(2048, 4096, 4096) if a.small else bench_tp_loopback(8192, 8192, 7168)
     if a.what in ("kv_gather", "all"):

@@ -92,8 +92,14 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
   const int n_chunks = (a.T + 31) / 32;
   uint16_t* s_hist = reinterpret_cast<uint16_t*>(ll_dyn);              // [n_chunks][E] counts, then exclusive bases
   uint16_t* s_sidx = s_hist + (size_t)n_chunks * g.E;                  // [T * K] positions
+  int16_t* s_eid = reinterpret_cast<int16_t*>(s_sidx + (size_t)a.T * g.K);   // [T * K] expert ids (-1 = none)
   __shared__ int s_npe[1024];
   if (own_layout) {
+    // all indices first, in one round of loads: the walk below must not wait on global memory at every step
+    for (int i = threadIdx.x; i < a.T * g.K; i += blockDim.x) {
+      const long long ee = a.topk_idx[i];
+      s_eid[i] = (ee >= 0 && ee < g.E) ? (int16_t)ee : (int16_t)-1;
+    }
     for (int i = threadIdx.x; i < n_chunks * g.E; i += blockDim.x) s_hist[i] = 0;
     __syncthreads();
     for (int c = warp; c < n_chunks; c += kLLWarps) {
@@ -101,9 +107,9 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
       const int t_end = min(a.T, (c + 1) * 32);
       for (int t = c * 32; t < t_end; ++t) {
         if (lane < g.K) {
-          const long long ee = a.topk_idx[(size_t)t * g.K + lane];
+          const int ee = s_eid[(size_t)t * g.K + lane];
           uint16_t pos = 0xffff;
-          if (ee >= 0 && ee < g.E) {
+          if (ee >= 0) {
             // the K experts of one token are distinct, so the lanes touch different counters; a repeated expert in
             // one row would only make the two entries share a position, which the bounds checks below reject
             pos = hist[ee];
@@ -126,8 +132,8 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
     }
     __syncthreads();
     for (int i = threadIdx.x; i < a.T * g.K; i += blockDim.x) {
-      const long long ee = a.topk_idx[i];
-      if (ee >= 0 && ee < g.E) s_sidx[i] += s_hist[(size_t)((i / g.K) / 32) * g.E + ee];
+      const int ee = s_eid[i];
+      if (ee >= 0) s_sidx[i] += s_hist[(size_t)((i / g.K) / 32) * g.E + ee];
     }
   }
   __syncthreads();
@@ -200,10 +206,14 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
   __syncthreads();
 
   const int nblk = g.H / 128;
-  for (int t = blockIdx.x * kLLWarps + warp; t < a.T; t += gridDim.x * kLLWarps) {
+  // One work item = 16 consecutive 1x128 blocks (2 KiB of fp8) of one token: a warp has all its eight 16-byte loads
+  // in flight at once, and a decode-sized batch still spreads over every warp of the grid.
+  const int nparts = (nblk + 15) / 16;
+  for (int item = blockIdx.x * kLLWarps + warp; item < a.T * nparts; item += gridDim.x * kLLWarps) {
+    const int t = item / nparts, part = item - t * nparts;
     __syncwarp();
     if (lane < g.K) {
-      const long long ee = a.topk_idx[(size_t)t * g.K + lane];
+      const long long ee = own_layout ? (long long)s_eid[(size_t)t * g.K + lane] : a.topk_idx[(size_t)t * g.K + lane];
       uint8_t* dx = nullptr;
       float* ds = nullptr;
       if (ee >= 0 && ee < g.E) {
@@ -215,9 +225,11 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
         } else {
           dx = a.peers.base[d] + a.off.slab_x[0] + (size_t)row * g.H;
           ds = reinterpret_cast<float*>(a.peers.base[d] + a.off.slab_s[0]) + (size_t)row * nblk;
-          int* meta = reinterpret_cast<int*>(a.peers.base[d] + a.off.slab_meta[0]) + (size_t)row * 2;
-          meta[0] = g.rank;
-          meta[1] = t * g.K + lane;
+          if (part == 0) {
+            int* meta = reinterpret_cast<int*>(a.peers.base[d] + a.off.slab_meta[0]) + (size_t)row * 2;
+            meta[0] = g.rank;
+            meta[1] = t * g.K + lane;
+          }
         }
       }
       s_dx[warp][lane] = dx;
@@ -225,34 +237,32 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
     }
     __syncwarp();
     const int4* xrow = reinterpret_cast<const int4*>(a.x + (size_t)t * g.H);
-    // four groups of four 1x128 blocks per step: eight 16-byte loads per lane are in flight together
-    for (int b0 = 0; b0 < nblk; b0 += 16) {
-      int4 raw[4][2];
+    const int b0 = part * 16;
+    int4 raw[4][2];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int blk = b0 + 4 * u + (lane >> 3);
-        if (blk < nblk) {
-          raw[u][0] = __ldg(xrow + blk * 16 + (lane & 7) * 2);
-          raw[u][1] = __ldg(xrow + blk * 16 + (lane & 7) * 2 + 1);
-        } else {
-          raw[u][0] = raw[u][1] = make_int4(0, 0, 0, 0);
-        }
+    for (int u = 0; u < 4; ++u) {
+      const int blk = b0 + 4 * u + (lane >> 3);
+      if (blk < nblk) {
+        raw[u][0] = __ldg(xrow + blk * 16 + (lane & 7) * 2);
+        raw[u][1] = __ldg(xrow + blk * 16 + (lane & 7) * 2 + 1);
+      } else {
+        raw[u][0] = raw[u][1] = make_int4(0, 0, 0, 0);
       }
+    }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int blk = b0 + 4 * u + (lane >> 3);
-        float f[16];
-        bf16x8_to_float(raw[u][0], f);
-        bf16x8_to_float(raw[u][1], f + 8);
-        float scale;
-        const int4 q = quant16(f, &scale);   // shuffles inside: executed by all lanes
-        if (blk < nblk) {
-          for (int k = 0; k < g.K; ++k) {
-            uint8_t* dx = s_dx[warp][k];
-            if (dx == nullptr) continue;
-            st_na_v4(dx + blk * 128 + (lane & 7) * 16, q);
-            if ((lane & 7) == 0) s_ds[warp][k][blk] = scale;
-          }
+    for (int u = 0; u < 4; ++u) {
+      const int blk = b0 + 4 * u + (lane >> 3);
+      float f[16];
+      bf16x8_to_float(raw[u][0], f);
+      bf16x8_to_float(raw[u][1], f + 8);
+      float scale;
+      const int4 q = quant16(f, &scale);   // shuffles inside: executed by all lanes
+      if (blk < nblk) {
+        for (int k = 0; k < g.K; ++k) {
+          uint8_t* dx = s_dx[warp][k];
+          if (dx == nullptr) continue;
+          st_na_v4(dx + blk * 128 + (lane & 7) * 16, q);
+          if ((lane & 7) == 0) s_ds[warp][k][blk] = scale;
         }
       }
     }
@@ -371,7 +381,7 @@ UMDK_API int umdk_ep_ll_dispatch(const UmdkEpLLDispatchParams* p, void* stream) 
     // layout inside the kernel: 16-bit counters and positions, so at most 65535 entries per expert and a table that
     // fits in shared memory
     if (p->num_per_expert || p->T > 2048 || p->E > 1024) return -UMDK_ERR_BAD_ARG;
-    dyn = sizeof(uint16_t) * ((size_t)((p->T + 31) / 32) * p->E + (size_t)p->T * p->K);
+    dyn = sizeof(uint16_t) * ((size_t)((p->T + 31) / 32) * p->E + 2 * (size_t)p->T * p->K);
     if (dyn > 160 * 1024) return -UMDK_ERR_BAD_ARG;
     if (dyn > 16 * 1024) {
       UMDK_CUDA_CHECK(cudaFuncSetAttribute(ep_ll_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));

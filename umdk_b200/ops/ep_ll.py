@@ -221,7 +221,7 @@ class EpLowLatency:
         assert T <= self.T_cap and x.shape[1] == self.H
         # decode-sized inputs: the dispatch kernel derives bucket positions and sizes itself (no layout launch)
         inline = lay is None and self.inline_layout and T <= 2048 and self.E <= 1024 and \
-            2 * (((T + 31) // 32) * self.E + T * self.K) <= 160 * 1024
+            2 * (((T + 31) // 32) * self.E + 2 * T * self.K) <= 160 * 1024
         if lay is None and not inline:
             lay = ep_layout(topk_idx, self.E, self.R, self.layout_scratch, self.layout_bar, self.status)
         p = _LLDispatchParams()
