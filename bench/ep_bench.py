@@ -100,7 +100,7 @@ def bench_normal(rank, world, a):
     y = torch.randn(out.recv_x.shape[0], H, device="cuda").to(torch.bfloat16)
     res = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
     remote_frac = (world - 1) / world
-    t_lay = timed(lambda: st.layout(idx), a.iters, a.warmup, world)
+    t_lay = timed(lambda: st.layout(idx, out=lay), a.iters, a.warmup, world)
     t_disp = timed(lambda: st.dispatch(x, idx, w, lay=lay, quant=True, out=out), a.iters, a.warmup, world)
     t_comb = timed(lambda: st.combine(y, out, out=res), a.iters, a.warmup, world)
     st.check("normal")

@@ -46,6 +46,13 @@ def test_layout_matches_reference(T, K, E, R):
     assert torch.equal(got.is_token_in_rank.cpu(), want.is_token_in_rank)
     assert torch.equal(got.send_token_idx.cpu(), want.send_token_idx)
     assert torch.equal(got.rank_slot.cpu(), want.rank_slot)
+    # the same call into the tensors of the earlier result (no allocations on the call path)
+    idx2 = torch.roll(idxs[0], 3, 0)
+    again = layout(idx2.cuda(), E, R, out=got)
+    want2 = ref.ref_layout(idx2, E, R)
+    torch.cuda.synchronize()
+    assert again is got and torch.equal(got.send_token_idx.cpu(), want2.send_token_idx)
+    assert torch.equal(got.is_token_in_rank.cpu(), want2.is_token_in_rank)
 
 
 @pytest.mark.parametrize("R,T,H,E,K,quant", [

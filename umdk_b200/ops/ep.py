@@ -116,19 +116,25 @@ class DispatchResult:
     num_recv: Optional[int] = None       # host value of N when the caller asked for it
 
 
-def layout(topk_idx: torch.Tensor, num_experts: int, num_ranks: int, scratch=None, bar=None, status=None
-           ) -> LayoutResult:
-    """GPU ``get_dispatch_layout``: stable bucket positions per expert and per destination rank."""
+def layout(topk_idx: torch.Tensor, num_experts: int, num_ranks: int, scratch=None, bar=None, status=None,
+           out: Optional[LayoutResult] = None) -> LayoutResult:
+    """GPU ``get_dispatch_layout``: stable bucket positions per expert and per destination rank. ``out`` reuses the
+    tensors of an earlier result of the same shape (no allocations on the call path)."""
     lib = _native.cam()
     assert topk_idx.is_cuda and topk_idx.dtype == torch.int64 and topk_idx.is_contiguous()
     T, K = topk_idx.shape
     dev = topk_idx.device
     E, R = num_experts, num_ranks
-    npe = torch.empty(E, dtype=torch.int32, device=dev)
-    npr = torch.empty(R, dtype=torch.int32, device=dev)
-    inr = torch.empty(T, R, dtype=torch.uint8, device=dev)
-    sidx = torch.empty(T, K, dtype=torch.int32, device=dev)
-    rslot = torch.empty(T, R, dtype=torch.int32, device=dev)
+    if out is not None:
+        npe, npr, sidx, rslot = out.num_tokens_per_expert, out.num_tokens_per_rank, out.send_token_idx, out.rank_slot
+        inr = out.is_token_in_rank.view(torch.uint8)
+        assert sidx.shape == (T, K) and rslot.shape == (T, R) and npe.numel() == E
+    else:
+        npe = torch.empty(E, dtype=torch.int32, device=dev)
+        npr = torch.empty(R, dtype=torch.int32, device=dev)
+        inr = torch.empty(T, R, dtype=torch.uint8, device=dev)
+        sidx = torch.empty(T, K, dtype=torch.int32, device=dev)
+        rslot = torch.empty(T, R, dtype=torch.int32, device=dev)
     chunks = (T + 31) // 32
     if scratch is None or scratch.numel() < max(1, chunks) * (E + R):
         scratch = torch.empty(max(1, chunks) * (E + R), dtype=torch.int32, device=dev)
@@ -141,7 +147,7 @@ def layout(topk_idx: torch.Tensor, num_experts: int, num_ranks: int, scratch=Non
                             _native.ptr(status), _native.stream_ptr())
     if rc != 0:
         raise RuntimeError(f"umdk_ep_layout failed: {rc}")
-    return LayoutResult(npe, npr, inr.view(torch.bool), sidx, rslot)
+    return out if out is not None else LayoutResult(npe, npr, inr.view(torch.bool), sidx, rslot)
 
 
 class EpNormal:
@@ -185,8 +191,8 @@ class EpNormal:
         return int(n)
 
     @_trace.traced("umdk.ep.layout")
-    def layout(self, topk_idx: torch.Tensor) -> LayoutResult:
-        return layout(topk_idx, self.E, self.R, self.layout_scratch, self.layout_bar, self.status)
+    def layout(self, topk_idx: torch.Tensor, out: Optional[LayoutResult] = None) -> LayoutResult:
+        return layout(topk_idx, self.E, self.R, self.layout_scratch, self.layout_bar, self.status, out=out)
 
     @_trace.traced("umdk.ep.notify")
     def notify(self, lay: LayoutResult, phase_mask: int = 3, out: Optional[NotifyResult] = None) -> NotifyResult:

@@ -50,7 +50,7 @@ class TpComm:
     ``ag_gemm(x_shard [Ts, K], w [N, K]) -> [R*Ts, N]`` and ``gemm_rs(y [R*Ts, Kr], w [N, Kr]) -> [Ts, N]``.
     """
 
-    def __init__(self, heap: SymmetricHeap, ts: int, k_ag: int, n_rs: int, n_copy: int = 16, max_ctas: int = 0,
+    def __init__(self, heap: SymmetricHeap, ts: int, k_ag: int, n_rs: int, n_copy: int = 0, max_ctas: int = 0,
                  single_cta: bool = False):
         self.lib = _native.cam()
         self.heap, self.R, self.rank = heap, heap.world, heap.rank
@@ -75,6 +75,10 @@ class TpComm:
         self.chunk_done = torch.zeros(self.R, dtype=torch.int32, device=dev)
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
         self.xg = torch.empty(self.R * ts, k_ag, dtype=torch.bfloat16, device=dev)
+        # CTAs that only move peer shards (all-gather -> GEMM): enough to stay ahead of the GEMM, no more, because
+        # each one is taken from the GEMM. 0 = by group size: 4 for two ranks up to 16 for eight.
+        if n_copy <= 0:
+            n_copy = min(16, max(4, 2 * (self.R - 1) + 2))
         self.n_copy, self.max_ctas = n_copy, max_ctas
         # False: CTA pairs (256 x 256 tiles) where Ts and N are multiples of 256; True: always one CTA per tile
         self.single_cta = single_cta
