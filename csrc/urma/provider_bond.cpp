@@ -761,7 +761,20 @@ urma_status_t op_delete_jetty_indexed(urma_jetty_t* jt) {
 
 urma_status_t op_query_jetty(urma_jetty_t* jt, urma_jetty_cfg_t* cfg, urma_jetty_state_t* st) {
   *cfg = jt->cfg;
-  *st = URMA_JETTY_STATE_READY;
+  // the virtual jetty is as ready as its best member: READY while any member path is, else the first member's state
+  BJetty* j = reinterpret_cast<BJetty*>(jt->priv);
+  urma_jetty_state_t first = URMA_JETTY_STATE_READY;
+  bool have = false, ready = false;
+  for (auto* p : j->p) {
+    if (!p) continue;
+    urma_jetty_cfg_t pc;
+    urma_jetty_state_t ps;
+    if (urma_query_jetty(p, &pc, &ps) != URMA_SUCCESS) continue;
+    if (!have) first = ps;
+    have = true;
+    ready |= ps == URMA_JETTY_STATE_READY;
+  }
+  *st = (!have || ready) ? URMA_JETTY_STATE_READY : first;
   return URMA_SUCCESS;
 }
 

@@ -45,6 +45,7 @@ Core& core() {
 // ------------------------------------------------------------------------------------------------ logging
 std::atomic<int> g_log_level{URMA_VLOG_LEVEL_WARNING};
 urma_log_cb_t g_log_cb = nullptr;
+urma_loc_log_cb g_loc_log_cb = nullptr;
 thread_local char t_tag[32] = "";
 std::atomic<uint64_t> g_last_log_ns{0};
 std::atomic<uint32_t> g_suppressed{0};
@@ -135,7 +136,9 @@ void urma_log(int level, const char* func, int line, const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(msg + off, sizeof(msg) - off, fmt, ap);
   va_end(ap);
-  if (g_log_cb) {
+  if (g_loc_log_cb) {
+    g_loc_log_cb(level, func, line, msg + off);
+  } else if (g_log_cb) {
     g_log_cb(level, msg);
   } else {
     syslog(level, "%s", msg);
@@ -157,6 +160,11 @@ void urma_log_set_level(urma_vlog_level_t level) {
   if (level >= URMA_VLOG_LEVEL_EMERG && level <= URMA_VLOG_LEVEL_DEBUG) g_log_level = level;
 }
 void urma_log_set_thread_tag(const char* tag) { snprintf(t_tag, sizeof(t_tag), "%s", tag ? tag : ""); }
+const char* urma_log_get_thread_tag(void) { return t_tag; }
+urma_status_t urma_register_loc_log_func(urma_loc_log_cb func) {
+  g_loc_log_cb = func;  // NULL goes back to the plain callback / syslog
+  return URMA_SUCCESS;
+}
 
 // ================================================================================================ perf API
 urma_status_t urma_start_perf(void) {

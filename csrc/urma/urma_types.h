@@ -418,6 +418,118 @@ typedef enum urma_vlog_level {
   URMA_VLOG_LEVEL_DEBUG
 } urma_vlog_level_t;
 typedef void (*urma_log_cb_t)(int level, char* message);
+/* like urma_log_cb_t, with the source location as separate arguments */
+typedef void (*urma_loc_log_cb)(int level, const char* function, int line, const char* message);
+
+/* ---- extended control plane (urma_ext.cpp) ---- */
+/* Options of urma_set_*_opt / urma_get_*_opt. "rw": may be changed between urma_alloc_* and urma_active_*;
+ * "ro": fixed by the cfg given to urma_alloc_*, readable at any time. */
+typedef enum urma_opt_name {
+  URMA_OPT_DEPTH = 1,            /* ro uint32 */
+  URMA_OPT_FLAG = 2,             /* ro uint32 */
+  URMA_OPT_USER_CTX = 3,         /* rw uint64 */
+  URMA_OPT_TRANS_MODE = 4,       /* ro uint32 (jfs, jfr, jetty) */
+  URMA_OPT_PRIORITY = 5,         /* rw uint8 (jfs, jetty) */
+  URMA_OPT_RNR_RETRY = 6,        /* rw uint8 (jfs, jetty) */
+  URMA_OPT_ERR_TIMEOUT = 7,      /* rw uint8 (jfs, jetty) */
+  URMA_OPT_MIN_RNR_TIMER = 8,    /* rw uint8 (jfr, jetty) */
+  URMA_OPT_MODERATE_COUNT = 9,   /* rw uint32 (jfc): completions per event */
+  URMA_OPT_MODERATE_PERIOD = 10, /* rw uint32 (jfc): microseconds */
+  URMA_OPT_RX_THRESHOLD = 11,    /* rw uint32 (jfr): low-watermark event */
+  URMA_OPT_ID = 12,              /* ro uint32: the object's id */
+  URMA_OPT_STATE = 13,           /* ro uint32: urma_jetty_state_t (jfs, jfr, jetty); 1 when active (jfc) */
+  URMA_OPT_CTX_LOG_TAG = 100,    /* rw string (context): tag put into this thread's log lines by context calls */
+  URMA_OPT_CTX_USER_DATA = 101   /* rw uint64 (context) */
+} urma_opt_name_t;
+
+typedef enum urma_notify_type { URMA_IMPORT_JETTY_NOTIFY = 0, URMA_BIND_JETTY_NOTIFY = 1, URMA_ADVISE_JFR_NOTIFY = 2 }
+    urma_notify_type_t;
+typedef struct urma_notify {
+  urma_notify_type_t type;
+  urma_status_t status;
+  uint64_t user_ctx;
+  union {
+    urma_target_jetty_t* tjetty; /* import, advise */
+    urma_jetty_t* jetty;         /* bind */
+  };
+} urma_notify_t;
+typedef struct urma_notifier {
+  urma_context_t* ctx;
+  int fd; /* readable while notifications are pending (eventfd) */
+  void* priv;
+} urma_notifier_t;
+typedef void (*urma_advise_async_cb_func)(urma_status_t status, void* arg);
+
+typedef struct urma_import_jetty_ex_cfg {
+  uint64_t tp_handle;      /* 0 = let the library pick the transport path */
+  uint64_t peer_tp_handle;
+  uint64_t tag;
+} urma_import_jetty_ex_cfg_t;
+typedef urma_import_jetty_ex_cfg_t urma_import_jfr_ex_cfg_t;
+typedef urma_import_jetty_ex_cfg_t urma_bind_jetty_ex_cfg_t;
+typedef union urma_token_id_flag {
+  struct {
+    uint32_t multi_seg : 1; /* the id may cover several segments */
+    uint32_t reserved : 31;
+  } bs;
+  uint32_t value;
+} urma_token_id_flag_t;
+
+/* transport paths and addressing */
+#define URMA_IP_ADDR_BYTES 16
+#define URMA_MAC_BYTES 6
+typedef struct urma_net_addr {
+  uint32_t sin_family; /* AF_INET or AF_INET6 */
+  uint8_t addr[URMA_IP_ADDR_BYTES]; /* IPv4 in the first 4 bytes */
+  uint16_t vlan;
+  uint8_t mac[URMA_MAC_BYTES];
+  uint32_t prefix_len;
+} urma_net_addr_t;
+typedef struct urma_net_addr_info {
+  urma_net_addr_t netaddr;
+  uint32_t index;
+} urma_net_addr_info_t;
+typedef struct urma_get_tp_cfg {
+  uint32_t flag;
+  urma_transport_mode_t trans_mode;
+  urma_eid_t local_eid;
+  urma_eid_t peer_eid;
+} urma_get_tp_cfg_t;
+typedef struct urma_tp_info {
+  uint64_t tp_handle;
+} urma_tp_info_t;
+typedef struct urma_tp_attr_value {
+  uint8_t retry_times_init;
+  uint8_t at;
+  uint8_t sip[URMA_IP_ADDR_BYTES];
+  uint8_t dip[URMA_IP_ADDR_BYTES];
+  uint8_t sma[URMA_MAC_BYTES];
+  uint8_t dma[URMA_MAC_BYTES];
+  uint16_t vlan_id;
+  uint8_t vlan_en;
+  uint8_t dscp;
+  uint8_t at_times;
+  uint8_t sl;
+  uint8_t ttl;
+  uint16_t ack_udp_srcport;
+  uint16_t data_udp_srcport;
+} urma_tp_attr_value_t;
+/* bits of tp_attr_bitmap, in the order of the fields above */
+enum { URMA_TP_ATTR_RETRY = 1u << 0, URMA_TP_ATTR_AT = 1u << 1, URMA_TP_ATTR_SIP = 1u << 2, URMA_TP_ATTR_DIP = 1u << 3,
+       URMA_TP_ATTR_SMA = 1u << 4, URMA_TP_ATTR_DMA = 1u << 5, URMA_TP_ATTR_VLAN = 1u << 6, URMA_TP_ATTR_DSCP = 1u << 7,
+       URMA_TP_ATTR_SL = 1u << 8, URMA_TP_ATTR_TTL = 1u << 9, URMA_TP_ATTR_UDP_PORTS = 1u << 10 };
+typedef struct urma_tp_cfg {
+  urma_transport_mode_t trans_mode;
+  urma_eid_t local_eid;
+  urma_eid_t peer_eid;
+} urma_tp_cfg_t;
+typedef struct urma_tp_attr {
+  uint32_t peer_tpn;
+  uint32_t state; /* 0 reset, 1 ready, 2 error */
+  uint32_t tx_psn, rx_psn;
+  uint32_t mtu;
+} urma_tp_attr_t;
+typedef uint32_t urma_tp_attr_mask_t; /* bit 0 peer_tpn, 1 state, 2 tx_psn, 3 rx_psn, 4 mtu */
 
 #ifdef __cplusplus
 }

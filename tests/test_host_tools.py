@@ -267,3 +267,10 @@ def test_urma_admin_topology_aggregation_and_path_statistics(tmp_path):
     assert len(rows) == 2 and all(r[1] == "1" and int(r[2]) > 0 and r[3] == "0" for r in rows), out   # both up, balanced
     rc, out = _run([BIN / "urma_admin", "stats", "shm0"], tmp_path)
     assert rc == 0 and "0 path(s)" in out, out
+
+
+@pytest.mark.parametrize("dev", ["shm0", "bond0"])
+def test_urma_extended_control_plane(dev, tmp_path):
+    """Two-phase creation, options, batch deletion, notifier-based import / bind, transport paths, addressing."""
+    rc, out = _run([BIN / "urma_ext_selftest", dev], tmp_path)
+    assert rc == 0 and f"urma_ext_selftest: OK ({dev})" in out, out
