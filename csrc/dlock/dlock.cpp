@@ -42,7 +42,7 @@ namespace {
 
 constexpr uint32_t kMagic = 0x444c4f43;  // "DLOC"
 enum CtlOp : uint32_t { C_INIT = 1, C_REINIT, C_DEINIT, C_HEARTBEAT, C_GET_LOCK, C_RELEASE_LOCK, C_OBJ_CREATE,
-                        C_OBJ_GET, C_OBJ_DESTROY, C_UPDATE_LOCK };
+                        C_OBJ_GET, C_OBJ_DESTROY, C_UPDATE_LOCK, C_REINIT_DONE, C_OBJ_RELEASE };
 struct CtlMsg {
   uint32_t magic, op;
   int32_t client_id, status;
@@ -256,6 +256,7 @@ struct SrvClient {
   urma_target_jetty_t* ep = nullptr;
   uint64_t last_seen;
   bool alive = true;
+  bool reinit_done = false;
 };
 struct Server {
   dlock_server_cfg_t cfg;
@@ -295,6 +296,17 @@ void srv_handle_ctl(Server* s, SrvClient* c, const CtlMsg& in) {
   c->last_seen = ub::now_ns();
   switch (in.op) {
     case C_HEARTBEAT: ++s->mem.st.heartbeat; break;
+    case C_REINIT_DONE: {
+      // this client has pushed all its locks; when every connected client has said so, recovery is over at once
+      c->reinit_done = true;
+      bool all = true;
+      for (auto* o : s->clients) all &= !o->alive || o->reinit_done;
+      if (all && s->recovered_clients >= s->cfg.recovery_client_num) s->recovering = false;
+      break;
+    }
+    case C_OBJ_RELEASE:
+      if (in.id < 0 || in.id >= (int32_t)s->obj_used.size() || !s->obj_used[in.id]) out.status = DLOCK_LOCK_NOT_FOUND;
+      break;   // the object stays until it is destroyed; the client only drops its handle
     case C_GET_LOCK: {
       const std::string name(in.name, strnlen(in.name, DLOCK_NAME_LEN));
       auto it = s->mem.by_name.find(name);
@@ -602,6 +614,9 @@ struct Client {
   uint32_t seq = 1;
   CmdMsg tx;
   CmdWire tx_wire, rx[8];
+  bool async_pending = false;   // a lock_request_async is outstanding
+  dlock_lock_req_t async_req{};
+  uint64_t async_deadline = 0;
   uint64_t result;
   std::map<int32_t, HeldLock> locks;  // lock id -> description and state (the recovery cache)
   dlock_debug_stats_t st{};
@@ -609,6 +624,8 @@ struct Client {
 std::mutex g_cli_mu;
 std::map<int, Client*> g_clients;
 int g_next_client = 1;
+
+const char* g_default_dev_name();
 
 Client* cli(int handle) {
   std::lock_guard<std::mutex> l(g_cli_mu);
@@ -679,19 +696,22 @@ int connect_server(Client* c, const char* ip, uint16_t port, bool reinit) {
   return DLOCK_SUCCESS;
 }
 
-// one request/response exchange on the data channel
-int data_call(Client* c, int32_t lock_id, uint32_t op, uint32_t expire_ms) {
+// Data channel: a request is one sealed (or plain) command sent to the server; its reply is matched by sequence number.
+int data_send(Client* c, int32_t lock_id, uint32_t op, uint32_t expire_ms) {
   c->tx = CmdMsg{kMagic, c->seq++, c->id, lock_id, op, expire_ms, 0, c->epoch};
   ++c->st.data_msgs;
   pack_cmd(&c->tx_wire, c->tx, &c->key);
   if (urma_simple_post(c->ep, c->srv, URMA_OPC_SEND, nullptr, 0, nullptr, reinterpret_cast<uint64_t>(&c->tx_wire),
                        sizeof(CmdWire), 0, 0, 0) != 0)
     return DLOCK_BAD_RESPONSE;
+  return DLOCK_SUCCESS;
+}
+// Polls for the reply of the last data_send until `deadline_ns`. DLOCK_ASYNC_AGAIN = nothing yet.
+int data_poll(Client* c, uint64_t deadline_ns) {
   int st[4];
   uint64_t uc[4], imm[4];
   uint32_t len[4], flag[4];
-  const uint64_t deadline = ub::now_ns() + 1500000000ull;
-  while (ub::now_ns() < deadline) {
+  do {
     const int n = urma_simple_poll(c->ep, 4, st, uc, len, imm, flag);
     for (int i = 0; i < n; ++i) {
       if (!(flag[i] & URMA_CR_FLAG_RECV)) {
@@ -708,8 +728,16 @@ int data_call(Client* c, int32_t lock_id, uint32_t op, uint32_t expire_ms) {
       }
     }
     if (n <= 0) sched_yield();
-  }
-  return DLOCK_BAD_RESPONSE;  // the server did not answer: it is gone or was restarted
+  } while (ub::now_ns() < deadline_ns);
+  return DLOCK_ASYNC_AGAIN;
+}
+// one request/response exchange on the data channel
+int data_call(Client* c, int32_t lock_id, uint32_t op, uint32_t expire_ms) {
+  if (c->async_pending) return DLOCK_EASYNC;  // the reply slot belongs to the outstanding asynchronous request
+  const int rc = data_send(c, lock_id, op, expire_ms);
+  if (rc != DLOCK_SUCCESS) return rc;
+  const int got = data_poll(c, ub::now_ns() + 1500000000ull);
+  return got == DLOCK_ASYNC_AGAIN ? DLOCK_BAD_RESPONSE : got;  // no answer: the server is gone or was restarted
 }
 
 }  // namespace
@@ -829,7 +857,7 @@ int dlock_get_server_debug_stats(int server_id, dlock_debug_stats_t* out) {
 int dlock_client_init(int* client_id, const char* ip, uint16_t port) {
   if (!client_id) return DLOCK_EINVAL;
   Client* c = new Client();
-  c->ctx = urma_simple_open("shm0");
+  c->ctx = urma_simple_open(g_default_dev_name());
   c->ep = c->ctx ? urma_simple_ep_create(c->ctx, 64, 0x646c, 0) : nullptr;
   if (!c->ep) {
     delete c;
@@ -1005,6 +1033,152 @@ int dlock_batch_unlock(int handle, uint32_t n, const int32_t* ids, int* results)
   return worst;
 }
 
+int dlock_batch_lock_extend(int handle, uint32_t n, const dlock_lock_req_t* reqs, int* results) {
+  if (n == 0 || n > DLOCK_MAX_BATCH || !reqs || !results) return DLOCK_EINVAL;
+  int worst = DLOCK_SUCCESS;
+  for (uint32_t i = 0; i < n; ++i) {
+    results[i] = dlock_lock_extend(handle, reqs[i].lock_id, reqs[i].expire_ms);
+    if (results[i] != DLOCK_SUCCESS) worst = results[i];
+  }
+  return worst;
+}
+int dlock_batch_release_lock(int handle, uint32_t n, const int32_t* ids) {
+  if (n == 0 || n > DLOCK_MAX_BATCH || !ids) return DLOCK_EINVAL;
+  int worst = DLOCK_SUCCESS;
+  for (uint32_t i = 0; i < n; ++i) {
+    const int rc = dlock_release_lock(handle, ids[i]);
+    if (rc != DLOCK_SUCCESS) worst = rc;
+  }
+  return worst;
+}
+
+// Asynchronous lock request: the command goes out, the caller does other work and collects the answer later. One
+// request may be outstanding per client (the reference's rule, dlock_client_api.h:341-389).
+int dlock_lock_request_async(int handle, const dlock_lock_req_t* req) {
+  Client* c = cli(handle);
+  if (!c) return DLOCK_CLIENT_NOT_INIT;
+  if (!req) return DLOCK_EINVAL;
+  std::lock_guard<std::mutex> l(c->mu);
+  if (c->async_pending) return DLOCK_EASYNC;
+  const int rc = data_send(c, req->lock_id, req->op, req->expire_ms);
+  if (rc != DLOCK_SUCCESS) return rc;
+  c->async_pending = true;
+  c->async_req = *req;
+  c->async_deadline = ub::now_ns() + 5000000000ull;
+  return DLOCK_SUCCESS;
+}
+int dlock_lock_result_check(int handle, int* result) {
+  Client* c = cli(handle);
+  if (!c) return DLOCK_CLIENT_NOT_INIT;
+  if (!result) return DLOCK_EINVAL;
+  std::lock_guard<std::mutex> l(c->mu);
+  if (!c->async_pending) return DLOCK_NO_ASYNC;
+  const int rc = data_poll(c, ub::now_ns() + 100000ull);   // a short look, never a long wait
+  if (rc == DLOCK_ASYNC_AGAIN) {
+    if (ub::now_ns() < c->async_deadline) return DLOCK_ASYNC_AGAIN;
+    c->async_pending = false;
+    return DLOCK_TIMEOUT;
+  }
+  c->async_pending = false;
+  *result = rc;
+  const dlock_lock_req_t& r = c->async_req;
+  auto it = c->locks.find(r.lock_id);
+  if (rc == DLOCK_SUCCESS && it != c->locks.end()) {
+    if (r.op == DLOCK_LOCK_EXCLUSIVE || r.op == DLOCK_LOCK_SHARED) {
+      ++c->st.trylock_ok;
+      it->second.mode = r.op;
+      it->second.expiry_ns = ub::now_ns() + uint64_t(r.expire_ms ? r.expire_ms : 10000) * 1000000ull;
+    } else if (r.op == DLOCK_UNLOCK) {
+      ++c->st.unlock_ok;
+      it->second.mode = -1;
+    } else if (r.op == DLOCK_EXTEND) {
+      ++c->st.extend_ok;
+      it->second.expiry_ns = ub::now_ns() + uint64_t(r.expire_ms) * 1000000ull;
+    }
+  } else if (rc == DLOCK_EAGAIN) {
+    ++c->st.trylock_busy;
+  }
+  return rc;
+}
+
+int dlock_client_reinit_done(int handle) {
+  Client* c = cli(handle);
+  if (!c) return DLOCK_CLIENT_NOT_INIT;
+  std::lock_guard<std::mutex> l(c->mu);
+  CtlMsg m{};
+  m.op = C_REINIT_DONE;
+  return ctl_call(c, &m);
+}
+int dlock_clear_client_debug_stats(int handle) {
+  Client* c = cli(handle);
+  if (!c) return DLOCK_CLIENT_NOT_INIT;
+  std::lock_guard<std::mutex> l(c->mu);
+  c->st = dlock_debug_stats_t{};
+  return DLOCK_SUCCESS;
+}
+int dlock_clear_server_debug_stats(int server_id) {
+  std::lock_guard<std::mutex> l(g_srv_mu);
+  auto it = g_servers.find(server_id);
+  if (it == g_servers.end()) return DLOCK_EINVAL;
+  std::lock_guard<std::mutex> l2(it->second->mu);
+  const uint64_t clients = it->second->mem.st.clients, objects = it->second->mem.st.objects;
+  it->second->mem.st = dlock_debug_stats_t{};
+  it->second->mem.st.clients = clients;     // gauges, not event counters
+  it->second->mem.st.objects = objects;
+  return DLOCK_SUCCESS;
+}
+
+// Library contexts (the reference's dclient_lib_init / dserver_lib_init): defaults for the instances created
+// afterwards, and a tear-down that leaves no instance behind.
+static std::mutex g_lib_mu;
+static int g_client_lib = 0, g_server_lib = 0;
+static char g_default_dev[64] = "shm0";
+}  // extern "C"
+namespace {
+const char* g_default_dev_name() { return g_default_dev; }
+}  // namespace
+extern "C" {
+int dlock_client_lib_init(const dlock_lib_cfg_t* cfg) {
+  std::lock_guard<std::mutex> l(g_lib_mu);
+  if (cfg) {
+    if (cfg->dev_name[0]) snprintf(g_default_dev, sizeof(g_default_dev), "%s", cfg->dev_name);
+    if (cfg->psk_hex[0] && dlock_set_psk(cfg->psk_hex, cfg->psk_identity) != DLOCK_SUCCESS) return DLOCK_EINVAL;
+  }
+  ++g_client_lib;
+  return DLOCK_SUCCESS;
+}
+void dlock_client_lib_deinit(void) {
+  std::vector<int> ids;
+  {
+    std::lock_guard<std::mutex> l(g_lib_mu);
+    if (g_client_lib > 0) --g_client_lib;
+    if (g_client_lib > 0) return;
+    std::lock_guard<std::mutex> l2(g_cli_mu);
+    for (auto& kv : g_clients) ids.push_back(kv.first);
+  }
+  for (int id : ids) dlock_client_deinit(id);
+}
+int dlock_server_lib_init(const dlock_lib_cfg_t* cfg) {
+  std::lock_guard<std::mutex> l(g_lib_mu);
+  if (cfg) {
+    if (cfg->dev_name[0]) snprintf(g_default_dev, sizeof(g_default_dev), "%s", cfg->dev_name);
+    if (cfg->psk_hex[0] && dlock_set_psk(cfg->psk_hex, cfg->psk_identity) != DLOCK_SUCCESS) return DLOCK_EINVAL;
+  }
+  ++g_server_lib;
+  return DLOCK_SUCCESS;
+}
+void dlock_server_lib_deinit(void) {
+  std::vector<int> ids;
+  {
+    std::lock_guard<std::mutex> l(g_lib_mu);
+    if (g_server_lib > 0) --g_server_lib;
+    if (g_server_lib > 0) return;
+    std::lock_guard<std::mutex> l2(g_srv_mu);
+    for (auto& kv : g_servers) ids.push_back(kv.first);
+  }
+  for (int id : ids) dlock_server_stop(id);
+}
+
 int dlock_update_all_locks(int handle) {
   Client* c = cli(handle);
   if (!c) return DLOCK_CLIENT_NOT_INIT;
@@ -1057,6 +1231,7 @@ int dlock_umo_atomic64_get(int h, const char* name, int32_t* id) {
   return name && id ? obj_ctl(h, C_OBJ_GET, name, 0, 0, id) : DLOCK_EINVAL;
 }
 int dlock_umo_atomic64_destroy(int h, int32_t id) { return obj_ctl(h, C_OBJ_DESTROY, nullptr, 0, id, nullptr); }
+int dlock_umo_atomic64_release(int h, int32_t id) { return obj_ctl(h, C_OBJ_RELEASE, nullptr, 0, id, nullptr); }
 
 static int obj_atomic(int handle, int opcode, int32_t id, uint64_t operand, uint64_t cmp, uint64_t* old) {
   Client* c = cli(handle);

@@ -26,6 +26,9 @@ typedef enum dlock_status {
   DLOCK_BAD_RESPONSE = 0x2001,    /* server unreachable or restarted: call dlock_client_reinit */
   DLOCK_NOT_READY = 0x2002,       /* server is still recovering lock state from its clients */
   DLOCK_SERVER_FULL = 0x2003,
+  DLOCK_EASYNC = 0x2004,          /* an asynchronous request is outstanding: collect it first */
+  DLOCK_NO_ASYNC = 0x2005,        /* dlock_lock_result_check without a request */
+  DLOCK_ASYNC_AGAIN = 0x2006,     /* the answer has not arrived yet: check again */
 } dlock_status_t;
 
 typedef enum dlock_type { DLOCK_ATOMIC = 0, DLOCK_RW = 1, DLOCK_FAIR = 2 } dlock_type_t;
@@ -84,11 +87,32 @@ DLOCK_EXPORT int dlock_lock_extend(int client_id, int32_t lock_id, uint32_t expi
 DLOCK_EXPORT int dlock_batch_trylock(int client_id, uint32_t n, const dlock_lock_req_t* reqs, int* results);
 DLOCK_EXPORT int dlock_batch_unlock(int client_id, uint32_t n, const int32_t* lock_ids, int* results);
 DLOCK_EXPORT int dlock_update_all_locks(int client_id); /* after reinit: push held locks to the new server */
+DLOCK_EXPORT int dlock_client_reinit_done(int client_id); /* after update_all_locks: this client is fully back */
+DLOCK_EXPORT int dlock_batch_lock_extend(int client_id, uint32_t n, const dlock_lock_req_t* reqs, int* results);
+DLOCK_EXPORT int dlock_batch_release_lock(int client_id, uint32_t n, const int32_t* lock_ids);
+/* One asynchronous lock / unlock / extend per client: send now, collect the status later with result_check
+ * (DLOCK_ASYNC_AGAIN until the answer is there, DLOCK_TIMEOUT after 5 s). */
+DLOCK_EXPORT int dlock_lock_request_async(int client_id, const dlock_lock_req_t* req);
+DLOCK_EXPORT int dlock_lock_result_check(int client_id, int* result);
+DLOCK_EXPORT int dlock_clear_client_debug_stats(int client_id);
+DLOCK_EXPORT int dlock_clear_server_debug_stats(int server_id);
+/* Library contexts: defaults (URMA device, pre-shared key) for instances created afterwards; the last deinit stops
+ * every instance that is still running. */
+typedef struct dlock_lib_cfg {
+  char dev_name[64];
+  char psk_hex[132];
+  char psk_identity[64];
+} dlock_lib_cfg_t;
+DLOCK_EXPORT int dlock_client_lib_init(const dlock_lib_cfg_t* cfg);
+DLOCK_EXPORT void dlock_client_lib_deinit(void);
+DLOCK_EXPORT int dlock_server_lib_init(const dlock_lib_cfg_t* cfg);
+DLOCK_EXPORT void dlock_server_lib_deinit(void);
 DLOCK_EXPORT int dlock_get_client_debug_stats(int client_id, dlock_debug_stats_t* out);
 /* 64-bit atomic objects (one-sided URMA atomics on the server's object segment) */
 DLOCK_EXPORT int dlock_umo_atomic64_create(int client_id, const char* name, uint64_t init, int32_t* obj_id);
 DLOCK_EXPORT int dlock_umo_atomic64_get(int client_id, const char* name, int32_t* obj_id);
 DLOCK_EXPORT int dlock_umo_atomic64_destroy(int client_id, int32_t obj_id);
+DLOCK_EXPORT int dlock_umo_atomic64_release(int client_id, int32_t obj_id); /* drop the handle, keep the object */
 DLOCK_EXPORT int dlock_umo_atomic64_faa(int client_id, int32_t obj_id, uint64_t add, uint64_t* old);
 DLOCK_EXPORT int dlock_umo_atomic64_cas(int client_id, int32_t obj_id, uint64_t cmp, uint64_t swap, uint64_t* old);
 DLOCK_EXPORT int dlock_umo_atomic64_get_snapshot(int client_id, int32_t obj_id, uint64_t* value);

@@ -120,3 +120,34 @@ def test_secured_service_locks_work_and_wrong_keys_are_refused(tmp_path):
         if srv is not None:
             srv.stop()
         dlock.set_psk("", "")
+
+
+def test_async_request_batches_and_stat_reset(service):
+    dlock, srv, a, b = service
+    ids = [a.get_lock(f"B{i}", dlock.ATOMIC) for i in range(3)]
+    # asynchronous lock: send, look, collect; a second request while one is outstanding is refused
+    a.request_async(ids[0], dlock.EXCLUSIVE, expire_ms=2000)
+    with pytest.raises(dlock.DlockError) as e:
+        a.request_async(ids[1])
+    assert e.value.code == dlock.EASYNC
+    deadline = time.monotonic() + 3
+    res = None
+    while res is None and time.monotonic() < deadline:
+        res = a.result()
+    assert res == dlock.SUCCESS
+    with pytest.raises(dlock.DlockError) as e:
+        a.result()
+    assert e.value.code == dlock.NO_ASYNC
+    lb = b.get_lock("B0", dlock.ATOMIC)
+    assert b.trylock(lb) is False                          # the asynchronous request really took the lock
+    assert a.trylock(ids[1]) and a.trylock(ids[2])
+    assert a.batch_extend(ids, 5000) == [0, 0, 0]
+    assert a.batch_unlock(ids) == [0, 0, 0]
+    assert b.trylock(lb) is True
+    b.unlock(lb)
+    assert a.batch_release(ids) == 0
+    assert srv.stats()["trylock_ok"] >= 3
+    srv.clear_stats()
+    a.clear_stats()
+    assert srv.stats()["trylock_ok"] == 0 and srv.stats()["clients"] == 2 and a.stats()["trylock_ok"] == 0
+    a.reinit_done()                                        # harmless outside a recovery

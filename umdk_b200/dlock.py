@@ -13,6 +13,7 @@ from typing import List, Optional, Sequence, Tuple
 from . import _native
 
 SUCCESS, EAGAIN, ALREADY_LOCKED, NOT_OWNER, TIMEOUT = 0, 0x1000, 0x1001, 0x1002, 0x1004
+CLIENT_NOT_INIT, EASYNC, NO_ASYNC, ASYNC_AGAIN = 0x2000, 0x2004, 0x2005, 0x2006
 BAD_RESPONSE, NOT_READY = 0x2001, 0x2002
 ATOMIC, RW, FAIR = 0, 1, 2
 EXCLUSIVE, SHARED = 0, 1
@@ -84,6 +85,9 @@ class Server:
         s = _Stats()
         _lib().dlock_get_server_debug_stats(self.id, ctypes.byref(s))
         return _stats_dict(s)
+
+    def clear_stats(self) -> None:
+        _lib().dlock_clear_server_debug_stats(self.id)
 
     def stop(self):
         if self.id >= 0:
@@ -163,6 +167,43 @@ class Client:
         rc = _lib().dlock_update_all_locks(self.id)
         if rc != SUCCESS:
             raise DlockError("dlock_update_all_locks", rc)
+
+    def reinit_done(self) -> None:
+        """After reinit + update_all_locks: tells the restarted server that this client is fully back."""
+        rc = _lib().dlock_client_reinit_done(self.id)
+        if rc != SUCCESS:
+            raise DlockError("dlock_client_reinit_done", rc)
+
+    def request_async(self, lock_id: int, op: int = EXCLUSIVE, expire_ms: int = 10000) -> None:
+        """Sends a lock / unlock / extend request without waiting; collect the outcome with ``result()``."""
+        r = _LockReq(lock_id, op, expire_ms)
+        rc = _lib().dlock_lock_request_async(self.id, ctypes.byref(r))
+        if rc != SUCCESS:
+            raise DlockError("dlock_lock_request_async", rc)
+
+    def result(self) -> Optional[int]:
+        """Status of the outstanding asynchronous request, or None while the answer has not arrived."""
+        res = ctypes.c_int(0)
+        rc = _lib().dlock_lock_result_check(self.id, ctypes.byref(res))
+        if rc == ASYNC_AGAIN:
+            return None
+        if rc in (NO_ASYNC, TIMEOUT, CLIENT_NOT_INIT):
+            raise DlockError("dlock_lock_result_check", rc)
+        return rc
+
+    def batch_extend(self, lock_ids: Sequence[int], expire_ms: int) -> List[int]:
+        n = len(lock_ids)
+        reqs = (_LockReq * n)(*[_LockReq(i, 3, expire_ms) for i in lock_ids])
+        res = (ctypes.c_int * n)()
+        _lib().dlock_batch_lock_extend(self.id, n, reqs, res)
+        return list(res)
+
+    def batch_release(self, lock_ids: Sequence[int]) -> int:
+        n = len(lock_ids)
+        return _lib().dlock_batch_release_lock(self.id, n, (ctypes.c_int32 * n)(*lock_ids))
+
+    def clear_stats(self) -> None:
+        _lib().dlock_clear_client_debug_stats(self.id)
 
     # ---- 64-bit atomic objects ----
     def atomic_create(self, name: str, init: int = 0) -> int:
