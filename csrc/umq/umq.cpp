@@ -12,11 +12,14 @@
 
 #include <stdlib.h>
 #include <string.h>
+#include <sys/eventfd.h>
 #include <sys/syscall.h>
 #include <unistd.h>
 
 #include <atomic>
+#include <algorithm>
 #include <deque>
+#include <map>
 #include <memory>
 #include <thread>
 #include <mutex>
@@ -26,6 +29,7 @@
 
 #include "ub_util.h"
 #include "urma_simple.h"
+#include "uvs_topo.h"
 
 namespace {
 
@@ -49,6 +53,8 @@ struct Pool {
   std::vector<char*> slabs;
   uint64_t total = 0, huge_allocs = 0, alloc_calls = 0, free_calls = 0, failures = 0;
   bool inited = false;
+  std::map<const char*, Block*> by_mem;   // data area -> descriptor (umq_data_to_head)
+  uint64_t generation = 0;
 };
 Pool g_pool;
 // Per-thread cache of free blocks. A thread that ends hands its cached blocks back to the global pool (a worker
@@ -84,10 +90,17 @@ ub::Logger g_log("UMQ");
 // umq_async_event_get, like the reference's UMQ_EVENT_QH_ERR (doc/en/urpc/UMQ Abnormal Event.md).
 std::mutex g_ev_mu;
 std::deque<umq_async_event_t> g_events;
+int g_ev_fd = -1;   // created on demand by umq_async_event_fd_get; readable while events are queued
 void push_event(umq_async_event_type_t type, uint64_t h, int detail) {
   std::lock_guard<std::mutex> l(g_ev_mu);
   if (g_events.size() >= 1024) g_events.pop_front();
   g_events.push_back(umq_async_event_t{type, h, detail});
+  if (g_ev_fd >= 0) {
+    const uint64_t one = 1;
+    if (write(g_ev_fd, &one, sizeof(one)) < 0) {
+      // counter saturated: the fd is readable anyway
+    }
+  }
 }
 std::atomic<umq_io_perf_cb_t> g_perf_cb{nullptr};
 std::atomic<void*> g_perf_cb_ctx{nullptr};
@@ -244,6 +257,7 @@ void pool_init(uint32_t block, uint64_t bytes) {
     Block* b = block_new(block, false);
     if (!b) break;
     g_pool.free_list.push_back(b);
+    g_pool.by_mem[b->mem] = b;
     ++g_pool.total;
   }
   g_pool.inited = true;
@@ -253,8 +267,12 @@ Block* block_get(uint32_t need) {
     if (need > UMQ_MAX_MSG_SIZE) return nullptr;
     Block* b = block_new(need, true);
     std::lock_guard<std::mutex> l(g_pool.mu);
-    if (b) ++g_pool.huge_allocs;
-    else ++g_pool.failures;
+    if (b) {
+      ++g_pool.huge_allocs;
+      g_pool.by_mem[b->mem] = b;
+    } else {
+      ++g_pool.failures;
+    }
     return b;
   }
   if (!t_cache.empty()) {
@@ -278,6 +296,10 @@ Block* block_get(uint32_t need) {
 }
 void block_put(Block* b) {
   if (b->huge) {
+    {
+      std::lock_guard<std::mutex> l(g_pool.mu);
+      g_pool.by_mem.erase(b->mem);
+    }
     free(b->mem);
     free(b);
     return;
@@ -783,6 +805,361 @@ int umq_stats_perf_get(umq_perf_entry_t* e) {
   }
   return UMQ_SUCCESS;
 }
+// ---------------------------------------------------------------------------------------------- buffer list helpers
+int umq_buf_split(umq_buf_t* head, umq_buf_t* node) {
+  if (!head || !node || head == node) return UMQ_ERR_EINVAL;
+  uint32_t before = 0;
+  umq_buf_t* prev = nullptr;
+  for (umq_buf_t* b = head; b; prev = b, b = b->qbuf_next) {
+    if (b == node) {
+      prev->qbuf_next = nullptr;
+      uint32_t after = 0;
+      for (umq_buf_t* x = node; x; x = x->qbuf_next) after += x->data_size;
+      head->total_data_size = before;
+      node->total_data_size = after;
+      return UMQ_SUCCESS;
+    }
+    before += b->data_size;
+  }
+  return UMQ_ERR_EINVAL;  // node is not on the list
+}
+// A list may hold several messages back to back; the first buffer of each carries the message's total_data_size.
+// Frees the buffers of the first message and returns the first buffer of the next one (NULL if there is none).
+umq_buf_t* umq_buf_break_and_free(umq_buf_t* qbuf) {
+  if (!qbuf) return nullptr;
+  uint32_t left = qbuf->total_data_size;
+  umq_buf_t* b = qbuf;
+  umq_buf_t* last = nullptr;
+  do {
+    left -= b->data_size < left ? b->data_size : left;
+    last = b;
+    b = b->qbuf_next;
+  } while (b && left > 0);
+  last->qbuf_next = nullptr;
+  umq_buf_free(qbuf);
+  return b;
+}
+umq_buf_t* umq_data_to_head(void* data) {
+  if (!data) return nullptr;
+  // the data area of a pooled block starts right after its descriptor + headroom; walk the pool's arenas
+  std::lock_guard<std::mutex> l(g_pool.mu);
+  const char* p = static_cast<const char*>(data);
+  auto it = g_pool.by_mem.upper_bound(p);
+  if (it == g_pool.by_mem.begin()) return nullptr;
+  --it;
+  Block* b = it->second;
+  return (p >= b->mem && p < b->mem + b->cap) ? &b->meta : nullptr;
+}
+void umq_notify(uint64_t h) {
+  // sends are handed to the device at enqueue time, so there is nothing deferred to flush: make progress instead,
+  // which returns credits and completes finished sends
+  Queue* q = find(h);
+  if (!q) return;
+  std::lock_guard<std::mutex> l(q->mu);
+  progress(q);
+}
+
+// ---------------------------------------------------------------------------------------------- queries
+int umq_cfg_get(uint64_t h, umq_cfg_get_t* cfg) {
+  Queue* q = find(h);
+  if (!q || !cfg) return UMQ_ERR_EINVAL;
+  cfg->create_option = q->opt;
+  cfg->state = static_cast<umq_state_t>(q->state.load());
+  cfg->feature = g.cfg.feature;
+  cfg->trans_mode = g.cfg.trans_mode;
+  cfg->block_size = g_pool.block;
+  return UMQ_SUCCESS;
+}
+int umq_info_get(uint64_t h, umq_info_t* info) {
+  Queue* q = find(h);
+  if (!q || !info) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  memset(info, 0, sizeof(*info));
+  info->umqh = h;
+  snprintf(info->name, sizeof(info->name), "%s", q->opt.name);
+  info->state = static_cast<umq_state_t>(q->state.load());
+  info->bound = q->peer != nullptr;
+  info->rx_posted = q->rx_posted;
+  info->rx_ready = static_cast<uint32_t>(q->rx_ready.size());
+  info->tx_in_flight = static_cast<uint32_t>(q->in_flight.size()) - (q->rx_posted < q->in_flight.size() ? q->rx_posted : 0);
+  info->credits = q->credits;
+  info->io = q->io;
+  return UMQ_SUCCESS;
+}
+int umq_log_config_get(int* level) {
+  if (!level) return UMQ_ERR_EINVAL;
+  *level = g_log.level();
+  return UMQ_SUCCESS;
+}
+int umq_dev_info_get(const char* dev_name, umq_trans_mode_t mode, umq_dev_info_t* out) {
+  if (!dev_name || !out) return UMQ_ERR_EINVAL;
+  urma_device_t* d = urma_get_device_by_name(dev_name);
+  if (!d) return UMQ_ERR_EINVAL;
+  memset(out, 0, sizeof(*out));
+  snprintf(out->dev_name, sizeof(out->dev_name), "%s", d->name);
+  memcpy(out->eid, d->eid.raw, sizeof(out->eid));
+  out->trans_mode = mode;
+  urma_device_attr_t a;
+  if (urma_query_device(d, &a) == URMA_SUCCESS) {
+    out->max_msg_size = a.max_msg_size;
+    out->port_cnt = a.port_cnt;
+  }
+  return UMQ_SUCCESS;
+}
+umq_dev_info_t* umq_dev_info_list_get(umq_trans_mode_t mode, int* dev_num) {
+  if (!dev_num) return nullptr;
+  int n = 0;
+  urma_device_t** list = urma_get_device_list(&n);
+  if (!list || n <= 0) {
+    *dev_num = 0;
+    return nullptr;
+  }
+  umq_dev_info_t* out = static_cast<umq_dev_info_t*>(calloc(n, sizeof(umq_dev_info_t)));
+  int k = 0;
+  for (int i = 0; i < n && out; ++i)
+    if (umq_dev_info_get(list[i]->name, mode, &out[k]) == UMQ_SUCCESS) ++k;
+  urma_free_device_list(list);
+  *dev_num = k;
+  return out;
+}
+void umq_dev_info_list_free(umq_trans_mode_t, umq_dev_info_t* list) { free(list); }
+int umq_dev_add(const char* dev_name) {
+  // queues are created on the device named at umq_init; another device only has to exist to be usable by a later
+  // umq_init, so adding one is a presence check
+  return dev_name && urma_get_device_by_name(dev_name) ? UMQ_SUCCESS : UMQ_ERR_EINVAL;
+}
+int umq_get_route_list(const umq_route_key_t* key, umq_trans_mode_t, umq_route_list_t* out) {
+  if (!key || !out) return UMQ_ERR_EINVAL;
+  memset(out, 0, sizeof(*out));
+  urma_eid_t src, dst;
+  memcpy(src.raw, key->src_eid, sizeof(src.raw));
+  memcpy(dst.raw, key->dst_eid, sizeof(dst.raw));
+  uvs_path_set_t ps;
+  if (uvs_get_path_set(&src, &dst, UVS_RTP, &ps) != 0) {
+    if (uvs_discover_local_topology() <= 0 || uvs_get_path_set(&src, &dst, UVS_RTP, &ps) != 0) return UMQ_FAIL;
+  }
+  out->route_num = ps.path_count < UMQ_MAX_ROUTES ? ps.path_count : UMQ_MAX_ROUTES;
+  for (uint32_t i = 0; i < out->route_num; ++i) {
+    memcpy(out->routes[i].src_port_eid, ps.paths[i].src_eid.raw, 16);
+    memcpy(out->routes[i].dst_port_eid, ps.paths[i].dst_eid.raw, 16);
+  }
+  return UMQ_SUCCESS;
+}
+int umq_mempool_state_get(uint64_t, uint32_t mempool_id, umq_mempool_state_t* out) {
+  if (!out || mempool_id != 0) return UMQ_ERR_EINVAL;   // one pool: id 0
+  std::lock_guard<std::mutex> l(g_pool.mu);
+  out->block_size = g_pool.block;
+  out->blocks_total = g_pool.total;
+  out->blocks_free = g_pool.free_list.size();
+  out->registered = g_pool.total != 0;
+  out->generation = g_pool.generation;
+  return UMQ_SUCCESS;
+}
+int umq_mempool_state_refresh(uint64_t, uint32_t mempool_id) {
+  if (mempool_id != 0) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g_pool.mu);
+  ++g_pool.generation;   // users compare generations to learn that the pool was looked at again
+  return UMQ_SUCCESS;
+}
+int umq_user_ctl(uint64_t h, umq_user_ctl_in_t* in, umq_user_ctl_out_t* out) {
+  Queue* q = find(h);
+  if (!q || !in) return UMQ_ERR_EINVAL;
+  switch (in->opcode) {
+    case UMQ_USER_CTL_PROGRESS: {   // run the completion path now; out->value = messages ready to dequeue
+      std::lock_guard<std::mutex> l(q->mu);
+      progress(q);
+      if (out) out->value = q->rx_ready.size();
+      return UMQ_SUCCESS;
+    }
+    case UMQ_USER_CTL_RETURN_CREDITS: {   // push owed credits back to the peer without waiting for the batch size
+      std::lock_guard<std::mutex> l(q->mu);
+      if (out) out->value = q->to_return;
+      send_credit_return(q);
+      return UMQ_SUCCESS;
+    }
+    default: return UMQ_ERR_EINVAL;
+  }
+}
+int umq_interrupt_fd_list_get(uint64_t h, umq_io_direction_t, int* fds, uint32_t max) {
+  const int fd = umq_interrupt_fd_get(h);
+  if (fd < 0 || !fds || max == 0) return UMQ_FAIL;
+  fds[0] = fd;   // one completion channel serves both directions
+  return 1;
+}
+int umq_get_cq_event(uint64_t h, umq_io_direction_t) { return umq_wait_interrupt(h, 0); }
+int umq_async_event_fd_get(void) {
+  std::lock_guard<std::mutex> l(g_ev_mu);
+  if (g_ev_fd < 0) g_ev_fd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+  return g_ev_fd;
+}
+int umq_get_async_event(umq_async_event_t* ev) { return umq_async_event_get(ev); }
+void umq_ack_async_event(umq_async_event_t*) {}   // events are copied out and hold nothing
+
+// ---------------------------------------------------------------------------------------------- statistics helpers
+int umq_stats_io_reset(uint64_t h) {
+  Queue* q = find(h);
+  if (!q) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(q->mu);
+  q->io = umq_io_stats_t{};
+  return UMQ_SUCCESS;
+}
+int umq_stats_perf_reset(void) {
+  std::lock_guard<std::mutex> l(g.perf_mu);
+  for (auto& hst : g.perf) hst.reset();
+  return UMQ_SUCCESS;
+}
+int umq_io_stats_to_str(const umq_io_stats_t* s, char* buf, uint32_t len) {
+  if (!s || !buf || !len) return UMQ_ERR_EINVAL;
+  return snprintf(buf, len, "tx %llu msgs %llu B, rx %llu msgs %llu B, tx_errors %llu, rx_errors %llu, tx_eagain %llu",
+                  (unsigned long long)s->tx_msgs, (unsigned long long)s->tx_bytes, (unsigned long long)s->rx_msgs,
+                  (unsigned long long)s->rx_bytes, (unsigned long long)s->tx_errors, (unsigned long long)s->rx_errors,
+                  (unsigned long long)s->tx_eagain);
+}
+int umq_flow_control_stats_to_str(const umq_fc_stats_t* s, char* buf, uint32_t len) {
+  if (!s || !buf || !len) return UMQ_ERR_EINVAL;
+  return snprintf(buf, len, "window %llu, credits local %llu remote %llu, granted %llu, returned %llu, stalls %llu",
+                  (unsigned long long)s->window, (unsigned long long)s->credits_local,
+                  (unsigned long long)s->credits_remote, (unsigned long long)s->credits_granted,
+                  (unsigned long long)s->credits_returned, (unsigned long long)s->stalls);
+}
+int umq_qbuf_pool_stats_to_str(const umq_qbuf_stats_t* s, char* buf, uint32_t len) {
+  if (!s || !buf || !len) return UMQ_ERR_EINVAL;
+  return snprintf(buf, len, "block %llu B, blocks %llu total %llu free, huge %llu, alloc %llu, free %llu, failures %llu",
+                  (unsigned long long)s->block_size, (unsigned long long)s->blocks_total,
+                  (unsigned long long)s->blocks_free, (unsigned long long)s->huge_allocs,
+                  (unsigned long long)s->alloc_calls, (unsigned long long)s->free_calls,
+                  (unsigned long long)s->alloc_failures);
+}
+int umq_stats_perf_to_str(char* buf, uint32_t len) {
+  if (!buf || !len) return UMQ_ERR_EINVAL;
+  umq_perf_entry_t e[UMQ_PERF_RECORD_MAX];
+  umq_stats_perf_get(e);
+  int off = 0;
+  for (int i = 0; i < UMQ_PERF_RECORD_MAX && off < (int)len; ++i)
+    off += snprintf(buf + off, len - off, "%-10s count %llu avg %llu ns min %llu max %llu p99 %llu\n", kRecordNames[i],
+                    (unsigned long long)e[i].count, (unsigned long long)e[i].avg_ns, (unsigned long long)e[i].min_ns,
+                    (unsigned long long)e[i].max_ns, (unsigned long long)e[i].p99_ns);
+  return off;
+}
+int umq_stats_trace_start(const char* path) { return umq_trace_start(path, 0, 0); }
+int umq_stats_trace_stop(void) { return umq_trace_stop(); }
+// transport-level (URMA data-plane) latency sampling, passed through to the URMA perf sampler
+int umq_stats_tp_perf_start(void) { return urma_start_perf() == URMA_SUCCESS ? UMQ_SUCCESS : UMQ_FAIL; }
+int umq_stats_tp_perf_stop(void) { return urma_stop_perf() == URMA_SUCCESS ? UMQ_SUCCESS : UMQ_FAIL; }
+int umq_stats_tp_perf_info_get(char* buf, uint32_t* len) {
+  if (!buf || !len) return UMQ_ERR_EINVAL;
+  return urma_get_perf_info(nullptr, buf, len) == URMA_SUCCESS ? UMQ_SUCCESS : UMQ_FAIL;
+}
+
+// ---------------------------------------------------------------------------------------------- plug-in locks
+// Applications with their own threading runtime (coroutines, user-level threads) may supply the lock and
+// thread-key primitives; the library's own structures keep using std::mutex, and the registered primitives guard the
+// application-visible critical sections reached through umq_external_lock / unlock.
+static umq_external_mutex_ops_t g_ext_mutex{};
+static umq_external_rwlock_ops_t g_ext_rwlock{};
+static umq_external_thread_key_ops_t g_ext_key{};
+int umq_external_mutex_lock_ops_register(const umq_external_mutex_ops_t* ops) {
+  if (ops && (!ops->create || !ops->lock || !ops->unlock || !ops->destroy)) return UMQ_ERR_EINVAL;
+  g_ext_mutex = ops ? *ops : umq_external_mutex_ops_t{};
+  return UMQ_SUCCESS;
+}
+int umq_external_rwlock_ops_register(const umq_external_rwlock_ops_t* ops) {
+  if (ops && (!ops->create || !ops->rdlock || !ops->wrlock || !ops->unlock || !ops->destroy)) return UMQ_ERR_EINVAL;
+  g_ext_rwlock = ops ? *ops : umq_external_rwlock_ops_t{};
+  return UMQ_SUCCESS;
+}
+int umq_external_thread_key_ops_register(const umq_external_thread_key_ops_t* ops) {
+  if (ops && (!ops->create || !ops->set || !ops->get || !ops->destroy)) return UMQ_ERR_EINVAL;
+  g_ext_key = ops ? *ops : umq_external_thread_key_ops_t{};
+  return UMQ_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------------- transport pool
+// A transport pool groups the completion channels of several queues behind one eventfd, so that one thread can
+// sleep on many queues (the reference's time-division jetty pool serves the same purpose for many connections).
+struct TpPool {
+  int efd = -1;
+  std::vector<uint64_t> queues;
+  uint64_t wakeups = 0;
+};
+static std::mutex g_tpp_mu;
+static std::map<uint64_t, TpPool> g_tp_pools;
+static uint64_t g_tpp_next = 1;
+uint64_t umq_transport_pool_resource_create(void) {
+  std::lock_guard<std::mutex> l(g_tpp_mu);
+  TpPool p;
+  p.efd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+  if (p.efd < 0) return 0;
+  const uint64_t id = g_tpp_next++;
+  g_tp_pools[id] = p;
+  return id;
+}
+int umq_transport_pool_resource_modify(uint64_t pool, uint64_t umqh, int add) {
+  if (!find(umqh)) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g_tpp_mu);
+  auto it = g_tp_pools.find(pool);
+  if (it == g_tp_pools.end()) return UMQ_ERR_EINVAL;
+  auto& v = it->second.queues;
+  auto pos = std::find(v.begin(), v.end(), umqh);
+  if (add) {
+    if (pos != v.end()) return UMQ_ERR_EINVAL;
+    v.push_back(umqh);
+  } else {
+    if (pos == v.end()) return UMQ_ERR_EINVAL;
+    v.erase(pos);
+  }
+  return UMQ_SUCCESS;
+}
+int umq_transport_pool_resource_destroy(uint64_t pool) {
+  std::lock_guard<std::mutex> l(g_tpp_mu);
+  auto it = g_tp_pools.find(pool);
+  if (it == g_tp_pools.end()) return UMQ_ERR_EINVAL;
+  close(it->second.efd);
+  g_tp_pools.erase(it);
+  return UMQ_SUCCESS;
+}
+int umq_transport_pool_eventfd_get(uint64_t pool) {
+  std::lock_guard<std::mutex> l(g_tpp_mu);
+  auto it = g_tp_pools.find(pool);
+  return it == g_tp_pools.end() ? -1 : it->second.efd;
+}
+// Polls the member queues once; returns how many have messages ready and signals the pool's eventfd if any has.
+int umq_stats_transport_pool_get(uint64_t pool, umq_transport_pool_stats_t* out) {
+  std::vector<uint64_t> qs;
+  int efd;
+  {
+    std::lock_guard<std::mutex> l(g_tpp_mu);
+    auto it = g_tp_pools.find(pool);
+    if (it == g_tp_pools.end() || !out) return UMQ_ERR_EINVAL;
+    qs = it->second.queues;
+    efd = it->second.efd;
+  }
+  uint32_t ready = 0;
+  for (uint64_t h : qs) {
+    Queue* q = find(h);
+    if (!q) continue;
+    std::lock_guard<std::mutex> l(q->mu);
+    progress(q);
+    if (!q->rx_ready.empty()) ++ready;
+  }
+  std::lock_guard<std::mutex> l(g_tpp_mu);
+  auto it = g_tp_pools.find(pool);
+  if (it == g_tp_pools.end()) return UMQ_ERR_EINVAL;
+  if (ready) {
+    const uint64_t one = 1;
+    if (write(efd, &one, sizeof(one)) > 0) ++it->second.wakeups;
+  }
+  out->queues = static_cast<uint32_t>(qs.size());
+  out->queues_ready = ready;
+  out->wakeups = it->second.wakeups;
+  return UMQ_SUCCESS;
+}
+int umq_transport_pool_stats_to_str(const umq_transport_pool_stats_t* s, char* buf, uint32_t len) {
+  if (!s || !buf || !len) return UMQ_ERR_EINVAL;
+  return snprintf(buf, len, "queues %u, ready %u, wakeups %llu", s->queues, s->queues_ready,
+                  (unsigned long long)s->wakeups);
+}
+
 int umq_log_config_set(int level, umq_log_cb_t cb) {
   if (level < 0 || level > 4) return UMQ_ERR_EINVAL;
   g_log.configure(level, cb);

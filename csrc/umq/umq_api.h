@@ -110,6 +110,103 @@ UMQ_EXPORT int umq_stats_qbuf_pool_get(umq_qbuf_stats_t* out);
 UMQ_EXPORT int umq_stats_perf_start(void);
 UMQ_EXPORT int umq_stats_perf_stop(void);
 UMQ_EXPORT int umq_stats_perf_get(umq_perf_entry_t* entries /* [UMQ_PERF_RECORD_MAX] */);
+/* ---- buffer lists ---- */
+/* Cuts the list at `node`: `head` keeps the buffers before it, `node` starts a list of its own (sizes recomputed). */
+UMQ_EXPORT int umq_buf_split(umq_buf_t* head, umq_buf_t* node);
+/* A list may hold several messages back to back: frees the first one, returns the first buffer of the next. */
+UMQ_EXPORT umq_buf_t* umq_buf_break_and_free(umq_buf_t* qbuf);
+/* The buffer whose data area contains `data` (NULL if it is not a buffer of this library). */
+UMQ_EXPORT umq_buf_t* umq_data_to_head(void* data);
+/* Runs the completion path of the queue (returns credits, completes sends). */
+UMQ_EXPORT void umq_notify(uint64_t umqh);
+
+/* ---- queries ---- */
+typedef struct umq_cfg_get {
+  umq_create_option_t create_option;
+  umq_state_t state;
+  uint32_t feature;
+  umq_trans_mode_t trans_mode;
+  uint32_t block_size;
+} umq_cfg_get_t;
+UMQ_EXPORT int umq_cfg_get(uint64_t umqh, umq_cfg_get_t* cfg);
+typedef struct umq_dev_info {
+  char dev_name[64];
+  uint8_t eid[16];
+  umq_trans_mode_t trans_mode;
+  uint64_t max_msg_size;
+  uint32_t port_cnt;
+} umq_dev_info_t;
+UMQ_EXPORT int umq_dev_add(const char* dev_name);
+UMQ_EXPORT int umq_dev_info_get(const char* dev_name, umq_trans_mode_t mode, umq_dev_info_t* out);
+UMQ_EXPORT umq_dev_info_t* umq_dev_info_list_get(umq_trans_mode_t mode, int* dev_num);
+UMQ_EXPORT void umq_dev_info_list_free(umq_trans_mode_t mode, umq_dev_info_t* list);
+#define UMQ_MAX_ROUTES 32
+typedef struct umq_route_key {
+  uint8_t src_eid[16], dst_eid[16];
+} umq_route_key_t;
+typedef struct umq_route_list {
+  uint32_t route_num;
+  struct {
+    uint8_t src_port_eid[16], dst_port_eid[16];
+  } routes[UMQ_MAX_ROUTES];
+} umq_route_list_t;
+/* Port pairs that connect two devices according to the topology registry (uvs_topo.h). */
+UMQ_EXPORT int umq_get_route_list(const umq_route_key_t* key, umq_trans_mode_t mode, umq_route_list_t* out);
+typedef struct umq_mempool_state {
+  uint64_t block_size, blocks_total, blocks_free, generation;
+  int registered;
+} umq_mempool_state_t;
+UMQ_EXPORT int umq_mempool_state_get(uint64_t umqh, uint32_t mempool_id, umq_mempool_state_t* out);
+UMQ_EXPORT int umq_mempool_state_refresh(uint64_t umqh, uint32_t mempool_id);
+typedef enum umq_user_ctl_opcode { UMQ_USER_CTL_PROGRESS = 1, UMQ_USER_CTL_RETURN_CREDITS = 2 } umq_user_ctl_opcode_t;
+typedef struct umq_user_ctl_in {
+  uint32_t opcode;
+  uint64_t arg;
+} umq_user_ctl_in_t;
+typedef struct umq_user_ctl_out {
+  uint64_t value;
+} umq_user_ctl_out_t;
+UMQ_EXPORT int umq_user_ctl(uint64_t umqh, umq_user_ctl_in_t* in, umq_user_ctl_out_t* out);
+UMQ_EXPORT int umq_interrupt_fd_list_get(uint64_t umqh, umq_io_direction_t dir, int* fds, uint32_t max);
+UMQ_EXPORT int umq_get_cq_event(uint64_t umqh, umq_io_direction_t dir);
+
+/* ---- plug-in lock / thread-key primitives for applications with their own threading runtime ---- */
+typedef struct umq_external_mutex_ops {
+  void* (*create)(void);
+  int (*lock)(void*);
+  int (*unlock)(void*);
+  void (*destroy)(void*);
+} umq_external_mutex_ops_t;
+typedef struct umq_external_rwlock_ops {
+  void* (*create)(void);
+  int (*rdlock)(void*);
+  int (*wrlock)(void*);
+  int (*unlock)(void*);
+  void (*destroy)(void*);
+} umq_external_rwlock_ops_t;
+typedef struct umq_external_thread_key_ops {
+  int (*create)(uint32_t* key);
+  int (*set)(uint32_t key, void* value);
+  void* (*get)(uint32_t key);
+  void (*destroy)(uint32_t key);
+} umq_external_thread_key_ops_t;
+UMQ_EXPORT int umq_external_mutex_lock_ops_register(const umq_external_mutex_ops_t* ops);
+UMQ_EXPORT int umq_external_rwlock_ops_register(const umq_external_rwlock_ops_t* ops);
+UMQ_EXPORT int umq_external_thread_key_ops_register(const umq_external_thread_key_ops_t* ops);
+
+/* ---- transport pool: several queues behind one eventfd ---- */
+typedef struct umq_transport_pool_stats {
+  uint32_t queues, queues_ready;
+  uint64_t wakeups;
+} umq_transport_pool_stats_t;
+UMQ_EXPORT uint64_t umq_transport_pool_resource_create(void);
+UMQ_EXPORT int umq_transport_pool_resource_modify(uint64_t pool, uint64_t umqh, int add);
+UMQ_EXPORT int umq_transport_pool_resource_destroy(uint64_t pool);
+UMQ_EXPORT int umq_transport_pool_eventfd_get(uint64_t pool);
+/* Polls the member queues once, signals the eventfd if any has messages ready, and reports the counts. */
+UMQ_EXPORT int umq_stats_transport_pool_get(uint64_t pool, umq_transport_pool_stats_t* out);
+UMQ_EXPORT int umq_transport_pool_stats_to_str(const umq_transport_pool_stats_t* s, char* buf, uint32_t len);
+
 /* Logging: level 0 (errors) .. 4 (debug), default 1 or UMQ_LOG_LEVEL; cb NULL = stderr. */
 typedef void (*umq_log_cb_t)(int level, const char* msg);
 UMQ_EXPORT int umq_log_config_set(int level, umq_log_cb_t cb);
@@ -125,12 +222,38 @@ typedef struct umq_async_event {
   int detail;
 } umq_async_event_t;
 UMQ_EXPORT int umq_async_event_get(umq_async_event_t* ev);
+UMQ_EXPORT int umq_get_async_event(umq_async_event_t* ev);   /* same, under the reference's name */
+UMQ_EXPORT void umq_ack_async_event(umq_async_event_t* ev);
+UMQ_EXPORT int umq_async_event_fd_get(void);                 /* readable while events are queued */
+UMQ_EXPORT int umq_log_config_get(int* level);
 /* Trace: one text line `start_ns tid record duration_ns` per API call at the perf record points, collected in
  * per-thread rings (ring_entries each, 0 = 4096; a full ring drops and counts) and appended to `path` by a flusher
  * thread every flush_interval_ms (0 = 100). */
 UMQ_EXPORT int umq_trace_start(const char* path, uint32_t flush_interval_ms, uint32_t ring_entries);
 UMQ_EXPORT int umq_trace_stop(void);
 UMQ_EXPORT int umq_trace_stats(uint64_t* written, uint64_t* dropped);
+typedef struct umq_info {
+  uint64_t umqh;
+  char name[32];
+  umq_state_t state;
+  int bound;
+  uint32_t rx_posted, rx_ready, tx_in_flight;
+  int64_t credits;
+  umq_io_stats_t io;
+} umq_info_t;
+UMQ_EXPORT int umq_info_get(uint64_t umqh, umq_info_t* info);
+UMQ_EXPORT int umq_stats_io_reset(uint64_t umqh);
+UMQ_EXPORT int umq_stats_perf_reset(void);
+UMQ_EXPORT int umq_io_stats_to_str(const umq_io_stats_t* s, char* buf, uint32_t len);
+UMQ_EXPORT int umq_flow_control_stats_to_str(const umq_fc_stats_t* s, char* buf, uint32_t len);
+UMQ_EXPORT int umq_qbuf_pool_stats_to_str(const umq_qbuf_stats_t* s, char* buf, uint32_t len);
+UMQ_EXPORT int umq_stats_perf_to_str(char* buf, uint32_t len);
+UMQ_EXPORT int umq_stats_trace_start(const char* path);   /* umq_trace_start with default ring size and interval */
+UMQ_EXPORT int umq_stats_trace_stop(void);
+/* latency of the transport (URMA data-plane) calls underneath, from the URMA perf sampler */
+UMQ_EXPORT int umq_stats_tp_perf_start(void);
+UMQ_EXPORT int umq_stats_tp_perf_stop(void);
+UMQ_EXPORT int umq_stats_tp_perf_info_get(char* buf, uint32_t* len);
 UMQ_EXPORT int umq_info_to_str(uint64_t umqh, char* buf, uint32_t len);
 #ifdef __cplusplus
 }

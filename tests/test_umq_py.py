@@ -80,3 +80,106 @@ def test_perf_callback_log_sink_and_error_event(pair):
     finally:
         umq.io_perf_callback(None)
         umq.log_config(1, None)
+
+
+def test_buffer_lists_queries_and_transport_pool(pair):
+    """The helper calls around the queue: list surgery on buffers, configuration / device / pool queries, user
+    control, text forms of the statistics, and a transport pool that watches several queues through one eventfd."""
+    import ctypes
+    umq, a, b = pair
+    lib = umq._lib()
+    Buf = umq._Buf
+    lib.umq_buf_alloc.restype = ctypes.POINTER(Buf)
+    lib.umq_buf_break_and_free.restype = ctypes.POINTER(Buf)
+    lib.umq_data_to_head.restype = ctypes.POINTER(Buf)
+    lib.umq_data_to_head.argtypes = [ctypes.c_void_p]
+    # three buffers of 100 bytes in one list; cut after the first
+    head = lib.umq_buf_alloc(100, 3, ctypes.c_uint64(a.h))
+    assert head and head.contents.total_data_size == 300
+    second = ctypes.cast(head.contents.qbuf_next, ctypes.POINTER(Buf))   # a copy of the pointer, not a view
+    assert lib.umq_buf_split(head, second) == 0
+    assert head.contents.total_data_size == 100 and not head.contents.qbuf_next
+    assert second.contents.total_data_size == 200
+    assert lib.umq_buf_split(head, second) != 0                      # no longer on that list
+    # a pointer into a data area leads back to its buffer
+    inner = ctypes.c_void_p(second.contents.buf_data + 17)
+    back = lib.umq_data_to_head(inner)
+    assert ctypes.addressof(back.contents) == ctypes.addressof(second.contents)
+    assert not lib.umq_data_to_head(ctypes.c_void_p(ctypes.addressof(ctypes.c_int(0))))
+    # two messages back to back: the first is freed, the second returned
+    second.contents.total_data_size = 100                             # message 1 = one buffer, message 2 = the next
+    third = ctypes.cast(second.contents.qbuf_next, ctypes.POINTER(Buf))
+    third.contents.total_data_size = 100
+    rest = lib.umq_buf_break_and_free(second)
+    assert ctypes.addressof(rest.contents) == ctypes.addressof(third.contents)
+    lib.umq_buf_free(rest)
+    lib.umq_buf_free(head)
+
+    class CfgGet(ctypes.Structure):
+        _fields_ = [("create_option", umq._CreateOpt), ("state", ctypes.c_int), ("feature", ctypes.c_uint32),
+                    ("trans_mode", ctypes.c_int), ("block_size", ctypes.c_uint32)]
+    cfg = CfgGet()
+    assert lib.umq_cfg_get(ctypes.c_uint64(a.h), ctypes.byref(cfg)) == 0
+    assert cfg.create_option.name == b"a" and cfg.state == 1 and cfg.block_size >= 8192
+
+    class DevInfo(ctypes.Structure):
+        _fields_ = [("dev_name", ctypes.c_char * 64), ("eid", ctypes.c_uint8 * 16), ("trans_mode", ctypes.c_int),
+                    ("max_msg_size", ctypes.c_uint64), ("port_cnt", ctypes.c_uint32)]
+    n = ctypes.c_int(0)
+    lib.umq_dev_info_list_get.restype = ctypes.POINTER(DevInfo)
+    devs = lib.umq_dev_info_list_get(0, ctypes.byref(n))
+    names = {devs[i].dev_name for i in range(n.value)}
+    assert {b"shm0", b"shm1"} <= names
+    lib.umq_dev_info_list_free(0, devs)
+    assert lib.umq_dev_add(b"shm1") == 0 and lib.umq_dev_add(b"nope") != 0
+
+    class Pool(ctypes.Structure):
+        _fields_ = [(k, ctypes.c_uint64) for k in ("block_size", "blocks_total", "blocks_free", "generation")] + \
+                   [("registered", ctypes.c_int)]
+    st = Pool()
+    assert lib.umq_mempool_state_get(ctypes.c_uint64(a.h), 0, ctypes.byref(st)) == 0 and st.registered == 1
+    gen = st.generation
+    assert lib.umq_mempool_state_refresh(ctypes.c_uint64(a.h), 0) == 0
+    lib.umq_mempool_state_get(ctypes.c_uint64(a.h), 0, ctypes.byref(st))
+    assert st.generation == gen + 1 and lib.umq_mempool_state_get(ctypes.c_uint64(a.h), 7, ctypes.byref(st)) != 0
+
+    # transport pool over both queues: nothing ready, then a message for b
+    lib.umq_transport_pool_resource_create.restype = ctypes.c_uint64
+    pool = lib.umq_transport_pool_resource_create()
+    assert pool and lib.umq_transport_pool_eventfd_get(ctypes.c_uint64(pool)) >= 0
+    for q in (a, b):
+        assert lib.umq_transport_pool_resource_modify(ctypes.c_uint64(pool), ctypes.c_uint64(q.h), 1) == 0
+    assert lib.umq_transport_pool_resource_modify(ctypes.c_uint64(pool), ctypes.c_uint64(a.h), 1) != 0   # twice
+
+    class PoolStats(ctypes.Structure):
+        _fields_ = [("queues", ctypes.c_uint32), ("queues_ready", ctypes.c_uint32), ("wakeups", ctypes.c_uint64)]
+    ps = PoolStats()
+    assert lib.umq_stats_transport_pool_get(ctypes.c_uint64(pool), ctypes.byref(ps)) == 0
+    assert (ps.queues, ps.queues_ready) == (2, 0)
+    a.send(b"wake up")
+    import time
+    deadline = time.monotonic() + 2
+    while ps.queues_ready == 0 and time.monotonic() < deadline:
+        lib.umq_stats_transport_pool_get(ctypes.c_uint64(pool), ctypes.byref(ps))
+    assert ps.queues_ready == 1 and ps.wakeups >= 1
+    assert b.recv() == b"wake up"
+    txt = ctypes.create_string_buffer(256)
+    assert lib.umq_transport_pool_stats_to_str(ctypes.byref(ps), txt, 256) > 0 and b"queues 2" in txt.value
+    assert lib.umq_transport_pool_resource_destroy(ctypes.c_uint64(pool)) == 0
+
+    # user control, statistics as text, reset
+    class CtlIn(ctypes.Structure):
+        _fields_ = [("opcode", ctypes.c_uint32), ("arg", ctypes.c_uint64)]
+    class CtlOut(ctypes.Structure):
+        _fields_ = [("value", ctypes.c_uint64)]
+    out = CtlOut()
+    assert lib.umq_user_ctl(ctypes.c_uint64(b.h), ctypes.byref(CtlIn(1, 0)), ctypes.byref(out)) == 0
+    assert lib.umq_user_ctl(ctypes.c_uint64(b.h), ctypes.byref(CtlIn(99, 0)), ctypes.byref(out)) != 0
+    io = umq._IoStats()
+    lib.umq_stats_io_get(ctypes.c_uint64(a.h), ctypes.byref(io))
+    assert lib.umq_io_stats_to_str(ctypes.byref(io), txt, 256) > 0 and b"tx 1 msgs" in txt.value
+    assert lib.umq_stats_io_reset(ctypes.c_uint64(a.h)) == 0 and a.io_stats()["tx_msgs"] == 0
+    lvl = ctypes.c_int(-1)
+    assert lib.umq_log_config_get(ctypes.byref(lvl)) == 0 and 0 <= lvl.value <= 4
+    big = ctypes.create_string_buffer(2048)
+    assert lib.umq_stats_perf_to_str(big, 2048) > 0 and b"enqueue" in big.value
