@@ -18,6 +18,7 @@
 #include <string.h>
 #include <sys/socket.h>
 #include <sys/un.h>
+#include <sys/eventfd.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -91,6 +92,9 @@ struct Channel {
   std::deque<Ready> ready;
   uint32_t next_req = 1;
   uint32_t ka_outstanding = 0;
+  uint32_t timeout_ms = 0;          // 0 = the library default
+  std::string server_ip;
+  uint16_t server_port = 0;
 };
 struct Session {
   uint64_t umqh;
@@ -124,6 +128,9 @@ struct Global {
   std::string admin_path;
   std::thread admin_thr;
   std::atomic<bool> admin_stop{false};
+  std::unordered_map<std::string, uint64_t> func_names;   // registered names -> function ids
+  std::deque<urpc_async_event_t> events;
+  int event_fd = -1;
   ub::PskConfig psk;
   ub::PskConfig server_psk;   // the key in force when the server was started
   bool psk_set = false;   // urpc_set_psk was called: the environment is not consulted
@@ -132,6 +139,20 @@ Global g;
 ub::Logger g_log("URPC");
 std::atomic<urpc_perf_recorder_t> g_recorder{nullptr};
 std::atomic<void*> g_recorder_ctx{nullptr};
+thread_local bool g_lookup_call = false;   // set by urpc_func_id_get around its own call of the lookup function
+std::atomic<urpc_func_poll_cb_t> g_poll_cb{nullptr};
+std::atomic<urpc_ctrl_cb_t> g_ctrl_cb{nullptr};
+void push_event(urpc_async_event_type_t type, uint32_t chid, int detail) {
+  std::lock_guard<std::mutex> l(g.stat_mu);
+  if (g.events.size() >= 1024) g.events.pop_front();
+  g.events.push_back(urpc_async_event_t{type, chid, detail});
+  if (g.event_fd >= 0) {
+    const uint64_t one = 1;
+    if (write(g.event_fd, &one, sizeof(one)) < 0) {
+      // saturated counter: still readable
+    }
+  }
+}
 inline void record(urpc_perf_point_t pt, uint64_t ns) {
   if (urpc_perf_recorder_t cb = g_recorder.load(std::memory_order_relaxed)) cb(pt, ns, g_recorder_ctx.load());
 }
@@ -379,6 +400,7 @@ void accept_loop() {
       g.sessions.push_back(s);
     }
     s->conn = std::move(conn);
+    if (urpc_ctrl_cb_t cb = g_ctrl_cb.load()) cb(URPC_CTRL_ATTACH, s->id, hello.channel);
     if (!s->conn->write_full(&rsp, sizeof(rsp))) {
       // the client went away during the handshake; the session is reaped by server_poll when its socket closes
     }
@@ -418,12 +440,18 @@ void keepalive_loop() {
           ++g.stats.keepalive_lost;
         }
         g_log.log(ub::kLogWarn, "channel %u: peer missed %u keepalive probes, marked lost", ch->id, limit);
+        push_event(URPC_EVENT_CHANNEL_LOST, ch->id, (int)limit);
         if (g.ka_cb) g.ka_cb(ch->id, 0, g.ka_ctx);
       }
     }
   }
 }
 
+// caller holds g.mu
+Channel* get_channel_unlocked(uint32_t id) {
+  auto it = g.channels.find(id);
+  return it == g.channels.end() ? nullptr : it->second;
+}
 Channel* get_channel(uint32_t id) {
   std::lock_guard<std::mutex> l(g.mu);
   auto it = g.channels.find(id);
@@ -517,7 +545,7 @@ int urpc_server_start(const char* ip, uint16_t port) {
 }
 
 int urpc_func_register(uint64_t func_id, urpc_func_t fn, void* ctx) {
-  if (!fn || func_id >= URPC_FUNC_ID_KEEPALIVE) return URPC_ERR_EINVAL;
+  if (!fn || func_id >= URPC_FUNC_ID_LOOKUP) return URPC_ERR_EINVAL;   // the two top ids are reserved
   std::lock_guard<std::mutex> l(g.mu);
   if (g.funcs.count(func_id)) return URPC_ERR_EINVAL;
   g.funcs[func_id] = Func{fn, ctx};
@@ -556,6 +584,18 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
       Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, h.func_id, h.req_id, h.channel, 0, 0};
       if (h.func_id == URPC_FUNC_ID_KEEPALIVE) {
         send_msg(s->umqh, rh, nullptr, 0, nullptr, 0, &s->seal);
+        umq_buf_free(b);
+        continue;
+      }
+      if (h.func_id == URPC_FUNC_ID_LOOKUP) {   // name -> function id
+        uint64_t id = 0;
+        {
+          std::lock_guard<std::mutex> l(g.mu);
+          auto it = g.func_names.find(std::string(args, strnlen(args, alen)));
+          if (it != g.func_names.end()) id = it->second;
+          else rh.status = static_cast<int8_t>(URPC_ERR_FUNC_NOT_FOUND);
+        }
+        send_msg(s->umqh, rh, nullptr, 0, &id, sizeof(id), &s->seal);
         umq_buf_free(b);
         continue;
       }
@@ -670,6 +710,8 @@ int urpc_channel_server_attach(uint32_t chid, const char* ip, uint16_t port) {
   }
   ch->conn = std::move(conn);
   ch->tcp = fd;
+  ch->server_ip = ip && *ip ? ip : "127.0.0.1";
+  ch->server_port = port;
   ch->lost = false;
   ch->attached = true;
   return URPC_SUCCESS;
@@ -713,8 +755,9 @@ int urpc_channel_destroy(uint32_t chid) {
 int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_option_t* opt) {
   Channel* ch = get_channel(chid);
   if (!ch || !wr || wr->func_id >= URPC_FUNC_ID_KEEPALIVE) return URPC_ERR_EINVAL;
+  if (wr->func_id == URPC_FUNC_ID_LOOKUP && !g_lookup_call) return URPC_ERR_EINVAL;
   if (!ch->attached.load() || ch->lost.load()) return URPC_ERR_SESSION_CLOSE;
-  const uint32_t tmo = opt && opt->timeout_ms ? opt->timeout_ms : g.cfg.default_timeout_ms;
+  const uint32_t tmo = opt && opt->timeout_ms ? opt->timeout_ms : (ch->timeout_ms ? ch->timeout_ms : g.cfg.default_timeout_ms);
   uint32_t req_id;
   {
     std::lock_guard<std::mutex> l(ch->mu);
@@ -782,6 +825,7 @@ int urpc_func_poll(uint32_t chid, urpc_poll_msg_t* msgs, int max) {
     msgs[n].priv = r.buf;
     msgs[n].data = r.buf ? r.buf->buf_data + sizeof(urpc_req_head_t) : nullptr;
     msgs[n].len = r.buf ? r.buf->data_size - sizeof(urpc_req_head_t) : 0;
+    if (urpc_func_poll_cb_t cb = g_poll_cb.load()) cb(chid, &msgs[n]);
     ++n;
   }
   return n;
@@ -924,6 +968,203 @@ int urpc_stats_get(urpc_stats_t* out) {
   *out = g.stats;
   return URPC_SUCCESS;
 }
+int urpc_perf_recorder_unregister(void) {
+  g_recorder = nullptr;
+  g_recorder_ctx = nullptr;
+  return URPC_SUCCESS;
+}
+int urpc_log_config_get(int* level) {
+  if (!level) return URPC_ERR_EINVAL;
+  *level = g_log.level();
+  return URPC_SUCCESS;
+}
+uint32_t urpc_hdr_size_get(urpc_hdr_type_t type, uint16_t) {
+  // requests, acknowledgements and responses share one fixed 32-byte header here; a sealed message adds a tag
+  (void)type;
+  return sizeof(urpc_req_head_t);
+}
+int urpc_ssl_config_set(const urpc_ssl_config_t* cfg) {
+  if (!cfg) return URPC_ERR_EINVAL;
+  return urpc_set_psk(cfg->enable ? cfg->psk_hex : "", cfg->psk_identity);
+}
+int urpc_func_name_register(uint64_t func_id, const char* name) {
+  if (!name || !*name || func_id >= URPC_FUNC_ID_LOOKUP) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g.mu);
+  if (!g.funcs.count(func_id)) return URPC_ERR_FUNC_NOT_FOUND;
+  g.func_names[name] = func_id;
+  return URPC_SUCCESS;
+}
+uint64_t urpc_func_id_get(uint32_t chid, const char* name) {
+  if (!name || !*name) return 0;
+  {   // a function of this process
+    std::lock_guard<std::mutex> l(g.mu);
+    auto it = g.func_names.find(name);
+    if (it != g.func_names.end() && !get_channel_unlocked(chid)) return it->second;
+  }
+  uint64_t id = 0;
+  uint32_t rlen = 0;
+  urpc_sge_t sge{const_cast<char*>(name), static_cast<uint32_t>(strlen(name) + 1)};
+  urpc_call_wr_t wr{URPC_FUNC_ID_LOOKUP, &sge, 1, 0};
+  urpc_call_option_t opt{0, 1, &id, sizeof(id), &rlen};
+  g_lookup_call = true;
+  const int rc = urpc_func_call(chid, &wr, &opt);
+  g_lookup_call = false;
+  return rc == 0 && rlen == sizeof(id) ? id : 0;
+}
+// Runs a registered function in this process, without a channel: the same handler a remote caller would reach.
+int urpc_func_exec(uint64_t func_id, urpc_sge_t* args, uint32_t num_args, void* rsp, uint32_t* rsp_len) {
+  Func f{nullptr, nullptr};
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    auto it = g.funcs.find(func_id);
+    if (it != g.funcs.end()) f = it->second;
+  }
+  if (!f.fn) return URPC_ERR_FUNC_NOT_FOUND;
+  if (!rsp || !rsp_len || (!args && num_args)) return URPC_ERR_EINVAL;
+  std::vector<char> flat;
+  for (uint32_t i = 0; i < num_args; ++i)
+    flat.insert(flat.end(), static_cast<char*>(args[i].addr), static_cast<char*>(args[i].addr) + args[i].len);
+  const uint64_t t0 = ub::now_ns();
+  const int st = f.fn(flat.data(), static_cast<uint32_t>(flat.size()), rsp, rsp_len, f.ctx);
+  record(URPC_PERF_FUNC_EXEC, ub::now_ns() - t0);
+  return st;
+}
+// The same on a helper thread; `done(status, rsp, rsp_len, user_ctx)` runs there when the handler returns.
+int urpc_func_async_exec(uint64_t func_id, urpc_sge_t* args, uint32_t num_args, urpc_async_exec_cb_t done,
+                         void* user_ctx) {
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    if (!g.funcs.count(func_id)) return URPC_ERR_FUNC_NOT_FOUND;
+  }
+  if (!done || (!args && num_args)) return URPC_ERR_EINVAL;
+  std::vector<char> flat;
+  for (uint32_t i = 0; i < num_args; ++i)
+    flat.insert(flat.end(), static_cast<char*>(args[i].addr), static_cast<char*>(args[i].addr) + args[i].len);
+  std::thread([func_id, flat, done, user_ctx]() mutable {
+    std::vector<char> rsp(64 * 1024);
+    uint32_t rlen = static_cast<uint32_t>(rsp.size());
+    urpc_sge_t sge{flat.data(), static_cast<uint32_t>(flat.size())};
+    const int st = urpc_func_exec(func_id, &sge, 1, rsp.data(), &rlen);
+    done(st, rsp.data(), rlen, user_ctx);
+  }).detach();
+  return URPC_SUCCESS;
+}
+int urpc_func_poll_cb_register(urpc_func_poll_cb_t cb) {
+  if (!cb) return URPC_ERR_EINVAL;
+  g_poll_cb = cb;
+  return URPC_SUCCESS;
+}
+int urpc_func_poll_cb_unregister(void) {
+  g_poll_cb = nullptr;
+  return URPC_SUCCESS;
+}
+int urpc_func_poll_wait(uint32_t chid, urpc_poll_msg_t* msgs, int max, int timeout_ms) {
+  const uint64_t deadline = ub::now_ns() + uint64_t(timeout_ms < 0 ? 0 : timeout_ms) * 1000000ull;
+  for (;;) {
+    const int n = urpc_func_poll(chid, msgs, max);
+    if (n != 0 || ub::now_ns() >= deadline) return n;
+    usleep(50);
+  }
+}
+int urpc_ctrl_msg_cb_register(urpc_ctrl_cb_t cb) {
+  g_ctrl_cb = cb;
+  return URPC_SUCCESS;
+}
+int urpc_async_event_get(urpc_async_event_t* events, int num) {
+  if (!events || num <= 0) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g.stat_mu);
+  int n = 0;
+  while (n < num && !g.events.empty()) {
+    events[n++] = g.events.front();
+    g.events.pop_front();
+  }
+  if (g.events.empty() && g.event_fd >= 0) {
+    uint64_t drained;
+    if (read(g.event_fd, &drained, sizeof(drained)) < 0) {
+      // nothing pending
+    }
+  }
+  return n;
+}
+int urpc_async_event_fd_get(void) {
+  std::lock_guard<std::mutex> l(g.stat_mu);
+  if (g.event_fd < 0) g.event_fd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+  return g.event_fd;
+}
+int urpc_channel_cfg_get(uint32_t chid, urpc_channel_cfg_t* cfg) {
+  Channel* ch = get_channel(chid);
+  if (!ch || !cfg) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(ch->mu);
+  cfg->timeout_ms = ch->timeout_ms ? ch->timeout_ms : g.cfg.default_timeout_ms;
+  cfg->attached = ch->attached.load();
+  cfg->lost = ch->lost.load();
+  cfg->sealed = ch->seal.on();
+  cfg->pending_calls = static_cast<uint32_t>(ch->pending.size());
+  snprintf(cfg->server_ip, sizeof(cfg->server_ip), "%s", ch->server_ip.c_str());
+  cfg->server_port = ch->server_port;
+  return URPC_SUCCESS;
+}
+int urpc_channel_cfg_set(uint32_t chid, const urpc_channel_cfg_t* cfg) {
+  Channel* ch = get_channel(chid);
+  if (!ch || !cfg) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(ch->mu);
+  ch->timeout_ms = cfg->timeout_ms;   // the only settable field; the rest of the structure reports state
+  return URPC_SUCCESS;
+}
+int urpc_channel_server_refresh(uint32_t chid) {
+  Channel* ch = get_channel(chid);
+  if (!ch || ch->server_port == 0) return URPC_ERR_EINVAL;
+  const std::string ip = ch->server_ip;
+  const uint16_t port = ch->server_port;
+  if (ch->attached.load()) urpc_channel_server_detach(chid);
+  const int rc = urpc_channel_server_attach(chid, ip.c_str(), port);
+  if (rc == URPC_SUCCESS) push_event(URPC_EVENT_CHANNEL_REFRESHED, chid, 0);
+  return rc;
+}
+// The queue of a channel is its UMQ handle: the queue calls below take the handle urpc_channel_queue_query returns.
+int urpc_channel_queue_query(uint32_t chid, uint64_t* qh, uint32_t max) {
+  Channel* ch = get_channel(chid);
+  if (!ch || !qh || max == 0) return URPC_ERR_EINVAL;
+  qh[0] = ch->umqh;
+  return 1;
+}
+int urpc_queue_status_query(uint64_t qh, urpc_queue_status_t* status) {
+  if (!status) return URPC_ERR_EINVAL;
+  const umq_state_t st = umq_state_get(qh);
+  *status = st == UMQ_STATE_READY ? URPC_QUEUE_READY : (st == UMQ_STATE_IDLE ? URPC_QUEUE_IDLE : URPC_QUEUE_ERROR);
+  return URPC_SUCCESS;
+}
+int urpc_queue_interrupt_fd_get(uint64_t qh) { return umq_interrupt_fd_get(qh); }
+static const char* const kQueueStatNames[] = {"tx_msgs", "tx_bytes", "rx_msgs", "rx_bytes"};
+static const char* const kQueueErrNames[] = {"tx_errors", "rx_errors", "tx_eagain"};
+int urpc_queue_stats_get(uint64_t qh, uint64_t* stats, int len) {
+  umq_io_stats_t io;
+  if (!stats || len < 4 || umq_stats_io_get(qh, &io) != UMQ_SUCCESS) return URPC_ERR_EINVAL;
+  stats[0] = io.tx_msgs;
+  stats[1] = io.tx_bytes;
+  stats[2] = io.rx_msgs;
+  stats[3] = io.rx_bytes;
+  return 4;
+}
+const char* urpc_queue_stats_name_get(int type) { return type >= 0 && type < 4 ? kQueueStatNames[type] : nullptr; }
+int urpc_queue_error_stats_get(uint64_t qh, uint64_t* stats, int len) {
+  umq_io_stats_t io;
+  if (!stats || len < 3 || umq_stats_io_get(qh, &io) != UMQ_SUCCESS) return URPC_ERR_EINVAL;
+  stats[0] = io.tx_errors;
+  stats[1] = io.rx_errors;
+  stats[2] = io.tx_eagain;
+  return 3;
+}
+const char* urpc_queue_error_stats_name_get(int type) { return type >= 0 && type < 3 ? kQueueErrNames[type] : nullptr; }
+int urpc_error_stats_get(uint64_t* stats, int len) {
+  if (!stats || len < 3) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g.stat_mu);
+  stats[0] = g.stats.errors;
+  stats[1] = g.stats.timeouts;
+  stats[2] = g.stats.keepalive_lost;
+  return 3;
+}
+
 int urpc_perf_recorder_register(urpc_perf_recorder_t cb, void* ctx) {
   g_recorder_ctx = ctx;
   g_recorder = cb;

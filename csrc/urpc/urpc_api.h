@@ -26,6 +26,7 @@ typedef enum urpc_poll_event { URPC_POLL_REQ = 1, URPC_POLL_RSP = 2, URPC_POLL_E
     urpc_poll_event_t;
 
 #define URPC_FUNC_ID_KEEPALIVE 0xFFFFFFFFFFFFull /* reserved 48-bit id */
+#define URPC_FUNC_ID_LOOKUP 0xFFFFFFFFFFFEull    /* reserved: function name -> id (urpc_func_id_get) */
 
 typedef struct urpc_config {
   urpc_role_t role;
@@ -116,6 +117,60 @@ URPC_EXPORT int urpc_perf_recorder_register(urpc_perf_recorder_t cb, void* ctx);
 /* Logging: level 0 (errors) .. 4 (debug), default 1 or URPC_LOG_LEVEL; cb NULL = stderr. */
 typedef void (*urpc_log_cb_t)(int level, const char* msg);
 URPC_EXPORT int urpc_log_config_set(int level, urpc_log_cb_t cb);
+URPC_EXPORT int urpc_perf_recorder_unregister(void);
+URPC_EXPORT int urpc_log_config_get(int* level);
+typedef enum urpc_hdr_type { URPC_HDR_REQ = 0, URPC_HDR_ACK = 1, URPC_HDR_RSP = 2 } urpc_hdr_type_t;
+URPC_EXPORT uint32_t urpc_hdr_size_get(urpc_hdr_type_t type, uint16_t flag);
+typedef struct urpc_ssl_config {
+  int enable;
+  char psk_hex[132];
+  char psk_identity[64];
+} urpc_ssl_config_t;
+URPC_EXPORT int urpc_ssl_config_set(const urpc_ssl_config_t* cfg); /* urpc_set_psk from a structure */
+/* Function names: the server gives a registered function a name, a client looks the id up over its channel. */
+URPC_EXPORT int urpc_func_name_register(uint64_t func_id, const char* name);
+URPC_EXPORT uint64_t urpc_func_id_get(uint32_t chid, const char* name); /* 0 = unknown */
+/* Local execution of a registered function (same handler a remote caller reaches), inline or on a helper thread. */
+URPC_EXPORT int urpc_func_exec(uint64_t func_id, urpc_sge_t* args, uint32_t num_args, void* rsp, uint32_t* rsp_len);
+typedef void (*urpc_async_exec_cb_t)(int status, const void* rsp, uint32_t rsp_len, void* user_ctx);
+URPC_EXPORT int urpc_func_async_exec(uint64_t func_id, urpc_sge_t* args, uint32_t num_args, urpc_async_exec_cb_t done,
+                                     void* user_ctx);
+typedef void (*urpc_func_poll_cb_t)(uint32_t chid, const urpc_poll_msg_t* msg);
+URPC_EXPORT int urpc_func_poll_cb_register(urpc_func_poll_cb_t cb); /* called for every message urpc_func_poll returns */
+URPC_EXPORT int urpc_func_poll_cb_unregister(void);
+URPC_EXPORT int urpc_func_poll_wait(uint32_t chid, urpc_poll_msg_t* msgs, int max, int timeout_ms);
+typedef enum urpc_ctrl_msg_type { URPC_CTRL_ATTACH = 1, URPC_CTRL_DETACH = 2 } urpc_ctrl_msg_type_t;
+typedef void (*urpc_ctrl_cb_t)(urpc_ctrl_msg_type_t type, uint32_t session, uint32_t client_channel);
+URPC_EXPORT int urpc_ctrl_msg_cb_register(urpc_ctrl_cb_t cb); /* server: a client attached / detached */
+typedef enum urpc_async_event_type { URPC_EVENT_CHANNEL_LOST = 1, URPC_EVENT_CHANNEL_REFRESHED = 2 }
+    urpc_async_event_type_t;
+typedef struct urpc_async_event {
+  urpc_async_event_type_t type;
+  uint32_t chid;
+  int detail;
+} urpc_async_event_t;
+URPC_EXPORT int urpc_async_event_get(urpc_async_event_t* events, int num);
+URPC_EXPORT int urpc_async_event_fd_get(void);
+typedef struct urpc_channel_cfg {
+  uint32_t timeout_ms; /* settable: request timeout of this channel (0 = library default) */
+  int attached, lost, sealed;
+  uint32_t pending_calls;
+  char server_ip[64];
+  uint16_t server_port;
+} urpc_channel_cfg_t;
+URPC_EXPORT int urpc_channel_cfg_get(uint32_t chid, urpc_channel_cfg_t* cfg);
+URPC_EXPORT int urpc_channel_cfg_set(uint32_t chid, const urpc_channel_cfg_t* cfg);
+URPC_EXPORT int urpc_channel_server_refresh(uint32_t chid); /* detach + attach to the same server: new queue pair */
+/* Queues: a channel's queue is a UMQ handle; these calls report on it. */
+typedef enum urpc_queue_status { URPC_QUEUE_IDLE = 0, URPC_QUEUE_READY = 1, URPC_QUEUE_ERROR = 2 } urpc_queue_status_t;
+URPC_EXPORT int urpc_channel_queue_query(uint32_t chid, uint64_t* qh, uint32_t max);
+URPC_EXPORT int urpc_queue_status_query(uint64_t qh, urpc_queue_status_t* status);
+URPC_EXPORT int urpc_queue_interrupt_fd_get(uint64_t qh);
+URPC_EXPORT int urpc_queue_stats_get(uint64_t qh, uint64_t* stats, int len);       /* 4 counters */
+URPC_EXPORT const char* urpc_queue_stats_name_get(int type);
+URPC_EXPORT int urpc_queue_error_stats_get(uint64_t qh, uint64_t* stats, int len); /* 3 counters */
+URPC_EXPORT const char* urpc_queue_error_stats_name_get(int type);
+URPC_EXPORT int urpc_error_stats_get(uint64_t* stats, int len);                    /* errors, timeouts, peers lost */
 /* Management socket: a unix-domain stream socket at `path` that answers one text command per connection
  * ("version", "stats", "perf", "channels", "sessions", "funcs") with a text report; `urpc_admin` is its client.
  * Also started by urpc_init when the environment names a path in URPC_ADMIN_SOCKET. */

@@ -89,3 +89,60 @@ def test_perf_recorder_sees_every_point(rpc):
     assert set(got) == set(urpc.PERF_POINTS)
     assert all(len(v) >= 5 for v in got.values())
     assert min(got["call_to_response"]) >= min(got["func_exec"])
+
+
+def test_names_local_exec_channel_config_and_queue_reports(rpc):
+    import ctypes
+    urpc, srv, ch = rpc
+    lib = urpc._lib()
+    # a name for function 1, looked up by the client over its channel
+    assert lib.urpc_func_name_register(ctypes.c_uint64(1), b"reverse") == 0
+    assert lib.urpc_func_name_register(ctypes.c_uint64(77), b"nothing") != 0          # not registered
+    lib.urpc_func_id_get.restype = ctypes.c_uint64
+    assert lib.urpc_func_id_get(ch.id, b"reverse") == 1 and lib.urpc_func_id_get(ch.id, b"unknown") == 0
+    # the same handler run in this process
+    arg = ctypes.create_string_buffer(b"local", 5)
+    sge = urpc._Sge(ctypes.cast(arg, ctypes.c_void_p), 5)
+    rsp, rlen = ctypes.create_string_buffer(64), ctypes.c_uint32(64)
+    assert lib.urpc_func_exec(ctypes.c_uint64(1), ctypes.byref(sge), 1, rsp, ctypes.byref(rlen)) == 0
+    assert rsp.raw[:rlen.value] == b"lacol"
+    assert lib.urpc_func_exec(ctypes.c_uint64(99), ctypes.byref(sge), 1, rsp, ctypes.byref(rlen)) != 0
+
+    class ChCfg(ctypes.Structure):
+        _fields_ = [("timeout_ms", ctypes.c_uint32), ("attached", ctypes.c_int), ("lost", ctypes.c_int),
+                    ("sealed", ctypes.c_int), ("pending_calls", ctypes.c_uint32), ("server_ip", ctypes.c_char * 64),
+                    ("server_port", ctypes.c_uint16)]
+    cfg = ChCfg()
+    assert lib.urpc_channel_cfg_get(ch.id, ctypes.byref(cfg)) == 0
+    assert cfg.attached == 1 and cfg.lost == 0 and cfg.server_port == srv.port and cfg.timeout_ms == 2000
+    cfg.timeout_ms = 150
+    assert lib.urpc_channel_cfg_set(ch.id, ctypes.byref(cfg)) == 0
+    srv.paused = True
+    t0 = time.monotonic()
+    with pytest.raises(urpc.UrpcError):
+        ch.call(1, b"x")                       # the channel's own timeout applies
+    assert time.monotonic() - t0 < 1.0
+    srv.paused = False
+    # refresh = a new connection to the same server; calls keep working and an event reports it
+    assert lib.urpc_channel_server_refresh(ch.id) == 0
+    assert ch.call(1, b"again") == b"niaga"
+
+    class Event(ctypes.Structure):
+        _fields_ = [("type", ctypes.c_int), ("chid", ctypes.c_uint32), ("detail", ctypes.c_int)]
+    ev = (Event * 4)()
+    n = lib.urpc_async_event_get(ev, 4)
+    assert n >= 1 and any(ev[i].type == 2 and ev[i].chid == ch.id for i in range(n))
+    qh = (ctypes.c_uint64 * 1)()
+    assert lib.urpc_channel_queue_query(ch.id, qh, 1) == 1
+    status = ctypes.c_int(-1)
+    assert lib.urpc_queue_status_query(ctypes.c_uint64(qh[0]), ctypes.byref(status)) == 0 and status.value == 1
+    st = (ctypes.c_uint64 * 4)()
+    assert lib.urpc_queue_stats_get(ctypes.c_uint64(qh[0]), st, 4) == 4 and st[0] >= 1 and st[2] >= 1
+    lib.urpc_queue_stats_name_get.restype = ctypes.c_char_p
+    assert lib.urpc_queue_stats_name_get(0) == b"tx_msgs" and lib.urpc_queue_stats_name_get(9) is None
+    err = (ctypes.c_uint64 * 3)()
+    assert lib.urpc_error_stats_get(err, 3) == 3 and err[1] >= 1            # the timeout above
+    assert lib.urpc_hdr_size_get(0, 0) == 32
+    msgs = (urpc._PollMsg * 4)()
+    t0 = time.monotonic()
+    assert lib.urpc_func_poll_wait(ch.id, msgs, 4, 100) == 0 and time.monotonic() - t0 >= 0.09
