@@ -227,6 +227,10 @@ struct Queue {
   umq_io_stats_t io{};
   umq_fc_stats_t fcs{};
   bool base_api_tx = true;      // enqueue frees buffers on completion; post hands them back through poll
+  // one-sided reads issued with umq_remote_read: completion statuses by read id (ids are odd, see progress())
+  std::unordered_map<uint64_t, int> read_done;
+  uint64_t next_read = 1;
+  std::map<std::string, urma_target_seg_t*> imported;   // peer segments, by blob
 };
 
 Queue* find(uint64_t h) {
@@ -383,6 +387,8 @@ void progress(Queue* q) {
         q->rx_ready.push_back(&b->meta);
         ++q->io.rx_msgs;
         q->io.rx_bytes += len[i];
+      } else if (uc[i] & 1) {
+        q->read_done[uc[i]] = st[i];   // a one-sided read: buffer descriptors are aligned, so their low bit is 0
       } else if (uc[i] != 0) {
         Block* b = reinterpret_cast<Block*>(uc[i]);
         q->in_flight.erase(b);
@@ -520,6 +526,7 @@ int umq_destroy(uint64_t h) {
   }
   for (auto* b : q->rx_ready) block_put(reinterpret_cast<Block*>(b));
   for (auto* b : q->tx_done) block_put(reinterpret_cast<Block*>(b));
+  for (auto& kv : q->imported) urma_unimport_seg(kv.second);
   if (q->peer) urma_unimport_jetty(q->peer);
   urma_simple_ep_destroy(q->ep);
   // the endpoint is gone: nothing can complete into the blocks it still held (posted receives, unfinished sends)
@@ -857,6 +864,73 @@ void umq_notify(uint64_t h) {
   if (!q) return;
   std::lock_guard<std::mutex> l(q->mu);
   progress(q);
+}
+
+// ---------------------------------------------------------------------------------------------- memory by reference
+// A sender registers memory and ships its description inside a message; the receiver pulls the bytes with a
+// one-sided read over the queue's own endpoint. This is what carries large RPC arguments by reference (the DMA table
+// of the reference's request header and urpc_ref_read, src/urpc/framework/lib/datapath/dp.c:1333-1452).
+struct MemSeg {
+  urma_target_seg_t* seg;
+  uint8_t blob[URMA_SIMPLE_SEG_BLOB];
+};
+static std::mutex g_seg_mu;
+static std::map<uint64_t, MemSeg> g_segs;
+static uint64_t g_seg_next = 1;
+uint64_t umq_mem_seg_register(void* va, uint64_t len, uint32_t token, uint8_t* blob, uint32_t blob_cap) {
+  if (!g.inited || !va || !len || !blob || blob_cap < URMA_SIMPLE_SEG_BLOB) return 0;
+  MemSeg m;
+  m.seg = urma_simple_seg_register(g.ctx, va, len, URMA_ACCESS_READ, token, m.blob);
+  if (!m.seg) return 0;
+  memcpy(blob, m.blob, URMA_SIMPLE_SEG_BLOB);
+  std::lock_guard<std::mutex> l(g_seg_mu);
+  const uint64_t h = g_seg_next++;
+  g_segs[h] = m;
+  return h;
+}
+int umq_mem_seg_unregister(uint64_t seg_h) {
+  std::lock_guard<std::mutex> l(g_seg_mu);
+  auto it = g_segs.find(seg_h);
+  if (it == g_segs.end()) return UMQ_ERR_EINVAL;
+  urma_unregister_seg(it->second.seg);
+  g_segs.erase(it);
+  return UMQ_SUCCESS;
+}
+int umq_remote_read(uint64_t h, const uint8_t* seg_blob, uint32_t token, uint64_t remote_addr, void* local,
+                    uint32_t len, int timeout_ms) {
+  Queue* q = find(h);
+  if (!q || !seg_blob || !local || !len) return UMQ_ERR_EINVAL;
+  uint64_t id;
+  {
+    std::lock_guard<std::mutex> l(q->mu);
+    if (!q->peer) return UMQ_ERR_ESTATE;
+    const std::string key(reinterpret_cast<const char*>(seg_blob), URMA_SIMPLE_SEG_BLOB);
+    urma_target_seg_t*& rseg = q->imported[key];
+    if (!rseg) rseg = urma_simple_seg_import(g.ctx, seg_blob, token);
+    if (!rseg) {
+      q->imported.erase(key);
+      return UMQ_ERR_EINVAL;
+    }
+    id = (q->next_read++ << 1) | 1;
+    if (urma_simple_post(q->ep, q->peer, URMA_OPC_READ, rseg, remote_addr, nullptr, reinterpret_cast<uint64_t>(local),
+                         len, 0, id, 1) != 0)
+      return UMQ_FAIL;
+  }
+  const uint64_t deadline = ub::now_ns() + uint64_t(timeout_ms > 0 ? timeout_ms : 5000) * 1000000ull;
+  for (;;) {
+    {
+      std::lock_guard<std::mutex> l(q->mu);
+      progress(q);
+      auto it = q->read_done.find(id);
+      if (it != q->read_done.end()) {
+        const int st = it->second;
+        q->read_done.erase(it);
+        return st == 0 ? UMQ_SUCCESS : UMQ_FAIL;   // a refused read (bad token, out of range) completes in error
+      }
+    }
+    if (ub::now_ns() > deadline) return UMQ_ERR_EAGAIN;
+    sched_yield();
+  }
 }
 
 // ---------------------------------------------------------------------------------------------- queries

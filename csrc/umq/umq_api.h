@@ -120,6 +120,15 @@ UMQ_EXPORT umq_buf_t* umq_data_to_head(void* data);
 /* Runs the completion path of the queue (returns credits, completes sends). */
 UMQ_EXPORT void umq_notify(uint64_t umqh);
 
+/* ---- memory by reference ---- */
+/* Registers readable memory; `blob` (UMQ_SEG_BLOB_SIZE bytes) is the description a peer needs to read it. */
+#define UMQ_SEG_BLOB_SIZE 64
+UMQ_EXPORT uint64_t umq_mem_seg_register(void* va, uint64_t len, uint32_t token, uint8_t* blob, uint32_t blob_cap);
+UMQ_EXPORT int umq_mem_seg_unregister(uint64_t seg_h);
+/* One-sided read of the peer's registered memory over the queue's endpoint; blocks until done or timeout. */
+UMQ_EXPORT int umq_remote_read(uint64_t umqh, const uint8_t* seg_blob, uint32_t token, uint64_t remote_addr, void* local,
+                               uint32_t len, int timeout_ms);
+
 /* ---- queries ---- */
 typedef struct umq_cfg_get {
   umq_create_option_t create_option;

@@ -139,6 +139,30 @@ Global g;
 ub::Logger g_log("URPC");
 std::atomic<urpc_perf_recorder_t> g_recorder{nullptr};
 std::atomic<void*> g_recorder_ctx{nullptr};
+// Arguments by reference: entries appended to a request, each describing registered client memory.
+constexpr uint8_t kFlagRefs = 0x40;
+struct RefEntry {
+  uint64_t addr;
+  uint32_t len, token;
+  uint8_t blob[UMQ_SEG_BLOB_SIZE];
+};
+struct CurrentReq {
+  uint64_t umqh;
+  const RefEntry* refs;
+  uint32_t nrefs;
+};
+thread_local CurrentReq* t_current = nullptr;
+thread_local uint8_t t_call_flags = 0;   // extra header flags for the request urpc_func_call sends next
+struct MemSeg {
+  void* va;
+  uint64_t len;
+  uint32_t token;
+  uint64_t umq_h;   // 0 while remote access is disabled
+  uint8_t blob[UMQ_SEG_BLOB_SIZE];
+};
+std::mutex g_mem_mu;
+std::map<uint64_t, MemSeg> g_mem;
+uint64_t g_mem_next = 1;
 thread_local bool g_lookup_call = false;   // set by urpc_func_id_get around its own call of the lookup function
 std::atomic<urpc_func_poll_cb_t> g_poll_cb{nullptr};
 std::atomic<urpc_ctrl_cb_t> g_ctrl_cb{nullptr};
@@ -580,7 +604,19 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         continue;
       }
       const char* args = b->buf_data + sizeof(urpc_req_head_t);
-      const uint32_t alen = b->data_size - sizeof(urpc_req_head_t);
+      uint32_t alen = b->data_size - sizeof(urpc_req_head_t);
+      uint32_t nrefs = 0;
+      if (h.flags & kFlagRefs) {   // [inline args][reference table][count]: the handler sees the inline part only
+        if (alen >= 4) memcpy(&nrefs, args + alen - 4, 4);
+        if (nrefs == 0 || nrefs > URPC_MAX_REFS || alen < 4 + nrefs * sizeof(RefEntry)) {
+          std::lock_guard<std::mutex> l(g.stat_mu);
+          ++g.stats.errors;
+          umq_buf_free(b);
+          continue;
+        }
+        alen -= 4 + nrefs * sizeof(RefEntry);
+      }
+      CurrentReq cur{s->umqh, reinterpret_cast<const RefEntry*>(args + alen), nrefs};
       Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, h.func_id, h.req_id, h.channel, 0, 0};
       if (h.func_id == URPC_FUNC_ID_KEEPALIVE) {
         send_msg(s->umqh, rh, nullptr, 0, nullptr, 0, &s->seal);
@@ -613,7 +649,9 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
       if (f.fn) {
         uint32_t rlen = static_cast<uint32_t>(rsp.size());
         const uint64_t e0 = ub::now_ns();
+        t_current = &cur;   // urpc_ref_read(NULL, ...) inside the handler reads this request's references
         const int st = f.fn(args, alen, rsp.data(), &rlen, f.ctx);
+        t_current = nullptr;
         const uint64_t e1 = ub::now_ns();
         record(URPC_PERF_FUNC_EXEC, e1 - e0);
         rh.status = static_cast<int8_t>(st);
@@ -769,7 +807,7 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
     p.deadline = p.t0 + uint64_t(tmo) * 1000000ull;
     p.sync = opt && opt->sync;
     ch->pending[req_id] = std::move(p);
-    Head h{urpc_proto::kVersion, URPC_MSG_REQ, 1, wr->func_id, req_id, chid, 0, 0};
+    Head h{urpc_proto::kVersion, URPC_MSG_REQ, static_cast<uint8_t>(1 | t_call_flags), wr->func_id, req_id, chid, 0, 0};
     const int rc = send_msg(ch->umqh, h, wr->args, wr->num_args, nullptr, 0, &ch->seal);
     record(URPC_PERF_FUNC_CALL, ub::now_ns() - ch->pending[req_id].t0);
     if (rc != URPC_SUCCESS) {
@@ -968,6 +1006,125 @@ int urpc_stats_get(urpc_stats_t* out) {
   *out = g.stats;
   return URPC_SUCCESS;
 }
+uint64_t urpc_mem_seg_register(void* va, uint64_t len) {
+  if (!va || !len) return 0;
+  MemSeg m{va, len, 0, 0, {0}};
+  ub::random_bytes(&m.token, sizeof(m.token));
+  m.umq_h = umq_mem_seg_register(va, len, m.token, m.blob, sizeof(m.blob));
+  if (!m.umq_h) return 0;
+  std::lock_guard<std::mutex> l(g_mem_mu);
+  const uint64_t h = g_mem_next++;
+  g_mem[h] = m;
+  return h;
+}
+int urpc_mem_seg_unregister(uint64_t mem_h) {
+  std::lock_guard<std::mutex> l(g_mem_mu);
+  auto it = g_mem.find(mem_h);
+  if (it == g_mem.end()) return URPC_ERR_EINVAL;
+  if (it->second.umq_h) umq_mem_seg_unregister(it->second.umq_h);
+  g_mem.erase(it);
+  return URPC_SUCCESS;
+}
+int urpc_mem_seg_token_get(uint64_t mem_h, uint32_t* token) {
+  std::lock_guard<std::mutex> l(g_mem_mu);
+  auto it = g_mem.find(mem_h);
+  if (it == g_mem.end() || !token) return URPC_ERR_EINVAL;
+  *token = it->second.token;
+  return URPC_SUCCESS;
+}
+int urpc_mem_seg_remote_access_disable(uint64_t mem_h) {
+  std::lock_guard<std::mutex> l(g_mem_mu);
+  auto it = g_mem.find(mem_h);
+  if (it == g_mem.end()) return URPC_ERR_EINVAL;
+  if (it->second.umq_h) umq_mem_seg_unregister(it->second.umq_h);   // descriptions already sent stop working
+  it->second.umq_h = 0;
+  return URPC_SUCCESS;
+}
+int urpc_mem_seg_remote_access_enable(uint64_t mem_h) {
+  std::lock_guard<std::mutex> l(g_mem_mu);
+  auto it = g_mem.find(mem_h);
+  if (it == g_mem.end()) return URPC_ERR_EINVAL;
+  MemSeg& m = it->second;
+  if (m.umq_h) return URPC_SUCCESS;
+  ub::random_bytes(&m.token, sizeof(m.token));   // a fresh token: old descriptions stay dead
+  m.umq_h = umq_mem_seg_register(m.va, m.len, m.token, m.blob, sizeof(m.blob));
+  return m.umq_h ? URPC_SUCCESS : URPC_FAIL;
+}
+int urpc_func_call_ref(uint32_t chid, const urpc_call_wr_t* wr, const urpc_mem_ref_t* refs, uint32_t num_refs,
+                       const urpc_call_option_t* opt) {
+  if (!wr || !refs || num_refs == 0 || num_refs > URPC_MAX_REFS) return URPC_ERR_EINVAL;
+  // the table rides behind the inline arguments as one more scatter element
+  std::vector<uint8_t> table(num_refs * sizeof(RefEntry) + 4);
+  {
+    std::lock_guard<std::mutex> l(g_mem_mu);
+    for (uint32_t i = 0; i < num_refs; ++i) {
+      auto it = g_mem.find(refs[i].mem_h);
+      if (it == g_mem.end() || !it->second.umq_h) return URPC_ERR_EINVAL;
+      const MemSeg& m = it->second;
+      const uint64_t base = reinterpret_cast<uint64_t>(m.va);
+      if (refs[i].addr < base || refs[i].addr + refs[i].len > base + m.len) return URPC_ERR_EINVAL;
+      RefEntry e{refs[i].addr, refs[i].len, m.token, {0}};
+      memcpy(e.blob, m.blob, sizeof(e.blob));
+      memcpy(table.data() + i * sizeof(RefEntry), &e, sizeof(e));
+    }
+  }
+  memcpy(table.data() + num_refs * sizeof(RefEntry), &num_refs, 4);
+  std::vector<urpc_sge_t> sg(wr->args, wr->args + wr->num_args);
+  sg.push_back(urpc_sge_t{table.data(), static_cast<uint32_t>(table.size())});
+  urpc_call_wr_t w2 = *wr;
+  w2.args = sg.data();
+  w2.num_args = static_cast<uint32_t>(sg.size());
+  t_call_flags = kFlagRefs;
+  const int rc = urpc_func_call(chid, &w2, opt);
+  t_call_flags = 0;
+  return rc;
+}
+static const CurrentReq* req_of(const urpc_poll_msg_t* req, CurrentReq* tmp) {
+  if (!req) return t_current;
+  // a request taken with urpc_server_poll: the table sits behind the inline arguments in the same buffer
+  umq_buf_t* b = static_cast<umq_buf_t*>(req->priv);
+  if (!b || req->event != URPC_POLL_REQ) return nullptr;
+  Head h;
+  if (!urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) || !(h.flags & kFlagRefs)) return nullptr;
+  const char* args = b->buf_data + sizeof(urpc_req_head_t);
+  const uint32_t all = b->data_size - sizeof(urpc_req_head_t);
+  uint32_t n = 0;
+  memcpy(&n, args + all - 4, 4);
+  Session* s = nullptr;
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    const uint32_t sid = static_cast<uint32_t>(req->user_ctx >> 32);
+    if (sid < g.sessions.size()) s = g.sessions[sid];
+  }
+  if (!s || n == 0 || n > URPC_MAX_REFS) return nullptr;
+  *tmp = CurrentReq{s->umqh, reinterpret_cast<const RefEntry*>(args + all - 4 - n * sizeof(RefEntry)), n};
+  return tmp;
+}
+int urpc_ref_count(const urpc_poll_msg_t* req) {
+  CurrentReq tmp;
+  const CurrentReq* c = req_of(req, &tmp);
+  return c ? static_cast<int>(c->nrefs) : 0;
+}
+int urpc_ref_len(const urpc_poll_msg_t* req, uint32_t idx, uint32_t* len) {
+  CurrentReq tmp;
+  const CurrentReq* c = req_of(req, &tmp);
+  if (!c || idx >= c->nrefs || !len) return URPC_ERR_EINVAL;
+  RefEntry e;
+  memcpy(&e, &c->refs[idx], sizeof(e));
+  *len = e.len;
+  return URPC_SUCCESS;
+}
+int urpc_ref_read(const urpc_poll_msg_t* req, uint32_t idx, uint64_t offset, void* buf, uint32_t len) {
+  CurrentReq tmp;
+  const CurrentReq* c = req_of(req, &tmp);
+  if (!c || idx >= c->nrefs || !buf || !len) return URPC_ERR_EINVAL;
+  RefEntry e;
+  memcpy(&e, &c->refs[idx], sizeof(e));
+  if (offset + len > e.len) return URPC_ERR_EINVAL;
+  const int rc = umq_remote_read(c->umqh, e.blob, e.token, e.addr + offset, buf, len, 3000);
+  return rc == UMQ_SUCCESS ? URPC_SUCCESS : (rc == UMQ_ERR_EAGAIN ? URPC_ERR_TIMEOUT : URPC_FAIL);
+}
+
 int urpc_perf_recorder_unregister(void) {
   g_recorder = nullptr;
   g_recorder_ctx = nullptr;

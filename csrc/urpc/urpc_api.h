@@ -117,6 +117,25 @@ URPC_EXPORT int urpc_perf_recorder_register(urpc_perf_recorder_t cb, void* ctx);
 /* Logging: level 0 (errors) .. 4 (debug), default 1 or URPC_LOG_LEVEL; cb NULL = stderr. */
 typedef void (*urpc_log_cb_t)(int level, const char* msg);
 URPC_EXPORT int urpc_log_config_set(int level, urpc_log_cb_t cb);
+/* Arguments by reference: register memory once, pass (handle, address, length) with a call, and let the server pull
+ * the bytes it wants with one-sided reads instead of receiving them inline. Inside a registered handler pass
+ * req = NULL ("the request being handled"); for requests taken with urpc_server_poll pass the message. */
+#define URPC_MAX_REFS 16
+typedef struct urpc_mem_ref {
+  uint64_t mem_h;
+  uint64_t addr;
+  uint32_t len;
+} urpc_mem_ref_t;
+URPC_EXPORT uint64_t urpc_mem_seg_register(void* va, uint64_t len); /* 0 on failure */
+URPC_EXPORT int urpc_mem_seg_unregister(uint64_t mem_h);
+URPC_EXPORT int urpc_mem_seg_token_get(uint64_t mem_h, uint32_t* token);
+URPC_EXPORT int urpc_mem_seg_remote_access_disable(uint64_t mem_h); /* descriptions already sent stop working */
+URPC_EXPORT int urpc_mem_seg_remote_access_enable(uint64_t mem_h);
+URPC_EXPORT int urpc_func_call_ref(uint32_t chid, const urpc_call_wr_t* wr, const urpc_mem_ref_t* refs,
+                                   uint32_t num_refs, const urpc_call_option_t* opt);
+URPC_EXPORT int urpc_ref_count(const urpc_poll_msg_t* req);
+URPC_EXPORT int urpc_ref_len(const urpc_poll_msg_t* req, uint32_t idx, uint32_t* len);
+URPC_EXPORT int urpc_ref_read(const urpc_poll_msg_t* req, uint32_t idx, uint64_t offset, void* buf, uint32_t len);
 URPC_EXPORT int urpc_perf_recorder_unregister(void);
 URPC_EXPORT int urpc_log_config_get(int* level);
 typedef enum urpc_hdr_type { URPC_HDR_REQ = 0, URPC_HDR_ACK = 1, URPC_HDR_RSP = 2 } urpc_hdr_type_t;

@@ -146,3 +146,41 @@ def test_names_local_exec_channel_config_and_queue_reports(rpc):
     msgs = (urpc._PollMsg * 4)()
     t0 = time.monotonic()
     assert lib.urpc_func_poll_wait(ch.id, msgs, 4, 100) == 0 and time.monotonic() - t0 >= 0.09
+
+
+def test_arguments_by_reference(rpc):
+    """A megabyte of client memory travels as a 90-byte description; the handler pulls it with one-sided reads."""
+    import ctypes
+    import zlib
+    urpc, srv, ch = rpc
+    seen = {}
+
+    def checksum(args: bytes) -> bytes:
+        seen["inline"], seen["refs"] = args, urpc.ref_count()
+        try:
+            head = urpc.ref_read(0, 0, 16)
+            body = urpc.ref_read(0)
+        except urpc.UrpcError as e:
+            return b"ERR %d" % e.code
+        return head + str(zlib.crc32(body)).encode()
+    srv.register(5, checksum)
+    n = 1 << 20
+    mem = (ctypes.c_uint8 * n)(*([i * 7 & 0xff for i in range(4096)] * (n // 4096)))
+    h = urpc.register_memory(ctypes.addressof(mem), n)
+    out = ch.call_ref(5, b"crc", [(h, ctypes.addressof(mem), n)])
+    assert seen == {"inline": b"crc", "refs": 1}
+    assert out == bytes(mem[:16]) + str(zlib.crc32(bytes(mem))).encode()
+    # a window of the registered memory; a window outside it is refused before anything is sent
+    out = ch.call_ref(5, b"", [(h, ctypes.addressof(mem) + 4096, 8192)])
+    assert out == bytes(mem[4096:4112]) + str(zlib.crc32(bytes(mem[4096:4096 + 8192]))).encode()
+    with pytest.raises(urpc.UrpcError):
+        ch.call_ref(5, b"", [(h, ctypes.addressof(mem) + n - 8, 64)])
+    # remote access switched off: the call is refused; an ordinary call still shows no references
+    lib = urpc._lib()
+    assert lib.urpc_mem_seg_remote_access_disable(ctypes.c_uint64(h)) == 0
+    with pytest.raises(urpc.UrpcError):
+        ch.call_ref(5, b"", [(h, ctypes.addressof(mem), 64)])
+    assert lib.urpc_mem_seg_remote_access_enable(ctypes.c_uint64(h)) == 0
+    assert ch.call_ref(5, b"", [(h, ctypes.addressof(mem), 64)])[:16] == bytes(mem[:16])
+    assert ch.call(5, b"plain").startswith(b"ERR") and seen["refs"] == 0
+    urpc.unregister_memory(h)

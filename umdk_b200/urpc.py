@@ -115,6 +115,44 @@ def log_config(level: int, cb: Optional[Callable[[int, str], None]] = None) -> N
         raise UrpcError("urpc_log_config_set", rc)
 
 
+class _MemRef(ctypes.Structure):
+    _fields_ = [("mem_h", ctypes.c_uint64), ("addr", ctypes.c_uint64), ("len", ctypes.c_uint32)]
+
+
+def register_memory(addr: int, nbytes: int) -> int:
+    """Registers memory whose address can then be passed by reference with ``Channel.call_ref``."""
+    lib = _lib()
+    lib.urpc_mem_seg_register.restype = ctypes.c_uint64
+    h = lib.urpc_mem_seg_register(ctypes.c_void_p(addr), ctypes.c_uint64(nbytes))
+    if not h:
+        raise UrpcError("urpc_mem_seg_register", -1)
+    return int(h)
+
+
+def unregister_memory(mem_h: int) -> None:
+    _lib().urpc_mem_seg_unregister(ctypes.c_uint64(mem_h))
+
+
+def ref_count() -> int:
+    """Inside a handler: how many by-reference arguments the request being handled carries."""
+    return int(_lib().urpc_ref_count(None))
+
+
+def ref_read(idx: int, offset: int = 0, nbytes: Optional[int] = None) -> bytes:
+    """Inside a handler: pulls bytes of by-reference argument ``idx`` from the caller's memory."""
+    lib = _lib()
+    if nbytes is None:
+        n = ctypes.c_uint32(0)
+        if lib.urpc_ref_len(None, idx, ctypes.byref(n)) != 0:
+            raise UrpcError("urpc_ref_len", -22)
+        nbytes = n.value - offset
+    buf = ctypes.create_string_buffer(nbytes)
+    rc = lib.urpc_ref_read(None, idx, ctypes.c_uint64(offset), buf, nbytes)
+    if rc != 0:
+        raise UrpcError("urpc_ref_read", rc)
+    return buf.raw
+
+
 def admin_query(command: str) -> str:
     """The management report (`version`, `stats`, `perf`, `channels`, `sessions`, `functions`) as text."""
     buf = ctypes.create_string_buffer(16384)
@@ -213,6 +251,20 @@ class Channel:
         rc = _lib().urpc_func_call(self.id, ctypes.byref(wr), ctypes.byref(opt))
         if rc != 0:
             raise UrpcError("urpc_func_call", rc)
+        return rsp.raw[:n.value]
+
+    def call_ref(self, func_id: int, args: bytes, refs: List[Tuple[int, int, int]], timeout_ms: int = 0,
+                 max_rsp: int = 65536) -> bytes:
+        """Call with arguments by reference: ``refs`` = [(memory handle from register_memory, address, length)];
+        the server pulls what it needs with ``ref_read`` instead of receiving the bytes inline."""
+        wr, keep = self._wr(func_id, args, 0)
+        arr = (_MemRef * len(refs))(*[_MemRef(h, a, n) for h, a, n in refs])
+        rsp = ctypes.create_string_buffer(max_rsp)
+        n = ctypes.c_uint32(0)
+        opt = _CallOpt(timeout_ms, 1, ctypes.cast(rsp, ctypes.c_void_p), max_rsp, ctypes.pointer(n))
+        rc = _lib().urpc_func_call_ref(self.id, ctypes.byref(wr), arr, len(refs), ctypes.byref(opt))
+        if rc != 0:
+            raise UrpcError("urpc_func_call_ref", rc)
         return rsp.raw[:n.value]
 
     def call_async(self, func_id: int, args: bytes = b"", user_ctx: int = 0, timeout_ms: int = 0) -> int:
