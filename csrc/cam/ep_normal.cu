@@ -347,15 +347,16 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
   const bool is_receiver = (a.phase_mask & 2) && (!both || warp >= n_send_warps);
   uint8_t* self = a.peers.base[g.rank];
 
-  if (is_sender) {
+  if (a.phase_mask & 1) {
+    // Pass 0 (quantise everything once, keep what stays here) is done by ALL warps: nothing has arrived yet that the
+    // receiving warps could work on. From pass 1 on only the sending warps continue.
     const int sw = warp;                       // sender warps are always the first ones
-    const int nthr = n_send_warps * 32;
     const bool stage = g.quant && g.R > 1;
     uint8_t* stage_x = self + a.off.stage_x;
     float* stage_s = reinterpret_cast<float*>(self + a.off.stage_scale);
     // ---- notify: CTA 0, one warp per destination rank (looping) ----
     if (blockIdx.x == 0) {
-      for (int d = sw; d < g.R; d += n_send_warps) {
+      for (int d = sw; d < g.R; d += kEpWarps) {
         int* dst = reinterpret_cast<int*>(a.peers.base[d] + a.off.notify[h]) + (size_t)g.rank * nw;
         for (int i = lane; i < g.E_local; i += 32) dst[i] = a.num_per_expert[d * g.E_local + i];
         if (lane == 0) dst[g.E_local] = a.num_per_rank[d];
@@ -367,9 +368,13 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
       }
     }
     for (int pass = 0; pass < g.R; ++pass) {
+      if (pass > 0 && !is_sender) break;
+      const int nsw = pass == 0 ? kEpWarps : n_send_warps;   // warps working on this pass
+      const int nthr = nsw * 32;
+      const int bar_id = pass == 0 ? 3 : 1;
       const int d = (g.rank + pass) % g.R;
       uint8_t* peer = a.peers.base[d];
-      for (int t = blockIdx.x * n_send_warps + sw; t < a.T; t += gridDim.x * n_send_warps) {
+      for (int t = blockIdx.x * nsw + sw; t < a.T; t += gridDim.x * nsw) {
         const int slot = a.rank_slot[(size_t)t * g.R + d];
         if (slot >= g.cap) {
           if (lane == 0) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, d, slot);
@@ -403,7 +408,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
         }
       }
       // ---- end of the pass: the last CTA to finish it raises this rank's data flag on the destination ----
-      role_sync(1, nthr);
+      role_sync(bar_id, nthr);
       if (threadIdx.x == 0) {
         __threadfence_system();
         const uint32_t old = atomicAdd(&a.ctrl[16 + pass], 1u);
@@ -431,7 +436,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
         }
       }
       if (pass == 0 && stage) {
-        role_sync(1, nthr);
+        role_sync(bar_id, nthr);
         if (!s_ok_send) break;
       }
     }
