@@ -93,6 +93,7 @@ struct Channel {
   uint32_t next_req = 1;
   uint32_t ka_outstanding = 0;
   uint32_t timeout_ms = 0;          // 0 = the library default
+  bool user_queue = false;          // umqh came from urpc_queue_create (not destroyed with the channel)
   std::string server_ip;
   uint16_t server_port = 0;
 };
@@ -204,12 +205,13 @@ bool write_full(int fd, const void* buf, size_t n) {
   return true;
 }
 
-uint64_t make_queue(const char* name) {
+uint64_t make_queue(const char* name, const urpc_queue_cfg_t* cfg = nullptr) {
   umq_create_option_t o{};
   snprintf(o.name, sizeof(o.name), "%s", name);
-  o.rx_depth = 128;
-  o.tx_depth = 128;
-  o.rx_buf_size = 64 * 1024;
+  o.rx_depth = cfg && cfg->rx_depth ? cfg->rx_depth : 128;
+  o.tx_depth = cfg && cfg->tx_depth ? cfg->tx_depth : 128;
+  o.rx_buf_size = cfg && cfg->rx_buf_size ? cfg->rx_buf_size : 64 * 1024;
+  if (cfg && cfg->interrupt) o.mode = UMQ_MODE_INTERRUPT;
   o.token = 0x75727063;
   return umq_create(&o);
 }
@@ -785,7 +787,7 @@ int urpc_channel_destroy(uint32_t chid) {
   if (ch->tcp >= 0) close(ch->tcp);
   for (auto& r : ch->ready)
     if (r.buf) umq_buf_free(r.buf);
-  umq_destroy(ch->umqh);
+  if (!ch->user_queue) umq_destroy(ch->umqh);   // a queue from urpc_queue_create stays with its creator
   delete ch;
   return URPC_SUCCESS;
 }
@@ -1285,6 +1287,118 @@ int urpc_channel_queue_query(uint32_t chid, uint64_t* qh, uint32_t max) {
   qh[0] = ch->umqh;
   return 1;
 }
+// Explicit queues: created on their own, given to a channel before it attaches (the channel then uses it instead of
+// the queue it made for itself), taken back after a detach.
+static std::mutex g_q_mu;
+static std::map<uint64_t, urpc_queue_cfg_t> g_user_queues;   // queues made by urpc_queue_create -> their cfg
+uint64_t urpc_queue_create(const urpc_queue_cfg_t* cfg) {
+  if (!g.inited) return 0;
+  const uint64_t q = make_queue("urpc-user", cfg);
+  if (!q) return 0;
+  std::lock_guard<std::mutex> l(g_q_mu);
+  g_user_queues[q] = cfg ? *cfg : urpc_queue_cfg_t{128, 128, 64 * 1024, 0};
+  return q;
+}
+int urpc_queue_destroy(uint64_t qh) {
+  {
+    std::lock_guard<std::mutex> l(g_q_mu);
+    if (!g_user_queues.erase(qh)) return URPC_ERR_EINVAL;
+  }
+  {   // a queue that a channel still uses cannot go away
+    std::lock_guard<std::mutex> l(g.mu);
+    for (auto& kv : g.channels)
+      if (kv.second->umqh == qh) {
+        std::lock_guard<std::mutex> l2(g_q_mu);
+        g_user_queues[qh] = urpc_queue_cfg_t{};
+        return URPC_ERR_EAGAIN;
+      }
+  }
+  return umq_destroy(qh) == UMQ_SUCCESS ? URPC_SUCCESS : URPC_FAIL;
+}
+int urpc_queue_cfg_get(uint64_t qh, urpc_queue_cfg_t* cfg) {
+  umq_cfg_get_t c;
+  if (!cfg || umq_cfg_get(qh, &c) != UMQ_SUCCESS) return URPC_ERR_EINVAL;
+  cfg->rx_depth = c.create_option.rx_depth;
+  cfg->tx_depth = c.create_option.tx_depth;
+  cfg->rx_buf_size = c.create_option.rx_buf_size;
+  cfg->interrupt = c.create_option.mode == UMQ_MODE_INTERRUPT;
+  return URPC_SUCCESS;
+}
+int urpc_queue_cfg_set(uint64_t qh, const urpc_queue_cfg_t* cfg) {
+  // depths and buffer size are fixed when the queue is created: only a matching configuration is accepted
+  urpc_queue_cfg_t cur;
+  if (!cfg || urpc_queue_cfg_get(qh, &cur) != URPC_SUCCESS) return URPC_ERR_EINVAL;
+  return (cfg->rx_depth == cur.rx_depth && cfg->tx_depth == cur.tx_depth && cfg->rx_buf_size == cur.rx_buf_size)
+             ? URPC_SUCCESS : URPC_ERR_EINVAL;
+}
+int urpc_queue_modify(uint64_t qh, urpc_queue_status_t status) {
+  const umq_state_t st = status == URPC_QUEUE_READY ? UMQ_STATE_READY
+                         : (status == URPC_QUEUE_IDLE ? UMQ_STATE_IDLE : UMQ_STATE_ERR);
+  return umq_state_set(qh, st) == UMQ_SUCCESS ? URPC_SUCCESS : URPC_ERR_EINVAL;
+}
+int urpc_queue_rx_post(uint64_t qh, uint32_t) {
+  // receive buffers are posted and re-posted by the queue itself; this runs its completion path, which does that
+  umq_user_ctl_in_t in{UMQ_USER_CTL_PROGRESS, 0};
+  umq_user_ctl_out_t out{};
+  return umq_user_ctl(qh, &in, &out) == UMQ_SUCCESS ? URPC_SUCCESS : URPC_ERR_EINVAL;
+}
+int urpc_channel_queue_add(uint32_t chid, uint64_t qh) {
+  Channel* ch = get_channel(chid);
+  {
+    std::lock_guard<std::mutex> l(g_q_mu);
+    if (!g_user_queues.count(qh)) return URPC_ERR_EINVAL;
+  }
+  if (!ch || ch->attached.load()) return URPC_ERR_EINVAL;   // queues change hands only while detached
+  std::lock_guard<std::mutex> l(ch->mu);
+  if (ch->umqh == qh) return URPC_ERR_EINVAL;
+  if (!ch->user_queue) umq_destroy(ch->umqh);             // the queue the channel made for itself
+  ch->umqh = qh;
+  ch->user_queue = true;
+  return URPC_SUCCESS;
+}
+int urpc_channel_queue_rm(uint32_t chid, uint64_t qh) {
+  Channel* ch = get_channel(chid);
+  if (!ch || ch->attached.load()) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(ch->mu);
+  if (ch->umqh != qh || !ch->user_queue) return URPC_ERR_EINVAL;
+  const uint64_t own = make_queue("urpc-cli");
+  if (!own) return URPC_FAIL;
+  ch->umqh = own;
+  ch->user_queue = false;
+  return URPC_SUCCESS;
+}
+// Pairing a local queue with the server's happens during attach; these report / undo it for one channel.
+int urpc_channel_queue_pair(uint32_t chid, uint64_t local_qh) {
+  Channel* ch = get_channel(chid);
+  if (!ch || ch->umqh != local_qh) return URPC_ERR_EINVAL;
+  return ch->attached.load() ? URPC_SUCCESS : URPC_ERR_SESSION_CLOSE;
+}
+int urpc_channel_queue_unpair(uint32_t chid, uint64_t local_qh) {
+  Channel* ch = get_channel(chid);
+  if (!ch || ch->umqh != local_qh) return URPC_ERR_EINVAL;
+  return urpc_channel_server_detach(chid);
+}
+// Allocator plug-in for the copies the library makes of responses to synchronous calls.
+static urpc_allocator_t g_alloc{};
+int urpc_allocator_register(const urpc_allocator_t* a) {
+  if (!a || !a->alloc || !a->free) return URPC_ERR_EINVAL;
+  g_alloc = *a;
+  return URPC_SUCCESS;
+}
+int urpc_allocator_unregister(void) {
+  g_alloc = urpc_allocator_t{};
+  return URPC_SUCCESS;
+}
+void* urpc_rsp_copy(const void* data, uint32_t len) {
+  void* p = g_alloc.alloc ? g_alloc.alloc(len ? len : 1) : malloc(len ? len : 1);
+  if (p && len) memcpy(p, data, len);
+  return p;
+}
+void urpc_rsp_free(void* p) {
+  if (g_alloc.free) g_alloc.free(p);
+  else free(p);
+}
+
 int urpc_queue_status_query(uint64_t qh, urpc_queue_status_t* status) {
   if (!status) return URPC_ERR_EINVAL;
   const umq_state_t st = umq_state_get(qh);

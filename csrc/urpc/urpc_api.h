@@ -5,6 +5,7 @@
  * 24-bit client channel, total size, DMA descriptor count). */
 #ifndef UMDK_URPC_API_H
 #define UMDK_URPC_API_H
+#include <stddef.h>
 #include <stdint.h>
 #ifdef __cplusplus
 extern "C" {
@@ -182,6 +183,31 @@ URPC_EXPORT int urpc_channel_cfg_set(uint32_t chid, const urpc_channel_cfg_t* cf
 URPC_EXPORT int urpc_channel_server_refresh(uint32_t chid); /* detach + attach to the same server: new queue pair */
 /* Queues: a channel's queue is a UMQ handle; these calls report on it. */
 typedef enum urpc_queue_status { URPC_QUEUE_IDLE = 0, URPC_QUEUE_READY = 1, URPC_QUEUE_ERROR = 2 } urpc_queue_status_t;
+typedef struct urpc_queue_cfg {
+  uint32_t rx_depth, tx_depth, rx_buf_size; /* 0 = 128, 128, 64 KiB */
+  int interrupt;                            /* completion events instead of polling */
+} urpc_queue_cfg_t;
+/* Explicit queues: created on their own and given to a channel BEFORE it attaches (the channel then uses it instead
+ * of the one it made for itself); taken back after a detach. Depths and sizes are fixed at creation. */
+URPC_EXPORT uint64_t urpc_queue_create(const urpc_queue_cfg_t* cfg); /* 0 on failure */
+URPC_EXPORT int urpc_queue_destroy(uint64_t qh);
+URPC_EXPORT int urpc_queue_cfg_get(uint64_t qh, urpc_queue_cfg_t* cfg);
+URPC_EXPORT int urpc_queue_cfg_set(uint64_t qh, const urpc_queue_cfg_t* cfg);
+URPC_EXPORT int urpc_queue_modify(uint64_t qh, urpc_queue_status_t status);
+URPC_EXPORT int urpc_queue_rx_post(uint64_t qh, uint32_t num);
+URPC_EXPORT int urpc_channel_queue_add(uint32_t chid, uint64_t qh);
+URPC_EXPORT int urpc_channel_queue_rm(uint32_t chid, uint64_t qh);
+URPC_EXPORT int urpc_channel_queue_pair(uint32_t chid, uint64_t local_qh);
+URPC_EXPORT int urpc_channel_queue_unpair(uint32_t chid, uint64_t local_qh);
+typedef struct urpc_allocator {
+  void* (*alloc)(size_t);
+  void (*free)(void*);
+} urpc_allocator_t;
+/* Allocator for the copies handed out by urpc_rsp_copy (a response kept beyond urpc_msg_release). */
+URPC_EXPORT int urpc_allocator_register(const urpc_allocator_t* a);
+URPC_EXPORT int urpc_allocator_unregister(void);
+URPC_EXPORT void* urpc_rsp_copy(const void* data, uint32_t len);
+URPC_EXPORT void urpc_rsp_free(void* p);
 URPC_EXPORT int urpc_channel_queue_query(uint32_t chid, uint64_t* qh, uint32_t max);
 URPC_EXPORT int urpc_queue_status_query(uint64_t qh, urpc_queue_status_t* status);
 URPC_EXPORT int urpc_queue_interrupt_fd_get(uint64_t qh);

@@ -184,3 +184,45 @@ def test_arguments_by_reference(rpc):
     assert ch.call_ref(5, b"", [(h, ctypes.addressof(mem), 64)])[:16] == bytes(mem[:16])
     assert ch.call(5, b"plain").startswith(b"ERR") and seen["refs"] == 0
     urpc.unregister_memory(h)
+
+
+def test_explicit_queue_given_to_a_channel(rpc):
+    """A queue created on its own serves a channel that takes it before attaching; it survives the channel."""
+    import ctypes
+    urpc, srv, ch0 = rpc
+    lib = urpc._lib()
+
+    class QCfg(ctypes.Structure):
+        _fields_ = [("rx_depth", ctypes.c_uint32), ("tx_depth", ctypes.c_uint32), ("rx_buf_size", ctypes.c_uint32),
+                    ("interrupt", ctypes.c_int)]
+    lib.urpc_queue_create.restype = ctypes.c_uint64
+    qh = lib.urpc_queue_create(ctypes.byref(QCfg(32, 32, 16384, 0)))
+    assert qh
+    got = QCfg()
+    assert lib.urpc_queue_cfg_get(ctypes.c_uint64(qh), ctypes.byref(got)) == 0 and got.rx_depth == 32
+    assert lib.urpc_queue_cfg_set(ctypes.c_uint64(qh), ctypes.byref(QCfg(64, 32, 16384, 0))) != 0   # fixed at creation
+    chid = lib.urpc_channel_create()
+    assert chid >= 0 and lib.urpc_channel_queue_add(chid, ctypes.c_uint64(qh)) == 0
+    assert lib.urpc_channel_queue_add(ch0.id, ctypes.c_uint64(qh)) != 0                 # ch0 is attached
+    assert lib.urpc_channel_queue_pair(chid, ctypes.c_uint64(qh)) != 0                  # not attached yet
+    assert lib.urpc_channel_server_attach(chid, srv.ip.encode(), srv.port) == 0
+    assert lib.urpc_channel_queue_pair(chid, ctypes.c_uint64(qh)) == 0
+    q = (ctypes.c_uint64 * 1)()
+    assert lib.urpc_channel_queue_query(chid, q, 1) == 1 and q[0] == qh
+    # a call through the explicit queue
+    arg = ctypes.create_string_buffer(b"via my queue", 12)
+    sge = urpc._Sge(ctypes.cast(arg, ctypes.c_void_p), 12)
+    wr = urpc._CallWr(1, ctypes.pointer(sge), 1, 0)
+    rsp, n = ctypes.create_string_buffer(64), ctypes.c_uint32(0)
+    opt = urpc._CallOpt(0, 1, ctypes.cast(rsp, ctypes.c_void_p), 64, ctypes.pointer(n))
+    assert lib.urpc_func_call(chid, ctypes.byref(wr), ctypes.byref(opt)) == 0 and rsp.raw[:n.value] == b"eueuq ym aiv"
+    assert lib.urpc_queue_destroy(ctypes.c_uint64(qh)) != 0                             # still in use
+    assert lib.urpc_channel_queue_unpair(chid, ctypes.c_uint64(qh)) == 0
+    assert lib.urpc_channel_queue_rm(chid, ctypes.c_uint64(qh)) == 0
+    assert lib.urpc_channel_destroy(chid) == 0
+    assert lib.urpc_queue_destroy(ctypes.c_uint64(qh)) == 0
+    # allocator plug-in
+    lib.urpc_rsp_copy.restype = ctypes.c_void_p
+    p = lib.urpc_rsp_copy(b"keep me", 7)
+    assert ctypes.string_at(p, 7) == b"keep me"
+    lib.urpc_rsp_free(ctypes.c_void_p(p))
