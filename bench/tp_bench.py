@@ -131,7 +131,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--n-copy", type=int, default=0, help="copy CTAs of all-gather -> GEMM; 0 = chosen by group size")
+    ap.add_argument("--n-copy", type=int, default=0, help="copy CTAs of all-gather -> GEMM; 0 = the default (16)")
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--no-nvls", action="store_true")
     a = ap.parse_args()
