@@ -31,3 +31,11 @@ def test_tp_kernels_allreduce_and_urma_across_gpus():
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     rc, out = _torchrun("mp_tp_worker.py", n)
     assert rc == 0 and "MP_TP_OK" in out, out[-4000:]
+
+
+def test_rank_leaves_between_steps_and_survivors_stop_cleanly():
+    """Failure handling without a GPU fault: a rank departs between steps, the others learn of it on the host before
+    their next launch (NVLS off, plain peer loads)."""
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    rc, out = _torchrun("mp_leave_worker.py", n)
+    assert rc == 0 and out.count("MP_LEAVE_OK") == n, out[-4000:]
