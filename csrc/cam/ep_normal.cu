@@ -375,7 +375,13 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
       const int bar_id = pass == 0 ? 3 : 1;
       const int d = (g.rank + pass) % g.R;
       uint8_t* peer = a.peers.base[d];
-      for (int t = blockIdx.x * nsw + sw; t < a.T; t += gridDim.x * nsw) {
+      // From pass 1 on the last sending warp copies nothing: it only publishes the end of each pass (a system-scope
+      // fence that waits for the remote stores, a counter, the flag), so that the copying warps never sit behind
+      // that fence and go straight on to the next destination.
+      const bool have_signaller = pass > 0 && nsw >= 2;
+      const bool signaller = have_signaller && sw == nsw - 1;
+      const int ncopy = have_signaller ? nsw - 1 : nsw;
+      for (int t = blockIdx.x * ncopy + sw; t < a.T && !signaller; t += gridDim.x * ncopy) {
         const int slot = a.rank_slot[(size_t)t * g.R + d];
         if (slot >= g.cap) {
           if (lane == 0) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, d, slot);
@@ -410,7 +416,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
       }
       // ---- end of the pass: the last CTA to finish it raises this rank's data flag on the destination ----
       role_sync(bar_id, nthr);
-      if (threadIdx.x == 0) {
+      if (have_signaller ? (signaller && lane == 0) : threadIdx.x == 0) {
         __threadfence_system();
         const uint32_t old = atomicAdd(&a.ctrl[16 + pass], 1u);
         if (old == gridDim.x - 1) {
