@@ -242,7 +242,7 @@ __device__ __forceinline__ void role_sync(int id, int nthreads) {
 
 // One warp quantises token t (bf16 -> fp8 e4m3, fp32 scale per 1x128 block) and writes the row to up to two places.
 __device__ __forceinline__ void quant_row_to(const int4* xrow, int H, int lane, uint8_t* px0, float* ps0, uint8_t* px1,
-                                             float* ps1) {
+                                             float* ps1, uint8_t* px2 = nullptr, float* ps2 = nullptr) {
   const int nblk = H / 128;
   // each lane: 16 elements per step; 8 lanes share one 1x128 block; two groups of four blocks per iteration with all
   // four 16-byte loads of a lane issued first
@@ -284,9 +284,11 @@ __device__ __forceinline__ void quant_row_to(const int4* xrow, int H, int lane, 
         const int o = blk * 128 + (lane & 7) * 16;
         if (px0) st_na_v4(px0 + o, q);
         if (px1) st_na_v4(px1 + o, q);
+        if (px2) st_na_v4(px2 + o, q);
         if ((lane & 7) == 0) {
           if (ps0) ps0[blk] = scale;
           if (ps1) ps1[blk] = scale;
+          if (ps2) ps2[blk] = scale;
         }
       }
     }
@@ -368,8 +370,13 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
         }
       }
     }
+    // With staging, pass 0 also serves the right-hand neighbour (the quantised row is in registers anyway), so the
+    // first remote pass costs no extra read of the staging area and no extra end-of-pass round.
+    const bool merged = stage;
+    const int d_next = (g.rank + 1) % g.R;
     for (int pass = 0; pass < g.R; ++pass) {
       if (pass > 0 && !is_sender) break;
+      if (pass == 1 && merged) continue;
       const int nsw = pass == 0 ? kEpWarps : n_send_warps;   // warps working on this pass
       const int nthr = nsw * 32;
       const int bar_id = pass == 0 ? 3 : 1;
@@ -389,17 +396,31 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
         const bool goes = slot >= 0 && slot < g.cap;
         if (!goes && !(pass == 0 && stage)) continue;
         const size_t rec = (size_t)g.rank * g.cap + (goes ? slot : 0);
-        if (goes) {
-          // metadata: lanes 0..K-1 hold (local expert << 16 | bucket position) or -1, then the weights, then the token
-          int* meta = reinterpret_cast<int*>(peer + a.off.arr_meta[h]) + rec * g.meta_words;
+        // metadata: lanes 0..K-1 hold (local expert << 16 | bucket position) or -1, then the weights, then the token
+        auto put_meta = [&](int dd, size_t rr) {
+          int* meta = reinterpret_cast<int*>(a.peers.base[dd] + a.off.arr_meta[h]) + rr * g.meta_words;
           if (lane < g.K) {
             const long long ee = a.topk_idx[(size_t)t * g.K + lane];
             const int e = (ee >= 0 && ee < g.E) ? (int)ee : -1;
-            const bool mine = e >= 0 && (e / g.E_local) == d;
+            const bool mine = e >= 0 && (e / g.E_local) == dd;
             meta[lane] = mine ? (((e % g.E_local) << 16) | (a.send_idx[(size_t)t * g.K + lane] & 0xffff)) : -1;
             meta[g.K + lane] = __float_as_int(a.topk_w ? a.topk_w[(size_t)t * g.K + lane] : 1.f);
           }
           if (lane == 0) meta[2 * g.K] = t;
+        };
+        if (goes) put_meta(d, rec);
+        uint8_t* px2 = nullptr;
+        float* ps2 = nullptr;
+        if (pass == 0 && merged) {
+          const int slot1 = a.rank_slot[(size_t)t * g.R + d_next];
+          if (slot1 >= g.cap) {
+            if (lane == 0) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, d_next, slot1);
+          } else if (slot1 >= 0) {
+            const size_t rec1 = (size_t)g.rank * g.cap + slot1;
+            put_meta(d_next, rec1);
+            px2 = a.peers.base[d_next] + a.off.arr_x[h] + rec1 * g.row_bytes;
+            ps2 = reinterpret_cast<float*>(a.peers.base[d_next] + a.off.arr_scale[h]) + rec1 * g.nscale;
+          }
         }
         uint8_t* px = goes ? peer + a.off.arr_x[h] + rec * g.row_bytes : nullptr;
         float* ps = goes ? reinterpret_cast<float*>(peer + a.off.arr_scale[h]) + rec * g.nscale : nullptr;
@@ -408,7 +429,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
         } else if (pass == 0) {
           quant_row_to(reinterpret_cast<const int4*>(a.x + (size_t)t * g.H), g.H, lane,
                        stage ? stage_x + (size_t)t * g.H : nullptr, stage ? stage_s + (size_t)t * g.nscale : nullptr,
-                       px, ps);
+                       px, ps, px2, ps2);
         } else {
           warp_copy_row<true>(px, stage_x + (size_t)t * g.H, g.row_bytes, lane);
           for (int v = lane; v < g.nscale; v += 32) ps[v] = __ldcg(stage_s + (size_t)t * g.nscale + v);
@@ -423,6 +444,9 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
           a.ctrl[16 + pass] = 0;
           __threadfence_system();
           st_release_sys(reinterpret_cast<uint64_t*>(peer + a.off.data_flag[h]) + g.rank, tag);
+          if (pass == 0 && merged && d_next != g.rank) {
+            st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[d_next] + a.off.data_flag[h]) + g.rank, tag);
+          }
           if (pass == 0 && stage) {   // staging area complete: open the gate for this call
             __threadfence();
             atomicExch(&a.ctrl[10], epoch + 1);
