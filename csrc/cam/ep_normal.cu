@@ -344,7 +344,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
   const uint64_t tag = (uint64_t)epoch + 1;
   const int nw = ep_notify_words(g.E_local);
   const bool both = (a.phase_mask & 3) == 3;
-  // Half of the warps send, half expand: measured on 8 GPUs 396 us, against 414 us with a quarter sending.
+  // Half of the warps send, half expand. Measured on 8 GPUs: 343 us; with 6 of 16 warps sending 353 us; with 4 of 16
+  // (before the signalling warp existed) 414 us against 396 us.
   const int n_send_warps = both ? kEpWarps / 2 : kEpWarps;
   const bool is_sender = (a.phase_mask & 1) && (!both || warp < n_send_warps);
   const bool is_receiver = (a.phase_mask & 2) && (!both || warp >= n_send_warps);
