@@ -355,7 +355,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
     // Pass 0 (quantise everything once, keep what stays here) is done by ALL warps: nothing has arrived yet that the
     // receiving warps could work on. From pass 1 on only the sending warps continue.
     const int sw = warp;                       // sender warps are always the first ones
-    const bool stage = g.quant && g.R > 1;
+    const bool stage = g.quant && g.R > 2;    // two ranks: pass 0 reaches both destinations, nothing is read back
     uint8_t* stage_x = self + a.off.stage_x;
     float* stage_s = reinterpret_cast<float*>(self + a.off.stage_scale);
     // ---- notify: CTA 0, one warp per destination rank (looping) ----
@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
     }
     // With staging, pass 0 also serves the right-hand neighbour (the quantised row is in registers anyway), so the
     // first remote pass costs no extra read of the staging area and no extra end-of-pass round.
-    const bool merged = stage;
+    const bool merged = g.quant && g.R > 1;
     const int d_next = (g.rank + 1) % g.R;
     for (int pass = 0; pass < g.R; ++pass) {
       if (pass > 0 && !is_sender) break;
@@ -395,7 +395,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
           if (lane == 0) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, d, slot);
         }
         const bool goes = slot >= 0 && slot < g.cap;
-        if (!goes && !(pass == 0 && stage)) continue;
+        const int slot_next = (pass == 0 && merged) ? a.rank_slot[(size_t)t * g.R + d_next] : -1;
+        if (!goes && !(pass == 0 && (stage || slot_next >= 0))) continue;
         const size_t rec = (size_t)g.rank * g.cap + (goes ? slot : 0);
         // metadata: lanes 0..K-1 hold (local expert << 16 | bucket position) or -1, then the weights, then the token
         auto put_meta = [&](int dd, size_t rr) {
@@ -413,7 +414,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
         uint8_t* px2 = nullptr;
         float* ps2 = nullptr;
         if (pass == 0 && merged) {
-          const int slot1 = a.rank_slot[(size_t)t * g.R + d_next];
+          const int slot1 = slot_next;
           if (slot1 >= g.cap) {
             if (lane == 0) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_DISPATCH_DATA, d_next, slot1);
           } else if (slot1 >= 0) {
