@@ -92,6 +92,7 @@ int main(int argc, char** argv) {
   urma_simple_ep_blob(ea, mine.ep);
   urma_simple_ep_t* eb = nullptr;
   urma_context_t* ctx_b = nullptr;
+  urma_target_seg_t* seg_b_reg = nullptr;
   int tcp = -1;
   if (server >= 0 || client >= 0) {
     if (server >= 0) {
@@ -120,6 +121,7 @@ int main(int argc, char** argv) {
     ctx_b = urma_simple_open(dev.c_str());
     eb = urma_simple_ep_create(ctx_b, depth * 2, 1, 0);
     urma_target_seg_t* seg_b = urma_simple_seg_register(ctx_b, mem_b.data(), seg_bytes, 14, 1, peer.seg);
+    seg_b_reg = seg_b;
     if (!eb || !seg_b) return fail("second endpoint");
     urma_simple_ep_blob(eb, peer.ep);
   }
@@ -300,9 +302,21 @@ int main(int argc, char** argv) {
     }
     close(tcp);
   }
+  const bool data_ok = !(!two_sided && !atomic && opc == URMA_OPC_WRITE && eb && memcmp(mem_a.data(), mem_b.data(), size) != 0);
+  // tear down in the reverse order of the bring-up (imports, endpoints, segments, contexts)
+  for (auto* t : ex_t) urma_unimport_jetty(t);
+  urma_unimport_jetty(tj);
+  urma_unimport_seg(rseg);
+  for (auto* e : ex_a) urma_simple_ep_destroy(e);
+  for (auto* e : ex_b) urma_simple_ep_destroy(e);
+  urma_simple_ep_destroy(ea);
+  if (eb) urma_simple_ep_destroy(eb);
+  urma_unregister_seg(seg_a);
+  if (seg_b_reg) urma_unregister_seg(seg_b_reg);
+  if (ctx_b) urma_simple_close(ctx_b);
+  urma_simple_close(ctx);
   if (bad) return fail("completions with error status");
-  if (!two_sided && !atomic && opc == URMA_OPC_WRITE && eb && memcmp(mem_a.data(), mem_b.data(), size) != 0)
-    return fail("written data differs");
+  if (!data_ok) return fail("written data differs");
   printf("urma_perftest: OK\n");
   return 0;
 }
