@@ -52,6 +52,7 @@ struct Pool {
   std::vector<Block*> free_list;
   std::vector<char*> slabs;
   uint64_t total = 0, huge_allocs = 0, alloc_calls = 0, free_calls = 0, failures = 0;
+  uint64_t max_total = 0, grown = 0;   // growth cap in blocks; blocks added after pool_init
   bool inited = false;
   std::map<const char*, Block*> by_mem;   // data area -> descriptor (umq_data_to_head)
   uint64_t generation = 0;
@@ -264,6 +265,7 @@ void pool_init(uint32_t block, uint64_t bytes) {
     g_pool.by_mem[b->mem] = b;
     ++g_pool.total;
   }
+  g_pool.max_total = n * 16;
   g_pool.inited = true;
 }
 Block* block_get(uint32_t need) {
@@ -289,6 +291,16 @@ Block* block_get(uint32_t need) {
   for (int i = 0; i < 8 && !g_pool.free_list.empty(); ++i) {
     t_cache.push_back(g_pool.free_list.back());
     g_pool.free_list.pop_back();
+  }
+  // an empty pool grows by a batch, up to 16 times the size it started with (many queues each keep a full receive
+  // ring posted; the first size is a floor, not a cap on the number of queues)
+  for (int i = 0; t_cache.empty() && i < 8 && g_pool.total < g_pool.max_total; ++i) {
+    Block* nb = block_new(g_pool.block, false);
+    if (!nb) break;
+    g_pool.by_mem[nb->mem] = nb;
+    ++g_pool.total;
+    ++g_pool.grown;
+    t_cache.push_back(nb);
   }
   if (t_cache.empty()) {
     ++g_pool.failures;

@@ -39,7 +39,7 @@ typedef struct umq_init_cfg {
   umq_trans_mode_t trans_mode;
   char dev_name[64]; /* URMA device, "" = shm0 */
   uint32_t block_size_kb; /* qbuf block size: 8, 16, 32 or 64 (0 = 8) */
-  uint64_t pool_bytes;    /* global pool size, 0 = 64 MiB */
+  uint64_t pool_bytes;    /* pool size at start, 0 = 64 MiB; an exhausted pool grows in batches up to 16 times this */
 } umq_init_cfg_t;
 
 typedef struct umq_create_option {

@@ -48,6 +48,11 @@ struct Hello {
   uint8_t blob[UMQ_BIND_INFO_SIZE];
   uint32_t sealed;        // response: 1 = data_key is valid and every payload must be sealed with it
   uint8_t data_key[32];   // only ever sent inside the TLS channel
+  uint32_t n_extra;       // request: LaneHello records that follow; response: lanes the server made (same number)
+};
+struct LaneHello {
+  uint32_t blob_len;
+  uint8_t blob[UMQ_BIND_INFO_SIZE];
 };
 
 struct Pending {
@@ -72,16 +77,35 @@ struct Sealer {
   std::mutex mu;
   std::unique_ptr<ub::AeadCipher> tx, rx;
   uint64_t tx_nonce = 0, rx_last = 0;
-  void set(const uint8_t key[32], bool is_server) {
-    tx.reset(new ub::AeadCipher(key, is_server ? 1u : 0u));
-    rx.reset(new ub::AeadCipher(key, is_server ? 0u : 1u));
+  // One key serves every queue pair of a session: the salt names the lane and the direction, so no two senders ever
+  // share a (key, nonce) pair, and each lane keeps its own replay counter.
+  void set(const uint8_t key[32], bool is_server, uint32_t lane = 0) {
+    tx.reset(new ub::AeadCipher(key, 2 * lane + (is_server ? 1u : 0u)));
+    rx.reset(new ub::AeadCipher(key, 2 * lane + (is_server ? 0u : 1u)));
+    tx_nonce = rx_last = 0;
+  }
+  void clear() {
+    tx.reset();
+    rx.reset();
+    tx_nonce = rx_last = 0;
   }
   bool on() const { return tx != nullptr; }
 };
 
+// A further queue pair of a channel / session beside the first one (the reference's several queues per channel,
+// src/urpc/include/framework/urpc_framework_api.h urpc_channel_queue_add / _pair). On the client it is always a queue
+// from urpc_queue_create; on the server it is made during the attach.
+struct Lane {
+  uint64_t umqh = 0;
+  Sealer seal;
+};
+constexpr uint32_t kMaxLanes = 16;
+
 struct Channel {
   uint32_t id;
   uint64_t umqh = 0;
+  std::vector<std::unique_ptr<Lane>> extra;   // lanes 1..n
+  uint32_t rr = 0;                            // round-robin cursor of urpc_func_call over the lanes
   int tcp = -1;
   std::unique_ptr<ub::SecureConn> conn;
   Sealer seal;
@@ -97,8 +121,16 @@ struct Channel {
   std::string server_ip;
   uint16_t server_port = 0;
 };
+// Lane index of a queue inside a channel (0 = the first queue), -1 when the channel does not hold it.
+int channel_lane(Channel* ch, uint64_t qh) {
+  if (ch->umqh == qh) return 0;
+  for (size_t i = 0; i < ch->extra.size(); ++i)
+    if (ch->extra[i]->umqh == qh) return static_cast<int>(i + 1);
+  return -1;
+}
 struct Session {
   uint64_t umqh;
+  std::vector<std::unique_ptr<Lane>> extra;   // fixed before the session is published
   int tcp;
   uint32_t id;
   std::unique_ptr<ub::SecureConn> conn;
@@ -153,6 +185,7 @@ struct CurrentReq {
   uint32_t nrefs;
 };
 thread_local CurrentReq* t_current = nullptr;
+thread_local uint64_t t_call_queue = 0;   // queue the request urpc_func_call sends next must use (0 = round robin)
 thread_local uint8_t t_call_flags = 0;   // extra header flags for the request urpc_func_call sends next
 struct MemSeg {
   void* va;
@@ -286,13 +319,18 @@ bool open_msg(umq_buf_t* b, const Head& h, Sealer* seal) {
 
 // Drains the channel's queue: responses complete pending calls, expired calls time out. Caller holds ch->mu.
 void channel_progress(Channel* ch) {
-  for (;;) {
-    umq_buf_t* b = umq_dequeue(ch->umqh);
-    if (!b) break;
+  for (size_t lane = 0; lane <= ch->extra.size();) {
+    const uint64_t q = lane ? ch->extra[lane - 1]->umqh : ch->umqh;
+    Sealer* seal = lane ? &ch->extra[lane - 1]->seal : &ch->seal;
+    umq_buf_t* b = umq_dequeue(q);
+    if (!b) {
+      ++lane;
+      continue;
+    }
     Head h;
     if (b->data_size < sizeof(urpc_req_head_t) ||
         !urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) ||
-        (h.type != URPC_MSG_RSP && h.type != URPC_MSG_ACK_AND_RSP) || !open_msg(b, h, &ch->seal)) {
+        (h.type != URPC_MSG_RSP && h.type != URPC_MSG_ACK_AND_RSP) || !open_msg(b, h, seal)) {
       if (b->data_size >= sizeof(urpc_req_head_t)) {
         std::lock_guard<std::mutex> l(g.stat_mu);
         ++g.stats.errors;
@@ -393,32 +431,49 @@ void accept_loop() {
       close(fd);
       continue;
     }
-    const uint64_t q = make_queue("urpc-srv");
+    // one server queue per queue of the client's channel; the session is published only when all are bound
+    std::vector<LaneHello> lane_req(hello.n_extra < kMaxLanes ? hello.n_extra : 0), lane_rsp(lane_req.size());
+    bool ok = hello.n_extra < kMaxLanes;
+    for (size_t i = 0; ok && i < lane_req.size(); ++i)
+      ok = conn->read_full(&lane_req[i], sizeof(LaneHello), 5000) && lane_req[i].blob_len <= UMQ_BIND_INFO_SIZE;
+    const uint64_t q = ok ? make_queue("urpc-srv") : 0;
     Hello rsp{};
     rsp.magic = kHelloMagic;
     rsp.version = urpc_proto::kVersion;
-    if (!q || umq_bind(q, hello.blob, hello.blob_len) != UMQ_SUCCESS) {
+    rsp.n_extra = static_cast<uint32_t>(lane_req.size());
+    Session* s = new Session();
+    ok = ok && q && umq_bind(q, hello.blob, hello.blob_len) == UMQ_SUCCESS;
+    for (size_t i = 0; ok && i < lane_req.size(); ++i) {
+      const uint64_t lq = make_queue("urpc-srv");
+      if (!lq) {
+        ok = false;
+        break;
+      }
+      s->extra.emplace_back(new Lane());
+      s->extra.back()->umqh = lq;
+      ok = umq_bind(lq, lane_req[i].blob, lane_req[i].blob_len) == UMQ_SUCCESS;
+      lane_rsp[i].blob_len = umq_bind_info_get(lq, lane_rsp[i].blob, sizeof(lane_rsp[i].blob));
+    }
+    if (ok && conn->encrypted()) {
+      ok = ub::random_bytes(rsp.data_key, sizeof(rsp.data_key));
+      if (ok) {
+        rsp.sealed = 1;
+        s->seal.set(rsp.data_key, true, 0);
+        for (size_t i = 0; i < s->extra.size(); ++i) s->extra[i]->seal.set(rsp.data_key, true, static_cast<uint32_t>(i + 1));
+      }
+    }
+    if (!ok) {
       if (q) umq_destroy(q);
+      for (auto& ln : s->extra) umq_destroy(ln->umqh);
+      delete s;
       conn.reset();
       close(fd);
       continue;
     }
     rsp.blob_len = umq_bind_info_get(q, rsp.blob, sizeof(rsp.blob));
-    Session* s = new Session();
     s->umqh = q;
     s->tcp = fd;
     s->id = 0;
-    if (conn->encrypted()) {
-      if (!ub::random_bytes(rsp.data_key, sizeof(rsp.data_key))) {
-        umq_destroy(q);
-        delete s;
-        conn.reset();
-        close(fd);
-        continue;
-      }
-      rsp.sealed = 1;
-      s->seal.set(rsp.data_key, true);
-    }
     {
       std::lock_guard<std::mutex> l(g.mu);
       s->id = static_cast<uint32_t>(g.sessions.size());
@@ -427,9 +482,9 @@ void accept_loop() {
     }
     s->conn = std::move(conn);
     if (urpc_ctrl_cb_t cb = g_ctrl_cb.load()) cb(URPC_CTRL_ATTACH, s->id, hello.channel);
-    if (!s->conn->write_full(&rsp, sizeof(rsp))) {
-      // the client went away during the handshake; the session is reaped by server_poll when its socket closes
-    }
+    bool sent = s->conn->write_full(&rsp, sizeof(rsp));
+    for (size_t i = 0; sent && i < lane_rsp.size(); ++i) sent = s->conn->write_full(&lane_rsp[i], sizeof(LaneHello));
+    // a client that went away during the handshake leaves a session that never receives a request
   }
 }
 
@@ -540,6 +595,7 @@ void urpc_uninit(void) {
     s->conn.reset();
     if (s->tcp >= 0) close(s->tcp);
     umq_destroy(s->umqh);
+    for (auto& ln : s->extra) umq_destroy(ln->umqh);
     delete s;
   }
   g.sessions.clear();
@@ -590,14 +646,17 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
   }
   int n = 0;
   static thread_local std::vector<uint8_t> rsp(64 * 1024);
-  for (Session* s : ss) {
+  for (Session* s : ss)
+   for (size_t lane = 0; lane <= s->extra.size(); ++lane) {   // every queue pair of the session in turn
+    const uint64_t lq = lane ? s->extra[lane - 1]->umqh : s->umqh;
+    Sealer* lseal = lane ? &s->extra[lane - 1]->seal : &s->seal;
     for (int budget = 0; budget < 64; ++budget) {
-      umq_buf_t* b = umq_dequeue(s->umqh);
+      umq_buf_t* b = umq_dequeue(lq);
       if (!b) break;
       Head h;
       if (b->data_size < sizeof(urpc_req_head_t) ||
           !urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) || h.type != URPC_MSG_REQ ||
-          !open_msg(b, h, &s->seal)) {
+          !open_msg(b, h, lseal)) {
         if (b->data_size >= sizeof(urpc_req_head_t)) {  // a request that fails the seal check is dropped and counted
           std::lock_guard<std::mutex> l(g.stat_mu);
           ++g.stats.errors;
@@ -618,10 +677,10 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         }
         alen -= 4 + nrefs * sizeof(RefEntry);
       }
-      CurrentReq cur{s->umqh, reinterpret_cast<const RefEntry*>(args + alen), nrefs};
+      CurrentReq cur{lq, reinterpret_cast<const RefEntry*>(args + alen), nrefs};
       Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, h.func_id, h.req_id, h.channel, 0, 0};
       if (h.func_id == URPC_FUNC_ID_KEEPALIVE) {
-        send_msg(s->umqh, rh, nullptr, 0, nullptr, 0, &s->seal);
+        send_msg(lq, rh, nullptr, 0, nullptr, 0, lseal);
         umq_buf_free(b);
         continue;
       }
@@ -633,7 +692,7 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
           if (it != g.func_names.end()) id = it->second;
           else rh.status = static_cast<int8_t>(URPC_ERR_FUNC_NOT_FOUND);
         }
-        send_msg(s->umqh, rh, nullptr, 0, &id, sizeof(id), &s->seal);
+        send_msg(lq, rh, nullptr, 0, &id, sizeof(id), lseal);
         umq_buf_free(b);
         continue;
       }
@@ -657,14 +716,14 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         const uint64_t e1 = ub::now_ns();
         record(URPC_PERF_FUNC_EXEC, e1 - e0);
         rh.status = static_cast<int8_t>(st);
-        send_msg(s->umqh, rh, nullptr, 0, rsp.data(), rlen > rsp.size() ? 0 : rlen, &s->seal);
+        send_msg(lq, rh, nullptr, 0, rsp.data(), rlen > rsp.size() ? 0 : rlen, lseal);
         record(URPC_PERF_FUNC_RETURN, ub::now_ns() - e1);
         umq_buf_free(b);
       } else if (msgs && n < max) {
         msgs[n].event = URPC_POLL_REQ;
         msgs[n].func_id = h.func_id;
         msgs[n].req_id = h.req_id;
-        msgs[n].user_ctx = (uint64_t(s->id) << 32) | h.channel;
+        msgs[n].user_ctx = (uint64_t(s->id) << 32) | (uint64_t(lane) << 24) | (h.channel & 0xffffff);
         msgs[n].data = const_cast<char*>(args);
         msgs[n].len = alen;
         msgs[n].status = 0;
@@ -672,7 +731,7 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         ++n;
       } else {
         rh.status = static_cast<int8_t>(URPC_ERR_FUNC_NOT_FOUND);
-        send_msg(s->umqh, rh, nullptr, 0, nullptr, 0, &s->seal);
+        send_msg(lq, rh, nullptr, 0, nullptr, 0, lseal);
         umq_buf_free(b);
       }
     }
@@ -691,7 +750,10 @@ int urpc_func_return(const urpc_poll_msg_t* req, const void* rsp, uint32_t len, 
   if (!s) return URPC_ERR_EINVAL;
   Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, req->func_id, req->req_id,
           static_cast<uint32_t>(req->user_ctx & 0xffffff), 0, static_cast<int8_t>(status)};
-  return send_msg(s->umqh, rh, nullptr, 0, rsp, len, &s->seal);
+  const uint32_t lane = static_cast<uint32_t>(req->user_ctx >> 24) & 0xff;   // answer on the lane of the request
+  if (lane > s->extra.size()) return URPC_ERR_EINVAL;
+  return send_msg(lane ? s->extra[lane - 1]->umqh : s->umqh, rh, nullptr, 0, rsp, len,
+                  lane ? &s->extra[lane - 1]->seal : &s->seal);
 }
 
 int urpc_channel_create(void) {
@@ -734,19 +796,35 @@ int urpc_channel_server_attach(uint32_t chid, const char* ip, uint16_t port) {
   hello.version = urpc_proto::kVersion;
   hello.channel = chid;
   hello.blob_len = umq_bind_info_get(ch->umqh, hello.blob, sizeof(hello.blob));
+  hello.n_extra = static_cast<uint32_t>(ch->extra.size());
+  // every further queue of the channel travels with the hello, so the server publishes a complete session
+  bool ok = conn->write_full(&hello, sizeof(hello));
+  for (size_t i = 0; ok && i < ch->extra.size(); ++i) {
+    LaneHello lh{};
+    lh.blob_len = umq_bind_info_get(ch->extra[i]->umqh, lh.blob, sizeof(lh.blob));
+    ok = conn->write_full(&lh, sizeof(lh));
+  }
   Hello rsp;
-  if (!conn->write_full(&hello, sizeof(hello)) || !conn->read_full(&rsp, sizeof(rsp), 5000) ||
-      rsp.magic != kHelloMagic || (conn->encrypted() && !rsp.sealed) ||
-      umq_bind(ch->umqh, rsp.blob, rsp.blob_len) != UMQ_SUCCESS) {
+  ok = ok && conn->read_full(&rsp, sizeof(rsp), 5000) && rsp.magic == kHelloMagic &&
+       !(conn->encrypted() && !rsp.sealed) && rsp.n_extra == hello.n_extra &&
+       umq_bind(ch->umqh, rsp.blob, rsp.blob_len) == UMQ_SUCCESS;
+  size_t bound = 0;
+  for (; ok && bound < ch->extra.size(); ++bound) {
+    LaneHello lr;
+    ok = conn->read_full(&lr, sizeof(lr), 5000) && umq_bind(ch->extra[bound]->umqh, lr.blob, lr.blob_len) == UMQ_SUCCESS;
+    if (!ok) break;
+  }
+  if (!ok) {
+    for (size_t i = 0; i < bound; ++i) umq_unbind(ch->extra[i]->umqh);
     conn.reset();
     close(fd);
     return URPC_FAIL;
   }
-  {
-    std::lock_guard<std::mutex> l(ch->seal.mu);
-    if (rsp.sealed) ch->seal.set(rsp.data_key, false);
-    else ch->seal.tx.reset(), ch->seal.rx.reset();
-    ch->seal.tx_nonce = ch->seal.rx_last = 0;
+  for (size_t lane = 0; lane <= ch->extra.size(); ++lane) {
+    Sealer& sl = lane ? ch->extra[lane - 1]->seal : ch->seal;
+    std::lock_guard<std::mutex> l(sl.mu);
+    if (rsp.sealed) sl.set(rsp.data_key, false, static_cast<uint32_t>(lane));
+    else sl.clear();
   }
   ch->conn = std::move(conn);
   ch->tcp = fd;
@@ -763,6 +841,7 @@ int urpc_channel_server_detach(uint32_t chid) {
   std::lock_guard<std::mutex> l(ch->mu);
   ch->attached = false;
   umq_unbind(ch->umqh);
+  for (auto& ln : ch->extra) umq_unbind(ln->umqh);
   ch->conn.reset();
   if (ch->tcp >= 0) close(ch->tcp);
   ch->tcp = -1;
@@ -810,7 +889,18 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
     p.sync = opt && opt->sync;
     ch->pending[req_id] = std::move(p);
     Head h{urpc_proto::kVersion, URPC_MSG_REQ, static_cast<uint8_t>(1 | t_call_flags), wr->func_id, req_id, chid, 0, 0};
-    const int rc = send_msg(ch->umqh, h, wr->args, wr->num_args, nullptr, 0, &ch->seal);
+    // the queue the caller named (urpc_func_call_on), else the lanes in turn
+    size_t lane = ch->extra.empty() ? 0 : ch->rr++ % (ch->extra.size() + 1);
+    if (t_call_queue) {
+      lane = ch->extra.size() + 1;
+      if (ch->umqh == t_call_queue) lane = 0;
+      for (size_t i = 0; i < ch->extra.size(); ++i)
+        if (ch->extra[i]->umqh == t_call_queue) lane = i + 1;
+    }
+    const int rc = lane > ch->extra.size()
+                       ? URPC_ERR_EINVAL
+                       : send_msg(lane ? ch->extra[lane - 1]->umqh : ch->umqh, h, wr->args, wr->num_args, nullptr, 0,
+                                  lane ? &ch->extra[lane - 1]->seal : &ch->seal);
     record(URPC_PERF_FUNC_CALL, ub::now_ns() - ch->pending[req_id].t0);
     if (rc != URPC_SUCCESS) {
       ch->pending.erase(req_id);
@@ -1098,8 +1188,9 @@ static const CurrentReq* req_of(const urpc_poll_msg_t* req, CurrentReq* tmp) {
     const uint32_t sid = static_cast<uint32_t>(req->user_ctx >> 32);
     if (sid < g.sessions.size()) s = g.sessions[sid];
   }
-  if (!s || n == 0 || n > URPC_MAX_REFS) return nullptr;
-  *tmp = CurrentReq{s->umqh, reinterpret_cast<const RefEntry*>(args + all - 4 - n * sizeof(RefEntry)), n};
+  const uint32_t lane = static_cast<uint32_t>(req->user_ctx >> 24) & 0xff;
+  if (!s || n == 0 || n > URPC_MAX_REFS || lane > s->extra.size()) return nullptr;
+  *tmp = CurrentReq{lane ? s->extra[lane - 1]->umqh : s->umqh, reinterpret_cast<const RefEntry*>(args + all - 4 - n * sizeof(RefEntry)), n};
   return tmp;
 }
 int urpc_ref_count(const urpc_poll_msg_t* req) {
@@ -1280,12 +1371,15 @@ int urpc_channel_server_refresh(uint32_t chid) {
   if (rc == URPC_SUCCESS) push_event(URPC_EVENT_CHANNEL_REFRESHED, chid, 0);
   return rc;
 }
-// The queue of a channel is its UMQ handle: the queue calls below take the handle urpc_channel_queue_query returns.
+// A queue of a channel is its UMQ handle: the queue calls below take the handles urpc_channel_queue_query returns
+// (lane order; at most `max` are written, the return value is the number the channel holds).
 int urpc_channel_queue_query(uint32_t chid, uint64_t* qh, uint32_t max) {
   Channel* ch = get_channel(chid);
   if (!ch || !qh || max == 0) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(ch->mu);
   qh[0] = ch->umqh;
-  return 1;
+  for (size_t i = 0; i < ch->extra.size() && i + 1 < max; ++i) qh[i + 1] = ch->extra[i]->umqh;
+  return static_cast<int>(ch->extra.size() + 1);
 }
 // Explicit queues: created on their own, given to a channel before it attaches (the channel then uses it instead of
 // the queue it made for itself), taken back after a detach.
@@ -1307,7 +1401,7 @@ int urpc_queue_destroy(uint64_t qh) {
   {   // a queue that a channel still uses cannot go away
     std::lock_guard<std::mutex> l(g.mu);
     for (auto& kv : g.channels)
-      if (kv.second->umqh == qh) {
+      if (channel_lane(kv.second, qh) >= 0) {
         std::lock_guard<std::mutex> l2(g_q_mu);
         g_user_queues[qh] = urpc_queue_cfg_t{};
         return URPC_ERR_EAGAIN;
@@ -1349,18 +1443,38 @@ int urpc_channel_queue_add(uint32_t chid, uint64_t qh) {
     if (!g_user_queues.count(qh)) return URPC_ERR_EINVAL;
   }
   if (!ch || ch->attached.load()) return URPC_ERR_EINVAL;   // queues change hands only while detached
+  {   // one queue serves one channel
+    std::lock_guard<std::mutex> l(g.mu);
+    for (auto& kv : g.channels)
+      if (channel_lane(kv.second, qh) >= 0) return URPC_ERR_EINVAL;
+  }
   std::lock_guard<std::mutex> l(ch->mu);
-  if (ch->umqh == qh) return URPC_ERR_EINVAL;
-  if (!ch->user_queue) umq_destroy(ch->umqh);             // the queue the channel made for itself
-  ch->umqh = qh;
-  ch->user_queue = true;
+  if (!ch->user_queue) {   // the first explicit queue takes the place of the one the channel made for itself
+    umq_destroy(ch->umqh);
+    ch->umqh = qh;
+    ch->user_queue = true;
+    return URPC_SUCCESS;
+  }
+  if (ch->extra.size() + 1 >= kMaxLanes) return URPC_ERR_EINVAL;
+  ch->extra.emplace_back(new Lane());
+  ch->extra.back()->umqh = qh;
   return URPC_SUCCESS;
 }
 int urpc_channel_queue_rm(uint32_t chid, uint64_t qh) {
   Channel* ch = get_channel(chid);
   if (!ch || ch->attached.load()) return URPC_ERR_EINVAL;
   std::lock_guard<std::mutex> l(ch->mu);
-  if (ch->umqh != qh || !ch->user_queue) return URPC_ERR_EINVAL;
+  const int lane = channel_lane(ch, qh);
+  if (lane < 0 || !ch->user_queue) return URPC_ERR_EINVAL;
+  if (lane > 0) {
+    ch->extra.erase(ch->extra.begin() + (lane - 1));
+    return URPC_SUCCESS;
+  }
+  if (!ch->extra.empty()) {   // the next lane moves up
+    ch->umqh = ch->extra.front()->umqh;
+    ch->extra.erase(ch->extra.begin());
+    return URPC_SUCCESS;
+  }
   const uint64_t own = make_queue("urpc-cli");
   if (!own) return URPC_FAIL;
   ch->umqh = own;
@@ -1370,13 +1484,21 @@ int urpc_channel_queue_rm(uint32_t chid, uint64_t qh) {
 // Pairing a local queue with the server's happens during attach; these report / undo it for one channel.
 int urpc_channel_queue_pair(uint32_t chid, uint64_t local_qh) {
   Channel* ch = get_channel(chid);
-  if (!ch || ch->umqh != local_qh) return URPC_ERR_EINVAL;
+  if (!ch || channel_lane(ch, local_qh) < 0) return URPC_ERR_EINVAL;
   return ch->attached.load() ? URPC_SUCCESS : URPC_ERR_SESSION_CLOSE;
 }
 int urpc_channel_queue_unpair(uint32_t chid, uint64_t local_qh) {
   Channel* ch = get_channel(chid);
-  if (!ch || ch->umqh != local_qh) return URPC_ERR_EINVAL;
+  if (!ch || channel_lane(ch, local_qh) < 0) return URPC_ERR_EINVAL;
   return urpc_channel_server_detach(chid);
+}
+// urpc_func_call on one named queue of the channel instead of the lanes in turn.
+int urpc_func_call_on(uint32_t chid, uint64_t qh, const urpc_call_wr_t* wr, const urpc_call_option_t* opt) {
+  if (!qh) return URPC_ERR_EINVAL;
+  t_call_queue = qh;
+  const int rc = urpc_func_call(chid, wr, opt);
+  t_call_queue = 0;
+  return rc;
 }
 // Allocator plug-in for the copies the library makes of responses to synchronous calls.
 static urpc_allocator_t g_alloc{};

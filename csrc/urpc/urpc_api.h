@@ -195,6 +195,10 @@ URPC_EXPORT int urpc_queue_cfg_get(uint64_t qh, urpc_queue_cfg_t* cfg);
 URPC_EXPORT int urpc_queue_cfg_set(uint64_t qh, const urpc_queue_cfg_t* cfg);
 URPC_EXPORT int urpc_queue_modify(uint64_t qh, urpc_queue_status_t status);
 URPC_EXPORT int urpc_queue_rx_post(uint64_t qh, uint32_t num);
+// A channel holds up to 16 queues. The first explicit queue replaces the one the channel made for itself, each further
+// one becomes another lane; all of them are paired with queues of the server during the attach. urpc_func_call spreads
+// requests over the lanes in turn, urpc_func_call_on names the lane; the response returns on the lane of its request.
+URPC_EXPORT int urpc_func_call_on(uint32_t chid, uint64_t qh, const urpc_call_wr_t* wr, const urpc_call_option_t* opt);
 URPC_EXPORT int urpc_channel_queue_add(uint32_t chid, uint64_t qh);
 URPC_EXPORT int urpc_channel_queue_rm(uint32_t chid, uint64_t qh);
 URPC_EXPORT int urpc_channel_queue_pair(uint32_t chid, uint64_t local_qh);

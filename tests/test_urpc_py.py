@@ -226,3 +226,138 @@ def test_explicit_queue_given_to_a_channel(rpc):
     p = lib.urpc_rsp_copy(b"keep me", 7)
     assert ctypes.string_at(p, 7) == b"keep me"
     lib.urpc_rsp_free(ctypes.c_void_p(p))
+
+
+@pytest.mark.parametrize("sealed", [False, True])
+def test_several_queues_on_one_channel(tmp_path, sealed):
+    """A channel with three explicit queues: all are paired during the attach, calls spread over them in turn or go to
+    the queue the caller names, and each response returns on the queue of its request (clear and sealed)."""
+    import ctypes
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import urpc
+    urpc.init(default_timeout_ms=2000)
+    urpc.set_psk("5a" * 32 if sealed else "")
+    srv = urpc.Server()
+    srv.register(1, lambda b: b[::-1])
+    lib = urpc._lib()
+    lib.urpc_queue_create.restype = ctypes.c_uint64
+    errors0 = urpc.stats()["errors"]                         # the counters outlive uninit
+    try:
+        qs = [lib.urpc_queue_create(None) for _ in range(3)]
+        assert all(qs)
+        chid = lib.urpc_channel_create()
+        for q in qs:
+            assert lib.urpc_channel_queue_add(chid, ctypes.c_uint64(q)) == 0
+        assert lib.urpc_channel_queue_add(chid, ctypes.c_uint64(qs[1])) != 0          # already a lane of this channel
+        other = lib.urpc_channel_create()
+        assert lib.urpc_channel_queue_add(other, ctypes.c_uint64(qs[2])) != 0         # one queue serves one channel
+        assert lib.urpc_channel_destroy(other) == 0
+        got = (ctypes.c_uint64 * 4)()
+        assert lib.urpc_channel_queue_query(chid, got, 4) == 3 and list(got)[:3] == qs
+        assert lib.urpc_channel_server_attach(chid, srv.ip.encode(), srv.port) == 0
+        for q in qs:
+            assert lib.urpc_channel_queue_pair(chid, ctypes.c_uint64(q)) == 0
+
+        def call(payload, on=None):
+            arg = ctypes.create_string_buffer(payload, len(payload))
+            sge = urpc._Sge(ctypes.cast(arg, ctypes.c_void_p), len(payload))
+            wr = urpc._CallWr(1, ctypes.pointer(sge), 1, 0)
+            rsp, n = ctypes.create_string_buffer(256), ctypes.c_uint32(0)
+            opt = urpc._CallOpt(0, 1, ctypes.cast(rsp, ctypes.c_void_p), 256, ctypes.pointer(n))
+            rc = (lib.urpc_func_call(chid, ctypes.byref(wr), ctypes.byref(opt)) if on is None else
+                  lib.urpc_func_call_on(chid, ctypes.c_uint64(on), ctypes.byref(wr), ctypes.byref(opt)))
+            return rc, rsp.raw[:n.value]
+
+        def tx_rx(q):
+            st = (ctypes.c_uint64 * 4)()
+            assert lib.urpc_queue_stats_get(ctypes.c_uint64(q), st, 4) == 4
+            return st[0], st[2]
+
+        for i in range(9):                                   # in turn: three requests and responses per lane
+            msg = b"lane message %d" % i
+            assert call(msg) == (0, msg[::-1])
+        assert [tx_rx(q) for q in qs] == [(3, 3)] * 3
+        for i in range(4):                                   # a named lane takes them all
+            assert call(b"only here", on=qs[2]) == (0, b"ereh ylno")
+        assert [tx_rx(q) for q in qs] == [(3, 3), (3, 3), (7, 7)]
+        assert urpc.stats()["errors"] == errors0             # nothing failed a seal or replay check on any lane
+        assert call(b"x", on=0xdead)[0] != 0                 # not a queue of this channel
+        # a lane leaves only while detached; the next one moves up
+        assert lib.urpc_channel_queue_rm(chid, ctypes.c_uint64(qs[0])) != 0
+        assert lib.urpc_channel_server_detach(chid) == 0
+        assert lib.urpc_channel_queue_rm(chid, ctypes.c_uint64(qs[0])) == 0
+        assert lib.urpc_channel_queue_query(chid, got, 4) == 2 and list(got)[:2] == qs[1:]
+        assert lib.urpc_queue_destroy(ctypes.c_uint64(qs[0])) == 0
+        assert lib.urpc_queue_destroy(ctypes.c_uint64(qs[1])) != 0                    # still held by the channel
+        assert lib.urpc_channel_server_attach(chid, srv.ip.encode(), srv.port) == 0   # two lanes this time
+        for i in range(4):
+            assert call(b"again %d" % i) == (0, (b"again %d" % i)[::-1])
+        assert lib.urpc_channel_destroy(chid) == 0
+        for q in qs[1:]:
+            assert lib.urpc_queue_destroy(ctypes.c_uint64(q)) == 0
+    finally:
+        srv.stop()
+        urpc.set_psk("")
+        urpc.uninit()
+
+
+def test_channel_binding_with_lanes_and_deferred_reply(rpc):
+    """`Channel(queues=3)`: asynchronous calls spread over the lanes; a request that the application answers later
+    (urpc_func_return) still gets its response on the lane it came in on."""
+    import ctypes
+    urpc, srv, _ = rpc
+    lib = urpc._lib()
+    ch = urpc.Channel(srv.ip, srv.port, queues=3)
+    try:
+        assert len(ch.queues) == 3
+        for i in range(6):
+            ch.call_async(1, b"abc%d" % i, user_ctx=i)
+        got, deadline = {}, time.monotonic() + 5
+        while len(got) < 6 and time.monotonic() < deadline:
+            for ev, ctx, status, data in ch.poll():
+                got[ctx] = data
+        assert got == {i: (b"abc%d" % i)[::-1] for i in range(6)}
+        assert ch.queue_stats() == [(2, 2)] * 3
+        assert ch.call(1, b"named", queue=1) == b"deman" and ch.queue_stats()[1] == (3, 3)
+        # function 77 has no handler: the request surfaces in the server's poll and is answered by hand
+        srv.paused = True
+        time.sleep(0.05)
+        ch.call_async(77, b"answer me later", user_ctx=900, queue=2)
+        msgs, n, deadline = (urpc._PollMsg * 4)(), 0, time.monotonic() + 5
+        while n == 0 and time.monotonic() < deadline:
+            n = lib.urpc_server_poll(msgs, 4)
+        assert n == 1 and msgs[0].func_id == 77 and ctypes.string_at(msgs[0].data, msgs[0].len) == b"answer me later"
+        assert lib.urpc_func_return(ctypes.byref(msgs[0]), b"late", 4, 0) == 0
+        lib.urpc_msg_release(ctypes.byref(msgs[0]))
+        out, deadline = [], time.monotonic() + 5
+        while not out and time.monotonic() < deadline:
+            out = ch.poll()
+        assert [(ctx, data) for _, ctx, _, data in out] == [(900, b"late")]
+        assert ch.queue_stats() == [(2, 2), (3, 3), (3, 3)]
+    finally:
+        srv.paused = False
+        ch.close()
+
+
+def test_many_channels_outgrow_the_first_buffer_pool(rpc):
+    """Every queue keeps a full receive ring posted, so a dozen queues need more blocks than the pool starts with: the
+    pool grows instead of failing sends (UMQ mempool state reports the larger total)."""
+    import ctypes
+    urpc, srv, ch0 = rpc
+    chans = [urpc.Channel(srv.ip, srv.port) for _ in range(6)]
+    try:
+        for i, ch in enumerate(chans):
+            assert ch.call(1, b"channel %d" % i) == (b"channel %d" % i)[::-1]
+        from umdk_b200 import umq
+
+        class State(ctypes.Structure):
+            _fields_ = [("block_size", ctypes.c_uint64), ("blocks_total", ctypes.c_uint64),
+                        ("blocks_free", ctypes.c_uint64), ("generation", ctypes.c_uint64), ("registered", ctypes.c_int)]
+        buf = ctypes.create_string_buffer(256)
+        assert umq._lib().umq_mempool_state_get(ctypes.c_uint64(0), 0, buf) == 0
+        st = State.from_buffer(buf)
+        assert st.block_size == 65536 and st.blocks_total > 1024   # 64 MiB of 64 KiB blocks at the start
+    finally:
+        for ch in chans:
+            ch.close()

@@ -227,15 +227,48 @@ class Server:
 
 
 class Channel:
-    def __init__(self, ip: str, port: int):
-        ch = _lib().urpc_channel_create()
+    """A client channel attached to one server. ``queues`` > 1 gives it that many queue pairs (made with
+    ``urpc_queue_create`` and added before the attach): calls then spread over them in turn, or go to the one
+    ``call(..., queue=i)`` names, and each response returns on the queue pair of its request."""
+
+    def __init__(self, ip: str, port: int, queues: int = 1):
+        lib = _lib()
+        ch = lib.urpc_channel_create()
         if ch < 0:
             raise UrpcError("urpc_channel_create", ch)
         self.id = ch
-        rc = _lib().urpc_channel_server_attach(ch, ip.encode(), port)
+        self.queues: List[int] = []
+        lib.urpc_queue_create.restype = ctypes.c_uint64
+        rc = 0
+        for _ in range(queues if queues > 1 else 0):
+            q = lib.urpc_queue_create(None)
+            rc = lib.urpc_channel_queue_add(ch, ctypes.c_uint64(q)) if q else -1
+            if q:
+                self.queues.append(q)
+            if rc != 0:
+                break
+        if rc == 0:
+            rc = lib.urpc_channel_server_attach(ch, ip.encode(), port)
         if rc != 0:
-            _lib().urpc_channel_destroy(ch)
+            lib.urpc_channel_destroy(ch)
+            for q in self.queues:
+                lib.urpc_queue_destroy(ctypes.c_uint64(q))
             raise UrpcError("urpc_channel_server_attach", rc)
+
+    def _call(self, wr, opt, queue: Optional[int]):
+        if queue is None:
+            return _lib().urpc_func_call(self.id, ctypes.byref(wr), ctypes.byref(opt))
+        return _lib().urpc_func_call_on(self.id, ctypes.c_uint64(self.queues[queue]), ctypes.byref(wr),
+                                        ctypes.byref(opt))
+
+    def queue_stats(self) -> List[Tuple[int, int]]:
+        """(messages sent, messages received) of every explicit queue pair, in lane order."""
+        out = []
+        for q in self.queues:
+            st = (ctypes.c_uint64 * 4)()
+            _lib().urpc_queue_stats_get(ctypes.c_uint64(q), st, 4)
+            out.append((int(st[0]), int(st[2])))
+        return out
 
     def _wr(self, func_id: int, args: bytes, user_ctx: int):
         buf = ctypes.create_string_buffer(args, len(args)) if args else None
@@ -243,12 +276,13 @@ class Channel:
         wr = _CallWr(func_id, ctypes.pointer(sge), 1 if args else 0, user_ctx)
         return wr, (buf, sge)
 
-    def call(self, func_id: int, args: bytes = b"", timeout_ms: int = 0, max_rsp: int = 65536) -> bytes:
+    def call(self, func_id: int, args: bytes = b"", timeout_ms: int = 0, max_rsp: int = 65536,
+             queue: Optional[int] = None) -> bytes:
         wr, keep = self._wr(func_id, args, 0)
         rsp = ctypes.create_string_buffer(max_rsp)
         n = ctypes.c_uint32(0)
         opt = _CallOpt(timeout_ms, 1, ctypes.cast(rsp, ctypes.c_void_p), max_rsp, ctypes.pointer(n))
-        rc = _lib().urpc_func_call(self.id, ctypes.byref(wr), ctypes.byref(opt))
+        rc = self._call(wr, opt, queue)
         if rc != 0:
             raise UrpcError("urpc_func_call", rc)
         return rsp.raw[:n.value]
@@ -267,10 +301,11 @@ class Channel:
             raise UrpcError("urpc_func_call_ref", rc)
         return rsp.raw[:n.value]
 
-    def call_async(self, func_id: int, args: bytes = b"", user_ctx: int = 0, timeout_ms: int = 0) -> int:
+    def call_async(self, func_id: int, args: bytes = b"", user_ctx: int = 0, timeout_ms: int = 0,
+                   queue: Optional[int] = None) -> int:
         wr, keep = self._wr(func_id, args, user_ctx)
         opt = _CallOpt(timeout_ms, 0, None, 0, None)
-        rc = _lib().urpc_func_call(self.id, ctypes.byref(wr), ctypes.byref(opt))
+        rc = self._call(wr, opt, queue)
         if rc < 0:
             raise UrpcError("urpc_func_call", rc)
         return rc   # request id
@@ -290,4 +325,7 @@ class Channel:
         if self.id >= 0:
             _lib().urpc_channel_server_detach(self.id)
             _lib().urpc_channel_destroy(self.id)
+            for q in self.queues:
+                _lib().urpc_queue_destroy(ctypes.c_uint64(q))
+            self.queues = []
             self.id = -1
