@@ -1,6 +1,7 @@
 // urpc_perftest: latency / call-rate measurement and self-check of the URPC framework (server thread + client in
 // one process by default; `--server PORT` / `--client PORT` run the two sides as separate processes).
-//   urpc_perftest [--size N] [--iters N] [--selftest]
+//   urpc_perftest [--size N] [--iters N] [--queues N] [--selftest]
+// --queues N gives the channel N explicit queue pairs (calls spread over them in turn).
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -40,11 +41,12 @@ int main(int argc, char** argv) {
   uint32_t size = 4096, iters = 5000;
   bool selftest = false;
   int hold_ms = 0;  // keep the process (and its management socket) alive this long after the run
-  int server_port = -1, client_port = -1;
+  int server_port = -1, client_port = -1, queues = 1;
   for (int i = 1; i < argc; ++i) {
     if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--selftest")) selftest = true;
+    else if (!strcmp(argv[i], "--queues") && i + 1 < argc) queues = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--hold-ms") && i + 1 < argc) hold_ms = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--server") && i + 1 < argc) server_port = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--client") && i + 1 < argc) client_port = atoi(argv[++i]);
@@ -90,6 +92,12 @@ int main(int argc, char** argv) {
     }
   }
   const int ch = urpc_channel_create();
+  std::vector<uint64_t> lanes;
+  for (int i = 0; ch >= 0 && queues > 1 && i < queues; ++i) {
+    const uint64_t q = urpc_queue_create(nullptr);
+    if (!q || urpc_channel_queue_add(ch, q) != URPC_SUCCESS) return fail("queue add");
+    lanes.push_back(q);
+  }
   if (ch < 0 || urpc_channel_server_attach(ch, "127.0.0.1", (uint16_t)port) != URPC_SUCCESS) return fail("attach");
   std::vector<uint8_t> arg(size), rsp(size + 64);
   for (uint32_t i = 0; i < size; ++i) arg[i] = (uint8_t)(i * 7 + 1);
@@ -138,8 +146,13 @@ int main(int argc, char** argv) {
   const double sec = (ub::now_ns() - t0) * 1e-9;
   uint64_t cnt, avg, p99;
   urpc_perf_get(&cnt, &avg, &p99);
-  printf("size=%u: sync echo %.1f us/call; async %.0f calls/s (%.1f MB/s args); call latency avg %.1f us p99 %.1f us\n",
-         size, lat_us, iters / sec, iters * (double)size / sec / 1e6, avg / 1e3, p99 / 1e3);
+  for (uint64_t q : lanes) {   // every lane carried its share
+    uint64_t st[4] = {0, 0, 0, 0};
+    if (urpc_queue_stats_get(q, st, 4) != 4 || st[0] < (iters + lat_iters) / lanes.size() - 1 || st[2] < st[0] - 1)
+      rc = fail("lane share");
+  }
+  printf("size=%u queues=%d: sync echo %.1f us/call; async %.0f calls/s (%.1f MB/s args); call latency avg %.1f us p99 %.1f us\n",
+         size, queues, lat_us, iters / sec, iters * (double)size / sec / 1e6, avg / 1e3, p99 / 1e3);
   if (selftest && rc == 0) {
     // request handled by the application through poll / return
     wr.func_id = 7;
@@ -183,6 +196,7 @@ int main(int argc, char** argv) {
   }
   urpc_channel_server_detach(ch);
   urpc_channel_destroy(ch);
+  for (uint64_t q : lanes) urpc_queue_destroy(q);
   stop = true;
   if (srv.joinable()) srv.join();
   urpc_uninit();

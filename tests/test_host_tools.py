@@ -40,6 +40,12 @@ def test_urpc_selftest_timeouts_and_keepalive(tmp_path):
     assert rc == 0 and "urpc_perftest: OK" in out, out
 
 
+def test_urpc_selftest_over_three_queue_pairs(tmp_path):
+    """The same self-test with a channel of three queue pairs: each lane carries its share of the calls."""
+    rc, out = _run([BIN / "urpc_perftest", "--selftest", "--iters", "2000", "--queues", "3"], tmp_path)
+    assert rc == 0 and "queues=3" in out and "urpc_perftest: OK" in out, out
+
+
 def test_urpc_admin_reads_the_management_socket(tmp_path):
     sock = str(tmp_path / "urpc.sock")
     env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"), URPC_ADMIN_SOCKET=sock)
