@@ -98,6 +98,17 @@ PskConfig PskConfig::from_env(const char* prefix, bool* bad) {
       if (bad) *bad = true;
     }
   }
+  const char* ca = getenv((p + "_TLS_CA").c_str());
+  const char* cert = getenv((p + "_TLS_CERT").c_str());
+  const char* pkey = getenv((p + "_TLS_KEY").c_str());
+  const int given = (ca && *ca ? 1 : 0) + (cert && *cert ? 1 : 0) + (pkey && *pkey ? 1 : 0);
+  if (given == 3) {
+    c.ca_file = ca;
+    c.cert_file = cert;
+    c.key_file = pkey;
+  } else if (given != 0 && bad) {
+    *bad = true;
+  }
   return c;
 }
 
@@ -148,8 +159,17 @@ std::unique_ptr<SecureConn> SecureConn::make(int fd, const PskConfig& cfg, bool 
   SSL_CTX_set_max_proto_version(ctx, TLS1_3_VERSION);
   SSL_CTX_set_ciphersuites(ctx, "TLS_AES_256_GCM_SHA384");
   SSL_CTX_set_mode(ctx, SSL_MODE_AUTO_RETRY);
-  if (is_server) {
-    SSL_CTX_set_num_tickets(ctx, 0);  // no post-handshake messages: the first record after the handshake is data
+  if (is_server) SSL_CTX_set_num_tickets(ctx, 0);  // no post-handshake messages: the first record after the handshake is data
+  if (cfg.use_certs()) {
+    // mutual authentication: present our chain, accept only a peer that presents one ending at the configured CA
+    if (SSL_CTX_use_certificate_chain_file(ctx, cfg.cert_file.c_str()) != 1 ||
+        SSL_CTX_use_PrivateKey_file(ctx, cfg.key_file.c_str(), SSL_FILETYPE_PEM) != 1 ||
+        SSL_CTX_check_private_key(ctx) != 1 || SSL_CTX_load_verify_locations(ctx, cfg.ca_file.c_str(), nullptr) != 1) {
+      if (err) *err = ssl_error_text("loading the certificate, key or CA file");
+      return nullptr;
+    }
+    SSL_CTX_set_verify(ctx, SSL_VERIFY_PEER | SSL_VERIFY_FAIL_IF_NO_PEER_CERT, nullptr);
+  } else if (is_server) {
     SSL_CTX_set_psk_find_session_callback(ctx, &SecureConnCallbacks::find_session);
   } else {
     SSL_CTX_set_psk_use_session_callback(ctx, &SecureConnCallbacks::use_session);
@@ -168,7 +188,15 @@ std::unique_ptr<SecureConn> SecureConn::make(int fd, const PskConfig& cfg, bool 
     if (err) *err = ssl_error_text(is_server ? "TLS accept" : "TLS connect");
     return nullptr;
   }
-  if (!SSL_session_reused(ssl)) {  // a handshake that did not use the key cannot happen without certificates; be sure
+  if (cfg.use_certs()) {
+    X509* peer = SSL_get1_peer_certificate(ssl);
+    const bool verified = peer && SSL_get_verify_result(ssl) == X509_V_OK;
+    if (peer) X509_free(peer);
+    if (!verified) {
+      if (err) *err = "TLS handshake finished without a verified peer certificate";
+      return nullptr;
+    }
+  } else if (!SSL_session_reused(ssl)) {  // a handshake that did not use the key cannot happen without certificates; be sure
     if (err) *err = "TLS handshake finished without the pre-shared key";
     return nullptr;
   }
@@ -323,11 +351,27 @@ UB_SECURE_EXPORT long ub_secure_open(const char* psk_hex, const char* label, uin
                                                                              : -1;
 }
 
+static int echo_over(int fd, int is_server, const ub::PskConfig& cfg, size_t n, int timeout_ms, char* cipher,
+                     size_t cipher_cap);
 UB_SECURE_EXPORT int ub_secure_echo(int fd, int is_server, const char* psk_hex, const char* identity, size_t n,
                                     int timeout_ms, char* cipher, size_t cipher_cap) {
   ub::PskConfig cfg;
   if (psk_hex && *psk_hex && !ub::PskConfig::parse_hex(psk_hex, &cfg.key)) return -2;
   if (identity && *identity) cfg.identity = identity;
+  return echo_over(fd, is_server, cfg, n, timeout_ms, cipher, cipher_cap);
+}
+UB_SECURE_EXPORT int ub_secure_echo_cert(int fd, int is_server, const char* ca_file, const char* cert_file,
+                                         const char* key_file, size_t n, int timeout_ms, char* cipher,
+                                         size_t cipher_cap) {
+  if (!ca_file || !cert_file || !key_file) return -2;
+  ub::PskConfig cfg;
+  cfg.ca_file = ca_file;
+  cfg.cert_file = cert_file;
+  cfg.key_file = key_file;
+  return echo_over(fd, is_server, cfg, n, timeout_ms, cipher, cipher_cap);
+}
+static int echo_over(int fd, int is_server, const ub::PskConfig& cfg, size_t n, int timeout_ms, char* cipher,
+                     size_t cipher_cap) {
   std::string err;
   auto conn = is_server ? ub::SecureConn::server(fd, cfg, timeout_ms, &err) : ub::SecureConn::client(fd, cfg, timeout_ms, &err);
   if (!conn) return -3;

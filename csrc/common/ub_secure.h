@@ -2,7 +2,8 @@
 //
 // SecureConn wraps a connected TCP socket. With an empty pre-shared key it is a plain pass-through; with a key the
 // two sides run a TLS 1.3 handshake in PSK mode restricted to TLS_AES_256_GCM_SHA384 and every later byte travels in
-// TLS records. AeadCipher seals single messages (AES-256-GCM, 96-bit nonce = 32-bit salt || 64-bit sequence number)
+// TLS records. With certificate files instead of a key the handshake is TLS 1.3 with mutual authentication: each
+// side presents its certificate and accepts only a peer whose chain ends at the configured CA. AeadCipher seals single messages (AES-256-GCM, 96-bit nonce = 32-bit salt || 64-bit sequence number)
 // for data-plane traffic that does not go through the socket; its key is derived from the pre-shared key with
 // HKDF-SHA256 and a per-use label.
 //
@@ -24,11 +25,16 @@ namespace ub {
 
 struct UB_PUBLIC PskConfig {
   std::string identity = "umdk";
-  std::vector<uint8_t> key;  // 16..64 bytes; empty = security off
+  std::vector<uint8_t> key;  // 16..64 bytes; empty = no pre-shared key
+  // Certificate mode (takes precedence over the key): PEM files of the CA that signs the peers, of this side's
+  // certificate chain and of its private key. All three or none.
+  std::string ca_file, cert_file, key_file;
 
-  bool enabled() const { return !key.empty(); }
-  // Reads <PREFIX>_PSK (hex string, 32..128 digits) and <PREFIX>_PSK_ID. A malformed key leaves the config disabled
-  // and sets *bad (when given) so that callers can refuse to start instead of silently running in the clear.
+  bool use_certs() const { return !cert_file.empty(); }
+  bool enabled() const { return !key.empty() || use_certs(); }
+  // Reads <PREFIX>_PSK (hex string, 32..128 digits), <PREFIX>_PSK_ID and <PREFIX>_TLS_CA / _TLS_CERT / _TLS_KEY. A
+  // malformed key or an incomplete set of files leaves the config disabled and sets *bad (when given) so that callers
+  // can refuse to start instead of silently running in the clear.
   static PskConfig from_env(const char* prefix, bool* bad = nullptr);
   static bool parse_hex(const char* hex, std::vector<uint8_t>* out);
 };
@@ -100,4 +106,7 @@ long ub_secure_open(const char* psk_hex, const char* label, uint32_t salt, uint6
 // is given the negotiated suite name is copied there.
 int ub_secure_echo(int fd, int is_server, const char* psk_hex, const char* identity, size_t n, int timeout_ms,
                    char* cipher, size_t cipher_cap);
+// The same over a certificate-authenticated connection.
+int ub_secure_echo_cert(int fd, int is_server, const char* ca_file, const char* cert_file, const char* key_file, size_t n,
+                        int timeout_ms, char* cipher, size_t cipher_cap);
 }

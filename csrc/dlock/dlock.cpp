@@ -845,6 +845,20 @@ int dlock_set_psk(const char* key_hex, const char* identity) {
   return DLOCK_SUCCESS;
 }
 
+int dlock_set_tls_files(const char* ca_file, const char* cert_file, const char* key_file) {
+  const bool any = (ca_file && *ca_file) || (cert_file && *cert_file) || (key_file && *key_file);
+  const bool all = ca_file && *ca_file && cert_file && *cert_file && key_file && *key_file;
+  if (any && !all) return DLOCK_EINVAL;
+  std::lock_guard<std::mutex> l(g_psk_mu);
+  if (!g_psk_loaded) g_psk = ub::PskConfig();
+  g_psk.ca_file = all ? ca_file : "";
+  g_psk.cert_file = all ? cert_file : "";
+  g_psk.key_file = all ? key_file : "";
+  g_psk_loaded = true;
+  g_psk_bad = false;
+  return DLOCK_SUCCESS;
+}
+
 int dlock_get_server_debug_stats(int server_id, dlock_debug_stats_t* out) {
   std::lock_guard<std::mutex> l(g_srv_mu);
   auto it = g_servers.find(server_id);

@@ -67,6 +67,11 @@ typedef struct dlock_debug_stats {
  * channel with AES-256-GCM; an empty key switches both off. Applies to servers started and clients initialised
  * afterwards. Without a call the key comes from DLOCK_PSK / DLOCK_PSK_ID in the environment. */
 DLOCK_EXPORT int dlock_set_psk(const char* key_hex, const char* identity);
+/* Certificates instead of a shared key (they take precedence): PEM files of the CA that signs the peers, of this
+ * process's certificate chain and of its private key. The control channel then runs TLS 1.3 with mutual
+ * authentication (a peer without a certificate of that CA is refused) and the data channel is sealed as with a key.
+ * Three empty strings switch it off. Environment: DLOCK_TLS_CA / DLOCK_TLS_CERT / DLOCK_TLS_KEY. */
+DLOCK_EXPORT int dlock_set_tls_files(const char* ca_file, const char* cert_file, const char* key_file);
 
 /* server */
 DLOCK_EXPORT int dlock_server_start(const dlock_server_cfg_t* cfg, int* server_id, uint16_t* port_out);

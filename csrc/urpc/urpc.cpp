@@ -555,6 +555,18 @@ int urpc_set_psk(const char* key_hex, const char* identity) {
   return URPC_SUCCESS;
 }
 
+int urpc_set_tls_files(const char* ca_file, const char* cert_file, const char* key_file) {
+  const bool any = (ca_file && *ca_file) || (cert_file && *cert_file) || (key_file && *key_file);
+  const bool all = ca_file && *ca_file && cert_file && *cert_file && key_file && *key_file;
+  if (any && !all) return URPC_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g.mu);
+  g.psk.ca_file = all ? ca_file : "";
+  g.psk.cert_file = all ? cert_file : "";
+  g.psk.key_file = all ? key_file : "";
+  g.psk_set = true;
+  return URPC_SUCCESS;
+}
+
 int urpc_init(const urpc_config_t* cfg) {
   std::lock_guard<std::mutex> l(g.mu);
   if (g.inited) return URPC_SUCCESS;

@@ -82,6 +82,10 @@ typedef void (*urpc_keepalive_cb_t)(uint32_t chid, int alive, void* ctx);
  * the server hands out in that handshake. Empty key = off. Without a call the key comes from URPC_PSK /
  * URPC_PSK_ID in the environment. Call before urpc_server_start / urpc_channel_server_attach. */
 URPC_EXPORT int urpc_set_psk(const char* key_hex, const char* identity);
+/* Certificates instead of a shared key (they take precedence): PEM files of the CA, of this process's certificate chain
+ * and of its private key; the handshake is then TLS 1.3 with mutual authentication. Three empty strings switch it off.
+ * Environment: URPC_TLS_CA / URPC_TLS_CERT / URPC_TLS_KEY. */
+URPC_EXPORT int urpc_set_tls_files(const char* ca_file, const char* cert_file, const char* key_file);
 URPC_EXPORT int urpc_init(const urpc_config_t* cfg);
 URPC_EXPORT void urpc_uninit(void);
 /* server */

@@ -82,3 +82,138 @@ def test_seal_open_roundtrip_and_tamper_detection():
     bad = bytearray(sealed.raw)
     bad[10] ^= 1
     assert lib.ub_secure_open(PSK.encode(), b"dlock-cmd", 7, 42, aad, len(aad), bytes(bad), n, plain, len(plain)) == -1
+
+
+# ------------------------------------------------------------------------------------------------ certificates
+def _make_pki(tmp_path, name):
+    """A CA and two leaf certificates (server, client) signed by it, as PEM files."""
+    import datetime
+    from cryptography import x509
+    from cryptography.hazmat.primitives import hashes, serialization
+    from cryptography.hazmat.primitives.asymmetric import ec
+    from cryptography.x509.oid import NameOID
+
+    def write(path, data):
+        path.write_bytes(data)
+        return str(path)
+
+    def key_pem(k):
+        return k.private_bytes(serialization.Encoding.PEM, serialization.PrivateFormat.PKCS8,
+                               serialization.NoEncryption())
+    now = datetime.datetime.now(datetime.timezone.utc)
+    ca_key = ec.generate_private_key(ec.SECP384R1())
+    ca_name = x509.Name([x509.NameAttribute(NameOID.COMMON_NAME, f"{name} test CA")])
+    ca = (x509.CertificateBuilder().subject_name(ca_name).issuer_name(ca_name).public_key(ca_key.public_key())
+          .serial_number(x509.random_serial_number()).not_valid_before(now - datetime.timedelta(days=1))
+          .not_valid_after(now + datetime.timedelta(days=30))
+          .add_extension(x509.BasicConstraints(ca=True, path_length=None), critical=True)
+          .sign(ca_key, hashes.SHA384()))
+    out = {"ca": write(tmp_path / f"{name}_ca.pem", ca.public_bytes(serialization.Encoding.PEM))}
+    for leaf in ("server", "client"):
+        k = ec.generate_private_key(ec.SECP384R1())
+        cert = (x509.CertificateBuilder()
+                .subject_name(x509.Name([x509.NameAttribute(NameOID.COMMON_NAME, f"{name} {leaf}")]))
+                .issuer_name(ca_name).public_key(k.public_key()).serial_number(x509.random_serial_number())
+                .not_valid_before(now - datetime.timedelta(days=1)).not_valid_after(now + datetime.timedelta(days=30))
+                .add_extension(x509.BasicConstraints(ca=False, path_length=None), critical=True)
+                .sign(ca_key, hashes.SHA384()))
+        out[leaf] = (write(tmp_path / f"{name}_{leaf}.pem", cert.public_bytes(serialization.Encoding.PEM)),
+                     write(tmp_path / f"{name}_{leaf}.key", key_pem(k)))
+    return out
+
+
+def _echo_pair_cert(lib, srv_files, cli_files, n=50000):
+    a, b = socket.socketpair()
+    out = {}
+
+    def server():
+        c = ctypes.create_string_buffer(64)
+        out["srv"] = lib.ub_secure_echo_cert(a.fileno(), 1, *[f.encode() for f in srv_files], n, 3000, c, 64)
+        out["srv_cipher"] = c.value
+    t = threading.Thread(target=server)
+    t.start()
+    c = ctypes.create_string_buffer(64)
+    out["cli"] = lib.ub_secure_echo_cert(b.fileno(), 0, *[f.encode() for f in cli_files], n, 3000, c, 64)
+    out["cli_cipher"] = c.value
+    b.close()   # a refused client must not leave the server waiting for its timeout
+    t.join()
+    a.close()
+    return out
+
+
+def test_tls_with_certificates_mutual_authentication(tmp_path):
+    lib = _lib()
+    lib.ub_secure_echo_cert.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p,
+                                        ctypes.c_size_t, ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t]
+    ours, theirs = _make_pki(tmp_path, "ours"), _make_pki(tmp_path, "theirs")
+    good = _echo_pair_cert(lib, (ours["ca"], *ours["server"]), (ours["ca"], *ours["client"]))
+    assert good["srv"] == 0 and good["cli"] == 0
+    assert good["cli_cipher"] == b"TLS_AES_256_GCM_SHA384" == good["srv_cipher"]
+    # a client whose certificate comes from another CA is refused by the server ...
+    bad = _echo_pair_cert(lib, (ours["ca"], *ours["server"]), (ours["ca"], *theirs["client"]), n=64)
+    assert bad["srv"] != 0 and bad["cli"] != 0
+    # ... and a client refuses a server that is not signed by the CA it trusts
+    bad = _echo_pair_cert(lib, (theirs["ca"], *theirs["server"]), (ours["ca"], *ours["client"]), n=64)
+    assert bad["cli"] != 0
+    # a key that does not belong to the certificate never gets as far as a handshake
+    bad = _echo_pair_cert(lib, (ours["ca"], *ours["server"]), (ours["ca"], ours["client"][0], ours["server"][1]), n=64)
+    assert bad["cli"] != 0
+
+
+def test_dlock_and_urpc_services_with_certificates(tmp_path):
+    """The lock service and the RPC framework with certificate files instead of a shared key: peers of the same CA
+    work (control channel in TLS 1.3, payloads sealed), a client with a certificate of another CA cannot join."""
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import dlock, urpc
+    ours, theirs = _make_pki(tmp_path, "ours"), _make_pki(tmp_path, "theirs")
+    srv = None
+    try:
+        dlock.set_tls_files(ours["ca"], *ours["server"])
+        srv = dlock.Server()                                  # keeps the files it was started with
+        dlock.set_tls_files(ours["ca"], *ours["client"])
+        a, b = dlock.Client(srv.ip, srv.port), dlock.Client(srv.ip, srv.port)
+        la, lb = a.get_lock("C1", dlock.ATOMIC), b.get_lock("C1", dlock.ATOMIC)
+        assert a.trylock(la) is True and b.trylock(lb) is False
+        a.unlock(la)
+        assert b.trylock(lb) is True
+        b.unlock(lb)
+        st = srv.stats()
+        assert st["tls_rejected"] == 0 and st["sealed_rejected"] == 0 and st["data_msgs"] >= 3
+        dlock.set_tls_files(ours["ca"], *theirs["client"])
+        with pytest.raises(dlock.DlockError):
+            dlock.Client(srv.ip, srv.port)
+        dlock.set_tls_files()                                 # clear text against a server that wants certificates
+        with pytest.raises(dlock.DlockError):
+            dlock.Client(srv.ip, srv.port)
+        assert srv.stats()["tls_rejected"] == 2
+        with pytest.raises(dlock.DlockError):
+            dlock.set_tls_files(ours["ca"], "", "")           # all three files or none
+        a.close()
+        b.close()
+    finally:
+        if srv is not None:
+            srv.stop()
+        dlock.set_psk("", "")
+
+    urpc.init(default_timeout_ms=2000)
+    rsrv = None
+    try:
+        urpc.set_tls_files(ours["ca"], *ours["server"])
+        rsrv = urpc.Server()
+        rsrv.register(1, lambda x: x[::-1])
+        urpc.set_tls_files(ours["ca"], *ours["client"])
+        ch = urpc.Channel(rsrv.ip, rsrv.port, queues=2)
+        big = bytes(range(256)) * 100
+        assert ch.call(1, b"with certificates") == b"setacifitrec htiw" and ch.call(1, big) == big[::-1]
+        rep = urpc.admin_query("sessions")
+        assert "TLS_AES_256_GCM_SHA384" in rep and "payload sealed" in rep
+        ch.close()
+        urpc.set_tls_files(ours["ca"], *theirs["client"])
+        with pytest.raises(urpc.UrpcError):
+            urpc.Channel(rsrv.ip, rsrv.port)
+    finally:
+        if rsrv is not None:
+            rsrv.stop()
+        urpc.set_psk("", "")
+        urpc.uninit()

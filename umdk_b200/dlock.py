@@ -69,6 +69,14 @@ def set_psk(key_hex: str = "", identity: str = "") -> None:
         raise DlockError("set_psk", rc)
 
 
+def set_tls_files(ca_file: str = "", cert_file: str = "", key_file: str = "") -> None:
+    """Certificates instead of a shared key for servers started and clients created afterwards: the control channel
+    runs TLS 1.3 with mutual authentication against ``ca_file``. Three empty strings switch it off."""
+    rc = _lib().dlock_set_tls_files(ca_file.encode(), cert_file.encode(), key_file.encode())
+    if rc != 0:
+        raise DlockError("set_tls_files", rc)
+
+
 class Server:
     def __init__(self, ip: str = "127.0.0.1", port: int = 0, dev: str = "shm0", recovery_clients: int = 0,
                  recovery_timeout_ms: int = 3000):

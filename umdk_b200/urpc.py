@@ -89,6 +89,14 @@ def set_psk(key_hex: str = "", identity: str = "") -> None:
         raise UrpcError("urpc_set_psk", rc)
 
 
+def set_tls_files(ca_file: str = "", cert_file: str = "", key_file: str = "") -> None:
+    """Certificates instead of a shared key: the connection handshake runs in TLS 1.3 with mutual authentication
+    against ``ca_file``. Three empty strings switch it off."""
+    rc = _lib().urpc_set_tls_files(ca_file.encode(), cert_file.encode(), key_file.encode())
+    if rc != 0:
+        raise UrpcError("urpc_set_tls_files", rc)
+
+
 PERF_POINTS = ("func_call", "call_to_response", "func_exec", "func_return")
 _REC_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p)
 _LOG_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_char_p)
