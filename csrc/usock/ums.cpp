@@ -1,5 +1,6 @@
 // UMS implementation (see ums.h).
 #include "ums.h"
+#include "ums_agent_proto.h"
 
 #include "ub_secure.h"
 #include "ums_shm.h"
@@ -104,6 +105,32 @@ bool clc_verify(const Clc& m, bool from_server) {
   ub::AeadCipher c(a.key, from_server ? 1u : 0u);
   uint8_t none = 0;
   return c.open(m.nonce, &m, kClcSigned, m.tag, sizeof(m.tag), &none);
+}
+
+// Token exchange through the agents (ums_agent): with UMS_AGENT_SOCK and UMS_AGENT_ADDR (the "ip:port" other agents
+// reach this host's agent on) a connecting endpoint stores the ring name with its agent and sends only
+// "@<token id>@<agent address>"; the accepting endpoint has its own agent fetch the name over the agents' TLS
+// connection. The name itself never travels on the application's connection
+// (the reference: ums_agent_token_proxy.c, token request on connection setup).
+bool agent_mode_tx() {
+  const char* s = getenv("UMS_AGENT_SOCK");
+  const char* a = getenv("UMS_AGENT_ADDR");
+  return s && *s && a && *a && strlen(a) < 40;
+}
+// Replaces an "@id@addr" reference by the ring name; false when it cannot be resolved.
+bool agent_resolve(char name[64]) {
+  if (name[0] != '@') return true;
+  const char* s = getenv("UMS_AGENT_SOCK");
+  if (!s || !*s) return false;
+  char* end = nullptr;
+  const uint64_t id = strtoull(name + 1, &end, 16);
+  if (!end || *end != '@' || !end[1]) return false;
+  char value[UMS_AGENT_MAX_VALUE];
+  uint32_t len = sizeof(value);
+  if (ums_agent_get(nullptr, end + 1, id, value, &len) != 0 || len == 0 || len >= 64) return false;
+  memcpy(name, value, len);
+  name[len] = 0;
+  return true;
 }
 
 struct Conn {
@@ -242,7 +269,7 @@ int ums_adopt_accepted(int listen_fd, int fd) {
     Clc out{};
     out.magic = kClcMagic;
     in.shm_name[sizeof(in.shm_name) - 1] = 0;
-    const bool trusted = clc_verify(in, false) && !strchr(in.shm_name, '/');
+    const bool trusted = clc_verify(in, false) && agent_resolve(in.shm_name) && !strchr(in.shm_name, '/');
     if (!trusted) {
       std::lock_guard<std::mutex> l(g_mu);
       ++g_stats.conns_auth_fail;
@@ -292,8 +319,18 @@ int ums_adopt_connected(int fd, const struct sockaddr* peer) {
     Clc out{};
     out.magic = kClcMagic;
     snprintf(out.shm_name, sizeof(out.shm_name), "conn_%d_%llu", getpid(), (unsigned long long)g_seq.fetch_add(1));
-    clc_sign(&out, false);
     const std::string path = dir() + "/" + out.shm_name;
+    uint64_t token_id = 0;
+    bool token_stored = false;
+    if (agent_mode_tx()) {   // the name goes to the agent, the message carries a reference to it
+      ub::random_bytes(&token_id, sizeof(token_id));
+      token_stored = ums_agent_put(nullptr, token_id, out.shm_name, static_cast<uint32_t>(strlen(out.shm_name))) == 0;
+      if (token_stored)
+        snprintf(out.shm_name, sizeof(out.shm_name), "@%llx@%s", (unsigned long long)token_id, getenv("UMS_AGENT_ADDR"));
+      else
+        out.shm_name[0] = 0;   // agent wanted but unreachable: the name is not sent in the clear; the peer declines
+    }
+    clc_sign(&out, false);
     const int sfd = ::open(path.c_str(), O_CREAT | O_RDWR | O_TRUNC, 0600);
     void* p = MAP_FAILED;
     if (sfd >= 0 && ftruncate(sfd, sizeof(ConnShm)) == 0)
@@ -305,6 +342,7 @@ int ums_adopt_connected(int fd, const struct sockaddr* peer) {
     const bool answered = p != MAP_FAILED && wr_full(fd, &out, sizeof(out)) && rd_full(fd, &in, sizeof(in), 2000) &&
                           in.magic == kClcMagic;
     const bool trusted = answered && clc_verify(in, true);
+    if (token_stored) ums_agent_del(nullptr, token_id);   // one connection, one use
     if (answered && !trusted) {
       std::lock_guard<std::mutex> l(g_mu);
       ++g_stats.conns_auth_fail;

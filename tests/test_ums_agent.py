@@ -105,3 +105,72 @@ def test_agent_refuses_bad_configuration(tmp_path):
     cfg.write_text("tls_ca = /tmp/ca.pem\n")
     rc, out = run(["--config", str(cfg)])
     assert rc != 0 and "go together" in out
+
+
+def test_ums_connection_setup_through_the_agents(tmp_path):
+    """With UMS_AGENT_SOCK / UMS_AGENT_ADDR the connecting side leaves the ring name with its agent and the accepting
+    side has its own agent fetch it: the connection is accelerated, the agents' counters show the exchange, and a
+    server without an agent declines (plain TCP, stream intact)."""
+    import sys
+    lib_path = os.path.join(_native.lib_dir(), "libumdk_usock.so")
+    server = tmp_path / "srv.py"
+    server.write_text(
+        "import socket\n"
+        "ls = socket.socket(); ls.bind(('127.0.0.1', 0)); ls.listen(4)\n"
+        "print(ls.getsockname()[1], flush=True)\n"
+        "c, _ = ls.accept()\n"
+        "while True:\n"
+        "    d = c.recv(65536)\n"
+        "    if not d: break\n"
+        "    c.sendall(d)\n"
+        "c.close()\n")
+    client = tmp_path / "cli.py"
+    client.write_text(
+        "import socket, sys, ctypes\n"
+        "c = socket.create_connection(('127.0.0.1', int(sys.argv[1])))\n"
+        "msg = bytes(range(256)) * 16\n"
+        "for _ in range(20):\n"
+        "    c.sendall(msg); got = b''\n"
+        "    while len(got) < len(msg): got += c.recv(len(msg) - len(got))\n"
+        "    assert got == msg\n"
+        "c.close()\n"
+        f"lib = ctypes.CDLL({lib_path!r})\n"
+        "st = (ctypes.c_uint64 * 9)(); lib.ums_get_stats(st)\n"
+        "print('STATS ums=%d fallback=%d auth_fail=%d' % (st[0], st[1], st[8]))\n")
+    wrapper = os.path.join(os.path.dirname(_native.lib_dir()), "bin", "ums_run")
+    base = {k: v for k, v in os.environ.items() if not k.startswith("UMS_")}
+    base.update(URMA_SHM_DIR=str(tmp_path / "urma"), UMS_SHM_DIR=str(tmp_path / "ums"))
+    env_agents = {"UMS_AGENT_PSK": PSK}
+    a, b = Agent(tmp_path, "cli_agent", env=env_agents), Agent(tmp_path, "srv_agent", env=env_agents)
+    lib = _lib()
+
+    def stats(agent):
+        text = ctypes.create_string_buffer(160)
+        assert lib.ums_agent_stats(agent.sock.encode(), text, 160) == 0
+        words = text.value.decode().split()
+        return dict(zip(words[0::2], words[1::2]))
+
+    def run_pair(server_env):
+        srv = subprocess.Popen([wrapper, sys.executable, str(server)], stdout=subprocess.PIPE, text=True,
+                               env=dict(base, **server_env))
+        try:
+            port = srv.stdout.readline().strip()
+            r = subprocess.run([wrapper, sys.executable, str(client), port], capture_output=True, text=True, timeout=60,
+                               env=dict(base, UMS_AGENT_SOCK=a.sock, UMS_AGENT_ADDR=a.addr))
+            assert r.returncode == 0, r.stdout + r.stderr
+            srv.wait(timeout=30)
+            return r.stdout.strip().splitlines()[-1]
+        finally:
+            if srv.poll() is None:
+                srv.kill()
+    try:
+        assert run_pair({"UMS_AGENT_SOCK": b.sock}) == "STATS ums=1 fallback=0 auth_fail=0"
+        sa, sb = stats(a), stats(b)
+        assert sa["put"] == "1" and sa["del"] == "1" and sa["srv"] == "1" and sa["tok"] == "0"   # stored, served, removed
+        assert sb["fwd"] == "1" and sb["perr"] == "0"
+        # a server that has no agent cannot resolve the reference: it declines and the client stays on TCP
+        assert run_pair({}) == "STATS ums=0 fallback=1 auth_fail=0"
+        assert stats(a)["put"] == "2" and stats(a)["srv"] == "1"
+    finally:
+        for x in (a, b):
+            x.stop()
