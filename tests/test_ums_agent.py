@@ -174,3 +174,23 @@ def test_ums_connection_setup_through_the_agents(tmp_path):
     finally:
         for x in (a, b):
             x.stop()
+
+
+def test_sample_configuration_parses(tmp_path):
+    """The sample configuration shipped beside the unit file uses only keys the daemon knows (it stops at the missing
+    certificate files, not at the parser)."""
+    sample = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "ums_agent",
+                          "ums_agent.conf")
+    text = open(sample).read().replace("/run/umdk/ums_agent.sock", str(tmp_path / "s.sock")).replace("7471", "0")
+    cfg = tmp_path / "sample.conf"
+    cfg.write_text(text)
+    env = {k: v for k, v in os.environ.items() if not k.startswith("UMS_AGENT_")}
+    p = subprocess.Popen([BIN, "--config", str(cfg), "--ip", "127.0.0.1"], stdout=subprocess.PIPE,
+                         stderr=subprocess.STDOUT, text=True, env=env)
+    line = p.stdout.readline()
+    try:
+        assert "listening on 127.0.0.1:" in line and "certificates" in line, line
+    finally:
+        p.send_signal(signal.SIGTERM)
+        p.communicate(timeout=10)
+    assert p.returncode == 0
