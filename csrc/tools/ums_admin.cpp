@@ -1,6 +1,7 @@
 // ums_admin: shows the accelerated listeners and connections of the user-space UMS sockets on this host.
 //
 //   ums_admin show [directory]      default directory: $UMS_SHM_DIR or /dev/shm/ums_<uid>
+//   ums_admin agent [socket]        counters of the token agent (default socket: $UMS_AGENT_SOCK)
 //
 // Every accelerated listener leaves a marker file and every accelerated connection one shared-memory file with two
 // byte rings; the tool maps the rings read-only and prints, per direction, the bytes produced and consumed so far, what
@@ -17,11 +18,38 @@
 
 #include <string>
 
+#include "ums_agent_proto.h"
 #include "ums_shm.h"
 
+// Prints the agent's one-line report as one counter per line.
+static int show_agent(const char* sock) {
+  char text[UMS_AGENT_MAX_VALUE + 1];
+  const int rc = ums_agent_stats(sock, text, sizeof(text));
+  if (rc != 0) {
+    fprintf(stderr, "ums_admin: the agent does not answer (%d)\n", rc);
+    return 1;
+  }
+  static const char* const names[][2] = {
+      {"tok", "tokens stored"},          {"put", "tokens published"},       {"del", "tokens removed"},
+      {"get", "local lookups"},          {"fwd", "lookups sent to a peer"}, {"srv", "lookups served to peers"},
+      {"miss", "unknown token ids"},     {"perr", "peer failures"},         {"tls", "TLS accepted/refused"},
+      {"pool", "pool open/dials/reuses"}};
+  char* save = nullptr;
+  for (char* k = strtok_r(text, " ", &save); k; k = strtok_r(nullptr, " ", &save)) {
+    const char* v = strtok_r(nullptr, " ", &save);
+    if (!v) break;
+    const char* label = k;
+    for (auto& n : names)
+      if (!strcmp(n[0], k)) label = n[1];
+    printf("%-26s %s\n", label, v);
+  }
+  return 0;
+}
+
 int main(int argc, char** argv) {
+  if (argc >= 2 && !strcmp(argv[1], "agent")) return show_agent(argc >= 3 ? argv[2] : nullptr);
   if (argc < 2 || strcmp(argv[1], "show") != 0) {
-    fprintf(stderr, "usage: ums_admin show [directory]\n");
+    fprintf(stderr, "usage: ums_admin show [directory] | ums_admin agent [socket]\n");
     return 2;
   }
   std::string dir;

@@ -77,6 +77,11 @@ def test_two_agents_exchange_tokens_over_tls(tmp_path):
         sb = dict(zip(text.value.decode().split()[0::2], text.value.decode().split()[1::2]))
         assert sb["fwd"] == "6" and sb["perr"] == "1" and sb["pool"].startswith("1/1/")   # one dial, then reuse
         assert lib.ums_agent_get(b"/nonexistent/agent.sock", None, 1, text, ctypes.byref(ctypes.c_uint32(128))) == -1
+        admin = subprocess.run([os.path.join(_native.lib_dir(), "bin", "ums_admin"), "agent", a.sock],
+                               capture_output=True, text=True, timeout=10)
+        assert admin.returncode == 0 and "tokens stored" in admin.stdout and "lookups served to peers" in admin.stdout
+        rows = dict(line.rsplit(None, 1) for line in admin.stdout.strip().splitlines())
+        assert rows["lookups served to peers"] == "5" and rows["TLS accepted/refused"] == "1/1"
     finally:
         results = [x.stop() for x in (a, b, c)]
     for rc, out in results:
