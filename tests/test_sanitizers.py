@@ -31,6 +31,8 @@ def test_address_and_leak_sanitizer_clean(tmp_path):
     assert rc == 0 and "umq_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
     rc, out = _run(outs["tool_urpc_perftest"], ["--selftest", "--iters", "300"], tmp_path)
     assert rc == 0 and "urpc_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
+    rc, out = _run(outs["tool_urpc_perftest"], ["--iters", "600", "--queues", "3"], tmp_path)   # three queue pairs
+    assert rc == 0 and "urpc_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
 
 
 @needs_gxx
@@ -39,3 +41,5 @@ def test_thread_sanitizer_clean(tmp_path):
     for _ in range(2):   # the teardown race this guards against showed up in about one run out of three
         rc, out = _run(outs["tool_umq_perftest"], ["--iters", "300", "--flow-control"], tmp_path)
         assert rc == 0 and "umq_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
+    rc, out = _run(outs["tool_urpc_perftest"], ["--iters", "300", "--queues", "3"], tmp_path)
+    assert rc == 0 and "urpc_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
