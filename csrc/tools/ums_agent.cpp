@@ -354,6 +354,9 @@ void handle_local(Agent* ag, const ums_agent_msg_t& m, ums_agent_msg_t* r) {
         r->status = static_cast<uint32_t>(ag->table.get(m.token_id, r->value, &r->len));
         ++g_st.gets_local;
       } else {
+        // The forward runs inside the main loop: a peer that does not answer holds up the other local requests for
+        // at most peer_timeout_ms (connect, handshake and reply each have that limit). Inbound agent connections are
+        // served by their own threads, so two agents that ask each other at the same time do not wait on one another.
         ums_agent_msg_t q = m;
         const int st = ag->pool.fetch(peer, &q);
         ++g_st.gets_forwarded;
