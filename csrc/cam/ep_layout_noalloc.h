@@ -17,11 +17,19 @@
 // Rules for callers:
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device, with
 //     that device current). Make that first call during start-up, before any stream capture begins.
+//   * The array itself becomes resident when the CUDA driver loads this library's module on a device. With CUDA's
+//     default lazy module loading that happens at the first call of this entry point, or at any earlier kernel of
+//     this library on that device - not at dlopen time. A process that later gives away all free device memory
+//     must therefore make that first call (or run any other kernel of the library) BEFORE it does so; after the
+//     module is loaded, calls neither take nor return device memory.
+//   * The address is cached per device ordinal. cudaDeviceReset destroys the context the address belongs to; a
+//     process that resets a device must not call this entry point on that device afterwards.
 //   * All calls on one device share the array. Two calls whose kernels may overlap on the GPU (different streams
 //     without an ordering between them) race on it; keep calls on one stream or order them with events.
 //   * Nothing in the array has to survive between calls. The barrier words are reset on the caller's stream at the
 //     start of every call; the histogram part is fully rewritten by the kernel before it is read.
-//   * No cudaMalloc, cudaFree or allocating library routine is called, on the first call or later.
+//   * The entry point itself calls no cudaMalloc, cudaFree or allocating library routine, on the first call or
+//     later; the only memory event is the driver's one-time module load described above.
 #pragma once
 #include <stdint.h>
 

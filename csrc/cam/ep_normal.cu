@@ -904,7 +904,8 @@ UMDK_API long long umdk_ep_normal_heap_bytes(int R, int E, int K, int H, int cap
   return (long long)ep_normal_offsets(layout_geom(g)).total;
 }
 
-// scratch: int32[(ceil(T/32)) * (E + R)]; bar: uint32[2] zero-initialised once.
+// scratch: int32[(ceil(T/32)) * (E + R)]; bar: uint32[2], reset on the caller's stream at the start of every call
+// that uses it (an earlier call cut short by a barrier time-out may have left a partial arrival count).
 UMDK_API int umdk_ep_layout(const int64_t* topk_idx, int T, int K, int E, int R, int* num_per_expert,
                             int* num_per_rank, uint8_t* in_rank, int* send_idx, int* rank_slot, int* scratch,
                             uint32_t* bar, int* status, void* stream) {
@@ -937,6 +938,7 @@ UMDK_API int umdk_ep_layout(const int64_t* topk_idx, int T, int K, int E, int R,
   if (smem > 48 * 1024) {
     UMDK_CUDA_CHECK(cudaFuncSetAttribute(ep_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
+  UMDK_CUDA_CHECK(cudaMemsetAsync(bar, 0, 2 * sizeof(uint32_t), s));
   ep_layout_kernel<<<grid, kLayoutWarps * 32, smem, s>>>(topk_idx, T, K, E, R, num_per_expert, num_per_rank, in_rank,
                                                          send_idx, rank_slot, scratch, bar, status);
   UMDK_CUDA_CHECK(cudaGetLastError());

@@ -40,10 +40,17 @@ def _call_noalloc(lib, idx, E, R):
     return rc, out, status
 
 
-def test_noalloc_layout_matches_regular_entry_point_twice():
-    from umdk_b200.ops.ep import layout
+def _load():
+    from umdk_b200 import _native
+    _native.cam()          # builds the library on a fresh checkout; the symbol itself is called through plain ctypes
     lib = ctypes.CDLL(LIB)
     lib.umdk_ep_layout_noalloc.restype = ctypes.c_int
+    return lib
+
+
+def test_noalloc_layout_matches_regular_entry_point_twice():
+    from umdk_b200.ops.ep import layout
+    lib = _load()
     for call, (T, K, E, R) in enumerate([(4096, 8, 256, 8), (777, 4, 64, 4)]):
         idx = _topk(T, K, E, seed=call).cuda()
         rc, got, status = _call_noalloc(lib, idx, E, R)
@@ -58,9 +65,36 @@ def test_noalloc_layout_matches_regular_entry_point_twice():
         assert torch.equal(got["rslot"], want.rank_slot)
 
 
+def test_noalloc_layout_takes_no_device_memory_after_its_first_call():
+    """Free device memory as the driver reports it is the same before and after the second and third call: the
+    claim a caller whose pool owns every free byte relies on. (The first call may load the module.)"""
+    lib = _load()
+    idx = _topk(2048, 8, 128, seed=11).cuda()
+    rc, _, _ = _call_noalloc(lib, idx, 128, 8)
+    assert rc == 0
+    torch.cuda.synchronize()
+    dev = idx.device
+    bufs = dict(npe=torch.empty(128, dtype=torch.int32, device=dev), npr=torch.empty(8, dtype=torch.int32, device=dev),
+                inr=torch.empty(2048, 8, dtype=torch.uint8, device=dev),
+                sidx=torch.empty(2048, 8, dtype=torch.int32, device=dev),
+                rslot=torch.empty(2048, 8, dtype=torch.int32, device=dev))
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(2):
+        rc = lib.umdk_ep_layout_noalloc(p(idx), 2048, 8, 128, 8, p(bufs["npe"]), p(bufs["npr"]), p(bufs["inr"]),
+                                        p(bufs["sidx"]), p(bufs["rslot"]), p(status), stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        free1, _ = torch.cuda.mem_get_info()
+        assert free1 == free0
+    assert status.tolist()[0] == 0 and int(bufs["npe"].sum()) == int((idx >= 0).sum())
+
+
 def test_noalloc_layout_rejects_sizes_beyond_its_scratch():
-    lib = ctypes.CDLL(LIB)
-    lib.umdk_ep_layout_noalloc.restype = ctypes.c_int
+    lib = _load()
     idx = _topk(64, 2, 16, seed=3).cuda()
     null = ctypes.c_void_p(0)
     # token count above the limit: refused before anything is launched (outputs are never touched)
