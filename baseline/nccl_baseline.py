@@ -1,22 +1,33 @@
-"""Plain PyTorch + NCCL (+cuBLAS) statements of the benchmarked pipelines, used as the comparison baseline.
+"""Plain PyTorch + NCCL (+ library GEMM) statements of the benchmarked pipelines: the comparison baseline.
 
-The reference project has no CUDA path to run on this hardware, so the baseline reproduces its *algorithm split* with
-library collectives: layout on the GPU -> all_to_all_single of the counts -> separate quantisation kernel ->
-all_to_all_single of tokens and scales -> expert compute -> all_to_all_single back -> weighted index_add.
+The reference project has no CUDA path that runs on this hardware, so the baseline reproduces its *algorithm split*
+the way a careful user of library collectives would write it, with none of this package's kernels:
+
+* normal mode (prefill): every token travels once per destination RANK (not once per expert); all index work and the
+  split sizes come from a handle prepared once per routing (outside the timed call, like the product's layout); the
+  timed dispatch is gather -> fp8 1x128 quantisation (torch ops) -> ONE all_to_all_single of packed rows -> expand
+  into expert-major order; the timed combine is weighted pre-reduction per arrival -> all_to_all_single back ->
+  index_add over the source ranks.
+* low-latency (decode) layer: static shapes, no host synchronisation at all: all_gather of the quantised tokens and
+  their routing -> sort (token, k) pairs by local expert on the device -> ONE grouped GEMM per projection
+  (``GroupedFfn``) -> weighted pre-reduction -> reduce_scatter (the sum over expert ranks happens in NCCL / NVLS).
+* ``bare_all_to_all`` times the collective alone on the same bytes: the wire-only bound of the library path.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import Optional, Tuple
 
 import torch
 import torch.distributed as dist
+
+FP8 = torch.float8_e4m3fn
 
 
 def quant_1x128(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     T, H = x.shape
     xf = x.float().view(T, H // 128, 128)
     amax = xf.abs().amax(dim=-1).clamp_min(1e-4)
-    q = (xf * (448.0 / amax).unsqueeze(-1)).to(torch.float8_e4m3fn).view(T, H)
+    q = (xf * (448.0 / amax).unsqueeze(-1)).to(FP8).view(T, H)
     return q, amax / 448.0
 
 
@@ -25,66 +36,277 @@ def dequant_1x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     return (q.float().view(T, H // 128, 128) * s.unsqueeze(-1)).view(T, H)
 
 
+def quant_rowwise(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[M, K] -> (fp8 e4m3 [M, K], fp32 scale [M]) with one scale per row."""
+    amax = x.abs().amax(dim=-1, keepdim=True).float().clamp_min(1e-4)
+    q = (x.float() * (448.0 / amax)).to(FP8)
+    return q, (amax / 448.0).squeeze(-1)
+
+
+def _world(group):
+    return (dist.get_world_size(group), dist.get_rank(group)) if dist.is_initialized() else (1, 0)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# normal mode: dispatch / combine over all_to_all_single
+# ----------------------------------------------------------------------------------------------------------------
 class NcclEp:
-    """Dispatch / combine with NCCL all_to_all_single. One row per (token, k), rows sorted by destination expert."""
+    """Dispatch / combine with NCCL all_to_all_single, one row per (token, destination rank)."""
 
     def __init__(self, group, num_experts: int):
         self.group = group
-        self.R = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        self.R, self.rank = _world(group)
         self.E = num_experts
         self.el = num_experts // self.R
 
-    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, quant: bool):
+    def prepare(self, topk_idx: torch.Tensor) -> dict:
+        """Everything that depends only on the routing: send order, split sizes (host lists), the routing metadata
+        of the rows this rank will receive and the permutation that puts them in expert-major order. Contains the
+        host synchronisations; the timed dispatch / combine have none."""
         T, K = topk_idx.shape
-        flat = topk_idx.reshape(-1)
-        order = torch.argsort(flat, stable=True)          # rows by expert, stable in (t, k)
-        tok = order // K
-        counts = torch.bincount(flat, minlength=self.E)
-        send_counts = counts.view(self.R, self.el)
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        in_splits = send_counts.sum(1).tolist()           # host sync, as in the reference's .item() calls
-        out_splits = recv_counts.sum(1).tolist()
-        rows = x[tok]
+        R, el, dev = self.R, self.el, topk_idx.device
+        dst = torch.where(topk_idx >= 0, torch.div(topk_idx, el, rounding_mode="floor"), R)      # [T, K]
+        in_rank = torch.zeros(T, R + 1, dtype=torch.bool, device=dev).scatter_(1, dst, True)[:, :R]
+        r_of, t_of = torch.nonzero(in_rank.t(), as_tuple=True)          # sorted by rank, then token
+        in_splits = in_rank.sum(0).to(torch.int64)
+        out_splits = torch.empty_like(in_splits)
+        if R > 1:
+            dist.all_to_all_single(out_splits, in_splits, group=self.group)
+        else:
+            out_splits.copy_(in_splits)
+        in_l, out_l = in_splits.tolist(), out_splits.tolist()
+        n_arr = sum(out_l)
+        meta = topk_idx[t_of].to(torch.int32).contiguous()              # routing of every row sent
+        rmeta = torch.empty(n_arr, K, dtype=torch.int32, device=dev)
+        if R > 1:
+            dist.all_to_all_single(rmeta, meta, out_l, in_l, group=self.group)
+        else:
+            rmeta.copy_(meta)
+        loc = rmeta.to(torch.int64) - self.rank * el
+        valid = (rmeta >= 0) & (loc >= 0) & (loc < el)
+        key = torch.where(valid, loc, el).reshape(-1)
+        order = torch.argsort(key, stable=True)
+        n_rows = int(valid.sum().item())
+        order = order[:n_rows]
+        return dict(T=T, K=K, t_of=t_of, in_l=in_l, out_l=out_l, n_arr=n_arr, n_rows=n_rows,
+                    arr_of_row=torch.div(order, K, rounding_mode="floor"), k_of_row=order % K,
+                    counts=torch.bincount(key, minlength=el + 1)[:el])
+
+    def dispatch(self, x: torch.Tensor, h: dict, quant: bool = True):
+        """-> expert-major rows (fp8 [n, H], fp32 scales [n, H/128]) or bf16 [n, H]."""
+        H = x.shape[1]
+        rows = x[h["t_of"]]
         if quant:
             q, s = quant_1x128(rows)
-            recv_q = torch.empty(sum(out_splits), x.shape[1], dtype=torch.uint8, device=x.device)
-            dist.all_to_all_single(recv_q, q.view(torch.uint8), out_splits, in_splits, group=self.group)
-            recv_s = torch.empty(sum(out_splits), s.shape[1], dtype=torch.float32, device=x.device)
-            dist.all_to_all_single(recv_s, s, out_splits, in_splits, group=self.group)
-            recv = (recv_q.view(torch.float8_e4m3fn), recv_s)
+            send = torch.cat((q.view(torch.uint8), s.view(torch.uint8).view(-1, (H // 128) * 4)), dim=1)
         else:
-            r = torch.empty(sum(out_splits), x.shape[1], dtype=x.dtype, device=x.device)
-            dist.all_to_all_single(r, rows, out_splits, in_splits, group=self.group)
-            recv = r
-        return recv, dict(order=order, in_splits=in_splits, out_splits=out_splits, recv_counts=recv_counts, T=T, K=K)
+            send = rows.view(torch.uint8).view(-1, 2 * H)
+        recv = torch.empty(h["n_arr"], send.shape[1], dtype=torch.uint8, device=x.device)
+        if self.R > 1:
+            dist.all_to_all_single(recv, send.contiguous(), h["out_l"], h["in_l"], group=self.group)
+        else:
+            recv.copy_(send)
+        exp = recv[h["arr_of_row"]]
+        if quant:
+            return exp[:, :H].contiguous().view(FP8), exp[:, H:].contiguous().view(torch.float32)
+        return exp.view(torch.bfloat16)
 
-    def combine(self, y: torch.Tensor, h: dict, topk_w: torch.Tensor) -> torch.Tensor:
-        back = torch.empty(sum(h["in_splits"]), y.shape[1], dtype=y.dtype, device=y.device)
-        dist.all_to_all_single(back, y, h["in_splits"], h["out_splits"], group=self.group)
-        order = h["order"]
-        tok, k = order // h["K"], order % h["K"]
-        out = torch.zeros(h["T"], y.shape[1], dtype=torch.float32, device=y.device)
-        out.index_add_(0, tok, back.float() * topk_w[tok, k].unsqueeze(1))
+    def combine(self, y: torch.Tensor, h: dict, topk_w_recv: Optional[torch.Tensor], topk_w: torch.Tensor):
+        """y [n, H] bf16 expert-major. Weighted pre-reduction per arrival needs the weights of the received rows;
+        without them (``topk_w_recv`` None) rows return unweighted, one per (token, rank), and the owner applies the
+        mean weight - for timing only. With identity experts the benchmark passes the exchanged weights."""
+        H = y.shape[1]
+        acc = torch.zeros(h["n_arr"], H, dtype=torch.float32, device=y.device)
+        wrow = topk_w_recv[h["arr_of_row"], h["k_of_row"]].unsqueeze(1) if topk_w_recv is not None else 1.0
+        acc.index_add_(0, h["arr_of_row"], y.float() * wrow)
+        send = acc.to(torch.bfloat16)
+        back = torch.empty(len(h["t_of"]), H, dtype=torch.bfloat16, device=y.device)
+        if self.R > 1:
+            dist.all_to_all_single(back, send, h["in_l"], h["out_l"], group=self.group)
+        else:
+            back.copy_(send)
+        out = torch.zeros(h["T"], H, dtype=torch.float32, device=y.device)
+        out.index_add_(0, h["t_of"], back.float())
         return out.to(torch.bfloat16)
 
+    def exchange_weights(self, topk_w: torch.Tensor, h: dict) -> torch.Tensor:
+        """Routing weights of the rows this rank receives (part of the handle; not timed)."""
+        send = topk_w[h["t_of"]].float().contiguous()
+        recv = torch.empty(h["n_arr"], h["K"], dtype=torch.float32, device=topk_w.device)
+        if self.R > 1:
+            dist.all_to_all_single(recv, send, h["out_l"], h["in_l"], group=self.group)
+        else:
+            recv.copy_(send)
+        return recv
 
-def expert_ffn_bf16(recv_q, recv_s, recv_counts, w1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
-    """Per-expert SwiGLU FFN with cuBLAS bf16 GEMMs on dequantised inputs. Rows arrive grouped by source rank, then
-    by local expert; w1 [el, 2F, H], w2 [el, H, F] are bf16 copies of the fp8 weights."""
-    x = dequant_1x128(recv_q, recv_s).to(torch.bfloat16)
-    R, el = recv_counts.shape
-    cnt = recv_counts.tolist()
-    y = torch.empty(x.shape[0], w2.shape[1], dtype=torch.bfloat16, device=x.device)
-    F = w1.shape[1] // 2
-    pos = 0
-    for s in range(R):
-        for e in range(el):
-            c = cnt[s][e]
-            if c:
-                h1 = x[pos:pos + c] @ w1[e].t()
-                hh = torch.nn.functional.silu(h1[:, :F]) * h1[:, F:]
-                y[pos:pos + c] = hh @ w2[e].t()
-                pos += c
-    return y
+    def bare_all_to_all(self, h: dict, row_bytes: int, reverse: bool = False):
+        """Returns a closure that runs all_to_all_single alone on buffers of the dispatch (or combine) size."""
+        n_in, n_out = len(h["t_of"]), h["n_arr"]
+        a = torch.empty(n_in, row_bytes, dtype=torch.uint8, device="cuda")
+        b = torch.empty(n_out, row_bytes, dtype=torch.uint8, device="cuda")
+        if self.R == 1:
+            return (lambda: a.copy_(b)) if reverse else (lambda: b.copy_(a))
+        if reverse:
+            return lambda: dist.all_to_all_single(a, b, h["in_l"], h["out_l"], group=self.group)
+        return lambda: dist.all_to_all_single(b, a, h["out_l"], h["in_l"], group=self.group)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# grouped SwiGLU FFN with library GEMMs
+# ----------------------------------------------------------------------------------------------------------------
+class GroupedFfn:
+    """SwiGLU FFN over rows sorted by group as ONE grouped library GEMM per projection; group sizes stay on the
+    device (``offs``), so there is no host synchronisation and no Python loop over experts.
+
+    Back ends, first that works on this GPU / torch build (``backend`` names it):
+      fp8_rowwise   torch._scaled_grouped_mm on fp8 e4m3 weights re-quantised with one scale per output row and
+                    activations quantised per token (same bytes per weight as the product's fp8 format)
+      bf16_grouped  torch._grouped_mm on bf16 copies of the weights (twice the weight bytes)
+      bf16_bmm      rows scattered into [G, cap, K] and torch.bmm on bf16 copies, cap = padded group size
+    Weights arrive as the product stores them: fp8 e4m3 with 128x128 block scales, w1 [G, 2F, H], w2 [G, H, F].
+    """
+
+    def __init__(self, w1q, w1s, w2q, w2s, backend: Optional[str] = None, bmm_cap: int = 0):
+        from umdk_b200.ops.reference import dequant_fp8_128x128
+        self.G, F2, self.H = w1q.shape
+        self.F = F2 // 2
+        self.bmm_cap = bmm_cap
+        self.backend = backend or self.pick_backend()
+        dev = w1q.device
+        if self.backend == "fp8_rowwise":
+            self.w1 = torch.empty(self.G, F2, self.H, dtype=torch.uint8, device=dev).view(FP8)
+            self.w2 = torch.empty(self.G, self.H, self.F, dtype=torch.uint8, device=dev).view(FP8)
+            self.s1 = torch.empty(self.G, F2, dtype=torch.float32, device=dev)
+            self.s2 = torch.empty(self.G, self.H, dtype=torch.float32, device=dev)
+            for g in range(self.G):
+                self.w1[g], self.s1[g] = quant_rowwise(dequant_fp8_128x128(w1q[g], w1s[g]))
+                self.w2[g], self.s2[g] = quant_rowwise(dequant_fp8_128x128(w2q[g], w2s[g]))
+        else:
+            self.w1 = torch.empty(self.G, F2, self.H, dtype=torch.bfloat16, device=dev)
+            self.w2 = torch.empty(self.G, self.H, self.F, dtype=torch.bfloat16, device=dev)
+            for g in range(self.G):
+                self.w1[g] = dequant_fp8_128x128(w1q[g], w1s[g]).to(torch.bfloat16)
+                self.w2[g] = dequant_fp8_128x128(w2q[g], w2s[g]).to(torch.bfloat16)
+
+    _picked: Optional[str] = None
+
+    @classmethod
+    def pick_backend(cls) -> str:
+        """Tries each back end once on a tiny problem against a per-group fp32 loop."""
+        if cls._picked is not None:
+            return cls._picked
+        from umdk_b200.models.dsv3_decoder import _quant_experts
+        g = torch.Generator(device="cuda").manual_seed(7)
+        G, F, H = 3, 128, 256
+        w1q, w1s = _quant_experts(G, 2 * F, H, "cuda", g)
+        w2q, w2s = _quant_experts(G, H, F, "cuda", g)
+        x = torch.randn(48, H, device="cuda", generator=g).to(torch.bfloat16)
+        offs = torch.tensor([16, 16, 40], dtype=torch.int32, device="cuda")    # an empty group, an unused tail
+        why = {}
+        for name in ("fp8_rowwise", "bf16_grouped", "bf16_bmm"):
+            try:
+                ffn = cls(w1q, w1s, w2q, w2s, backend=name, bmm_cap=32)
+                y = ffn(x, offs)[:40].float()
+                ref = ffn.loop_reference(x, offs)[:40]
+                torch.cuda.synchronize()
+                err = float((y - ref).abs().sum() / ref.abs().sum())
+                if not (err < 0.06):
+                    raise RuntimeError(f"mean relative error {err:.3f}")
+                cls._picked = name
+                cls.why_not = why
+                return name
+            except Exception as e:   # noqa: BLE001 - any failure moves on to the next back end
+                why[name] = f"{type(e).__name__}: {str(e)[:160]}"
+        raise RuntimeError(f"no grouped GEMM back end works here: {why}")
+
+    def loop_reference(self, x, offs):
+        from umdk_b200.ops.reference import dequant_fp8_128x128  # noqa: F401
+        o = [0] + offs.tolist()
+        y = torch.zeros(x.shape[0], self.H, dtype=torch.float32, device=x.device)
+        for g in range(self.G):
+            a, b = o[g], o[g + 1]
+            if b > a:
+                w1 = self.w1[g].float() * (self.s1[g].unsqueeze(1) if self.backend == "fp8_rowwise" else 1.0)
+                w2 = self.w2[g].float() * (self.s2[g].unsqueeze(1) if self.backend == "fp8_rowwise" else 1.0)
+                h1 = x[a:b].float() @ w1.t()
+                y[a:b] = (torch.nn.functional.silu(h1[:, :self.F]) * h1[:, self.F:]) @ w2.t()
+        return y
+
+    def _mm(self, x, w, s, offs):
+        if self.backend == "fp8_rowwise":
+            xq, xs = quant_rowwise(x)
+            return torch._scaled_grouped_mm(xq, w.transpose(-2, -1), xs, s, offs=offs, out_dtype=torch.bfloat16,
+                                            use_fast_accum=True)
+        if self.backend == "bf16_grouped":
+            return torch._grouped_mm(x, w.transpose(-2, -1), offs=offs, out_dtype=torch.bfloat16)
+        # padded bmm: row i of group g sits at [g, i - start(g)]
+        M, cap = x.shape[0], self.bmm_cap
+        start = torch.cat((offs.new_zeros(1), offs[:-1])).to(torch.int64)
+        rows = torch.arange(M, device=x.device)
+        grp = torch.searchsorted(offs.to(torch.int64), rows, right=True).clamp_max(self.G - 1)
+        pos = (rows - start[grp]).clamp_(0, cap - 1)
+        buf = torch.zeros(self.G, cap, x.shape[1], dtype=x.dtype, device=x.device)
+        buf[grp, pos] = x
+        return torch.bmm(buf, w.transpose(-2, -1))[grp, pos]
+
+    def __call__(self, x: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
+        """x [M, H] bf16 rows sorted by group, offs [G] int32 cumulative group ends -> [M, H] bf16 (rows past
+        offs[-1] are undefined)."""
+        h1 = self._mm(x, self.w1, getattr(self, "s1", None), offs)
+        h = torch.nn.functional.silu(h1[:, :self.F].float()) * h1[:, self.F:].float()
+        return self._mm(h.to(torch.bfloat16), self.w2, getattr(self, "s2", None), offs)
+
+
+class NcclLowLatencyMoe:
+    """Decode-sized MoE layer on library calls only: all_gather dispatch, grouped library GEMMs, reduce_scatter
+    combine. Static shapes, no host synchronisation, capturable like the product path."""
+
+    def __init__(self, group, num_experts: int, top_k: int, ffn: GroupedFfn, shared_first: bool):
+        """``shared_first``: group 0 of ``ffn`` is the (replicated) shared expert, run on this rank's own tokens;
+        groups 1.. are the routed local experts."""
+        self.group = group
+        self.R, self.rank = _world(group)
+        self.el = num_experts // self.R
+        self.K = top_k
+        self.ffn = ffn
+        self.shared_first = shared_first
+        assert ffn.G == self.el + (1 if shared_first else 0)
+
+    def __call__(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor):
+        """x [T, H] bf16, topk_idx [T, K] int64, topk_w [T, K] fp32 -> (combine_x [T, H] bf16, share_out or None)."""
+        T, H = x.shape
+        R, el, K, dev = self.R, self.el, self.K, x.device
+        if R > 1:
+            xa = torch.empty(R * T, H, dtype=x.dtype, device=dev)
+            dist.all_gather_into_tensor(xa, x, group=self.group)
+            meta = torch.cat((topk_idx.to(torch.int32), topk_w.float().view(torch.int32)), dim=1).contiguous()
+            ma = torch.empty(R * T, 2 * K, dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(ma, meta, group=self.group)
+            idx_a, w_a = ma[:, :K].to(torch.int64), ma[:, K:].contiguous().view(torch.float32)
+        else:
+            xa, idx_a, w_a = x, topk_idx, topk_w.float()
+        loc = idx_a - self.rank * el
+        valid = (idx_a >= 0) & (loc >= 0) & (loc < el)
+        key = torch.where(valid, loc, el).reshape(-1)
+        order = torch.argsort(key, stable=True)
+        tok = torch.div(order, K, rounding_mode="floor")
+        counts = torch.bincount(key, minlength=el + 1)[:el]
+        wrow = torch.where(valid, w_a, 0.0).reshape(-1)[order]
+        rows = xa[tok]
+        if self.shared_first:
+            rows = torch.cat((x, rows))
+            counts = torch.cat((counts.new_full((1,), T), counts))
+        offs = torch.cumsum(counts, 0).to(torch.int32)
+        y = self.ffn(rows, offs)
+        share = None
+        if self.shared_first:
+            share, y = y[:T], y[T:]
+        live = (torch.arange(y.shape[0], device=dev) < (offs[-1] - (T if self.shared_first else 0))).unsqueeze(1)
+        contrib = torch.zeros(R * T, H, dtype=torch.float32, device=dev)
+        contrib.index_add_(0, tok, torch.where(live, y.float() * wrow.unsqueeze(1), 0.0))
+        if R > 1:
+            out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+            dist.reduce_scatter_tensor(out, contrib.to(torch.bfloat16), group=self.group)
+        else:
+            out = contrib.to(torch.bfloat16)
+        return out, share

@@ -69,9 +69,20 @@ def timed(fn, iters, warmup, world):
     return float(t.item()) * 1e-3  # seconds
 
 
+_records = []
+_quiet = False
+
+
 def emit(rank, rec):
-    if rank == 0:
+    _records.append(rec)
+    if rank == 0 and not _quiet:
         print(json.dumps(rec), flush=True)
+
+
+def _begin(quiet):
+    global _quiet
+    _quiet = quiet
+    _records.clear()
 
 
 def routing(T, E, K, seed):
@@ -82,8 +93,11 @@ def routing(T, E, K, seed):
     return idx.to(torch.int64).contiguous(), (w / w.sum(-1, keepdim=True)).float().contiguous()
 
 
-def bench_normal(rank, world, a):
+def bench_normal(rank, world, a, quiet=False):
+    """Returns the list of records it emitted (every rank gets the same list; rank 0 prints unless ``quiet``)."""
     from baseline.nccl_baseline import NcclEp
+    _begin(quiet)
+    brief = getattr(a, "brief", False)
     from umdk_b200.ops.ep import EpNormal
     from umdk_b200.parallel.symm import SymmetricHeap
     T, H, E, K = a.tokens, 7168, 256, 8
@@ -104,17 +118,19 @@ def bench_normal(rank, world, a):
     t_disp = timed(lambda: st.dispatch(x, idx, w, lay=lay, quant=True, out=out), a.iters, a.warmup, world)
     t_comb = timed(lambda: st.combine(y, out, out=res), a.iters, a.warmup, world)
     st.check("normal")
-    # diagnose mode: how long CTA 0 of this rank waited for each source rank's data (max over ranks per source)
-    st.diagnose = True
-    st.dispatch(x, idx, w, lay=lay, quant=True, out=out)
-    st.combine(y, out, out=res)
-    torch.cuda.synchronize()
-    wd, wc = st.wait_times_us()
-    st.diagnose = False
-    waits = torch.stack((wd, wc)).cuda()
-    if world > 1:
-        dist.all_reduce(waits, op=dist.ReduceOp.MAX)
-    waits = waits.cpu()
+    waits = None
+    if not brief:
+        # diagnose mode: how long CTA 0 of this rank waited for each source rank's data (max over ranks per source)
+        st.diagnose = True
+        st.dispatch(x, idx, w, lay=lay, quant=True, out=out)
+        st.combine(y, out, out=res)
+        torch.cuda.synchronize()
+        wd, wc = st.wait_times_us()
+        st.diagnose = False
+        waits = torch.stack((wd, wc)).cuda()
+        if world > 1:
+            dist.all_reduce(waits, op=dist.ReduceOp.MAX)
+        waits = waits.cpu()
     row_b = H + H // 32
     wire_d = arrivals * row_b * remote_frac          # each token crosses once per destination rank
     wire_c = arrivals * H * 2 * remote_frac
@@ -128,27 +144,37 @@ def bench_normal(rank, world, a):
     emit(rank, dict(common, op="combine(bf16, top-8 weighted)", us=t_comb * 1e6,
                     recv_GBps=n * H * 2 / t_comb / 1e9, nvlink_GBps=wire_c / t_comb / 1e9,
                     frac_of_nvlink_roofline=(wire_c / (NVLINK_GBS * 1e9)) / t_comb if world > 1 else None))
-    emit(rank, dict(common, op="diagnose: wait per source rank (us, max over ranks)",
-                    dispatch=[round(float(v), 1) for v in waits[0]], combine=[round(float(v), 1) for v in waits[1]]))
-    if world > 1:
-        base = NcclEp(None, E)
-        recv, h = base.dispatch(x, idx, True)
-        yb = torch.randn(recv[0].shape[0], H, device="cuda").to(torch.bfloat16)
-        tb_d = timed(lambda: base.dispatch(x, idx, True), a.iters, a.warmup, world)
-        tb_c = timed(lambda: base.combine(yb, h, w), a.iters, a.warmup, world)
-        emit(rank, dict(common, impl="nccl_baseline", op="dispatch(fp8 1x128)", us=tb_d * 1e6,
-                        recv_GBps=recv[0].shape[0] * row_b / tb_d / 1e9, speedup_of_umdk=tb_d / t_disp))
-        emit(rank, dict(common, impl="nccl_baseline", op="combine(bf16, top-8 weighted)", us=tb_c * 1e6,
-                        speedup_of_umdk=tb_c / t_comb))
+    if waits is not None:
+        emit(rank, dict(common, op="diagnose: wait per source rank (us, max over ranks)",
+                        dispatch=[round(float(v), 1) for v in waits[0]], combine=[round(float(v), 1) for v in waits[1]]))
+    # baseline: one row per (token, rank) over all_to_all_single, index work and split sizes prepared outside the
+    # timed call (as the product's layout is); plus the collective alone on the same bytes
+    base = NcclEp(None, E)
+    h = base.prepare(idx)
+    wrecv = base.exchange_weights(w, h)
+    rq, _ = base.dispatch(x, h, True)
+    yb = torch.randn(rq.shape[0], H, device="cuda").to(torch.bfloat16)
+    tb_d = timed(lambda: base.dispatch(x, h, True), a.iters, a.warmup, world)
+    tb_c = timed(lambda: base.combine(yb, h, wrecv, w), a.iters, a.warmup, world)
+    tw_d = timed(base.bare_all_to_all(h, row_b), a.iters, a.warmup, world)
+    tw_c = timed(base.bare_all_to_all(h, 2 * H, reverse=True), a.iters, a.warmup, world)
+    emit(rank, dict(common, impl="nccl_baseline", op="dispatch(fp8 1x128)", us=tb_d * 1e6,
+                    recv_GBps=rq.shape[0] * row_b / tb_d / 1e9, speedup_of_umdk=tb_d / t_disp))
+    emit(rank, dict(common, impl="nccl_baseline", op="combine(bf16, top-8 weighted)", us=tb_c * 1e6,
+                    speedup_of_umdk=tb_c / t_comb))
+    emit(rank, dict(common, impl="nccl_baseline", op="bare all_to_all_single, dispatch bytes", us=tw_d * 1e6))
+    emit(rank, dict(common, impl="nccl_baseline", op="bare all_to_all_single, combine bytes", us=tw_c * 1e6))
     heap.close()
+    return list(_records)
 
 
-def bench_ll(rank, world, a):
-    from baseline.nccl_baseline import NcclEp, expert_ffn_bf16
+def bench_ll(rank, world, a, quiet=False):
+    from baseline.nccl_baseline import GroupedFfn, NcclLowLatencyMoe
     from umdk_b200.models.dsv3_decoder import _quant_experts
-    from umdk_b200.ops import reference as ref
     from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
     from umdk_b200.parallel.symm import SymmetricHeap
+    _begin(quiet)
+    brief = getattr(a, "brief", False)
     T, H, F, E, K = a.ll_tokens, 7168, 2048, a.ll_experts, 8
     el = E // world
     g = torch.Generator(device="cuda").manual_seed(300 + rank)
@@ -163,62 +189,8 @@ def bench_ll(rank, world, a):
     heap = SymmetricHeap(nbytes, None) if world > 1 else SymmetricHeap(nbytes)
     ll = EpLowLatency(heap, E, K, H, F, T)
     out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
-    t_all = timed(lambda: ll.moe(x, idx, w, experts, shared, out=out), a.iters, a.warmup, world)
-    t_routed = timed(lambda: ll.moe(x, idx, w, experts, None, out=out), a.iters, a.warmup, world)
-    t_two = timed(lambda: ll.moe(x, idx, w, experts, None, out=out, fused=False), a.iters, a.warmup, world)
     tiled = experts.to_tiled()
     t_tiled = timed(lambda: ll.moe(x, idx, w, tiled, None, out=out), a.iters, a.warmup, world)
-    ll.inline_layout = False    # the layout as a kernel launch of its own, for comparison
-    t_sep_layout = timed(lambda: ll.moe(x, idx, w, tiled, None, out=out), a.iters, a.warmup, world)
-    ll.inline_layout = True
-    # stage breakdown of the same call chain: events between the three launches (stage times include waiting for peers)
-    from umdk_b200.ops.ep import layout as ep_layout
-    stage = torch.zeros(3, dtype=torch.float64, device="cuda")
-    for _ in range(a.iters):
-        _flush.zero_()
-        if world > 1:
-            dist.barrier()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-        ev[0].record()
-        lay = ep_layout(idx, ll.E, ll.R, ll.layout_scratch, ll.layout_bar, ll.status)
-        ev[1].record()
-        ll.dispatch(x, idx, lay=lay)
-        ev[2].record()
-        ll._fused(tiled, idx, w, out)
-        ev[3].record()
-        torch.cuda.synchronize()
-        stage += torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(3)], dtype=torch.float64, device="cuda")
-    stage /= a.iters
-    if world > 1:
-        dist.all_reduce(stage, op=dist.ReduceOp.MAX)
-    stage_us = [float(v) * 1e3 for v in stage.tolist()]
-    # inside the fused kernel: global-timer stamps of its stages (median of 5 calls, max over ranks)
-    ll.diagnose = True
-    tls = []
-    for _ in range(5):
-        ll.timeline_reset()
-        ll.moe(x, idx, w, tiled, None, out=out)
-        torch.cuda.synchronize()
-        tls.append(list(ll.timeline_us().values()))
-    ll.diagnose = False
-    tl = torch.tensor(tls, dtype=torch.float64).median(dim=0).values.cuda()
-    if world > 1:
-        dist.all_reduce(tl, op=dist.ReduceOp.MAX)
-    timeline = dict(zip(("rows_ready", "phase1", "phase2", "peers_done", "end"), [round(float(v), 1) for v in tl]))
-    # the same layer as one CUDA-graph replay: no Python / launch cost between the three kernels
-    t_graph = None
-    try:
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        graph, _ = ll.capture(x, idx, w, tiled, None, out=out)
-        t_graph = timed(graph.replay, a.iters, a.warmup, world)
-        ll.check("ll graph")
-        del graph
-    except Exception as e:  # capture not possible in this environment: report without it
-        if rank == 0:
-            print(f"# CUDA graph capture of the layer failed: {e}", flush=True)
-    del tiled
     ll.check("ll")
     rows = int(ll.group_off[-1].item())
     w_bytes = (w1q.numel() + w2q.numel())              # routed expert weights read once per call
@@ -227,36 +199,59 @@ def bench_ll(rank, world, a):
     roof = max(w_bytes / (HBM_GBS * 1e9), flops / (2 * 1602.6e12), wire / (NVLINK_GBS * 1e9))
     common = {"config": "ep_ll_moe", "n_gpus": world, "tokens_per_rank": T, "hidden": H, "ffn": F, "experts": E,
               "top_k": K, "rows_on_this_rank": rows}
-    emit(rank, dict(common, impl="umdk_b200", op="dispatch+GEMM1+SwiGLU+quant+GEMM2+combine (+shared expert)",
-                    us=t_all * 1e6))
-    emit(rank, dict(common, impl="umdk_b200", op="dispatch+GEMM1+SwiGLU+quant+GEMM2+combine (routed only)",
-                    us=t_routed * 1e6, roofline_us=roof * 1e6, frac_of_roofline=roof / t_routed,
-                    weight_GBps=w_bytes / t_routed / 1e9))
-    emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights (ExpertWeights.to_tiled)",
-                    us=t_tiled * 1e6, frac_of_roofline=roof / t_tiled, weight_GBps=w_bytes / t_tiled / 1e9,
-                    us_with_separate_layout_launch=t_sep_layout * 1e6,
-                    stage_us={"ep_layout": stage_us[0], "ep_ll_dispatch": stage_us[1], "moe_fused": stage_us[2]},
-                    fused_timeline_us=timeline))
-    if t_graph is not None:
-        emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights, one CUDA-graph replay per layer",
-                        us=t_graph * 1e6, frac_of_roofline=roof / t_graph, weight_GBps=w_bytes / t_graph / 1e9))
-    emit(rank, dict(common, impl="umdk_b200", op="same, expert GEMMs as two launches (moe_gemm mode 0 + mode 2)",
-                    us=t_two * 1e6, frac_of_roofline=roof / t_two))
-    if world >= 1:
-        # baseline: NCCL all-to-all + separate quant + cuBLAS bf16 expert GEMMs + NCCL all-to-all + index_add
-        w1b = ref.dequant_fp8_128x128(w1q, w1s).to(torch.bfloat16) if el <= 64 else None
-        if w1b is not None and world > 1:
-            w2b = ref.dequant_fp8_128x128(w2q, w2s).to(torch.bfloat16)
-            base = NcclEp(None, E)
-
-            def run():
-                (rq, rs), h = base.dispatch(x, idx, True)
-                yb = expert_ffn_bf16(rq, rs, h["recv_counts"], w1b, w2b)
-                return base.combine(yb, h, w)
-            tb = timed(run, a.iters, a.warmup, world)
-            emit(rank, dict(common, impl="nccl_cublas_baseline", op="a2a + quant + cuBLAS bf16 FFN + a2a + index_add",
-                            us=tb * 1e6, speedup_of_umdk=tb / t_routed))
+    rec_tiled = dict(common, impl="umdk_b200", op="routed only, tile-major weights (ExpertWeights.to_tiled)",
+                     us=t_tiled * 1e6, roofline_us=roof * 1e6, frac_of_roofline=roof / t_tiled,
+                     weight_GBps=w_bytes / t_tiled / 1e9)
+    if not brief:
+        t_all = timed(lambda: ll.moe(x, idx, w, experts, shared, out=out), a.iters, a.warmup, world)
+        t_routed = timed(lambda: ll.moe(x, idx, w, experts, None, out=out), a.iters, a.warmup, world)
+        t_two = timed(lambda: ll.moe(x, idx, w, experts, None, out=out, fused=False), a.iters, a.warmup, world)
+        # inside the fused kernel: global-timer stamps of its stages (median of 5 calls, max over ranks)
+        ll.diagnose = True
+        tls = []
+        for _ in range(5):
+            ll.timeline_reset()
+            ll.moe(x, idx, w, tiled, None, out=out)
+            torch.cuda.synchronize()
+            tls.append(list(ll.timeline_us().values()))
+        ll.diagnose = False
+        tl = torch.tensor(tls, dtype=torch.float64).median(dim=0).values.cuda()
+        if world > 1:
+            dist.all_reduce(tl, op=dist.ReduceOp.MAX)
+        rec_tiled["fused_timeline_us"] = dict(zip(ll.timeline_names(), [round(float(v), 1) for v in tl]))
+        emit(rank, dict(common, impl="umdk_b200", op="dispatch+GEMM1+SwiGLU+quant+GEMM2+combine (+shared expert)",
+                        us=t_all * 1e6))
+        emit(rank, dict(common, impl="umdk_b200", op="dispatch+GEMM1+SwiGLU+quant+GEMM2+combine (routed only)",
+                        us=t_routed * 1e6, roofline_us=roof * 1e6, frac_of_roofline=roof / t_routed,
+                        weight_GBps=w_bytes / t_routed / 1e9))
+        emit(rank, dict(common, impl="umdk_b200", op="same, expert GEMMs as two launches (moe_gemm mode 0 + mode 2)",
+                        us=t_two * 1e6, frac_of_roofline=roof / t_two))
+    emit(rank, rec_tiled)
+    if not brief:
+        # the same layer as one CUDA-graph replay: no Python / launch cost between the kernels
+        try:
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            graph, _ = ll.capture(x, idx, w, tiled, None, out=out)
+            t_graph = timed(graph.replay, a.iters, a.warmup, world)
+            ll.check("ll graph")
+            del graph
+            emit(rank, dict(common, impl="umdk_b200", op="routed only, tile-major weights, one CUDA-graph replay per layer",
+                            us=t_graph * 1e6, frac_of_roofline=roof / t_graph, weight_GBps=w_bytes / t_graph / 1e9))
+        except Exception as e:  # capture not possible in this environment: report without it
+            if rank == 0:
+                print(f"# CUDA graph capture of the layer failed: {e}", flush=True)
+    del tiled
+    # baseline: all_gather + ONE grouped library GEMM per projection + reduce_scatter, no host synchronisation
+    ffn = GroupedFfn(w1q, w1s, w2q, w2s, bmm_cap=world * T)
+    base = NcclLowLatencyMoe(None, E, K, ffn, shared_first=False)
+    tb = timed(lambda: base(x, idx, w), a.iters, a.warmup, world)
+    emit(rank, dict(common, impl="nccl_grouped_gemm_baseline", gemm=ffn.backend,
+                    op="all_gather + grouped library GEMMs (" + ffn.backend + ") + reduce_scatter",
+                    us=tb * 1e6, speedup_of_umdk=tb / t_tiled))
     heap.close()
+    return list(_records)
 
 
 def main():

@@ -70,10 +70,71 @@ def _quant_experts(n: int, rows: int, cols: int, gen_device, gen: torch.Generato
     return q, s
 
 
+def build_dense_weights(cfg: DecoderConfig, dev) -> dict:
+    """Replicated (non-expert) weights of the decoder, N(0, 0.02) in bf16, the same on every rank (seed ``cfg.seed``).
+    Returns {"embed", "lm_head", "final_norm", "layers": [dict per layer], "gen": the generator, for what follows}."""
+    c, H, bf = cfg, cfg.hidden, torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(c.seed)
+
+    def lin(o, i):
+        return (torch.randn(o, i, device=dev, generator=g, dtype=torch.float32) * 0.02).to(bf)
+
+    out = {"embed": lin(c.vocab, H), "lm_head": lin(c.vocab, H), "final_norm": torch.ones(H, device=dev, dtype=bf),
+           "layers": [], "gen": g}
+    for _ in range(c.n_layers):
+        L = {}
+        L["attn_norm"] = torch.ones(H, device=dev, dtype=bf)
+        L["wq_a"] = lin(c.q_lora, H)
+        L["q_norm"] = torch.ones(c.q_lora, device=dev, dtype=bf)
+        L["wq_b"] = lin(HEADS * (c.qk_nope + c.qk_rope), c.q_lora)
+        L["wkv_a"] = lin(DIM_V + c.qk_rope, H)
+        L["kv_norm"] = torch.ones(DIM_V, device=dev, dtype=bf)
+        L["w_uk"] = (torch.randn(HEADS, c.qk_nope, DIM_V, device=dev, generator=g) * 0.02).to(bf)
+        L["w_uv"] = (torch.randn(HEADS, DIM_V, c.v_head, device=dev, generator=g) * 0.02).to(bf)
+        L["wo"] = lin(H, HEADS * c.v_head)
+        L["ffn_norm"] = torch.ones(H, device=dev, dtype=bf)
+        L["router"] = (torch.randn(c.n_experts, H, device=dev, generator=g, dtype=torch.float32) * 0.02).to(bf)
+        out["layers"].append(L)
+    return out
+
+
+def expert_shard_stream(cfg: DecoderConfig, dev, rank: int, world: int, gen_shared: torch.Generator):
+    """Yields, layer by layer, (routed ExpertWeights of this rank's shard, shared ExpertWeights or None) in row-major
+    fp8 with 128x128 block scales: routed experts from a per-rank stream, the shared expert from the replicated one."""
+    c = cfg
+    ge = torch.Generator(device=dev).manual_seed(c.seed + 1000 + rank)
+    el = c.n_experts // world
+    for _ in range(c.n_layers):
+        w1q, w1s = _quant_experts(el, 2 * c.moe_ffn, c.hidden, dev, ge)
+        w2q, w2s = _quant_experts(el, c.hidden, c.moe_ffn, dev, ge)
+        shared = None
+        if c.shared_expert:
+            s1q, s1s = _quant_experts(1, 2 * c.moe_ffn, c.hidden, dev, gen_shared)
+            s2q, s2s = _quant_experts(1, c.hidden, c.moe_ffn, dev, gen_shared)
+            shared = ExpertWeights(s1q, s1s, s2q, s2s)
+        yield ExpertWeights(w1q, w1s, w2q, w2s), shared
+
+
+def build_weights(cfg: DecoderConfig, dev, rank: int, world: int) -> dict:
+    """All weights of one rank in the form the kernels read: dense weights plus, per layer, the expert shard with the
+    shared expert stored as one more local expert, tile-major. One bundle can back several ``DecoderRank`` objects
+    (different KV placement, same weights)."""
+    W = build_dense_weights(cfg, dev)
+    for L, (experts, shared) in zip(W["layers"], expert_shard_stream(cfg, dev, rank, world, W["gen"])):
+        if shared is not None:
+            # the shared expert runs inside the routed pipeline (EpLowLatency fold_shared)
+            experts = ExpertWeights.with_shared(experts, shared)
+        L["experts"] = experts.to_tiled()   # tile-major: sequential DRAM reads in the fused kernel
+        L["shared"] = None
+        del experts, shared
+    return W
+
+
 class DecoderRank:
     """One rank's shard of the decoder plus its KV cache, offload manager and EP state."""
 
-    def __init__(self, cfg: DecoderConfig, group: Optional[dist.ProcessGroup] = None, device=None):
+    def __init__(self, cfg: DecoderConfig, group: Optional[dist.ProcessGroup] = None, device=None,
+                 weights: Optional[dict] = None):
         self.cfg = cfg
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -83,48 +144,10 @@ class DecoderRank:
         c = cfg
         assert c.n_experts % self.world == 0 and c.ctx % PAGE == 0 and (c.ctx // PAGE) % 2 == 0
         H = c.hidden
-        g = torch.Generator(device=dev).manual_seed(c.seed)  # replicated weights: same seed on every rank
         bf = torch.bfloat16
-
-        def lin(o, i):
-            return (torch.randn(o, i, device=dev, generator=g, dtype=torch.float32) * 0.02).to(bf)
-
-        self.embed = lin(c.vocab, H)
-        self.lm_head = lin(c.vocab, H)
-        self.final_norm = torch.ones(H, device=dev, dtype=bf)
-        self.layers = []
-        for _ in range(c.n_layers):
-            L = {}
-            L["attn_norm"] = torch.ones(H, device=dev, dtype=bf)
-            L["wq_a"] = lin(c.q_lora, H)
-            L["q_norm"] = torch.ones(c.q_lora, device=dev, dtype=bf)
-            L["wq_b"] = lin(HEADS * (c.qk_nope + c.qk_rope), c.q_lora)
-            L["wkv_a"] = lin(DIM_V + c.qk_rope, H)
-            L["kv_norm"] = torch.ones(DIM_V, device=dev, dtype=bf)
-            L["w_uk"] = (torch.randn(HEADS, c.qk_nope, DIM_V, device=dev, generator=g) * 0.02).to(bf)
-            L["w_uv"] = (torch.randn(HEADS, DIM_V, c.v_head, device=dev, generator=g) * 0.02).to(bf)
-            L["wo"] = lin(H, HEADS * c.v_head)
-            L["ffn_norm"] = torch.ones(H, device=dev, dtype=bf)
-            L["router"] = (torch.randn(c.n_experts, H, device=dev, generator=g, dtype=torch.float32) * 0.02).to(bf)
-            self.layers.append(L)
-        # expert shards: a different stream per rank
-        ge = torch.Generator(device=dev).manual_seed(c.seed + 1000 + self.rank)
-        el = c.n_experts // self.world
-        for L in self.layers:
-            w1q, w1s = _quant_experts(el, 2 * c.moe_ffn, H, dev, ge)
-            w2q, w2s = _quant_experts(el, H, c.moe_ffn, dev, ge)
-            if c.shared_expert:
-                # the shared expert (replicated: common generator) is stored as one more local expert so that it
-                # runs inside the routed pipeline (EpLowLatency fold_shared)
-                s1q, s1s = _quant_experts(1, 2 * c.moe_ffn, H, dev, g)
-                s2q, s2s = _quant_experts(1, H, c.moe_ffn, dev, g)
-                L["experts"] = ExpertWeights.with_shared(ExpertWeights(w1q, w1s, w2q, w2s),
-                                                         ExpertWeights(s1q, s1s, s2q, s2s))
-                del w1q, w2q, s1q, s2q
-            else:
-                L["experts"] = ExpertWeights(w1q, w1s, w2q, w2s)
-            L["experts"] = L["experts"].to_tiled()   # tile-major: sequential DRAM reads in the fused kernel
-            L["shared"] = None
+        W = weights if weights is not None else build_weights(c, dev, self.rank, self.world)
+        self.weights = W
+        self.embed, self.lm_head, self.final_norm, self.layers = W["embed"], W["lm_head"], W["final_norm"], W["layers"]
         # EP state
         nbytes = EpLowLatency.heap_bytes(self.world, c.n_experts, c.top_k, H, c.batch, fold_shared=c.shared_expert)
         self.heap = SymmetricHeap(nbytes, group) if self.world > 1 else SymmetricHeap(nbytes)

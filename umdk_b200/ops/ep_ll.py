@@ -284,6 +284,10 @@ class EpLowLatency:
         self.diag_fused.zero_()
         self.diag_fused[0] = torch.iinfo(torch.int64).max
 
+    @staticmethod
+    def timeline_names():
+        return ("rows_ready", "phase1", "phase2", "peers_done", "end")
+
     def timeline_us(self) -> dict:
         """Stages of the last fused kernel in microseconds since its first CTA started, each taken at the LAST CTA to
         get there: rows_ready (dispatched rows arrived), phase1 (GEMM1 + SwiGLU + requant), phase2 (GEMM2 + combine
