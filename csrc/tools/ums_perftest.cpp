@@ -8,6 +8,7 @@
 #include <string.h>
 #include <unistd.h>
 
+#include <chrono>
 #include <thread>
 #include <vector>
 
@@ -135,6 +136,58 @@ int main(int argc, char** argv) {
     ums_close(c);
     close(ls);
     if (memcmp(b, e, 5)) return fail("fallback data");
+    // the other direction: an ordinary TCP client that sends five bytes at once to a UMS listener, and one that
+    // first waits for a banner from the server; neither may lose bytes nor be held up by the handshake probe
+    for (int banner = 0; banner < 2; ++banner) {
+      const int ul = ums_socket(AF_INET, SOCK_STREAM, 0);
+      sockaddr_in ua{};
+      ua.sin_family = AF_INET;
+      ua.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+      if (ums_bind(ul, (sockaddr*)&ua, sizeof(ua)) || ums_listen(ul, 4)) return fail("ums listen");
+      socklen_t ll = sizeof(ua);
+      getsockname(ul, (sockaddr*)&ua, &ll);
+      bool srv_ok = false;
+      std::thread usrv([&] {
+        const int sc = ums_accept(ul, nullptr, nullptr);
+        if (sc < 0 || ums_is_accelerated(sc) != 0) return;
+        if (banner && ums_send(sc, "READY", 5, 0) != 5) return;
+        char bb[5];
+        size_t got = 0;
+        while (got < 5) {
+          const ssize_t r = ums_recv(sc, bb + got, 5 - got, 0);
+          if (r <= 0) return;
+          got += (size_t)r;
+        }
+        srv_ok = ums_send(sc, bb, 5, 0) == 5;
+        ums_close(sc);
+      });
+      const int pc = socket(AF_INET, SOCK_STREAM, 0);
+      if (connect(pc, (sockaddr*)&ua, sizeof(ua))) return fail("plain connect");
+      char rb[5] = {0};
+      const auto tb0 = std::chrono::steady_clock::now();
+      if (banner) {
+        size_t got = 0;
+        while (got < 5) {
+          const ssize_t r = recv(pc, rb + got, 5 - got, 0);
+          if (r <= 0) return fail("banner");
+          got += (size_t)r;
+        }
+        if (memcmp(rb, "READY", 5)) return fail("banner bytes");
+        const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - tb0).count();
+        if (ms > 1000.0) return fail("a client that waits for a banner was held up by the handshake probe");
+      }
+      send(pc, "plain", 5, 0);
+      size_t got = 0;
+      while (got < 5) {
+        const ssize_t r = recv(pc, rb + got, 5 - got, 0);
+        if (r <= 0) return fail("plain client: server closed early (bytes were swallowed?)");
+        got += (size_t)r;
+      }
+      usrv.join();
+      close(pc);
+      ums_close(ul);
+      if (!srv_ok || memcmp(rb, "plain", 5)) return fail("plain client to a UMS listener lost bytes");
+    }
     ums_stats_t st;
     ums_get_stats(&st);
     if (st.conns_ums < 2 || st.conns_fallback < 1 || st.bytes_tx_ring == 0) return fail("statistics");

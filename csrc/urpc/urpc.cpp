@@ -75,19 +75,41 @@ struct Ready {
 constexpr uint8_t kFlagSealed = 0x80;
 struct Sealer {
   std::mutex mu;
+  // Held from the moment a message takes its counter until it sits in the queue, so that several threads replying
+  // on one lane (deferred urpc_func_return calls, the poll thread's inline replies) enqueue in counter order.
+  std::mutex tx_order;
   std::unique_ptr<ub::AeadCipher> tx, rx;
   uint64_t tx_nonce = 0, rx_last = 0;
+  // Replay window: bit i set = counter (rx_last - i) has been accepted. A message older than the window, or one
+  // whose bit is set, is dropped; a late one inside the window is still accepted once.
+  uint64_t rx_seen = 0;
+  bool replay_check(uint64_t nonce) const {
+    if (nonce == 0) return false;
+    if (nonce > rx_last) return true;
+    const uint64_t d = rx_last - nonce;
+    return d < 64 && !((rx_seen >> d) & 1);
+  }
+  void replay_accept(uint64_t nonce) {
+    if (nonce > rx_last) {
+      const uint64_t d = nonce - rx_last;
+      rx_seen = d >= 64 ? 0 : (rx_seen << d);
+      rx_seen |= 1;
+      rx_last = nonce;
+    } else {
+      rx_seen |= 1ull << (rx_last - nonce);
+    }
+  }
   // One key serves every queue pair of a session: the salt names the lane and the direction, so no two senders ever
   // share a (key, nonce) pair, and each lane keeps its own replay counter.
   void set(const uint8_t key[32], bool is_server, uint32_t lane = 0) {
     tx.reset(new ub::AeadCipher(key, 2 * lane + (is_server ? 1u : 0u)));
     rx.reset(new ub::AeadCipher(key, 2 * lane + (is_server ? 0u : 1u)));
-    tx_nonce = rx_last = 0;
+    tx_nonce = rx_last = rx_seen = 0;
   }
   void clear() {
     tx.reset();
     rx.reset();
-    tx_nonce = rx_last = 0;
+    tx_nonce = rx_last = rx_seen = 0;
   }
   bool on() const { return tx != nullptr; }
 };
@@ -267,6 +289,8 @@ int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, c
     p += sg[i].len;
   }
   if (flat_len) memcpy(p, flat, flat_len);
+  std::unique_lock<std::mutex> order;
+  if (sealed) order = std::unique_lock<std::mutex>(seal->tx_order);
   if (sealed) {
     // seal in place: header (with the message counter) authenticated, payload encrypted, tag appended
     std::lock_guard<std::mutex> l(seal->mu);
@@ -293,6 +317,7 @@ int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, c
     }
     sched_yield();
   }
+  if (order.owns_lock()) order.unlock();
   std::lock_guard<std::mutex> l(g.stat_mu);
   g.stats.bytes_tx += total;
   return URPC_SUCCESS;
@@ -307,11 +332,11 @@ bool open_msg(umq_buf_t* b, const Head& h, Sealer* seal) {
   std::lock_guard<std::mutex> l(seal->mu);
   uint8_t* hb = reinterpret_cast<uint8_t*>(b->buf_data);
   const uint64_t nonce = urpc_proto::get_le(hb + 20, 8);
-  if (nonce <= seal->rx_last) return false;
+  if (!seal->replay_check(nonce)) return false;
   const size_t n_sealed = b->data_size - sizeof(urpc_req_head_t);
   std::vector<uint8_t> pt(n_sealed);
   if (!seal->rx->open(nonce, hb, sizeof(urpc_req_head_t), hb + sizeof(urpc_req_head_t), n_sealed, pt.data())) return false;
-  seal->rx_last = nonce;
+  seal->replay_accept(nonce);
   memcpy(hb + sizeof(urpc_req_head_t), pt.data(), n_sealed - ub::AeadCipher::kTagBytes);
   b->data_size -= ub::AeadCipher::kTagBytes;
   return true;

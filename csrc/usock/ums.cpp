@@ -20,8 +20,10 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <chrono>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <unordered_map>
 
 namespace {
@@ -167,6 +169,17 @@ std::string dir() {
 }
 std::string listen_marker(uint16_t port) { return dir() + "/listen_" + std::to_string(port); }
 
+// How long an accepted loopback connection may stay silent before it is taken for an ordinary TCP client
+// (UMS_PEEK_MS, default 50: a UMS client sends its handshake right after connect()).
+int peek_limit_ms() {
+  static const int v = [] {
+    const char* e = getenv("UMS_PEEK_MS");
+    const int x = e ? atoi(e) : 50;
+    return x < 0 ? 0 : (x > 2000 ? 2000 : x);
+  }();
+  return v;
+}
+
 bool rd_full(int fd, void* b, size_t n, int tmo_ms) {
   char* p = static_cast<char*>(b);
   while (n) {
@@ -262,10 +275,43 @@ int ums_adopt_accepted(int listen_fd, int fd) {
     Conn* lc = find(listen_fd);
     if (!lc || !lc->listener) return 0;
   }
-  // server side of the handshake: the client speaks first
+  // Server side of the handshake: a UMS client speaks first, but an ordinary TCP client (or a UMS client on another
+  // host, which never sends the handshake) does not. So nothing is consumed until the stream is known to start with
+  // the handshake magic: only loopback peers are candidates, their first bytes are PEEKED with a short limit, and
+  // anything else leaves the byte stream untouched and falls back to TCP at once.
   Clc in{};
   Conn c;
-  if (rd_full(fd, &in, sizeof(in), 2000) && in.magic == kClcMagic) {
+  bool candidate = false;
+  {
+    sockaddr_storage ps{};
+    socklen_t pl = sizeof(ps);
+    if (getpeername(fd, reinterpret_cast<sockaddr*>(&ps), &pl) == 0 && ps.ss_family == AF_INET)
+      candidate = (ntohl(reinterpret_cast<sockaddr_in*>(&ps)->sin_addr.s_addr) >> 24) == 127;
+  }
+  if (candidate) {
+    candidate = false;
+    const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(peek_limit_ms());
+    for (;;) {
+      uint32_t magic = 0;
+      const ssize_t r = libc().recv(fd, &magic, sizeof(magic), MSG_PEEK | MSG_DONTWAIT);
+      if (r == (ssize_t)sizeof(magic)) {
+        candidate = magic == kClcMagic;
+        break;
+      }
+      if (r == 0 || (r < 0 && errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR)) break;
+      if (r > 0 && memcmp(&magic, &kClcMagic, (size_t)r) != 0) break;   // already differs: not a handshake
+      const auto left = std::chrono::duration_cast<std::chrono::milliseconds>(t_end - std::chrono::steady_clock::now());
+      if (left.count() <= 0) break;
+      pollfd pf{fd, POLLIN, 0};
+      if (r > 0) {
+        // a partial magic is pending: POLLIN would return at once, so just yield briefly
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+      } else if (poll(&pf, 1, (int)left.count()) <= 0) {
+        break;
+      }
+    }
+  }
+  if (candidate && rd_full(fd, &in, sizeof(in), 2000) && in.magic == kClcMagic) {
     Clc out{};
     out.magic = kClcMagic;
     in.shm_name[sizeof(in.shm_name) - 1] = 0;
@@ -275,10 +321,14 @@ int ums_adopt_accepted(int listen_fd, int fd) {
       ++g_stats.conns_auth_fail;
     }
     const std::string path = dir() + "/" + in.shm_name;
-    const int sfd = trusted ? ::open(path.c_str(), O_RDWR) : -1;
+    const int sfd = trusted ? ::open(path.c_str(), O_RDWR | O_NOFOLLOW) : -1;
     void* p = MAP_FAILED;
     if (sfd >= 0) {
-      p = mmap(nullptr, sizeof(ConnShm), PROT_READ | PROT_WRITE, MAP_SHARED, sfd, 0);
+      // the ring file must be what a client of this user created: a regular file of exactly the ring size
+      struct stat sb{};
+      if (fstat(sfd, &sb) == 0 && S_ISREG(sb.st_mode) && sb.st_uid == geteuid() &&
+          sb.st_size == (off_t)sizeof(ConnShm))
+        p = mmap(nullptr, sizeof(ConnShm), PROT_READ | PROT_WRITE, MAP_SHARED, sfd, 0);
       libc().close(sfd);
     }
     if (p != MAP_FAILED) {
@@ -318,7 +368,10 @@ int ums_adopt_connected(int fd, const struct sockaddr* peer) {
   if (try_ums) {
     Clc out{};
     out.magic = kClcMagic;
-    snprintf(out.shm_name, sizeof(out.shm_name), "conn_%d_%llu", getpid(), (unsigned long long)g_seq.fetch_add(1));
+    uint64_t salt = 0;   // unguessable ring names: another local process cannot name a connection's ring file
+    ub::random_bytes(&salt, sizeof(salt));
+    snprintf(out.shm_name, sizeof(out.shm_name), "conn_%d_%llu_%016llx", getpid(),
+             (unsigned long long)g_seq.fetch_add(1), (unsigned long long)salt);
     const std::string path = dir() + "/" + out.shm_name;
     uint64_t token_id = 0;
     bool token_stored = false;

@@ -361,3 +361,60 @@ def test_many_channels_outgrow_the_first_buffer_pool(rpc):
     finally:
         for ch in chans:
             ch.close()
+
+
+def test_sealed_lane_with_four_threads_replying_at_once(tmp_path):
+    """With a pre-shared key every message carries a counter that the receiver checks for replays. Four application
+    threads answer deferred requests of ONE lane at the same time: counters must reach the wire in an order the
+    receiver accepts, so every one of the replies arrives."""
+    import ctypes
+    import threading
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import urpc
+    urpc.set_psk("3a" * 32, "rpc")
+    urpc.init(default_timeout_ms=5000)
+    srv = urpc.Server()
+    lib = urpc._lib()
+    ch = None
+    try:
+        ch = urpc.Channel(srv.ip, srv.port)
+        srv.paused = True
+        time.sleep(0.05)
+        N = 32
+        for i in range(N):
+            ch.call_async(77, b"req %02d" % i, user_ctx=i)
+        msgs = (urpc._PollMsg * N)()
+        n, deadline = 0, time.monotonic() + 5
+        while n < N and time.monotonic() < deadline:
+            got = lib.urpc_server_poll(ctypes.byref(msgs, n * ctypes.sizeof(urpc._PollMsg)), N - n)
+            n += max(got, 0)
+        assert n == N
+        rcs = [None] * N
+
+        def answer(lo, hi):
+            for j in range(lo, hi):
+                body = b"rsp " + ctypes.string_at(msgs[j].data, msgs[j].len)
+                rcs[j] = lib.urpc_func_return(ctypes.byref(msgs[j]), body, len(body), 0)
+
+        ths = [threading.Thread(target=answer, args=(k * 8, k * 8 + 8)) for k in range(4)]
+        for t in ths:
+            t.start()
+        for t in ths:
+            t.join()
+        assert rcs == [0] * N
+        for j in range(N):
+            lib.urpc_msg_release(ctypes.byref(msgs[j]))
+        out, deadline = {}, time.monotonic() + 5
+        while len(out) < N and time.monotonic() < deadline:
+            for _, ctx, status, data in ch.poll():
+                assert status == 0
+                out[ctx] = data
+        assert out == {i: b"rsp req %02d" % i for i in range(N)}
+    finally:
+        srv.paused = False
+        if ch is not None:
+            ch.close()
+        srv.stop()
+        urpc.uninit()
+        urpc.set_psk("", "")
