@@ -36,13 +36,6 @@ def dequant_1x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     return (q.float().view(T, H // 128, 128) * s.unsqueeze(-1)).view(T, H)
 
 
-def quant_rowwise(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """[M, K] -> (fp8 e4m3 [M, K], fp32 scale [M]) with one scale per row."""
-    amax = x.abs().amax(dim=-1, keepdim=True).float().clamp_min(1e-4)
-    q = (x.float() * (448.0 / amax)).to(FP8)
-    return q, (amax / 448.0).squeeze(-1)
-
-
 def _world(group):
     return (dist.get_world_size(group), dist.get_rank(group)) if dist.is_initialized() else (1, 0)
 
@@ -159,10 +152,12 @@ class GroupedFfn:
     device (``offs``), so there is no host synchronisation and no Python loop over experts.
 
     Back ends, first that works on this GPU / torch build (``backend`` names it):
-      fp8_rowwise   torch._scaled_grouped_mm on fp8 e4m3 weights re-quantised with one scale per output row and
-                    activations quantised per token (same bytes per weight as the product's fp8 format)
-      bf16_grouped  torch._grouped_mm on bf16 copies of the weights (twice the weight bytes)
+      bf16_grouped  torch._grouped_mm on bf16 copies of the weights
       bf16_bmm      rows scattered into [G, cap, K] and torch.bmm on bf16 copies, cap = padded group size
+    Both read bf16 weights, twice the bytes of the product's fp8 format: torch's only fp8 grouped GEMM,
+    torch._scaled_grouped_mm, raised a CUDA launch failure on this GPU / torch build when it was probed and is
+    therefore not used. Candidates are probed in a child process, so a back end that fails cannot take this
+    process's CUDA context with it.
     Weights arrive as the product stores them: fp8 e4m3 with 128x128 block scales, w1 [G, 2F, H], w2 [G, H, F].
     """
 
@@ -173,51 +168,68 @@ class GroupedFfn:
         self.bmm_cap = bmm_cap
         self.backend = backend or self.pick_backend()
         dev = w1q.device
-        if self.backend == "fp8_rowwise":
-            self.w1 = torch.empty(self.G, F2, self.H, dtype=torch.uint8, device=dev).view(FP8)
-            self.w2 = torch.empty(self.G, self.H, self.F, dtype=torch.uint8, device=dev).view(FP8)
-            self.s1 = torch.empty(self.G, F2, dtype=torch.float32, device=dev)
-            self.s2 = torch.empty(self.G, self.H, dtype=torch.float32, device=dev)
-            for g in range(self.G):
-                self.w1[g], self.s1[g] = quant_rowwise(dequant_fp8_128x128(w1q[g], w1s[g]))
-                self.w2[g], self.s2[g] = quant_rowwise(dequant_fp8_128x128(w2q[g], w2s[g]))
-        else:
-            self.w1 = torch.empty(self.G, F2, self.H, dtype=torch.bfloat16, device=dev)
-            self.w2 = torch.empty(self.G, self.H, self.F, dtype=torch.bfloat16, device=dev)
-            for g in range(self.G):
-                self.w1[g] = dequant_fp8_128x128(w1q[g], w1s[g]).to(torch.bfloat16)
-                self.w2[g] = dequant_fp8_128x128(w2q[g], w2s[g]).to(torch.bfloat16)
+        assert self.backend in ("bf16_grouped", "bf16_bmm"), self.backend
+        self.w1 = torch.empty(self.G, F2, self.H, dtype=torch.bfloat16, device=dev)
+        self.w2 = torch.empty(self.G, self.H, self.F, dtype=torch.bfloat16, device=dev)
+        for g in range(self.G):
+            self.w1[g] = dequant_fp8_128x128(w1q[g], w1s[g]).to(torch.bfloat16)
+            self.w2[g] = dequant_fp8_128x128(w2q[g], w2s[g]).to(torch.bfloat16)
 
     _picked: Optional[str] = None
+    why_not: dict = {}
 
     @classmethod
     def pick_backend(cls) -> str:
-        """Tries each back end once on a tiny problem against a per-group fp32 loop."""
+        """Tries each back end once on a tiny problem against a per-group fp32 loop, each in a child process (local
+        rank 0 probes; the other ranks of a process group take its answer)."""
         if cls._picked is not None:
             return cls._picked
+        import json
+        import os
+        import subprocess
+        import sys
+        name, why = None, {}
+        if not dist.is_initialized() or dist.get_rank() == 0:
+            root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+            for cand in ("bf16_grouped", "bf16_bmm"):
+                code = ("import sys; sys.path.insert(0, %r); import torch; torch.cuda.set_device(%d); "
+                        "from baseline.nccl_baseline import GroupedFfn; "
+                        "print('PROBE', GroupedFfn.probe(%r))" % (root, torch.cuda.current_device(), cand))
+                try:
+                    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+                    ok = r.returncode == 0 and "PROBE ok" in r.stdout
+                    if ok:
+                        name = cand
+                        break
+                    why[cand] = (r.stdout + r.stderr).strip()[-200:]
+                except Exception as e:   # noqa: BLE001
+                    why[cand] = f"{type(e).__name__}: {e}"
+        if dist.is_initialized():
+            box = [name, why]
+            dist.broadcast_object_list(box, src=0)
+            name, why = box
+        if name is None:
+            raise RuntimeError(f"no grouped GEMM back end works here: {json.dumps(why)}")
+        cls._picked, cls.why_not = name, why
+        return name
+
+    @classmethod
+    def probe(cls, name: str) -> str:
+        """One small case of back end ``name`` (non-empty groups of 16-row multiples, one empty group, a few unused
+        rows at the end) against the fp32 loop; 'ok' or an error text."""
         from umdk_b200.models.dsv3_decoder import _quant_experts
         g = torch.Generator(device="cuda").manual_seed(7)
-        G, F, H = 3, 128, 256
+        G, F, H = 4, 128, 256
         w1q, w1s = _quant_experts(G, 2 * F, H, "cuda", g)
         w2q, w2s = _quant_experts(G, H, F, "cuda", g)
-        x = torch.randn(48, H, device="cuda", generator=g).to(torch.bfloat16)
-        offs = torch.tensor([16, 16, 40], dtype=torch.int32, device="cuda")    # an empty group, an unused tail
-        why = {}
-        for name in ("fp8_rowwise", "bf16_grouped", "bf16_bmm"):
-            try:
-                ffn = cls(w1q, w1s, w2q, w2s, backend=name, bmm_cap=32)
-                y = ffn(x, offs)[:40].float()
-                ref = ffn.loop_reference(x, offs)[:40]
-                torch.cuda.synchronize()
-                err = float((y - ref).abs().sum() / ref.abs().sum())
-                if not (err < 0.06):
-                    raise RuntimeError(f"mean relative error {err:.3f}")
-                cls._picked = name
-                cls.why_not = why
-                return name
-            except Exception as e:   # noqa: BLE001 - any failure moves on to the next back end
-                why[name] = f"{type(e).__name__}: {str(e)[:160]}"
-        raise RuntimeError(f"no grouped GEMM back end works here: {why}")
+        x = torch.randn(64, H, device="cuda", generator=g).to(torch.bfloat16)
+        offs = torch.tensor([16, 32, 32, 48], dtype=torch.int32, device="cuda")
+        ffn = cls(w1q, w1s, w2q, w2s, backend=name, bmm_cap=32)
+        y = ffn(x, offs)[:48].float()
+        ref = ffn.loop_reference(x, offs)[:48]
+        torch.cuda.synchronize()
+        err = float((y - ref).abs().sum() / ref.abs().sum())
+        return "ok" if err < 0.03 else f"mean relative error {err:.3f}"
 
     def loop_reference(self, x, offs):
         from umdk_b200.ops.reference import dequant_fp8_128x128  # noqa: F401
@@ -226,17 +238,12 @@ class GroupedFfn:
         for g in range(self.G):
             a, b = o[g], o[g + 1]
             if b > a:
-                w1 = self.w1[g].float() * (self.s1[g].unsqueeze(1) if self.backend == "fp8_rowwise" else 1.0)
-                w2 = self.w2[g].float() * (self.s2[g].unsqueeze(1) if self.backend == "fp8_rowwise" else 1.0)
+                w1, w2 = self.w1[g].float(), self.w2[g].float()
                 h1 = x[a:b].float() @ w1.t()
                 y[a:b] = (torch.nn.functional.silu(h1[:, :self.F]) * h1[:, self.F:]) @ w2.t()
         return y
 
-    def _mm(self, x, w, s, offs):
-        if self.backend == "fp8_rowwise":
-            xq, xs = quant_rowwise(x)
-            return torch._scaled_grouped_mm(xq, w.transpose(-2, -1), xs, s, offs=offs, out_dtype=torch.bfloat16,
-                                            use_fast_accum=True)
+    def _mm(self, x, w, offs):
         if self.backend == "bf16_grouped":
             return torch._grouped_mm(x, w.transpose(-2, -1), offs=offs, out_dtype=torch.bfloat16)
         # padded bmm: row i of group g sits at [g, i - start(g)]
@@ -252,9 +259,9 @@ class GroupedFfn:
     def __call__(self, x: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
         """x [M, H] bf16 rows sorted by group, offs [G] int32 cumulative group ends -> [M, H] bf16 (rows past
         offs[-1] are undefined)."""
-        h1 = self._mm(x, self.w1, getattr(self, "s1", None), offs)
+        h1 = self._mm(x, self.w1, offs)
         h = torch.nn.functional.silu(h1[:, :self.F].float()) * h1[:, self.F:].float()
-        return self._mm(h.to(torch.bfloat16), self.w2, getattr(self, "s2", None), offs)
+        return self._mm(h.to(torch.bfloat16), self.w2, offs)
 
 
 class NcclLowLatencyMoe:
