@@ -5,16 +5,27 @@
 // 576-wide latent rows of the paged cache, and the value of a key is the first 512 entries of that row. Only the
 // `topk` rows listed in `indices` take part (-1 or >= seq_len: masked).
 //
-// Mapping to the hardware: the 128 heads are exactly the M = 128 rows of one tcgen05 MMA.
-//   S[128 x 64]  = Q[128 x 576] * Kc[64 x 576]^T      36 MMAs (K = 16), Q resident in shared memory (TMA, 9 slabs)
-//   P            = online softmax of S, one head per thread of the 4 softmax warps (tcgen05.ld), bf16 into smem
-//   O[128 x 256] += P[128 x 64] * Vc[64 x 256]         4 MMAs (K = 16 keys), V read from the SAME gathered smem tile
-//                                                      through an MN-major descriptor (no second copy of K)
-// Each sequence is handled by two CTAs that own one 256-wide half of the output (O for all 512 columns plus S does
-// not fit the 512 TMEM columns) and by `num_splits` CTAs along the key list; a merge kernel joins the splits.
-// The 64 selected rows of a chunk are gathered with 16-byte cp.async into the 128-byte-swizzled layout that both
-// descriptors expect. There is no attention code in the reference project; the op is specified by the serving
-// configuration only.
+// Mapping to the hardware: the 128 heads are exactly the M = 128 rows of one tcgen05 MMA, and one sequence (one
+// split of its key list) is handled by a CLUSTER OF TWO CTAs that split the work by feature dimension:
+//   CTA 0 owns latent dims [0, 256) plus the 64 rope dims, CTA 1 owns latent dims [256, 512).
+// Per chunk of 48 selected keys each CTA
+//   gathers only ITS dims of the 48 rows (640 or 512 bytes per row; no byte of the cache is read twice),
+//   computes a PARTIAL S[128 x 48] = Q[:, own dims] * K[:, own dims]^T   (20 or 16 MMAs of K = 16),
+//   sends the partial to its partner through distributed shared memory and adds the partner's partial,
+//   runs the online softmax (one head per thread; both CTAs arrive at the same P),
+//   and accumulates its own 256 output columns O[128 x 256] += P[128 x 48] * V[48 x own latent dims]  (3 MMAs),
+//   reading V from the SAME gathered tile through an MN-major descriptor.
+// Splitting by dimension halves the resident Q (80 KB instead of 144 KB), which makes room for a three-stage ring
+// of key tiles, and halves the Q*K^T work of each SM. Roles inside a CTA (9 warps):
+//   warps 0-3  softmax: tcgen05.ld of S, exchange, exp2, P to shared memory, lazy rescale of O
+//   warp  4    one thread issues every MMA: Q*K^T of chunk c+1 is issued BEFORE P*V of chunk c, so the tensor
+//              pipe works on the next scores while the softmax of the current chunk runs (S is double-buffered)
+//   warps 5-8  gather producers: 16-byte cp.async into the 128-byte-swizzled tiles, two chunks in flight
+// All row addresses of the split are resolved once, up front, into shared memory (index -> page -> row).
+// The running maximum is only raised when it grows by more than 8 (in log2 units); P then stays below 2^8 and the
+// accumulated O needs rescaling only a few times per row instead of in most chunks.
+// Every wait is bounded; a CTA that gives up raises the abort flag of both CTAs so the partner leaves at once.
+// There is no attention code in the reference project; the op is specified by the serving configuration only.
 #include "common.h"
 #include "ptx.cuh"
 
@@ -25,17 +36,30 @@ constexpr int kHeads = 128;
 constexpr int kDim = 576;
 constexpr int kDimV = 512;
 constexpr int kPage = 64;
-constexpr int kChunk = 64;
-constexpr int kSlabs = kDim / 64;              // 9 slabs of 64 dims
-constexpr int kQSlabBytes = kHeads * 128;      // 16 KB
-constexpr int kKSlabBytes = kChunk * 128;      // 8 KB
-constexpr int kQBytes = kSlabs * kQSlabBytes;  // 147456
-constexpr int kKBytes = kSlabs * kKSlabBytes;  // 73728
-constexpr int kThreads = 256;
+constexpr int kChunk = 48;                       // keys per pipeline step
+constexpr int kStages = 3;
+constexpr int kMaxSlabs = 5;                     // 64-dim slabs per CTA: 4 latent (+ 1 rope in CTA 0)
+constexpr int kQSlabBytes = kHeads * 128;        // 16 KB
+constexpr int kKSlabBytes = kChunk * 128;        // 6 KB
+constexpr int kQBytes = kMaxSlabs * kQSlabBytes; // 81920
+constexpr int kStageBytes = kMaxSlabs * kKSlabBytes;  // 30720
+constexpr int kPBytes = kHeads * 128;            // 16 KB (96 of every 128 bytes used)
+constexpr int kXBytes = kChunk * kHeads * 4;     // 24 KB, [key][head] fp32
+constexpr int kMaxChunks = 43;                   // 2064 keys per split at most
+constexpr int kMaxKeys = kMaxChunks * kChunk;
+constexpr int kThreads = 288;
+constexpr int kProducers = 128;
 constexpr int kTmemCols = 512;
-constexpr int kColS = 0;
-constexpr int kColO = 64;
-constexpr int kSmemBytes = 1024 + kQBytes + kKBytes + 1024;
+constexpr int kColS = 0;                         // two S buffers of 64 columns (48 used)
+constexpr int kColO = 128;
+constexpr int kOffK = kQBytes;
+constexpr int kOffP = kOffK + kStages * kStageBytes;
+constexpr int kOffX = kOffP + kPBytes;
+constexpr int kOffRows = kOffX + kXBytes;
+constexpr int kOffTail = kOffRows + kMaxKeys * 4;
+constexpr int kSmemBytes = 1024 + kOffTail + 256;
+static_assert(kSmemBytes <= 232448, "shared memory budget");
+static_assert(kStageBytes % 1024 == 0 && kKSlabBytes % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
 
 struct MlaArgs {
   const __nv_bfloat16* kv;   // [num_pages, 64, 576]
@@ -51,27 +75,68 @@ struct MlaArgs {
   int* status;
 };
 
-__device__ __forceinline__ void bar_softmax() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded waits that also leave when either CTA of the pair has raised the abort flag.
+template <bool kCluster>
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!(kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity))) {
+    if ((++spins & 31u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kSpinLimitCycles) return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_sm = smem;
-  uint8_t* k_sm = smem + kQBytes;
-  uint8_t* tail = k_sm + kKBytes;
-  uint64_t* bar_q = reinterpret_cast<uint64_t*>(tail);
-  uint64_t* bar_s = bar_q + 1;
-  uint64_t* bar_o = bar_q + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 3);
-  int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
-  int* idx_sm = reinterpret_cast<int*>(tail + 64);                                   // [64]
-  const uint8_t** row_sm = reinterpret_cast<const uint8_t**>(tail + 64 + 256);        // [64]
+  uint8_t* k_sm = smem + kOffK;
+  uint8_t* p_sm = smem + kOffP;
+  float* x_sm = reinterpret_cast<float*>(smem + kOffX);
+  int* rows_sm = reinterpret_cast<int*>(smem + kOffRows);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffTail);
+  uint64_t* bar_q = bars;            // 1
+  uint64_t* bar_full = bars + 1;     // kStages, 128 producer arrivals
+  uint64_t* bar_empty = bars + 4;    // kStages, one commit
+  uint64_t* bar_s = bars + 7;        // 2, one commit
+  uint64_t* bar_sfree = bars + 9;    // 2, 128 softmax arrivals
+  uint64_t* bar_p = bars + 11;       // 128 softmax arrivals
+  uint64_t* bar_o = bars + 12;       // one commit
+  uint64_t* bar_xfull = bars + 13;   // 128 arrivals from the partner's softmax threads: its partial S has landed
+  uint64_t* bar_xfree = bars + 14;   // 128 arrivals from the partner's softmax threads: its X may be overwritten
+  uint64_t* bar_fin = bars + 15;     // one commit (drain on the abort path)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.y;
-  const int half = blockIdx.x & 1;
+  const int half = static_cast<int>(cluster_ctarank());   // == blockIdx.x & 1
   const int split = blockIdx.x >> 1;
+  const int n_slabs = half == 0 ? 5 : 4;
   const int per_split = ((a.topk + a.num_splits - 1) / a.num_splits + kChunk - 1) / kChunk * kChunk;
   const int k_begin = split * per_split;
   const int k_end = min(a.topk, k_begin + per_split);
@@ -80,221 +145,322 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(bar_s, 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&bar_full[i], kProducers);
+      mbar_init(&bar_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_s[i], 1);
+      mbar_init(&bar_sfree[i], 128);
+    }
+    mbar_init(bar_p, 128);
     mbar_init(bar_o, 1);
+    mbar_init(bar_xfull, 128);
+    mbar_init(bar_xfree, 128);
+    mbar_init(bar_fin, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
     *s_abort = 0;
   }
-  if (warp == 1) {
+  if (warp == 4) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
+  // resolve every selected row of this split once: index -> page -> row number in the pool (-1 = masked)
+  for (int k = tid; k < num_chunks * kChunk; k += kThreads) {
+    const int kpos = k_begin + k;
+    int idx = kpos < k_end ? a.indices[(size_t)b * a.topk + kpos] : -1;
+    if (idx < 0 || idx >= seq_len) idx = -1;
+    int row = -1;
+    if (idx >= 0) {
+      const int pg = idx / kPage;
+      const int page = pg < a.max_pages ? a.block_table[(size_t)b * a.max_pages + pg] : -1;
+      if (page < 0 || page >= a.num_pages) {
+        umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_NONE, b, idx);
+      } else {
+        row = page * kPage + (idx % kPage);
+      }
+    }
+    rows_sm[k] = row;
+  }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();   // the partner's barriers exist before anything is signalled across
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t peer = static_cast<uint32_t>(half ^ 1);
+  const uint32_t peer_abort = map_to_cta(const_cast<int*>(s_abort), peer);
 
-  if (tid == 0 && num_chunks > 0) {
-    mbar_expect_tx(bar_q, kQBytes);
-    for (int j = 0; j < kSlabs; ++j) tma_load_2d(q_sm + j * kQSlabBytes, &tmQ, bar_q, j * 64, b * kHeads);
-  }
+  auto give_up = [&](int phase, int detail) {
+    if (!*s_abort) umdk_set_status(a.status, UMDK_ERR_TIMEOUT, phase, b, detail);
+    *s_abort = 1;
+    st_cluster_u32(peer_abort, 1u);
+  };
 
-  // softmax state of this thread's head (softmax warps only)
-  const int head = (warp & 3) * 32 + lane;
-  float m_run = -INFINITY, l_run = 0.f;
-  const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-  uint8_t* p_sm = k_sm + (half ? 0 : 4) * kKSlabBytes;  // P lives in two slabs this CTA does not need for P*V
-
-  for (int c = 0; c < num_chunks; ++c) {
-    const uint32_t ph = c & 1;
-    // ---- 1. gather 64 key rows into the swizzled slabs ----
-    if (tid < kChunk) {
-      const int kpos = k_begin + c * kChunk + tid;
-      int idx = kpos < k_end ? a.indices[(size_t)b * a.topk + kpos] : -1;
-      if (idx < 0 || idx >= seq_len) idx = -1;
-      size_t row = 0;
-      if (idx >= 0) {
-        const int pg = idx / kPage;
-        int page = pg < a.max_pages ? a.block_table[(size_t)b * a.max_pages + pg] : -1;
-        if (page < 0 || page >= a.num_pages) {
-          umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_NONE, b, idx);
-          idx = -1;
-        } else {
-          row = (size_t)page * kPage + (idx % kPage);
-        }
-      }
-      idx_sm[tid] = idx;
-      row_sm[tid] = reinterpret_cast<const uint8_t*>(a.kv) + row * (kDim * 2);
-    }
-    __syncthreads();
-#pragma unroll 6
-    for (int it = 0; it < (kChunk * 72) / kThreads; ++it) {
-      const int i = it * kThreads + tid;
-      const int key = i / 72, ch = i - key * 72;
-      const int slab = ch >> 3, c8 = ch & 7;
-      cp_async_16(k_sm + slab * kKSlabBytes + key * 128 + ((c8 ^ (key & 7)) << 4), row_sm[key] + ch * 16);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    fence_proxy_async_smem();
-    __syncthreads();
-
-    // ---- 2. S = Q K^T ----
-    if (tid == 0) {
+  if (num_chunks > 0) {
+    if (warp < 4) {
+      // ===================================== softmax ======================================================
+      const int head = tid;   // == TMEM lane
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+      const uint32_t peer_x = map_to_cta(x_sm, peer) + static_cast<uint32_t>(head) * 4u;
+      const uint32_t peer_xfull = map_to_cta(bar_xfull, peer);
+      const uint32_t peer_xfree = map_to_cta(bar_xfree, peer);
+      float m_run = -INFINITY, l_run = 0.f;
       bool ok = true;
-      if (c == 0) ok = mbar_wait(bar_q, 0);
-      if (!ok) {
-        umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_TMA_FULL, b, 0);
-        *s_abort = 1;
-      }
-      tc_fence_after();
-      constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, kHeads, kChunk);
-#pragma unroll 1
-      for (int j = 0; j < kSlabs; ++j) {
-        const uint64_t ad = umma_desc_k_sw128(smem_u32(q_sm + j * kQSlabBytes));
-        const uint64_t bd = umma_desc_k_sw128(smem_u32(k_sm + j * kKSlabBytes));
+      for (int c = 0; c < num_chunks && ok; ++c) {
+        const int sb = c & 1;
+        if (!__all_sync(0xffffffffu, wait_bar<false>(&bar_s[sb], (c >> 1) & 1, s_abort))) {
+          give_up(UMDK_PH_TMEM_FULL, c);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t sr[kChunk];
+        tmem_ld_x16(lane_addr + kColS + sb * 64, sr);
+        tmem_ld_x16(lane_addr + kColS + sb * 64 + 16, sr + 16);
+        tmem_ld_x16(lane_addr + kColS + sb * 64 + 32, sr + 32);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&bar_sfree[sb]);
+        // partial scores to the partner, the partner's partial in
+        if (c >= 1 && !__all_sync(0xffffffffu, wait_bar<false>(bar_xfree, (c - 1) & 1, s_abort))) {
+          give_up(UMDK_PH_GROUP_READY, c);
+          ok = false;
+          break;
+        }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_f16(tmem_base + kColS, ad + 2 * k, bd + 2 * k, idesc, (j | k) ? 1u : 0u);
-      }
-      umma_commit(bar_s);
-    }
-
-    // ---- 3. online softmax, P to smem, O += P V ----
-    if (warp >= 4) {
-      if (!mbar_wait(bar_s, ph)) {
-        umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_TMEM_FULL, b, c);
-        *s_abort = 1;
-      }
-      tc_fence_after();
-      uint32_t sr[64];
-      tmem_ld_x32(lane_addr + kColS, sr);
-      tmem_ld_x32(lane_addr + kColS + 32, sr + 32);
-      tmem_ld_wait();
-      float mx = -INFINITY;
+        for (int j = 0; j < kChunk; ++j) st_cluster_f32(peer_x + j * (kHeads * 4), __uint_as_float(sr[j]));
+        mbar_arrive_cluster(peer_xfull);
+        if (!__all_sync(0xffffffffu, wait_bar<true>(bar_xfull, c & 1, s_abort))) {
+          give_up(UMDK_PH_GROUP_READY, 1000 + c);
+          ok = false;
+          break;
+        }
+        float mx = -INFINITY;
+        const int* rows_c = rows_sm + c * kChunk;
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        float s = __uint_as_float(sr[j]) * a.scale_log2;
-        if (idx_sm[j] < 0) s = -INFINITY;
-        sr[j] = __float_as_uint(s);
-        mx = fmaxf(mx, s);
-      }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);  // m_run = -inf -> 0
-      float sum = 0.f;
-      uint8_t* prow = p_sm + head * 128;
+        for (int j = 0; j < kChunk; ++j) {
+          float s = (__uint_as_float(sr[j]) + x_sm[j * kHeads + head]) * a.scale_log2;
+          if (rows_c[j] < 0) s = -INFINITY;
+          sr[j] = __float_as_uint(s);
+          mx = fmaxf(mx, s);
+        }
+        mbar_arrive_cluster(peer_xfree);
+        // lazy maximum: raise it only when it grows by more than 8 (P stays below 2^8)
+        float alpha = 1.f;
+        if (mx > m_run + 8.f || m_run == -INFINITY) {
+          const float m_new = fmaxf(m_run, mx);
+          alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+          if (m_new == -INFINITY) alpha = 1.f;   // nothing seen yet, nothing to scale
+          m_run = m_new;
+        }
+        const float m_use = m_run == -INFINITY ? 0.f : m_run;
+        float sum = 0.f;
+        uint32_t pk[kChunk / 2];
 #pragma unroll
-      for (int j8 = 0; j8 < 8; ++j8) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float p0 = exp2f(__uint_as_float(sr[j8 * 8 + 2 * q]) - m_use);
-          const float p1 = exp2f(__uint_as_float(sr[j8 * 8 + 2 * q + 1]) - m_use);
+        for (int j = 0; j < kChunk / 2; ++j) {
+          const float p0 = exp2f(__uint_as_float(sr[2 * j]) - m_use);
+          const float p1 = exp2f(__uint_as_float(sr[2 * j + 1]) - m_use);
           sum += p0 + p1;
           const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-          pk[q] = *reinterpret_cast<const uint32_t*>(&hh);
+          pk[j] = *reinterpret_cast<const uint32_t*>(&hh);
         }
-        *reinterpret_cast<uint4*>(prow + ((j8 ^ (head & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-      }
-      l_run = l_run * alpha + sum;
-      m_run = m_new;
-      // rescale the running output when the maximum moved (warp-uniform decision)
-      if (c > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < 256; c0 += 32) {
-          uint32_t o[32];
-          tmem_ld_x32(lane_addr + kColO + c0, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-          tmem_st_x32(lane_addr + kColO + c0, o);
+        l_run = l_run * alpha + sum;
+        // P(c) overwrites P(c-1) and O may be rescaled: P(c-1) * V must have finished
+        if (c >= 1 && !__all_sync(0xffffffffu, wait_bar<false>(bar_o, (c - 1) & 1, s_abort))) {
+          give_up(UMDK_PH_TMEM_EMPTY, c);
+          ok = false;
+          break;
         }
-        tmem_st_wait();
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      bar_softmax();
-      if (tid == 128) {
         tc_fence_after();
-        constexpr uint32_t idesc_pv = umma_idesc(kFmtBF16, kFmtBF16, kHeads, 256, 0, 1);
-        const uint32_t v_base = smem_u32(k_sm + (half * 4) * kKSlabBytes);
+        if (c >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < 256; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld_x32(lane_addr + kColO + c0, o);
+            tmem_ld_wait();
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {  // 16 keys per step: A advances 32 bytes, B advances two 8-key groups
-          const uint64_t ad = umma_desc_k_sw128(smem_u32(p_sm)) + 2 * k;
-          const uint64_t bd = umma_desc_mn_sw128(v_base + k * 2048, kKSlabBytes, 1024);
-          umma_f16(tmem_base + kColO, ad, bd, idesc_pv, (c | k) ? 1u : 0u);
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st_x32(lane_addr + kColO + c0, o);
+          }
+          tmem_st_wait();
         }
-        umma_commit(bar_o);
+        uint8_t* prow = p_sm + head * 128;
+#pragma unroll
+        for (int j8 = 0; j8 < kChunk / 8; ++j8)
+          *reinterpret_cast<uint4*>(prow + ((j8 ^ (head & 7)) << 4)) =
+              make_uint4(pk[4 * j8], pk[4 * j8 + 1], pk[4 * j8 + 2], pk[4 * j8 + 3]);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar_p);
       }
+      // ---- epilogue: this CTA's 256 output columns ----
+      // (every decision below is warp-uniform: the TMEM loads are warp-collective)
+      if (ok && !__all_sync(0xffffffffu, wait_bar<false>(bar_o, (num_chunks - 1) & 1, s_abort))) {
+        give_up(UMDK_PH_TMEM_EMPTY, 2000);
+        ok = false;
+      }
+      tc_fence_after();
+      if (ok) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        const float lse2 = l_run > 0.f ? m_run + log2f(l_run) : -INFINITY;
+        if (a.num_splits == 1) {
+          __nv_bfloat16* dst = a.out + ((size_t)b * kHeads + head) * kDimV + half * 256;
+#pragma unroll 1
+          for (int c0 = 0; c0 < 256; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld_x32(lane_addr + kColO + c0, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t w4[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[q * 8 + 2 * i]) * inv,
+                                                                __uint_as_float(o[q * 8 + 2 * i + 1]) * inv);
+                w4[i] = *reinterpret_cast<const uint32_t*>(&hh);
+              }
+              *reinterpret_cast<uint4*>(dst + c0 + q * 8) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+          }
+          if (half == 0 && a.lse) a.lse[(size_t)b * kHeads + head] = lse2 * 0.6931471805599453f;
+        } else {
+          float* dst = a.part_o + (((size_t)b * a.num_splits + split) * kHeads + head) * kDimV + half * 256;
+#pragma unroll 1
+          for (int c0 = 0; c0 < 256; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld_x32(lane_addr + kColO + c0, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              *reinterpret_cast<float4*>(dst + c0 + q * 4) =
+                  make_float4(__uint_as_float(o[q * 4]) * inv, __uint_as_float(o[q * 4 + 1]) * inv,
+                              __uint_as_float(o[q * 4 + 2]) * inv, __uint_as_float(o[q * 4 + 3]) * inv);
+            }
+          }
+          if (half == 0) a.part_lse[((size_t)b * a.num_splits + split) * kHeads + head] = lse2;
+        }
+      }
+    } else if (warp == 4) {
+      // ===================================== MMA issuer ===================================================
+      if (lane == 0) {
+        mbar_expect_tx(bar_q, static_cast<uint32_t>(n_slabs) * kQSlabBytes);
+        for (int j = 0; j < n_slabs; ++j) {
+          const int dim0 = j < 4 ? half * 256 + j * 64 : 512;
+          tma_load_2d(q_sm + j * kQSlabBytes, &tmQ, bar_q, dim0, b * kHeads);
+        }
+        constexpr uint32_t idesc_qk = umma_idesc(kFmtBF16, kFmtBF16, kHeads, kChunk);
+        constexpr uint32_t idesc_pv = umma_idesc(kFmtBF16, kFmtBF16, kHeads, 256, 0, 1);
+        bool ok = wait_bar<false>(bar_q, 0, s_abort);
+        if (!ok) give_up(UMDK_PH_TMA_FULL, 0);
+        auto issue_qk = [&](int c) -> bool {
+          const int st = c % kStages;
+          if (!wait_bar<false>(&bar_full[st], (c / kStages) & 1, s_abort)) {
+            give_up(UMDK_PH_TMA_FULL, 100 + c);
+            return false;
+          }
+          if (c >= 2 && !wait_bar<false>(&bar_sfree[c & 1], ((c >> 1) - 1) & 1, s_abort)) {
+            give_up(UMDK_PH_TMEM_EMPTY, 100 + c);
+            return false;
+          }
+          tc_fence_after();
+          const uint32_t d = tmem_base + kColS + (c & 1) * 64;
+          for (int j = 0; j < n_slabs; ++j) {
+            const uint64_t ad = umma_desc_k_sw128(smem_u32(q_sm + j * kQSlabBytes));
+            const uint64_t bd = umma_desc_k_sw128(smem_u32(k_sm + st * kStageBytes + j * kKSlabBytes));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_f16(d, ad + 2 * k, bd + 2 * k, idesc_qk, (j | k) ? 1u : 0u);
+          }
+          umma_commit(&bar_s[c & 1]);
+          return true;
+        };
+        if (ok) ok = issue_qk(0);
+        for (int c = 0; c < num_chunks && ok; ++c) {
+          if (c + 1 < num_chunks) ok = issue_qk(c + 1);
+          if (!ok) break;
+          if (!wait_bar<false>(bar_p, c & 1, s_abort)) {
+            give_up(UMDK_PH_GROUP_READY, 200 + c);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const int st = c % kStages;
+          const uint32_t v_base = smem_u32(k_sm + st * kStageBytes);
+#pragma unroll
+          for (int k = 0; k < kChunk / 16; ++k) {   // 16 keys per step: A advances 32 bytes, B two 8-key groups
+            const uint64_t ad = umma_desc_k_sw128(smem_u32(p_sm)) + 2 * k;
+            const uint64_t bd = umma_desc_mn_sw128(v_base + k * 2048, kKSlabBytes, 1024);
+            umma_f16(tmem_base + kColO, ad, bd, idesc_pv, (c | k) ? 1u : 0u);
+          }
+          umma_commit(&bar_empty[st]);
+          umma_commit(bar_o);
+        }
+        if (!ok) {   // leave only after every MMA already issued has retired (they read smem and write TMEM)
+          umma_commit(bar_fin);
+          mbar_wait(bar_fin, 0);
+        }
+      }
+    } else {
+      // ===================================== gather producers =============================================
+      const int p = tid - (kThreads - kProducers);
+      const int per_key = n_slabs * 8;            // 16-byte pieces per key row
+      const int items = kChunk * per_key;
+      const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(a.kv);
+      bool ok = true;
+      for (int c = 0; c < num_chunks; ++c) {
+        const int st = c % kStages;
+        // Chunk c-2 is announced BEFORE this thread may block on a free stage: the stage frees when P*V of chunk
+        // c-3 retires, that is issued behind Q*K^T of chunk c-2, and Q*K^T of chunk c-2 waits for this arrival.
+        if (c >= 2) {
+          cp_async_wait<1>();
+          fence_proxy_async_smem();
+          mbar_arrive(&bar_full[(c - 2) % kStages]);
+        }
+        if (c >= kStages && !wait_bar<false>(&bar_empty[st], ((c / kStages) - 1) & 1, s_abort)) {
+          give_up(UMDK_PH_TMA_EMPTY, c);
+          ok = false;
+          break;
+        }
+        uint8_t* stage = k_sm + st * kStageBytes;
+        const int* rows_c = rows_sm + c * kChunk;
+        for (int i = p; i < items; i += kProducers) {
+          const int key = i / per_key, ch = i - key * per_key;
+          const int slab = ch >> 3, c8 = ch & 7;
+          const int row = rows_c[key];
+          const int dim_byte = (slab < 4 ? half * 256 + slab * 64 : 512) * 2 + c8 * 16;
+          const uint8_t* src = kv_bytes + (size_t)(row < 0 ? 0 : row) * (kDim * 2) + dim_byte;
+          cp_async_16(stage + slab * kKSlabBytes + key * 128 + ((c8 ^ (key & 7)) << 4), src);
+        }
+        cp_async_commit();
+      }
+      // drain: the last two chunks (fewer when the loop ended early)
+      cp_async_wait<1>();
+      fence_proxy_async_smem();
+      if (ok && num_chunks >= 2) mbar_arrive(&bar_full[(num_chunks - 2) % kStages]);
+      cp_async_wait<0>();
+      fence_proxy_async_smem();
+      if (ok) mbar_arrive(&bar_full[(num_chunks - 1) % kStages]);
     }
-    // ---- 4. the tile (and P) may be overwritten only after P V has finished ----
-    if (!mbar_wait(bar_o, ph)) {
-      umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_TMEM_EMPTY, b, c);
-      *s_abort = 1;
-    }
-    tc_fence_after();
-    __syncthreads();
-    if (*s_abort) break;
-  }
-
-  // ---- epilogue ----
-  if (warp >= 4 && !*s_abort) {
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    const float lse2 = l_run > 0.f ? m_run + log2f(l_run) : -INFINITY;
+  } else if (warp < 4) {
+    // empty split: zeros and -inf so that the merge ignores it
+    const int head = tid;
     if (a.num_splits == 1) {
       __nv_bfloat16* dst = a.out + ((size_t)b * kHeads + head) * kDimV + half * 256;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 256; c0 += 32) {
-        uint32_t o[32];
-        if (num_chunks > 0) {
-          tmem_ld_x32(lane_addr + kColO + c0, o);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = 0;
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t pk[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[q * 8 + 2 * i]) * inv,
-                                                            __uint_as_float(o[q * 8 + 2 * i + 1]) * inv);
-            pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
-          }
-          *reinterpret_cast<uint4*>(dst + c0 + q * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        }
-      }
-      if (half == 0 && a.lse) a.lse[(size_t)b * kHeads + head] = lse2 * 0.6931471805599453f;
+      for (int c0 = 0; c0 < 256; c0 += 8) *reinterpret_cast<uint4*>(dst + c0) = make_uint4(0, 0, 0, 0);
+      if (half == 0 && a.lse) a.lse[(size_t)b * kHeads + head] = -INFINITY;
     } else {
       float* dst = a.part_o + (((size_t)b * a.num_splits + split) * kHeads + head) * kDimV + half * 256;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 256; c0 += 32) {
-        uint32_t o[32];
-        if (num_chunks > 0) {
-          tmem_ld_x32(lane_addr + kColO + c0, o);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = 0;
-        }
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          *reinterpret_cast<float4*>(dst + c0 + q * 4) =
-              make_float4(__uint_as_float(o[q * 4]) * inv, __uint_as_float(o[q * 4 + 1]) * inv,
-                          __uint_as_float(o[q * 4 + 2]) * inv, __uint_as_float(o[q * 4 + 3]) * inv);
-        }
-      }
-      if (half == 0) a.part_lse[((size_t)b * a.num_splits + split) * kHeads + head] = lse2;
+      for (int c0 = 0; c0 < 256; c0 += 4) *reinterpret_cast<float4*>(dst + c0) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (half == 0) a.part_lse[((size_t)b * a.num_splits + split) * kHeads + head] = -INFINITY;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 4) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  cluster_sync_all();   // neither CTA leaves while the other may still write into its shared memory
 }
 
 // Joins the key-list splits: out = sum_i exp2(lse_i - lse) * o_i.
@@ -328,6 +494,9 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(const float* __restrict_
 
 using namespace umdk;
 
+// Smallest num_splits the kernel accepts for a key list of `topk` entries.
+UMDK_API int umdk_sparse_mla_min_splits(int topk) { return (topk + kMaxKeys - 1) / kMaxKeys; }
+
 // q: [B, 128, 576] bf16; kv: [num_pages, 64, 576] bf16; block_table: [B, max_pages]; indices: [B, topk];
 // out: [B, 128, 512] bf16; lse: [B, 128] fp32 (may be null). part_o / part_lse: scratch for num_splits > 1
 // ([B, splits, 128, 512] and [B, splits, 128] fp32).
@@ -337,6 +506,9 @@ UMDK_API int umdk_sparse_mla_decode(const void* q, const void* kv, const int* bl
                                     int* status, void* stream) {
   if (B < 1 || topk < 1 || max_pages < 1 || num_pages < 1 || num_splits < 1) return -UMDK_ERR_BAD_ARG;
   if (num_splits > 1 && (part_o == nullptr || part_lse == nullptr)) return -UMDK_ERR_BAD_ARG;
+  // one CTA pair resolves at most kMaxKeys rows of the key list up front (see umdk_sparse_mla_min_splits)
+  if (((topk + num_splits - 1) / num_splits + kChunk - 1) / kChunk > kMaxChunks) return -UMDK_ERR_BAD_ARG;
+  if ((size_t)num_pages * kPage > 0x7fffffffull) return -UMDK_ERR_BAD_ARG;
   CUtensorMap tmQ;
   if (make_tmap_2d(&tmQ, TMAP_BF16, q, kDim, (uint64_t)B * kHeads, kDim * 2, 64, kHeads, TMAP_SW_128B))
     return -UMDK_ERR_BAD_ARG;

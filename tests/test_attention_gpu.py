@@ -28,6 +28,9 @@ def _case(B, ctx, topk, seed, frac_invalid=0.0):
     (2, 4096, 512, 2, 0.0),
     (4, 8192, 2048, 1, 0.0),
     (2, 8192, 2048, 4, 0.05),
+    (2, 32768, 2048, 1, 0.0),      # the serving benchmark's context and key count
+    (1, 8192, 4096, 1, 0.02),      # more keys than one CTA pair resolves: the wrapper raises the split count
+    (3, 300, 50, 3, 0.0),          # splits with no keys at all
 ])
 def test_sparse_mla_decode(B, ctx, topk, splits, inv):
     from umdk_b200.ops.attention import ref_sparse_mla_decode, sparse_mla_decode

@@ -73,3 +73,42 @@ def test_decoder_moe_block_matches_oracle():
     assert ref.mean_rel_err(out.float().cpu(), want) < 0.02
     assert int(cnt.sum()) == cfg.batch * cfg.top_k
     m.close()
+
+
+def test_fused_step_and_graph_replay_match_the_plain_torch_step():
+    """The step built from the fused glue kernels (residual + RMSNorm, q/kv post-processing, rotary, router) must give
+    the logits of the same step written with plain torch ops, and the CUDA-graph replay must sample the same tokens
+    as the fused step run launch by launch."""
+    from umdk_b200.models.dsv3_decoder import DecoderConfig, DecoderRank
+    cfg = DecoderConfig.tiny()
+    cfg.offload = False
+    m = DecoderRank(cfg)
+    try:
+        tokens, idx = _inputs(cfg, seed=5)
+        want = m.step_eager(tokens, idx, return_logits=True).float()
+        got = m.step_logits(tokens, idx).float()
+        torch.cuda.synchronize()
+        m.check()
+        rel = ((got - want).norm() / want.norm()).item()
+        assert rel < 2e-2, rel
+        # the router picks the same experts as softmax + topk (ties aside) with the same renormalised weights
+        from umdk_b200.ops import glue
+        g = torch.Generator().manual_seed(9)
+        logits = torch.randn(cfg.batch, cfg.n_experts, generator=g).to(torch.bfloat16).cuda()
+        ridx, rw = glue.router_topk(logits, cfg.top_k)
+        pw, pidx = torch.topk(torch.softmax(logits.float(), -1), cfg.top_k, dim=-1)
+        assert torch.equal(ridx.sort(-1).values, pidx.sort(-1).values)
+        assert torch.allclose(rw.sum(-1), torch.ones(cfg.batch, device="cuda"), atol=1e-5)
+        assert torch.allclose(rw, pw / pw.sum(-1, keepdim=True), atol=1e-5)
+        fidx, fw = glue.router_topk(logits, cfg.top_k, fold_el=4, rank=2)
+        assert torch.equal(fidx[:, :cfg.top_k], ridx + ridx // 4) and torch.all(fidx[:, -1] == 2 * 5 + 4)
+        assert torch.all(fw[:, -1] == 1.0) and torch.allclose(fw[:, :-1], rw)
+        # graphs: first call eager, second records, third replays
+        outs = [m.step(tokens, idx).clone() for _ in range(3)]
+        torch.cuda.synchronize()
+        m.check()
+        assert m._graphs is not None
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+        assert torch.equal(outs[2], torch.argmax(got, dim=-1))
+    finally:
+        m.close()

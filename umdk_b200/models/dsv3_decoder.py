@@ -6,8 +6,12 @@ on a side stream -> RMSNorm -> softmax top-k router -> expert-parallel low-laten
 GEMMs, combine fused in the down-projection epilogue) plus a shared expert. Attention is data parallel (every rank
 decodes its own batch), experts are sharded over the ranks of the EP group.
 
-Dense projections (q/kv/o, router, lm_head) are plain library GEMMs through torch.matmul. The reference project has
-no model code; the architecture and shapes come from the serving benchmark configuration.
+Dense projections (q/kv/o, router, lm_head) are plain library GEMMs through torch.matmul; everything between them
+(residual adds, RMSNorm, rotary embedding, the KV row write, the router's softmax / top-k / renormalisation) runs in
+the fused kernels of ops/glue.py, and the step is replayed as CUDA graphs: one graph per stretch between two
+attention calls (the attention launches and the event waits of the KV prefetch stay outside the graphs). The
+reference project has no model code; the architecture and shapes come from the serving benchmark configuration.
+``DecoderRank.step_eager`` is the same step written with plain torch ops (the oracle of the fused path).
 """
 from __future__ import annotations
 
@@ -20,6 +24,8 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
+from .. import _native
+from ..ops import glue
 from ..ops import reference as ref
 from ..ops.attention import DIM as KV_DIM, DIM_V, HEADS, PAGE, sparse_mla_decode
 from ..ops.ep_ll import EpLowLatency, ExpertWeights
@@ -84,10 +90,14 @@ def build_dense_weights(cfg: DecoderConfig, dev) -> dict:
     for _ in range(c.n_layers):
         L = {}
         L["attn_norm"] = torch.ones(H, device=dev, dtype=bf)
-        L["wq_a"] = lin(c.q_lora, H)
+        wq_a = lin(c.q_lora, H)
         L["q_norm"] = torch.ones(c.q_lora, device=dev, dtype=bf)
         L["wq_b"] = lin(HEADS * (c.qk_nope + c.qk_rope), c.q_lora)
-        L["wkv_a"] = lin(DIM_V + c.qk_rope, H)
+        wkv_a = lin(DIM_V + c.qk_rope, H)
+        # the two projections of the normalised hidden state share one GEMM: rows [q_a | kv_a]
+        L["w_qkv_a"] = torch.cat((wq_a, wkv_a)).contiguous()
+        L["wq_a"], L["wkv_a"] = L["w_qkv_a"][:c.q_lora], L["w_qkv_a"][c.q_lora:]
+        del wq_a, wkv_a
         L["kv_norm"] = torch.ones(DIM_V, device=dev, dtype=bf)
         L["w_uk"] = (torch.randn(HEADS, c.qk_nope, DIM_V, device=dev, generator=g) * 0.02).to(bf)
         L["w_uv"] = (torch.randn(HEADS, DIM_V, c.v_head, device=dev, generator=g) * 0.02).to(bf)
@@ -229,8 +239,13 @@ class DecoderRank:
         self.sin = torch.sin(pos * inv_freq)
         self.sm_scale = 1.0 / math.sqrt(c.qk_nope + c.qk_rope)
         self.attn_status = torch.zeros(4, dtype=torch.int32, device=dev)
-        self.kernel_launches_per_step = 0
+        self.new_row = (self.new_page * PAGE).contiguous()      # row (in units of 576 elements) of the new token
+        self._o_lat = [torch.empty(B, HEADS, DIM_V, device=dev, dtype=bf) for _ in range(c.n_layers)]
         self._prefetched = False
+        # CUDA-graph replay of the step (captured lazily by the first step() after one eager step)
+        self.use_graphs = True
+        self._graphs = None
+        self._steps_run = 0
 
     # ------------------------------------------------------------------------------------------------------------
     def _rope(self, x: torch.Tensor) -> torch.Tensor:
@@ -256,7 +271,121 @@ class DecoderRank:
                 self.kvm.prefetch(l, self.kv[l], self._dev_ids, self._host_ids[l], self.n_staging)
         self._prefetched = True
 
-    def _layer(self, l: int, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    # ---- fused path: torch GEMMs + ops/glue.py kernels --------------------------------------------------------
+    def _pre_attn(self, l: int, x: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor]):
+        """x + a + b -> (new residual, absorbed query [B, 128, 576]); also writes the new token's KV row."""
+        c, L = self.cfg, self.layers[l]
+        B = x.shape[0]
+        x, h = glue.add_rmsnorm(x, L["attn_norm"], a, b)
+        qkv = h @ L["w_qkv_a"].t()
+        qa = glue.qkv_post(qkv, c.q_lora, L["q_norm"], L["kv_norm"], self.cos, self.sin, self.kv[l], self.new_row,
+                           self.attn_status)
+        q = (qa @ L["wq_b"].t()).view(B, HEADS, c.qk_nope + c.qk_rope)
+        q_full = torch.empty(B, HEADS, KV_DIM, device=x.device, dtype=x.dtype)
+        # absorb W_uk: per head [B, nope] x [nope, 512], written straight into the latent part of q_full
+        torch.bmm(q[..., :c.qk_nope].transpose(0, 1), L["w_uk"], out=q_full[..., :DIM_V].transpose(0, 1))
+        glue.q_rope(q, c.qk_nope, self.cos, self.sin, q_full)
+        return x, q_full
+
+    def _attn(self, l: int, q_full: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        if self.kvm is not None:
+            self.kvm.wait(l)
+            if self.rows_mode:
+                indices = self._idx_remap[l]
+        sparse_mla_decode(q_full, self.kv[l], self.block_table, indices, self.sm_scale, out=self._o_lat[l],
+                          status=self.attn_status)
+        if self.kvm is not None:
+            self.kvm.release(l)
+        return self._o_lat[l]
+
+    def _post_attn(self, l: int, x: torch.Tensor, o_lat: torch.Tensor):
+        """-> (residual after attention, routed MoE output, shared-expert output or None)."""
+        c, L = self.cfg, self.layers[l]
+        B = x.shape[0]
+        o = torch.empty(B, HEADS, c.v_head, device=x.device, dtype=x.dtype)
+        torch.bmm(o_lat.transpose(0, 1), L["w_uv"], out=o.transpose(0, 1))
+        x = torch.addmm(x, o.view(B, HEADS * c.v_head), L["wo"].t())
+        _, h = glue.add_rmsnorm(x, L["ffn_norm"])
+        logits = h @ L["router"].t()
+        if c.shared_expert:
+            idx, w = glue.router_topk(logits, c.top_k, c.n_experts // self.world, self.rank)
+            moe, share, _ = self.ep.moe(h, idx, w, L["experts"], None, prefolded=True)
+        else:
+            idx, w = glue.router_topk(logits, c.top_k)
+            moe, share, _ = self.ep.moe(h, idx, w, L["experts"], L["shared"])
+        return x, moe, share
+
+    def _head(self, x, a, b):
+        _, h = glue.add_rmsnorm(x, self.final_norm, a, b)
+        return torch.argmax(h @ self.lm_head.t(), dim=-1)
+
+    def _capture(self):
+        """Records the step as n_layers + 1 CUDA graphs that share one memory pool: [embed .. q of layer 0],
+        [after attention l .. q of layer l + 1] for every l, [after the last attention .. sampled tokens]."""
+        c = self.cfg
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self._tok_in = torch.zeros(c.batch, dtype=torch.int64, device=self.device)
+        pool = torch.cuda.graph_pool_handle()
+        segs, keep = [], []
+
+        def record(fn):
+            n0 = _native.LAUNCH_COUNT
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool, capture_error_mode="thread_local"):
+                res = fn()
+            segs.append((g, _native.LAUNCH_COUNT - n0))
+            keep.append(res)
+            return res
+
+        x, q_full = record(lambda: self._pre_attn(0, self.embed[self._tok_in], None, None))
+        q_fulls = [q_full]
+        for l in range(c.n_layers - 1):
+            def mid(l=l, x=x):
+                x2, a, b = self._post_attn(l, x, self._o_lat[l])
+                return self._pre_attn(l + 1, x2, a, b)
+            x, q_full = record(mid)
+            q_fulls.append(q_full)
+
+        def last(x=x):
+            x2, a, b = self._post_attn(c.n_layers - 1, x, self._o_lat[c.n_layers - 1])
+            return self._head(x2, a, b)
+        out = record(last)
+        torch.cuda.synchronize()
+        self._graphs = dict(segs=segs, q_fulls=q_fulls, out=out, keep=keep)
+
+    def step(self, tokens: torch.Tensor, indices: List[torch.Tensor]) -> torch.Tensor:
+        """tokens [B] int64 (device), indices[l] [B, topk_kv] int32 (device) -> next tokens [B] int64 (device).
+        With ``use_graphs`` the first call runs eagerly, the second records the graphs, later calls replay them
+        (the result then lives in a buffer that the next call overwrites)."""
+        if self.kvm is not None and not self._prefetched:
+            self.prefetch(indices)
+        self._prefetched = False
+        self._steps_run += 1
+        if self.use_graphs and self._graphs is None and self._steps_run >= 2:
+            self._capture()
+        if self._graphs is not None:
+            G = self._graphs
+            self._tok_in.copy_(tokens, non_blocking=True)
+            for l in range(self.cfg.n_layers):
+                g, n = G["segs"][l]
+                g.replay()
+                _native.LAUNCH_COUNT += n
+                self._attn(l, G["q_fulls"][l], indices[l])
+            g, n = G["segs"][-1]
+            g.replay()
+            _native.LAUNCH_COUNT += n
+            return G["out"]
+        x, a, b = self.embed[tokens], None, None
+        for l in range(self.cfg.n_layers):
+            x, q_full = self._pre_attn(l, x, a, b)
+            o_lat = self._attn(l, q_full, indices[l])
+            x, a, b = self._post_attn(l, x, o_lat)
+        return self._head(x, a, b)
+
+    # ---- the same step in plain torch ops (oracle of the fused path) -----------------------------------------
+    def _layer_eager(self, l: int, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
         c, L = self.cfg, self.layers[l]
         B, H = x.shape
         h = F.rms_norm(x, (H,), L["attn_norm"])
@@ -268,14 +397,7 @@ class DecoderRank:
         self.kv[l][self.new_page, 0] = torch.cat((ckv, krope), dim=-1)
         q_lat = torch.einsum("bhd,hdc->bhc", q[..., :c.qk_nope], L["w_uk"])
         q_full = torch.cat((q_lat, self._rope(q[..., c.qk_nope:])), dim=-1).contiguous()
-        if self.kvm is not None:
-            self.kvm.wait(l)
-            if self.rows_mode:
-                indices = self._idx_remap[l]
-        o_lat, _ = sparse_mla_decode(q_full, self.kv[l], self.block_table, indices, self.sm_scale,
-                                     status=self.attn_status)
-        if self.kvm is not None:
-            self.kvm.release(l)
+        o_lat = self._attn(l, q_full, indices)
         o = torch.einsum("bhc,hcd->bhd", o_lat, L["w_uv"]).reshape(B, HEADS * c.v_head)
         x = x + o @ L["wo"].t()
         h = F.rms_norm(x, (H,), L["ffn_norm"])
@@ -288,17 +410,29 @@ class DecoderRank:
             x = x + share
         return x
 
-    def step(self, tokens: torch.Tensor, indices: List[torch.Tensor]) -> torch.Tensor:
-        """tokens [B] int64 (device), indices[l] [B, topk_kv] int32 (device) -> next tokens [B] int64 (device)."""
+    def step_eager(self, tokens: torch.Tensor, indices: List[torch.Tensor], return_logits: bool = False):
         if self.kvm is not None and not self._prefetched:
             self.prefetch(indices)
         self._prefetched = False
         x = self.embed[tokens]
         for l in range(self.cfg.n_layers):
-            x = self._layer(l, x, indices[l])
+            x = self._layer_eager(l, x, indices[l])
         x = F.rms_norm(x, (self.cfg.hidden,), self.final_norm)
         logits = x @ self.lm_head.t()
-        return torch.argmax(logits, dim=-1)
+        return logits if return_logits else torch.argmax(logits, dim=-1)
+
+    def step_logits(self, tokens: torch.Tensor, indices: List[torch.Tensor]) -> torch.Tensor:
+        """The fused path without graphs, returning the logits (for comparisons against ``step_eager``)."""
+        if self.kvm is not None and not self._prefetched:
+            self.prefetch(indices)
+        self._prefetched = False
+        x, a, b = self.embed[tokens], None, None
+        for l in range(self.cfg.n_layers):
+            x, q_full = self._pre_attn(l, x, a, b)
+            o_lat = self._attn(l, q_full, indices[l])
+            x, a, b = self._post_attn(l, x, o_lat)
+        _, h = glue.add_rmsnorm(x, self.final_norm, a, b)
+        return h @ self.lm_head.t()
 
     def check(self):
         from ..ops.ep import check_status

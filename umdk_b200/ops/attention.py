@@ -1,4 +1,5 @@
-"""Sparse top-k MLA flash-attention decode over a paged KV cache (csrc/cam/sparse_mla_decode.cu)."""
+"""Sparse top-k MLA flash-attention decode over a paged KV cache (csrc/cam/sparse_mla_decode.cu): one cluster of two
+CTAs per (sequence, key-list split), the feature dimensions divided between them."""
 from __future__ import annotations
 
 from typing import Optional, Tuple
@@ -33,6 +34,10 @@ def sparse_mla_decode(q: torch.Tensor, kv_pages: torch.Tensor, block_table: torc
     lse = torch.empty(B, HEADS, dtype=torch.float32, device=dev)
     if status is None:
         status = torch.zeros(4, dtype=torch.int32, device=dev)
+    # one CTA pair resolves at most 2064 selected rows up front: longer key lists need more splits
+    num_splits = max(num_splits, int(lib.umdk_sparse_mla_min_splits(topk)))
+    if workspace is not None and workspace[0].shape[1] != num_splits:
+        workspace = None
     po = pl = None
     if num_splits > 1:
         if workspace is None:

@@ -70,13 +70,73 @@ _PHASES = {1: "tma-empty", 2: "tma-full", 3: "tmem-full", 4: "tmem-empty", 5: "d
 _CODES = {1: "timeout", 2: "bad-argument", 3: "overflow", 4: "cuda-error"}
 
 
-def check_status(status: torch.Tensor, what: str = "kernel"):
-    """Reads the 4-int status record (synchronises) and raises if a kernel reported an error."""
+def check_status(status: torch.Tensor, what: str = "kernel", owner=None):
+    """Reads the 4-int status record (synchronises) and raises if a kernel reported an error. ``owner`` (an object
+    with the ``Recoverable`` mix-in) is marked poisoned: a kernel that gave up on a wait may have left its shared
+    counters and epoch words half-updated, so further launches are refused until ``owner.reset()``."""
     s = status.tolist()
     if s[0] != 0:
         status.zero_()
-        raise KernelStatusError(f"{what}: {_CODES.get(s[0], s[0])} in phase {_PHASES.get(s[1], s[1])} "
-                                f"(detail {s[2]}, {s[3]})")
+        msg = (f"{what}: {_CODES.get(s[0], s[0])} in phase {_PHASES.get(s[1], s[1])} "
+               f"(detail {s[2]}, {s[3]})")
+        if owner is not None:
+            owner._poisoned = msg
+        raise KernelStatusError(msg)
+
+
+class Recoverable:
+    """Mix-in for objects that own device-side protocol state (control words with epoch counters, arrival counters,
+    grid-barrier words). After a kernel reported a time-out, arrival counters may hold a partial count and the ranks'
+    epochs may differ; carrying on would make the next call's "last CTA" fire early or a flag wait pass on stale data.
+    So ``check()`` poisons the object, every launch method calls ``_guard()`` first, and ``reset()`` puts the state
+    back: all counters zero, every epoch word set to a value above anything any rank has used (agreed over the
+    process group, or passed in by a caller that drives several virtual ranks in one process)."""
+
+    _poisoned: Optional[str] = None
+    # attribute name of an int32 control tensor -> indices of its epoch words; other words are counters
+    _epoch_words: dict = {}
+    # further int32 / int64 tensors that must be zero between calls
+    _zero_between_calls: tuple = ()
+
+    def _guard(self):
+        if self._poisoned is not None:
+            raise KernelStatusError(f"object is poisoned by an earlier kernel error ({self._poisoned}); call reset()")
+
+    def max_epoch(self) -> int:
+        m = 0
+        for name, words in self._epoch_words.items():
+            t = getattr(self, name)
+            for i in words:
+                m = max(m, int(t[i].item()) & 0x7fffffff)
+        return m
+
+    def reset(self, epoch: Optional[int] = None, group=None) -> int:
+        """Clears the poison. Every rank of the group must call it (it synchronises the device and, with a process
+        group, the ranks). Returns the epoch now in force."""
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        if epoch is None:
+            epoch = self.max_epoch() + 2
+            heap = getattr(self, "heap", None)
+            group = group if group is not None else getattr(heap, "group", None)
+            if dist.is_initialized() and heap is not None and heap.world > 1 and not getattr(heap, "is_virtual", False):
+                t = torch.tensor([epoch], dtype=torch.int64, device=self.status.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+                epoch = int(t.item())
+        for name, words in self._epoch_words.items():
+            t = getattr(self, name)
+            t.zero_()
+            for i in words:
+                t[i] = epoch
+        for name in self._zero_between_calls:
+            getattr(self, name).zero_()
+        self.status.zero_()
+        torch.cuda.synchronize()
+        heap = getattr(self, "heap", None)
+        if dist.is_initialized() and heap is not None and heap.world > 1 and not getattr(heap, "is_virtual", False):
+            dist.barrier(group=group)
+        self._poisoned = None
+        return epoch
 
 
 @dataclass
@@ -150,8 +210,11 @@ def layout(topk_idx: torch.Tensor, num_experts: int, num_ranks: int, scratch=Non
     return out if out is not None else LayoutResult(npe, npr, inr.view(torch.bool), sidx, rslot)
 
 
-class EpNormal:
+class EpNormal(Recoverable):
     """State of one rank for normal-mode dispatch / combine at a fixed geometry (E, K, H, cap)."""
+
+    _epoch_words = {"ctrl": (0, 3, 8)}      # dispatch, combine, notify epochs (ep_normal.cu)
+    _zero_between_calls = ("layout_bar",)
 
     def __init__(self, heap: SymmetricHeap, num_experts: int, top_k: int, hidden: int, cap: int,
                  num_ctas: int = 0, device=None):
@@ -199,6 +262,7 @@ class EpNormal:
         """Count exchange alone: tells every peer how many rows / tokens this rank will send to each of its local
         experts and returns what this rank will receive. ``dispatch`` does the same exchange internally; call this
         when the sizes are needed first (to size buffers, or to balance load) - one launch of one CTA."""
+        self._guard()
         El = self.E // self.R
         if out is None:
             dev = self.device
@@ -226,6 +290,7 @@ class EpNormal:
                  sync_counts: bool = False) -> DispatchResult:
         """Runs notify + quantise + push + expand. ``phase_mask`` 1 / 2 run only the send / receive half (used to
         drive several virtual ranks from one process on one GPU)."""
+        self._guard()
         assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
         T, H = x.shape
         assert H == self.H and T <= self.cap
@@ -270,7 +335,7 @@ class EpNormal:
             raise RuntimeError(f"umdk_ep_dispatch failed: {rc}")
         if sync_counts and (phase_mask & 2):
             torch.cuda.current_stream().synchronize()
-            check_status(self.status, "ep_dispatch")
+            check_status(self.status, "ep_dispatch", owner=self)
             out.num_recv = int(self.mirror.host[0])
         return out
 
@@ -278,6 +343,7 @@ class EpNormal:
     def combine(self, y: torch.Tensor, disp: DispatchResult, apply_weights: bool = True, phase_mask: int = 3,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Per-rank pre-reduced combine: out[t] = sum over ranks of (sum_k w[t,k] * y_row(t,k))."""
+        self._guard()
         assert y.is_cuda and y.dtype == torch.bfloat16 and y.is_contiguous() and y.shape[1] == self.H
         T = disp.num_tokens
         if out is None:
@@ -302,6 +368,7 @@ class EpNormal:
                      topk_weights: torch.Tensor, phase_mask: int = 3, out: Optional[torch.Tensor] = None
                      ) -> torch.Tensor:
         """Row-per-(token,k) combine with the reference's stateless contract (moe_combine_prefill)."""
+        self._guard()
         T = topk_idx.shape[0]
         if out is None:
             out = torch.empty(T, self.H, dtype=torch.bfloat16, device=y.device)
@@ -321,4 +388,4 @@ class EpNormal:
         return out
 
     def check(self, what: str = "ep"):
-        check_status(self.status, what)
+        check_status(self.status, what, owner=self)

@@ -24,7 +24,7 @@ import torch
 from .. import _native
 from ..parallel.symm import SymmetricHeap
 from . import moe_gemm
-from .ep import check_status, layout as ep_layout
+from .ep import Recoverable, check_status, layout as ep_layout
 from ..utils import trace as _trace
 
 MAX_RANKS = 32
@@ -135,8 +135,11 @@ class ExpertWeights:
                              cat8(experts.w2q, shared.w2q), torch.cat((experts.w2s, shared.w2s)).contiguous())
 
 
-class EpLowLatency:
+class EpLowLatency(Recoverable):
     """Per-rank state of the low-latency MoE path at a fixed geometry."""
+
+    _epoch_words = {"ctrl": (0,)}
+    _zero_between_calls = ("layout_bar", "tile_done")
 
     def __init__(self, heap: SymmetricHeap, num_experts: int, top_k: int, hidden: int, ffn: int, t_cap: int,
                  dispatch_ctas: int = 32, gemm_ctas: int = 0, fold_shared: bool = False):
@@ -216,6 +219,7 @@ class EpLowLatency:
     # -- kernels -------------------------------------------------------------------------------------------------
     @_trace.traced("umdk.ep_ll.dispatch")
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, phase_mask: int = 3, lay=None):
+        self._guard()
         assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and topk_idx.dtype == torch.int64
         T = x.shape[0]
         assert T <= self.T_cap and x.shape[1] == self.H
@@ -332,16 +336,20 @@ class EpLowLatency:
 
     @_trace.traced("umdk.ep_ll.moe")
     def moe(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w: ExpertWeights,
-            shared: Optional[ExpertWeights] = None, out: Optional[torch.Tensor] = None, fused: bool = True):
+            shared: Optional[ExpertWeights] = None, out: Optional[torch.Tensor] = None, fused: bool = True,
+            prefolded: bool = False):
         """Full layer: returns (combine_x [T, H] bf16, share_output or None, expert_token_nums [E_local] int64).
-        ``fused`` runs both expert GEMMs and the combine as one persistent kernel; otherwise as two launches."""
+        ``fused`` runs both expert GEMMs and the combine as one persistent kernel; otherwise as two launches.
+        ``prefolded`` (fold_shared only): ``topk_idx`` / ``topk_w`` are already [T, K + 1] in the folded numbering
+        (what ``fold_routing`` or ops.glue.router_topk(fold_el=...) produce)."""
         T = x.shape[0]
         if out is None:
             out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
         if self.fold:
             assert shared is None and fused and w.w1q.shape[0] == self.E_local, \
                 "fold_shared: pass ExpertWeights.with_shared(experts, shared) as w"
-            idx, wts = self.fold_routing(topk_idx, topk_w)
+            idx, wts = (topk_idx, topk_w) if prefolded else self.fold_routing(topk_idx, topk_w)
+            assert idx.shape[1] == self.K
             share_out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
             self.dispatch(x, idx)
             self._fused(w, idx, wts, out, share_out=share_out)
@@ -376,4 +384,4 @@ class EpLowLatency:
         return g, res
 
     def check(self, what: str = "ep_ll"):
-        check_status(self.status, what)
+        check_status(self.status, what, owner=self)

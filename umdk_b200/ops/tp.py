@@ -9,7 +9,7 @@ import torch
 
 from .. import _native
 from ..parallel.symm import SymmetricHeap
-from .ep import check_status
+from .ep import Recoverable, check_status
 from ..utils import trace as _trace
 
 MAX_RANKS = 32
@@ -44,11 +44,14 @@ def _align(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
 
-class TpComm:
+class TpComm(Recoverable):
     """Per-rank state of the fused tensor-parallel GEMMs for fixed shard sizes.
 
     ``ag_gemm(x_shard [Ts, K], w [N, K]) -> [R*Ts, N]`` and ``gemm_rs(y [R*Ts, Kr], w [N, Kr]) -> [Ts, N]``.
     """
+
+    _epoch_words = {"ctrl_ag": (0,), "ctrl_rs": (0,)}
+    _zero_between_calls = ("chunk_done",)
 
     def __init__(self, heap: SymmetricHeap, ts: int, k_ag: int, n_rs: int, n_copy: int = 0, max_ctas: int = 0,
                  single_cta: bool = False):
@@ -109,6 +112,7 @@ class TpComm:
     @_trace.traced("umdk.tp.ag_gemm")
     def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                 phase_mask: int = 3) -> torch.Tensor:
+        self._guard()
         assert x_shard.dtype == torch.bfloat16 and x_shard.is_contiguous() and w.is_contiguous()
         assert x_shard.shape == (self.Ts, self.K_ag) and w.shape[1] == self.K_ag
         N = w.shape[0]
@@ -127,6 +131,7 @@ class TpComm:
     @_trace.traced("umdk.tp.gemm_rs")
     def gemm_rs(self, y: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                 phase_mask: int = 3) -> torch.Tensor:
+        self._guard()
         assert y.dtype == torch.bfloat16 and y.is_contiguous() and w.is_contiguous()
         assert y.shape[0] == self.R * self.Ts and w.shape == (self.N_rs, y.shape[1])
         if out is None:
@@ -142,15 +147,22 @@ class TpComm:
         return out
 
     def check(self):
-        check_status(self.status, "tp_gemm")
+        check_status(self.status, "tp_gemm", owner=self)
 
 
-class AllReduce:
+class AllReduce(Recoverable):
     """bf16 sum all-reduce over NVLink peer memory. ``algo``: 'one_shot' (every rank loads all peers' data),
     'two_shot' (reduce-scatter + all-gather with peer loads), 'push' (the same two stages with peer STORES only; needs
     buffers of twice the message size), 'nvls' (multimem reduce / broadcast inside NVSwitch; multicast heap), or
     'one_shot_push' (every rank stores its vector into a slot on every peer, then sums locally; needs world x the
     message size), or 'auto' (by size and heap kind)."""
+
+    _epoch_words = {"ctrl": (0,)}
+
+    def reset(self, epoch=None, group=None) -> int:
+        epoch = super().reset(epoch, group)
+        self.calls = epoch   # the host mirror of the device epoch picks the buffer parity of the next call
+        return epoch
 
     def __init__(self, heap: SymmetricHeap, max_bytes: int):
         self.lib = _native.cam()
@@ -186,6 +198,7 @@ class AllReduce:
     def __call__(self, x: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, algo: str = "auto",
                  num_ctas: int = 0, phase_mask: int = 3, in_place: bool = False, n: Optional[int] = None
                  ) -> Optional[torch.Tensor]:
+        self._guard()
         if not in_place:
             assert x.dtype == torch.bfloat16 and x.is_contiguous()
             n = x.numel()
@@ -230,4 +243,4 @@ class AllReduce:
         return out
 
     def check(self):
-        check_status(self.status, "allreduce")
+        check_status(self.status, "allreduce", owner=self)

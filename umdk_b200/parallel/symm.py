@@ -78,6 +78,7 @@ class SymmetricHeap:
             h._imported = []
             h.peer_ptrs = list(ptrs)
             h._virtual_children = []
+            h.is_virtual = True
             heaps.append(h)
         return heaps
 
