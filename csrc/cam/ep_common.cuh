@@ -141,6 +141,22 @@ __host__ __device__ inline EpLLOffsets ep_ll_offsets(const EpLLGeom& g) {
   return o;
 }
 
+// Checks and fills the low-latency geometry; 0 on success.
+inline int fill_ll_geom(EpLLGeom* g, int R, int rank, int E, int K, int H, int T_cap) {
+  if (R < 1 || R > kMaxRanks || rank < 0 || rank >= R || E < R || (E % R) || E > 1024 || K < 1 || K > kMaxTopk ||
+      H < 128 || (H % 128) || T_cap < 1)
+    return -UMDK_ERR_BAD_ARG;
+  g->R = R;
+  g->rank = rank;
+  g->E = E;
+  g->E_local = E / R;
+  g->K = K;
+  g->H = H;
+  g->T_cap = T_cap;
+  g->n_cap = ep_ll_n_cap(R, T_cap, K, E / R);
+  return 0;
+}
+
 struct PeerTable {
   uint8_t* base[kMaxRanks];
 };

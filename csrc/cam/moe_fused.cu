@@ -1,5 +1,9 @@
-// One persistent kernel for the whole expert FFN of the low-latency MoE layer, including the combine:
+// One persistent kernel for the whole low-latency MoE layer: dispatch, expert FFN and combine in ONE launch.
 //
+//   dispatch (optional prologue, ep_ll_dispatch.cuh) every CTA derives the routing layout in shared memory, the
+//          per-expert counts are all-gathered through peer memory, and all warps of the grid quantise this rank's
+//          tokens to fp8 1x128 and store them into their final slab rows on the destination ranks over NVLink;
+//          TMEM allocation, barrier set-up and descriptor prefetch of the GEMM pipeline are already done by then
 //   gate   wait (bounded) until the dispatched fp8 rows of every source rank have landed in this rank's slab
 //   phase 1  grouped gate/up GEMM (tcgen05, fp8 e4m3, TMEM) + block-scale promotion + SwiGLU + fp8 1x128 re-quant
 //   phase 2  grouped down GEMM whose epilogue stores each bf16 row straight into the token owner's combine buffer
@@ -15,9 +19,7 @@
 // fused_deep_moe.h:354-448), whose cube cores likewise wait per expert group for arrived tokens
 // (gemm/kernel/grouped_matmul_slice_m_per_token_dequant_swiglu_quant_multistage_workspace.h:271-280) - there with an
 // unbounded spin, here with a cycle budget and a status record.
-#include "ep_common.cuh"
-#include "ptx.cuh"
-#include "sync.cuh"
+#include "ep_ll_dispatch.cuh"
 
 namespace umdk {
 namespace {
@@ -54,7 +56,12 @@ struct FusedArgs {
   int T, Kt, T_cap;
   uint32_t* ctrl;          // [0] epoch (advanced here), [1] send-done, [2] reduce-done
   int w_tiled;             // weights are stored tile by tile (see umdk_moe_fused)
-  int phase_mask;          // bit0: gate + both GEMM phases + combine-send + flags; bit1: wait + reduce + epoch advance
+  int phase_mask;          // bit0: gate + both GEMM phases + combine-send + flags; bit1: wait + reduce + epoch advance;
+                           // bit2: dispatch prologue, publish counts; bit3: dispatch prologue, push rows + data flags
+  int fuse_dispatch;       // the dispatch runs inside this kernel (disp / ll_geom / ll_off are valid)
+  EpLLGeom ll_geom;
+  EpLLOffsets ll_off;
+  LLDispatchIO disp;
   int* status;
   // optional [6] global-timer stamps (ns): [0] earliest CTA start, then the latest CTA to pass: [1] the wait for the
   // dispatched rows, [2] phase 1, [3] phase 2, [4] the wait for the peers' combine flags, [5] the end of the kernel
@@ -434,7 +441,20 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
   };
   stamp(0);
 
-  if (a.wait_n > 0) {
+  bool goff_local = false;
+  if (a.fuse_dispatch && (a.phase_mask & 12)) {
+    // dispatch prologue: the operand ring is free until phase 1 and serves as its scratch
+    LLDispatchIO io = a.disp;
+    io.phase_mask = (a.phase_mask >> 2) & 3;
+    const bool sent = ll_dispatch_body<kThreads>(a.ll_geom, a.ll_off, a.peers, io, sh.ring, sh.goff);
+    goff_local = (io.phase_mask & 2) != 0 && sent;
+    fence_proxy_async_smem();   // the ring is written by TMA next
+    __syncthreads();
+    if (!sent && threadIdx.x == 0) s_ok = 0;
+    __syncthreads();
+  }
+
+  if (a.wait_n > 0 && (a.phase_mask & 1)) {
     if (threadIdx.x < a.wait_n) {
       if (!wait_flag_ge_sys(a.wait_flags + threadIdx.x, tag)) {
         umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_GROUP_READY, threadIdx.x, (int)epoch);
@@ -444,7 +464,10 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
     __syncthreads();
   }
   stamp(1);
-  for (int i = threadIdx.x; i <= a.G; i += blockDim.x) sh.goff[i] = a.group_off[i];
+  // group offsets: from the prologue of this launch (every CTA computed them) or from an earlier dispatch launch
+  if (!goff_local) {
+    for (int i = threadIdx.x; i <= a.G; i += blockDim.x) sh.goff[i] = a.group_off[i];
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -613,6 +636,11 @@ struct UmdkMoeFusedParams {
   int phase_mask;
   int* status;
   unsigned long long* diag;   // optional timeline, see FusedArgs::diag
+  // dispatch inside the kernel (disp_x != null): this rank's tokens and the routed geometry; phase_mask bits 2 / 3
+  const void* disp_x;         // bf16 [T, H]
+  int E;                      // experts over all ranks (G * R)
+  int64_t* recv_per_expert;   // out [G]
+  int* group_off_out;         // out [G + 1] (may be the same array as group_off)
 };
 
 // Weight layouts. Row-major (w_tiled = 0): every 128 x 128-byte weight tile that a k-block needs is 128 separate
@@ -657,6 +685,30 @@ UMDK_API int umdk_moe_fused(const UmdkMoeFusedParams* p, void* stream) {
   a.w_tiled = p->w_tiled;
   a.status = p->status;
   a.diag = p->diag;
+  a.fuse_dispatch = p->disp_x != nullptr ? 1 : 0;
+  if (a.fuse_dispatch) {
+    if (p->E != p->G * p->R || p->T > 2048 || p->T > p->T_cap || !p->recv_per_expert || !p->group_off_out)
+      return -UMDK_ERR_BAD_ARG;
+    if (int rc = fill_ll_geom(&a.ll_geom, p->R, p->rank, p->E, p->Kt, p->H, p->T_cap)) return rc;
+    if (a.ll_geom.n_cap != p->n_rows_cap) return -UMDK_ERR_BAD_ARG;
+    a.ll_off = ep_ll_offsets(a.ll_geom);
+    if (ll_dispatch_smem_bytes(p->T, p->E, p->Kt, kThreads / 32, true) > (size_t)kRingBytes) return -UMDK_ERR_BAD_ARG;
+    a.disp.x = static_cast<const __nv_bfloat16*>(p->disp_x);
+    a.disp.topk_idx = p->topk_idx;
+    a.disp.send_idx = nullptr;
+    a.disp.num_per_expert = nullptr;
+    a.disp.T = p->T;
+    a.disp.group_off = p->group_off_out;
+    a.disp.recv_per_expert = p->recv_per_expert;
+    a.disp.ctrl = p->ctrl;
+    a.disp.status = p->status;
+    a.disp.phase_mask = 3;
+  } else {
+    if (a.phase_mask & 12) return -UMDK_ERR_BAD_ARG;
+    a.ll_geom = EpLLGeom{};
+    a.ll_off = EpLLOffsets{};
+    a.disp = LLDispatchIO{};
+  }
   CUtensorMap tmW1, tmX, tmW2, tmH;
   int bad;
   if (p->w_tiled) {

@@ -73,6 +73,11 @@ struct MlaArgs {
   int B, topk, max_pages, num_pages, num_splits;
   float scale_log2;
   int* status;
+  // optional [16] cycle counters of the first CTA (diagnose mode): softmax thread 0: [0] wait S, [1] TMEM load,
+  // [2] wait partner-free, [3] remote stores, [4] wait partner's partial, [5] add + max + exp2, [6] wait P*V, [7] P
+  // store (+ rescale); MMA thread: [8] wait tile, [9] wait S buffer, [10] wait P, [11] issue; producer thread 0:
+  // [12] wait landed, [13] wait free stage, [14] issue; [15] total cycles of the CTA
+  long long* diag;
 };
 
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
@@ -120,14 +125,17 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
   int* rows_sm = reinterpret_cast<int*>(smem + kOffRows);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffTail);
   uint64_t* bar_q = bars;            // 1
-  uint64_t* bar_full = bars + 1;     // kStages, 128 producer arrivals
+  // Arrivals are one per WARP: the lanes order their own accesses before a __syncwarp() and lane 0 arrives, so a
+  // barrier sees 4 arrivals per phase instead of 128 (128 arrivals on one barrier, remote ones above all, cost
+  // more than the work they guard).
+  uint64_t* bar_full = bars + 1;     // kStages, 4 producer-warp arrivals
   uint64_t* bar_empty = bars + 4;    // kStages, one commit
   uint64_t* bar_s = bars + 7;        // 2, one commit
-  uint64_t* bar_sfree = bars + 9;    // 2, 128 softmax arrivals
-  uint64_t* bar_p = bars + 11;       // 128 softmax arrivals
+  uint64_t* bar_sfree = bars + 9;    // 2, 4 softmax-warp arrivals
+  uint64_t* bar_p = bars + 11;       // 4 softmax-warp arrivals
   uint64_t* bar_o = bars + 12;       // one commit
-  uint64_t* bar_xfull = bars + 13;   // 128 arrivals from the partner's softmax threads: its partial S has landed
-  uint64_t* bar_xfree = bars + 14;   // 128 arrivals from the partner's softmax threads: its X may be overwritten
+  uint64_t* bar_xfull = bars + 13;   // 4 arrivals from the partner's softmax warps: its partial S has landed
+  uint64_t* bar_xfree = bars + 14;   // 4 arrivals from the partner's softmax warps: its X may be overwritten
   uint64_t* bar_fin = bars + 15;     // one commit (drain on the abort path)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -146,17 +154,17 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
   if (tid == 0) {
     mbar_init(bar_q, 1);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(&bar_full[i], kProducers);
+      mbar_init(&bar_full[i], kProducers / 32);
       mbar_init(&bar_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_s[i], 1);
-      mbar_init(&bar_sfree[i], 128);
+      mbar_init(&bar_sfree[i], 4);
     }
-    mbar_init(bar_p, 128);
+    mbar_init(bar_p, 4);
     mbar_init(bar_o, 1);
-    mbar_init(bar_xfull, 128);
-    mbar_init(bar_xfree, 128);
+    mbar_init(bar_xfull, 4);
+    mbar_init(bar_xfree, 4);
     mbar_init(bar_fin, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -207,6 +215,16 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
       const uint32_t peer_xfree = map_to_cta(bar_xfree, peer);
       float m_run = -INFINITY, l_run = 0.f;
       bool ok = true;
+      const bool dg = a.diag != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
+      long long dt[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      long long t_prev = dg ? clock64() : 0;
+      auto lap = [&](int i) {
+        if (dg) {
+          const long long t = clock64();
+          dt[i] += t - t_prev;
+          t_prev = t;
+        }
+      };
       for (int c = 0; c < num_chunks && ok; ++c) {
         const int sb = c & 1;
         if (!__all_sync(0xffffffffu, wait_bar<false>(&bar_s[sb], (c >> 1) & 1, s_abort))) {
@@ -214,6 +232,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
           ok = false;
           break;
         }
+        lap(0);
         tc_fence_after();
         uint32_t sr[kChunk];
         tmem_ld_x16(lane_addr + kColS + sb * 64, sr);
@@ -221,21 +240,27 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
         tmem_ld_x16(lane_addr + kColS + sb * 64 + 32, sr + 32);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(&bar_sfree[sb]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_sfree[sb]);
+        lap(1);
         // partial scores to the partner, the partner's partial in
         if (c >= 1 && !__all_sync(0xffffffffu, wait_bar<false>(bar_xfree, (c - 1) & 1, s_abort))) {
           give_up(UMDK_PH_GROUP_READY, c);
           ok = false;
           break;
         }
+        lap(2);
 #pragma unroll
         for (int j = 0; j < kChunk; ++j) st_cluster_f32(peer_x + j * (kHeads * 4), __uint_as_float(sr[j]));
-        mbar_arrive_cluster(peer_xfull);
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(peer_xfull);   // release.cluster: cumulative over the warp's stores
+        lap(3);
         if (!__all_sync(0xffffffffu, wait_bar<true>(bar_xfull, c & 1, s_abort))) {
           give_up(UMDK_PH_GROUP_READY, 1000 + c);
           ok = false;
           break;
         }
+        lap(4);
         float mx = -INFINITY;
         const int* rows_c = rows_sm + c * kChunk;
 #pragma unroll
@@ -245,7 +270,8 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
           sr[j] = __float_as_uint(s);
           mx = fmaxf(mx, s);
         }
-        mbar_arrive_cluster(peer_xfree);
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(peer_xfree);
         // lazy maximum: raise it only when it grows by more than 8 (P stays below 2^8)
         float alpha = 1.f;
         if (mx > m_run + 8.f || m_run == -INFINITY) {
@@ -266,12 +292,14 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
           pk[j] = *reinterpret_cast<const uint32_t*>(&hh);
         }
         l_run = l_run * alpha + sum;
+        lap(5);
         // P(c) overwrites P(c-1) and O may be rescaled: P(c-1) * V must have finished
         if (c >= 1 && !__all_sync(0xffffffffu, wait_bar<false>(bar_o, (c - 1) & 1, s_abort))) {
           give_up(UMDK_PH_TMEM_EMPTY, c);
           ok = false;
           break;
         }
+        lap(6);
         tc_fence_after();
         if (c >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
@@ -292,7 +320,12 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
               make_uint4(pk[4 * j8], pk[4 * j8 + 1], pk[4 * j8 + 2], pk[4 * j8 + 3]);
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(bar_p);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p);
+        lap(7);
+      }
+      if (dg) {
+        for (int i = 0; i < 8; ++i) a.diag[i] = dt[i];
       }
       // ---- epilogue: this CTA's 256 output columns ----
       // (every decision below is warp-uniform: the TMEM loads are warp-collective)
@@ -353,16 +386,29 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
         constexpr uint32_t idesc_pv = umma_idesc(kFmtBF16, kFmtBF16, kHeads, 256, 0, 1);
         bool ok = wait_bar<false>(bar_q, 0, s_abort);
         if (!ok) give_up(UMDK_PH_TMA_FULL, 0);
+        const bool dg = a.diag != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+        long long dt[4] = {0, 0, 0, 0};
+        const long long t_begin = dg ? clock64() : 0;
+        long long t_prev = t_begin;
+        auto lap = [&](int i) {
+          if (dg) {
+            const long long t = clock64();
+            dt[i] += t - t_prev;
+            t_prev = t;
+          }
+        };
         auto issue_qk = [&](int c) -> bool {
           const int st = c % kStages;
           if (!wait_bar<false>(&bar_full[st], (c / kStages) & 1, s_abort)) {
             give_up(UMDK_PH_TMA_FULL, 100 + c);
             return false;
           }
+          lap(0);
           if (c >= 2 && !wait_bar<false>(&bar_sfree[c & 1], ((c >> 1) - 1) & 1, s_abort)) {
             give_up(UMDK_PH_TMEM_EMPTY, 100 + c);
             return false;
           }
+          lap(1);
           tc_fence_after();
           const uint32_t d = tmem_base + kColS + (c & 1) * 64;
           for (int j = 0; j < n_slabs; ++j) {
@@ -372,6 +418,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
             for (int k = 0; k < 4; ++k) umma_f16(d, ad + 2 * k, bd + 2 * k, idesc_qk, (j | k) ? 1u : 0u);
           }
           umma_commit(&bar_s[c & 1]);
+          lap(3);
           return true;
         };
         if (ok) ok = issue_qk(0);
@@ -383,6 +430,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
             ok = false;
             break;
           }
+          lap(2);
           tc_fence_after();
           const int st = c % kStages;
           const uint32_t v_base = smem_u32(k_sm + st * kStageBytes);
@@ -394,6 +442,11 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
           }
           umma_commit(&bar_empty[st]);
           umma_commit(bar_o);
+          lap(3);
+        }
+        if (dg) {
+          for (int i = 0; i < 4; ++i) a.diag[8 + i] = dt[i];
+          a.diag[15] = clock64() - t_begin;
         }
         if (!ok) {   // leave only after every MMA already issued has retired (they read smem and write TMEM)
           umma_commit(bar_fin);
@@ -407,6 +460,16 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
       const int items = kChunk * per_key;
       const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(a.kv);
       bool ok = true;
+      const bool dg = a.diag != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && p == 0;
+      long long dt[3] = {0, 0, 0};
+      long long t_prev = dg ? clock64() : 0;
+      auto lap = [&](int i) {
+        if (dg) {
+          const long long t = clock64();
+          dt[i] += t - t_prev;
+          t_prev = t;
+        }
+      };
       for (int c = 0; c < num_chunks; ++c) {
         const int st = c % kStages;
         // Chunk c-2 is announced BEFORE this thread may block on a free stage: the stage frees when P*V of chunk
@@ -414,13 +477,16 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
         if (c >= 2) {
           cp_async_wait<1>();
           fence_proxy_async_smem();
-          mbar_arrive(&bar_full[(c - 2) % kStages]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_full[(c - 2) % kStages]);
         }
+        lap(0);
         if (c >= kStages && !wait_bar<false>(&bar_empty[st], ((c / kStages) - 1) & 1, s_abort)) {
           give_up(UMDK_PH_TMA_EMPTY, c);
           ok = false;
           break;
         }
+        lap(1);
         uint8_t* stage = k_sm + st * kStageBytes;
         const int* rows_c = rows_sm + c * kChunk;
         for (int i = p; i < items; i += kProducers) {
@@ -432,14 +498,20 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
           cp_async_16(stage + slab * kKSlabBytes + key * 128 + ((c8 ^ (key & 7)) << 4), src);
         }
         cp_async_commit();
+        lap(2);
+      }
+      if (dg) {
+        for (int i = 0; i < 3; ++i) a.diag[12 + i] = dt[i];
       }
       // drain: the last two chunks (fewer when the loop ended early)
       cp_async_wait<1>();
       fence_proxy_async_smem();
-      if (ok && num_chunks >= 2) mbar_arrive(&bar_full[(num_chunks - 2) % kStages]);
+      __syncwarp();
+      if (ok && num_chunks >= 2 && lane == 0) mbar_arrive(&bar_full[(num_chunks - 2) % kStages]);
       cp_async_wait<0>();
       fence_proxy_async_smem();
-      if (ok) mbar_arrive(&bar_full[(num_chunks - 1) % kStages]);
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(&bar_full[(num_chunks - 1) % kStages]);
     }
   } else if (warp < 4) {
     // empty split: zeros and -inf so that the merge ignores it
@@ -503,7 +575,7 @@ UMDK_API int umdk_sparse_mla_min_splits(int topk) { return (topk + kMaxKeys - 1)
 UMDK_API int umdk_sparse_mla_decode(const void* q, const void* kv, const int* block_table, const int* indices,
                                     const int* seq_lens, void* out, float* lse, float* part_o, float* part_lse,
                                     int B, int topk, int max_pages, int num_pages, int num_splits, float sm_scale,
-                                    int* status, void* stream) {
+                                    int* status, void* stream, long long* diag) {
   if (B < 1 || topk < 1 || max_pages < 1 || num_pages < 1 || num_splits < 1) return -UMDK_ERR_BAD_ARG;
   if (num_splits > 1 && (part_o == nullptr || part_lse == nullptr)) return -UMDK_ERR_BAD_ARG;
   // one CTA pair resolves at most kMaxKeys rows of the key list up front (see umdk_sparse_mla_min_splits)
@@ -534,6 +606,7 @@ UMDK_API int umdk_sparse_mla_decode(const void* q, const void* kv, const int* bl
   a.num_splits = num_splits;
   a.scale_log2 = sm_scale * 1.4426950408889634f;
   a.status = status;
+  a.diag = diag;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(2 * num_splits, B);
   sparse_mla_decode_kernel<<<grid, kThreads, kSmemBytes, s>>>(tmQ, a);

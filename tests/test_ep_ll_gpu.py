@@ -30,7 +30,7 @@ def _inputs(R, T, H, E, K, seed):
     return xs, idxs, ws
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "with_dispatch"])
 @pytest.mark.parametrize("R,T,H,F,E,K", [
     (1, 16, 512, 256, 4, 2),
     (2, 40, 1024, 256, 8, 2),
@@ -55,11 +55,19 @@ def test_low_latency_moe_virtual_ranks(R, T, H, F, E, K, fused):
         di = [i.cuda() for i in idxs]
         dw = [w.cuda() for w in ws]
         for rnd in range(2):
-            lays = [st[r].dispatch(dx[r], di[r], phase_mask=1) for r in range(R)]
-            for r in range(R):
-                st[r].dispatch(dx[r], di[r], phase_mask=2, lay=lays[r])
             outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
-            if fused:
+            if fused == "with_dispatch":
+                # the dispatch runs inside the fused kernel: its two phases, then the kernel's own two, rank by rank
+                for pm in (4, 8, 1, 2):
+                    for r in range(R):
+                        st[r]._fused(wts[r], di[r], dw[r], outs[r], phase_mask=pm, x=dx[r])
+            else:
+                lays = [st[r].dispatch(dx[r], di[r], phase_mask=1) for r in range(R)]
+                for r in range(R):
+                    st[r].dispatch(dx[r], di[r], phase_mask=2, lay=lays[r])
+            if fused == "with_dispatch":
+                pass
+            elif fused:
                 for r in range(R):
                     st[r]._fused(wts[r], di[r], dw[r], outs[r], phase_mask=1)
                 for r in range(R):

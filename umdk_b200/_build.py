@@ -62,6 +62,21 @@ def _targets():
         t["urma_cuda_ipc"] = dict(kind="cuda_shared", sources=cu_prov, includes=[CSRC / "urma", CSRC / "common"],
                                   libs=["-lcudart", "-L" + str(LIB), "-Xlinker", "-rpath=$ORIGIN/..", "-lumdk_urma",
                                         "-lpthread"], deps=["umdk_urma"], out=LIB / "urma" / "liburma-cuda-ipc.so")
+    # operator library for torch (schemas + Meta shape functions + Autograd registration): needs torch's headers
+    tx = sorted((CSRC / "torch_ext").glob("*.cpp"))
+    if tx:
+        try:
+            import torch
+            from torch.utils import cpp_extension as _ce
+            tinc = [Path(p) for p in _ce.include_paths()]
+            tlib = Path(torch.__file__).resolve().parent / "lib"
+            t["umdk_cam_torch"] = dict(
+                kind="cxx_shared", sources=tx, includes=tinc,
+                cxxflags=["-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI), "-Wno-attributes"],
+                libs=["-L" + str(tlib), "-Wl,-rpath," + str(tlib), "-ltorch", "-ltorch_cpu", "-lc10"],
+                out=LIB / "libumdk_cam_torch.so")
+        except Exception:   # no torch in this interpreter: the Python package then registers the schemas itself
+            pass
     pre = CSRC / "usock" / "ums_preload.cpp"
     if pre.exists():
         t["ums_preload"] = dict(kind="cxx_shared", sources=[pre], includes=[CSRC / "usock", CSRC / "common"],
@@ -112,7 +127,7 @@ def _compile_one(src: Path, tgt: dict, force: bool, verbose: bool, hdr_digest: s
         cmd = [NVCC, "-O2", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden", *inc, "-c", str(src), "-o",
                str(obj)]
     else:
-        cmd = [CXX, *CXX_FLAGS, *inc, "-c", str(src), "-o", str(obj)]
+        cmd = [CXX, *CXX_FLAGS, *tgt.get("cxxflags", []), *inc, "-c", str(src), "-o", str(obj)]
     _run(cmd, verbose, log_path=obj.with_suffix(".log"))
     stamp.write_text(key)
     return obj
@@ -126,7 +141,7 @@ def build_all(force: bool = False, verbose: bool = False, only=None) -> dict:
     OBJ.mkdir(parents=True, exist_ok=True)
     targets = _targets()
     order = ["umdk_cam", "umdk_urma", "urma_cuda_ipc", "umdk_umq", "umdk_usock", "umdk_dlock", "umdk_urpc",
-             "ums_preload"]
+             "ums_preload", "umdk_cam_torch"]
     order += [n for n in targets if n.startswith("tool_")]
     outs = {}
     # compile all objects of all targets in parallel first

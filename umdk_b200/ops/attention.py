@@ -17,10 +17,12 @@ PAGE = 64
 def sparse_mla_decode(q: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor, indices: torch.Tensor,
                       sm_scale: float, seq_lens: Optional[torch.Tensor] = None, num_splits: int = 1,
                       out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-                      workspace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
-                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+                      workspace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                      diag: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """q [B,128,576] bf16, kv_pages [P,64,576] bf16, block_table [B,max_pages] int32, indices [B,topk] int32
-    (token positions; -1 = unused) -> (out [B,128,512] bf16, lse [B,128] fp32)."""
+    (token positions; -1 = unused) -> (out [B,128,512] bf16, lse [B,128] fp32).
+    ``diag`` (int64 [16], device): the first CTA records how many cycles its roles spent in each of their waits and
+    work sections (see MlaArgs::diag in the kernel source); for finding what bounds the pipeline."""
     lib = _native.cam()
     assert q.is_cuda and q.dtype == torch.bfloat16 and q.is_contiguous() and q.shape[1:] == (HEADS, DIM)
     assert kv_pages.dtype == torch.bfloat16 and kv_pages.is_contiguous() and kv_pages.shape[1:] == (PAGE, DIM)
@@ -49,7 +51,7 @@ def sparse_mla_decode(q: torch.Tensor, kv_pages: torch.Tensor, block_table: torc
         _native.ptr(q), _native.ptr(kv_pages), _native.ptr(block_table), _native.ptr(indices),
         _native.ptr(seq_lens), _native.ptr(out), _native.ptr(lse), _native.ptr(po), _native.ptr(pl),
         B, topk, block_table.shape[1], kv_pages.shape[0], num_splits, ctypes.c_float(sm_scale),
-        _native.ptr(status), _native.stream_ptr())
+        _native.ptr(status), _native.stream_ptr(), _native.ptr(diag))
     if rc != 0:
         raise RuntimeError(f"umdk_sparse_mla_decode failed: {rc}")
     return out, lse

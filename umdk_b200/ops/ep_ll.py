@@ -1,12 +1,12 @@
 """Low-latency (decode) expert-parallel MoE layer on the GPU: dispatch -> grouped fp8 GEMM1 + SwiGLU + re-quant ->
 grouped fp8 GEMM2 whose epilogue stores rows into the token owners' combine buffers -> top-k weighted reduction.
 
-Kernel chain per call (all on the caller's stream, capturable in a CUDA graph):
-  ep_layout           bucket positions of (token, k) per expert
-  ep_ll_dispatch      count all-gather + fp8 1x128 quantisation + direct push into the destination slab rows
-  moe_fused           waits for the arrival flags, gate/up projection + SwiGLU + fp8 re-quantisation, down projection
-                      with the combine-send epilogue, completion flags, owner-side weighted reduction: one launch
-                      (or, with fused=False, moe_gemm mode 0 followed by moe_gemm mode 2)
+One launch per call (on the caller's stream, capturable in a CUDA graph): ``moe_fused`` runs the dispatch as its
+prologue (routing layout in shared memory, count all-gather, fp8 1x128 quantisation, direct push into the destination
+slab rows), waits for the arrival flags, then gate/up projection + SwiGLU + fp8 re-quantisation, down projection with
+the combine-send epilogue, completion flags and the owner-side weighted reduction. The stages also exist as separate
+launches (``dispatch`` = ep_ll_dispatch, ``fuse_dispatch=False``; ``fused=False`` = moe_gemm mode 0 then mode 2), which
+is how tests drive several emulated ranks on one GPU and what ``Buffer.low_latency_dispatch`` uses.
 The shared expert (if any) runs through the same GEMM kernels on the locally quantised tokens.
 
 Mirrors the contract of the reference's ``fused_deep_moe`` (src/cam/comm_operator/pybind/fused_deep_moe.cpp:30-83;
@@ -62,6 +62,8 @@ class _MoeFusedParams(ctypes.Structure):
         ("row_meta", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p), ("topk_w", ctypes.c_void_p),
         ("out", ctypes.c_void_p), ("share_out", ctypes.c_void_p), ("ctrl", ctypes.c_void_p),
         ("phase_mask", ctypes.c_int), ("status", ctypes.c_void_p), ("diag", ctypes.c_void_p),
+        ("disp_x", ctypes.c_void_p), ("E", ctypes.c_int), ("recv_per_expert", ctypes.c_void_p),
+        ("group_off_out", ctypes.c_void_p),
     ]
 
 
@@ -168,6 +170,7 @@ class EpLowLatency(Recoverable):
         self.diagnose = False
         self.diag_fused = torch.zeros(6, dtype=torch.int64, device=dev)
         self.inline_layout = True   # False: run the layout kernel as a launch of its own before every dispatch
+        self.fuse_dispatch = True   # moe(): the dispatch runs inside the fused kernel (one launch per layer)
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
         self.layout_bar = torch.zeros(2, dtype=torch.int32, device=dev)
         self.layout_scratch = torch.empty(((t_cap + 31) // 32) * (num_experts + self.R), dtype=torch.int32, device=dev)
@@ -300,10 +303,22 @@ class EpLowLatency(Recoverable):
         names = ("rows_ready", "phase1", "phase2", "peers_done", "end")
         return {n: (d[i + 1] - d[0]) / 1e3 for i, n in enumerate(names)}
 
-    def _fused(self, w: ExpertWeights, topk_idx, topk_w, out, phase_mask: int = 3, share_out=None):
+    def can_fuse_dispatch(self, T: int) -> bool:
+        """The in-kernel dispatch derives the layout in shared memory (16-bit tables inside the operand ring)."""
+        return T <= 2048 and self.E <= 1024 and \
+            64 + 16 * self.E + 2 * (((T + 31) // 32) * self.E + 2 * T * self.K) + 3072 <= 160 * 1024
+
+    def _fused(self, w: ExpertWeights, topk_idx, topk_w, out, phase_mask: int = 3, share_out=None, x=None):
         """GEMM1 + SwiGLU + re-quant + GEMM2 + combine-send + weighted reduction in ONE persistent launch
-        (csrc/cam/moe_fused.cu)."""
+        (csrc/cam/moe_fused.cu). With ``x`` (this rank's bf16 tokens) the dispatch runs inside the same launch:
+        phase_mask bit 2 publishes the counts, bit 3 pushes the rows, bit 0 / bit 1 as without it (15 = everything)."""
+        self._guard()
         p = _MoeFusedParams()
+        if x is not None:
+            assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape == (topk_idx.shape[0], self.H)
+            assert self.can_fuse_dispatch(x.shape[0])
+            p.disp_x, p.E = x.data_ptr(), self.E
+            p.recv_per_expert, p.group_off_out = self.recv_per_expert.data_ptr(), self.group_off.data_ptr()
         p.G, p.F, p.H, p.n_rows_cap, p.max_ctas = self.E_local, self.F, self.H, self.n_cap, self.gemm_ctas
         p.w_tiled = 1 if w.tiled else 0
         p.w1, p.w1s, p.w2, p.w2s = w.w1q.data_ptr(), w.w1s.data_ptr(), w.w2q.data_ptr(), w.w2s.data_ptr()
@@ -351,12 +366,19 @@ class EpLowLatency(Recoverable):
             idx, wts = (topk_idx, topk_w) if prefolded else self.fold_routing(topk_idx, topk_w)
             assert idx.shape[1] == self.K
             share_out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
-            self.dispatch(x, idx)
-            self._fused(w, idx, wts, out, share_out=share_out)
+            if self.fuse_dispatch and self.inline_layout and self.can_fuse_dispatch(T):
+                self._fused(w, idx, wts, out, share_out=share_out, x=x, phase_mask=15)
+            else:
+                self.dispatch(x, idx)
+                self._fused(w, idx, wts, out, share_out=share_out)
             return out, share_out, self.recv_per_expert[:self.E_local - 1]
-        self.dispatch(x, topk_idx)
+        one_launch = fused and self.fuse_dispatch and self.inline_layout and self.can_fuse_dispatch(T)
+        if not one_launch:
+            self.dispatch(x, topk_idx)
         share_out = self.shared_expert(x, shared) if shared is not None else None
-        if fused:
+        if one_launch:
+            self._fused(w, topk_idx, topk_w, out, x=x, phase_mask=15)
+        elif fused:
             self._fused(w, topk_idx, topk_w, out)
         else:
             assert not w.tiled, "the two-launch path reads row-major weights"

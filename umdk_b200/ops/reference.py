@@ -227,6 +227,16 @@ def mean_rel_err(a: torch.Tensor, ref: torch.Tensor) -> float:
     return float(((a - ref).abs().sum() / ref.abs().sum().clamp_min(1e-12)))
 
 
+def max_row_rel_err(a: torch.Tensor, ref: torch.Tensor) -> float:
+    """Largest per-row relative error sum|a - ref| / sum|ref|: one wrong or missing row shows up here even when the
+    mean over the whole tensor hides it."""
+    a = a.double()
+    ref = ref.double()
+    num = (a - ref).abs().sum(dim=-1)
+    den = ref.abs().sum(dim=-1).clamp_min(1e-12)
+    return float((num / den).max())
+
+
 # ------------------------------------------------------------------------------------------------------------------
 # expert FFN (fp8 block-scaled) reference
 # ------------------------------------------------------------------------------------------------------------------
@@ -289,3 +299,27 @@ def ref_fused_moe(x, topk_idx, topk_w, w1q, w1s, w2q, w2s):
         y2 = (dequant_fp8_1x128(hq, hs) @ w2.t()).to(torch.bfloat16).float()
         out.index_add_(0, t, y2 * w[t, k].unsqueeze(1))
     return out
+
+
+def ref_moe_unquantised(x, topk_idx, topk_w, w1q, w1s, w2q, w2s):
+    """The same layer computed in fp32 from the bf16 activations WITHOUT quantising them (the fp8 weights are what
+    the model stores, so they are used as given): the yardstick of the reference's accuracy requirement
+    (doc/en/cam/CAM API Guide.md:146-148: mean relative error of combine_x against an unquantised computation)."""
+    T, K = topk_idx.shape
+    xf = x.float().cpu()
+    F = w1q.shape[1] // 2
+    out = torch.zeros(T, w2q.shape[1], dtype=torch.float32)
+    idx = topk_idx.cpu()
+    w = topk_w.cpu().float()
+    for e in torch.unique(idx).tolist():
+        if e < 0:
+            continue
+        tk = torch.nonzero(idx == e)
+        t, k = tk[:, 0], tk[:, 1]
+        w1 = dequant_fp8_128x128(w1q[e].cpu(), w1s[e].cpu())
+        w2 = dequant_fp8_128x128(w2q[e].cpu(), w2s[e].cpu())
+        y1 = xf[t] @ w1.t()
+        h = torch.nn.functional.silu(y1[:, :F]) * y1[:, F:]
+        out.index_add_(0, t, (h @ w2.t()) * w[t, k].unsqueeze(1))
+    return out
+
