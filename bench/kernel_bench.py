@@ -47,6 +47,9 @@ def time_kernel(fn, iters=10, warmup=3):
     for _ in range(iters):
         _flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # keep the GPU busy for ~100 us while the host queues the call, so that the interval between the two events
+        # is the kernel and not the time the Python wrapper needs to launch it
+        torch.cuda._sleep(200000)
         e0.record()
         fn()
         e1.record()

@@ -28,6 +28,90 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_dispatch_kernel(const LLD
   ll_dispatch_body<kLLThreads>(a.g, a.off, a.peers, a.io, ll_scratch, nullptr);
 }
 
+// Low-latency combine as an operator of its own (the counterpart of the fused kernel's tail for callers that ran
+// their own expert computation between low_latency_dispatch and low_latency_combine): every bf16 row of the slab goes
+// back to its token's owner over NVLink into the owner's combine buffer (the slot comes from the row metadata the
+// dispatch left beside the slab), completion flags go to every peer, and after all peers' flags have arrived the owner
+// sums its rows with the routing weights. No host synchronisation: the row count is read from group_off on the
+// device. Reference: cam_moe_distribute_combine.h:238-320 (status set / wait), :627-717 (weighted sum).
+struct LLCombineArgs {
+  EpLLGeom g;
+  EpLLOffsets off;
+  PeerTable peers;
+  const __nv_bfloat16* y;     // [>= n, H] expert outputs in slab row order
+  const int* group_off;       // [E_local + 1]; n = group_off[E_local]
+  const int64_t* topk_idx;    // [T, K]
+  const float* topk_w;        // [T, K]
+  __nv_bfloat16* out;         // [T, H]
+  int T;
+  uint32_t* ctrl;             // [0] epoch (advanced here), [1] send-done, [2] reduce-done
+  int* status;
+  int phase_mask;             // bit0: send rows + flags; bit1: wait flags + weighted sum + epoch advance
+};
+
+__global__ void __launch_bounds__(kLLThreads, 1) ep_ll_combine_kernel(const LLCombineArgs a) {
+  const EpLLGeom& g = a.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_epoch = a.ctrl[0];
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const uint64_t tag = (uint64_t)epoch + 1;
+  uint8_t* self = a.peers.base[g.rank];
+  if (a.phase_mask & 1) {
+    const int n = min(a.group_off[g.E_local], g.n_cap);
+    const int* meta = reinterpret_cast<const int*>(self + a.off.slab_meta[0]);
+    // one work item = 4 KiB of one row (32 lanes x 8 x 16 bytes): all loads of an item are in flight together
+    const int nvec = g.H / 8;
+    const int nparts = (nvec + 255) / 256;
+    for (int item = blockIdx.x * kLLWarps + warp; item < n * nparts; item += gridDim.x * kLLWarps) {
+      const int row = item / nparts, part = item - row * nparts;
+      const int owner = meta[2 * row], slot = meta[2 * row + 1];
+      if (owner < 0 || owner >= g.R || slot < 0 || slot >= g.T_cap * g.K) {
+        if (lane == 0) umdk_set_status(a.status, UMDK_ERR_OVERFLOW, UMDK_PH_COMBINE_DATA, owner, slot);
+        continue;
+      }
+      const int4* src = reinterpret_cast<const int4*>(a.y + (size_t)row * g.H);
+      uint8_t* dst = a.peers.base[owner] + a.off.comb_buf[0] + (size_t)slot * g.H * 2;
+      int4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = part * 256 + u * 32 + lane;
+        v[u] = i < nvec ? __ldg(src + i) : make_int4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = part * 256 + u * 32 + lane;
+        if (i < nvec) st_na_v4(dst + (size_t)i * 16, v[u]);
+      }
+    }
+    if (cta_done_is_last(&a.ctrl[1], gridDim.x)) {
+      if (threadIdx.x < g.R) {
+        st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.off.comb_flag[0]) + g.rank, tag);
+      }
+    }
+  }
+  if (!(a.phase_mask & 2)) return;
+  if (threadIdx.x < g.R) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.comb_flag[0]) + threadIdx.x;
+    if (!wait_flag_ge_sys(f, tag)) {
+      umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_COMBINE_DATA, threadIdx.x, (int)epoch);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    ll_weighted_reduce<kLLThreads>(self + a.off.comb_buf[0], a.topk_idx, a.topk_w, a.out, nullptr, a.T, g.K, g.H);
+  }
+  if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {
+    if (threadIdx.x == 0) a.ctrl[0] = epoch + 1;
+  }
+}
+
 // Stand-alone fp8 e4m3 1x128 quantisation of local rows (shared expert input, tests).
 __global__ void __launch_bounds__(256) quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, int T, int H,
                                                         uint8_t* __restrict__ q, float* __restrict__ s) {
@@ -129,6 +213,40 @@ UMDK_API int umdk_ep_ll_dispatch(const UmdkEpLLDispatchParams* p, void* stream) 
     UMDK_CUDA_CHECK(cudaFuncSetAttribute(ep_ll_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
   }
   ep_ll_dispatch_kernel<<<grid, kLLThreads, dyn, static_cast<cudaStream_t>(stream)>>>(a);
+  UMDK_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+struct UmdkEpLLCombineParams {
+  int R, rank, E, K, H, T_cap, T, num_ctas, phase_mask;
+  void* peers[kMaxRanks];
+  const void* y;
+  const int* group_off;
+  const int64_t* topk_idx;
+  const float* topk_w;
+  void* out;
+  uint32_t* ctrl;
+  int* status;
+};
+
+UMDK_API int umdk_ep_ll_combine(const UmdkEpLLCombineParams* p, void* stream) {
+  LLCombineArgs a;
+  if (int rc = fill_ll_geom(&a.g, p->R, p->rank, p->E, p->K, p->H, p->T_cap)) return rc;
+  if (p->T > p->T_cap || p->T < 0) return -UMDK_ERR_BAD_ARG;
+  a.off = ep_ll_offsets(a.g);
+  for (int i = 0; i < kMaxRanks; ++i) a.peers.base[i] = i < p->R ? static_cast<uint8_t*>(p->peers[i]) : nullptr;
+  a.y = static_cast<const __nv_bfloat16*>(p->y);
+  a.group_off = p->group_off;
+  a.topk_idx = p->topk_idx;
+  a.topk_w = p->topk_w;
+  a.out = static_cast<__nv_bfloat16*>(p->out);
+  a.T = p->T;
+  a.ctrl = p->ctrl;
+  a.status = p->status;
+  a.phase_mask = p->phase_mask ? p->phase_mask : 3;
+  int grid = p->num_ctas > 0 ? p->num_ctas : 64;
+  if (grid > sm_count()) grid = sm_count();
+  ep_ll_combine_kernel<<<grid, kLLThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   UMDK_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

@@ -288,4 +288,64 @@ __device__ __forceinline__ bool ll_dispatch_body(const EpLLGeom& g, const EpLLOf
 #undef s_ok
 }
 
+// Owner-side tail of the combine: out[t] = sum_k w[t, k] * row(t, k) over the rows that the expert ranks stored into
+// this rank's combine buffer ([T][Kt][H] bf16), accumulated in fp32 and rounded once. With `share_out` the row of the
+// LAST slot is copied there unweighted instead of being summed (the folded shared expert). The caller has already
+// waited for every peer's completion flag.
+template <int kThreads>
+__device__ __forceinline__ void ll_weighted_reduce(const uint8_t* comb_buf, const int64_t* topk_idx,
+                                                   const float* topk_w, __nv_bfloat16* out, __nv_bfloat16* share_out,
+                                                   int T, int Kt, int H) {
+  const int warp = threadIdx.x >> 5;
+  // One work item = 512 bytes of one token's output (32 lanes x 16 bytes), spread over every warp of the grid: with
+  // decode-sized batches a warp per token would leave most of the GPU idle while a few warps walk whole rows.
+  // All K rows of an item are loaded before the first is used.
+  const int lane = threadIdx.x & 31;
+  const int nvec = H / 8;
+  const int nchunk = (nvec + 31) / 32;
+  const int nwarps = kThreads / 32;
+  const int k_sum = share_out ? Kt - 1 : Kt;
+  constexpr int kMaxK = 8;
+  for (int item = blockIdx.x * nwarps + warp; item < T * nchunk; item += gridDim.x * nwarps) {
+    const int t = item / nchunk;
+    const int v = (item % nchunk) * 32 + lane;
+    if (v >= nvec) continue;
+    const int4* src = reinterpret_cast<const int4*>(comb_buf + (size_t)t * Kt * H * 2);
+    if (share_out) {
+      const bool have = topk_idx[(size_t)t * Kt + k_sum] >= 0;
+      const int4 val = have ? ld_relaxed_sys_v4(src + (size_t)k_sum * nvec + v) : make_int4(0, 0, 0, 0);
+      reinterpret_cast<int4*>(share_out + (size_t)t * H)[v] = val;
+    }
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int k0 = 0; k0 < k_sum; k0 += kMaxK) {
+      int4 vals[kMaxK];
+      float wk[kMaxK];
+#pragma unroll
+      for (int u = 0; u < kMaxK; ++u) {
+        const int k = k0 + u;
+        const bool on = k < k_sum && topk_idx[(size_t)t * Kt + k] >= 0;
+        wk[u] = on ? topk_w[(size_t)t * Kt + k] : 0.f;
+        vals[u] = on ? ld_relaxed_sys_v4(src + (size_t)k * nvec + v) : make_int4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < kMaxK; ++u) {
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&vals[u]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(p[i]);
+          acc[2 * i] = fmaf(wk[u], f.x, acc[2 * i]);
+          acc[2 * i + 1] = fmaf(wk[u], f.y, acc[2 * i + 1]);
+        }
+      }
+    }
+    int4 o;
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    reinterpret_cast<int4*>(out + (size_t)t * H)[v] = o;
+  }
+}
+
 }  // namespace umdk

@@ -548,55 +548,7 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
   __syncthreads();
   stamp(4);
   if (s_ok) {
-    // One work item = 512 bytes of one token's output (32 lanes x 16 bytes), spread over every warp of the grid: with
-    // decode-sized batches a warp per token would leave most of the GPU idle while a few warps walk whole rows.
-    // All K rows of an item are loaded before the first is used.
-    const int lane = threadIdx.x & 31;
-    const int nvec = a.H / 8;
-    const int nchunk = (nvec + 31) / 32;
-    const int nwarps = kThreads / 32;
-    const int k_sum = a.share_out ? a.Kt - 1 : a.Kt;
-    constexpr int kMaxK = 8;
-    for (int item = blockIdx.x * nwarps + warp; item < a.T * nchunk; item += gridDim.x * nwarps) {
-      const int t = item / nchunk;
-      const int v = (item % nchunk) * 32 + lane;
-      if (v >= nvec) continue;
-      const int4* src = reinterpret_cast<const int4*>(self + a.comb_buf_off + (size_t)t * a.Kt * a.H * 2);
-      if (a.share_out) {
-        const bool have = a.topk_idx[(size_t)t * a.Kt + k_sum] >= 0;
-        const int4 val = have ? ld_relaxed_sys_v4(src + (size_t)k_sum * nvec + v) : make_int4(0, 0, 0, 0);
-        reinterpret_cast<int4*>(a.share_out + (size_t)t * a.H)[v] = val;
-      }
-      float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int k0 = 0; k0 < k_sum; k0 += kMaxK) {
-        int4 vals[kMaxK];
-        float wk[kMaxK];
-#pragma unroll
-        for (int u = 0; u < kMaxK; ++u) {
-          const int k = k0 + u;
-          const bool on = k < k_sum && a.topk_idx[(size_t)t * a.Kt + k] >= 0;
-          wk[u] = on ? a.topk_w[(size_t)t * a.Kt + k] : 0.f;
-          vals[u] = on ? ld_relaxed_sys_v4(src + (size_t)k * nvec + v) : make_int4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int u = 0; u < kMaxK; ++u) {
-          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&vals[u]);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(p[i]);
-            acc[2 * i] = fmaf(wk[u], f.x, acc[2 * i]);
-            acc[2 * i + 1] = fmaf(wk[u], f.y, acc[2 * i + 1]);
-          }
-        }
-      }
-      int4 o;
-      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-      reinterpret_cast<int4*>(a.out + (size_t)t * a.H)[v] = o;
-    }
+    ll_weighted_reduce<kThreads>(self + a.comb_buf_off, a.topk_idx, a.topk_w, a.out, a.share_out, a.T, a.Kt, a.H);
   }
   stamp(5);
   if (cta_done_is_last(&a.ctrl[2], gridDim.x)) {

@@ -16,11 +16,14 @@
 //   and accumulates its own 256 output columns O[128 x 256] += P[128 x 48] * V[48 x own latent dims]  (3 MMAs),
 //   reading V from the SAME gathered tile through an MN-major descriptor.
 // Splitting by dimension halves the resident Q (80 KB instead of 144 KB), which makes room for a three-stage ring
-// of key tiles, and halves the Q*K^T work of each SM. Roles inside a CTA (9 warps):
+// of key tiles, and halves the Q*K^T work of each SM. Roles inside a CTA (6 warps):
 //   warps 0-3  softmax: tcgen05.ld of S, exchange, exp2, P to shared memory, lazy rescale of O
 //   warp  4    one thread issues every MMA: Q*K^T of chunk c+1 is issued BEFORE P*V of chunk c, so the tensor
 //              pipe works on the next scores while the softmax of the current chunk runs (S is double-buffered)
-//   warps 5-8  gather producers: 16-byte cp.async into the 128-byte-swizzled tiles, two chunks in flight
+//   warp  5    gather producer: TMA tile::gather4 copies (four selected rows x 128 bytes per instruction, written
+//              in the 128-byte-swizzled layout the MMA descriptors expect), completion counted in bytes on the
+//              stage's barrier. Gathering with 16-byte cp.async was measured first: an SM sustains only about
+//              10 bytes per clock of such loads (2800 cycles for a 30 KB tile), whatever the access pattern
 // All row addresses of the split are resolved once, up front, into shared memory (index -> page -> row).
 // The running maximum is only raised when it grows by more than 8 (in log2 units); P then stays below 2^8 and the
 // accumulated O needs rescaling only a few times per row instead of in most chunks.
@@ -44,11 +47,11 @@ constexpr int kKSlabBytes = kChunk * 128;        // 6 KB
 constexpr int kQBytes = kMaxSlabs * kQSlabBytes; // 81920
 constexpr int kStageBytes = kMaxSlabs * kKSlabBytes;  // 30720
 constexpr int kPBytes = kHeads * 128;            // 16 KB (96 of every 128 bytes used)
-constexpr int kXBytes = kChunk * kHeads * 4;     // 24 KB, [key][head] fp32
+constexpr int kXBytes = kChunk * kHeads * 4;     // 24 KB, [key / 4][head][4] fp32
 constexpr int kMaxChunks = 43;                   // 2064 keys per split at most
 constexpr int kMaxKeys = kMaxChunks * kChunk;
 constexpr int kThreads = 288;
-constexpr int kProducers = 128;
+constexpr int kProducerWarps = 4;   // warps 5..8 issue the gather copies: the TMA unit takes them faster from several warps
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;                         // two S buffers of 64 columns (48 used)
 constexpr int kColO = 128;
@@ -56,7 +59,8 @@ constexpr int kOffK = kQBytes;
 constexpr int kOffP = kOffK + kStages * kStageBytes;
 constexpr int kOffX = kOffP + kPBytes;
 constexpr int kOffRows = kOffX + kXBytes;
-constexpr int kOffTail = kOffRows + kMaxKeys * 4;
+constexpr int kOffMask = kOffRows + kMaxKeys * 4;   // one 64-bit validity mask per chunk
+constexpr int kOffTail = kOffMask + ((kMaxChunks * 8 + 63) / 64) * 64;
 constexpr int kSmemBytes = 1024 + kOffTail + 256;
 static_assert(kSmemBytes <= 232448, "shared memory budget");
 static_assert(kStageBytes % 1024 == 0 && kKSlabBytes % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
@@ -107,15 +111,44 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
   }
   return true;
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+// Asynchronous 16-byte store into the partner CTA's shared memory; the bytes are counted on the partner's mbarrier
+// (complete_tx), so the sender needs no release fence that would wait for every store to be acknowledged.
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                            uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(
+                   cluster_addr),
+               "r"(a), "r"(b), "r"(c), "r"(d), "r"(cluster_bar)
+               : "memory");
+}
+// Four rows of a 2-D tensor (row numbers r.x .. r.w, `col` = first element of the box in each row) into four
+// consecutive 128-byte rows of shared memory; the tensor map has a box of {64 elements, 1 row} and the 128-byte swizzle.
+__device__ __forceinline__ void tma_gather4(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int col, int4 r) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
+      "%5, %6, %7}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(col), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w)
+      : "memory");
+}
+// Arrival on the partner's barrier WITHOUT release semantics. A release at cluster scope waits until every store this
+// thread has in flight (the asynchronous remote stores above all) is acknowledged, which was measured at about 3000
+// cycles per chunk. The barrier it is used for (`partner may overwrite my exchange buffer`) only has to follow this
+// warp's LOADS of that buffer, and those have completed once their values were used: instructions issue in order.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2^x with the special-function unit's native approximation (2 ulp; -inf gives 0): P is rounded to bf16 anyway.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs a) {
+sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV,
+                         const MlaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_sm = smem;
@@ -123,18 +156,19 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
   uint8_t* p_sm = smem + kOffP;
   float* x_sm = reinterpret_cast<float*>(smem + kOffX);
   int* rows_sm = reinterpret_cast<int*>(smem + kOffRows);
+  unsigned long long* mask_sm = reinterpret_cast<unsigned long long*>(smem + kOffMask);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffTail);
   uint64_t* bar_q = bars;            // 1
   // Arrivals are one per WARP: the lanes order their own accesses before a __syncwarp() and lane 0 arrives, so a
   // barrier sees 4 arrivals per phase instead of 128 (128 arrivals on one barrier, remote ones above all, cost
   // more than the work they guard).
-  uint64_t* bar_full = bars + 1;     // kStages, 4 producer-warp arrivals
+  uint64_t* bar_full = bars + 1;     // kStages, one arrival that expects the tile's bytes from the TMA gathers
   uint64_t* bar_empty = bars + 4;    // kStages, one commit
   uint64_t* bar_s = bars + 7;        // 2, one commit
   uint64_t* bar_sfree = bars + 9;    // 2, 4 softmax-warp arrivals
   uint64_t* bar_p = bars + 11;       // 4 softmax-warp arrivals
   uint64_t* bar_o = bars + 12;       // one commit
-  uint64_t* bar_xfull = bars + 13;   // 4 arrivals from the partner's softmax warps: its partial S has landed
+  uint64_t* bar_xfull = bars + 13;   // one local arrival that expects the 24 KB the partner's st.async stores deliver
   uint64_t* bar_xfree = bars + 14;   // 4 arrivals from the partner's softmax warps: its X may be overwritten
   uint64_t* bar_fin = bars + 15;     // one commit (drain on the abort path)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
@@ -154,7 +188,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
   if (tid == 0) {
     mbar_init(bar_q, 1);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(&bar_full[i], kProducers / 32);
+      mbar_init(&bar_full[i], 1);
       mbar_init(&bar_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -163,11 +197,12 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
     }
     mbar_init(bar_p, 4);
     mbar_init(bar_o, 1);
-    mbar_init(bar_xfull, 4);
+    mbar_init(bar_xfull, 1);
     mbar_init(bar_xfree, 4);
     mbar_init(bar_fin, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmKV);
     *s_abort = 0;
   }
   if (warp == 4) {
@@ -191,6 +226,13 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
     }
     rows_sm[k] = row;
   }
+  __syncthreads();
+  for (int c = tid; c < num_chunks; c += kThreads) {   // bit j of mask c: key j of chunk c takes part
+    unsigned long long m = 0;
+    for (int j = 0; j < kChunk; ++j)
+      if (rows_sm[c * kChunk + j] >= 0) m |= 1ull << j;
+    mask_sm[c] = m;
+  }
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();   // the partner's barriers exist before anything is signalled across
@@ -210,7 +252,8 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
       // ===================================== softmax ======================================================
       const int head = tid;   // == TMEM lane
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-      const uint32_t peer_x = map_to_cta(x_sm, peer) + static_cast<uint32_t>(head) * 4u;
+      const uint32_t peer_x = map_to_cta(x_sm, peer) + static_cast<uint32_t>(head) * 16u;
+      if (tid == 0) mbar_expect_tx(bar_xfull, kXBytes);   // arms the first phase; re-armed after every chunk
       const uint32_t peer_xfull = map_to_cta(bar_xfull, peer);
       const uint32_t peer_xfree = map_to_cta(bar_xfree, peer);
       float m_run = -INFINITY, l_run = 0.f;
@@ -251,9 +294,9 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
         }
         lap(2);
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) st_cluster_f32(peer_x + j * (kHeads * 4), __uint_as_float(sr[j]));
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(peer_xfull);   // release.cluster: cumulative over the warp's stores
+        for (int j4 = 0; j4 < kChunk / 4; ++j4)
+          st_async_v4(peer_x + j4 * (kHeads * 16), sr[4 * j4], sr[4 * j4 + 1], sr[4 * j4 + 2], sr[4 * j4 + 3],
+                      peer_xfull);
         lap(3);
         if (!__all_sync(0xffffffffu, wait_bar<true>(bar_xfull, c & 1, s_abort))) {
           give_up(UMDK_PH_GROUP_READY, 1000 + c);
@@ -261,32 +304,43 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
           break;
         }
         lap(4);
+        // S = own partial + partner's partial (raw dot products; the scale is folded into the exponent below)
+        const unsigned long long valid = mask_sm[c];
         float mx = -INFINITY;
-        const int* rows_c = rows_sm + c * kChunk;
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) {
-          float s = (__uint_as_float(sr[j]) + x_sm[j * kHeads + head]) * a.scale_log2;
-          if (rows_c[j] < 0) s = -INFINITY;
-          sr[j] = __float_as_uint(s);
-          mx = fmaxf(mx, s);
+        for (int j4 = 0; j4 < kChunk / 4; ++j4) {
+          const float4 xv = reinterpret_cast<const float4*>(x_sm)[j4 * kHeads + head];
+          const float xs4[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = 4 * j4 + u;
+            float t = __uint_as_float(sr[j]) + xs4[u];
+            if (!((valid >> j) & 1ull)) t = -INFINITY;
+            sr[j] = __float_as_uint(t);
+            mx = fmaxf(mx, t);
+          }
         }
+        // every lane's loads of x_sm have returned (mx depends on them); keep the arrival behind that dependence
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 0));
+        if (tid == 0 && c + 1 < num_chunks) mbar_expect_tx(bar_xfull, kXBytes);   // next phase, before the partner may send
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(peer_xfree);
+        if (lane == 0) mbar_arrive_cluster_relaxed(peer_xfree);
+        mx *= a.scale_log2;   // scale_log2 > 0: the maximum of the scaled scores
         // lazy maximum: raise it only when it grows by more than 8 (P stays below 2^8)
         float alpha = 1.f;
         if (mx > m_run + 8.f || m_run == -INFINITY) {
           const float m_new = fmaxf(m_run, mx);
-          alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+          alpha = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_new);
           if (m_new == -INFINITY) alpha = 1.f;   // nothing seen yet, nothing to scale
           m_run = m_new;
         }
-        const float m_use = m_run == -INFINITY ? 0.f : m_run;
+        const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
         float sum = 0.f;
         uint32_t pk[kChunk / 2];
 #pragma unroll
         for (int j = 0; j < kChunk / 2; ++j) {
-          const float p0 = exp2f(__uint_as_float(sr[2 * j]) - m_use);
-          const float p1 = exp2f(__uint_as_float(sr[2 * j + 1]) - m_use);
+          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[2 * j]), a.scale_log2, neg_m));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[2 * j + 1]), a.scale_log2, neg_m));
           sum += p0 + p1;
           const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
           pk[j] = *reinterpret_cast<const uint32_t*>(&hh);
@@ -453,14 +507,10 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
           mbar_wait(bar_fin, 0);
         }
       }
-    } else {
-      // ===================================== gather producers =============================================
-      const int p = tid - (kThreads - kProducers);
-      const int per_key = n_slabs * 8;            // 16-byte pieces per key row
-      const int items = kChunk * per_key;
-      const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(a.kv);
+    } else if (warp >= 5 && warp < 5 + kProducerWarps) {
+      // ===================================== gather producers (warps 5..) =====================================
       bool ok = true;
-      const bool dg = a.diag != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && p == 0;
+      const bool dg = a.diag != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && warp == 5;
       long long dt[3] = {0, 0, 0};
       long long t_prev = dg ? clock64() : 0;
       auto lap = [&](int i) {
@@ -470,48 +520,36 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaArgs 
           t_prev = t;
         }
       };
-      for (int c = 0; c < num_chunks; ++c) {
+      const int n_inst = (kChunk / 4) * n_slabs;   // gather4 copies per tile
+      for (int c = 0; c < num_chunks && ok; ++c) {
         const int st = c % kStages;
-        // Chunk c-2 is announced BEFORE this thread may block on a free stage: the stage frees when P*V of chunk
-        // c-3 retires, that is issued behind Q*K^T of chunk c-2, and Q*K^T of chunk c-2 waits for this arrival.
-        if (c >= 2) {
-          cp_async_wait<1>();
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bar_full[(c - 2) % kStages]);
-        }
-        lap(0);
-        if (c >= kStages && !wait_bar<false>(&bar_empty[st], ((c / kStages) - 1) & 1, s_abort)) {
-          give_up(UMDK_PH_TMA_EMPTY, c);
-          ok = false;
-          break;
+        if (c >= kStages) {
+          ok = __all_sync(0xffffffffu, wait_bar<false>(&bar_empty[st], ((c / kStages) - 1) & 1, s_abort));
+          if (!ok) {
+            if (lane == 0) give_up(UMDK_PH_TMA_EMPTY, c);
+            break;
+          }
         }
         lap(1);
+        if (warp == 5 && lane == 0) mbar_expect_tx(&bar_full[st], static_cast<uint32_t>(n_slabs) * kKSlabBytes);
+        __syncwarp();
         uint8_t* stage = k_sm + st * kStageBytes;
-        const int* rows_c = rows_sm + c * kChunk;
-        for (int i = p; i < items; i += kProducers) {
-          const int key = i / per_key, ch = i - key * per_key;
-          const int slab = ch >> 3, c8 = ch & 7;
-          const int row = rows_c[key];
-          const int dim_byte = (slab < 4 ? half * 256 + slab * 64 : 512) * 2 + c8 * 16;
-          const uint8_t* src = kv_bytes + (size_t)(row < 0 ? 0 : row) * (kDim * 2) + dim_byte;
-          cp_async_16(stage + slab * kKSlabBytes + key * 128 + ((c8 ^ (key & 7)) << 4), src);
+        const int4* rows4 = reinterpret_cast<const int4*>(rows_sm + c * kChunk);
+        for (int u = (warp - 5) * 32 + lane; u < n_inst; u += 32 * kProducerWarps) {
+          const int grp = u / n_slabs, slab = u - grp * n_slabs;
+          int4 r = rows4[grp];
+          r.x = max(r.x, 0);   // masked keys read row 0: their scores are set to -inf before the softmax
+          r.y = max(r.y, 0);
+          r.z = max(r.z, 0);
+          r.w = max(r.w, 0);
+          const int col = slab < 4 ? half * 256 + slab * 64 : 512;
+          tma_gather4(stage + slab * kKSlabBytes + grp * 512, &tmKV, &bar_full[st], col, r);
         }
-        cp_async_commit();
         lap(2);
       }
       if (dg) {
         for (int i = 0; i < 3; ++i) a.diag[12 + i] = dt[i];
       }
-      // drain: the last two chunks (fewer when the loop ended early)
-      cp_async_wait<1>();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (ok && num_chunks >= 2 && lane == 0) mbar_arrive(&bar_full[(num_chunks - 2) % kStages]);
-      cp_async_wait<0>();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (ok && lane == 0) mbar_arrive(&bar_full[(num_chunks - 1) % kStages]);
     }
   } else if (warp < 4) {
     // empty split: zeros and -inf so that the merge ignores it
@@ -581,8 +619,11 @@ UMDK_API int umdk_sparse_mla_decode(const void* q, const void* kv, const int* bl
   // one CTA pair resolves at most kMaxKeys rows of the key list up front (see umdk_sparse_mla_min_splits)
   if (((topk + num_splits - 1) / num_splits + kChunk - 1) / kChunk > kMaxChunks) return -UMDK_ERR_BAD_ARG;
   if ((size_t)num_pages * kPage > 0x7fffffffull) return -UMDK_ERR_BAD_ARG;
-  CUtensorMap tmQ;
+  CUtensorMap tmQ, tmKV;
   if (make_tmap_2d(&tmQ, TMAP_BF16, q, kDim, (uint64_t)B * kHeads, kDim * 2, 64, kHeads, TMAP_SW_128B))
+    return -UMDK_ERR_BAD_ARG;
+  // the cache as a matrix of token rows; box = one 128-byte piece of one row (tile::gather4 takes four of them)
+  if (make_tmap_2d(&tmKV, TMAP_BF16, kv, kDim, (uint64_t)num_pages * kPage, kDim * 2, 64, 1, TMAP_SW_128B))
     return -UMDK_ERR_BAD_ARG;
   static bool attr = false;
   if (!attr) {
@@ -609,7 +650,7 @@ UMDK_API int umdk_sparse_mla_decode(const void* q, const void* kv, const int* bl
   a.diag = diag;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(2 * num_splits, B);
-  sparse_mla_decode_kernel<<<grid, kThreads, kSmemBytes, s>>>(tmQ, a);
+  sparse_mla_decode_kernel<<<grid, kThreads, kSmemBytes, s>>>(tmQ, tmKV, a);
   UMDK_CUDA_CHECK(cudaGetLastError());
   if (num_splits > 1) {
     mla_merge_kernel<<<B * kHeads, 128, 0, s>>>(part_o, part_lse, static_cast<__nv_bfloat16*>(out), lse, num_splits);

@@ -11,22 +11,39 @@
 // (bondp_dp_failback.c:249-483), switches BOND_ENABLE_FAILOVER / BOND_ENABLE_FAILBACK / BOND_ENABLE_HEALTH_CHECK /
 // BOND_HEALTH_CHECK_ACTIVE_INTERVAL (bondp_env.c:18-24). Like the reference, only Jetty objects are supported on
 // the bond device (no stand-alone JFS / JFR, no event channel).
+//
+// Path scheduling in BALANCE mode follows one of five policies (BOND_SCHED_POLICY or user_ctl 5; the reference's
+// priority / chip-affinity / least-load / random selection, bondp_datapath_schedule.c:44-215, 236-259):
+//   round_robin  paths in turn (default)
+//   priority     the first usable path of an ordered list (BOND_PATH_PRIORITY="2,0,1", user_ctl 6)
+//   affinity     the path that belongs to the calling thread's CPU (cpu % npaths, the stand-in for the chip a
+//                thread runs on), then the priority list as the failover route
+//   least_load   the usable path with the fewest work requests in flight, ties broken at random
+//   random       any usable path, uniformly
+// A work request whose path failed is not resent at once: the resend is put on a timing wheel (bond_timewheel.h,
+// BOND_RESEND_DELAY_MS, default one tick of 5 ms) so that a burst of failures does not pile onto the surviving paths
+// while their own completions are still draining, and failback probes are wheel tasks too. The wheel is advanced by
+// the context's timer thread (the health thread of the earlier design).
 #include <fcntl.h>
+#include <sched.h>
 #include <stdlib.h>
 #include <string.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
 #include <condition_variable>
 #include <deque>
+#include <functional>
 #include <mutex>
 #include <string>
 #include <thread>
 #include <unordered_map>
 #include <vector>
 
+#include "bond_timewheel.h"
 #include "bond_window.h"
 #include "ub_util.h"
 #include "urma_api.h"
@@ -39,6 +56,7 @@ constexpr int kMaxPaths = 4;
 constexpr uint32_t kRegEntries = 8192;
 constexpr uint32_t kBondMagic = 0x424f4e44;  // "BOND"
 enum BondMode { MODE_STANDALONE = 0, MODE_ACTIVE_BACKUP = 1, MODE_BALANCE = 2 };
+enum BondPolicy { POL_ROUND_ROBIN = 0, POL_PRIORITY = 1, POL_AFFINITY = 2, POL_LEAST_LOAD = 3, POL_RANDOM = 4, POL_LAST = 4 };
 enum RegType : uint32_t { REG_FREE = 0, REG_BUSY = 1, REG_JETTY = 2, REG_SEG = 3 };
 
 struct RegEntry {
@@ -128,6 +146,7 @@ struct PathState {
   std::atomic<bool> up{true};
   std::atomic<bool> admin_down{false};
   std::atomic<uint64_t> tx{0}, errors{0}, failovers{0}, failbacks{0};
+  std::atomic<int64_t> inflight{0};   // work requests posted on this path whose completion has not been seen
   urma_jfc_t* probe_jfc = nullptr;
   urma_jetty_t* probe_jetty = nullptr;
   urma_target_jetty_t* probe_self = nullptr;
@@ -138,8 +157,13 @@ struct BondCtx {
   urma_context_t* p[kMaxPaths] = {nullptr};
   PathState path[kMaxPaths];
   int mode = MODE_BALANCE;
+  std::atomic<int> policy{POL_ROUND_ROBIN};
+  int priority[kMaxPaths] = {0, 1, 2, 3};   // path numbers, most preferred first
   bool failover = true, failback = true, health = true;
   uint32_t health_ms = 1000;
+  uint32_t resend_delay_ms = 5;
+  bond::TimeWheel wheel{5, 256};
+  std::atomic<uint64_t> deferred_resends{0};
   std::atomic<uint32_t> rr{0};
   std::mutex mu;
   std::unordered_map<uint64_t, StoredWr*> store;
@@ -188,6 +212,50 @@ int pick_path(BondCtx* c, int avoid = -1) {
     for (int i = 0; i < c->npaths; ++i)
       if (i != avoid && path_usable(c, i)) return i;
     return -1;
+  }
+  auto first_of_priority = [&]() {
+    for (int k = 0; k < c->npaths; ++k) {
+      const int i = c->priority[k];
+      if (i >= 0 && i < c->npaths && i != avoid && path_usable(c, i)) return i;
+    }
+    return -1;
+  };
+  static thread_local uint64_t rng = ub::now_ns() ^ (uint64_t)(uintptr_t)&rng;
+  auto next_rand = [&]() {
+    rng ^= rng << 13;
+    rng ^= rng >> 7;
+    rng ^= rng << 17;
+    return rng;
+  };
+  switch (c->policy.load()) {
+    case POL_PRIORITY: return first_of_priority();
+    case POL_AFFINITY: {
+      const int cpu = sched_getcpu();
+      const int i = cpu >= 0 ? cpu % c->npaths : 0;
+      if (i != avoid && path_usable(c, i)) return i;
+      return first_of_priority();   // the failover route
+    }
+    case POL_LEAST_LOAD: {
+      int cand[kMaxPaths], n = 0;
+      int64_t best = INT64_MAX;
+      for (int i = 0; i < c->npaths; ++i) {
+        if (i == avoid || !path_usable(c, i)) continue;
+        const int64_t v = c->path[i].inflight.load();
+        if (v < best) {
+          best = v;
+          n = 0;
+        }
+        if (v == best) cand[n++] = i;
+      }
+      return n == 0 ? -1 : cand[next_rand() % n];
+    }
+    case POL_RANDOM: {
+      int cand[kMaxPaths], n = 0;
+      for (int i = 0; i < c->npaths; ++i)
+        if (i != avoid && path_usable(c, i)) cand[n++] = i;
+      return n == 0 ? -1 : cand[next_rand() % n];
+    }
+    default: break;
   }
   const uint32_t start = c->rr.fetch_add(1);
   for (int k = 0; k < c->npaths; ++k) {
@@ -260,7 +328,10 @@ urma_status_t post_stored(BondCtx* c, StoredWr* s, uint64_t id) {
   w.next = nullptr;
   urma_jfs_wr_t* bad = nullptr;
   c->path[p].tx.fetch_add(1);
-  return urma_post_jetty_send_wr(s->jetty->p[p], &w, &bad);
+  c->path[p].inflight.fetch_add(1);
+  const urma_status_t rc = urma_post_jetty_send_wr(s->jetty->p[p], &w, &bad);
+  if (rc != URMA_SUCCESS) c->path[p].inflight.fetch_sub(1);
+  return rc;
 }
 
 // ------------------------------------------------------------------------------------------- ops
@@ -625,6 +696,7 @@ bool translate(BondCtx* c, BJfc* vj, int path, const urma_cr_t& pc, urma_cr_t* o
     if (it == c->store.end()) return false;
     s = it->second;
   }
+  c->path[path].inflight.fetch_sub(1);
   if (pc.status != URMA_CR_SUCCESS && pc.status != URMA_CR_REM_ACCESS_ABORT_ERR &&
       pc.status != URMA_CR_REM_OPERATION_ERR) {
     // transport-level failure: the path is suspect
@@ -637,6 +709,29 @@ bool translate(BondCtx* c, BJfc* vj, int path, const urma_cr_t& pc, urma_cr_t* o
         s->path = np;
         ++s->tries;
         c->path[np].failovers.fetch_add(1);
+        if (c->resend_delay_ms > 0 && c->health_thr.joinable()) {
+          // resend from the timing wheel; if that post fails too the request completes with an error there
+          const uint64_t id = pc.user_ctx;
+          const urma_cr_t orig = pc;
+          c->deferred_resends.fetch_add(1);
+          c->wheel.schedule(c->resend_delay_ms, [c, s, id, orig, vj](bond::TimeWheel::Reason why) {
+            if (why == bond::TimeWheel::kExecuted && post_stored(c, s, id) == URMA_SUCCESS) return;
+            {
+              std::lock_guard<std::mutex> l(c->mu);
+              c->store.erase(id);
+            }
+            urma_cr_t out = orig;
+            out.user_ctx = s->user_ctx;
+            out.local_id = s->jetty->v_id;
+            out.remote_id = s->target->pub.id;
+            {
+              std::lock_guard<std::mutex> l(vj->mu);
+              vj->ready.push_back(out);
+            }
+            delete s;
+          });
+          return false;
+        }
         if (post_stored(c, s, pc.user_ctx) == URMA_SUCCESS) return false;  // completion will come from the new path
       }
     }
@@ -782,6 +877,10 @@ urma_status_t op_query_jetty(urma_jetty_t* jt, urma_jetty_cfg_t* cfg, urma_jetty
 //           2 = administratively set path state: in->addr = path, in->len = 1 (down) / 0 (up)
 //           3 = set aggregation mode: in->addr = 0 standalone, 1 active-backup, 2 balance
 //           4 = inject a link fault on a physical path: in->addr = path, in->len = 1 (drop) / 0 (restore)
+//           5 = set the scheduling policy of BALANCE mode: in->addr = 0 round-robin, 1 priority, 2 affinity,
+//               3 least-load, 4 random
+//           6 = set the priority list: in->addr = path numbers packed 4 bits each, most preferred in the low nibble
+//           7 = scheduler statistics -> out->addr points to uint64[2 + npaths] {policy, deferred resends, in flight...}
 int op_user_ctl(urma_context_t* ctx, urma_user_ctl_in_t* in, urma_user_ctl_out_t* out) {
   BondCtx* c = C(ctx);
   switch (in->opcode) {
@@ -813,18 +912,64 @@ int op_user_ctl(urma_context_t* ctx, urma_user_ctl_in_t* in, urma_user_ctl_out_t
       urma_user_ctl_out_t pout{};
       return urma_user_ctl(c->p[in->addr], &pin, &pout);
     }
+    case 5:
+      if (in->addr > POL_LAST) return -1;
+      c->policy = static_cast<int>(in->addr);
+      return 0;
+    case 6: {
+      int order[kMaxPaths];
+      uint32_t seen = 0;
+      for (int k = 0; k < c->npaths; ++k) {
+        order[k] = static_cast<int>((in->addr >> (4 * k)) & 0xf);
+        if (order[k] >= c->npaths || (seen & (1u << order[k]))) return -1;
+        seen |= 1u << order[k];
+      }
+      for (int k = 0; k < c->npaths; ++k) c->priority[k] = order[k];
+      return 0;
+    }
+    case 7: {
+      uint64_t* o = reinterpret_cast<uint64_t*>(out->addr);
+      if (!o || out->len < sizeof(uint64_t) * (2 + c->npaths)) return -1;
+      o[0] = static_cast<uint64_t>(c->policy.load());
+      o[1] = c->deferred_resends.load();
+      for (int i = 0; i < c->npaths; ++i) o[2 + i] = static_cast<uint64_t>(std::max<int64_t>(0, c->path[i].inflight.load()));
+      out->rsv = c->npaths;
+      return 0;
+    }
     default: return -1;
   }
 }
 
+void probe_paths(BondCtx* c);
+
+// Timer thread: advances the timing wheel by wall-clock ticks. Failback probing is itself a wheel task that puts
+// itself back on the wheel every `health_ms` (and at once when a path goes down: hcv).
 void health_loop(BondCtx* c) {
-  urma_log_set_thread_tag("bond-health");
+  urma_log_set_thread_tag("bond-timer");
+  uint64_t last = ub::now_ns();
+  std::function<void(bond::TimeWheel::Reason)> probe_task = [&, c](bond::TimeWheel::Reason why) {
+    if (why != bond::TimeWheel::kExecuted || c->stop.load()) return;
+    if (c->health) probe_paths(c);
+    c->wheel.schedule(c->health_ms, probe_task);
+  };
+  c->wheel.schedule(c->health_ms, probe_task);
   while (!c->stop.load()) {
     {
       std::unique_lock<std::mutex> l(c->hmu);
-      c->hcv.wait_for(l, std::chrono::milliseconds(c->health_ms));
+      c->hcv.wait_for(l, std::chrono::milliseconds(c->wheel.tick_ms()));
     }
     if (c->stop.load()) break;
+    const uint64_t now = ub::now_ns();
+    const uint64_t ticks = (now - last) / (1000000ull * c->wheel.tick_ms());
+    if (ticks > 0) {
+      c->wheel.advance(static_cast<uint32_t>(std::min<uint64_t>(ticks, 1024)));
+      last += ticks * 1000000ull * c->wheel.tick_ms();
+    }
+  }
+}
+
+void probe_paths(BondCtx* c) {
+  {
     for (int i = 0; i < c->npaths; ++i) {
       PathState& ps = c->path[i];
       if (ps.up.load() || !c->failback || !ps.probe_jetty) continue;
@@ -954,6 +1099,24 @@ urma_context_t* prov_create_context(urma_device_t*, uint32_t) {
   c->health = env_on("BOND_ENABLE_HEALTH_CHECK", true);
   if (const char* e = getenv("BOND_HEALTH_CHECK_ACTIVE_INTERVAL")) c->health_ms = std::max(10, atoi(e));
   if (const char* e = getenv("BOND_MODE")) c->mode = std::max(0, std::min(2, atoi(e)));
+  if (const char* e = getenv("BOND_SCHED_POLICY")) {
+    static const char* names[] = {"round_robin", "priority", "affinity", "least_load", "random"};
+    for (int i = 0; i <= POL_LAST; ++i)
+      if (!strcmp(e, names[i]) || (e[0] == '0' + i && !e[1])) c->policy = i;
+  }
+  if (const char* e = getenv("BOND_PATH_PRIORITY")) {   // "2,0,1": paths not named keep their order behind those named
+    std::vector<int> order;
+    for (const char* q = e; *q;) {
+      const int v = atoi(q);
+      if (v >= 0 && v < c->npaths && std::find(order.begin(), order.end(), v) == order.end()) order.push_back(v);
+      while (*q && *q != ',') ++q;
+      if (*q == ',') ++q;
+    }
+    for (int i = 0; i < c->npaths; ++i)
+      if (std::find(order.begin(), order.end(), i) == order.end()) order.push_back(i);
+    for (int i = 0; i < c->npaths; ++i) c->priority[i] = order[i];
+  }
+  if (const char* e = getenv("BOND_RESEND_DELAY_MS")) c->resend_delay_ms = static_cast<uint32_t>(std::max(0, atoi(e)));
   c->pub.ops = &g_ops;
   c->pub.eid = g_dev.eid;
   c->pub.uasid = g_dev.reg->next_uasid.fetch_add(1) + 1;
@@ -977,7 +1140,7 @@ urma_context_t* prov_create_context(urma_device_t*, uint32_t) {
       ps.probe_self = urma_import_jetty(c->p[i], &rj, &t);
     }
   }
-  if (c->health) c->health_thr = std::thread(health_loop, c);
+  c->health_thr = std::thread(health_loop, c);   // timer thread: timing wheel (deferred resends, failback probes)
   return &c->pub;
 }
 urma_status_t prov_delete_context(urma_context_t* ctx) {

@@ -10,12 +10,20 @@
 //                  pinned host memory and is copied to the caller's result buffer when the completion is reaped
 //   completion     every request records an event; poll_jfc reaps finished events in order and emits completion
 //                  records (token and access violations are reported as URMA_CR_REM_ACCESS_ABORT_ERR at post time)
-// Two-sided SEND / RECV are not offered by this provider (use the shm provider for messaging and this one for bulk
-// data), the same split as a NIC with a separate control network. This provider takes the place of the reference's
-// hardware user driver (src/urma/hw/udma) for GPUs of one box.
+//   SEND / RECV    every jetty owns a small shared-memory file with a ring of posted receive buffers (device
+//                  memory, exported with CUDA IPC when it is posted) and a ring of receive completions. A SEND /
+//                  SEND_IMM takes the oldest posted buffer of the target jetty, copies the payload into it with
+//                  cudaMemcpyAsync on the sender's stream, and - once the copy's event has fired - writes the
+//                  receive completion (length, immediate data, source jetty) into the target's ring, where the
+//                  receiver's poll_jfc finds it. No posted buffer = receiver-not-ready error on the sender; a payload
+//                  longer than the buffer = length error on both sides. The counterpart of the send path and the
+//                  receive queue of the reference's hardware user driver (src/urma/hw/udma/udma_u_jfs.c:819-873,
+//                  udma_u_jfr.c).
+// This provider takes the place of the reference's hardware user driver (src/urma/hw/udma) for GPUs of one box.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <fcntl.h>
+#include <stddef.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -109,6 +117,84 @@ __global__ void atomic_kernel(unsigned long long* addr, int opcode, unsigned lon
   *old_out = old;
 }
 
+// ---- two-sided messaging state shared between processes (one file per jetty) ----
+constexpr uint32_t kRq = 256;   // posted receive buffers per jetty
+constexpr uint32_t kRcq = 512;  // receive completions per jetty
+constexpr uint32_t kJettyMagic = 0x544a4355;  // "UCJT"
+struct RecvSlot {
+  std::atomic<uint32_t> state;  // 0 free, 1 posted
+  uint32_t pid, dev, len;
+  uint64_t user_ctx, va, alloc_base;
+  cudaIpcMemHandle_t handle;
+};
+struct RecvComp {
+  std::atomic<uint32_t> state;  // 0 free, 1 being written, 2 valid
+  uint32_t status, len, opcode;
+  uint64_t user_ctx, imm;
+  urma_jetty_id_t remote;
+};
+struct JettyShm {
+  std::atomic<uint32_t> magic;
+  std::atomic<uint32_t> alive;
+  std::atomic<uint64_t> rq_head, rq_tail;   // consumers (senders) advance head with CAS, the owner advances tail
+  std::atomic<uint64_t> cq_head, cq_tail;   // producers (senders) reserve at tail with fetch_add, the owner drains head
+  RecvSlot rq[kRq];
+  RecvComp cq[kRcq];
+};
+
+std::string shm_dir() {
+  const char* e = getenv("URMA_SHM_DIR");
+  const std::string d = (e && *e) ? e : "/dev/shm/umdk_urma_" + std::to_string(getuid());
+  mkdir(d.c_str(), 0700);
+  return d;
+}
+std::string jetty_path(uint32_t uasid, uint32_t id) {
+  return shm_dir() + "/cuda_jetty_" + std::to_string(uasid) + "_" + std::to_string(id);
+}
+JettyShm* map_jetty(uint32_t uasid, uint32_t id, bool create) {
+  const std::string path = jetty_path(uasid, id);
+  const int fd = open(path.c_str(), create ? (O_RDWR | O_CREAT | O_TRUNC) : O_RDWR, 0600);
+  if (fd < 0) return nullptr;
+  if (create && ftruncate(fd, sizeof(JettyShm)) != 0) {
+    close(fd);
+    return nullptr;
+  }
+  struct stat sb{};
+  if (fstat(fd, &sb) != 0 || sb.st_size != (off_t)sizeof(JettyShm)) {
+    close(fd);
+    return nullptr;
+  }
+  void* p = mmap(nullptr, sizeof(JettyShm), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) return nullptr;
+  JettyShm* j = static_cast<JettyShm*>(p);
+  if (create) {
+    j->alive.store(1);
+    j->magic.store(kJettyMagic, std::memory_order_release);
+  } else if (j->magic.load(std::memory_order_acquire) != kJettyMagic) {
+    munmap(p, sizeof(JettyShm));
+    return nullptr;
+  }
+  return j;
+}
+
+// Receive buffers of other processes, opened once per allocation (keyed by the IPC handle bytes).
+std::mutex g_ipc_mu;
+std::unordered_map<std::string, void*> g_ipc_open;
+void* open_remote_alloc(const cudaIpcMemHandle_t& h) {
+  const std::string key(reinterpret_cast<const char*>(&h), sizeof(h));
+  std::lock_guard<std::mutex> l(g_ipc_mu);
+  auto it = g_ipc_open.find(key);
+  if (it != g_ipc_open.end()) return it->second;
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  g_ipc_open[key] = p;
+  return p;
+}
+
 struct CJfc {
   urma_jfc_t pub;
 };
@@ -120,6 +206,10 @@ struct Req {
   unsigned long long* old_host;  // pinned slot for atomics (or null)
   uint64_t result_addr;          // where the caller wants the old value
   urma_cr_status_t early;        // != SUCCESS: failed at post time, no event
+  // SEND: where the receive completion goes once the copy has finished
+  JettyShm* rx = nullptr;
+  uint64_t rx_user_ctx = 0, imm = 0;
+  uint32_t rx_opcode = 0, rx_status = 0;
 };
 struct CCtx {
   urma_context_t pub;
@@ -136,6 +226,8 @@ struct CJetty {
   uint32_t id;
   CJfc* jfc;
   std::atomic<int> state{URMA_JETTY_STATE_READY};
+  JettyShm* shm = nullptr;   // this jetty's receive queue and receive-completion ring
+  urma_jfc_t* rx_jfc = nullptr;
 };
 struct CSeg {
   urma_target_seg_t pub;
@@ -145,6 +237,7 @@ struct CSeg {
 };
 struct CTarget {
   urma_target_jetty_t pub;
+  JettyShm* shm = nullptr;   // the remote jetty's rings (null: the jetty has none, SEND is refused)
 };
 CCtx* C(urma_context_t* c) { return reinterpret_cast<CCtx*>(c->priv); }
 
@@ -171,8 +264,11 @@ urma_jetty_t* op_create_jetty(urma_context_t* ctx, const urma_jetty_cfg_t* cfg) 
   j->pub.jetty_id.uasid = ctx->uasid;
   j->pub.jetty_id.id = j->id;
   j->pub.priv = j;
+  j->shm = map_jetty(ctx->uasid, j->id, true);
+  j->rx_jfc = cfg->jfr_cfg.jfc ? cfg->jfr_cfg.jfc : cfg->jfs_cfg.jfc;
   std::lock_guard<std::mutex> l(g_jmu);
   g_jfc_jetties[cfg->jfs_cfg.jfc].push_back(j);
+  if (j->rx_jfc != cfg->jfs_cfg.jfc) g_jfc_jetties[j->rx_jfc].push_back(j);
   return &j->pub;
 }
 urma_status_t op_modify_jetty(urma_jetty_t* jt, urma_jetty_state_t st) {
@@ -188,12 +284,19 @@ urma_status_t op_delete_jetty(urma_jetty_t* jt) {
   CJetty* j = reinterpret_cast<CJetty*>(jt->priv);
   {
     std::lock_guard<std::mutex> l(g_jmu);
-    auto& v = g_jfc_jetties[jt->cfg.jfs_cfg.jfc];
-    for (size_t i = 0; i < v.size(); ++i)
-      if (v[i] == j) {
-        v.erase(v.begin() + i);
-        break;
-      }
+    for (urma_jfc_t* q : {jt->cfg.jfs_cfg.jfc, j->rx_jfc}) {
+      auto& v = g_jfc_jetties[q];
+      for (size_t i = 0; i < v.size(); ++i)
+        if (v[i] == j) {
+          v.erase(v.begin() + i);
+          break;
+        }
+    }
+  }
+  if (j->shm) {
+    j->shm->alive.store(0);
+    munmap(j->shm, sizeof(JettyShm));
+    unlink(jetty_path(jt->jetty_id.uasid, j->id).c_str());
   }
   for (auto& r : j->inflight)
     if (r.early == URMA_CR_SUCCESS) cudaEventDestroy(r.ev);
@@ -206,10 +309,13 @@ urma_target_jetty_t* op_import_jetty(urma_context_t*, const urma_rjetty_t* rj, c
   t->pub.trans_mode = rj->trans_mode;
   t->pub.type = rj->type;
   t->pub.priv = t;
+  t->shm = map_jetty(rj->jetty_id.uasid, rj->jetty_id.id, false);
   return &t->pub;
 }
 urma_status_t op_unimport_jetty(urma_target_jetty_t* t) {
-  delete reinterpret_cast<CTarget*>(t->priv);
+  CTarget* ct = reinterpret_cast<CTarget*>(t->priv);
+  if (ct->shm) munmap(ct->shm, sizeof(JettyShm));
+  delete ct;
   return URMA_SUCCESS;
 }
 urma_status_t op_bind(urma_jetty_t*, urma_target_jetty_t*) { return URMA_SUCCESS; }
@@ -401,10 +507,79 @@ urma_status_t op_post_send(urma_jetty_t* jt, urma_jfs_wr_t* wr, urma_jfs_wr_t** 
         }
         break;
       }
+      case URMA_OPC_SEND:
+      case URMA_OPC_SEND_IMM: {
+        CTarget* ct = reinterpret_cast<CTarget*>(tj->priv);
+        if (w->send.src.num_sge != 1 || !ct->shm) {
+          *bad = w;
+          return URMA_EINVAL;
+        }
+        JettyShm* rx = ct->shm;
+        r.len = w->send.src.sge[0].len;
+        // take the oldest posted receive buffer of the target (several senders may race for it)
+        RecvSlot taken{};
+        bool have = false;
+        if (rx->alive.load()) {
+          for (;;) {
+            uint64_t h = rx->rq_head.load(std::memory_order_acquire);
+            if (h == rx->rq_tail.load(std::memory_order_acquire)) break;
+            RecvSlot& sl = rx->rq[h % kRq];
+            if (sl.state.load(std::memory_order_acquire) != 1) break;
+            memcpy(&taken.pid, &sl.pid, sizeof(RecvSlot) - offsetof(RecvSlot, pid));
+            if (rx->rq_head.compare_exchange_weak(h, h + 1, std::memory_order_acq_rel)) {
+              sl.state.store(0, std::memory_order_release);
+              have = true;
+              break;
+            }
+          }
+        }
+        if (!have) {
+          r.early = URMA_CR_RNR_RETRY_CNT_EXC_ERR;   // receiver not ready: nothing was consumed on the other side
+          break;
+        }
+        r.rx = rx;
+        r.rx_user_ctx = taken.user_ctx;
+        r.imm = w->opcode == URMA_OPC_SEND_IMM ? w->send.imm_data : 0;
+        r.rx_opcode = w->opcode == URMA_OPC_SEND_IMM ? URMA_CR_OPC_SEND_WITH_IMM : URMA_CR_OPC_SEND;
+        r.rx_status = URMA_CR_SUCCESS;
+        if (r.len > taken.len) {
+          // the message does not fit: both sides learn it, the buffer is spent (as on a NIC)
+          r.rx_status = URMA_CR_LOC_LEN_ERR;
+          r.early = URMA_CR_REM_RESP_LEN_ERR;
+        } else {
+          void* dst = nullptr;
+          if (taken.pid == (uint32_t)getpid()) {
+            dst = reinterpret_cast<void*>(taken.va);
+          } else {
+            void* base = open_remote_alloc(taken.handle);
+            if (base) dst = static_cast<char*>(base) + (taken.va - taken.alloc_base);
+          }
+          if (!dst) {
+            r.rx_status = URMA_CR_REM_OPERATION_ERR;
+            r.early = URMA_CR_REM_OPERATION_ERR;
+          } else {
+            ce = cudaMemcpyAsync(dst, reinterpret_cast<void*>(w->send.src.sge[0].addr), r.len, cudaMemcpyDefault,
+                                 c->stream);
+          }
+        }
+        if (r.early != URMA_CR_SUCCESS) {   // no copy was queued: tell the receiver now
+          const uint64_t t = rx->cq_tail.fetch_add(1);
+          RecvComp& cc = rx->cq[t % kRcq];
+          cc.status = r.rx_status;
+          cc.len = 0;
+          cc.opcode = r.rx_opcode;
+          cc.user_ctx = r.rx_user_ctx;
+          cc.imm = r.imm;
+          cc.remote = jt->jetty_id;
+          cc.state.store(2, std::memory_order_release);
+          r.rx = nullptr;
+        }
+        break;
+      }
       case URMA_OPC_NOP: break;
       default:
         *bad = w;
-        return URMA_EINVAL;  // two-sided verbs are not offered by this provider
+        return URMA_EINVAL;
     }
     if (ce != cudaSuccess) {
       *bad = w;
@@ -416,6 +591,58 @@ urma_status_t op_post_send(urma_jetty_t* jt, urma_jfs_wr_t* wr, urma_jfs_wr_t** 
     }
     std::lock_guard<std::mutex> l(j->mu);
     j->inflight.push_back(r);
+  }
+  *bad = nullptr;
+  return URMA_SUCCESS;
+}
+
+urma_status_t op_post_recv(urma_jetty_t* jt, urma_jfr_wr_t* wr, urma_jfr_wr_t** bad) {
+  CCtx* c = C(jt->ctx);
+  CJetty* j = reinterpret_cast<CJetty*>(jt->priv);
+  if (!j->shm) {
+    *bad = wr;
+    return URMA_FAIL;
+  }
+  cudaSetDevice(c->dev);
+  for (urma_jfr_wr_t* w = wr; w; w = w->next) {
+    if (w->src.num_sge != 1) {
+      *bad = w;
+      return URMA_EINVAL;
+    }
+    void* buf = reinterpret_cast<void*>(w->src.sge[0].addr);
+    cudaPointerAttributes at;
+    void* base = nullptr;
+    size_t alloc_len = 0;
+    if (cudaPointerGetAttributes(&at, buf) != cudaSuccess || at.type != cudaMemoryTypeDevice ||
+        !alloc_range(buf, &base, &alloc_len)) {
+      cudaGetLastError();
+      *bad = w;
+      return URMA_EINVAL;   // receive buffers of this provider are device memory
+    }
+    std::lock_guard<std::mutex> l(j->mu);
+    const uint64_t t = j->shm->rq_tail.load(std::memory_order_relaxed);
+    if (t - j->shm->rq_head.load(std::memory_order_acquire) >= kRq) {
+      *bad = w;
+      return URMA_EAGAIN;
+    }
+    RecvSlot& sl = j->shm->rq[t % kRq];
+    if (sl.state.load(std::memory_order_acquire) != 0) {   // the sender that took it has not let go of it yet
+      *bad = w;
+      return URMA_EAGAIN;
+    }
+    if (cudaIpcGetMemHandle(&sl.handle, base) != cudaSuccess) {
+      cudaGetLastError();
+      *bad = w;
+      return URMA_FAIL;
+    }
+    sl.pid = getpid();
+    sl.dev = c->dev;
+    sl.len = w->src.sge[0].len;
+    sl.user_ctx = w->user_ctx;
+    sl.va = w->src.sge[0].addr;
+    sl.alloc_base = reinterpret_cast<uint64_t>(base);
+    sl.state.store(1, std::memory_order_release);
+    j->shm->rq_tail.store(t + 1, std::memory_order_release);
   }
   *bad = nullptr;
   return URMA_SUCCESS;
@@ -438,7 +665,20 @@ int op_poll_jfc(urma_jfc_t* jfc, int n, urma_cr_t* cr) {
         if (q == cudaErrorNotReady) break;  // completions are delivered in order per jetty
         cudaEventDestroy(r.ev);
         if (q != cudaSuccess) st = URMA_CR_LOC_OPERATION_ERR;
-        else if (r.old_host && r.result_addr) {
+        if (r.rx) {   // the payload has landed: hand the receiver its completion
+          const uint64_t t = r.rx->cq_tail.fetch_add(1);
+          RecvComp& cc = r.rx->cq[t % kRcq];
+          cc.status = q == cudaSuccess ? (uint32_t)URMA_CR_SUCCESS : (uint32_t)URMA_CR_REM_OPERATION_ERR;
+          cc.len = r.len;
+          cc.opcode = r.rx_opcode;
+          cc.user_ctx = r.rx_user_ctx;
+          cc.imm = r.imm;
+          cc.remote.eid = j->pub.jetty_id.eid;
+          cc.remote.uasid = j->pub.jetty_id.uasid;
+          cc.remote.id = j->id;
+          cc.state.store(2, std::memory_order_release);
+        }
+        if (q == cudaSuccess && r.old_host && r.result_addr) {
           // the caller's result buffer may be host or device memory
           cudaMemcpy(reinterpret_cast<void*>(r.result_addr), r.old_host, 8, cudaMemcpyDefault);
         }
@@ -453,6 +693,26 @@ int op_poll_jfc(urma_jfc_t* jfc, int n, urma_cr_t* cr) {
         ++k;
       }
       j->inflight.pop_front();
+    }
+    // receive side: completions that senders left in this jetty's ring
+    if (j->shm && j->rx_jfc == jfc) {
+      while (k < n) {
+        const uint64_t h = j->shm->cq_head.load(std::memory_order_relaxed);
+        RecvComp& cc = j->shm->cq[h % kRcq];
+        if (cc.state.load(std::memory_order_acquire) != 2) break;
+        cr[k] = urma_cr_t{};
+        cr[k].status = static_cast<urma_cr_status_t>(cc.status);
+        cr[k].user_ctx = cc.user_ctx;
+        cr[k].opcode = static_cast<urma_cr_opcode_t>(cc.opcode);
+        cr[k].flag = URMA_CR_FLAG_RECV;
+        cr[k].completion_len = cc.len;
+        cr[k].local_id = j->id;
+        cr[k].remote_id = cc.remote;
+        cr[k].imm_data = cc.imm;
+        ++k;
+        cc.state.store(0, std::memory_order_release);
+        j->shm->cq_head.store(h + 1, std::memory_order_release);
+      }
     }
   }
   return k;
@@ -475,7 +735,7 @@ const urma_ops_t g_ops = {
     op_create_jetty, op_modify_jetty, op_query_jetty, nullptr, op_delete_jetty,
     op_import_jetty, op_unimport_jetty, op_bind, op_unbind, nullptr, nullptr,
     op_alloc_token, op_free_token, op_register_seg, op_unregister_seg, op_import_seg, op_unimport_seg,
-    nullptr, nullptr, op_post_send, nullptr, op_poll_jfc, nullptr, nullptr, nullptr,
+    nullptr, nullptr, op_post_send, op_post_recv, op_poll_jfc, nullptr, nullptr, nullptr,
     nullptr, nullptr, op_user_ctl,
 };
 

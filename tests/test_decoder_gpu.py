@@ -70,7 +70,8 @@ def test_decoder_moe_block_matches_oracle():
     torch.cuda.synchronize()
     m.check()
     want = reference_layer_moe(cfg, h.cpu(), idx.cpu(), w.cpu(), L["experts"])
-    assert ref.mean_rel_err(out.float().cpu(), want) < 0.02
+    assert ref.mean_rel_err(out.float().cpu(), want) < 0.012
+    assert ref.max_row_rel_err(out.float().cpu(), want) < 0.05
     assert int(cnt.sum()) == cfg.batch * cfg.top_k
     m.close()
 

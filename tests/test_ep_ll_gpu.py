@@ -7,6 +7,23 @@ from umdk_b200.ops import reference as ref
 
 pytestmark = pytest.mark.gpu
 
+# Error bounds. The oracle `ref_fused_moe` applies the same fp8 quantisation steps as the kernels, so what is left is
+# accumulation order, the bf16 rounding of every expert row before the weighted sum, and the fp8 steps that an
+# intermediate value crosses when it differs in the last bf16 bit: measured 0.6 - 0.8 % mean relative error and 3 %
+# on the worst row. MEAN_TOL / ROW_TOL sit just above that; a dropped or misrouted (token, k) row moves a row by tens
+# of per cent. Against a computation that does NOT quantise the activations the fp8 e4m3 format itself costs 4.4 %
+# (the quantisation-aware oracle is 4.4 % away from it too), which is why the reference's 1 % bar for its int8
+# per-token format (doc/en/cam/CAM API Guide.md:146-148) is stated here as UNQUANT_TOL for fp8.
+MEAN_TOL = 0.012
+ROW_TOL = 0.05
+UNQUANT_TOL = 0.06
+
+
+def _check(out, want, what=(), mean_tol=MEAN_TOL):
+    o = out.float().cpu()
+    assert ref.mean_rel_err(o, want) < mean_tol, (what, ref.mean_rel_err(o, want))
+    assert ref.max_row_rel_err(o, want) < ROW_TOL, (what, ref.max_row_rel_err(o, want))
+
 
 def _weights(E, H, F, seed):
     g = torch.Generator().manual_seed(seed)
@@ -91,9 +108,10 @@ def test_low_latency_moe_virtual_ranks(R, T, H, F, E, K, fused):
                     want_cnt += torch.bincount(v, minlength=el)
                 assert torch.equal(st[r].recv_per_expert.cpu(), want_cnt)
             for r in range(R):
-                want = ref.ref_fused_moe(xs[r], idxs[r], ws[r], w1q, w1s, w2q, w2s)
-                err = ref.mean_rel_err(outs[r].float().cpu(), want)
-                assert err < 0.02, (rnd, r, err)
+                _check(outs[r], ref.ref_fused_moe(xs[r], idxs[r], ws[r], w1q, w1s, w2q, w2s), (rnd, r))
+                if rnd == 0 and r == 0:
+                    unq = ref.ref_moe_unquantised(xs[r], idxs[r], ws[r], w1q, w1s, w2q, w2s)
+                    assert ref.mean_rel_err(outs[r].float().cpu(), unq) < UNQUANT_TOL
     finally:
         for h in heaps:
             h.close()
@@ -120,10 +138,10 @@ def test_low_latency_moe_single_call_with_shared_expert():
             out, share, cnt = st.moe(xs[0].cuda(), idxs[0].cuda(), ws[0].cuda(), weights, shared=sh, fused=fused)
             torch.cuda.synchronize()
             st.check()
-            assert ref.mean_rel_err(out.float().cpu(), want) < 0.02, (fused, weights.tiled)
+            _check(out, want, (fused, weights.tiled))
         ones = torch.ones(T, 1)
         want_sh = ref.ref_fused_moe(xs[0], torch.zeros(T, 1, dtype=torch.int64), ones, s1q, s1s, s2q, s2s)
-        assert ref.mean_rel_err(share.float().cpu(), want_sh) < 0.02
+        _check(share, want_sh)
         assert int(cnt.sum().item()) == int((idxs[0] >= 0).sum().item())
     finally:
         heap.close()
@@ -163,15 +181,14 @@ def test_low_latency_moe_shared_expert_folded_into_routed_pipeline(R, T, H, F, E
                 s.check()
             ones = torch.ones(T, 1)
             for r in range(R):
-                want = ref.ref_fused_moe(xs[r], idxs[r], ws[r], w1q, w1s, w2q, w2s)
-                assert ref.mean_rel_err(outs[r].float().cpu(), want) < 0.02, (rnd, r)
+                _check(outs[r], ref.ref_fused_moe(xs[r], idxs[r], ws[r], w1q, w1s, w2q, w2s), (rnd, r))
                 want_sh = ref.ref_fused_moe(xs[r], torch.zeros(T, 1, dtype=torch.int64), ones, s1q, s1s, s2q, s2s)
-                assert ref.mean_rel_err(shares[r].float().cpu(), want_sh) < 0.02, (rnd, r)
+                _check(shares[r], want_sh, (rnd, r, "shared"))
         if R == 1:
             out, share, cnt = st[0].moe(dx[0], idxs[0].cuda(), ws[0].cuda(), wts[0])
             torch.cuda.synchronize()
             st[0].check()
-            assert ref.mean_rel_err(out.float().cpu(), ref.ref_fused_moe(xs[0], idxs[0], ws[0], w1q, w1s, w2q, w2s)) < 0.02
+            _check(out, ref.ref_fused_moe(xs[0], idxs[0], ws[0], w1q, w1s, w2q, w2s))
             assert cnt.shape[0] == el and int(cnt.sum()) == int((idxs[0] >= 0).sum())
     finally:
         for h in heaps:
@@ -199,8 +216,7 @@ def test_low_latency_moe_cuda_graph_replay():
             graph.replay()
             torch.cuda.synchronize()
             st.check()
-            want = ref.ref_fused_moe(xin, iin, win, w1q, w1s, w2q, w2s)
-            assert ref.mean_rel_err(out.float().cpu(), want) < 0.02
+            _check(out, ref.ref_fused_moe(xin, iin, win, w1q, w1s, w2q, w2s))
             assert int(cnt.sum()) == int((iin >= 0).sum())
     finally:
         heap.close()
@@ -225,8 +241,7 @@ def test_fused_kernel_timeline_in_diagnose_mode():
         tl = st.timeline_us()
         order = [tl[k] for k in ("rows_ready", "phase1", "phase2", "peers_done", "end")]
         assert order[0] >= 0 and all(b >= a for a, b in zip(order, order[1:])) and order[-1] < 1e6, tl
-        want = ref.ref_fused_moe(xs[0], idxs[0], ws[0], w1q, w1s, w2q, w2s)
-        assert ref.mean_rel_err(out.float().cpu(), want) < 0.02
+        _check(out, ref.ref_fused_moe(xs[0], idxs[0], ws[0], w1q, w1s, w2q, w2s))
     finally:
         heap.close()
 
@@ -262,3 +277,139 @@ def test_dispatch_with_layout_inside_matches_separate_layout(T, E, K):
         assert int(outs[0][0][-1]) == int((idx >= 0).sum())
     finally:
         heap.close()
+
+
+def test_benchmark_shape_sampled_rows():
+    """The benchmark's layer shape (hidden 7168, FFN 2048, 256 experts top-8, 128 tokens, tile-major weights) on one
+    GPU: the rows of a few sampled tokens against the oracle (the whole output would take the CPU oracle minutes)."""
+    from umdk_b200.models.dsv3_decoder import _quant_experts
+    from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
+    from umdk_b200.parallel.symm import SymmetricHeap
+    T, H, F, E, K = 128, 7168, 2048, 256, 8
+    g = torch.Generator(device="cuda").manual_seed(11)
+    w1q, w1s = _quant_experts(E, 2 * F, H, "cuda", g)
+    w2q, w2s = _quant_experts(E, H, F, "cuda", g)
+    xs, idxs, ws = _inputs(1, T, H, E, K, seed=77)
+    heap = SymmetricHeap(EpLowLatency.heap_bytes(1, E, K, H, T))
+    try:
+        st = EpLowLatency(heap, E, K, H, F, T)
+        w = ExpertWeights(w1q, w1s, w2q, w2s).to_tiled()
+        out, _, cnt = st.moe(xs[0].cuda(), idxs[0].cuda(), ws[0].cuda(), w, None)
+        torch.cuda.synchronize()
+        st.check()
+        assert int(cnt.sum()) == int((idxs[0] >= 0).sum())
+        rows = torch.tensor([0, 5, 37, 64, 127])
+        want = ref.ref_fused_moe(xs[0][rows], idxs[0][rows], ws[0][rows], w1q, w1s, w2q, w2s)
+        # reductions of 7168 and 2048 terms: more intermediate values land next to an fp8 step than in the small
+        # cases (1.6 % measured against 0.6 - 0.8 % there)
+        _check(out[rows.cuda()], want, "benchmark shape", mean_tol=0.025)
+        assert bool(torch.isfinite(out.float()).all())
+    finally:
+        heap.close()
+
+
+
+@pytest.mark.parametrize("R,T,H,E,K", [(1, 40, 1024, 8, 2), (4, 33, 2048, 16, 4)])
+def test_low_latency_combine_kernel_virtual_ranks(R, T, H, E, K):
+    """dispatch -> caller-side "experts" (row * (global expert + 1)) -> the stand-alone combine kernel, against the
+    dense reference. Two rounds: the combine ends the call, so the next dispatch starts a new epoch."""
+    from umdk_b200.ops.ep_ll import EpLowLatency
+    from umdk_b200.parallel.symm import SymmetricHeap
+    xs, idxs, ws = _inputs(R, T, H, E, K, seed=R + T)
+    heaps = SymmetricHeap.virtual(EpLowLatency.heap_bytes(R, E, K, H, T), R)
+    try:
+        st = [EpLowLatency(h, E, K, H, 256, T) for h in heaps]
+        el = E // R
+        dx, di, dw = [x.cuda() for x in xs], [i.cuda() for i in idxs], [w.cuda() for w in ws]
+        for rnd in range(2):
+            for r in range(R):
+                st[r].dispatch(dx[r], di[r], phase_mask=1)
+            for r in range(R):
+                st[r].dispatch(dx[r], di[r], phase_mask=2)
+            ys = []
+            for r in range(R):
+                sx, ss, _ = st[r].slab_views()
+                n = int(st[r].group_off[-1])
+                le = torch.repeat_interleave(torch.arange(el, device="cuda"), st[r].recv_per_expert)
+                rows = ref.dequant_fp8_1x128(sx[:n].cpu(), ss[:n].cpu()).cuda()
+                y = torch.zeros(st[r].n_cap, H, dtype=torch.bfloat16, device="cuda")
+                y[:n] = (rows * (le + r * el + 1).float().unsqueeze(1)).to(torch.bfloat16)
+                ys.append(y)
+            outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+            for pm in (1, 2):
+                for r in range(R):
+                    st[r].combine(ys[r], di[r], dw[r], out=outs[r], phase_mask=pm)
+            torch.cuda.synchronize()
+            for r in range(R):
+                st[r].check()
+                xq = ref.dequant_fp8_1x128(*ref.quant_fp8_1x128(xs[r]))
+                want = ref.dense_moe_reference(xq, idxs[r], ws[r], lambda e, rows: rows * (e + 1))
+                assert ref.mean_rel_err(outs[r].float().cpu(), want) < 0.01, (rnd, r)
+                assert ref.max_row_rel_err(outs[r].float().cpu(), want) < 0.02, (rnd, r)
+    finally:
+        for h in heaps:
+            h.close()
+
+
+def test_buffer_low_latency_dispatch_then_combine_without_host_sync():
+    from umdk_b200 import Buffer
+    T, H, E, K = 48, 1024, 8, 4
+    xs, idxs, ws = _inputs(1, T, H, E, K, seed=3)
+    buf = Buffer(None, low_latency_mode=True, num_experts=E, hidden=H, top_k=K, ffn_hidden=256)
+    try:
+        x, idx, w = xs[0].cuda(), idxs[0].cuda(), ws[0].cuda()
+        for _ in range(2):
+            (sx, ss), cnt, handle, _, _ = buf.low_latency_dispatch(x, idx, T, E)
+            n = int(cnt.sum())
+            le = torch.repeat_interleave(torch.arange(E, device="cuda"), cnt)
+            y = torch.zeros(sx.shape[0], H, dtype=torch.bfloat16, device="cuda")
+            y[:n] = (ref.dequant_fp8_1x128(sx[:n].cpu(), ss[:n].cpu()).cuda() * (le + 1).float().unsqueeze(1)).to(torch.bfloat16)
+            out, _, _ = buf.low_latency_combine(y, idx, w, handle)
+            torch.cuda.synchronize()
+            handle.check()
+            xq = ref.dequant_fp8_1x128(*ref.quant_fp8_1x128(xs[0]))
+            want = ref.dense_moe_reference(xq, idxs[0], ws[0], lambda e, rows: rows * (e + 1))
+            assert ref.mean_rel_err(out.float().cpu(), want) < 0.01
+    finally:
+        buf.destroy()
+
+
+def test_timed_out_wait_poisons_the_object_until_reset():
+    """A receive phase whose counts nobody publishes runs out of its (about two-second) cycle budget and reports it;
+    the object then refuses further launches until reset() has put its counters and epoch words back, after which
+    a normal call matches the oracle again. Nothing faults and the context stays usable."""
+    from umdk_b200.ops.ep import KernelStatusError
+    from umdk_b200.ops.ep_ll import EpLowLatency, ExpertWeights
+    from umdk_b200.parallel.symm import SymmetricHeap
+    R, T, H, F, E, K = 2, 16, 512, 256, 4, 2
+    w1q, w1s, w2q, w2s = _weights(E, H, F, seed=1)
+    xs, idxs, ws = _inputs(R, T, H, E, K, seed=2)
+    heaps = SymmetricHeap.virtual(EpLowLatency.heap_bytes(R, E, K, H, T), R)
+    try:
+        st = [EpLowLatency(h, E, K, H, F, T) for h in heaps]
+        # rank 0 waits for rank 1's counts, which are never published
+        st[0].dispatch(xs[0].cuda(), idxs[0].cuda(), phase_mask=1)
+        st[0].dispatch(xs[0].cuda(), idxs[0].cuda(), phase_mask=2)
+        torch.cuda.synchronize()
+        with pytest.raises(KernelStatusError, match="timeout"):
+            st[0].check()
+        with pytest.raises(KernelStatusError, match="poisoned"):
+            st[0].dispatch(xs[0].cuda(), idxs[0].cuda(), phase_mask=1)
+        epoch = max(s.max_epoch() for s in st) + 2
+        for s in st:
+            s.reset(epoch=epoch)
+        el = E // R
+        wts = [ExpertWeights(*(t[r * el:(r + 1) * el].cuda().contiguous() for t in (w1q, w1s, w2q, w2s)))
+               for r in range(R)]
+        dx, di, dw = [x.cuda() for x in xs], [i.cuda() for i in idxs], [w.cuda() for w in ws]
+        outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+        for pm in (4, 8, 1, 2):
+            for r in range(R):
+                st[r]._fused(wts[r], di[r], dw[r], outs[r], phase_mask=pm, x=dx[r])
+        torch.cuda.synchronize()
+        for r in range(R):
+            st[r].check()
+            _check(outs[r], ref.ref_fused_moe(xs[r], idxs[r], ws[r], w1q, w1s, w2q, w2s), r)
+    finally:
+        for h in heaps:
+            h.close()

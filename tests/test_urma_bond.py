@@ -91,3 +91,81 @@ def test_bond_failover_and_failback(bond_env):
     finally:
         a.close()
         b.close()
+
+
+def test_bond_scheduling_policies(bond_env):
+    """priority: everything on the preferred path until it is taken down, then the next of the list; least_load and
+    random: both paths carry traffic; affinity: the path of the calling thread's CPU; an unknown policy is refused."""
+    from umdk_b200 import urma
+    a, b = urma.Context("bond0"), urma.Context("bond0")
+    try:
+        ea, eb = a.endpoint(depth=64, recv_token=3), b.endpoint(depth=64, recv_token=3)
+        mem_b = torch.zeros(1024, dtype=torch.int64)
+        seg_b = b.register(mem_b, token=9)
+        peer_b = a.import_endpoint(eb.blob, token=3)
+        rseg = a.import_segment(seg_b.blob, token=9)
+        src = torch.arange(1024, dtype=torch.int64)
+
+        def burst(n=16):
+            before = [s["tx"] for s in urma.bond_path_stats(a)]
+            for i in range(n):
+                ea.write(peer_b, rseg, rseg.va + (i % 8) * 64, src.data_ptr(), 64)
+            ea.wait(n)
+            return [s["tx"] - b0 for s, b0 in zip(urma.bond_path_stats(a), before)]
+
+        urma.bond_set_policy(a, "priority", priority=[1, 0])
+        assert urma.bond_sched_stats(a)["policy"] == "priority"
+        assert burst() == [0, 16]
+        urma.user_ctl(a, 2, addr=1, length=1)          # path 1 administratively down: next of the list
+        assert burst() == [16, 0]
+        urma.user_ctl(a, 2, addr=1, length=0)
+        urma.bond_set_policy(a, "priority", priority=[0, 1])
+        assert burst() == [16, 0]
+        for pol in ("least_load", "random"):
+            urma.bond_set_policy(a, pol)
+            d = burst(64)
+            assert sum(d) == 64 and d[0] > 0 and d[1] > 0, (pol, d)
+        urma.bond_set_policy(a, "affinity", priority=[0, 1])
+        cpu = sorted(os.sched_getaffinity(0))[0]
+        saved = os.sched_getaffinity(0)
+        os.sched_setaffinity(0, {cpu})
+        try:
+            d = burst()
+        finally:
+            os.sched_setaffinity(0, saved)
+        assert d[cpu % 2] == 16 and d[1 - cpu % 2] == 0
+        assert urma.bond_sched_stats(a)["inflight"] == [0, 0]     # every completion has been accounted
+        with pytest.raises(urma.UrmaError):
+            urma.user_ctl(a, 5, addr=9)
+        with pytest.raises(urma.UrmaError):
+            urma.user_ctl(a, 6, addr=0x00)                         # path 0 named twice
+    finally:
+        a.close()
+        b.close()
+
+
+def test_bond_resends_go_through_the_timing_wheel(bond_env, monkeypatch):
+    """A request whose path fails is resent from the timing wheel after BOND_RESEND_DELAY_MS, exactly once."""
+    from umdk_b200 import urma
+    monkeypatch.setenv("BOND_RESEND_DELAY_MS", "20")
+    a, b = urma.Context("bond0"), urma.Context("bond0")
+    try:
+        ea, eb = a.endpoint(depth=64, recv_token=3), b.endpoint(depth=64, recv_token=3)
+        mem_b = torch.zeros(16, dtype=torch.int64)
+        seg_b = b.register(mem_b, token=9)
+        peer_b = a.import_endpoint(eb.blob, token=3)
+        rseg = a.import_segment(seg_b.blob, token=9)
+        urma.bond_set_policy(a, "priority", priority=[0, 1])
+        urma.user_ctl(a, 4, addr=0, length=1)                       # path 0 drops everything
+        for _ in range(4):
+            ea.atomic(peer_b, urma.OPC_FADD, rseg, rseg.va, 1)
+        got, deadline = 0, time.time() + 20
+        while got < 4 and time.time() < deadline:
+            got += len(ea.wait(1, timeout_ms=3000))
+        assert got == 4 and int(mem_b[0]) == 4
+        st = urma.bond_sched_stats(a)
+        assert st["deferred_resends"] >= 1 and st["inflight"] == [0, 0]
+        urma.user_ctl(a, 4, addr=0, length=0)
+    finally:
+        a.close()
+        b.close()

@@ -1,5 +1,6 @@
-"""URMA over GPU memory (cuda_ipc provider): one-sided write / read between device segments and system-scope
-atomics, within one process on one GPU. The cross-process path (CUDA IPC handles) is covered by the multi-GPU test."""
+"""URMA over GPU memory (cuda_ipc provider): one-sided write / read between device segments, system-scope atomics and
+two-sided send / receive into posted device buffers, within one process on one GPU. The cross-process path (CUDA IPC
+handles) is covered by the multi-GPU test."""
 import ctypes
 
 import pytest
@@ -38,6 +39,41 @@ def test_cuda_ipc_write_read_atomics():
         ea.write(peer_b, bad, bad.va, src.data_ptr(), 16)
         c = ea.wait(1, check=False)
         assert c[0].status == urma.CR_REM_ACCESS_ABORT
+    finally:
+        a.close()
+        b.close()
+
+
+def test_cuda_ipc_send_recv_into_posted_device_buffers():
+    from umdk_b200 import urma
+    a, b = urma.Context("cuda0"), urma.Context("cuda0")
+    try:
+        ea, eb = a.endpoint(depth=64), b.endpoint(depth=64)
+        peer_b = a.import_endpoint(eb.blob)
+        bufs = [torch.zeros(1024, dtype=torch.float32, device="cuda") for _ in range(3)]
+        for i, t in enumerate(bufs):
+            eb.post_recv(t, user_ctx=100 + i)
+        m0 = torch.randn(1024, device="cuda")
+        m1 = torch.randn(256, device="cuda")
+        ea.send(peer_b, m0.data_ptr(), m0.numel() * 4, user_ctx=1)
+        ea.send(peer_b, m1.data_ptr(), m1.numel() * 4, user_ctx=2, imm=0xABCD)
+        sent = ea.wait(2)
+        assert [c.user_ctx for c in sent] == [1, 2]
+        got = eb.wait(2)
+        assert [c.user_ctx for c in got] == [100, 101] and [c.length for c in got] == [4096, 1024]
+        assert all(c.flags & urma.CR_FLAG_RECV for c in got) and got[1].imm == 0xABCD
+        assert torch.equal(bufs[0], m0) and torch.equal(bufs[1][:256], m1)
+        # a message longer than the posted buffer: both sides get an error completion, the buffer is spent
+        big = torch.randn(2048, device="cuda")
+        ea.send(peer_b, big.data_ptr(), big.numel() * 4, user_ctx=3)
+        assert ea.wait(1, check=False)[0].status != urma.CR_SUCCESS
+        r = eb.wait(1, check=False)
+        assert r[0].status != urma.CR_SUCCESS and r[0].user_ctx == 102
+        ea.recover()
+        # nothing posted: receiver-not-ready on the sender, nothing arrives
+        ea.send(peer_b, m1.data_ptr(), 64, user_ctx=4)
+        assert ea.wait(1, check=False)[0].status == urma.CR_RNR
+        assert eb.poll() == []
     finally:
         a.close()
         b.close()

@@ -45,7 +45,7 @@ _KERNEL_ENTRY_POINTS = {
     "umdk_ep_ll_dispatch": 1, "umdk_quant_fp8_1x128": 1, "umdk_sparse_mla_decode": 1, "umdk_allreduce": 1,
     "umdk_ag_gemm": 1, "umdk_gemm_rs": 1, "umdk_moe_fused": 1, "umdk_tp_gemm": 1, "umdk_gemm_bf16_2sm": 1,
     "umdk_kv_prefetch_rows": 1, "umdk_ep_notify": 1, "umdk_add_rmsnorm": 1, "umdk_qkv_post": 1, "umdk_q_rope": 1,
-    "umdk_router_topk": 1,
+    "umdk_router_topk": 1, "umdk_ep_ll_combine": 1,
 }
 LAUNCH_COUNT = 0
 

@@ -242,15 +242,9 @@ class Buffer:
                             async_finish: bool = False, return_recv_hook: bool = False,
                             out: Optional[torch.Tensor] = None):
         """x: expert outputs [>= N, H] bf16 in the slab row order of `low_latency_dispatch`.
-        -> (combined_x [T, H], event, hook)"""
+        -> (combined_x [T, H], event, hook). One kernel of its own (ep_ll_combine): rows go back to the token owners
+        over NVLink, completion flags, weighted sum; nothing is read back on the host."""
         st = handle
-        n = int(st.group_off[-1].item())
-        _, _, meta = st.slab_views()
-        K = topk_idx.shape[1]
-        src_idx = torch.stack((meta[:n, 0], meta[:n, 1] // K, meta[:n, 1] % K), dim=1).to(torch.int32).contiguous()
-        ns = self._normal_state(st.E, K, x.shape[1], max(topk_idx.shape[0], st.T_cap))
-        res = ns.combine_rows(x[:n].contiguous(), src_idx, topk_idx.contiguous(), topk_weights.contiguous(), out=out)
-        # the low-latency region is single-buffered: the next dispatch may start once this combine has finished
-        st.ctrl[0] += 1
+        res = st.combine(x.contiguous(), topk_idx.contiguous(), topk_weights.float().contiguous(), out=out)
         ev = EventOverlap(torch.cuda.current_stream().record_event()) if async_finish else EventOverlap()
         return res, ev, (lambda: None) if return_recv_hook else None

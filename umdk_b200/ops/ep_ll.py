@@ -47,6 +47,16 @@ class _LLDispatchParams(ctypes.Structure):
     ]
 
 
+class _LLCombineParams(ctypes.Structure):
+    _fields_ = [
+        ("R", ctypes.c_int), ("rank", ctypes.c_int), ("E", ctypes.c_int), ("K", ctypes.c_int), ("H", ctypes.c_int),
+        ("T_cap", ctypes.c_int), ("T", ctypes.c_int), ("num_ctas", ctypes.c_int), ("phase_mask", ctypes.c_int),
+        ("peers", ctypes.c_void_p * MAX_RANKS),
+        ("y", ctypes.c_void_p), ("group_off", ctypes.c_void_p), ("topk_idx", ctypes.c_void_p),
+        ("topk_w", ctypes.c_void_p), ("out", ctypes.c_void_p), ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+    ]
+
+
 class _MoeFusedParams(ctypes.Structure):
     _fields_ = [
         ("G", ctypes.c_int), ("F", ctypes.c_int), ("H", ctypes.c_int), ("n_rows_cap", ctypes.c_int),
@@ -247,6 +257,31 @@ class EpLowLatency(Recoverable):
         if rc != 0:
             raise RuntimeError(f"umdk_ep_ll_dispatch failed: {rc}")
         return lay
+
+    @_trace.traced("umdk.ep_ll.combine")
+    def combine(self, y: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
+                out: Optional[torch.Tensor] = None, phase_mask: int = 3, num_ctas: int = 0) -> torch.Tensor:
+        """Low-latency combine of caller-computed expert outputs ``y`` [>= rows, H] bf16 (slab row order of the last
+        ``dispatch``): rows return to their owners over NVLink, flags, weighted sum - one launch, no host
+        synchronisation (the row count is read on the device). Ends the call that ``dispatch`` began."""
+        self._guard()
+        assert y.is_cuda and y.dtype == torch.bfloat16 and y.is_contiguous() and y.shape[1] == self.H
+        assert y.shape[0] >= min(self.n_cap, y.shape[0]) and topk_idx.dtype == torch.int64 and topk_idx.is_contiguous()
+        T = topk_idx.shape[0]
+        if out is None:
+            out = torch.empty(T, self.H, dtype=torch.bfloat16, device=y.device)
+        p = _LLCombineParams()
+        p.R, p.rank, p.E, p.K, p.H, p.T_cap, p.T = self.R, self.rank, self.E, self.K, self.H, self.T_cap, T
+        p.num_ctas, p.phase_mask = num_ctas, phase_mask
+        for i, pp in enumerate(self.heap.peer_ptrs):
+            p.peers[i] = pp
+        p.y, p.group_off = y.data_ptr(), self.group_off.data_ptr()
+        p.topk_idx, p.topk_w, p.out = topk_idx.data_ptr(), topk_w.data_ptr(), out.data_ptr()
+        p.ctrl, p.status = self.ctrl.data_ptr(), self.status.data_ptr()
+        rc = self.lib.umdk_ep_ll_combine(ctypes.byref(p), _native.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"umdk_ep_ll_combine failed: {rc}")
+        return out
 
     def _gemm1(self, w: ExpertWeights):
         p = moe_gemm.MoeGemmParams()

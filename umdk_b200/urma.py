@@ -24,6 +24,8 @@ OPC_WRITE, OPC_WRITE_IMM, OPC_READ = 0x00, 0x01, 0x10
 OPC_CAS, OPC_SWAP, OPC_FADD, OPC_FSUB, OPC_FAND, OPC_FOR, OPC_FXOR = 0x20, 0x21, 0x22, 0x23, 0x24, 0x25, 0x26
 OPC_SEND, OPC_SEND_IMM, OPC_NOP = 0x40, 0x41, 0x51
 CR_SUCCESS, CR_REM_ACCESS_ABORT, CR_ACK_TIMEOUT, CR_FLUSH = 0, 8, 9, 11
+CR_RNR = 10        # URMA_CR_RNR_RETRY_CNT_EXC_ERR: the target had no receive buffer posted
+CR_FLAG_RECV = 1   # Completion.flag bit: receive-side completion
 SEG_BLOB, JETTY_BLOB = 64, 32
 
 
@@ -92,6 +94,7 @@ class Completion(tuple):
     user_ctx = property(lambda s: s[1])
     length = property(lambda s: s[2])
     imm = property(lambda s: s[3])
+    flags = property(lambda s: s[4])
     is_recv = property(lambda s: bool(s[4] & 1))
 
 
@@ -265,3 +268,26 @@ def bond_path_stats(ctx: Context):
     n = user_ctl(ctx, 1, out_buf=buf)
     keys = ("up", "tx", "errors", "failovers", "failbacks", "admin_down")
     return [dict(zip(keys, [int(buf[i * 6 + k]) for k in range(6)])) for i in range(n)]
+
+
+BOND_POLICIES = ("round_robin", "priority", "affinity", "least_load", "random")
+
+
+def bond_set_policy(ctx: Context, policy: str, priority=None):
+    """Path scheduling policy of a bond context in BALANCE mode (one of BOND_POLICIES); ``priority`` = path numbers,
+    most preferred first (used by 'priority' and as the failover route of 'affinity')."""
+    if priority is not None:
+        packed = 0
+        for k, p in enumerate(priority):
+            packed |= (int(p) & 0xf) << (4 * k)
+        user_ctl(ctx, 6, addr=packed)
+    user_ctl(ctx, 5, addr=BOND_POLICIES.index(policy))
+
+
+def bond_sched_stats(ctx: Context) -> dict:
+    """{policy, deferred_resends, inflight: [per path]}: the scheduler's view of a bond context."""
+    buf = (ctypes.c_uint64 * (2 + 4))()
+    n = user_ctl(ctx, 7, out_buf=buf)
+    return {"policy": BOND_POLICIES[int(buf[0])], "deferred_resends": int(buf[1]),
+            "inflight": [int(buf[2 + i]) for i in range(n)]}
+
