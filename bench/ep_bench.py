@@ -58,6 +58,9 @@ def timed(fn, iters, warmup, world):
         if world > 1:
             dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # the GPU idles ~100 us while the host queues the call: the events then bracket device time, not the time
+        # the Python wrapper needs to launch
+        torch.cuda._sleep(200000)
         e0.record()
         fn()
         e1.record()

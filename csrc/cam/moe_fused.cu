@@ -442,6 +442,20 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
   stamp(0);
 
   bool goff_local = false;
+  if (a.fuse_dispatch && (a.phase_mask & 8) && (a.phase_mask & 1) && a.w_tiled && threadIdx.x == 0) {
+    // While the dispatch is in flight HBM is idle: bring the first weight tiles this CTA will stream into L2.
+    // Which expert a phase-1 item belongs to is only known once the counts have arrived, so this is a guess - in a
+    // decode batch every local expert has rows and fewer than 64 of them, which makes token tile i = expert i.
+    // A wrong guess costs bandwidth nobody else wanted. About 100 MB over the grid, to stay inside L2.
+    const int NT1g = a.F / BMW, kbt = a.H / BKB;
+    const int w = blockIdx.x;
+    const int e = w / NT1g, j = w % NT1g;
+    if (e < a.G) {
+      int n = (100 << 20) / (int)gridDim.x / (2 * BMW * BKB);
+      if (n > kbt) n = kbt;
+      for (int kb = 0; kb < n; ++kb) tma_prefetch_l2_2d(&tmW1, 0, ((e * NT1g + j) * kbt + kb) * (2 * BMW));
+    }
+  }
   if (a.fuse_dispatch && (a.phase_mask & 12)) {
     // dispatch prologue: the operand ring is free until phase 1 and serves as its scratch
     LLDispatchIO io = a.disp;

@@ -16,8 +16,10 @@
 //   and accumulates its own 256 output columns O[128 x 256] += P[128 x 48] * V[48 x own latent dims]  (3 MMAs),
 //   reading V from the SAME gathered tile through an MN-major descriptor.
 // Splitting by dimension halves the resident Q (80 KB instead of 144 KB), which makes room for a three-stage ring
-// of key tiles, and halves the Q*K^T work of each SM. Roles inside a CTA (6 warps):
-//   warps 0-3  softmax: tcgen05.ld of S, exchange, exp2, P to shared memory, lazy rescale of O
+// of key tiles, and halves the Q*K^T work of each SM. Roles inside a CTA (13 warps):
+//   warps 0-3  softmax: tcgen05.ld of S, add the partner's partial, exp2, P to shared memory, lazy rescale of O
+//   warps 9-12 exchange: tcgen05.ld of the same S and asynchronous stores of it into the partner's shared memory,
+//              so that the round trip between the two CTAs is off the softmax warps' critical path
 //   warp  4    one thread issues every MMA: Q*K^T of chunk c+1 is issued BEFORE P*V of chunk c, so the tensor
 //              pipe works on the next scores while the softmax of the current chunk runs (S is double-buffered)
 //   warp  5    gather producer: TMA tile::gather4 copies (four selected rows x 128 bytes per instruction, written
@@ -50,7 +52,7 @@ constexpr int kPBytes = kHeads * 128;            // 16 KB (96 of every 128 bytes
 constexpr int kXBytes = kChunk * kHeads * 4;     // 24 KB, [key / 4][head][4] fp32
 constexpr int kMaxChunks = 43;                   // 2064 keys per split at most
 constexpr int kMaxKeys = kMaxChunks * kChunk;
-constexpr int kThreads = 288;
+constexpr int kThreads = 416;
 constexpr int kProducerWarps = 4;   // warps 5..8 issue the gather copies: the TMA unit takes them faster from several warps
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;                         // two S buffers of 64 columns (48 used)
@@ -165,7 +167,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   uint64_t* bar_full = bars + 1;     // kStages, one arrival that expects the tile's bytes from the TMA gathers
   uint64_t* bar_empty = bars + 4;    // kStages, one commit
   uint64_t* bar_s = bars + 7;        // 2, one commit
-  uint64_t* bar_sfree = bars + 9;    // 2, 4 softmax-warp arrivals
+  uint64_t* bar_sfree = bars + 9;    // 2, arrivals of the 4 softmax warps and the 4 exchange warps
   uint64_t* bar_p = bars + 11;       // 4 softmax-warp arrivals
   uint64_t* bar_o = bars + 12;       // one commit
   uint64_t* bar_xfull = bars + 13;   // one local arrival that expects the 24 KB the partner's st.async stores deliver
@@ -193,7 +195,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_s[i], 1);
-      mbar_init(&bar_sfree[i], 4);
+      mbar_init(&bar_sfree[i], 8);
     }
     mbar_init(bar_p, 4);
     mbar_init(bar_o, 1);
@@ -252,9 +254,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       // ===================================== softmax ======================================================
       const int head = tid;   // == TMEM lane
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-      const uint32_t peer_x = map_to_cta(x_sm, peer) + static_cast<uint32_t>(head) * 16u;
       if (tid == 0) mbar_expect_tx(bar_xfull, kXBytes);   // arms the first phase; re-armed after every chunk
-      const uint32_t peer_xfull = map_to_cta(bar_xfull, peer);
       const uint32_t peer_xfree = map_to_cta(bar_xfree, peer);
       float m_run = -INFINITY, l_run = 0.f;
       bool ok = true;
@@ -286,18 +286,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_sfree[sb]);
         lap(1);
-        // partial scores to the partner, the partner's partial in
-        if (c >= 1 && !__all_sync(0xffffffffu, wait_bar<false>(bar_xfree, (c - 1) & 1, s_abort))) {
-          give_up(UMDK_PH_GROUP_READY, c);
-          ok = false;
-          break;
-        }
-        lap(2);
-#pragma unroll
-        for (int j4 = 0; j4 < kChunk / 4; ++j4)
-          st_async_v4(peer_x + j4 * (kHeads * 16), sr[4 * j4], sr[4 * j4 + 1], sr[4 * j4 + 2], sr[4 * j4 + 3],
-                      peer_xfull);
-        lap(3);
+        // the partner's partial comes in through the exchange warps of the other CTA
         if (!__all_sync(0xffffffffu, wait_bar<true>(bar_xfull, c & 1, s_abort))) {
           give_up(UMDK_PH_GROUP_READY, 1000 + c);
           ok = false;
@@ -379,7 +368,8 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         lap(7);
       }
       if (dg) {
-        for (int i = 0; i < 8; ++i) a.diag[i] = dt[i];
+        for (int i = 0; i < 8; ++i)
+          if (i != 2 && i != 3) a.diag[i] = dt[i];
       }
       // ---- epilogue: this CTA's 256 output columns ----
       // (every decision below is warp-uniform: the TMEM loads are warp-collective)
@@ -506,6 +496,51 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
           umma_commit(bar_fin);
           mbar_wait(bar_fin, 0);
         }
+      }
+    } else if (warp >= 9) {
+      // ===================================== exchange (warps 9..12) =======================================
+      const int head = (warp & 3) * 32 + lane;   // == TMEM lane
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+      const uint32_t peer_x = map_to_cta(x_sm, peer) + static_cast<uint32_t>(head) * 16u;
+      const uint32_t peer_xfull = map_to_cta(bar_xfull, peer);
+      const bool dg = a.diag != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && head == 0;
+      long long dt[2] = {0, 0};
+      long long t_prev = dg ? clock64() : 0;
+      for (int c = 0; c < num_chunks; ++c) {
+        const int sb = c & 1;
+        if (!__all_sync(0xffffffffu, wait_bar<false>(&bar_s[sb], (c >> 1) & 1, s_abort))) {
+          give_up(UMDK_PH_TMEM_FULL, 3000 + c);
+          break;
+        }
+        tc_fence_after();
+        uint32_t sr[kChunk];
+        tmem_ld_x16(lane_addr + kColS + sb * 64, sr);
+        tmem_ld_x16(lane_addr + kColS + sb * 64 + 16, sr + 16);
+        tmem_ld_x16(lane_addr + kColS + sb * 64 + 32, sr + 32);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_sfree[sb]);
+        if (dg) t_prev = clock64();
+        // the partner's softmax warps must have read the previous partial out of their exchange buffer
+        if (c >= 1 && !__all_sync(0xffffffffu, wait_bar<false>(bar_xfree, (c - 1) & 1, s_abort))) {
+          give_up(UMDK_PH_GROUP_READY, c);
+          break;
+        }
+        if (dg) {
+          const long long t = clock64();
+          dt[0] += t - t_prev;
+          t_prev = t;
+        }
+#pragma unroll
+        for (int j4 = 0; j4 < kChunk / 4; ++j4)
+          st_async_v4(peer_x + j4 * (kHeads * 16), sr[4 * j4], sr[4 * j4 + 1], sr[4 * j4 + 2], sr[4 * j4 + 3],
+                      peer_xfull);
+        if (dg) dt[1] += clock64() - t_prev;
+      }
+      if (dg) {
+        a.diag[2] = dt[0];
+        a.diag[3] = dt[1];
       }
     } else if (warp >= 5 && warp < 5 + kProducerWarps) {
       // ===================================== gather producers (warps 5..) =====================================

@@ -42,9 +42,26 @@ inline uint64_t imm_make(ImmType t, uint32_t credits, uint32_t bytes) {
 struct Block {
   umq_buf_t meta;  // must be first: umq_buf_t* <-> Block*
   bool huge;
+  bool tiny;       // comes from the tiny pool (small control / RPC messages)
   char* mem;
   uint32_t cap;
+  uint32_t gen;    // pool generation the block was made in (blocks of an older generation are freed on return)
 };
+
+// Tiny pool: requests of at most kTinyBytes (headers, acknowledgements, small RPC arguments) are served from blocks
+// of that size carved out of large slabs, so that a flood of small messages does not pin one 8-64 KiB block each. It
+// has its own free list and per-thread cache and grows slab by slab. Counterpart of the reference's tiny buffer pool
+// (src/urpc/umq/qbuf/umq_tiny_qbuf_pool.c).
+constexpr uint32_t kTinyBytes = 512;
+constexpr uint32_t kTinyPerSlab = 1024;
+struct TinyPool {
+  std::mutex mu;
+  std::vector<Block*> free_list;
+  std::vector<char*> slabs;      // data slabs of kTinyPerSlab * kTinyBytes
+  std::vector<Block*> desc_slabs;
+  uint64_t total = 0, allocs = 0, frees = 0, max_total = 1u << 20;
+};
+TinyPool g_tiny;
 
 struct Pool {
   std::mutex mu;
@@ -71,6 +88,16 @@ ThreadCache::~ThreadCache() {
   for (Block* b : v) g_pool.free_list.push_back(b);
   v.clear();
 }
+struct TinyCache {
+  std::vector<Block*> v;
+  ~TinyCache() {
+    std::lock_guard<std::mutex> l(g_tiny.mu);
+    for (Block* b : v) g_tiny.free_list.push_back(b);
+    v.clear();
+  }
+};
+thread_local TinyCache t_tiny_holder;
+#define t_tiny (t_tiny_holder.v)
 constexpr size_t kCacheMax = 64;
 
 struct Global {
@@ -211,6 +238,8 @@ struct PerfScope {
 struct Queue {
   uint64_t h;
   umq_create_option_t opt;
+  const umq_transport_ops_t* tops = nullptr;   // non-null: served by a table entry instead of the URMA code below
+  void* tpriv = nullptr;
   urma_simple_ep_t* ep = nullptr;
   urma_target_jetty_t* peer = nullptr;
   std::atomic<int> state{UMQ_STATE_IDLE};
@@ -253,14 +282,33 @@ Block* block_new(uint32_t cap, bool huge) {
   b->huge = huge;
   return b;
 }
+std::atomic<uint32_t> g_pool_gen{1};
+void block_destroy(Block* b) {   // caller holds g_pool.mu
+  g_pool.by_mem.erase(b->mem);
+  free(b->mem);
+  free(b);
+}
 void pool_init(uint32_t block, uint64_t bytes) {
   std::lock_guard<std::mutex> l(g_pool.mu);
-  if (g_pool.inited) return;
+  if (g_pool.inited && g_pool.block == block) return;
+  if (g_pool.inited) {
+    // A new umq_init after umq_uninit asks for another block size: start a new generation. Free blocks go now, blocks
+    // still held by an application or parked in a thread's cache go when they come back.
+    g_pool_gen.fetch_add(1);
+    for (Block* b : g_pool.free_list) block_destroy(b);
+    g_pool.free_list.clear();
+    for (Block* b : t_cache) block_destroy(b);
+    t_cache.clear();
+    g_pool.total = 0;
+    g_pool.grown = 0;
+    ++g_pool.generation;
+  }
   g_pool.block = block;
   const uint64_t n = bytes / block;
   for (uint64_t i = 0; i < n; ++i) {
     Block* b = block_new(block, false);
     if (!b) break;
+    b->gen = g_pool_gen.load();
     g_pool.free_list.push_back(b);
     g_pool.by_mem[b->mem] = b;
     ++g_pool.total;
@@ -268,7 +316,60 @@ void pool_init(uint32_t block, uint64_t bytes) {
   g_pool.max_total = n * 16;
   g_pool.inited = true;
 }
-Block* block_get(uint32_t need) {
+bool g_tiny_on = true;   // UMQ_TINY_POOL=0 turns it off (every request then takes a full block)
+Block* tiny_get() {
+  if (!t_tiny.empty()) {
+    Block* b = t_tiny.back();
+    t_tiny.pop_back();
+    return b;
+  }
+  std::lock_guard<std::mutex> l(g_tiny.mu);
+  if (g_tiny.free_list.empty() && g_tiny.total < g_tiny.max_total) {
+    char* slab = static_cast<char*>(malloc((size_t)kTinyPerSlab * kTinyBytes));
+    Block* descs = static_cast<Block*>(calloc(kTinyPerSlab, sizeof(Block)));
+    if (slab && descs) {
+      g_tiny.slabs.push_back(slab);
+      g_tiny.desc_slabs.push_back(descs);
+      for (uint32_t i = 0; i < kTinyPerSlab; ++i) {
+        descs[i].tiny = true;
+        descs[i].mem = slab + (size_t)i * kTinyBytes;
+        descs[i].cap = kTinyBytes;
+        g_tiny.free_list.push_back(&descs[i]);
+      }
+      g_tiny.total += kTinyPerSlab;
+      std::lock_guard<std::mutex> lp(g_pool.mu);
+      for (uint32_t i = 0; i < kTinyPerSlab; ++i) g_pool.by_mem[descs[i].mem] = &descs[i];
+    } else {
+      free(slab);
+      free(descs);
+    }
+  }
+  for (int i = 0; i < 16 && !g_tiny.free_list.empty(); ++i) {
+    t_tiny.push_back(g_tiny.free_list.back());
+    g_tiny.free_list.pop_back();
+  }
+  if (t_tiny.empty()) return nullptr;
+  Block* b = t_tiny.back();
+  t_tiny.pop_back();
+  ++g_tiny.allocs;
+  return b;
+}
+void tiny_put(Block* b) {
+  t_tiny.push_back(b);
+  if (t_tiny.size() > 128) {
+    std::lock_guard<std::mutex> l(g_tiny.mu);
+    while (t_tiny.size() > 64) {
+      g_tiny.free_list.push_back(t_tiny.back());
+      t_tiny.pop_back();
+    }
+    ++g_tiny.frees;
+  }
+}
+
+Block* block_get(uint32_t need, bool allow_tiny = false) {
+  if (allow_tiny && g_tiny_on && need <= kTinyBytes) {
+    if (Block* b = tiny_get()) return b;
+  }
   if (need > g_pool.block) {
     if (need > UMQ_MAX_MSG_SIZE) return nullptr;
     Block* b = block_new(need, true);
@@ -281,10 +382,12 @@ Block* block_get(uint32_t need) {
     }
     return b;
   }
-  if (!t_cache.empty()) {
+  while (!t_cache.empty()) {
     Block* b = t_cache.back();
     t_cache.pop_back();
-    return b;
+    if (b->gen == g_pool_gen.load()) return b;
+    std::lock_guard<std::mutex> l(g_pool.mu);   // parked here since before the pool was rebuilt
+    block_destroy(b);
   }
   std::lock_guard<std::mutex> l(g_pool.mu);
   // refill the thread cache with a small batch
@@ -297,6 +400,7 @@ Block* block_get(uint32_t need) {
   for (int i = 0; t_cache.empty() && i < 8 && g_pool.total < g_pool.max_total; ++i) {
     Block* nb = block_new(g_pool.block, false);
     if (!nb) break;
+    nb->gen = g_pool_gen.load();
     g_pool.by_mem[nb->mem] = nb;
     ++g_pool.total;
     ++g_pool.grown;
@@ -311,6 +415,10 @@ Block* block_get(uint32_t need) {
   return b;
 }
 void block_put(Block* b) {
+  if (b->tiny) {
+    tiny_put(b);
+    return;
+  }
   if (b->huge) {
     {
       std::lock_guard<std::mutex> l(g_pool.mu);
@@ -318,6 +426,11 @@ void block_put(Block* b) {
     }
     free(b->mem);
     free(b);
+    return;
+  }
+  if (b->gen != g_pool_gen.load()) {   // made before the pool was rebuilt with another block size
+    std::lock_guard<std::mutex> l(g_pool.mu);
+    block_destroy(b);
     return;
   }
   t_cache.push_back(b);
@@ -469,6 +582,107 @@ struct BindBlob {
 
 extern "C" {
 
+// ------------------------------------------------------------------------------------------------ transports
+// In-process transport (mode IPC): queues bound to each other inside one process pass buffers by pointer.
+struct LocalQ {
+  uint64_t h;
+  std::mutex mu;
+  std::deque<umq_buf_t*> rx;
+  uint64_t peer = 0;
+  uint32_t depth = 128;
+};
+std::mutex g_local_mu;
+std::unordered_map<uint64_t, LocalQ*> g_local;
+int local_create(uint64_t h, const umq_create_option_t* opt, void** priv) {
+  LocalQ* q = new LocalQ();
+  q->h = h;
+  q->depth = opt->rx_depth ? opt->rx_depth : 128;
+  std::lock_guard<std::mutex> l(g_local_mu);
+  g_local[h] = q;
+  *priv = q;
+  return UMQ_SUCCESS;
+}
+void local_destroy(void* p) {
+  LocalQ* q = static_cast<LocalQ*>(p);
+  {
+    std::lock_guard<std::mutex> l(g_local_mu);
+    g_local.erase(q->h);
+  }
+  for (umq_buf_t* b : q->rx) umq_buf_free(b);
+  delete q;
+}
+uint32_t local_bind_info(void* p, uint8_t* out, uint32_t size) {
+  if (size < 16) return 0;
+  const uint64_t magic = 0x4c4f43414c514831ull;
+  memcpy(out, &magic, 8);
+  memcpy(out + 8, &static_cast<LocalQ*>(p)->h, 8);
+  return 16;
+}
+int local_bind(void* p, const uint8_t* info, uint32_t size) {
+  uint64_t magic = 0, peer = 0;
+  if (size < 16) return UMQ_ERR_EINVAL;
+  memcpy(&magic, info, 8);
+  memcpy(&peer, info + 8, 8);
+  if (magic != 0x4c4f43414c514831ull) return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(g_local_mu);
+  if (!g_local.count(peer)) return UMQ_ERR_EINVAL;   // the peer must live in this process
+  static_cast<LocalQ*>(p)->peer = peer;
+  return UMQ_SUCCESS;
+}
+int local_unbind(void* p) {
+  static_cast<LocalQ*>(p)->peer = 0;
+  return UMQ_SUCCESS;
+}
+int local_send(void* p, umq_buf_t* b) {
+  LocalQ* q = static_cast<LocalQ*>(p);
+  LocalQ* peer = nullptr;
+  {
+    std::lock_guard<std::mutex> l(g_local_mu);
+    auto it = g_local.find(q->peer);
+    if (it == g_local.end()) return UMQ_ERR_ESTATE;
+    peer = it->second;
+    std::lock_guard<std::mutex> lp(peer->mu);
+    if (peer->rx.size() >= peer->depth) return UMQ_ERR_EAGAIN;   // the receiver's ring is full: back-pressure
+    b->umqh = peer->h;
+    peer->rx.push_back(b);
+  }
+  return UMQ_SUCCESS;
+}
+umq_buf_t* local_recv(void* p) {
+  LocalQ* q = static_cast<LocalQ*>(p);
+  std::lock_guard<std::mutex> l(q->mu);
+  if (q->rx.empty()) return nullptr;
+  umq_buf_t* b = q->rx.front();
+  q->rx.pop_front();
+  return b;
+}
+const umq_transport_ops_t g_local_ops = {"ipc-local", local_create, local_destroy, local_bind_info, local_bind,
+                                         local_unbind,  local_send,   local_recv};
+constexpr int kMaxModes = 8;
+struct TransportTable {
+  std::mutex mu;
+  const umq_transport_ops_t* ops[kMaxModes] = {nullptr};   // null at index UB: the built-in URMA transport
+  TransportTable() { ops[UMQ_TRANS_MODE_IPC] = &g_local_ops; }
+};
+TransportTable& transports() {
+  static TransportTable t;
+  return t;
+}
+
+int umq_transport_register(umq_trans_mode_t mode, const umq_transport_ops_t* ops) {
+  if ((int)mode < 0 || (int)mode >= kMaxModes) return UMQ_ERR_EINVAL;
+  if (ops && (!ops->create || !ops->destroy || !ops->bind_info_get || !ops->bind || !ops->send || !ops->recv))
+    return UMQ_ERR_EINVAL;
+  std::lock_guard<std::mutex> l(transports().mu);
+  transports().ops[mode] = ops;   // null restores the built-in URMA transport for that mode
+  return UMQ_SUCCESS;
+}
+const char* umq_transport_name(umq_trans_mode_t mode) {
+  if ((int)mode < 0 || (int)mode >= kMaxModes) return nullptr;
+  std::lock_guard<std::mutex> l(transports().mu);
+  return transports().ops[mode] ? transports().ops[mode]->name : "urma";
+}
+
 int umq_init(const umq_init_cfg_t* cfg) {
   std::lock_guard<std::mutex> l(g.mu);
   if (g.inited) return UMQ_SUCCESS;
@@ -478,6 +692,7 @@ int umq_init(const umq_init_cfg_t* cfg) {
   g.ctx = urma_simple_open(g.cfg.dev_name[0] ? g.cfg.dev_name : "shm0");
   if (!g.ctx) return UMQ_FAIL;
   pool_init(kb * 1024, g.cfg.pool_bytes ? g.cfg.pool_bytes : (64ull << 20));
+  if (const char* e = getenv("UMQ_TINY_POOL")) g_tiny_on = !(e[0] == '0');
   g.inited = true;
   return UMQ_SUCCESS;
 }
@@ -508,6 +723,25 @@ uint64_t umq_create(const umq_create_option_t* opt) {
     delete q;
     return UMQ_INVALID_HANDLE;
   }
+  {
+    const int mode = q->opt.transport ? (int)q->opt.transport - 1 : (int)g.cfg.trans_mode;
+    if (mode < 0 || mode >= kMaxModes) {
+      delete q;
+      return UMQ_INVALID_HANDLE;
+    }
+    std::lock_guard<std::mutex> l(transports().mu);
+    q->tops = transports().ops[mode];
+  }
+  if (q->tops) {
+    q->h = g.next_h.fetch_add(1);
+    if (q->tops->create(q->h, &q->opt, &q->tpriv) != UMQ_SUCCESS) {
+      delete q;
+      return UMQ_INVALID_HANDLE;
+    }
+    std::lock_guard<std::mutex> l(g.mu);
+    g.queues[q->h] = q;
+    return q->h;
+  }
   q->fc = (g.cfg.feature & UMQ_FEATURE_FLOW_CONTROL) != 0;
   // the jetty must hold the data messages plus the occasional credit-return message
   q->ep = urma_simple_ep_create(g.ctx, q->opt.rx_depth + q->opt.tx_depth + 16, opt->token,
@@ -536,6 +770,11 @@ int umq_destroy(uint64_t h) {
     q = it->second;
     g.queues.erase(it);
   }
+  if (q->tops) {
+    q->tops->destroy(q->tpriv);
+    delete q;
+    return UMQ_SUCCESS;
+  }
   for (auto* b : q->rx_ready) block_put(reinterpret_cast<Block*>(b));
   for (auto* b : q->tx_done) block_put(reinterpret_cast<Block*>(b));
   for (auto& kv : q->imported) urma_unimport_seg(kv.second);
@@ -549,6 +788,7 @@ int umq_destroy(uint64_t h) {
 
 uint32_t umq_bind_info_get(uint64_t h, uint8_t* out, uint32_t size) {
   Queue* q = find(h);
+  if (q && q->tops) return out ? q->tops->bind_info_get(q->tpriv, out, size) : 0;
   if (!q || !out || size < sizeof(BindBlob)) return 0;
   BindBlob b{};
   b.magic = 0x554d5142;
@@ -563,6 +803,11 @@ uint32_t umq_bind_info_get(uint64_t h, uint8_t* out, uint32_t size) {
 
 int umq_bind(uint64_t h, const uint8_t* info, uint32_t size) {
   Queue* q = find(h);
+  if (q && q->tops) {
+    const int rc = info ? q->tops->bind(q->tpriv, info, size) : UMQ_ERR_EINVAL;
+    if (rc == UMQ_SUCCESS) q->state = UMQ_STATE_READY;
+    return rc;
+  }
   if (!q || !info || size < sizeof(BindBlob)) return UMQ_ERR_EINVAL;
   BindBlob b;
   memcpy(&b, info, sizeof(b));
@@ -582,6 +827,10 @@ int umq_bind(uint64_t h, const uint8_t* info, uint32_t size) {
 int umq_unbind(uint64_t h) {
   Queue* q = find(h);
   if (!q) return UMQ_ERR_EINVAL;
+  if (q->tops) {
+    q->state = UMQ_STATE_IDLE;
+    return q->tops->unbind ? q->tops->unbind(q->tpriv) : UMQ_SUCCESS;
+  }
   std::lock_guard<std::mutex> l(q->mu);
   if (!q->peer) return UMQ_ERR_ESTATE;
   urma_unimport_jetty(q->peer);
@@ -612,7 +861,9 @@ umq_buf_t* umq_buf_alloc(uint32_t request_size, uint32_t num, uint64_t h) {
   }
   umq_buf_t *head = nullptr, *tail = nullptr;
   for (uint32_t i = 0; i < num; ++i) {
-    Block* b = block_get(request_size ? request_size : 1);
+    // application buffers of tiny size come from the tiny pool; receive buffers (posted by the queue itself) and
+    // anything larger come from the block pool
+    Block* b = block_get(request_size ? request_size : 1, true);
     if (!b) {
       if (head) umq_buf_free(head);
       return nullptr;
@@ -660,11 +911,32 @@ int umq_buf_reset(umq_buf_t* qbuf) {
   return UMQ_SUCCESS;
 }
 
+static int plugin_send_chain(Queue* q, umq_buf_t* qbuf, umq_buf_t** bad) {
+  if (q->state.load() != UMQ_STATE_READY) return UMQ_ERR_ESTATE;
+  for (umq_buf_t* b = qbuf; b;) {
+    umq_buf_t* nx = b->qbuf_next;
+    b->qbuf_next = nullptr;
+    const uint32_t n = b->data_size;
+    const int rc = q->tops->send(q->tpriv, b);
+    if (rc != UMQ_SUCCESS) {
+      b->qbuf_next = nx;
+      if (bad) *bad = b;
+      return rc;
+    }
+    ++q->io.tx_msgs;
+    q->io.tx_bytes += n;
+    b = nx;
+  }
+  if (bad) *bad = nullptr;
+  return UMQ_SUCCESS;
+}
+
 int umq_enqueue(uint64_t h, umq_buf_t* qbuf, umq_buf_t** bad) {
   PerfScope ps(UMQ_PERF_ENQUEUE);
   Queue* q = find(h);
   if (!q || !qbuf) return UMQ_ERR_EINVAL;
   if (!(g.cfg.feature & UMQ_FEATURE_API_BASE) && g.cfg.feature) return UMQ_ERR_EINVAL;
+  if (q->tops) return plugin_send_chain(q, qbuf, bad);
   std::lock_guard<std::mutex> l(q->mu);
   for (umq_buf_t* b = qbuf; b;) {
     umq_buf_t* nx = b->qbuf_next;
@@ -686,6 +958,14 @@ umq_buf_t* umq_dequeue(uint64_t h) {
   PerfScope ps(UMQ_PERF_DEQUEUE);
   Queue* q = find(h);
   if (!q) return nullptr;
+  if (q->tops) {
+    umq_buf_t* b = q->tops->recv(q->tpriv);
+    if (b) {
+      ++q->io.rx_msgs;
+      q->io.rx_bytes += b->data_size;
+    }
+    return b;
+  }
   std::lock_guard<std::mutex> l(q->mu);
   progress(q);
   if (q->rx_ready.empty()) return nullptr;
@@ -698,6 +978,14 @@ int umq_post(uint64_t h, umq_buf_t* qbuf, umq_io_direction_t dir, umq_buf_t** ba
   PerfScope ps(UMQ_PERF_POST_TX);
   Queue* q = find(h);
   if (!q || !qbuf) return UMQ_ERR_EINVAL;
+  if (q->tops) {
+    if (dir == UMQ_IO_RX) {   // such transports own their receive side: buffers offered for it are simply returned
+      umq_buf_free(qbuf);
+      if (bad) *bad = nullptr;
+      return UMQ_SUCCESS;
+    }
+    return plugin_send_chain(q, qbuf, bad);
+  }
   std::lock_guard<std::mutex> l(q->mu);
   if (dir == UMQ_IO_RX) {
     // application-provided receive buffers (instead of the automatic refill)
@@ -737,6 +1025,15 @@ int umq_poll(uint64_t h, umq_io_direction_t dir, umq_buf_t** bufs, uint32_t max)
   PerfScope ps(UMQ_PERF_POLL_RX);
   Queue* q = find(h);
   if (!q || !bufs || max == 0) return UMQ_ERR_EINVAL;
+  if (q->tops) {
+    uint32_t n = 0;
+    while (dir == UMQ_IO_RX && n < max) {
+      umq_buf_t* b = q->tops->recv(q->tpriv);
+      if (!b) break;
+      bufs[n++] = b;
+    }
+    return static_cast<int>(n);
+  }
   std::lock_guard<std::mutex> l(q->mu);
   progress(q);
   std::deque<umq_buf_t*>& src = dir == UMQ_IO_RX ? q->rx_ready : q->tx_done;
@@ -1032,7 +1329,16 @@ int umq_get_route_list(const umq_route_key_t* key, umq_trans_mode_t, umq_route_l
   return UMQ_SUCCESS;
 }
 int umq_mempool_state_get(uint64_t, uint32_t mempool_id, umq_mempool_state_t* out) {
-  if (!out || mempool_id != 0) return UMQ_ERR_EINVAL;   // one pool: id 0
+  if (!out || mempool_id > 1) return UMQ_ERR_EINVAL;   // pool 0: blocks, pool 1: tiny buffers
+  if (mempool_id == 1) {
+    std::lock_guard<std::mutex> l(g_tiny.mu);
+    out->block_size = kTinyBytes;
+    out->blocks_total = g_tiny.total;
+    out->blocks_free = g_tiny.free_list.size();
+    out->registered = g_tiny_on ? 1 : 0;
+    out->generation = g_tiny.slabs.size();
+    return UMQ_SUCCESS;
+  }
   std::lock_guard<std::mutex> l(g_pool.mu);
   out->block_size = g_pool.block;
   out->blocks_total = g_pool.total;

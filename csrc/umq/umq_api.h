@@ -48,6 +48,7 @@ typedef struct umq_create_option {
   uint32_t rx_depth, tx_depth;       /* 0 = 128 */
   umq_queue_mode_t mode;
   uint32_t token;
+  uint32_t transport; /* 0 = the transport mode given to umq_init, else (umq_trans_mode_t value + 1) for this queue */
 } umq_create_option_t;
 
 /* Message buffer. `buf_data` points `headroom_size` bytes into the block; buffers chain through `qbuf_next`. */
@@ -110,6 +111,24 @@ UMQ_EXPORT int umq_stats_qbuf_pool_get(umq_qbuf_stats_t* out);
 UMQ_EXPORT int umq_stats_perf_start(void);
 UMQ_EXPORT int umq_stats_perf_stop(void);
 UMQ_EXPORT int umq_stats_perf_get(umq_perf_entry_t* entries /* [UMQ_PERF_RECORD_MAX] */);
+/* ---- transports ----
+ * Every transport mode has an entry in a table of operations; a queue is served by the entry of its mode. Mode UB is
+ * the built-in URMA transport (send / receive over jetties, credits in the immediate data). Mode IPC is a built-in
+ * in-process transport: two queues of one process hand buffers to each other without copying. Further modes can be
+ * added (or these replaced) with umq_transport_register before queues of that mode are created - the counterpart of the
+ * reference's per-mode framework table (src/urpc/umq/umq_api.c:65-204, 258-270). */
+typedef struct umq_transport_ops {
+  const char* name;
+  int (*create)(uint64_t umqh, const umq_create_option_t* opt, void** priv);
+  void (*destroy)(void* priv);
+  uint32_t (*bind_info_get)(void* priv, uint8_t* out, uint32_t size);
+  int (*bind)(void* priv, const uint8_t* info, uint32_t size);
+  int (*unbind)(void* priv);
+  int (*send)(void* priv, struct umq_buf* one); /* one buffer; ownership passes to the transport on success */
+  struct umq_buf* (*recv)(void* priv);          /* next received buffer or NULL; the caller frees it */
+} umq_transport_ops_t;
+UMQ_EXPORT int umq_transport_register(umq_trans_mode_t mode, const umq_transport_ops_t* ops);
+UMQ_EXPORT const char* umq_transport_name(umq_trans_mode_t mode);
 /* ---- buffer lists ---- */
 /* Cuts the list at `node`: `head` keeps the buffers before it, `node` starts a list of its own (sizes recomputed). */
 UMQ_EXPORT int umq_buf_split(umq_buf_t* head, umq_buf_t* node);

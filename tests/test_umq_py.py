@@ -183,3 +183,78 @@ def test_buffer_lists_queries_and_transport_pool(pair):
     assert lib.umq_log_config_get(ctypes.byref(lvl)) == 0 and 0 <= lvl.value <= 4
     big = ctypes.create_string_buffer(2048)
     assert lib.umq_stats_perf_to_str(big, 2048) > 0 and b"enqueue" in big.value
+
+
+def test_tiny_messages_come_from_the_tiny_pool(tmp_path):
+    """Buffers of at most 512 bytes are served from the tiny pool (pool id 1) and leave the block pool untouched;
+    a message sent from a tiny buffer arrives intact."""
+    import ctypes
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import umq
+    lib = umq._lib()
+
+    class State(ctypes.Structure):
+        _fields_ = [("block_size", ctypes.c_uint64), ("blocks_total", ctypes.c_uint64),
+                    ("blocks_free", ctypes.c_uint64), ("generation", ctypes.c_uint64), ("registered", ctypes.c_int)]
+
+    def state(pool):
+        st = State()
+        assert lib.umq_mempool_state_get(ctypes.c_uint64(0), pool, ctypes.byref(st)) == 0
+        return st
+
+    umq.init()
+    try:
+        a, b = umq.Queue("tiny_a", depth=16), umq.Queue("tiny_b", depth=16)
+        a.bind(b.bind_info())
+        b.bind(a.bind_info())
+        big0 = state(0).blocks_free
+        bufs = [lib.umq_buf_alloc(100, 1, a.h) for _ in range(300)]
+        assert all(bufs)
+        t = state(1)
+        assert t.block_size == 512 and t.blocks_total >= 1024 and t.registered == 1
+        assert state(0).blocks_free >= big0 - 8          # the block pool did not pay for them
+        for p in bufs:
+            lib.umq_buf_free(p)
+        a.send(b"tiny payload")
+        assert b.recv() == b"tiny payload"
+        assert lib.umq_mempool_state_get(ctypes.c_uint64(0), 2, ctypes.byref(State())) != 0
+        a.close()
+        b.close()
+    finally:
+        umq.uninit()
+
+
+def test_transport_table_serves_queues_by_mode(pair):
+    """Queues created with the in-process transport mode exchange buffers without touching URMA, side by side with
+    queues on the URMA transport; a full receiver pushes back; a mode can be given a user-supplied table entry."""
+    import ctypes
+    umq, a, b = pair
+    lib = umq._lib()
+    lib.umq_transport_name.restype = ctypes.c_char_p
+    assert lib.umq_transport_name(umq.TRANS_MODE_UB) == b"urma"
+    assert lib.umq_transport_name(umq.TRANS_MODE_IPC) == b"ipc-local"
+    x, y = umq.Queue("lx", depth=4, transport=umq.TRANS_MODE_IPC), umq.Queue("ly", depth=4, transport=umq.TRANS_MODE_IPC)
+    try:
+        x.bind(y.bind_info())
+        y.bind(x.bind_info())
+        for i in range(4):
+            x.send(bytes([i]) * 1000)
+        with pytest.raises(umq.UmqError):           # the receiver's ring of 4 is full
+            x.send(b"one too many")
+        assert [y.recv() for _ in range(4)] == [bytes([i]) * 1000 for i in range(4)]
+        y.send(b"back")
+        assert x.recv() == b"back" and x.recv(timeout_s=0.02) is None
+        assert x.io_stats()["tx_msgs"] == 4 and y.io_stats()["rx_msgs"] == 4
+        a.send(b"urma path still works")             # the URMA-backed pair is unaffected
+        assert b.recv() == b"urma path still works"
+        with pytest.raises(umq.UmqError):            # an in-process queue cannot bind to a URMA queue's blob
+            x2 = umq.Queue("lz", transport=umq.TRANS_MODE_IPC)
+            try:
+                x2.bind(a.bind_info())
+            finally:
+                x2.close()
+        assert lib.umq_transport_register(99, None) != 0
+    finally:
+        x.close()
+        y.close()

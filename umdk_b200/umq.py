@@ -27,10 +27,13 @@ class _InitCfg(ctypes.Structure):
                 ("block_size_kb", ctypes.c_uint32), ("pool_bytes", ctypes.c_uint64)]
 
 
+TRANS_MODE_UB, TRANS_MODE_IPC = 0, 3   # umq_trans_mode_t
+
+
 class _CreateOpt(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char * 32), ("rx_buf_size", ctypes.c_uint32), ("tx_buf_size", ctypes.c_uint32),
                 ("rx_depth", ctypes.c_uint32), ("tx_depth", ctypes.c_uint32), ("mode", ctypes.c_int),
-                ("token", ctypes.c_uint32)]
+                ("token", ctypes.c_uint32), ("transport", ctypes.c_uint32)]
 
 
 class _Buf(ctypes.Structure):
@@ -150,10 +153,14 @@ def trace_stop() -> dict:
 
 
 class Queue:
-    def __init__(self, name: str, depth: int = 128, buf_size: int = 0, token: int = 0x756d71):
+    def __init__(self, name: str, depth: int = 128, buf_size: int = 0, token: int = 0x756d71,
+                 transport: Optional[int] = None):
+        """``transport``: a transport mode for this queue (TRANS_MODE_UB = URMA, TRANS_MODE_IPC = the in-process
+        transport, or a mode registered with umq_transport_register); None = the mode given to ``init``."""
         o = _CreateOpt()
         o.name, o.rx_depth, o.tx_depth, o.rx_buf_size, o.tx_buf_size, o.token = \
             name.encode(), depth, depth, buf_size, buf_size, token
+        o.transport = 0 if transport is None else transport + 1
         self.h = _lib().umq_create(ctypes.byref(o))
         if not self.h:
             raise UmqError("umq_create failed")
