@@ -7,17 +7,28 @@
 //   urma_admin topo                 discovered topology: nodes, ports, and the path set between the first two nodes
 //   urma_admin stats <bond-dev> [seconds]   per-path state and counters of a multipath device while a loopback
 //                                   workload runs on it (up, sent, errors, failovers, failbacks, admin state)
+//   urma_admin eid add <dev> <eid> [index] | eid del <dev> <index> | eid show [dev] | eid mode <dev> static|dynamic
+//                                   extra EIDs of a device (indexes 1..8; contexts are created on them with
+//                                   urma_create_context(dev, index)) and how indexes are handed out
+//   urma_admin ns mode exclusive|shared     device visibility between namespaces (a system-wide setting)
+//   urma_admin sharing <dev> on|off         whether several processes may open the device at the same time
+//   urma_admin system show                  the system-wide settings and every device record
+// The eid / ns / sharing commands are sent to the library as TLV messages (urma_cmd_tlv.h), the form the reference's
+// tool uses towards its kernel core (admin_cmd_eid.c, admin_cmd_system.c).
 // Mirrors the `show` / `perf start|show` commands of the reference's urma_admin
 // (doc/en/urma/URMA User Guide.md:1874-2010) and the EID-level reachability check of its urma_ping.
 #include <sched.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/stat.h>
 #include <unistd.h>
 
+#include <string>
 #include <vector>
 
 #include "ub_util.h"
+#include "urma_cmd_tlv.h"
 #include "urma_simple.h"
 #include "uvs_topo.h"
 
@@ -197,7 +208,66 @@ static int stats(const char* dev, int seconds) {
   return 0;
 }
 
+extern "C" int urma_admin_cmd_exec(const uint8_t* cmd, uint32_t len, uint8_t* out, uint32_t* out_len);
+
+static int run_tlv(const urma_tlv::Encoder& enc) {
+  urma_init_attr_t attr{};
+  urma_init(&attr);
+  const std::vector<uint8_t> cmd = enc.finish();
+  std::vector<uint8_t> out(1 << 16);
+  uint32_t n = static_cast<uint32_t>(out.size());
+  if (urma_admin_cmd_exec(cmd.data(), static_cast<uint32_t>(cmd.size()), out.data(), &n) != 0) {
+    fprintf(stderr, "urma_admin: command rejected\n");
+    return 1;
+  }
+  urma_tlv::Decoder d;
+  int32_t status = -1;
+  std::string text;
+  if (!d.parse(out.data(), n) || !d.get_i32(urma_tlv::ATTR_STATUS, &status)) return 1;
+  d.get_str(urma_tlv::ATTR_TEXT, &text);
+  if (!text.empty()) fprintf(status == 0 ? stdout : stderr, "%s%s", text.c_str(), text.back() == '\n' ? "" : "\n");
+  return status == 0 ? 0 : 1;
+}
+
+static int admin_settings(int argc, char** argv) {
+  using namespace urma_tlv;
+  const std::string a = argv[1], b = argc >= 3 ? argv[2] : "";
+  if (a == "eid" && b == "add" && argc >= 5) {
+    urma_eid_t eid;
+    if (urma_str_to_eid(argv[4], &eid) != 0) {
+      fprintf(stderr, "urma_admin: bad EID %s\n", argv[4]);
+      return 2;
+    }
+    struct stat sb{};
+    uint64_t ns = stat("/proc/self/ns/net", &sb) == 0 ? (uint64_t)sb.st_ino : 0;
+    Encoder e(CMD_EID_ADD);
+    e.put_str(ATTR_DEV_NAME, argv[3]).put_bytes(ATTR_EID, eid.raw, 16).put_u64(ATTR_NS, ns);
+    if (argc >= 6) e.put_u32(ATTR_EID_INDEX, (uint32_t)atoi(argv[5]));
+    return run_tlv(e);
+  }
+  if (a == "eid" && b == "del" && argc >= 5)
+    return run_tlv(Encoder(CMD_EID_DEL).put_str(ATTR_DEV_NAME, argv[3]).put_u32(ATTR_EID_INDEX, (uint32_t)atoi(argv[4])));
+  if (a == "eid" && b == "show") {
+    Encoder e(CMD_EID_SHOW);
+    if (argc >= 4) e.put_str(ATTR_DEV_NAME, argv[3]);
+    return run_tlv(e);
+  }
+  if (a == "eid" && b == "mode" && argc >= 5)
+    return run_tlv(Encoder(CMD_EID_MODE).put_str(ATTR_DEV_NAME, argv[3]).put_u32(ATTR_FLAG, !strcmp(argv[4], "dynamic")));
+  if (a == "ns" && b == "mode" && argc >= 4)
+    return run_tlv(Encoder(CMD_NS_MODE).put_u32(ATTR_FLAG, !strcmp(argv[3], "shared")));
+  if (a == "sharing" && argc >= 4)
+    return run_tlv(Encoder(CMD_SHARING).put_str(ATTR_DEV_NAME, argv[2]).put_u32(ATTR_FLAG, !strcmp(argv[3], "on")));
+  if (a == "system" && b == "show") return run_tlv(Encoder(CMD_SYSTEM_SHOW));
+  return -1;
+}
+
 int main(int argc, char** argv) {
+  if (argc >= 2 && (!strcmp(argv[1], "eid") || !strcmp(argv[1], "ns") || !strcmp(argv[1], "sharing") ||
+                    !strcmp(argv[1], "system"))) {
+    const int rc = admin_settings(argc, argv);
+    if (rc >= 0) return rc;
+  }
   if (argc >= 2 && !strcmp(argv[1], "show")) return show();
   if (argc >= 3 && !strcmp(argv[1], "perf")) return perf(atoi(argv[2]));
   if (argc >= 3 && !strcmp(argv[1], "ping")) return ping(argv[2], argc >= 4 ? atoi(argv[3]) : 5);
@@ -205,6 +275,7 @@ int main(int argc, char** argv) {
   if (argc >= 2 && !strcmp(argv[1], "topo")) return topo();
   if (argc >= 3 && !strcmp(argv[1], "stats")) return stats(argv[2], argc >= 4 ? atoi(argv[3]) : 0);
   fprintf(stderr, "usage: urma_admin show | perf <seconds> | ping <dev> [count] | agg [name] | topo | "
-                  "stats <bond-dev> [seconds]\n");
+                  "stats <bond-dev> [seconds] | eid add|del|show|mode ... | ns mode exclusive|shared | "
+                  "sharing <dev> on|off | system show\n");
   return 2;
 }

@@ -325,12 +325,16 @@ urma_status_t urma_query_device(urma_device_t* dev, urma_device_attr_t* attr) {
   }
   return p->query_device ? p->query_device(dev, attr) : URMA_FAIL;
 }
+extern "C" int urma_eid_table_get(const char* dev_name, urma_eid_info_t* out, int max);
+extern "C" int urma_eid_table_claim(const char* dev_name);
+
+// Index 0 is the EID the provider reports; indexes 1..8 are EIDs an administrator added (urma_admin eid add).
 urma_eid_info_t* urma_get_eid_list(urma_device_t* dev, uint32_t* cnt) {
   if (!dev || !cnt) return nullptr;
-  urma_eid_info_t* l = static_cast<urma_eid_info_t*>(calloc(1, sizeof(urma_eid_info_t)));
+  urma_eid_info_t* l = static_cast<urma_eid_info_t*>(calloc(9, sizeof(urma_eid_info_t)));
   l[0].eid = dev->eid;
   l[0].eid_index = 0;
-  *cnt = 1;
+  *cnt = 1 + static_cast<uint32_t>(urma_eid_table_get(dev->name, l + 1, 8));
   return l;
 }
 void urma_free_eid_list(urma_eid_info_t* list) { free(list); }
@@ -380,10 +384,34 @@ urma_context_t* urma_create_context(urma_device_t* dev, uint32_t eid_index) {
     p = c.device_provider[dev->index];
   }
   if (!p->create_context) return nullptr;
-  urma_context_t* ctx = p->create_context(dev, eid_index);
+  urma_eid_t extra{};
+  if (eid_index > 0) {   // an EID added by the administrator: it must exist
+    urma_eid_info_t l[8];
+    const int n = urma_eid_table_get(dev->name, l, 8);
+    bool found = false;
+    for (int i = 0; i < n; ++i)
+      if (l[i].eid_index == eid_index) {
+        extra = l[i].eid;
+        found = true;
+      }
+    if (!found) {
+      urma_log(URMA_VLOG_LEVEL_ERR, __func__, __LINE__, "%s has no EID with index %u", dev->name, eid_index);
+      return nullptr;
+    }
+  }
+  if (!urma_eid_table_claim(dev->name)) {
+    urma_log(URMA_VLOG_LEVEL_ERR, __func__, __LINE__, "%s is exclusive and held by another process", dev->name);
+    return nullptr;
+  }
+  // the provider only knows its own EID (index 0); an added EID is attached to the context here
+  urma_context_t* ctx = p->create_context(dev, 0);
   if (ctx) {
     ctx->dev = dev;
     ctx->refcnt = 1;
+    if (eid_index > 0) {
+      ctx->eid = extra;
+      ctx->eid_index = eid_index;
+    }
   }
   return ctx;
 }

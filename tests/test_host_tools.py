@@ -280,3 +280,92 @@ def test_urma_extended_control_plane(dev, tmp_path):
     """Two-phase creation, options, batch deletion, notifier-based import / bind, transport paths, addressing."""
     rc, out = _run([BIN / "urma_ext_selftest", dev], tmp_path)
     assert rc == 0 and f"urma_ext_selftest: OK ({dev})" in out, out
+
+
+def test_urma_admin_eid_namespace_and_sharing_commands(tmp_path):
+    """EID add / del / show / mode, namespace mode and device sharing through the admin tool (TLV commands executed
+    by the library), then the library's view: the EID list of the device, a context on an added EID, and an
+    exclusive device that a second process cannot open."""
+    adm = BIN / "urma_admin"
+    e1, e2 = "fe80:0000:0000:0000:0000:0000:0000:0042", "fe80:0000:0000:0000:0000:0000:0000:0043"
+    rc, out = _run([adm, "eid", "add", "shm0", e1], tmp_path)
+    assert rc == 0 and "eid index 1" in out, out
+    rc, out = _run([adm, "eid", "add", "shm0", e2, "5"], tmp_path)
+    assert rc == 0 and "eid index 5" in out
+    assert _run([adm, "eid", "add", "shm0", e2], tmp_path)[0] == 1            # duplicate
+    assert _run([adm, "eid", "add", "nodev0", e1], tmp_path)[0] == 1          # unknown device
+    assert _run([adm, "eid", "add", "shm0", "not-an-eid"], tmp_path)[0] == 2
+    rc, out = _run([adm, "eid", "show", "shm0"], tmp_path)
+    assert rc == 0 and e1 in out and "[5] " + e2 in out
+    assert _run([adm, "eid", "mode", "shm0", "dynamic"], tmp_path)[0] == 0
+    assert _run([adm, "eid", "add", "shm0", "fe80::", "3"], tmp_path)[0] != 0   # dynamic mode hands out the index
+    assert _run([adm, "ns", "mode", "exclusive"], tmp_path)[0] == 0
+    rc, out = _run([adm, "system", "show"], tmp_path)
+    assert rc == 0 and "namespace mode: exclusive" in out and "eid mode dynamic" in out
+    # the library sees the added EIDs and opens a context on one of them
+    code = (
+        "import ctypes, os, sys\n"
+        "from umdk_b200 import _native\n"
+        "lib = _native.urma()\n"
+        "class Attr(ctypes.Structure): _fields_ = [('x', ctypes.c_uint8 * 64)]\n"
+        "lib.urma_init(ctypes.byref(Attr()))\n"
+        "lib.urma_get_device_by_name.restype = ctypes.c_void_p\n"
+        "dev = lib.urma_get_device_by_name(b'shm0')\n"
+        "class Info(ctypes.Structure): _fields_ = [('eid', ctypes.c_uint8 * 16), ('idx', ctypes.c_uint32), ('pad', ctypes.c_uint32)]\n"
+        "lib.urma_get_eid_list.restype = ctypes.POINTER(Info)\n"
+        "n = ctypes.c_uint32(0)\n"
+        "l = lib.urma_get_eid_list(ctypes.c_void_p(dev), ctypes.byref(n))\n"
+        "print('EIDS', sorted(l[i].idx for i in range(n.value)), bytes(l[1].eid)[-1])\n"
+        "lib.urma_create_context.restype = ctypes.c_void_p\n"
+        "print('CTX5', bool(lib.urma_create_context(ctypes.c_void_p(dev), 5)), "
+        "'CTX7', bool(lib.urma_create_context(ctypes.c_void_p(dev), 7)))\n"
+        "if len(sys.argv) > 1: sys.stdin.readline()\n")
+    rc, out = _run([sys.executable, "-c", code], tmp_path, env_extra={"PYTHONPATH": str(_native.lib_dir().parent.parent)})
+    assert rc == 0 and "EIDS [0, 1, 5] 66" in out and "CTX5 True CTX7 False" in out, out
+    # exclusive device: while one process holds it, another cannot open a context
+    assert _run([adm, "sharing", "shm0", "off"], tmp_path)[0] == 0
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"), PYTHONPATH=str(_native.lib_dir().parent.parent))
+    holder = subprocess.Popen([sys.executable, "-c", code, "hold"], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True, env=env)
+    try:
+        assert "CTX5 True" in holder.stdout.readline() + holder.stdout.readline()
+        rc, out = _run([sys.executable, "-c", code], tmp_path, env_extra={"PYTHONPATH": env["PYTHONPATH"]})
+        assert "CTX5 False" in out, out
+    finally:
+        holder.stdin.write("\n")
+        holder.stdin.flush()
+        holder.wait(timeout=30)
+    assert _run([adm, "sharing", "shm0", "on"], tmp_path)[0] == 0
+    assert _run([adm, "eid", "del", "shm0", "1"], tmp_path)[0] == 0
+    assert _run([adm, "eid", "del", "shm0", "1"], tmp_path)[0] == 1
+
+
+def test_tlv_commands_reject_malformed_input(tmp_path):
+    import ctypes
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    lib = _native.urma()
+    out = ctypes.create_string_buffer(4096)
+
+    def run(cmd: bytes):
+        n = ctypes.c_uint32(4096)
+        return lib.urma_admin_cmd_exec(cmd, len(cmd), out, ctypes.byref(n)), out.raw[:n.value]
+
+    import struct
+    def tlv(command, attrs):
+        body = b""
+        for t, v in attrs:
+            body += struct.pack("<HHI", t, 0, len(v)) + v + b"\0" * (-len(v) % 8)
+        return struct.pack("<IIII", 0x564c5455, command, len(attrs), 16 + len(body)) + body
+
+    good = tlv(7, [])
+    rc, rep = run(good)
+    assert rc == 0 and rep[:4] == struct.pack("<I", 0x564c5455) and b"namespace mode" in rep
+    assert run(good[:-1] if len(good) > 16 else good[:12])[0] == -1             # truncated
+    assert run(b"\0" * 16)[0] == -1                                             # wrong magic
+    bad_len = struct.pack("<IIII", 0x564c5455, 3, 1, 32) + struct.pack("<HHI", 1, 0, 4000) + b"x" * 8
+    assert run(bad_len)[0] == -1                                                # attribute runs past the end
+    dup = tlv(3, [(1, b"shm0"), (1, b"shm0")])
+    assert run(dup)[0] == -1                                                    # the same attribute twice
+    rc, rep = run(tlv(42, []))
+    assert rc == 0 and b"unknown command" in rep
