@@ -10,6 +10,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <syslog.h>
 #include <time.h>
 
 #include <atomic>
@@ -304,6 +305,8 @@ class Logger {
     char name[64];
     snprintf(name, sizeof(name), "%s_LOG_LEVEL", tag);
     if (const char* e = getenv(name)) level_ = atoi(e);
+    snprintf(name, sizeof(name), "%s_LOG_SYSLOG", tag);
+    if (const char* e = getenv(name)) to_syslog_ = atoi(e) != 0;
   }
   void configure(int level, log_cb_t cb) {
     level_ = level;
@@ -322,7 +325,12 @@ class Logger {
       cb(lvl, msg);
     } else {
       static const char* const names[] = {"ERR", "WARN", "NOTICE", "INFO", "DEBUG"};
-      fprintf(stderr, "[%s][%s] %s\n", tag_, names[lvl < 0 ? 0 : (lvl > 4 ? 4 : lvl)], msg);
+      static const int prio[] = {LOG_ERR, LOG_WARNING, LOG_NOTICE, LOG_INFO, LOG_DEBUG};
+      const int l = lvl < 0 ? 0 : (lvl > 4 ? 4 : lvl);
+      if (to_syslog_)  // same "[TAG][LEVEL]" prefix as on stderr: the packaged rsyslog rules route on it
+        syslog(prio[l], "[%s][%s] %s", tag_, names[l], msg);
+      else
+        fprintf(stderr, "[%s][%s] %s\n", tag_, names[l], msg);
     }
   }
 
@@ -330,6 +338,7 @@ class Logger {
   const char* tag_;
   std::atomic<int> level_{kLogWarn};
   std::atomic<log_cb_t> cb_{nullptr};
+  bool to_syslog_ = false;
 };
 
 }  // namespace ub

@@ -688,9 +688,15 @@ int umq_init(const umq_init_cfg_t* cfg) {
   if (g.inited) return UMQ_SUCCESS;
   if (cfg) g.cfg = *cfg;
   const uint32_t kb = g.cfg.block_size_kb ? g.cfg.block_size_kb : 8;
-  if (kb != 8 && kb != 16 && kb != 32 && kb != 64) return UMQ_ERR_EINVAL;
+  if (kb != 8 && kb != 16 && kb != 32 && kb != 64) {
+    g_log.log(ub::kLogErr, "umq_init: block size %u KB is not one of 8 / 16 / 32 / 64", kb);
+    return UMQ_ERR_EINVAL;
+  }
   g.ctx = urma_simple_open(g.cfg.dev_name[0] ? g.cfg.dev_name : "shm0");
-  if (!g.ctx) return UMQ_FAIL;
+  if (!g.ctx) {
+    g_log.log(ub::kLogErr, "umq_init: device %s cannot be opened", g.cfg.dev_name[0] ? g.cfg.dev_name : "shm0");
+    return UMQ_FAIL;
+  }
   pool_init(kb * 1024, g.cfg.pool_bytes ? g.cfg.pool_bytes : (64ull << 20));
   if (const char* e = getenv("UMQ_TINY_POOL")) g_tiny_on = !(e[0] == '0');
   g.inited = true;
@@ -712,7 +718,10 @@ void umq_uninit(void) {
 }
 
 uint64_t umq_create(const umq_create_option_t* opt) {
-  if (!opt || !g.inited) return UMQ_INVALID_HANDLE;
+  if (!opt || !g.inited) {
+    g_log.log(ub::kLogErr, "umq_create: %s", !opt ? "no options given" : "umq_init has not run");
+    return UMQ_INVALID_HANDLE;
+  }
   Queue* q = new Queue();
   q->opt = *opt;
   if (!q->opt.rx_depth) q->opt.rx_depth = 128;

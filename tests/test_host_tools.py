@@ -369,3 +369,31 @@ def test_tlv_commands_reject_malformed_input(tmp_path):
     assert run(dup)[0] == -1                                                    # the same attribute twice
     rc, rep = run(tlv(42, []))
     assert rc == 0 and b"unknown command" in rep
+
+
+def test_log_routing_configs_match_what_the_libraries_emit():
+    """The packaged rsyslog rules route on message prefixes: every prefix they name must be one a library really
+    writes, and the logrotate rules must cover every directory the rsyslog templates write to."""
+    import re
+    root = os.path.join(os.path.dirname(__file__), "..", "config")
+    rs = open(os.path.join(root, "umdk_b200_rsyslog.conf")).read()
+    lr = open(os.path.join(root, "umdk_b200_logrotate")).read()
+    prefixes = re.findall(r"\$msg contains '([^']+)'", rs)
+    assert set(prefixes) == {"URMA|", "[UMQ][", "[URPC][", "[UMS_AGENT]["}
+    dirs = set(re.findall(r'"(/var/log/umdk_b200/\w+)/%programname%\.log"', rs))
+    assert dirs and all(f"{d}/*.log" in lr for d in dirs)
+    assert "copytruncate" in lr and "\n    create" not in lr and "nocreate" not in lr
+    assert lr.count("{") == lr.count("}") == 1
+    # liburma: the prefix as written to stderr (the same string goes to syslog)
+    code = ("from umdk_b200 import _native; l=_native.urma(); "
+            "l.urma_log_set_level(7); l.urma_log(4, b'probe', 1, b'routed by prefix')")
+    env = dict(os.environ, URMA_LOG_STDERR="1", URMA_SHM_DIR="/tmp/umdk_logtest")
+    p = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stderr
+    assert any(line.startswith("URMA|") for line in p.stderr.splitlines()), p.stderr[-500:]
+    # the queue library's logger: "[UMQ][LEVEL] ..."
+    code = ("from umdk_b200 import _native; import ctypes; l=_native.umq(); l.umq_create.restype=ctypes.c_uint64; "
+            "l.umq_create(None)")
+    p = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, UMQ_LOG_LEVEL="4"), capture_output=True,
+                       text=True, timeout=120)
+    assert re.search(r"^\[UMQ\]\[(ERR|WARN|NOTICE|INFO|DEBUG)\] ", p.stderr, re.M), p.stderr[-500:]

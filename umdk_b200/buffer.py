@@ -142,8 +142,14 @@ class Buffer:
                  num_tokens_per_expert=None, topk_idx: Optional[torch.Tensor] = None,
                  topk_weights: Optional[torch.Tensor] = None, expert_alignment: int = 1, config: Optional[Config] = None,
                  previous_event=None, async_finish: bool = False, allocate_on_comm_stream: bool = False,
-                 use_fp8: bool = True, num_experts: Optional[int] = None):
-        """-> (recv_x, recv_topk_idx, recv_topk_weights, num_recv_tokens_per_expert_list, handle, event)"""
+                 use_fp8: bool = True, num_experts: Optional[int] = None, static_shapes: Optional[bool] = None):
+        """-> (recv_x, recv_topk_idx, recv_topk_weights, num_recv_tokens_per_expert_list, handle, event)
+
+        With ``static_shapes`` (argument, or the attribute of that name set on the buffer) nothing is read back on
+        the host: every result keeps its capacity-bound number of rows, ``num_recv_tokens_per_expert_list`` is the
+        device tensor of counts instead of a list, rows past the received ones carry expert id ``-1`` and weight 0.
+        That call sequence can be captured in a CUDA graph; the reference's host read of the counts
+        (deep_ep/buffer.py: ``num_recv_tokens_per_expert_list``) is what the default form keeps."""
         if previous_event is not None:
             previous_event.current_stream_wait()
         if handle is not None and topk_idx is None:
@@ -155,6 +161,8 @@ class Buffer:
         el = E // self.group_size
         if x.is_cuda:
             st = self._normal_state(E, K, x.shape[1], T)
+            if static_shapes if static_shapes is not None else getattr(self, "static_shapes", False):
+                return self._dispatch_static(st, x, topk_idx, topk_weights, use_fp8, el, async_finish)
             out = st.dispatch(x.contiguous(), topk_idx.contiguous(),
                               topk_weights.contiguous() if topk_weights is not None else None, quant=use_fp8,
                               sync_counts=True)
@@ -179,6 +187,29 @@ class Buffer:
         recv_x = (res.recv_x, res.recv_scales) if use_fp8 else res.recv_x
         h = DispatchHandle("cpu", topk_idx, topk_weights, T, cpu=res)
         return recv_x, rows_le, res.recv_weights, res.recv_tokens_per_expert.tolist(), h, EventOverlap()
+
+    def _dispatch_static(self, st, x, topk_idx, topk_weights, use_fp8, el, async_finish):
+        """Dispatch whose results keep their worst-case sizes; every count stays on the device."""
+        T, K = topk_idx.shape
+        out = st.dispatch(x.contiguous(), topk_idx.contiguous(),
+                          topk_weights.contiguous() if topk_weights is not None else None, quant=use_fp8)
+        dev = x.device
+        n_cap, a_cap = out.recv_x.shape[0], out.recv_meta.shape[0]
+        ends = out.recv_tokens_per_expert.cumsum(0)                       # [E_local] row where each expert ends
+        rows_le = torch.searchsorted(ends, torch.arange(n_cap, device=dev), right=True)
+        rows_le = torch.where(rows_le < el, rows_le, torch.full_like(rows_le, -1))
+        # weights ride in the arrival metadata; rows of arrivals that did not happen are sent to a spare slot
+        arrived = (torch.arange(a_cap, device=dev) < out.counts[1]).unsqueeze(1)
+        rows = out.recv_meta[:, 2:2 + K].long()
+        wbits = out.recv_meta[:, 2 + K:2 + 2 * K].contiguous().view(torch.float32)
+        ok = arrived & (rows >= 0) & (rows < n_cap)
+        recv_w = torch.zeros(n_cap + 1, dtype=torch.float32, device=dev)
+        recv_w.scatter_(0, torch.where(ok, rows, torch.full_like(rows, n_cap)).reshape(-1),
+                        torch.where(ok, wbits, torch.zeros_like(wbits)).reshape(-1))
+        recv_x = (out.recv_x, out.recv_scales) if use_fp8 else out.recv_x
+        h = DispatchHandle("gpu", topk_idx, topk_weights, T, gpu=out)
+        ev = EventOverlap(torch.cuda.current_stream().record_event()) if async_finish else EventOverlap()
+        return recv_x, rows_le, recv_w[:n_cap], out.recv_tokens_per_expert, h, ev
 
     @_trace.traced("umdk.buffer.combine")
     def combine(self, x: torch.Tensor, handle: DispatchHandle, topk_weights: Optional[torch.Tensor] = None,
