@@ -22,6 +22,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <set>
 #include <string>
 
 #include <atomic>
@@ -37,6 +38,7 @@
 #include "ub_util.h"
 #include "umq_api.h"
 #include "urpc_proto.h"
+#include "urpc_util.h"
 
 namespace {
 
@@ -57,6 +59,8 @@ struct LaneHello {
 
 struct Pending {
   uint64_t func_id, user_ctx, t0, deadline;
+  uint32_t lane_id = 0;     // the lane that carried the request (its response returns there)
+  bool want_ack = false, acked = false;
   bool sync = false;
   bool done = false;
   int status = 0;
@@ -118,16 +122,29 @@ struct Sealer {
 // src/urpc/include/framework/urpc_framework_api.h urpc_channel_queue_add / _pair). On the client it is always a queue
 // from urpc_queue_create; on the server it is made during the attach.
 struct Lane {
+  uint32_t id = 0;        // 1.. per attach, never handed out twice: the id is part of the sealing salt, so a queue
+                          // that joins later can never repeat a (key, counter) pair of one that left
   uint64_t umqh = 0;
   Sealer seal;
+  std::atomic<bool> closing{false};   // leaving: no new request is sent on it / taken from it
+  std::atomic<int> users{0};          // server: poll passes working on the queue right now
 };
-constexpr uint32_t kMaxLanes = 16;
+using LanePtr = std::shared_ptr<Lane>;
+constexpr uint32_t kMaxLanes = 16;      // queue pairs of one channel at any time
+constexpr uint32_t kMaxLaneId = 255;    // lane ids of one attach (8 bits of the deferred-request cookie)
 
 struct Channel {
   uint32_t id;
   uint64_t umqh = 0;
-  std::vector<std::unique_ptr<Lane>> extra;   // lanes 1..n
+  std::vector<LanePtr> extra;                 // the further lanes, in the order they joined
+  uint32_t next_lane_id = 1;
   uint32_t rr = 0;                            // round-robin cursor of urpc_func_call over the lanes
+  urpc_proto::Negotiated proto;               // version and capabilities agreed at attach time
+  uint8_t data_key[32] = {0};                 // sealing key of this attach (lanes that join later derive from it)
+  bool sealed = false;
+  std::mutex ctl_mu;                          // one control exchange at a time
+  uint32_t ctl_seq = 0;
+  std::vector<uint8_t> rxbuf;                 // control bytes read so far (under ctl_mu)
   int tcp = -1;
   std::unique_ptr<ub::SecureConn> conn;
   Sealer seal;
@@ -152,12 +169,44 @@ int channel_lane(Channel* ch, uint64_t qh) {
 }
 struct Session {
   uint64_t umqh;
-  std::vector<std::unique_ptr<Lane>> extra;   // fixed before the session is published
+  std::vector<LanePtr> extra;   // guarded by lanes_mu once the session is published
+  std::mutex lanes_mu;
   int tcp;
   uint32_t id;
   std::unique_ptr<ub::SecureConn> conn;
+  std::mutex conn_wmu;          // writers of the control connection (task answers, notices)
   Sealer seal;
+  urpc_proto::Negotiated proto;
+  uint8_t data_key[32] = {0};
+  bool sealed = false;
+  std::atomic<bool> closed{false};    // detached or connection lost: its queues are no longer polled
+  std::atomic<int> users{0};          // poll passes inside the session right now
+  std::mutex cancel_mu;
+  std::set<uint32_t> cancelled;       // deferred requests the client gave up on
+  std::vector<uint8_t> rxbuf;         // control bytes read so far (engine thread only)
 };
+// Lane of a session by id (0 = the first queue pair). Null when it has left.
+struct LaneRef {
+  uint64_t umqh = 0;
+  Sealer* seal = nullptr;
+  LanePtr keep;
+};
+bool session_lane(Session* s, uint32_t lane_id, LaneRef* out) {
+  if (lane_id == 0) {
+    out->umqh = s->umqh;
+    out->seal = &s->seal;
+    return !s->closed.load();
+  }
+  std::lock_guard<std::mutex> l(s->lanes_mu);
+  for (auto& ln : s->extra)
+    if (ln->id == lane_id && !ln->closing.load()) {
+      out->umqh = ln->umqh;
+      out->seal = &ln->seal;
+      out->keep = ln;
+      return !s->closed.load();
+    }
+  return false;
+}
 struct Func {
   urpc_func_t fn;
   void* ctx;
@@ -271,18 +320,20 @@ uint64_t make_queue(const char* name, const urpc_queue_cfg_t* cfg = nullptr) {
   return umq_create(&o);
 }
 
-int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, const void* flat, uint32_t flat_len,
-             Sealer* seal = nullptr) {
+// Queues one message: the 32-byte envelope `head` (already laid out for its kind; the size word and the sealed
+// flag are filled in here, they sit at the same place in every layout) followed by the payload.
+constexpr uint8_t kFlagKeepalive = 0x20;   // version 2 response head: answer to a keepalive probe
+int send_frame(uint64_t umqh, urpc_req_head_t head, const urpc_sge_t* sg, uint32_t nsg, const void* flat,
+               uint32_t flat_len, Sealer* seal) {
   uint32_t total = flat_len;
   for (uint32_t i = 0; i < nsg; ++i) total += sg[i].len;
   const bool sealed = seal && seal->on();
   const uint32_t tag = sealed ? (uint32_t)ub::AeadCipher::kTagBytes : 0u;
   umq_buf_t* b = umq_buf_alloc(sizeof(urpc_req_head_t) + total + tag, 1, umqh);
   if (!b) return URPC_ERR_EAGAIN;
-  Head hh = h;
-  hh.total_size = total;
-  if (sealed) hh.flags |= kFlagSealed;
-  urpc_proto::encode(hh, reinterpret_cast<urpc_req_head_t*>(b->buf_data));
+  if (sealed) head.bytes[1] |= kFlagSealed;
+  if ((head.bytes[0] & 0xf) != URPC_MSG_ACK) urpc_proto::put_le(head.bytes + 16, total, 4);
+  memcpy(b->buf_data, head.bytes, sizeof(head.bytes));
   char* p = b->buf_data + sizeof(urpc_req_head_t);
   for (uint32_t i = 0; i < nsg; ++i) {
     memcpy(p, sg[i].addr, sg[i].len);
@@ -322,11 +373,44 @@ int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, c
   g.stats.bytes_tx += total;
   return URPC_SUCCESS;
 }
+int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, const void* flat, uint32_t flat_len,
+             Sealer* seal = nullptr) {
+  urpc_req_head_t head;
+  urpc_proto::encode(h, &head);
+  return send_frame(umqh, head, sg, nsg, flat, flat_len, seal);
+}
+// A response in the layout of the negotiated version. `req_flags` are the flags of the request being answered:
+// a version-2 response to a request that asked for an acknowledgement is ACK_AND_RSP unless the acknowledgement
+// already went out by itself (`acked_separately`).
+int send_rsp(uint64_t umqh, Sealer* seal, uint8_t version, const Head& req, int status, const void* rsp, uint32_t len,
+             bool acked_separately = false, bool keepalive = false) {
+  urpc_req_head_t head;
+  if (version >= 2) {
+    urpc_proto::RspHead r{};
+    r.version = version;
+    r.type = ((req.flags & 1) && !acked_separately) ? URPC_MSG_ACK_AND_RSP : URPC_MSG_RSP;
+    r.flags = keepalive ? kFlagKeepalive : 0;
+    r.req_id_range = 1;
+    r.req_id = req.req_id;
+    r.channel = req.channel;
+    r.status = static_cast<int8_t>(status);
+    urpc_proto::encode_rsp(r, &head);
+  } else {
+    Head rh{version, URPC_MSG_RSP, 0, req.func_id, req.req_id, req.channel, 0, static_cast<int8_t>(status)};
+    urpc_proto::encode(rh, &head);
+  }
+  return send_frame(umqh, head, nullptr, 0, rsp, len, seal);
+}
+int send_ack(uint64_t umqh, Sealer* seal, uint8_t version, const Head& req) {
+  urpc_req_head_t head;
+  urpc_proto::encode_ack(urpc_proto::AckHead{version, 1, req.req_id, req.channel}, &head);
+  return send_frame(umqh, head, nullptr, 0, nullptr, 0, seal);
+}
 
 // Checks and removes the seal of a received message in place. False = drop it: sealed without a key, clear although a
 // key is set, replayed counter, or bad tag.
-bool open_msg(umq_buf_t* b, const Head& h, Sealer* seal) {
-  const bool sealed = (h.flags & kFlagSealed) != 0;
+bool open_msg(umq_buf_t* b, Sealer* seal) {
+  const bool sealed = b->data_size >= sizeof(urpc_req_head_t) && (static_cast<uint8_t>(b->buf_data[1]) & kFlagSealed);
   if (!seal || !seal->on()) return !sealed;
   if (!sealed || b->data_size < sizeof(urpc_req_head_t) + ub::AeadCipher::kTagBytes) return false;
   std::lock_guard<std::mutex> l(seal->mu);
@@ -352,27 +436,57 @@ void channel_progress(Channel* ch) {
       ++lane;
       continue;
     }
-    Head h;
-    if (b->data_size < sizeof(urpc_req_head_t) ||
-        !urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) ||
-        (h.type != URPC_MSG_RSP && h.type != URPC_MSG_ACK_AND_RSP) || !open_msg(b, h, seal)) {
-      if (b->data_size >= sizeof(urpc_req_head_t)) {
+    // one envelope, three layouts: the type nibble says which
+    const urpc_req_head_t* raw = reinterpret_cast<const urpc_req_head_t*>(b->buf_data);
+    const bool framed = b->data_size >= sizeof(urpc_req_head_t);
+    const uint8_t type = framed ? (raw->bytes[0] & 0xf) : 0xff;
+    const uint8_t version = framed ? (raw->bytes[0] >> 4) : 0;
+    urpc_proto::RspHead r{};
+    urpc_proto::AckHead ack{};
+    bool ok = framed && version == ch->proto.version && open_msg(b, seal);
+    bool keepalive = false;
+    if (ok && type == URPC_MSG_ACK) {
+      ok = version >= 2 && urpc_proto::decode_ack(raw, &ack);
+    } else if (ok && version >= 2) {
+      ok = urpc_proto::decode_rsp(raw, &r);
+      keepalive = (r.flags & kFlagKeepalive) != 0;
+    } else if (ok) {   // version 1: responses use the request layout
+      Head h;
+      ok = urpc_proto::decode(raw, &h) && h.type == URPC_MSG_RSP;
+      r.req_id = h.req_id;
+      r.status = h.status;
+      r.total_size = h.total_size;
+      keepalive = h.func_id == URPC_FUNC_ID_KEEPALIVE;
+    }
+    if (!ok) {
+      if (framed) {
         std::lock_guard<std::mutex> l(g.stat_mu);
         ++g.stats.errors;
       }
       umq_buf_free(b);
       continue;
     }
+    if (type == URPC_MSG_ACK) {   // the server has the request(s) and will answer later
+      for (uint32_t k = 0; k < ack.req_id_range; ++k) {
+        auto it = ch->pending.find(ack.req_id + k);
+        if (it == ch->pending.end() || it->second.acked) continue;
+        it->second.acked = true;
+        if (!it->second.sync && it->second.want_ack)
+          ch->ready.push_back(Ready{URPC_POLL_ACK, it->second.func_id, it->second.user_ctx, it->first, 0, nullptr});
+      }
+      umq_buf_free(b);
+      continue;
+    }
     {
       std::lock_guard<std::mutex> l(g.stat_mu);
-      g.stats.bytes_rx += h.total_size;
+      g.stats.bytes_rx += r.total_size;
     }
-    if (h.func_id == URPC_FUNC_ID_KEEPALIVE) {
+    if (keepalive) {
       ch->ka_outstanding = 0;
       umq_buf_free(b);
       continue;
     }
-    auto it = ch->pending.find(h.req_id);
+    auto it = ch->pending.find(r.req_id);
     if (it == ch->pending.end()) {  // late answer of a call that already timed out or was cancelled
       umq_buf_free(b);
       continue;
@@ -386,11 +500,11 @@ void channel_progress(Channel* ch) {
     }
     if (p.sync) {
       p.rsp.assign(b->buf_data + sizeof(urpc_req_head_t), b->buf_data + b->data_size);
-      p.status = h.status;
+      p.status = r.status;
       p.done = true;
       umq_buf_free(b);
     } else {
-      ch->ready.push_back(Ready{URPC_POLL_RSP, p.func_id, p.user_ctx, h.req_id, h.status, b});
+      ch->ready.push_back(Ready{URPC_POLL_RSP, p.func_id, p.user_ctx, r.req_id, r.status, b});
       ch->pending.erase(it);
     }
   }
@@ -432,6 +546,402 @@ ub::PskConfig current_psk() {
   return g.psk;
 }
 
+// The version word this process advertises. URPC_PROTO_MAX / URPC_PROTO_MIN narrow the range (an operator pins a
+// mixed fleet to the old protocol during an upgrade; tests use them to stand in for an older or newer build).
+uint32_t my_version_word() {
+  uint32_t hi = urpc_proto::kVersion, lo = urpc_proto::kVersionMin;
+  if (const char* e = getenv("URPC_PROTO_MAX")) hi = static_cast<uint32_t>(atoi(e));
+  if (const char* e = getenv("URPC_PROTO_MIN")) lo = static_cast<uint32_t>(atoi(e));
+  if (hi < 1 || hi > 255) hi = urpc_proto::kVersion;
+  if (lo < 1 || lo > hi) lo = hi < urpc_proto::kVersionMin ? hi : urpc_proto::kVersionMin;
+  if (hi == 1) return 1;   // exactly what a version-1 build sends
+  return urpc_proto::pack_version(static_cast<uint8_t>(hi), static_cast<uint8_t>(lo), urpc_proto::kCapsAll);
+}
+
+// ------------------------------------------------------------------------------------------ control task engine
+// One thread serves the control connections of all sessions. A control message becomes a task: an object in a slab
+// with an id, a step counter and a deadline. A step either finishes the task (the answer goes out) or asks to be
+// run again after a pause; the pause is a timer on the wheel, so a task that has to wait (for poll passes to leave a
+// queue that is being retired) never blocks the messages of other sessions. Reference: the asynchronous task
+// engine of the IP control plane (src/urpc/framework/lib/control/ip/task_engine.c) drives attach / detach / queue
+// changes as multi-step tasks in the same way.
+struct CtlTask {
+  uint32_t id = 0;
+  Session* s = nullptr;
+  uint16_t opcode = 0;
+  uint32_t seq = 0;
+  int step = 0;
+  uint64_t deadline_ms = 0;
+  uint32_t timer = 0;
+  std::vector<uint8_t> payload, answer;
+  LanePtr lane;
+};
+struct Engine {
+  std::mutex mu;                       // watch list and run queue
+  std::vector<Session*> watched;
+  std::deque<uint64_t> runq;           // slab handles of tasks ready for their next step
+  urpc_util::Slab<CtlTask> tasks{32};
+  urpc_util::IdGen ids{1, 4096};
+  std::unique_ptr<urpc_util::TimerWheel> wheel;   // made when the engine starts: its clock begins at that moment
+  std::thread thr;
+  std::atomic<bool> stop{false};
+  bool running = false;
+  urpc_ctl_stats_t st{};
+  std::mutex st_mu;
+};
+Engine g_eng;
+constexpr uint64_t kTaskDeadlineMs = 3000;
+uint64_t now_ms() { return ub::now_ns() / 1000000ull; }
+
+void ctl_answer(Session* s, uint16_t opcode, uint32_t seq, int status, const void* payload, uint32_t len) {
+  urpc_proto::CtlHead h{urpc_proto::kCtlMagic, opcode, urpc_proto::kCtlAnswer, seq, status, len};
+  std::lock_guard<std::mutex> l(s->conn_wmu);
+  if (!s->conn) return;
+  if (s->conn->write_full(&h, sizeof(h)) && len) s->conn->write_full(payload, len);
+}
+// Server -> client notice (no answer expected).
+void ctl_notice(Session* s, uint16_t opcode, const void* payload, uint32_t len) {
+  urpc_proto::CtlHead h{urpc_proto::kCtlMagic, opcode, 0, 0, 0, len};
+  std::lock_guard<std::mutex> l(s->conn_wmu);
+  if (!s->conn || s->closed.load()) return;
+  if (s->conn->write_full(&h, sizeof(h)) && len) s->conn->write_full(payload, len);
+  std::lock_guard<std::mutex> l2(g_eng.st_mu);
+  ++g_eng.st.notices_sent;
+}
+
+enum StepResult { kStepDone = 0, kStepAgain = 1 };
+// Retiring a session: stop polling it, wait until no poll pass is inside, then free its queues. The Session object
+// stays in the table (ids are positions) with no queues.
+StepResult step_retire(CtlTask& t, int* status) {
+  Session* s = t.s;
+  if (t.step == 0) {
+    s->closed = true;
+    t.step = 1;
+  }
+  if (s->users.load() > 0 && now_ms() < t.deadline_ms) return kStepAgain;
+  {
+    std::lock_guard<std::mutex> l(s->lanes_mu);
+    for (auto& ln : s->extra) {
+      umq_unbind(ln->umqh);
+      umq_destroy(ln->umqh);
+    }
+    s->extra.clear();
+  }
+  if (s->umqh) {
+    umq_unbind(s->umqh);
+    umq_destroy(s->umqh);
+    s->umqh = 0;
+  }
+  if (urpc_ctrl_cb_t cb = g_ctrl_cb.load()) cb(URPC_CTRL_DETACH, s->id, 0);
+  {
+    std::lock_guard<std::mutex> l(g_eng.st_mu);
+    ++g_eng.st.sessions_retired;
+  }
+  *status = URPC_SUCCESS;
+  return kStepDone;
+}
+StepResult step_queue_add(CtlTask& t, int* status) {
+  Session* s = t.s;
+  uint32_t lane_id = 0, blob_len = 0;
+  if (t.payload.size() < 8) {
+    *status = URPC_ERR_EINVAL;
+    return kStepDone;
+  }
+  memcpy(&lane_id, t.payload.data(), 4);
+  memcpy(&blob_len, t.payload.data() + 4, 4);
+  if (lane_id == 0 || lane_id > kMaxLaneId || blob_len > UMQ_BIND_INFO_SIZE || t.payload.size() < 8 + blob_len ||
+      !(s->proto.caps & urpc_proto::kCapLiveQueues)) {
+    *status = URPC_ERR_EINVAL;
+    return kStepDone;
+  }
+  {
+    std::lock_guard<std::mutex> l(s->lanes_mu);
+    bool clash = s->extra.size() + 1 >= kMaxLanes;
+    for (auto& ln : s->extra) clash = clash || ln->id >= lane_id;   // ids only grow: a salt is never used twice
+    if (clash) {
+      *status = URPC_ERR_EINVAL;
+      return kStepDone;
+    }
+  }
+  const uint64_t lq = make_queue("urpc-srv");
+  if (!lq || umq_bind(lq, t.payload.data() + 8, blob_len) != UMQ_SUCCESS) {
+    if (lq) umq_destroy(lq);
+    *status = URPC_FAIL;
+    return kStepDone;
+  }
+  LanePtr ln(new Lane());
+  ln->id = lane_id;
+  ln->umqh = lq;
+  if (s->sealed) ln->seal.set(s->data_key, true, lane_id);
+  t.answer.resize(UMQ_BIND_INFO_SIZE);
+  t.answer.resize(umq_bind_info_get(lq, t.answer.data(), UMQ_BIND_INFO_SIZE));
+  {
+    std::lock_guard<std::mutex> l(s->lanes_mu);
+    s->extra.push_back(ln);   // published: the next poll pass takes requests from it
+  }
+  *status = URPC_SUCCESS;
+  return kStepDone;
+}
+StepResult step_queue_rm(CtlTask& t, int* status) {
+  Session* s = t.s;
+  if (t.step == 0) {
+    uint32_t lane_id = 0;
+    if (t.payload.size() >= 4) memcpy(&lane_id, t.payload.data(), 4);
+    {
+      std::lock_guard<std::mutex> l(s->lanes_mu);
+      for (auto& ln : s->extra)
+        if (ln->id == lane_id && lane_id != 0) t.lane = ln;
+    }
+    if (!t.lane) {
+      *status = URPC_ERR_EINVAL;
+      return kStepDone;
+    }
+    t.lane->closing = true;   // poll passes that start from now on leave the queue alone
+    t.step = 1;
+  }
+  if (t.lane->users.load() > 0 && now_ms() < t.deadline_ms) return kStepAgain;   // a pass is still inside
+  {
+    std::lock_guard<std::mutex> l(s->lanes_mu);
+    s->extra.erase(std::remove(s->extra.begin(), s->extra.end(), t.lane), s->extra.end());
+  }
+  umq_unbind(t.lane->umqh);
+  umq_destroy(t.lane->umqh);
+  t.lane.reset();
+  *status = URPC_SUCCESS;
+  return kStepDone;
+}
+StepResult step_task_cancel(CtlTask& t, int* status) {
+  uint32_t req_id = 0;
+  if (t.payload.size() >= 4) memcpy(&req_id, t.payload.data(), 4);
+  std::lock_guard<std::mutex> l(t.s->cancel_mu);
+  if (t.s->cancelled.size() >= 1024) t.s->cancelled.erase(t.s->cancelled.begin());
+  t.s->cancelled.insert(req_id);
+  *status = URPC_SUCCESS;
+  return kStepDone;
+}
+
+void engine_enqueue(uint64_t h) {
+  std::lock_guard<std::mutex> l(g_eng.mu);
+  g_eng.runq.push_back(h);
+}
+// Creates the task of one control message (opcode 0 = the connection ended: retire without an answer).
+void engine_new_task(Session* s, uint16_t opcode, uint32_t seq, std::vector<uint8_t> payload) {
+  CtlTask* t = nullptr;
+  const uint64_t h = g_eng.tasks.acquire(&t);
+  uint32_t id = 0;
+  if (!g_eng.ids.alloc(&id)) {   // more live tasks than ids: refuse instead of queueing without bound
+    g_eng.tasks.release(h);
+    if (opcode) ctl_answer(s, opcode, seq, URPC_ERR_EAGAIN, nullptr, 0);
+    return;
+  }
+  t->id = id;
+  t->s = s;
+  t->opcode = opcode;
+  t->seq = seq;
+  t->payload = std::move(payload);
+  t->deadline_ms = now_ms() + kTaskDeadlineMs;
+  t->timer = g_eng.wheel->create([h] { engine_enqueue(h); });
+  {
+    std::lock_guard<std::mutex> l(g_eng.st_mu);
+    ++g_eng.st.tasks_started;
+  }
+  engine_enqueue(h);
+}
+void engine_run_task(uint64_t h) {
+  CtlTask* t = g_eng.tasks.get(h);
+  if (!t) return;
+  int status = URPC_FAIL;
+  StepResult r = kStepDone;
+  switch (t->opcode) {
+    case 0:
+    case urpc_proto::kCtlDetach: r = step_retire(*t, &status); break;
+    case urpc_proto::kCtlQueueAdd: r = step_queue_add(*t, &status); break;
+    case urpc_proto::kCtlQueueRm: r = step_queue_rm(*t, &status); break;
+    case urpc_proto::kCtlTaskCancel: r = step_task_cancel(*t, &status); break;
+    default: status = URPC_ERR_EINVAL; break;
+  }
+  if (r == kStepAgain) {
+    g_eng.wheel->start(t->timer, g_eng.wheel->tick_ms());
+    return;
+  }
+  const bool late = now_ms() >= t->deadline_ms;
+  if (t->opcode) ctl_answer(t->s, t->opcode, t->seq, status, t->answer.data(), static_cast<uint32_t>(t->answer.size()));
+  {
+    std::lock_guard<std::mutex> l(g_eng.st_mu);
+    if (status == URPC_SUCCESS) ++g_eng.st.tasks_done;
+    else ++g_eng.st.tasks_failed;
+    if (late) ++g_eng.st.tasks_timed_out;
+  }
+  g_eng.wheel->destroy(t->timer);
+  g_eng.ids.free(t->id);
+  g_eng.tasks.release(h);
+}
+// Reads what the control connection holds without ever waiting for more: bytes collect in the session's buffer
+// until a whole message is there. False = the connection ended (or sent something that is not a control message).
+bool engine_read(Session* s) {
+  for (;;) {
+    uint8_t tmp[512];
+    size_t want = sizeof(urpc_proto::CtlHead);
+    if (s->rxbuf.size() >= sizeof(urpc_proto::CtlHead)) {
+      urpc_proto::CtlHead h;
+      memcpy(&h, s->rxbuf.data(), sizeof(h));
+      if (h.magic != urpc_proto::kCtlMagic || h.len > urpc_proto::kCtlMaxPayload) return false;
+      want = sizeof(h) + h.len;
+      if (s->rxbuf.size() >= want) {
+        std::vector<uint8_t> payload(s->rxbuf.begin() + sizeof(h), s->rxbuf.begin() + want);
+        s->rxbuf.erase(s->rxbuf.begin(), s->rxbuf.begin() + want);
+        if (s->proto.version < 2) return false;   // a version-1 peer has no control messages
+        engine_new_task(s, h.opcode, h.seq, std::move(payload));
+        continue;
+      }
+    }
+    // one byte at a time would be slow, a blocking read of the rest could stall every other session: read what is
+    // there (pending() for decrypted bytes, poll() for the socket), never more than the message still needs
+    pollfd pf{s->tcp, POLLIN, 0};
+    if (!s->conn->pending() && poll(&pf, 1, 0) <= 0) return true;
+    size_t n = want - s->rxbuf.size();
+    if (n > sizeof(tmp)) n = sizeof(tmp);
+    // a TLS record may carry less than the message needs; one byte is always safe, the rest only when buffered
+    if (!s->conn->read_full(tmp, 1, 200)) return false;
+    s->rxbuf.push_back(tmp[0]);
+    while (--n > 0 && s->conn->pending()) {
+      if (!s->conn->read_full(tmp, 1, 200)) return false;
+      s->rxbuf.push_back(tmp[0]);
+    }
+  }
+}
+void engine_loop() {
+  while (!g_eng.stop.load()) {
+    std::vector<Session*> ss;
+    {
+      std::lock_guard<std::mutex> l(g_eng.mu);
+      ss = g_eng.watched;
+    }
+    std::vector<pollfd> pfs;
+    for (Session* s : ss) pfs.push_back(pollfd{s->tcp, POLLIN, 0});
+    bool buffered = false;
+    for (Session* s : ss) buffered = buffered || (s->conn && s->conn->pending());
+    if (pfs.empty()) usleep(g_eng.wheel->tick_ms() * 1000);
+    else poll(pfs.data(), pfs.size(), buffered ? 0 : static_cast<int>(g_eng.wheel->tick_ms()));
+    for (size_t i = 0; i < ss.size(); ++i) {
+      Session* s = ss[i];
+      if (!(pfs[i].revents & (POLLIN | POLLHUP | POLLERR)) && !s->conn->pending()) continue;
+      if (engine_read(s)) continue;
+      {   // the connection is gone: stop watching, retire the session
+        std::lock_guard<std::mutex> l(g_eng.mu);
+        g_eng.watched.erase(std::remove(g_eng.watched.begin(), g_eng.watched.end(), s), g_eng.watched.end());
+      }
+      if (!s->closed.load()) engine_new_task(s, 0, 0, {});
+    }
+    g_eng.wheel->run(now_ms());
+    for (;;) {
+      uint64_t h = 0;
+      {
+        std::lock_guard<std::mutex> l(g_eng.mu);
+        if (g_eng.runq.empty()) break;
+        h = g_eng.runq.front();
+        g_eng.runq.pop_front();
+      }
+      engine_run_task(h);
+    }
+  }
+}
+void engine_watch(Session* s) {
+  std::lock_guard<std::mutex> l(g_eng.mu);
+  g_eng.watched.push_back(s);
+  if (!g_eng.running) {
+    g_eng.stop = false;
+    g_eng.wheel.reset(new urpc_util::TimerWheel(5, now_ms()));
+    g_eng.thr = std::thread(engine_loop);
+    g_eng.running = true;
+  }
+}
+void engine_stop() {
+  {
+    std::lock_guard<std::mutex> l(g_eng.mu);
+    if (!g_eng.running) return;
+    g_eng.stop = true;
+  }
+  g_eng.thr.join();
+  std::lock_guard<std::mutex> l(g_eng.mu);
+  g_eng.running = false;
+  g_eng.watched.clear();
+  g_eng.runq.clear();
+}
+
+// ---------------------------------------------------------------------------------- control messages, client side
+// What the server sends without being asked (today: the function table changed) becomes an asynchronous event.
+void ctl_handle_notice(Channel* ch, const urpc_proto::CtlHead& h, const std::vector<uint8_t>& payload) {
+  if (h.opcode == urpc_proto::kCtlFuncChange && payload.size() >= 12) {
+    uint32_t added = 0;
+    memcpy(&added, payload.data() + 8, 4);
+    push_event(URPC_EVENT_FUNC_CHANGED, ch->id, static_cast<int>(added));
+  }
+}
+// Reads one whole control message if the connection has (or, within `wait_ms`, gets) one. 1 = message, 0 = none
+// yet, -1 = the connection ended. Caller holds ch->ctl_mu.
+int ctl_read_one(Channel* ch, urpc_proto::CtlHead* h, std::vector<uint8_t>* payload, int wait_ms) {
+  const uint64_t deadline = now_ms() + static_cast<uint64_t>(wait_ms);
+  for (;;) {
+    if (ch->rxbuf.size() >= sizeof(*h)) {
+      memcpy(h, ch->rxbuf.data(), sizeof(*h));
+      if (h->magic != urpc_proto::kCtlMagic || h->len > urpc_proto::kCtlMaxPayload) return -1;
+      if (ch->rxbuf.size() >= sizeof(*h) + h->len) {
+        payload->assign(ch->rxbuf.begin() + sizeof(*h), ch->rxbuf.begin() + sizeof(*h) + h->len);
+        ch->rxbuf.erase(ch->rxbuf.begin(), ch->rxbuf.begin() + sizeof(*h) + h->len);
+        return 1;
+      }
+    }
+    if (!ch->conn) return -1;
+    if (!ch->conn->pending()) {
+      const uint64_t now = now_ms();
+      pollfd pf{ch->tcp, POLLIN, 0};
+      if (poll(&pf, 1, now >= deadline ? 0 : static_cast<int>(deadline - now)) <= 0) return 0;
+    }
+    uint8_t byte;
+    if (!ch->conn->read_full(&byte, 1, 200)) return -1;
+    ch->rxbuf.push_back(byte);
+  }
+}
+// One request / answer exchange on the channel's control connection. Notices that arrive in between are handled.
+int ctl_call(Channel* ch, uint16_t opcode, const void* payload, uint32_t len, std::vector<uint8_t>* answer,
+             int timeout_ms) {
+  std::lock_guard<std::mutex> l(ch->ctl_mu);
+  if (!ch->conn) return URPC_ERR_SESSION_CLOSE;
+  urpc_proto::CtlHead h{urpc_proto::kCtlMagic, opcode, 0, ++ch->ctl_seq, 0, len};
+  if (!ch->conn->write_full(&h, sizeof(h)) || (len && !ch->conn->write_full(payload, len)))
+    return URPC_ERR_SESSION_CLOSE;
+  const uint64_t deadline = now_ms() + static_cast<uint64_t>(timeout_ms);
+  for (;;) {
+    const uint64_t now = now_ms();
+    if (now >= deadline) return URPC_ERR_TIMEOUT;
+    urpc_proto::CtlHead rh;
+    std::vector<uint8_t> rp;
+    const int rc = ctl_read_one(ch, &rh, &rp, static_cast<int>(deadline - now));
+    if (rc < 0) return URPC_ERR_SESSION_CLOSE;
+    if (rc == 0) continue;
+    if (!(rh.flags & urpc_proto::kCtlAnswer)) {
+      ctl_handle_notice(ch, rh, rp);
+      continue;
+    }
+    if (rh.seq != h.seq) continue;   // answer of an exchange that was given up earlier
+    if (answer) answer->swap(rp);
+    return rh.status;
+  }
+}
+// Picks up notices while nobody is in an exchange (called from the channel's progress path).
+void ctl_drain_notices(Channel* ch) {
+  if (ch->proto.version < 2 || !ch->attached.load()) return;
+  std::unique_lock<std::mutex> l(ch->ctl_mu, std::try_to_lock);
+  if (!l.owns_lock() || !ch->conn) return;
+  for (int i = 0; i < 8; ++i) {
+    urpc_proto::CtlHead rh;
+    std::vector<uint8_t> rp;
+    if (ctl_read_one(ch, &rh, &rp, 0) != 1) return;
+    if (!(rh.flags & urpc_proto::kCtlAnswer)) ctl_handle_notice(ch, rh, rp);
+  }
+}
+
 void accept_loop() {
   while (!g.stop.load()) {
     pollfd pf{g.listen_fd, POLLIN, 0};
@@ -450,10 +960,23 @@ void accept_loop() {
       close(fd);
       continue;
     }
-    if (!conn->read_full(&hello, sizeof(hello), 5000) || hello.magic != kHelloMagic ||
-        hello.version != urpc_proto::kVersion) {
+    if (!conn->read_full(&hello, sizeof(hello), 5000) || hello.magic != kHelloMagic) {
       conn.reset();
       close(fd);
+      continue;
+    }
+    const urpc_proto::Negotiated nego = urpc_proto::negotiate(my_version_word(), hello.version);
+    if (nego.version == 0) {   // nothing in common: say so (version word 0) instead of just hanging up
+      g_log.log(ub::kLogWarn, "attach refused: peer speaks protocol %u..%u, this side %u..%u",
+                (hello.version >> 8) & 0xff ? (hello.version >> 8) & 0xff : hello.version & 0xff, hello.version & 0xff,
+                (my_version_word() >> 8) & 0xff, my_version_word() & 0xff);
+      Hello no{};
+      no.magic = kHelloMagic;
+      conn->write_full(&no, sizeof(no));
+      conn.reset();
+      close(fd);
+      std::lock_guard<std::mutex> l(g.stat_mu);
+      ++g.stats.errors;
       continue;
     }
     // one server queue per queue of the client's channel; the session is published only when all are bound
@@ -464,9 +987,11 @@ void accept_loop() {
     const uint64_t q = ok ? make_queue("urpc-srv") : 0;
     Hello rsp{};
     rsp.magic = kHelloMagic;
-    rsp.version = urpc_proto::kVersion;
+    // the chosen version; a version-1 client compares the whole word with 1, so no capability bits for it
+    rsp.version = nego.version >= 2 ? urpc_proto::pack_version(nego.version, nego.version, nego.caps) : nego.version;
     rsp.n_extra = static_cast<uint32_t>(lane_req.size());
     Session* s = new Session();
+    s->proto = nego;
     ok = ok && q && umq_bind(q, hello.blob, hello.blob_len) == UMQ_SUCCESS;
     for (size_t i = 0; ok && i < lane_req.size(); ++i) {
       const uint64_t lq = make_queue("urpc-srv");
@@ -476,6 +1001,7 @@ void accept_loop() {
       }
       s->extra.emplace_back(new Lane());
       s->extra.back()->umqh = lq;
+      s->extra.back()->id = static_cast<uint32_t>(i + 1);
       ok = umq_bind(lq, lane_req[i].blob, lane_req[i].blob_len) == UMQ_SUCCESS;
       lane_rsp[i].blob_len = umq_bind_info_get(lq, lane_rsp[i].blob, sizeof(lane_rsp[i].blob));
     }
@@ -483,6 +1009,8 @@ void accept_loop() {
       ok = ub::random_bytes(rsp.data_key, sizeof(rsp.data_key));
       if (ok) {
         rsp.sealed = 1;
+        s->sealed = true;
+        memcpy(s->data_key, rsp.data_key, sizeof(s->data_key));
         s->seal.set(rsp.data_key, true, 0);
         for (size_t i = 0; i < s->extra.size(); ++i) s->extra[i]->seal.set(rsp.data_key, true, static_cast<uint32_t>(i + 1));
       }
@@ -509,7 +1037,9 @@ void accept_loop() {
     if (urpc_ctrl_cb_t cb = g_ctrl_cb.load()) cb(URPC_CTRL_ATTACH, s->id, hello.channel);
     bool sent = s->conn->write_full(&rsp, sizeof(rsp));
     for (size_t i = 0; sent && i < lane_rsp.size(); ++i) sent = s->conn->write_full(&lane_rsp[i], sizeof(LaneHello));
-    // a client that went away during the handshake leaves a session that never receives a request
+    // from here on the control connection belongs to the task engine: control messages of the client, and its end
+    // of file (a client that went away, also one that left during the handshake) retires the session
+    engine_watch(s);
   }
 }
 
@@ -525,6 +1055,7 @@ void keepalive_loop() {
     }
     for (Channel* ch : chs) {
       if (!ch->attached.load() || ch->lost.load()) continue;
+      ctl_drain_notices(ch);
       bool lost = false;
       {
         std::lock_guard<std::mutex> l(ch->mu);
@@ -532,7 +1063,7 @@ void keepalive_loop() {
         if (ch->ka_outstanding >= limit) {
           lost = true;
         } else {
-          Head h{urpc_proto::kVersion, URPC_MSG_REQ, 1, URPC_FUNC_ID_KEEPALIVE, 0, ch->id, 0, 0};
+          Head h{ch->proto.version, URPC_MSG_REQ, 1, URPC_FUNC_ID_KEEPALIVE, 0, ch->id, 0, 0};
           send_msg(ch->umqh, h, nullptr, 0, nullptr, 0, &ch->seal);
           ++ch->ka_outstanding;
           std::lock_guard<std::mutex> l2(g.stat_mu);
@@ -617,6 +1148,7 @@ void urpc_uninit(void) {
   }
   if (g.accept_thr.joinable()) g.accept_thr.join();
   if (g.ka_thr.joinable()) g.ka_thr.join();
+  engine_stop();
   urpc_admin_stop();
   std::lock_guard<std::mutex> l(g.mu);
   if (g.listen_fd >= 0) close(g.listen_fd);
@@ -631,7 +1163,7 @@ void urpc_uninit(void) {
   for (Session* s : g.sessions) {
     s->conn.reset();
     if (s->tcp >= 0) close(s->tcp);
-    umq_destroy(s->umqh);
+    if (s->umqh) umq_destroy(s->umqh);
     for (auto& ln : s->extra) umq_destroy(ln->umqh);
     delete s;
   }
@@ -663,16 +1195,38 @@ int urpc_server_start(const char* ip, uint16_t port) {
   return ntohs(a.sin_port);
 }
 
+// Tells every attached version-2 client that the function table changed. Caller holds g.mu.
+static void notify_func_change(uint64_t func_id, uint32_t added) {
+  uint8_t payload[12];
+  memcpy(payload, &func_id, 8);
+  memcpy(payload + 8, &added, 4);
+  for (Session* s : g.sessions)
+    if (s->proto.version >= 2 && !s->closed.load()) ctl_notice(s, urpc_proto::kCtlFuncChange, payload, sizeof(payload));
+}
 int urpc_func_register(uint64_t func_id, urpc_func_t fn, void* ctx) {
   if (!fn || func_id >= URPC_FUNC_ID_LOOKUP) return URPC_ERR_EINVAL;   // the two top ids are reserved
   std::lock_guard<std::mutex> l(g.mu);
   if (g.funcs.count(func_id)) return URPC_ERR_EINVAL;
   g.funcs[func_id] = Func{fn, ctx};
+  notify_func_change(func_id, 1);
   return URPC_SUCCESS;
 }
 int urpc_func_unregister(uint64_t func_id) {
   std::lock_guard<std::mutex> l(g.mu);
-  return g.funcs.erase(func_id) ? URPC_SUCCESS : URPC_ERR_FUNC_NOT_FOUND;
+  if (!g.funcs.erase(func_id)) return URPC_ERR_FUNC_NOT_FOUND;
+  notify_func_change(func_id, 0);
+  return URPC_SUCCESS;
+}
+int urpc_ctl_stats_get(urpc_ctl_stats_t* out) {
+  if (!out) return URPC_ERR_EINVAL;
+  {
+    std::lock_guard<std::mutex> l(g_eng.st_mu);
+    *out = g_eng.st;
+  }
+  out->tasks_live = g_eng.tasks.live();
+  std::lock_guard<std::mutex> l(g_eng.mu);
+  out->timers_armed = g_eng.wheel ? g_eng.wheel->armed_count() : 0;
+  return URPC_SUCCESS;
 }
 
 int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
@@ -683,17 +1237,38 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
   }
   int n = 0;
   static thread_local std::vector<uint8_t> rsp(64 * 1024);
-  for (Session* s : ss)
-   for (size_t lane = 0; lane <= s->extra.size(); ++lane) {   // every queue pair of the session in turn
-    const uint64_t lq = lane ? s->extra[lane - 1]->umqh : s->umqh;
-    Sealer* lseal = lane ? &s->extra[lane - 1]->seal : &s->seal;
+  for (Session* s : ss) {
+   // a session that is being retired, or a queue pair that is leaving, is not touched: the engine frees the queues
+   // once `users` shows that no pass is inside
+   struct Guard {
+     std::atomic<int>* c;
+     explicit Guard(std::atomic<int>* c_) : c(c_) { c->fetch_add(1); }
+     ~Guard() { c->fetch_sub(1); }
+   };
+   Guard in_session(&s->users);
+   if (s->closed.load()) continue;
+   std::vector<LanePtr> lanes(1);   // slot 0 stands for the first queue pair
+   {
+     std::lock_guard<std::mutex> l(s->lanes_mu);
+     lanes.insert(lanes.end(), s->extra.begin(), s->extra.end());
+   }
+   for (size_t li = 0; li < lanes.size(); ++li) {   // every queue pair of the session in turn
+    Lane* ln = lanes[li].get();
+    std::unique_ptr<Guard> in_lane;
+    if (ln) {
+      in_lane.reset(new Guard(&ln->users));
+      if (ln->closing.load()) continue;
+    }
+    const uint32_t lane = ln ? ln->id : 0;
+    const uint64_t lq = ln ? ln->umqh : s->umqh;
+    Sealer* lseal = ln ? &ln->seal : &s->seal;
     for (int budget = 0; budget < 64; ++budget) {
       umq_buf_t* b = umq_dequeue(lq);
       if (!b) break;
       Head h;
       if (b->data_size < sizeof(urpc_req_head_t) ||
           !urpc_proto::decode(reinterpret_cast<urpc_req_head_t*>(b->buf_data), &h) || h.type != URPC_MSG_REQ ||
-          !open_msg(b, h, lseal)) {
+          h.version != s->proto.version || !open_msg(b, lseal)) {
         if (b->data_size >= sizeof(urpc_req_head_t)) {  // a request that fails the seal check is dropped and counted
           std::lock_guard<std::mutex> l(g.stat_mu);
           ++g.stats.errors;
@@ -715,21 +1290,22 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         alen -= 4 + nrefs * sizeof(RefEntry);
       }
       CurrentReq cur{lq, reinterpret_cast<const RefEntry*>(args + alen), nrefs};
-      Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, h.func_id, h.req_id, h.channel, 0, 0};
+      const uint8_t ver = s->proto.version;
       if (h.func_id == URPC_FUNC_ID_KEEPALIVE) {
-        send_msg(lq, rh, nullptr, 0, nullptr, 0, lseal);
+        send_rsp(lq, lseal, ver, h, 0, nullptr, 0, false, true);
         umq_buf_free(b);
         continue;
       }
       if (h.func_id == URPC_FUNC_ID_LOOKUP) {   // name -> function id
         uint64_t id = 0;
+        int lst = 0;
         {
           std::lock_guard<std::mutex> l(g.mu);
           auto it = g.func_names.find(std::string(args, strnlen(args, alen)));
           if (it != g.func_names.end()) id = it->second;
-          else rh.status = static_cast<int8_t>(URPC_ERR_FUNC_NOT_FOUND);
+          else lst = URPC_ERR_FUNC_NOT_FOUND;
         }
-        send_msg(lq, rh, nullptr, 0, &id, sizeof(id), lseal);
+        send_rsp(lq, lseal, ver, h, lst, &id, sizeof(id));
         umq_buf_free(b);
         continue;
       }
@@ -752,11 +1328,12 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         t_current = nullptr;
         const uint64_t e1 = ub::now_ns();
         record(URPC_PERF_FUNC_EXEC, e1 - e0);
-        rh.status = static_cast<int8_t>(st);
-        send_msg(lq, rh, nullptr, 0, rsp.data(), rlen > rsp.size() ? 0 : rlen, lseal);
+        send_rsp(lq, lseal, ver, h, st, rsp.data(), rlen > rsp.size() ? 0 : rlen);
         record(URPC_PERF_FUNC_RETURN, ub::now_ns() - e1);
         umq_buf_free(b);
       } else if (msgs && n < max) {
+        // the answer comes later, from the application: acknowledge now if the caller asked for it
+        if ((h.flags & 1) && ver >= 2 && (s->proto.caps & urpc_proto::kCapAck)) send_ack(lq, lseal, ver, h);
         msgs[n].event = URPC_POLL_REQ;
         msgs[n].func_id = h.func_id;
         msgs[n].req_id = h.req_id;
@@ -767,11 +1344,11 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         msgs[n].priv = b;
         ++n;
       } else {
-        rh.status = static_cast<int8_t>(URPC_ERR_FUNC_NOT_FOUND);
-        send_msg(lq, rh, nullptr, 0, nullptr, 0, lseal);
+        send_rsp(lq, lseal, ver, h, URPC_ERR_FUNC_NOT_FOUND, nullptr, 0);
         umq_buf_free(b);
       }
     }
+   }
   }
   return n;
 }
@@ -785,12 +1362,22 @@ int urpc_func_return(const urpc_poll_msg_t* req, const void* rsp, uint32_t len, 
     if (sid < g.sessions.size()) s = g.sessions[sid];
   }
   if (!s) return URPC_ERR_EINVAL;
-  Head rh{urpc_proto::kVersion, URPC_MSG_RSP, 0, req->func_id, req->req_id,
-          static_cast<uint32_t>(req->user_ctx & 0xffffff), 0, static_cast<int8_t>(status)};
+  {   // the client gave the call up (control message TASK_CANCEL): nothing is sent
+    std::lock_guard<std::mutex> l(s->cancel_mu);
+    if (s->cancelled.erase(req->req_id)) return URPC_ERR_CANCELED;
+  }
+  // the request's own head still sits in its buffer: its flags say whether an acknowledgement was asked for (and,
+  // between version-2 peers, has been sent when the request was handed to the application)
+  Head rq{};
+  rq.func_id = req->func_id;
+  rq.req_id = req->req_id;
+  rq.channel = static_cast<uint32_t>(req->user_ctx & 0xffffff);
+  if (req->priv) rq.flags = static_cast<uint8_t>(static_cast<umq_buf_t*>(req->priv)->buf_data[1]);
   const uint32_t lane = static_cast<uint32_t>(req->user_ctx >> 24) & 0xff;   // answer on the lane of the request
-  if (lane > s->extra.size()) return URPC_ERR_EINVAL;
-  return send_msg(lane ? s->extra[lane - 1]->umqh : s->umqh, rh, nullptr, 0, rsp, len,
-                  lane ? &s->extra[lane - 1]->seal : &s->seal);
+  LaneRef lr;
+  if (!session_lane(s, lane, &lr)) return URPC_ERR_SESSION_CLOSE;
+  const bool acked = (rq.flags & 1) && s->proto.version >= 2 && (s->proto.caps & urpc_proto::kCapAck);
+  return send_rsp(lr.umqh, lr.seal, s->proto.version, rq, status, rsp, len, acked);
 }
 
 int urpc_channel_create(void) {
@@ -830,7 +1417,7 @@ int urpc_channel_server_attach(uint32_t chid, const char* ip, uint16_t port) {
   }
   Hello hello{};
   hello.magic = kHelloMagic;
-  hello.version = urpc_proto::kVersion;
+  hello.version = my_version_word();
   hello.channel = chid;
   hello.blob_len = umq_bind_info_get(ch->umqh, hello.blob, sizeof(hello.blob));
   hello.n_extra = static_cast<uint32_t>(ch->extra.size());
@@ -842,8 +1429,24 @@ int urpc_channel_server_attach(uint32_t chid, const char* ip, uint16_t port) {
     ok = conn->write_full(&lh, sizeof(lh));
   }
   Hello rsp;
-  ok = ok && conn->read_full(&rsp, sizeof(rsp), 5000) && rsp.magic == kHelloMagic &&
-       !(conn->encrypted() && !rsp.sealed) && rsp.n_extra == hello.n_extra &&
+  ok = ok && conn->read_full(&rsp, sizeof(rsp), 5000) && rsp.magic == kHelloMagic;
+  // the answer names the version to use: one number from a version-1 server, version + capabilities otherwise;
+  // it must lie inside what this side offered
+  urpc_proto::Negotiated nego;
+  if (ok) {
+    nego.version = static_cast<uint8_t>(rsp.version & 0xff);
+    nego.caps = (rsp.version >> 16) & (my_version_word() >> 16);
+    const uint32_t mine = my_version_word();
+    const uint8_t lo = (mine >> 8) & 0xff ? (mine >> 8) & 0xff : mine & 0xff;
+    if (nego.version == 0 || nego.version > (mine & 0xff) || nego.version < lo) {
+      g_log.log(ub::kLogWarn, "channel %u: no protocol version in common with the server", chid);
+      conn.reset();
+      close(fd);
+      return URPC_ERR_VERSION;
+    }
+    if (nego.version < 2) nego.caps = 0;
+  }
+  ok = ok && !(conn->encrypted() && !rsp.sealed) && rsp.n_extra == hello.n_extra &&
        umq_bind(ch->umqh, rsp.blob, rsp.blob_len) == UMQ_SUCCESS;
   size_t bound = 0;
   for (; ok && bound < ch->extra.size(); ++bound) {
@@ -859,10 +1462,19 @@ int urpc_channel_server_attach(uint32_t chid, const char* ip, uint16_t port) {
   }
   for (size_t lane = 0; lane <= ch->extra.size(); ++lane) {
     Sealer& sl = lane ? ch->extra[lane - 1]->seal : ch->seal;
+    if (lane) {
+      ch->extra[lane - 1]->id = static_cast<uint32_t>(lane);
+      ch->extra[lane - 1]->closing = false;
+    }
     std::lock_guard<std::mutex> l(sl.mu);
     if (rsp.sealed) sl.set(rsp.data_key, false, static_cast<uint32_t>(lane));
     else sl.clear();
   }
+  ch->next_lane_id = static_cast<uint32_t>(ch->extra.size() + 1);
+  ch->proto = nego;
+  ch->sealed = rsp.sealed != 0;
+  memcpy(ch->data_key, rsp.data_key, sizeof(ch->data_key));
+  ch->rxbuf.clear();
   ch->conn = std::move(conn);
   ch->tcp = fd;
   ch->server_ip = ip && *ip ? ip : "127.0.0.1";
@@ -875,13 +1487,21 @@ int urpc_channel_server_attach(uint32_t chid, const char* ip, uint16_t port) {
 int urpc_channel_server_detach(uint32_t chid) {
   Channel* ch = get_channel(chid);
   if (!ch || !ch->attached.load()) return URPC_ERR_EINVAL;
+  // version 2: say goodbye, so that the server retires the session now (it would notice the closed connection
+  // anyway, a little later); the answer is not needed to go on
+  if (ch->proto.version >= 2 && !ch->lost.load()) ctl_call(ch, urpc_proto::kCtlDetach, nullptr, 0, nullptr, 500);
   std::lock_guard<std::mutex> l(ch->mu);
   ch->attached = false;
+  ch->proto = urpc_proto::Negotiated();
   umq_unbind(ch->umqh);
   for (auto& ln : ch->extra) umq_unbind(ln->umqh);
-  ch->conn.reset();
-  if (ch->tcp >= 0) close(ch->tcp);
-  ch->tcp = -1;
+  {
+    std::lock_guard<std::mutex> cl(ch->ctl_mu);
+    ch->conn.reset();
+    if (ch->tcp >= 0) close(ch->tcp);
+    ch->tcp = -1;
+    ch->rxbuf.clear();
+  }
   for (auto& kv : ch->pending)
     if (!kv.second.sync)
       ch->ready.push_back(Ready{URPC_POLL_ERR, kv.second.func_id, kv.second.user_ctx, kv.first,
@@ -924,16 +1544,23 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
     p.t0 = ub::now_ns();
     p.deadline = p.t0 + uint64_t(tmo) * 1000000ull;
     p.sync = opt && opt->sync;
-    ch->pending[req_id] = std::move(p);
-    Head h{urpc_proto::kVersion, URPC_MSG_REQ, static_cast<uint8_t>(1 | t_call_flags), wr->func_id, req_id, chid, 0, 0};
-    // the queue the caller named (urpc_func_call_on), else the lanes in turn
+    // version 1 always set the bit (and nobody acted on it); version 2 sets it when the caller wants the event
+    p.want_ack = opt && opt->want_ack && (ch->proto.caps & urpc_proto::kCapAck);
+    const uint8_t ackbit = (ch->proto.version < 2 || p.want_ack) ? 1 : 0;
+    Head h{ch->proto.version, URPC_MSG_REQ, static_cast<uint8_t>(ackbit | t_call_flags), wr->func_id, req_id, chid, 0, 0};
+    // the queue the caller named (urpc_func_call_on), else the lanes in turn (one that is leaving takes no more)
     size_t lane = ch->extra.empty() ? 0 : ch->rr++ % (ch->extra.size() + 1);
+    for (size_t tries = 0; lane && ch->extra[lane - 1]->closing.load() && tries <= ch->extra.size(); ++tries)
+      lane = ch->rr++ % (ch->extra.size() + 1);
+    if (lane && ch->extra[lane - 1]->closing.load()) lane = 0;
     if (t_call_queue) {
       lane = ch->extra.size() + 1;
       if (ch->umqh == t_call_queue) lane = 0;
       for (size_t i = 0; i < ch->extra.size(); ++i)
-        if (ch->extra[i]->umqh == t_call_queue) lane = i + 1;
+        if (ch->extra[i]->umqh == t_call_queue && !ch->extra[i]->closing.load()) lane = i + 1;
     }
+    if (lane && lane <= ch->extra.size()) p.lane_id = ch->extra[lane - 1]->id;
+    ch->pending[req_id] = std::move(p);
     const int rc = lane > ch->extra.size()
                        ? URPC_ERR_EINVAL
                        : send_msg(lane ? ch->extra[lane - 1]->umqh : ch->umqh, h, wr->args, wr->num_args, nullptr, 0,
@@ -978,6 +1605,7 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
 int urpc_func_poll(uint32_t chid, urpc_poll_msg_t* msgs, int max) {
   Channel* ch = get_channel(chid);
   if (!ch || !msgs || max <= 0) return URPC_ERR_EINVAL;
+  ctl_drain_notices(ch);
   std::lock_guard<std::mutex> l(ch->mu);
   if (ch->attached.load()) channel_progress(ch);
   int n = 0;
@@ -1015,8 +1643,15 @@ int urpc_keepalive_callback_register(urpc_keepalive_cb_t cb, void* ctx) {
 int urpc_channel_task_cancel(uint32_t chid, uint32_t req_id) {
   Channel* ch = get_channel(chid);
   if (!ch) return URPC_ERR_EINVAL;
-  std::lock_guard<std::mutex> l(ch->mu);
-  return ch->pending.erase(req_id) ? URPC_SUCCESS : URPC_ERR_EINVAL;
+  {
+    std::lock_guard<std::mutex> l(ch->mu);
+    if (!ch->pending.erase(req_id)) return URPC_ERR_EINVAL;
+  }
+  // the server drops its deferred copy too (when it knows how); a peer without the capability just answers late
+  // and the answer is discarded here
+  if (ch->attached.load() && (ch->proto.caps & urpc_proto::kCapTaskCancel))
+    ctl_call(ch, urpc_proto::kCtlTaskCancel, &req_id, sizeof(req_id), nullptr, 1000);
+  return URPC_SUCCESS;
 }
 
 // ---------------------------------------------------------------------------------------------- management socket
@@ -1024,7 +1659,8 @@ static std::string admin_report(const std::string& cmd) {
   char line[512];
   std::string r;
   if (cmd == "version") {
-    r = "urpc 1.0 (umdk_b200), protocol version " + std::to_string((int)urpc_proto::kVersion) + "\n";
+    r = "urpc 1.0 (umdk_b200), protocol versions " + std::to_string((int)urpc_proto::kVersionMin) + ".." +
+        std::to_string((int)urpc_proto::kVersion) + "\n";
   } else if (cmd == "stats") {
     urpc_stats_t s{};
     urpc_stats_get(&s);
@@ -1054,11 +1690,28 @@ static std::string admin_report(const std::string& cmd) {
   } else if (cmd == "sessions") {
     std::lock_guard<std::mutex> l(g.mu);
     for (Session* s : g.sessions) {
-      snprintf(line, sizeof(line), "session %u tcp_fd %d queue %llx control %s payload %s\n", s->id, s->tcp,
-               (unsigned long long)s->umqh, s->conn ? s->conn->cipher() : "none", s->seal.on() ? "sealed" : "clear");
+      size_t lanes = 1;
+      {
+        std::lock_guard<std::mutex> ll(s->lanes_mu);
+        lanes += s->extra.size();
+      }
+      snprintf(line, sizeof(line), "session %u tcp_fd %d queue %llx control %s payload %s proto %u caps 0x%x lanes %zu %s\n",
+               s->id, s->tcp, (unsigned long long)s->umqh, s->conn ? s->conn->cipher() : "none",
+               s->seal.on() ? "sealed" : "clear", s->proto.version, s->proto.caps, lanes,
+               s->closed.load() ? "retired" : "live");
       r += line;
     }
     if (r.empty()) r = "(no sessions)\n";
+  } else if (cmd == "tasks") {
+    urpc_ctl_stats_t t{};
+    urpc_ctl_stats_get(&t);
+    snprintf(line, sizeof(line),
+             "tasks_started %llu\ntasks_done %llu\ntasks_failed %llu\ntasks_timed_out %llu\nnotices_sent %llu\n"
+             "sessions_retired %llu\ntasks_live %u\ntimers_armed %u\n",
+             (unsigned long long)t.tasks_started, (unsigned long long)t.tasks_done, (unsigned long long)t.tasks_failed,
+             (unsigned long long)t.tasks_timed_out, (unsigned long long)t.notices_sent,
+             (unsigned long long)t.sessions_retired, t.tasks_live, t.timers_armed);
+    r = line;
   } else if (cmd == "funcs") {
     std::lock_guard<std::mutex> l(g.mu);
     for (auto& kv : g.funcs) {
@@ -1067,7 +1720,7 @@ static std::string admin_report(const std::string& cmd) {
     }
     if (r.empty()) r = "(no functions)\n";
   } else {
-    r = "unknown command; try: version stats perf channels sessions funcs\n";
+    r = "unknown command; try: version stats perf channels sessions tasks funcs\n";
   }
   return r;
 }
@@ -1226,8 +1879,9 @@ static const CurrentReq* req_of(const urpc_poll_msg_t* req, CurrentReq* tmp) {
     if (sid < g.sessions.size()) s = g.sessions[sid];
   }
   const uint32_t lane = static_cast<uint32_t>(req->user_ctx >> 24) & 0xff;
-  if (!s || n == 0 || n > URPC_MAX_REFS || lane > s->extra.size()) return nullptr;
-  *tmp = CurrentReq{lane ? s->extra[lane - 1]->umqh : s->umqh, reinterpret_cast<const RefEntry*>(args + all - 4 - n * sizeof(RefEntry)), n};
+  LaneRef lr;
+  if (!s || n == 0 || n > URPC_MAX_REFS || !session_lane(s, lane, &lr)) return nullptr;
+  *tmp = CurrentReq{lr.umqh, reinterpret_cast<const RefEntry*>(args + all - 4 - n * sizeof(RefEntry)), n};
   return tmp;
 }
 int urpc_ref_count(const urpc_poll_msg_t* req) {
@@ -1359,6 +2013,14 @@ int urpc_ctrl_msg_cb_register(urpc_ctrl_cb_t cb) {
 }
 int urpc_async_event_get(urpc_async_event_t* events, int num) {
   if (!events || num <= 0) return URPC_ERR_EINVAL;
+  {   // notices of the servers (function table changes) sit on the control connections until somebody reads them
+    std::vector<Channel*> chs;
+    {
+      std::lock_guard<std::mutex> l(g.mu);
+      for (auto& kv : g.channels) chs.push_back(kv.second);
+    }
+    for (Channel* ch : chs) ctl_drain_notices(ch);
+  }
   std::lock_guard<std::mutex> l(g.stat_mu);
   int n = 0;
   while (n < num && !g.events.empty()) {
@@ -1386,6 +2048,8 @@ int urpc_channel_cfg_get(uint32_t chid, urpc_channel_cfg_t* cfg) {
   cfg->attached = ch->attached.load();
   cfg->lost = ch->lost.load();
   cfg->sealed = ch->seal.on();
+  cfg->proto_version = ch->attached.load() ? ch->proto.version : 0;
+  cfg->proto_caps = ch->attached.load() ? ch->proto.caps : 0;
   cfg->pending_calls = static_cast<uint32_t>(ch->pending.size());
   snprintf(cfg->server_ip, sizeof(cfg->server_ip), "%s", ch->server_ip.c_str());
   cfg->server_port = ch->server_port;
@@ -1479,11 +2143,37 @@ int urpc_channel_queue_add(uint32_t chid, uint64_t qh) {
     std::lock_guard<std::mutex> l(g_q_mu);
     if (!g_user_queues.count(qh)) return URPC_ERR_EINVAL;
   }
-  if (!ch || ch->attached.load()) return URPC_ERR_EINVAL;   // queues change hands only while detached
+  if (!ch) return URPC_ERR_EINVAL;
   {   // one queue serves one channel
     std::lock_guard<std::mutex> l(g.mu);
     for (auto& kv : g.channels)
       if (channel_lane(kv.second, qh) >= 0) return URPC_ERR_EINVAL;
+  }
+  if (ch->attached.load()) {
+    // Live channel: pair the queue with a new server queue through the control connection, then let calls use it.
+    // Needs a peer that negotiated version 2 with the capability; an older peer changes queues only while detached.
+    if (!(ch->proto.caps & urpc_proto::kCapLiveQueues) || ch->lost.load()) return URPC_ERR_EINVAL;
+    LanePtr ln(new Lane());
+    {
+      std::lock_guard<std::mutex> l(ch->mu);
+      if (ch->extra.size() + 1 >= kMaxLanes || ch->next_lane_id > kMaxLaneId) return URPC_ERR_EINVAL;
+      ln->id = ch->next_lane_id++;
+    }
+    ln->umqh = qh;
+    std::vector<uint8_t> msg(8 + UMQ_BIND_INFO_SIZE), answer;
+    const uint32_t blob_len = umq_bind_info_get(qh, msg.data() + 8, UMQ_BIND_INFO_SIZE);
+    memcpy(msg.data(), &ln->id, 4);
+    memcpy(msg.data() + 4, &blob_len, 4);
+    const int rc = ctl_call(ch, urpc_proto::kCtlQueueAdd, msg.data(), 8 + blob_len, &answer, 3000);
+    if (rc != URPC_SUCCESS) return rc;
+    if (umq_bind(qh, answer.data(), static_cast<uint32_t>(answer.size())) != UMQ_SUCCESS) {
+      ctl_call(ch, urpc_proto::kCtlQueueRm, &ln->id, 4, nullptr, 3000);   // undo the server half
+      return URPC_FAIL;
+    }
+    if (ch->sealed) ln->seal.set(ch->data_key, false, ln->id);
+    std::lock_guard<std::mutex> l(ch->mu);
+    ch->extra.push_back(ln);
+    return URPC_SUCCESS;
   }
   std::lock_guard<std::mutex> l(ch->mu);
   if (!ch->user_queue) {   // the first explicit queue takes the place of the one the channel made for itself
@@ -1499,7 +2189,37 @@ int urpc_channel_queue_add(uint32_t chid, uint64_t qh) {
 }
 int urpc_channel_queue_rm(uint32_t chid, uint64_t qh) {
   Channel* ch = get_channel(chid);
-  if (!ch || ch->attached.load()) return URPC_ERR_EINVAL;
+  if (!ch) return URPC_ERR_EINVAL;
+  if (ch->attached.load()) {
+    // Live channel: stop sending on the lane, wait for the calls in flight on it (their answers return on the same
+    // lane), have the server retire its half, then unbind. The first queue pair carries the keepalive probes and
+    // stays for the whole attach.
+    if (!(ch->proto.caps & urpc_proto::kCapLiveQueues)) return URPC_ERR_EINVAL;
+    LanePtr ln;
+    {
+      std::lock_guard<std::mutex> l(ch->mu);
+      const int lane = channel_lane(ch, qh);
+      if (lane <= 0) return URPC_ERR_EINVAL;
+      ln = ch->extra[lane - 1];
+      if (ln->closing.exchange(true)) return URPC_ERR_EINVAL;   // already leaving
+    }
+    const uint64_t deadline = now_ms() + (ch->timeout_ms ? ch->timeout_ms : g.cfg.default_timeout_ms) + 100;
+    for (;;) {
+      size_t inflight = 0;
+      {
+        std::lock_guard<std::mutex> l(ch->mu);
+        channel_progress(ch);
+        for (auto& kv : ch->pending) inflight += kv.second.lane_id == ln->id && !kv.second.done;
+      }
+      if (inflight == 0 || now_ms() > deadline || ch->lost.load()) break;
+      usleep(200);
+    }
+    const int rc = ctl_call(ch, urpc_proto::kCtlQueueRm, &ln->id, 4, nullptr, 4000);
+    std::lock_guard<std::mutex> l(ch->mu);
+    umq_unbind(ln->umqh);
+    ch->extra.erase(std::remove(ch->extra.begin(), ch->extra.end(), ln), ch->extra.end());
+    return rc == URPC_ERR_SESSION_CLOSE ? URPC_SUCCESS : rc;   // a server that is gone has nothing left to retire
+  }
   std::lock_guard<std::mutex> l(ch->mu);
   const int lane = channel_lane(ch, qh);
   if (lane < 0 || !ch->user_queue) return URPC_ERR_EINVAL;
@@ -1614,3 +2334,90 @@ int urpc_perf_get(uint64_t* count, uint64_t* avg_ns, uint64_t* p99_ns) {
 }
 
 }  // extern "C"
+
+// Self-checks of the header-only units (timer wheel, slab, id generator) and of the head codecs / negotiation.
+// 0 = all passed, else the source line of the first check that failed. Exported for the test-suite.
+extern "C" URPC_EXPORT int urpc_units_selftest(void) {
+#define UNIT_CHECK(c) \
+  do {                \
+    if (!(c)) return __LINE__; \
+  } while (0)
+  {   // id generator: lowest free after the last one, no reuse at once, double free reported
+    urpc_util::IdGen ids(10, 4);
+    uint32_t a, b, c, d, e;
+    UNIT_CHECK(ids.alloc(&a) && ids.alloc(&b) && ids.alloc(&c) && ids.alloc(&d));
+    UNIT_CHECK(a == 10 && b == 11 && c == 12 && d == 13 && !ids.alloc(&e) && ids.in_use() == 4);
+    UNIT_CHECK(ids.free(11) && !ids.free(11) && !ids.free(99) && ids.in_use() == 3);
+    UNIT_CHECK(ids.alloc(&e) && e == 11);
+    UNIT_CHECK(ids.free(10) && ids.free(12) && ids.alloc(&e) && e == 12);   // hint moved past 11
+  }
+  {   // slab: stable pointers, stale handles do not resolve, growth by chunks
+    urpc_util::Slab<std::vector<int>> slab(2);
+    std::vector<int>* p1 = nullptr;
+    std::vector<int>* p2 = nullptr;
+    std::vector<int>* p3 = nullptr;
+    const uint64_t h1 = slab.acquire(&p1), h2 = slab.acquire(&p2), h3 = slab.acquire(&p3);
+    p1->assign(3, 7);
+    UNIT_CHECK(slab.live() == 3 && slab.capacity() == 4 && slab.get(h1) == p1 && slab.get(h2) == p2);
+    UNIT_CHECK(slab.release(h2) && !slab.release(h2) && slab.get(h2) == nullptr && slab.live() == 2);
+    std::vector<int>* p4 = nullptr;
+    const uint64_t h4 = slab.acquire(&p4);
+    UNIT_CHECK(p4 == p2 && h4 != h2 && slab.get(h2) == nullptr && slab.get(h4) == p4 && p4->empty());
+    UNIT_CHECK(slab.get(h1)->size() == 3 && slab.get(h3) == p3);
+  }
+  {   // timer wheel: one-shot order, periodic re-arm, restart, stop, far wheel (beyond one turn of 256 ticks)
+    urpc_util::TimerWheel w(10, 1000);
+    std::vector<int> fired;
+    const uint32_t t1 = w.create([&] { fired.push_back(1); });
+    const uint32_t t2 = w.create([&] { fired.push_back(2); });
+    const uint32_t t3 = w.create([&] { fired.push_back(3); });
+    const uint32_t t4 = w.create([&] { fired.push_back(4); });
+    UNIT_CHECK(w.start(t1, 30) && w.start(t2, 20) && w.start(t3, 5000) && w.start(t4, 25, true));
+    UNIT_CHECK(w.run(1010) == 0 && fired.empty());
+    UNIT_CHECK(w.run(1030) == 3 && fired == (std::vector<int>{2, 1, 4}));   // t4 rounds 25 ms up to 3 ticks
+    UNIT_CHECK(w.armed(t4) && !w.armed(t1) && w.armed_count() == 2);
+    UNIT_CHECK(w.run(1060) == 1 && fired.back() == 4);                       // periodic: again after 3 ticks
+    UNIT_CHECK(w.stop(t4) && !w.stop(t4));
+    UNIT_CHECK(w.start(t1, 40) && w.start(t1, 100));                         // restart moves it
+    UNIT_CHECK(w.run(1120) == 0 && w.run(1160) == 1 && fired.back() == 1);
+    UNIT_CHECK(w.run(5990) == 0 && w.run(6000) == 1 && fired.back() == 3);   // 500 ticks away: far wheel
+    UNIT_CHECK(w.destroy(t2) && !w.start(t2, 10));
+    const uint32_t t5 = w.create([&] { fired.push_back(5); });
+    UNIT_CHECK(t5 == t2);                                                    // slot reused
+    UNIT_CHECK(w.start(t5, 256 * 10 * 300) && w.armed(t5));                  // more than one turn of the far wheel
+    UNIT_CHECK(w.run(6000 + 256 * 10 * 299) == 0 && w.run(6000 + 256 * 10 * 300) == 1 && fired.back() == 5);
+  }
+  {   // heads: every layout survives its codec, and the kinds do not decode as one another
+    urpc_req_head_t raw;
+    urpc_proto::AckHead a{2, 3, 0x01020304, 0xabcdef}, a2{};
+    urpc_proto::encode_ack(a, &raw);
+    UNIT_CHECK(urpc_proto::decode_ack(&raw, &a2) && a2.version == 2 && a2.req_id_range == 3 &&
+               a2.req_id == 0x01020304 && a2.channel == 0xabcdef);
+    urpc_proto::RspHead r{2, URPC_MSG_ACK_AND_RSP, 0x20, 1, 0xdeadbeef, 77, 0x123456, 4096, -38}, r2{};
+    UNIT_CHECK(!urpc_proto::decode_rsp(&raw, &r2));   // an ACK is not a response
+    urpc_proto::encode_rsp(r, &raw);
+    UNIT_CHECK(urpc_proto::decode_rsp(&raw, &r2) && r2.type == URPC_MSG_ACK_AND_RSP && r2.flags == 0x20 &&
+               r2.function_defined == 0xdeadbeef && r2.req_id == 77 && r2.channel == 0x123456 &&
+               r2.total_size == 4096 && r2.status == -38 && r2.req_id_range == 1);
+    UNIT_CHECK(!urpc_proto::decode_ack(&raw, &a2));
+    Head h{2, URPC_MSG_REQ, 1, 0x0000123456789abcull, 9, 5, 100, 0}, h2{};
+    urpc_proto::encode(h, &raw);
+    UNIT_CHECK(urpc_proto::decode(&raw, &h2) && h2.func_id == 0x123456789abcull && h2.req_id == 9 && h2.version == 2);
+    raw.bytes[0] = static_cast<uint8_t>((9 << 4) | URPC_MSG_REQ);
+    UNIT_CHECK(!urpc_proto::decode(&raw, &h2));       // a version nobody speaks
+  }
+  {   // negotiation: newest common version, capabilities only from version 2 on, old peers send the plain number
+    using urpc_proto::negotiate;
+    using urpc_proto::pack_version;
+    const uint32_t v2 = pack_version(2, 1, urpc_proto::kCapsAll);
+    UNIT_CHECK(negotiate(v2, v2).version == 2 && negotiate(v2, v2).caps == urpc_proto::kCapsAll);
+    UNIT_CHECK(negotiate(v2, 1).version == 1 && negotiate(v2, 1).caps == 0);
+    UNIT_CHECK(negotiate(1, v2).version == 1);
+    UNIT_CHECK(negotiate(pack_version(2, 2, urpc_proto::kCapsAll), 1).version == 0);   // needs 2, peer only 1
+    UNIT_CHECK(negotiate(pack_version(3, 2, 0xffff), pack_version(2, 1, urpc_proto::kCapAck)).version == 2);
+    UNIT_CHECK(negotiate(pack_version(3, 2, 0xffff), pack_version(2, 1, urpc_proto::kCapAck)).caps == urpc_proto::kCapAck);
+    UNIT_CHECK(negotiate(pack_version(3, 3, 0), v2).version == 0);
+  }
+#undef UNIT_CHECK
+  return 0;
+}

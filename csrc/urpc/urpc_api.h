@@ -19,12 +19,16 @@ extern "C" {
 #define URPC_ERR_TIMEOUT (-110)
 #define URPC_ERR_SESSION_CLOSE (-104)
 #define URPC_ERR_FUNC_NOT_FOUND (-38)
+#define URPC_ERR_VERSION (-71)   /* no protocol version in common with the peer */
+#define URPC_ERR_CANCELED (-125) /* the client cancelled the request this answer belongs to */
 
 typedef enum urpc_role { URPC_ROLE_SERVER = 0, URPC_ROLE_CLIENT = 1, URPC_ROLE_SERVER_CLIENT = 2 } urpc_role_t;
 typedef enum urpc_msg_type { URPC_MSG_REQ = 0, URPC_MSG_ACK = 1, URPC_MSG_RSP = 2, URPC_MSG_ACK_AND_RSP = 3,
                              URPC_MSG_READ = 4 } urpc_msg_type_t;
-typedef enum urpc_poll_event { URPC_POLL_REQ = 1, URPC_POLL_RSP = 2, URPC_POLL_ERR = 3, URPC_POLL_TIMEOUT = 4 }
-    urpc_poll_event_t;
+/* URPC_POLL_ACK: the server took a request that asked for an acknowledgement (want_ack) and will answer it later;
+ * the call stays pending. Only between peers that negotiated protocol version 2. */
+typedef enum urpc_poll_event { URPC_POLL_REQ = 1, URPC_POLL_RSP = 2, URPC_POLL_ERR = 3, URPC_POLL_TIMEOUT = 4,
+                               URPC_POLL_ACK = 5 } urpc_poll_event_t;
 
 #define URPC_FUNC_ID_KEEPALIVE 0xFFFFFFFFFFFFull /* reserved 48-bit id */
 #define URPC_FUNC_ID_LOOKUP 0xFFFFFFFFFFFEull    /* reserved: function name -> id (urpc_func_id_get) */
@@ -60,6 +64,7 @@ typedef struct urpc_call_option {
   void* rsp_buf;
   uint32_t rsp_buf_len;
   uint32_t* rsp_len;
+  int want_ack;        /* 1: ask the server to acknowledge the request when it defers the answer (URPC_POLL_ACK) */
 } urpc_call_option_t;
 
 typedef struct urpc_poll_msg {
@@ -166,8 +171,9 @@ URPC_EXPORT int urpc_func_poll_wait(uint32_t chid, urpc_poll_msg_t* msgs, int ma
 typedef enum urpc_ctrl_msg_type { URPC_CTRL_ATTACH = 1, URPC_CTRL_DETACH = 2 } urpc_ctrl_msg_type_t;
 typedef void (*urpc_ctrl_cb_t)(urpc_ctrl_msg_type_t type, uint32_t session, uint32_t client_channel);
 URPC_EXPORT int urpc_ctrl_msg_cb_register(urpc_ctrl_cb_t cb); /* server: a client attached / detached */
-typedef enum urpc_async_event_type { URPC_EVENT_CHANNEL_LOST = 1, URPC_EVENT_CHANNEL_REFRESHED = 2 }
-    urpc_async_event_type_t;
+/* FUNC_CHANGED: the attached server registered (detail 1) or unregistered (detail 0) a function. */
+typedef enum urpc_async_event_type { URPC_EVENT_CHANNEL_LOST = 1, URPC_EVENT_CHANNEL_REFRESHED = 2,
+                                     URPC_EVENT_FUNC_CHANGED = 3 } urpc_async_event_type_t;
 typedef struct urpc_async_event {
   urpc_async_event_type_t type;
   uint32_t chid;
@@ -178,6 +184,8 @@ URPC_EXPORT int urpc_async_event_fd_get(void);
 typedef struct urpc_channel_cfg {
   uint32_t timeout_ms; /* settable: request timeout of this channel (0 = library default) */
   int attached, lost, sealed;
+  int proto_version;   /* negotiated at attach time (0 while detached) */
+  uint32_t proto_caps; /* capability bits both sides have */
   uint32_t pending_calls;
   char server_ip[64];
   uint16_t server_port;
@@ -191,8 +199,17 @@ typedef struct urpc_queue_cfg {
   uint32_t rx_depth, tx_depth, rx_buf_size; /* 0 = 128, 128, 64 KiB */
   int interrupt;                            /* completion events instead of polling */
 } urpc_queue_cfg_t;
-/* Explicit queues: created on their own and given to a channel BEFORE it attaches (the channel then uses it instead
- * of the one it made for itself); taken back after a detach. Depths and sizes are fixed at creation. */
+/* Explicit queues: created on their own and given to a channel. Before the attach the first one replaces the queue
+ * the channel made for itself and the others become further queue pairs; on an ATTACHED channel (protocol version 2)
+ * urpc_channel_queue_add pairs the queue with a new server queue through a control message and calls start to use
+ * it at once, urpc_channel_queue_rm waits for the calls in flight on it, retires the pair and hands the queue
+ * back. Depths and sizes are fixed at creation. */
+/* Control-plane task engine of the server (one thread, asynchronous multi-step tasks): counters for dfx. */
+typedef struct urpc_ctl_stats {
+  uint64_t tasks_started, tasks_done, tasks_failed, tasks_timed_out, notices_sent, sessions_retired;
+  uint32_t tasks_live, timers_armed;
+} urpc_ctl_stats_t;
+URPC_EXPORT int urpc_ctl_stats_get(urpc_ctl_stats_t* out);
 URPC_EXPORT uint64_t urpc_queue_create(const urpc_queue_cfg_t* cfg); /* 0 on failure */
 URPC_EXPORT int urpc_queue_destroy(uint64_t qh);
 URPC_EXPORT int urpc_queue_cfg_get(uint64_t qh, urpc_queue_cfg_t* cfg);

@@ -108,11 +108,7 @@ def test_names_local_exec_channel_config_and_queue_reports(rpc):
     assert rsp.raw[:rlen.value] == b"lacol"
     assert lib.urpc_func_exec(ctypes.c_uint64(99), ctypes.byref(sge), 1, rsp, ctypes.byref(rlen)) != 0
 
-    class ChCfg(ctypes.Structure):
-        _fields_ = [("timeout_ms", ctypes.c_uint32), ("attached", ctypes.c_int), ("lost", ctypes.c_int),
-                    ("sealed", ctypes.c_int), ("pending_calls", ctypes.c_uint32), ("server_ip", ctypes.c_char * 64),
-                    ("server_port", ctypes.c_uint16)]
-    cfg = ChCfg()
+    cfg = urpc._ChannelCfg()
     assert lib.urpc_channel_cfg_get(ch.id, ctypes.byref(cfg)) == 0
     assert cfg.attached == 1 and cfg.lost == 0 and cfg.server_port == srv.port and cfg.timeout_ms == 2000
     cfg.timeout_ms = 150
@@ -418,3 +414,179 @@ def test_sealed_lane_with_four_threads_replying_at_once(tmp_path):
         srv.stop()
         urpc.uninit()
         urpc.set_psk("", "")
+
+
+def test_units_selftest():
+    """Timer wheel, slab, id generator, head codecs and version negotiation, checked inside the library."""
+    from umdk_b200 import _native
+    assert _native.urpc().urpc_units_selftest() == 0
+
+
+def _wait(cond, seconds=5.0):
+    deadline = time.monotonic() + seconds
+    while time.monotonic() < deadline:
+        if cond():
+            return True
+        time.sleep(0.002)
+    return cond()
+
+
+def test_queues_join_and_leave_an_attached_channel(rpc):
+    urpc, srv, ch = rpc
+    assert ch.protocol() == (2, urpc.CAP_LIVE_QUEUES | urpc.CAP_ACK | urpc.CAP_TASK_CANCEL)
+    assert ch.call(1, b"abc") == b"cba"
+    before = urpc.ctl_stats()
+    qa = ch.add_queue()            # control message QUEUE_ADD -> a new queue pair, usable at once
+    qb = ch.add_queue()
+    assert (qa, qb) == (0, 1)
+    assert ch.call(1, b"on a", queue=qa) == b"a no" and ch.call(1, b"on b", queue=qb) == b"b no"
+    for i in range(30):            # calls without a named queue take the lanes in turn
+        assert ch.call(2, bytes([i])) == str(i).encode()
+    sent = [s for s, _ in ch.queue_stats()]
+    assert all(n >= 10 for n in sent), sent
+    assert "lanes 3 live" in urpc.admin_query("sessions")
+    # leave while calls are in flight on the lane: every one of them still gets its answer
+    srv.paused = True
+    for i in range(6):
+        ch.call_async(1, bytes([97 + i]) * 4, user_ctx=i, queue=qa)
+    srv.paused = False
+    ch.remove_queue(qa)
+    got = {}
+    assert _wait(lambda: got.update({c: d for _, c, _, d in ch.poll()}) or len(got) == 6)
+    assert got == {i: bytes([97 + i]) * 4 for i in range(6)}
+    assert len(ch.queues) == 1 and ch.call(1, b"still b", queue=0) == b"b llits"
+    assert "lanes 2 live" in urpc.admin_query("sessions")
+    # a queue that joins later gets a new lane id (a sealing salt is never used twice)
+    qc = ch.add_queue()
+    assert ch.call(1, b"c", queue=qc) == b"c"
+    after = urpc.ctl_stats()
+    assert after["tasks_done"] - before["tasks_done"] == 4 and after["tasks_live"] == 0
+    assert after["tasks_failed"] == before["tasks_failed"]
+    assert "tasks_done" in urpc.admin_query("tasks")
+
+
+def test_live_queue_changes_on_a_sealed_channel(tmp_path):
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import urpc
+    urpc.set_psk("3e" * 32, "rpc")
+    urpc.init(default_timeout_ms=2000)
+    srv = urpc.Server()
+    try:
+        srv.register(1, lambda b: b.upper())
+        ch = urpc.Channel(srv.ip, srv.port)
+        errors = urpc.stats()["errors"]
+        q = ch.add_queue()
+        for i in range(20):
+            assert ch.call(1, b"sealed %d" % i, queue=q) == b"SEALED %d" % i
+        ch.remove_queue(q)
+        q2 = ch.add_queue()
+        assert ch.call(1, b"again", queue=q2) == b"AGAIN"
+        assert urpc.stats()["errors"] == errors     # nothing failed a seal check
+        ch.close()
+    finally:
+        srv.stop()
+        urpc.uninit()
+        urpc.set_psk("", "")
+
+
+def test_acknowledgement_cancel_and_function_notice(rpc):
+    urpc, srv, ch = rpc
+    srv.deferred = lambda fid, args: (b"late:" + args) if fid == 9 else None
+    srv.defer_s = 0.15
+    rid = ch.call_async(9, b"x", user_ctx=5, want_ack=True)
+    events = []
+    assert _wait(lambda: events.extend(ch.poll()) or len(events) >= 2)
+    assert [(e[0], e[1]) for e in events] == [(urpc.POLL_ACK, 5), (urpc.POLL_RSP, 5)] and events[1][3] == b"late:x"
+    # without want_ack there is no acknowledgement event
+    ch.call_async(9, b"y", user_ctx=6)
+    events = []
+    assert _wait(lambda: events.extend(ch.poll()) or len(events) >= 1)
+    time.sleep(0.05)
+    events.extend(ch.poll())
+    assert [(e[0], e[1]) for e in events] == [(urpc.POLL_RSP, 6)]
+    # a cancelled call: the server drops its deferred answer instead of sending it
+    srv.defer_s = 0.3
+    n_ret = len(srv.return_codes)
+    rid = ch.call_async(9, b"z", user_ctx=7)
+    time.sleep(0.05)
+    ch.cancel(rid)
+    assert _wait(lambda: len(srv.return_codes) > n_ret)
+    assert srv.return_codes[-1] == urpc.ERR_CANCELED
+    time.sleep(0.05)
+    assert ch.poll() == []
+    srv.defer_s = 0.0
+    # the server tells attached clients when its function table changes
+    urpc.async_events()
+    srv.register(33, lambda b: b)
+    assert _wait(lambda: any(t == urpc.EVENT_FUNC_CHANGED and d == 1 for t, _, d in urpc.async_events()))
+    assert ch.call(33, b"new") == b"new"
+
+
+def test_detach_retires_the_session_on_the_server(rpc):
+    urpc, srv, ch = rpc
+    extra = urpc.Channel(srv.ip, srv.port, queues=2)
+    assert extra.call(1, b"12") == b"21"
+    before = urpc.ctl_stats()["sessions_retired"]
+    extra.close()
+    assert _wait(lambda: urpc.ctl_stats()["sessions_retired"] == before + 1)
+    assert "retired" in urpc.admin_query("sessions")
+    assert ch.call(1, b"ok") == b"ko"          # the other session is untouched
+
+
+_PEER = r"""
+import sys, time
+from umdk_b200 import urpc
+urpc.init(default_timeout_ms=2000)
+srv = urpc.Server()
+srv.register(1, lambda b: b[::-1])
+print(srv.port, flush=True)
+sys.stdin.readline()
+srv.stop()
+urpc.uninit()
+"""
+
+
+@pytest.mark.parametrize("server_max,client_env,want", [
+    ("1", {}, (1, 0)),                                   # old server, new client: falls back to version 1
+    (None, {"URPC_PROTO_MAX": "1"}, (1, 0)),             # new server, old client
+    ("1", {"URPC_PROTO_MIN": "2"}, None),                # client insists on 2, server only has 1: refused
+])
+def test_version_negotiation_between_old_and_new_builds(tmp_path, server_max, client_env, want):
+    import subprocess
+    import sys
+    shm = tmp_path / "urma"
+    shm.mkdir(exist_ok=True)
+    env = dict(os.environ, URMA_SHM_DIR=str(shm))
+    if server_max:
+        env["URPC_PROTO_MAX"] = server_max
+    peer = subprocess.Popen([sys.executable, "-c", _PEER], env=env, stdin=subprocess.PIPE, stdout=subprocess.PIPE,
+                            text=True)
+    os.environ["URMA_SHM_DIR"] = str(shm)
+    from umdk_b200 import urpc
+    try:
+        port = int(peer.stdout.readline())
+        os.environ.update(client_env)
+        urpc.init(default_timeout_ms=2000)
+        if want is None:
+            with pytest.raises(urpc.UrpcError) as e:
+                urpc.Channel("127.0.0.1", port)
+            assert e.value.code == urpc.ERR_VERSION
+        else:
+            ch = urpc.Channel("127.0.0.1", port)
+            assert ch.protocol() == want
+            assert ch.call(1, b"compat") == b"tapmoc"
+            rid = ch.call_async(1, b"q", user_ctx=3, want_ack=True)   # no acknowledgements in version 1
+            got = []
+            assert _wait(lambda: got.extend(ch.poll()) or got)
+            assert [(g[0], g[1]) for g in got] == [(urpc.POLL_RSP, 3)]
+            with pytest.raises(urpc.UrpcError):
+                ch.add_queue()                         # queues change only while detached with such a peer
+            ch.close()
+    finally:
+        for k in client_env:
+            os.environ.pop(k, None)
+        urpc.uninit()
+        peer.stdin.write("\n")
+        peer.stdin.flush()
+        peer.wait(timeout=20)

@@ -41,7 +41,31 @@ class _CallWr(ctypes.Structure):
 
 class _CallOpt(ctypes.Structure):
     _fields_ = [("timeout_ms", ctypes.c_uint32), ("sync", ctypes.c_int), ("rsp_buf", ctypes.c_void_p),
-                ("rsp_buf_len", ctypes.c_uint32), ("rsp_len", ctypes.POINTER(ctypes.c_uint32))]
+                ("rsp_buf_len", ctypes.c_uint32), ("rsp_len", ctypes.POINTER(ctypes.c_uint32)),
+                ("want_ack", ctypes.c_int)]
+
+
+class _ChannelCfg(ctypes.Structure):
+    _fields_ = [("timeout_ms", ctypes.c_uint32), ("attached", ctypes.c_int), ("lost", ctypes.c_int),
+                ("sealed", ctypes.c_int), ("proto_version", ctypes.c_int), ("proto_caps", ctypes.c_uint32),
+                ("pending_calls", ctypes.c_uint32), ("server_ip", ctypes.c_char * 64),
+                ("server_port", ctypes.c_uint16)]
+
+
+class _CtlStats(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_uint64) for n in ("tasks_started", "tasks_done", "tasks_failed", "tasks_timed_out",
+                                               "notices_sent", "sessions_retired")] + \
+               [("tasks_live", ctypes.c_uint32), ("timers_armed", ctypes.c_uint32)]
+
+
+class _AsyncEvent(ctypes.Structure):
+    _fields_ = [("type", ctypes.c_int), ("chid", ctypes.c_uint32), ("detail", ctypes.c_int)]
+
+
+POLL_REQ, POLL_RSP, POLL_ERR, POLL_TIMEOUT, POLL_ACK = 1, 2, 3, 4, 5
+EVENT_CHANNEL_LOST, EVENT_CHANNEL_REFRESHED, EVENT_FUNC_CHANGED = 1, 2, 3
+CAP_LIVE_QUEUES, CAP_ACK, CAP_TASK_CANCEL = 1, 2, 4
+ERR_VERSION, ERR_CANCELED = -71, -125
 
 
 class _PollMsg(ctypes.Structure):
@@ -179,6 +203,20 @@ def stats() -> dict:
     return {n: int(getattr(s, n)) for n, _ in _Stats._fields_}
 
 
+def ctl_stats() -> dict:
+    """Counters of the server's control-plane task engine (tasks started / done / failed, notices, live tasks)."""
+    st = _CtlStats()
+    _lib().urpc_ctl_stats_get(ctypes.byref(st))
+    return {n: int(getattr(st, n)) for n, _ in _CtlStats._fields_}
+
+
+def async_events(max_n: int = 32) -> List[Tuple[int, int, int]]:
+    """[(event type, channel id, detail)]: lost channels, refreshed channels, function-table changes."""
+    ev = (_AsyncEvent * max_n)()
+    n = _lib().urpc_async_event_get(ev, max_n)
+    return [(ev[i].type, int(ev[i].chid), ev[i].detail) for i in range(max(n, 0))]
+
+
 def on_keepalive(cb: Callable[[int, bool], None]) -> None:
     """cb(channel_id, alive) when a peer stops or resumes answering keepalive probes."""
     c = _KA_CB(lambda chid, alive, _ctx: cb(int(chid), bool(alive)))
@@ -196,6 +234,11 @@ class Server:
         self.ip, self.port = ip, p
         self._stop = threading.Event()
         self.paused = False   # True: requests are left unanswered (to exercise timeouts / keepalive)
+        # requests of functions without a registered handler reach `deferred(func_id, args)`; it returns the answer
+        # bytes, or (answer, status), or None to leave the request unanswered; it runs after `defer_s` seconds
+        self.deferred: Optional[Callable[[int, bytes], object]] = None
+        self.defer_s = 0.0
+        self.return_codes: List[int] = []   # urpc_func_return results of deferred answers
         self._thr = threading.Thread(target=self._loop, daemon=True)
         self._thr.start()
 
@@ -225,7 +268,16 @@ class Server:
                 continue
             n = lib.urpc_server_poll(msgs, 16)
             for i in range(max(n, 0)):
-                lib.urpc_msg_release(ctypes.byref(msgs[i]))   # registered functions were executed by the library
+                m = msgs[i]
+                if self.deferred is not None and m.event == POLL_REQ:   # registered functions ran inside the library
+                    args = ctypes.string_at(m.data, m.len) if m.data and m.len else b""
+                    if self.defer_s:
+                        time.sleep(self.defer_s)
+                    out = self.deferred(int(m.func_id), args)
+                    if out is not None:
+                        body, status = out if isinstance(out, tuple) else (out, 0)
+                        self.return_codes.append(lib.urpc_func_return(ctypes.byref(m), body, len(body), status))
+                lib.urpc_msg_release(ctypes.byref(m))
             if n <= 0:
                 time.sleep(0.0002)
 
@@ -289,7 +341,7 @@ class Channel:
         wr, keep = self._wr(func_id, args, 0)
         rsp = ctypes.create_string_buffer(max_rsp)
         n = ctypes.c_uint32(0)
-        opt = _CallOpt(timeout_ms, 1, ctypes.cast(rsp, ctypes.c_void_p), max_rsp, ctypes.pointer(n))
+        opt = _CallOpt(timeout_ms, 1, ctypes.cast(rsp, ctypes.c_void_p), max_rsp, ctypes.pointer(n), 0)
         rc = self._call(wr, opt, queue)
         if rc != 0:
             raise UrpcError("urpc_func_call", rc)
@@ -303,16 +355,51 @@ class Channel:
         arr = (_MemRef * len(refs))(*[_MemRef(h, a, n) for h, a, n in refs])
         rsp = ctypes.create_string_buffer(max_rsp)
         n = ctypes.c_uint32(0)
-        opt = _CallOpt(timeout_ms, 1, ctypes.cast(rsp, ctypes.c_void_p), max_rsp, ctypes.pointer(n))
+        opt = _CallOpt(timeout_ms, 1, ctypes.cast(rsp, ctypes.c_void_p), max_rsp, ctypes.pointer(n), 0)
         rc = _lib().urpc_func_call_ref(self.id, ctypes.byref(wr), arr, len(refs), ctypes.byref(opt))
         if rc != 0:
             raise UrpcError("urpc_func_call_ref", rc)
         return rsp.raw[:n.value]
 
+    def add_queue(self) -> int:
+        """Adds one more queue pair to the channel, attached or not (an attached channel needs a server that
+        negotiated protocol version 2). -> index for ``call(..., queue=i)``."""
+        lib = _lib()
+        lib.urpc_queue_create.restype = ctypes.c_uint64
+        q = lib.urpc_queue_create(None)
+        if not q:
+            raise UrpcError("urpc_queue_create", -1)
+        rc = lib.urpc_channel_queue_add(self.id, ctypes.c_uint64(q))
+        if rc != 0:
+            lib.urpc_queue_destroy(ctypes.c_uint64(q))
+            raise UrpcError("urpc_channel_queue_add", rc)
+        self.queues.append(q)
+        return len(self.queues) - 1
+
+    def remove_queue(self, index: int) -> None:
+        """Takes a queue pair out of the channel (waits for the calls in flight on it) and destroys the queue."""
+        q = self.queues[index]
+        rc = _lib().urpc_channel_queue_rm(self.id, ctypes.c_uint64(q))
+        if rc != 0:
+            raise UrpcError("urpc_channel_queue_rm", rc)
+        self.queues.pop(index)
+        _lib().urpc_queue_destroy(ctypes.c_uint64(q))
+
+    def protocol(self) -> Tuple[int, int]:
+        """(negotiated protocol version, capability bits) of the attach; (0, 0) while detached."""
+        cfg = _ChannelCfg()
+        _lib().urpc_channel_cfg_get(self.id, ctypes.byref(cfg))
+        return cfg.proto_version, cfg.proto_caps
+
+    def cancel(self, req_id: int) -> None:
+        rc = _lib().urpc_channel_task_cancel(self.id, req_id)
+        if rc != 0:
+            raise UrpcError("urpc_channel_task_cancel", rc)
+
     def call_async(self, func_id: int, args: bytes = b"", user_ctx: int = 0, timeout_ms: int = 0,
-                   queue: Optional[int] = None) -> int:
+                   queue: Optional[int] = None, want_ack: bool = False) -> int:
         wr, keep = self._wr(func_id, args, user_ctx)
-        opt = _CallOpt(timeout_ms, 0, None, 0, None)
+        opt = _CallOpt(timeout_ms, 0, None, 0, None, int(want_ack))
         rc = self._call(wr, opt, queue)
         if rc < 0:
             raise UrpcError("urpc_func_call", rc)
