@@ -60,7 +60,7 @@ def test_urpc_admin_reads_the_management_socket(tmp_path):
         assert rc == 0 and "calls " in out and "bytes_tx " in out, out
         assert int(out.split("calls ")[1].split()[0]) >= 500
         rc, out = _run([BIN / "urpc_admin", sock, "version"], tmp_path)
-        assert rc == 0 and "protocol version 1" in out, out
+        assert rc == 0 and "protocol versions 1..2" in out, out
         rc, out = _run([BIN / "urpc_admin", sock, "channels"], tmp_path)
         assert rc == 0 and "channel 0 attached 1" in out, out
         srv.wait(timeout=30)
