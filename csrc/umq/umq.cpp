@@ -23,6 +23,7 @@
 #include <memory>
 #include <thread>
 #include <mutex>
+#include <random>
 #include <unordered_map>
 #include <unordered_set>
 #include <vector>
@@ -34,7 +35,16 @@
 namespace {
 
 // immediate data layout: [63:56] type, [55:32] credits returned, [31:0] message bytes
-enum ImmType : uint64_t { IMM_IO = 1, IMM_FC_RETURN = 2 };
+// IMM_PULL_REQ: the payload is a PullDesc - the message itself stays in the sender's memory and the receiver fetches
+// it with a one-sided read (messages larger than the peer's receive buffers); IMM_PULL_DONE / IMM_PULL_FAIL: the
+// receiver is through with the read (low 32 bits = the descriptor's cookie), the sender's buffer completes.
+enum ImmType : uint64_t { IMM_IO = 1, IMM_FC_RETURN = 2, IMM_PULL_REQ = 3, IMM_PULL_DONE = 4, IMM_PULL_FAIL = 5 };
+struct PullDesc {
+  uint32_t magic, cookie, token, len;
+  uint64_t addr;
+  uint8_t seg[URMA_SIMPLE_SEG_BLOB];
+};
+constexpr uint32_t kPullMagic = 0x50554c4c;   // "PULL"
 inline uint64_t imm_make(ImmType t, uint32_t credits, uint32_t bytes) {
   return (uint64_t(t) << 56) | (uint64_t(credits & 0xffffff) << 32) | bytes;
 }
@@ -261,7 +271,22 @@ struct Queue {
   std::unordered_map<uint64_t, int> read_done;
   uint64_t next_read = 1;
   std::map<std::string, urma_target_seg_t*> imported;   // peer segments, by blob
+  // large-message pull path (a message that does not fit the peer's receive buffers)
+  uint32_t peer_rx_buf = 0;     // from the peer's bind information
+  uint32_t next_cookie = 1;
+  struct PullTx {               // sender: message waiting for the receiver's read
+    struct Block* block;
+    urma_target_seg_t* seg;
+  };
+  struct PullRx {               // receiver: read in flight into `block`
+    struct Block* block;
+    urma_target_seg_t* rseg;
+    uint32_t cookie;
+  };
+  std::unordered_map<uint32_t, PullTx> pull_tx;    // by cookie
+  std::unordered_map<uint64_t, PullRx> pull_rx;    // by read id
 };
+constexpr uint64_t kRxPending = 1;   // umq_buf_t::rsvd[1] of a queued receive whose data is still being read
 
 Queue* find(uint64_t h) {
   std::lock_guard<std::mutex> l(g.mu);
@@ -481,6 +506,116 @@ void send_credit_return(Queue* q) {
   }
 }
 
+// ---------------------------------------------------------------------------------------- large-message pull path
+// Sender side of a message that does not fit the peer's receive buffers: the block is registered for remote reads
+// and only a descriptor travels. The block stays in flight until the receiver reports the end of its read.
+// Reference: the UB_PLUS transport's pull of large messages (src/urpc/umq/umq_ub/core/private/umq_pro_ub.c).
+void pull_control(Queue* q, ImmType t, uint32_t cookie) {
+  urma_simple_post(q->ep, q->peer, URMA_OPC_SEND_IMM, nullptr, 0, nullptr, 0, 0, imm_make(t, 0, cookie), 0, 0);
+}
+int pull_send(Queue* q, Block* b, uint32_t piggy) {
+  PullDesc d{};
+  d.magic = kPullMagic;
+  d.cookie = q->next_cookie++;
+  if (q->next_cookie == 0) q->next_cookie = 1;
+  static thread_local std::mt19937 rng{std::random_device{}()};
+  d.token = static_cast<uint32_t>(rng()) | 1u;   // one read permission per message
+  d.len = b->meta.data_size;
+  d.addr = reinterpret_cast<uint64_t>(b->meta.buf_data);
+  urma_target_seg_t* seg = urma_simple_seg_register(g.ctx, b->meta.buf_data, d.len, URMA_ACCESS_READ, d.token, d.seg);
+  if (!seg) return UMQ_FAIL;
+  Block* db = block_get(sizeof(PullDesc));
+  if (!db) {
+    urma_unregister_seg(seg);
+    return UMQ_ERR_ENOMEM;
+  }
+  buf_setup(db, q->h, sizeof(PullDesc));
+  memcpy(db->mem, &d, sizeof(d));
+  db->meta.rsvd[0] = 0;   // the descriptor's own block returns to the pool when its send completes
+  const int rc = urma_simple_post(q->ep, q->peer, URMA_OPC_SEND_IMM, nullptr, 0, nullptr,
+                                  reinterpret_cast<uint64_t>(db->mem), sizeof(PullDesc),
+                                  imm_make(IMM_PULL_REQ, piggy, sizeof(PullDesc)), reinterpret_cast<uint64_t>(db), 1);
+  if (rc != 0) {
+    block_put(db);
+    urma_unregister_seg(seg);
+    return rc == URMA_EAGAIN ? UMQ_ERR_EAGAIN : UMQ_FAIL;
+  }
+  q->in_flight.insert(db);
+  q->in_flight.insert(b);
+  q->pull_tx[d.cookie] = Queue::PullTx{b, seg};
+  ++q->io.pull_tx;
+  return UMQ_SUCCESS;
+}
+// The receiver finished (or gave up) its read: the message's buffer completes like any other send.
+void pull_finish_tx(Queue* q, uint64_t imm, uint64_t type) {
+  auto it = q->pull_tx.find(static_cast<uint32_t>(imm));
+  if (it == q->pull_tx.end()) return;
+  Block* b = it->second.block;
+  urma_unregister_seg(it->second.seg);
+  q->pull_tx.erase(it);
+  q->in_flight.erase(b);
+  b->meta.status = type == IMM_PULL_DONE ? UMQ_BUF_OK : UMQ_BUF_SEND_ERR;
+  if (type != IMM_PULL_DONE) ++q->io.tx_errors;
+  if (b->meta.rsvd[0]) q->tx_done.push_back(&b->meta);
+  else block_put(b);
+}
+// Receiver side: a descriptor arrived in `db`. The destination block takes the message's place in the receive order
+// at once (marked pending: dequeue does not pass it) and the read fills it.
+void pull_start_rx(Queue* q, Block* db, uint32_t len) {
+  PullDesc d;
+  if (len < sizeof(d)) {
+    ++q->io.rx_errors;
+    return;
+  }
+  memcpy(&d, db->mem, sizeof(d));
+  if (d.magic != kPullMagic || d.len == 0 || d.len > UMQ_MAX_MSG_SIZE) {
+    ++q->io.rx_errors;
+    return;
+  }
+  Block* dst = block_get(d.len);
+  urma_target_seg_t* rseg = dst ? urma_simple_seg_import(g.ctx, d.seg, d.token) : nullptr;
+  const uint64_t id = (q->next_read++ << 1) | 1;
+  if (!dst || !rseg ||
+      urma_simple_post(q->ep, q->peer, URMA_OPC_READ, rseg, d.addr, nullptr, reinterpret_cast<uint64_t>(dst->mem), d.len, 0,
+                       id, 1) != 0) {
+    if (rseg) urma_unimport_seg(rseg);
+    if (dst) block_put(dst);
+    ++q->io.rx_errors;
+    pull_control(q, IMM_PULL_FAIL, d.cookie);
+    return;
+  }
+  buf_setup(dst, q->h, d.len);
+  dst->meta.total_data_size = d.len;
+  dst->meta.rsvd[1] = kRxPending;
+  q->rx_ready.push_back(&dst->meta);
+  q->pull_rx[id] = Queue::PullRx{dst, rseg, d.cookie};
+}
+// Completion of a read. False when the id is not one of the pull path's.
+bool pull_finish_rx(Queue* q, uint64_t id, int status) {
+  auto it = q->pull_rx.find(id);
+  if (it == q->pull_rx.end()) return false;
+  Queue::PullRx r = it->second;
+  q->pull_rx.erase(it);
+  urma_unimport_seg(r.rseg);
+  r.block->meta.rsvd[1] = 0;
+  if (status == 0) {
+    r.block->meta.status = UMQ_BUF_OK;
+    ++q->io.rx_msgs;
+    ++q->io.pull_rx;
+    q->io.rx_bytes += r.block->meta.data_size;
+  } else {   // the message is lost: its place in the order is given up
+    ++q->io.rx_errors;
+    for (auto p = q->rx_ready.begin(); p != q->rx_ready.end(); ++p)
+      if (*p == &r.block->meta) {
+        q->rx_ready.erase(p);
+        break;
+      }
+    block_put(r.block);
+  }
+  pull_control(q, status == 0 ? IMM_PULL_DONE : IMM_PULL_FAIL, r.cookie);
+  return true;
+}
+
 // drains the completion queue of the endpoint into rx_ready / tx_done; caller holds q->mu
 void progress(Queue* q) {
   int st[32];
@@ -500,10 +635,16 @@ void progress(Queue* q) {
           q->credits += credits;
           q->fcs.credits_granted += credits;
         }
-        if (type == IMM_FC_RETURN || st[i] != 0) {
+        if ((type == IMM_PULL_DONE || type == IMM_PULL_FAIL) && st[i] == 0) pull_finish_tx(q, imm[i], type);
+        if (type == IMM_FC_RETURN || type == IMM_PULL_DONE || type == IMM_PULL_FAIL || st[i] != 0) {
           if (st[i] != 0) ++q->io.rx_errors;
           else ++q->fc_skip;
           block_put(b);  // control message or failed receive: the buffer goes straight back
+          continue;
+        }
+        if (type == IMM_PULL_REQ) {   // a descriptor: fetch the message it names, keep its place in the order
+          pull_start_rx(q, b, len[i]);
+          block_put(b);
           continue;
         }
         b->meta.data_size = len[i];
@@ -513,7 +654,9 @@ void progress(Queue* q) {
         ++q->io.rx_msgs;
         q->io.rx_bytes += len[i];
       } else if (uc[i] & 1) {
-        q->read_done[uc[i]] = st[i];   // a one-sided read: buffer descriptors are aligned, so their low bit is 0
+        // a one-sided read (buffer descriptors are aligned, so their low bit is 0): one of the pull path's, or one
+        // the application issued with umq_remote_read
+        if (!pull_finish_rx(q, uc[i], st[i])) q->read_done[uc[i]] = st[i];
       } else if (uc[i] != 0) {
         Block* b = reinterpret_cast<Block*>(uc[i]);
         q->in_flight.erase(b);
@@ -553,6 +696,21 @@ int send_one(Queue* q, umq_buf_t* buf, bool pro) {
   uint32_t piggy = 0;
   if (q->fc && q->to_return) {
     piggy = q->to_return;
+  }
+  if (q->peer_rx_buf && buf->data_size > q->peer_rx_buf) {   // does not fit over there: the peer pulls it
+    const int prc = pull_send(q, b, piggy);
+    if (prc != UMQ_SUCCESS) {
+      ++q->io.tx_eagain;
+      return prc;
+    }
+    if (piggy) {
+      q->fcs.credits_returned += piggy;
+      q->to_return = 0;
+    }
+    if (q->fc) --q->credits;
+    ++q->io.tx_msgs;
+    q->io.tx_bytes += buf->data_size;
+    return UMQ_SUCCESS;
   }
   const int rc = urma_simple_post(q->ep, q->peer, URMA_OPC_SEND_IMM, nullptr, 0, nullptr,
                                   reinterpret_cast<uint64_t>(buf->buf_data), buf->data_size,
@@ -784,11 +942,14 @@ int umq_destroy(uint64_t h) {
     delete q;
     return UMQ_SUCCESS;
   }
+  // the endpoint goes first: a pull read that is still running must not land in a block that is back in the pool
+  urma_simple_ep_destroy(q->ep);
+  for (auto& kv : q->pull_rx) urma_unimport_seg(kv.second.rseg);
+  for (auto& kv : q->pull_tx) urma_unregister_seg(kv.second.seg);   // their blocks are in in_flight
   for (auto* b : q->rx_ready) block_put(reinterpret_cast<Block*>(b));
   for (auto* b : q->tx_done) block_put(reinterpret_cast<Block*>(b));
   for (auto& kv : q->imported) urma_unimport_seg(kv.second);
   if (q->peer) urma_unimport_jetty(q->peer);
-  urma_simple_ep_destroy(q->ep);
   // the endpoint is gone: nothing can complete into the blocks it still held (posted receives, unfinished sends)
   for (Block* b : q->in_flight) block_put(b);
   delete q;
@@ -826,6 +987,7 @@ int umq_bind(uint64_t h, const uint8_t* info, uint32_t size) {
   q->peer = urma_simple_ep_import(g.ctx, b.jetty, b.token);
   if (!q->peer) return UMQ_FAIL;
   q->fc = q->fc && b.fc;
+  q->peer_rx_buf = b.rx_buf_size;
   q->window = b.rx_depth;
   q->credits = b.rx_depth;  // one credit per receive buffer the peer has posted
   q->fcs.window = b.rx_depth;
@@ -977,7 +1139,7 @@ umq_buf_t* umq_dequeue(uint64_t h) {
   }
   std::lock_guard<std::mutex> l(q->mu);
   progress(q);
-  if (q->rx_ready.empty()) return nullptr;
+  if (q->rx_ready.empty() || q->rx_ready.front()->rsvd[1] == kRxPending) return nullptr;   // head still being read
   umq_buf_t* b = q->rx_ready.front();
   q->rx_ready.pop_front();
   return b;
@@ -1047,7 +1209,7 @@ int umq_poll(uint64_t h, umq_io_direction_t dir, umq_buf_t** bufs, uint32_t max)
   progress(q);
   std::deque<umq_buf_t*>& src = dir == UMQ_IO_RX ? q->rx_ready : q->tx_done;
   uint32_t n = 0;
-  while (n < max && !src.empty()) {
+  while (n < max && !src.empty() && src.front()->rsvd[1] != kRxPending) {   // a message still being read waits
     bufs[n++] = src.front();
     src.pop_front();
   }

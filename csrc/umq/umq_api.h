@@ -93,6 +93,7 @@ UMQ_EXPORT int umq_interrupt_fd_get(uint64_t umqh);
 /* dfx */
 typedef struct umq_io_stats {
   uint64_t tx_msgs, tx_bytes, rx_msgs, rx_bytes, tx_errors, rx_errors, tx_eagain;
+  uint64_t pull_tx, pull_rx; /* messages that went through the large-message pull path (also counted above) */
 } umq_io_stats_t;
 typedef struct umq_fc_stats {
   uint64_t credits_local, credits_remote, credits_granted, credits_returned, stalls, window;

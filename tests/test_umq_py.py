@@ -258,3 +258,33 @@ def test_transport_table_serves_queues_by_mode(pair):
     finally:
         x.close()
         y.close()
+
+
+def test_large_messages_are_pulled_by_the_receiver_and_keep_their_place(pair):
+    """A message that does not fit the peer's receive buffers (8 KB blocks here) travels as a descriptor and the
+    receiver reads it from the sender's memory; delivery order and flow control are the same as for small ones."""
+    umq, a, b = pair
+    big = [bytes([i + 1]) * (100_000 + 4321 * i) for i in range(4)] + [os.urandom(3 << 20)]
+    order = []
+    for i, m in enumerate(big):
+        a.send(b"before %d" % i)
+        a.send(m)
+        a.send(b"after %d" % i)
+        order += [b"before %d" % i, m, b"after %d" % i]
+    for want in order:
+        got = b.recv()
+        assert got == want, (len(got or b""), len(want))
+    assert b.recv(timeout_s=0.05) is None
+    sa, sb = a.io_stats(), b.io_stats()
+    assert sa["pull_tx"] == len(big) and sb["pull_rx"] == len(big) and sa["pull_rx"] == 0
+    assert sa["tx_msgs"] == len(order) and sb["rx_msgs"] == len(order)
+    assert sb["rx_bytes"] == sum(map(len, order)) and sa["tx_errors"] == 0 and sb["rx_errors"] == 0
+    # more large messages than the queue depth, both directions at once: credits and buffers come back
+    for i in range(40):
+        a.send(bytes([i]) * 20_000)
+        b.send(bytes([255 - i]) * 30_000)
+        assert b.recv() == bytes([i]) * 20_000
+        assert a.recv() == bytes([255 - i]) * 30_000
+    pool = umq.qbuf_stats() if hasattr(umq, "qbuf_stats") else None
+    if pool:
+        assert pool["alloc_failures"] == 0

@@ -48,7 +48,8 @@ _Buf._fields_ = [("qbuf_next", ctypes.POINTER(_Buf)), ("umqh", ctypes.c_uint64),
 
 class _IoStats(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in
-                ("tx_msgs", "tx_bytes", "rx_msgs", "rx_bytes", "tx_errors", "rx_errors", "tx_eagain")]
+                ("tx_msgs", "tx_bytes", "rx_msgs", "rx_bytes", "tx_errors", "rx_errors", "tx_eagain", "pull_tx",
+                 "pull_rx")]
 
 
 class _FcStats(ctypes.Structure):
