@@ -24,6 +24,7 @@
 #include <thread>
 #include <mutex>
 #include <random>
+#include <shared_mutex>
 #include <unordered_map>
 #include <unordered_set>
 #include <vector>
@@ -34,7 +35,8 @@
 
 namespace {
 
-// immediate data layout: [63:56] type, [55:32] credits returned, [31:0] message bytes
+// immediate data layout: [63:56] type, [55:40] credits returned, [39:24] sub-queue the message is for (0 = the
+// queue that owns the endpoint), [23:0] message bytes or the cookie of a pull message
 // IMM_PULL_REQ: the payload is a PullDesc - the message itself stays in the sender's memory and the receiver fetches
 // it with a one-sided read (messages larger than the peer's receive buffers); IMM_PULL_DONE / IMM_PULL_FAIL: the
 // receiver is through with the read (low 32 bits = the descriptor's cookie), the sender's buffer completes.
@@ -45,9 +47,13 @@ struct PullDesc {
   uint8_t seg[URMA_SIMPLE_SEG_BLOB];
 };
 constexpr uint32_t kPullMagic = 0x50554c4c;   // "PULL"
-inline uint64_t imm_make(ImmType t, uint32_t credits, uint32_t bytes) {
-  return (uint64_t(t) << 56) | (uint64_t(credits & 0xffffff) << 32) | bytes;
+inline uint64_t imm_make(ImmType t, uint32_t credits, uint32_t bytes, uint32_t dst_sub = 0) {
+  return (uint64_t(t) << 56) | (uint64_t(credits & 0xffff) << 40) | (uint64_t(dst_sub & 0xffff) << 24) |
+         (bytes & 0xffffff);
 }
+inline uint32_t imm_credits(uint64_t imm) { return static_cast<uint32_t>((imm >> 40) & 0xffff); }
+inline uint32_t imm_sub(uint64_t imm) { return static_cast<uint32_t>((imm >> 24) & 0xffff); }
+inline uint32_t imm_low(uint64_t imm) { return static_cast<uint32_t>(imm & 0xffffff); }
 
 struct Block {
   umq_buf_t meta;  // must be first: umq_buf_t* <-> Block*
@@ -285,6 +291,24 @@ struct Queue {
   };
   std::unordered_map<uint32_t, PullTx> pull_tx;    // by cookie
   std::unordered_map<uint64_t, PullRx> pull_rx;    // by read id
+  // main / sub queues. A sub queue has no endpoint: it receives through its main queue's shared receive buffers
+  // (the sender names it in the immediate data) and sends through an endpoint borrowed from the jetty pool.
+  // Lock order: a sub queue's `mu`, then a main queue's `mu`; a main queue reaches its subs only through `inbox`.
+  Queue* main = nullptr;            // sub queue: the queue whose receive side it shares
+  uint32_t sub_id = 0;              // sub queue: its number inside the main queue (travels in the bind information)
+  uint32_t peer_sub = 0;            // destination number for what this queue sends (0: the peer is a plain queue)
+  std::unordered_map<uint32_t, Queue*> subs;   // main queue: sub queues by number (under mu)
+  uint32_t next_sub = 1;
+  bool in_pool = false;             // main queue: its endpoint serves the jetty pool
+  struct Event {
+    int kind;                       // 0 receive, 1 read done, 2 send done
+    int st;
+    uint64_t uc;
+    uint32_t len;
+    uint64_t imm;
+  };
+  std::mutex inbox_mu;              // leaf lock
+  std::vector<Event> inbox;         // completions another queue's progress found for this one
 };
 constexpr uint64_t kRxPending = 1;   // umq_buf_t::rsvd[1] of a queued receive whose data is still being read
 
@@ -293,6 +317,7 @@ Queue* find(uint64_t h) {
   auto it = g.queues.find(h);
   return it == g.queues.end() ? nullptr : it->second;
 }
+Queue* find_nolock_order(uint64_t h) { return find(h); }
 
 // ------------------------------------------------------------------------------------------------ buffers
 Block* block_new(uint32_t cap, bool huge) {
@@ -495,13 +520,57 @@ void refill_rx(Queue* q) {
   }
 }
 
+// -------------------------------------------------------------------------------------------------- jetty pool
+// Endpoints of main queues created with UMQ_CREATE_FLAG_SHARE_TRANSPORT. A sub queue borrows one for each message it
+// posts (time division at message granularity: any jetty can send to any imported target), so thousands of sub
+// queues need only as many jetties as there are main queues. Reference: src/urpc/umq/umq_ub/core/jetty_pool/
+// umq_ub_jetty_pool.h:64-102 (shared nodes, availability notification, alloc / free / miss counters).
+struct JettyPool {
+  std::shared_mutex mu;              // shared: posting through a member; exclusive: members join / leave
+  std::vector<Queue*> members;
+  std::atomic<uint64_t> allocs{0}, misses{0}, errs{0};
+  int efd = -1;                      // counts up whenever a member joins (a jetty became available)
+};
+JettyPool g_jpool;
+
+// Posts a work request for `q`: on its own endpoint, or - for a sub queue - on a borrowed one. The caller holds
+// q->mu (and, for a queue with an endpoint, nothing else).
+int q_post(Queue* q, int opcode, urma_target_seg_t* rseg, uint64_t raddr, uint64_t laddr, uint32_t len, uint64_t imm,
+           uint64_t uc, int signaled) {
+  if (q->ep) return urma_simple_post(q->ep, q->peer, opcode, rseg, raddr, nullptr, laddr, len, imm, uc, signaled);
+  static thread_local size_t cursor = 0;   // each thread keeps returning to the member that served it last
+  std::shared_lock<std::shared_mutex> pl(g_jpool.mu);
+  const size_t n = g_jpool.members.size();
+  int rc = URMA_EAGAIN;
+  for (size_t k = 0; k <= n; ++k) {
+    // the pool's members in turn, the queue's own main queue as the last resort (it need not be a member)
+    Queue* m = k < n ? g_jpool.members[(cursor + k) % n] : q->main;
+    if (k == n && m->in_pool) break;
+    if (m->state.load() == UMQ_STATE_ERR) {
+      g_jpool.errs.fetch_add(1, std::memory_order_relaxed);
+      continue;
+    }
+    std::lock_guard<std::mutex> ml(m->mu);
+    rc = urma_simple_post(m->ep, q->peer, opcode, rseg, raddr, nullptr, laddr, len, imm, uc, signaled);
+    if (rc == 0) {
+      if (k < n) cursor = (cursor + k) % n;
+      g_jpool.allocs.fetch_add(1, std::memory_order_relaxed);
+      return 0;
+    }
+    g_jpool.misses.fetch_add(1, std::memory_order_relaxed);   // its send queue is full: try the next one
+  }
+  return rc;
+}
+// Read ids name the queue that issued the read (a borrowed endpoint's owner sees the completion first).
+inline uint64_t read_id(Queue* q) { return (((q->h & 0x7fffffffffull) << 24 | (q->next_read++ & 0xffffff)) << 1) | 1; }
+inline uint64_t read_id_owner(uint64_t id) { return (id >> 25) & 0x7fffffffffull; }
+
 void send_credit_return(Queue* q) {
   if (!q->fc || !q->peer || q->to_return == 0) return;
-  const uint32_t n = q->to_return;
+  const uint32_t n = std::min<uint32_t>(q->to_return, 0xffff);
   // zero-length control message; it does not consume a credit on the other side's window accounting
-  if (urma_simple_post(q->ep, q->peer, URMA_OPC_SEND_IMM, nullptr, 0, nullptr, 0, 0, imm_make(IMM_FC_RETURN, n, 0),
-                       0, 0) == 0) {
-    q->to_return = 0;
+  if (q_post(q, URMA_OPC_SEND_IMM, nullptr, 0, 0, 0, imm_make(IMM_FC_RETURN, n, 0, q->peer_sub), 0, 0) == 0) {
+    q->to_return -= n;
     q->fcs.credits_returned += n;
   }
 }
@@ -511,13 +580,13 @@ void send_credit_return(Queue* q) {
 // and only a descriptor travels. The block stays in flight until the receiver reports the end of its read.
 // Reference: the UB_PLUS transport's pull of large messages (src/urpc/umq/umq_ub/core/private/umq_pro_ub.c).
 void pull_control(Queue* q, ImmType t, uint32_t cookie) {
-  urma_simple_post(q->ep, q->peer, URMA_OPC_SEND_IMM, nullptr, 0, nullptr, 0, 0, imm_make(t, 0, cookie), 0, 0);
+  q_post(q, URMA_OPC_SEND_IMM, nullptr, 0, 0, 0, imm_make(t, 0, cookie, q->peer_sub), 0, 0);
 }
 int pull_send(Queue* q, Block* b, uint32_t piggy) {
   PullDesc d{};
   d.magic = kPullMagic;
-  d.cookie = q->next_cookie++;
-  if (q->next_cookie == 0) q->next_cookie = 1;
+  d.cookie = q->next_cookie;
+  q->next_cookie = q->next_cookie % 0xffffff + 1;   // 24 bits of the immediate data, never 0
   static thread_local std::mt19937 rng{std::random_device{}()};
   d.token = static_cast<uint32_t>(rng()) | 1u;   // one read permission per message
   d.len = b->meta.data_size;
@@ -532,9 +601,8 @@ int pull_send(Queue* q, Block* b, uint32_t piggy) {
   buf_setup(db, q->h, sizeof(PullDesc));
   memcpy(db->mem, &d, sizeof(d));
   db->meta.rsvd[0] = 0;   // the descriptor's own block returns to the pool when its send completes
-  const int rc = urma_simple_post(q->ep, q->peer, URMA_OPC_SEND_IMM, nullptr, 0, nullptr,
-                                  reinterpret_cast<uint64_t>(db->mem), sizeof(PullDesc),
-                                  imm_make(IMM_PULL_REQ, piggy, sizeof(PullDesc)), reinterpret_cast<uint64_t>(db), 1);
+  const int rc = q_post(q, URMA_OPC_SEND_IMM, nullptr, 0, reinterpret_cast<uint64_t>(db->mem), sizeof(PullDesc),
+                        imm_make(IMM_PULL_REQ, piggy, sizeof(PullDesc), q->peer_sub), reinterpret_cast<uint64_t>(db), 1);
   if (rc != 0) {
     block_put(db);
     urma_unregister_seg(seg);
@@ -548,7 +616,7 @@ int pull_send(Queue* q, Block* b, uint32_t piggy) {
 }
 // The receiver finished (or gave up) its read: the message's buffer completes like any other send.
 void pull_finish_tx(Queue* q, uint64_t imm, uint64_t type) {
-  auto it = q->pull_tx.find(static_cast<uint32_t>(imm));
+  auto it = q->pull_tx.find(imm_low(imm));
   if (it == q->pull_tx.end()) return;
   Block* b = it->second.block;
   urma_unregister_seg(it->second.seg);
@@ -574,10 +642,9 @@ void pull_start_rx(Queue* q, Block* db, uint32_t len) {
   }
   Block* dst = block_get(d.len);
   urma_target_seg_t* rseg = dst ? urma_simple_seg_import(g.ctx, d.seg, d.token) : nullptr;
-  const uint64_t id = (q->next_read++ << 1) | 1;
+  const uint64_t id = read_id(q);
   if (!dst || !rseg ||
-      urma_simple_post(q->ep, q->peer, URMA_OPC_READ, rseg, d.addr, nullptr, reinterpret_cast<uint64_t>(dst->mem), d.len, 0,
-                       id, 1) != 0) {
+      q_post(q, URMA_OPC_READ, rseg, d.addr, reinterpret_cast<uint64_t>(dst->mem), d.len, 0, id, 1) != 0) {
     if (rseg) urma_unimport_seg(rseg);
     if (dst) block_put(dst);
     ++q->io.rx_errors;
@@ -616,8 +683,91 @@ bool pull_finish_rx(Queue* q, uint64_t id, int status) {
   return true;
 }
 
-// drains the completion queue of the endpoint into rx_ready / tx_done; caller holds q->mu
+// One completion, applied to the queue it belongs to. Caller holds q->mu.
+void handle_event(Queue* q, const Queue::Event& e) {
+  if (e.kind == 0) {   // a message arrived in block e.uc
+    Block* b = reinterpret_cast<Block*>(e.uc);
+    const uint64_t type = e.imm >> 56;
+    const uint32_t credits = imm_credits(e.imm);
+    if (credits) {
+      q->credits += credits;
+      q->fcs.credits_granted += credits;
+    }
+    if ((type == IMM_PULL_DONE || type == IMM_PULL_FAIL) && e.st == 0) pull_finish_tx(q, e.imm, type);
+    if (type == IMM_FC_RETURN || type == IMM_PULL_DONE || type == IMM_PULL_FAIL || e.st != 0) {
+      if (e.st != 0) ++q->io.rx_errors;
+      else if (q->ep) ++q->fc_skip;
+      block_put(b);  // control message or failed receive: the buffer goes straight back
+      return;
+    }
+    if (!q->ep && q->fc) ++q->to_return;   // sub queue: the main queue re-posts the buffer, the credit is ours to give
+    if (type == IMM_PULL_REQ) {   // a descriptor: fetch the message it names, keep its place in the order
+      pull_start_rx(q, b, e.len);
+      block_put(b);
+      return;
+    }
+    b->meta.umqh = q->h;
+    b->meta.data_size = e.len;
+    b->meta.total_data_size = e.len;
+    b->meta.status = UMQ_BUF_OK;
+    q->rx_ready.push_back(&b->meta);
+    ++q->io.rx_msgs;
+    q->io.rx_bytes += e.len;
+  } else if (e.kind == 1) {
+    // a one-sided read: one of the pull path's, or one the application issued with umq_remote_read
+    if (!pull_finish_rx(q, e.uc, e.st)) q->read_done[e.uc] = e.st;
+  } else {
+    Block* b = reinterpret_cast<Block*>(e.uc);
+    q->in_flight.erase(b);
+    b->meta.status = e.st == 0 ? UMQ_BUF_OK : UMQ_BUF_SEND_ERR;
+    if (e.st != 0) {
+      ++q->io.tx_errors;
+      if (q->state.exchange(UMQ_STATE_ERR) != UMQ_STATE_ERR) {
+        g_log.log(ub::kLogErr, "queue %llu (%s): send completed with status %d, queue set to ERR",
+                  (unsigned long long)q->h, q->opt.name, e.st);
+        push_event(UMQ_EVENT_QH_ERR, q->h, e.st);
+      }
+    }
+    if (b->meta.rsvd[0]) q->tx_done.push_back(&b->meta);  // pro API: hand back through poll(TX)
+    else block_put(b);
+  }
+}
+// Hands a completion to another queue (found while polling this one's endpoint). False: that queue is gone.
+bool forward_event(Queue* to, const Queue::Event& e) {
+  if (!to) return false;
+  std::lock_guard<std::mutex> l(to->inbox_mu);
+  to->inbox.push_back(e);
+  return true;
+}
+
+// Drains the completion queue of the endpoint; caller holds q->mu. What belongs to this queue is applied at once,
+// what belongs to a sub queue (or to a queue that borrowed the endpoint) goes to that queue's inbox. A sub queue
+// drives its main queue's endpoint first and then empties its own inbox.
 void progress(Queue* q) {
+  if (!q->ep) {
+    if (q->main) {
+      std::lock_guard<std::mutex> ml(q->main->mu);
+      progress(q->main);
+    }
+    if (!q->in_flight.empty() || !q->pull_rx.empty()) {
+      // work of this queue is outstanding on borrowed endpoints: their completions surface only when the owner's
+      // completion queue is polled, and the owner may be idle
+      std::shared_lock<std::shared_mutex> pl(g_jpool.mu);
+      for (Queue* m : g_jpool.members) {
+        if (m == q->main) continue;
+        std::unique_lock<std::mutex> ml(m->mu, std::try_to_lock);   // busy = its own thread is polling it right now
+        if (ml.owns_lock()) progress(m);
+      }
+    }
+    std::vector<Queue::Event> evs;
+    {
+      std::lock_guard<std::mutex> l(q->inbox_mu);
+      evs.swap(q->inbox);
+    }
+    for (auto& e : evs) handle_event(q, e);
+    if (q->fc && q->to_return >= std::max<uint32_t>(1, q->window / 4)) send_credit_return(q);
+    return;
+  }
   int st[32];
   uint64_t uc[32], imm[32];
   uint32_t len[32], flag[32];
@@ -625,54 +775,43 @@ void progress(Queue* q) {
     const int n = urma_simple_poll(q->ep, 32, st, uc, len, imm, flag);
     if (n <= 0) break;
     for (int i = 0; i < n; ++i) {
+      Queue::Event e{0, st[i], uc[i], len[i], imm[i]};
       if (flag[i] & URMA_CR_FLAG_RECV) {
         Block* b = reinterpret_cast<Block*>(uc[i]);
         --q->rx_posted;
         q->in_flight.erase(b);
-        const uint64_t type = imm[i] >> 56;
-        const uint32_t credits = static_cast<uint32_t>((imm[i] >> 32) & 0xffffff);
-        if (credits) {
-          q->credits += credits;
-          q->fcs.credits_granted += credits;
-        }
-        if ((type == IMM_PULL_DONE || type == IMM_PULL_FAIL) && st[i] == 0) pull_finish_tx(q, imm[i], type);
-        if (type == IMM_FC_RETURN || type == IMM_PULL_DONE || type == IMM_PULL_FAIL || st[i] != 0) {
-          if (st[i] != 0) ++q->io.rx_errors;
-          else ++q->fc_skip;
-          block_put(b);  // control message or failed receive: the buffer goes straight back
+        const uint32_t dst = imm_sub(imm[i]);
+        if (dst == 0) {
+          handle_event(q, e);
           continue;
         }
-        if (type == IMM_PULL_REQ) {   // a descriptor: fetch the message it names, keep its place in the order
-          pull_start_rx(q, b, len[i]);
+        // for a sub queue: the buffer that replaces this one grants nothing to this queue's own peer
+        if (q->fc) ++q->fc_skip;
+        auto it = q->subs.find(dst);
+        if (it == q->subs.end() || !forward_event(it->second, e)) {
+          ++q->io.rx_errors;   // nobody of that number (any more)
           block_put(b);
-          continue;
         }
-        b->meta.data_size = len[i];
-        b->meta.total_data_size = len[i];
-        b->meta.status = UMQ_BUF_OK;
-        q->rx_ready.push_back(&b->meta);
-        ++q->io.rx_msgs;
-        q->io.rx_bytes += len[i];
-      } else if (uc[i] & 1) {
-        // a one-sided read (buffer descriptors are aligned, so their low bit is 0): one of the pull path's, or one
-        // the application issued with umq_remote_read
-        if (!pull_finish_rx(q, uc[i], st[i])) q->read_done[uc[i]] = st[i];
+      } else if (uc[i] & 1) {   // reads carry odd ids (buffer descriptors are aligned, so their low bit is 0)
+        e.kind = 1;
+        const uint64_t owner = read_id_owner(uc[i]);
+        if (owner == (q->h & 0x7fffffffffull)) handle_event(q, e);
+        else forward_event(find_nolock_order(owner), e);
       } else if (uc[i] != 0) {
+        e.kind = 2;
         Block* b = reinterpret_cast<Block*>(uc[i]);
-        q->in_flight.erase(b);
-        b->meta.status = st[i] == 0 ? UMQ_BUF_OK : UMQ_BUF_SEND_ERR;
-        if (st[i] != 0) {
-          ++q->io.tx_errors;
-          if (q->state.exchange(UMQ_STATE_ERR) != UMQ_STATE_ERR) {
-            g_log.log(ub::kLogErr, "queue %llu (%s): send completed with status %d, queue set to ERR",
-                      (unsigned long long)q->h, q->opt.name, st[i]);
-            push_event(UMQ_EVENT_QH_ERR, q->h, st[i]);
-          }
-        }
-        if (b->meta.rsvd[0]) q->tx_done.push_back(&b->meta);  // pro API: hand back through poll(TX)
-        else block_put(b);
+        if (b->meta.umqh == q->h) handle_event(q, e);
+        else if (!forward_event(find_nolock_order(b->meta.umqh), e)) block_put(b);   // its queue was destroyed
       }
     }
+  }
+  {   // completions that the owner of another endpoint found for this queue
+    std::vector<Queue::Event> evs;
+    {
+      std::lock_guard<std::mutex> l(q->inbox_mu);
+      evs.swap(q->inbox);
+    }
+    for (auto& e : evs) handle_event(q, e);
   }
   refill_rx(q);
   if (q->fc && q->to_return >= std::max<uint32_t>(1, q->window / 4)) send_credit_return(q);
@@ -695,8 +834,9 @@ int send_one(Queue* q, umq_buf_t* buf, bool pro) {
   b->meta.rsvd[0] = pro ? 1 : 0;
   uint32_t piggy = 0;
   if (q->fc && q->to_return) {
-    piggy = q->to_return;
+    piggy = std::min<uint32_t>(q->to_return, 0xffff);
   }
+  b->meta.umqh = q->h;   // the completion finds its queue by this (the endpoint may be a borrowed one)
   if (q->peer_rx_buf && buf->data_size > q->peer_rx_buf) {   // does not fit over there: the peer pulls it
     const int prc = pull_send(q, b, piggy);
     if (prc != UMQ_SUCCESS) {
@@ -705,16 +845,15 @@ int send_one(Queue* q, umq_buf_t* buf, bool pro) {
     }
     if (piggy) {
       q->fcs.credits_returned += piggy;
-      q->to_return = 0;
+      q->to_return -= piggy;
     }
     if (q->fc) --q->credits;
     ++q->io.tx_msgs;
     q->io.tx_bytes += buf->data_size;
     return UMQ_SUCCESS;
   }
-  const int rc = urma_simple_post(q->ep, q->peer, URMA_OPC_SEND_IMM, nullptr, 0, nullptr,
-                                  reinterpret_cast<uint64_t>(buf->buf_data), buf->data_size,
-                                  imm_make(IMM_IO, piggy, buf->data_size), reinterpret_cast<uint64_t>(b), 1);
+  const int rc = q_post(q, URMA_OPC_SEND_IMM, nullptr, 0, reinterpret_cast<uint64_t>(buf->buf_data), buf->data_size,
+                        imm_make(IMM_IO, piggy, buf->data_size, q->peer_sub), reinterpret_cast<uint64_t>(b), 1);
   if (rc != 0) {
     ++q->io.tx_eagain;
     return rc == URMA_EAGAIN ? UMQ_ERR_EAGAIN : UMQ_FAIL;
@@ -722,7 +861,7 @@ int send_one(Queue* q, umq_buf_t* buf, bool pro) {
   q->in_flight.insert(b);
   if (piggy) {
     q->fcs.credits_returned += piggy;
-    q->to_return = 0;
+    q->to_return -= piggy;
   }
   if (q->fc) --q->credits;
   ++q->io.tx_msgs;
@@ -734,6 +873,7 @@ struct BindBlob {
   uint32_t magic, rx_buf_size, rx_depth, fc;
   uint8_t jetty[URMA_SIMPLE_JETTY_BLOB];
   uint32_t token;
+  uint32_t sub_id;   // 0: a queue with its own endpoint; else the sub queue's number inside the queue that owns `jetty`
 };
 
 }  // namespace
@@ -866,7 +1006,10 @@ void umq_uninit(void) {
   {
     std::lock_guard<std::mutex> l(g.mu);
     if (!g.inited) return;
-    for (auto& kv : g.queues) hs.push_back(kv.first);
+    for (auto& kv : g.queues)
+      if (!kv.second->tops && !kv.second->ep) hs.push_back(kv.first);   // sub queues before their main queues
+    for (auto& kv : g.queues)
+      if (kv.second->tops || kv.second->ep) hs.push_back(kv.first);
   }
   for (uint64_t h : hs) umq_destroy(h);
   std::lock_guard<std::mutex> l(g.mu);
@@ -910,6 +1053,33 @@ uint64_t umq_create(const umq_create_option_t* opt) {
     return q->h;
   }
   q->fc = (g.cfg.feature & UMQ_FEATURE_FLOW_CONTROL) != 0;
+  if (opt->create_flag & UMQ_CREATE_FLAG_SUB) {
+    // no endpoint: receives through the main queue's buffers, sends through the jetty pool
+    Queue* m = find(opt->share_rq_umqh);
+    if (!m || !m->ep || !(m->opt.create_flag & UMQ_CREATE_FLAG_MAIN)) {
+      g_log.log(ub::kLogErr, "umq_create: share_rq_umqh does not name a main queue");
+      delete q;
+      return UMQ_INVALID_HANDLE;
+    }
+    q->main = m;
+    q->opt.rx_buf_size = m->opt.rx_buf_size;
+    q->h = g.next_h.fetch_add(1);
+    {
+      std::lock_guard<std::mutex> l(m->mu);
+      if (m->subs.size() >= 0xfffe) {
+        delete q;
+        return UMQ_INVALID_HANDLE;
+      }
+      do {
+        q->sub_id = m->next_sub;
+        m->next_sub = m->next_sub % 0xffff + 1;
+      } while (m->subs.count(q->sub_id));
+      m->subs[q->sub_id] = q;
+    }
+    std::lock_guard<std::mutex> l(g.mu);
+    g.queues[q->h] = q;
+    return q->h;
+  }
   // the jetty must hold the data messages plus the occasional credit-return message
   q->ep = urma_simple_ep_create(g.ctx, q->opt.rx_depth + q->opt.tx_depth + 16, opt->token,
                                 opt->mode == UMQ_MODE_INTERRUPT);
@@ -923,8 +1093,21 @@ uint64_t umq_create(const umq_create_option_t* opt) {
     refill_rx(q);
     q->to_return = 0;  // the initial window travels in the bind blob
   }
-  std::lock_guard<std::mutex> l(g.mu);
-  g.queues[q->h] = q;
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    g.queues[q->h] = q;
+  }
+  if ((opt->create_flag & UMQ_CREATE_FLAG_MAIN) && (opt->create_flag & UMQ_CREATE_FLAG_SHARE_TRANSPORT)) {
+    std::unique_lock<std::shared_mutex> pl(g_jpool.mu);
+    g_jpool.members.push_back(q);
+    q->in_pool = true;
+    if (g_jpool.efd >= 0) {   // a jetty became available
+      const uint64_t one = 1;
+      if (write(g_jpool.efd, &one, sizeof(one)) < 0) {
+        // counter saturated: readable anyway
+      }
+    }
+  }
   return q->h;
 }
 
@@ -935,7 +1118,32 @@ int umq_destroy(uint64_t h) {
     auto it = g.queues.find(h);
     if (it == g.queues.end()) return UMQ_ERR_EINVAL;
     q = it->second;
+    if (!q->tops && q->ep) {   // a main queue goes after its sub queues
+      std::lock_guard<std::mutex> ql(q->mu);
+      if (!q->subs.empty()) return UMQ_ERR_ESTATE;
+    }
     g.queues.erase(it);
+  }
+  if (!q->tops && q->in_pool) {
+    std::unique_lock<std::shared_mutex> pl(g_jpool.mu);   // waits for posts that borrowed the endpoint
+    auto& v = g_jpool.members;
+    v.erase(std::remove(v.begin(), v.end(), q), v.end());
+  }
+  if (!q->tops && !q->ep) {   // sub queue
+    {
+      std::lock_guard<std::mutex> ml(q->main->mu);
+      q->main->subs.erase(q->sub_id);
+    }
+    for (auto& e : q->inbox)
+      if (e.kind != 1) block_put(reinterpret_cast<Block*>(e.uc));
+    for (auto& kv : q->pull_tx) urma_unregister_seg(kv.second.seg);
+    for (auto* b : q->rx_ready) block_put(reinterpret_cast<Block*>(b));
+    for (auto* b : q->tx_done) block_put(reinterpret_cast<Block*>(b));
+    if (q->peer) urma_unimport_jetty(q->peer);
+    // blocks still in flight complete on the endpoint that carried them; its owner returns them to the pool when
+    // it finds that their queue is gone
+    delete q;
+    return UMQ_SUCCESS;
   }
   if (q->tops) {
     q->tops->destroy(q->tpriv);
@@ -965,8 +1173,9 @@ uint32_t umq_bind_info_get(uint64_t h, uint8_t* out, uint32_t size) {
   b.rx_buf_size = q->opt.rx_buf_size;
   b.rx_depth = q->opt.rx_depth;
   b.fc = q->fc;
-  b.token = q->opt.token;
-  urma_simple_ep_blob(q->ep, b.jetty);
+  b.token = q->ep ? q->opt.token : q->main->opt.token;
+  b.sub_id = q->sub_id;
+  urma_simple_ep_blob(q->ep ? q->ep : q->main->ep, b.jetty);
   memcpy(out, &b, sizeof(b));
   return sizeof(b);
 }
@@ -987,6 +1196,7 @@ int umq_bind(uint64_t h, const uint8_t* info, uint32_t size) {
   q->peer = urma_simple_ep_import(g.ctx, b.jetty, b.token);
   if (!q->peer) return UMQ_FAIL;
   q->fc = q->fc && b.fc;
+  q->peer_sub = b.sub_id;
   q->peer_rx_buf = b.rx_buf_size;
   q->window = b.rx_depth;
   q->credits = b.rx_depth;  // one credit per receive buffer the peer has posted
@@ -1157,6 +1367,7 @@ int umq_post(uint64_t h, umq_buf_t* qbuf, umq_io_direction_t dir, umq_buf_t** ba
     }
     return plugin_send_chain(q, qbuf, bad);
   }
+  if (dir == UMQ_IO_RX && !q->ep) return UMQ_ERR_EINVAL;   // a sub queue's receive buffers are its main queue's
   std::lock_guard<std::mutex> l(q->mu);
   if (dir == UMQ_IO_RX) {
     // application-provided receive buffers (instead of the automatic refill)
@@ -1216,29 +1427,31 @@ int umq_poll(uint64_t h, umq_io_direction_t dir, umq_buf_t** bufs, uint32_t max)
   return static_cast<int>(n);
 }
 
+// The endpoint whose completion channel wakes the queue: its own, or its main queue's.
+static urma_simple_ep_t* event_ep(Queue* q) { return q->ep ? q->ep : (q->main ? q->main->ep : nullptr); }
 int umq_rearm_interrupt(uint64_t h, int, umq_io_direction_t) {
   Queue* q = find(h);
-  if (!q) return UMQ_ERR_EINVAL;
-  return urma_rearm_jfc(urma_simple_ep_jfc(q->ep), false) == URMA_SUCCESS ? UMQ_SUCCESS : UMQ_FAIL;
+  if (!q || !event_ep(q)) return UMQ_ERR_EINVAL;
+  return urma_rearm_jfc(urma_simple_ep_jfc(event_ep(q)), false) == URMA_SUCCESS ? UMQ_SUCCESS : UMQ_FAIL;
 }
 int umq_wait_interrupt(uint64_t h, int timeout_ms) {
   Queue* q = find(h);
-  if (!q) return UMQ_ERR_EINVAL;
-  urma_jfc_t* jfc = urma_simple_ep_jfc(q->ep);
+  if (!q || !event_ep(q)) return UMQ_ERR_EINVAL;
+  urma_jfc_t* jfc = urma_simple_ep_jfc(event_ep(q));
   if (!jfc->cfg.jfce) return UMQ_ERR_EINVAL;
   urma_jfc_t* fired[1];
   return urma_wait_jfc(jfc->cfg.jfce, 1, timeout_ms, fired);
 }
 void umq_ack_interrupt(uint64_t h, uint32_t nevents) {
   Queue* q = find(h);
-  if (!q) return;
-  urma_jfc_t* jfc = urma_simple_ep_jfc(q->ep);
+  if (!q || !event_ep(q)) return;
+  urma_jfc_t* jfc = urma_simple_ep_jfc(event_ep(q));
   urma_ack_jfc(&jfc, &nevents, 1);
 }
 int umq_interrupt_fd_get(uint64_t h) {
   Queue* q = find(h);
-  if (!q) return -1;
-  urma_jfc_t* jfc = urma_simple_ep_jfc(q->ep);
+  if (!q || !event_ep(q)) return -1;
+  urma_jfc_t* jfc = urma_simple_ep_jfc(event_ep(q));
   return jfc->cfg.jfce ? jfc->cfg.jfce->fd : -1;
 }
 
@@ -1379,7 +1592,7 @@ int umq_mem_seg_unregister(uint64_t seg_h) {
 int umq_remote_read(uint64_t h, const uint8_t* seg_blob, uint32_t token, uint64_t remote_addr, void* local,
                     uint32_t len, int timeout_ms) {
   Queue* q = find(h);
-  if (!q || !seg_blob || !local || !len) return UMQ_ERR_EINVAL;
+  if (!q || !q->ep || !seg_blob || !local || !len) return UMQ_ERR_EINVAL;   // queues with an endpoint of their own
   uint64_t id;
   {
     std::lock_guard<std::mutex> l(q->mu);
@@ -1391,7 +1604,7 @@ int umq_remote_read(uint64_t h, const uint8_t* seg_blob, uint32_t token, uint64_
       q->imported.erase(key);
       return UMQ_ERR_EINVAL;
     }
-    id = (q->next_read++ << 1) | 1;
+    id = read_id(q);
     if (urma_simple_post(q->ep, q->peer, URMA_OPC_READ, rseg, remote_addr, nullptr, reinterpret_cast<uint64_t>(local),
                          len, 0, id, 1) != 0)
       return UMQ_FAIL;
@@ -1687,6 +1900,25 @@ int umq_transport_pool_eventfd_get(uint64_t pool) {
   return it == g_tp_pools.end() ? -1 : it->second.efd;
 }
 // Polls the member queues once; returns how many have messages ready and signals the pool's eventfd if any has.
+int umq_jetty_pool_stats_get(umq_jetty_pool_stats_t* out) {
+  if (!out) return UMQ_ERR_EINVAL;
+  memset(out, 0, sizeof(*out));
+  {
+    std::shared_lock<std::shared_mutex> pl(g_jpool.mu);
+    out->total_num = g_jpool.members.size();
+    for (Queue* m : g_jpool.members) out->err_num += m->state.load() == UMQ_STATE_ERR;
+  }
+  out->acc_alloc_num = out->acc_free_num = g_jpool.allocs.load();
+  out->acc_miss_num = g_jpool.misses.load();
+  std::lock_guard<std::mutex> l(g.mu);
+  for (auto& kv : g.queues) out->sub_queues += !kv.second->tops && !kv.second->ep;
+  return UMQ_SUCCESS;
+}
+int umq_jetty_pool_eventfd_get(void) {
+  std::unique_lock<std::shared_mutex> pl(g_jpool.mu);
+  if (g_jpool.efd < 0) g_jpool.efd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+  return g_jpool.efd;
+}
 int umq_stats_transport_pool_get(uint64_t pool, umq_transport_pool_stats_t* out) {
   std::vector<uint64_t> qs;
   int efd;

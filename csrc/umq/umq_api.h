@@ -49,7 +49,28 @@ typedef struct umq_create_option {
   umq_queue_mode_t mode;
   uint32_t token;
   uint32_t transport; /* 0 = the transport mode given to umq_init, else (umq_trans_mode_t value + 1) for this queue */
+  uint32_t create_flag;   /* UMQ_CREATE_FLAG_* */
+  uint64_t share_rq_umqh; /* UMQ_CREATE_FLAG_SUB: the main queue whose receive buffers this queue shares */
 } umq_create_option_t;
+/* Main and sub queues. A MAIN queue is an ordinary queue that can also host sub queues; with SHARE_TRANSPORT its
+ * endpoint joins the jetty pool. A SUB queue has no endpoint of its own: messages for it arrive in the main queue's
+ * receive buffers (rx_depth and rx_buf_size are the main queue's, shared by all its sub queues) and it sends through
+ * an endpoint borrowed from the pool, message by message - so a process with thousands of connections needs
+ * receive buffers and jetties for its main queues only. A sub queue binds like any queue (to a plain queue, a main
+ * queue or another sub queue); the main queue must be destroyed after its sub queues. */
+#define UMQ_CREATE_FLAG_MAIN 1u
+#define UMQ_CREATE_FLAG_SHARE_TRANSPORT 2u
+#define UMQ_CREATE_FLAG_SUB 4u
+typedef struct umq_jetty_pool_stats {
+  uint64_t total_num;     /* endpoints in the pool */
+  uint64_t err_num;       /* of which in the ERR state right now */
+  uint64_t acc_alloc_num; /* posts that borrowed an endpoint */
+  uint64_t acc_free_num;  /* ... and gave it back (an endpoint is held for one post) */
+  uint64_t acc_miss_num;  /* attempts that found an endpoint's send queue full and moved on */
+  uint64_t sub_queues;    /* sub queues alive */
+} umq_jetty_pool_stats_t;
+UMQ_EXPORT int umq_jetty_pool_stats_get(umq_jetty_pool_stats_t* out);
+UMQ_EXPORT int umq_jetty_pool_eventfd_get(void); /* becomes readable when an endpoint joins the pool */
 
 /* Message buffer. `buf_data` points `headroom_size` bytes into the block; buffers chain through `qbuf_next`. */
 typedef struct umq_buf {

@@ -1,5 +1,6 @@
 """UMQ through the Python binding: two queues in one process bound to each other, ordered delivery of messages of
 several sizes in both directions, more messages than the queue depth (credits must flow back), statistics."""
+import ctypes
 import os
 
 import pytest
@@ -288,3 +289,63 @@ def test_large_messages_are_pulled_by_the_receiver_and_keep_their_place(pair):
     pool = umq.qbuf_stats() if hasattr(umq, "qbuf_stats") else None
     if pool:
         assert pool["alloc_failures"] == 0
+
+
+def test_sub_queues_share_receive_buffers_and_borrow_jetties(tmp_path):
+    """Many sub queues on two main queues: no endpoint and no receive buffers of their own. Every pair keeps its
+    own order and flow control, large messages are pulled, the jetty pool counts the borrowed posts."""
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import umq
+    umq.init(flow_control=True)
+    made = []
+    try:
+        before = umq.jetty_pool_stats()
+        ma = umq.Queue("main-a", depth=64, main=True, share_transport=True)
+        mb = umq.Queue("main-b", depth=64, main=True, share_transport=True)
+        made += [ma, mb]
+        ma.bind(mb.bind_info())
+        mb.bind(ma.bind_info())
+        n_sub = 24
+        sa = [umq.Queue(f"sa{i}", depth=8, sub_of=ma) for i in range(n_sub)]
+        sb = [umq.Queue(f"sb{i}", depth=8, sub_of=mb) for i in range(n_sub)]
+        made = sa + sb + made          # closed in this order: sub queues first
+        for x, y in zip(sa, sb):
+            x.bind(y.bind_info())
+            y.bind(x.bind_info())
+        st = umq.jetty_pool_stats()
+        assert st["total_num"] - before["total_num"] == 2 and st["sub_queues"] - before["sub_queues"] == 2 * n_sub
+        # interleaved traffic on all pairs and on the main queues themselves
+        for rnd in range(6):
+            for i, (x, y) in enumerate(zip(sa, sb)):
+                x.send(b"a%d-%d" % (i, rnd))
+                y.send(b"b%d-%d" % (i, rnd) * 50)
+            ma.send(b"main %d" % rnd)
+            assert mb.recv() == b"main %d" % rnd
+            for i, (x, y) in enumerate(zip(sa, sb)):
+                assert y.recv() == b"a%d-%d" % (i, rnd)
+                assert x.recv() == b"b%d-%d" % (i, rnd) * 50
+        # more messages than a sub queue's window of 8: credits return per sub queue
+        big = os.urandom(200_000)
+        for k in range(40):
+            sa[3].send(bytes([k]) * 100)
+            if k % 4 == 3:
+                for j in range(k - 3, k + 1):
+                    assert sb[3].recv() == bytes([j]) * 100
+        sa[5].send(b"small first")
+        sa[5].send(big)                  # beyond the 8 KB receive buffers: pulled through a borrowed endpoint
+        sa[5].send(b"small last")
+        assert [sb[5].recv(), sb[5].recv(), sb[5].recv()] == [b"small first", big, b"small last"]
+        assert sb[5].io_stats()["pull_rx"] == 1 and sa[5].io_stats()["pull_tx"] == 1
+        assert all(q.recv(timeout_s=0.01) is None for q in sb[:4])      # nothing leaked into other sub queues
+        assert sa[3].flow_control_stats()["credits_granted"] > 0
+        st2 = umq.jetty_pool_stats()
+        assert st2["acc_alloc_num"] - before["acc_alloc_num"] >= 6 * 2 * n_sub + 43
+        assert st2["acc_alloc_num"] == st2["acc_free_num"] and st2["err_num"] == 0
+        # a main queue cannot go while it has sub queues
+        assert umq._lib().umq_destroy(ctypes.c_uint64(ma.h)) != 0
+        assert ma.io_stats()["rx_errors"] == 0 and mb.io_stats()["rx_errors"] == 0
+    finally:
+        for q in made:
+            q.close()
+        umq.uninit()

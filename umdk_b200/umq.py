@@ -33,7 +33,22 @@ TRANS_MODE_UB, TRANS_MODE_IPC = 0, 3   # umq_trans_mode_t
 class _CreateOpt(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char * 32), ("rx_buf_size", ctypes.c_uint32), ("tx_buf_size", ctypes.c_uint32),
                 ("rx_depth", ctypes.c_uint32), ("tx_depth", ctypes.c_uint32), ("mode", ctypes.c_int),
-                ("token", ctypes.c_uint32), ("transport", ctypes.c_uint32)]
+                ("token", ctypes.c_uint32), ("transport", ctypes.c_uint32), ("create_flag", ctypes.c_uint32),
+                ("share_rq_umqh", ctypes.c_uint64)]
+
+
+class _JettyPoolStats(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_uint64) for n in
+                ("total_num", "err_num", "acc_alloc_num", "acc_free_num", "acc_miss_num", "sub_queues")]
+
+
+CREATE_FLAG_MAIN, CREATE_FLAG_SHARE_TRANSPORT, CREATE_FLAG_SUB = 1, 2, 4
+
+
+def jetty_pool_stats() -> dict:
+    st = _JettyPoolStats()
+    _lib().umq_jetty_pool_stats_get(ctypes.byref(st))
+    return {n: int(getattr(st, n)) for n, _ in _JettyPoolStats._fields_}
 
 
 class _Buf(ctypes.Structure):
@@ -155,10 +170,16 @@ def trace_stop() -> dict:
 
 class Queue:
     def __init__(self, name: str, depth: int = 128, buf_size: int = 0, token: int = 0x756d71,
-                 transport: Optional[int] = None):
+                 transport: Optional[int] = None, main: bool = False, share_transport: bool = False,
+                 sub_of: Optional["Queue"] = None):
         """``transport``: a transport mode for this queue (TRANS_MODE_UB = URMA, TRANS_MODE_IPC = the in-process
-        transport, or a mode registered with umq_transport_register); None = the mode given to ``init``."""
+        transport, or a mode registered with umq_transport_register); None = the mode given to ``init``.
+        ``main``: the queue can host sub queues (``share_transport``: its endpoint also joins the jetty pool);
+        ``sub_of``: make a sub queue of that main queue (no endpoint and no receive buffers of its own)."""
         o = _CreateOpt()
+        o.create_flag = (CREATE_FLAG_MAIN if main else 0) | (CREATE_FLAG_SHARE_TRANSPORT if share_transport else 0) | \
+            (CREATE_FLAG_SUB if sub_of is not None else 0)
+        o.share_rq_umqh = sub_of.h if sub_of is not None else 0
         o.name, o.rx_depth, o.tx_depth, o.rx_buf_size, o.tx_buf_size, o.token = \
             name.encode(), depth, depth, buf_size, buf_size, token
         o.transport = 0 if transport is None else transport + 1
