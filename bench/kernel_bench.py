@@ -244,6 +244,46 @@ def bench_dispatch_combine(T, H, E, K):
     return res
 
 
+def bench_allreduce(nbytes):
+    """Two-shot all-reduce kernel with a single rank: the reduce-scatter and all-gather passes run against this
+    GPU's own heap (read x, write the slice, read it back, write out), which is the kernel's memory path."""
+    from umdk_b200.ops.tp import AllReduce
+    from umdk_b200.parallel.symm import SymmetricHeap
+    heap = SymmetricHeap(AllReduce.heap_bytes(nbytes, 1))
+    ar = AllReduce(heap, nbytes)
+    x = torch.randn(nbytes // 2, device="cuda").to(torch.bfloat16)
+    med, mn = time_kernel(lambda: ar(x, algo="two_shot"))
+    ar.check()
+    r = report("allreduce two_shot (world=1)", med, mn, 4 * nbytes, 0, {"bytes": nbytes})
+    heap.close()
+    return r
+
+
+def bench_ll_combine(T, H, E, K):
+    """The stand-alone low-latency combine kernel at EP = 1: rows of the expert-major slab go back to the token
+    owner's combine buffer (local stores here), flags, weighted sum."""
+    from umdk_b200.ops.ep_ll import EpLowLatency
+    from umdk_b200.parallel.symm import SymmetricHeap
+    heap = SymmetricHeap(EpLowLatency.heap_bytes(1, E, K, H, T))
+    st = EpLowLatency(heap, E, K, H, 256, T)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    idx = torch.topk(torch.rand(T, E, device="cuda"), K, dim=-1).indices.to(torch.int64)
+    w = torch.rand(T, K, device="cuda")
+    y = torch.randn(st.n_cap, H, device="cuda").to(torch.bfloat16)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        st.dispatch(x, idx)
+        st.combine(y, idx, w, out=out)
+    med, mn = time_kernel(step)
+    st.check()
+    n = T * K
+    r = report("ep_ll_dispatch + ep_ll_combine (EP=1)", med, mn, T * H * 2 + 2 * n * H + 3 * n * H * 2 + T * H * 2, 0,
+               {"T": T, "H": H, "rows": n})
+    heap.close()
+    return r
+
+
 def bench_gemm_bf16(M, N, K):
     from umdk_b200 import _native
     lib = _native.cam()
@@ -281,7 +321,7 @@ def bench_quant(T, H):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["moe_gemm1", "moe_gemm2", "mla", "kv_gather", "dispatch", "gemm_bf16", "quant", "moe_fused", "tp", "all"])
+    ap.add_argument("what", choices=["moe_gemm1", "moe_gemm2", "mla", "kv_gather", "dispatch", "gemm_bf16", "quant", "moe_fused", "tp", "allreduce", "ll_combine", "all"])
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--tokens-per-expert", type=int, default=32)
     ap.add_argument("--batch", type=int, default=64)
@@ -311,6 +351,10 @@ def main():
         bench_dispatch_combine(a.tokens, 7168, 256, 8)
     if a.what in ("gemm_bf16", "all"):
         bench_gemm_bf16(8192, 8192, 8192) if not a.small else bench_gemm_bf16(4096, 4096, 4096)
+    if a.what in ("allreduce", "all"):
+        bench_allreduce((256 << 20) if a.small else (1 << 30))
+    if a.what in ("ll_combine", "all"):
+        bench_ll_combine(128 if not a.small else 64, 7168, 256 if not a.small else 32, 8)
     if a.what in ("quant", "all"):
         bench_quant(a.tokens, 7168)
 

@@ -61,7 +61,7 @@ int main(int argc, char** argv) {
     printf("no UMS state in %s\n", dir.c_str());
     return 0;
   }
-  int listeners = 0, conns = 0;
+  int listeners = 0, conns = 0, links = 0;
   while (dirent* e = readdir(d)) {
     const std::string name = e->d_name;
     if (name == "." || name == "..") continue;
@@ -72,6 +72,38 @@ int main(int argc, char** argv) {
     }
     const std::string path = dir + "/" + name;
     struct stat st;
+    if (name.rfind("lg_", 0) == 0) {   // a link: up to 32 connections in one file plus the control rings
+      if (stat(path.c_str(), &st) != 0 || (size_t)st.st_size != sizeof(ums_shm::LinkShm)) continue;
+      const int lfd = open(path.c_str(), O_RDONLY);
+      if (lfd < 0) continue;
+      void* lp = mmap(nullptr, sizeof(ums_shm::LinkShm), PROT_READ, MAP_SHARED, lfd, 0);
+      close(lfd);
+      if (lp == MAP_FAILED) continue;
+      const ums_shm::LinkShm* lk = static_cast<const ums_shm::LinkShm*>(lp);
+      static const char* const states[] = {"created", "active", "deleted"};
+      const uint32_t used = lk->slot_used.load(), done = lk->closed_c.load() & lk->closed_s.load();
+      const uint32_t state = lk->state.load();
+      printf("link %s  group %.63s  state %s  client pid %u  server pid %u  connections carried %u\n", name.c_str(),
+             lk->group, states[state < 3 ? state : 0], lk->owner_pid, lk->peer_pid.load(), lk->conns_total.load());
+      printf("  control ring client->server %llu/%llu  server->client %llu/%llu (produced/consumed)\n",
+             (unsigned long long)lk->llc_c2s.prod.load(), (unsigned long long)lk->llc_c2s.cons.load(),
+             (unsigned long long)lk->llc_s2c.prod.load(), (unsigned long long)lk->llc_s2c.cons.load());
+      for (uint32_t i = 0; i < ums_shm::kLinkSlots; ++i) {
+        if (!(used & (1u << i)) || (done & (1u << i))) continue;
+        const ums_shm::Ring* rings[2] = {&lk->conn[i].c2s, &lk->conn[i].s2c};
+        const char* label[2] = {"client->server", "server->client"};
+        printf("connection %s slot %u\n", name.c_str(), i);
+        for (int k = 0; k < 2; ++k) {
+          const unsigned long long prod = rings[k]->prod.load(), cons = rings[k]->cons.load();
+          printf("  %s  produced %llu  consumed %llu  in flight %llu  %s\n", label[k], prod, cons, prod - cons,
+                 rings[k]->closed.load() ? "closed" : "open");
+        }
+        ++conns;
+      }
+      munmap(lp, sizeof(ums_shm::LinkShm));
+      ++links;
+      continue;
+    }
     if (stat(path.c_str(), &st) != 0 || (size_t)st.st_size < sizeof(ums_shm::ConnShm)) continue;
     const int fd = open(path.c_str(), O_RDONLY);
     if (fd < 0) continue;
@@ -91,6 +123,6 @@ int main(int argc, char** argv) {
     ++conns;
   }
   closedir(d);
-  printf("%d listener(s), %d connection(s) in %s\n", listeners, conns, dir.c_str());
+  printf("%d listener(s), %d connection(s), %d link(s) in %s\n", listeners, conns, links, dir.c_str());
   return 0;
 }

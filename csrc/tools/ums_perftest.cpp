@@ -1,5 +1,5 @@
 // ums_perftest: ping-pong latency and streaming throughput of a UMS connection compared with plain TCP on loopback,
-// plus a self-check of the fallback path. `ums_perftest [--size N] [--iters N] [--selftest]`
+// plus a self-check of the fallback path. `ums_perftest [--size N] [--iters N] [--selftest] [--linkgroups]`
 #include <arpa/inet.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
@@ -8,6 +8,7 @@
 #include <string.h>
 #include <unistd.h>
 
+#include <atomic>
 #include <chrono>
 #include <thread>
 #include <vector>
@@ -89,10 +90,133 @@ static int run(const Api& a, const char* name, size_t size, int iters, double* l
   return 0;
 }
 
+// Link groups, control messages and receive moderation: 40 connections to one listener must share two link files
+// (32 slots + 8), closed slots are reused, TEST LINK is answered by a peer that sleeps in recv, empty links go away
+// after the linger time, and the busy-poll budget of a connection whose peer is slow comes down.
+static int linkgroup_check() {
+  ums_stats_t s0;
+  ums_get_stats(&s0);
+  const int ls = ums_socket(AF_INET, SOCK_STREAM, 0);
+  sockaddr_in ad{};
+  ad.sin_family = AF_INET;
+  ad.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+  if (bind(ls, (sockaddr*)&ad, sizeof(ad)) || ums_listen(ls, 64)) return fail("listen");
+  socklen_t l = sizeof(ad);
+  getsockname(ls, (sockaddr*)&ad, &l);
+  constexpr int kConns = 40, kExtra = 10;
+  std::atomic<int> slow_ms{0};
+  std::vector<std::thread> workers;
+  std::thread acceptor([&] {
+    for (int i = 0; i < kConns + kExtra; ++i) {
+      const int c = ums_accept(ls, nullptr, nullptr);
+      if (c < 0) return;
+      workers.emplace_back([c, &slow_ms] {   // echo until the client closes
+        char b[256];
+        for (;;) {
+          const ssize_t r = ums_recv(c, b, sizeof(b), 0);
+          if (r <= 0) break;
+          if (slow_ms.load()) std::this_thread::sleep_for(std::chrono::milliseconds(slow_ms.load()));
+          ums_send(c, b, r, 0);
+        }
+        ums_close(c);
+      });
+    }
+  });
+  auto echo = [](int fd, int tag) {
+    char out[64], in[64];
+    const int n = snprintf(out, sizeof(out), "conn %d says hello", tag);
+    if (ums_send(fd, out, n, 0) != n) return false;
+    int got = 0;
+    while (got < n) {
+      const ssize_t r = ums_recv(fd, in + got, n - got, 0);
+      if (r <= 0) return false;
+      got += (int)r;
+    }
+    return memcmp(in, out, n) == 0;
+  };
+  std::vector<int> fds;
+  std::vector<ums_conn_info_t> info(kConns);
+  for (int i = 0; i < kConns; ++i) {
+    const int fd = ums_socket(AF_INET, SOCK_STREAM, 0);
+    if (ums_connect(fd, (sockaddr*)&ad, sizeof(ad)) || ums_is_accelerated(fd) != 1) return fail("connect");
+    fds.push_back(fd);
+    if (ums_conn_info(fd, &info[i]) || !info[i].link[0]) return fail("connection is not on a link");
+  }
+  for (int i = 0; i < kConns; ++i)
+    if (!echo(fds[i], i)) return fail("echo on a link slot");
+  // first 32 connections on one link, slots 0..31; the rest on a second link of the group
+  for (int i = 0; i < kConns; ++i) {
+    const bool first = i < 32;
+    if (strcmp(info[i].link, info[first ? 0 : 32].link) || info[i].slot != (uint32_t)(first ? i : i - 32))
+      return fail("slot assignment");
+  }
+  if (!strcmp(info[0].link, info[32].link)) return fail("a 33rd connection needs a second link");
+  ums_stats_t s1;
+  ums_get_stats(&s1);
+  // both ends live in this process: every link is mapped once per role
+  if (s1.links_created - s0.links_created != 4 || s1.conns_on_links - s0.conns_on_links != 2 * kConns)
+    return fail("link statistics");
+  if (s1.llc_tx == s0.llc_tx || s1.llc_rx == s0.llc_rx) return fail("no control messages were exchanged");
+  ums_conn_info(fds[0], &info[0]);
+  if (info[0].link_state != 1 || info[0].link_conns != 32) return fail("link not ACTIVE after CONFIRM LINK");
+  // TEST LINK: the peers sit in recv (asleep on their descriptors) and must still answer
+  std::this_thread::sleep_for(std::chrono::milliseconds(20));
+  if (ums_link_test(fds[0], 2000) || ums_link_test(fds[39], 2000)) return fail("TEST LINK was not answered");
+  // closed slots are handed out again, no new link is made
+  for (int i = 5; i < 5 + kExtra; ++i) ums_close(fds[i]);
+  std::this_thread::sleep_for(std::chrono::milliseconds(50));   // the echo threads close their ends
+  for (int i = 5; i < 5 + kExtra; ++i) {
+    const int fd = ums_socket(AF_INET, SOCK_STREAM, 0);
+    if (ums_connect(fd, (sockaddr*)&ad, sizeof(ad)) || ums_is_accelerated(fd) != 1) return fail("reconnect");
+    ums_conn_info_t ci;
+    ums_conn_info(fd, &ci);
+    if (strcmp(ci.link, info[0].link) || ci.slot < 5 || ci.slot >= 5 + (uint32_t)kExtra) return fail("slot not reused");
+    if (!echo(fd, 100 + i)) return fail("echo on a reused slot");
+    fds[i] = fd;
+  }
+  ums_stats_t s2;
+  ums_get_stats(&s2);
+  if (s2.links_created != s1.links_created) return fail("a link was created although slots were free");
+  // receive moderation: a partner that answers after 3 ms makes busy-polling pointless; the level comes down
+  ums_conn_info(fds[1], &info[1]);
+  const uint32_t level0 = info[1].dim_level;
+  slow_ms = 3;
+  for (int i = 0; i < 70; ++i)
+    if (!echo(fds[1], i)) return fail("echo (slow partner)");
+  slow_ms = 0;
+  ums_conn_info(fds[1], &info[1]);
+  ums_stats_t s3;
+  ums_get_stats(&s3);
+  if (!(info[1].dim_level < level0) || s3.dim_down == s2.dim_down) return fail("moderation level did not come down");
+  // a partner that answers at once: polling catches the answer, nothing pushes the level further down
+  const uint32_t level1 = info[1].dim_level;
+  for (int i = 0; i < 200; ++i)
+    if (!echo(fds[2], i)) return fail("echo (fast partner)");
+  ums_conn_info(fds[2], &info[2]);
+  if (info[2].dim_level < 1) return fail("moderation gave up polling although the partner is fast");
+  (void)level1;
+  for (int fd : fds) ums_close(fd);
+  acceptor.join();
+  for (auto& w : workers) w.join();
+  ums_close(ls);
+  // links linger for UMS_LINK_LINGER_MS after their last connection, then their files are removed
+  const char* lg = getenv("UMS_LINK_LINGER_MS");
+  std::this_thread::sleep_for(std::chrono::milliseconds((lg ? atoi(lg) : 1000) + 100));
+  ums_stats_t s4;
+  ums_get_stats(&s4);
+  ums_get_stats(&s4);   // the second pass frees the accepting side's mappings of files that are now gone
+  if (s4.links_active != 0 || s4.links_freed - s0.links_freed != 4) return fail("links were not freed after the linger time");
+  printf("link groups: %d connections on 2 links, %llu control messages, moderation level %u -> %u: OK\n", kConns,
+         (unsigned long long)(s4.llc_tx - s0.llc_tx), level0, info[1].dim_level);
+  return 0;
+}
+
 int main(int argc, char** argv) {
   size_t size = 8192;
   int iters = 20000;
   bool selftest = false;
+  for (int i = 1; i < argc; ++i)
+    if (!strcmp(argv[i], "--linkgroups")) return linkgroup_check();
   for (int i = 1; i < argc; ++i) {
     if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);

@@ -79,6 +79,24 @@ def test_ums_accelerated_and_fallback(tmp_path):
     assert rc == 0 and "ums_perftest: OK" in out, out
 
 
+def test_ums_link_groups_control_messages_and_moderation(tmp_path):
+    """40 connections share two link files, closed slots are reused, TEST LINK is answered by sleeping peers, empty
+    links are removed after the linger time, the busy-poll budget follows the partner's speed."""
+    os.environ["UMS_LINK_LINGER_MS"] = "100"
+    try:
+        rc, out = _run([BIN / "ums_perftest", "--linkgroups"], tmp_path)
+    finally:
+        del os.environ["UMS_LINK_LINGER_MS"]
+    assert rc == 0 and "40 connections on 2 links" in out and ": OK" in out, out
+    # without link groups every connection has a file of its own, as before
+    os.environ["UMS_LINK_GROUP"] = "0"
+    try:
+        rc, out = _run([BIN / "ums_perftest", "--selftest", "--iters", "500"], tmp_path)
+    finally:
+        del os.environ["UMS_LINK_GROUP"]
+    assert rc == 0 and "ums_perftest: OK" in out, out
+
+
 @pytest.mark.parametrize("op", ["write", "read", "send", "faa", "cas"])
 def test_urma_perftest_single_process(tmp_path, op):
     rc, out = _run([BIN / "urma_perftest", "--op", op, "--iters", "2000"], tmp_path)
@@ -186,8 +204,9 @@ def test_ums_admin_shows_live_connections(tmp_path):
     try:
         assert "HOLDING" in p.stdout.readline()
         rc, out = _run([BIN / "ums_admin", "show", tmp_path / "ums"], tmp_path)
-        assert rc == 0 and "1 listener(s)" in out and "1 connection(s)" in out, out
+        assert rc == 0 and "1 listener(s)" in out and "1 connection(s), 1 link(s)" in out, out
         assert "produced 5000  consumed 5000  in flight 0  open" in out, out
+        assert "state active" in out and "slot 0" in out, out
         p.wait(timeout=30)
     finally:
         if p.poll() is None:
@@ -221,7 +240,7 @@ def test_ums_handshake_is_authenticated_with_a_pre_shared_key(tmp_path):
         "    assert got == msg\n"
         "c.close()\n"
         f"lib = ctypes.CDLL({str(lib)!r})\n"
-        "st = (ctypes.c_uint64 * 9)(); lib.ums_get_stats(st)\n"
+        "st = (ctypes.c_uint64 * 18)(); lib.ums_get_stats(st)\n"
         "print('STATS ums=%d fallback=%d auth_fail=%d' % (st[0], st[1], st[8]))\n")
     wrapper = _native.lib_dir().parent / "bin" / "ums_run"
     base = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"), UMS_SHM_DIR=str(tmp_path / "ums"))

@@ -140,7 +140,7 @@ def test_ums_connection_setup_through_the_agents(tmp_path):
         "    assert got == msg\n"
         "c.close()\n"
         f"lib = ctypes.CDLL({lib_path!r})\n"
-        "st = (ctypes.c_uint64 * 9)(); lib.ums_get_stats(st)\n"
+        "st = (ctypes.c_uint64 * 18)(); lib.ums_get_stats(st)\n"
         "print('STATS ums=%d fallback=%d auth_fail=%d' % (st[0], st[1], st[8]))\n")
     wrapper = os.path.join(os.path.dirname(_native.lib_dir()), "bin", "ums_run")
     base = {k: v for k, v in os.environ.items() if not k.startswith("UMS_")}
