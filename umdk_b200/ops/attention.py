@@ -15,12 +15,14 @@ PAGE = 64
 
 
 def sparse_mla_decode(q: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor, indices: torch.Tensor,
-                      sm_scale: float, seq_lens: Optional[torch.Tensor] = None, num_splits: int = 1,
+                      sm_scale: float, seq_lens: Optional[torch.Tensor] = None, num_splits: int = 0,
                       out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
                       workspace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                       diag: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """q [B,128,576] bf16, kv_pages [P,64,576] bf16, block_table [B,max_pages] int32, indices [B,topk] int32
     (token positions; -1 = unused) -> (out [B,128,512] bf16, lse [B,128] fp32).
+    ``num_splits`` 0 = as many splits of the key list as it takes to put a CTA pair on every SM (a batch of 64
+    already does with one split), each split keeping at least four 48-key chunks.
     ``diag`` (int64 [16], device): the first CTA records how many cycles its roles spent in each of their waits and
     work sections (see MlaArgs::diag in the kernel source); for finding what bounds the pipeline."""
     lib = _native.cam()
@@ -37,6 +39,9 @@ def sparse_mla_decode(q: torch.Tensor, kv_pages: torch.Tensor, block_table: torc
     if status is None:
         status = torch.zeros(4, dtype=torch.int32, device=dev)
     # one CTA pair resolves at most 2064 selected rows up front: longer key lists need more splits
+    if num_splits <= 0:
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        num_splits = max(1, min(sms // (2 * B), topk // (4 * 48), 16))
     num_splits = max(num_splits, int(lib.umdk_sparse_mla_min_splits(topk)))
     if workspace is not None and workspace[0].shape[1] != num_splits:
         workspace = None

@@ -86,31 +86,71 @@ class SymmetricHeap:
     def multicast(cls, nbytes: int, group: Optional[dist.ProcessGroup] = None) -> "SymmetricHeap":
         """Heap whose slabs are also bound to an NVLink multicast object (NVLS): besides the per-peer pointers it
         offers ``multicast_ptr``, an address on which ``multimem`` loads reduce over all ranks inside NVSwitch and
-        ``multimem`` stores broadcast to all ranks. Allocation and handle exchange go through
-        ``torch.distributed._symmetric_memory`` (plumbing only; the kernels that use the pointers are this
-        package's). Raises if the platform cannot provide a multicast mapping."""
-        import torch.distributed._symmetric_memory as symm_mem
+        ``multimem`` stores broadcast to all ranks. Built on the driver's virtual-memory-management calls
+        (csrc/cam/symm_mc.cu): every rank creates its memory, the descriptors travel between the processes with
+        pidfd_getfd, rank 0 creates the multicast object, all ranks join, bind and map it. Raises when the GPUs or
+        the driver cannot do multicast; callers then stay on the peer-pointer algorithms."""
+        lib = _native.cam()
         pg = group if group is not None else dist.group.WORLD
-        dev = torch.device("cuda", torch.cuda.current_device())
-        t = symm_mem.empty(int(nbytes), dtype=torch.uint8, device=dev)
-        hdl = symm_mem.rendezvous(t, pg)
-        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
-        if mc == 0:
-            raise RuntimeError("no NVLink multicast mapping available for this group")
-        t.zero_()
-        torch.cuda.synchronize()
-        dist.barrier(group=group)
+        rank, world = dist.get_rank(pg), dist.get_world_size(pg)
+        # every rank must take the same branch: agree first
+        ok = torch.tensor([int(lib.umdk_mc_supported())], dtype=torch.int32, device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=pg)
+        if int(ok.item()) == 0:
+            raise RuntimeError("no NVLink multicast support on this group's GPUs")
+        import os
+        heap, local = ctypes.c_void_p(), ctypes.c_void_p()
+        fd, padded = ctypes.c_int(-1), ctypes.c_size_t(0)
+
+        def agree(rc: int, what: str):
+            """Raises on EVERY rank when the step failed on any rank (a rank that went on alone would wait forever)."""
+            t = torch.tensor([int(rc != 0)], dtype=torch.int32, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=pg)
+            if int(t.item()):
+                if heap.value:
+                    lib.umdk_mc_destroy(heap)
+                raise RuntimeError(f"multicast heap: {what} failed (rc {rc} on rank {rank})")
+
+        agree(lib.umdk_mc_local_create(ctypes.c_size_t(int(nbytes)), world, ctypes.byref(heap), ctypes.byref(local),
+                                       ctypes.byref(fd), ctypes.byref(padded)), "local allocation")
+        mc_fd = ctypes.c_int(-1)
+        rc = lib.umdk_mc_group_create(heap, ctypes.byref(mc_fd)) if rank == 0 else 0
+        agree(rc, "multicast object creation")
+        # (pid, descriptor of the local memory, descriptor of the multicast object on rank 0) of every rank
+        infos = [None] * world
+        dist.all_gather_object(infos, (os.getpid(), fd.value, mc_fd.value), group=pg)
+        rc = 0
+        if rank != 0:
+            got = lib.umdk_fd_from_process(infos[0][0], infos[0][2])
+            rc = lib.umdk_mc_group_import(heap, got) if got >= 0 else got
+            if got >= 0:
+                os.close(got)
+        agree(rc, "multicast object import")
+        agree(lib.umdk_mc_add_device(heap), "joining the multicast object")      # all joined before anyone binds
+        mc_ptr = ctypes.c_void_p()
+        agree(lib.umdk_mc_bind_map(heap, ctypes.byref(mc_ptr)), "binding / mapping the multicast object")
+        peer_ptrs, rc = [0] * world, 0
+        for r in range(world):
+            if r == rank:
+                peer_ptrs[r] = local.value
+                continue
+            got = lib.umdk_fd_from_process(infos[r][0], infos[r][1])
+            p = ctypes.c_void_p()
+            rc = rc or (lib.umdk_mc_import_peer(heap, got, ctypes.byref(p)) if got >= 0 else got)
+            if got >= 0:
+                os.close(got)
+            peer_ptrs[r] = p.value or 0
+        agree(rc, "mapping the peers' memory")     # also: nobody closes its descriptors before all have duplicated them
         h = cls.__new__(cls)
         h.nbytes = int(nbytes)
         h.group = group
-        h.rank = dist.get_rank(group)
-        h.world = dist.get_world_size(group)
-        h._lib = _native.cam()
-        h._local = ctypes.c_void_p(int(hdl.buffer_ptrs[h.rank]))
+        h.rank, h.world = rank, world
+        h._lib = lib
+        h._local = ctypes.c_void_p(local.value)
         h._imported = []
-        h.peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
-        h.multicast_ptr = mc
-        h._torch_keepalive = (t, hdl)
+        h.peer_ptrs = peer_ptrs
+        h.multicast_ptr = mc_ptr.value
+        h._mc_heap = heap
         h._virtual_children = []
         return h
 
@@ -126,9 +166,11 @@ class SymmetricHeap:
 
     def close(self):
         lib = self._lib
-        if getattr(self, "_torch_keepalive", None) is not None:
-            self._torch_keepalive = None  # memory is owned by torch's symmetric-memory allocator
+        if getattr(self, "_mc_heap", None) is not None:   # unmaps the peers, the multicast range and the local memory
+            lib.umdk_mc_destroy(self._mc_heap)
+            self._mc_heap = None
             self._local = ctypes.c_void_p()
+            self.multicast_ptr = 0
             return
         for p in self._imported:
             lib.umdk_symm_unimport(ctypes.c_void_p(p))
