@@ -31,6 +31,13 @@ def test_tp_kernels_allreduce_and_urma_across_gpus():
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     rc, out = _torchrun("mp_tp_worker.py", n)
     assert rc == 0 and "MP_TP_OK" in out, out[-4000:]
+    # on GPUs that can join an NVLink multicast object the in-switch all-reduce must have run on the package's own
+    # multicast heap: a silent fall-back to the peer-pointer algorithms would hide a broken heap
+    from umdk_b200 import _native
+    line = [ln for ln in out.splitlines() if "MP_TP_OK" in ln][-1]
+    print(line)
+    if _native.cam().umdk_mc_supported():
+        assert "nvls=ok" in line, out[-4000:]
 
 
 def test_rank_leaves_between_steps_and_survivors_stop_cleanly():
