@@ -1,6 +1,8 @@
 // urma_perftest: latency and bandwidth of URMA verbs (write / read / send / atomic) between two endpoints.
-//   urma_perftest [--dev shm0|bond0] [--op write|read|send|faa|cas] [--size N] [--iters N] [--depth N]
-//                 [--duration SEC] [--jettys N] [--cq-mod N] [--rate-limit MB/s]
+//   urma_perftest [--dev shm0|bond0|cudaN] [--peer-dev cudaM] [--op write|read|send|faa|cas] [--size N] [--iters N]
+//                 [--depth N] [--duration SEC] [--jettys N] [--cq-mod N] [--rate-limit MB/s]
+//     --dev cudaN  the buffers live in the memory of GPU N (allocated through the CUDA runtime, loaded at run time);
+//                  --peer-dev cudaM puts the second endpoint of the in-process mode on GPU M (default: the same GPU)
 //     --duration   run the pipelined part for a time instead of a number of operations
 //     --jettys     N endpoint pairs driven round-robin (in-process mode)
 //     --cq-mod     ask for a completion only on every N-th operation (completion moderation)
@@ -11,6 +13,7 @@
 // (src/urma/tools/urma_perftest, doc/en/urma/URMA User Guide.md:1690-1740: test type, message size, iterations,
 // queue depth, out-of-band TCP exchange of segment and jetty information).
 #include <arpa/inet.h>
+#include <dlfcn.h>
 #include <netinet/in.h>
 #include <sched.h>
 #include <stdio.h>
@@ -43,6 +46,43 @@ static bool xfer(int fd, void* b, size_t n, bool tx) {
   }
   return true;
 }
+// Buffers: host memory, or - for the cudaN devices - memory of that GPU. The tool is a plain host program: the CUDA
+// runtime is loaded when (and only when) a GPU device is named.
+struct GpuRt {
+  int (*set_device)(int) = nullptr;
+  int (*malloc_)(void**, size_t) = nullptr;
+  int (*memset_)(void*, int, size_t) = nullptr;
+  int (*sync)() = nullptr;
+  bool load() {
+    if (malloc_) return true;
+    void* h = nullptr;
+    for (const char* n : {"libcudart.so.12", "libcudart.so.13", "libcudart.so"})
+      if ((h = dlopen(n, RTLD_NOW | RTLD_GLOBAL))) break;
+    if (!h) return false;
+    set_device = reinterpret_cast<int (*)(int)>(dlsym(h, "cudaSetDevice"));
+    malloc_ = reinterpret_cast<int (*)(void**, size_t)>(dlsym(h, "cudaMalloc"));
+    memset_ = reinterpret_cast<int (*)(void*, int, size_t)>(dlsym(h, "cudaMemset"));
+    sync = reinterpret_cast<int (*)()>(dlsym(h, "cudaDeviceSynchronize"));
+    return set_device && malloc_ && memset_ && sync;
+  }
+};
+static GpuRt g_rt;
+// -1 for a device that is not a GPU, else the GPU's index.
+static int gpu_index(const std::string& dev) { return dev.rfind("cuda", 0) == 0 ? atoi(dev.c_str() + 4) : -1; }
+static uint8_t* alloc_buf(const std::string& dev, size_t bytes, int fill) {
+  const int gi = gpu_index(dev);
+  if (gi < 0) {
+    uint8_t* p = static_cast<uint8_t*>(malloc(bytes));
+    if (p) memset(p, fill, bytes);
+    return p;
+  }
+  void* p = nullptr;
+  if (!g_rt.load() || g_rt.set_device(gi) != 0 || g_rt.malloc_(&p, bytes) != 0 || g_rt.memset_(p, fill, bytes) != 0 ||
+      g_rt.sync() != 0)
+    return nullptr;
+  return static_cast<uint8_t*>(p);
+}
+
 static int wait_n(urma_simple_ep_t* ep, int want, int* bad) {
   int st[64];
   uint64_t uc[64];
@@ -60,7 +100,7 @@ static int wait_n(urma_simple_ep_t* ep, int want, int* bad) {
 }
 
 int main(int argc, char** argv) {
-  std::string dev = "shm0", op = "write", host = "127.0.0.1";
+  std::string dev = "shm0", peer_dev, op = "write", host = "127.0.0.1";
   uint32_t size = 4096, iters = 20000, depth = 64;
   int server = -1, client = -1;
   uint32_t jettys = 1, cq_mod = 1;
@@ -71,6 +111,7 @@ int main(int argc, char** argv) {
     else if (!strcmp(argv[i], "--cq-mod") && i + 1 < argc) cq_mod = std::max(1, atoi(argv[++i]));
     else if (!strcmp(argv[i], "--rate-limit") && i + 1 < argc) rate_mbs = atof(argv[++i]);
     else if (!strcmp(argv[i], "--dev") && i + 1 < argc) dev = argv[++i];
+    else if (!strcmp(argv[i], "--peer-dev") && i + 1 < argc) peer_dev = argv[++i];
     else if (!strcmp(argv[i], "--op") && i + 1 < argc) op = argv[++i];
     else if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
@@ -84,7 +125,15 @@ int main(int argc, char** argv) {
   urma_context_t* ctx = urma_simple_open(dev.c_str());
   if (!ctx) return fail("open device");
   const uint32_t seg_bytes = std::max<uint32_t>(size, 4096) * 2;
-  std::vector<uint8_t> mem_a(seg_bytes, 1), mem_b(seg_bytes, 2);
+  if (peer_dev.empty()) peer_dev = dev;
+  if ((gpu_index(dev) >= 0) != (gpu_index(peer_dev) >= 0)) return fail("--dev and --peer-dev must both be GPUs or both not");
+  // (named like the vectors they replace: .data() is the buffer, in host or GPU memory)
+  struct Buf {
+    uint8_t* p = nullptr;
+    uint8_t* data() const { return p; }
+  };
+  Buf mem_a{alloc_buf(dev, seg_bytes, 1)}, mem_b{alloc_buf(peer_dev, seg_bytes, 2)};
+  if (!mem_a.p || !mem_b.p) return fail("buffer allocation (for cudaN: is the CUDA runtime library on the loader path?)");
   urma_simple_ep_t* ea = urma_simple_ep_create(ctx, depth * 2, 1, 0);
   Blob mine{}, peer{};
   urma_target_seg_t* seg_a = urma_simple_seg_register(ctx, mem_a.data(), seg_bytes, 14, 1, mine.seg);
@@ -118,7 +167,7 @@ int main(int argc, char** argv) {
     }
     if (!xfer(tcp, &mine, sizeof(mine), true) || !xfer(tcp, &peer, sizeof(peer), false)) return fail("exchange");
   } else {
-    ctx_b = urma_simple_open(dev.c_str());
+    ctx_b = urma_simple_open(peer_dev.c_str());
     eb = urma_simple_ep_create(ctx_b, depth * 2, 1, 0);
     urma_target_seg_t* seg_b = urma_simple_seg_register(ctx_b, mem_b.data(), seg_bytes, 14, 1, peer.seg);
     seg_b_reg = seg_b;
@@ -149,8 +198,12 @@ int main(int argc, char** argv) {
   if (!tj || !rseg) return fail("import");
   const uint64_t rva = rseg->seg.ubva.va;
   if (server >= 0) {  // passive side: keep receives posted until the client says goodbye
-    std::vector<std::vector<uint8_t>> rb(depth, std::vector<uint8_t>(size));
-    for (uint32_t i = 0; i < depth; ++i) urma_simple_post_recv(ea, rb[i].data(), size, i);
+    std::vector<Buf> rb(depth);
+    for (uint32_t i = 0; i < depth; ++i) {
+      rb[i].p = alloc_buf(dev, size, 0);
+      if (!rb[i].p) return fail("receive buffer allocation");
+      urma_simple_post_recv(ea, rb[i].data(), size, i);
+    }
     char bye;
     for (;;) {
       int st[32];
@@ -185,10 +238,14 @@ int main(int argc, char** argv) {
     atomic = true;
     size = 8;
   }
-  std::vector<std::vector<uint8_t>> rb;
+  std::vector<Buf> rb;
   if (two_sided && eb) {
-    rb.assign(depth * 2, std::vector<uint8_t>(size));
-    for (uint32_t i = 0; i < depth * 2; ++i) urma_simple_post_recv(eb, rb[i].data(), size, i);
+    rb.resize(depth * 2);
+    for (uint32_t i = 0; i < depth * 2; ++i) {
+      rb[i].p = alloc_buf(peer_dev, size, 0);
+      if (!rb[i].p) return fail("receive buffer allocation");
+      urma_simple_post_recv(eb, rb[i].data(), size, i);
+    }
   }
   auto post = [&](uint64_t id) {
     if (atomic) return urma_simple_atomic(ea, tj, opc, rseg, rva, 1, 0, nullptr, id);

@@ -77,3 +77,21 @@ def test_cuda_ipc_send_recv_into_posted_device_buffers():
     finally:
         a.close()
         b.close()
+
+
+@pytest.mark.parametrize("op", ["write", "read", "send"])
+def test_urma_perftest_on_gpu_memory(tmp_path, op):
+    """The command-line tool with its buffers in GPU memory (`--dev cuda0`), the second endpoint on another GPU when
+    the box has one: one-sided verbs and two-sided SEND into posted device buffers."""
+    import os
+    import subprocess
+    from umdk_b200 import _native
+    tool = _native.lib_dir() / "bin" / "urma_perftest"
+    args = [str(tool), "--dev", "cuda0", "--op", op, "--size", "65536", "--iters", "400", "--depth", "16"]
+    if torch.cuda.device_count() >= 2:
+        args += ["--peer-dev", "cuda1"]
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"))
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    p = subprocess.run(args, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=180)
+    assert p.returncode == 0 and "urma_perftest: OK" in p.stdout and "errors 0" in p.stdout, p.stdout[-2000:]
+    assert f"{op} dev=cuda0 size=65536" in p.stdout
