@@ -22,14 +22,10 @@
 //              so that the round trip between the two CTAs is off the softmax warps' critical path
 //   warp  4    one thread issues every MMA: Q*K^T of chunk c+1 is issued BEFORE P*V of chunk c, so the tensor
 //              pipe works on the next scores while the softmax of the current chunk runs (S is double-buffered)
-//   warps 5-6  gather producers, TMA half: tile::gather4 copies (four selected rows x 128 bytes per instruction,
-//              written in the 128-byte-swizzled layout the MMA descriptors expect), completion counted in bytes on
-//              the stage's barrier
-//   warps 7-8  gather producers, load/store-unit half: the same (four rows x 128 bytes) units as 16-byte cp.async
-//              copies into the same swizzled positions; each warp arrives on the stage's barrier once its copies of
-//              the tile have landed. Measured per SM: the TMA unit takes a gather4 every 41 cycles (12.5 bytes per
-//              clock, two issuing warps reach it), 16-byte cp.async sustains 10.7 bytes per clock - two different
-//              units, so a tile is split between them in about that proportion
+//   warp  5    gather producer: TMA tile::gather4 copies (four selected rows x 128 bytes per instruction, written
+//              in the 128-byte-swizzled layout the MMA descriptors expect), completion counted in bytes on the
+//              stage's barrier. Gathering with 16-byte cp.async was measured first: an SM sustains only about
+//              10 bytes per clock of such loads (2800 cycles for a 30 KB tile), whatever the access pattern
 // All row addresses of the split are resolved once, up front, into shared memory (index -> page -> row).
 // The running maximum is only raised when it grows by more than 8 (in log2 units); P then stays below 2^8 and the
 // accumulated O needs rescaling only a few times per row instead of in most chunks.
@@ -57,10 +53,7 @@ constexpr int kXBytes = kChunk * kHeads * 4;     // 24 KB, [key / 4][head][4] fp
 constexpr int kMaxChunks = 43;                   // 2064 keys per split at most
 constexpr int kMaxKeys = kMaxChunks * kChunk;
 constexpr int kThreads = 416;
-constexpr int kProducerWarps = 4;   // warps 5..8 gather: kTmaWarps through the TMA unit, the rest with cp.async
-constexpr int kTmaWarps = 2;
-constexpr int kLsuWarps = kProducerWarps - kTmaWarps;
-constexpr int kLsuShare256 = 118;   // of 256: share of a tile's gather units that goes to the cp.async warps
+constexpr int kProducerWarps = 4;   // warps 5..8 issue the gather copies: the TMA unit takes them faster from several warps
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;                         // two S buffers of 64 columns (48 used)
 constexpr int kColO = 128;
@@ -197,7 +190,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   if (tid == 0) {
     mbar_init(bar_q, 1);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(&bar_full[i], 1 + kLsuWarps);   // the TMA bytes (one expect_tx arrival) + one arrival per cp.async warp
+      mbar_init(&bar_full[i], 1);
       mbar_init(&bar_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -562,14 +555,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
           t_prev = t;
         }
       };
-      // A tile is (kChunk / 4) * n_slabs units of four rows x 128 bytes. Units [0, n_tma) go through the TMA unit,
-      // the rest through cp.async.
-      const int n_inst = (kChunk / 4) * n_slabs;
-      const int n_lsu = (n_inst * kLsuShare256) >> 8;
-      const int n_tma = n_inst - n_lsu;
-      const bool lsu = warp >= 5 + kTmaWarps;
-      const int pw = lsu ? warp - 5 - kTmaWarps : warp - 5;   // index among the warps of this half
-      auto unit_col = [&](int slab) { return slab < 4 ? half * 256 + slab * 64 : 512; };
+      const int n_inst = (kChunk / 4) * n_slabs;   // gather4 copies per tile
       for (int c = 0; c < num_chunks && ok; ++c) {
         const int st = c % kStages;
         if (c >= kStages) {
@@ -580,50 +566,21 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
           }
         }
         lap(1);
+        if (warp == 5 && lane == 0) mbar_expect_tx(&bar_full[st], static_cast<uint32_t>(n_slabs) * kKSlabBytes);
+        __syncwarp();
         uint8_t* stage = k_sm + st * kStageBytes;
-        if (!lsu) {
-          if (warp == 5 && lane == 0) mbar_expect_tx(&bar_full[st], static_cast<uint32_t>(n_tma) * 512u);
-          __syncwarp();
-          const int4* rows4 = reinterpret_cast<const int4*>(rows_sm + c * kChunk);
-          for (int u = pw * 32 + lane; u < n_tma; u += 32 * kTmaWarps) {
-            const int grp = u / n_slabs, slab = u - grp * n_slabs;
-            int4 r = rows4[grp];
-            r.x = max(r.x, 0);   // masked keys read row 0: their scores are set to -inf before the softmax
-            r.y = max(r.y, 0);
-            r.z = max(r.z, 0);
-            r.w = max(r.w, 0);
-            tma_gather4(stage + slab * kKSlabBytes + grp * 512, &tmKV, &bar_full[st], unit_col(slab), r);
-          }
-        } else {
-          // one unit per warp instruction: lane = (row of the group, 16-byte piece of the 128-byte segment); the
-          // destination is the position the 128-byte swizzle gives that piece (piece index XOR row index mod 8)
-          const int r4 = lane >> 3, piece = lane & 7;
-          for (int u = n_tma + pw; u < n_inst; u += kLsuWarps) {
-            const int grp = u / n_slabs, slab = u - grp * n_slabs;
-            const int key = grp * 4 + r4;
-            const int row = max(rows_sm[c * kChunk + key], 0);
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv) + ((size_t)row * kDim + unit_col(slab)) * 2 + piece * 16;
-            cp_async_16(stage + slab * kKSlabBytes + key * 128 + ((piece ^ (key & 7)) << 4), src);
-          }
-          cp_async_commit();
-          // the previous tile's copies have landed by the time this one's are in flight: publish that tile (the
-          // arrival of tile c - 1 never waits behind the free-stage wait of tile c + 1, so the ring cannot lock up)
-          if (c > 0) {
-            cp_async_wait<1>();
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_full[(c - 1) % kStages]);
-          }
+        const int4* rows4 = reinterpret_cast<const int4*>(rows_sm + c * kChunk);
+        for (int u = (warp - 5) * 32 + lane; u < n_inst; u += 32 * kProducerWarps) {
+          const int grp = u / n_slabs, slab = u - grp * n_slabs;
+          int4 r = rows4[grp];
+          r.x = max(r.x, 0);   // masked keys read row 0: their scores are set to -inf before the softmax
+          r.y = max(r.y, 0);
+          r.z = max(r.z, 0);
+          r.w = max(r.w, 0);
+          const int col = slab < 4 ? half * 256 + slab * 64 : 512;
+          tma_gather4(stage + slab * kKSlabBytes + grp * 512, &tmKV, &bar_full[st], col, r);
         }
         lap(2);
-      }
-      if (lsu && ok && num_chunks > 0) {
-        cp_async_wait<0>();
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_full[(num_chunks - 1) % kStages]);
-      } else if (lsu) {
-        cp_async_wait<0>();   // leaving early: nothing of this warp may still be writing shared memory
       }
       if (dg) {
         for (int i = 0; i < 3; ++i) a.diag[12 + i] = dt[i];
