@@ -75,6 +75,8 @@ def test_prefill_sample_gpu():
     ("urma_sample.py", ["--self"]),
     ("urpc_echo.py", ["--calls", "50", "--psk", "ab" * 32]),
     ("umq_pingpong.py", ["--rounds", "50"]),
+    ("urpc_live_queues.py", ["--calls", "40"]),
+    ("umq_sub_queues.py", ["--connections", "16"]),
     ("dlock_counter.py", ["--threads", "3", "--increments", "50", "--fair"]),
 ])
 def test_host_library_samples(script, args, tmp_path):
