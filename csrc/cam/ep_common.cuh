@@ -93,6 +93,9 @@ struct EpLLOffsets {
   uint64_t cnt_flag[2];   // [R] uint64
   uint64_t data_flag[2];  // [R] uint64
   uint64_t comb_flag[2];  // [R] uint64
+  uint64_t exp_cnt[2];    // [E_local] uint32: row parts that have landed per local expert in the running call (every
+                          // sender adds one per 2 KiB part it stored; the receiver zeroes the words when it ends the call,
+                          // before it raises the combine flags that let the senders start the next one)
   uint64_t slab_x[2];     // [n_cap][H] fp8
   uint64_t slab_s[2];     // [n_cap][H/128] fp32
   uint64_t slab_meta[2];  // [n_cap][2] int32: owner rank, owner slot (token * K + k)
@@ -118,6 +121,8 @@ __host__ __device__ inline EpLLOffsets ep_ll_offsets(const EpLLGeom& g) {
     off = align_up_u64(off + (uint64_t)g.R * 8, 256);
     o.comb_flag[h] = off;
     off = align_up_u64(off + (uint64_t)g.R * 8, 256);
+    o.exp_cnt[h] = off;
+    off = align_up_u64(off + (uint64_t)g.E_local * 4, 256);
   }
   for (int h = 0; h < 1; ++h) {
     o.slab_x[h] = off;
@@ -133,6 +138,7 @@ __host__ __device__ inline EpLLOffsets ep_ll_offsets(const EpLLGeom& g) {
   o.cnt_flag[1] = o.cnt_flag[0];
   o.data_flag[1] = o.data_flag[0];
   o.comb_flag[1] = o.comb_flag[0];
+  o.exp_cnt[1] = o.exp_cnt[0];
   o.slab_x[1] = o.slab_x[0];
   o.slab_s[1] = o.slab_s[0];
   o.slab_meta[1] = o.slab_meta[0];
@@ -156,6 +162,9 @@ inline int fill_ll_geom(EpLLGeom* g, int R, int rank, int E, int K, int H, int T
   g->n_cap = ep_ll_n_cap(R, T_cap, K, E / R);
   return 0;
 }
+
+// 2 KiB parts per slab row: the unit in which the low-latency dispatch stores rows and counts their arrival.
+__host__ __device__ inline int ep_ll_row_parts(int H) { return (H / 128 + 15) / 16; }
 
 struct PeerTable {
   uint8_t* base[kMaxRanks];

@@ -90,6 +90,12 @@ __global__ void __launch_bounds__(kLLThreads, 1) ep_ll_combine_kernel(const LLCo
       }
     }
     if (cta_done_is_last(&a.ctrl[1], gridDim.x)) {
+      // the call ends here for this rank's slab: its arrival words go back to zero before the flags that let the
+      // peers start their next dispatch
+      uint32_t* exp_cnt = reinterpret_cast<uint32_t*>(self + a.off.exp_cnt[0]);
+      for (int i = threadIdx.x; i < g.E_local; i += blockDim.x) exp_cnt[i] = 0;
+      __threadfence_system();
+      __syncthreads();
       if (threadIdx.x < g.R) {
         st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.off.comb_flag[0]) + g.rank, tag);
       }
@@ -149,6 +155,7 @@ using namespace umdk;
 struct UmdkEpLLLayout {
   uint64_t cnt, cnt_flag, data_flag, comb_flag, slab_x, slab_s, slab_meta, comb_buf, total;
   int n_cap;
+  uint64_t exp_cnt;   // arrival words per local expert
 };
 
 // Offsets of the low-latency regions inside each rank's symmetric heap, and the heap size needed.
@@ -164,6 +171,7 @@ UMDK_API int umdk_ep_ll_layout(int R, int E, int K, int H, int T_cap, UmdkEpLLLa
   out->slab_s = o.slab_s[0];
   out->slab_meta = o.slab_meta[0];
   out->comb_buf = o.comb_buf[0];
+  out->exp_cnt = o.exp_cnt[0];
   out->total = o.total;
   out->n_cap = g.n_cap;
   return 0;

@@ -277,6 +277,16 @@ __device__ __forceinline__ bool ll_dispatch_body(const EpLLGeom& g, const EpLLOf
         }
       }
     }
+    // This part of the row has been stored at every destination: count it on each destination expert's arrival
+    // word (the warp's stores are ordered before the release by the warp barrier). An expert's rows are complete
+    // when its word has reached rows x parts-per-row; the fused kernel starts that expert's GEMM tiles then,
+    // without waiting for the rest of the slab.
+    __syncwarp();
+    if (lane < g.K && s_dx[warp * kMaxTopk + lane] != nullptr) {
+      const long long ee = own_layout ? (long long)s_eid[(size_t)t * g.K + lane] : a.topk_idx[(size_t)t * g.K + lane];
+      const int e = (int)ee, d = e / g.E_local;
+      red_add_release_sys(reinterpret_cast<uint32_t*>(peers.base[d] + off.exp_cnt[0]) + (e - d * g.E_local), 1u);
+    }
   }
   if (cta_done_is_last(&a.ctrl[3], gridDim.x)) {
     if (threadIdx.x < g.R) {

@@ -44,6 +44,9 @@ struct FusedArgs {
   float* hs;               // [n_rows_cap, F/128]
   uint32_t* tile_done;     // [>= n_rows_cap/64 + G] zero between calls (reset by this kernel)
   const uint64_t* wait_flags;
+  uint32_t* exp_cnt;       // [G] arrival words of this rank's experts (row parts landed in the running call)
+  int exp_parts;           // parts per row (ep_ll_row_parts)
+  int exp_gate;            // 1: a phase-1 item waits for ITS expert's rows only; 0: the whole slab is awaited first
   int wait_n;
   PeerTable peers;
   int R, rank;
@@ -133,12 +136,23 @@ __device__ __forceinline__ void run_phase(const CUtensorMap* tmW, const CUtensor
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      int ready_tile = -1;
+      int ready_tile = -1, ready_e = -1;
       for (int w = first; w < last && ok; w += step) {
         int e, row0, m;
         const int tile = w / NT;
         locate_tile(sh.tile_pref, sh.goff, a.G, tile, &e, &row0, &m);
         const int j = w % NT;
+        if (PH == 1 && a.exp_gate && e != ready_e) {
+          // per-expert gate: this expert's rows (all parts of all its rows, from every source) have landed; other
+          // experts' rows may still be in flight while this item computes
+          const uint32_t need = (uint32_t)(sh.goff[e + 1] - sh.goff[e]) * (uint32_t)a.exp_parts;
+          if (!wait_flag_ge_sys(a.exp_cnt + e, need)) {
+            umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_GROUP_READY, e, (int)need);
+            break;
+          }
+          ready_e = e;
+          fence_proxy_async_all();   // the rows were written with ordinary stores and are read by TMA
+        }
         if (PH == 2 && tile != ready_tile) {
           // the intermediate rows of this token tile are complete when all its phase-1 items have finished
           if (!wait_flag_ge_gpu(&a.tile_done[tile], (uint32_t)NT1)) {
@@ -468,7 +482,7 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
     __syncthreads();
   }
 
-  if (a.wait_n > 0 && (a.phase_mask & 1)) {
+  if (a.wait_n > 0 && (a.phase_mask & 1) && !a.exp_gate) {
     if (threadIdx.x < a.wait_n) {
       if (!wait_flag_ge_sys(a.wait_flags + threadIdx.x, tag)) {
         umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_GROUP_READY, threadIdx.x, (int)epoch);
@@ -544,10 +558,16 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant
   // ---- combine tail ----
   if (a.phase_mask & 1) {
     if (cta_done_is_last(&a.ctrl[1], gridDim.x)) {
+      // Every CTA is through with the slab: the arrival words go back to zero BEFORE the combine flags go out - a
+      // peer starts its next call (and adds to these words again) only after it has seen this rank's flag.
+      if (a.exp_cnt != nullptr)
+        for (int i = threadIdx.x; i < a.G; i += blockDim.x) a.exp_cnt[i] = 0;
+      for (int i = threadIdx.x; i < tiles; i += blockDim.x) a.tile_done[i] = 0;  // counters start from zero next call
+      __threadfence_system();
+      __syncthreads();
       if (threadIdx.x < a.R) {
         st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.comb_flag_off) + a.rank, tag);
       }
-      for (int i = threadIdx.x; i < tiles; i += blockDim.x) a.tile_done[i] = 0;  // counters start from zero next call
     }
   }
   if (!(a.phase_mask & 2)) return;
@@ -652,6 +672,23 @@ UMDK_API int umdk_moe_fused(const UmdkMoeFusedParams* p, void* stream) {
   a.status = p->status;
   a.diag = p->diag;
   a.fuse_dispatch = p->disp_x != nullptr ? 1 : 0;
+  {
+    // the arrival words live in the low-latency region of this rank's heap (the dispatch, fused or not, adds to them)
+    EpLLGeom lg;
+    if (fill_ll_geom(&lg, p->R, p->rank, p->G * p->R, p->Kt, p->H, p->T_cap) == 0 && a.peers.base[p->rank] != nullptr) {
+      a.exp_cnt = reinterpret_cast<uint32_t*>(a.peers.base[p->rank] + ep_ll_offsets(lg).exp_cnt[0]);
+      a.exp_parts = ep_ll_row_parts(p->H);
+      static const int gate = [] {
+        const char* e = getenv("UMDK_LL_EXPERT_GATE");
+        return (e && e[0] == '0') ? 0 : 1;
+      }();
+      a.exp_gate = (gate && p->wait_n > 0) ? 1 : 0;   // callers that pass no flags to wait for gate nothing
+    } else {
+      a.exp_cnt = nullptr;
+      a.exp_parts = 0;
+      a.exp_gate = 0;
+    }
+  }
   if (a.fuse_dispatch) {
     if (p->E != p->G * p->R || p->T > 2048 || p->T > p->T_cap || !p->recv_per_expert || !p->group_off_out)
       return -UMDK_ERR_BAD_ARG;

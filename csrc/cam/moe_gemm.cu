@@ -51,6 +51,7 @@ struct MoeGemmArgs {
   int R, rank;
   uint64_t comb_buf_off[2];   // [T_cap][Kt][Nout] bf16 on every rank
   uint64_t comb_flag_off[2];  // [R] uint64 on every rank
+  uint32_t* exp_cnt;          // [G] arrival words of the low-latency dispatch (zeroed here when the call ends)
   const int* row_meta;        // [n_rows_cap][2]: owner rank, owner slot (token * Kt + k)
   const int64_t* topk_idx;    // [T, Kt] on the owner
   const float* topk_w;        // [T, Kt]
@@ -389,6 +390,11 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     // ---- completion flags to every peer, then the owner-side weighted reduction ----
     if (a.phase_mask & 1) {
       if (cta_done_is_last(&a.ctrl[1], gridDim.x)) {
+        // the slab has been consumed: its arrival words return to zero before the flags that let the peers go on
+        if (a.exp_cnt != nullptr)
+          for (int i = threadIdx.x; i < a.G; i += blockDim.x) a.exp_cnt[i] = 0;
+        __threadfence_system();
+        __syncthreads();
         if (threadIdx.x < a.R) {
           st_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.comb_flag_off[h]) + a.rank, tag);
         }
@@ -522,6 +528,12 @@ UMDK_API int umdk_moe_gemm(const UmdkMoeGemmParams* p, void* stream) {
   a.comb_buf_off[1] = p->comb_buf_off[1];
   a.comb_flag_off[0] = p->comb_flag_off[0];
   a.comb_flag_off[1] = p->comb_flag_off[1];
+  a.exp_cnt = nullptr;
+  if (p->mode == 2 && p->R >= 1 && p->R <= kMaxRanks && a.peers.base[p->rank] != nullptr) {
+    EpLLGeom lg;
+    if (fill_ll_geom(&lg, p->R, p->rank, p->G * p->R, p->Kt, p->Nout, p->T_cap) == 0)
+      a.exp_cnt = reinterpret_cast<uint32_t*>(a.peers.base[p->rank] + ep_ll_offsets(lg).exp_cnt[0]);
+  }
   a.row_meta = p->row_meta;
   a.topk_idx = p->topk_idx;
   a.topk_w = p->topk_w;

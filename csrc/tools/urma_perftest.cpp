@@ -53,6 +53,7 @@ struct GpuRt {
   int (*malloc_)(void**, size_t) = nullptr;
   int (*memset_)(void*, int, size_t) = nullptr;
   int (*sync)() = nullptr;
+  int (*memcpy_)(void*, const void*, size_t, int) = nullptr;
   bool load() {
     if (malloc_) return true;
     void* h = nullptr;
@@ -63,7 +64,8 @@ struct GpuRt {
     malloc_ = reinterpret_cast<int (*)(void**, size_t)>(dlsym(h, "cudaMalloc"));
     memset_ = reinterpret_cast<int (*)(void*, int, size_t)>(dlsym(h, "cudaMemset"));
     sync = reinterpret_cast<int (*)()>(dlsym(h, "cudaDeviceSynchronize"));
-    return set_device && malloc_ && memset_ && sync;
+    memcpy_ = reinterpret_cast<int (*)(void*, const void*, size_t, int)>(dlsym(h, "cudaMemcpy"));
+    return set_device && malloc_ && memset_ && sync && memcpy_;
   }
 };
 static GpuRt g_rt;
@@ -81,6 +83,14 @@ static uint8_t* alloc_buf(const std::string& dev, size_t bytes, int fill) {
       g_rt.sync() != 0)
     return nullptr;
   return static_cast<uint8_t*>(p);
+}
+
+// The first `bytes` of a buffer as host memory (a copy for GPU buffers).
+static std::vector<uint8_t> host_copy(const std::string& dev, const uint8_t* p, size_t bytes) {
+  std::vector<uint8_t> out(bytes);
+  if (gpu_index(dev) < 0) memcpy(out.data(), p, bytes);
+  else if (g_rt.sync() != 0 || g_rt.memcpy_(out.data(), p, bytes, 4 /* cudaMemcpyDefault */) != 0) out.clear();
+  return out;
 }
 
 static int wait_n(urma_simple_ep_t* ep, int want, int* bad) {
@@ -359,7 +369,11 @@ int main(int argc, char** argv) {
     }
     close(tcp);
   }
-  const bool data_ok = !(!two_sided && !atomic && opc == URMA_OPC_WRITE && eb && memcmp(mem_a.data(), mem_b.data(), size) != 0);
+  bool data_ok = true;
+  if (!two_sided && !atomic && opc == URMA_OPC_WRITE && eb) {   // a write must have carried the source buffer over
+    const std::vector<uint8_t> ha = host_copy(dev, mem_a.data(), size), hb = host_copy(peer_dev, mem_b.data(), size);
+    data_ok = ha.size() == size && hb.size() == size && memcmp(ha.data(), hb.data(), size) == 0;
+  }
   // tear down in the reverse order of the bring-up (imports, endpoints, segments, contexts)
   for (auto* t : ex_t) urma_unimport_jetty(t);
   urma_unimport_jetty(tj);

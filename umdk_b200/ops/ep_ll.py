@@ -33,7 +33,7 @@ MAX_RANKS = 32
 class _LLLayout(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in
                 ("cnt", "cnt_flag", "data_flag", "comb_flag", "slab_x", "slab_s", "slab_meta", "comb_buf", "total")] + \
-               [("n_cap", ctypes.c_int)]
+               [("n_cap", ctypes.c_int), ("exp_cnt", ctypes.c_uint64)]
 
 
 class _LLDispatchParams(ctypes.Structure):
@@ -151,7 +151,7 @@ class EpLowLatency(Recoverable):
     """Per-rank state of the low-latency MoE path at a fixed geometry."""
 
     _epoch_words = {"ctrl": (0,)}
-    _zero_between_calls = ("layout_bar", "tile_done")
+    _zero_between_calls = ("layout_bar", "tile_done", "exp_cnt")
 
     def __init__(self, heap: SymmetricHeap, num_experts: int, top_k: int, hidden: int, ffn: int, t_cap: int,
                  dispatch_ctas: int = 32, gemm_ctas: int = 0, fold_shared: bool = False):
@@ -195,6 +195,10 @@ class EpLowLatency(Recoverable):
         self.sh_off = torch.tensor([0, 0], dtype=torch.int32, device=dev)
         self.sh_hq = torch.empty(t_cap, ffn, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
         self.sh_hs = torch.empty(t_cap, ffn // 128, dtype=torch.float32, device=dev)
+        # per-expert arrival words in this rank's heap (added to by every sender's dispatch, zeroed by whatever ends
+        # the call here); part of what reset() clears
+        from ..utils.rawtensor import from_ptr
+        self.exp_cnt = from_ptr(self._local(self.lay.exp_cnt), (self.E_local,), torch.int32, dev)
 
     @staticmethod
     def heap_bytes(R: int, E: int, K: int, H: int, T_cap: int, fold_shared: bool = False) -> int:
