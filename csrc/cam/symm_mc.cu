@@ -288,8 +288,10 @@ UMDK_API int umdk_mc_destroy(void* heap) {
   return 0;
 }
 
-// Duplicates descriptor `fd` of process `pid` into this process (pidfd_open + pidfd_getfd; same user, or root).
-// Returns the new descriptor or a negative errno.
+// Duplicates descriptor `fd` of process `pid` into this process (pidfd_open + pidfd_getfd). The kernel allows it to
+// a process that may ptrace the other one: root, or the same user where the ptrace scope permits it; where it does
+// not, this returns -EPERM, the heap set-up fails on every rank together and the callers stay on the peer-pointer
+// algorithms. Returns the new descriptor or a negative errno.
 UMDK_API int umdk_fd_from_process(int pid, int fd) {
 #if defined(SYS_pidfd_open) && defined(SYS_pidfd_getfd)
   const int pidfd = static_cast<int>(syscall(SYS_pidfd_open, pid, 0));
