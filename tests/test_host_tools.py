@@ -63,6 +63,10 @@ def test_urpc_admin_reads_the_management_socket(tmp_path):
         assert rc == 0 and "protocol versions 1..2" in out, out
         rc, out = _run([BIN / "urpc_admin", sock, "channels"], tmp_path)
         assert rc == 0 and "channel 0 attached 1" in out, out
+        rc, out = _run([BIN / "urpc_admin", sock, "sessions"], tmp_path)
+        assert rc == 0 and "proto 2" in out and "lanes" in out, out
+        rc, out = _run([BIN / "urpc_admin", sock, "tasks"], tmp_path)
+        assert rc == 0 and "tasks_started" in out and "sessions_retired" in out, out
         srv.wait(timeout=30)
     finally:
         if srv.poll() is None:
