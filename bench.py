@@ -193,6 +193,7 @@ def time_product(hx, model, inputs, steps, warmup, repeats, count_launches=False
                 model.kvm.wait(l)
 
     k = 0
+    hx.barrier()   # the ranks built their models at their own pace: meet before the first step
     for _ in range(warmup):
         model.step(dev_tokens[k % ring], dev_idx[k % ring])
         model.prefetch(dev_idx[(k + 1) % ring], after_compute=False)

@@ -72,3 +72,10 @@ int make_tmap_3d(CUtensorMap* out, TmapDtype dt, const void* base, uint64_t inne
 int sm_count();
 
 }  // namespace umdk
+
+// Budget of the waits at which a collective call MEETS its peers for the first time (the count exchange of the
+// expert-parallel dispatches): ranks may enter a step seconds apart (allocation, graph capture, host work), so this
+// wait is far more patient than the waits inside a call, which see their data within microseconds once every rank
+// has arrived. Default 16 s; tests that make a wait run out set it to a fraction of a second.
+UMDK_API void umdk_set_rendezvous_timeout_ms(int ms);
+long long umdk_rendezvous_cycles();

@@ -205,6 +205,7 @@ UMDK_API int umdk_ep_ll_dispatch(const UmdkEpLLDispatchParams* p, void* stream) 
   a.io.recv_per_expert = p->recv_per_expert;
   a.io.ctrl = p->ctrl;
   a.io.status = p->status;
+  a.io.meet_cycles = umdk_rendezvous_cycles();
   a.io.phase_mask = p->phase_mask ? p->phase_mask : 3;
   int grid = p->num_ctas > 0 ? p->num_ctas : 32;
   if (grid > sm_count()) grid = sm_count();

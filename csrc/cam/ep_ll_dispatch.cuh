@@ -22,6 +22,7 @@ struct LLDispatchIO {
   uint32_t* ctrl;             // [0] epoch (read), [3] send-done counter
   int* status;
   int phase_mask;             // bit0: publish counts; bit1: wait counts, push rows, raise data flags
+  long long meet_cycles;      // budget of the wait for the peers' counts (where the ranks meet); 0 = the usual budget
 };
 
 // Shared-memory bytes the body needs: four int tables over the experts, destination pointers per warp, and (layout
@@ -161,7 +162,7 @@ __device__ __forceinline__ bool ll_dispatch_body(const EpLLGeom& g, const EpLLOf
 
   if (threadIdx.x < g.R) {
     const uint64_t* f = reinterpret_cast<const uint64_t*>(self + off.cnt_flag[0]) + threadIdx.x;
-    if (!wait_flag_ge_sys(f, tag)) {
+    if (!wait_flag_ge_sys(f, tag, a.meet_cycles > 0 ? a.meet_cycles : kSpinLimitCycles)) {
       umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_COUNT, threadIdx.x, (int)epoch);
       s_ok = 0;
     }

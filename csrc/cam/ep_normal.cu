@@ -191,6 +191,7 @@ struct DispatchArgs {
   EpGeom g;
   EpNormalOffsets off;
   PeerTable peers;
+  long long meet_cycles;       // budget of the wait for the peers' counts (where the ranks meet)
   // inputs on this rank
   const __nv_bfloat16* x;      // [T, H]
   const int64_t* topk_idx;     // [T, K]
@@ -484,7 +485,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(const Dispat
   // ---- receive: wait for every source's counts, build offsets ----
   if (rtid < g.R) {
     const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.notify_flag[h]) + rtid;
-    if (!wait_flag_ge_sys(f, tag)) {
+    if (!wait_flag_ge_sys(f, tag, a.meet_cycles)) {
       umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_COUNT, rtid, (int)epoch);
       s_ok_recv = 0;
     }
@@ -971,6 +972,7 @@ struct UmdkEpDispatchParams {
 
 UMDK_API int umdk_ep_dispatch(const UmdkEpDispatchParams* p, void* stream) {
   DispatchArgs a;
+  a.meet_cycles = umdk_rendezvous_cycles();
   if (int rc = fill_geom(&a.g, p->R, p->rank, p->E, p->K, p->H, p->cap, p->quant)) return rc;
   if (p->T > p->cap) return -UMDK_ERR_BAD_ARG;
   a.off = ep_normal_offsets(layout_geom(a.g));
@@ -1064,6 +1066,7 @@ struct NotifyArgs {
   EpGeom g;
   EpNormalOffsets off;
   PeerTable peers;
+  long long meet_cycles;       // budget of the wait for the peers' counts
   const int* num_per_expert;   // [E]
   const int* num_per_rank;     // [R]
   int* recv_count;             // [E_local * R] inclusive prefix, index = le * R + src
@@ -1102,7 +1105,7 @@ __global__ void __launch_bounds__(256, 1) ep_notify_kernel(const NotifyArgs a) {
   uint8_t* self = a.peers.base[g.rank];
   if (threadIdx.x < g.R) {
     const uint64_t* f = reinterpret_cast<const uint64_t*>(self + a.off.snotify_flag[h]) + threadIdx.x;
-    if (!wait_flag_ge_sys(f, tag)) {
+    if (!wait_flag_ge_sys(f, tag, a.meet_cycles)) {
       umdk_set_status(a.status, UMDK_ERR_TIMEOUT, UMDK_PH_DISPATCH_COUNT, threadIdx.x, (int)epoch);
       s_ok = 0;
     }
@@ -1152,6 +1155,7 @@ struct UmdkEpNotifyParams {
 
 UMDK_API int umdk_ep_notify(const UmdkEpNotifyParams* p, void* stream) {
   NotifyArgs a;
+  a.meet_cycles = umdk_rendezvous_cycles();
   if (int rc = fill_geom(&a.g, p->R, p->rank, p->E, p->K, p->H, p->cap, 0)) return rc;
   if (a.g.E_local * a.g.R > 1024) return -UMDK_ERR_BAD_ARG;
   a.off = ep_normal_offsets(layout_geom(a.g));

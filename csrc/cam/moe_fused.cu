@@ -706,6 +706,7 @@ UMDK_API int umdk_moe_fused(const UmdkMoeFusedParams* p, void* stream) {
     a.disp.ctrl = p->ctrl;
     a.disp.status = p->status;
     a.disp.phase_mask = 3;
+    a.disp.meet_cycles = umdk_rendezvous_cycles();
   } else {
     if (a.phase_mask & 12) return -UMDK_ERR_BAD_ARG;
     a.ll_geom = EpLLGeom{};

@@ -42,6 +42,10 @@ UMDK_API int umdk_symm_unimport(void* p) {
   return 0;
 }
 
+static long long g_rendezvous_ms = 16000;
+UMDK_API void umdk_set_rendezvous_timeout_ms(int ms) { g_rendezvous_ms = ms > 0 ? ms : 16000; }
+long long umdk_rendezvous_cycles() { return g_rendezvous_ms * 2000000LL; }   // the SM clock is just under 2 GHz
+
 UMDK_API int umdk_ipc_handle_bytes() { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
 
 // Pinned, device-mapped host memory used to mirror small results (receive counts) to the CPU without a

@@ -68,6 +68,7 @@ def main():
     wt = ExpertWeights(*(t[rank * el:(rank + 1) * el].cuda().contiguous() for t in (w1q, w1s, w2q, w2s)))
     want = ref.ref_fused_moe(xs[rank], idxs[rank], ws[rank], w1q, w1s, w2q, w2s)
     x, idx, w = xs[rank].cuda(), idxs[rank].cuda(), ws[rank].cuda()
+    dist.barrier()   # the CPU reference above takes each rank a different time
     for rnd in range(4):
         out, _, cnt = ll.moe(x, idx, w, wt)
         torch.cuda.synchronize()

@@ -375,7 +375,7 @@ def test_buffer_low_latency_dispatch_then_combine_without_host_sync():
 
 
 def test_timed_out_wait_poisons_the_object_until_reset():
-    """A receive phase whose counts nobody publishes runs out of its (about two-second) cycle budget and reports it;
+    """A receive phase whose counts nobody publishes runs out of its cycle budget (one second here) and reports it;
     the object then refuses further launches until reset() has put its counters and epoch words back, after which
     a normal call matches the oracle again. Nothing faults and the context stays usable."""
     from umdk_b200.ops.ep import KernelStatusError
@@ -387,10 +387,16 @@ def test_timed_out_wait_poisons_the_object_until_reset():
     heaps = SymmetricHeap.virtual(EpLowLatency.heap_bytes(R, E, K, H, T), R)
     try:
         st = [EpLowLatency(h, E, K, H, F, T) for h in heaps]
-        # rank 0 waits for rank 1's counts, which are never published
-        st[0].dispatch(xs[0].cuda(), idxs[0].cuda(), phase_mask=1)
-        st[0].dispatch(xs[0].cuda(), idxs[0].cuda(), phase_mask=2)
-        torch.cuda.synchronize()
+        # rank 0 waits for rank 1's counts, which are never published. The wait at which the ranks of a call meet is
+        # patient by default (ranks may enter a step seconds apart); for this test it gets a one-second budget.
+        from umdk_b200 import _native
+        _native.cam().umdk_set_rendezvous_timeout_ms(1000)
+        try:
+            st[0].dispatch(xs[0].cuda(), idxs[0].cuda(), phase_mask=1)
+            st[0].dispatch(xs[0].cuda(), idxs[0].cuda(), phase_mask=2)
+            torch.cuda.synchronize()
+        finally:
+            _native.cam().umdk_set_rendezvous_timeout_ms(16000)
         with pytest.raises(KernelStatusError, match="timeout"):
             st[0].check()
         with pytest.raises(KernelStatusError, match="poisoned"):
