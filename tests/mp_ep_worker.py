@@ -31,6 +31,7 @@ def main():
     st = EpNormal(heap, E, K, H, T)
     x, idx, w = xs[rank].cuda(), idxs[rank].cuda(), ws[rank].cuda()
     want = ref.ref_dispatch_all(xs, idxs, ws, E, True)
+    dist.barrier()   # the CPU oracle above takes each rank a different time
     for rnd in range(3):
         out = st.dispatch(x, idx, w, quant=True, sync_counts=True)
         n = out.num_recv
@@ -83,4 +84,11 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException as e:   # the launcher only keeps the tail of the output: say what failed in one line
+        import traceback
+        tb = traceback.extract_tb(e.__traceback__)[-1]
+        print(f"MP_WORKER_ERROR rank={os.environ.get('RANK')} {type(e).__name__}: {str(e)[:300]} "
+              f"at {os.path.basename(tb.filename)}:{tb.lineno}", flush=True)
+        raise

@@ -103,4 +103,11 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException as e:   # the launcher only keeps the tail of the output: say what failed in one line
+        import traceback
+        tb = traceback.extract_tb(e.__traceback__)[-1]
+        print(f"MP_WORKER_ERROR rank={os.environ.get('RANK')} {type(e).__name__}: {str(e)[:300]} "
+              f"at {os.path.basename(tb.filename)}:{tb.lineno}", flush=True)
+        raise

@@ -23,14 +23,16 @@ def test_ep_kernels_across_gpus():
     n = min(torch.cuda.device_count(), 8)
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     rc, out = _torchrun("mp_ep_worker.py", n)
-    assert rc == 0 and "MP_EP_OK" in out, out[-4000:]
+    errors = "\n".join(ln for ln in out.splitlines() if "MP_WORKER_ERROR" in ln)
+    assert rc == 0 and "MP_EP_OK" in out, errors + "\n" + out[-3000:]
 
 
 def test_tp_kernels_allreduce_and_urma_across_gpus():
     n = min(torch.cuda.device_count(), 8)
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     rc, out = _torchrun("mp_tp_worker.py", n)
-    assert rc == 0 and "MP_TP_OK" in out, out[-4000:]
+    errors = "\n".join(ln for ln in out.splitlines() if "MP_WORKER_ERROR" in ln)
+    assert rc == 0 and "MP_TP_OK" in out, errors + "\n" + out[-3000:]
     # on GPUs that can join an NVLink multicast object the in-switch all-reduce must have run on the package's own
     # multicast heap: a silent fall-back to the peer-pointer algorithms would hide a broken heap
     from umdk_b200 import _native
