@@ -281,7 +281,9 @@ __device__ __forceinline__ bool ll_dispatch_body(const EpLLGeom& g, const EpLLOf
     // This part of the row has been stored at every destination: count it on each destination expert's arrival
     // word (the warp's stores are ordered before the release by the warp barrier). An expert's rows are complete
     // when its word has reached rows x parts-per-row; the fused kernel starts that expert's GEMM tiles then,
-    // without waiting for the rest of the slab.
+    // without waiting for the rest of the slab. Every lane fences its own stores at system scope first: the counting
+    // lanes' release alone does not wait for stores that OTHER lanes still have in flight to the peer.
+    __threadfence_system();
     __syncwarp();
     if (lane < g.K && s_dx[warp * kMaxTopk + lane] != nullptr) {
       const long long ee = own_layout ? (long long)s_eid[(size_t)t * g.K + lane] : a.topk_idx[(size_t)t * g.K + lane];
