@@ -420,3 +420,28 @@ def test_log_routing_configs_match_what_the_libraries_emit():
     p = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, UMQ_LOG_LEVEL="4"), capture_output=True,
                        text=True, timeout=120)
     assert re.search(r"^\[UMQ\]\[(ERR|WARN|NOTICE|INFO|DEBUG)\] ", p.stderr, re.M), p.stderr[-500:]
+
+
+def test_descriptor_passing_for_the_multicast_heap():
+    """The multicast symmetric heap hands memory descriptors from process to process with pidfd_getfd: duplicate a
+    pipe's write end out of a child process and write through it. On a machine without GPUs the heap itself reports
+    that multicast is not supported (and `SymmetricHeap.multicast` would raise on every rank together)."""
+    lib = _native.cam()
+    assert lib.umdk_mc_supported() in (0, 1)
+    r, w = os.pipe()
+    os.set_inheritable(w, True)
+    child = subprocess.Popen([sys.executable, "-c", "import sys,time; sys.stdin.readline()"], stdin=subprocess.PIPE,
+                             pass_fds=(w,))
+    try:
+        got = lib.umdk_fd_from_process(child.pid, w)     # the child holds descriptor number `w` too
+        assert got >= 0, got
+        os.close(w)
+        os.write(got, b"through the duplicate")
+        assert os.read(r, 64) == b"through the duplicate"
+        os.close(got)
+        assert lib.umdk_fd_from_process(child.pid, 987654) < 0   # no such descriptor there
+    finally:
+        child.stdin.write(b"\n")
+        child.stdin.flush()
+        child.wait(timeout=20)
+        os.close(r)
