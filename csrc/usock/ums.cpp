@@ -490,6 +490,19 @@ std::shared_ptr<Link> link_pick(const std::string& key, uint64_t salt, uint32_t*
     llc_push(grp.front().get(), LLC_ADD_LINK, 0, 0, 0, l->name.c_str());   // announce it on the group's first link
   grp.push_back(l);
   g_links["c:" + l->name] = l;
+  static const bool cleanup_registered = [] {
+    // a process that exits with connections still open must not leave its link files behind
+    atexit([] {
+      std::lock_guard<std::mutex> lk(g_mu);
+      for (auto& kv : g_links)
+        if (kv.second->owner && kv.second->shm) {
+          kv.second->shm->state.store(LINK_DELETED);
+          unlink(kv.second->path.c_str());
+        }
+    });
+    return true;
+  }();
+  (void)cleanup_registered;
   ++g_stats.links_created;
   l->shm->slot_used.fetch_or(1u);
   *slot = 0;
