@@ -1,6 +1,7 @@
 // umq_perftest: latency / message-rate test and self-check of the UMQ layer between two queues of one process (or
 // of two threads), in the spirit of the reference's src/urpc/tools/perftest umq_perftest.
 //   umq_perftest [--size N] [--iters N] [--flow-control] [--pro] [--selftest]
+#include <sched.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -169,6 +170,70 @@ int main(int argc, char** argv) {
     if (h) umq_buf_free(h);
     if (umq_buf_alloc(UMQ_MAX_MSG_SIZE + 1, 1, a) != nullptr) rc = fail("oversized request must be refused");
     if (umq_unbind(a) != UMQ_SUCCESS || umq_state_get(a) != UMQ_STATE_IDLE) rc = fail("unbind");
+    // main / sub queues over the jetty pool, with one message large enough to be pulled by the receiver
+    {
+      umq_create_option_t mo{};
+      snprintf(mo.name, sizeof(mo.name), "main");
+      mo.rx_depth = mo.tx_depth = 64;
+      mo.create_flag = UMQ_CREATE_FLAG_MAIN | UMQ_CREATE_FLAG_SHARE_TRANSPORT;
+      const uint64_t ma = umq_create(&mo), mb = umq_create(&mo);
+      uint8_t info[UMQ_BIND_INFO_SIZE];
+      uint64_t sa[4], sb[4];
+      bool ok = ma && mb;
+      for (int i = 0; i < 4 && ok; ++i) {
+        umq_create_option_t so{};
+        snprintf(so.name, sizeof(so.name), "sub%d", i);
+        so.rx_depth = so.tx_depth = 8;
+        so.create_flag = UMQ_CREATE_FLAG_SUB;
+        so.share_rq_umqh = ma;
+        sa[i] = umq_create(&so);
+        so.share_rq_umqh = mb;
+        sb[i] = umq_create(&so);
+        ok = sa[i] && sb[i];
+        uint32_t n = ok ? umq_bind_info_get(sb[i], info, sizeof(info)) : 0;
+        ok = ok && n && umq_bind(sa[i], info, n) == UMQ_SUCCESS;
+        n = ok ? umq_bind_info_get(sa[i], info, sizeof(info)) : 0;
+        ok = ok && n && umq_bind(sb[i], info, n) == UMQ_SUCCESS;
+      }
+      auto xfer = [&](uint64_t from, uint64_t to, uint32_t bytes, char fill) {
+        umq_buf_t* b = umq_buf_alloc(bytes, 1, from);
+        if (!b) return false;
+        memset(b->buf_data, fill, bytes);
+        b->data_size = b->total_data_size = bytes;
+        umq_buf_t* bad = nullptr;
+        for (int tries = 0; umq_enqueue(from, b, &bad) != UMQ_SUCCESS; ++tries) {
+          if (tries > 100000) return false;
+          sched_yield();
+        }
+        for (int tries = 0; tries < 2000000; ++tries) {
+          umq_buf_t* r = umq_dequeue(to);
+          if (r) {
+            const bool good = r->data_size == bytes && r->buf_data[0] == fill && r->buf_data[bytes - 1] == fill;
+            umq_buf_free(r);
+            umq_dequeue(from);   // lets the sender see its completion
+            return good;
+          }
+          umq_dequeue(from);
+        }
+        return false;
+      };
+      for (int round = 0; round < 20 && ok; ++round)
+        for (int i = 0; i < 4 && ok; ++i) ok = xfer(sa[i], sb[i], 300 + round, 'a' + i) && xfer(sb[i], sa[i], 700, 'A' + i);
+      ok = ok && xfer(sa[2], sb[2], 200000, 'P');   // beyond the receive buffer size: descriptor + read
+      umq_io_stats_t ps{};
+      if (ok) umq_stats_io_get(sb[2], &ps);
+      umq_jetty_pool_stats_t jp{};
+      umq_jetty_pool_stats_get(&jp);
+      if (!ok || ps.pull_rx != 1 || jp.total_num != 2 || jp.sub_queues != 8 || jp.acc_alloc_num < 160)
+        rc = fail("sub queues / jetty pool / pulled message");
+      if (umq_destroy(ma) == UMQ_SUCCESS) rc = fail("a main queue must outlive its sub queues");
+      for (int i = 0; i < 4; ++i) {
+        if (sa[i]) umq_destroy(sa[i]);
+        if (sb[i]) umq_destroy(sb[i]);
+      }
+      if (ma) umq_destroy(ma);
+      if (mb) umq_destroy(mb);
+    }
   }
   umq_destroy(a);
   umq_destroy(b);

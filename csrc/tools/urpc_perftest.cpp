@@ -158,6 +158,40 @@ int main(int argc, char** argv) {
     wr.func_id = 7;
     if (urpc_func_call(ch, &wr, &sync) != 0 || rlen != size || rsp[0] != arg[size - 1] || rsp[size - 1] != arg[0])
       rc = fail("manual return");
+    // a queue pair joins the attached channel through the control plane, carries calls, and leaves again while
+    // the server thread keeps polling (protocol version 2; the task engine serves both requests)
+    {
+      urpc_channel_cfg_t cc{};
+      urpc_channel_cfg_get(ch, &cc);
+      if (cc.proto_version >= 2) {
+        urpc_ctl_stats_t t0{}, t1{};
+        urpc_ctl_stats_get(&t0);
+        const uint64_t lq = urpc_queue_create(nullptr);
+        if (!lq || urpc_channel_queue_add(ch, lq) != URPC_SUCCESS) rc = fail("queue add on an attached channel");
+        wr.func_id = 1;
+        for (int i = 0; i < 50 && rc == 0; ++i)
+          if (urpc_func_call_on(ch, lq, &wr, &sync) != 0 || rlen != size) rc = fail("call on the new lane");
+        for (int i = 0; i < 8 && rc == 0; ++i) {   // calls in flight while the lane leaves
+          urpc_call_option_t async_opt{2000, 0, nullptr, 0, nullptr};
+          if (urpc_func_call_on(ch, lq, &wr, &async_opt) < 0) rc = fail("async call on the new lane");
+        }
+        if (rc == 0 && urpc_channel_queue_rm(ch, lq) != URPC_SUCCESS) rc = fail("queue remove on an attached channel");
+        int answered = 0;
+        for (int tries = 0; tries < 2000 && answered < 8 && rc == 0; ++tries) {
+          const int n = urpc_func_poll(ch, m, 4);
+          for (int i = 0; i < n; ++i) {
+            answered += m[i].event == URPC_POLL_RSP;
+            urpc_msg_release(&m[i]);
+          }
+          if (n == 0) usleep(200);
+        }
+        if (rc == 0 && answered != 8) rc = fail("calls in flight on a leaving lane lost their answers");
+        if (lq) urpc_queue_destroy(lq);
+        urpc_ctl_stats_get(&t1);
+        if (rc == 0 && (t1.tasks_done - t0.tasks_done != 2 || t1.tasks_live != 0)) rc = fail("control task accounting");
+        if (urpc_func_call(ch, &wr, &sync) != 0) rc = fail("call after the lane left");
+      }
+    }
     // a call that the server never answers times out, synchronously and asynchronously
     wr.func_id = 9;
     urpc_call_option_t quick{200, 1, rsp.data(), (uint32_t)rsp.size(), &rlen};

@@ -300,6 +300,7 @@ struct Queue {
   std::unordered_map<uint32_t, Queue*> subs;   // main queue: sub queues by number (under mu)
   uint32_t next_sub = 1;
   bool in_pool = false;             // main queue: its endpoint serves the jetty pool
+  bool closing = false;             // main queue: being destroyed, takes no new sub queues (under mu)
   struct Event {
     int kind;                       // 0 receive, 1 read done, 2 send done
     int st;
@@ -1066,7 +1067,7 @@ uint64_t umq_create(const umq_create_option_t* opt) {
     q->h = g.next_h.fetch_add(1);
     {
       std::lock_guard<std::mutex> l(m->mu);
-      if (m->subs.size() >= 0xfffe) {
+      if (m->subs.size() >= 0xfffe || m->closing) {
         delete q;
         return UMQ_INVALID_HANDLE;
       }
@@ -1118,11 +1119,17 @@ int umq_destroy(uint64_t h) {
     auto it = g.queues.find(h);
     if (it == g.queues.end()) return UMQ_ERR_EINVAL;
     q = it->second;
-    if (!q->tops && q->ep) {   // a main queue goes after its sub queues
-      std::lock_guard<std::mutex> ql(q->mu);
-      if (!q->subs.empty()) return UMQ_ERR_ESTATE;
-    }
-    g.queues.erase(it);
+  }
+  if (!q->tops && q->ep) {
+    // A main queue goes after its sub queues. (The queue's lock is taken without the table lock: progress() looks
+    // queues up in the table while it holds a queue's lock.)
+    std::lock_guard<std::mutex> ql(q->mu);
+    if (!q->subs.empty()) return UMQ_ERR_ESTATE;
+    q->closing = true;   // no new sub queue attaches from here on
+  }
+  {
+    std::lock_guard<std::mutex> l(g.mu);
+    if (!g.queues.erase(h)) return UMQ_ERR_EINVAL;   // somebody else destroyed it in between
   }
   if (!q->tops && q->in_pool) {
     std::unique_lock<std::shared_mutex> pl(g_jpool.mu);   // waits for posts that borrowed the endpoint

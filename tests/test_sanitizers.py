@@ -29,6 +29,10 @@ def test_address_and_leak_sanitizer_clean(tmp_path):
     outs = _build.build_sanitized("address")
     rc, out = _run(outs["tool_umq_perftest"], ["--iters", "500", "--flow-control"], tmp_path)
     assert rc == 0 and "umq_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
+    # self-test flavour: huge buffers, sub queues over the jetty pool, a pulled large message
+    rc, out = _run(outs["tool_umq_perftest"], ["--iters", "300", "--selftest"], tmp_path)
+    assert rc == 0 and "umq_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
+    # (includes a queue pair joining and leaving the attached channel through the control-plane task engine)
     rc, out = _run(outs["tool_urpc_perftest"], ["--selftest", "--iters", "300"], tmp_path)
     assert rc == 0 and "urpc_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
     rc, out = _run(outs["tool_urpc_perftest"], ["--iters", "600", "--queues", "3"], tmp_path)   # three queue pairs
@@ -43,3 +47,8 @@ def test_thread_sanitizer_clean(tmp_path):
         assert rc == 0 and "umq_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
     rc, out = _run(outs["tool_urpc_perftest"], ["--iters", "300", "--queues", "3"], tmp_path)
     assert rc == 0 and "urpc_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
+    # control-plane task engine against the polling server thread and the client: queue add / remove on a live channel
+    rc, out = _run(outs["tool_urpc_perftest"], ["--selftest", "--iters", "200"], tmp_path)
+    assert rc == 0 and "urpc_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
+    rc, out = _run(outs["tool_umq_perftest"], ["--iters", "200", "--selftest"], tmp_path)
+    assert rc == 0 and "umq_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
