@@ -46,11 +46,12 @@ static int run(const Api& a, const char* name, size_t size, int iters, double* l
   if (bind(ls, (sockaddr*)&ad, sizeof(ad)) || a.listen_(ls, 8)) return fail("listen");
   socklen_t l = sizeof(ad);
   getsockname(ls, (sockaddr*)&ad, &l);
-  bool ok = true;
+  std::atomic<bool> ok{true};   // written by both threads
   std::thread srv([&] {
     const int c = a.accept_(ls, nullptr, nullptr);
     std::vector<char> b(size);
-    for (int i = 0; i < iters && ok; ++i) ok &= xfer_all(a, c, b.data(), size, false) && xfer_all(a, c, b.data(), size, true);
+    for (int i = 0; i < iters && ok; ++i)
+      if (!(xfer_all(a, c, b.data(), size, false) && xfer_all(a, c, b.data(), size, true))) ok = false;
     std::vector<char> big(1 << 20);
     size_t total = 0;
     for (;;) {
@@ -70,18 +71,19 @@ static int run(const Api& a, const char* name, size_t size, int iters, double* l
   for (size_t i = 0; i < size; ++i) b[i] = (char)(i * 13 + 7);
   uint64_t t0 = ub::now_ns();
   for (int i = 0; i < iters && ok; ++i) {
-    ok &= xfer_all(a, c, b.data(), size, true) && xfer_all(a, c, e.data(), size, false);
+    if (!(xfer_all(a, c, b.data(), size, true) && xfer_all(a, c, e.data(), size, false))) ok = false;
     if (ok && memcmp(b.data(), e.data(), size)) ok = false;
   }
   *lat_us = (ub::now_ns() - t0) / 1e3 / iters / 2;
   std::vector<char> big(1 << 20, 'x');
   const size_t stream = 512u << 20;
   t0 = ub::now_ns();
-  for (size_t s = 0; s < stream && ok; s += big.size()) ok &= xfer_all(a, c, big.data(), big.size(), true);
+  for (size_t s = 0; s < stream && ok; s += big.size())
+    if (!xfer_all(a, c, big.data(), big.size(), true)) ok = false;
   shutdown(c, SHUT_WR);
   if (*accel) ums_shutdown(c, SHUT_WR);
   size_t got = 0;
-  ok &= xfer_all(a, c, (char*)&got, sizeof(got), false);
+  if (!xfer_all(a, c, (char*)&got, sizeof(got), false)) ok = false;
   *gbps = stream / ((ub::now_ns() - t0) * 1e-9) / 1e9;
   a.close_(c);
   srv.join();

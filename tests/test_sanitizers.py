@@ -41,7 +41,8 @@ def test_address_and_leak_sanitizer_clean(tmp_path):
 
 @needs_gxx
 def test_thread_sanitizer_clean(tmp_path):
-    outs = _build.build_sanitized("thread")
+    outs = _build.build_sanitized("thread", only=_build.HOST_LIBS + ("tool_umq_perftest", "tool_urpc_perftest",
+                                                                      "tool_ums_perftest"))
     for _ in range(2):   # the teardown race this guards against showed up in about one run out of three
         rc, out = _run(outs["tool_umq_perftest"], ["--iters", "300", "--flow-control"], tmp_path)
         assert rc == 0 and "umq_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
@@ -52,3 +53,9 @@ def test_thread_sanitizer_clean(tmp_path):
     assert rc == 0 and "urpc_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
     rc, out = _run(outs["tool_umq_perftest"], ["--iters", "200", "--selftest"], tmp_path)
     assert rc == 0 and "umq_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
+    # stream sockets: link groups (40 connections, echo threads, control rings, link reaping) and the fallback paths
+    ums_env = {"UMS_SHM_DIR": str(tmp_path / "ums"), "UMS_LINK_LINGER_MS": "100"}
+    rc, out = _run(outs["tool_ums_perftest"], ["--linkgroups"], tmp_path, ums_env)
+    assert rc == 0 and ": OK" in out and "ThreadSanitizer" not in out, out[-3000:]
+    rc, out = _run(outs["tool_ums_perftest"], ["--selftest", "--iters", "300"], tmp_path, ums_env)
+    assert rc == 0 and "ums_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
