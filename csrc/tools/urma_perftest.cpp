@@ -71,11 +71,25 @@ struct GpuRt {
 static GpuRt g_rt;
 // -1 for a device that is not a GPU, else the GPU's index.
 static int gpu_index(const std::string& dev) { return dev.rfind("cuda", 0) == 0 ? atoi(dev.c_str() + 4) : -1; }
+// Host buffers live until the program ends (endpoints may still reference them while it winds down) and are
+// released then; GPU buffers go with the CUDA context.
+static std::vector<void*>& host_bufs() {
+  static std::vector<void*> v;
+  return v;
+}
 static uint8_t* alloc_buf(const std::string& dev, size_t bytes, int fill) {
   const int gi = gpu_index(dev);
   if (gi < 0) {
     uint8_t* p = static_cast<uint8_t*>(malloc(bytes));
-    if (p) memset(p, fill, bytes);
+    if (p) {
+      memset(p, fill, bytes);
+      if (host_bufs().empty())
+        atexit([] {
+          for (void* q : host_bufs()) free(q);
+          host_bufs().clear();
+        });
+      host_bufs().push_back(p);
+    }
     return p;
   }
   void* p = nullptr;
