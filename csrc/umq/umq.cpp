@@ -318,7 +318,17 @@ Queue* find(uint64_t h) {
   auto it = g.queues.find(h);
   return it == g.queues.end() ? nullptr : it->second;
 }
-Queue* find_nolock_order(uint64_t h) { return find(h); }
+// Hands a completion to the queue with handle `h` if it still exists. The table lock is held across look-up and
+// hand-over, so a queue that is being destroyed (erased from the table first, deleted afterwards) either still gets
+// the event and frees it with its inbox, or is no longer found.
+bool forward_to_handle(uint64_t h, const Queue::Event& e) {
+  std::lock_guard<std::mutex> l(g.mu);
+  auto it = g.queues.find(h);
+  if (it == g.queues.end()) return false;
+  std::lock_guard<std::mutex> il(it->second->inbox_mu);
+  it->second->inbox.push_back(e);
+  return true;
+}
 
 // ------------------------------------------------------------------------------------------------ buffers
 Block* block_new(uint32_t cap, bool huge) {
@@ -797,12 +807,12 @@ void progress(Queue* q) {
         e.kind = 1;
         const uint64_t owner = read_id_owner(uc[i]);
         if (owner == (q->h & 0x7fffffffffull)) handle_event(q, e);
-        else forward_event(find_nolock_order(owner), e);
+        else forward_to_handle(owner, e);
       } else if (uc[i] != 0) {
         e.kind = 2;
         Block* b = reinterpret_cast<Block*>(uc[i]);
         if (b->meta.umqh == q->h) handle_event(q, e);
-        else if (!forward_event(find_nolock_order(b->meta.umqh), e)) block_put(b);   // its queue was destroyed
+        else if (!forward_to_handle(b->meta.umqh, e)) block_put(b);   // its queue was destroyed
       }
     }
   }
