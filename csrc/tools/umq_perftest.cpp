@@ -219,12 +219,23 @@ int main(int argc, char** argv) {
       };
       for (int round = 0; round < 20 && ok; ++round)
         for (int i = 0; i < 4 && ok; ++i) ok = xfer(sa[i], sb[i], 300 + round, 'a' + i) && xfer(sb[i], sa[i], 700, 'A' + i);
+      {   // two threads on different sub-queue pairs of the same main queues at the same time
+        std::atomic<bool> tok{true};
+        auto pump = [&](int i) {
+          for (int round = 0; round < 150 && tok; ++round)
+            if (!(xfer(sa[i], sb[i], 1000 + round, 'x') && xfer(sb[i], sa[i], 64, 'y'))) tok = false;
+        };
+        std::thread t1(pump, 0), t2(pump, 1);
+        t1.join();
+        t2.join();
+        ok = ok && tok;
+      }
       ok = ok && xfer(sa[2], sb[2], 200000, 'P');   // beyond the receive buffer size: descriptor + read
       umq_io_stats_t ps{};
       if (ok) umq_stats_io_get(sb[2], &ps);
       umq_jetty_pool_stats_t jp{};
       umq_jetty_pool_stats_get(&jp);
-      if (!ok || ps.pull_rx != 1 || jp.total_num != 2 || jp.sub_queues != 8 || jp.acc_alloc_num < 160)
+      if (!ok || ps.pull_rx != 1 || jp.total_num != 2 || jp.sub_queues != 8 || jp.acc_alloc_num < 700)
         rc = fail("sub queues / jetty pool / pulled message");
       if (umq_destroy(ma) == UMQ_SUCCESS) rc = fail("a main queue must outlive its sub queues");
       for (int i = 0; i < 4; ++i) {
