@@ -134,12 +134,50 @@ struct Device {
 std::vector<Device> g_devs;
 std::mutex g_mu;
 
+inline void cpu_relax() {
+#if defined(__x86_64__) || defined(__i386__)
+  __builtin_ia32_pause();
+#elif defined(__aarch64__)
+  asm volatile("yield");
+#endif
+}
+// The queues below are touched for a few dozen nanoseconds at a time by an application thread and a NIC thread that
+// both poll: a mutex that puts the loser to sleep costs more than the whole critical section, so they spin (and
+// give the core away when the holder seems to have been descheduled).
+class SpinLock {
+ public:
+  void lock() {
+    for (uint32_t n = 0;; ++n) {
+      if (!f_.load(std::memory_order_relaxed) && !f_.exchange(true, std::memory_order_acquire)) return;
+      if ((n & 255) == 255) sched_yield();
+      else cpu_relax();
+    }
+  }
+  void unlock() { f_.store(false, std::memory_order_release); }
+
+ private:
+  std::atomic<bool> f_{false};
+};
+
 struct SegReg {
   uint64_t va, len;
   uint32_t access, token_val;
 };
+struct SgeList {  // a scatter / gather list held by value (no allocation on the data path)
+  urma_sge_t sge[URMA_MAX_SGE];
+  uint32_t n = 0;
+  void assign(const urma_sge_t* src, uint32_t cnt) {
+    n = cnt > URMA_MAX_SGE ? URMA_MAX_SGE : cnt;
+    for (uint32_t i = 0; i < n; ++i) sge[i] = src[i];
+  }
+  uint32_t bytes() const {
+    uint32_t t = 0;
+    for (uint32_t i = 0; i < n; ++i) t += sge[i].len;
+    return t;
+  }
+};
 struct RecvWr {
-  std::vector<urma_sge_t> sges;
+  SgeList sges;
   uint64_t user_ctx;
 };
 struct Unexpected {
@@ -159,8 +197,10 @@ struct ShmJfce {
 };
 struct ShmJfc {
   urma_jfc_t pub;
-  std::mutex mu;
-  std::deque<urma_cr_t> q;
+  SpinLock mu;
+  std::vector<urma_cr_t> ring;      // cfg.depth records
+  uint32_t head = 0, tail = 0;      // under mu: next to pop / next to push (free-running)
+  std::atomic<uint32_t> count{0};   // lets a poller see "empty" without taking the lock
   bool armed = false;
   uint32_t overflow = 0;
 };
@@ -170,7 +210,7 @@ struct RecvQueue {  // a JFR, or the receive half of a jetty
   ShmJfc* jfc;
   uint32_t depth;
   uint32_t token_val;
-  std::mutex mu;
+  SpinLock mu;
   std::deque<RecvWr> posted;
   std::deque<Unexpected> unexpected;
   std::atomic<int> state{URMA_JETTY_STATE_READY};
@@ -202,7 +242,7 @@ struct Pending {
   uint64_t user_ctx;
   uint32_t flag;
   urma_opcode_t opcode;
-  std::vector<urma_sge_t> local;  // destination of READ data / atomic old value
+  SgeList local;  // destination of READ data / atomic old value
   uint32_t total = 0, received = 0;
   uint64_t deadline_ns;
   urma_jetty_id_t remote;
@@ -210,6 +250,17 @@ struct Pending {
 struct Reasm {
   std::vector<uint8_t> data;
   uint32_t got = 0;
+};
+constexpr uint32_t kPendSlots = 4096;  // power of two
+constexpr uint64_t kPendBusy = ~0ull;
+struct PendSlot {
+  std::atomic<uint64_t> id{0};
+  Pending p;
+};
+constexpr uint32_t kPeerHints = 64;  // power of two
+struct PeerHint {
+  std::atomic<uint32_t> uasid{0};
+  std::atomic<Inbox*> in{nullptr};
 };
 struct ShmCtx {
   urma_context_t pub;
@@ -225,9 +276,19 @@ struct ShmCtx {
   std::mutex life_mu;
   std::unordered_map<uint32_t, SegReg> segs;
   std::unordered_map<uint32_t, RecvQueue*> rqs;
-  std::unordered_map<uint64_t, Pending> pending;
+  // Requests that wait for their answer. A request id names its slot (id modulo the table size); the slot's `id`
+  // word is the whole protocol: 0 = free, kPendBusy = a thread is filling or emptying it, anything else = the
+  // request that lives there. The posting thread claims and fills, whoever ends the request (the NIC thread on the
+  // answer, the deadline scan, a flush, a failed post) claims it back with one compare-and-swap, so no two threads
+  // ever complete one request and none of them takes a lock. An id whose slot is still held by a request 4096 ids
+  // older goes to `pending_more` under `pend_mu` instead.
+  PendSlot pend[kPendSlots];
+  std::mutex pend_mu;
+  std::unordered_map<uint64_t, Pending> pending_more;
+  std::atomic<uint32_t> pending_more_n{0};
   std::atomic<uint64_t> next_wr{1};
   std::unordered_map<uint32_t, Inbox*> peers;
+  PeerHint peer_hint[kPeerHints];   // lock-free front of `peers` (mappings live until the context goes)
   std::map<std::pair<uint32_t, uint64_t>, Reasm> reasm;
   std::deque<urma_async_event_t> events;
   int event_fd = -1;
@@ -247,12 +308,14 @@ void push_cr(ShmJfc* jfc, const urma_cr_t& cr) {
   if (!jfc) return;
   ShmJfce* ce = nullptr;
   {
-    std::lock_guard<std::mutex> l(jfc->mu);
-    if (jfc->q.size() >= jfc->pub.cfg.depth) {
+    std::lock_guard<SpinLock> l(jfc->mu);
+    const uint32_t cap = static_cast<uint32_t>(jfc->ring.size());
+    if (jfc->tail - jfc->head >= cap) {
       ++jfc->overflow;
       return;
     }
-    jfc->q.push_back(cr);
+    jfc->ring[jfc->tail++ % cap] = cr;
+    jfc->count.store(jfc->tail - jfc->head, std::memory_order_release);
     if (jfc->armed && jfc->pub.cfg.jfce) {
       jfc->armed = false;
       ce = reinterpret_cast<ShmJfce*>(jfc->pub.cfg.jfce->priv);
@@ -271,39 +334,79 @@ void push_cr(ShmJfc* jfc, const urma_cr_t& cr) {
 
 Inbox* peer_inbox(ShmCtx* c, uint32_t uasid) {
   if (uasid == c->pub.uasid) return c->inbox;
-  std::lock_guard<std::mutex> l(c->mu);
-  auto it = c->peers.find(uasid);
-  if (it != c->peers.end()) return it->second;
-  const std::string path = shm_dir() + "/inbox_" + c->dev->name + "_" + std::to_string(uasid);
-  Inbox* in = static_cast<Inbox*>(map_file(path, sizeof(Inbox), false));
-  if (in && in->magic.load() != kRegMagic) {
-    munmap(in, sizeof(Inbox));
-    in = nullptr;
+  PeerHint& hint = c->peer_hint[uasid & (kPeerHints - 1)];
+  if (hint.uasid.load(std::memory_order_acquire) == uasid) {
+    // `in` and `uasid` are two words: a writer that replaces the pair may be between its two stores, so the pair
+    // counts only if the tag still reads the same after the pointer was taken
+    Inbox* in = hint.in.load(std::memory_order_acquire);
+    if (in && hint.uasid.load(std::memory_order_acquire) == uasid) return in;
   }
-  if (in) c->peers[uasid] = in;
+  std::lock_guard<std::mutex> l(c->mu);
+  Inbox* in = nullptr;
+  auto it = c->peers.find(uasid);
+  if (it != c->peers.end()) {
+    in = it->second;
+  } else {
+    const std::string path = shm_dir() + "/inbox_" + c->dev->name + "_" + std::to_string(uasid);
+    in = static_cast<Inbox*>(map_file(path, sizeof(Inbox), false));
+    if (in && in->magic.load() != kRegMagic) {
+      munmap(in, sizeof(Inbox));
+      in = nullptr;
+    }
+    if (in) c->peers[uasid] = in;
+  }
+  if (in) {   // writers are serialised by c->mu; the tag is taken down while the pair changes
+    hint.uasid.store(0, std::memory_order_release);
+    hint.in.store(in, std::memory_order_release);
+    hint.uasid.store(uasid, std::memory_order_release);
+  }
   return in;
 }
 
 // Blocks (bounded) until a slot is free in the target inbox. Returns false if the ring stayed full.
-bool send_msg(Inbox* in, const MsgHdr& h, const void* payload, uint32_t timeout_ms = 2000) {
-  const uint64_t t0 = ub::now_ns();
-  for (;;) {
-    uint64_t pos;
-    Slot* s = ring_reserve(in, &pos);
-    if (s) {
-      s->h = h;
-      if (h.len && payload) memcpy(s->payload, payload, h.len);
-      ring_publish(s, pos);
-      return true;
+Slot* reserve_wait(Inbox* in, uint64_t* pos, uint32_t timeout_ms) {
+  uint64_t t0 = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    if (Slot* s = ring_reserve(in, pos)) return s;
+    if ((spins & 63) == 63) {
+      const uint64_t now = ub::now_ns();
+      if (!t0) t0 = now;
+      if (now - t0 > uint64_t(timeout_ms) * 1000000ull) return nullptr;
+      sched_yield();
+    } else {
+      cpu_relax();
     }
-    if (ub::now_ns() - t0 > uint64_t(timeout_ms) * 1000000ull) return false;
-    sched_yield();
   }
+}
+bool send_msg(Inbox* in, const MsgHdr& h, const void* payload, uint32_t timeout_ms = 2000) {
+  uint64_t pos;
+  Slot* s = reserve_wait(in, &pos, timeout_ms);
+  if (!s) return false;
+  s->h = h;
+  if (h.len && payload) memcpy(s->payload, payload, h.len);
+  ring_publish(s, pos);
+  return true;
+}
+// Copies up to kSlotPayload bytes of a gather list into `dst`, continuing at (*si, *so); returns the bytes copied.
+uint32_t gather_frag(const urma_sg_t& src, uint32_t* si, uint32_t* so, uint8_t* dst) {
+  uint32_t n = 0;
+  while (n < kSlotPayload && *si < src.num_sge) {
+    const uint32_t take = std::min(kSlotPayload - n, src.sge[*si].len - *so);
+    if (take) memcpy(dst + n, reinterpret_cast<void*>(src.sge[*si].addr + *so), take);
+    n += take;
+    *so += take;
+    if (*so == src.sge[*si].len) {
+      ++*si;
+      *so = 0;
+    }
+  }
+  return n;
 }
 
 // scatter `len` bytes at `src` into an SGE list starting at byte offset `off`
-void scatter(const std::vector<urma_sge_t>& sges, uint32_t off, const uint8_t* src, uint32_t len) {
-  for (const auto& g : sges) {
+void scatter(const SgeList& sges, uint32_t off, const uint8_t* src, uint32_t len) {
+  for (uint32_t i = 0; i < sges.n; ++i) {
+    const urma_sge_t& g = sges.sge[i];
     if (len == 0) break;
     if (off >= g.len) {
       off -= g.len;
@@ -382,57 +485,144 @@ void flush_deferred(ShmCtx* c) {
   }
 }
 
-// Delivers a complete incoming message into a posted receive buffer, or parks it until one is posted.
-void deliver(ShmCtx* c, RecvQueue* rq, Unexpected&& u) {
-  RecvWr wr;
-  {
-    std::lock_guard<std::mutex> l(rq->mu);
-    if (rq->posted.empty()) {
-      rq->unexpected.push_back(std::move(u));
-      return;
-    }
-    wr = std::move(rq->posted.front());
-    rq->posted.pop_front();
-  }
-  uint32_t cap = 0;
-  for (auto& g : wr.sges) cap += g.len;
+// Completes one receive request with `len` bytes at `data`; `m` carries who sent them (its own data is not used).
+void finish_recv(ShmCtx* c, RecvQueue* rq, const RecvWr& wr, const uint8_t* data, uint32_t len, const Unexpected& m) {
   urma_cr_t cr{};
   cr.user_ctx = wr.user_ctx;
   cr.flag = URMA_CR_FLAG_RECV;
   cr.local_id = rq->id;
-  cr.remote_id.eid = u.src_eid;
-  cr.remote_id.uasid = u.src_uasid;
-  cr.remote_id.id = u.src_jetty;
-  cr.imm_data = u.imm;
-  cr.opcode = u.has_imm ? URMA_CR_OPC_SEND_WITH_IMM : URMA_CR_OPC_SEND;
+  cr.remote_id.eid = m.src_eid;
+  cr.remote_id.uasid = m.src_uasid;
+  cr.remote_id.id = m.src_jetty;
+  cr.imm_data = m.imm;
+  cr.opcode = m.has_imm ? URMA_CR_OPC_SEND_WITH_IMM : URMA_CR_OPC_SEND;
   urma_cr_status_t st = URMA_CR_SUCCESS;
-  if (u.data.size() > cap) {
+  if (len > wr.sges.bytes()) {
     st = URMA_CR_LOC_LEN_ERR;
   } else {
-    scatter(wr.sges, 0, u.data.data(), static_cast<uint32_t>(u.data.size()));
-    cr.completion_len = static_cast<uint32_t>(u.data.size());
+    scatter(wr.sges, 0, data, len);
+    cr.completion_len = len;
   }
   cr.status = st;
   push_cr(rq->jfc, cr);
-  if (u.want_ack) {
+  if (m.want_ack) {
     MsgHdr req{};
-    req.src_uasid = u.src_uasid;
-    req.wr_id = u.wr_id;
+    req.src_uasid = m.src_uasid;
+    req.wr_id = m.wr_id;
     req.opcode = URMA_OPC_SEND;
     reply(c, req, MSG_RESP, st == URMA_CR_SUCCESS ? URMA_CR_SUCCESS : URMA_CR_REM_RESP_LEN_ERR);
   }
 }
 
+// Delivers a complete incoming message into a posted receive buffer, or parks it until one is posted.
+void deliver(ShmCtx* c, RecvQueue* rq, Unexpected&& u) {
+  RecvWr wr;
+  {
+    std::lock_guard<SpinLock> l(rq->mu);
+    if (rq->posted.empty()) {
+      rq->unexpected.push_back(std::move(u));
+      return;
+    }
+    wr = rq->posted.front();
+    rq->posted.pop_front();
+  }
+  finish_recv(c, rq, wr, u.data.data(), static_cast<uint32_t>(u.data.size()), u);
+}
+
+// ---- the table of requests in flight
+bool pend_put(ShmCtx* c, uint64_t id, const Pending& p) {
+  PendSlot& e = c->pend[id & (kPendSlots - 1)];
+  uint64_t free_word = 0;
+  if (e.id.load(std::memory_order_relaxed) == 0 &&
+      e.id.compare_exchange_strong(free_word, kPendBusy, std::memory_order_acquire)) {
+    e.p = p;
+    e.id.store(id, std::memory_order_release);
+    return true;
+  }
+  std::lock_guard<std::mutex> l(c->pend_mu);
+  c->pending_more[id] = p;
+  c->pending_more_n.fetch_add(1, std::memory_order_release);
+  return true;
+}
+// Takes the request out of the table; false when somebody else already ended it (or it never existed).
+bool pend_take(ShmCtx* c, uint64_t id, Pending* out) {
+  PendSlot& e = c->pend[id & (kPendSlots - 1)];
+  for (;;) {
+    uint64_t cur = e.id.load(std::memory_order_acquire);
+    if (cur == id) {
+      if (!e.id.compare_exchange_strong(cur, kPendBusy, std::memory_order_acquire)) continue;
+      *out = e.p;
+      e.id.store(0, std::memory_order_release);
+      return true;
+    }
+    if (cur == kPendBusy) {   // being filled (not ours: ours was published before its message left) or being
+      cpu_relax();            // read for a data fragment by the NIC thread, which puts it back at once
+      continue;
+    }
+    break;
+  }
+  if (c->pending_more_n.load(std::memory_order_acquire) == 0) return false;
+  std::lock_guard<std::mutex> l(c->pend_mu);
+  auto it = c->pending_more.find(id);
+  if (it == c->pending_more.end()) return false;
+  *out = it->second;
+  c->pending_more.erase(it);
+  c->pending_more_n.fetch_sub(1, std::memory_order_release);
+  return true;
+}
+// Runs `fn(Pending&)` on the request while it stays in the table (data fragments of a READ land this way).
+template <typename F>
+bool pend_with(ShmCtx* c, uint64_t id, F fn) {
+  PendSlot& e = c->pend[id & (kPendSlots - 1)];
+  for (;;) {
+    uint64_t cur = e.id.load(std::memory_order_acquire);
+    if (cur == id) {
+      if (!e.id.compare_exchange_strong(cur, kPendBusy, std::memory_order_acquire)) continue;
+      fn(e.p);
+      e.id.store(id, std::memory_order_release);
+      return true;
+    }
+    if (cur != kPendBusy) break;
+    cpu_relax();
+  }
+  if (c->pending_more_n.load(std::memory_order_acquire) == 0) return false;
+  std::lock_guard<std::mutex> l(c->pend_mu);
+  auto it = c->pending_more.find(id);
+  if (it == c->pending_more.end()) return false;
+  fn(it->second);
+  return true;
+}
+// Ids of the requests for which `pred(Pending&)` holds (a snapshot: each id still has to be taken).
+template <typename F>
+std::vector<uint64_t> pend_select(ShmCtx* c, F pred) {
+  std::vector<uint64_t> ids;
+  for (uint32_t i = 0; i < kPendSlots; ++i) {
+    PendSlot& e = c->pend[i];
+    uint64_t cur = e.id.load(std::memory_order_acquire);
+    if (cur == 0 || cur == kPendBusy) continue;
+    const uint64_t id = cur;
+    if (!e.id.compare_exchange_strong(cur, kPendBusy, std::memory_order_acquire)) continue;
+    const bool hit = pred(e.p);
+    e.id.store(id, std::memory_order_release);
+    if (hit) ids.push_back(id);
+  }
+  if (c->pending_more_n.load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> l(c->pend_mu);
+    for (auto& kv : c->pending_more)
+      if (pred(kv.second)) ids.push_back(kv.first);
+  }
+  return ids;
+}
+uint32_t pend_count(ShmCtx* c) {
+  uint32_t n = c->pending_more_n.load();
+  for (uint32_t i = 0; i < kPendSlots; ++i) n += c->pend[i].id.load(std::memory_order_relaxed) != 0;
+  return n;
+}
+
 void complete_pending(ShmCtx* c, uint64_t wr_id, urma_cr_status_t st, uint64_t operand, bool have_operand) {
   Pending p;
-  {
-    std::lock_guard<std::mutex> l(c->mu);
-    auto it = c->pending.find(wr_id);
-    if (it == c->pending.end()) return;
-    p = std::move(it->second);
-    c->pending.erase(it);
-  }
-  if (have_operand && !p.local.empty() && st == URMA_CR_SUCCESS)
+  if (!pend_take(c, wr_id, &p)) return;
+  if (have_operand && p.local.n && st == URMA_CR_SUCCESS)
     scatter(p.local, 0, reinterpret_cast<const uint8_t*>(&operand), 8);
   p.sq->inflight.fetch_sub(1);
   if ((p.flag & URMA_WR_FLAG_COMPLETE_ENABLE) || st != URMA_CR_SUCCESS) {
@@ -465,7 +655,7 @@ void handle(ShmCtx* c, Slot* s) {
             RecvWr wr;
             bool have = false;
             {
-              std::lock_guard<std::mutex> l(rq->mu);
+              std::lock_guard<SpinLock> l(rq->mu);
               if (!rq->posted.empty()) {
                 wr = std::move(rq->posted.front());
                 rq->posted.pop_front();
@@ -548,6 +738,32 @@ void handle(ShmCtx* c, Slot* s) {
         if (h.flags & F_LAST) reply(c, h, MSG_RESP, rq ? URMA_CR_REM_ACCESS_ABORT_ERR : URMA_CR_REM_OPERATION_ERR);
         break;
       }
+      if ((h.flags & (F_FIRST | F_LAST)) == (F_FIRST | F_LAST)) {
+        // the whole message is in this slot: straight into the posted buffer, no reassembly and no staging copy
+        Unexpected u;
+        u.imm = h.operand;
+        u.has_imm = (h.flags & F_IMM) != 0;
+        u.src_uasid = h.src_uasid;
+        u.src_jetty = h.src_jetty;
+        u.wr_id = h.wr_id;
+        u.want_ack = true;
+        memcpy(u.src_eid.raw, h.src_eid, 16);
+        RecvWr wr;
+        bool have = false;
+        {
+          std::lock_guard<SpinLock> l(rq->mu);
+          if (!rq->posted.empty()) {
+            wr = rq->posted.front();
+            rq->posted.pop_front();
+            have = true;
+          } else {
+            u.data.assign(s->payload, s->payload + h.len);
+            rq->unexpected.push_back(std::move(u));
+          }
+        }
+        if (have) finish_recv(c, rq, wr, s->payload, h.len, u);
+        break;
+      }
       const auto key = std::make_pair(h.src_uasid, h.wr_id);
       Reasm* r;
       {
@@ -577,17 +793,11 @@ void handle(ShmCtx* c, Slot* s) {
     case MSG_RESP: complete_pending(c, h.wr_id, static_cast<urma_cr_status_t>(h.status), h.operand,
                                     h.opcode >= URMA_OPC_CAS && h.opcode <= URMA_OPC_FXOR); break;
     case MSG_RESP_DATA: {
-      bool done = false;
-      {
-        std::lock_guard<std::mutex> l(c->mu);
-        auto it = c->pending.find(h.wr_id);
-        if (it != c->pending.end()) {
-          scatter(it->second.local, h.frag_off, s->payload, h.len);
-          it->second.received += h.len;
-          done = (h.flags & F_LAST) != 0;
-        }
-      }
-      if (done) complete_pending(c, h.wr_id, URMA_CR_SUCCESS, 0, false);
+      const bool known = pend_with(c, h.wr_id, [&](Pending& p) {
+        scatter(p.local, h.frag_off, s->payload, h.len);
+        p.received += h.len;
+      });
+      if (known && (h.flags & F_LAST)) complete_pending(c, h.wr_id, URMA_CR_SUCCESS, 0, false);
       break;
     }
     case MSG_PROBE: reply(c, h, MSG_RESP, URMA_CR_SUCCESS); break;
@@ -623,13 +833,7 @@ void nic_loop(ShmCtx* c) {
     if (now - last_scan > 20000000ull) {  // every 20 ms: heartbeat + request deadlines
       last_scan = now;
       if (c->reg_slot >= 0) c->dev->reg->ctx[c->reg_slot].heartbeat_ns.store(now);
-      std::vector<uint64_t> expired;
-      {
-        std::lock_guard<std::mutex> l(c->mu);
-        for (auto& kv : c->pending)
-          if (now > kv.second.deadline_ns) expired.push_back(kv.first);
-      }
-      for (uint64_t id : expired) complete_pending(c, id, URMA_CR_ACK_TIMEOUT_ERR, 0, false);
+      for (uint64_t id : pend_select(c, [now](Pending& p) { return now > p.deadline_ns; })) complete_pending(c, id, URMA_CR_ACK_TIMEOUT_ERR, 0, false);
     }
   }
 }
@@ -641,6 +845,7 @@ urma_jfc_t* op_create_jfc(urma_context_t*, const urma_jfc_cfg_t* cfg) {
   ShmJfc* j = new ShmJfc();
   j->pub.cfg = *cfg;
   j->pub.priv = j;
+  j->ring.resize(cfg->depth ? cfg->depth : 1);
   static std::atomic<uint32_t> ids{1};
   j->pub.id = ids++;
   return &j->pub;
@@ -696,23 +901,11 @@ urma_status_t op_query_jfs(urma_jfs_t* jfs, urma_jfs_cfg_t* cfg, urma_jetty_stat
   return URMA_SUCCESS;
 }
 int flush_sq(ShmCtx* c, SendQueue* sq, int cr_cnt, urma_cr_t* cr) {
-  std::vector<uint64_t> ids;
-  {
-    std::lock_guard<std::mutex> l(c->mu);
-    for (auto& kv : c->pending)
-      if (kv.second.sq == sq) ids.push_back(kv.first);
-  }
   int n = 0;
-  for (uint64_t id : ids) {
+  for (uint64_t id : pend_select(c, [sq](Pending& p) { return p.sq == sq; })) {
     if (n >= cr_cnt) break;
     Pending p;
-    {
-      std::lock_guard<std::mutex> l(c->mu);
-      auto it = c->pending.find(id);
-      if (it == c->pending.end()) continue;
-      p = std::move(it->second);
-      c->pending.erase(it);
-    }
+    if (!pend_take(c, id, &p)) continue;
     sq->inflight.fetch_sub(1);
     cr[n] = urma_cr_t{};
     cr[n].status = URMA_CR_WR_FLUSH_ERR;
@@ -942,12 +1135,30 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
   memcpy(h.src_eid, c->pub.eid.raw, 16);
   auto add_pending = [&]() {
     sq->inflight.fetch_add(1);
-    std::lock_guard<std::mutex> l(c->mu);
-    c->pending[id] = std::move(p);
+    pend_put(c, id, p);
   };
   auto fail_pending = [&]() {
-    std::lock_guard<std::mutex> l(c->mu);
-    if (c->pending.erase(id)) sq->inflight.fetch_sub(1);
+    Pending gone;
+    if (pend_take(c, id, &gone)) sq->inflight.fetch_sub(1);
+  };
+  // One fragment: the slot is reserved first and the gather list is copied straight into it.
+  auto send_frag = [&](const urma_sg_t& src, uint32_t* si, uint32_t* so, uint32_t off, uint32_t total, uint32_t extra,
+                       uint64_t va) -> int {   // bytes sent, or -1 when the peer's ring stayed full
+    if (c->drop_tx.load(std::memory_order_relaxed)) {
+      uint8_t sink[kSlotPayload];
+      return static_cast<int>(gather_frag(src, si, so, sink));
+    }
+    uint64_t pos;
+    Slot* s = reserve_wait(in, &pos, sq->err_timeout_ms);
+    if (!s) return -1;
+    const uint32_t n = gather_frag(src, si, so, s->payload);
+    h.len = n;
+    h.frag_off = off;
+    h.remote_va = va;
+    h.flags = (off == 0 ? F_FIRST : 0) | (off + n == total ? F_LAST : 0) | extra;
+    s->h = h;
+    ring_publish(s, pos);
+    return static_cast<int>(n);
   };
   switch (wr->opcode) {
     case URMA_OPC_WRITE:
@@ -965,31 +1176,15 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
       h.operand = wr->rw.notify_data;
       p.total = total;
       add_pending();
-      // gather source SGEs into fragments
       uint32_t off = 0, si = 0, so = 0;
-      uint8_t buf[kSlotPayload];
       do {
-        uint32_t n = 0;
-        while (n < kSlotPayload && si < src.num_sge) {
-          const uint32_t take = std::min(kSlotPayload - n, src.sge[si].len - so);
-          memcpy(buf + n, reinterpret_cast<void*>(src.sge[si].addr + so), take);
-          n += take;
-          so += take;
-          if (so == src.sge[si].len) {
-            ++si;
-            so = 0;
-          }
-        }
-        h.len = n;
-        h.frag_off = off;
-        h.remote_va = dst.sge[0].addr + off;
-        h.flags = (off == 0 ? F_FIRST : 0) | (off + n == total ? F_LAST : 0) |
-                  (wr->opcode != URMA_OPC_WRITE ? F_IMM : 0);
-        if (!c->drop_tx.load() && !send_msg(in, h, buf, sq->err_timeout_ms)) {
+        const int n = send_frag(src, &si, &so, off, total, wr->opcode != URMA_OPC_WRITE ? F_IMM : 0,
+                                dst.sge[0].addr + off);
+        if (n < 0) {
           fail_pending();
           return URMA_EAGAIN;
         }
-        off += n;
+        off += static_cast<uint32_t>(n);
       } while (off < total);
       return URMA_SUCCESS;
     }
@@ -1005,7 +1200,7 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
       h.total_len = total;
       h.remote_va = src.sge[0].addr;
       p.total = total;
-      p.local.assign(dst.sge, dst.sge + dst.num_sge);
+      p.local.assign(dst.sge, dst.num_sge);
       add_pending();
       if (!c->drop_tx.load() && !send_msg(in, h, nullptr, sq->err_timeout_ms)) {
         fail_pending();
@@ -1032,7 +1227,7 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
       h.operand = cas ? wr->cas.swap_data : wr->faa.operand;
       h.cmp = cas ? wr->cas.cmp_data : 0;
       p.total = 8;
-      if (s && s->addr) p.local.push_back(*s);
+      if (s && s->addr) p.local.assign(s, 1);
       add_pending();
       if (!c->drop_tx.load() && !send_msg(in, h, nullptr, sq->err_timeout_ms)) {
         fail_pending();
@@ -1053,28 +1248,13 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
       p.total = total;
       add_pending();
       uint32_t off = 0, si = 0, so = 0;
-      uint8_t buf[kSlotPayload];
       do {
-        uint32_t n = 0;
-        while (n < kSlotPayload && si < src.num_sge) {
-          const uint32_t take = std::min(kSlotPayload - n, src.sge[si].len - so);
-          if (take) memcpy(buf + n, reinterpret_cast<void*>(src.sge[si].addr + so), take);
-          n += take;
-          so += take;
-          if (so == src.sge[si].len) {
-            ++si;
-            so = 0;
-          }
-        }
-        h.len = n;
-        h.frag_off = off;
-        h.flags = (off == 0 ? F_FIRST : 0) | (off + n == total ? F_LAST : 0) |
-                  (wr->opcode == URMA_OPC_SEND_IMM ? F_IMM : 0);
-        if (!c->drop_tx.load() && !send_msg(in, h, buf, sq->err_timeout_ms)) {
+        const int n = send_frag(src, &si, &so, off, total, wr->opcode == URMA_OPC_SEND_IMM ? F_IMM : 0, 0);
+        if (n < 0) {
           fail_pending();
           return URMA_EAGAIN;
         }
-        off += n;
+        off += static_cast<uint32_t>(n);
       } while (off < total);
       return URMA_SUCCESS;
     }
@@ -1111,11 +1291,11 @@ urma_status_t post_recv_list(ShmCtx* c, RecvQueue* rq, urma_jfr_wr_t* wr, urma_j
     }
     RecvWr r;
     r.user_ctx = w->user_ctx;
-    r.sges.assign(w->src.sge, w->src.sge + w->src.num_sge);
+    r.sges.assign(w->src.sge, w->src.num_sge);
     Unexpected u;
     bool have = false;
     {
-      std::lock_guard<std::mutex> l(rq->mu);
+      std::lock_guard<SpinLock> l(rq->mu);
       if (rq->posted.size() >= rq->depth) {
         *bad = w;
         return URMA_EAGAIN;
@@ -1146,20 +1326,20 @@ urma_status_t op_post_jetty_recv(urma_jetty_t* jt, urma_jfr_wr_t* wr, urma_jfr_w
 }
 int op_poll_jfc(urma_jfc_t* jfc, int n, urma_cr_t* cr) {
   ShmJfc* j = reinterpret_cast<ShmJfc*>(jfc->priv);
-  std::lock_guard<std::mutex> l(j->mu);
+  if (j->count.load(std::memory_order_acquire) == 0) return 0;   // the common answer of a polling loop: no lock
+  std::lock_guard<SpinLock> l(j->mu);
+  const uint32_t cap = static_cast<uint32_t>(j->ring.size());
   int k = 0;
-  while (k < n && !j->q.empty()) {
-    cr[k++] = j->q.front();
-    j->q.pop_front();
-  }
+  while (k < n && j->head != j->tail) cr[k++] = j->ring[j->head++ % cap];
+  j->count.store(j->tail - j->head, std::memory_order_release);
   return k;
 }
 urma_status_t op_rearm_jfc(urma_jfc_t* jfc, bool) {
   ShmJfc* j = reinterpret_cast<ShmJfc*>(jfc->priv);
   ShmJfce* ce = nullptr;
   {
-    std::lock_guard<std::mutex> l(j->mu);
-    if (!j->q.empty() && jfc->cfg.jfce) ce = reinterpret_cast<ShmJfce*>(jfc->cfg.jfce->priv);  // fire at once
+    std::lock_guard<SpinLock> l(j->mu);
+    if (j->head != j->tail && jfc->cfg.jfce) ce = reinterpret_cast<ShmJfce*>(jfc->cfg.jfce->priv);  // fire at once
     else j->armed = true;
   }
   if (ce) {
@@ -1219,8 +1399,7 @@ int op_user_ctl(urma_context_t* ctx, urma_user_ctl_in_t* in, urma_user_ctl_out_t
   ShmCtx* c = C(ctx);
   switch (in->opcode) {
     case 1: {
-      std::lock_guard<std::mutex> l(c->mu);
-      out->rsv = static_cast<uint32_t>(c->pending.size());
+      out->rsv = pend_count(c);
       return 0;
     }
     case 2: {
