@@ -239,6 +239,16 @@ inline uint64_t cycles() {
 #endif
 }
 
+// One step of a polling loop: tells the core that this is a spin-wait (frees the pipeline for the sibling thread,
+// avoids the memory-order mis-speculation penalty on leaving the loop).
+inline void cpu_relax() {
+#if defined(__x86_64__) || defined(__i386__)
+  __builtin_ia32_pause();
+#elif defined(__aarch64__)
+  __asm__ __volatile__("yield");
+#endif
+}
+
 // ---------------------------------------------------------------- latency histogram (log2 buckets x 8 sub-buckets)
 class PerfHist {
  public:

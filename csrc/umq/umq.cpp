@@ -62,6 +62,35 @@ struct Block {
   char* mem;
   uint32_t cap;
   uint32_t gen;    // pool generation the block was made in (blocks of an older generation are freed on return)
+  Block* fl_prev = nullptr;   // links of the owning queue's in-flight list (under that queue's lock)
+  Block* fl_next = nullptr;
+  bool in_fl = false;
+};
+// The blocks an endpoint owns at the moment (posted receives, sends not yet completed), as a list threaded through
+// the blocks themselves: every message enters and leaves it once, so it must cost neither an allocation nor a hash.
+struct FlightList {
+  Block* head = nullptr;
+  uint32_t n = 0;
+  void insert(Block* b) {
+    if (b->in_fl) return;
+    b->in_fl = true;
+    b->fl_prev = nullptr;
+    b->fl_next = head;
+    if (head) head->fl_prev = b;
+    head = b;
+    ++n;
+  }
+  void erase(Block* b) {
+    if (!b->in_fl) return;
+    b->in_fl = false;
+    if (b->fl_prev) b->fl_prev->fl_next = b->fl_next;
+    else head = b->fl_next;
+    if (b->fl_next) b->fl_next->fl_prev = b->fl_prev;
+    b->fl_prev = b->fl_next = nullptr;
+    --n;
+  }
+  bool empty() const { return n == 0; }
+  uint32_t size() const { return n; }
 };
 
 // Tiny pool: requests of at most kTinyBytes (headers, acknowledgements, small RPC arguments) are served from blocks
@@ -263,7 +292,7 @@ struct Queue {
   std::deque<umq_buf_t*> rx_ready;      // received messages not yet dequeued
   std::deque<umq_buf_t*> tx_done;       // sent buffers whose completion arrived (pro API)
   uint32_t rx_posted = 0;
-  std::unordered_set<struct Block*> in_flight;  // blocks owned by the endpoint: posted receives, sends not yet completed
+  FlightList in_flight;  // blocks owned by the endpoint: posted receives, sends not yet completed
   // flow control
   bool fc = false;
   int64_t credits = 0;          // messages we may still send
@@ -313,10 +342,40 @@ struct Queue {
 };
 constexpr uint64_t kRxPending = 1;   // umq_buf_t::rsvd[1] of a queued receive whose data is still being read
 
+// Every call of the API starts with a look-up by handle, from every thread that drives a queue: the table's mutex
+// would be the one lock all of them meet on. A direct-mapped front (handle modulo its size) answers without it. An
+// entry is a (tag, pointer) pair that only changes under g.mu: the writer takes the tag down, swaps the pointer,
+// puts the new tag up; a reader trusts the pointer only if the tag read the same before and after.
+constexpr uint32_t kQHints = 256;
+struct QHint {
+  std::atomic<uint64_t> h{0};
+  std::atomic<Queue*> q{nullptr};
+};
+QHint g_qhint[kQHints];
+void qhint_set(uint64_t h, Queue* q) {   // caller holds g.mu
+  QHint& e = g_qhint[h & (kQHints - 1)];
+  e.h.store(0, std::memory_order_release);
+  e.q.store(q, std::memory_order_release);
+  e.h.store(h, std::memory_order_release);
+}
+void qhint_drop(uint64_t h) {   // caller holds g.mu
+  QHint& e = g_qhint[h & (kQHints - 1)];
+  if (e.h.load(std::memory_order_relaxed) == h) {
+    e.h.store(0, std::memory_order_release);
+    e.q.store(nullptr, std::memory_order_release);
+  }
+}
 Queue* find(uint64_t h) {
+  QHint& e = g_qhint[h & (kQHints - 1)];
+  if (h && e.h.load(std::memory_order_acquire) == h) {
+    Queue* q = e.q.load(std::memory_order_acquire);
+    if (q && e.h.load(std::memory_order_acquire) == h) return q;
+  }
   std::lock_guard<std::mutex> l(g.mu);
   auto it = g.queues.find(h);
-  return it == g.queues.end() ? nullptr : it->second;
+  if (it == g.queues.end()) return nullptr;
+  qhint_set(h, it->second);
+  return it->second;
 }
 // Hands a completion to the queue with handle `h` if it still exists. The table lock is held across look-up and
 // hand-over, so a queue that is being destroyed (erased from the table first, deleted afterwards) either still gets
@@ -1140,6 +1199,7 @@ int umq_destroy(uint64_t h) {
   {
     std::lock_guard<std::mutex> l(g.mu);
     if (!g.queues.erase(h)) return UMQ_ERR_EINVAL;   // somebody else destroyed it in between
+    qhint_drop(h);
   }
   if (!q->tops && q->in_pool) {
     std::unique_lock<std::shared_mutex> pl(g_jpool.mu);   // waits for posts that borrowed the endpoint
@@ -1176,7 +1236,10 @@ int umq_destroy(uint64_t h) {
   for (auto& kv : q->imported) urma_unimport_seg(kv.second);
   if (q->peer) urma_unimport_jetty(q->peer);
   // the endpoint is gone: nothing can complete into the blocks it still held (posted receives, unfinished sends)
-  for (Block* b : q->in_flight) block_put(b);
+  while (Block* b = q->in_flight.head) {
+    q->in_flight.erase(b);
+    block_put(b);
+  }
   delete q;
   return UMQ_SUCCESS;
 }

@@ -134,13 +134,7 @@ struct Device {
 std::vector<Device> g_devs;
 std::mutex g_mu;
 
-inline void cpu_relax() {
-#if defined(__x86_64__) || defined(__i386__)
-  __builtin_ia32_pause();
-#elif defined(__aarch64__)
-  asm volatile("yield");
-#endif
-}
+using ub::cpu_relax;
 // The queues below are touched for a few dozen nanoseconds at a time by an application thread and a NIC thread that
 // both poll: a mutex that puts the loser to sleep costs more than the whole critical section, so they spin (and
 // give the core away when the holder seems to have been descheduled).
@@ -203,7 +197,9 @@ struct ShmJfc {
   std::atomic<uint32_t> count{0};   // lets a poller see "empty" without taking the lock
   bool armed = false;
   uint32_t overflow = 0;
+  std::atomic<uint32_t> empty_polls{0};   // consecutive polls that found nothing (a hint; races between pollers are harmless)
 };
+constexpr uint32_t kInlineAfterEmptyPolls = 3;
 struct ShmCtx;
 struct RecvQueue {  // a JFR, or the receive half of a jetty
   uint32_t id;
@@ -211,7 +207,15 @@ struct RecvQueue {  // a JFR, or the receive half of a jetty
   uint32_t depth;
   uint32_t token_val;
   SpinLock mu;
-  std::deque<RecvWr> posted;
+  // posted receive requests: a ring of `depth` entries made once (a request is 200 bytes of scatter list; a deque
+  // would allocate for nearly every one)
+  std::vector<RecvWr> ring;
+  uint32_t head = 0, tail = 0;   // free-running, under mu
+  bool posted_empty() const { return head == tail; }
+  uint32_t posted_size() const { return tail - head; }
+  RecvWr& posted_front() { return ring[head % ring.size()]; }
+  void posted_pop() { ++head; }
+  void posted_push(const RecvWr& w) { ring[tail++ % ring.size()] = w; }
   std::deque<Unexpected> unexpected;
   std::atomic<int> state{URMA_JETTY_STATE_READY};
 };
@@ -292,6 +296,8 @@ struct ShmCtx {
   std::map<std::pair<uint32_t, uint64_t>, Reasm> reasm;
   std::deque<urma_async_event_t> events;
   int event_fd = -1;
+  std::atomic<uint64_t> app_poll_ticks{0};   // fast_ticks() of the last poll of an empty completion queue
+  bool inline_poll = true;              // URMA_SHM_INLINE_POLL=0: only the context's own thread executes the inbox
   std::atomic<bool> drop_tx{false};  // fault injection: outgoing requests vanish (a dead link)
   // Answers that did not fit into a full peer inbox. The NIC thread never blocks on a full ring (two NIC threads
   // answering into each other's full inbox would deadlock); it parks the answer here and retries later.
@@ -300,7 +306,7 @@ struct ShmCtx {
     MsgHdr h;
     std::vector<uint8_t> payload;
   };
-  std::deque<Deferred> deferred;  // touched by the NIC thread only
+  std::deque<Deferred> deferred;  // under life_mu
 };
 
 // ---------------------------------------------------------------------------------------------- helpers
@@ -519,12 +525,12 @@ void deliver(ShmCtx* c, RecvQueue* rq, Unexpected&& u) {
   RecvWr wr;
   {
     std::lock_guard<SpinLock> l(rq->mu);
-    if (rq->posted.empty()) {
+    if (rq->posted_empty()) {
       rq->unexpected.push_back(std::move(u));
       return;
     }
-    wr = rq->posted.front();
-    rq->posted.pop_front();
+    wr = rq->posted_front();
+    rq->posted_pop();
   }
   finish_recv(c, rq, wr, u.data.data(), static_cast<uint32_t>(u.data.size()), u);
 }
@@ -656,9 +662,9 @@ void handle(ShmCtx* c, Slot* s) {
             bool have = false;
             {
               std::lock_guard<SpinLock> l(rq->mu);
-              if (!rq->posted.empty()) {
-                wr = std::move(rq->posted.front());
-                rq->posted.pop_front();
+              if (!rq->posted_empty()) {
+                wr = rq->posted_front();
+                rq->posted_pop();
                 have = true;
               }
             }
@@ -752,9 +758,9 @@ void handle(ShmCtx* c, Slot* s) {
         bool have = false;
         {
           std::lock_guard<SpinLock> l(rq->mu);
-          if (!rq->posted.empty()) {
-            wr = rq->posted.front();
-            rq->posted.pop_front();
+          if (!rq->posted_empty()) {
+            wr = rq->posted_front();
+            rq->posted_pop();
             have = true;
           } else {
             u.data.assign(s->payload, s->payload + h.len);
@@ -805,27 +811,62 @@ void handle(ShmCtx* c, Slot* s) {
   }
 }
 
+// Executes up to `budget` messages of the context's inbox. The inbox has one consumer at a time: whoever holds
+// `life_mu` (the same lock that keeps queues alive while a message is handled). Threads that cannot have it at once
+// go away empty-handed - somebody else is doing the work.
+int consume(ShmCtx* c, int budget) {
+  std::unique_lock<std::mutex> life(c->life_mu, std::try_to_lock);
+  if (!life.owns_lock()) return 0;
+  if (!c->deferred.empty()) flush_deferred(c);
+  Inbox* in = c->inbox;
+  int done = 0;
+  while (done < budget) {
+    const uint64_t pos = in->deq.load(std::memory_order_relaxed);
+    Slot* s = &in->slots[pos & (kRingSlots - 1)];
+    if (s->seq.load(std::memory_order_acquire) != pos + 1) break;
+    handle(c, s);
+    in->deq.store(pos + 1, std::memory_order_relaxed);
+    s->seq.store(pos + kRingSlots, std::memory_order_release);
+    ++done;
+  }
+  return done;
+}
+
+// A cheap clock for "did the application poll just now": the cycle counter.
+inline uint64_t fast_ticks() { return ub::cycles(); }
+uint64_t ticks_per_us() {
+  static const uint64_t v = [] {
+    const uint64_t n0 = ub::now_ns(), t0 = fast_ticks();
+    while (ub::now_ns() - n0 < 200000) cpu_relax();
+    const uint64_t per = (fast_ticks() - t0) * 1000 / (ub::now_ns() - n0);
+    return per ? per : 1;
+  }();
+  return v;
+}
+
+// The context's own thread. An application that polls its completion queues executes the inbox itself, inside the
+// poll (see op_poll_jfc): the message is then copied once, by the thread that is about to read it, instead of being
+// copied by this thread on another core first. Every such poll leaves a time stamp; while the last one is younger
+// than a few microseconds this thread stays out of the way, and the moment the application stops polling (it sleeps
+// on a completion event, computes, or only ever posts) it executes the inbox as a NIC would, so requests of peers
+// progress in any case.
 void nic_loop(ShmCtx* c) {
   urma_log_set_thread_tag("shm-nic");
   uint32_t idle = 0;
   uint64_t last_scan = ub::now_ns();
+  const uint64_t defer_ticks = 3 * ticks_per_us();
   while (!c->stop.load(std::memory_order_relaxed)) {
-    if (!c->deferred.empty()) flush_deferred(c);
-    Inbox* in = c->inbox;
-    const uint64_t pos = in->deq.load(std::memory_order_relaxed);
-    Slot* s = &in->slots[pos & (kRingSlots - 1)];
-    if (s->seq.load(std::memory_order_acquire) == pos + 1) {
-      {
-        std::lock_guard<std::mutex> life(c->life_mu);
-        handle(c, s);
-      }
-      in->deq.store(pos + 1, std::memory_order_relaxed);
-      s->seq.store(pos + kRingSlots, std::memory_order_release);
+    const bool app_drives =
+        c->inline_poll && fast_ticks() - c->app_poll_ticks.load(std::memory_order_relaxed) < defer_ticks;
+    if (app_drives) {
+      for (int i = 0; i < 8; ++i) cpu_relax();
+      if ((++idle & 1023) != 0) continue;   // the periodic work below still runs now and then
+    } else if (consume(c, 64) > 0) {
       idle = 0;
       continue;
-    }
-    if (++idle < 4000) {
+    } else if (++idle < 4000) {
       if ((idle & 63) == 0) sched_yield();
+      else cpu_relax();
     } else {
       usleep(50);
     }
@@ -833,7 +874,8 @@ void nic_loop(ShmCtx* c) {
     if (now - last_scan > 20000000ull) {  // every 20 ms: heartbeat + request deadlines
       last_scan = now;
       if (c->reg_slot >= 0) c->dev->reg->ctx[c->reg_slot].heartbeat_ns.store(now);
-      for (uint64_t id : pend_select(c, [now](Pending& p) { return now > p.deadline_ns; })) complete_pending(c, id, URMA_CR_ACK_TIMEOUT_ERR, 0, false);
+      for (uint64_t id : pend_select(c, [now](Pending& p) { return now > p.deadline_ns; }))
+        complete_pending(c, id, URMA_CR_ACK_TIMEOUT_ERR, 0, false);
     }
   }
 }
@@ -932,6 +974,7 @@ void rq_init(ShmCtx* c, RecvQueue* rq, const urma_jfr_cfg_t* cfg) {
   rq->id = new_jetty_id(c, cfg->id);
   rq->jfc = reinterpret_cast<ShmJfc*>(cfg->jfc->priv);
   rq->depth = cfg->depth;
+  rq->ring.resize(cfg->depth ? cfg->depth : 1);
   rq->token_val = cfg->token_value.token;
   std::lock_guard<std::mutex> l(c->mu);
   c->rqs[rq->id] = rq;
@@ -1296,18 +1339,21 @@ urma_status_t post_recv_list(ShmCtx* c, RecvQueue* rq, urma_jfr_wr_t* wr, urma_j
     bool have = false;
     {
       std::lock_guard<SpinLock> l(rq->mu);
-      if (rq->posted.size() >= rq->depth) {
+      if (rq->posted_size() >= rq->depth) {
         *bad = w;
         return URMA_EAGAIN;
       }
-      rq->posted.push_back(std::move(r));
+      rq->posted_push(r);
       if (!rq->unexpected.empty()) {
         u = std::move(rq->unexpected.front());
         rq->unexpected.pop_front();
         have = true;
       }
     }
-    if (have) deliver(c, rq, std::move(u));
+    if (have) {   // answering the sender touches what the inbox's consumer owns (the list of parked answers)
+      std::lock_guard<std::mutex> life(c->life_mu);
+      deliver(c, rq, std::move(u));
+    }
   }
   *bad = nullptr;
   return URMA_SUCCESS;
@@ -1326,7 +1372,18 @@ urma_status_t op_post_jetty_recv(urma_jetty_t* jt, urma_jfr_wr_t* wr, urma_jfr_w
 }
 int op_poll_jfc(urma_jfc_t* jfc, int n, urma_cr_t* cr) {
   ShmJfc* j = reinterpret_cast<ShmJfc*>(jfc->priv);
-  if (j->count.load(std::memory_order_acquire) == 0) return 0;   // the common answer of a polling loop: no lock
+  if (j->count.load(std::memory_order_acquire) == 0) {
+    // nothing completed yet: do the NIC's work on this thread (requests and answers waiting in the inbox), which is
+    // what fills this queue; still nothing -> the common answer of a polling loop, without a lock
+    // (only a thread that has found the queue empty several times in a row is waiting for something; one that
+    // finds completions most of the time is part of a pipelined flow, which the context's own thread serves in
+    // parallel)
+    ShmCtx* c = C(jfc->ctx);
+    if (!c->inline_poll || j->empty_polls.fetch_add(1, std::memory_order_relaxed) + 1 < kInlineAfterEmptyPolls) return 0;
+    c->app_poll_ticks.store(fast_ticks(), std::memory_order_relaxed);
+    if (consume(c, 32) == 0 || j->count.load(std::memory_order_acquire) == 0) return 0;
+  }
+  j->empty_polls.store(0, std::memory_order_relaxed);
   std::lock_guard<SpinLock> l(j->mu);
   const uint32_t cap = static_cast<uint32_t>(j->ring.size());
   int k = 0;
@@ -1532,6 +1589,8 @@ urma_context_t* prov_create_context(urma_device_t* dev, uint32_t eid_index) {
   c->inbox->magic.store(kRegMagic, std::memory_order_release);
   c->event_fd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC | EFD_SEMAPHORE);
   c->pub.async_fd = c->event_fd;
+  if (const char* e = getenv("URMA_SHM_INLINE_POLL")) c->inline_poll = e[0] != '0';
+  ticks_per_us();   // calibrated before the first thread needs it
   c->nic = std::thread(nic_loop, c);
   return &c->pub;
 }

@@ -152,6 +152,7 @@ struct Channel {
   std::atomic<bool> lost{false};
   std::mutex mu;
   std::unordered_map<uint32_t, Pending> pending;
+  uint64_t next_deadline_scan = 0;   // under mu
   std::deque<Ready> ready;
   uint32_t next_req = 1;
   uint32_t ka_outstanding = 0;
@@ -227,6 +228,7 @@ struct Global {
   void* ka_ctx = nullptr;
   urpc_stats_t stats{};
   ub::PerfHist lat;
+  std::mutex lat_mu;   // guards `lat`
   std::mutex stat_mu;
   int admin_fd = -1;
   std::string admin_path;
@@ -282,6 +284,9 @@ void push_event(urpc_async_event_type_t type, uint32_t chid, int detail) {
     }
   }
 }
+// Counters are bumped from every thread that sends or polls: relaxed atomic adds, no lock (readers take a snapshot
+// that may be a few events apart between fields, which is all statistics need).
+inline void stat_add(uint64_t& field, uint64_t n = 1) { __atomic_fetch_add(&field, n, __ATOMIC_RELAXED); }
 inline void record(urpc_perf_point_t pt, uint64_t ns) {
   if (urpc_perf_recorder_t cb = g_recorder.load(std::memory_order_relaxed)) cb(pt, ns, g_recorder_ctx.load());
 }
@@ -369,8 +374,7 @@ int send_frame(uint64_t umqh, urpc_req_head_t head, const urpc_sge_t* sg, uint32
     sched_yield();
   }
   if (order.owns_lock()) order.unlock();
-  std::lock_guard<std::mutex> l(g.stat_mu);
-  g.stats.bytes_tx += total;
+  stat_add(g.stats.bytes_tx, total);
   return URPC_SUCCESS;
 }
 int send_msg(uint64_t umqh, const Head& h, const urpc_sge_t* sg, uint32_t nsg, const void* flat, uint32_t flat_len,
@@ -459,10 +463,7 @@ void channel_progress(Channel* ch) {
       keepalive = h.func_id == URPC_FUNC_ID_KEEPALIVE;
     }
     if (!ok) {
-      if (framed) {
-        std::lock_guard<std::mutex> l(g.stat_mu);
-        ++g.stats.errors;
-      }
+      if (framed) stat_add(g.stats.errors);
       umq_buf_free(b);
       continue;
     }
@@ -477,10 +478,7 @@ void channel_progress(Channel* ch) {
       umq_buf_free(b);
       continue;
     }
-    {
-      std::lock_guard<std::mutex> l(g.stat_mu);
-      g.stats.bytes_rx += r.total_size;
-    }
+    stat_add(g.stats.bytes_rx, r.total_size);
     if (keepalive) {
       ch->ka_outstanding = 0;
       umq_buf_free(b);
@@ -493,10 +491,13 @@ void channel_progress(Channel* ch) {
     }
     Pending& p = it->second;
     {
-      std::lock_guard<std::mutex> l(g.stat_mu);
-      ++g.stats.responses;
-      g.lat.add(ub::now_ns() - p.t0);
-      record(URPC_PERF_CALL_TO_RESPONSE, ub::now_ns() - p.t0);
+      const uint64_t took = ub::now_ns() - p.t0;
+      stat_add(g.stats.responses);
+      {
+        std::lock_guard<std::mutex> l(g.lat_mu);
+        g.lat.add(took);
+      }
+      record(URPC_PERF_CALL_TO_RESPONSE, took);
     }
     if (p.sync) {
       p.rsp.assign(b->buf_data + sizeof(urpc_req_head_t), b->buf_data + b->data_size);
@@ -508,14 +509,15 @@ void channel_progress(Channel* ch) {
       ch->pending.erase(it);
     }
   }
+  // deadlines are whole milliseconds: the table of calls in flight is walked at most once per millisecond, not on
+  // every poll of a busy channel
   const uint64_t now = ub::now_ns();
+  if (now < ch->next_deadline_scan) return;
+  ch->next_deadline_scan = now + 1000000ull;
   for (auto it = ch->pending.begin(); it != ch->pending.end();) {
     Pending& p = it->second;
     if (!p.done && now > p.deadline) {
-      {
-        std::lock_guard<std::mutex> l(g.stat_mu);
-        ++g.stats.timeouts;
-      }
+      stat_add(g.stats.timeouts);
       if (p.sync) {
         p.status = URPC_ERR_TIMEOUT;
         p.done = true;
@@ -956,7 +958,7 @@ void accept_loop() {
     if (!conn) {  // wrong key, clear-text client, or a client that stalled in the handshake
       g_log.log(ub::kLogWarn, "connection refused in the secure handshake: %s", err.c_str());
       std::lock_guard<std::mutex> l(g.stat_mu);
-      ++g.stats.errors;
+      stat_add(g.stats.errors);
       close(fd);
       continue;
     }
@@ -976,7 +978,7 @@ void accept_loop() {
       conn.reset();
       close(fd);
       std::lock_guard<std::mutex> l(g.stat_mu);
-      ++g.stats.errors;
+      stat_add(g.stats.errors);
       continue;
     }
     // one server queue per queue of the client's channel; the session is published only when all are bound
@@ -1067,15 +1069,12 @@ void keepalive_loop() {
           send_msg(ch->umqh, h, nullptr, 0, nullptr, 0, &ch->seal);
           ++ch->ka_outstanding;
           std::lock_guard<std::mutex> l2(g.stat_mu);
-          ++g.stats.keepalive_sent;
+          stat_add(g.stats.keepalive_sent);
         }
       }
       if (lost) {
         ch->lost = true;
-        {
-          std::lock_guard<std::mutex> l(g.stat_mu);
-          ++g.stats.keepalive_lost;
-        }
+        stat_add(g.stats.keepalive_lost);
         g_log.log(ub::kLogWarn, "channel %u: peer missed %u keepalive probes, marked lost", ch->id, limit);
         push_event(URPC_EVENT_CHANNEL_LOST, ch->id, (int)limit);
         if (g.ka_cb) g.ka_cb(ch->id, 0, g.ka_ctx);
@@ -1271,7 +1270,7 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
           h.version != s->proto.version || !open_msg(b, lseal)) {
         if (b->data_size >= sizeof(urpc_req_head_t)) {  // a request that fails the seal check is dropped and counted
           std::lock_guard<std::mutex> l(g.stat_mu);
-          ++g.stats.errors;
+          stat_add(g.stats.errors);
         }
         umq_buf_free(b);
         continue;
@@ -1283,7 +1282,7 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         if (alen >= 4) memcpy(&nrefs, args + alen - 4, 4);
         if (nrefs == 0 || nrefs > URPC_MAX_REFS || alen < 4 + nrefs * sizeof(RefEntry)) {
           std::lock_guard<std::mutex> l(g.stat_mu);
-          ++g.stats.errors;
+          stat_add(g.stats.errors);
           umq_buf_free(b);
           continue;
         }
@@ -1315,11 +1314,8 @@ int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
         auto it = g.funcs.find(h.func_id);
         if (it != g.funcs.end()) f = it->second;
       }
-      {
-        std::lock_guard<std::mutex> l(g.stat_mu);
-        ++g.stats.requests_served;
-        g.stats.bytes_rx += alen;
-      }
+      stat_add(g.stats.requests_served);
+      stat_add(g.stats.bytes_rx, alen);
       if (f.fn) {
         uint32_t rlen = static_cast<uint32_t>(rsp.size());
         const uint64_t e0 = ub::now_ns();
@@ -1568,15 +1564,13 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
     record(URPC_PERF_FUNC_CALL, ub::now_ns() - ch->pending[req_id].t0);
     if (rc != URPC_SUCCESS) {
       ch->pending.erase(req_id);
-      std::lock_guard<std::mutex> l2(g.stat_mu);
-      ++g.stats.errors;
+      stat_add(g.stats.errors);
       return rc;
     }
-    std::lock_guard<std::mutex> l2(g.stat_mu);
-    ++g.stats.calls;
+    stat_add(g.stats.calls);
   }
   if (!(opt && opt->sync)) return static_cast<int>(req_id);
-  for (;;) {
+  for (uint32_t spins = 0;; ++spins) {
     {
       std::lock_guard<std::mutex> l(ch->mu);
       channel_progress(ch);
@@ -1598,7 +1592,9 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
       ch->pending.erase(req_id);
       return URPC_ERR_SESSION_CLOSE;
     }
-    sched_yield();
+    // an answer usually takes microseconds: poll tightly for that long before giving the core away between polls
+    if (spins < 256) ub::cpu_relax();
+    else sched_yield();
   }
 }
 
@@ -1784,8 +1780,10 @@ int urpc_admin_query(const char* command, char* out, uint32_t cap) {
 
 int urpc_stats_get(urpc_stats_t* out) {
   if (!out) return URPC_ERR_EINVAL;
-  std::lock_guard<std::mutex> l(g.stat_mu);
-  *out = g.stats;
+  const uint64_t* src = reinterpret_cast<const uint64_t*>(&g.stats);
+  uint64_t* dst = reinterpret_cast<uint64_t*>(out);
+  static_assert(sizeof(urpc_stats_t) % sizeof(uint64_t) == 0, "urpc_stats_t is a row of 64-bit counters");
+  for (size_t i = 0; i < sizeof(urpc_stats_t) / sizeof(uint64_t); ++i) dst[i] = __atomic_load_n(src + i, __ATOMIC_RELAXED);
   return URPC_SUCCESS;
 }
 uint64_t urpc_mem_seg_register(void* va, uint64_t len) {
@@ -2308,10 +2306,9 @@ int urpc_queue_error_stats_get(uint64_t qh, uint64_t* stats, int len) {
 const char* urpc_queue_error_stats_name_get(int type) { return type >= 0 && type < 3 ? kQueueErrNames[type] : nullptr; }
 int urpc_error_stats_get(uint64_t* stats, int len) {
   if (!stats || len < 3) return URPC_ERR_EINVAL;
-  std::lock_guard<std::mutex> l(g.stat_mu);
-  stats[0] = g.stats.errors;
-  stats[1] = g.stats.timeouts;
-  stats[2] = g.stats.keepalive_lost;
+  stats[0] = __atomic_load_n(&g.stats.errors, __ATOMIC_RELAXED);
+  stats[1] = __atomic_load_n(&g.stats.timeouts, __ATOMIC_RELAXED);
+  stats[2] = __atomic_load_n(&g.stats.keepalive_lost, __ATOMIC_RELAXED);
   return 3;
 }
 
@@ -2326,7 +2323,7 @@ int urpc_log_config_set(int level, urpc_log_cb_t cb) {
   return URPC_SUCCESS;
 }
 int urpc_perf_get(uint64_t* count, uint64_t* avg_ns, uint64_t* p99_ns) {
-  std::lock_guard<std::mutex> l(g.stat_mu);
+  std::lock_guard<std::mutex> l(g.lat_mu);
   if (count) *count = g.lat.count();
   if (avg_ns) *avg_ns = static_cast<uint64_t>(g.lat.mean());
   if (p99_ns) *p99_ns = g.lat.quantile(0.99);
