@@ -1,6 +1,6 @@
 // dlock_example: exercises the distributed lock service end to end inside one process (server + client threads) and
-// prints lock-operation latency / throughput. With --selftest it also checks mutual exclusion, reader/writer
-// semantics, FIFO order of the fair lock, lease expiry, atomic objects and recovery after a server restart.
+// prints lock-operation latency / throughput (--clients N: N clients in parallel, each on its own lock). With
+// --selftest it also checks mutual exclusion, reader/writer semantics, FIFO order of the fair lock, lease expiry, atomic objects and recovery after a server restart.
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -31,10 +31,11 @@ static dlock_lock_desc_t desc(const char* name, dlock_type_t t) {
 
 int main(int argc, char** argv) {
   bool selftest = false;
-  int iters = 20000;
+  int iters = 20000, nclients = 0;
   for (int i = 1; i < argc; ++i) {
     if (!strcmp(argv[i], "--selftest")) selftest = true;
     else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--clients") && i + 1 < argc) nclients = atoi(argv[++i]);
   }
   dlock_server_cfg_t sc{};
   int sid;
@@ -65,6 +66,40 @@ int main(int argc, char** argv) {
   for (int i = 0; i < iters; ++i) CHECK(dlock_umo_atomic64_faa(c1, ob, 1, &old) == DLOCK_SUCCESS, "faa");
   sec = (ub::now_ns() - t0) * 1e-9;
   printf("object fetch-add: %.1f us end to end, %.0f ops/s\n", sec / iters * 1e6, iters / sec);
+
+  if (nclients > 0) {
+    // aggregate rate: every client (own connection, own thread) works on a lock of its own, as the clients of a
+    // cluster that partition their data do; the server's one command thread serves them all
+    std::vector<int> cl(nclients);
+    std::vector<int32_t> ids(nclients);
+    for (int k = 0; k < nclients; ++k) {
+      CHECK(dlock_client_init(&cl[k], "127.0.0.1", port) == DLOCK_SUCCESS, "client init (--clients)");
+      char nm[32];
+      snprintf(nm, sizeof(nm), "part-%d", k);
+      dlock_lock_desc_t dk = desc(nm, DLOCK_ATOMIC);
+      CHECK(dlock_get_lock(cl[k], &dk, &ids[k]) == DLOCK_SUCCESS, "get_lock (--clients)");
+    }
+    std::atomic<int> go{0}, failed{0};
+    std::vector<std::thread> th;
+    for (int k = 0; k < nclients; ++k)
+      th.emplace_back([&, k] {
+        dlock_lock_req_t r{ids[k], DLOCK_LOCK_EXCLUSIVE, 5000};
+        while (!go.load()) sched_yield();
+        for (int i = 0; i < iters; ++i)
+          if (dlock_trylock(cl[k], &r) != DLOCK_SUCCESS || dlock_unlock(cl[k], ids[k]) != DLOCK_SUCCESS) {
+            ++failed;
+            return;
+          }
+      });
+    t0 = ub::now_ns();
+    go = 1;
+    for (auto& t : th) t.join();
+    sec = (ub::now_ns() - t0) * 1e-9;
+    CHECK(failed.load() == 0, "lock operations of the parallel clients");
+    printf("%d clients: %.0f lock ops/s in total, %.1f us per operation seen by a client\n", nclients,
+           2.0 * iters * nclients / sec, sec / (2.0 * iters) * 1e6);
+    for (int k = 0; k < nclients; ++k) dlock_client_deinit(cl[k]);
+  }
 
   if (selftest) {
     // mutual exclusion: three clients increment a plain counter under the lock

@@ -852,16 +852,22 @@ uint64_t ticks_per_us() {
 // progress in any case.
 void nic_loop(ShmCtx* c) {
   urma_log_set_thread_tag("shm-nic");
-  uint32_t idle = 0;
+  uint32_t idle = 0, deferred_rounds = 0;
   uint64_t last_scan = ub::now_ns();
   const uint64_t defer_ticks = 3 * ticks_per_us();
   while (!c->stop.load(std::memory_order_relaxed)) {
     const bool app_drives =
         c->inline_poll && fast_ticks() - c->app_poll_ticks.load(std::memory_order_relaxed) < defer_ticks;
     if (app_drives) {
-      for (int i = 0; i < 8; ++i) cpu_relax();
-      if ((++idle & 1023) != 0) continue;   // the periodic work below still runs now and then
-    } else if (consume(c, 64) > 0) {
+      // stays close for a while (the application may stop polling any moment), then stops burning a core for an
+      // application that evidently polls all the time: it looks in every 50 us
+      if (++deferred_rounds < 2000) {
+        for (int i = 0; i < 8; ++i) cpu_relax();
+        if ((deferred_rounds & 1023) != 0) continue;   // the periodic work below still runs now and then
+      } else {
+        usleep(50);
+      }
+    } else if (deferred_rounds = 0, consume(c, 64) > 0) {
       idle = 0;
       continue;
     } else if (++idle < 4000) {
