@@ -78,6 +78,11 @@ def test_dlock_selftest_including_recovery(tmp_path):
     assert rc == 0 and "dlock_example: OK" in out, out
 
 
+def test_dlock_parallel_clients_on_their_own_locks(tmp_path):
+    rc, out = _run([BIN / "dlock_example", "--clients", "3", "--iters", "3000"], tmp_path)
+    assert rc == 0 and "3 clients:" in out and "dlock_example: OK" in out, out
+
+
 def test_ums_accelerated_and_fallback(tmp_path):
     rc, out = _run([BIN / "ums_perftest", "--selftest", "--iters", "3000"], tmp_path)
     assert rc == 0 and "ums_perftest: OK" in out, out
@@ -105,6 +110,15 @@ def test_ums_link_groups_control_messages_and_moderation(tmp_path):
 def test_urma_perftest_single_process(tmp_path, op):
     rc, out = _run([BIN / "urma_perftest", "--op", op, "--iters", "2000"], tmp_path)
     assert rc == 0 and "urma_perftest: OK" in out, out
+
+
+@pytest.mark.parametrize("op", ["write", "send", "read"])
+def test_urma_perftest_with_the_context_thread_doing_all_the_work(tmp_path, op):
+    """The inbox of a context is executed by the polling application thread by default; with the switch off only the
+    context's own thread does it. Both ways must give the same results."""
+    rc, out = _run([BIN / "urma_perftest", "--op", op, "--iters", "2000", "--size", "20000"], tmp_path,
+                   env_extra={"URMA_SHM_INLINE_POLL": "0"})
+    assert rc == 0 and "urma_perftest: OK" in out and "errors 0" in out, out
 
 
 def test_urma_perftest_over_bond_device(tmp_path):
