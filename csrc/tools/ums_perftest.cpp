@@ -1,5 +1,5 @@
 // ums_perftest: ping-pong latency and streaming throughput of a UMS connection compared with plain TCP on loopback,
-// plus a self-check of the fallback path. `ums_perftest [--size N] [--iters N] [--selftest] [--linkgroups]`
+// plus a self-check of the fallback path. `ums_perftest [--size N] [--iters N] [--conns N] [--selftest] [--linkgroups]`
 #include <arpa/inet.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
@@ -89,6 +89,67 @@ static int run(const Api& a, const char* name, size_t size, int iters, double* l
   srv.join();
   a.close_(ls);
   if (!ok || got != stream) return fail(name);
+  return 0;
+}
+
+// `conns` connections at once, each a ping-pong between a client thread and a server thread of its own: the average
+// one-way latency over all of them (the reference's "10 connections" row).
+static int run_many(const Api& a, const char* name, size_t size, int iters, int conns, double* lat_us) {
+  const int ls = a.sock(AF_INET, SOCK_STREAM, 0);
+  sockaddr_in ad{};
+  ad.sin_family = AF_INET;
+  ad.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+  if (bind(ls, (sockaddr*)&ad, sizeof(ad)) || a.listen_(ls, conns + 4)) return fail("listen");
+  socklen_t l = sizeof(ad);
+  getsockname(ls, (sockaddr*)&ad, &l);
+  std::atomic<bool> ok{true};
+  std::atomic<int> ready{0};
+  std::vector<std::thread> servers, clients;
+  std::thread acceptor([&] {
+    for (int k = 0; k < conns; ++k) {
+      const int c = a.accept_(ls, nullptr, nullptr);
+      if (c < 0) {
+        ok = false;
+        return;
+      }
+      servers.emplace_back([&, c] {
+        std::vector<char> b(size);
+        for (int i = 0; i < iters && ok; ++i)
+          if (!(xfer_all(a, c, b.data(), size, false) && xfer_all(a, c, b.data(), size, true))) ok = false;
+        a.close_(c);
+      });
+    }
+  });
+  std::vector<double> each(conns, 0.0);
+  for (int k = 0; k < conns; ++k)
+    clients.emplace_back([&, k] {
+      const int c = a.sock(AF_INET, SOCK_STREAM, 0);
+      if (a.connect_(c, (sockaddr*)&ad, sizeof(ad))) {
+        ok = false;
+        ++ready;
+        return;
+      }
+      int one = 1;
+      setsockopt(c, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+      std::vector<char> b(size, (char)(k + 1)), e(size);
+      ++ready;
+      while (ready.load() < conns && ok) std::this_thread::yield();   // all connections start together
+      const uint64_t t0 = ub::now_ns();
+      for (int i = 0; i < iters && ok; ++i) {
+        if (!(xfer_all(a, c, b.data(), size, true) && xfer_all(a, c, e.data(), size, false))) ok = false;
+        if (ok && (e[0] != b[0] || e[size - 1] != b[size - 1])) ok = false;
+      }
+      each[k] = (ub::now_ns() - t0) / 1e3 / iters / 2;
+      a.close_(c);
+    });
+  for (auto& t : clients) t.join();
+  acceptor.join();
+  for (auto& t : servers) t.join();
+  a.close_(ls);
+  if (!ok) return fail(name);
+  double sum = 0;
+  for (double v : each) sum += v;
+  *lat_us = sum / conns;
   return 0;
 }
 
@@ -217,15 +278,26 @@ int main(int argc, char** argv) {
   size_t size = 8192;
   int iters = 20000;
   bool selftest = false;
+  int conns = 0;
   for (int i = 1; i < argc; ++i)
     if (!strcmp(argv[i], "--linkgroups")) return linkgroup_check();
   for (int i = 1; i < argc; ++i) {
     if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--selftest")) selftest = true;
+    else if (!strcmp(argv[i], "--conns") && i + 1 < argc) conns = atoi(argv[++i]);
   }
   const Api ums{ums_socket, ums_listen, ums_accept, ums_connect, ums_send, ums_recv, ums_close};
   const Api tcp{socket, listen, accept, connect, send, recv, close};
+  if (conns > 0) {
+    double mu, mt;
+    if (run_many(ums, "ums (many connections)", size, iters, conns, &mu)) return 1;
+    if (run_many(tcp, "tcp (many connections)", size, iters, conns, &mt)) return 1;
+    printf("size=%zu, %d connections at once: UMS one-way latency %.2f us | TCP loopback %.2f us | latency %.0f%% lower\n",
+           size, conns, mu, mt, (1.0 - mu / mt) * 100.0);
+    printf("ums_perftest: OK\n");
+    return 0;
+  }
   double lu, gu, lt, gt;
   bool au, at;
   if (run(ums, "ums", size, iters, &lu, &gu, &au)) return 1;

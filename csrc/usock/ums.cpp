@@ -3,6 +3,7 @@
 #include "ums_agent_proto.h"
 
 #include "ub_secure.h"
+#include "ub_util.h"
 #include "ums_shm.h"
 
 #include <arpa/inet.h>
@@ -178,6 +179,9 @@ struct Conn {
 struct State {
   std::mutex mu;
   std::unordered_map<int, Conn> conns;
+  // Moves whenever `conns` changes (under mu). A thread keeps a copy of the connection it used last together with
+  // the value it saw: while the two agree the copy is the table's entry, and send / recv need no lock at all.
+  std::atomic<uint64_t> conns_gen{1};
   ums_stats_t stats{};
   std::unordered_map<std::string, std::shared_ptr<Link>> links;                 // every mapped link, by role ("c:" created here, "s:" accepted here) and name
   std::unordered_map<std::string, std::vector<std::shared_ptr<Link>>> groups;   // links this process owns, by server
@@ -191,6 +195,8 @@ State& state() {
 #define g_links (state().links)
 #define g_groups (state().groups)
 #define g_stats (state().stats)
+// Counters are bumped from every thread that sends or receives: relaxed atomic adds, never under a lock of their own.
+inline void stat_add(uint64_t& f, uint64_t n = 1) { __atomic_fetch_add(&f, n, __ATOMIC_RELAXED); }
 std::atomic<uint64_t> g_seq{1};
 
 std::string dir() {
@@ -239,6 +245,27 @@ Conn* find(int fd) {
   auto it = g_conns.find(fd);
   return it == g_conns.end() ? nullptr : &it->second;
 }
+inline void conns_changed() { state().conns_gen.fetch_add(1, std::memory_order_release); }   // caller holds g_mu
+// The data calls' view of a descriptor: known = the table has it. Served from the calling thread's copy while the
+// table has not changed since the copy was made.
+struct ConnView {
+  int fd = -1;
+  uint64_t gen = 0;
+  bool known = false;
+  Conn c;
+};
+const ConnView& lookup(int fd) {
+  static thread_local ConnView v;
+  const uint64_t gen = state().conns_gen.load(std::memory_order_acquire);
+  if (v.fd == fd && v.gen == gen) return v;
+  std::lock_guard<std::mutex> l(g_mu);
+  v.gen = state().conns_gen.load(std::memory_order_relaxed);
+  v.fd = fd;
+  Conn* p = find(fd);
+  v.known = p != nullptr;
+  v.c = p ? *p : Conn();
+  return v;
+}
 
 size_t ring_write(Ring* r, const char* src, size_t n) {
   const uint64_t prod = r->prod.load(std::memory_order_relaxed);
@@ -286,9 +313,8 @@ void dim_sample(Dim* d, uint32_t level, bool caught, bool late) {
   if (slept >= 24 && level > 0) next = level - 1;
   else if (slept + lt >= 12 && slept < 12 && level < 4) next = level + 1;
   if (next != level && d->level.compare_exchange_strong(level, next)) {
-    std::lock_guard<std::mutex> l(g_mu);
-    if (next > level) ++g_stats.dim_up;
-    else ++g_stats.dim_down;
+    if (next > level) stat_add(g_stats.dim_up);
+    else stat_add(g_stats.dim_down);
   }
 }
 
@@ -361,7 +387,7 @@ bool llc_push(Link* l, uint32_t type, uint32_t flags, uint32_t seq, uint32_t slo
   memset(m.name, 0, sizeof(m.name));
   if (name) snprintf(m.name, sizeof(m.name), "%s", name);
   r.prod.store(prod + 1, std::memory_order_release);
-  ++g_stats.llc_tx;
+  stat_add(g_stats.llc_tx);
   return true;
 }
 bool llc_has_input(Link* l) {
@@ -376,7 +402,7 @@ void llc_progress(Link* l) {
     if (cons == r.prod.load(std::memory_order_acquire)) return;
     const LlcMsg m = r.msg[cons % kLlcEntries];
     r.cons.store(cons + 1, std::memory_order_release);
-    ++g_stats.llc_rx;
+    stat_add(g_stats.llc_rx);
     const bool rsp = (m.flags & kLlcResponse) != 0;
     switch (m.type) {
       case LLC_CONFIRM_LINK:
@@ -393,7 +419,7 @@ void llc_progress(Link* l) {
               nl->group = l->group;
               nl->empty_since_ms = now_ms();
               g_links[std::string("s:") + nm] = nl;
-              ++g_stats.links_created;
+              stat_add(g_stats.links_created);
             }
           }
           llc_push(l, LLC_ADD_LINK, kLlcResponse, m.seq, 0);
@@ -407,7 +433,7 @@ void llc_progress(Link* l) {
           llc_push(l, LLC_TEST_LINK, kLlcResponse, m.seq, 0);
         } else {
           l->test_acked = m.seq;
-          ++g_stats.link_tests_ok;
+          stat_add(g_stats.link_tests_ok);
         }
         break;
       default: break;   // DELETE_CONN is a notice
@@ -447,7 +473,7 @@ void reap_links() {
     }
     munmap(l->shm, sizeof(LinkShm));
     l->shm = nullptr;
-    ++g_stats.links_freed;
+    stat_add(g_stats.links_freed);
     it = g_links.erase(it);
   }
 }
@@ -503,7 +529,7 @@ std::shared_ptr<Link> link_pick(const std::string& key, uint64_t salt, uint32_t*
     return true;
   }();
   (void)cleanup_registered;
-  ++g_stats.links_created;
+  stat_add(g_stats.links_created);
   l->shm->slot_used.fetch_or(1u);
   *slot = 0;
   *first = 1;
@@ -527,6 +553,7 @@ int ums_socket(int domain, int type, int protocol) {
   if (fd >= 0 && (domain == AF_INET || domain == AF_INET6) && (type & 0xf) == SOCK_STREAM) {
     std::lock_guard<std::mutex> l(g_mu);
     g_conns[fd] = Conn();
+    conns_changed();
   }
   return fd;
 }
@@ -542,6 +569,7 @@ int ums_adopt_listener(int fd) {
   ub::random_bytes(&tok, sizeof(tok));
   std::lock_guard<std::mutex> lk(g_mu);
   Conn& c = g_conns[fd];
+  conns_changed();
   c.listener = true;
   c.port = ntohs(a.sin_port);
   const int m = ::open(listen_marker(c.port).c_str(), O_CREAT | O_WRONLY | O_TRUNC, 0600);  // "this port speaks UMS"
@@ -611,7 +639,7 @@ int ums_adopt_accepted(int listen_fd, int fd) {
     const bool trusted = clc_verify(in, false) && agent_resolve(in.shm_name) && !strchr(in.shm_name, '/');
     if (!trusted) {
       std::lock_guard<std::mutex> l(g_mu);
-      ++g_stats.conns_auth_fail;
+      stat_add(g_stats.conns_auth_fail);
     }
     const std::string path = dir() + "/" + in.shm_name;
     if (trusted && in.slot != kNoSlot) {   // a slot of a link: the link is mapped once, however many connections
@@ -624,7 +652,7 @@ int ums_adopt_accepted(int listen_fd, int fd) {
       else if ((lk = link_map(in.shm_name, false))) {
         lk->group = std::string(lk->shm->group, strnlen(lk->shm->group, sizeof(lk->shm->group)));
         g_links["s:" + lk->name] = lk;
-        ++g_stats.links_created;
+        stat_add(g_stats.links_created);
       }
       if (lk && !lk->owner && in.slot < kLinkSlots && (lk->shm->slot_used.load() & (1u << in.slot)) &&
           lk->shm->state.load() != LINK_DELETED) {
@@ -642,7 +670,7 @@ int ums_adopt_accepted(int listen_fd, int fd) {
         c.tx = &c.shm->s2c;
         c.rx = &c.shm->c2s;
         c.dim = std::make_shared<Dim>();
-        ++g_stats.conns_on_links;
+        stat_add(g_stats.conns_on_links);
       }
     }
     const int sfd = (trusted && in.slot == kNoSlot) ? ::open(path.c_str(), O_RDWR | O_NOFOLLOW) : -1;
@@ -671,9 +699,10 @@ int ums_adopt_accepted(int listen_fd, int fd) {
   int one = 1;
   setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
   std::lock_guard<std::mutex> l(g_mu);
-  if (c.accelerated) ++g_stats.conns_ums;
-  else ++g_stats.conns_fallback;
+  if (c.accelerated) stat_add(g_stats.conns_ums);
+  else stat_add(g_stats.conns_fallback);
   g_conns[fd] = c;
+  conns_changed();
   return c.accelerated ? 1 : 0;
 }
 int ums_accept(int fd, struct sockaddr* addr, socklen_t* len) {
@@ -741,7 +770,7 @@ int ums_adopt_connected(int fd, const struct sockaddr* peer) {
     if (token_stored) ums_agent_del(nullptr, token_id);   // one connection, one use
     if (answered && !trusted) {
       std::lock_guard<std::mutex> l(g_mu);
-      ++g_stats.conns_auth_fail;
+      stat_add(g_stats.conns_auth_fail);
     }
     if (trusted && in.accept && lk && in.slot == out.slot) {
       c.accelerated = true;
@@ -753,7 +782,7 @@ int ums_adopt_connected(int fd, const struct sockaddr* peer) {
       c.dim = std::make_shared<Dim>();
       std::lock_guard<std::mutex> l(g_mu);
       llc_progress(lk.get());   // the server's CONFIRM LINK came before its answer: reply, the link is ACTIVE
-      ++g_stats.conns_on_links;
+      stat_add(g_stats.conns_on_links);
     } else if (trusted && in.accept && !lk) {
       c.accelerated = true;
       c.shm = static_cast<ConnShm*>(p);
@@ -775,9 +804,10 @@ int ums_adopt_connected(int fd, const struct sockaddr* peer) {
     setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
   }
   std::lock_guard<std::mutex> l(g_mu);
-  if (c.accelerated) ++g_stats.conns_ums;
-  else ++g_stats.conns_fallback;
+  if (c.accelerated) stat_add(g_stats.conns_ums);
+  else stat_add(g_stats.conns_fallback);
   g_conns[fd] = c;
+  conns_changed();
   return c.accelerated ? 1 : 0;
 }
 int ums_connect(int fd, const struct sockaddr* addr, socklen_t len) {
@@ -787,18 +817,12 @@ int ums_connect(int fd, const struct sockaddr* addr, socklen_t len) {
 }
 
 ssize_t ums_send(int fd, const void* buf, size_t n, int flags) {
-  Conn c;
-  {
-    std::lock_guard<std::mutex> l(g_mu);
-    Conn* p = find(fd);
-    if (!p || !p->accelerated) {
-      if (p) g_stats.bytes_tx_tcp += n;
-      c.accelerated = false;
-    } else {
-      c = *p;
-    }
+  const ConnView& view = lookup(fd);
+  const Conn& c = view.c;
+  if (!c.accelerated) {
+    if (view.known) stat_add(g_stats.bytes_tx_tcp, n);
+    return libc().send(fd, buf, n, flags);
   }
-  if (!c.accelerated) return libc().send(fd, buf, n, flags);
   if (c.link && llc_has_input(c.link.get())) {   // control messages of the link are served from inside data calls
     std::lock_guard<std::mutex> l(g_mu);
     llc_progress(c.link.get());
@@ -809,7 +833,12 @@ ssize_t ums_send(int fd, const void* buf, size_t n, int flags) {
   }
   const char* p = static_cast<const char*>(buf);
   size_t sent = 0;
-  const bool nb = nonblocking(fd) || (flags & MSG_DONTWAIT);
+  // (whether the descriptor is non-blocking is a system call to find out: asked only when the call would wait)
+  int nb_state = (flags & MSG_DONTWAIT) ? 1 : -1;
+  auto nb_now = [&]() {
+    if (nb_state < 0) nb_state = nonblocking(fd) ? 1 : 0;
+    return nb_state == 1;
+  };
   uint32_t spins = 0;
   while (sent < n) {
     const uint64_t before = c.tx->prod.load(std::memory_order_relaxed);
@@ -826,13 +855,12 @@ ssize_t ums_send(int fd, const void* buf, size_t n, int flags) {
           if (sent) break;
           return -1;
         }
-        std::lock_guard<std::mutex> l(g_mu);
-        ++g_stats.doorbells;
+        stat_add(g_stats.doorbells);
       }
       spins = 0;
       continue;
     }
-    if (nb) {
+    if (nb_now()) {
       if (sent) break;
       errno = EAGAIN;
       return -1;
@@ -845,40 +873,32 @@ ssize_t ums_send(int fd, const void* buf, size_t n, int flags) {
         errno = EPIPE;
         return sent ? (ssize_t)sent : -1;
       }
-      std::lock_guard<std::mutex> l(g_mu);
-      ++g_stats.tx_waits;
+      stat_add(g_stats.tx_waits);
     } else {
       sched_yield();
     }
   }
-  std::lock_guard<std::mutex> l(g_mu);
-  g_stats.bytes_tx_ring += sent;
+  stat_add(g_stats.bytes_tx_ring, sent);
   return static_cast<ssize_t>(sent);
 }
 
 ssize_t ums_recv(int fd, void* buf, size_t n, int flags) {
-  Conn c;
-  {
-    std::lock_guard<std::mutex> l(g_mu);
-    Conn* p = find(fd);
-    if (!p || !p->accelerated) c.accelerated = false;
-    else c = *p;
-  }
+  const ConnView& view = lookup(fd);
+  const Conn& c = view.c;
   if (!c.accelerated) {
     const ssize_t r = libc().recv(fd, buf, n, flags);
-    if (r > 0) {
-      std::lock_guard<std::mutex> l(g_mu);
-      g_stats.bytes_rx_tcp += r;
-    }
+    if (r > 0) stat_add(g_stats.bytes_rx_tcp, r);
     return r;
   }
-  const bool nb = nonblocking(fd) || (flags & MSG_DONTWAIT);
+  int nb_state = (flags & MSG_DONTWAIT) ? 1 : -1;   // found out (a system call) only when the ring is empty
   for (;;) {
     if (c.link && llc_has_input(c.link.get())) {
       std::lock_guard<std::mutex> l(g_mu);
       llc_progress(c.link.get());
     }
     size_t k = ring_read(c.rx, static_cast<char*>(buf), n, flags & MSG_PEEK);
+    if (!k && nb_state < 0) nb_state = nonblocking(fd) ? 1 : 0;
+    const bool nb = nb_state == 1;
     if (!k && !nb) {
       // short busy-poll before sleeping: a request/response partner usually answers within microseconds, and the
       // answer is then picked up without a system call on either side
@@ -888,11 +908,7 @@ ssize_t ums_recv(int fd, void* buf, size_t n, int flags) {
       const uint32_t budget = kDimSpins[level];
       uint32_t spin = 0;
       for (; spin < budget && !k; ++spin) {
-#if defined(__x86_64__)
-        __builtin_ia32_pause();
-#else
-        __asm__ __volatile__("" ::: "memory");
-#endif
+        ub::cpu_relax();
         k = ring_read(c.rx, static_cast<char*>(buf), n, flags & MSG_PEEK);
       }
       if (c.dim) dim_sample(c.dim.get(), level, k != 0, k != 0 && spin > budget / 2);
@@ -905,8 +921,7 @@ ssize_t ums_recv(int fd, void* buf, size_t n, int flags) {
     }
     if (k) {
       if (c.rx->waiter.load(std::memory_order_relaxed)) c.rx->waiter.store(0, std::memory_order_relaxed);
-      std::lock_guard<std::mutex> l(g_mu);
-      g_stats.bytes_rx_ring += k;
+      stat_add(g_stats.bytes_rx_ring, k);
       return static_cast<ssize_t>(k);
     }
     // nothing in the ring: consume doorbells (or learn that the peer closed)
@@ -944,6 +959,7 @@ int ums_close(int fd) {
       c = it->second;
       known = true;
       g_conns.erase(it);
+      conns_changed();
     }
   }
   if (known) {
@@ -981,8 +997,11 @@ int ums_owns(int fd) {
 void ums_get_stats(ums_stats_t* out) {
   std::lock_guard<std::mutex> l(g_mu);
   reap_links();
-  g_stats.links_active = g_links.size();
-  *out = g_stats;
+  __atomic_store_n(&g_stats.links_active, g_links.size(), __ATOMIC_RELAXED);
+  const uint64_t* src = reinterpret_cast<const uint64_t*>(&g_stats);
+  uint64_t* dst = reinterpret_cast<uint64_t*>(out);
+  static_assert(sizeof(ums_stats_t) % sizeof(uint64_t) == 0, "ums_stats_t is a row of 64-bit counters");
+  for (size_t i = 0; i < sizeof(ums_stats_t) / sizeof(uint64_t); ++i) dst[i] = __atomic_load_n(src + i, __ATOMIC_RELAXED);
 }
 int ums_link_test(int fd, int timeout_ms) {
   std::shared_ptr<Link> lk;
@@ -996,7 +1015,7 @@ int ums_link_test(int fd, int timeout_ms) {
     if (!llc_push(lk.get(), LLC_TEST_LINK, 0, seq, p->slot)) return -1;
     if (p->tx->waiter.load()) {   // the peer sleeps in recv on this connection: wake it, it looks at the control ring
       const char bell = 1;
-      if (libc().send(fd, &bell, 1, MSG_NOSIGNAL | MSG_DONTWAIT) > 0) ++g_stats.doorbells;
+      if (libc().send(fd, &bell, 1, MSG_NOSIGNAL | MSG_DONTWAIT) > 0) stat_add(g_stats.doorbells);
     }
   }
   const uint64_t deadline = now_ms() + static_cast<uint64_t>(timeout_ms > 0 ? timeout_ms : 0);

@@ -88,6 +88,11 @@ def test_ums_accelerated_and_fallback(tmp_path):
     assert rc == 0 and "ums_perftest: OK" in out, out
 
 
+def test_ums_several_connections_at_once(tmp_path):
+    rc, out = _run([BIN / "ums_perftest", "--conns", "4", "--iters", "2000", "--size", "8192"], tmp_path)
+    assert rc == 0 and "4 connections at once" in out and "ums_perftest: OK" in out, out
+
+
 def test_ums_link_groups_control_messages_and_moderation(tmp_path):
     """40 connections share two link files, closed slots are reused, TEST LINK is answered by sleeping peers, empty
     links are removed after the linger time, the busy-poll budget follows the partner's speed."""
