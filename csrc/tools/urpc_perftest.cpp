@@ -1,12 +1,13 @@
 // urpc_perftest: latency / call-rate measurement and self-check of the URPC framework (server thread + client in
 // one process by default; `--server PORT` / `--client PORT` run the two sides as separate processes).
-//   urpc_perftest [--size N] [--iters N] [--queues N] [--selftest]
+//   urpc_perftest [--size N] [--iters N] [--queues N] [--server-threads N] [--selftest]
 // --queues N gives the channel N explicit queue pairs (calls spread over them in turn).
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
 #include <thread>
 #include <vector>
@@ -53,7 +54,7 @@ int main(int argc, char** argv) {
   uint32_t size = 4096, iters = 5000;
   bool selftest = false;
   int hold_ms = 0;  // keep the process (and its management socket) alive this long after the run
-  int server_port = -1, client_port = -1, queues = 1;
+  int server_port = -1, client_port = -1, queues = 1, server_threads = 1;
   for (int i = 1; i < argc; ++i) {
     if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
@@ -62,6 +63,7 @@ int main(int argc, char** argv) {
     else if (!strcmp(argv[i], "--hold-ms") && i + 1 < argc) hold_ms = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--server") && i + 1 < argc) server_port = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--client") && i + 1 < argc) client_port = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--server-threads") && i + 1 < argc) server_threads = std::max(1, atoi(argv[++i]));
   }
   urpc_config_t cfg{};
   cfg.role = URPC_ROLE_SERVER_CLIENT;
@@ -71,21 +73,22 @@ int main(int argc, char** argv) {
   if (urpc_init(&cfg) != URPC_SUCCESS) return fail("urpc_init");
   urpc_keepalive_callback_register(ka_cb, nullptr);
   std::atomic<bool> stop{false}, serve{true};
-  std::thread srv;
+  std::vector<std::thread> srv;
   int port = client_port;
   if (client_port < 0) {
     urpc_func_register(1, echo_fn, nullptr);
     urpc_func_register(2, sum_fn, nullptr);
     port = urpc_server_start("127.0.0.1", server_port > 0 ? server_port : 0);
     if (port <= 0) return fail("server_start");
-    srv = std::thread([&] {
+    // each server thread serves its share of the attached clients (session number modulo the thread count)
+    for (int k = 0; k < server_threads; ++k) srv.emplace_back([&, k] {
       urpc_poll_msg_t m[8];
       while (!stop.load()) {
         if (!serve.load()) {
           usleep(1000);
           continue;
         }
-        const int n = urpc_server_poll(m, 8);
+        const int n = urpc_server_poll_shard((uint32_t)k, (uint32_t)server_threads, m, 8);
         for (int i = 0; i < n; ++i) {
           if (m[i].func_id == 7) {  // handled by the application: reverse the bytes
             std::vector<uint8_t> r(static_cast<uint8_t*>(m[i].data), static_cast<uint8_t*>(m[i].data) + m[i].len);
@@ -243,7 +246,7 @@ int main(int argc, char** argv) {
   urpc_channel_destroy(ch);
   for (uint64_t q : lanes) urpc_queue_destroy(q);
   stop = true;
-  if (srv.joinable()) srv.join();
+  for (auto& t : srv) t.join();
   urpc_uninit();
   if (rc == 0) printf("urpc_perftest: OK\n");
   return rc;

@@ -26,6 +26,7 @@
 #include <map>
 #include <memory>
 #include <mutex>
+#include <shared_mutex>
 #include <string>
 #include <thread>
 #include <unordered_map>
@@ -38,7 +39,8 @@
 namespace {
 
 constexpr uint32_t kSlotPayload = 4096;
-constexpr uint32_t kRingSlots = 1024;  // power of two
+constexpr uint32_t kRings = 4;          // rings per inbox (power of two)
+constexpr uint32_t kRingSlots = 256;   // slots per ring (power of two)
 constexpr uint32_t kMaxCtx = 256;
 constexpr uint32_t kRegMagic = 0x55524d41;  // "URMA"
 
@@ -57,15 +59,23 @@ struct Slot {
   MsgHdr h;
   uint8_t payload[kSlotPayload];
 };
-struct Inbox {
-  std::atomic<uint32_t> magic;
-  std::atomic<uint32_t> owner_pid;
+// An inbox is several rings. A message goes to the ring that its queue's number selects (requests: the target
+// jetty; answers: the send queue that asked), so everything whose order matters shares a ring, while the rings can be
+// executed by different threads at the same time - what several receive queues do for a NIC.
+struct Ring {
   std::atomic<uint64_t> enq;
-  char pad0[48];
+  char pad0[56];
   std::atomic<uint64_t> deq;
   char pad1[56];
   Slot slots[kRingSlots];
 };
+struct Inbox {
+  std::atomic<uint32_t> magic;
+  std::atomic<uint32_t> owner_pid;
+  char pad[56];
+  Ring ring[kRings];
+};
+inline Ring* ring_of(Inbox* in, uint32_t queue_id) { return &in->ring[queue_id & (kRings - 1)]; }
 struct CtxSlot {
   std::atomic<uint32_t> uasid;  // 0 = free
   std::atomic<uint32_t> pid;
@@ -106,7 +116,7 @@ void* map_file(const std::string& path, size_t bytes, bool create, bool* created
 }
 
 // Vyukov bounded queue, multi-producer side. Returns the reserved slot or nullptr when the ring is full.
-Slot* ring_reserve(Inbox* in, uint64_t* pos_out) {
+Slot* ring_reserve(Ring* in, uint64_t* pos_out) {
   uint64_t pos = in->enq.load(std::memory_order_relaxed);
   for (;;) {
     Slot* s = &in->slots[pos & (kRingSlots - 1)];
@@ -252,8 +262,10 @@ struct Pending {
   urma_jetty_id_t remote;
 };
 struct Reasm {
-  std::vector<uint8_t> data;
+  std::vector<uint8_t> data;   // staging, used only when no receive request was posted when the message began
   uint32_t got = 0;
+  bool direct = false;         // fragments go straight into `wr`'s buffers
+  RecvWr wr;
 };
 constexpr uint32_t kPendSlots = 4096;  // power of two
 constexpr uint64_t kPendBusy = ~0ull;
@@ -275,9 +287,12 @@ struct ShmCtx {
   std::thread nic;
   std::atomic<bool> stop{false};
   std::mutex mu;  // guards the tables below
-  // Held by the NIC thread while it handles one message (it may touch queues it looked up under `mu` after dropping
-  // `mu`) and by the delete operations while they free a queue: an object is never freed under the NIC thread's feet.
-  std::mutex life_mu;
+  // Held shared by whoever handles messages (they may touch queues they looked up under `mu` after dropping `mu`)
+  // and exclusively by the delete operations while they free a queue: an object is never freed under a handler's
+  // feet. `deleters` makes the handlers step aside for a waiting delete (a reader-preferring lock would starve it).
+  std::shared_mutex life_mu;
+  std::atomic<int> deleters{0};
+  std::atomic<bool> ring_busy[kRings] = {};   // ring r is being executed
   std::unordered_map<uint32_t, SegReg> segs;
   std::unordered_map<uint32_t, RecvQueue*> rqs;
   // Requests that wait for their answer. A request id names its slot (id modulo the table size); the slot's `id`
@@ -303,10 +318,13 @@ struct ShmCtx {
   // answering into each other's full inbox would deadlock); it parks the answer here and retries later.
   struct Deferred {
     uint32_t uasid;
+    uint32_t queue;   // selects the ring of the peer's inbox
     MsgHdr h;
     std::vector<uint8_t> payload;
   };
-  std::deque<Deferred> deferred;  // under life_mu
+  SpinLock deferred_mu;
+  std::deque<Deferred> deferred;            // under deferred_mu
+  std::atomic<uint32_t> deferred_n{0};      // its size, readable without the lock
 };
 
 // ---------------------------------------------------------------------------------------------- helpers
@@ -370,7 +388,7 @@ Inbox* peer_inbox(ShmCtx* c, uint32_t uasid) {
 }
 
 // Blocks (bounded) until a slot is free in the target inbox. Returns false if the ring stayed full.
-Slot* reserve_wait(Inbox* in, uint64_t* pos, uint32_t timeout_ms) {
+Slot* reserve_wait(Ring* in, uint64_t* pos, uint32_t timeout_ms) {
   uint64_t t0 = 0;
   for (uint32_t spins = 0;; ++spins) {
     if (Slot* s = ring_reserve(in, pos)) return s;
@@ -384,7 +402,7 @@ Slot* reserve_wait(Inbox* in, uint64_t* pos, uint32_t timeout_ms) {
     }
   }
 }
-bool send_msg(Inbox* in, const MsgHdr& h, const void* payload, uint32_t timeout_ms = 2000) {
+bool send_msg(Ring* in, const MsgHdr& h, const void* payload, uint32_t timeout_ms = 2000) {
   uint64_t pos;
   Slot* s = reserve_wait(in, &pos, timeout_ms);
   if (!s) return false;
@@ -456,9 +474,10 @@ void reply(ShmCtx* c, const MsgHdr& req, uint32_t type, urma_cr_status_t st, uin
   r.operand = operand;
   r.len = len;
   r.frag_off = off;
-  if (c->deferred.empty()) {
+  // answers go to the ring of the send queue that asked: its completions keep their order
+  if (c->deferred_n.load(std::memory_order_acquire) == 0) {
     uint64_t pos;
-    if (Slot* s = ring_reserve(in, &pos)) {
+    if (Slot* s = ring_reserve(ring_of(in, req.src_jetty), &pos)) {
       s->h = r;
       if (len && payload) memcpy(s->payload, payload, len);
       ring_publish(s, pos);
@@ -467,31 +486,35 @@ void reply(ShmCtx* c, const MsgHdr& req, uint32_t type, urma_cr_status_t st, uin
   }
   ShmCtx::Deferred d;
   d.uasid = req.src_uasid;
+  d.queue = req.src_jetty;
   d.h = r;
   if (len && payload) d.payload.assign(static_cast<const uint8_t*>(payload), static_cast<const uint8_t*>(payload) + len);
+  std::lock_guard<SpinLock> l(c->deferred_mu);
   c->deferred.push_back(std::move(d));
+  c->deferred_n.store(static_cast<uint32_t>(c->deferred.size()), std::memory_order_release);
 }
 
 // Retries parked answers in order; stops at the first one that still does not fit.
 void flush_deferred(ShmCtx* c) {
+  std::lock_guard<SpinLock> l(c->deferred_mu);
   while (!c->deferred.empty()) {
     ShmCtx::Deferred& d = c->deferred.front();
     Inbox* in = peer_inbox(c, d.uasid);
-    if (!in) {
-      c->deferred.pop_front();
-      continue;
+    if (in) {
+      uint64_t pos;
+      Slot* s = ring_reserve(ring_of(in, d.queue), &pos);
+      if (!s) break;
+      s->h = d.h;
+      if (!d.payload.empty()) memcpy(s->payload, d.payload.data(), d.payload.size());
+      ring_publish(s, pos);
     }
-    uint64_t pos;
-    Slot* s = ring_reserve(in, &pos);
-    if (!s) return;
-    s->h = d.h;
-    if (!d.payload.empty()) memcpy(s->payload, d.payload.data(), d.payload.size());
-    ring_publish(s, pos);
     c->deferred.pop_front();
   }
+  c->deferred_n.store(static_cast<uint32_t>(c->deferred.size()), std::memory_order_release);
 }
 
-// Completes one receive request with `len` bytes at `data`; `m` carries who sent them (its own data is not used).
+// Completes one receive request with `len` bytes at `data` (null: the bytes are in the buffer already, a message
+// reassembled in place); `m` carries who sent them (its own data is not used).
 void finish_recv(ShmCtx* c, RecvQueue* rq, const RecvWr& wr, const uint8_t* data, uint32_t len, const Unexpected& m) {
   urma_cr_t cr{};
   cr.user_ctx = wr.user_ctx;
@@ -506,7 +529,7 @@ void finish_recv(ShmCtx* c, RecvQueue* rq, const RecvWr& wr, const uint8_t* data
   if (len > wr.sges.bytes()) {
     st = URMA_CR_LOC_LEN_ERR;
   } else {
-    scatter(wr.sges, 0, data, len);
+    if (data) scatter(wr.sges, 0, data, len);
     cr.completion_len = len;
   }
   cr.status = st;
@@ -514,6 +537,7 @@ void finish_recv(ShmCtx* c, RecvQueue* rq, const RecvWr& wr, const uint8_t* data
   if (m.want_ack) {
     MsgHdr req{};
     req.src_uasid = m.src_uasid;
+    req.src_jetty = m.src_jetty;
     req.wr_id = m.wr_id;
     req.opcode = URMA_OPC_SEND;
     reply(c, req, MSG_RESP, st == URMA_CR_SUCCESS ? URMA_CR_SUCCESS : URMA_CR_REM_RESP_LEN_ERR);
@@ -776,11 +800,24 @@ void handle(ShmCtx* c, Slot* s) {
         std::lock_guard<std::mutex> l(c->mu);
         r = &c->reasm[key];
       }
-      if (h.flags & F_FIRST) r->data.resize(h.total_len);
-      if (h.frag_off + h.len <= r->data.size() && h.len) memcpy(r->data.data() + h.frag_off, s->payload, h.len);
+      if (h.flags & F_FIRST) {
+        // a receive request that is already posted takes the fragments as they come (no staging copy); its turn in
+        // the queue is the moment the message begins
+        std::lock_guard<SpinLock> l(rq->mu);
+        if (!rq->posted_empty()) {
+          r->wr = rq->posted_front();
+          rq->posted_pop();
+          r->direct = true;
+        }
+      }
+      if (r->direct) {
+        if (h.len && uint64_t(h.frag_off) + h.len <= r->wr.sges.bytes()) scatter(r->wr.sges, h.frag_off, s->payload, h.len);
+      } else {
+        if (h.flags & F_FIRST) r->data.resize(h.total_len);
+        if (h.frag_off + h.len <= r->data.size() && h.len) memcpy(r->data.data() + h.frag_off, s->payload, h.len);
+      }
       if (h.flags & F_LAST) {
         Unexpected u;
-        u.data = std::move(r->data);
         u.imm = h.operand;
         u.has_imm = (h.flags & F_IMM) != 0;
         u.src_uasid = h.src_uasid;
@@ -788,11 +825,15 @@ void handle(ShmCtx* c, Slot* s) {
         u.wr_id = h.wr_id;
         u.want_ack = true;
         memcpy(u.src_eid.raw, h.src_eid, 16);
+        const bool direct = r->direct;
+        const RecvWr wr = r->wr;
+        if (!direct) u.data = std::move(r->data);
         {
           std::lock_guard<std::mutex> l(c->mu);
           c->reasm.erase(key);
         }
-        deliver(c, rq, std::move(u));
+        if (direct) finish_recv(c, rq, wr, nullptr, h.total_len, u);   // too long for the buffer: nothing was copied
+        else deliver(c, rq, std::move(u));
       }
       break;
     }
@@ -811,26 +852,56 @@ void handle(ShmCtx* c, Slot* s) {
   }
 }
 
-// Executes up to `budget` messages of the context's inbox. The inbox has one consumer at a time: whoever holds
-// `life_mu` (the same lock that keeps queues alive while a message is handled). Threads that cannot have it at once
-// go away empty-handed - somebody else is doing the work.
+// Executes up to `budget` messages of the context's inbox. Each ring has one consumer at a time (a flag taken with
+// a try); different rings are executed by different threads at once, all of them holding the lifetime lock shared -
+// the operations that free a queue take it exclusively and so wait until no message is being handled. A thread that
+// finds a ring taken moves on to the next: somebody else is doing that work.
+inline bool ring_ready(Ring* in) {
+  const uint64_t pos = in->deq.load(std::memory_order_relaxed);
+  return in->slots[pos & (kRingSlots - 1)].seq.load(std::memory_order_acquire) == pos + 1;
+}
 int consume(ShmCtx* c, int budget) {
-  std::unique_lock<std::mutex> life(c->life_mu, std::try_to_lock);
+  // a look without taking anything: most polls find every ring empty
+  uint32_t ready = 0;
+  for (uint32_t r = 0; r < kRings; ++r) ready |= ring_ready(&c->inbox->ring[r]) ? 1u << r : 0;
+  if (!ready && c->deferred_n.load(std::memory_order_acquire) == 0) return 0;
+  if (c->deleters.load(std::memory_order_acquire)) return 0;   // let a waiting delete through
+  std::shared_lock<std::shared_mutex> life(c->life_mu, std::try_to_lock);
   if (!life.owns_lock()) return 0;
-  if (!c->deferred.empty()) flush_deferred(c);
-  Inbox* in = c->inbox;
+  if (c->deferred_n.load(std::memory_order_acquire)) flush_deferred(c);
   int done = 0;
-  while (done < budget) {
-    const uint64_t pos = in->deq.load(std::memory_order_relaxed);
-    Slot* s = &in->slots[pos & (kRingSlots - 1)];
-    if (s->seq.load(std::memory_order_acquire) != pos + 1) break;
-    handle(c, s);
-    in->deq.store(pos + 1, std::memory_order_relaxed);
-    s->seq.store(pos + kRingSlots, std::memory_order_release);
-    ++done;
+  static thread_local uint32_t first = 0;   // successive calls of a thread start at different rings
+  ++first;
+  for (uint32_t k = 0; k < kRings && done < budget; ++k) {
+    const uint32_t ri = (first + k) & (kRings - 1);
+    if (!(ready >> ri & 1)) continue;
+    Ring* in = &c->inbox->ring[ri];
+    if (c->ring_busy[ri].exchange(true, std::memory_order_acquire)) continue;
+    while (done < budget) {
+      const uint64_t pos = in->deq.load(std::memory_order_relaxed);
+      Slot* s = &in->slots[pos & (kRingSlots - 1)];
+      if (s->seq.load(std::memory_order_acquire) != pos + 1) break;
+      handle(c, s);
+      in->deq.store(pos + 1, std::memory_order_relaxed);
+      s->seq.store(pos + kRingSlots, std::memory_order_release);
+      ++done;
+    }
+    c->ring_busy[ri].store(false, std::memory_order_release);
   }
   return done;
 }
+// Taken by the operations that free a queue or a completion queue.
+struct LifeExclusive {
+  ShmCtx* c;
+  explicit LifeExclusive(ShmCtx* c_) : c(c_) {
+    c->deleters.fetch_add(1, std::memory_order_acq_rel);
+    c->life_mu.lock();
+  }
+  ~LifeExclusive() {
+    c->life_mu.unlock();
+    c->deleters.fetch_sub(1, std::memory_order_acq_rel);
+  }
+};
 
 // A cheap clock for "did the application poll just now": the cycle counter.
 inline uint64_t fast_ticks() { return ub::cycles(); }
@@ -900,7 +971,7 @@ urma_jfc_t* op_create_jfc(urma_context_t*, const urma_jfc_cfg_t* cfg) {
 }
 urma_status_t op_modify_jfc(urma_jfc_t*, uint32_t, uint32_t) { return URMA_SUCCESS; }
 urma_status_t op_delete_jfc(urma_jfc_t* jfc) {
-  std::lock_guard<std::mutex> life(C(jfc->ctx)->life_mu);
+  LifeExclusive life(C(jfc->ctx));
   delete reinterpret_cast<ShmJfc*>(jfc->priv);
   return URMA_SUCCESS;
 }
@@ -971,7 +1042,7 @@ urma_status_t op_delete_jfs(urma_jfs_t* jfs) {
   urma_cr_t tmp[16];
   while (flush_sq(C(jfs->ctx), &j->sq, 16, tmp) == 16) {
   }
-  std::lock_guard<std::mutex> life(C(jfs->ctx)->life_mu);
+  LifeExclusive life(C(jfs->ctx));
   delete j;
   return URMA_SUCCESS;
 }
@@ -1009,7 +1080,7 @@ urma_status_t op_query_jfr(urma_jfr_t* jfr, urma_jfr_cfg_t* cfg, urma_jetty_stat
 urma_status_t op_delete_jfr(urma_jfr_t* jfr) {
   ShmJfr* j = reinterpret_cast<ShmJfr*>(jfr->priv);
   rq_fini(C(jfr->ctx), &j->rq);
-  std::lock_guard<std::mutex> life(C(jfr->ctx)->life_mu);
+  LifeExclusive life(C(jfr->ctx));
   delete j;
   return URMA_SUCCESS;
 }
@@ -1082,7 +1153,7 @@ urma_status_t op_delete_jetty(urma_jetty_t* jt) {
   while (flush_sq(C(jt->ctx), &j->sq, 16, tmp) == 16) {
   }
   if (j->rq == &j->own_rq) rq_fini(C(jt->ctx), &j->own_rq);
-  std::lock_guard<std::mutex> life(C(jt->ctx)->life_mu);
+  LifeExclusive life(C(jt->ctx));
   delete j;
   return URMA_SUCCESS;
 }
@@ -1165,8 +1236,9 @@ urma_status_t post_one(ShmCtx* c, SendQueue* sq, urma_target_jetty_t* bound, urm
   urma_target_jetty_t* tj = wr->tjetty ? wr->tjetty : bound;
   if (!tj) return URMA_EINVAL;
   if (sq->inflight.load() >= sq->depth) return URMA_EAGAIN;
-  Inbox* in = peer_inbox(c, tj->id.uasid);
-  if (!in) return URMA_FAIL;
+  Inbox* box = peer_inbox(c, tj->id.uasid);
+  if (!box) return URMA_FAIL;
+  Ring* in = ring_of(box, tj->id.id);   // everything for one target jetty travels through one ring, in order
   const uint64_t id = c->next_wr.fetch_add(1);
   Pending p;
   p.sq = sq;
@@ -1356,10 +1428,7 @@ urma_status_t post_recv_list(ShmCtx* c, RecvQueue* rq, urma_jfr_wr_t* wr, urma_j
         have = true;
       }
     }
-    if (have) {   // answering the sender touches what the inbox's consumer owns (the list of parked answers)
-      std::lock_guard<std::mutex> life(c->life_mu);
-      deliver(c, rq, std::move(u));
-    }
+    if (have) deliver(c, rq, std::move(u));
   }
   *bad = nullptr;
   return URMA_SUCCESS;
@@ -1588,9 +1657,11 @@ urma_context_t* prov_create_context(urma_device_t* dev, uint32_t eid_index) {
     delete c;
     return nullptr;
   }
-  for (uint32_t i = 0; i < kRingSlots; ++i) c->inbox->slots[i].seq.store(i);
-  c->inbox->enq = 0;
-  c->inbox->deq = 0;
+  for (uint32_t r = 0; r < kRings; ++r) {
+    for (uint32_t i = 0; i < kRingSlots; ++i) c->inbox->ring[r].slots[i].seq.store(i);
+    c->inbox->ring[r].enq = 0;
+    c->inbox->ring[r].deq = 0;
+  }
   c->inbox->owner_pid = getpid();
   c->inbox->magic.store(kRegMagic, std::memory_order_release);
   c->event_fd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC | EFD_SEMAPHORE);

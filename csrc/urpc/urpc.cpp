@@ -1228,11 +1228,15 @@ int urpc_ctl_stats_get(urpc_ctl_stats_t* out) {
   return URPC_SUCCESS;
 }
 
-int urpc_server_poll(urpc_poll_msg_t* msgs, int max) {
-  std::vector<Session*> ss;
+int urpc_server_poll(urpc_poll_msg_t* msgs, int max) { return urpc_server_poll_shard(0, 1, msgs, max); }
+int urpc_server_poll_shard(uint32_t shard, uint32_t nshards, urpc_poll_msg_t* msgs, int max) {
+  if (nshards == 0 || shard >= nshards) return URPC_ERR_EINVAL;
+  static thread_local std::vector<Session*> ss;
+  ss.clear();
   {
     std::lock_guard<std::mutex> l(g.mu);
-    ss = g.sessions;
+    for (Session* s : g.sessions)
+      if (s->id % nshards == shard) ss.push_back(s);
   }
   int n = 0;
   static thread_local std::vector<uint8_t> rsp(64 * 1024);

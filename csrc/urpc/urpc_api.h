@@ -100,6 +100,9 @@ URPC_EXPORT int urpc_func_unregister(uint64_t func_id);
 /* Polls every attached client: executes registered functions and returns their results (auto mode), or hands the
  * request to the caller when no function is registered. Returns the number of messages written to msgs. */
 URPC_EXPORT int urpc_server_poll(urpc_poll_msg_t* msgs, int max);
+/* The same for one share of the clients: thread k of n server threads calls it with (k, n) and serves the sessions
+ * whose number is k modulo n, so the threads never meet on a queue. */
+URPC_EXPORT int urpc_server_poll_shard(uint32_t shard, uint32_t nshards, urpc_poll_msg_t* msgs, int max);
 URPC_EXPORT int urpc_func_return(const urpc_poll_msg_t* req, const void* rsp, uint32_t len, int status);
 /* client */
 URPC_EXPORT int urpc_channel_create(void); /* returns channel id >= 0 */
