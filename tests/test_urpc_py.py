@@ -590,3 +590,28 @@ def test_version_negotiation_between_old_and_new_builds(tmp_path, server_max, cl
         peer.stdin.write("\n")
         peer.stdin.flush()
         peer.wait(timeout=20)
+
+
+def test_server_threads_serve_their_own_share_of_the_clients(tmp_path):
+    """Two polling threads on the server: each serves the sessions whose number is its own modulo two, so with four
+    attached channels both threads get requests and every call is answered exactly once."""
+    os.environ["URMA_SHM_DIR"] = str(tmp_path / "urma")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    from umdk_b200 import urpc
+    urpc.init(default_timeout_ms=3000)
+    srv = urpc.Server(threads=2)
+    srv.register(1, lambda b: b[::-1])                       # runs inside the library on whichever thread polls
+    srv.deferred = lambda fid, args: b"d:" + args            # function 5 has no handler: handed to the thread
+    chans = [urpc.Channel(srv.ip, srv.port) for _ in range(4)]
+    try:
+        for rnd in range(20):
+            for i, ch in enumerate(chans):
+                assert ch.call(1, b"abc%d" % i) == (b"abc%d" % i)[::-1]
+                assert ch.call(5, b"x%d.%d" % (i, rnd)) == b"d:x%d.%d" % (i, rnd)
+        assert sum(srv.served_by) == 80 and min(srv.served_by) > 0, srv.served_by
+        assert urpc._lib().urpc_server_poll_shard(2, 2, None, 0) < 0     # shard out of range
+    finally:
+        for ch in chans:
+            ch.close()
+        srv.stop()
+        urpc.uninit()

@@ -225,9 +225,10 @@ def on_keepalive(cb: Callable[[int, bool], None]) -> None:
 
 
 class Server:
-    """Serves registered functions from a background polling thread."""
+    """Serves registered functions from background polling threads. With ``threads`` > 1 each thread serves its share
+    of the attached clients (``urpc_server_poll_shard``: session number modulo the thread count)."""
 
-    def __init__(self, ip: str = "127.0.0.1", port: int = 0):
+    def __init__(self, ip: str = "127.0.0.1", port: int = 0, threads: int = 1):
         p = _lib().urpc_server_start(ip.encode(), port)
         if p <= 0:
             raise UrpcError("urpc_server_start", p)
@@ -239,8 +240,11 @@ class Server:
         self.deferred: Optional[Callable[[int, bytes], object]] = None
         self.defer_s = 0.0
         self.return_codes: List[int] = []   # urpc_func_return results of deferred answers
-        self._thr = threading.Thread(target=self._loop, daemon=True)
-        self._thr.start()
+        self.threads = max(1, int(threads))
+        self.served_by: List[int] = [0] * self.threads   # requests handed to `deferred`, per polling thread
+        self._thrs = [threading.Thread(target=self._loop, args=(k,), daemon=True) for k in range(self.threads)]
+        for t in self._thrs:
+            t.start()
 
     def register(self, func_id: int, fn: Callable[[bytes], bytes]) -> None:
         def handler(args, n, rsp, rsp_len, _ctx):
@@ -259,17 +263,18 @@ class Server:
         if rc != 0:
             raise UrpcError("urpc_func_register", rc)
 
-    def _loop(self):
+    def _loop(self, shard: int = 0):
         msgs = (_PollMsg * 16)()
         lib = _lib()
         while not self._stop.is_set():
             if self.paused:
                 time.sleep(0.005)
                 continue
-            n = lib.urpc_server_poll(msgs, 16)
+            n = lib.urpc_server_poll_shard(shard, self.threads, msgs, 16)
             for i in range(max(n, 0)):
                 m = msgs[i]
                 if self.deferred is not None and m.event == POLL_REQ:   # registered functions ran inside the library
+                    self.served_by[shard] += 1
                     args = ctypes.string_at(m.data, m.len) if m.data and m.len else b""
                     if self.defer_s:
                         time.sleep(self.defer_s)
@@ -283,7 +288,8 @@ class Server:
 
     def stop(self):
         self._stop.set()
-        self._thr.join(timeout=2)
+        for t in self._thrs:
+            t.join(timeout=2)
 
 
 class Channel:
