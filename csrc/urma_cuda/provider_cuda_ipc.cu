@@ -218,7 +218,34 @@ struct CCtx {
   std::mutex mu;
   unsigned long long* pinned = nullptr;  // ring of result slots
   uint32_t pinned_next = 0;
+  // Completion events are recycled: creating and destroying one per request costs more than a small copy itself.
+  std::mutex ev_mu;
+  std::vector<cudaEvent_t> ev_free;
 };
+cudaEvent_t event_get(CCtx* c) {
+  {
+    std::lock_guard<std::mutex> l(c->ev_mu);
+    if (!c->ev_free.empty()) {
+      cudaEvent_t e = c->ev_free.back();
+      c->ev_free.pop_back();
+      return e;
+    }
+  }
+  cudaEvent_t e = nullptr;
+  cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+  return e;
+}
+void event_put(CCtx* c, cudaEvent_t e) {
+  if (!e) return;
+  {
+    std::lock_guard<std::mutex> l(c->ev_mu);
+    if (c->ev_free.size() < 4096) {
+      c->ev_free.push_back(e);
+      return;
+    }
+  }
+  cudaEventDestroy(e);
+}
 struct CJetty {
   urma_jetty_t pub;
   std::mutex mu;
@@ -299,7 +326,7 @@ urma_status_t op_delete_jetty(urma_jetty_t* jt) {
     unlink(jetty_path(jt->jetty_id.uasid, j->id).c_str());
   }
   for (auto& r : j->inflight)
-    if (r.early == URMA_CR_SUCCESS) cudaEventDestroy(r.ev);
+    if (r.early == URMA_CR_SUCCESS) event_put(reinterpret_cast<CCtx*>(jt->ctx->priv), r.ev);
   delete j;
   return URMA_SUCCESS;
 }
@@ -586,7 +613,7 @@ urma_status_t op_post_send(urma_jetty_t* jt, urma_jfs_wr_t* wr, urma_jfs_wr_t** 
       return URMA_FAIL;
     }
     if (r.early == URMA_CR_SUCCESS) {
-      cudaEventCreateWithFlags(&r.ev, cudaEventDisableTiming);
+      r.ev = event_get(c);
       cudaEventRecord(r.ev, c->stream);
     }
     std::lock_guard<std::mutex> l(j->mu);
@@ -649,7 +676,7 @@ urma_status_t op_post_recv(urma_jetty_t* jt, urma_jfr_wr_t* wr, urma_jfr_wr_t** 
 }
 
 int op_poll_jfc(urma_jfc_t* jfc, int n, urma_cr_t* cr) {
-  std::vector<CJetty*> js;
+  static thread_local std::vector<CJetty*> js;   // reused: a poll must not allocate
   {
     std::lock_guard<std::mutex> l(g_jmu);
     js = g_jfc_jetties[jfc];
@@ -663,7 +690,7 @@ int op_poll_jfc(urma_jfc_t* jfc, int n, urma_cr_t* cr) {
       if (st == URMA_CR_SUCCESS) {
         const cudaError_t q = cudaEventQuery(r.ev);
         if (q == cudaErrorNotReady) break;  // completions are delivered in order per jetty
-        cudaEventDestroy(r.ev);
+        event_put(C(jfc->ctx), r.ev);
         if (q != cudaSuccess) st = URMA_CR_LOC_OPERATION_ERR;
         if (r.rx) {   // the payload has landed: hand the receiver its completion
           const uint64_t t = r.rx->cq_tail.fetch_add(1);
@@ -795,6 +822,7 @@ urma_status_t prov_delete_context(urma_context_t* ctx) {
   cudaStreamSynchronize(c->stream);
   cudaStreamDestroy(c->stream);
   cudaFreeHost(c->pinned);
+  for (cudaEvent_t e : c->ev_free) cudaEventDestroy(e);
   delete c;
   return URMA_SUCCESS;
 }
