@@ -256,9 +256,36 @@ struct CJetty {
   JettyShm* shm = nullptr;   // this jetty's receive queue and receive-completion ring
   urma_jfc_t* rx_jfc = nullptr;
 };
+// Direct access from device `from` to memory of device `to` inside this process. Without it a copy between the two
+// is staged through host memory by the runtime (tens of GB/s instead of NVLink's hundreds) and a kernel on `from`
+// must not touch `to`'s memory at all. Enabled once per pair, the first time a context on `from` is made or a
+// segment of `to` is imported; the answer is remembered.
+constexpr int kMaxDev = 64;
+std::mutex g_peer_mu;
+int8_t g_peer[kMaxDev][kMaxDev];   // 0 unknown, 1 direct access works, -1 it does not
+bool peer_direct(int from, int to) {
+  if (from == to) return true;
+  if (from < 0 || to < 0 || from >= kMaxDev || to >= kMaxDev) return false;
+  std::lock_guard<std::mutex> l(g_peer_mu);
+  if (g_peer[from][to] == 0) {
+    int can = 0, cur = -1;
+    cudaGetDevice(&cur);
+    bool ok = cudaDeviceCanAccessPeer(&can, from, to) == cudaSuccess && can;
+    if (ok && cudaSetDevice(from) == cudaSuccess) {
+      const cudaError_t e = cudaDeviceEnablePeerAccess(to, 0);
+      ok = e == cudaSuccess || e == cudaErrorPeerAccessAlreadyEnabled;
+    }
+    cudaGetLastError();   // "already enabled" is not an error to carry around
+    if (cur >= 0) cudaSetDevice(cur);
+    g_peer[from][to] = ok ? 1 : -1;
+  }
+  return g_peer[from][to] == 1;
+}
+
 struct CSeg {
   urma_target_seg_t pub;
   uint32_t token_val;
+  bool direct = true;   // kernels of this context's device may touch the segment (false: copies only, staged)
   void* mapped_base = nullptr;  // base returned by cudaIpcOpenMemHandle (imports from another process)
   DirEntry* entry = nullptr;
 };
@@ -433,7 +460,9 @@ urma_target_seg_t* op_import_seg(urma_context_t* ctx, const urma_seg_t* seg, con
   s->entry = e;
   cudaSetDevice(c->dev);
   if (e->pid == (uint32_t)getpid()) {
-    s->pub.mva = e->va;  // same process: the pointer is directly usable (peer access is enabled lazily by memcpy)
+    s->pub.mva = e->va;  // same process: the pointer itself, once this device may reach the owner's memory
+    s->direct = peer_direct(c->dev, static_cast<int>(e->dev));
+    peer_direct(static_cast<int>(e->dev), c->dev);   // reads come back the other way
   } else {
     void* p = nullptr;
     if (cudaIpcOpenMemHandle(&p, e->handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
@@ -520,7 +549,11 @@ urma_status_t op_post_send(urma_jetty_t* jt, urma_jfs_wr_t* wr, urma_jfs_wr_t** 
           return URMA_EINVAL;
         }
         r.len = 8;
-        const uint64_t ra = remote_addr(reinterpret_cast<CSeg*>(d->tseg->priv), d->addr, 8, URMA_ACCESS_ATOMIC, &r.early);
+        uint64_t ra = remote_addr(reinterpret_cast<CSeg*>(d->tseg->priv), d->addr, 8, URMA_ACCESS_ATOMIC, &r.early);
+        if (r.early == URMA_CR_SUCCESS && !reinterpret_cast<CSeg*>(d->tseg->priv)->direct) {
+          r.early = URMA_CR_REM_UNSUPPORTED_REQ_ERR;   // no direct path between the two GPUs: no kernel may go there
+          ra = 0;
+        }
         if (r.early == URMA_CR_SUCCESS) {
           {
             std::lock_guard<std::mutex> l(c->mu);
@@ -577,6 +610,7 @@ urma_status_t op_post_send(urma_jetty_t* jt, urma_jfs_wr_t* wr, urma_jfs_wr_t** 
           void* dst = nullptr;
           if (taken.pid == (uint32_t)getpid()) {
             dst = reinterpret_cast<void*>(taken.va);
+            peer_direct(c->dev, static_cast<int>(taken.dev));   // a copy to another GPU should not go through the host
           } else {
             void* base = open_remote_alloc(taken.handle);
             if (base) dst = static_cast<char*>(base) + (taken.va - taken.alloc_base);

@@ -95,3 +95,25 @@ def test_urma_perftest_on_gpu_memory(tmp_path, op):
     p = subprocess.run(args, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=180)
     assert p.returncode == 0 and "urma_perftest: OK" in p.stdout and "errors 0" in p.stdout, p.stdout[-2000:]
     assert f"{op} dev=cuda0 size=65536" in p.stdout
+
+
+def test_urma_perftest_between_two_gpus_uses_the_direct_path(tmp_path):
+    """Two endpoints of one process on two GPUs: the copy must go over NVLink (the devices are given access to each
+    other when a segment or a receive buffer of the other GPU is first used; staged through host memory the same copy
+    reaches a few tens of GB/s), and an atomic on the other GPU's memory must work."""
+    import os
+    import re
+    import subprocess
+    from umdk_b200 import _native
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    tool = _native.lib_dir() / "bin" / "urma_perftest"
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"))
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    for op, size in (("write", 67108864), ("send", 67108864), ("faa", 8)):
+        args = [str(tool), "--dev", "cuda0", "--peer-dev", "cuda1", "--op", op, "--size", str(size), "--iters", "100"]
+        p = subprocess.run(args, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=180)
+        assert p.returncode == 0 and "urma_perftest: OK" in p.stdout and "errors 0" in p.stdout, p.stdout[-2000:]
+        if op != "faa":
+            mbs = float(re.search(r"ops/s, ([0-9.]+) MB/s", p.stdout).group(1))
+            assert mbs > 200e3, p.stdout   # 64 MiB copies: NVLink gives about 700 GB/s, the host path about 36 GB/s
