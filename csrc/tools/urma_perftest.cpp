@@ -1,5 +1,5 @@
 // urma_perftest: latency and bandwidth of URMA verbs (write / read / send / atomic) between two endpoints.
-//   urma_perftest [--dev shm0|bond0|cudaN] [--peer-dev cudaM] [--op write|read|send|faa|cas] [--size N] [--iters N]
+//   urma_perftest [--stress THREADS] [--dev shm0|bond0|cudaN] [--peer-dev cudaM] [--op write|read|send|faa|cas] [--size N] [--iters N]
 //                 [--depth N] [--duration SEC] [--jettys N] [--cq-mod N] [--rate-limit MB/s]
 //     --dev cudaN  the buffers live in the memory of GPU N (allocated through the CUDA runtime, loaded at run time);
 //                  --peer-dev cudaM puts the second endpoint of the in-process mode on GPU M (default: the same GPU)
@@ -22,7 +22,9 @@
 #include <string.h>
 #include <unistd.h>
 
+#include <atomic>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "ub_util.h"
@@ -123,13 +125,124 @@ static int wait_n(urma_simple_ep_t* ep, int want, int* bad) {
   return got;
 }
 
+// --stress N: N threads at once between two contexts of this process, each with an endpoint pair of its own. Every
+// round a thread sends a message of its own length and pattern (one slot up to several fragments) and receives it on
+// the other side, writes a slice of the shared segment and reads it back, and adds to one shared counter. All data is
+// checked; the counter must end at threads x rounds. What runs concurrently underneath: the posting threads, the two
+// contexts' own threads, and the same application threads executing the inboxes from inside their polls.
+static int stress(const std::string& dev, uint32_t threads, uint32_t rounds, uint32_t size) {
+  urma_context_t* ca = urma_simple_open(dev.c_str());
+  urma_context_t* cb = urma_simple_open(dev.c_str());
+  if (!ca || !cb) return fail("open device (stress)");
+  const uint32_t max_msg = size * 3 + 17;
+  const uint32_t slice = max_msg;
+  const uint64_t seg_bytes = uint64_t(slice) * threads + 64;
+  std::vector<uint8_t> seg_mem(seg_bytes, 0);
+  uint8_t seg_blob[URMA_SIMPLE_SEG_BLOB];
+  urma_target_seg_t* seg = urma_simple_seg_register(cb, seg_mem.data(), seg_bytes, 14, 7, seg_blob);
+  urma_target_seg_t* rseg = seg ? urma_simple_seg_import(ca, seg_blob, 7) : nullptr;
+  if (!seg || !rseg) return fail("segment (stress)");
+  const uint64_t counter_off = uint64_t(slice) * threads;   // 8-byte aligned below
+  const uint64_t counter_va = (rseg->seg.ubva.va + counter_off + 7) & ~7ull;
+  std::atomic<int> failed{0};
+  std::atomic<uint32_t> ready{0};
+  auto worker = [&](uint32_t t) {
+    auto bail = [&](const char* what) {
+      fprintf(stderr, "urma_perftest: stress thread %u: %s\n", t, what);
+      ++failed;
+    };
+    urma_simple_ep_t* a = urma_simple_ep_create(ca, 32, 1, 0);
+    urma_simple_ep_t* b = urma_simple_ep_create(cb, 32, 1, 0);
+    if (!a || !b) return bail("endpoints");
+    uint8_t blob[URMA_SIMPLE_JETTY_BLOB];
+    urma_simple_ep_blob(b, blob);
+    urma_target_jetty_t* tb = urma_simple_ep_import(ca, blob, 1);
+    if (!tb) return bail("import");
+    constexpr uint32_t kRecv = 4;
+    std::vector<std::vector<uint8_t>> rbuf(kRecv, std::vector<uint8_t>(max_msg));
+    for (uint32_t i = 0; i < kRecv; ++i)
+      if (urma_simple_post_recv(b, rbuf[i].data(), max_msg, i) != 0) return bail("post_recv");
+    std::vector<uint8_t> out(max_msg), back(max_msg);
+    ++ready;
+    while (ready.load() < threads && !failed.load()) sched_yield();   // everybody starts together
+    auto wait_one = [&](urma_simple_ep_t* ep, bool want_recv, uint64_t* uc, uint32_t* len, uint64_t* imm) {
+      const uint64_t deadline = ub::now_ns() + 20000000000ull;
+      while (ub::now_ns() < deadline && !failed.load()) {
+        int st;
+        uint32_t fl;
+        const int n = urma_simple_poll(ep, 1, &st, uc, len, imm, &fl);
+        if (n == 1) {
+          if (st != 0) return false;
+          if (((fl & URMA_CR_FLAG_RECV) != 0) == want_recv) return true;
+        }
+      }
+      return false;
+    };
+    for (uint32_t i = 0; i < rounds && !failed.load(); ++i) {
+      // lengths walk through: tiny, one slot, just over a slot, several fragments
+      const uint32_t lens[4] = {1 + (i + t) % 97, size, size + 1 + (i % 7), max_msg - (i % 13)};
+      const uint32_t len = lens[(i + t) & 3];
+      for (uint32_t k = 0; k < len; ++k) out[k] = (uint8_t)(k * 31 + i * 7 + t * 13 + 1);
+      uint64_t uc = 0, imm = 0;
+      uint32_t got = 0;
+      if (urma_simple_post(a, tb, URMA_OPC_SEND_IMM, nullptr, 0, nullptr, (uint64_t)out.data(), len, (uint64_t(t) << 32) | i, i, 1) != 0)
+        return bail("post send");
+      if (!wait_one(b, true, &uc, &got, &imm)) return bail("receive completion");
+      if (got != len || imm != ((uint64_t(t) << 32) | i) || uc >= kRecv || memcmp(rbuf[uc].data(), out.data(), len))
+        return bail("received data differs");
+      if (urma_simple_post_recv(b, rbuf[uc].data(), max_msg, uc) != 0) return bail("re-post receive");
+      if (!wait_one(a, false, &uc, &got, &imm)) return bail("send completion");
+      // one-sided: write this thread's slice, read it back
+      const uint64_t va = rseg->seg.ubva.va + uint64_t(slice) * t;
+      if (urma_simple_post(a, tb, URMA_OPC_WRITE, rseg, va, nullptr, (uint64_t)out.data(), len, 0, i, 1) != 0 ||
+          !wait_one(a, false, &uc, &got, &imm))
+        return bail("write");
+      memset(back.data(), 0, len);
+      if (urma_simple_post(a, tb, URMA_OPC_READ, rseg, va, nullptr, (uint64_t)back.data(), len, 0, i, 1) != 0 ||
+          !wait_one(a, false, &uc, &got, &imm))
+        return bail("read");
+      if (memcmp(back.data(), out.data(), len)) return bail("read back differs from what was written");
+      uint64_t old = 0;
+      if (urma_simple_atomic(a, tb, URMA_OPC_FADD, rseg, counter_va, 1, 0, &old, i) != 0 ||
+          !wait_one(a, false, &uc, &got, &imm))
+        return bail("fetch-add");
+    }
+    urma_unimport_jetty(tb);
+    urma_simple_ep_destroy(a);
+    urma_simple_ep_destroy(b);
+  };
+  const uint64_t t0 = ub::now_ns();
+  std::vector<std::thread> th;
+  for (uint32_t t = 0; t < threads; ++t) th.emplace_back(worker, t);
+  for (auto& x : th) x.join();
+  const double sec = (ub::now_ns() - t0) * 1e-9;
+  uint64_t total = 0;
+  memcpy(&total, seg_mem.data() + (counter_va - rseg->seg.ubva.va), 8);
+  if (failed.load() == 0 && total != uint64_t(threads) * rounds) {
+    fprintf(stderr, "urma_perftest: shared counter is %llu, expected %llu\n", (unsigned long long)total,
+            (unsigned long long)threads * rounds);
+    ++failed;
+  }
+  printf("stress dev=%s threads=%u rounds=%u size=%u: %.0f operations/s in total, %s\n", dev.c_str(), threads, rounds,
+         size, 4.0 * threads * rounds / sec, failed.load() ? "FAILED" : "all data verified");
+  urma_unimport_seg(rseg);
+  urma_unregister_seg(seg);
+  if (urma_simple_close(ca) != 0 || urma_simple_close(cb) != 0) return fail("contexts still had objects at the end");
+  if (failed.load()) return fail("stress");
+  printf("urma_perftest: OK\n");
+  return 0;
+}
+
 int main(int argc, char** argv) {
   std::string dev = "shm0", peer_dev, op = "write", host = "127.0.0.1";
   uint32_t size = 4096, iters = 20000, depth = 64;
   int server = -1, client = -1;
   uint32_t jettys = 1, cq_mod = 1;
   double duration = 0, rate_mbs = 0;
+  uint32_t stress_threads = 0;
   for (int i = 1; i < argc; ++i) {
+    if (!strcmp(argv[i], "--stress") && i + 1 < argc) stress_threads = std::max(1, atoi(argv[++i]));
+    else
     if (!strcmp(argv[i], "--duration") && i + 1 < argc) duration = atof(argv[++i]);
     else if (!strcmp(argv[i], "--jettys") && i + 1 < argc) jettys = std::max(1, atoi(argv[++i]));
     else if (!strcmp(argv[i], "--cq-mod") && i + 1 < argc) cq_mod = std::max(1, atoi(argv[++i]));
@@ -145,6 +258,10 @@ int main(int argc, char** argv) {
       host = argv[++i];
       client = atoi(argv[++i]);
     }
+  }
+  if (stress_threads) {
+    if (gpu_index(dev) >= 0) return fail("--stress runs on host devices");
+    return stress(dev, stress_threads, iters, size);
   }
   urma_context_t* ctx = urma_simple_open(dev.c_str());
   if (!ctx) return fail("open device");

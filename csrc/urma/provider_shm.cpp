@@ -141,7 +141,8 @@ struct Device {
   urma_eid_t eid;
   DevReg* reg = nullptr;
 };
-std::vector<Device> g_devs;
+// (never destroyed: a context that the application left open still has its thread running while the process exits)
+std::vector<Device>& g_devs = *new std::vector<Device>();
 std::mutex g_mu;
 
 using ub::cpu_relax;

@@ -126,6 +126,13 @@ def test_urma_perftest_with_the_context_thread_doing_all_the_work(tmp_path, op):
     assert rc == 0 and "urma_perftest: OK" in out and "errors 0" in out, out
 
 
+@pytest.mark.parametrize("dev,threads", [("shm0", 6), ("bond0", 3)])
+def test_urma_stress_many_threads_all_data_verified(tmp_path, dev, threads):
+    rc, out = _run([BIN / "urma_perftest", "--stress", threads, "--iters", "3000", "--size", "4096", "--dev", dev],
+                   tmp_path)
+    assert rc == 0 and "all data verified" in out and "urma_perftest: OK" in out, out
+
+
 def test_urma_perftest_over_bond_device(tmp_path):
     rc, out = _run([BIN / "urma_perftest", "--dev", "bond0", "--op", "write", "--iters", "1000"], tmp_path)
     assert rc == 0 and "urma_perftest: OK" in out, out

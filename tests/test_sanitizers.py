@@ -42,7 +42,15 @@ def test_address_and_leak_sanitizer_clean(tmp_path):
 @needs_gxx
 def test_thread_sanitizer_clean(tmp_path):
     outs = _build.build_sanitized("thread", only=_build.HOST_LIBS + ("tool_umq_perftest", "tool_urpc_perftest",
-                                                                      "tool_ums_perftest"))
+                                                                      "tool_ums_perftest", "tool_urma_perftest"))
+    # the shared-memory device with four threads at once: sends of one slot and of several fragments, writes, reads
+    # and atomics, executed by the contexts' own threads and by the polling threads themselves (and by the contexts'
+    # threads alone)
+    rc, out = _run(outs["tool_urma_perftest"], ["--stress", "4", "--iters", "400", "--size", "4096"], tmp_path)
+    assert rc == 0 and "all data verified" in out and "ThreadSanitizer" not in out, out[-3000:]
+    rc, out = _run(outs["tool_urma_perftest"], ["--stress", "3", "--iters", "300", "--size", "1000"], tmp_path,
+                   {"URMA_SHM_INLINE_POLL": "0"})
+    assert rc == 0 and "all data verified" in out and "ThreadSanitizer" not in out, out[-3000:]
     for _ in range(2):   # the teardown race this guards against showed up in about one run out of three
         rc, out = _run(outs["tool_umq_perftest"], ["--iters", "300", "--flow-control"], tmp_path)
         assert rc == 0 and "umq_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
