@@ -527,8 +527,10 @@ void srv_cmd_loop(Server* s) {
   while (!s->stop.load()) {
     const int n = urma_simple_poll(s->ep, 32, st, uc, len, imm, flag);
     if (n <= 0) {
-      if (++idle > 2000) usleep(50);
-      else sched_yield();
+      // the next command usually follows within microseconds: poll tightly first, then offer the core, then sleep
+      if (++idle > 4000) usleep(50);
+      else if (idle > 200) sched_yield();
+      else ub::cpu_relax();
       continue;
     }
     idle = 0;
@@ -711,6 +713,7 @@ int data_poll(Client* c, uint64_t deadline_ns) {
   int st[4];
   uint64_t uc[4], imm[4];
   uint32_t len[4], flag[4];
+  uint32_t spins = 0;
   do {
     const int n = urma_simple_poll(c->ep, 4, st, uc, len, imm, flag);
     for (int i = 0; i < n; ++i) {
@@ -727,7 +730,10 @@ int data_poll(Client* c, uint64_t deadline_ns) {
         return got.status;
       }
     }
-    if (n <= 0) sched_yield();
+    if (n <= 0) {   // an answer takes a microsecond or two: a system call between polls would double that
+      if (++spins < 400) ub::cpu_relax();
+      else sched_yield();
+    }
   } while (ub::now_ns() < deadline_ns);
   return DLOCK_ASYNC_AGAIN;
 }
