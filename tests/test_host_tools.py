@@ -133,6 +133,13 @@ def test_urma_stress_many_threads_all_data_verified(tmp_path, dev, threads):
     assert rc == 0 and "all data verified" in out and "urma_perftest: OK" in out, out
 
 
+@pytest.mark.parametrize("dev", ["shm0", "bond0"])
+def test_urma_raw_api_sample(tmp_path, dev):
+    """The bring-up sequence without the convenience wrapper (the program the verbs migration guide walks through)."""
+    rc, out = _run([BIN / "urma_raw_sample", "--dev", dev], tmp_path)
+    assert rc == 0 and "urma_raw_sample: OK" in out, out
+
+
 def test_urma_perftest_over_bond_device(tmp_path):
     rc, out = _run([BIN / "urma_perftest", "--dev", "bond0", "--op", "write", "--iters", "1000"], tmp_path)
     assert rc == 0 and "urma_perftest: OK" in out, out
