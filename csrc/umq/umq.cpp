@@ -260,6 +260,73 @@ void trace_flush_loop() {
   }
 }
 
+// Call-latency histograms are kept per thread (as the reference keeps its cycle histograms per thread,
+// src/urpc/umq/dfx/perf.c): recording takes only the recording thread's own lock, which nobody else holds except a
+// reader for the moment of its merge. A restart (umq_stats_perf_start / reset) moves an epoch; a thread clears its
+// tables when it next records, and a reader skips tables of an older epoch. A thread that ends leaves its counts in
+// the process-wide table.
+struct ThreadPerf {
+  std::mutex mu;
+  uint64_t epoch = 0;
+  ub::PerfHist h[UMQ_PERF_RECORD_MAX];
+};
+std::atomic<uint64_t> g_perf_epoch{1};
+std::vector<ThreadPerf*>& perf_threads() {   // under g.perf_mu
+  static std::vector<ThreadPerf*>* v = new std::vector<ThreadPerf*>();
+  return *v;
+}
+struct ThreadPerfHolder {
+  ThreadPerf* tp = nullptr;
+  ThreadPerf* get() {
+    if (!tp) {
+      tp = new ThreadPerf();
+      std::lock_guard<std::mutex> l(g.perf_mu);
+      perf_threads().push_back(tp);
+    }
+    return tp;
+  }
+  ~ThreadPerfHolder() {
+    if (!tp) return;
+    std::lock_guard<std::mutex> l(g.perf_mu);
+    if (tp->epoch == g_perf_epoch.load())
+      for (int i = 0; i < UMQ_PERF_RECORD_MAX; ++i) g.perf[i].merge(tp->h[i]);
+    auto& v = perf_threads();
+    for (size_t i = 0; i < v.size(); ++i)
+      if (v[i] == tp) {
+        v[i] = v.back();
+        v.pop_back();
+        break;
+      }
+    delete tp;
+  }
+};
+thread_local ThreadPerfHolder t_perf;
+inline void perf_record(int rec, uint64_t dt) {
+  ThreadPerf* tp = t_perf.get();
+  std::lock_guard<std::mutex> l(tp->mu);
+  const uint64_t ep = g_perf_epoch.load(std::memory_order_acquire);
+  if (tp->epoch != ep) {
+    for (auto& h : tp->h) h.reset();
+    tp->epoch = ep;
+  }
+  tp->h[rec].add(dt);
+}
+// Everything recorded since the last restart, merged into `out[UMQ_PERF_RECORD_MAX]`. Caller holds g.perf_mu.
+void perf_collect(ub::PerfHist* out) {
+  const uint64_t ep = g_perf_epoch.load(std::memory_order_acquire);
+  for (int i = 0; i < UMQ_PERF_RECORD_MAX; ++i) out[i] = g.perf[i];
+  for (ThreadPerf* tp : perf_threads()) {
+    std::lock_guard<std::mutex> l(tp->mu);
+    if (tp->epoch != ep) continue;
+    for (int i = 0; i < UMQ_PERF_RECORD_MAX; ++i) out[i].merge(tp->h[i]);
+  }
+}
+// Forgets everything recorded so far. Caller holds g.perf_mu.
+void perf_restart() {
+  for (auto& h : g.perf) h.reset();
+  g_perf_epoch.fetch_add(1, std::memory_order_acq_rel);
+}
+
 struct PerfScope {
   int rec;
   uint64_t t0;
@@ -272,10 +339,7 @@ struct PerfScope {
       const uint64_t dt = ub::now_ns() - t0;
       if (g_trace.on.load(std::memory_order_relaxed)) trace_add(rec, t0, dt);
       if (umq_io_perf_cb_t cb = g_perf_cb.load(std::memory_order_relaxed)) cb(rec, dt, g_perf_cb_ctx.load());
-      if (g.perf_on.load(std::memory_order_relaxed)) {
-        std::lock_guard<std::mutex> l(g.perf_mu);
-        g.perf[rec].add(dt);
-      }
+      if (g.perf_on.load(std::memory_order_relaxed)) perf_record(rec, dt);
     }
   }
 };
@@ -1565,7 +1629,7 @@ int umq_stats_qbuf_pool_get(umq_qbuf_stats_t* out) {
 }
 int umq_stats_perf_start(void) {
   std::lock_guard<std::mutex> l(g.perf_mu);
-  for (auto& h : g.perf) h.reset();
+  perf_restart();
   g.perf_on = true;
   return UMQ_SUCCESS;
 }
@@ -1576,12 +1640,14 @@ int umq_stats_perf_stop(void) {
 int umq_stats_perf_get(umq_perf_entry_t* e) {
   if (!e) return UMQ_ERR_EINVAL;
   std::lock_guard<std::mutex> l(g.perf_mu);
+  static ub::PerfHist all[UMQ_PERF_RECORD_MAX];   // (under the lock; too large for the stack of a small thread)
+  perf_collect(all);
   for (int i = 0; i < UMQ_PERF_RECORD_MAX; ++i) {
-    e[i].count = g.perf[i].count();
-    e[i].avg_ns = static_cast<uint64_t>(g.perf[i].mean());
-    e[i].min_ns = g.perf[i].min();
-    e[i].max_ns = g.perf[i].max();
-    e[i].p99_ns = g.perf[i].quantile(0.99);
+    e[i].count = all[i].count();
+    e[i].avg_ns = static_cast<uint64_t>(all[i].mean());
+    e[i].min_ns = all[i].min();
+    e[i].max_ns = all[i].max();
+    e[i].p99_ns = all[i].quantile(0.99);
   }
   return UMQ_SUCCESS;
 }
@@ -1861,7 +1927,7 @@ int umq_stats_io_reset(uint64_t h) {
 }
 int umq_stats_perf_reset(void) {
   std::lock_guard<std::mutex> l(g.perf_mu);
-  for (auto& hst : g.perf) hst.reset();
+  perf_restart();
   return UMQ_SUCCESS;
 }
 int umq_io_stats_to_str(const umq_io_stats_t* s, char* buf, uint32_t len) {
