@@ -5,12 +5,19 @@
 // (src/urma/hw/udma: udma_u_jfs.c post_sq_wr / udma_u_jfc.c poll) and doubles as the fake device that the
 // reference's unit tests build with link-time mocks (test/urma/include/urma_hw_mock.h).
 //
-// Wire model: every context owns an "inbox", a bounded multi-producer ring in a shared-memory file. Initiators write
-// request messages (header + up to 4 KiB of payload per slot, larger transfers are fragmented) into the target's
-// inbox; the target's NIC thread executes them against the target process's memory after checking segment token,
-// bounds and access rights, and answers into the initiator's inbox; the initiator's NIC thread turns answers into
-// completion records. Pending requests carry a deadline, so a dead peer produces URMA_CR_ACK_TIMEOUT_ERR rather
-// than a hang.
+// Wire model: every context owns an "inbox" in a shared-memory file: four bounded multi-producer rings. Initiators
+// write request messages (header + up to 4 KiB of payload per slot, gathered straight into the slot; larger transfers
+// are fragmented) into the ring that the target jetty's number selects; whoever executes the target's inbox runs them
+// against the target process's memory after checking segment token, bounds and access rights, and answers into the
+// ring of the initiator that the asking send queue's number selects; executing those answers turns them into
+// completion records. Requests in flight live in a lock-free table and carry a deadline, so a dead peer produces
+// URMA_CR_ACK_TIMEOUT_ERR rather than a hang.
+//
+// Who executes an inbox: an application thread that polls an empty completion queue does it itself, inside the poll
+// (a message is then copied once, by the thread that is about to read it), and the context's own thread does it
+// whenever nobody has polled for a few microseconds (requests of peers must progress while the application sleeps
+// on a completion event or computes). Rings are executed concurrently, one consumer each; the operations that free
+// a queue wait until no message is being handled.
 #include <errno.h>
 #include <fcntl.h>
 #include <poll.h>
