@@ -30,6 +30,7 @@
 #include <deque>
 #include <map>
 #include <mutex>
+#include <optional>
 #include <thread>
 #include <unordered_map>
 #include <vector>
@@ -1250,16 +1251,20 @@ int urpc_server_poll_shard(uint32_t shard, uint32_t nshards, urpc_poll_msg_t* ms
    };
    Guard in_session(&s->users);
    if (s->closed.load()) continue;
-   std::vector<LanePtr> lanes(1);   // slot 0 stands for the first queue pair
+   // (a poll pass allocates nothing: the list is a per-thread vector that keeps its storage, a guard lives on the
+   // stack)
+   static thread_local std::vector<LanePtr> lanes;
+   lanes.clear();
+   lanes.emplace_back();   // slot 0 stands for the first queue pair
    {
      std::lock_guard<std::mutex> l(s->lanes_mu);
      lanes.insert(lanes.end(), s->extra.begin(), s->extra.end());
    }
    for (size_t li = 0; li < lanes.size(); ++li) {   // every queue pair of the session in turn
     Lane* ln = lanes[li].get();
-    std::unique_ptr<Guard> in_lane;
+    std::optional<Guard> in_lane;
     if (ln) {
-      in_lane.reset(new Guard(&ln->users));
+      in_lane.emplace(&ln->users);
       if (ln->closing.load()) continue;
     }
     const uint32_t lane = ln ? ln->id : 0;
@@ -1349,6 +1354,7 @@ int urpc_server_poll_shard(uint32_t shard, uint32_t nshards, urpc_poll_msg_t* ms
       }
     }
    }
+   lanes.clear();   // the pass holds no lane beyond its own end
   }
   return n;
 }
