@@ -1,5 +1,5 @@
 // urma_perftest: latency and bandwidth of URMA verbs (write / read / send / atomic) between two endpoints.
-//   urma_perftest [--stress THREADS] [--dev shm0|bond0|cudaN] [--peer-dev cudaM] [--op write|read|send|faa|cas] [--size N] [--iters N]
+//   urma_perftest [--stress THREADS] [--dev shm0|bond0|cudaN] [--peer-dev cudaM] [--mem cudaN] [--op write|read|send|faa|cas] [--size N] [--iters N]
 //                 [--depth N] [--duration SEC] [--jettys N] [--cq-mod N] [--rate-limit MB/s]
 //     --dev cudaN  the buffers live in the memory of GPU N (allocated through the CUDA runtime, loaded at run time);
 //                  --peer-dev cudaM puts the second endpoint of the in-process mode on GPU M (default: the same GPU)
@@ -234,7 +234,7 @@ static int stress(const std::string& dev, uint32_t threads, uint32_t rounds, uin
 }
 
 int main(int argc, char** argv) {
-  std::string dev = "shm0", peer_dev, op = "write", host = "127.0.0.1";
+  std::string dev = "shm0", peer_dev, op = "write", host = "127.0.0.1", mem;
   uint32_t size = 4096, iters = 20000, depth = 64;
   int server = -1, client = -1;
   uint32_t jettys = 1, cq_mod = 1;
@@ -249,6 +249,7 @@ int main(int argc, char** argv) {
     else if (!strcmp(argv[i], "--rate-limit") && i + 1 < argc) rate_mbs = atof(argv[++i]);
     else if (!strcmp(argv[i], "--dev") && i + 1 < argc) dev = argv[++i];
     else if (!strcmp(argv[i], "--peer-dev") && i + 1 < argc) peer_dev = argv[++i];
+    else if (!strcmp(argv[i], "--mem") && i + 1 < argc) mem = argv[++i];
     else if (!strcmp(argv[i], "--op") && i + 1 < argc) op = argv[++i];
     else if (!strcmp(argv[i], "--size") && i + 1 < argc) size = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--iters") && i + 1 < argc) iters = atoi(argv[++i]);
@@ -273,7 +274,10 @@ int main(int argc, char** argv) {
     uint8_t* p = nullptr;
     uint8_t* data() const { return p; }
   };
-  Buf mem_a{alloc_buf(dev, seg_bytes, 1)}, mem_b{alloc_buf(peer_dev, seg_bytes, 2)};
+  // where the buffers live: with the device by default; --mem cudaN puts them on a GPU whatever the device is called
+  // (a bond device whose paths are cudaN devices)
+  const std::string mem_a_dev = mem.empty() ? dev : mem, mem_b_dev = mem.empty() ? peer_dev : mem;
+  Buf mem_a{alloc_buf(mem_a_dev, seg_bytes, 1)}, mem_b{alloc_buf(mem_b_dev, seg_bytes, 2)};
   if (!mem_a.p || !mem_b.p) return fail("buffer allocation (for cudaN: is the CUDA runtime library on the loader path?)");
   urma_simple_ep_t* ea = urma_simple_ep_create(ctx, depth * 2, 1, 0);
   Blob mine{}, peer{};
@@ -341,7 +345,7 @@ int main(int argc, char** argv) {
   if (server >= 0) {  // passive side: keep receives posted until the client says goodbye
     std::vector<Buf> rb(depth);
     for (uint32_t i = 0; i < depth; ++i) {
-      rb[i].p = alloc_buf(dev, size, 0);
+      rb[i].p = alloc_buf(mem_a_dev, size, 0);
       if (!rb[i].p) return fail("receive buffer allocation");
       urma_simple_post_recv(ea, rb[i].data(), size, i);
     }
@@ -383,7 +387,7 @@ int main(int argc, char** argv) {
   if (two_sided && eb) {
     rb.resize(depth * 2);
     for (uint32_t i = 0; i < depth * 2; ++i) {
-      rb[i].p = alloc_buf(peer_dev, size, 0);
+      rb[i].p = alloc_buf(mem_b_dev, size, 0);
       if (!rb[i].p) return fail("receive buffer allocation");
       urma_simple_post_recv(eb, rb[i].data(), size, i);
     }
@@ -502,7 +506,7 @@ int main(int argc, char** argv) {
   }
   bool data_ok = true;
   if (!two_sided && !atomic && opc == URMA_OPC_WRITE && eb) {   // a write must have carried the source buffer over
-    const std::vector<uint8_t> ha = host_copy(dev, mem_a.data(), size), hb = host_copy(peer_dev, mem_b.data(), size);
+    const std::vector<uint8_t> ha = host_copy(mem_a_dev, mem_a.data(), size), hb = host_copy(mem_b_dev, mem_b.data(), size);
     data_ok = ha.size() == size && hb.size() == size && memcmp(ha.data(), hb.data(), size) == 0;
   }
   // tear down in the reverse order of the bring-up (imports, endpoints, segments, contexts)

@@ -117,3 +117,20 @@ def test_urma_perftest_between_two_gpus_uses_the_direct_path(tmp_path):
         if op != "faa":
             mbs = float(re.search(r"ops/s, ([0-9.]+) MB/s", p.stdout).group(1))
             assert mbs > 200e3, p.stdout   # 64 MiB copies: NVLink gives about 700 GB/s, the host path about 36 GB/s
+
+
+@pytest.mark.parametrize("op", ["write", "read", "faa"])
+def test_bond_device_over_gpu_paths(tmp_path, op):
+    """The multipath device with GPU paths (`BOND_DEVICES=cuda0,cuda0`: two contexts, two streams on the GPU) and
+    buffers in GPU memory: one-sided operations and atomics go through the bond layer's scheduling, store and
+    completion handling untouched by it (two-sided sends of the bond layer use host bounce buffers and stay on host
+    devices)."""
+    import os
+    import subprocess
+    from umdk_b200 import _native
+    tool = _native.lib_dir() / "bin" / "urma_perftest"
+    env = dict(os.environ, URMA_SHM_DIR=str(tmp_path / "urma"), BOND_DEVICES="cuda0,cuda0")
+    (tmp_path / "urma").mkdir(exist_ok=True)
+    args = [str(tool), "--dev", "bond0", "--mem", "cuda0", "--op", op, "--size", "65536", "--iters", "400"]
+    p = subprocess.run(args, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=180)
+    assert p.returncode == 0 and "urma_perftest: OK" in p.stdout and "errors 0" in p.stdout, p.stdout[-2000:]
