@@ -349,3 +349,60 @@ def test_sub_queues_share_receive_buffers_and_borrow_jetties(tmp_path):
         for q in made:
             q.close()
         umq.uninit()
+
+
+def test_call_latency_histograms_merge_over_threads_and_restart(pair):
+    """Latencies are recorded per thread: the report must add up what every thread recorded (also one that has ended
+    since), and a restart must forget all of it."""
+    import threading
+    umq, a, b = pair
+    lib = umq._lib()
+
+    class Entry(ctypes.Structure):
+        _fields_ = [(n, ctypes.c_uint64) for n in ("count", "avg_ns", "min_ns", "max_ns", "p99_ns")]
+    ent = (Entry * 5)()
+
+    def enqueue_count():
+        assert lib.umq_stats_perf_get(ent) == 0
+        return int(ent[0].count)   # UMQ_PERF_ENQUEUE
+
+    got = []
+    stop = threading.Event()
+
+    def drain():                       # the receiver returns credits while the senders run
+        while not stop.is_set():
+            m = b.recv(timeout_s=0.05)
+            if m is not None:
+                got.append(m)
+
+    rx = threading.Thread(target=drain)
+    rx.start()
+    try:
+        assert lib.umq_stats_perf_start() == 0
+        assert enqueue_count() == 0
+
+        def sender(n):
+            for i in range(n):
+                a.send(b"t%d" % i)
+
+        workers = [threading.Thread(target=sender, args=(20,)) for _ in range(3)]
+        for t in workers:
+            t.start()
+        for t in workers:
+            t.join()                   # the threads are gone: their counts must not be
+        sender(5)                      # ... and this thread's come on top
+        for _ in range(200):
+            if len(got) >= 65:
+                break
+            stop.wait(0.025)
+        assert len(got) == 65
+        assert enqueue_count() == 65 and ent[0].max_ns >= ent[0].min_ns > 0
+        assert lib.umq_stats_perf_reset() == 0 and enqueue_count() == 0
+        a.send(b"after")
+        assert enqueue_count() == 1
+        assert lib.umq_stats_perf_stop() == 0
+        a.send(b"unseen")
+        assert enqueue_count() == 1
+    finally:
+        stop.set()
+        rx.join()
