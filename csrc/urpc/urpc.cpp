@@ -65,7 +65,10 @@ struct Pending {
   bool sync = false;
   bool done = false;
   int status = 0;
-  std::vector<uint8_t> rsp;
+  // A synchronous caller waits inside urpc_func_call with its answer buffer at hand: the answer is copied straight
+  // there by whichever thread polls the channel (under the channel's lock), once.
+  void* sync_buf = nullptr;
+  uint32_t sync_cap = 0, rsp_len = 0;
 };
 struct Ready {
   urpc_poll_event_t ev;
@@ -501,7 +504,9 @@ void channel_progress(Channel* ch) {
       record(URPC_PERF_CALL_TO_RESPONSE, took);
     }
     if (p.sync) {
-      p.rsp.assign(b->buf_data + sizeof(urpc_req_head_t), b->buf_data + b->data_size);
+      p.rsp_len = b->data_size - static_cast<uint32_t>(sizeof(urpc_req_head_t));
+      if (p.sync_buf && p.rsp_len)
+        memcpy(p.sync_buf, b->buf_data + sizeof(urpc_req_head_t), std::min(p.rsp_len, p.sync_cap));
       p.status = r.status;
       p.done = true;
       umq_buf_free(b);
@@ -1550,6 +1555,10 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
     p.t0 = ub::now_ns();
     p.deadline = p.t0 + uint64_t(tmo) * 1000000ull;
     p.sync = opt && opt->sync;
+    if (p.sync) {
+      p.sync_buf = opt->rsp_buf;
+      p.sync_cap = opt->rsp_buf ? opt->rsp_buf_len : 0;
+    }
     // version 1 always set the bit (and nobody acted on it); version 2 sets it when the caller wants the event
     p.want_ack = opt && opt->want_ack && (ch->proto.caps & urpc_proto::kCapAck);
     const uint8_t ackbit = (ch->proto.version < 2 || p.want_ack) ? 1 : 0;
@@ -1588,11 +1597,7 @@ int urpc_func_call(uint32_t chid, const urpc_call_wr_t* wr, const urpc_call_opti
       if (it == ch->pending.end()) return URPC_FAIL;
       if (it->second.done) {
         const int st = it->second.status;
-        if (st == 0 && opt->rsp_buf) {
-          const uint32_t n = std::min<uint32_t>(opt->rsp_buf_len, it->second.rsp.size());
-          memcpy(opt->rsp_buf, it->second.rsp.data(), n);
-          if (opt->rsp_len) *opt->rsp_len = static_cast<uint32_t>(it->second.rsp.size());
-        }
+        if (st == 0 && opt->rsp_len) *opt->rsp_len = it->second.rsp_len;   // (the bytes are in rsp_buf already)
         ch->pending.erase(it);
         return st;
       }
