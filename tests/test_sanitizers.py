@@ -42,7 +42,8 @@ def test_address_and_leak_sanitizer_clean(tmp_path):
 @needs_gxx
 def test_thread_sanitizer_clean(tmp_path):
     outs = _build.build_sanitized("thread", only=_build.HOST_LIBS + ("tool_umq_perftest", "tool_urpc_perftest",
-                                                                      "tool_ums_perftest", "tool_urma_perftest"))
+                                                                      "tool_ums_perftest", "tool_urma_perftest",
+                                                                      "tool_dlock_example"))
     # the shared-memory device with four threads at once: sends of one slot and of several fragments, writes, reads
     # and atomics, executed by the contexts' own threads and by the polling threads themselves (and by the contexts'
     # threads alone)
@@ -67,3 +68,9 @@ def test_thread_sanitizer_clean(tmp_path):
     assert rc == 0 and ": OK" in out and "ThreadSanitizer" not in out, out[-3000:]
     rc, out = _run(outs["tool_ums_perftest"], ["--selftest", "--iters", "300"], tmp_path, ums_env)
     assert rc == 0 and "ums_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
+    # several connections at once: every thread keeps its own view of the connection table
+    rc, out = _run(outs["tool_ums_perftest"], ["--conns", "4", "--iters", "300"], tmp_path, ums_env)
+    assert rc == 0 and "ums_perftest: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
+    # lock service: three clients in parallel against the command thread, then the self-test with its restart
+    rc, out = _run(outs["tool_dlock_example"], ["--clients", "3", "--iters", "300"], tmp_path)
+    assert rc == 0 and "dlock_example: OK" in out and "ThreadSanitizer" not in out, out[-3000:]
