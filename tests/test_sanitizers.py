@@ -26,7 +26,8 @@ needs_gxx = pytest.mark.skipif(not os.path.exists("/usr/bin/g++") and shutil.whi
 
 @needs_gxx
 def test_address_and_leak_sanitizer_clean(tmp_path):
-    outs = _build.build_sanitized("address")
+    outs = _build.build_sanitized("address", only=_build.HOST_LIBS + (
+        "tool_umq_perftest", "tool_urpc_perftest", "tool_urma_perftest", "tool_urma_raw_sample", "tool_dlock_example"))
     rc, out = _run(outs["tool_umq_perftest"], ["--iters", "500", "--flow-control"], tmp_path)
     assert rc == 0 and "umq_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
     # self-test flavour: huge buffers, sub queues over the jetty pool, a pulled large message
@@ -37,6 +38,14 @@ def test_address_and_leak_sanitizer_clean(tmp_path):
     assert rc == 0 and "urpc_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
     rc, out = _run(outs["tool_urpc_perftest"], ["--iters", "600", "--queues", "3"], tmp_path)   # three queue pairs
     assert rc == 0 and "urpc_perftest: OK" in out and "Sanitizer" not in out, out[-3000:]
+    # the shared-memory device itself: four threads of mixed traffic (rings of requests, the table of requests in
+    # flight, messages reassembled in the posted buffers), the raw-API walk-through, and the lock service
+    rc, out = _run(outs["tool_urma_perftest"], ["--stress", "4", "--iters", "500", "--size", "4096"], tmp_path)
+    assert rc == 0 and "all data verified" in out and "Sanitizer" not in out, out[-3000:]
+    rc, out = _run(outs["tool_urma_raw_sample"], [], tmp_path)
+    assert rc == 0 and "urma_raw_sample: OK" in out and "Sanitizer" not in out, out[-3000:]
+    rc, out = _run(outs["tool_dlock_example"], ["--selftest", "--iters", "500"], tmp_path)
+    assert rc == 0 and "dlock_example: OK" in out and "Sanitizer" not in out, out[-3000:]
 
 
 @needs_gxx
